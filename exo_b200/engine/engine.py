@@ -1,0 +1,154 @@
+"""Token-level inference engine: scheduler + executor behind ``submit`` / ``step``.
+
+This is the object a runner process drives; it has the same call surface the reference
+gives its engines (``src/exo/worker/engines/base.py:16-60``: warmup / submit / step / close),
+working on token ids — tokenisation, chat templates and output parsing live above it.
+"""
+from __future__ import annotations
+
+import time
+import uuid
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..models.config import ModelConfig
+from ..models.weights import ModelWeights, ShardSpec
+from ..ops import reference as ref
+from .executor import Executor
+from .kv import BlockAllocator, SamplingParams, Sequence
+from .plan import StepPlan
+from .scheduler import Scheduler
+
+
+@dataclass
+class StepOutput:
+    req_id: str
+    token: int | None          # None while the request is still prefilling
+    finished: bool
+    finish_reason: str | None
+    n_prompt: int
+    n_generated: int
+    n_cached: int
+    logprob: float | None = None
+    top_logprobs: list[tuple[int, float]] | None = None
+    prefill_done: int = 0      # prompt tokens processed so far (for progress reporting)
+
+
+class Engine:
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None = None, comm=None,
+                 n_blocks: int = 512, block_size: int = 16, max_seqs: int = 64, prefill_chunk: int = 4096,
+                 max_blocks_per_seq: int | None = None, device: str | torch.device = "cpu",
+                 use_graphs: bool | None = None, seed: int = 0, plan_sink=None):
+        self.cfg = cfg
+        mbs = max_blocks_per_seq or min(n_blocks, -(-cfg.max_position // block_size))
+        self.alloc = BlockAllocator(n_blocks, block_size)
+        self.scratch_block = self.alloc.alloc()  # block 0: target of padded rows, never read
+        assert self.scratch_block == 0
+        self.sched = Scheduler(self.alloc, max_seqs=max_seqs, prefill_chunk=prefill_chunk, max_blocks_per_seq=mbs,
+                               eos_token_ids=cfg.eos_token_ids, max_context=cfg.max_position, seed=seed)
+        self.exe = Executor(cfg, weights, spec, comm, n_blocks=n_blocks, block_size=block_size,
+                            max_blocks_per_seq=mbs, max_tokens_per_step=max(prefill_chunk, max_seqs),
+                            max_seqs=max_seqs, device=device, use_graphs=use_graphs)
+        self.seqs: dict[str, Sequence] = {}
+        self.plan_sink = plan_sink  # callable(StepPlan): broadcasts the plan to follower ranks
+        self.n_steps = 0
+
+    # ---- requests ----
+    def submit(self, prompt: list[int], params: SamplingParams | None = None, req_id: str | None = None,
+               use_prefix_cache: bool = True, media=None) -> str:
+        rid = req_id or uuid.uuid4().hex
+        if not prompt:
+            raise ValueError("empty prompt")
+        s = Sequence(rid, list(prompt), params or SamplingParams(), media=media, use_prefix_cache=use_prefix_cache)
+        self.seqs[rid] = s
+        self.sched.add(s)
+        return rid
+
+    def cancel(self, req_id: str) -> bool:
+        ok = self.sched.cancel(req_id)
+        self.seqs.pop(req_id, None)
+        return ok
+
+    @property
+    def has_work(self) -> bool:
+        return self.sched.has_work
+
+    # ---- stepping ----
+    def _processor(self, entries):
+        """Logits processor for steps where some sequence wants penalties."""
+        seqs = [s for s, _ in entries]
+        if not any(s.params.has_penalties for s in seqs):
+            return None
+        V = self.cfg.vocab
+
+        def proc(logits: torch.Tensor) -> torch.Tensor:
+            counts = torch.zeros(len(seqs), V, device=logits.device)
+            for b, s in enumerate(seqs):
+                if s.params.has_penalties and s.output:
+                    idx = torch.tensor(s.output, device=logits.device)
+                    counts[b].index_add_(0, idx, torch.ones(len(s.output), device=logits.device))
+            rep = torch.tensor([s.params.repetition_penalty for s in seqs], device=logits.device)
+            pres = torch.tensor([s.params.presence_penalty for s in seqs], device=logits.device)
+            freq = torch.tensor([s.params.frequency_penalty for s in seqs], device=logits.device)
+            return ref.apply_penalties(logits, counts, rep, pres, freq)
+        return proc
+
+    def step(self) -> list[StepOutput]:
+        plan, entries = self.sched.schedule()
+        if plan is None:
+            return []
+        if self.plan_sink is not None:
+            self.plan_sink(plan)
+        want_lp = any(s.params.logprobs for s, _ in entries)
+        proc = self._processor(entries)
+        if want_lp and proc is None:
+            proc = lambda x: x  # noqa: E731 - forces the eager path that keeps logits
+        ids = self.exe.run(plan, proc)
+        sampled = self.exe.fetch(ids)
+        lp = None
+        if want_lp:
+            k = max(1, max(s.params.top_logprobs for s, _ in entries))
+            chosen = torch.as_tensor(sampled, device=self.exe.last_logits.device)
+            lp = tuple(t.cpu() for t in ref.top_logprobs(self.exe.last_logits[:len(entries)], chosen, k))
+        self.n_steps += 1
+        outs: list[StepOutput] = []
+        for b, (s, tok) in enumerate(self.sched.commit(entries, sampled)):
+            o = StepOutput(s.req_id, tok, s.finished, s.finish_reason, len(s.prompt), len(s.output),
+                           s.n_cached_prefix, prefill_done=min(s.n_computed, len(s.prompt)))
+            if lp is not None and tok is not None and s.params.logprobs:
+                row = [e[0].req_id for e in entries].index(s.req_id)
+                o.logprob = float(lp[0][row])
+                o.top_logprobs = [(int(i), float(v)) for v, i in zip(lp[1][row], lp[2][row])][:s.params.top_logprobs]
+            outs.append(o)
+            if s.finished:
+                self.seqs.pop(s.req_id, None)
+        return outs
+
+    def generate(self, prompt: list[int], params: SamplingParams | None = None) -> list[int]:
+        """Convenience: run one request to completion and return its generated ids."""
+        rid = self.submit(prompt, params, use_prefix_cache=False)
+        out: list[int] = []
+        while True:
+            for o in self.step():
+                if o.req_id == rid:
+                    if o.token is not None:
+                        out.append(o.token)
+                    if o.finished:
+                        return out
+
+    def warmup(self, n_tokens: int = 8) -> float:
+        t0 = time.perf_counter()
+        self.generate([1, 2, 3, 4], SamplingParams(temperature=0.0, max_tokens=n_tokens, ignore_eos=True))
+        return time.perf_counter() - t0
+
+
+class FollowerEngine:
+    """Non-leader rank: executes the plans the leader broadcasts, keeps no request state."""
+
+    def __init__(self, executor: Executor):
+        self.exe = executor
+
+    def run_plan(self, plan: StepPlan) -> None:
+        self.exe.run(plan)

@@ -1,0 +1,142 @@
+"""Per-rank step executor: turns a packed StepPlan into kernel launches.
+
+One executor lives in each GPU process.  A step is: one host→device copy of the packed
+plan from pinned memory, the decoder forward over this rank's shard, the vocabulary gather,
+sampling on device, and one device→host copy of the sampled ids.  Pure-decode steps (one new
+token per sequence) replay a CUDA graph captured per batch bucket, so the per-step host cost
+is one memcpy and one graph launch.  This is the role the reference gives to mlx-lm's
+``BatchGenerator`` step with its one-step-ahead ``async_eval`` pipelining
+(``src/exo/worker/engines/mlx/patches/opt_batch_gen.py:57-136``).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.config import ModelConfig
+from ..models.transformer import Decoder, KVPool, StepInputs
+from ..models.weights import ModelWeights, ShardSpec
+from .plan import HEADER, PlanLayout, StepPlan, bucket, FLAG_ALL_GREEDY
+
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+class Executor:
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None = None, comm=None,
+                 n_blocks: int = 256, block_size: int = 16, max_blocks_per_seq: int = 256,
+                 max_tokens_per_step: int = 4096, max_seqs: int = 64, device: str | torch.device = "cpu",
+                 use_graphs: bool | None = None):
+        self.cfg = cfg
+        self.spec = spec or ShardSpec()
+        self.device = torch.device(device)
+        self.model = Decoder(cfg, weights, self.spec, comm)
+        self.kv = KVPool(cfg, self.spec, n_blocks, block_size, self.device)
+        self.block_size, self.max_blocks = block_size, max_blocks_per_seq
+        self.max_T, self.max_B = max_tokens_per_step, max_seqs
+        words = PlanLayout(max(self.max_T, self.max_B), self.max_B, self.max_blocks).words
+        self.cuda = self.device.type == "cuda"
+        self.host = torch.zeros(words, dtype=torch.int32, pin_memory=self.cuda)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(words, dtype=torch.int32, device=self.device)
+        self.use_graphs = self.cuda if use_graphs is None else use_graphs
+        self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self.out_host = torch.zeros(self.max_B, dtype=torch.int32, pin_memory=self.cuda)
+        self.prev_sampled = torch.zeros(max(self.max_B, 256), dtype=torch.int32, device=self.device)
+        self.last_logits: torch.Tensor | None = None
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.n_launch_steps = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _views(self, L: PlanLayout) -> tuple[StepInputs, dict[str, torch.Tensor]]:
+        d = self.dev
+        f = d.view(torch.float32)
+        inp = StepInputs(
+            tokens=d[L.tokens:L.tokens + L.T], positions=d[L.positions:L.positions + L.T],
+            slots=d[L.slots:L.slots + L.T], cu_q=d[L.cu_q:L.cu_q + L.B + 1], seq_lens=d[L.seq_lens:L.seq_lens + L.B],
+            block_tables=d[L.block_tables:L.block_tables + L.B * L.max_blocks].view(L.B, L.max_blocks),
+            logit_rows=d[L.logit_rows:L.logit_rows + L.B], max_q_len=1)
+        samp = dict(top_k=d[L.top_k:L.top_k + L.B], temperature=f[L.temperature:L.temperature + L.B],
+                    top_p=f[L.top_p:L.top_p + L.B], min_p=f[L.min_p:L.min_p + L.B],
+                    uniform=f[L.uniform:L.uniform + L.B], prev_rows=d[L.prev_rows:L.prev_rows + L.B])
+        return inp, samp
+
+    def _forward_sample(self, inp: StepInputs, samp: dict[str, torch.Tensor], greedy: bool,
+                        from_prev: bool) -> torch.Tensor:
+        if from_prev:
+            # decode continuation: input token of row b = previous step's sample at prev_rows[b]
+            pr = samp["prev_rows"]
+            prev = self.prev_sampled[pr.clamp_min(0).long()]
+            inp.tokens.copy_(torch.where(pr >= 0, prev, inp.tokens))
+        logits = self.model.comm.gather_vocab(self.model.forward(inp, self.kv))
+        self.last_logits = logits
+        if greedy:
+            ids = ops.argmax(logits[:, :self.cfg.vocab])
+        else:
+            ids = ops.sample(logits[:, :self.cfg.vocab], samp["temperature"], samp["top_k"], samp["top_p"],
+                             samp["min_p"], samp["uniform"])
+        ids = ids.to(torch.int32)
+        self.prev_sampled[:ids.numel()].copy_(ids)
+        return ids
+
+    # ------------------------------------------------------------------ step
+    def run(self, plan: StepPlan, logits_processor=None) -> torch.Tensor:
+        """Execute one step; returns the sampled ids ``[n_seqs]`` on device (int32)."""
+        decode = plan.is_decode
+        if decode:
+            bB = bucket(plan.n_seqs, DECODE_BUCKETS)
+            bT = bB
+        else:
+            bB, bT = plan.n_seqs, plan.n_tokens
+        mb = self.max_blocks if decode else max(1, plan.block_tables.shape[1])
+        L = plan.pack(self.host_np, bT, bB, mb)
+        self.dev[:L.words].copy_(self.host[:L.words], non_blocking=True)
+        self.h2d_bytes += L.words * 4
+        greedy = bool(plan.flags & FLAG_ALL_GREEDY)
+        from_prev = bool(plan.flags & 1)
+        self.n_launch_steps += 1
+        if decode and self.use_graphs and logits_processor is None:
+            key = (bB, greedy, from_prev)
+            if key not in self.graphs:
+                self._capture(key, L)
+            g, out = self.graphs[key]
+            g.replay()
+            return out[:plan.n_seqs]
+        inp, samp = self._views(L)
+        inp.max_q_len = plan.max_q_len
+        if logits_processor is None:
+            return self._forward_sample(inp, samp, greedy, from_prev)[:plan.n_seqs]
+        # slow path (penalties / logit bias / logprobs): processor edits full logits before sampling
+        logits = self.model.comm.gather_vocab(self.model.forward(inp, self.kv))[:, :self.cfg.vocab]
+        logits = logits_processor(logits[:plan.n_seqs].float())
+        self.last_logits = logits
+        ids = ops.sample(logits, samp["temperature"][:plan.n_seqs], samp["top_k"][:plan.n_seqs],
+                         samp["top_p"][:plan.n_seqs], samp["min_p"][:plan.n_seqs],
+                         samp["uniform"][:plan.n_seqs]).to(torch.int32)
+        self.prev_sampled[:ids.numel()].copy_(ids)
+        return ids
+
+    def _capture(self, key: tuple[int, bool, bool], L: PlanLayout) -> None:
+        bB, greedy, from_prev = key
+        inp, samp = self._views(L)
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):  # warm-up outside capture (lazy inits, autotune-free)
+            for _ in range(2):
+                self._forward_sample(inp, samp, greedy, from_prev)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            out = self._forward_sample(inp, samp, greedy, from_prev)
+        self.graphs[key] = (g, out)
+
+    def fetch(self, ids: torch.Tensor) -> np.ndarray:
+        """Blocking device→host read of a step's sampled ids."""
+        n = ids.numel()
+        self.out_host[:n].copy_(ids, non_blocking=True)
+        if self.cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        self.d2h_bytes += n * 4
+        return self.out_host[:n].numpy().copy()

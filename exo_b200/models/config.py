@@ -1,0 +1,261 @@
+"""Model architecture description shared by every engine component.
+
+One flat dataclass covers the decoder families the framework serves: dense
+Llama-style (Llama, Mistral, Qwen2/3 dense), softmax-routed MoE (Qwen3-MoE),
+and DeepSeek-V3-style MLA + sigmoid-routed MoE.  It is built either from a
+HuggingFace ``config.json`` (the checkpoint format the reference consumes, see
+``src/exo/shared/models/model_cards.py:265-339`` in the reference for the alias
+handling this mirrors) or from one of the named presets used by the benchmarks.
+"""
+from __future__ import annotations
+
+import json
+import math
+from dataclasses import dataclass, field, asdict
+from pathlib import Path
+from typing import Any
+
+
+@dataclass
+class RopeConfig:
+    theta: float = 10000.0
+    kind: str = "default"  # default | linear | llama3 | yarn
+    factor: float = 1.0
+    low_freq_factor: float = 1.0
+    high_freq_factor: float = 4.0
+    original_max_position: int = 8192
+    beta_fast: float = 32.0
+    beta_slow: float = 1.0
+    mscale: float = 1.0
+    mscale_all_dim: float = 0.0
+    partial_rotary_factor: float = 1.0
+
+
+@dataclass
+class ModelConfig:
+    name: str = "model"
+    family: str = "llama"  # llama | qwen3 | qwen3_moe | deepseek_v3 | gpt_oss
+    n_layers: int = 2
+    hidden: int = 256
+    n_heads: int = 4
+    n_kv_heads: int = 2
+    head_dim: int = 64
+    ffn: int = 688
+    vocab: int = 32000
+    rms_eps: float = 1e-5
+    rope: RopeConfig = field(default_factory=RopeConfig)
+    tie_embeddings: bool = False
+    qk_norm: bool = False  # per-head RMSNorm on q and k (Qwen3)
+    attn_bias: bool = False
+    max_position: int = 131072
+    dtype: str = "bf16"  # bf16 | fp32
+    # weight storage format of the linear layers
+    quant: str = "none"  # none | mxfp8 (1x32 e8m0) | dsfp8 (128x128 blocks)
+    # ---- MoE ----
+    n_experts: int = 0
+    n_experts_per_tok: int = 0
+    moe_ffn: int = 0
+    n_shared_experts: int = 0
+    first_dense_layers: int = 0  # leading layers that keep a dense FFN
+    router: str = "softmax"  # softmax | sigmoid
+    norm_topk_prob: bool = True
+    routed_scaling: float = 1.0
+    n_group: int = 1
+    topk_group: int = 1
+    router_bias: bool = False
+    # ---- MLA ----
+    mla: bool = False
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_dim: int = 0
+    qk_rope_dim: int = 0
+    v_head_dim: int = 0
+    # ---- sliding window / sinks (GPT-OSS class) ----
+    sliding_window: int = 0
+    attn_sinks: bool = False
+    eos_token_ids: tuple[int, ...] = ()
+
+    # -------- derived --------
+    @property
+    def q_dim(self) -> int:
+        return self.n_heads * (self.head_dim if not self.mla else self.qk_nope_dim + self.qk_rope_dim)
+
+    @property
+    def kv_dim(self) -> int:
+        return self.n_kv_heads * self.head_dim
+
+    @property
+    def is_moe(self) -> bool:
+        return self.n_experts > 0
+
+    def layer_is_moe(self, i: int) -> bool:
+        return self.is_moe and i >= self.first_dense_layers
+
+    @property
+    def kv_bytes_per_token_per_layer(self) -> int:
+        el = 2 if self.dtype == "bf16" else 4
+        if self.mla:
+            return (self.kv_lora_rank + self.qk_rope_dim) * el
+        return 2 * self.n_kv_heads * self.head_dim * el
+
+    def param_count(self) -> int:
+        h = self.hidden
+        attn = h * self.q_dim + 2 * h * self.kv_dim + self.n_heads * self.head_dim * h
+        if self.mla:
+            qk = self.qk_nope_dim + self.qk_rope_dim
+            attn = (h * self.q_lora_rank + self.q_lora_rank * self.n_heads * qk
+                    + h * (self.kv_lora_rank + self.qk_rope_dim)
+                    + self.kv_lora_rank * self.n_heads * (self.qk_nope_dim + self.v_head_dim)
+                    + self.n_heads * self.v_head_dim * h)
+        total = 0
+        for i in range(self.n_layers):
+            total += attn + 2 * h
+            if self.layer_is_moe(i):
+                total += self.n_experts * 3 * h * self.moe_ffn + h * self.n_experts
+                total += self.n_shared_experts * 3 * h * self.moe_ffn
+            else:
+                total += 3 * h * self.ffn
+        total += self.vocab * h * (1 if self.tie_embeddings else 2) + h
+        return total
+
+    def weight_bytes(self) -> int:
+        per = {"none": 2.0 if self.dtype == "bf16" else 4.0, "mxfp8": 1.0 + 1 / 32, "dsfp8": 1.0 + 4 / (128 * 128)}[self.quant]
+        return int(self.param_count() * per)
+
+    def to_dict(self) -> dict[str, Any]:
+        return asdict(self)
+
+    # -------- constructors --------
+    @staticmethod
+    def from_hf(cfg: dict[str, Any], name: str = "model") -> "ModelConfig":
+        """Build from a HuggingFace ``config.json`` dict (text_config is unwrapped)."""
+        if "text_config" in cfg and isinstance(cfg["text_config"], dict):
+            inner = dict(cfg["text_config"])
+            inner.setdefault("model_type", cfg.get("model_type", "llama"))
+            cfg = inner
+        mt = cfg.get("model_type", "llama")
+
+        def g(*names: str, default: Any = None) -> Any:
+            for n in names:
+                if n in cfg and cfg[n] is not None:
+                    return cfg[n]
+            return default
+
+        hidden = g("hidden_size", "n_embd", "d_model")
+        n_heads = g("num_attention_heads", "n_head")
+        n_kv = g("num_key_value_heads", default=n_heads)
+        head_dim = g("head_dim", default=hidden // n_heads)
+        rope_scaling = g("rope_scaling", default=None) or {}
+        kind = rope_scaling.get("rope_type", rope_scaling.get("type", "default"))
+        rope = RopeConfig(
+            theta=float(g("rope_theta", default=10000.0)),
+            kind=kind if kind in ("default", "linear", "llama3", "yarn") else "default",
+            factor=float(rope_scaling.get("factor", 1.0)),
+            low_freq_factor=float(rope_scaling.get("low_freq_factor", 1.0)),
+            high_freq_factor=float(rope_scaling.get("high_freq_factor", 4.0)),
+            original_max_position=int(rope_scaling.get("original_max_position_embeddings", 8192)),
+            beta_fast=float(rope_scaling.get("beta_fast", 32.0)),
+            beta_slow=float(rope_scaling.get("beta_slow", 1.0)),
+            mscale=float(rope_scaling.get("mscale", 1.0)),
+            mscale_all_dim=float(rope_scaling.get("mscale_all_dim", 0.0)),
+            partial_rotary_factor=float(g("partial_rotary_factor", default=1.0)),
+        )
+        eos = g("eos_token_id", default=())
+        if isinstance(eos, int):
+            eos = (eos,)
+        family = {"llama": "llama", "mistral": "llama", "qwen2": "llama", "qwen3": "qwen3",
+                  "qwen3_moe": "qwen3_moe", "deepseek_v3": "deepseek_v3", "deepseek_v32": "deepseek_v3",
+                  "kimi_k2": "deepseek_v3", "gpt_oss": "gpt_oss"}.get(mt, "llama")
+        mc = ModelConfig(
+            name=name, family=family,
+            n_layers=g("num_hidden_layers", "n_layer"), hidden=hidden, n_heads=n_heads,
+            n_kv_heads=n_kv, head_dim=head_dim,
+            ffn=g("intermediate_size", default=4 * hidden), vocab=g("vocab_size"),
+            rms_eps=float(g("rms_norm_eps", default=1e-5)), rope=rope,
+            tie_embeddings=bool(g("tie_word_embeddings", default=False)),
+            qk_norm=family in ("qwen3", "qwen3_moe"),
+            attn_bias=bool(g("attention_bias", default=mt == "qwen2")),
+            max_position=int(g("max_position_embeddings", default=131072)),
+            eos_token_ids=tuple(eos),
+            sliding_window=int(g("sliding_window", default=0) or 0) if mt == "gpt_oss" else 0,
+            attn_sinks=mt == "gpt_oss",
+        )
+        if family == "qwen3_moe":
+            mc.n_experts = g("num_experts")
+            mc.n_experts_per_tok = g("num_experts_per_tok")
+            mc.moe_ffn = g("moe_intermediate_size")
+            mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
+            mc.router = "softmax"
+        if family == "deepseek_v3":
+            mc.mla = True
+            mc.q_lora_rank = g("q_lora_rank", default=0) or 0
+            mc.kv_lora_rank = g("kv_lora_rank")
+            mc.qk_nope_dim = g("qk_nope_head_dim")
+            mc.qk_rope_dim = g("qk_rope_head_dim")
+            mc.v_head_dim = g("v_head_dim")
+            mc.n_experts = g("n_routed_experts", default=0)
+            mc.n_experts_per_tok = g("num_experts_per_tok", default=0)
+            mc.moe_ffn = g("moe_intermediate_size", default=0)
+            mc.n_shared_experts = g("n_shared_experts", default=0) or 0
+            mc.first_dense_layers = g("first_k_dense_replace", default=0)
+            mc.router = "sigmoid" if g("scoring_func", default="sigmoid") == "sigmoid" else "softmax"
+            mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
+            mc.routed_scaling = float(g("routed_scaling_factor", default=1.0))
+            mc.n_group = g("n_group", default=1) or 1
+            mc.topk_group = g("topk_group", default=1) or 1
+            mc.router_bias = True
+            mc.head_dim = mc.qk_nope_dim + mc.qk_rope_dim
+        return mc
+
+    @staticmethod
+    def from_pretrained(path: str | Path) -> "ModelConfig":
+        p = Path(path)
+        with open(p / "config.json") as f:
+            return ModelConfig.from_hf(json.load(f), name=p.name)
+
+
+def yarn_mscale(scale: float, mscale: float) -> float:
+    return 1.0 if scale <= 1 else 0.1 * mscale * math.log(scale) + 1.0
+
+
+# ----------------------------------------------------------------------------
+# Named presets: the architectures the benchmark configs are quoted on.
+# ----------------------------------------------------------------------------
+def preset(name: str) -> ModelConfig:
+    n = name.lower()
+    if n in ("tiny-llama", "tiny"):
+        return ModelConfig(name="tiny-llama", family="llama", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2,
+                           head_dim=64, ffn=688, vocab=32000, rms_eps=1e-5, rope=RopeConfig(theta=10000.0),
+                           dtype="fp32")
+    if n in ("llama-3.1-8b", "llama8b"):
+        return ModelConfig(name="llama-3.1-8b", family="llama", n_layers=32, hidden=4096, n_heads=32, n_kv_heads=8,
+                           head_dim=128, ffn=14336, vocab=128256, rope=RopeConfig(theta=500000.0))
+    if n in ("llama-3.1-70b", "llama70b"):
+        return ModelConfig(name="llama-3.1-70b", family="llama", n_layers=80, hidden=8192, n_heads=64, n_kv_heads=8,
+                           head_dim=128, ffn=28672, vocab=128256, rope=RopeConfig(theta=500000.0), quant="mxfp8")
+    if n in ("qwen3-235b-a22b", "qwen3-235b"):
+        return ModelConfig(name="qwen3-235b-a22b", family="qwen3_moe", n_layers=94, hidden=4096, n_heads=64,
+                           n_kv_heads=4, head_dim=128, ffn=12288, vocab=151936, rms_eps=1e-6,
+                           rope=RopeConfig(theta=1000000.0), qk_norm=True, n_experts=128, n_experts_per_tok=8,
+                           moe_ffn=1536, router="softmax", quant="mxfp8")
+    if n in ("deepseek-v3", "deepseek-v3-671b"):
+        return ModelConfig(name="deepseek-v3", family="deepseek_v3", n_layers=61, hidden=7168, n_heads=128,
+                           n_kv_heads=128, head_dim=192, ffn=18432, vocab=129280, rms_eps=1e-6,
+                           rope=RopeConfig(theta=10000.0), mla=True, q_lora_rank=1536, kv_lora_rank=512,
+                           qk_nope_dim=128, qk_rope_dim=64, v_head_dim=128, n_experts=256, n_experts_per_tok=8,
+                           moe_ffn=2048, n_shared_experts=1, first_dense_layers=3, router="sigmoid",
+                           routed_scaling=2.5, n_group=8, topk_group=4, router_bias=True, quant="dsfp8")
+    if n in ("tiny-moe",):
+        return ModelConfig(name="tiny-moe", family="qwen3_moe", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2,
+                           head_dim=64, ffn=512, vocab=1024, qk_norm=True, n_experts=8, n_experts_per_tok=2,
+                           moe_ffn=128, router="softmax", dtype="fp32")
+    if n in ("tiny-mla",):
+        return ModelConfig(name="tiny-mla", family="deepseek_v3", n_layers=3, hidden=256, n_heads=4, n_kv_heads=4,
+                           head_dim=48, ffn=512, vocab=1024, mla=True, q_lora_rank=64, kv_lora_rank=32,
+                           qk_nope_dim=32, qk_rope_dim=16, v_head_dim=32, n_experts=8, n_experts_per_tok=2,
+                           moe_ffn=128, n_shared_experts=1, first_dense_layers=1, router="sigmoid",
+                           routed_scaling=1.5, n_group=2, topk_group=1, router_bias=True, dtype="fp32")
+    raise KeyError(f"unknown preset {name!r}")
+
+
+PRESETS = ("tiny-llama", "llama-3.1-8b", "llama-3.1-70b", "qwen3-235b-a22b", "deepseek-v3", "tiny-moe", "tiny-mla")

@@ -1,0 +1,193 @@
+"""The decoder forward pass for one rank's shard, written as a flat sequence of hot ops.
+
+There is no ``nn.Module`` tree: a step is a fixed list of kernel launches over the shard's
+weight tensors and a paged KV pool, which is what a CUDA graph captures on the decode path.
+The same function serves prefill chunks (many tokens per sequence) and decode (one token per
+sequence) because the attention op takes ragged query lengths.
+
+Per-layer structure and collective placement follow the reference's tensor-parallel layer
+(``src/exo/worker/engines/mlx/auto_parallel.py:628-652`` Llama, ``:688-767`` DeepSeek MLA and
+MoE, ``:1121-1283`` Qwen3-MoE): column-parallel q/k/v and gate/up, row-parallel o and down with
+one sum over ranks each.  That sum is delegated to ``comm.row_linear`` so the fused
+GEMM+all-reduce kernel, the NCCL baseline and the single-rank case share this file.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..ops import reference as ref
+from .config import ModelConfig
+from .weights import ModelWeights, ShardSpec, local_heads, expert_range
+
+
+class LocalComm:
+    """Single-rank communicator: every collective is the identity."""
+    size = 1
+    rank = 0
+
+    def row_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, w)
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def gather_vocab(self, logits_local: torch.Tensor) -> torch.Tensor:
+        return logits_local
+
+    def send(self, x: torch.Tensor, dst: int) -> None:  # pragma: no cover
+        raise RuntimeError("no peer")
+
+    def recv(self, x: torch.Tensor, src: int) -> None:  # pragma: no cover
+        raise RuntimeError("no peer")
+
+
+@dataclass
+class StepInputs:
+    """Device-side description of one forward step over ``B`` sequences and ``T`` new tokens."""
+    tokens: torch.Tensor        # [T] int32/int64
+    positions: torch.Tensor     # [T] int32
+    slots: torch.Tensor         # [T] int32/64 flat KV slots (block*block_size+offset)
+    cu_q: torch.Tensor          # [B+1] int32
+    seq_lens: torch.Tensor      # [B] int32 (KV length including the new tokens)
+    block_tables: torch.Tensor  # [B, max_blocks] int32
+    logit_rows: torch.Tensor    # [B'] int32/64 rows of the T tokens whose logits are wanted
+    max_q_len: int = 1
+
+
+class KVPool:
+    """Paged KV storage for the layers this rank holds (block size 16 by default)."""
+
+    def __init__(self, cfg: ModelConfig, spec: ShardSpec, n_blocks: int, block_size: int = 16,
+                 device: str | torch.device = "cpu", dtype: torch.dtype | None = None):
+        self.cfg, self.block_size, self.n_blocks = cfg, block_size, n_blocks
+        dt = dtype or (torch.bfloat16 if cfg.dtype == "bf16" else torch.float32)
+        self.layers: dict[int, tuple[torch.Tensor, torch.Tensor | None]] = {}
+        _, hkv = local_heads(cfg, spec)
+        for i in spec.layers(cfg):
+            if cfg.mla:
+                c = torch.zeros(n_blocks, block_size, cfg.kv_lora_rank + cfg.qk_rope_dim, dtype=dt, device=device)
+                self.layers[i] = (c, None)
+            else:
+                k = torch.zeros(n_blocks, block_size, hkv, cfg.head_dim, dtype=dt, device=device)
+                v = torch.zeros(n_blocks, block_size, hkv, cfg.head_dim, dtype=dt, device=device)
+                self.layers[i] = (k, v)
+
+    @staticmethod
+    def bytes_per_block(cfg: ModelConfig, spec: ShardSpec, block_size: int = 16) -> int:
+        el = 2 if cfg.dtype == "bf16" else 4
+        n_layers = len(spec.layers(cfg))
+        if cfg.mla:
+            return n_layers * block_size * (cfg.kv_lora_rank + cfg.qk_rope_dim) * el
+        _, hkv = local_heads(cfg, spec)
+        return n_layers * 2 * block_size * hkv * cfg.head_dim * el
+
+
+class Decoder:
+    """One rank's model shard + forward."""
+
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None = None, comm=None):
+        self.cfg, self.w = cfg, weights
+        self.spec = spec or ShardSpec()
+        self.comm = comm or LocalComm()
+        dev = next(weights.tensors()).device
+        rot_dim = cfg.qk_rope_dim if cfg.mla else cfg.head_dim
+        inv, mscale = ref.rope_inv_freq(rot_dim, cfg.rope)
+        self.inv_freq = inv.to(dev)
+        self.rope_mscale = mscale
+        self.n_q, self.n_kv = local_heads(cfg, self.spec)
+        if cfg.mla:
+            self.scale = (cfg.qk_nope_dim + cfg.qk_rope_dim) ** -0.5
+            if cfg.rope.kind == "yarn" and cfg.rope.mscale_all_dim:
+                m = 0.1 * cfg.rope.mscale_all_dim * __import__("math").log(cfg.rope.factor) + 1.0
+                self.scale *= m * m
+        else:
+            self.scale = cfg.head_dim ** -0.5
+
+    # ------------------------------------------------------------------ attention
+    def _attn_gqa(self, lw, x, inp: StepInputs, kv) -> torch.Tensor:
+        cfg = self.cfg
+        qkv = ops.linear(x, lw.wqkv, lw.bqkv)
+        kc, vc = kv
+        q = ops.qk_rope_append(qkv, inp.positions, self.inv_freq, self.rope_mscale, self.n_q, self.n_kv,
+                               cfg.head_dim, kc, vc, inp.slots, lw.q_norm, lw.k_norm, cfg.rms_eps)
+        o = ops.paged_attention(q, kc, vc, inp.block_tables, inp.seq_lens, inp.cu_q, self.scale,
+                                cfg.sliding_window, lw.sinks, inp.max_q_len)
+        return self.comm.row_linear(o.reshape(o.shape[0], -1), lw.wo)
+
+    def _attn_mla(self, lw, x, inp: StepInputs, kv) -> torch.Tensor:
+        cfg = self.cfg
+        T = x.shape[0]
+        if lw.wq_a is not None:
+            qa = ops.linear(x, lw.wq_a)
+            qa, _ = ops.rmsnorm(qa, lw.q_a_norm, cfg.rms_eps)
+            q = ops.linear(qa, lw.wq_b)
+        else:
+            q = ops.linear(x, lw.wq_b)
+        q = q.view(T, self.n_q, cfg.qk_nope_dim + cfg.qk_rope_dim)
+        q_nope, q_rope = q[..., :cfg.qk_nope_dim], q[..., cfg.qk_nope_dim:]
+        kva = ops.linear(x, lw.wkv_a)
+        c_kv, _ = ops.rmsnorm(kva[:, :cfg.kv_lora_rank].contiguous(), lw.kv_a_norm, cfg.rms_eps)
+        k_rope = ref.rope(kva[:, None, cfg.kv_lora_rank:], inp.positions, self.inv_freq, self.rope_mscale, True)[:, 0]
+        q_rope = ref.rope(q_rope, inp.positions, self.inv_freq, self.rope_mscale, True)
+        ckv = kv[0]
+        ckv.view(-1, ckv.shape[-1])[inp.slots.long()] = torch.cat((c_kv, k_rope), -1).to(ckv.dtype)
+        # weight absorption: scores are taken in the kv_lora latent space
+        q_lat = torch.einsum("thn,hnc->thc", q_nope.float(), lw.w_uk.float()).to(x.dtype)
+        o_lat = ops.mla_paged_attention(q_lat, q_rope.contiguous(), ckv, inp.block_tables, inp.seq_lens, inp.cu_q,
+                                        self.scale, cfg.kv_lora_rank, inp.max_q_len)
+        o = torch.einsum("thc,hvc->thv", o_lat.float(), lw.w_uv.float()).to(x.dtype)
+        return self.comm.row_linear(o.reshape(T, -1), lw.wo)
+
+    # ------------------------------------------------------------------ ffn
+    def _ffn_dense(self, lw, x) -> torch.Tensor:
+        return self.comm.row_linear(ops.swiglu(ops.linear(x, lw.w_gate_up)), lw.w_down)
+
+    def _ffn_moe(self, lw, x) -> torch.Tensor:
+        """Token-replicated expert parallelism.
+
+        After the attention all-reduce every rank holds all ``T`` hidden rows, so dispatch
+        is a local gather of the rows routed to this rank's experts; combine is one sum over
+        ranks of the weighted expert outputs (shared-expert partial folded into the same sum).
+        """
+        cfg = self.cfg
+        logits = ops.linear(x, lw.router)
+        wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, cfg.router, cfg.norm_topk_prob, lw.router_bias,
+                                 cfg.n_group, cfg.topk_group, cfg.routed_scaling)
+        elo, _ = expert_range(cfg, self.spec)
+        y = ops.moe_experts(x, lw.e_gate_up, lw.e_down, wts, ids, elo)
+        if lw.s_gate_up is not None:
+            y = y + ops.linear(ops.swiglu(ops.linear(x, lw.s_gate_up)), lw.s_down)
+        return self.comm.all_reduce(y)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, inp: StepInputs, kv: KVPool, hidden_in: torch.Tensor | None = None,
+                residual_in: torch.Tensor | None = None):
+        """Run this shard.  Last pipeline stage returns local-vocab logits ``[B', V/N]``;
+        other stages return ``(x, h)`` = (last branch output, residual stream) to forward."""
+        cfg, w = self.cfg, self.w
+        if self.spec.is_first_stage:
+            x = ops.embedding(w.embed, inp.tokens)
+            h = None
+        else:
+            x, h = hidden_in, residual_in
+        for i in self.spec.layers(cfg):
+            lw = w.layers[i]
+            normed, h = ops.rmsnorm(x, lw.attn_norm, cfg.rms_eps, h)
+            x = (self._attn_mla if cfg.mla else self._attn_gqa)(lw, normed, inp, kv.layers[i])
+            normed, h = ops.rmsnorm(x, lw.ffn_norm, cfg.rms_eps, h)
+            x = self._ffn_moe(lw, normed) if cfg.layer_is_moe(i) else self._ffn_dense(lw, normed)
+        if not self.spec.is_last_stage:
+            return x, h
+        # only the rows whose logits are needed go through the final norm + vocabulary GEMM
+        rows = inp.logit_rows.long()
+        xs, hs = x[rows], h[rows]
+        normed, _ = ops.rmsnorm(xs, w.final_norm, cfg.rms_eps, hs)
+        return ops.linear(normed, w.lm_head)
+
+    def logits(self, inp: StepInputs, kv: KVPool) -> torch.Tensor:
+        """Full-vocabulary logits ``[B', V]`` (vocab shards gathered across the TP group)."""
+        out = self.forward(inp, kv)
+        return self.comm.gather_vocab(out)[:, :self.cfg.vocab]

@@ -1,0 +1,404 @@
+"""Weight containers: random initialisation, HF safetensors loading and TP/EP sharding.
+
+The checkpoint format is the HuggingFace repository layout the reference loads through
+``mlx_lm.utils.load_model`` (``src/exo/worker/engines/mlx/utils_mlx.py:163-286``):
+``config.json`` + ``*.safetensors`` (+ ``model.safetensors.index.json``).  Tensor-parallel
+slicing follows the Megatron convention the reference applies per family
+(``src/exo/worker/engines/mlx/auto_parallel.py:628-652`` for Llama, ``:688-767`` for
+DeepSeek/MoE): q/k/v/gate/up split on the output dim, o/down split on the input dim.
+Differences by design: the vocabulary projection is sharded too, KV heads are replicated
+when there are fewer of them than ranks, and routed experts are partitioned whole (expert
+parallel) instead of being sliced on their FFN dim.
+"""
+from __future__ import annotations
+
+import json
+import struct
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Callable, Iterator
+
+import torch
+
+from .config import ModelConfig
+
+_DTYPES = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}
+
+
+@dataclass
+class ShardSpec:
+    """Which slice of the model one rank holds."""
+    tp_rank: int = 0
+    tp_size: int = 1
+    layer_start: int = 0
+    layer_end: int = -1  # exclusive; -1 = n_layers
+    pp_rank: int = 0
+    pp_size: int = 1
+
+    def layers(self, cfg: ModelConfig) -> range:
+        return range(self.layer_start, cfg.n_layers if self.layer_end < 0 else self.layer_end)
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.pp_rank == 0
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.pp_rank == self.pp_size - 1
+
+
+def _rows(t: torch.Tensor, r: int, n: int) -> torch.Tensor:
+    c = t.shape[0] // n
+    return t[r * c:(r + 1) * c]
+
+
+def _cols(t: torch.Tensor, r: int, n: int) -> torch.Tensor:
+    c = t.shape[1] // n
+    return t[:, r * c:(r + 1) * c]
+
+
+def kv_head_range(cfg: ModelConfig, spec: ShardSpec) -> tuple[int, int]:
+    """KV heads ``[lo, hi)`` owned by this rank; replicated when ``n_kv_heads < tp_size``."""
+    n, r = spec.tp_size, spec.tp_rank
+    if cfg.n_kv_heads >= n:
+        c = cfg.n_kv_heads // n
+        return r * c, (r + 1) * c
+    h = r * cfg.n_kv_heads // n
+    return h, h + 1
+
+
+def local_heads(cfg: ModelConfig, spec: ShardSpec) -> tuple[int, int]:
+    """``(q heads, kv heads)`` on this rank."""
+    lo, hi = kv_head_range(cfg, spec)
+    return cfg.n_heads // spec.tp_size, hi - lo
+
+
+def expert_range(cfg: ModelConfig, spec: ShardSpec) -> tuple[int, int]:
+    c = cfg.n_experts // spec.tp_size
+    return spec.tp_rank * c, (spec.tp_rank + 1) * c
+
+
+class TensorSource:
+    """Produces full (unsharded) tensors by HF name; implementations: random or safetensors."""
+
+    def get(self, name: str, shape: tuple[int, ...]) -> torch.Tensor:  # pragma: no cover - interface
+        raise NotImplementedError
+
+    def has(self, name: str) -> bool:
+        return True
+
+
+class RandomSource(TensorSource):
+    """Deterministic N(0, std) tensors: the value of a tensor depends only on (seed, name).
+
+    ``names starting with a norm`` get ones.  Router gates use ``router_std`` (the Qwen3
+    benchmark config asks for N(0,1) router logits, i.e. a larger gate init).
+    """
+
+    def __init__(self, seed: int = 0, std: float = 0.02, device: str | torch.device = "cpu",
+                 dtype: torch.dtype = torch.float32, router_std: float | None = None):
+        self.seed, self.std, self.device, self.dtype = seed, std, torch.device(device), dtype
+        self.router_std = router_std
+
+    def _gen(self, name: str) -> torch.Generator:
+        h = 1469598103934665603
+        for ch in name.encode():
+            h = ((h ^ ch) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+        g = torch.Generator(device=self.device)
+        g.manual_seed((h ^ (self.seed * 0x9E3779B97F4A7C15)) & 0x7FFFFFFFFFFFFFFF)
+        return g
+
+    def get(self, name: str, shape: tuple[int, ...]) -> torch.Tensor:
+        if "norm" in name and name.endswith("weight"):
+            return torch.ones(shape, dtype=self.dtype, device=self.device)
+        if name.endswith("e_score_correction_bias"):
+            return torch.zeros(shape, dtype=torch.float32, device=self.device)
+        std = self.std
+        if self.router_std is not None and name.endswith("mlp.gate.weight"):
+            std = self.router_std
+        t = torch.empty(shape, dtype=torch.float32, device=self.device)
+        t.normal_(0.0, std, generator=self._gen(name))
+        return t.to(self.dtype)
+
+
+class SafetensorsSource(TensorSource):
+    """Lazy reader of a HF checkpoint directory (memory-mapped, one tensor at a time)."""
+
+    _ST = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "F8_E4M3": torch.float8_e4m3fn,
+           "I32": torch.int32, "I64": torch.int64, "U8": torch.uint8, "I8": torch.int8}
+
+    def __init__(self, path: str | Path, device: str | torch.device = "cpu", dtype: torch.dtype = torch.bfloat16):
+        self.path, self.device, self.dtype = Path(path), torch.device(device), dtype
+        self.index: dict[str, tuple[Path, str, tuple[int, ...], int, int]] = {}
+        files = sorted(self.path.glob("*.safetensors"))
+        if not files:
+            raise FileNotFoundError(f"no *.safetensors under {self.path}")
+        for f in files:
+            with open(f, "rb") as fh:
+                (n,) = struct.unpack("<Q", fh.read(8))
+                meta = json.loads(fh.read(n))
+            for k, v in meta.items():
+                if k == "__metadata__":
+                    continue
+                b, e = v["data_offsets"]
+                self.index[k] = (f, v["dtype"], tuple(v["shape"]), 8 + n + b, e - b)
+
+    def has(self, name: str) -> bool:
+        return name in self.index
+
+    def names(self) -> Iterator[str]:
+        return iter(self.index)
+
+    def get(self, name: str, shape: tuple[int, ...] | None = None) -> torch.Tensor:
+        f, dt, shp, off, nbytes = self.index[name]
+        import numpy as np
+        raw = np.memmap(f, dtype=np.uint8, mode="r", offset=off, shape=(nbytes,))
+        t = torch.frombuffer(bytearray(raw), dtype=self._ST[dt]).view(shp)
+        if shape is not None and tuple(shape) != tuple(shp):
+            raise ValueError(f"{name}: checkpoint shape {shp} != expected {shape}")
+        if t.is_floating_point():
+            t = t.to(self.dtype)
+        return t.to(self.device)
+
+
+def write_safetensors(path: str | Path, tensors: dict[str, torch.Tensor]) -> None:
+    """Minimal safetensors writer (used by tests and by the fp8 re-pack cache)."""
+    names = {torch.bfloat16: "BF16", torch.float16: "F16", torch.float32: "F32", torch.int32: "I32",
+             torch.int64: "I64", torch.uint8: "U8", torch.int8: "I8", torch.float8_e4m3fn: "F8_E4M3"}
+    header, blobs, off = {}, [], 0
+    for k, t in tensors.items():
+        t = t.contiguous().cpu()
+        b = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[k] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    hj = json.dumps(header).encode()
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor
+    ffn_norm: torch.Tensor
+    # GQA attention
+    wqkv: torch.Tensor | None = None   # [(hq + 2 hkv) * D, H] local
+    bqkv: torch.Tensor | None = None
+    wo: torch.Tensor | None = None     # [H, hq * Dv] local
+    q_norm: torch.Tensor | None = None
+    k_norm: torch.Tensor | None = None
+    sinks: torch.Tensor | None = None
+    # MLA
+    wq_a: torch.Tensor | None = None
+    q_a_norm: torch.Tensor | None = None
+    wq_b: torch.Tensor | None = None   # [h_local * (nope + rope), q_lora]
+    wkv_a: torch.Tensor | None = None  # [kv_lora + rope, H]
+    kv_a_norm: torch.Tensor | None = None
+    w_uk: torch.Tensor | None = None   # [h_local, nope, kv_lora]
+    w_uv: torch.Tensor | None = None   # [h_local, v, kv_lora]
+    # dense FFN
+    w_gate_up: torch.Tensor | None = None  # [2F/N, H]  (gate rows then up rows)
+    w_down: torch.Tensor | None = None     # [H, F/N]
+    # MoE
+    router: torch.Tensor | None = None       # [E, H]
+    router_bias: torch.Tensor | None = None  # [E]
+    e_gate_up: torch.Tensor | None = None    # [E_local, 2F, H]
+    e_down: torch.Tensor | None = None       # [E_local, H, F]
+    s_gate_up: torch.Tensor | None = None    # shared experts, TP-sliced
+    s_down: torch.Tensor | None = None
+
+
+@dataclass
+class ModelWeights:
+    embed: torch.Tensor | None
+    layers: dict[int, LayerWeights]
+    final_norm: torch.Tensor | None
+    lm_head: torch.Tensor | None  # [V/N, H] local vocab shard
+
+    def nbytes(self) -> int:
+        n = 0
+        for t in self.tensors():
+            n += t.numel() * t.element_size()
+        return n
+
+    def tensors(self) -> Iterator[torch.Tensor]:
+        for t in (self.embed, self.final_norm, self.lm_head):
+            if t is not None:
+                yield t
+        for lw in self.layers.values():
+            for v in vars(lw).values():
+                if isinstance(v, torch.Tensor):
+                    yield v
+
+
+def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: str | torch.device = "cpu",
+                  progress: Callable[[int, int], None] | None = None) -> ModelWeights:
+    """Materialise this rank's shard from ``src`` (full tensors are sliced, then dropped)."""
+    dt = _DTYPES[cfg.dtype]
+    dev = torch.device(device)
+    r, n = spec.tp_rank, spec.tp_size
+    H, D = cfg.hidden, cfg.head_dim
+
+    def fin(t: torch.Tensor, dtype: torch.dtype | None = None) -> torch.Tensor:
+        return t.to(device=dev, dtype=dtype or dt).contiguous()
+
+    layers: dict[int, LayerWeights] = {}
+    lrange = spec.layers(cfg)
+    for li, i in enumerate(lrange):
+        p = f"model.layers.{i}."
+        lw = LayerWeights(attn_norm=fin(src.get(p + "input_layernorm.weight", (H,))),
+                          ffn_norm=fin(src.get(p + "post_attention_layernorm.weight", (H,))))
+        a = p + "self_attn."
+        if cfg.mla:
+            qk = cfg.qk_nope_dim + cfg.qk_rope_dim
+            hl = cfg.n_heads // n
+            if cfg.q_lora_rank:
+                lw.wq_a = fin(src.get(a + "q_a_proj.weight", (cfg.q_lora_rank, H)))
+                lw.q_a_norm = fin(src.get(a + "q_a_layernorm.weight", (cfg.q_lora_rank,)))
+                wq_b = src.get(a + "q_b_proj.weight", (cfg.n_heads * qk, cfg.q_lora_rank))
+            else:
+                wq_b = src.get(a + "q_proj.weight", (cfg.n_heads * qk, H))
+            lw.wq_b = fin(_rows(wq_b, r, n))
+            lw.wkv_a = fin(src.get(a + "kv_a_proj_with_mqa.weight", (cfg.kv_lora_rank + cfg.qk_rope_dim, H)))
+            lw.kv_a_norm = fin(src.get(a + "kv_a_layernorm.weight", (cfg.kv_lora_rank,)))
+            wkv_b = src.get(a + "kv_b_proj.weight", (cfg.n_heads * (cfg.qk_nope_dim + cfg.v_head_dim), cfg.kv_lora_rank))
+            wkv_b = wkv_b.view(cfg.n_heads, cfg.qk_nope_dim + cfg.v_head_dim, cfg.kv_lora_rank)[r * hl:(r + 1) * hl]
+            lw.w_uk = fin(wkv_b[:, :cfg.qk_nope_dim])
+            lw.w_uv = fin(wkv_b[:, cfg.qk_nope_dim:])
+            lw.wo = fin(_cols(src.get(a + "o_proj.weight", (H, cfg.n_heads * cfg.v_head_dim)), r, n))
+        else:
+            klo, khi = kv_head_range(cfg, spec)
+            wq = _rows(src.get(a + "q_proj.weight", (cfg.n_heads * D, H)), r, n)
+            wk = src.get(a + "k_proj.weight", (cfg.n_kv_heads * D, H))[klo * D:khi * D]
+            wv = src.get(a + "v_proj.weight", (cfg.n_kv_heads * D, H))[klo * D:khi * D]
+            lw.wqkv = fin(torch.cat((wq, wk, wv), 0))
+            if cfg.attn_bias:
+                bq = _rows(src.get(a + "q_proj.bias", (cfg.n_heads * D,)), r, n)
+                bk = src.get(a + "k_proj.bias", (cfg.n_kv_heads * D,))[klo * D:khi * D]
+                bv = src.get(a + "v_proj.bias", (cfg.n_kv_heads * D,))[klo * D:khi * D]
+                lw.bqkv = fin(torch.cat((bq, bk, bv), 0))
+            lw.wo = fin(_cols(src.get(a + "o_proj.weight", (H, cfg.n_heads * D)), r, n))
+            if cfg.qk_norm:
+                lw.q_norm = fin(src.get(a + "q_norm.weight", (D,)))
+                lw.k_norm = fin(src.get(a + "k_norm.weight", (D,)))
+            if cfg.attn_sinks:
+                lw.sinks = fin(_rows(src.get(a + "sinks", (cfg.n_heads,)), r, n), torch.float32)
+        m = p + "mlp."
+        if cfg.layer_is_moe(i):
+            E, F = cfg.n_experts, cfg.moe_ffn
+            lw.router = fin(src.get(m + "gate.weight", (E, H)))
+            if cfg.router_bias:
+                lw.router_bias = fin(src.get(m + "gate.e_score_correction_bias", (E,)), torch.float32)
+            elo, ehi = expert_range(cfg, spec)
+            gus, dns = [], []
+            for e in range(elo, ehi):
+                ep = f"{m}experts.{e}."
+                gus.append(torch.cat((src.get(ep + "gate_proj.weight", (F, H)), src.get(ep + "up_proj.weight", (F, H))), 0))
+                dns.append(src.get(ep + "down_proj.weight", (H, F)))
+            lw.e_gate_up = fin(torch.stack(gus))
+            lw.e_down = fin(torch.stack(dns))
+            if cfg.n_shared_experts:
+                Fs = F * cfg.n_shared_experts
+                sp = m + "shared_experts."
+                lw.s_gate_up = fin(torch.cat((_rows(src.get(sp + "gate_proj.weight", (Fs, H)), r, n),
+                                              _rows(src.get(sp + "up_proj.weight", (Fs, H)), r, n)), 0))
+                lw.s_down = fin(_cols(src.get(sp + "down_proj.weight", (H, Fs)), r, n))
+        else:
+            F = cfg.ffn
+            lw.w_gate_up = fin(torch.cat((_rows(src.get(m + "gate_proj.weight", (F, H)), r, n),
+                                          _rows(src.get(m + "up_proj.weight", (F, H)), r, n)), 0))
+            lw.w_down = fin(_cols(src.get(m + "down_proj.weight", (H, F)), r, n))
+        layers[i] = lw
+        if progress is not None:
+            progress(li + 1, len(lrange))
+    embed = final_norm = lm_head = None
+    if spec.is_first_stage or (cfg.tie_embeddings and spec.is_last_stage):
+        embed = fin(src.get("model.embed_tokens.weight", (cfg.vocab, H)))
+    if spec.is_last_stage:
+        final_norm = fin(src.get("model.norm.weight", (H,)))
+        name = "model.embed_tokens.weight" if cfg.tie_embeddings or not src.has("lm_head.weight") else "lm_head.weight"
+        full = src.get(name, (cfg.vocab, H))
+        vpad = -(-cfg.vocab // n)
+        lm_head = fin(full[r * vpad:min((r + 1) * vpad, cfg.vocab)])
+        if lm_head.shape[0] < vpad:  # last rank pads so that every rank has the same shard height
+            lm_head = torch.cat((lm_head, torch.zeros(vpad - lm_head.shape[0], H, dtype=lm_head.dtype, device=dev)), 0)
+    return ModelWeights(embed=embed, layers=layers, final_norm=final_norm, lm_head=lm_head)
+
+
+def fast_random_weights(cfg: ModelConfig, spec: ShardSpec, device: str | torch.device, seed: int = 0,
+                        router_std: float | None = None) -> ModelWeights:
+    """Random-init directly at shard shapes (benchmarks): never materialises a full tensor.
+
+    Values differ from ``build_weights(RandomSource)`` (each rank draws its own stream), so
+    this is for throughput runs where only the shapes and the N(0, 0.02) statistics matter.
+    """
+    class _Shard(TensorSource):
+        def __init__(self) -> None:
+            self.g = torch.Generator(device=device)
+            self.g.manual_seed(seed * 1000003 + spec.tp_rank * 7919 + spec.pp_rank * 104729)
+
+        def get(self, name: str, shape: tuple[int, ...]) -> torch.Tensor:
+            if "norm" in name and name.endswith("weight"):
+                return torch.ones(shape, dtype=_DTYPES[cfg.dtype], device=device)
+            if name.endswith("e_score_correction_bias"):
+                return torch.zeros(shape, dtype=torch.float32, device=device)
+            std = router_std if (router_std is not None and name.endswith("mlp.gate.weight")) else 0.02
+            t = torch.empty(shape, dtype=_DTYPES[cfg.dtype], device=device)
+            t.normal_(0.0, std, generator=self.g)
+            return t
+
+    return _fast_shard(cfg, spec, _Shard(), device)
+
+
+def _fast_shard(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device) -> ModelWeights:
+    dt = _DTYPES[cfg.dtype]
+    n = spec.tp_size
+    H, D = cfg.hidden, cfg.head_dim
+    hq, hkv = local_heads(cfg, spec)
+    layers: dict[int, LayerWeights] = {}
+    for i in spec.layers(cfg):
+        p = f"L{i}."
+        lw = LayerWeights(attn_norm=torch.ones(H, dtype=dt, device=device), ffn_norm=torch.ones(H, dtype=dt, device=device))
+        if cfg.mla:
+            qk = cfg.qk_nope_dim + cfg.qk_rope_dim
+            if cfg.q_lora_rank:
+                lw.wq_a = src.get(p + "qa", (cfg.q_lora_rank, H))
+                lw.q_a_norm = torch.ones(cfg.q_lora_rank, dtype=dt, device=device)
+                lw.wq_b = src.get(p + "qb", (hq * qk, cfg.q_lora_rank))
+            else:
+                lw.wq_b = src.get(p + "qb", (hq * qk, H))
+            lw.wkv_a = src.get(p + "kva", (cfg.kv_lora_rank + cfg.qk_rope_dim, H))
+            lw.kv_a_norm = torch.ones(cfg.kv_lora_rank, dtype=dt, device=device)
+            lw.w_uk = src.get(p + "uk", (hq, cfg.qk_nope_dim, cfg.kv_lora_rank))
+            lw.w_uv = src.get(p + "uv", (hq, cfg.v_head_dim, cfg.kv_lora_rank))
+            lw.wo = src.get(p + "o", (H, hq * cfg.v_head_dim))
+        else:
+            lw.wqkv = src.get(p + "qkv", ((hq + 2 * hkv) * D, H))
+            lw.wo = src.get(p + "o", (H, hq * D))
+            if cfg.qk_norm:
+                lw.q_norm = torch.ones(D, dtype=dt, device=device)
+                lw.k_norm = torch.ones(D, dtype=dt, device=device)
+        if cfg.layer_is_moe(i):
+            E, F = cfg.n_experts, cfg.moe_ffn
+            el = E // n
+            lw.router = src.get("model.layers.%d.mlp.gate.weight" % i, (E, H))
+            if cfg.router_bias:
+                lw.router_bias = torch.zeros(E, dtype=torch.float32, device=device)
+            lw.e_gate_up = src.get(p + "egu", (el, 2 * F, H))
+            lw.e_down = src.get(p + "ed", (el, H, F))
+            if cfg.n_shared_experts:
+                Fs = F * cfg.n_shared_experts // n
+                lw.s_gate_up = src.get(p + "sgu", (2 * Fs, H))
+                lw.s_down = src.get(p + "sd", (H, Fs))
+        else:
+            lw.w_gate_up = src.get(p + "gu", (2 * cfg.ffn // n, H))
+            lw.w_down = src.get(p + "d", (H, cfg.ffn // n))
+        layers[i] = lw
+    embed = src.get("embed", (cfg.vocab, H)) if spec.is_first_stage else None
+    final_norm = torch.ones(H, dtype=dt, device=device) if spec.is_last_stage else None
+    lm_head = src.get("lm_head", (-(-cfg.vocab // n), H)) if spec.is_last_stage else None
+    return ModelWeights(embed, layers, final_norm, lm_head)

@@ -1,0 +1,105 @@
+"""Hot-op entry points.
+
+Each function takes tensors on one device.  CUDA tensors go to the hand-written
+sm_100a kernels in ``exo_b200/ops/csrc`` (bound through ``exo_b200.ops.cuda``); a
+missing extension on a CUDA device is an error, never a silent fallback.  CPU tensors
+run the fp32 PyTorch definitions in ``exo_b200.ops.reference`` — that path is the
+correctness oracle, not a second backend.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import reference as ref
+
+_cuda = None
+
+
+def cuda_ops():
+    """The ctypes binding of the kernel library (loaded on first use; raises if absent)."""
+    global _cuda
+    if _cuda is None:
+        from . import cuda as _c
+        _c.load()
+        _cuda = _c
+    return _cuda
+
+
+def rmsnorm(x, w, eps, residual=None):
+    if x.is_cuda:
+        return cuda_ops().rmsnorm(x, w, eps, residual)
+    return ref.rmsnorm(x, w, eps, residual)
+
+
+def linear(x, w, bias=None, residual=None):
+    if x.is_cuda:
+        return cuda_ops().linear(x, w, bias, residual)
+    return ref.linear(x, w, bias, residual)
+
+
+def swiglu(gate_up):
+    if gate_up.is_cuda:
+        return cuda_ops().swiglu(gate_up)
+    return ref.swiglu(gate_up)
+
+
+def qk_rope_append(qkv, positions, inv_freq, mscale, n_q, n_kv, head_dim, kcache, vcache, slots,
+                   q_norm=None, k_norm=None, eps=1e-6):
+    """Split fused ``qkv [T,(n_q+2n_kv)*D]``, apply optional per-head RMSNorm and RoPE to q/k,
+    append k/v to the paged cache at ``slots``.  Returns ``q [T, n_q, D]``."""
+    if qkv.is_cuda:
+        return cuda_ops().qk_rope_append(qkv, positions, inv_freq, mscale, n_q, n_kv, head_dim, kcache, vcache,
+                                         slots, q_norm, k_norm, eps)
+    T = qkv.shape[0]
+    q, k, v = qkv.split((n_q * head_dim, n_kv * head_dim, n_kv * head_dim), dim=-1)
+    q, k, v = q.reshape(T, n_q, head_dim), k.reshape(T, n_kv, head_dim), v.reshape(T, n_kv, head_dim)
+    if q_norm is not None:
+        q, k = ref.head_rmsnorm(q, q_norm, eps), ref.head_rmsnorm(k, k_norm, eps)
+    q, k = ref.rope(q, positions, inv_freq, mscale), ref.rope(k, positions, inv_freq, mscale)
+    ref.kv_append(k, v, kcache, vcache, slots)
+    return q
+
+
+def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, sliding_window=0, sinks=None,
+                    max_q_len=None):
+    if q.is_cuda:
+        return cuda_ops().paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, sliding_window,
+                                          sinks, max_q_len)
+    return ref.paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, sliding_window, sinks)
+
+
+def mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora, max_q_len=None):
+    if q_lat.is_cuda:
+        return cuda_ops().mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora,
+                                              max_q_len)
+    return ref.mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora)
+
+
+def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling):
+    if logits.is_cuda:
+        return cuda_ops().moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling)
+    return ref.moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling)
+
+
+def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0):
+    if x.is_cuda:
+        return cuda_ops().moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
+    return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
+
+
+def embedding(table, ids):
+    if table.is_cuda:
+        return cuda_ops().embedding(table, ids)
+    return table[ids.long()]
+
+
+def sample(logits, temperature, top_k, top_p, min_p, uniform):
+    if logits.is_cuda:
+        return cuda_ops().sample(logits, temperature, top_k, top_p, min_p, uniform)
+    return ref.sample(logits, temperature, top_k, top_p, min_p, uniform)
+
+
+def argmax(logits):
+    if logits.is_cuda:
+        return cuda_ops().argmax(logits)
+    return logits.float().argmax(-1)

@@ -1,0 +1,285 @@
+"""Plain PyTorch (fp32-accumulating) definitions of every hot op.
+
+These are the semantic ground truth: the CPU oracle runs on them, and every
+sm_100a kernel in ``exo_b200/ops/csrc`` is tested against them.  They replace
+the MLX library calls the reference makes for the same work (RMSNorm / RoPE /
+SDPA / SwitchGLU / sampling; the call sites are listed in the reference at
+``src/exo/worker/engines/mlx/auto_parallel.py:628-652`` and
+``src/exo/worker/engines/mlx/generator/generate.py:599-619``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
+    """Returns ``(normed, h)`` where ``h = x + residual`` (or ``x``) and ``normed = h/rms(h)*w``."""
+    h = x.float() if residual is None else x.float() + residual.float()
+    var = h.pow(2).mean(-1, keepdim=True)
+    out = (h * torch.rsqrt(var + eps)) * w.float()
+    return out.to(x.dtype), h.to(x.dtype)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+           residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``y = x @ w.T (+bias) (+residual)`` with fp32 accumulation; ``w`` is ``[out, in]``."""
+    y = x.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up = [gate | up]`` concatenated on the last dim."""
+    g, u = gate_up.float().chunk(2, dim=-1)
+    return (F.silu(g) * u).to(gate_up.dtype)
+
+
+def rope_inv_freq(head_dim: int, rope) -> tuple[torch.Tensor, float]:
+    """Inverse frequencies (``rot_dim/2`` floats) and the attention magnitude scale.
+
+    Implements default, linear, Llama-3 banded scaling and YaRN (inverse-frequency
+    blending with a linear ramp, the convention the reference patches in at
+    ``src/exo/worker/engines/mlx/patches/standard_yarn_rope.py:10-67``).
+    """
+    rot = int(head_dim * rope.partial_rotary_factor)
+    rot -= rot % 2
+    idx = torch.arange(0, rot, 2, dtype=torch.float64)
+    inv = 1.0 / (rope.theta ** (idx / rot))
+    mscale = 1.0
+    if rope.kind == "linear":
+        inv = inv / rope.factor
+    elif rope.kind == "llama3":
+        low_wl = rope.original_max_position / rope.low_freq_factor
+        high_wl = rope.original_max_position / rope.high_freq_factor
+        wl = 2 * math.pi / inv
+        smooth = (rope.original_max_position / wl - rope.low_freq_factor) / (rope.high_freq_factor - rope.low_freq_factor)
+        blended = (1 - smooth) * inv / rope.factor + smooth * inv
+        inv = torch.where(wl > low_wl, inv / rope.factor, torch.where(wl < high_wl, inv, blended))
+    elif rope.kind == "yarn":
+        def corr_dim(n_rot: float) -> float:
+            return rot * math.log(rope.original_max_position / (n_rot * 2 * math.pi)) / (2 * math.log(rope.theta))
+        low = max(math.floor(corr_dim(rope.beta_fast)), 0)
+        high = min(math.ceil(corr_dim(rope.beta_slow)), rot // 2 - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(rot // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
+        extrap_mask = 1 - ramp
+        inv = inv / rope.factor * (1 - extrap_mask) + inv * extrap_mask
+
+        def ms(scale: float, m: float) -> float:
+            return 1.0 if scale <= 1 else 0.1 * m * math.log(scale) + 1.0
+        if rope.mscale_all_dim:
+            mscale = ms(rope.factor, rope.mscale) / ms(rope.factor, rope.mscale_all_dim)
+        else:
+            mscale = ms(rope.factor, 1.0)
+    return inv.float(), float(mscale)
+
+
+def rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, mscale: float = 1.0,
+         interleaved: bool = False) -> torch.Tensor:
+    """Rotary embedding on the first ``2*len(inv_freq)`` dims of ``x [T, heads, D]``.
+
+    ``interleaved=False`` rotates pairs ``(i, i+rot/2)`` (HF Llama); ``True`` rotates
+    adjacent pairs ``(2i, 2i+1)`` (DeepSeek's rope sub-vector).
+    """
+    rot = inv_freq.numel() * 2
+    ang = positions.float()[:, None] * inv_freq.float()[None, :]  # [T, rot/2]
+    cos, sin = (ang.cos() * mscale)[:, None, :], (ang.sin() * mscale)[:, None, :]
+    xr = x[..., :rot].float()
+    if interleaved:
+        x1, x2 = xr[..., 0::2], xr[..., 1::2]
+        o = torch.stack((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).flatten(-2)
+    else:
+        x1, x2 = xr[..., : rot // 2], xr[..., rot // 2:]
+        o = torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1)
+    out = x.clone()
+    out[..., :rot] = o.to(x.dtype)
+    return out
+
+
+def head_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm over the last (head) dim of ``x [T, heads, D]`` (Qwen3 q/k norm)."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+
+
+def kv_append(k: torch.Tensor, v: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+              slots: torch.Tensor) -> None:
+    """Scatter ``k, v [T, Hkv, D]`` into paged caches ``[blocks, bs, Hkv, D]`` at flat ``slots [T]``."""
+    kc = kcache.view(-1, *kcache.shape[2:])
+    vc = vcache.view(-1, *vcache.shape[2:])
+    kc[slots.long()] = k.to(kc.dtype)
+    vc[slots.long()] = v.to(vc.dtype)
+
+
+def _gather_seq(cache: torch.Tensor, table: torch.Tensor, n: int) -> torch.Tensor:
+    bs = cache.shape[1]
+    nb = (n + bs - 1) // bs
+    return cache[table[:nb].long()].reshape(nb * bs, *cache.shape[2:])[:n]
+
+
+def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                    seq_lens: torch.Tensor, cu_q: torch.Tensor, scale: float, sliding_window: int = 0,
+                    sinks: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal GQA attention of new queries over a paged KV cache.
+
+    ``q [T, Hq, D]`` holds the concatenated new tokens of ``B`` sequences, ``cu_q [B+1]``
+    their offsets; ``seq_lens[b]`` is the KV length *including* those new tokens (already
+    appended).  Query ``j`` of sequence ``b`` sits at position ``seq_lens[b]-q_len+j``.
+    """
+    T, Hq, D = q.shape
+    Hkv = kcache.shape[2]
+    Dv = vcache.shape[-1]
+    out = torch.empty(T, Hq, Dv, dtype=q.dtype, device=q.device)
+    g = Hq // Hkv
+    for b in range(seq_lens.numel()):
+        s, e = int(cu_q[b]), int(cu_q[b + 1])
+        if e == s:
+            continue
+        n = int(seq_lens[b])
+        k = _gather_seq(kcache, block_tables[b], n).float()  # [n, Hkv, D]
+        v = _gather_seq(vcache, block_tables[b], n).float()
+        qb = q[s:e].float().view(e - s, Hkv, g, D)
+        sc = torch.einsum("thgd,nhd->hgtn", qb, k) * scale
+        qpos = torch.arange(n - (e - s), n, device=q.device)[:, None]
+        kpos = torch.arange(n, device=q.device)[None, :]
+        mask = kpos <= qpos
+        if sliding_window:
+            mask &= kpos > qpos - sliding_window
+        sc = sc.masked_fill(~mask[None, None], float("-inf"))
+        if sinks is not None:
+            sk = sinks.float().view(Hkv, g, 1, 1).expand(Hkv, g, e - s, 1)
+            p = torch.softmax(torch.cat((sc, sk), -1), -1)[..., :-1]
+        else:
+            p = torch.softmax(sc, -1)
+        out[s:e] = torch.einsum("hgtn,nhd->thgd", p, v).reshape(e - s, Hq, Dv).to(q.dtype)
+    return out
+
+
+def mla_paged_attention(q_lat: torch.Tensor, q_rope: torch.Tensor, ckv: torch.Tensor, block_tables: torch.Tensor,
+                        seq_lens: torch.Tensor, cu_q: torch.Tensor, scale: float, kv_lora: int) -> torch.Tensor:
+    """Weight-absorbed MLA attention over a paged latent cache.
+
+    ``q_lat [T, H, kv_lora]`` is ``q_nope·W_UK``; ``q_rope [T, H, r]``; the cache row per
+    token is ``[c_kv (kv_lora) | k_rope (r)]`` shared by all heads.  Returns the attention
+    output still in latent space ``[T, H, kv_lora]`` (the caller applies ``W_UV``).
+    """
+    T, H, _ = q_lat.shape
+    out = torch.empty(T, H, kv_lora, dtype=q_lat.dtype, device=q_lat.device)
+    for b in range(seq_lens.numel()):
+        s, e = int(cu_q[b]), int(cu_q[b + 1])
+        if e == s:
+            continue
+        n = int(seq_lens[b])
+        c = _gather_seq(ckv, block_tables[b], n).float()  # [n, kv_lora + r]
+        sc = (torch.einsum("thc,nc->htn", q_lat[s:e].float(), c[:, :kv_lora])
+              + torch.einsum("thr,nr->htn", q_rope[s:e].float(), c[:, kv_lora:])) * scale
+        qpos = torch.arange(n - (e - s), n, device=q_lat.device)[:, None]
+        mask = torch.arange(n, device=q_lat.device)[None, :] <= qpos
+        p = torch.softmax(sc.masked_fill(~mask[None], float("-inf")), -1)
+        out[s:e] = torch.einsum("htn,nc->thc", p, c[:, :kv_lora]).to(q_lat.dtype)
+    return out
+
+
+def moe_route(logits: torch.Tensor, top_k: int, kind: str = "softmax", norm_topk: bool = True,
+              bias: torch.Tensor | None = None, n_group: int = 1, topk_group: int = 1,
+              scaling: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Top-k routing.  Returns ``(weights [T,k] fp32, expert ids [T,k] int32)``.
+
+    ``softmax``: probabilities over all experts, top-k, optional renormalisation (Qwen3-MoE).
+    ``sigmoid``: DeepSeek-V3 — sigmoid scores, selection on ``score+bias`` restricted to the
+    best ``topk_group`` of ``n_group`` groups (group score = sum of its two best), weights
+    taken from the unbiased scores, renormalised and multiplied by ``scaling``.
+    """
+    lf = logits.float()
+    if kind == "softmax":
+        p = torch.softmax(lf, -1)
+        w, idx = torch.topk(p, top_k, dim=-1)
+        if norm_topk:
+            w = w / w.sum(-1, keepdim=True)
+        return w * scaling, idx.int()
+    s = torch.sigmoid(lf)
+    sel = s + bias.float() if bias is not None else s
+    if n_group > 1:
+        T, E = sel.shape
+        gs = sel.view(T, n_group, E // n_group).topk(2, dim=-1)[0].sum(-1)
+        gidx = gs.topk(topk_group, dim=-1)[1]
+        gmask = torch.zeros_like(gs).scatter_(1, gidx, 1.0)
+        sel = sel.masked_fill(gmask[:, :, None].expand(T, n_group, E // n_group).reshape(T, E) == 0, float("-inf"))
+    idx = sel.topk(top_k, dim=-1)[1]
+    w = s.gather(1, idx)
+    if norm_topk:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return w * scaling, idx.int()
+
+
+def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, weights: torch.Tensor,
+                ids: torch.Tensor, expert_offset: int = 0) -> torch.Tensor:
+    """Weighted sum of SwiGLU experts: ``w_gate_up [E, 2F, H]``, ``w_down [E, H, F]``.
+
+    Only experts ``expert_offset <= id < expert_offset+E`` are evaluated (the caller's local
+    shard under expert parallelism); others contribute zero.
+    """
+    T, H = x.shape
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    E = w_gate_up.shape[0]
+    for e in range(E):
+        tok, slot = torch.where(ids == e + expert_offset)
+        if tok.numel() == 0:
+            continue
+        h = swiglu(linear(x[tok], w_gate_up[e]))
+        y = linear(h, w_down[e]).float()
+        out.index_add_(0, tok, y * weights[tok, slot][:, None])
+    return out.to(x.dtype)
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
+    """Per-row temperature / top-k / top-p / min-p sampling by inverse CDF with ``uniform [B]``.
+
+    ``temperature == 0`` selects argmax.  Filters compose in the order top-k → top-p → min-p
+    on the temperature-scaled distribution.  Returns int64 ids ``[B]``.
+    """
+    B, V = logits.shape
+    lf = logits.float()
+    greedy = lf.argmax(-1)
+    t = temperature.float().clamp_min(1e-6)[:, None]
+    probs = torch.softmax(lf / t, -1)
+    sp, si = probs.sort(-1, descending=True)
+    rank = torch.arange(V, device=logits.device)[None, :]
+    k = torch.where(top_k > 0, top_k, torch.full_like(top_k, V))[:, None]
+    keep = rank < k
+    cum = sp.cumsum(-1)
+    keep &= (cum - sp) < top_p.float()[:, None]
+    keep &= sp >= min_p.float()[:, None] * sp[:, :1]
+    keep[:, 0] = True
+    sp = sp * keep
+    cdf = sp.cumsum(-1)
+    target = uniform.float()[:, None] * cdf[:, -1:]
+    pick = (cdf < target).sum(-1).clamp_max(V - 1)
+    sampled = si.gather(1, pick[:, None])[:, 0]
+    return torch.where(temperature <= 0, greedy, sampled)
+
+
+def apply_penalties(logits: torch.Tensor, counts: torch.Tensor, repetition: torch.Tensor,
+                    presence: torch.Tensor, frequency: torch.Tensor) -> torch.Tensor:
+    """Repetition (multiplicative), presence and frequency (additive) penalties from token counts ``[B,V]``."""
+    lf = logits.float()
+    seen = counts > 0
+    rep = repetition.float()[:, None]
+    lf = torch.where(seen, torch.where(lf > 0, lf / rep, lf * rep), lf)
+    lf = lf - presence.float()[:, None] * seen.float() - frequency.float()[:, None] * counts.float()
+    return lf
+
+
+def top_logprobs(logits: torch.Tensor, chosen: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``(logprob of chosen [B], top-k logprobs [B,k], top-k ids [B,k])`` from raw logits."""
+    lp = torch.log_softmax(logits.float(), -1)
+    tv, ti = lp.topk(k, dim=-1)
+    return lp.gather(1, chosen.long()[:, None])[:, 0], tv, ti
