@@ -47,6 +47,7 @@ class Executor:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.n_launch_steps = 0
+        self.launches_per_graph: dict[int, int] = {}
 
     # ------------------------------------------------------------------ helpers
     def _views(self, L: PlanLayout) -> tuple[StepInputs, dict[str, torch.Tensor]]:
@@ -122,14 +123,19 @@ class Executor:
         inp, samp = self._views(L)
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))
-        with torch.cuda.stream(stream):  # warm-up outside capture (lazy inits, autotune-free)
+        saved = self.prev_sampled.clone()  # warm-up runs must not disturb the token chain
+        with torch.cuda.stream(stream):  # warm-up outside capture (per-device scratch set-up)
             for _ in range(2):
                 self._forward_sample(inp, samp, greedy, from_prev)
+                self.prev_sampled.copy_(saved)
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
+        from ..ops import cuda as _k
+        before = _k.launch_count
         with torch.cuda.graph(g, stream=stream):
             out = self._forward_sample(inp, samp, greedy, from_prev)
+        self.launches_per_graph[bB] = _k.launch_count - before  # own kernels replayed per step
         self.graphs[key] = (g, out)
 
     def fetch(self, ids: torch.Tensor) -> np.ndarray:

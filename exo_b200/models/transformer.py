@@ -28,11 +28,12 @@ class LocalComm:
     size = 1
     rank = 0
 
-    def row_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, w)
+    def row_linear(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``residual + sum over ranks of x_r @ w_r.T``."""
+        return ops.linear(x, w, residual=residual)
 
-    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
-        return x
+    def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        return x if residual is None else x + residual
 
     def gather_vocab(self, logits_local: torch.Tensor) -> torch.Tensor:
         return logits_local
@@ -107,23 +108,22 @@ class Decoder:
             self.scale = cfg.head_dim ** -0.5
 
     # ------------------------------------------------------------------ attention
-    def _attn_gqa(self, lw, x, inp: StepInputs, kv) -> torch.Tensor:
+    def _attn_gqa(self, lw, h, inp: StepInputs, kv) -> torch.Tensor:
         cfg = self.cfg
-        qkv = ops.linear(x, lw.wqkv, lw.bqkv)
+        qkv = ops.norm_linear(h, lw.attn_norm, cfg.rms_eps, lw.wqkv, lw.bqkv)
         kc, vc = kv
         q = ops.qk_rope_append(qkv, inp.positions, self.inv_freq, self.rope_mscale, self.n_q, self.n_kv,
                                cfg.head_dim, kc, vc, inp.slots, lw.q_norm, lw.k_norm, cfg.rms_eps)
         o = ops.paged_attention(q, kc, vc, inp.block_tables, inp.seq_lens, inp.cu_q, self.scale,
                                 cfg.sliding_window, lw.sinks, inp.max_q_len)
-        return self.comm.row_linear(o.reshape(o.shape[0], -1), lw.wo)
+        return self.comm.row_linear(o.reshape(o.shape[0], -1), lw.wo, h)
 
-    def _attn_mla(self, lw, x, inp: StepInputs, kv) -> torch.Tensor:
+    def _attn_mla(self, lw, h, inp: StepInputs, kv) -> torch.Tensor:
         cfg = self.cfg
-        T = x.shape[0]
+        T = h.shape[0]
+        x, _ = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps)
         if lw.wq_a is not None:
-            qa = ops.linear(x, lw.wq_a)
-            qa, _ = ops.rmsnorm(qa, lw.q_a_norm, cfg.rms_eps)
-            q = ops.linear(qa, lw.wq_b)
+            q = ops.norm_linear(ops.linear(x, lw.wq_a), lw.q_a_norm, cfg.rms_eps, lw.wq_b)
         else:
             q = ops.linear(x, lw.wq_b)
         q = q.view(T, self.n_q, cfg.qk_nope_dim + cfg.qk_rope_dim)
@@ -135,17 +135,18 @@ class Decoder:
         ckv = kv[0]
         ckv.view(-1, ckv.shape[-1])[inp.slots.long()] = torch.cat((c_kv, k_rope), -1).to(ckv.dtype)
         # weight absorption: scores are taken in the kv_lora latent space
-        q_lat = torch.einsum("thn,hnc->thc", q_nope.float(), lw.w_uk.float()).to(x.dtype)
+        q_lat = torch.einsum("thn,hnc->thc", q_nope.float(), lw.w_uk.float()).to(h.dtype)
         o_lat = ops.mla_paged_attention(q_lat, q_rope.contiguous(), ckv, inp.block_tables, inp.seq_lens, inp.cu_q,
                                         self.scale, cfg.kv_lora_rank, inp.max_q_len)
-        o = torch.einsum("thc,hvc->thv", o_lat.float(), lw.w_uv.float()).to(x.dtype)
-        return self.comm.row_linear(o.reshape(T, -1), lw.wo)
+        o = torch.einsum("thc,hvc->thv", o_lat.float(), lw.w_uv.float()).to(h.dtype)
+        return self.comm.row_linear(o.reshape(T, -1), lw.wo, h)
 
     # ------------------------------------------------------------------ ffn
-    def _ffn_dense(self, lw, x) -> torch.Tensor:
-        return self.comm.row_linear(ops.swiglu(ops.linear(x, lw.w_gate_up)), lw.w_down)
+    def _ffn_dense(self, lw, h) -> torch.Tensor:
+        act = ops.norm_linear(h, lw.ffn_norm, self.cfg.rms_eps, lw.w_gate_up, swiglu=True)
+        return self.comm.row_linear(act, lw.w_down, h)
 
-    def _ffn_moe(self, lw, x) -> torch.Tensor:
+    def _ffn_moe(self, lw, h) -> torch.Tensor:
         """Token-replicated expert parallelism.
 
         After the attention all-reduce every rank holds all ``T`` hidden rows, so dispatch
@@ -153,39 +154,31 @@ class Decoder:
         ranks of the weighted expert outputs (shared-expert partial folded into the same sum).
         """
         cfg = self.cfg
+        x, _ = ops.rmsnorm(h, lw.ffn_norm, cfg.rms_eps)
         logits = ops.linear(x, lw.router)
         wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, cfg.router, cfg.norm_topk_prob, lw.router_bias,
                                  cfg.n_group, cfg.topk_group, cfg.routed_scaling)
         elo, _ = expert_range(cfg, self.spec)
         y = ops.moe_experts(x, lw.e_gate_up, lw.e_down, wts, ids, elo)
         if lw.s_gate_up is not None:
-            y = y + ops.linear(ops.swiglu(ops.linear(x, lw.s_gate_up)), lw.s_down)
-        return self.comm.all_reduce(y)
+            y = ops.linear(ops.linear(x, lw.s_gate_up, swiglu=True), lw.s_down, residual=y)
+        return self.comm.all_reduce(y, h)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, inp: StepInputs, kv: KVPool, hidden_in: torch.Tensor | None = None,
-                residual_in: torch.Tensor | None = None):
-        """Run this shard.  Last pipeline stage returns local-vocab logits ``[B', V/N]``;
-        other stages return ``(x, h)`` = (last branch output, residual stream) to forward."""
+    def forward(self, inp: StepInputs, kv: KVPool, hidden_in: torch.Tensor | None = None):
+        """Run this shard over the residual stream ``h [T, H]``.  The last pipeline stage returns
+        local-vocab logits ``[B', V/N]``; other stages return ``h`` to send to the next stage."""
         cfg, w = self.cfg, self.w
-        if self.spec.is_first_stage:
-            x = ops.embedding(w.embed, inp.tokens)
-            h = None
-        else:
-            x, h = hidden_in, residual_in
+        h = ops.embedding(w.embed, inp.tokens) if self.spec.is_first_stage else hidden_in
         for i in self.spec.layers(cfg):
             lw = w.layers[i]
-            normed, h = ops.rmsnorm(x, lw.attn_norm, cfg.rms_eps, h)
-            x = (self._attn_mla if cfg.mla else self._attn_gqa)(lw, normed, inp, kv.layers[i])
-            normed, h = ops.rmsnorm(x, lw.ffn_norm, cfg.rms_eps, h)
-            x = self._ffn_moe(lw, normed) if cfg.layer_is_moe(i) else self._ffn_dense(lw, normed)
+            h = (self._attn_mla if cfg.mla else self._attn_gqa)(lw, h, inp, kv.layers[i])
+            h = self._ffn_moe(lw, h) if cfg.layer_is_moe(i) else self._ffn_dense(lw, h)
         if not self.spec.is_last_stage:
-            return x, h
+            return h
         # only the rows whose logits are needed go through the final norm + vocabulary GEMM
-        rows = inp.logit_rows.long()
-        xs, hs = x[rows], h[rows]
-        normed, _ = ops.rmsnorm(xs, w.final_norm, cfg.rms_eps, hs)
-        return ops.linear(normed, w.lm_head)
+        hs = h if (inp.max_q_len == 1 and inp.logit_rows.numel() == h.shape[0]) else h[inp.logit_rows.long()]
+        return ops.norm_linear(hs, w.final_norm, cfg.rms_eps, w.lm_head)
 
     def logits(self, inp: StepInputs, kv: KVPool) -> torch.Tensor:
         """Full-vocabulary logits ``[B', V]`` (vocab shards gathered across the TP group)."""

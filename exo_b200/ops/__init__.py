@@ -31,10 +31,20 @@ def rmsnorm(x, w, eps, residual=None):
     return ref.rmsnorm(x, w, eps, residual)
 
 
-def linear(x, w, bias=None, residual=None):
+def linear(x, w, bias=None, residual=None, swiglu=False):
+    """``y = x @ w.T (+bias) (+residual)``; ``swiglu=True`` returns ``silu(y[:, :F]) * y[:, F:]``."""
     if x.is_cuda:
-        return cuda_ops().linear(x, w, bias, residual)
-    return ref.linear(x, w, bias, residual)
+        return cuda_ops().linear(x, w, bias, residual, None, 0.0, swiglu)
+    y = ref.linear(x, w, bias, residual)
+    return ref.swiglu(y) if swiglu else y
+
+
+def norm_linear(h, norm_w, eps, w, bias=None, swiglu=False):
+    """``linear(rmsnorm(h, norm_w), w)`` — one kernel on the small-batch path."""
+    if h.is_cuda:
+        return cuda_ops().linear(h, w, bias, None, norm_w, eps, swiglu)
+    y = ref.linear(ref.rmsnorm(h, norm_w, eps)[0], w, bias)
+    return ref.swiglu(y) if swiglu else y
 
 
 def swiglu(gate_up):

@@ -1,0 +1,360 @@
+// bf16 GEMM on the 5th-generation tensor cores:  out[M, N] = x[M, K] . W[N, K]^T  (+bias)(+residual).
+//
+// The problem is issued "swapped": the weight tile is the MMA's M operand (128 output features on
+// the 128 TMEM lanes) and the activation rows are the MMA's N operand (BN = 16..256 columns).  Both
+// operands are K-major in memory as they are, so no transpose is ever materialised, and a decode
+// batch of 9..256 rows maps onto ONE instruction shape without padding the batch to 128.  The
+// kernel is therefore weight-bandwidth bound for decode and tensor bound for prefill.
+//
+// CTA = 6 warps:  warp 0 = TMA producer (one elected lane), warp 1 = TMEM owner + MMA issuer (one
+// elected lane), warps 2..5 = epilogue (tcgen05.ld of the four 32-lane TMEM quadrants).
+// Pipeline: STAGES x {W tile 128x64, x tile BNx64} in 128B-swizzled shared memory, full/empty
+// mbarriers, accumulator in TMEM, tcgen05.commit releases stages and publishes the accumulator.
+//
+// Split-K (grid.z): each split writes an fp32 partial tile to a workspace; the last CTA to arrive
+// on the tile's counter sums the partials in split order (deterministic) and runs the epilogue.
+#include <mutex>
+#include <unordered_map>
+
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int BM = 128;  // output features per CTA (TMEM lanes)
+constexpr int BK = 64;   // K elements per stage (128 bytes of bf16: one swizzle atom)
+
+struct GemmParams {
+  int M, N, K;            // x rows, W rows (output features), reduction length
+  int kb_per_split;       // K blocks handled by one split
+  int splits;
+  const __nv_bfloat16* bias;       // [N] or null
+  const __nv_bfloat16* residual;   // [M, ldo] or null (may alias out)
+  __nv_bfloat16* out;              // [M, ldo]
+  int ldo;
+  float* partial;         // [splits, M, N] fp32 (split-K only)
+  int* counters;          // [tiles] zero-initialised, self-resetting
+  int* err;               // device error word
+};
+
+template <int BN, int STAGES>
+struct Smem {
+  alignas(1024) __nv_bfloat16 a[STAGES][BM * BK];
+  alignas(1024) __nv_bfloat16 b[STAGES][BN * BK];
+  uint64_t full[STAGES], empty[STAGES], acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                    const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  using S = Smem<BN, STAGES>;
+  S& s = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t STAGE_BYTES = (BM * BK + BN * BK) * 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb0 = split * p.kb_per_split;
+  const int nkb = min(p.kb_per_split, kb_total - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; i++) { tc::mbar_init(&s.full[i], 1); tc::mbar_init(&s.empty[i], 1); }
+    tc::mbar_init(&s.acc_full, 1);
+    s.abort_flag = 0;
+    s.is_last = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (tc::elect_one()) {
+      tc::prefetch_tmap(&tmap_w);
+      tc::prefetch_tmap(&tmap_x);
+      for (int i = 0; i < nkb; i++) {
+        int st = i % STAGES;
+        if (i >= STAGES && !tc::mbar_wait(&s.empty[st], ((i / STAGES) - 1) & 1)) {
+          atomicExch(p.err, tc::ERR_EMPTY_TIMEOUT);
+          s.abort_flag = 1;
+          break;
+        }
+        tc::mbar_expect_tx(&s.full[st], STAGE_BYTES);
+        int k = (kb0 + i) * BK;
+        tc::tma_load_2d(s.a[st], &tmap_w, k, n0, &s.full[st]);
+        tc::tma_load_2d(s.b[st], &tmap_x, k, m0, &s.full[st]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (tc::elect_one()) {
+      constexpr uint32_t idesc = tc::umma_idesc_bf16(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; i++) {
+        int st = i % STAGES;
+        if (!tc::mbar_wait(&s.full[st], (i / STAGES) & 1)) {
+          atomicExch(p.err, tc::ERR_FULL_TIMEOUT);
+          s.abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc::tc_fence_after();
+        uint64_t ad = tc::umma_desc_sw128(tc::smem_u32(s.a[st]));
+        uint64_t bd = tc::umma_desc_sw128(tc::smem_u32(s.b[st]));
+#pragma unroll
+        for (int k = 0; k < BK / 16; k++)  // +32 bytes per K step of 16 bf16 → +2 in the >>4 address field
+          tc::umma_bf16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) != 0);
+        tc::umma_commit(&s.empty[st]);  // stage reusable once these MMAs have read it
+      }
+      tc::umma_commit(&s.acc_full);  // accumulator complete (also arrives if we bailed out: nothing pending)
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ------------------------------
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int n = n0 + quad * 32 + lane;       // output feature owned by this thread
+    bool ok = tc::mbar_wait(&s.acc_full, 0);
+    if (!ok) { atomicExch(p.err, tc::ERR_ACC_TIMEOUT); s.abort_flag = 1; }
+    tc::tc_fence_after();
+    ok = ok && !*(volatile int*)&s.abort_flag && nkb > 0;
+    const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
+    if (p.splits == 1) {
+      float bias = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        tc::tmem_ld16(taddr + c, v);   // warp-collective: executed by all lanes regardless of bounds
+        tc::tmem_ld_wait();
+        if (ok && n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) {
+            int m = m0 + c + j;
+            if (m < p.M) {
+              float y = v[j] + bias;
+              size_t o = (size_t)m * p.ldo + n;
+              if (p.residual) y += __bfloat162float(p.residual[o]);
+              p.out[o] = __float2bfloat16_rn(y);
+            }
+          }
+        }
+      }
+    } else {
+      // split-K: publish the fp32 partial tile
+      float* part = p.partial + (size_t)split * p.M * p.N;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        tc::tmem_ld16(taddr + c, v);
+        tc::tmem_ld_wait();
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) {
+            int m = m0 + c + j;
+            if (m < p.M) part[(size_t)m * p.N + n] = ok ? v[j] : 0.f;
+          }
+        }
+      }
+      __threadfence();
+      // named barrier over the 4 epilogue warps (128 threads), then one thread takes a ticket
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        int ticket = atomicAdd(&p.counters[tile], 1);
+        s.is_last = (ticket == p.splits - 1);
+        if (s.is_last) p.counters[tile] = 0;  // self-reset for the next launch / graph replay
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (s.is_last) {
+        __threadfence();
+        if (n < p.N) {
+          float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+          for (int mm = 0; mm < BN; mm++) {
+            int m = m0 + mm;
+            if (m >= p.M) break;
+            float y = bias;
+            for (int sp = 0; sp < p.splits; sp++) y += __ldcg(p.partial + ((size_t)sp * p.M + m) * p.N + n);
+            size_t o = (size_t)m * p.ldo + n;
+            if (p.residual) y += __bfloat162float(p.residual[o]);
+            p.out[o] = __float2bfloat16_rn(y);
+          }
+        }
+      }
+    }
+  }
+  // ------------------------------ teardown ------------------------------
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+  static EncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeFn)p;
+  }
+  return fn;
+}
+
+struct Key {
+  const void* base; uint64_t rows, cols; uint32_t box;
+  bool operator==(const Key& o) const { return base == o.base && rows == o.rows && cols == o.cols && box == o.box; }
+};
+struct KeyHash {
+  size_t operator()(const Key& k) const {
+    return std::hash<uint64_t>()((uint64_t)k.base * 1000003u ^ k.rows * 7919u ^ k.cols * 104729u ^ k.box);
+  }
+};
+std::unordered_map<Key, CUtensorMap*, KeyHash> g_maps;
+std::mutex g_maps_mu;
+
+int* g_err[16] = {nullptr};
+int* g_counters[16] = {nullptr};
+float* g_partial[16] = {nullptr};
+size_t g_partial_floats[16] = {0};
+constexpr int MAX_TILES = 1 << 16;
+
+}  // namespace
+
+const CUtensorMap* exo_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  std::lock_guard<std::mutex> lk(g_maps_mu);
+  Key k{base, rows, cols, box_rows};
+  auto it = g_maps.find(k);
+  if (it != g_maps.end()) return it->second;
+  EncodeFn enc = get_encode();
+  if (!enc || (cols * 2) % 16 != 0 || ((uintptr_t)base & 15)) return nullptr;
+  CUtensorMap* m = new CUtensorMap;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { delete m; return nullptr; }
+  if (g_maps.size() > 8192) {  // activations come and go: bound the cache
+    for (auto& kv : g_maps) delete kv.second;
+    g_maps.clear();
+  }
+  g_maps[k] = m;
+  return m;
+}
+
+// Per-device scratch set up on first use (NOT inside stream capture: call exo_gemm_init first).
+EXO_API int exo_gemm_init(long partial_floats) {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16) return -1;
+  if (!g_err[dev]) {
+    if (cudaMalloc(&g_err[dev], sizeof(int)) != cudaSuccess) return -1;
+    cudaMemset(g_err[dev], 0, sizeof(int));
+    if (cudaMalloc(&g_counters[dev], MAX_TILES * sizeof(int)) != cudaSuccess) return -1;
+    cudaMemset(g_counters[dev], 0, MAX_TILES * sizeof(int));
+  }
+  if ((size_t)partial_floats > g_partial_floats[dev]) {
+    if (g_partial[dev]) cudaFree(g_partial[dev]);
+    if (cudaMalloc(&g_partial[dev], (size_t)partial_floats * sizeof(float)) != cudaSuccess) return -1;
+    g_partial_floats[dev] = (size_t)partial_floats;
+  }
+  return 0;
+}
+
+// Reads and clears the device error word (synchronises the device).
+EXO_API int exo_gemm_last_error() {
+  int dev, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_err[dev]) return 0;
+  cudaMemcpy(&v, g_err[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (v) cudaMemset(g_err[dev], 0, sizeof(int));
+  return v;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap* tw, const CUtensorMap* tx, GemmParams p, cudaStream_t st) {
+  using S = Smem<BN, STAGES>;
+  size_t smem = sizeof(S) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_swapped_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
+  gemm_swapped_kernel<BN, STAGES><<<grid, 192, smem, st>>>(*tw, *tx, p);
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+// Suggested split count for a (M, N, K) problem: fill the 148 SMs when there are few output tiles.
+EXO_API int exo_gemm_splits(int M, int N, int K) {
+  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  long tiles = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+  int kb = (K + BK - 1) / BK;
+  if (tiles >= 120 || kb < 8) return 1;
+  int s = (int)((148 + tiles - 1) / tiles);
+  if (s > kb / 4) s = kb / 4;
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
+
+EXO_API int exo_gemm_bf16(const void* x, const void* W, const void* bias, const void* residual, void* out, int M, int N,
+                          int K, int ldo, int splits, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 8 != 0 || K < BK) return -2;
+  int dev;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !g_err[dev]) return -4;  // exo_gemm_init not called on this device
+  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const CUtensorMap* tw = exo_tmap_2d_bf16(W, N, K, BM);
+  const CUtensorMap* tx = exo_tmap_2d_bf16(x, M, K, bn);
+  if (!tw || !tx) return -5;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  int kb_total = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > kb_total) splits = kb_total;
+  p.kb_per_split = (kb_total + splits - 1) / splits;
+  splits = (kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  p.splits = splits;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.residual = (const __nv_bfloat16*)residual;
+  p.out = (__nv_bfloat16*)out;
+  p.ldo = ldo;
+  p.partial = g_partial[dev];
+  p.counters = g_counters[dev];
+  p.err = g_err[dev];
+  if (splits > 1) {
+    long tiles = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+    if ((size_t)splits * M * N > g_partial_floats[dev] || tiles > MAX_TILES) return -6;
+  }
+  switch (bn) {
+    case 16: return launch_gemm<16, 8>(tw, tx, p, st);
+    case 32: return launch_gemm<32, 8>(tw, tx, p, st);
+    case 64: return launch_gemm<64, 8>(tw, tx, p, st);
+    case 128: return launch_gemm<128, 6>(tw, tx, p, st);
+    default: return launch_gemm<256, 4>(tw, tx, p, st);
+  }
+}

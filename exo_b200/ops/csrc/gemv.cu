@@ -1,0 +1,187 @@
+// Small-batch linear layers (M <= 8 rows): y = x W^T, weight-bandwidth bound.
+//
+// Every weight byte is read exactly once with 16-byte streaming loads; each warp produces two
+// output rows so that two independent load streams are in flight per lane.  Three fusions remove
+// whole launches and activation round trips from the decode step:
+//   * prologue RMSNorm: the warp's lanes cover all of K anyway, so sum(x^2) is accumulated in the
+//     same loop and y = rstd * (W . (x * norm_w));
+//   * epilogue SwiGLU: the warp's two rows are gate row n and up row n + F, it writes silu(g) * u;
+//   * epilogue bias / residual add (out may alias residual).
+#include "common.cuh"
+
+template <typename T> struct Vec16;
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load_stream(const __nv_bfloat16* p, float* f) { unpack8(ld_stream16(p), f); }
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    unpack8(*reinterpret_cast<const uint4*>(p), f);
+  }
+};
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load_stream(const float* p, float* f) {
+    uint4 u = ld_stream16(p);
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    float4 u = *reinterpret_cast<const float4*>(p);
+    f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+  }
+};
+
+template <typename T, int M, bool NORM, bool SWIGLU>
+__global__ void __launch_bounds__(128)
+linear_small_kernel(const T* __restrict__ x, const T* __restrict__ W, const T* __restrict__ bias,
+                    const T* residual, T* out, const T* __restrict__ norm_w, float eps, int N, int K, int n_pairs,
+                    int ldo) {
+  constexpr int V = Vec16<T>::N;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n_pairs) return;
+  // rows handled by this warp
+  int r0, r1;
+  if (SWIGLU) { r0 = warp; r1 = warp + N / 2; }
+  else { r0 = 2 * warp; r1 = min(2 * warp + 1, N - 1); }
+  const T* w0 = W + (size_t)r0 * K;
+  const T* w1 = W + (size_t)r1 * K;
+  float a0[M], a1[M], ss[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) { a0[m] = 0.f; a1[m] = 0.f; ss[m] = 0.f; }
+#pragma unroll 2
+  for (int k = lane * V; k < K; k += 32 * V) {
+    float f0[V], f1[V], nw[V];
+    Vec16<T>::load_stream(w0 + k, f0);
+    Vec16<T>::load_stream(w1 + k, f1);
+    if (NORM) Vec16<T>::load(norm_w + k, nw);
+#pragma unroll
+    for (int m = 0; m < M; m++) {
+      float xf[V];
+      Vec16<T>::load(x + (size_t)m * K + k, xf);
+#pragma unroll
+      for (int j = 0; j < V; j++) {
+        float xv = xf[j];
+        if (NORM) { ss[m] += xv * xv; xv *= nw[j]; }
+        a0[m] += f0[j] * xv;
+        a1[m] += f1[j] * xv;
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < M; m++) {
+    float y0 = warp_sum(a0[m]), y1 = warp_sum(a1[m]);
+    if (NORM) {
+      float rstd = rsqrtf(warp_sum(ss[m]) / K + eps);
+      y0 *= rstd;
+      y1 *= rstd;
+    }
+    if (lane == 0) {
+      if (bias) { y0 += Cvt<T>::to_f(bias[r0]); y1 += Cvt<T>::to_f(bias[r1]); }
+      if (SWIGLU) {
+        out[(size_t)m * ldo + r0] = Cvt<T>::from_f(silu_f(y0) * y1);
+      } else {
+        if (residual) {
+          y0 += Cvt<T>::to_f(residual[(size_t)m * ldo + r0]);
+          y1 += Cvt<T>::to_f(residual[(size_t)m * ldo + r1]);
+        }
+        out[(size_t)m * ldo + r0] = Cvt<T>::from_f(y0);
+        if (r1 != r0) out[(size_t)m * ldo + r1] = Cvt<T>::from_f(y1);
+      }
+    }
+  }
+}
+
+template <typename T, int M>
+static int launch_small(const void* x, const void* W, const void* bias, const void* residual, void* out,
+                        const void* norm_w, float eps, int N, int K, int swiglu, cudaStream_t st) {
+  int n_pairs = swiglu ? N / 2 : (N + 1) / 2;
+  int blocks = (n_pairs + 3) / 4;
+  int ldo = swiglu ? N / 2 : N;
+#define L(NORM, SW)                                                                                              \
+  linear_small_kernel<T, M, NORM, SW><<<blocks, 128, 0, st>>>((const T*)x, (const T*)W, (const T*)bias,            \
+                                                              (const T*)residual, (T*)out, (const T*)norm_w, eps, \
+                                                              N, K, n_pairs, ldo)
+  if (norm_w) { if (swiglu) L(true, true); else L(true, false); }
+  else { if (swiglu) L(false, true); else L(false, false); }
+#undef L
+  return 0;
+}
+
+// y[M,N] = f(x[M,K]) W[N,K]^T ; M in 1..8.  norm_w != null → RMSNorm prologue.  swiglu != 0 → out is [M, N/2].
+EXO_API int exo_linear_small(const void* x, const void* W, const void* bias, const void* residual, void* out,
+                             const void* norm_w, float eps, int M, int N, int K, int swiglu, int dtype,
+                             cudaStream_t st) {
+  if (M <= 0 || M > 8) return -2;
+  int vec = dtype == EXO_BF16 ? 8 : 4;
+  if (K % vec != 0) return -2;
+  if (swiglu && (N % 2)) return -2;
+#define BY_M(T)                                                                                   \
+  switch (M) {                                                                                    \
+    case 1: launch_small<T, 1>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 2: launch_small<T, 2>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 3: launch_small<T, 3>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 4: launch_small<T, 4>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 5: launch_small<T, 5>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 6: launch_small<T, 6>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 7: launch_small<T, 7>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    default: launch_small<T, 8>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break; \
+  }
+  if (dtype == EXO_BF16) { BY_M(__nv_bfloat16) } else { BY_M(float) }
+#undef BY_M
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Generic fp32/bf16 tiled GEMM on CUDA cores: y[M,N] = x[M,K] W[N,K]^T (+bias)(+residual).
+// Only used for fp32 models (the CPU-oracle configs run on a GPU) — bf16 models go to tcgen05.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+linear_tiled_kernel(const T* __restrict__ x, const T* __restrict__ W, const T* __restrict__ bias, const T* residual,
+                    T* out, int M, int N, int K) {
+  __shared__ float xs[32][33], ws[32][33];
+  int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  int m0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < K; k0 += 32) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      int r = ty + i * 8;
+      int m = m0 + r, n = n0 + r, k = k0 + tx;
+      xs[r][tx] = (m < M && k < K) ? Cvt<T>::to_f(x[(size_t)m * K + k]) : 0.f;
+      ws[r][tx] = (n < N && k < K) ? Cvt<T>::to_f(W[(size_t)n * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 32; kk++) {
+      float wv = ws[tx][kk];
+#pragma unroll
+      for (int i = 0; i < 4; i++) acc[i] += xs[ty + i * 8][kk] * wv;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    int m = m0 + ty + i * 8, n = n0 + tx;
+    if (m < M && n < N) {
+      float y = acc[i];
+      if (bias) y += Cvt<T>::to_f(bias[n]);
+      if (residual) y += Cvt<T>::to_f(residual[(size_t)m * N + n]);
+      out[(size_t)m * N + n] = Cvt<T>::from_f(y);
+    }
+  }
+}
+
+EXO_API int exo_linear_tiled(const void* x, const void* W, const void* bias, const void* residual, void* out, int M,
+                             int N, int K, int dtype, cudaStream_t st) {
+  if (M == 0 || N == 0) return 0;
+  dim3 grid((N + 31) / 32, (M + 31) / 32);
+  if (dtype == EXO_BF16)
+    linear_tiled_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W,
+                                                             (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
+                                                             (__nv_bfloat16*)out, M, N, K);
+  else
+    linear_tiled_kernel<float><<<grid, 256, 0, st>>>((const float*)x, (const float*)W, (const float*)bias,
+                                                     (const float*)residual, (float*)out, M, N, K);
+  EXO_CHECK_LAUNCH();
+  return 0;
+}

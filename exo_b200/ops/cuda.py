@@ -1,0 +1,267 @@
+"""ctypes binding of ``_kernels.so`` (the sm_100a kernel library).
+
+Launchers take raw device pointers and the current CUDA stream, so every call is graph
+capturable and costs one ctypes dispatch.  Tensors are allocated by the caller's framework
+(PyTorch) — the kernels themselves never allocate.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch
+
+from . import reference as ref
+
+_lib: C.CDLL | None = None
+_SO = Path(__file__).resolve().parent / "_kernels.so"
+
+BF16, F32 = 0, 1
+_DT = {torch.bfloat16: BF16, torch.float32: F32}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not _SO.exists():
+            raise KernelError(f"{_SO} is missing: run `python -m exo_b200.build` (CUDA ops have no fallback)")
+        _lib = C.CDLL(str(_SO))
+        for name in dir(_Sig):
+            if name.startswith("exo_"):
+                fn = getattr(_lib, name)
+                fn.restype, fn.argtypes = getattr(_Sig, name)
+    return _lib
+
+
+_p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_long
+
+
+class _Sig:
+    exo_rmsnorm = (_i, [_p, _p, _p, _p, _p, _i, _i, _f, _i, _p])
+    exo_swiglu = (_i, [_p, _p, _i, _i, _i, _p])
+    exo_embedding = (_i, [_p, _p, _p, _i, _i, _i, _i, _p])
+    exo_qk_rope_append = (_i, [_p, _p, _p, _f, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _f, _i, _i, _p])
+    exo_argmax = (_i, [_p, _p, _i, _i, _l, _i, _p])
+    exo_sample = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _l, _i, _p])
+    exo_paged_decode_workspace = (_l, [_i, _i, _i, _i])
+    exo_paged_decode_splits = (_i, [_i, _i, _i])
+    exo_paged_decode = (_i, [_p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
+    exo_token_seq = (_i, [_p, _p, _i, _p])
+    exo_paged_ragged = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
+    exo_linear_small = (_i, [_p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _p])
+    exo_linear_tiled = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
+    exo_gemm_init = (_i, [_l])
+    exo_gemm_last_error = (_i, [])
+    exo_gemm_splits = (_i, [_i, _i, _i])
+    exo_gemm_bf16 = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+
+
+def _st() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _chk(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}" + (" (unsupported shape/dtype)" if rc == -2 else ""))
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {t.dtype}") from None
+
+
+launch_count = 0  # launches issued through this module (read by the benchmark)
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+# ------------------------------------------------------------------------------------------
+def rmsnorm(x, w, eps, residual=None):
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    h = torch.empty_like(x) if residual is not None else x
+    _chk(load().exo_rmsnorm(_ptr(x), _ptr(residual), _ptr(w), _ptr(out), _ptr(h) if residual is not None else None,
+                            x.shape[0], x.shape[1], eps, _dt(x), _st()), "rmsnorm")
+    _count()
+    return out, h
+
+
+def swiglu(gate_up):
+    gate_up = gate_up.contiguous()
+    rows, F2 = gate_up.shape
+    out = torch.empty(rows, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    _chk(load().exo_swiglu(_ptr(gate_up), _ptr(out), rows, F2 // 2, _dt(gate_up), _st()), "swiglu")
+    _count()
+    return out
+
+
+def embedding(table, ids):
+    ids = ids.to(torch.int32)
+    out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    _chk(load().exo_embedding(_ptr(table), _ptr(ids), _ptr(out), ids.numel(), table.shape[1], table.shape[0],
+                              _dt(table), _st()), "embedding")
+    _count()
+    return out
+
+
+SMALL_M = 8
+GEMM_PARTIAL_FLOATS = 16 << 20
+_gemm_ready: set[int] = set()
+
+
+def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False):
+    """tcgen05 GEMM ``x[M,K] @ w[N,K].T``; per-device scratch is set up on first use, which
+    must therefore happen outside CUDA-graph capture (the executor warms up before capturing)."""
+    lib = load()
+    dev = x.device.index or 0
+    if dev not in _gemm_ready:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("first GEMM call on a device must not be inside graph capture")
+        _chk(lib.exo_gemm_init(GEMM_PARTIAL_FLOATS), "gemm_init")
+        _gemm_ready.add(dev)
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    splits = lib.exo_gemm_splits(M, N, K)
+    while splits > 1 and splits * M * N > GEMM_PARTIAL_FLOATS:
+        splits -= 1
+    _chk(lib.exo_gemm_bf16(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, N, splits, _st()),
+         "gemm_bf16")
+    _count()
+    return swiglu(out) if swiglu_out else out
+
+
+def gemm_check() -> None:
+    """Raise if any tensor-core kernel since the last check recorded a wait timeout."""
+    code = load().exo_gemm_last_error()
+    if code:
+        raise KernelError(f"tcgen05 GEMM reported device-side timeout code {code}")
+
+
+gemm_impl = None if os.environ.get("EXO_DISABLE_TCGEN05") == "1" else gemm_bf16
+
+
+def linear(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=False):
+    """Dispatch by batch rows: M <= 8 → fused small-batch kernel; bf16 larger M → tcgen05 GEMM;
+    fp32 larger M → CUDA-core tiled kernel (oracle configs only)."""
+    x = x.contiguous()
+    M, K = x.shape
+    N = w.shape[0]
+    lib = load()
+    if M <= SMALL_M:
+        out = torch.empty(M, N // 2 if swiglu_out else N, dtype=x.dtype, device=x.device)
+        if M:
+            _chk(lib.exo_linear_small(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), _ptr(norm_w), eps, M, N,
+                                      K, int(swiglu_out), _dt(x), _st()), "linear_small")
+            _count()
+        return out
+    if norm_w is not None:
+        x, _ = rmsnorm(x, norm_w, eps)
+    if x.dtype == torch.bfloat16 and gemm_impl is not None and K >= 64 and K % 8 == 0:
+        return gemm_impl(x, w, bias, residual, swiglu_out)
+    out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    _chk(lib.exo_linear_tiled(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, _dt(x), _st()),
+         "linear_tiled")
+    _count()
+    return swiglu(out) if swiglu_out else out
+
+
+def qk_rope_append(qkv, positions, inv_freq, mscale, n_q, n_kv, head_dim, kcache, vcache, slots, q_norm=None,
+                   k_norm=None, eps=1e-6):
+    qkv = qkv.contiguous()
+    T = qkv.shape[0]
+    q = torch.empty(T, n_q, head_dim, dtype=qkv.dtype, device=qkv.device)
+    rot = inv_freq.numel() * 2
+    _chk(load().exo_qk_rope_append(_ptr(qkv), _ptr(positions), _ptr(inv_freq), float(mscale), n_q, n_kv, head_dim, rot,
+                                   _ptr(q), _ptr(kcache), _ptr(vcache), _ptr(slots), _ptr(q_norm), _ptr(k_norm),
+                                   float(eps), T, _dt(qkv), _st()), "qk_rope_append")
+    _count()
+    return q
+
+
+_ws: dict[tuple, torch.Tensor] = {}
+
+
+def _workspace(dev: torch.device, n_floats: int) -> torch.Tensor:
+    key = (dev.index,)
+    t = _ws.get(key)
+    if t is None or t.numel() < n_floats:
+        t = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=dev)
+        _ws[key] = t
+    return t
+
+
+prefill_attention_impl = None  # set when the tensor-core prefill kernel is available
+
+
+def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, sliding_window=0, sinks=None,
+                    max_q_len=None):
+    lib = load()
+    q = q.contiguous()
+    T, Hq, D = q.shape
+    nblk, bs, Hkv, _ = kcache.shape
+    B = seq_lens.numel()
+    out = torch.empty_like(q)
+    max_blocks = block_tables.shape[1]
+    if max_q_len == 1 and T == B:
+        ns = lib.exo_paged_decode_splits(B, Hkv, max_blocks * bs)
+        ws = _workspace(q.device, lib.exo_paged_decode_workspace(B, Hq, D, ns))
+        _chk(lib.exo_paged_decode(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(seq_lens), _ptr(out),
+                                  _ptr(ws), float(scale), B, Hq, Hkv, D, max_blocks, bs, ns, int(sliding_window),
+                                  _ptr(sinks), _dt(q), _st()), "paged_decode")
+        _count(2)
+        return out
+    if (prefill_attention_impl is not None and q.dtype == torch.bfloat16 and sinks is None and not sliding_window
+            and D in (64, 128)):
+        return prefill_attention_impl(q, kcache, vcache, block_tables, seq_lens, cu_q, scale)
+    tok_seq = torch.empty(T, dtype=torch.int32, device=q.device)
+    _chk(lib.exo_token_seq(_ptr(cu_q), _ptr(tok_seq), B, _st()), "token_seq")
+    _chk(lib.exo_paged_ragged(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(seq_lens), _ptr(cu_q),
+                              _ptr(tok_seq), _ptr(out), float(scale), T, Hq, Hkv, D, max_blocks, bs,
+                              int(sliding_window), _ptr(sinks), _dt(q), _st()), "paged_ragged")
+    _count(2)
+    return out
+
+
+def argmax(logits):
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _chk(load().exo_argmax(_ptr(logits), _ptr(out), rows, V, logits.stride(0), _dt(logits), _st()), "argmax")
+    _count()
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, uniform):
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _chk(load().exo_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform),
+                           _ptr(out), rows, V, logits.stride(0), _dt(logits), _st()), "sample")
+    _count()
+    return out
+
+
+# ---- ops whose kernels are composed from the above / from torch on device for now ----------
+def mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora, max_q_len=None):
+    return ref.mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora)
+
+
+def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling):
+    return ref.moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling)
+
+
+def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0):
+    return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)

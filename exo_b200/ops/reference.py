@@ -259,11 +259,14 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     keep &= (cum - sp) < top_p.float()[:, None]
     keep &= sp >= min_p.float()[:, None] * sp[:, :1]
     keep[:, 0] = True
-    sp = sp * keep
-    cdf = sp.cumsum(-1)
+    # inverse CDF over the kept tokens in *vocabulary* order (what the device kernel does)
+    kept = torch.zeros_like(probs).scatter_(1, si, sp * keep)
+    cdf = kept.cumsum(-1)
     target = uniform.float()[:, None] * cdf[:, -1:]
-    pick = (cdf < target).sum(-1).clamp_max(V - 1)
-    sampled = si.gather(1, pick[:, None])[:, 0]
+    pick = (cdf <= target).sum(-1).clamp_max(V - 1)
+    # never return a filtered token (target == total mass lands past the last kept one)
+    last_kept = (V - 1) - (kept.flip(-1) > 0).float().argmax(-1)
+    sampled = torch.minimum(pick, last_kept)
     return torch.where(temperature <= 0, greedy, sampled)
 
 

@@ -1,0 +1,187 @@
+"""Each sm_100a kernel against the plain PyTorch fp32 definition of the same op."""
+import math
+
+import pytest
+import torch
+
+from exo_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from exo_b200.ops import cuda
+    cuda.load()
+    return cuda
+
+
+def close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    scale = b.abs().max().item()
+    assert err <= atol + rtol * scale, f"max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,cols", [(1, 4096), (5, 256), (33, 7168)])
+def test_rmsnorm(K, dtype, rows, cols):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(rows, cols, device="cuda", generator=g).to(dtype)
+    r = torch.randn(rows, cols, device="cuda", generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(cols, device="cuda", generator=g)).to(dtype)
+    o, h = K.rmsnorm(x, w, 1e-5, r)
+    ro, rh = ref.rmsnorm(x.float(), w.float(), 1e-5, r.float())
+    close(h, rh, 1e-2, 1e-2)
+    close(o, ro)
+    o2, _ = K.rmsnorm(x, w, 1e-5)
+    close(o2, ref.rmsnorm(x.float(), w.float(), 1e-5)[0])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K_", [(512, 256), (6144, 4096), (1001 * 2, 1024)])
+def test_linear_small(K, dtype, M, N, K_):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(M, K_, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(N, K_, device="cuda", generator=g) / math.sqrt(K_)).to(dtype)
+    b = torch.randn(N, device="cuda", generator=g).to(dtype)
+    r = torch.randn(M, N, device="cuda", generator=g).to(dtype)
+    nw = (1 + 0.1 * torch.randn(K_, device="cuda", generator=g)).to(dtype)
+    close(K.linear(x, w), ref.linear(x.float(), w.float()))
+    close(K.linear(x, w, b, r), ref.linear(x.float(), w.float(), b.float(), r.float()))
+    want = ref.linear(ref.rmsnorm(x.float(), nw.float(), 1e-5)[0], w.float())
+    close(K.linear(x, w, None, None, nw, 1e-5), want)
+    close(K.linear(x, w, None, None, nw, 1e-5, True), ref.swiglu(want))
+
+
+@pytest.mark.parametrize("M,N,K_", [(9, 256, 64), (16, 4096, 4096), (32, 6144, 4096), (48, 1024, 14336),
+                                     (100, 384, 512), (128, 4096, 1024), (300, 2048, 4096), (2048, 1536, 2048),
+                                     (17, 128256 // 8, 4096)])
+def test_gemm_tcgen05(K, M, N, K_):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(M, K_, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K_, device="cuda", generator=g) / math.sqrt(K_)).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g).bfloat16()
+    r = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    got = K.gemm_bf16(x, w)
+    K.gemm_check()
+    close(got, ref.linear(x.float(), w.float()))
+    got = K.gemm_bf16(x, w, b, r)
+    K.gemm_check()
+    close(got, ref.linear(x.float(), w.float(), b.float(), r.float()))
+    # in-place residual (out aliases residual is not used by the binding, but repeated calls must agree)
+    again = K.gemm_bf16(x, w, b, r)
+    assert torch.equal(got, again)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_linear_tiled_fp32_path(K, dtype):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(37, 200, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(91, 200, device="cuda", generator=g) / 14).to(dtype)
+    import exo_b200.ops.cuda as c
+    saved, c.gemm_impl = c.gemm_impl, None
+    try:
+        close(K.linear(x, w), ref.linear(x.float(), w.float()))
+    finally:
+        c.gemm_impl = saved
+
+
+def _paged_setup(dtype, B, Hq, Hkv, D, lens, qlens, bs=16, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    max_blocks = max(-(-n // bs) for n in lens) + 1
+    n_blocks = B * max_blocks + 1
+    kc = torch.randn(n_blocks, bs, Hkv, D, device="cuda", generator=g).to(dtype)
+    vc = torch.randn(n_blocks, bs, Hkv, D, device="cuda", generator=g).to(dtype)
+    perm = torch.randperm(n_blocks - 1, device="cuda", generator=g) + 1
+    bt = perm[: B * max_blocks].view(B, max_blocks).int()
+    T = sum(qlens)
+    q = torch.randn(T, Hq, D, device="cuda", generator=g).to(dtype)
+    cu = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), device="cuda", dtype=torch.int32)
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    return q, kc, vc, bt, sl, cu
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (4, 2, 64), (8, 1, 128), (16, 16, 64)])
+def test_paged_decode(K, dtype, Hq, Hkv, D):
+    lens = [1, 17, 300, 2049]
+    q, kc, vc, bt, sl, cu = _paged_setup(dtype, 4, Hq, Hkv, D, lens, [1] * 4)
+    got = K.paged_attention(q, kc, vc, bt, sl, cu, D ** -0.5, max_q_len=1)
+    want = ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, cu, D ** -0.5)
+    close(got, want)
+
+
+def test_paged_decode_window_and_sinks(K):
+    lens = [5, 200, 1000]
+    q, kc, vc, bt, sl, cu = _paged_setup(torch.bfloat16, 3, 8, 2, 64, lens, [1] * 3)
+    sinks = torch.randn(8, device="cuda")
+    got = K.paged_attention(q, kc, vc, bt, sl, cu, 0.125, sliding_window=128, sinks=sinks, max_q_len=1)
+    want = ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, cu, 0.125, 128, sinks)
+    close(got, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_paged_ragged_prefill(K, dtype):
+    lens, qlens = [40, 130, 64, 7], [40, 30, 1, 7]
+    q, kc, vc, bt, sl, cu = _paged_setup(dtype, 4, 8, 2, 64, lens, qlens)
+    got = K.paged_attention(q, kc, vc, bt, sl, cu, 0.125, max_q_len=40)
+    want = ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, cu, 0.125)
+    close(got, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("D,qknorm", [(128, False), (64, True), (128, True)])
+def test_qk_rope_append(K, dtype, D, qknorm):
+    from exo_b200.models.config import RopeConfig
+    g = torch.Generator(device="cuda").manual_seed(4)
+    T, nq, nkv, bs, nb = 19, 6, 2, 16, 8
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, device="cuda", generator=g).to(dtype)
+    pos = torch.randint(0, 5000, (T,), device="cuda", generator=g).int()
+    slots = (torch.randperm(nb * bs - bs, device="cuda", generator=g)[:T] + bs).int()
+    inv, ms = ref.rope_inv_freq(D, RopeConfig(theta=500000.0))
+    inv = inv.cuda()
+    kc = torch.zeros(nb, bs, nkv, D, device="cuda", dtype=dtype)
+    vc = torch.zeros_like(kc)
+    qn = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(dtype) if qknorm else None
+    kn = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(dtype) if qknorm else None
+    q = K.qk_rope_append(qkv, pos, inv, ms, nq, nkv, D, kc, vc, slots, qn, kn, 1e-6)
+    qf, kf, vf = qkv.float().split((nq * D, nkv * D, nkv * D), -1)
+    qf, kf, vf = qf.view(T, nq, D), kf.view(T, nkv, D), vf.view(T, nkv, D)
+    if qknorm:
+        qf, kf = ref.head_rmsnorm(qf, qn.float(), 1e-6), ref.head_rmsnorm(kf, kn.float(), 1e-6)
+    qf, kf = ref.rope(qf, pos, inv, ms), ref.rope(kf, pos, inv, ms)
+    close(q, qf)
+    close(kc.view(-1, nkv, D)[slots.long()], kf)
+    close(vc.view(-1, nkv, D)[slots.long()], vf, 1e-3, 1e-3)
+
+
+def test_swiglu_embedding_argmax(K):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    gu = torch.randn(7, 2 * 300, device="cuda", generator=g).bfloat16()
+    close(K.swiglu(gu), ref.swiglu(gu.float()))
+    table = torch.randn(1000, 256, device="cuda", generator=g).bfloat16()
+    ids = torch.randint(0, 1000, (33,), device="cuda", generator=g).int()
+    assert torch.equal(K.embedding(table, ids), table[ids.long()])
+    logits = torch.randn(9, 128256, device="cuda", generator=g).bfloat16()
+    assert torch.equal(K.argmax(logits).long(), logits.float().argmax(-1))
+
+
+@pytest.mark.parametrize("V", [1000, 32000, 128256])
+def test_sample_matches_reference(K, V):
+    g = torch.Generator(device="cuda").manual_seed(6)
+    B = 16
+    logits = (3 * torch.randn(B, V, device="cuda", generator=g)).float()
+    temp = torch.tensor([0.0, 0.7, 1.0, 1.3] * 4, device="cuda")
+    top_k = torch.tensor([0, 0, 50, 5] * 4, device="cuda", dtype=torch.int32)
+    top_p = torch.tensor([1.0, 0.9, 1.0, 0.5] * 4, device="cuda")
+    min_p = torch.tensor([0.0, 0.05, 0.0, 0.0] * 4, device="cuda")
+    u = torch.rand(B, device="cuda", generator=g)
+    got = K.sample(logits, temp, top_k, top_p, min_p, u).long()
+    want = ref.sample(logits, temp, top_k, top_p, min_p, u)
+    # fp ordering differences can move a draw that sits exactly on a CDF edge: allow one miss,
+    # and require that every sampled token is in the reference keep set
+    assert (got == want).sum().item() >= B - 1, (got, want)
+    probs = torch.softmax(logits / temp.clamp_min(1e-6)[:, None], -1)
+    assert (probs.gather(1, got[:, None]) > 0).all()
