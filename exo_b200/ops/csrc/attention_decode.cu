@@ -2,27 +2,33 @@
 //
 // Grid (n_splits, Hkv * (g / GT), B).  A CTA streams its slice of one KV head once and scores
 // it against GT query heads that share that KV head (GQA), so K/V bytes are read once per group.
-// Inside a warp, 8 lanes cooperate on one key (D/8 dims each) and 4 keys are in flight; every
-// (lane-group, head) keeps its own online-softmax state, merged at the end through shuffles and
-// shared memory.  Partials (m, l, o) go to a workspace and a second kernel merges the splits.
+// Inside a warp, 8 lanes cooperate on one key (D/8 dims each), 4 lane-groups x 2 keys are in
+// flight per iteration; every (lane-group, head) keeps its own online-softmax state, merged at the
+// end through shuffles and shared memory.  Each split publishes (m, l, o) partials to a workspace
+// and takes a ticket; the CTA that draws the last ticket of its (sequence, head group) merges the
+// splits and writes the output, so there is no second launch.
 #include "common.cuh"
 
 template <typename T, int D, int GT>
 __global__ void __launch_bounds__(128)
 paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                     const int* __restrict__ block_tables, const int* __restrict__ seq_lens,
-                    float* __restrict__ part_o, float* __restrict__ part_ml, float scale, int Hq, int Hkv,
-                    int max_blocks, int block_size, int window, const float* __restrict__ sinks) {
+                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
+                    T* __restrict__ out, float scale, int Hq, int Hkv, int max_blocks, int block_size, int window,
+                    const float* __restrict__ sinks) {
   constexpr int DPL = D / 8;  // dims per lane
+  constexpr int U = 2;        // keys per lane-group per iteration
   const int split = blockIdx.x, n_splits = gridDim.x, b = blockIdx.z;
   const int g = Hq / Hkv, tiles_per_kv = g / GT;
   const int kvh = blockIdx.y / tiles_per_kv, h0 = kvh * g + (blockIdx.y % tiles_per_kv) * GT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 3, ls = lane & 7;
+  pdl_trigger();
+  pdl_wait();  // q, the appended K/V row and the step inputs come from the preceding kernels
   const int n = seq_lens[b];
-  int lo_lim = (window > 0 && n > window) ? n - window : 0;
+  const int lo_lim = (window > 0 && n > window) ? n - window : 0;
   // chunk of keys for this split, in whole blocks
-  int per = ((n - lo_lim + n_splits - 1) / n_splits + block_size - 1) / block_size * block_size;
-  int t0 = lo_lim / block_size * block_size + split * per, t1 = min(n, t0 + per);
+  const int per = ((n - lo_lim + n_splits - 1) / n_splits + block_size - 1) / block_size * block_size;
+  const int t0 = lo_lim / block_size * block_size + split * per, t1 = min(n, t0 + per);
 
   float qr[GT][DPL], acc[GT][DPL], m[GT], l[GT];
 #pragma unroll
@@ -34,42 +40,51 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
     l[i] = 0.f;
   }
   const int* bt = block_tables + (size_t)b * max_blocks;
-  for (int base = t0 + warp * 4; base < t1; base += 16) {  // warp-uniform trip count
-    int t = base + lg;
-    bool valid = t < t1 && t >= lo_lim;
-    float kf[DPL], vf[DPL];
+  for (int base = t0 + warp * (4 * U); base < t1; base += 16 * U) {  // warp-uniform trip count
+    float kf[U][DPL], vf[U][DPL];
+    bool valid[U];
 #pragma unroll
-    for (int d = 0; d < DPL; d++) { kf[d] = 0.f; vf[d] = 0.f; }
-    if (valid) {
-      int blk = bt[t / block_size];
-      size_t off = (((size_t)blk * block_size + t % block_size) * Hkv + kvh) * D + ls * DPL;
-      if constexpr (sizeof(T) == 2) {
+    for (int u = 0; u < U; u++) {
+      int t = base + u * 4 + lg;
+      valid[u] = t < t1 && t >= lo_lim;
+      if (valid[u]) {
+        int blk = bt[t / block_size];
+        size_t off = (((size_t)blk * block_size + t % block_size) * Hkv + kvh) * D + ls * DPL;
+        if constexpr (sizeof(T) == 2) {
 #pragma unroll
-        for (int d = 0; d < DPL; d += 8) {
-          uint4 ku = *reinterpret_cast<const uint4*>(kcache + off + d);
-          uint4 vu = *reinterpret_cast<const uint4*>(vcache + off + d);
-          unpack8(ku, kf + d);
-          unpack8(vu, vf + d);
+          for (int d = 0; d < DPL; d += 8) {
+            unpack8(*reinterpret_cast<const uint4*>(kcache + off + d), kf[u] + d);
+            unpack8(*reinterpret_cast<const uint4*>(vcache + off + d), vf[u] + d);
+          }
+        } else {
+#pragma unroll
+          for (int d = 0; d < DPL; d++) { kf[u][d] = Cvt<T>::to_f(kcache[off + d]); vf[u][d] = Cvt<T>::to_f(vcache[off + d]); }
         }
       } else {
 #pragma unroll
-        for (int d = 0; d < DPL; d++) { kf[d] = Cvt<T>::to_f(kcache[off + d]); vf[d] = Cvt<T>::to_f(vcache[off + d]); }
+        for (int d = 0; d < DPL; d++) { kf[u][d] = 0.f; vf[u][d] = 0.f; }
       }
     }
 #pragma unroll
     for (int i = 0; i < GT; i++) {
-      float s = 0.f;
+      float s[U];
 #pragma unroll
-      for (int d = 0; d < DPL; d++) s += qr[i][d] * kf[d];
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      s += __shfl_xor_sync(0xffffffffu, s, 4);
-      if (valid) {
-        float mn = fmaxf(m[i], s);
-        float corr = __expf(m[i] - mn), p = __expf(s - mn);
-        l[i] = l[i] * corr + p;
+      for (int u = 0; u < U; u++) {
+        float a = 0.f;
 #pragma unroll
-        for (int d = 0; d < DPL; d++) acc[i][d] = acc[i][d] * corr + p * vf[d];
+        for (int d = 0; d < DPL; d++) a += qr[i][d] * kf[u][d];
+        a += __shfl_xor_sync(0xffffffffu, a, 1);
+        a += __shfl_xor_sync(0xffffffffu, a, 2);
+        a += __shfl_xor_sync(0xffffffffu, a, 4);
+        s[u] = valid[u] ? a : -INFINITY;
+      }
+      float mn = fmaxf(m[i], fmaxf(s[0], s[1]));
+      if (mn > -INFINITY) {
+        float corr = __expf(m[i] - mn);
+        float p0 = __expf(s[0] - mn), p1 = __expf(s[1] - mn);
+        l[i] = l[i] * corr + p0 + p1;
+#pragma unroll
+        for (int d = 0; d < DPL; d++) acc[i][d] = acc[i][d] * corr + p0 * vf[0][d] + p1 * vf[1][d];
         m[i] = mn;
       }
     }
@@ -94,6 +109,7 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
   // merge the 4 warps through shared memory
   __shared__ float sm_m[4][GT], sm_l[4][GT];
   __shared__ float sm_o[4][GT][D];
+  __shared__ int is_last;
   if (lg == 0) {
 #pragma unroll
     for (int i = 0; i < GT; i++) {
@@ -113,49 +129,67 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
       o += sm_o[w][i][d] * c;
       lt += sm_l[w][i] * c;
     }
-    size_t pi = ((size_t)b * Hq + h0 + i) * n_splits + split;
-    part_o[pi * D + d] = o;
-    if (d == 0) { part_ml[pi * 2] = mn; part_ml[pi * 2 + 1] = lt; }
+    if (n_splits == 1) {  // nothing to merge across CTAs: finish here
+      float sink = 0.f;
+      if (sinks) { float sk = sinks[h0 + i], m2 = fmaxf(mn, sk); o *= __expf(mn - m2); lt = lt * __expf(mn - m2) + __expf(sk - m2); }
+      (void)sink;
+      out[((size_t)b * Hq + h0 + i) * D + d] = Cvt<T>::from_f(lt > 0.f ? o / lt : 0.f);
+    } else {
+      size_t pi = ((size_t)b * Hq + h0 + i) * n_splits + split;
+      part_o[pi * D + d] = o;
+      if (d == 0) { part_ml[pi * 2] = mn; part_ml[pi * 2 + 1] = lt; }
+    }
+  }
+  if (n_splits == 1) return;
+  // ticket: the last split of this (sequence, head group) to finish merges all of them
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* tk = tickets + (size_t)b * gridDim.y + blockIdx.y;
+    int t = atomicAdd(tk, 1);
+    is_last = (t == n_splits - 1);
+    if (is_last) *tk = 0;  // self-reset for the next launch / graph replay
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < GT * D; idx += blockDim.x) {
+    int i = idx / D, d = idx % D;
+    size_t bh = (size_t)b * Hq + h0 + i;
+    float mn = -INFINITY;
+    for (int s2 = 0; s2 < n_splits; s2++) mn = fmaxf(mn, __ldcg(part_ml + (bh * n_splits + s2) * 2));
+    float lsum = 0.f;
+    if (sinks) { float sk = sinks[h0 + i]; mn = fmaxf(mn, sk); lsum = __expf(sk - mn); }
+    float o = 0.f;
+    for (int s2 = 0; s2 < n_splits; s2++) {
+      float ms = __ldcg(part_ml + (bh * n_splits + s2) * 2);
+      float c = (ms == -INFINITY) ? 0.f : __expf(ms - mn);
+      o += __ldcg(part_o + (bh * n_splits + s2) * D + d) * c;
+      lsum += __ldcg(part_ml + (bh * n_splits + s2) * 2 + 1) * c;
+    }
+    out[bh * D + d] = Cvt<T>::from_f(lsum > 0.f ? o / lsum : 0.f);
   }
 }
 
-template <typename T, int D>
-__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    T* __restrict__ out, int n_splits, const float* __restrict__ sinks, int Hq) {
-  size_t bh = blockIdx.x;
-  int d = threadIdx.x;
-  float mn = -INFINITY;
-  for (int s = 0; s < n_splits; s++) mn = fmaxf(mn, part_ml[(bh * n_splits + s) * 2]);
-  float sink = 0.f;
-  if (sinks) { float sk = sinks[bh % Hq]; mn = fmaxf(mn, sk); sink = __expf(sk - mn); }
-  float o = 0.f, l = sink;
-  for (int s = 0; s < n_splits; s++) {
-    float ms = part_ml[(bh * n_splits + s) * 2];
-    float c = (ms == -INFINITY) ? 0.f : __expf(ms - mn);
-    o += part_o[(bh * n_splits + s) * D + d] * c;
-    l += part_ml[(bh * n_splits + s) * 2 + 1] * c;
-  }
-  out[bh * D + d] = Cvt<T>::from_f(l > 0.f ? o / l : 0.f);
-}
-
-// workspace floats needed: B*Hq*n_splits*(D+2)
+// workspace floats needed: partial outputs + (m, l) pairs + one ticket word per (sequence, head group)
 EXO_API long exo_paged_decode_workspace(int B, int Hq, int D, int n_splits) {
-  return (long)B * Hq * n_splits * (D + 2);
+  return (long)B * Hq * n_splits * (D + 2) + (long)B * Hq + 64;
 }
 
 EXO_API int exo_paged_decode_splits(int B, int Hkv, int max_len) {
-  int want = (2 * 148 + B * Hkv - 1) / (B * Hkv);
-  int cap = (max_len + 63) / 64;
+  int want = (4 * 148 + B * Hkv - 1) / (B * Hkv);
+  int cap = (max_len + 127) / 128;
   int s = want < cap ? want : cap;
   if (s < 1) s = 1;
   if (s > 64) s = 64;
   return s;
 }
 
+// `tickets` must be zero before the first launch (the kernel leaves it zero afterwards).
 EXO_API int exo_paged_decode(const void* q, const void* kcache, const void* vcache, const int* block_tables,
-                             const int* seq_lens, void* out, float* workspace, float scale, int B, int Hq, int Hkv,
-                             int D, int max_blocks, int block_size, int n_splits, int window, const float* sinks,
-                             int dtype, cudaStream_t st) {
+                             const int* seq_lens, void* out, float* workspace, int* tickets, float scale, int B, int Hq,
+                             int Hkv, int D, int max_blocks, int block_size, int n_splits, int window,
+                             const float* sinks, int dtype, cudaStream_t st) {
   if (B == 0) return 0;
   int g = Hq / Hkv;
   if (g * Hkv != Hq) return -2;
@@ -163,10 +197,11 @@ EXO_API int exo_paged_decode(const void* q, const void* kcache, const void* vcac
   float* part_ml = workspace + (size_t)B * Hq * n_splits * D;
   int GT = (g % 4 == 0) ? 4 : (g % 2 == 0 ? 2 : 1);
   dim3 grid(n_splits, Hkv * (g / GT), B);
-#define LAUNCH(TT, DD, GG)                                                                                         \
-  paged_decode_kernel<TT, DD, GG><<<grid, 128, 0, st>>>((const TT*)q, (const TT*)kcache, (const TT*)vcache,         \
-                                                        block_tables, seq_lens, part_o, part_ml, scale, Hq, Hkv,    \
-                                                        max_blocks, block_size, window, sinks)
+  cudaError_t e = cudaSuccess;
+#define LAUNCH(TT, DD, GG)                                                                                        \
+  e = launch_pdl(paged_decode_kernel<TT, DD, GG>, grid, dim3(128), 0, st, (const TT*)q, (const TT*)kcache,         \
+                 (const TT*)vcache, block_tables, seq_lens, part_o, part_ml, tickets, (TT*)out, scale, Hq, Hkv,    \
+                 max_blocks, block_size, window, sinks)
 #define BY_G(TT, DD)                       \
   if (GT == 4) LAUNCH(TT, DD, 4);          \
   else if (GT == 2) LAUNCH(TT, DD, 2);     \
@@ -180,16 +215,9 @@ EXO_API int exo_paged_decode(const void* q, const void* kcache, const void* vcac
     else if (D == 64) { BY_G(float, 64); }
     else return -2;
   }
-  EXO_CHECK_LAUNCH();
-  if (dtype == EXO_BF16) {
-    if (D == 128) decode_merge_kernel<__nv_bfloat16, 128><<<B * Hq, 128, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits, sinks, Hq);
-    else decode_merge_kernel<__nv_bfloat16, 64><<<B * Hq, 64, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits, sinks, Hq);
-  } else {
-    if (D == 128) decode_merge_kernel<float, 128><<<B * Hq, 128, 0, st>>>(part_o, part_ml, (float*)out, n_splits, sinks, Hq);
-    else decode_merge_kernel<float, 64><<<B * Hq, 64, 0, st>>>(part_o, part_ml, (float*)out, n_splits, sinks, Hq);
-  }
 #undef BY_G
 #undef LAUNCH
+  if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
   return 0;
 }

@@ -189,25 +189,31 @@ EXO_API int exo_qk_rope_append(const void* qkv, const int* positions, const floa
 }
 
 // ------------------------------------------------------------------------------------------
-// argmax over the last dim.  One CTA per row.  Ties resolve to the lowest index.
+// argmax over the last dim, two stages: grid (chunks, rows) finds per-chunk maxima, one warp per row
+// merges them.  Ties resolve to the lowest index.
 // ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void argmax_combine(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+}
+
 template <typename T>
-__global__ void argmax_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, size_t stride) {
+__global__ void argmax_partial_kernel(const T* __restrict__ logits, float* __restrict__ pv, int* __restrict__ pi,
+                                      int V, size_t stride, int chunk) {
   __shared__ float sv[32];
   __shared__ int si[32];
-  const T* row = logits + (size_t)blockIdx.x * stride;
+  pdl_trigger();
+  pdl_wait();
+  const T* row = logits + (size_t)blockIdx.y * stride;
+  int c0 = blockIdx.x * chunk, c1 = min(V, c0 + chunk);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int c = threadIdx.x; c < V; c += blockDim.x) {
+  for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
     float v = Cvt<T>::to_f(row[c]);
     if (v > best) { best = v; bi = c; }
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-  }
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_combine(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
   int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   if (l == 0) { sv[w] = best; si[w] = bi; }
   __syncthreads();
@@ -216,21 +222,49 @@ __global__ void argmax_kernel(const T* __restrict__ logits, int* __restrict__ ou
     best = l < nw ? sv[l] : -INFINITY;
     bi = l < nw ? si[l] : 0x7fffffff;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (l == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    for (int o = 16; o > 0; o >>= 1)
+      argmax_combine(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if (l == 0) { pv[blockIdx.y * gridDim.x + blockIdx.x] = best; pi[blockIdx.y * gridDim.x + blockIdx.x] = bi; }
   }
 }
 
-EXO_API int exo_argmax(const void* logits, int* out, int rows, int V, long stride, int dtype, cudaStream_t st) {
+__global__ void argmax_merge_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int* __restrict__ out,
+                                    int chunks) {
+  pdl_trigger();
+  pdl_wait();
+  int row = blockIdx.x, l = threadIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = l; c < chunks; c += 32) argmax_combine(best, bi, pv[row * chunks + c], pi[row * chunks + c]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_combine(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if (l == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+}
+
+EXO_API int exo_argmax_chunks(int rows, int V) {
+  int c = (4 * 148 + rows - 1) / rows;
+  int cap = (V + 1023) / 1024;
+  c = c < cap ? c : cap;
+  return c < 1 ? 1 : (c > 256 ? 256 : c);
+}
+
+// scratch: chunks*rows floats (pv) and chunks*rows ints (pi)
+EXO_API int exo_argmax(const void* logits, int* out, float* pv, int* pi, int chunks, int rows, int V, long stride,
+                       int dtype, cudaStream_t st) {
   if (rows == 0) return 0;
+  int chunk = (V + chunks - 1) / chunks;
+  dim3 grid(chunks, rows);
+  cudaError_t e;
   if (dtype == EXO_BF16)
-    argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, st>>>((const __nv_bfloat16*)logits, out, V, (size_t)stride);
+    e = launch_pdl(argmax_partial_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, (const __nv_bfloat16*)logits, pv, pi,
+                   V, (size_t)stride, chunk);
   else
-    argmax_kernel<float><<<rows, 1024, 0, st>>>((const float*)logits, out, V, (size_t)stride);
+    e = launch_pdl(argmax_partial_kernel<float>, grid, dim3(256), 0, st, (const float*)logits, pv, pi, V,
+                   (size_t)stride, chunk);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_pdl(argmax_merge_kernel, dim3(rows), dim3(32), 0, st, (const float*)pv, (const int*)pi, out, chunks);
+  if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
   return 0;
 }

@@ -47,7 +47,7 @@ struct Smem {
 };
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, (BN <= 128 ? 2 : 1))
 gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -313,8 +313,10 @@ EXO_API int exo_gemm_splits(int M, int N, int K) {
   int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   long tiles = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
   int kb = (K + BK - 1) / BK;
-  if (tiles >= 120 || kb < 8) return 1;
-  int s = (int)((148 + tiles - 1) / tiles);
+  // two CTAs are co-resident per SM (BN <= 128): aim for ~296 CTAs so every SM streams weights
+  int target = bn <= 128 ? 296 : 148;
+  if (tiles * 4 >= target * 3 || kb < 8) return 1;
+  int s = (int)((target + tiles / 2) / tiles);
   if (s > kb / 4) s = kb / 4;
   if (s > 16) s = 16;
   return s < 1 ? 1 : s;
@@ -351,10 +353,10 @@ EXO_API int exo_gemm_bf16(const void* x, const void* W, const void* bias, const 
     if ((size_t)splits * M * N > g_partial_floats[dev] || tiles > MAX_TILES) return -6;
   }
   switch (bn) {
-    case 16: return launch_gemm<16, 8>(tw, tx, p, st);
-    case 32: return launch_gemm<32, 8>(tw, tx, p, st);
-    case 64: return launch_gemm<64, 8>(tw, tx, p, st);
-    case 128: return launch_gemm<128, 6>(tw, tx, p, st);
-    default: return launch_gemm<256, 4>(tw, tx, p, st);
+    case 16: return launch_gemm<16, 5>(tw, tx, p, st);   //  5 x 18 KB
+    case 32: return launch_gemm<32, 5>(tw, tx, p, st);   //  5 x 20 KB
+    case 64: return launch_gemm<64, 4>(tw, tx, p, st);   //  4 x 24 KB
+    case 128: return launch_gemm<128, 3>(tw, tx, p, st); //  3 x 32 KB  (two CTAs per SM)
+    default: return launch_gemm<256, 4>(tw, tx, p, st);  //  4 x 48 KB  (one CTA per SM)
   }
 }

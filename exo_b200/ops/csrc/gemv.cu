@@ -16,6 +16,7 @@ template <> struct Vec16<__nv_bfloat16> {
   static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
     unpack8(*reinterpret_cast<const uint4*>(p), f);
   }
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) { unpack8(u, f); }
 };
 template <> struct Vec16<float> {
   static constexpr int N = 4;
@@ -27,31 +28,55 @@ template <> struct Vec16<float> {
     float4 u = *reinterpret_cast<const float4*>(p);
     f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
   }
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
 };
 
-template <typename T, int M, bool NORM, bool SWIGLU>
+template <typename T, int M, int R, bool NORM, bool SWIGLU>
 __global__ void __launch_bounds__(128)
 linear_small_kernel(const T* __restrict__ x, const T* __restrict__ W, const T* __restrict__ bias,
-                    const T* residual, T* out, const T* __restrict__ norm_w, float eps, int N, int K, int n_pairs,
+                    const T* residual, T* out, const T* __restrict__ norm_w, float eps, int N, int K, int n_groups,
                     int ldo) {
   constexpr int V = Vec16<T>::N;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= n_pairs) return;
-  // rows handled by this warp
-  int r0, r1;
-  if (SWIGLU) { r0 = warp; r1 = warp + N / 2; }
-  else { r0 = 2 * warp; r1 = min(2 * warp + 1, N - 1); }
-  const T* w0 = W + (size_t)r0 * K;
-  const T* w1 = W + (size_t)r1 * K;
-  float a0[M], a1[M], ss[M];
+  pdl_trigger();  // the next kernel in the stream may begin launching (it waits before reading our output)
+  if (warp >= n_groups) return;
+  // output rows of this warp: R consecutive rows, or R/2 (gate, up) pairs when SWIGLU
+  int rows[R];
+  const int F = N / 2;
 #pragma unroll
-  for (int m = 0; m < M; m++) { a0[m] = 0.f; a1[m] = 0.f; ss[m] = 0.f; }
-#pragma unroll 2
-  for (int k = lane * V; k < K; k += 32 * V) {
-    float f0[V], f1[V], nw[V];
-    Vec16<T>::load_stream(w0 + k, f0);
-    Vec16<T>::load_stream(w1 + k, f1);
+  for (int i = 0; i < R; i++) {
+    if (SWIGLU) rows[i] = min(warp * (R / 2) + i / 2, F - 1) + (i & 1) * F;
+    else rows[i] = min(warp * R + i, N - 1);
+  }
+  const T* wp[R];
+#pragma unroll
+  for (int i = 0; i < R; i++) wp[i] = W + (size_t)rows[i] * K;
+  float acc[R][M], ss[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) {
+    ss[m] = 0.f;
+#pragma unroll
+    for (int i = 0; i < R; i++) acc[i][m] = 0.f;
+  }
+  // software pipeline: weights for step k+1 are in flight while step k is consumed; the very first
+  // batch is issued BEFORE waiting on the producer of x, so weight streaming overlaps its tail.
+  int k = lane * V;
+  uint4 cur[R];
+#pragma unroll
+  for (int i = 0; i < R; i++) cur[i] = k < K ? ld_stream16(wp[i] + k) : make_uint4(0, 0, 0, 0);
+  pdl_wait();
+  for (; k < K; k += 32 * V) {
+    uint4 nxt[R];
+    const int kn = k + 32 * V;
+#pragma unroll
+    for (int i = 0; i < R; i++) nxt[i] = kn < K ? ld_stream16(wp[i] + kn) : make_uint4(0, 0, 0, 0);
+    float nw[V];
     if (NORM) Vec16<T>::load(norm_w + k, nw);
+    float wf[R][V];
+#pragma unroll
+    for (int i = 0; i < R; i++) Vec16<T>::unpack(cur[i], wf[i]);
 #pragma unroll
     for (int m = 0; m < M; m++) {
       float xf[V];
@@ -60,30 +85,37 @@ linear_small_kernel(const T* __restrict__ x, const T* __restrict__ W, const T* _
       for (int j = 0; j < V; j++) {
         float xv = xf[j];
         if (NORM) { ss[m] += xv * xv; xv *= nw[j]; }
-        a0[m] += f0[j] * xv;
-        a1[m] += f1[j] * xv;
+#pragma unroll
+        for (int i = 0; i < R; i++) acc[i][m] += wf[i][j] * xv;
       }
     }
+#pragma unroll
+    for (int i = 0; i < R; i++) cur[i] = nxt[i];
   }
 #pragma unroll
   for (int m = 0; m < M; m++) {
-    float y0 = warp_sum(a0[m]), y1 = warp_sum(a1[m]);
-    if (NORM) {
-      float rstd = rsqrtf(warp_sum(ss[m]) / K + eps);
-      y0 *= rstd;
-      y1 *= rstd;
-    }
+    float rstd = 1.f;
+    if (NORM) rstd = rsqrtf(warp_sum(ss[m]) / K + eps);
+    float y[R];
+#pragma unroll
+    for (int i = 0; i < R; i++) y[i] = warp_sum(acc[i][m]) * rstd;
     if (lane == 0) {
-      if (bias) { y0 += Cvt<T>::to_f(bias[r0]); y1 += Cvt<T>::to_f(bias[r1]); }
+#pragma unroll
+      for (int i = 0; i < R; i++)
+        if (bias) y[i] += Cvt<T>::to_f(bias[rows[i]]);
       if (SWIGLU) {
-        out[(size_t)m * ldo + r0] = Cvt<T>::from_f(silu_f(y0) * y1);
+#pragma unroll
+        for (int i = 0; i < R; i += 2)
+          if (warp * (R / 2) + i / 2 < F) out[(size_t)m * ldo + rows[i]] = Cvt<T>::from_f(silu_f(y[i]) * y[i + 1]);
       } else {
-        if (residual) {
-          y0 += Cvt<T>::to_f(residual[(size_t)m * ldo + r0]);
-          y1 += Cvt<T>::to_f(residual[(size_t)m * ldo + r1]);
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+          if (warp * R + i < N) {
+            float v = y[i];
+            if (residual) v += Cvt<T>::to_f(residual[(size_t)m * ldo + rows[i]]);
+            out[(size_t)m * ldo + rows[i]] = Cvt<T>::from_f(v);
+          }
         }
-        out[(size_t)m * ldo + r0] = Cvt<T>::from_f(y0);
-        if (r1 != r0) out[(size_t)m * ldo + r1] = Cvt<T>::from_f(y1);
       }
     }
   }
@@ -92,17 +124,18 @@ linear_small_kernel(const T* __restrict__ x, const T* __restrict__ W, const T* _
 template <typename T, int M>
 static int launch_small(const void* x, const void* W, const void* bias, const void* residual, void* out,
                         const void* norm_w, float eps, int N, int K, int swiglu, cudaStream_t st) {
-  int n_pairs = swiglu ? N / 2 : (N + 1) / 2;
-  int blocks = (n_pairs + 3) / 4;
+  constexpr int R = M <= 4 ? 4 : 2;
+  int n_groups = swiglu ? (N / 2 + R / 2 - 1) / (R / 2) : (N + R - 1) / R;
+  int blocks = (n_groups + 3) / 4;
   int ldo = swiglu ? N / 2 : N;
-#define L(NORM, SW)                                                                                              \
-  linear_small_kernel<T, M, NORM, SW><<<blocks, 128, 0, st>>>((const T*)x, (const T*)W, (const T*)bias,            \
-                                                              (const T*)residual, (T*)out, (const T*)norm_w, eps, \
-                                                              N, K, n_pairs, ldo)
+  cudaError_t e;
+#define L(NORM, SW)                                                                                             \
+  e = launch_pdl(linear_small_kernel<T, M, R, NORM, SW>, dim3(blocks), dim3(128), 0, st, (const T*)x, (const T*)W, \
+                 (const T*)bias, (const T*)residual, (T*)out, (const T*)norm_w, eps, N, K, n_groups, ldo)
   if (norm_w) { if (swiglu) L(true, true); else L(true, false); }
   else { if (swiglu) L(false, true); else L(false, false); }
 #undef L
-  return 0;
+  return (int)e;
 }
 
 // y[M,N] = f(x[M,K]) W[N,K]^T ; M in 1..8.  norm_w != null → RMSNorm prologue.  swiglu != 0 → out is [M, N/2].
@@ -113,19 +146,21 @@ EXO_API int exo_linear_small(const void* x, const void* W, const void* bias, con
   int vec = dtype == EXO_BF16 ? 8 : 4;
   if (K % vec != 0) return -2;
   if (swiglu && (N % 2)) return -2;
-#define BY_M(T)                                                                                   \
-  switch (M) {                                                                                    \
-    case 1: launch_small<T, 1>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
-    case 2: launch_small<T, 2>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
-    case 3: launch_small<T, 3>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
-    case 4: launch_small<T, 4>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
-    case 5: launch_small<T, 5>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
-    case 6: launch_small<T, 6>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
-    case 7: launch_small<T, 7>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
-    default: launch_small<T, 8>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break; \
+  int rc = 0;
+#define BY_M(T)                                                                                        \
+  switch (M) {                                                                                         \
+    case 1: rc = launch_small<T, 1>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 2: rc = launch_small<T, 2>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 3: rc = launch_small<T, 3>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 4: rc = launch_small<T, 4>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 5: rc = launch_small<T, 5>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 6: rc = launch_small<T, 6>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    case 7: rc = launch_small<T, 7>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break;  \
+    default: rc = launch_small<T, 8>(x, W, bias, residual, out, norm_w, eps, N, K, swiglu, st); break; \
   }
   if (dtype == EXO_BF16) { BY_M(__nv_bfloat16) } else { BY_M(float) }
 #undef BY_M
+  if (rc) return rc;
   EXO_CHECK_LAUNCH();
   return 0;
 }

@@ -46,11 +46,12 @@ class _Sig:
     exo_swiglu = (_i, [_p, _p, _i, _i, _i, _p])
     exo_embedding = (_i, [_p, _p, _p, _i, _i, _i, _i, _p])
     exo_qk_rope_append = (_i, [_p, _p, _p, _f, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _f, _i, _i, _p])
-    exo_argmax = (_i, [_p, _p, _i, _i, _l, _i, _p])
+    exo_argmax_chunks = (_i, [_i, _i])
+    exo_argmax = (_i, [_p, _p, _p, _p, _i, _i, _i, _l, _i, _p])
     exo_sample = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _l, _i, _p])
     exo_paged_decode_workspace = (_l, [_i, _i, _i, _i])
     exo_paged_decode_splits = (_i, [_i, _i, _i])
-    exo_paged_decode = (_i, [_p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
+    exo_paged_decode = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
     exo_token_seq = (_i, [_p, _p, _i, _p])
     exo_paged_ragged = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
     exo_linear_small = (_i, [_p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _p])
@@ -194,6 +195,7 @@ def qk_rope_append(qkv, positions, inv_freq, mscale, n_q, n_kv, head_dim, kcache
 
 
 _ws: dict[tuple, torch.Tensor] = {}
+_tickets: dict[int | None, torch.Tensor] = {}
 
 
 def _workspace(dev: torch.device, n_floats: int) -> torch.Tensor:
@@ -220,10 +222,13 @@ def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, slid
     if max_q_len == 1 and T == B:
         ns = lib.exo_paged_decode_splits(B, Hkv, max_blocks * bs)
         ws = _workspace(q.device, lib.exo_paged_decode_workspace(B, Hq, D, ns))
+        tk = _tickets.get(q.device.index)
+        if tk is None or tk.numel() < B * Hq:
+            tk = _tickets[q.device.index] = torch.zeros(max(B * Hq, 1 << 14), dtype=torch.int32, device=q.device)
         _chk(lib.exo_paged_decode(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(seq_lens), _ptr(out),
-                                  _ptr(ws), float(scale), B, Hq, Hkv, D, max_blocks, bs, ns, int(sliding_window),
-                                  _ptr(sinks), _dt(q), _st()), "paged_decode")
-        _count(2)
+                                  _ptr(ws), _ptr(tk), float(scale), B, Hq, Hkv, D, max_blocks, bs, ns,
+                                  int(sliding_window), _ptr(sinks), _dt(q), _st()), "paged_decode")
+        _count()
         return out
     if (prefill_attention_impl is not None and q.dtype == torch.bfloat16 and sinks is None and not sliding_window
             and D in (64, 128)):
@@ -240,8 +245,13 @@ def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, slid
 def argmax(logits):
     rows, V = logits.shape
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    _chk(load().exo_argmax(_ptr(logits), _ptr(out), rows, V, logits.stride(0), _dt(logits), _st()), "argmax")
-    _count()
+    lib = load()
+    chunks = lib.exo_argmax_chunks(rows, V)
+    pv = torch.empty(rows * chunks, dtype=torch.float32, device=logits.device)
+    pi = torch.empty(rows * chunks, dtype=torch.int32, device=logits.device)
+    _chk(lib.exo_argmax(_ptr(logits), _ptr(out), _ptr(pv), _ptr(pi), chunks, rows, V, logits.stride(0), _dt(logits),
+                        _st()), "argmax")
+    _count(2)
     return out
 
 

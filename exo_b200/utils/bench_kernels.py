@@ -1,0 +1,120 @@
+"""Micro-benchmarks of the individual sm_100a kernels against the measured roofline.
+
+    python -m exo_b200.utils.bench_kernels [--only gemv,gemm,attn,prefill] [--peaks MEASURED_PEAKS.json]
+
+Every case is timed with CUDA events after warm-up; a 256 MB buffer is overwritten between
+iterations so that no operand survives in the 126 MB L2.  Output: achieved GB/s or TFLOP/s and
+the fraction of the measured copy bandwidth / cuBLAS bf16 throughput.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+from pathlib import Path
+
+import torch
+
+from ..ops import cuda as K
+from ..ops import reference as ref
+
+
+def timeit(fn, iters: int = 10, warm: int = 3) -> float:
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(iters):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return best  # ms
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="gemv,gemm,attn,prefill,misc")
+    ap.add_argument("--peaks", default=str(Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"))
+    a = ap.parse_args()
+    hbm, tf, basis = 6650.0, 1590.0, "fallback"
+    try:
+        p = json.loads(Path(a.peaks).read_text())
+        hbm, tf, basis = p["hbm_gbs"], p["bf16_tflops"], "measured"
+    except (OSError, KeyError, ValueError):
+        pass
+    only = set(a.only.split(","))
+    K.load()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    bf = torch.bfloat16
+
+    def rnd(*s):
+        return (torch.randn(*s, device="cuda", generator=g) * 0.05).to(bf)
+
+    print(f"roofline basis: HBM {hbm:.0f} GB/s, bf16 {tf:.0f} TFLOP/s ({basis})")
+    if "gemv" in only:
+        for M in (1, 4, 8):
+            for N, Kd in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (16032, 4096), (4096, 512)):
+                x, w = rnd(M, Kd), rnd(N, Kd)
+                nw = rnd(Kd)
+                ms = timeit(lambda: K.linear(x, w, None, None, nw, 1e-5))
+                gb = N * Kd * 2 / 1e9
+                print(f"gemv M={M} N={N} K={Kd}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s  "
+                      f"{gb / ms * 1e3 / hbm:5.2f} of {basis} HBM")
+    if "gemm" in only:
+        for M in (16, 32, 64, 128, 256, 2048, 4096):
+            for N, Kd in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)):
+                x, w = rnd(M, Kd), rnd(N, Kd)
+                ms = timeit(lambda: K.gemm_bf16(x, w))
+                gb = (N * Kd + M * Kd + M * N) * 2 / 1e9
+                fl = 2.0 * M * N * Kd / 1e12
+                print(f"gemm M={M} N={N} K={Kd}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s ({gb / ms * 1e3 / hbm:4.2f})  "
+                      f"{fl / ms * 1e3:7.1f} TFLOP/s ({fl / ms * 1e3 / tf:4.2f}) of {basis}")
+        K.gemm_check()
+    if "attn" in only:
+        Hq, Hkv, D, bs = 32, 8, 128, 16
+        for B, ctx in ((1, 2048), (1, 8192), (32, 2048), (64, 4096)):
+            nb = B * (ctx // bs + 1) + 1
+            kc, vc = rnd(nb, bs, Hkv, D), rnd(nb, bs, Hkv, D)
+            bt = (torch.arange(B * (ctx // bs + 1), device="cuda", dtype=torch.int32) + 1).view(B, -1)
+            sl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+            cu = torch.arange(B + 1, device="cuda", dtype=torch.int32)
+            q = rnd(B, Hq, D)
+            ms = timeit(lambda: K.paged_attention(q, kc, vc, bt, sl, cu, D ** -0.5, max_q_len=1))
+            gb = B * ctx * Hkv * D * 2 * 2 / 1e9
+            print(f"decode-attn B={B} ctx={ctx}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s  "
+                  f"{gb / ms * 1e3 / hbm:5.2f} of {basis} HBM")
+    if "prefill" in only:
+        Hq, Hkv, D, bs = 32, 8, 128, 16
+        for T in (512, 2048, 4096):
+            nb = T // bs + 2
+            kc, vc = rnd(nb, bs, Hkv, D), rnd(nb, bs, Hkv, D)
+            bt = (torch.arange(nb - 1, device="cuda", dtype=torch.int32) + 1).view(1, -1)
+            sl = torch.tensor([T], device="cuda", dtype=torch.int32)
+            cu = torch.tensor([0, T], device="cuda", dtype=torch.int32)
+            q = rnd(T, Hq, D)
+            ms = timeit(lambda: K.paged_attention(q, kc, vc, bt, sl, cu, D ** -0.5, max_q_len=T), iters=5)
+            fl = 4.0 * T * T * Hq * D / 2 / 1e12
+            print(f"prefill-attn T={T}: {ms * 1e3:8.1f} us  {fl / ms * 1e3:7.1f} TFLOP/s (causal)  "
+                  f"{fl / ms * 1e3 / tf:5.2f} of {basis} bf16")
+    if "misc" in only:
+        logits = rnd(32, 128256)
+        print(f"argmax 32x128256: {timeit(lambda: K.argmax(logits)) * 1e3:.1f} us")
+        one = rnd(1, 128256)
+        print(f"argmax 1x128256: {timeit(lambda: K.argmax(one)) * 1e3:.1f} us")
+        t = torch.full((32,), 0.7, device="cuda")
+        tk = torch.zeros(32, device="cuda", dtype=torch.int32)
+        tp = torch.full((32,), 0.9, device="cuda")
+        mp = torch.full((32,), 0.05, device="cuda")
+        u = torch.rand(32, device="cuda")
+        print(f"sample 32x128256: {timeit(lambda: K.sample(logits, t, tk, tp, mp, u)) * 1e3:.1f} us")
+        x, w = rnd(32, 4096), rnd(4096)
+        print(f"rmsnorm 32x4096: {timeit(lambda: K.rmsnorm(x, w, 1e-5, x)) * 1e3:.1f} us")
+
+
+if __name__ == "__main__":
+    main()
