@@ -27,8 +27,9 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
   const int n = seq_lens[b];
   const int lo_lim = (window > 0 && n > window) ? n - window : 0;
   // chunk of keys for this split, in whole blocks
-  const int per = ((n - lo_lim + n_splits - 1) / n_splits + block_size - 1) / block_size * block_size;
-  const int t0 = lo_lim / block_size * block_size + split * per, t1 = min(n, t0 + per);
+  const int start = lo_lim / block_size * block_size;
+  const int per = ((n - start + n_splits - 1) / n_splits + block_size - 1) / block_size * block_size;
+  const int t0 = start + split * per, t1 = min(n, t0 + per);
 
   float qr[GT][DPL], acc[GT][DPL], m[GT], l[GT];
 #pragma unroll
@@ -153,21 +154,59 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // parallel merge: one thread per (head, split) turns its (m, l) into a normalised weight, then
+  // every thread accumulates its output dims with the split loads unrolled (independent loads)
+  __shared__ float wgt[GT][64];
+  __shared__ float hm[GT], hl[GT];
+  for (int idx = threadIdx.x; idx < GT * 64; idx += blockDim.x) {
+    int i = idx / 64, s2 = idx % 64;
+    size_t bh = (size_t)b * Hq + h0 + i;
+    wgt[i][s2] = s2 < n_splits ? __ldcg(part_ml + (bh * n_splits + s2) * 2) : -INFINITY;
+  }
+  __syncthreads();
+  if (threadIdx.x < GT) {
+    int i = threadIdx.x;
+    float mn = -INFINITY;
+    for (int s2 = 0; s2 < n_splits; s2++) mn = fmaxf(mn, wgt[i][s2]);
+    if (sinks) mn = fmaxf(mn, sinks[h0 + i]);
+    hm[i] = mn;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < GT * 64; idx += blockDim.x) {
+    int i = idx / 64, s2 = idx % 64;
+    size_t bh = (size_t)b * Hq + h0 + i;
+    float ms = wgt[i][s2];
+    float c = (ms == -INFINITY) ? 0.f : __expf(ms - hm[i]);
+    float lpart = s2 < n_splits ? __ldcg(part_ml + (bh * n_splits + s2) * 2 + 1) * c : 0.f;
+    // sum of l * c over the 64 slots of this head: two warps per head → shuffle + smem
+    lpart = warp_sum(lpart);
+    __syncwarp();
+    wgt[i][s2] = c;
+    if ((s2 & 31) == 0) sm_l[s2 >> 5][i] = lpart;
+  }
+  __syncthreads();
+  if (threadIdx.x < GT) {
+    int i = threadIdx.x;
+    float lsum = sm_l[0][i] + sm_l[1][i];
+    if (sinks) lsum += __expf(sinks[h0 + i] - hm[i]);
+    hl[i] = lsum > 0.f ? 1.f / lsum : 0.f;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < GT * D; idx += blockDim.x) {
     int i = idx / D, d = idx % D;
     size_t bh = (size_t)b * Hq + h0 + i;
-    float mn = -INFINITY;
-    for (int s2 = 0; s2 < n_splits; s2++) mn = fmaxf(mn, __ldcg(part_ml + (bh * n_splits + s2) * 2));
-    float lsum = 0.f;
-    if (sinks) { float sk = sinks[h0 + i]; mn = fmaxf(mn, sk); lsum = __expf(sk - mn); }
+    const float* po = part_o + bh * n_splits * D + d;
     float o = 0.f;
-    for (int s2 = 0; s2 < n_splits; s2++) {
-      float ms = __ldcg(part_ml + (bh * n_splits + s2) * 2);
-      float c = (ms == -INFINITY) ? 0.f : __expf(ms - mn);
-      o += __ldcg(part_o + (bh * n_splits + s2) * D + d) * c;
-      lsum += __ldcg(part_ml + (bh * n_splits + s2) * 2 + 1) * c;
+    int s2 = 0;
+    for (; s2 + 8 <= n_splits; s2 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) v[u] = __ldcg(po + (size_t)(s2 + u) * D);
+#pragma unroll
+      for (int u = 0; u < 8; u++) o += v[u] * wgt[i][s2 + u];
     }
-    out[bh * D + d] = Cvt<T>::from_f(lsum > 0.f ? o / lsum : 0.f);
+    for (; s2 < n_splits; s2++) o += __ldcg(po + (size_t)s2 * D) * wgt[i][s2];
+    out[bh * D + d] = Cvt<T>::from_f(o * hl[i]);
   }
 }
 
@@ -177,8 +216,8 @@ EXO_API long exo_paged_decode_workspace(int B, int Hq, int D, int n_splits) {
 }
 
 EXO_API int exo_paged_decode_splits(int B, int Hkv, int max_len) {
-  int want = (4 * 148 + B * Hkv - 1) / (B * Hkv);
-  int cap = (max_len + 127) / 128;
+  int want = (3 * 148 + B * Hkv - 1) / (B * Hkv);
+  int cap = (max_len + 63) / 64;
   int s = want < cap ? want : cap;
   if (s < 1) s = 1;
   if (s > 64) s = 64;

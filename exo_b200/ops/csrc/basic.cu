@@ -10,40 +10,44 @@ template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
                                T* __restrict__ out, T* __restrict__ h_out, int cols, float eps) {
   __shared__ float red[32];
-  extern __shared__ float hbuf[];  // cols floats
   size_t row = blockIdx.x;
   const T* xr = x + row * cols;
   const T* rr = res ? res + row * cols : nullptr;
+  pdl_trigger();
+  pdl_wait();
   float ss = 0.f;
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
     float h = Cvt<T>::to_f(xr[c]);
-    if (rr) h += Cvt<T>::to_f(rr[c]);
-    if (h_out) {
+    if (rr) {
+      h += Cvt<T>::to_f(rr[c]);
       T hq = Cvt<T>::from_f(h);
       h_out[row * cols + c] = hq;
       h = Cvt<T>::to_f(hq);  // normalise the value the residual stream actually keeps
     }
-    hbuf[c] = h;
     ss += h * h;
   }
   float tot = block_sum(ss, red);
   float rstd = rsqrtf(tot / cols + eps);
+  // second pass re-reads the row (each thread reads back exactly what it wrote: L1/L2 resident)
+  const T* hr = rr ? h_out + row * cols : xr;
   for (int c = threadIdx.x; c < cols; c += blockDim.x)
-    out[row * cols + c] = Cvt<T>::from_f(hbuf[c] * rstd * Cvt<T>::to_f(w[c]));
+    out[row * cols + c] = Cvt<T>::from_f(Cvt<T>::to_f(hr[c]) * rstd * Cvt<T>::to_f(w[c]));
 }
 
 EXO_API int exo_rmsnorm(const void* x, const void* res, const void* w, void* out, void* h_out, int rows, int cols,
                         float eps, int dtype, cudaStream_t st) {
   if (rows == 0) return 0;
-  size_t sm = (size_t)cols * sizeof(float);
+  if (res && !h_out) return -2;
   int threads = cols >= 2048 ? 512 : 256;
+  cudaError_t e;
   if (dtype == EXO_BF16)
-    rmsnorm_kernel<__nv_bfloat16><<<rows, threads, sm, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res,
-                                                             (const __nv_bfloat16*)w, (__nv_bfloat16*)out,
-                                                             (__nv_bfloat16*)h_out, cols, eps);
+    e = launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, st, (const __nv_bfloat16*)x,
+                   (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (__nv_bfloat16*)h_out, cols,
+                   eps);
   else
-    rmsnorm_kernel<float><<<rows, threads, sm, st>>>((const float*)x, (const float*)res, (const float*)w, (float*)out,
-                                                     (float*)h_out, cols, eps);
+    e = launch_pdl(rmsnorm_kernel<float>, dim3(rows), dim3(threads), 0, st, (const float*)x, (const float*)res,
+                   (const float*)w, (float*)out, (float*)h_out, cols, eps);
+  if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
   return 0;
 }

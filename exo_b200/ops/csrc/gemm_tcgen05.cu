@@ -177,14 +177,25 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         __threadfence();
         if (n < p.N) {
           float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
-          for (int mm = 0; mm < BN; mm++) {
-            int m = m0 + mm;
-            if (m >= p.M) break;
-            float y = bias;
-            for (int sp = 0; sp < p.splits; sp++) y += __ldcg(p.partial + ((size_t)sp * p.M + m) * p.N + n);
-            size_t o = (size_t)m * p.ldo + n;
-            if (p.residual) y += __bfloat162float(p.residual[o]);
-            p.out[o] = __float2bfloat16_rn(y);
+          const int mcount = min(BN, p.M - m0);
+          const size_t plane = (size_t)p.M * p.N;
+          for (int mm = 0; mm < mcount; mm += 4) {
+            float y[4] = {bias, bias, bias, bias};
+            const float* base = p.partial + (size_t)(m0 + mm) * p.N + n;
+            for (int sp = 0; sp < p.splits; sp++) {  // fixed split order → deterministic sum
+#pragma unroll
+              for (int j = 0; j < 4; j++)
+                if (mm + j < mcount) y[j] += __ldcg(base + sp * plane + (size_t)j * p.N);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              if (mm + j < mcount) {
+                size_t o = (size_t)(m0 + mm + j) * p.ldo + n;
+                float v = y[j];
+                if (p.residual) v += __bfloat162float(p.residual[o]);
+                p.out[o] = __float2bfloat16_rn(v);
+              }
+            }
           }
         }
       }
@@ -315,6 +326,7 @@ EXO_API int exo_gemm_splits(int M, int N, int K) {
   int kb = (K + BK - 1) / BK;
   // two CTAs are co-resident per SM (BN <= 128): aim for ~296 CTAs so every SM streams weights
   int target = bn <= 128 ? 296 : 148;
+  if (M > 64) return 1;  // tensor-bound shapes: a split only adds a reduction pass
   if (tiles * 4 >= target * 3 || kb < 8) return 1;
   int s = (int)((target + tiles / 2) / tiles);
   if (s > kb / 4) s = kb / 4;

@@ -33,22 +33,25 @@ template <> struct Vec16<float> {
   }
 };
 
+// CTA = 128 threads cooperating on R output rows: the K range is dealt out in 16-byte vectors,
+// vector (it * 128 + tid) to thread tid, U vectors per row issued back to back, so a thread has
+// U * R independent 16-byte loads in flight and the grid has N / R CTAs — enough outstanding
+// bytes to cover HBM latency even for a 4096 x 4096 projection (the whole matrix is in flight).
 template <typename T, int M, int R, bool NORM, bool SWIGLU>
 __global__ void __launch_bounds__(128)
 linear_small_kernel(const T* __restrict__ x, const T* __restrict__ W, const T* __restrict__ bias,
-                    const T* residual, T* out, const T* __restrict__ norm_w, float eps, int N, int K, int n_groups,
-                    int ldo) {
+                    const T* residual, T* out, const T* __restrict__ norm_w, float eps, int N, int K, int ldo) {
   constexpr int V = Vec16<T>::N;
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  constexpr int U = 4;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   pdl_trigger();  // the next kernel in the stream may begin launching (it waits before reading our output)
-  if (warp >= n_groups) return;
-  // output rows of this warp: R consecutive rows, or R/2 (gate, up) pairs when SWIGLU
+  // output rows of this CTA: R consecutive rows, or R/2 (gate, up) pairs when SWIGLU
   int rows[R];
   const int F = N / 2;
 #pragma unroll
   for (int i = 0; i < R; i++) {
-    if (SWIGLU) rows[i] = min(warp * (R / 2) + i / 2, F - 1) + (i & 1) * F;
-    else rows[i] = min(warp * R + i, N - 1);
+    if (SWIGLU) rows[i] = min((int)blockIdx.x * (R / 2) + i / 2, F - 1) + (i & 1) * F;
+    else rows[i] = min((int)blockIdx.x * R + i, N - 1);
   }
   const T* wp[R];
 #pragma unroll
@@ -60,61 +63,93 @@ linear_small_kernel(const T* __restrict__ x, const T* __restrict__ W, const T* _
 #pragma unroll
     for (int i = 0; i < R; i++) acc[i][m] = 0.f;
   }
-  // software pipeline: weights for step k+1 are in flight while step k is consumed; the very first
-  // batch is issued BEFORE waiting on the producer of x, so weight streaming overlaps its tail.
-  int k = lane * V;
-  uint4 cur[R];
+  const int stride = 128 * V;  // elements covered by the CTA per vector step
+  uint4 wv[U][R];
+  // first batch of weights is requested BEFORE waiting on the producer of x (weights never change)
 #pragma unroll
-  for (int i = 0; i < R; i++) cur[i] = k < K ? ld_stream16(wp[i] + k) : make_uint4(0, 0, 0, 0);
+  for (int u = 0; u < U; u++) {
+    int k = (u * 128 + tid) * V;
+#pragma unroll
+    for (int i = 0; i < R; i++) wv[u][i] = k < K ? ld_stream16(wp[i] + k) : make_uint4(0, 0, 0, 0);
+  }
   pdl_wait();
-  for (; k < K; k += 32 * V) {
-    uint4 nxt[R];
-    const int kn = k + 32 * V;
+  for (int k0 = 0; k0 < K; k0 += U * stride) {
+    uint4 nx[U][R];
+    const int kn0 = k0 + U * stride;
+    if (kn0 < K) {
 #pragma unroll
-    for (int i = 0; i < R; i++) nxt[i] = kn < K ? ld_stream16(wp[i] + kn) : make_uint4(0, 0, 0, 0);
-    float nw[V];
-    if (NORM) Vec16<T>::load(norm_w + k, nw);
-    float wf[R][V];
+      for (int u = 0; u < U; u++) {
+        int k = kn0 + (u * 128 + tid) * V;
 #pragma unroll
-    for (int i = 0; i < R; i++) Vec16<T>::unpack(cur[i], wf[i]);
-#pragma unroll
-    for (int m = 0; m < M; m++) {
-      float xf[V];
-      Vec16<T>::load(x + (size_t)m * K + k, xf);
-#pragma unroll
-      for (int j = 0; j < V; j++) {
-        float xv = xf[j];
-        if (NORM) { ss[m] += xv * xv; xv *= nw[j]; }
-#pragma unroll
-        for (int i = 0; i < R; i++) acc[i][m] += wf[i][j] * xv;
+        for (int i = 0; i < R; i++) nx[u][i] = k < K ? ld_stream16(wp[i] + k) : make_uint4(0, 0, 0, 0);
       }
     }
 #pragma unroll
-    for (int i = 0; i < R; i++) cur[i] = nxt[i];
+    for (int u = 0; u < U; u++) {
+      int k = k0 + (u * 128 + tid) * V;
+      if (k < K) {
+        float nw[V];
+        if (NORM) Vec16<T>::load(norm_w + k, nw);
+        float wf[R][V];
+#pragma unroll
+        for (int i = 0; i < R; i++) Vec16<T>::unpack(wv[u][i], wf[i]);
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+          float xf[V];
+          Vec16<T>::load(x + (size_t)m * K + k, xf);
+#pragma unroll
+          for (int j = 0; j < V; j++) {
+            float xv = xf[j];
+            if (NORM) { ss[m] += xv * xv; xv *= nw[j]; }
+#pragma unroll
+            for (int i = 0; i < R; i++) acc[i][m] += wf[i][j] * xv;
+          }
+        }
+      }
+    }
+    if (kn0 < K) {
+#pragma unroll
+      for (int u = 0; u < U; u++)
+#pragma unroll
+        for (int i = 0; i < R; i++) wv[u][i] = nx[u][i];
+    }
   }
+  // reduce: lanes by shuffle, warps through shared memory
+  __shared__ float red[4][R * M + M];
 #pragma unroll
   for (int m = 0; m < M; m++) {
+#pragma unroll
+    for (int i = 0; i < R; i++) {
+      float v = warp_sum(acc[i][m]);
+      if (lane == 0) red[warp][i * M + m] = v;
+    }
+    if (NORM) {
+      float v = warp_sum(ss[m]);
+      if (lane == 0) red[warp][R * M + m] = v;
+    }
+  }
+  __syncthreads();
+  if (tid < M) {
+    const int m = tid;
     float rstd = 1.f;
-    if (NORM) rstd = rsqrtf(warp_sum(ss[m]) / K + eps);
+    if (NORM) rstd = rsqrtf((red[0][R * M + m] + red[1][R * M + m] + red[2][R * M + m] + red[3][R * M + m]) / K + eps);
     float y[R];
 #pragma unroll
-    for (int i = 0; i < R; i++) y[i] = warp_sum(acc[i][m]) * rstd;
-    if (lane == 0) {
+    for (int i = 0; i < R; i++) {
+      y[i] = (red[0][i * M + m] + red[1][i * M + m] + red[2][i * M + m] + red[3][i * M + m]) * rstd;
+      if (bias) y[i] += Cvt<T>::to_f(bias[rows[i]]);
+    }
+    if (SWIGLU) {
 #pragma unroll
-      for (int i = 0; i < R; i++)
-        if (bias) y[i] += Cvt<T>::to_f(bias[rows[i]]);
-      if (SWIGLU) {
+      for (int i = 0; i < R; i += 2)
+        if ((int)blockIdx.x * (R / 2) + i / 2 < F) out[(size_t)m * ldo + rows[i]] = Cvt<T>::from_f(silu_f(y[i]) * y[i + 1]);
+    } else {
 #pragma unroll
-        for (int i = 0; i < R; i += 2)
-          if (warp * (R / 2) + i / 2 < F) out[(size_t)m * ldo + rows[i]] = Cvt<T>::from_f(silu_f(y[i]) * y[i + 1]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < R; i++) {
-          if (warp * R + i < N) {
-            float v = y[i];
-            if (residual) v += Cvt<T>::to_f(residual[(size_t)m * ldo + rows[i]]);
-            out[(size_t)m * ldo + rows[i]] = Cvt<T>::from_f(v);
-          }
+      for (int i = 0; i < R; i++) {
+        if ((int)blockIdx.x * R + i < N) {
+          float v = y[i];
+          if (residual) v += Cvt<T>::to_f(residual[(size_t)m * ldo + rows[i]]);
+          out[(size_t)m * ldo + rows[i]] = Cvt<T>::from_f(v);
         }
       }
     }
@@ -124,14 +159,13 @@ linear_small_kernel(const T* __restrict__ x, const T* __restrict__ W, const T* _
 template <typename T, int M>
 static int launch_small(const void* x, const void* W, const void* bias, const void* residual, void* out,
                         const void* norm_w, float eps, int N, int K, int swiglu, cudaStream_t st) {
-  constexpr int R = M <= 4 ? 4 : 2;
-  int n_groups = swiglu ? (N / 2 + R / 2 - 1) / (R / 2) : (N + R - 1) / R;
-  int blocks = (n_groups + 3) / 4;
+  constexpr int R = M <= 2 ? 4 : 2;
+  int blocks = swiglu ? (N / 2 + R / 2 - 1) / (R / 2) : (N + R - 1) / R;
   int ldo = swiglu ? N / 2 : N;
   cudaError_t e;
 #define L(NORM, SW)                                                                                             \
   e = launch_pdl(linear_small_kernel<T, M, R, NORM, SW>, dim3(blocks), dim3(128), 0, st, (const T*)x, (const T*)W, \
-                 (const T*)bias, (const T*)residual, (T*)out, (const T*)norm_w, eps, N, K, n_groups, ldo)
+                 (const T*)bias, (const T*)residual, (T*)out, (const T*)norm_w, eps, N, K, ldo)
   if (norm_w) { if (swiglu) L(true, true); else L(true, false); }
   else { if (swiglu) L(false, true); else L(false, false); }
 #undef L

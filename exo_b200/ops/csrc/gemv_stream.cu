@@ -1,0 +1,347 @@
+// Batch-1/2 linear layer as a persistent, bulk-async-copy pipelined weight stream.
+//
+//   y[m, n] = sum_k f(x)[m, k] * W[n, k]          (bf16 in, fp32 accumulate, M = 1 or 2)
+//
+// Decode at batch 1 reads every weight byte once and does two flops with it: the only thing that
+// matters is keeping HBM busy.  One CTA per SM stays resident for the whole call.  A producer warp
+// walks the CTA's row groups and keeps a ring of STAGES shared-memory buffers full with
+// `cp.async.bulk` copies (a group of RS consecutive weight rows is one contiguous run of bytes), so
+// ~150 KB per SM are always in flight no matter what the eight consumer warps are doing, and — the
+// weights being constants — it starts BEFORE the programmatic-dependent-launch wait, i.e. while the
+// previous kernel of the decode step is still draining.  Each consumer warp owns one eighth of the
+// K range, holds its slice of the (normalised) activation in registers for the whole kernel, and
+// dots it with every row of every stage; per-row partials meet in shared memory.
+//
+// Fused: RMSNorm prologue (sum of squares + norm weight), bias, residual add, SwiGLU epilogue
+// (a stage then carries RS/2 gate rows and the matching RS/2 up rows as two copies).
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int CONSUMER_WARPS = 8;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int RS_MAX = 32;
+
+struct StreamParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* W;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  __nv_bfloat16* out;
+  const __nv_bfloat16* norm_w;
+  float eps;
+  int N, K, RS, n_groups, ldo, stages, stage_bytes;
+  int* err;
+};
+
+__device__ __forceinline__ void bulk_g2s(void* smem, const void* gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(tc::smem_u32(smem)), "l"(gmem), "r"(bytes), "r"(tc::smem_u32(bar))
+               : "memory");
+}
+
+template <int M, int JV, int RB, bool NORM, bool SWIGLU>
+__global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+  uint64_t* full = reinterpret_cast<uint64_t*>(base);
+  uint64_t* empty = full + 8;
+  float* part = reinterpret_cast<float*>(base + 128);                     // [2][RS_MAX][CONSUMER_WARPS][M]
+  float* red = part + 2 * RS_MAX * CONSUMER_WARPS * M;                    // [CONSUMER_WARPS][M]
+  uint8_t* ring = base + 128 + ((2 * RS_MAX * CONSUMER_WARPS * M + CONSUMER_WARPS * M) * 4 + 127) / 128 * 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = p.K, RS = p.RS, F = p.N / 2;
+  const int row_bytes = K * 2;
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < p.stages; i++) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], CONSUMER_WARPS); }
+    tc::fence_barrier_init();
+  }
+  __syncthreads();
+  const int my_groups = (p.n_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+
+  if (warp == CONSUMER_WARPS) {
+    // ------------------------------ producer ------------------------------
+    if (tc::elect_one()) {
+      for (int i = 0; i < my_groups; i++) {
+        const int st = i % p.stages, g = blockIdx.x + i * gridDim.x;
+        if (i >= p.stages && !tc::mbar_wait(&empty[st], ((i / p.stages) - 1) & 1)) {
+          atomicExch(p.err, tc::ERR_EMPTY_TIMEOUT);
+          break;
+        }
+        uint8_t* dst = ring + (size_t)st * p.stage_bytes;
+        if (SWIGLU) {
+          const int half = RS / 2, r0 = g * half, rows = min(half, F - r0);
+          const uint32_t bytes = (uint32_t)rows * row_bytes;
+          tc::mbar_expect_tx(&full[st], 2 * bytes);
+          bulk_g2s(dst, p.W + (size_t)r0 * K, bytes, &full[st]);
+          bulk_g2s(dst + (size_t)half * row_bytes, p.W + (size_t)(F + r0) * K, bytes, &full[st]);
+        } else {
+          const int r0 = g * RS, rows = min(RS, p.N - r0);
+          const uint32_t bytes = (uint32_t)rows * row_bytes;
+          tc::mbar_expect_tx(&full[st], bytes);
+          bulk_g2s(dst, p.W + (size_t)r0 * K, bytes, &full[st]);
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------ consumers ------------------------------
+  const int KS = K / CONSUMER_WARPS;          // this warp's K slice
+  const int k_lo = warp * KS, nvec = KS / 8;  // in 16-byte vectors
+  pdl_wait();                                 // x comes from the previous kernel
+  float xr[M][JV][8];
+  float ss[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) {
+    ss[m] = 0.f;
+#pragma unroll
+    for (int j = 0; j < JV; j++) {
+      const int v = lane + 32 * j;
+      if (v < nvec) {
+        unpack8(*reinterpret_cast<const uint4*>(p.x + (size_t)m * K + k_lo + v * 8), xr[m][j]);
+        if (NORM) {
+          float nw[8];
+          unpack8(*reinterpret_cast<const uint4*>(p.norm_w + k_lo + v * 8), nw);
+#pragma unroll
+          for (int e = 0; e < 8; e++) { ss[m] += xr[m][j][e] * xr[m][j][e]; xr[m][j][e] *= nw[e]; }
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; e++) xr[m][j][e] = 0.f;
+      }
+    }
+  }
+  float rstd[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) rstd[m] = 1.f;
+  if (NORM) {
+#pragma unroll
+    for (int m = 0; m < M; m++) {
+      float v = warp_sum(ss[m]);
+      if (lane == 0) red[warp * M + m] = v;
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+#pragma unroll
+    for (int m = 0; m < M; m++) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < CONSUMER_WARPS; w++) t += red[w * M + m];
+      rstd[m] = rsqrtf(t / K + p.eps);
+    }
+  }
+
+  bool ok = true;
+  for (int i = 0; i < my_groups; i++) {
+    const int st = i % p.stages, g = blockIdx.x + i * gridDim.x;
+    if (ok && !tc::mbar_wait(&full[st], (i / p.stages) & 1)) {
+      atomicExch(p.err, tc::ERR_FULL_TIMEOUT);
+      ok = false;
+    }
+    const uint8_t* src = ring + (size_t)st * p.stage_bytes + (size_t)k_lo * 2;
+    float* pb = part + (size_t)(i & 1) * RS_MAX * CONSUMER_WARPS * M;
+    // RB rows at a time: RB independent load / FMA / shuffle chains per lane hide each other's latency
+    for (int rb = 0; rb < RS; rb += RB) {
+      float acc[RB][M][2];
+#pragma unroll
+      for (int rr = 0; rr < RB; rr++)
+#pragma unroll
+        for (int m = 0; m < M; m++) { acc[rr][m][0] = 0.f; acc[rr][m][1] = 0.f; }
+#pragma unroll
+      for (int j = 0; j < JV; j++) {
+        const int v = lane + 32 * j;
+        if (v < nvec) {
+          uint4 wv[RB];
+#pragma unroll
+          for (int rr = 0; rr < RB; rr++)
+            wv[rr] = *reinterpret_cast<const uint4*>(src + (size_t)(rb + rr) * row_bytes + v * 16);
+#pragma unroll
+          for (int rr = 0; rr < RB; rr++) {
+            float wf[8];
+            unpack8(wv[rr], wf);
+#pragma unroll
+            for (int m = 0; m < M; m++)
+#pragma unroll
+              for (int e = 0; e < 8; e++) acc[rr][m][e & 1] += wf[e] * xr[m][j][e];
+          }
+        }
+      }
+      float tot[RB][M];
+#pragma unroll
+      for (int rr = 0; rr < RB; rr++)
+#pragma unroll
+        for (int m = 0; m < M; m++) tot[rr][m] = acc[rr][m][0] + acc[rr][m][1];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int rr = 0; rr < RB; rr++)
+#pragma unroll
+          for (int m = 0; m < M; m++) tot[rr][m] += __shfl_xor_sync(0xffffffffu, tot[rr][m], o);
+      if (lane == 0) {
+#pragma unroll
+        for (int rr = 0; rr < RB; rr++)
+#pragma unroll
+          for (int m = 0; m < M; m++) pb[((rb + rr) * CONSUMER_WARPS + warp) * M + m] = tot[rr][m];
+      }
+    }
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(&empty[st]);  // this warp is done reading the stage
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    // finalise: thread t handles (row slot, m)
+    const int t = threadIdx.x;
+    if (ok) {
+      if (SWIGLU) {
+        const int half = RS / 2;
+        if (t < half * M) {
+          const int r = t / M, m = t % M, n = g * half + r;
+          if (n < F) {
+            float gsum = 0.f, usum = 0.f;
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; w++) {
+              gsum += pb[(r * CONSUMER_WARPS + w) * M + m];
+              usum += pb[((r + half) * CONSUMER_WARPS + w) * M + m];
+            }
+            gsum *= rstd[m];
+            usum *= rstd[m];
+            if (p.bias) { gsum += __bfloat162float(p.bias[n]); usum += __bfloat162float(p.bias[F + n]); }
+            p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(silu_f(gsum) * usum);
+          }
+        }
+      } else if (t < RS * M) {
+        const int r = t / M, m = t % M, n = g * RS + r;
+        if (n < p.N) {
+          float y = 0.f;
+#pragma unroll
+          for (int w = 0; w < CONSUMER_WARPS; w++) y += pb[(r * CONSUMER_WARPS + w) * M + m];
+          y *= rstd[m];
+          if (p.bias) y += __bfloat162float(p.bias[n]);
+          if (p.residual) y += __bfloat162float(p.residual[(size_t)m * p.ldo + n]);
+          p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(y);
+        }
+      }
+    }
+  }
+}
+
+int* g_err_stream[16] = {nullptr};
+
+template <int M, int JV, int RB>
+int launch_stream_rb(const StreamParams& p, bool norm, bool swiglu, int grid, size_t smem, cudaStream_t st) {
+  cudaError_t e;
+#define L(NORM, SW)                                                                                              \
+  {                                                                                                              \
+    static bool attr = false;                                                                                    \
+    if (!attr) {                                                                                                 \
+      if (cudaFuncSetAttribute(gemv_stream_kernel<M, JV, RB, NORM, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                               200 * 1024) != cudaSuccess)                                                       \
+        return -3;                                                                                               \
+      attr = true;                                                                                               \
+    }                                                                                                            \
+    e = launch_pdl(gemv_stream_kernel<M, JV, RB, NORM, SW>, dim3(grid), dim3(THREADS), smem, st, p);              \
+  }
+  if (norm) { if (swiglu) L(true, true) else L(true, false) }
+  else { if (swiglu) L(false, true) else L(false, false) }
+#undef L
+  return (int)e;
+}
+
+// long rows (JV >= 4) come one or two per stage; short rows in blocks of four
+template <int M, int JV>
+int launch_stream(const StreamParams& p, bool norm, bool swiglu, int grid, size_t smem, cudaStream_t st) {
+  if constexpr (JV >= 4) {
+    if (p.RS % 2 == 0) return launch_stream_rb<M, JV, 2>(p, norm, swiglu, grid, smem, st);
+    return launch_stream_rb<M, JV, 1>(p, norm, swiglu, grid, smem, st);
+  } else {
+    if (p.RS % 4 == 0) return launch_stream_rb<M, JV, 4>(p, norm, swiglu, grid, smem, st);
+    if (p.RS % 2 == 0) return launch_stream_rb<M, JV, 2>(p, norm, swiglu, grid, smem, st);
+    return launch_stream_rb<M, JV, 1>(p, norm, swiglu, grid, smem, st);
+  }
+}
+
+}  // namespace
+
+EXO_API int exo_gemv_stream_init() {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16) return -1;
+  if (!g_err_stream[dev]) {
+    if (cudaMalloc(&g_err_stream[dev], sizeof(int)) != cudaSuccess) return -1;
+    cudaMemset(g_err_stream[dev], 0, sizeof(int));
+  }
+  return 0;
+}
+
+EXO_API int exo_gemv_stream_last_error() {
+  int dev, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_err_stream[dev]) return 0;
+  cudaMemcpy(&v, g_err_stream[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (v) cudaMemset(g_err_stream[dev], 0, sizeof(int));
+  return v;
+}
+
+// Stage geometry for a (M, K, swiglu) problem; false when the ring would not hold two stages.
+static bool stream_config(int M, int K, int swiglu, int* RS_out, int* stages_out, size_t* fixed_out) {
+  const int row_bytes = K * 2;
+  int RS = (32 * 1024) / row_bytes;  // ~32 KB stages
+  if (RS < 1) RS = 1;
+  if (RS > RS_MAX) RS = RS_MAX;
+  if (RS >= 4) RS &= ~3;  // whole row blocks
+  if (swiglu) { RS &= ~1; if (RS < 2) RS = 2; }
+  const size_t fixed = 128 + ((2 * RS_MAX * CONSUMER_WARPS * M + CONSUMER_WARPS * M) * 4 + 127) / 128 * 128 + 128;
+  // The whole shared memory of the SM is the ring: ~190 KB in flight per SM is what it takes to
+  // cover HBM latency at full bandwidth (a 104 KB ring, tried so that the next kernel's CTA could
+  // co-reside and prefetch, lost 25 % of the bandwidth).
+  size_t budget = 196 * 1024;
+  int stages = (int)((budget - fixed) / ((size_t)RS * row_bytes));
+  if (stages > 8) stages = 8;
+  *RS_out = RS; *stages_out = stages; *fixed_out = fixed;
+  return stages >= 2;
+}
+
+// Returns 1 when (M, N, K) is served by the streaming kernel.
+EXO_API int exo_gemv_stream_supported(int M, int N, int K, int swiglu) {
+  if (M < 1 || M > 2) return 0;
+  if (K % 64 != 0 || K < 256) return 0;
+  int jv = (K / 8 / 8 + 31) / 32;
+  if (jv > 16 || (M == 2 && jv > 8)) return 0;
+  if (swiglu && (N % 2)) return 0;
+  if ((long)N * K < (1 << 20)) return 0;  // tiny matrices: the plain kernel has less set-up
+  int RS, stages; size_t fixed;
+  return stream_config(M, K, swiglu, &RS, &stages, &fixed) ? 1 : 0;
+}
+
+EXO_API int exo_gemv_stream(const void* x, const void* W, const void* bias, const void* residual, void* out,
+                            const void* norm_w, float eps, int M, int N, int K, int swiglu, cudaStream_t st) {
+  if (!exo_gemv_stream_supported(M, N, K, swiglu)) return -2;
+  int dev;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !g_err_stream[dev]) return -4;
+  StreamParams p;
+  p.x = (const __nv_bfloat16*)x; p.W = (const __nv_bfloat16*)W; p.bias = (const __nv_bfloat16*)bias;
+  p.residual = (const __nv_bfloat16*)residual; p.out = (__nv_bfloat16*)out; p.norm_w = (const __nv_bfloat16*)norm_w;
+  p.eps = eps; p.N = N; p.K = K; p.ldo = swiglu ? N / 2 : N; p.err = g_err_stream[dev];
+  const int row_bytes = K * 2;
+  int RS, stages; size_t fixed;
+  stream_config(M, K, swiglu, &RS, &stages, &fixed);
+  const int rows_total = swiglu ? N / 2 : N;
+  const int rows_per_group = swiglu ? RS / 2 : RS;
+  p.RS = RS;
+  p.n_groups = (rows_total + rows_per_group - 1) / rows_per_group;
+  p.stage_bytes = RS * row_bytes;
+  p.stages = stages;
+  const size_t smem = fixed + (size_t)stages * p.stage_bytes;
+  int grid = p.n_groups < 148 ? p.n_groups : 148;
+  const int jv = (K / 8 / 8 + 31) / 32;
+  int rc;
+#define BY_JV(MM)                                                                              \
+  if (jv <= 1) rc = launch_stream<MM, 1>(p, norm_w != nullptr, swiglu != 0, grid, smem, st);      \
+  else if (jv <= 2) rc = launch_stream<MM, 2>(p, norm_w != nullptr, swiglu != 0, grid, smem, st); \
+  else if (jv <= 4) rc = launch_stream<MM, 4>(p, norm_w != nullptr, swiglu != 0, grid, smem, st); \
+  else if (jv <= 8) rc = launch_stream<MM, 8>(p, norm_w != nullptr, swiglu != 0, grid, smem, st); \
+  else rc = launch_stream<1, 16>(p, norm_w != nullptr, swiglu != 0, grid, smem, st)
+  if (M == 1) { BY_JV(1); } else { BY_JV(2); }
+#undef BY_JV
+  if (rc) return rc;
+  EXO_CHECK_LAUNCH();
+  return 0;
+}

@@ -56,6 +56,10 @@ class _Sig:
     exo_paged_ragged = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
     exo_linear_small = (_i, [_p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _p])
     exo_linear_tiled = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
+    exo_gemv_stream_init = (_i, [])
+    exo_gemv_stream_last_error = (_i, [])
+    exo_gemv_stream_supported = (_i, [_i, _i, _i, _i])
+    exo_gemv_stream = (_i, [_p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p])
     exo_gemm_init = (_i, [_l])
     exo_gemm_last_error = (_i, [])
     exo_gemm_splits = (_i, [_i, _i, _i])
@@ -72,7 +76,8 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 def _chk(rc: int, what: str) -> None:
     if rc != 0:
-        raise KernelError(f"{what} failed with code {rc}" + (" (unsupported shape/dtype)" if rc == -2 else ""))
+        raise KernelError(f"{what} failed with code {rc}" + (" (unsupported shape/dtype)" if rc == -2 else "")
+                          + (f": {torch.cuda.get_device_name()}" if rc > 0 else ""))
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -119,7 +124,9 @@ def embedding(table, ids):
     return out
 
 
-SMALL_M = 8
+SMALL_M = 2   # rows served by CUDA-core kernels; above that the tensor-core GEMM streams weights better
+_stream_ready: set[int] = set()
+use_stream_gemv = os.environ.get("EXO_DISABLE_STREAM_GEMV") != "1"
 GEMM_PARTIAL_FLOATS = 16 << 20
 _gemm_ready: set[int] = set()
 
@@ -151,6 +158,9 @@ def gemm_check() -> None:
     code = load().exo_gemm_last_error()
     if code:
         raise KernelError(f"tcgen05 GEMM reported device-side timeout code {code}")
+    code = load().exo_gemv_stream_last_error()
+    if code:
+        raise KernelError(f"streaming GEMV reported device-side timeout code {code}")
 
 
 gemm_impl = None if os.environ.get("EXO_DISABLE_TCGEN05") == "1" else gemm_bf16
@@ -163,7 +173,20 @@ def linear(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=Fals
     M, K = x.shape
     N = w.shape[0]
     lib = load()
-    if M <= SMALL_M:
+    if (use_stream_gemv and 0 < M <= 2 and x.dtype == torch.bfloat16
+            and lib.exo_gemv_stream_supported(M, N, K, int(swiglu_out))):
+        dev = x.device.index or 0
+        if dev not in _stream_ready:
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError("first streaming-GEMV call on a device must not be inside graph capture")
+            _chk(lib.exo_gemv_stream_init(), "gemv_stream_init")
+            _stream_ready.add(dev)
+        out = torch.empty(M, N // 2 if swiglu_out else N, dtype=x.dtype, device=x.device)
+        _chk(lib.exo_gemv_stream(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), _ptr(norm_w), eps, M, N, K,
+                                 int(swiglu_out), _st()), "gemv_stream")
+        _count()
+        return out
+    if M <= SMALL_M or (x.dtype != torch.bfloat16 and M <= 8):
         out = torch.empty(M, N // 2 if swiglu_out else N, dtype=x.dtype, device=x.device)
         if M:
             _chk(lib.exo_linear_small(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), _ptr(norm_w), eps, M, N,

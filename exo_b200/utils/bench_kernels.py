@@ -20,13 +20,18 @@ from ..ops import reference as ref
 
 
 def timeit(fn, iters: int = 10, warm: int = 3) -> float:
+    # L2 flush = write 256 MB, then read another 256 MB: the read sweep forces the write-back of the
+    # dirty lines, so the timed kernel starts on a cold but CLEAN L2 (dirty lines would be written
+    # back during the timed reads and charge it with DRAM traffic that is not its own)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    sweep = torch.zeros(64 << 20, dtype=torch.float32, device="cuda")
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
     best = float("inf")
     for _ in range(iters):
         flush.fill_(1)
+        sweep.sum()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         fn()
@@ -34,6 +39,37 @@ def timeit(fn, iters: int = 10, warm: int = 3) -> float:
         torch.cuda.synchronize()
         best = min(best, e0.elapsed_time(e1))
     return best  # ms
+
+
+def timeit_rot(fns, reps: int = 0, iters: int = 5) -> float:
+    """Per-call time of a list of equivalent calls on DIFFERENT operands run back to back.
+
+    The operands together exceed the L2 several times over, so each call streams from HBM, and
+    the event pair brackets many calls, so its own microseconds do not bias short kernels.
+    """
+    reps = reps or max(len(fns), 8)
+    for i in range(len(fns)):
+        fns[i]()
+    torch.cuda.synchronize()
+    # the calls are captured in a CUDA graph: a Python-driven launch costs ~10 us of host time,
+    # more than most of these kernels run, and would turn the measurement into a launch benchmark
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        for i in range(reps):
+            fns[i % len(fns)]()
+    g.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / reps)
+    return best
 
 
 def main() -> None:
@@ -59,17 +95,20 @@ def main() -> None:
     if "gemv" in only:
         for M in (1, 4, 8):
             for N, Kd in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (16032, 4096), (4096, 512)):
-                x, w = rnd(M, Kd), rnd(N, Kd)
-                nw = rnd(Kd)
-                ms = timeit(lambda: K.linear(x, w, None, None, nw, 1e-5))
+                x, nw = rnd(M, Kd), rnd(Kd)
+                copies = max(2, -(-(400 << 20) // (N * Kd * 2)))
+                ws = [rnd(N, Kd) for _ in range(copies)]
+                ms = timeit_rot([(lambda w=w: K.linear(x, w, None, None, nw, 1e-5)) for w in ws])
                 gb = N * Kd * 2 / 1e9
                 print(f"gemv M={M} N={N} K={Kd}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s  "
                       f"{gb / ms * 1e3 / hbm:5.2f} of {basis} HBM")
     if "gemm" in only:
         for M in (16, 32, 64, 128, 256, 2048, 4096):
             for N, Kd in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)):
-                x, w = rnd(M, Kd), rnd(N, Kd)
-                ms = timeit(lambda: K.gemm_bf16(x, w))
+                x = rnd(M, Kd)
+                copies = max(2, -(-(400 << 20) // (N * Kd * 2)))
+                ws = [rnd(N, Kd) for _ in range(copies)]
+                ms = timeit_rot([(lambda w=w: K.gemm_bf16(x, w)) for w in ws])
                 gb = (N * Kd + M * Kd + M * N) * 2 / 1e9
                 fl = 2.0 * M * N * Kd / 1e12
                 print(f"gemm M={M} N={N} K={Kd}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s ({gb / ms * 1e3 / hbm:4.2f})  "
@@ -79,13 +118,15 @@ def main() -> None:
         Hq, Hkv, D, bs = 32, 8, 128, 16
         for B, ctx in ((1, 2048), (1, 8192), (32, 2048), (64, 4096)):
             nb = B * (ctx // bs + 1) + 1
-            kc, vc = rnd(nb, bs, Hkv, D), rnd(nb, bs, Hkv, D)
             bt = (torch.arange(B * (ctx // bs + 1), device="cuda", dtype=torch.int32) + 1).view(B, -1)
             sl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
             cu = torch.arange(B + 1, device="cuda", dtype=torch.int32)
             q = rnd(B, Hq, D)
-            ms = timeit(lambda: K.paged_attention(q, kc, vc, bt, sl, cu, D ** -0.5, max_q_len=1))
             gb = B * ctx * Hkv * D * 2 * 2 / 1e9
+            copies = max(2, int(0.4 / gb) + 1)
+            caches = [(rnd(nb, bs, Hkv, D), rnd(nb, bs, Hkv, D)) for _ in range(copies)]
+            ms = timeit_rot([(lambda kc=kc, vc=vc: K.paged_attention(q, kc, vc, bt, sl, cu, D ** -0.5, max_q_len=1))
+                             for kc, vc in caches])
             print(f"decode-attn B={B} ctx={ctx}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s  "
                   f"{gb / ms * 1e3 / hbm:5.2f} of {basis} HBM")
     if "prefill" in only:

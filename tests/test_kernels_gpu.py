@@ -55,7 +55,28 @@ def test_linear_small(K, dtype, M, N, K_):
     close(K.linear(x, w, None, None, nw, 1e-5, True), ref.swiglu(want))
 
 
-@pytest.mark.parametrize("M,N,K_", [(9, 256, 64), (16, 4096, 4096), (32, 6144, 4096), (48, 1024, 14336),
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("N,K_", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (16032, 4096),
+                                   (4096, 512), (4100, 1024), (1002 * 2, 28672)])
+def test_gemv_stream(K, M, N, K_):
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x = torch.randn(M, K_, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K_, device="cuda", generator=g) / math.sqrt(K_)).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g).bfloat16()
+    r = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    nw = (1 + 0.1 * torch.randn(K_, device="cuda", generator=g)).bfloat16()
+    assert K.load().exo_gemv_stream_supported(M, N, K_, 0) == (0 if (M == 2 and K_ > 16384) else 1)
+    close(K.linear(x, w), ref.linear(x.float(), w.float()))
+    close(K.linear(x, w, b, r), ref.linear(x.float(), w.float(), b.float(), r.float()))
+    want = ref.linear(ref.rmsnorm(x.float(), nw.float(), 1e-5)[0], w.float())
+    close(K.linear(x, w, None, None, nw, 1e-5), want)
+    close(K.linear(x, w, None, None, nw, 1e-5, True), ref.swiglu(want))
+    K.gemm_check()
+    again = K.linear(x, w, b, r)
+    assert torch.equal(again, K.linear(x, w, b, r))
+
+
+@pytest.mark.parametrize("M,N,K_", [(9, 256, 64), (5, 4096, 4096), (16, 4096, 4096), (32, 6144, 4096), (48, 1024, 14336),
                                      (100, 384, 512), (128, 4096, 1024), (300, 2048, 4096), (2048, 1536, 2048),
                                      (17, 128256 // 8, 4096)])
 def test_gemm_tcgen05(K, M, N, K_):
