@@ -73,6 +73,12 @@ def local_heads(cfg: ModelConfig, spec: ShardSpec) -> tuple[int, int]:
     return cfg.n_heads // spec.tp_size, hi - lo
 
 
+def vocab_shard(vocab: int, n: int) -> int:
+    """Rows of the vocabulary projection per rank: ceil(vocab / n) rounded up to 8 (16-byte rows
+    of bf16 logits for the fused all-gather); the tail of the last rank is zero padding."""
+    return -(-(-(-vocab // n)) // 8) * 8 if n > 1 else vocab
+
+
 def expert_range(cfg: ModelConfig, spec: ShardSpec) -> tuple[int, int]:
     c = cfg.n_experts // spec.tp_size
     return spec.tp_rank * c, (spec.tp_rank + 1) * c
@@ -322,8 +328,8 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
         final_norm = fin(src.get("model.norm.weight", (H,)))
         name = "model.embed_tokens.weight" if cfg.tie_embeddings or not src.has("lm_head.weight") else "lm_head.weight"
         full = src.get(name, (cfg.vocab, H))
-        vpad = -(-cfg.vocab // n)
-        lm_head = fin(full[r * vpad:min((r + 1) * vpad, cfg.vocab)])
+        vpad = vocab_shard(cfg.vocab, n)
+        lm_head = fin(full[min(r * vpad, cfg.vocab):min((r + 1) * vpad, cfg.vocab)])
         if lm_head.shape[0] < vpad:  # last rank pads so that every rank has the same shard height
             lm_head = torch.cat((lm_head, torch.zeros(vpad - lm_head.shape[0], H, dtype=lm_head.dtype, device=dev)), 0)
     return ModelWeights(embed=embed, layers=layers, final_norm=final_norm, lm_head=lm_head)
@@ -400,5 +406,5 @@ def _fast_shard(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device) ->
         layers[i] = lw
     embed = src.get("embed", (cfg.vocab, H)) if spec.is_first_stage else None
     final_norm = torch.ones(H, dtype=dt, device=device) if spec.is_last_stage else None
-    lm_head = src.get("lm_head", (-(-cfg.vocab // n), H)) if spec.is_last_stage else None
+    lm_head = src.get("lm_head", (vocab_shard(cfg.vocab, n), H)) if spec.is_last_stage else None
     return ModelWeights(embed, layers, final_norm, lm_head)

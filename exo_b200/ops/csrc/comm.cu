@@ -1,0 +1,306 @@
+// Tensor-parallel collectives over NVLink peer memory (no NCCL on this path).
+//
+// Every rank owns one "arena" allocated with cudaMalloc and exported through CUDA IPC; all ranks
+// map all arenas, so a kernel can store straight into a peer's HBM through NVSwitch.  Layout of an
+// arena (identical on every rank):
+//
+//   [0, 4 KB)        flags   int32 [2 parities][8 source ranks]   signals received, reset by reader
+//                    tickets int32 [2 parities] at +256          local CTA tickets
+//                    status  int32 at +512                       device-side error word (timeouts)
+//   [4 KB, ...)      staging [2 parities][n_ranks][slot_bytes]   partials pushed by each source rank
+//   [... , end)      gather  [gather_bytes]                      all-gather target (vocab logits)
+//
+// One-shot all-reduce (small / decode-sized tensors): every rank pushes its partial into every
+// rank's staging[parity][src], signals with a release-scoped remote atomic, waits (bounded) until
+// all sources have signalled, and sums the partials in rank order — every rank computes the same
+// bits.  Two calls in flight are separated by the parity bit; a rank cannot run two collectives
+// ahead of a peer because each reduction needs that peer's next partial.
+//
+// Waits are bounded by a globaltimer budget: on expiry the kernel records an error code in the
+// status word and returns normally, so the context stays usable and the host raises.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_RANKS = 8;
+constexpr size_t HDR_BYTES = 4096;
+constexpr unsigned long long WAIT_NS = 2000000000ull;  // 2 s
+
+struct CommCtx {
+  uint8_t* arena[MAX_RANKS];  // arena[r] = base of rank r's arena as mapped in this process
+  int n, rank;
+  size_t slot_bytes;          // bytes of one staging slot
+  size_t gather_off;          // byte offset of the gather region
+};
+
+__device__ __forceinline__ int* flag_ptr(uint8_t* arena, int parity, int src) {
+  return reinterpret_cast<int*>(arena) + parity * MAX_RANKS + src;
+}
+__device__ __forceinline__ uint8_t* slot_ptr(const CommCtx& c, uint8_t* arena, int parity, int src) {
+  return arena + HDR_BYTES + ((size_t)parity * c.n + src) * c.slot_bytes;
+}
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_cg16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+
+// Bounded wait until all n sources have signalled `need` times on (parity).  Returns false on timeout.
+__device__ bool wait_all(const CommCtx& c, int parity, int need) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < c.n) {
+    const int* f = flag_ptr(c.arena[c.rank], parity, threadIdx.x);
+    unsigned long long t0 = gtime();
+    while (ld_acquire_sys(f) < need) {
+      if (gtime() - t0 > WAIT_NS) {
+        ok_s = 0;
+        atomicExch(reinterpret_cast<int*>(c.arena[c.rank] + 512), 4 /* peer timeout */);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+// Signal every rank (including self): this CTA's share of (parity) is complete.
+__device__ void signal_all(const CommCtx& c, int parity) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < c.n) red_release_sys_add(flag_ptr(c.arena[threadIdx.x], parity, c.rank), 1);
+}
+
+// Last CTA of the grid (local ticket) resets the flags of (parity) for their next use.
+__device__ void finish_and_reset(const CommCtx& c, int parity) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* tk = reinterpret_cast<int*>(c.arena[c.rank] + 256) + parity;
+    __threadfence();
+    if (atomicAdd(tk, 1) == (int)gridDim.x - 1) {
+      *tk = 0;
+      for (int r = 0; r < c.n; r++) *flag_ptr(c.arena[c.rank], parity, r) = 0;
+      __threadfence_system();
+    }
+  }
+}
+
+// out = residual + sum_r partial_r     (bf16, fp32 accumulation in rank order), n_vec 16-byte vectors
+__global__ void __launch_bounds__(256)
+allreduce_oneshot_kernel(const CommCtx c, const uint4* __restrict__ in, const uint4* residual, uint4* out, int n_vec,
+                         int parity) {
+  pdl_trigger();
+  pdl_wait();
+  const int per = (n_vec + gridDim.x - 1) / gridDim.x;
+  const int v0 = blockIdx.x * per, v1 = min(n_vec, v0 + per);
+  // push my slice of the partial into every rank's staging[parity][me]
+  for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    uint4 x = in[v];
+    for (int r = 0; r < c.n; r++) reinterpret_cast<uint4*>(slot_ptr(c, c.arena[r], parity, c.rank))[v] = x;
+  }
+  signal_all(c, parity);
+  const bool ok = wait_all(c, parity, gridDim.x);
+  if (ok) {
+    for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+      float acc[8];
+      if (residual) unpack8(residual[v], acc);
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] = 0.f;
+      }
+      for (int r = 0; r < c.n; r++) {
+        float f[8];
+        unpack8(ld_cg16(reinterpret_cast<const uint4*>(slot_ptr(c, c.arena[c.rank], parity, r)) + v), f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] += f[e];
+      }
+      out[v] = pack8(acc);
+    }
+  }
+  finish_and_reset(c, parity);
+}
+
+// Two-shot all-reduce for large tensors: reduce-scatter (each rank pushes slice j to rank j),
+// rank j sums its slice, then broadcasts the reduced slice to everyone's `out` through a second
+// staging round.  Bytes on the wire per rank: 2 (n-1)/n of the tensor instead of (n-1) x.
+__global__ void __launch_bounds__(256)
+allreduce_twoshot_kernel(const CommCtx c, const uint4* __restrict__ in, const uint4* residual, uint4* out, int n_vec,
+                         int parity) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = c.n;
+  const int per_rank = (n_vec + n - 1) / n;  // slice owned by each rank
+  // phase 1: scatter — my contribution to slice j goes to rank j's staging[parity][me] (slice-local index)
+  for (int j = 0; j < n; j++) {
+    const int s0 = j * per_rank, s1 = min(n_vec, s0 + per_rank);
+    uint4* dst = reinterpret_cast<uint4*>(slot_ptr(c, c.arena[j], parity, c.rank));
+    for (int v = s0 + blockIdx.x * blockDim.x + threadIdx.x; v < s1; v += gridDim.x * blockDim.x) dst[v - s0] = in[v];
+  }
+  signal_all(c, parity);
+  bool ok = wait_all(c, parity, gridDim.x);
+  // phase 2: reduce my slice and push the result into every rank's second half of the slot
+  const int m0 = c.rank * per_rank, m1 = min(n_vec, m0 + per_rank);
+  const size_t half = c.slot_bytes / 2 / sizeof(uint4);
+  if (ok) {
+    for (int v = m0 + blockIdx.x * blockDim.x + threadIdx.x; v < m1; v += gridDim.x * blockDim.x) {
+      float acc[8];
+      if (residual) unpack8(residual[v], acc);
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] = 0.f;
+      }
+      for (int r = 0; r < n; r++) {
+        float f[8];
+        unpack8(ld_cg16(reinterpret_cast<const uint4*>(slot_ptr(c, c.arena[c.rank], parity, r)) + (v - m0)), f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] += f[e];
+      }
+      uint4 y = pack8(acc);
+      for (int r = 0; r < n; r++)
+        (reinterpret_cast<uint4*>(slot_ptr(c, c.arena[r], parity, c.rank)) + half)[v - m0] = y;
+    }
+  }
+  signal_all(c, parity);
+  ok = wait_all(c, parity, 2 * gridDim.x) && ok;
+  // phase 3: gather the reduced slices from my staging into out
+  if (ok) {
+    for (int j = 0; j < n; j++) {
+      const int s0 = j * per_rank, s1 = min(n_vec, s0 + per_rank);
+      const uint4* src = reinterpret_cast<const uint4*>(slot_ptr(c, c.arena[c.rank], parity, j)) + half;
+      for (int v = s0 + blockIdx.x * blockDim.x + threadIdx.x; v < s1; v += gridDim.x * blockDim.x)
+        out[v] = ld_cg16(src + (v - s0));
+    }
+  }
+  finish_and_reset(c, parity);
+}
+
+// All-gather of column shards: in [rows, cols] local shard → every rank's gather region
+// [rows, n * cols] at column offset rank * cols.  cols * 2 bytes must be a multiple of 16.
+__global__ void __launch_bounds__(256)
+allgather_cols_kernel(const CommCtx c, const uint4* __restrict__ in, int rows, int cols_vec, int parity) {
+  pdl_trigger();
+  pdl_wait();
+  const int total = rows * cols_vec;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int r = i / cols_vec, cv = i - r * cols_vec;
+    uint4 x = in[i];
+    const size_t dst = (size_t)r * c.n * cols_vec + (size_t)c.rank * cols_vec + cv;
+    for (int p = 0; p < c.n; p++) reinterpret_cast<uint4*>(c.arena[p] + c.gather_off)[dst] = x;
+  }
+  signal_all(c, parity);
+  wait_all(c, parity, gridDim.x);
+  finish_and_reset(c, parity);
+}
+
+CommCtx g_ctx[16];
+bool g_ctx_set[16] = {false};
+
+}  // namespace
+
+// ---- arena management (host) ------------------------------------------------------------------
+EXO_API void* exo_symm_alloc(size_t bytes) {
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) return nullptr;
+  cudaMemset(p, 0, bytes);
+  cudaDeviceSynchronize();
+  return p;
+}
+EXO_API int exo_symm_free(void* p) { return (int)cudaFree(p); }
+EXO_API int exo_symm_handle(void* p, void* out64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return (int)e;
+  memcpy(out64, &h, sizeof(h));
+  return 0;
+}
+EXO_API void* exo_symm_open(const void* handle64) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return nullptr;
+  return p;
+}
+EXO_API int exo_symm_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+EXO_API size_t exo_comm_header_bytes() { return HDR_BYTES; }
+
+// arenas: n pointers (index = rank; own arena at [rank]).
+EXO_API int exo_comm_init(void** arenas, int n, int rank, size_t slot_bytes, size_t gather_off) {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || n > MAX_RANKS) return -1;
+  CommCtx c;
+  for (int i = 0; i < MAX_RANKS; i++) c.arena[i] = i < n ? (uint8_t*)arenas[i] : nullptr;
+  c.n = n; c.rank = rank; c.slot_bytes = slot_bytes; c.gather_off = gather_off;
+  g_ctx[dev] = c;
+  g_ctx_set[dev] = true;
+  return 0;
+}
+
+EXO_API int exo_comm_status() {  // reads and clears the device-side error word (synchronises)
+  int dev, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return 0;
+  uint8_t* a = g_ctx[dev].arena[g_ctx[dev].rank];
+  cudaMemcpy(&v, a + 512, sizeof(int), cudaMemcpyDeviceToHost);
+  if (v) cudaMemset(a + 512, 0, sizeof(int));
+  return v;
+}
+
+static int grid_for(int n_vec) {
+  int g = (n_vec + 255) / 256;
+  if (g > 64) g = 64;  // few CTAs: every CTA costs n remote atomics and the tensors are small
+  return g < 1 ? 1 : g;
+}
+
+// out = residual + all-reduce(in) over bf16 tensors of n_elems (multiple of 8) elements.
+EXO_API int exo_allreduce_bf16(const void* in, const void* residual, void* out, long n_elems, int parity,
+                               cudaStream_t st) {
+  int dev;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !g_ctx_set[dev]) return -4;
+  const CommCtx& c = g_ctx[dev];
+  if (n_elems % 8) return -2;
+  const int n_vec = (int)(n_elems / 8);
+  const size_t bytes = (size_t)n_elems * 2;
+  cudaError_t e;
+  if (bytes <= c.slot_bytes && bytes <= (512u << 10)) {
+    e = launch_pdl(allreduce_oneshot_kernel, dim3(grid_for(n_vec)), dim3(256), 0, st, c, (const uint4*)in,
+                   (const uint4*)residual, (uint4*)out, n_vec, parity);
+  } else {
+    const int per_rank = (n_vec + c.n - 1) / c.n;
+    if ((size_t)per_rank * 16 > c.slot_bytes / 2) return -6;  // slot too small
+    e = launch_pdl(allreduce_twoshot_kernel, dim3(148), dim3(256), 0, st, c, (const uint4*)in, (const uint4*)residual,
+                   (uint4*)out, n_vec, parity);
+  }
+  if (e != cudaSuccess) return (int)e;
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+// gather region of every rank ← [rows, n*cols] with this rank's [rows, cols] shard in place.
+EXO_API int exo_allgather_cols_bf16(const void* in, int rows, int cols, int parity, cudaStream_t st) {
+  int dev;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !g_ctx_set[dev]) return -4;
+  const CommCtx& c = g_ctx[dev];
+  if (cols % 8) return -2;
+  int total = rows * (cols / 8);
+  cudaError_t e = launch_pdl(allgather_cols_kernel, dim3(grid_for(total)), dim3(256), 0, st, c, (const uint4*)in, rows,
+                             cols / 8, parity);
+  if (e != cudaSuccess) return (int)e;
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
