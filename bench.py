@@ -94,8 +94,16 @@ def main() -> None:
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return
 
+    import faulthandler
+    # a stuck collective must end the run with a stack dump, not sit until an outer limit kills it
+    faulthandler.dump_traceback_later(int(os.environ.get("EXO_BENCH_WATCHDOG_S", "900")), exit=True)
+
     import torch
     import torch.distributed as dist
+
+    def note(msg: str) -> None:
+        if os.environ.get("EXO_BENCH_VERBOSE"):
+            print(f"[bench r{os.environ.get('RANK', '0')} {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -139,8 +147,10 @@ def main() -> None:
             comm = NcclComm()
             comm_name = "nccl"
 
+    note(f"comm={comm_name}; building weights")
     weights = fast_random_weights(cfg, spec, dev, seed=0)
     torch.cuda.synchronize()
+    note("weights ready")
     max_b = max(args.batch, 1 if args.no_also else args.also_batch)
     per_seq_blocks = -(-(args.prompt + 2 * args.warmup + 4 * args.steps + 64) // 16)
     n_blocks = max_b * per_seq_blocks + 64
@@ -180,8 +190,11 @@ def main() -> None:
         torch.cuda.synchronize()
         return max_over_ranks(e0.elapsed_time(e1))
 
+    note("ttft warm-up")
     ttft_once()  # warm-up (kernel loading, descriptor caches)
+    note("ttft timed")
     ttfts = [ttft_once() for _ in range(3)]
+    note(f"ttft {ttfts}")
     ttft_ms = min(ttfts)
     K.gemm_check()
 
@@ -193,8 +206,10 @@ def main() -> None:
                            SamplingParams(max_tokens=10 ** 6, **greedy), use_prefix_cache=False) for _ in range(B)]
         while any(eng.seqs[r].in_prefill or not eng.seqs[r].output for r in rids):
             eng.step()
+        note(f"decode B={B}: prefill done, warming up")
         for _ in range(max(warm, 3)):
             eng.step()
+        note("e2e timed loop")
         # --- end to end: public API, H2D of the plan and D2H of the ids every step ---
         h0, d0 = eng.exe.h2d_bytes, eng.exe.d2h_bytes
         sampler = ClockSampler(local)
@@ -230,6 +245,7 @@ def main() -> None:
                             top_k=np.zeros(B, np.int32), temperature=np.zeros(B, np.float32),
                             top_p=np.ones(B, np.float32), min_p=np.zeros(B, np.float32),
                             uniform=np.zeros(B, np.float32), prev_rows=rows, block_tables=bt)
+        note("device timed loop")
         plans = [plan_at(i) for i in range(steps + max(warm, 3))]
         for i in range(max(warm, 3)):
             eng.exe.run(plans[i])
@@ -278,9 +294,15 @@ def main() -> None:
                            f"e2e_tok_s_bs{also['B']}": round(also["e2e_tok_s"], 1),
                            "ms_per_step": round(also["dev_ms_per_step"], 4)}
         print(json.dumps(out), flush=True)
+    faulthandler.cancel_dump_traceback_later()
+    sys.stdout.flush()
+    sys.stderr.flush()
     if world > 1:
+        # Leave without tearing NCCL down: destroying a communicator whose collectives were captured
+        # in still-alive CUDA graphs blocked for minutes (both ranks sat in destroy_process_group).
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 if __name__ == "__main__":
