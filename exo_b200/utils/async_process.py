@@ -20,11 +20,13 @@ from typing import Any
 import anyio
 
 
-def _child_main(target: Callable[..., Any], args: tuple, out_fd: int, err_fd: int) -> None:
-    os.dup2(out_fd, 1)
-    os.dup2(err_fd, 2)
-    os.close(out_fd)
-    os.close(err_fd)
+def _child_main(target: Callable[..., Any], args: tuple, out_conn: Any, err_conn: Any) -> None:
+    # the pipe ends arrive as multiprocessing Connections (the only way to hand an fd to a spawned
+    # child); from here on they are plain stdout / stderr
+    os.dup2(out_conn.fileno(), 1)
+    os.dup2(err_conn.fileno(), 2)
+    out_conn.close()
+    err_conn.close()
     sys.stdout = os.fdopen(1, "w", buffering=1, closefd=False)
     sys.stderr = os.fdopen(2, "w", buffering=1, closefd=False)
     faulthandler.enable(file=sys.stderr, all_threads=True)
@@ -37,18 +39,19 @@ class AsyncProcess:
 
     def __init__(self, target: Callable[..., Any], args: tuple = (), name: str | None = None, daemon: bool = True):
         self.ctx = mp.get_context("spawn")
-        self._out_r, out_w = os.pipe()
-        self._err_r, err_w = os.pipe()
-        for fd in (out_w, err_w):
-            os.set_inheritable(fd, True)
+        out_r, out_w = self.ctx.Pipe(duplex=False)
+        err_r, err_w = self.ctx.Pipe(duplex=False)
+        self._out_r, self._err_r = os.dup(out_r.fileno()), os.dup(err_r.fileno())
+        out_r.close()
+        err_r.close()
         self.proc = self.ctx.Process(target=_child_main, args=(target, args, out_w, err_w), name=name, daemon=daemon)
         self._w = (out_w, err_w)
         self.started = False
 
     def start(self) -> None:
         self.proc.start()
-        for fd in self._w:
-            os.close(fd)
+        for c in self._w:
+            c.close()
         self.started = True
 
     @property
