@@ -1,0 +1,246 @@
+"""Bring-up of one rank of a B200 instance, and the leader → follower plan channel.
+
+See ``builder.py`` for the serving engine.  The rank group is a ``torch.distributed`` world on
+127.0.0.1 (NCCL for tensors on GPUs, gloo for the small host-side control messages and for CPU
+ranks).  Every step the leader broadcasts one control message ``(packed plan | None, finished task
+ids, stop flag)``; a follower executes the plan and reports the finished tasks to its own runner.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from collections.abc import Iterable, Iterator
+from pathlib import Path
+from typing import Any
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ....engine.engine import Engine as TokenEngine
+from ....engine.executor import Executor
+from ....engine.plan import HEADER, PlanLayout, StepPlan
+from ....models.config import ModelConfig
+from ....models.transformer import KVPool
+from ....models.weights import (RandomSource, SafetensorsSource, ShardSpec, build_weights, fast_random_weights,
+                                vocab_shard)
+from ....shared import constants
+from ....shared.base import TaskId
+from ....shared.messages import GenerationTask
+from ....shared.wire import BoundInstance, NvlinkInstance
+from ..base import Builder, Cancelled, Engine, Finished, LoadProgress, StepItem
+from .builder import ServingEngine, find_model_dir
+from .tokenizer import eos_ids, load_tokenizer
+
+
+class PlanChannel:
+    """Control messages from rank 0 to the other ranks of the instance (gloo broadcast)."""
+
+    def __init__(self, group, rank: int):
+        self.group, self.rank = group, rank
+
+    def send(self, plan: StepPlan | None, finished: list[str], stop: bool = False) -> None:
+        packed = None
+        if plan is not None:
+            mb = max(1, plan.block_tables.shape[1])
+            buf = np.zeros(PlanLayout(plan.n_tokens, plan.n_seqs, mb).words, np.int32)
+            plan.pack(buf, plan.n_tokens, plan.n_seqs, mb)
+            packed = buf
+        dist.broadcast_object_list([(packed, finished, stop)], src=0, group=self.group)
+
+    def recv(self) -> tuple[StepPlan | None, list[str], bool]:
+        box: list[Any] = [None]
+        dist.broadcast_object_list(box, src=0, group=self.group)
+        packed, finished, stop = box[0]
+        return (StepPlan.unpack(packed) if packed is not None else None), finished, stop
+
+    def close(self) -> None:
+        if self.rank == 0:
+            try:
+                self.send(None, [], stop=True)
+            except RuntimeError:
+                pass
+
+
+class LeaderServingEngine(ServingEngine):
+    """Rank 0 of a multi-rank instance: every plan and every completion is broadcast."""
+
+    def warmup(self) -> None:
+        super().warmup()
+        self.control.send(None, ["warmup"])   # releases the followers' warm-up loop
+
+    def step(self):
+        items = list(super().step())
+        done = [str(t) for t, it in items if isinstance(it, (Finished, Cancelled))]
+        if done:
+            self.control.send(None, done)
+        return items
+
+    def _sink(self, plan: StepPlan) -> None:
+        self.control.send(plan, [])
+
+
+class FollowerServingEngine(Engine):
+    """Ranks > 0: execute broadcast plans; know tasks only by id."""
+
+    def __init__(self, executor: Executor, control: PlanChannel):
+        self.exe, self.control = executor, control
+        self.active: set[str] = set()
+        self.stopped = False
+
+    def warmup(self) -> None:
+        self._drain_until_idle()
+
+    def _drain_until_idle(self) -> None:
+        # the leader's warm-up generation is a normal request stream that ends with a completion message
+        while True:
+            plan, finished, stop = self.control.recv()
+            if plan is not None:
+                self.exe.run(plan)
+            if stop:
+                self.stopped = True
+                return
+            if finished:
+                return
+
+    def submit(self, task: GenerationTask) -> None:
+        self.active.add(str(task.task_id))
+
+    def cancel(self, task_id: TaskId) -> None:
+        pass  # the leader decides; its completion message releases the task here
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.active) and not self.stopped
+
+    def step(self) -> Iterable[tuple[TaskId, StepItem]]:
+        plan, finished, stop = self.control.recv()
+        if plan is not None:
+            self.exe.run(plan)
+        out: list[tuple[TaskId, StepItem]] = []
+        for t in finished:
+            if t in self.active:
+                self.active.discard(t)
+                out.append((TaskId(t), Finished()))
+        if stop:
+            self.stopped = True
+            for t in list(self.active):
+                out.append((TaskId(t), Finished()))
+            self.active.clear()
+        return out
+
+
+class B200Builder(Builder):
+    def __init__(self, bound_instance: BoundInstance):
+        super().__init__(bound_instance)
+        sh = bound_instance.bound_shard
+        self.card = sh.model_card
+        self.rank, self.world = sh.device_rank, sh.world_size
+        self.spec = ShardSpec(tp_rank=sh.tp_rank, tp_size=sh.tp_size, layer_start=sh.start_layer, layer_end=sh.end_layer,
+                              pp_rank=sh.pp_rank, pp_size=sh.pp_size)
+        want_cpu = os.environ.get("EXO_DEVICE", "").lower() == "cpu" or not torch.cuda.is_available()
+        gpu = sh.gpu_index if sh.gpu_index is not None else int(os.environ.get("EXO_GPU_INDEX", "0"))
+        self.device = torch.device("cpu") if want_cpu else torch.device("cuda", gpu)
+        self.comm = None
+        self.control: PlanChannel | None = None
+        self.weights = None
+        self.cfg: ModelConfig | None = None
+        self.model_dir = find_model_dir(str(self.card.model_id))
+
+    def connect(self) -> None:
+        sh = self.bound_instance.bound_shard
+        if sh.should_timeout:
+            import time
+            time.sleep(sh.should_timeout)
+        if self.world == 1:
+            return
+        inst = self.bound_instance.instance
+        port = inst.rendezvous_port if isinstance(inst, NvlinkInstance) else getattr(inst, "ephemeral_port", 29555)
+        backend = "gloo" if self.device.type == "cpu" else "nccl"
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        dist.init_process_group(backend, init_method=f"tcp://127.0.0.1:{port}", rank=self.rank, world_size=self.world,
+                                timeout=datetime.timedelta(seconds=int(os.environ.get("EXO_GROUP_TIMEOUT_S", "120"))),
+                                **({"device_id": self.device} if backend == "nccl" else {}))
+        ctl = dist.new_group(backend="gloo") if backend == "nccl" else dist.group.WORLD
+        self.control = PlanChannel(ctl, self.rank)
+
+    def _config(self) -> ModelConfig:
+        if self.model_dir is not None:
+            cfg = ModelConfig.from_pretrained(self.model_dir)
+        else:
+            raise FileNotFoundError(f"no checkpoint directory for {self.card.model_id}")
+        cfg.dtype = "fp32" if self.device.type == "cpu" else "bf16"
+        return cfg
+
+    def load(self) -> Iterator[LoadProgress]:
+        self.cfg = cfg = self._config()
+        total = len(self.spec.layers(cfg))
+        progress: list[int] = []
+        has_weights = self.model_dir is not None and any(self.model_dir.glob("*.safetensors"))
+        if has_weights:
+            src = SafetensorsSource(self.model_dir, device="cpu",
+                                    dtype=torch.float32 if cfg.dtype == "fp32" else torch.bfloat16)
+        elif os.environ.get("EXO_RANDOM_INIT", "0") == "1":
+            src = RandomSource(seed=0, dtype=torch.float32 if cfg.dtype == "fp32" else torch.bfloat16)
+        else:
+            raise FileNotFoundError(f"no *.safetensors under {self.model_dir} (set EXO_RANDOM_INIT=1 for random weights)")
+        # build_weights reports per layer; it is a plain function, so collect and replay as progress
+        self.weights = build_weights(cfg, self.spec, src, self.device, progress=lambda d, t: progress.append(d))
+        for d in progress or [total]:
+            yield LoadProgress(d, total)
+
+    def _n_blocks(self, cfg: ModelConfig) -> int:
+        per_block = max(1, KVPool.bytes_per_block(cfg, self.spec, constants.EXO_KV_BLOCK_SIZE))
+        if self.device.type == "cuda":
+            free, _total = torch.cuda.mem_get_info(self.device)
+            budget = int(free * constants.EXO_GPU_MEMORY_FRACTION)
+        else:
+            budget = 256 << 20
+        cap = int(os.environ.get("EXO_MAX_KV_BLOCKS", "0"))
+        n = max(64, budget // per_block)
+        return min(n, cap) if cap else n
+
+    def build(self) -> Engine:
+        assert self.cfg is not None and self.weights is not None
+        cfg = self.cfg
+        if self.world > 1:
+            if self.device.type == "cuda" and cfg.dtype == "bf16" and os.environ.get("EXO_COMM", "fused") == "fused":
+                from ....parallel.fused import FusedComm
+                self.comm = FusedComm(self.device, max_rows=constants.PREFILL_CHUNK, hidden=cfg.hidden,
+                                      vocab_shard=vocab_shard(cfg.vocab, self.spec.tp_size))
+            else:
+                from ....parallel.comm import DistComm
+                self.comm = DistComm()
+        n_blocks = self._n_blocks(cfg)
+        max_seqs = max(constants.EXO_MAX_CONCURRENT_REQUESTS, 8)
+        mbs = min(n_blocks, -(-min(cfg.max_position, 1 << 17) // constants.EXO_KV_BLOCK_SIZE))
+        if self.rank != 0:
+            exe = Executor(cfg, self.weights, self.spec, self.comm, n_blocks=n_blocks, max_blocks_per_seq=mbs,
+                           max_tokens_per_step=constants.PREFILL_CHUNK, max_seqs=max_seqs, device=self.device,
+                           use_graphs=False)
+            assert self.control is not None
+            return FollowerServingEngine(exe, self.control)
+        tok = load_tokenizer(self.model_dir, cfg.vocab)
+        eos = eos_ids(tok, self.model_dir, cfg.eos_token_ids)
+        cfg.eos_token_ids = eos
+        cls = LeaderServingEngine if self.world > 1 else ServingEngine
+        te = TokenEngine(cfg, self.weights, self.spec, self.comm, n_blocks=n_blocks, max_seqs=max_seqs,
+                         prefill_chunk=constants.PREFILL_CHUNK, max_blocks_per_seq=mbs, device=self.device,
+                         use_graphs=None if self.world == 1 else False)
+        eng = cls(cfg, te, tok, str(self.card.model_id), self.card.family, eos, self.card.reasoning_dialect, self.rank,
+                  self.control)
+        if self.world > 1:
+            te.plan_sink = eng._sink
+        return eng
+
+    def close(self) -> None:
+        try:
+            if self.comm is not None and hasattr(self.comm, "close"):
+                self.comm.close()
+        finally:
+            if dist.is_available() and dist.is_initialized():
+                try:
+                    dist.destroy_process_group()
+                except RuntimeError:
+                    pass

@@ -33,7 +33,7 @@ def make_builder(bound: BoundInstance):
     if bound.is_image_model:
         from ..engines.image.builder import ImageBuilder
         return ImageBuilder(bound)
-    from ..engines.b200.builder import B200Builder
+    from ..engines.b200.bringup import B200Builder
     return B200Builder(bound)
 
 
