@@ -19,6 +19,13 @@ from exo_b200.shared.wire import (BoundInstance, NvlinkInstance, RunnerFailed, R
 from exo_b200.utils.channels import channel
 
 
+@pytest.fixture(autouse=True)
+def _engine_env(monkeypatch):
+    monkeypatch.setenv("EXO_ENGINE", "b200")
+    monkeypatch.setenv("EXO_DEVICE", "cpu")
+    monkeypatch.setenv("EXO_MAX_KV_BLOCKS", "128")
+
+
 def make_checkpoint(tmp_path):
     """A tiny Llama checkpoint in HF layout (config.json + model.safetensors), byte-level vocab."""
     cfg = preset("tiny-llama")
@@ -64,9 +71,6 @@ def gen_task(inst, text, **kw):
 
 
 def drive(inst, nodes, rids, tasks_fn, timeout=120):
-    os.environ["EXO_ENGINE"] = "b200"
-    os.environ["EXO_DEVICE"] = "cpu"
-    os.environ["EXO_MAX_KV_BLOCKS"] = "128"
     from exo_b200.worker.runner.supervisor import RunnerSupervisor
     events = []
 
