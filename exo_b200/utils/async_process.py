@@ -135,8 +135,10 @@ class TaskGroup:
         return self
 
     async def __aexit__(self, *exc: Any) -> bool | None:
-        cm, self._cm, self._tg = self._cm, None, None
-        return await cm.__aexit__(*exc)
+        try:   # children may keep spawning siblings while the group waits for them
+            return await self._cm.__aexit__(*exc)
+        finally:
+            self._cm, self._tg = None, None
 
     def start_soon(self, fn: Callable[..., Awaitable[Any]], *args: Any) -> None:
         assert self._tg is not None, "task group is not running"
