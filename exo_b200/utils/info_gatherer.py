@@ -119,7 +119,7 @@ def kernels_available() -> bool:
 
 
 class InfoGatherer:
-    def __init__(self, sender: Sender[GatheredInfo], *, gpu_index: int | None = None, probe: GpuProbe = nvml_probe,
+    def __init__(self, sender: Sender[GatheredInfo], *, gpu_index: int | None = None, probe: GpuProbe | None = None,
                  memory_interval: float = 1.0, perf_interval: float = 1.0, disk_interval: float = 30.0,
                  network_interval: float = 10.0, misc_interval: float = 60.0, nvlink_interval: float = 30.0):
         self.sender, self.probe = sender, probe
@@ -130,7 +130,7 @@ class InfoGatherer:
     # ---- single readings (also used directly by tests and the power sampler) ----
     def _gpus(self) -> list[GpuSample]:
         try:
-            return self.probe()
+            return (self.probe or nvml_probe)()
         except Exception:  # a flaky driver call must not end telemetry
             return []
 

@@ -112,12 +112,12 @@ def _connect(c: Ctx) -> Task | None:
         peers = c.peers(r)
         if len(peers) == 1 or not isinstance(r.status, RunnerIdle):
             continue
-        if not c.all_in(peers, (RunnerConnecting, RunnerIdle)):
+        if not c.all_in(peers, (RunnerConnecting, RunnerIdle, RunnerConnected)):   # Connected: a rendezvous that does not block
             continue
         sh = r.bound_instance.bound_shard
         me = r.bound_instance.bound_runner_id
         last = sh.device_rank == sh.world_size - 1
-        if not last or c.all_in([p for p in peers if p != me], RunnerConnecting):
+        if not last or c.all_in([p for p in peers if p != me], (RunnerConnecting, RunnerConnected)):
             return ConnectToGroup(instance_id=r.bound_instance.instance.instance_id)
     return None
 
@@ -146,8 +146,8 @@ def _warmup(c: Ctx) -> Task | None:
         peers = c.peers(r)
         me = r.bound_instance.bound_runner_id
         rank = r.bound_instance.bound_shard.device_rank
-        followers_ready = rank > 0 and c.all_in(peers, (RunnerLoaded, RunnerWarmingUp))
-        leader_ready = rank == 0 and c.all_in([p for p in peers if p != me], RunnerWarmingUp)
+        followers_ready = rank > 0 and c.all_in(peers, (RunnerLoaded, RunnerWarmingUp, RunnerReady))
+        leader_ready = rank == 0 and c.all_in([p for p in peers if p != me], (RunnerWarmingUp, RunnerReady))
         if followers_ready or leader_ready:
             return StartWarmup(instance_id=r.bound_instance.instance.instance_id)
     return None

@@ -41,6 +41,8 @@ class RunnerSupervisor:
         self._ev_recv, self._task_send, self._cancel_send = ev_recv, task_send, cancel_send
         self._diag = DiagnosticCollector()
         self._dead = False
+        self._follower = bound_instance.bound_shard.device_rank != 0
+        self._events_done = anyio.Event()
         self._tg: anyio.abc.TaskGroup | None = None
 
     @classmethod
@@ -72,6 +74,12 @@ class RunnerSupervisor:
                 f.close()
 
     async def _forward_events(self) -> None:
+        try:
+            await self._forward_events_inner()
+        finally:
+            self._events_done.set()
+
+    async def _forward_events_inner(self) -> None:
         while True:
             try:
                 ev = await self._ev_recv.receive_async()
@@ -88,11 +96,18 @@ class RunnerSupervisor:
                                                                           TaskStatus.Cancelled, TaskStatus.TimedOut):
                 self.in_progress.discard(ev.task_id)
                 self.completed.add(ev.task_id)
+            if isinstance(ev, TaskStatusUpdated) and self._follower and ev.task_status != TaskStatus.Failed \
+                    and isinstance(self.tasks.get(ev.task_id), GENERATION):
+                # rank 0 speaks for the instance: a follower that starts or ends a generation early must not flip
+                # the cluster-wide task status under the other ranks' planners
+                continue
             await self._events_out.send(ev)
 
     async def _watch(self) -> None:
         while self._proc.is_alive():
             await anyio.sleep(min(LIVENESS_POLL, 0.25))
+        with anyio.move_on_after(1.0):      # what the child said last (its final status) decides clean vs failed
+            await self._events_done.wait()
         await self._on_death()
 
     async def _on_death(self) -> None:
@@ -156,5 +171,7 @@ class RunnerSupervisor:
                 await anyio.sleep(0.05)
         if self._proc.is_alive():
             await self._proc.stop()
+        with anyio.move_on_after(1.0):      # let the child's last events (its final status) through before stopping the pumps
+            await self._events_done.wait()
         if self._tg is not None:
             self._tg.cancel_scope.cancel()
