@@ -293,6 +293,13 @@ EXO_API int exo_gemm_init(long partial_floats) {
   return 0;
 }
 
+// The device error word of the current device, shared by every tensor-core kernel (nullptr before exo_gemm_init).
+int* exo_tc_err_ptr() {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16) return nullptr;
+  return g_err[dev];
+}
+
 // Reads and clears the device error word (synchronises the device).
 EXO_API int exo_gemm_last_error() {
   int dev, v = 0;

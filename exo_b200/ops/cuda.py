@@ -54,6 +54,7 @@ class _Sig:
     exo_paged_decode = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
     exo_token_seq = (_i, [_p, _p, _i, _p])
     exo_paged_ragged = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
+    exo_prefill_attn_tc = (_i, [_p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p])
     exo_linear_small = (_i, [_p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _p])
     exo_linear_tiled = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
     exo_gemv_stream_init = (_i, [])
@@ -131,16 +132,21 @@ GEMM_PARTIAL_FLOATS = 16 << 20
 _gemm_ready: set[int] = set()
 
 
+def ensure_gemm_init(device) -> None:
+    """Per-device scratch of the tensor-core kernels (error word, split-K buffers); not capturable."""
+    dev = device.index or 0
+    if dev not in _gemm_ready:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("first tensor-core kernel call on a device must not be inside graph capture")
+        _chk(load().exo_gemm_init(GEMM_PARTIAL_FLOATS), "gemm_init")
+        _gemm_ready.add(dev)
+
+
 def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False):
     """tcgen05 GEMM ``x[M,K] @ w[N,K].T``; per-device scratch is set up on first use, which
     must therefore happen outside CUDA-graph capture (the executor warms up before capturing)."""
     lib = load()
-    dev = x.device.index or 0
-    if dev not in _gemm_ready:
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("first GEMM call on a device must not be inside graph capture")
-        _chk(lib.exo_gemm_init(GEMM_PARTIAL_FLOATS), "gemm_init")
-        _gemm_ready.add(dev)
+    ensure_gemm_init(x.device)
     M, K = x.shape
     N = w.shape[0]
     out = torch.empty(M, N, dtype=x.dtype, device=x.device)
@@ -230,7 +236,8 @@ def _workspace(dev: torch.device, n_floats: int) -> torch.Tensor:
     return t
 
 
-prefill_attention_impl = None  # set when the tensor-core prefill kernel is available
+# tensor-core prefill attention (head_dim 128, 16-key pages, bf16); EXO_DISABLE_TC_ATTENTION=1 forces the generic kernel
+prefill_attention_impl = None if os.environ.get("EXO_DISABLE_TC_ATTENTION") == "1" else "tcgen05"
 
 
 def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, sliding_window=0, sinks=None,
@@ -253,9 +260,16 @@ def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, slid
                                   int(sliding_window), _ptr(sinks), _dt(q), _st()), "paged_decode")
         _count()
         return out
-    if (prefill_attention_impl is not None and q.dtype == torch.bfloat16 and sinks is None and not sliding_window
-            and D in (64, 128)):
-        return prefill_attention_impl(q, kcache, vcache, block_tables, seq_lens, cu_q, scale)
+    if prefill_attention_impl is not None and q.dtype == torch.bfloat16 and sinks is None and D == 128 and bs == 16:
+        ensure_gemm_init(q.device)
+        rc = lib.exo_prefill_attn_tc(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(seq_lens), _ptr(cu_q),
+                                     _ptr(out), float(scale), T, B, Hq, Hkv, D, nblk, max_blocks, bs, int(sliding_window),
+                                     _st())
+        if rc == 0:
+            _count()
+            return out
+        if rc not in (-2, -5):      # -2 / -5: shape not handled there -> generic kernel below
+            _chk(rc, "prefill_attn_tc")
     tok_seq = torch.empty(T, dtype=torch.int32, device=q.device)
     _chk(lib.exo_token_seq(_ptr(cu_q), _ptr(tok_seq), B, _st()), "token_seq")
     _chk(lib.exo_paged_ragged(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(seq_lens), _ptr(cu_q),

@@ -152,6 +152,23 @@ def test_paged_ragged_prefill(K, dtype):
     close(got, want)
 
 
+@pytest.mark.parametrize("window", [0, 200])
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
+def test_prefill_attention_tcgen05(K, Hq, Hkv, window):
+    """head_dim 128 / 16-key pages take the tensor-core kernel: fresh prompts, a chunk on top of
+    cached context, a decode row in the same step, lengths that are not multiples of the tiles."""
+    from exo_b200.ops import cuda as c
+    lens, qlens = [300, 777, 129, 1, 2048 + 5], [300, 260, 129, 1, 517]
+    q, kc, vc, bt, sl, cu = _paged_setup(torch.bfloat16, 5, Hq, Hkv, 128, lens, qlens, seed=3)
+    before = c.launch_count
+    got = K.paged_attention(q, kc, vc, bt, sl, cu, 128 ** -0.5, sliding_window=window, max_q_len=max(qlens))
+    assert c.launch_count - before == 1          # one launch: the generic path needs two
+    torch.cuda.synchronize()
+    c.gemm_check()
+    want = ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, cu, 128 ** -0.5, window)
+    close(got, want)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("D,qknorm", [(128, False), (64, True), (128, True)])
 def test_qk_rope_append(K, dtype, D, qknorm):
