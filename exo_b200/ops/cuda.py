@@ -55,6 +55,9 @@ class _Sig:
     exo_token_seq = (_i, [_p, _p, _i, _p])
     exo_paged_ragged = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
     exo_prefill_attn_tc = (_i, [_p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p])
+    exo_decode_attn_tc = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p])
+    exo_decode_attn_tc_splits = (_i, [_i, _i, _i])
+    exo_decode_attn_tc_workspace = (_l, [_i, _i, _i])
     exo_linear_small = (_i, [_p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _p])
     exo_linear_tiled = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
     exo_gemv_stream_init = (_i, [])
@@ -238,6 +241,7 @@ def _workspace(dev: torch.device, n_floats: int) -> torch.Tensor:
 
 # tensor-core prefill attention (head_dim 128, 16-key pages, bf16); EXO_DISABLE_TC_ATTENTION=1 forces the generic kernel
 prefill_attention_impl = None if os.environ.get("EXO_DISABLE_TC_ATTENTION") == "1" else "tcgen05"
+decode_attention_tc = os.environ.get("EXO_DISABLE_TC_DECODE") != "1"
 
 
 def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, sliding_window=0, sinks=None,
@@ -250,11 +254,21 @@ def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, slid
     out = torch.empty_like(q)
     max_blocks = block_tables.shape[1]
     if max_q_len == 1 and T == B:
-        ns = lib.exo_paged_decode_splits(B, Hkv, max_blocks * bs)
-        ws = _workspace(q.device, lib.exo_paged_decode_workspace(B, Hq, D, ns))
         tk = _tickets.get(q.device.index)
         if tk is None or tk.numel() < B * Hq:
             tk = _tickets[q.device.index] = torch.zeros(max(B * Hq, 1 << 14), dtype=torch.int32, device=q.device)
+        if (prefill_attention_impl is not None and decode_attention_tc and q.dtype == torch.bfloat16 and sinks is None
+                and D == 128 and bs == 16 and Hq % Hkv == 0 and Hq // Hkv in (1, 2, 4, 8)):
+            ensure_gemm_init(q.device)
+            ns = lib.exo_decode_attn_tc_splits(B, Hkv, max_blocks * bs)
+            ws = _workspace(q.device, lib.exo_decode_attn_tc_workspace(B, Hq, ns))
+            _chk(lib.exo_decode_attn_tc(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(seq_lens), _ptr(out),
+                                        _ptr(ws), _ptr(tk), float(scale), B, Hq, Hkv, D, nblk, max_blocks, bs, ns,
+                                        int(sliding_window), _st()), "decode_attn_tc")
+            _count()
+            return out
+        ns = lib.exo_paged_decode_splits(B, Hkv, max_blocks * bs)
+        ws = _workspace(q.device, lib.exo_paged_decode_workspace(B, Hq, D, ns))
         _chk(lib.exo_paged_decode(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(seq_lens), _ptr(out),
                                   _ptr(ws), _ptr(tk), float(scale), B, Hq, Hkv, D, max_blocks, bs, ns,
                                   int(sliding_window), _ptr(sinks), _dt(q), _st()), "paged_decode")

@@ -152,6 +152,23 @@ def test_paged_ragged_prefill(K, dtype):
     close(got, want)
 
 
+@pytest.mark.parametrize("window", [0, 300])
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4), (16, 8), (8, 1)])
+def test_decode_attention_tcgen05(K, Hq, Hkv, window):
+    """bf16 / head_dim 128 / 16-key pages decode goes through the tensor-core split-KV kernel:
+    contexts shorter than a block, longer than the 3-stage ring, not multiples of anything."""
+    from exo_b200.ops import cuda as c
+    lens = [1, 127, 128, 129, 1000, 5003]
+    q, kc, vc, bt, sl, cu = _paged_setup(torch.bfloat16, 6, Hq, Hkv, 128, lens, [1] * 6, seed=5)
+    got = K.paged_attention(q, kc, vc, bt, sl, cu, 128 ** -0.5, sliding_window=window, max_q_len=1)
+    torch.cuda.synchronize()
+    c.gemm_check()
+    want = ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, cu, 128 ** -0.5, window)
+    close(got, want)
+    again = K.paged_attention(q, kc, vc, bt, sl, cu, 128 ** -0.5, sliding_window=window, max_q_len=1)
+    assert torch.equal(got, again)      # tickets were left clean and the merge order is fixed
+
+
 @pytest.mark.parametrize("window", [0, 200])
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
 def test_prefill_attention_tcgen05(K, Hq, Hkv, window):
