@@ -40,7 +40,7 @@ class Engine:
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None = None, comm=None,
                  n_blocks: int = 512, block_size: int = 16, max_seqs: int = 64, prefill_chunk: int = 4096,
                  max_blocks_per_seq: int | None = None, device: str | torch.device = "cpu",
-                 use_graphs: bool | None = None, seed: int = 0, plan_sink=None):
+                 use_graphs: bool | None = None, seed: int = 0, plan_sink=None, pipe=None):
         self.cfg = cfg
         mbs = max_blocks_per_seq or min(n_blocks, -(-cfg.max_position // block_size))
         self.alloc = BlockAllocator(n_blocks, block_size)
@@ -50,7 +50,7 @@ class Engine:
                                eos_token_ids=cfg.eos_token_ids, max_context=cfg.max_position, seed=seed)
         self.exe = Executor(cfg, weights, spec, comm, n_blocks=n_blocks, block_size=block_size,
                             max_blocks_per_seq=mbs, max_tokens_per_step=max(prefill_chunk, max_seqs),
-                            max_seqs=max_seqs, device=device, use_graphs=use_graphs)
+                            max_seqs=max_seqs, device=device, use_graphs=use_graphs, pipe=pipe)
         self.seqs: dict[str, Sequence] = {}
         self.plan_sink = plan_sink  # callable(StepPlan): broadcasts the plan to follower ranks
         self.n_steps = 0

@@ -26,8 +26,9 @@ class Executor:
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None = None, comm=None,
                  n_blocks: int = 256, block_size: int = 16, max_blocks_per_seq: int = 256,
                  max_tokens_per_step: int = 4096, max_seqs: int = 64, device: str | torch.device = "cpu",
-                 use_graphs: bool | None = None):
+                 use_graphs: bool | None = None, pipe=None):
         self.cfg = cfg
+        self.pipe = pipe if (pipe is not None and pipe.pp_size > 1) else None
         self.spec = spec or ShardSpec()
         self.device = torch.device(device)
         self.model = Decoder(cfg, weights, self.spec, comm)
@@ -70,14 +71,40 @@ class Executor:
             pr = samp["prev_rows"]
             prev = self.prev_sampled[pr.clamp_min(0).long()]
             inp.tokens.copy_(torch.where(pr >= 0, prev, inp.tokens))
+        if self.pipe is not None:
+            return self._forward_sample_pipelined(inp, samp, greedy)
         logits = self.model.comm.gather_vocab(self.model.forward(inp, self.kv))
         self.last_logits = logits
+        ids = self._sample(logits, samp, greedy)
+        self.prev_sampled[:ids.numel()].copy_(ids)
+        return ids
+
+    def _sample(self, logits: torch.Tensor, samp: dict[str, torch.Tensor], greedy: bool) -> torch.Tensor:
         if greedy:
             ids = ops.argmax(logits[:, :self.cfg.vocab])
         else:
             ids = ops.sample(logits[:, :self.cfg.vocab], samp["temperature"], samp["top_k"], samp["top_p"],
                              samp["min_p"], samp["uniform"])
-        ids = ids.to(torch.int32)
+        return ids.to(torch.int32)
+
+    def _forward_sample_pipelined(self, inp: StepInputs, samp: dict[str, torch.Tensor], greedy: bool) -> torch.Tensor:
+        """One pipeline stage of a step: receive the residual stream, run this stage's layers, pass
+        it on; the last stage samples and its ids go back to every stage of the lane."""
+        spec, pipe = self.spec, self.pipe
+        h_in = None
+        if not spec.is_first_stage:
+            dt = torch.bfloat16 if self.cfg.dtype == "bf16" else torch.float32
+            h_in = pipe.recv_hidden(torch.empty(inp.tokens.shape[0], self.cfg.hidden, dtype=dt, device=self.device))
+        out = self.model.forward(inp, self.kv, h_in)
+        n = inp.logit_rows.numel()
+        if spec.is_last_stage:
+            logits = self.model.comm.gather_vocab(out)
+            self.last_logits = logits
+            ids = self._sample(logits, samp, greedy)
+        else:
+            pipe.send_hidden(out)
+            ids = torch.zeros(n, dtype=torch.int32, device=self.device)
+        ids = pipe.share_ids(ids)
         self.prev_sampled[:ids.numel()].copy_(ids)
         return ids
 

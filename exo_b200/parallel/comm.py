@@ -62,3 +62,40 @@ class DistComm:
 
 NcclComm = DistComm
 GlooComm = DistComm
+
+
+class PipeComm:
+    """Pipeline-stage links of one tensor-parallel lane: activations hop stage to stage, the ids
+    sampled on the last stage go back to every stage (the first needs them as next-step input,
+    global rank 0 for the scheduler).  World layout: ``rank = pp_rank * tp_size + tp_rank``.
+
+    The reference moves the hidden state with ``send`` / ``recv_like`` between
+    ``PipelineLastLayer`` and ``PipelineFirstLayer`` and then all-gathers the final stage's output
+    so that every rank can sample (``auto_parallel.py:132-194``); here only the sampled ids
+    (4 bytes per sequence) travel back.
+    """
+
+    def __init__(self, pp_rank: int, pp_size: int, tp_rank: int, tp_size: int, lane_group=None):
+        self.pp_rank, self.pp_size = pp_rank, pp_size
+        self.lane_group = lane_group          # the pp_size ranks that share this tp_rank
+        g = lambda stage: stage * tp_size + tp_rank
+        self.prev = g(pp_rank - 1) if pp_rank > 0 else None
+        self.next = g(pp_rank + 1) if pp_rank < pp_size - 1 else None
+        self.last = g(pp_size - 1)
+        self.n_hops = 0
+
+    def recv_hidden(self, like: torch.Tensor) -> torch.Tensor:
+        buf = like.float() if (like.device.type == "cpu" and like.dtype == torch.bfloat16) else like
+        dist.recv(buf, self.prev)
+        self.n_hops += 1
+        return buf.to(like.dtype)
+
+    def send_hidden(self, h: torch.Tensor) -> None:
+        if h.device.type == "cpu" and h.dtype == torch.bfloat16:
+            h = h.float()
+        dist.send(h.contiguous(), self.next)
+        self.n_hops += 1
+
+    def share_ids(self, ids: torch.Tensor) -> torch.Tensor:
+        dist.broadcast(ids, src=self.last, group=self.lane_group)
+        return ids

@@ -22,6 +22,7 @@ from ....engine.executor import Executor
 from ....engine.plan import HEADER, PlanLayout, StepPlan
 from ....models.config import ModelConfig
 from ....models.transformer import KVPool
+from ....parallel.comm import PipeComm
 from ....models.weights import (RandomSource, SafetensorsSource, ShardSpec, build_weights, fast_random_weights,
                                 vocab_shard)
 from ....shared import constants
@@ -142,6 +143,8 @@ class B200Builder(Builder):
         gpu = sh.gpu_index if sh.gpu_index is not None else int(os.environ.get("EXO_GPU_INDEX", "0"))
         self.device = torch.device("cpu") if want_cpu else torch.device("cuda", gpu)
         self.comm = None
+        self.tp_group = None
+        self.pipe: PipeComm | None = None
         self.control: PlanChannel | None = None
         self.weights = None
         self.cfg: ModelConfig | None = None
@@ -164,6 +167,12 @@ class B200Builder(Builder):
                                 **({"device_id": self.device} if backend == "nccl" else {}))
         ctl = dist.new_group(backend="gloo") if backend == "nccl" else dist.group.WORLD
         self.control = PlanChannel(ctl, self.rank)
+        tp, pp = self.spec.tp_size, self.spec.pp_size
+        if pp > 1:      # every rank creates every group, in the same order: one per stage, then one per lane
+            stage_groups = [dist.new_group([s * tp + t for t in range(tp)]) for s in range(pp)]
+            lane_groups = [dist.new_group([s * tp + t for s in range(pp)]) for t in range(tp)]
+            self.tp_group = stage_groups[self.spec.pp_rank]
+            self.pipe = PipeComm(self.spec.pp_rank, pp, self.spec.tp_rank, tp, lane_groups[self.spec.tp_rank])
 
     def _config(self) -> ModelConfig:
         if self.model_dir is not None:
@@ -204,21 +213,24 @@ class B200Builder(Builder):
     def build(self) -> Engine:
         assert self.cfg is not None and self.weights is not None
         cfg = self.cfg
-        if self.world > 1:
-            if self.device.type == "cuda" and cfg.dtype == "bf16" and os.environ.get("EXO_COMM", "fused") == "fused":
+        if self.spec.tp_size > 1:
+            # the peer-memory collectives span the whole rank group: with pipeline stages the TP group is a
+            # subset, and the stage-local all-reduce goes through the process group instead
+            if (self.device.type == "cuda" and cfg.dtype == "bf16" and self.spec.pp_size == 1
+                    and os.environ.get("EXO_COMM", "fused") == "fused"):
                 from ....parallel.fused import FusedComm
                 self.comm = FusedComm(self.device, max_rows=constants.PREFILL_CHUNK, hidden=cfg.hidden,
                                       vocab_shard=vocab_shard(cfg.vocab, self.spec.tp_size))
             else:
                 from ....parallel.comm import DistComm
-                self.comm = DistComm()
+                self.comm = DistComm(self.tp_group)
         n_blocks = self._n_blocks(cfg)
         max_seqs = max(constants.EXO_MAX_CONCURRENT_REQUESTS, 8)
         mbs = min(n_blocks, -(-min(cfg.max_position, 1 << 17) // constants.EXO_KV_BLOCK_SIZE))
         if self.rank != 0:
             exe = Executor(cfg, self.weights, self.spec, self.comm, n_blocks=n_blocks, max_blocks_per_seq=mbs,
                            max_tokens_per_step=constants.PREFILL_CHUNK, max_seqs=max_seqs, device=self.device,
-                           use_graphs=False)
+                           use_graphs=False, pipe=self.pipe)
             assert self.control is not None
             return FollowerServingEngine(exe, self.control)
         tok = load_tokenizer(self.model_dir, cfg.vocab)
@@ -227,7 +239,7 @@ class B200Builder(Builder):
         cls = LeaderServingEngine if self.world > 1 else ServingEngine
         te = TokenEngine(cfg, self.weights, self.spec, self.comm, n_blocks=n_blocks, max_seqs=max_seqs,
                          prefill_chunk=constants.PREFILL_CHUNK, max_blocks_per_seq=mbs, device=self.device,
-                         use_graphs=None if self.world == 1 else False)
+                         use_graphs=None if self.world == 1 else False, pipe=self.pipe)
         eng = cls(cfg, te, tok, str(self.card.model_id), self.card.family, eos, self.card.reasoning_dialect, self.rank,
                   self.control)
         if self.world > 1:

@@ -14,7 +14,7 @@ from exo_b200.shared.cards import ModelCard
 from exo_b200.shared.events import ChunkGenerated, RunnerStatusUpdated
 from exo_b200.shared.messages import (ConnectToGroup, InputMessage, LoadModel, Shutdown, StartWarmup, TextGeneration,
                                       TextGenerationTaskParams)
-from exo_b200.shared.wire import (BoundInstance, NvlinkInstance, RunnerFailed, RunnerReady, RunnerShutdown,
+from exo_b200.shared.wire import (BoundInstance, NvlinkInstance, PipelineShardMetadata, RunnerFailed, RunnerReady, RunnerShutdown,
                                   ShardAssignments, TensorShardMetadata, TokenChunk, ToolCallChunk)
 from exo_b200.utils.channels import channel
 
@@ -50,7 +50,7 @@ def make_checkpoint(tmp_path):
     return d, cfg
 
 
-def instance(model_dir, n):
+def instance(model_dir, n, pp=1):
     card = ModelCard(model_id=ModelId(str(model_dir)), storage_size=Memory.from_mb(10), n_layers=2, hidden_size=256,
                      supports_tensor=True, num_key_value_heads=2, tasks=["TextGeneration"], family="llama")
     nodes = [NodeId(f"n{i}") for i in range(n)]
@@ -58,8 +58,13 @@ def instance(model_dir, n):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    r2s = {rids[i]: TensorShardMetadata(model_card=card, device_rank=i, world_size=n, start_layer=0, end_layer=2, n_layers=2,
-                                        tp_size=n, tp_rank=i) for i in range(n)}
+    if pp > 1:      # one layer per stage, rank = pp_rank * tp + tp_rank
+        tp = n // pp
+        r2s = {rids[i]: PipelineShardMetadata(model_card=card, device_rank=i, world_size=n, start_layer=i // tp, end_layer=i // tp + 1,
+                                              n_layers=2, tp_size=tp, tp_rank=i % tp, pp_size=pp, pp_rank=i // tp) for i in range(n)}
+    else:
+        r2s = {rids[i]: TensorShardMetadata(model_card=card, device_rank=i, world_size=n, start_layer=0, end_layer=2, n_layers=2,
+                                            tp_size=n, tp_rank=i) for i in range(n)}
     return NvlinkInstance(instance_id=InstanceId("i"), shard_assignments=ShardAssignments(
         model_id=card.model_id, runner_to_shard=r2s, node_to_runner=dict(zip(nodes, rids))), rendezvous_port=port,
         gpu_by_node={x: i for i, x in enumerate(nodes)}), nodes, rids
@@ -137,6 +142,18 @@ def test_two_rank_tp_serving_on_gloo_matches_single_rank(tmp_path):
     one = [e.chunk.token_id for e in drive(inst1, n1, r1, lambda: [t1]) if isinstance(e, ChunkGenerated) and isinstance(e.chunk, TokenChunk)]
     inst2, n2, r2 = instance(d, 2)
     t2 = gen_task(inst2, "abc", max_output_tokens=8, bench=True)
+    evs = drive(inst2, n2, r2, lambda: [t2])
+    two = [e.chunk.token_id for e in evs if isinstance(e, ChunkGenerated) and isinstance(e.chunk, TokenChunk)]
+    assert len(two) == 8 and two == one
+
+
+def test_two_stage_pipeline_serving_on_gloo_matches_single_rank(tmp_path):
+    d, cfg = make_checkpoint(tmp_path)
+    inst1, n1, r1 = instance(d, 1)
+    t1 = gen_task(inst1, "pipeline", max_output_tokens=8, bench=True)
+    one = [e.chunk.token_id for e in drive(inst1, n1, r1, lambda: [t1]) if isinstance(e, ChunkGenerated) and isinstance(e.chunk, TokenChunk)]
+    inst2, n2, r2 = instance(d, 2, pp=2)
+    t2 = gen_task(inst2, "pipeline", max_output_tokens=8, bench=True)
     evs = drive(inst2, n2, r2, lambda: [t2])
     two = [e.chunk.token_id for e in evs if isinstance(e, ChunkGenerated) and isinstance(e.chunk, TokenChunk)]
     assert len(two) == 8 and two == one

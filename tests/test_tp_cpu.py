@@ -52,3 +52,51 @@ def test_tp_ranks_reproduce_oracle_tokens(name, world):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got == want
+
+
+def _pp_worker(rank, world, port, name, pp, prompt, n_new, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from exo_b200.engine.engine import Engine
+        from exo_b200.engine.kv import SamplingParams
+        from exo_b200.parallel.comm import GlooComm, PipeComm
+        cfg = preset(name)
+        tp = world // pp
+        pp_rank, tp_rank = divmod(rank, tp)
+        # every rank creates every group, in the same order
+        tp_groups = [dist.new_group([s * tp + t for t in range(tp)]) for s in range(pp)]
+        lane_groups = [dist.new_group([s * tp + t for s in range(pp)]) for t in range(tp)]
+        per = cfg.n_layers // pp
+        spec = ShardSpec(tp_rank=tp_rank, tp_size=tp, pp_rank=pp_rank, pp_size=pp, layer_start=pp_rank * per,
+                         layer_end=cfg.n_layers if pp_rank == pp - 1 else (pp_rank + 1) * per)
+        w = build_weights(cfg, spec, RandomSource(seed=0))
+        comm = GlooComm(tp_groups[pp_rank]) if tp > 1 else None
+        pipe = PipeComm(pp_rank, pp, tp_rank, tp, lane_groups[tp_rank])
+        eng = Engine(cfg, w, spec, comm, n_blocks=64, pipe=pipe, prefill_chunk=32)
+        out = eng.generate(prompt, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+        if rank == 0:
+            q.put((out, pipe.n_hops))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name,world,pp", [("tiny-llama", 2, 2), ("tiny-llama", 4, 2), ("tiny-moe", 2, 2)])
+def test_pipeline_stages_reproduce_oracle_tokens(name, world, pp):
+    """PP2 and PP2 x TP2: stages own contiguous layer ranges, the residual stream hops stage to
+    stage (chunked prefill of 48 tokens in 32-token chunks, then decode), ids come back to rank 0."""
+    cfg = preset(name)
+    prompt = oracle_prompt(48, cfg.vocab, seed=11).tolist()
+    want = OracleModel(cfg, RandomSource(seed=0)).greedy(torch.tensor(prompt), 10)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pp_worker, args=(r, world, port, name, pp, prompt, 10, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got, hops = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == want
+    assert hops == 2 + 9      # first stage: one send per step (2 prefill chunks + 9 decode steps after the first token)
