@@ -57,14 +57,48 @@ class Engine:
 
     # ---- requests ----
     def submit(self, prompt: list[int], params: SamplingParams | None = None, req_id: str | None = None,
-               use_prefix_cache: bool = True, media=None) -> str:
+               use_prefix_cache: bool = True, media=None, kv_prefill=None) -> str:
+        """Queue a request.  ``kv_prefill = (n_tokens, [(k, v) per local layer])`` installs KV computed
+        elsewhere (a prefill instance) for the first ``n_tokens`` prompt tokens; prefill continues after them."""
         rid = req_id or uuid.uuid4().hex
         if not prompt:
             raise ValueError("empty prompt")
         s = Sequence(rid, list(prompt), params or SamplingParams(), media=media, use_prefix_cache=use_prefix_cache)
+        if kv_prefill is not None:
+            n, layers = kv_prefill
+            n = min(int(n), len(prompt) - 1)       # the last prompt token is always computed here (it yields the logits)
+            if n > 0 and self.sched._ensure_blocks(s, n):
+                self.import_kv(s.blocks, n, layers)
+                s.n_computed = n
+            else:
+                self.alloc.release_all(s.blocks)
+                s.blocks = []
         self.seqs[rid] = s
         self.sched.add(s)
         return rid
+
+    # ---- KV hand-over (prefill/decode disaggregation) ----
+    def _slots(self, blocks: list[int], n_tokens: int) -> torch.Tensor:
+        bs = self.alloc.block_size
+        b = torch.tensor(blocks[:-(-n_tokens // bs)], dtype=torch.long, device=self.exe.device)
+        return (b[:, None] * bs + torch.arange(bs, device=self.exe.device)[None, :]).reshape(-1)[:n_tokens]
+
+    def export_kv(self, blocks: list[int], n_tokens: int) -> list[tuple[torch.Tensor, torch.Tensor | None]]:
+        """KV of the first ``n_tokens`` positions held in ``blocks``, per local layer: ``[n_tokens, heads, dim]``."""
+        slots = self._slots(blocks, n_tokens)
+        out = []
+        for i in self.exe.spec.layers(self.cfg):
+            k, v = self.exe.kv.layers[i]
+            out.append((k.view(-1, *k.shape[2:])[slots], None if v is None else v.view(-1, *v.shape[2:])[slots]))
+        return out
+
+    def import_kv(self, blocks: list[int], n_tokens: int, layers) -> None:
+        slots = self._slots(blocks, n_tokens)
+        for i, (k_new, v_new) in zip(self.exe.spec.layers(self.cfg), layers):
+            k, v = self.exe.kv.layers[i]
+            k.view(-1, *k.shape[2:])[slots] = k_new[:n_tokens].to(device=k.device, dtype=k.dtype)
+            if v is not None and v_new is not None:
+                v.view(-1, *v.shape[2:])[slots] = v_new[:n_tokens].to(device=v.device, dtype=v.dtype)
 
     def cancel(self, req_id: str) -> bool:
         ok = self.sched.cancel(req_id)

@@ -174,6 +174,7 @@ class Sequence:
     t_last_token: float = 0.0
     t_prefill_start: float = 0.0
     rng_state: int = 0
+    final_blocks: list[int] = field(default_factory=list)   # block ids at the moment the sequence finished
     embeds: object | None = None  # optional [n_prompt, H] tensor rows replacing token embeddings (vision)
 
     @property

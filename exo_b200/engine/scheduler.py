@@ -58,6 +58,7 @@ class Scheduler:
     def _finish(self, s: Sequence, reason: str) -> None:
         s.finished, s.finish_reason = True, reason
         self._publish_full_blocks(s)
+        s.final_blocks = list(s.blocks)       # still holds the sequence's KV until the allocator hands them out again
         self.alloc.release_all(s.blocks)
         s.blocks = []
         if s in self.running:

@@ -14,6 +14,7 @@
 //
 // Fused: RMSNorm prologue (sum of squares + norm weight), bias, residual add, SwiGLU epilogue
 // (a stage then carries RS/2 gate rows and the matching RS/2 up rows as two copies).
+#include <cstdlib>
 #include "tc_common.cuh"
 
 namespace {
@@ -279,6 +280,19 @@ EXO_API int exo_gemv_stream_last_error() {
   return v;
 }
 
+// CTAs co-resident per SM (EXO_GEMV_CTAS_PER_SM, 1 or 2).  With 2, each CTA's ring is half as deep
+// and the grid twice as wide: the same bytes are in flight per SM, and a CTA of the NEXT kernel in
+// the stream can become resident (programmatic dependent launch) and start its weight stream while
+// this kernel's last CTAs drain.
+static int ctas_per_sm() {
+  static int v = 0;
+  if (!v) {
+    const char* e = getenv("EXO_GEMV_CTAS_PER_SM");
+    v = (e && e[0] == '2') ? 2 : 1;
+  }
+  return v;
+}
+
 // Stage geometry for a (M, K, swiglu) problem; false when the ring would not hold two stages.
 static bool stream_config(int M, int K, int swiglu, int* RS_out, int* stages_out, size_t* fixed_out) {
   const int row_bytes = K * 2;
@@ -291,7 +305,13 @@ static bool stream_config(int M, int K, int swiglu, int* RS_out, int* stages_out
   // The whole shared memory of the SM is the ring: ~190 KB in flight per SM is what it takes to
   // cover HBM latency at full bandwidth (a 104 KB ring, tried so that the next kernel's CTA could
   // co-reside and prefetch, lost 25 % of the bandwidth).
-  size_t budget = 196 * 1024;
+  size_t budget = ctas_per_sm() == 2 ? 104 * 1024 : 196 * 1024;
+  if (ctas_per_sm() == 2 && (size_t)RS * row_bytes > 16 * 1024) {   // smaller stages so that the ring still has depth
+    RS = (16 * 1024) / row_bytes;
+    if (RS < 1) RS = 1;
+    if (RS >= 4) RS &= ~3;
+    if (swiglu) { RS &= ~1; if (RS < 2) RS = 2; }
+  }
   int stages = (int)((budget - fixed) / ((size_t)RS * row_bytes));
   if (stages > 8) stages = 8;
   *RS_out = RS; *stages_out = stages; *fixed_out = fixed;
@@ -330,7 +350,8 @@ EXO_API int exo_gemv_stream(const void* x, const void* W, const void* bias, cons
   p.stage_bytes = RS * row_bytes;
   p.stages = stages;
   const size_t smem = fixed + (size_t)stages * p.stage_bytes;
-  int grid = p.n_groups < 148 ? p.n_groups : 148;
+  const int max_grid = 148 * ctas_per_sm();
+  int grid = p.n_groups < max_grid ? p.n_groups : max_grid;
   const int jv = (K / 8 / 8 + 31) / 32;
   int rc;
 #define BY_JV(MM)                                                                              \

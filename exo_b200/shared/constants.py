@@ -94,6 +94,7 @@ EXO_GPU_MEMORY_FRACTION = float(os.getenv("EXO_GPU_MEMORY_FRACTION", "0.90"))
 MAX_TOKENS = 32168
 DEFAULT_TOP_LOGPROBS = 5
 PREFILL_CHUNK = 4096
+REMOTE_PREFILL_MIN_TOKENS = int(os.getenv("EXO_REMOTE_PREFILL_MIN_TOKENS", "1000"))   # shorter prompts are prefilled locally
 
 DEFAULT_API_PORT = 52415
 DEFAULT_BUS_PORT = 52414

@@ -244,6 +244,8 @@ class B200Builder(Builder):
                   self.control)
         if self.world > 1:
             te.plan_sink = eng._sink
+        elif constants.ENABLE_DISAGGREGATION and not cfg.mla:
+            eng.enable_prefill_server()      # its port travels in RunnerReady; the master pairs instances through links
         return eng
 
     def close(self) -> None:

@@ -10,7 +10,10 @@ broadcasts each step's packed plan; the other ranks execute plans and keep no re
 from __future__ import annotations
 
 import os
+import queue
+import threading
 import time
+import uuid
 from collections.abc import Iterable, Iterator
 from pathlib import Path
 from typing import Any
@@ -35,6 +38,42 @@ from ..base import Builder, Cancelled, Engine, Finished, LoadProgress, StepItem
 from .parsers import tool_dialect_for
 from .stream_parser import HarmonyParser, StreamParser
 from .tokenizer import Detokenizer, eos_ids, load_tokenizer, render_prompt
+from ...disaggregated import protocol as dproto
+from ...disaggregated.server import PrefillServer, remote_prefill_fetch
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}
+_DTYPE_NAME = {v: k for k, v in _TORCH_DTYPE.items()}
+KV_CHUNK_TOKENS = 4096
+
+
+class _PrefillJob:
+    """A prompt whose KV a decode instance asked for; filled in by the engine loop, sent by the server thread."""
+
+    def __init__(self, request: dproto.PrefillRequest):
+        self.request = request
+        self.done = threading.Event()
+        self.layers: list[tuple[torch.Tensor, torch.Tensor | None]] = []     # CPU tensors [tokens, heads, dim]
+        self.n_tokens = 0
+        self.error: str | None = None
+
+
+class _RemoteFetch:
+    """A request waiting for its prompt KV from a prefill instance (fetched on a side thread)."""
+
+    def __init__(self, task: TextGeneration, ids: list[int], endpoint: str, model_id: str):
+        self.task, self.ids = task, ids
+        self.result = None
+        self.error: Exception | None = None
+        self.t0 = time.perf_counter()
+        req = dproto.PrefillRequest(request_id=str(task.task_id), model_id=model_id, token_ids=list(ids), start_pos=0)
+
+        def run() -> None:
+            try:
+                self.result = remote_prefill_fetch(endpoint, req)
+            except Exception as e:  # noqa: BLE001 - any failure falls back to local prefill
+                self.error = e
+        self.thread = threading.Thread(target=run, name="remote-prefill", daemon=True)
+        self.thread.start()
 
 
 def find_model_dir(model_id: str) -> Path | None:
@@ -70,6 +109,13 @@ class ServingEngine(Engine):
         self.reqs: dict[str, _Request] = {}
         self.finished_buffer: list[tuple[TaskId, StepItem]] = []
         self.peak_mem = 0
+        # prefill/decode disaggregation: jobs served for other instances, and fetches this instance waits for
+        self.prefill_server: PrefillServer | None = None
+        self.prefill_server_port: int | None = None
+        self.prefill_jobs: "queue.Queue[_PrefillJob]" = queue.Queue()
+        self.prefill_running: dict[str, tuple[_PrefillJob, Any, int]] = {}
+        self.remote: dict[str, _RemoteFetch] = {}
+        self.remote_prefills = 0
 
     # ---- Engine interface ----
     def warmup(self) -> None:
@@ -77,7 +123,101 @@ class ServingEngine(Engine):
 
     @property
     def has_work(self) -> bool:
-        return bool(self.reqs) or bool(self.finished_buffer) or self.te.has_work
+        return (bool(self.reqs) or bool(self.finished_buffer) or self.te.has_work or bool(self.remote)
+                or bool(self.prefill_running) or not self.prefill_jobs.empty())
+
+    # ---- disaggregation: prefill side ----
+    def enable_prefill_server(self, host: str = "0.0.0.0", port: int = 0) -> int:
+        """Serve prompt KV to decode instances (single-rank instances only: one rank holds every KV head)."""
+        self.prefill_server = PrefillServer(self._resolve_prefill, host, port)
+        self.prefill_server_port = self.prefill_server.port
+        return self.prefill_server.port
+
+    def _resolve_prefill(self, request: dproto.PrefillRequest, wfile) -> bool:
+        """Server thread: queue the prompt for the engine loop, wait, stream the KV back."""
+        if request.model_id and request.model_id != self.model_id:
+            raise ValueError(f"this instance serves {self.model_id}, not {request.model_id}")
+        job = _PrefillJob(request)
+        self.prefill_jobs.put(job)
+        if not job.done.wait(timeout=float(os.environ.get("EXO_PREFILL_JOB_TIMEOUT_S", "600"))):
+            return False
+        if job.error is not None:
+            raise RuntimeError(job.error)
+        dt = _DTYPE_NAME[job.layers[0][0].dtype] if job.layers else "float32"
+        dproto.write_header(wfile, dproto.Header(request_id=request.request_id, model_id=self.model_id,
+                                                 num_layers=len(job.layers), dtype=dt, start_pos=request.start_pos))
+        lo = min(request.start_pos, job.n_tokens)
+        for t0 in range(lo, job.n_tokens, KV_CHUNK_TOKENS):
+            t1 = min(job.n_tokens, t0 + KV_CHUNK_TOKENS)
+            for li, (k, v) in enumerate(job.layers):
+                kb = k[t0:t1].contiguous().view(torch.uint8).numpy().tobytes()
+                vb = b"" if v is None else v[t0:t1].contiguous().view(torch.uint8).numpy().tobytes()
+                dproto.write_message(wfile, dproto.KVChunk(layer_idx=li, num_tokens=t1 - t0, n_heads=k.shape[1] if k.dim() == 3 else 1,
+                                                           head_dim=k.shape[-1], dtype=dt, keys=kb, values=vb))
+        dproto.write_message(wfile, dproto.Done(total_tokens=job.n_tokens))
+        return True
+
+    def _start_prefill_jobs(self) -> None:
+        while True:
+            try:
+                job = self.prefill_jobs.get_nowait()
+            except queue.Empty:
+                return
+            ids = job.request.token_ids
+            target = max(0, len(ids) - 2)       # the decode side computes the last two tokens itself
+            if target == 0:
+                job.done.set()
+                continue
+            rid = f"prefill-{uuid.uuid4().hex}"
+            try:
+                self.te.submit(ids[:target], SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True), req_id=rid)
+            except Exception as e:  # noqa: BLE001
+                job.error = str(e)
+                job.done.set()
+                continue
+            self.prefill_running[rid] = (job, self.te.seqs[rid], target)
+
+    def _finish_prefill_job(self, rid: str) -> None:
+        job, seq, target = self.prefill_running.pop(rid)
+        try:
+            # the sequence's blocks were just released but nothing has been allocated since: the data is intact
+            job.layers = [(k.cpu(), None if v is None else v.cpu()) for k, v in self.te.export_kv(seq.final_blocks, target)]
+            job.n_tokens = target
+        except Exception as e:  # noqa: BLE001
+            job.error = str(e)
+        job.done.set()
+
+    # ---- disaggregation: decode side ----
+    def _want_remote_prefill(self, p, ids: list[int]) -> bool:
+        return (bool(p.prefill_endpoint) and len(ids) > constants.REMOTE_PREFILL_MIN_TOKENS
+                and self.te.exe.spec.tp_size == 1 and self.te.exe.spec.pp_size == 1 and not self.cfg.mla)
+
+    def _admit_remote(self) -> None:
+        for rid, f in list(self.remote.items()):
+            if f.thread.is_alive():
+                continue
+            del self.remote[rid]
+            r = self.reqs.get(rid)
+            if r is None:      # cancelled while the KV was in flight
+                continue
+            p = f.task.task_params
+            kv = None
+            if f.error is None and f.result is not None and f.result.total_tokens > 0:
+                try:
+                    dt = _TORCH_DTYPE[f.result.header.dtype]
+                    layers = []
+                    for li in range(f.result.header.num_layers):
+                        chunks = f.result.chunks[li]
+                        shape = (-1, chunks[0].n_heads, chunks[0].head_dim)
+                        k = torch.frombuffer(bytearray(b"".join(c.keys for c in chunks)), dtype=dt).view(shape)
+                        v = torch.frombuffer(bytearray(b"".join(c.values for c in chunks)), dtype=dt).view(shape)
+                        layers.append((k, v))
+                    kv = (f.result.total_tokens, layers)
+                    self.remote_prefills += 1
+                except Exception:  # noqa: BLE001 - malformed stream: compute locally
+                    kv = None
+            self.te.submit(f.ids, self._sampling(p), req_id=rid, use_prefix_cache=p.use_prefix_cache or not p.bench,
+                           kv_prefill=kv)
 
     def _sampling(self, p) -> SamplingParams:
         bench = p.bench
@@ -111,6 +251,9 @@ class ServingEngine(Engine):
         stops = [p.stop] if isinstance(p.stop, str) else list(p.stop or [])
         rid = str(task.task_id)
         self.reqs[rid] = _Request(task, ids, Detokenizer(self.tok, ids), parser, stops)
+        if self._want_remote_prefill(p, ids):
+            self.remote[rid] = _RemoteFetch(task, ids, p.prefill_endpoint, self.model_id)
+            return
         self.te.submit(ids, self._sampling(p), req_id=rid, use_prefix_cache=p.use_prefix_cache or not p.bench)
 
     def cancel(self, task_id: TaskId) -> None:
@@ -170,12 +313,19 @@ class ServingEngine(Engine):
 
     def step(self) -> Iterable[tuple[TaskId, StepItem]]:
         out, self.finished_buffer = self.finished_buffer, []
+        self._start_prefill_jobs()
+        self._admit_remote()
         if not self.te.has_work:
+            if self.remote:
+                time.sleep(0.002)      # only waiting for KV from a prefill instance
             return out
         with tracing.trace("engine.step", self.rank, "step", cuda=self.te.exe.cuda):
             outs = self.te.step()
         now = time.perf_counter()
         for o in outs:
+            if o.finished and o.req_id in self.prefill_running:
+                self._finish_prefill_job(o.req_id)
+                continue
             r = self.reqs.get(o.req_id)
             if r is None:
                 continue
@@ -215,5 +365,7 @@ class ServingEngine(Engine):
         return spans
 
     def close(self) -> None:
+        if self.prefill_server is not None:
+            self.prefill_server.stop()
         if self.control is not None:
             self.control.close()
