@@ -174,27 +174,46 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (s.is_last) {
+        // The last split of this tile to arrive sums the partial planes.  All 128 epilogue threads take
+        // part: a thread owns four consecutive features and every fourth row, and keeps eight 16-byte
+        // loads in flight per row (the planes are a split apart in memory), so the reduce costs a few
+        // L2 round trips instead of one per (split, row).  Splits are added in index order: the sum
+        // does not depend on which CTA came last.
         __threadfence();
-        if (n < p.N) {
-          float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
-          const int mcount = min(BN, p.M - m0);
-          const size_t plane = (size_t)p.M * p.N;
-          for (int mm = 0; mm < mcount; mm += 4) {
-            float y[4] = {bias, bias, bias, bias};
-            const float* base = p.partial + (size_t)(m0 + mm) * p.N + n;
-            for (int sp = 0; sp < p.splits; sp++) {  // fixed split order → deterministic sum
+        const int et = threadIdx.x - 64;          // 0..127 among the epilogue warps
+        const int nq = n0 + (et & 31) * 4;
+        const int mcount = min(BN, p.M - m0);
+        const size_t plane = (size_t)p.M * p.N;
+        const bool vec = (p.N & 3) == 0 && nq + 3 < p.N;
+        for (int mm = et >> 5; mm < mcount; mm += 4) {
+          const float* base = p.partial + (size_t)(m0 + mm) * p.N + nq;
+          float y[4] = {0.f, 0.f, 0.f, 0.f};
+          if (vec) {
+            int sp = 0;
+            for (; sp + 8 <= p.splits; sp += 8) {
+              float4 v[8];
+#pragma unroll
+              for (int u = 0; u < 8; u++) v[u] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)(sp + u) * plane));
+#pragma unroll
+              for (int u = 0; u < 8; u++) { y[0] += v[u].x; y[1] += v[u].y; y[2] += v[u].z; y[3] += v[u].w; }
+            }
+            for (; sp < p.splits; sp++) {
+              float4 v = __ldcg(reinterpret_cast<const float4*>(base + (size_t)sp * plane));
+              y[0] += v.x; y[1] += v.y; y[2] += v.z; y[3] += v.w;
+            }
+          } else {
+            for (int sp = 0; sp < p.splits; sp++)
 #pragma unroll
               for (int j = 0; j < 4; j++)
-                if (mm + j < mcount) y[j] += __ldcg(base + sp * plane + (size_t)j * p.N);
-            }
+                if (nq + j < p.N) y[j] += __ldcg(base + (size_t)sp * plane + j);
+          }
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-              if (mm + j < mcount) {
-                size_t o = (size_t)(m0 + mm + j) * p.ldo + n;
-                float v = y[j];
-                if (p.residual) v += __bfloat162float(p.residual[o]);
-                p.out[o] = __float2bfloat16_rn(v);
-              }
+          for (int j = 0; j < 4; j++) {
+            if (nq + j < p.N) {
+              size_t o = (size_t)(m0 + mm) * p.ldo + nq + j;
+              float v = y[j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
+              if (p.residual) v += __bfloat162float(p.residual[o]);
+              p.out[o] = __float2bfloat16_rn(v);
             }
           }
         }
