@@ -1,0 +1,194 @@
+"""Throughput benchmark of a running cluster through ``/bench/chat/completions``.
+
+Method (the reference's, ``bench/METHODOLOGY.md`` and ``bench/exo_bench.py``): prompts of an exact
+token length are built by binary search over a repeated atom string, measured with the model's own
+tokenizer and chat template when they are available locally (otherwise with the server's reported
+``prompt_tokens``); the bench endpoint runs with the prefix cache off (unless
+``--use-prefix-cache``), EOS banned and output parsing bypassed; prefill and generation rates are
+the server's per-task figures (``generation_tps = (tokens - 1) / (t_last - t_first)``); with
+``--concurrency N`` the N requests are released together by a barrier and the aggregate is
+``max(per-request tps) * N``.  Results are one JSON object per (pp, tg, concurrency, repeat).
+
+    python -m exo_b200.bench.exo_bench --model meta-llama/Llama-3.1-8B-Instruct --pp 512,2048 --tg 128 \
+        --concurrency 1,8 --repeat 3 --place --sharding Tensor --min-nodes 2 --json-out results.jsonl
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+import threading
+import time
+from collections.abc import Callable
+from typing import Any
+
+from .client import ApiError, ExoClient
+
+ATOM = "a "
+
+
+def build_prompt(count_tokens: Callable[[str], int], target: int, atom: str = ATOM) -> tuple[str, int]:
+    """Content whose rendered prompt has exactly ``target`` tokens (or the closest reachable count)."""
+    lo, hi = 0, max(8, target * 4)
+    while count_tokens(atom * hi) < target and hi < (1 << 20):      # a counter that never grows must not loop forever
+        hi *= 2
+    best = (atom * hi, count_tokens(atom * hi))
+    while lo <= hi:
+        mid = (lo + hi) // 2
+        n = count_tokens(atom * mid)
+        if abs(n - target) < abs(best[1] - target):
+            best = (atom * mid, n)
+        if n == target:
+            return atom * mid, n
+        if n < target:
+            lo = mid + 1
+        else:
+            hi = mid - 1
+    return best
+
+
+def local_token_counter(model_dir: str | None, vocab: int = 0) -> Callable[[str], int] | None:
+    if not model_dir:
+        return None
+    from ..shared.messages import InputMessage, TextGenerationTaskParams
+    from ..worker.engines.b200.tokenizer import load_tokenizer, render_prompt
+    from pathlib import Path
+    tok = load_tokenizer(Path(model_dir), vocab or 1 << 17)
+
+    def count(content: str) -> int:
+        p = TextGenerationTaskParams(model="m", input=[InputMessage(role="user", content=content)])
+        text, _ = render_prompt(tok, p)
+        return len(tok.encode(text, add_special_tokens=not getattr(tok, "chat_template", None)))
+    return count
+
+
+def server_token_counter(client: ExoClient, model: str) -> Callable[[str], int]:
+    """No local tokenizer: ask the server (one-token bench request, read ``usage.prompt_tokens``)."""
+    cache: dict[int, int] = {}
+
+    def count(content: str) -> int:
+        k = len(content)
+        if k not in cache:
+            r = client.post("/bench/chat/completions", {"model": model, "max_tokens": 2, "messages": [{"role": "user", "content": content}]})
+            cache[k] = int(r["usage"]["prompt_tokens"])
+        return cache[k]
+    return count
+
+
+def one_request(client: ExoClient, model: str, content: str, tg: int, use_prefix_cache: bool) -> dict[str, Any]:
+    t0 = time.perf_counter()
+    r = client.post("/bench/chat/completions", {"model": model, "max_tokens": tg, "temperature": 0.0, "use_prefix_cache": use_prefix_cache,
+                                                "messages": [{"role": "user", "content": content}]})
+    el = time.perf_counter() - t0
+    gs = r.get("generation_stats") or {}
+    return {"elapsed_s": el, "prompt_tps": gs.get("prompt_tps"), "generation_tps": gs.get("generation_tps"),
+            "pp_tokens": gs.get("prompt_tokens") or (r.get("usage") or {}).get("prompt_tokens"),
+            "tg_tokens": gs.get("generation_tokens") or (r.get("usage") or {}).get("completion_tokens"),
+            "peak_memory_bytes": (gs.get("peak_memory_usage") or {}).get("inBytes") if isinstance(gs.get("peak_memory_usage"), dict) else None,
+            "power": r.get("power_usage")}
+
+
+def concurrent_requests(make_client: Callable[[], ExoClient], n: int, model: str, content: str, tg: int, use_prefix_cache: bool) -> list[dict[str, Any]]:
+    """N requests released at the same instant; every ``elapsed_s`` counts from the shared start."""
+    barrier = threading.Barrier(n)
+    start: list[float] = []
+    lock = threading.Lock()
+    results: list[dict[str, Any] | BaseException] = [RuntimeError("not run")] * n
+
+    def work(i: int) -> None:
+        c = make_client()
+        barrier.wait()
+        with lock:
+            if not start:
+                start.append(time.perf_counter())
+        try:
+            r = one_request(c, model, content, tg, use_prefix_cache)
+            r["elapsed_s"] = time.perf_counter() - start[0]
+            results[i] = r
+        except BaseException as e:  # noqa: BLE001 - reported per request
+            results[i] = e
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(n)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    errs = [r for r in results if isinstance(r, BaseException)]
+    if errs:
+        raise errs[0]
+    return results  # type: ignore[return-value]
+
+
+def aggregate(rows: list[dict[str, Any]], concurrency: int) -> dict[str, Any]:
+    tps = [r["generation_tps"] for r in rows if r.get("generation_tps")]
+    pps = [r["prompt_tps"] for r in rows if r.get("prompt_tps")]
+    per_req = max(tps) if tps else None
+    return {"concurrency": concurrency, "per_req_gen_tps": per_req, "agg_gen_tps": per_req * concurrency if per_req else None,
+            "mean_prompt_tps": statistics.fmean(pps) if pps else None, "batch_wall_s": max(r["elapsed_s"] for r in rows),
+            "pp_tokens": rows[0].get("pp_tokens"), "tg_tokens": rows[0].get("tg_tokens")}
+
+
+def main(argv: list[str] | None = None) -> int:
+    ap = argparse.ArgumentParser(prog="exo-bench")
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=52415)
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--pp", default="512", help="prompt lengths, comma separated")
+    ap.add_argument("--tg", default="128", help="generation lengths, comma separated (>= 2)")
+    ap.add_argument("--concurrency", default="1")
+    ap.add_argument("--repeat", type=int, default=1)
+    ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--use-prefix-cache", action="store_true")
+    ap.add_argument("--model-dir", default=None, help="local checkpoint directory: exact prompt sizing with its tokenizer")
+    ap.add_argument("--place", action="store_true", help="place an instance first (and delete it afterwards)")
+    ap.add_argument("--sharding", default="Tensor", choices=["Tensor", "Pipeline"])
+    ap.add_argument("--min-nodes", type=int, default=1)
+    ap.add_argument("--json-out", default=None)
+    ap.add_argument("--stdout", action="store_true")
+    a = ap.parse_args(argv)
+    client = ExoClient(a.host, a.port)
+    placed = None
+    if a.place:
+        client.place(a.model, a.sharding, a.min_nodes)
+    iid = client.wait_ready(a.model)
+    if a.place:
+        placed = iid
+    counter = local_token_counter(a.model_dir) or server_token_counter(client, a.model)
+    out = open(a.json_out, "a") if a.json_out else None
+    rc = 0
+    try:
+        for pp in [int(x) for x in a.pp.split(",")]:
+            content, actual = build_prompt(counter, pp)
+            for tg in [int(x) for x in a.tg.split(",")]:
+                if tg < 2:
+                    print("tg must be >= 2: the generation rate is measured between the first and the last token", file=sys.stderr)
+                    return 2
+                for conc in [int(x) for x in a.concurrency.split(",")]:
+                    for rep in range(-a.warmup, a.repeat):
+                        try:
+                            rows = ([one_request(client, a.model, content, tg, a.use_prefix_cache)] if conc == 1 else
+                                    concurrent_requests(lambda: ExoClient(a.host, a.port), conc, a.model, content, tg, a.use_prefix_cache))
+                        except ApiError as e:
+                            print(f"pp={pp} tg={tg} c={conc}: {e}", file=sys.stderr)
+                            rc = 1
+                            continue
+                        if rep < 0:
+                            continue
+                        row = {"model": a.model, "pp_target": pp, "pp_built": actual, "tg": tg, "repeat": rep, **aggregate(rows, conc),
+                               "requests": rows}
+                        line = json.dumps(row)
+                        if out:
+                            out.write(line + "\n")
+                            out.flush()
+                        if a.stdout or not out:
+                            print(line)
+    finally:
+        if out:
+            out.close()
+        if placed:
+            client.delete_instance(placed)
+    return rc
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

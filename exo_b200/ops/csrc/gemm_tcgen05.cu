@@ -185,35 +185,56 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const int mcount = min(BN, p.M - m0);
         const size_t plane = (size_t)p.M * p.N;
         const bool vec = (p.N & 3) == 0 && nq + 3 < p.N;
-        for (int mm = et >> 5; mm < mcount; mm += 4) {
-          const float* base = p.partial + (size_t)(m0 + mm) * p.N + nq;
-          float y[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int mm = et >> 5; mm < mcount; mm += 8) {      // two rows per pass: up to 16 loads in flight per thread
+          const bool two = mm + 4 < mcount;
+          const float* base0 = p.partial + (size_t)(m0 + mm) * p.N + nq;
+          const float* base1 = base0 + (size_t)4 * p.N;
+          float y[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
           if (vec) {
             int sp = 0;
             for (; sp + 8 <= p.splits; sp += 8) {
-              float4 v[8];
+              float4 v[2][8];
 #pragma unroll
-              for (int u = 0; u < 8; u++) v[u] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)(sp + u) * plane));
+              for (int u = 0; u < 8; u++) {
+                v[0][u] = __ldcg(reinterpret_cast<const float4*>(base0 + (size_t)(sp + u) * plane));
+                v[1][u] = two ? __ldcg(reinterpret_cast<const float4*>(base1 + (size_t)(sp + u) * plane)) : make_float4(0, 0, 0, 0);
+              }
 #pragma unroll
-              for (int u = 0; u < 8; u++) { y[0] += v[u].x; y[1] += v[u].y; y[2] += v[u].z; y[3] += v[u].w; }
+              for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int u = 0; u < 8; u++) { y[r][0] += v[r][u].x; y[r][1] += v[r][u].y; y[r][2] += v[r][u].z; y[r][3] += v[r][u].w; }
             }
-            for (; sp < p.splits; sp++) {
-              float4 v = __ldcg(reinterpret_cast<const float4*>(base + (size_t)sp * plane));
-              y[0] += v.x; y[1] += v.y; y[2] += v.z; y[3] += v.w;
+            float4 t[2][7];
+            const int rem = p.splits - sp;
+#pragma unroll
+            for (int u = 0; u < 7; u++) {
+              t[0][u] = u < rem ? __ldcg(reinterpret_cast<const float4*>(base0 + (size_t)(sp + u) * plane)) : make_float4(0, 0, 0, 0);
+              t[1][u] = (two && u < rem) ? __ldcg(reinterpret_cast<const float4*>(base1 + (size_t)(sp + u) * plane)) : make_float4(0, 0, 0, 0);
             }
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+              for (int u = 0; u < 7; u++) { y[r][0] += t[r][u].x; y[r][1] += t[r][u].y; y[r][2] += t[r][u].z; y[r][3] += t[r][u].w; }
           } else {
             for (int sp = 0; sp < p.splits; sp++)
 #pragma unroll
               for (int j = 0; j < 4; j++)
-                if (nq + j < p.N) y[j] += __ldcg(base + (size_t)sp * plane + j);
+                if (nq + j < p.N) {
+                  y[0][j] += __ldcg(base0 + (size_t)sp * plane + j);
+                  if (two) y[1][j] += __ldcg(base1 + (size_t)sp * plane + j);
+                }
           }
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            if (nq + j < p.N) {
-              size_t o = (size_t)(m0 + mm) * p.ldo + nq + j;
-              float v = y[j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
-              if (p.residual) v += __bfloat162float(p.residual[o]);
-              p.out[o] = __float2bfloat16_rn(v);
+          for (int r = 0; r < 2; r++) {
+            if (r == 1 && !two) break;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              if (nq + j < p.N) {
+                size_t o = (size_t)(m0 + mm + 4 * r) * p.ldo + nq + j;
+                float v = y[r][j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
+                if (p.residual) v += __bfloat162float(p.residual[o]);
+                p.out[o] = __float2bfloat16_rn(v);
+              }
             }
           }
         }

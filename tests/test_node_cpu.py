@@ -120,6 +120,14 @@ def test_two_nodes_place_generate_in_every_dialect_and_delete(cluster_env):
                 # bench endpoint reports stats-bearing response shape
                 r = await http.post("/bench/chat/completions", json=body)
                 assert r.status_code == 200 and "power_usage" in r.json()
+                # the benchmark tool drives the same endpoint (blocking client, so off the event loop)
+                from exo_b200.bench import exo_bench
+                out_file = cluster_env / "bench.jsonl"
+                rc = await anyio.to_thread.run_sync(lambda: exo_bench.main(
+                    ["--port", str(port), "--model", "org/tiny", "--pp", "1", "--tg", "4", "--concurrency", "1,2", "--warmup", "0",
+                     "--json-out", str(out_file)]))
+                rows = [json.loads(ln) for ln in out_file.read_text().splitlines()]
+                assert rc == 0 and [r["concurrency"] for r in rows] == [1, 2] and len(rows[1]["requests"]) == 2
                 # delete: runners shut down, instance disappears
                 iid = next(iter((await http.get("/state")).json()["instances"]))
                 assert (await http.delete(f"/instance/{iid}")).status_code == 200
