@@ -95,7 +95,13 @@ class FusedComm:
         if x.dtype != torch.bfloat16 or x.numel() % 8:
             raise K.KernelError("fused all-reduce takes bf16 tensors whose size is a multiple of 8")
         if x.numel() > self.max_elems:
-            raise K.KernelError(f"tensor of {x.numel()} elements exceeds the arena slot ({self.max_elems})")
+            # larger than one arena slot (a long prefill chunk): reduce it in row blocks that fit
+            if x.dim() != 2 or x.shape[1] > self.max_elems:
+                raise K.KernelError(f"tensor of {x.numel()} elements exceeds the arena slot ({self.max_elems})")
+            rows = max(8, (self.max_elems // x.shape[1]) // 8 * 8)
+            parts = [self.all_reduce(x[r:r + rows], None if residual is None else residual[r:r + rows])
+                     for r in range(0, x.shape[0], rows)]
+            return torch.cat(parts, dim=0)
         out = torch.empty_like(x)
         parity = self._ar & 1
         self._ar += 1

@@ -1,0 +1,160 @@
+"""Distributed denoising schedules: pipeline stages, CFG-parallel groups, PipeFusion patches.
+
+Mirrors the roles of the reference's ``DiffusionRunner`` (``src/exo/worker/engines/image/
+pipeline/runner.py``): the transformer blocks are split into contiguous ranges over the ranks of a
+pipeline group; with classifier-free guidance and an even world the ranks form two mirrored
+groups, one denoising the prompt and one the empty prompt, whose last stages swap their
+predictions every step (C10); after ``num_sync_steps`` synchronous steps that fill every block's
+image K/V cache, the latent is cut into as many row patches as there are stages and the patches
+flow through the pipeline back to back, each attending to fresh K/V of its own rows and to the
+previous step's K/V of the others (PipeFusion), so all stages are busy at once.  Rank layout:
+``rank = cfg_rank * pipe_world + pipe_rank``.  Every rank draws the same noise from the seed and
+ends every step holding the same latent.
+"""
+from __future__ import annotations
+
+from collections.abc import Callable, Iterator
+
+import torch
+import torch.distributed as dist
+
+from .dit import Dit, timesteps
+
+
+class DiffusionRunner:
+    def __init__(self, model: Dit, *, rank: int = 0, world: int = 1, cfg_parallel: bool = False, num_sync_steps: int = 1,
+                 pipe_groups: list | None = None):
+        self.m, self.rank, self.world = model, rank, world
+        self.cfg_parallel = cfg_parallel and world % 2 == 0 and model.cfg.uses_cfg
+        self.pipe_world = world // 2 if self.cfg_parallel else world
+        self.cfg_rank, self.pipe_rank = divmod(rank, self.pipe_world)
+        self.base = self.cfg_rank * self.pipe_world               # first rank of this pipeline group
+        self.group = None if pipe_groups is None else pipe_groups[self.cfg_rank]
+        self.num_sync_steps = num_sync_steps
+        self.first, self.last = self.pipe_rank == 0, self.pipe_rank == self.pipe_world - 1
+        self.n_exchanges = self.n_patch_hops = 0
+
+    # ---- p2p helpers (blocking; tensors are tiny next to the compute) ----
+    def _send(self, t: torch.Tensor, dst: int) -> None:
+        dist.send(t.contiguous().cpu() if t.device.type == "cpu" else t.contiguous(), dst)
+
+    def _recv(self, like: torch.Tensor, src: int) -> torch.Tensor:
+        buf = torch.empty_like(like)
+        dist.recv(buf, src)
+        return buf
+
+    # ---- one prediction of this pipeline group ----
+    def _predict_sync(self, lat, t, txt0, pooled, caches) -> torch.Tensor:
+        """Whole-image pass through the stages in order; fills the K/V caches.  Returns v on every stage."""
+        m = self.m
+        gh, gw = lat.shape[1] // m.cfg.patch, lat.shape[2] // m.cfg.patch
+        vec = m.time_vec(t, pooled)
+        if self.first:
+            txt, img = txt0, m.embed_tokens(lat, gh, gw)
+        else:
+            txt = self._recv(txt0, self.base + self.pipe_rank - 1)
+            img = self._recv(torch.empty(gh * gw, m.cfg.hidden, device=m.device), self.base + self.pipe_rank - 1)
+        txt, img = m.run_blocks(txt, img, vec, caches)
+        if not self.last:
+            self._send(txt, self.base + self.pipe_rank + 1)
+            self._send(img, self.base + self.pipe_rank + 1)
+        v = m.head(img, gh, gw) if self.last else torch.empty_like(lat)
+        if self.pipe_world > 1:
+            dist.broadcast(v, src=self.base + self.pipe_world - 1, group=self.group)
+        return v
+
+    def _predict_patches(self, lat, t, txt0, pooled, caches) -> torch.Tensor:
+        """PipeFusion step: row patches flow through the stages one after another."""
+        m, P = self.m, self.pipe_world
+        gh, gw = lat.shape[1] // m.cfg.patch, lat.shape[2] // m.cfg.patch
+        vec = m.time_vec(t, pooled)
+        bounds = [(gh * p // P) * gw for p in range(P + 1)]
+        tokens_in = m.embed_tokens(lat, gh, gw) if self.first else None
+        out = torch.empty(gh * gw, m.cfg.latent_channels * m.cfg.patch ** 2, device=m.device) if self.last else None
+        for p in range(P):
+            rows = slice(bounds[p], bounds[p + 1])
+            n = bounds[p + 1] - bounds[p]
+            if self.first:
+                txt, img = txt0, tokens_in[rows]
+            else:
+                txt = self._recv(txt0, self.base + self.pipe_rank - 1)
+                img = self._recv(torch.empty(n, m.cfg.hidden, device=m.device), self.base + self.pipe_rank - 1)
+            txt, img = m.run_blocks(txt, img, vec, caches, rows)
+            if not self.last:
+                self._send(txt, self.base + self.pipe_rank + 1)
+                self._send(img, self.base + self.pipe_rank + 1)
+                self.n_patch_hops += 1
+            else:
+                out[rows] = torch.nn.functional.linear(torch.nn.functional.layer_norm(img, (m.cfg.hidden,)), m.img_out)
+        v = m.unpatchify(out, gh, gw) if self.last else torch.empty_like(lat)
+        dist.broadcast(v, src=self.base + P - 1, group=self.group)
+        return v
+
+    def _guided(self, v: torch.Tensor, v_other_fn: Callable[[], torch.Tensor] | None, guidance: float) -> torch.Tensor:
+        """Combine the conditional and unconditional predictions (local second pass, or swap with the mirror group)."""
+        if self.cfg_parallel:
+            partner = (1 - self.cfg_rank) * self.pipe_world + self.pipe_rank
+            if self.cfg_rank == 0:
+                self._send(v, partner)
+                other = self._recv(v, partner)
+            else:
+                other = self._recv(v, partner)
+                self._send(v, partner)
+            self.n_exchanges += 1
+            cond, uncond = (v, other) if self.cfg_rank == 0 else (other, v)
+            return uncond + guidance * (cond - uncond)
+        if v_other_fn is not None:
+            uncond = v_other_fn()
+            return uncond + guidance * (v - uncond)
+        return v
+
+    # ---- the sampler ----
+    def generate(self, prompt: str, height: int, width: int, steps: int, seed: int, *, guidance: float | None = None,
+                 init_image: torch.Tensor | None = None, strength: float = 0.7, partial_images: int = 0,
+                 should_stop: Callable[[], bool] = lambda: False) -> Iterator[tuple[str, torch.Tensor, int, int]]:
+        """Yields ``("partial", rgb, index, total)`` previews and finally ``("final", rgb, 0, 0)``
+        (or nothing more after ``should_stop()`` turned true; it is evaluated identically on every rank)."""
+        m = self.m
+        g = m.cfg.guidance if guidance is None else guidance
+        gh, gw = m.grid(height, width)
+        p = m.cfg.patch
+        noise = torch.randn(m.cfg.latent_channels, gh * p, gw * p, generator=torch.Generator().manual_seed(seed)).to(m.device)
+        start = 1.0
+        lat = noise
+        if init_image is not None:
+            start = min(1.0, max(0.05, 1.0 - strength))     # high fidelity = little noise
+            start = 1.0 - start if strength <= 1.0 else 1.0
+            x0 = m.encode_image(init_image.to(m.device), gh, gw)
+        ts = timesteps(steps, 1.0)
+        if init_image is not None:
+            skip = min(steps - 1, int(round(steps * (1.0 - strength))))
+            ts = ts[skip:]
+            lat = ts[0] * noise + (1 - ts[0]) * x0
+        use_cfg = m.cfg.uses_cfg
+        my_prompt = "" if (self.cfg_parallel and self.cfg_rank == 1) else prompt
+        txt, pooled = m.encode_text(my_prompt)
+        txt_u, pooled_u = m.encode_text("") if (use_cfg and not self.cfg_parallel) else (None, None)
+        caches = {i: [None, None] for i in m.block_range} if self.pipe_world > 1 else None
+        caches_u = {i: [None, None] for i in m.block_range} if (caches is not None and txt_u is not None) else None
+        n_steps = len(ts) - 1
+        every = max(1, n_steps // (partial_images + 1)) if partial_images > 0 else 0
+        sent = 0
+        for i in range(n_steps):
+            if should_stop():
+                return
+            t, t_next = ts[i], ts[i + 1]
+            patches = self.pipe_world > 1 and i >= self.num_sync_steps
+            predict = self._predict_patches if patches else self._predict_sync
+            if self.pipe_world == 1:
+                v = m.velocity(lat, t, txt, pooled)
+                other = (lambda: m.velocity(lat, t, txt_u, pooled_u)) if txt_u is not None else None
+            else:
+                v = predict(lat, t, txt, pooled, caches)
+                other = (lambda: predict(lat, t, txt_u, pooled_u, caches_u)) if txt_u is not None else None
+            v = self._guided(v, other, g) if use_cfg else v
+            lat = lat + (t_next - t) * v
+            if every and (i + 1) % every == 0 and sent < partial_images and i + 1 < n_steps:
+                x0_hat = lat - t_next * v
+                yield "partial", m.decode(x0_hat), sent, partial_images
+                sent += 1
+        yield "final", m.decode(lat), 0, 0
