@@ -58,6 +58,11 @@ class StepInputs:
     max_q_len: int = 1
 
 
+def resolve(h):
+    """Tensor behind ``h``: a tensor-parallel hand-over (``parallel.fused.Handover``) is finished first."""
+    return h if isinstance(h, torch.Tensor) or h is None else h.value()
+
+
 class KVPool:
     """Paged KV storage for the layers this rank holds (block size 16 by default)."""
 
@@ -120,6 +125,7 @@ class Decoder:
 
     def _attn_mla(self, lw, h, inp: StepInputs, kv) -> torch.Tensor:
         cfg = self.cfg
+        h = resolve(h)
         T = h.shape[0]
         x, _ = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps)
         if lw.wq_a is not None:
@@ -154,6 +160,7 @@ class Decoder:
         ranks of the weighted expert outputs (shared-expert partial folded into the same sum).
         """
         cfg = self.cfg
+        h = resolve(h)
         x, _ = ops.rmsnorm(h, lw.ffn_norm, cfg.rms_eps)
         logits = ops.linear(x, lw.router)
         wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, cfg.router, cfg.norm_topk_prob, lw.router_bias,
@@ -175,9 +182,9 @@ class Decoder:
             h = (self._attn_mla if cfg.mla else self._attn_gqa)(lw, h, inp, kv.layers[i])
             h = self._ffn_moe(lw, h) if cfg.layer_is_moe(i) else self._ffn_dense(lw, h)
         if not self.spec.is_last_stage:
-            return h
+            return resolve(h)
         # only the rows whose logits are needed go through the final norm + vocabulary GEMM
-        hs = h if (inp.max_q_len == 1 and inp.logit_rows.numel() == h.shape[0]) else h[inp.logit_rows.long()]
+        hs = h if (inp.max_q_len == 1 and inp.logit_rows.numel() == h.shape[0]) else resolve(h)[inp.logit_rows.long()]
         return ops.norm_linear(hs, w.final_norm, cfg.rms_eps, w.lm_head)
 
     def logits(self, inp: StepInputs, kv: KVPool) -> torch.Tensor:

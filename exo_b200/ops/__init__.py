@@ -40,7 +40,10 @@ def linear(x, w, bias=None, residual=None, swiglu=False):
 
 
 def norm_linear(h, norm_w, eps, w, bias=None, swiglu=False):
-    """``linear(rmsnorm(h, norm_w), w)`` — one kernel on the small-batch path."""
+    """``linear(rmsnorm(h, norm_w), w)`` — one kernel on the small-batch path.  ``h`` may be a
+    tensor-parallel hand-over (``parallel.fused.Handover``): the reduction then happens in this kernel's prologue."""
+    if hasattr(h, "norm_linear"):
+        return h.norm_linear(norm_w, eps, w, bias, swiglu)
     if h.is_cuda:
         return cuda_ops().linear(h, w, bias, None, norm_w, eps, swiglu)
     y = ref.linear(ref.rmsnorm(h, norm_w, eps)[0], w, bias)

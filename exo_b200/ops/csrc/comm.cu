@@ -19,10 +19,14 @@
 // Waits are bounded by a globaltimer budget: on expiry the kernel records an error code in the
 // status word and returns normally, so the context stays usable and the host raises.
 #include "common.cuh"
+#include "tp_handover.cuh"
 
 namespace {
 
 constexpr int MAX_RANKS = 8;
+// hand-over region of the header: flags int32 [2][8] at +1024, producer tickets [2] at +1280, consumer tickets [2] at +1344
+constexpr size_t HO_FLAGS = 1024, HO_PTICKET = 1280, HO_CTICKET = 1344;
+constexpr size_t HO_SLOT_BYTES = 64 << 10;   // one partial of up to 2 rows x 16384 bf16
 constexpr size_t HDR_BYTES = 4096;
 constexpr unsigned long long WAIT_NS = 2000000000ull;  // 2 s
 
@@ -31,6 +35,7 @@ struct CommCtx {
   int n, rank;
   size_t slot_bytes;          // bytes of one staging slot
   size_t gather_off;          // byte offset of the gather region
+  size_t handover_off;        // byte offset of the hand-over staging [2 parities][n][HO_SLOT_BYTES] (0 = none)
 };
 
 __device__ __forceinline__ int* flag_ptr(uint8_t* arena, int parity, int src) {
@@ -239,12 +244,14 @@ EXO_API int exo_symm_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 EXO_API size_t exo_comm_header_bytes() { return HDR_BYTES; }
 
 // arenas: n pointers (index = rank; own arena at [rank]).
-EXO_API int exo_comm_init(void** arenas, int n, int rank, size_t slot_bytes, size_t gather_off) {
+EXO_API size_t exo_comm_handover_bytes(int n) { return 2 * (size_t)n * HO_SLOT_BYTES; }
+
+EXO_API int exo_comm_init(void** arenas, int n, int rank, size_t slot_bytes, size_t gather_off, size_t handover_off) {
   int dev;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || n > MAX_RANKS) return -1;
   CommCtx c;
   for (int i = 0; i < MAX_RANKS; i++) c.arena[i] = i < n ? (uint8_t*)arenas[i] : nullptr;
-  c.n = n; c.rank = rank; c.slot_bytes = slot_bytes; c.gather_off = gather_off;
+  c.n = n; c.rank = rank; c.slot_bytes = slot_bytes; c.gather_off = gather_off; c.handover_off = handover_off;
   g_ctx[dev] = c;
   g_ctx_set[dev] = true;
   return 0;
@@ -300,6 +307,91 @@ EXO_API int exo_allgather_cols_bf16(const void* in, int rows, int cols, int pari
   int total = rows * (cols / 8);
   cudaError_t e = launch_pdl(allgather_cols_kernel, dim3(grid_for(total)), dim3(256), 0, st, c, (const uint4*)in, rows,
                              cols / 8, parity);
+  if (e != cudaSuccess) return (int)e;
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+// ---- hand-over (row-parallel projection -> consumer, no collective kernel) -----------------------
+namespace {
+
+// Stand-alone consumer: out = residual + sum_r slot[r]; used when the next op cannot take the
+// hand-over itself.  One CTA per 2048 elements; flags are cleared by the last CTA.
+__global__ void __launch_bounds__(256) handover_finish_kernel(const TpHandover h, __nv_bfloat16* out, int n_vec) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < h.n_part && !tp_wait_flag(h.part_flag[threadIdx.x], h.status)) ok_s = 0;
+  __syncthreads();
+  if (ok_s) {
+    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += gridDim.x * blockDim.x) {
+      float acc[8];
+      if (h.x_res) unpack8(reinterpret_cast<const uint4*>(h.x_res)[v], acc);
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] = 0.f;
+      }
+      for (int r = 0; r < h.n_part; r++) {
+        float f[8];
+        unpack8(ld_cg16(reinterpret_cast<const uint4*>(h.part[r]) + v), f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] += f[e];
+      }
+      reinterpret_cast<uint4*>(out)[v] = pack8(acc);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(h.part_ticket, 1) == (int)gridDim.x - 1) {
+      *h.part_ticket = 0;
+      for (int r = 0; r < h.n_part; r++) *h.part_flag[r] = 0;
+      __threadfence_system();
+    }
+  }
+}
+
+}  // namespace
+
+int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems) {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return -4;
+  const CommCtx& c = g_ctx[dev];
+  if (!c.handover_off || (size_t)n_elems * 2 > HO_SLOT_BYTES) return -6;
+  memset(out, 0, sizeof(*out));
+  uint8_t* mine = c.arena[c.rank];
+  out->status = reinterpret_cast<int*>(mine + 512);
+  if (mode == 1) {
+    out->n_push = c.n;
+    for (int r = 0; r < c.n; r++) {
+      out->push_dst[r] = reinterpret_cast<__nv_bfloat16*>(c.arena[r] + c.handover_off + ((size_t)parity * c.n + c.rank) * HO_SLOT_BYTES);
+      out->push_flag[r] = reinterpret_cast<int*>(c.arena[r] + HO_FLAGS) + parity * MAX_RANKS + c.rank;
+    }
+    out->push_ticket = reinterpret_cast<int*>(mine + HO_PTICKET) + parity;
+  } else {
+    out->n_part = c.n;
+    for (int r = 0; r < c.n; r++) {
+      out->part[r] = reinterpret_cast<const __nv_bfloat16*>(mine + c.handover_off + ((size_t)parity * c.n + r) * HO_SLOT_BYTES);
+      out->part_flag[r] = reinterpret_cast<int*>(mine + HO_FLAGS) + parity * MAX_RANKS + r;
+    }
+    out->part_ticket = reinterpret_cast<int*>(mine + HO_CTICKET) + parity;
+  }
+  return 0;
+}
+
+// out = residual + sum over ranks of the partials handed over on `parity` (n_elems multiple of 8).
+EXO_API int exo_tp_handover_finish(const void* residual, void* out, long n_elems, int parity, cudaStream_t st) {
+  if (n_elems % 8) return -2;
+  TpHandover h;
+  int rc = exo_tp_handover_fill(&h, 2, parity, n_elems);
+  if (rc) return rc;
+  h.x_res = (const __nv_bfloat16*)residual;
+  const int n_vec = (int)(n_elems / 8);
+  int grid = (n_vec + 255) / 256;
+  if (grid > 32) grid = 32;
+  cudaError_t e = launch_pdl(handover_finish_kernel, dim3(grid), dim3(256), 0, st, h, (__nv_bfloat16*)out, n_vec);
   if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
   return 0;

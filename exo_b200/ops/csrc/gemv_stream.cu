@@ -15,7 +15,9 @@
 // Fused: RMSNorm prologue (sum of squares + norm weight), bias, residual add, SwiGLU epilogue
 // (a stage then carries RS/2 gate rows and the matching RS/2 up rows as two copies).
 #include <cstdlib>
+#include <cstring>
 #include "tc_common.cuh"
+#include "tp_handover.cuh"
 
 namespace {
 
@@ -33,6 +35,7 @@ struct StreamParams {
   float eps;
   int N, K, RS, n_groups, ldo, stages, stage_bytes;
   int* err;
+  TpHandover ho;   // tensor-parallel hand-over (all zero when the projection is not part of one)
 };
 
 __device__ __forceinline__ void bulk_g2s(void* smem, const void* gmem, uint32_t bytes, uint64_t* bar) {
@@ -92,6 +95,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
   const int KS = K / CONSUMER_WARPS;          // this warp's K slice
   const int k_lo = warp * KS, nvec = KS / 8;  // in 16-byte vectors
   pdl_wait();                                 // x comes from the previous kernel
+  if (p.ho.n_part > 0) {
+    // x is handed over by the row-parallel projection of every rank: wait for all of them (bounded)
+    if (warp == 0 && lane < p.ho.n_part) tp_wait_flag(p.ho.part_flag[lane], p.ho.status);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+  }
   float xr[M][JV][8];
   float ss[M];
 #pragma unroll
@@ -101,7 +109,28 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
     for (int j = 0; j < JV; j++) {
       const int v = lane + 32 * j;
       if (v < nvec) {
-        unpack8(*reinterpret_cast<const uint4*>(p.x + (size_t)m * K + k_lo + v * 8), xr[m][j]);
+        if (p.ho.n_part > 0) {
+          // residual + partials in rank order, rounded to bf16: the same bits on every rank and the same
+          // value a separate all-reduce would have left in memory
+          const size_t off = (size_t)m * K + k_lo + v * 8;
+          float acc[8];
+          if (p.ho.x_res) unpack8(*reinterpret_cast<const uint4*>(p.ho.x_res + off), acc);
+          else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[e] = 0.f;
+          }
+          for (int r = 0; r < p.ho.n_part; r++) {
+            float f[8];
+            unpack8(tp_ld_cg16(p.ho.part[r] + off), f);
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[e] += f[e];
+          }
+          const uint4 packed = pack8(acc);
+          if (blockIdx.x == 0 && p.ho.x_out) *reinterpret_cast<uint4*>(p.ho.x_out + off) = packed;
+          unpack8(packed, xr[m][j]);
+        } else {
+          unpack8(*reinterpret_cast<const uint4*>(p.x + (size_t)m * K + k_lo + v * 8), xr[m][j]);
+        }
         if (NORM) {
           float nw[8];
           unpack8(*reinterpret_cast<const uint4*>(p.norm_w + k_lo + v * 8), nw);
@@ -206,7 +235,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
             gsum *= rstd[m];
             usum *= rstd[m];
             if (p.bias) { gsum += __bfloat162float(p.bias[n]); usum += __bfloat162float(p.bias[F + n]); }
-            p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(silu_f(gsum) * usum);
+            p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(silu_f(gsum) * usum);   // column-parallel: never handed over
           }
         }
       } else if (t < RS * M) {
@@ -218,8 +247,30 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
           y *= rstd[m];
           if (p.bias) y += __bfloat162float(p.bias[n]);
           if (p.residual) y += __bfloat162float(p.residual[(size_t)m * p.ldo + n]);
-          p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(y);
+          const __nv_bfloat16 yb = __float2bfloat16_rn(y);
+          if (p.ho.n_push > 0) {
+            for (int r = 0; r < p.ho.n_push; r++) p.ho.push_dst[r][(size_t)m * p.ldo + n] = yb;   // peer stores
+          } else {
+            p.out[(size_t)m * p.ldo + n] = yb;
+          }
         }
+      }
+    }
+  }
+  // ---- tensor-parallel hand-over bookkeeping (consumer warps only; the producer warp has returned) ----
+  if (p.ho.n_push > 0 || p.ho.n_part > 0) {
+    __threadfence_system();                               // this thread's peer stores before the ticket
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (threadIdx.x == 0) {
+      if (p.ho.n_push > 0 && atomicAdd(p.ho.push_ticket, 1) == (int)gridDim.x - 1) {
+        *p.ho.push_ticket = 0;                             // whole y is in every rank's staging slot: raise the flags
+        __threadfence_system();
+        for (int r = 0; r < p.ho.n_push; r++) tp_red_release_sys_add(p.ho.push_flag[r], 1);
+      }
+      if (p.ho.n_part > 0 && atomicAdd(p.ho.part_ticket, 1) == (int)gridDim.x - 1) {
+        *p.ho.part_ticket = 0;                             // every CTA has read the partials: clear for the parity's next use
+        for (int r = 0; r < p.ho.n_part; r++) *p.ho.part_flag[r] = 0;
+        __threadfence_system();
       }
     }
   }
@@ -330,8 +381,34 @@ EXO_API int exo_gemv_stream_supported(int M, int N, int K, int swiglu) {
   return stream_config(M, K, swiglu, &RS, &stages, &fixed) ? 1 : 0;
 }
 
+static int gemv_stream_launch(const void* x, const void* W, const void* bias, const void* residual, void* out,
+                              const void* norm_w, float eps, int M, int N, int K, int swiglu, const TpHandover* ho,
+                              cudaStream_t st);
+
 EXO_API int exo_gemv_stream(const void* x, const void* W, const void* bias, const void* residual, void* out,
                             const void* norm_w, float eps, int M, int N, int K, int swiglu, cudaStream_t st) {
+  return gemv_stream_launch(x, W, bias, residual, out, norm_w, eps, M, N, K, swiglu, nullptr, st);
+}
+
+// Row-parallel projection whose output is handed to every rank (mode 1: `out` is not written), or a
+// projection whose input is the hand-over of the previous one (mode 2: x = x_res + partials, and
+// the reduced residual stream is left in x_out).  `parity` alternates per hand-over.
+EXO_API int exo_gemv_stream_tp(const void* x, const void* W, const void* bias, void* out, const void* norm_w, float eps,
+                               int M, int N, int K, int swiglu, int mode, int parity, const void* x_res, void* x_out,
+                               cudaStream_t st) {
+  TpHandover ho;
+  int rc = exo_tp_handover_fill(&ho, mode, parity, mode == 1 ? (long)M * N : (long)M * K);
+  if (rc) return rc;
+  if (mode == 2) {
+    ho.x_res = (const __nv_bfloat16*)x_res;
+    ho.x_out = (__nv_bfloat16*)x_out;
+  }
+  return gemv_stream_launch(x, W, bias, nullptr, out, norm_w, eps, M, N, K, swiglu, &ho, st);
+}
+
+static int gemv_stream_launch(const void* x, const void* W, const void* bias, const void* residual, void* out,
+                              const void* norm_w, float eps, int M, int N, int K, int swiglu, const TpHandover* ho,
+                              cudaStream_t st) {
   if (!exo_gemv_stream_supported(M, N, K, swiglu)) return -2;
   int dev;
   cudaGetDevice(&dev);
@@ -340,6 +417,7 @@ EXO_API int exo_gemv_stream(const void* x, const void* W, const void* bias, cons
   p.x = (const __nv_bfloat16*)x; p.W = (const __nv_bfloat16*)W; p.bias = (const __nv_bfloat16*)bias;
   p.residual = (const __nv_bfloat16*)residual; p.out = (__nv_bfloat16*)out; p.norm_w = (const __nv_bfloat16*)norm_w;
   p.eps = eps; p.N = N; p.K = K; p.ldo = swiglu ? N / 2 : N; p.err = g_err_stream[dev];
+  if (ho) p.ho = *ho; else memset(&p.ho, 0, sizeof(p.ho));
   const int row_bytes = K * 2;
   int RS, stages; size_t fixed;
   stream_config(M, K, swiglu, &RS, &stages, &fixed);

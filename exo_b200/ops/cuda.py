@@ -175,6 +175,15 @@ def gemm_check() -> None:
 gemm_impl = None if os.environ.get("EXO_DISABLE_TCGEN05") == "1" else gemm_bf16
 
 
+def ensure_stream_init(device) -> None:
+    dev = device.index or 0
+    if dev not in _stream_ready:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("first streaming-GEMV call on a device must not be inside graph capture")
+        _chk(load().exo_gemv_stream_init(), "gemv_stream_init")
+        _stream_ready.add(dev)
+
+
 def linear(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=False):
     """Dispatch by batch rows: M <= 8 → fused small-batch kernel; bf16 larger M → tcgen05 GEMM;
     fp32 larger M → CUDA-core tiled kernel (oracle configs only)."""
@@ -184,12 +193,7 @@ def linear(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=Fals
     lib = load()
     if (use_stream_gemv and 0 < M <= 2 and x.dtype == torch.bfloat16
             and lib.exo_gemv_stream_supported(M, N, K, int(swiglu_out))):
-        dev = x.device.index or 0
-        if dev not in _stream_ready:
-            if torch.cuda.is_current_stream_capturing():
-                raise KernelError("first streaming-GEMV call on a device must not be inside graph capture")
-            _chk(lib.exo_gemv_stream_init(), "gemv_stream_init")
-            _stream_ready.add(dev)
+        ensure_stream_init(x.device)
         out = torch.empty(M, N // 2 if swiglu_out else N, dtype=x.dtype, device=x.device)
         _chk(lib.exo_gemv_stream(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), _ptr(norm_w), eps, M, N, K,
                                  int(swiglu_out), _st()), "gemv_stream")

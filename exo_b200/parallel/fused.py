@@ -13,6 +13,7 @@ Device-side waits are bounded (2 s): a rank whose peer never signals records an 
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -32,6 +33,48 @@ class _RawBuffer:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
+HANDOVER_SLOT = 64 << 10      # bytes of one staging slot of the hand-over region (2 rows x 16384 bf16)
+
+
+class Handover:
+    """The not-yet-reduced output of a row-parallel projection: partials of all ranks sit in this rank's
+    staging slots.  ``norm_linear`` consumes it inside the next projection; ``value()`` gives the tensor
+    (running the stand-alone finish kernel if nobody consumed it)."""
+
+    def __init__(self, comm: "FusedComm", parity: int, residual: torch.Tensor | None, rows: int, cols: int):
+        self.comm, self.parity, self.residual, self.shape = comm, parity, residual, (rows, cols)
+        ref = residual if residual is not None else None
+        self.out = torch.empty(rows, cols, dtype=torch.bfloat16, device=comm.device) if ref is None else torch.empty_like(ref)
+        self.done = False
+
+    def norm_linear(self, norm_w, eps, w, bias=None, swiglu=False):
+        M, Kd = self.shape
+        N = w.shape[0]
+        lib = self.comm.lib
+        if self.done or not lib.exo_gemv_stream_supported(M, N, Kd, int(swiglu)):
+            return K.linear(self.value(), w, bias, None, norm_w, eps, swiglu)
+        y = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device=self.out.device)
+        K._chk(lib.exo_gemv_stream_tp(None, w.data_ptr(), K._ptr(bias), y.data_ptr(), K._ptr(norm_w), eps, M, N, Kd, int(swiglu),
+                                      2, self.parity, K._ptr(self.residual), self.out.data_ptr(), K._st()), "gemv_stream_tp consume")
+        K._count()
+        self.done = True
+        return y
+
+    def value(self) -> torch.Tensor:
+        if not self.done:
+            n = self.shape[0] * self.shape[1]
+            K._chk(self.comm.lib.exo_tp_handover_finish(K._ptr(self.residual), self.out.data_ptr(), n, self.parity, K._st()),
+                   "handover finish")
+            K._count()
+            self.done = True
+        return self.out
+
+
+def resolve(h):
+    """A tensor for ``h``: hand-overs are finished, tensors pass through."""
+    return h.value() if isinstance(h, Handover) else h
+
+
 class FusedComm:
     def __init__(self, device: torch.device, max_rows: int, hidden: int, vocab_shard: int, group=None,
                  max_gather_rows: int = 256):
@@ -44,7 +87,11 @@ class FusedComm:
             "exo_symm_alloc": (C.c_void_p, [C.c_size_t]), "exo_symm_free": (C.c_int, [C.c_void_p]),
             "exo_symm_handle": (C.c_int, [C.c_void_p, C.c_void_p]), "exo_symm_open": (C.c_void_p, [C.c_void_p]),
             "exo_symm_close": (C.c_int, [C.c_void_p]), "exo_comm_header_bytes": (C.c_size_t, []),
-            "exo_comm_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_size_t]),
+            "exo_comm_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.c_size_t]),
+            "exo_comm_handover_bytes": (C.c_size_t, [C.c_int]),
+            "exo_tp_handover_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
+            "exo_gemv_stream_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
+                                             C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
             "exo_comm_status": (C.c_int, []),
             "exo_allreduce_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
             "exo_allgather_cols_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
@@ -62,7 +109,8 @@ class FusedComm:
         self.max_gather_rows = max_gather_rows
         self.gather_off = hdr + 2 * n * self.slot_bytes
         gather_bytes = max_gather_rows * n * vocab_shard * 2
-        self.arena_bytes = self.gather_off + gather_bytes
+        self.handover_off = (self.gather_off + gather_bytes + 4095) // 4096 * 4096
+        self.arena_bytes = self.handover_off + lib.exo_comm_handover_bytes(n)
         torch.cuda.set_device(device)
         self.local = lib.exo_symm_alloc(self.arena_bytes)
         if not self.local:
@@ -81,12 +129,15 @@ class FusedComm:
                     raise RuntimeError(f"rank {self.rank}: cannot map arena of rank {r} (no peer access?)")
                 self.peers.append(p)
         arr = (C.c_void_p * n)(*self.peers)
-        K._chk(lib.exo_comm_init(arr, n, self.rank, self.slot_bytes, self.gather_off), "comm init")
+        K._chk(lib.exo_comm_init(arr, n, self.rank, self.slot_bytes, self.gather_off, self.handover_off), "comm init")
         dist.barrier(group=group)
         raw = torch.as_tensor(_RawBuffer(self.local + self.gather_off, gather_bytes), device=device)
         self.gather_buf = raw.view(torch.bfloat16)
         self._ar = 0
+        self._ho = 0             # hand-overs issued so far (parity = low bit)
         self.n_collectives = 0
+        self.n_handovers = 0
+        self.use_handover = os.environ.get("EXO_DISABLE_TP_HANDOVER") != "1"
 
     # ---- collectives ----
     def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
@@ -111,7 +162,24 @@ class FusedComm:
         self.n_collectives += 1
         return out
 
-    def row_linear(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+    def row_linear(self, x: torch.Tensor, w: torch.Tensor, residual=None):
+        """``residual + all-reduce(x @ w.T)``.  At decode batch sizes the projection itself stores its rows
+        into every rank's staging slot and a :class:`Handover` is returned: the next ``norm_linear`` (or
+        ``resolve``) forms the sum, so no collective kernel is launched."""
+        residual = resolve(residual)
+        M, Kd = x.shape
+        N = w.shape[0]
+        if (self.use_handover and 0 < M <= 2 and x.dtype == torch.bfloat16 and K.use_stream_gemv and M * N * 2 <= HANDOVER_SLOT
+                and self.lib.exo_gemv_stream_supported(M, N, Kd, 0)):
+            K.ensure_stream_init(x.device)
+            parity = self._ho & 1
+            self._ho += 1
+            x = x.contiguous()
+            K._chk(self.lib.exo_gemv_stream_tp(x.data_ptr(), w.data_ptr(), None, None, None, 0.0, M, N, Kd, 0, 1, parity,
+                                               None, None, K._st()), "gemv_stream_tp push")
+            K._count()
+            self.n_handovers += 1
+            return Handover(self, parity, residual, M, N)
         return self.all_reduce(ops.linear(x, w), residual)
 
     def gather_vocab(self, logits_local: torch.Tensor) -> torch.Tensor:

@@ -132,3 +132,85 @@ def test_tp2_engine_fused_vs_nccl_vs_single():
     a, b = fused[0][1][1], nccl[0][1][1]
     assert (a - b).abs().max() < 0.05 * b.abs().max() + 0.05
     assert all(len(t) == 12 for t in fused[0][1][0])
+
+
+def _handover(rank, world):
+    """Row-parallel projection handed over to the next RMSNorm + projection without a collective kernel."""
+    import torch.distributed as dist
+    from exo_b200 import ops
+    from exo_b200.ops import reference as ref
+    from exo_b200.parallel.fused import FusedComm, Handover
+    dev = torch.device("cuda", rank)
+    comm = FusedComm(dev, max_rows=256, hidden=4096, vocab_shard=4008)
+    shared = torch.Generator(device=dev).manual_seed(5)           # same on every rank
+    mine = torch.Generator(device=dev).manual_seed(50 + rank)     # this rank's shard
+    H, Kr = 4096, 2048
+    w_o = (torch.randn(H, Kr, device=dev, generator=mine) / 64).bfloat16()
+    w_up = (torch.randn(6144, H, device=dev, generator=shared) / 64).bfloat16()
+    w_gate_up = (torch.randn(2 * 3584, H, device=dev, generator=shared) / 64).bfloat16()
+    norm_w = (1 + 0.1 * torch.randn(H, device=dev, generator=shared)).bfloat16()
+    worst = 0.0
+    for it in range(6):                                            # both parities, several times: flags must come back clean
+        M = 1 + it % 2
+        x = torch.randn(M, Kr, device=dev, generator=mine).bfloat16()
+        res = torch.randn(M, H, device=dev, generator=shared).bfloat16()
+        h = comm.row_linear(x, w_o, res)
+        assert isinstance(h, Handover)
+        swiglu = it % 3 == 2
+        if it == 4:
+            got_h = h.value().clone()                              # nobody consumes it: stand-alone finish kernel
+            got_y = ops.norm_linear(got_h, norm_w, 1e-5, w_up)
+        else:
+            got_y = ops.norm_linear(h, norm_w, 1e-5, w_gate_up if swiglu else w_up, swiglu=swiglu)
+            got_h = h.value().clone()
+        part = ref.linear(x.float(), w_o.float()).bfloat16().float()
+        dist.all_reduce(part)
+        want_h = (part + res.float()).bfloat16()
+        want_y = ref.linear(ref.rmsnorm(want_h.float(), norm_w.float(), 1e-5)[0], (w_gate_up if swiglu else w_up).float())
+        if swiglu:
+            want_y = ref.swiglu(want_y)
+        worst = max(worst, ((got_h.float() - want_h.float()).abs().max() / want_h.float().abs().max()).item(),
+                    ((got_y.float() - want_y).abs().max() / want_y.abs().max()).item())
+        other = got_y.clone()
+        dist.broadcast(other, 0)
+        assert torch.equal(other, got_y), "ranks disagree after the hand-over"
+    comm.check()
+    n = comm.n_handovers
+    comm.close()
+    return worst, n
+
+
+def _engine_handover(rank, world, use_handover):
+    from exo_b200.engine.engine import Engine
+    from exo_b200.engine.kv import SamplingParams
+    from exo_b200.models.config import ModelConfig, RopeConfig
+    from exo_b200.models.oracle import oracle_prompt
+    from exo_b200.models.weights import RandomSource, ShardSpec, build_weights, vocab_shard
+    from exo_b200.parallel.fused import FusedComm
+    dev = torch.device("cuda", rank)
+    cfg = ModelConfig(name="t", n_layers=2, hidden=2048, n_heads=16, n_kv_heads=4, head_dim=128, ffn=4096, vocab=32000,
+                      rope=RopeConfig(theta=500000.0), dtype="bf16")
+    spec = ShardSpec(tp_rank=rank, tp_size=world)
+    w = build_weights(cfg, spec, RandomSource(seed=0, dtype=torch.bfloat16), device=dev)
+    comm = FusedComm(dev, max_rows=256, hidden=cfg.hidden, vocab_shard=vocab_shard(cfg.vocab, world))
+    comm.use_handover = use_handover
+    eng = Engine(cfg, w, spec, comm, n_blocks=128, device=dev, max_seqs=4)       # CUDA graphs on: decode steps replay
+    toks = eng.generate(oracle_prompt(37, cfg.vocab, seed=3).tolist(), SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))
+    comm.check()
+    n = comm.n_handovers
+    comm.close()
+    return toks, n
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_row_parallel_handover_matches_all_reduce():
+    res = _run(_handover, 2)
+    assert max(r[1][0] for r in res) < 2e-2 and all(r[1][1] == 6 for r in res)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_decode_with_handover_reproduces_the_all_reduce_tokens():
+    on = _run(_engine_handover, 2, True)
+    off = _run(_engine_handover, 2, False)
+    assert on[0][1][0] == on[1][1][0] == off[0][1][0] and len(on[0][1][0]) == 24
+    assert on[0][1][1] > 0 and off[0][1][1] == 0          # the decode steps really went through the hand-over
