@@ -26,7 +26,6 @@ namespace {
 constexpr int MAX_RANKS = 8;
 // hand-over region of the header: flags int32 [2][8] at +1024, producer tickets [2] at +1280, consumer tickets [2] at +1344
 constexpr size_t HO_FLAGS = 1024, HO_PTICKET = 1280, HO_CTICKET = 1344;
-constexpr size_t HO_SLOT_BYTES = 64 << 10;   // one partial of up to 2 rows x 16384 bf16
 constexpr size_t HDR_BYTES = 4096;
 constexpr unsigned long long WAIT_NS = 2000000000ull;  // 2 s
 
@@ -35,7 +34,8 @@ struct CommCtx {
   int n, rank;
   size_t slot_bytes;          // bytes of one staging slot
   size_t gather_off;          // byte offset of the gather region
-  size_t handover_off;        // byte offset of the hand-over staging [2 parities][n][HO_SLOT_BYTES] (0 = none)
+  size_t handover_off;        // byte offset of the hand-over staging [2 parities][n][handover_slot] (0 = none)
+  size_t handover_slot;       // bytes of one hand-over slot
 };
 
 __device__ __forceinline__ int* flag_ptr(uint8_t* arena, int parity, int src) {
@@ -244,14 +244,15 @@ EXO_API int exo_symm_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 EXO_API size_t exo_comm_header_bytes() { return HDR_BYTES; }
 
 // arenas: n pointers (index = rank; own arena at [rank]).
-EXO_API size_t exo_comm_handover_bytes(int n) { return 2 * (size_t)n * HO_SLOT_BYTES; }
+EXO_API size_t exo_comm_handover_bytes(int n, size_t slot) { return 2 * (size_t)n * slot; }
 
-EXO_API int exo_comm_init(void** arenas, int n, int rank, size_t slot_bytes, size_t gather_off, size_t handover_off) {
+EXO_API int exo_comm_init(void** arenas, int n, int rank, size_t slot_bytes, size_t gather_off, size_t handover_off,
+                          size_t handover_slot) {
   int dev;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || n > MAX_RANKS) return -1;
   CommCtx c;
   for (int i = 0; i < MAX_RANKS; i++) c.arena[i] = i < n ? (uint8_t*)arenas[i] : nullptr;
-  c.n = n; c.rank = rank; c.slot_bytes = slot_bytes; c.gather_off = gather_off; c.handover_off = handover_off;
+  c.n = n; c.rank = rank; c.slot_bytes = slot_bytes; c.gather_off = gather_off; c.handover_off = handover_off; c.handover_slot = handover_slot;
   g_ctx[dev] = c;
   g_ctx_set[dev] = true;
   return 0;
@@ -353,27 +354,91 @@ __global__ void __launch_bounds__(256) handover_finish_kernel(const TpHandover h
   }
 }
 
+// Consumer for batches that go through the GEMM: one CTA per row forms h = residual + sum_r slot[r]
+// (rank order, rounded to bf16), leaves it in h_out and writes RMSNorm(h) * w into x_out.
+__global__ void __launch_bounds__(256) handover_rmsnorm_kernel(const TpHandover h, const __nv_bfloat16* norm_w, float eps,
+                                                               __nv_bfloat16* x_out, int cols) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ int ok_s;
+  __shared__ float red[8];
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < h.n_part && !tp_wait_flag(h.part_flag[threadIdx.x], h.status)) ok_s = 0;
+  __syncthreads();
+  const size_t row = (size_t)blockIdx.x * cols;
+  const int n_vec = cols / 8;
+  float ss = 0.f;
+  if (ok_s) {
+    for (int v = threadIdx.x; v < n_vec; v += blockDim.x) {
+      float acc[8];
+      if (h.x_res) unpack8(reinterpret_cast<const uint4*>(h.x_res + row)[v], acc);
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] = 0.f;
+      }
+      for (int r = 0; r < h.n_part; r++) {
+        float f[8];
+        unpack8(ld_cg16(reinterpret_cast<const uint4*>(h.part[r] + row) + v), f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] += f[e];
+      }
+      const uint4 packed = pack8(acc);
+      reinterpret_cast<uint4*>(h.x_out + row)[v] = packed;
+      unpack8(packed, acc);
+#pragma unroll
+      for (int e = 0; e < 8; e++) ss += acc[e] * acc[e];
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; w++) tot += red[w];
+  const float rstd = rsqrtf(tot / cols + eps);
+  if (ok_s) {
+    for (int v = threadIdx.x; v < n_vec; v += blockDim.x) {     // second pass re-reads what this CTA just wrote
+      float a[8], w8[8];
+      unpack8(reinterpret_cast<const uint4*>(h.x_out + row)[v], a);
+      unpack8(reinterpret_cast<const uint4*>(norm_w)[v], w8);
+#pragma unroll
+      for (int e = 0; e < 8; e++) a[e] = a[e] * rstd * w8[e];
+      reinterpret_cast<uint4*>(x_out + row)[v] = pack8(a);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(h.part_ticket, 1) == (int)gridDim.x - 1) {
+      *h.part_ticket = 0;
+      for (int r = 0; r < h.n_part; r++) *h.part_flag[r] = 0;
+      __threadfence_system();
+    }
+  }
+}
+
 }  // namespace
 
 int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems) {
   int dev;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return -4;
   const CommCtx& c = g_ctx[dev];
-  if (!c.handover_off || (size_t)n_elems * 2 > HO_SLOT_BYTES) return -6;
+  if (!c.handover_off || (size_t)n_elems * 2 > c.handover_slot) return -6;
   memset(out, 0, sizeof(*out));
   uint8_t* mine = c.arena[c.rank];
   out->status = reinterpret_cast<int*>(mine + 512);
   if (mode == 1) {
     out->n_push = c.n;
     for (int r = 0; r < c.n; r++) {
-      out->push_dst[r] = reinterpret_cast<__nv_bfloat16*>(c.arena[r] + c.handover_off + ((size_t)parity * c.n + c.rank) * HO_SLOT_BYTES);
+      out->push_dst[r] = reinterpret_cast<__nv_bfloat16*>(c.arena[r] + c.handover_off + ((size_t)parity * c.n + c.rank) * c.handover_slot);
       out->push_flag[r] = reinterpret_cast<int*>(c.arena[r] + HO_FLAGS) + parity * MAX_RANKS + c.rank;
     }
     out->push_ticket = reinterpret_cast<int*>(mine + HO_PTICKET) + parity;
   } else {
     out->n_part = c.n;
     for (int r = 0; r < c.n; r++) {
-      out->part[r] = reinterpret_cast<const __nv_bfloat16*>(mine + c.handover_off + ((size_t)parity * c.n + r) * HO_SLOT_BYTES);
+      out->part[r] = reinterpret_cast<const __nv_bfloat16*>(mine + c.handover_off + ((size_t)parity * c.n + r) * c.handover_slot);
       out->part_flag[r] = reinterpret_cast<int*>(mine + HO_FLAGS) + parity * MAX_RANKS + r;
     }
     out->part_ticket = reinterpret_cast<int*>(mine + HO_CTICKET) + parity;
@@ -392,6 +457,22 @@ EXO_API int exo_tp_handover_finish(const void* residual, void* out, long n_elems
   int grid = (n_vec + 255) / 256;
   if (grid > 32) grid = 32;
   cudaError_t e = launch_pdl(handover_finish_kernel, dim3(grid), dim3(256), 0, st, h, (__nv_bfloat16*)out, n_vec);
+  if (e != cudaSuccess) return (int)e;
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+// h_out = residual + sum of the handed-over partials; x_out = RMSNorm(h_out) * norm_w.   [rows, cols], cols % 8 == 0
+EXO_API int exo_tp_handover_rmsnorm(const void* residual, const void* norm_w, float eps, void* h_out, void* x_out, int rows,
+                                    int cols, int parity, cudaStream_t st) {
+  if (cols % 8 || rows <= 0) return -2;
+  TpHandover h;
+  int rc = exo_tp_handover_fill(&h, 2, parity, (long)rows * cols);
+  if (rc) return rc;
+  h.x_res = (const __nv_bfloat16*)residual;
+  h.x_out = (__nv_bfloat16*)h_out;
+  cudaError_t e = launch_pdl(handover_rmsnorm_kernel, dim3(rows), dim3(256), 0, st, h, (const __nv_bfloat16*)norm_w, eps,
+                             (__nv_bfloat16*)x_out, cols);
   if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
   return 0;

@@ -16,7 +16,9 @@
 #include <mutex>
 #include <unordered_map>
 
+#include <cstring>
 #include "tc_common.cuh"
+#include "tp_handover.cuh"
 
 namespace {
 
@@ -34,6 +36,7 @@ struct GemmParams {
   float* partial;         // [splits, M, N] fp32 (split-K only)
   int* counters;          // [tiles] zero-initialised, self-resetting
   int* err;               // device error word
+  TpHandover ho;          // row-parallel output handed to every rank (n_push > 0): `out` is then not written
 };
 
 template <int BN, int STAGES>
@@ -142,7 +145,12 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               float y = v[j] + bias;
               size_t o = (size_t)m * p.ldo + n;
               if (p.residual) y += __bfloat162float(p.residual[o]);
-              p.out[o] = __float2bfloat16_rn(y);
+              const __nv_bfloat16 yb = __float2bfloat16_rn(y);
+              if (p.ho.n_push > 0) {
+                for (int r = 0; r < p.ho.n_push; r++) p.ho.push_dst[r][o] = yb;     // peer stores
+              } else {
+                p.out[o] = yb;
+              }
             }
           }
         }
@@ -233,11 +241,29 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 size_t o = (size_t)(m0 + mm + 4 * r) * p.ldo + nq + j;
                 float v = y[r][j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
                 if (p.residual) v += __bfloat162float(p.residual[o]);
-                p.out[o] = __float2bfloat16_rn(v);
+                const __nv_bfloat16 yb = __float2bfloat16_rn(v);
+                if (p.ho.n_push > 0) {
+                  for (int rr = 0; rr < p.ho.n_push; rr++) p.ho.push_dst[rr][o] = yb;
+                } else {
+                  p.out[o] = yb;
+                }
               }
             }
           }
         }
+      }
+    }
+  }
+  // ---- hand-over: when every CTA of the grid is past its stores, raise one flag per rank ----
+  if (p.ho.n_push > 0 && warp >= 2) {
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (warp == 2 && lane == 0) {
+      const int total = gridDim.x * gridDim.y * gridDim.z;
+      if (atomicAdd(p.ho.push_ticket, 1) == total - 1) {
+        *p.ho.push_ticket = 0;
+        __threadfence_system();
+        for (int r = 0; r < p.ho.n_push; r++) tp_red_release_sys_add(p.ho.push_flag[r], 1);
       }
     }
   }
@@ -381,8 +407,25 @@ EXO_API int exo_gemm_splits(int M, int N, int K) {
   return s < 1 ? 1 : s;
 }
 
+static int gemm_launch(const void* x, const void* W, const void* bias, const void* residual, void* out, int M, int N,
+                       int K, int ldo, int splits, const TpHandover* ho, cudaStream_t st);
+
 EXO_API int exo_gemm_bf16(const void* x, const void* W, const void* bias, const void* residual, void* out, int M, int N,
                           int K, int ldo, int splits, cudaStream_t st) {
+  return gemm_launch(x, W, bias, residual, out, M, N, K, ldo, splits, nullptr, st);
+}
+
+// Row-parallel projection whose [M, N] output goes into every rank's hand-over slot (see tp_handover.cuh).
+EXO_API int exo_gemm_bf16_tp(const void* x, const void* W, const void* bias, int M, int N, int K, int splits, int parity,
+                             cudaStream_t st) {
+  TpHandover ho;
+  int rc = exo_tp_handover_fill(&ho, 1, parity, (long)M * N);
+  if (rc) return rc;
+  return gemm_launch(x, W, bias, nullptr, nullptr, M, N, K, N, splits, &ho, st);
+}
+
+static int gemm_launch(const void* x, const void* W, const void* bias, const void* residual, void* out, int M, int N,
+                       int K, int ldo, int splits, const TpHandover* ho, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || K < BK) return -2;
   int dev;
@@ -407,6 +450,7 @@ EXO_API int exo_gemm_bf16(const void* x, const void* W, const void* bias, const 
   p.partial = g_partial[dev];
   p.counters = g_counters[dev];
   p.err = g_err[dev];
+  if (ho) p.ho = *ho; else memset(&p.ho, 0, sizeof(p.ho));
   if (splits > 1) {
     long tiles = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     if ((size_t)splits * M * N > g_partial_floats[dev] || tiles > MAX_TILES) return -6;

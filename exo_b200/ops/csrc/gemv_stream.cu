@@ -247,31 +247,43 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
           y *= rstd[m];
           if (p.bias) y += __bfloat162float(p.bias[n]);
           if (p.residual) y += __bfloat162float(p.residual[(size_t)m * p.ldo + n]);
-          const __nv_bfloat16 yb = __float2bfloat16_rn(y);
-          if (p.ho.n_push > 0) {
-            for (int r = 0; r < p.ho.n_push; r++) p.ho.push_dst[r][(size_t)m * p.ldo + n] = yb;   // peer stores
-          } else {
-            p.out[(size_t)m * p.ldo + n] = yb;
-          }
+          p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(y);
         }
       }
     }
   }
-  // ---- tensor-parallel hand-over bookkeeping (consumer warps only; the producer warp has returned) ----
-  if (p.ho.n_push > 0 || p.ho.n_part > 0) {
-    __threadfence_system();                               // this thread's peer stores before the ticket
+  // ---- tensor-parallel hand-over (consumer warps only; the producer warp has returned) ----
+  if (p.ho.n_push > 0) {
+    // y sits in this GPU's memory.  The last CTA to finish copies it into every rank's staging slot with
+    // 16-byte peer stores, orders them with ONE system-scope fence and raises the flags (a fence per CTA
+    // after scattered 2-byte peer stores measured slower than a separate all-reduce kernel).
+    __shared__ int last_s;
+    __threadfence();
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (threadIdx.x == 0) {
-      if (p.ho.n_push > 0 && atomicAdd(p.ho.push_ticket, 1) == (int)gridDim.x - 1) {
-        *p.ho.push_ticket = 0;                             // whole y is in every rank's staging slot: raise the flags
-        __threadfence_system();
-        for (int r = 0; r < p.ho.n_push; r++) tp_red_release_sys_add(p.ho.push_flag[r], 1);
+      const int last = atomicAdd(p.ho.push_ticket, 1) == (int)gridDim.x - 1;
+      if (last) *p.ho.push_ticket = 0;
+      last_s = last;
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (last_s) {
+      __threadfence();
+      const int n_vec = M * p.ldo / 8;
+      for (int v = threadIdx.x; v < n_vec; v += CONSUMER_WARPS * 32) {
+        const uint4 val = tp_ld_cg16(reinterpret_cast<const uint4*>(p.out) + v);
+        for (int r = 0; r < p.ho.n_push; r++) reinterpret_cast<uint4*>(p.ho.push_dst[r])[v] = val;
       }
-      if (p.ho.n_part > 0 && atomicAdd(p.ho.part_ticket, 1) == (int)gridDim.x - 1) {
-        *p.ho.part_ticket = 0;                             // every CTA has read the partials: clear for the parity's next use
-        for (int r = 0; r < p.ho.n_part; r++) *p.ho.part_flag[r] = 0;
-        __threadfence_system();
-      }
+      __threadfence_system();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (threadIdx.x < p.ho.n_push) tp_red_release_sys_add(p.ho.push_flag[threadIdx.x], 1);
+    }
+  }
+  if (p.ho.n_part > 0) {
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (threadIdx.x == 0 && atomicAdd(p.ho.part_ticket, 1) == (int)gridDim.x - 1) {
+      *p.ho.part_ticket = 0;                               // every CTA has read the partials: clear for the parity's next use
+      for (int r = 0; r < p.ho.n_part; r++) *p.ho.part_flag[r] = 0;
+      __threadfence_system();
     }
   }
 }

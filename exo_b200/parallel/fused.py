@@ -33,7 +33,7 @@ class _RawBuffer:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
-HANDOVER_SLOT = 64 << 10      # bytes of one staging slot of the hand-over region (2 rows x 16384 bf16)
+HANDOVER_ROWS = 256           # rows of the residual stream one hand-over slot holds (decode batches)
 
 
 class Handover:
@@ -51,6 +51,16 @@ class Handover:
         M, Kd = self.shape
         N = w.shape[0]
         lib = self.comm.lib
+        if not self.done and os.environ.get("EXO_TP_HANDOVER_CONSUME") == "0":
+            return K.linear(self.value(), w, bias, None, norm_w, eps, swiglu)      # measurement aid: stand-alone finish kernel
+        if not self.done and M > 2 and Kd % 8 == 0:
+            # batched decode: one kernel finishes the reduction, leaves the residual stream and the normalised rows
+            xn = torch.empty_like(self.out)
+            K._chk(lib.exo_tp_handover_rmsnorm(K._ptr(self.residual), norm_w.data_ptr(), eps, self.out.data_ptr(), xn.data_ptr(),
+                                               M, Kd, self.parity, K._st()), "handover rmsnorm")
+            K._count()
+            self.done = True
+            return K.linear(xn, w, bias, None, None, 0.0, swiglu)
         if self.done or not lib.exo_gemv_stream_supported(M, N, Kd, int(swiglu)):
             return K.linear(self.value(), w, bias, None, norm_w, eps, swiglu)
         y = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device=self.out.device)
@@ -87,8 +97,12 @@ class FusedComm:
             "exo_symm_alloc": (C.c_void_p, [C.c_size_t]), "exo_symm_free": (C.c_int, [C.c_void_p]),
             "exo_symm_handle": (C.c_int, [C.c_void_p, C.c_void_p]), "exo_symm_open": (C.c_void_p, [C.c_void_p]),
             "exo_symm_close": (C.c_int, [C.c_void_p]), "exo_comm_header_bytes": (C.c_size_t, []),
-            "exo_comm_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.c_size_t]),
-            "exo_comm_handover_bytes": (C.c_size_t, [C.c_int]),
+            "exo_comm_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t]),
+            "exo_comm_handover_bytes": (C.c_size_t, [C.c_int, C.c_size_t]),
+            "exo_tp_handover_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                                  C.c_int, C.c_void_p]),
+            "exo_gemm_bf16_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                           C.c_void_p]),
             "exo_tp_handover_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
             "exo_gemv_stream_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
                                              C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -110,7 +124,8 @@ class FusedComm:
         self.gather_off = hdr + 2 * n * self.slot_bytes
         gather_bytes = max_gather_rows * n * vocab_shard * 2
         self.handover_off = (self.gather_off + gather_bytes + 4095) // 4096 * 4096
-        self.arena_bytes = self.handover_off + lib.exo_comm_handover_bytes(n)
+        self.handover_slot = (HANDOVER_ROWS * hidden * 2 + 4095) // 4096 * 4096
+        self.arena_bytes = self.handover_off + lib.exo_comm_handover_bytes(n, self.handover_slot)
         torch.cuda.set_device(device)
         self.local = lib.exo_symm_alloc(self.arena_bytes)
         if not self.local:
@@ -129,7 +144,8 @@ class FusedComm:
                     raise RuntimeError(f"rank {self.rank}: cannot map arena of rank {r} (no peer access?)")
                 self.peers.append(p)
         arr = (C.c_void_p * n)(*self.peers)
-        K._chk(lib.exo_comm_init(arr, n, self.rank, self.slot_bytes, self.gather_off, self.handover_off), "comm init")
+        K._chk(lib.exo_comm_init(arr, n, self.rank, self.slot_bytes, self.gather_off, self.handover_off,
+                                 self.handover_slot), "comm init")
         dist.barrier(group=group)
         raw = torch.as_tensor(_RawBuffer(self.local + self.gather_off, gather_bytes), device=device)
         self.gather_buf = raw.view(torch.bfloat16)
@@ -138,6 +154,8 @@ class FusedComm:
         self.n_collectives = 0
         self.n_handovers = 0
         self.use_handover = os.environ.get("EXO_DISABLE_TP_HANDOVER") != "1"
+        # the GEMM-epilogue variant (batches > 2) measured slower than GEMM + all-reduce kernel: off unless asked for
+        self.handover_gemm = os.environ.get("EXO_TP_HANDOVER_GEMM") == "1"
 
     # ---- collectives ----
     def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
@@ -169,14 +187,29 @@ class FusedComm:
         residual = resolve(residual)
         M, Kd = x.shape
         N = w.shape[0]
-        if (self.use_handover and 0 < M <= 2 and x.dtype == torch.bfloat16 and K.use_stream_gemv and M * N * 2 <= HANDOVER_SLOT
-                and self.lib.exo_gemv_stream_supported(M, N, Kd, 0)):
+        fits = self.use_handover and x.dtype == torch.bfloat16 and 0 < M and M * N * 2 <= self.handover_slot
+        if fits and M <= 2 and K.use_stream_gemv and self.lib.exo_gemv_stream_supported(M, N, Kd, 0):
             K.ensure_stream_init(x.device)
             parity = self._ho & 1
             self._ho += 1
             x = x.contiguous()
-            K._chk(self.lib.exo_gemv_stream_tp(x.data_ptr(), w.data_ptr(), None, None, None, 0.0, M, N, Kd, 0, 1, parity,
+            y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)      # this rank's partial (pushed by the kernel's last CTA)
+            K._chk(self.lib.exo_gemv_stream_tp(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), None, 0.0, M, N, Kd, 0, 1, parity,
                                                None, None, K._st()), "gemv_stream_tp push")
+            K._count()
+            self.n_handovers += 1
+            return Handover(self, parity, residual, M, N)
+        if (fits and self.handover_gemm and M > K.SMALL_M and K.gemm_impl is not None and Kd >= 64 and Kd % 8 == 0
+                and N % 8 == 0):
+            # batched decode: the tcgen05 GEMM's epilogue does the peer stores
+            K.ensure_gemm_init(x.device)
+            parity = self._ho & 1
+            self._ho += 1
+            x = x.contiguous()
+            splits = self.lib.exo_gemm_splits(M, N, Kd)
+            while splits > 1 and splits * M * N > K.GEMM_PARTIAL_FLOATS:
+                splits -= 1
+            K._chk(self.lib.exo_gemm_bf16_tp(x.data_ptr(), w.data_ptr(), None, M, N, Kd, splits, parity, K._st()), "gemm_tp push")
             K._count()
             self.n_handovers += 1
             return Handover(self, parity, residual, M, N)

@@ -142,6 +142,7 @@ def _handover(rank, world):
     from exo_b200.parallel.fused import FusedComm, Handover
     dev = torch.device("cuda", rank)
     comm = FusedComm(dev, max_rows=256, hidden=4096, vocab_shard=4008)
+    comm.handover_gemm = True                                      # also exercise the GEMM-epilogue variant
     shared = torch.Generator(device=dev).manual_seed(5)           # same on every rank
     mine = torch.Generator(device=dev).manual_seed(50 + rank)     # this rank's shard
     H, Kr = 4096, 2048
@@ -150,8 +151,8 @@ def _handover(rank, world):
     w_gate_up = (torch.randn(2 * 3584, H, device=dev, generator=shared) / 64).bfloat16()
     norm_w = (1 + 0.1 * torch.randn(H, device=dev, generator=shared)).bfloat16()
     worst = 0.0
-    for it in range(6):                                            # both parities, several times: flags must come back clean
-        M = 1 + it % 2
+    for it in range(10):                                           # both parities, several times: flags must come back clean
+        M = (1, 2, 1, 2, 1, 2, 32, 5, 200, 64)[it]                 # GEMV path (<= 2 rows) and GEMM path
         x = torch.randn(M, Kr, device=dev, generator=mine).bfloat16()
         res = torch.randn(M, H, device=dev, generator=shared).bfloat16()
         h = comm.row_linear(x, w_o, res)
@@ -205,7 +206,7 @@ def _engine_handover(rank, world, use_handover):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_row_parallel_handover_matches_all_reduce():
     res = _run(_handover, 2)
-    assert max(r[1][0] for r in res) < 2e-2 and all(r[1][1] == 6 for r in res)
+    assert max(r[1][0] for r in res) < 2e-2 and all(r[1][1] == 10 for r in res)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
