@@ -13,6 +13,7 @@
 // reduced once.  Splits write (O, m, l) partials; the last CTA of a (sequence, KV head) to finish
 // merges them (ticket counter, reset by that CTA so the buffer is reusable without a memset).
 // Every wait is bounded: on a timeout the kernel records a code, drains and returns.
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include "tc_common.cuh"
 
@@ -351,6 +352,306 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   if (warp == 0) tc::tmem_dealloc(tmem, TMEM_COLS);
 }
 
+
+// ---- two warpgroups per CTA -------------------------------------------------------------------
+// Same data path, but the CTA's key blocks alternate between two warpgroups, each with its own
+// S^T / O^T accumulators, P tile, running max and barriers, over the shared K/V ring: one
+// warpgroup's max-reduction / exp / P store runs while the other's MMAs and TMA refills proceed,
+// so the per-block dependency chain of a warpgroup no longer bounds the stream.  The two partial
+// results are merged through shared memory before the split's partial is published.
+struct __align__(1024) Smem2 {
+  uint8_t k[STAGES][TILE];
+  uint8_t v[STAGES][TILE];
+  uint8_t q[QTILE];
+  uint8_t p[2][QTILE];
+  uint64_t q_full, k_full[STAGES], v_full[STAGES], s_done[2], pv_done[2];
+  float wred[2][4][NQ];
+  float xo[NQ][HD];        // warpgroup 1's O^T for the merge
+  float xml[2][NQ];        // warpgroup 1's (m, l)
+  uint32_t tmem_base;
+  int is_last;
+};
+
+template <int G>
+__global__ void __launch_bounds__(256, 1)
+decode_attn2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem2& s = *reinterpret_cast<Smem2*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int wg = threadIdx.x >> 7, tid = threadIdx.x & 127, warp = tid >> 5, lane = tid & 31;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    tc::prefetch_tmap(&tmap_q);
+    tc::prefetch_tmap(&tmap_k);
+    tc::prefetch_tmap(&tmap_v);
+    tc::mbar_init(&s.q_full, 1);
+    for (int i = 0; i < STAGES; i++) {
+      tc::mbar_init(&s.k_full[i], 1);
+      tc::mbar_init(&s.v_full[i], 1);
+    }
+    for (int i = 0; i < 2; i++) {
+      tc::mbar_init(&s.s_done[i], 1);
+      tc::mbar_init(&s.pv_done[i], 1);
+    }
+    tc::fence_barrier_init();
+  }
+  reinterpret_cast<uint4*>(s.p[wg])[tid] = make_uint4(0, 0, 0, 0);
+  reinterpret_cast<uint4*>(s.p[wg])[tid + 128] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x < 32) {
+    tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t s_col = S_COL + wg * NQ, o_col = O_COL + wg * NQ;
+  pdl_wait();
+
+  const int n = p.seq_lens[b];
+  const int lo_key = p.window > 0 ? max(0, n - p.window) : 0;
+  const int first_blk = lo_key / BN, last_blk = (n + BN - 1) / BN;
+  const int per = (last_blk - first_blk + p.ns - 1) / p.ns;
+  const int blk_a = first_blk + split * per, blk_b = min(last_blk, blk_a + per);
+  const int nblk = max(0, blk_b - blk_a);
+  const int n_pages = (n + PAGE - 1) / PAGE;
+  const int* table = p.block_tables + (size_t)b * p.max_blocks;
+
+  constexpr uint32_t IDESC_S = tc::umma_idesc_bf16(BN, NQ);
+  constexpr uint32_t IDESC_PV = tc::umma_idesc_bf16(HD, NQ) | (1u << 15);
+  bool failed = false;
+
+  auto load_block = [&](int j) {
+    const int st = j % STAGES;
+    load_kv_block(s.k[st], &tmap_k, table, n_pages, (blk_a + j) * (BN / PAGE), kvh, &s.k_full[st]);
+    load_kv_block(s.v[st], &tmap_v, table, n_pages, (blk_a + j) * (BN / PAGE), kvh, &s.v_full[st]);
+  };
+  if (threadIdx.x == 0 && nblk > 0) {
+    tc::mbar_expect_tx(&s.q_full, QTILE);
+    tc::tma_load_2d(s.q, &tmap_q, 0, b * p.Hq + kvh * G, &s.q_full);
+    tc::tma_load_2d(s.q + QHALF, &tmap_q, 64, b * p.Hq + kvh * G, &s.q_full);
+    for (int j = 0; j < STAGES && j < nblk; j++) load_block(j);
+  }
+
+  float m_run[G], l_thr[G];
+#pragma unroll
+  for (int g = 0; g < G; g++) { m_run[g] = -INFINITY; l_thr[g] = 0.f; }
+  int n_mine = 0;
+
+  for (int j = wg; j < nblk; j += 2, n_mine++) {
+    const int st = j % STAGES;
+    if (tid == 0) {        // S^T(j) = K(j) Q^T
+      if (n_mine == 0 && !tc::mbar_wait(&s.q_full, 0)) failed = true;
+      if (!failed && !tc::mbar_wait(&s.k_full[st], (j / STAGES) & 1)) failed = true;
+      if (failed) atomicExch(p.err, tc::ERR_FULL_TIMEOUT);
+      else {
+        tc::tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) {
+          tc::umma_bf16(tmem + s_col, tc::umma_desc_sw128(tc::smem_u32(s.k[st]) + (ks >> 2) * HALF + (ks & 3) * 32),
+                        tc::umma_desc_sw128(tc::smem_u32(s.q) + (ks >> 2) * QHALF + (ks & 3) * 32), IDESC_S, ks > 0);
+        }
+        tc::umma_commit(&s.s_done[wg]);
+      }
+    }
+    if (!tc::mbar_wait(&s.s_done[wg], n_mine & 1)) {
+      if (tid == 0) atomicExch(p.err, tc::ERR_ACC_TIMEOUT);
+      failed = true;
+      break;
+    }
+    tc::tc_fence_after();
+    float sv[NQ];
+    tc::tmem_ld16(lane_addr + s_col, sv);
+    tc::tmem_ld_wait();
+    const int key = (blk_a + j) * BN + tid;
+    const bool vis = key >= lo_key && key < n;
+    float sc[G], mx[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      sc[g] = vis ? sv[g] * p.scale_log2 : -INFINITY;
+      mx[g] = sc[g];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xffffffffu, mx[g], o));
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int g = 0; g < G; g++) s.wred[wg][warp][g] = mx[g];
+    }
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+    float alpha[G];
+    bool moved = false;
+    uint16_t pb[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      float m_blk = fmaxf(fmaxf(s.wred[wg][0][g], s.wred[wg][1][g]), fmaxf(s.wred[wg][2][g], s.wred[wg][3][g]));
+      float m_new = fmaxf(m_run[g], m_blk);
+      float m_use = m_new == -INFINITY ? 0.f : m_new;
+      alpha[g] = m_run[g] == -INFINITY ? (m_new == -INFINITY ? 1.f : 0.f) : ex2(m_run[g] - m_use);
+      moved |= alpha[g] != 1.f;
+      __nv_bfloat16 pv = __float2bfloat16_rn(vis ? ex2(sc[g] - m_use) : 0.f);
+      l_thr[g] = l_thr[g] * alpha[g] + __bfloat162float(pv);
+      pb[g] = *reinterpret_cast<uint16_t*>(&pv);
+      m_run[g] = m_new;
+    }
+    if (n_mine > 0) {     // this warpgroup's previous O^T MMA still reads P and O^T until this fires
+      if (!tc::mbar_wait(&s.pv_done[wg], (n_mine - 1) & 1)) {
+        if (tid == 0) atomicExch(p.err, tc::ERR_ACC_TIMEOUT);
+        failed = true;
+        break;
+      }
+      tc::tc_fence_after();
+    }
+    {
+      const int col = tid & 63;
+      uint8_t* base = s.p[wg] + (tid >> 6) * QHALF + (col & 7) * 2;
+#pragma unroll
+      for (int g = 0; g < G; g++)
+        *reinterpret_cast<uint16_t*>(base + g * 128 + (((col >> 3) ^ (g & 7)) << 4)) = pb[g];
+    }
+    if (n_mine > 0 && moved) {
+      float ov[NQ];
+      tc::tmem_ld16(lane_addr + o_col, ov);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int g = 0; g < G; g++) ov[g] *= alpha[g];
+      tmem_st16(lane_addr + o_col, ov);
+      tmem_st_wait();
+    }
+    tc::fence_proxy_async();
+    tc::tc_fence_before();
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+    if (tid == 0 && !failed) {
+      tc::tc_fence_after();
+      if (!tc::mbar_wait(&s.v_full[st], (j / STAGES) & 1)) { failed = true; atomicExch(p.err, tc::ERR_FULL_TIMEOUT); }
+      if (!failed) {
+        tc::tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ks++) {
+          tc::umma_bf16(tmem + o_col, umma_desc_mn(tc::smem_u32(s.v[st]) + ks * 2048),
+                        tc::umma_desc_sw128(tc::smem_u32(s.p[wg]) + (ks >> 2) * QHALF + (ks & 3) * 32), IDESC_PV,
+                        n_mine > 0 || ks > 0);
+        }
+        tc::umma_commit(&s.pv_done[wg]);
+        // the stage is free as soon as these MMAs have read it: refill it with the block three ahead
+        if (j + STAGES < nblk) {
+          if (tc::mbar_wait(&s.pv_done[wg], n_mine & 1)) load_block(j + STAGES);
+          else { failed = true; atomicExch(p.err, tc::ERR_ACC_TIMEOUT); }
+        }
+      }
+    }
+  }
+  if (n_mine > 0 && !failed) {
+    if (!tc::mbar_wait(&s.pv_done[wg], (n_mine - 1) & 1)) {
+      if (tid == 0) atomicExch(p.err, tc::ERR_ACC_TIMEOUT);
+      failed = true;
+    }
+  }
+  tc::tc_fence_after();
+
+  float ov[NQ];
+#pragma unroll
+  for (int i = 0; i < NQ; i++) ov[i] = 0.f;
+  if (n_mine > 0 && !failed) {
+    tc::tmem_ld16(lane_addr + o_col, ov);
+    tc::tmem_ld_wait();
+  }
+  float l_tot[G];
+#pragma unroll
+  for (int g = 0; g < G; g++) {
+    float v = l_thr[g];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    l_tot[g] = v;
+  }
+  asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+  if (lane == 0) {
+#pragma unroll
+    for (int g = 0; g < G; g++) s.wred[wg][warp][g] = l_tot[g];
+  }
+  asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+#pragma unroll
+  for (int g = 0; g < G; g++) l_tot[g] = s.wred[wg][0][g] + s.wred[wg][1][g] + s.wred[wg][2][g] + s.wred[wg][3][g];
+  // ---- merge warpgroup 1 into warpgroup 0 ----
+  if (wg == 1) {
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      s.xo[g][tid] = ov[g];
+      if (tid == 0) { s.xml[0][g] = m_run[g]; s.xml[1][g] = failed ? -1.f : l_tot[g]; }
+    }
+  }
+  __syncthreads();
+  if (wg == 0) {
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      const float m1 = s.xml[0][g], l1 = s.xml[1][g];
+      if (l1 < 0.f) failed = true;
+      const float M = fmaxf(m_run[g], m1);
+      const float w0 = m_run[g] == -INFINITY ? 0.f : ex2(m_run[g] - M), w1 = m1 == -INFINITY ? 0.f : ex2(m1 - M);
+      ov[g] = ov[g] * w0 + s.xo[g][tid] * w1;
+      l_tot[g] = l_tot[g] * w0 + fmaxf(l1, 0.f) * w1;
+      m_run[g] = M;
+    }
+    if (!failed) {
+      if (p.ns == 1) {
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+          float inv = l_tot[g] > 0.f ? 1.f / l_tot[g] : 0.f;
+          p.out[((size_t)b * p.Hq + kvh * G + g) * HD + tid] = __float2bfloat16_rn(ov[g] * inv);
+        }
+      } else {
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+          size_t row = ((size_t)b * p.Hq + kvh * G + g) * p.ns + split;
+          p.part_o[row * HD + tid] = ov[g];
+          if (tid == 0) {
+            p.part_ml[row * 2] = m_run[g];
+            p.part_ml[row * 2 + 1] = l_tot[g];
+          }
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid == 0) {
+          int* tk = p.tickets + b * p.Hkv + kvh;
+          int old = atomicAdd(tk, 1);
+          s.is_last = old == p.ns - 1;
+          if (s.is_last) *tk = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s.is_last) {
+          __threadfence();
+#pragma unroll
+          for (int g = 0; g < G; g++) {
+            size_t row0 = ((size_t)b * p.Hq + kvh * G + g) * p.ns;
+            float M = -INFINITY;
+            for (int sp = 0; sp < p.ns; sp++) M = fmaxf(M, __ldcg(p.part_ml + (row0 + sp) * 2));
+            float L = 0.f, o = 0.f;
+            for (int sp = 0; sp < p.ns; sp++) {
+              float m_s = __ldcg(p.part_ml + (row0 + sp) * 2);
+              float w = m_s == -INFINITY ? 0.f : ex2(m_s - M);
+              L += __ldcg(p.part_ml + (row0 + sp) * 2 + 1) * w;
+              o += __ldcg(p.part_o + (row0 + sp) * HD + tid) * w;
+            }
+            p.out[((size_t)b * p.Hq + kvh * G + g) * HD + tid] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+          }
+        }
+      }
+    }
+  }
+  // ---- unwind: give copies that may still be in flight a bounded time to land, free the TMEM ----
+  if (failed && tid == 0) {
+    for (int i = 0; i < STAGES; i++) {
+      tc::mbar_wait(&s.k_full[i], 0, 1u << 14) || tc::mbar_wait(&s.k_full[i], 1, 1u << 14);
+      tc::mbar_wait(&s.v_full[i], 0, 1u << 14) || tc::mbar_wait(&s.v_full[i], 1, 1u << 14);
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) tc::tmem_dealloc(tmem, TMEM_COLS);
+}
+
 }  // namespace
 
 int* exo_tc_err_ptr();
@@ -397,6 +698,35 @@ EXO_API int exo_decode_attn_tc(const void* q, const void* kcache, const void* vc
   p.Hq = Hq; p.Hkv = Hkv; p.max_blocks = max_blocks; p.window = window; p.ns = ns;
   dim3 grid(ns, Hkv, B);
   cudaError_t e = cudaSuccess;
+  static int two_wg = -1;
+  if (two_wg < 0) {
+    const char* ev = getenv("EXO_DECODE_ATTN_WARPGROUPS");
+    two_wg = (ev && ev[0] == '2') ? 1 : 0;      // the two-warpgroup variant is opt-in
+  }
+  if (two_wg) {
+    size_t smem2 = sizeof(Smem2) + 1024;
+#define LAUNCH2(GG)                                                                                                  \
+  do {                                                                                                               \
+    static bool attr_set = false;                                                                                    \
+    if (!attr_set) {                                                                                                 \
+      if (cudaFuncSetAttribute(decode_attn2_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) !=  \
+          cudaSuccess)                                                                                               \
+        return -3;                                                                                                   \
+      attr_set = true;                                                                                               \
+    }                                                                                                                \
+    e = launch_pdl(decode_attn2_kernel<GG>, grid, dim3(256), smem2, st, *tq, *tk, *tv, p);                           \
+  } while (0)
+    switch (G) {
+      case 1: LAUNCH2(1); break;
+      case 2: LAUNCH2(2); break;
+      case 4: LAUNCH2(4); break;
+      default: LAUNCH2(8); break;
+    }
+#undef LAUNCH2
+    if (e != cudaSuccess) return (int)e;
+    EXO_CHECK_LAUNCH();
+    return 0;
+  }
 #define LAUNCH(GG)                                                                                                  \
   do {                                                                                                              \
     static bool attr_set = false;                                                                                   \
