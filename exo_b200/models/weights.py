@@ -20,6 +20,7 @@ from typing import Callable, Iterator
 
 import torch
 
+from ..ops.quant import Fp8Weight, quantize
 from .config import ModelConfig
 
 _DTYPES = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}
@@ -239,6 +240,26 @@ class ModelWeights:
             for v in vars(lw).values():
                 if isinstance(v, torch.Tensor):
                     yield v
+                elif isinstance(v, Fp8Weight):
+                    yield v.q
+                    yield v.scale
+
+
+QUANTIZED_FIELDS = ("wqkv", "wo", "w_gate_up", "w_down", "e_gate_up", "e_down", "s_gate_up", "s_down", "wq_a", "wq_b", "wkv_a")
+
+
+def quantize_layer(cfg: ModelConfig, lw: "LayerWeights") -> "LayerWeights":
+    """Pack this layer's projection matrices as block-scaled fp8 when the model card is served
+    quantised (``cfg.quant``); norms, router, and the absorbed MLA factors stay bf16.  Runs on the
+    weights' own device after sharding, one layer at a time, so the bf16 copy of a layer is
+    dropped before the next one is read."""
+    if cfg.quant == "none":
+        return lw
+    for name in QUANTIZED_FIELDS:
+        w = getattr(lw, name, None)
+        if isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 and w.shape[-1] % 32 == 0:
+            setattr(lw, name, quantize(w, cfg.quant))
+    return lw
 
 
 def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: str | torch.device = "cpu",
@@ -318,7 +339,7 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             lw.w_gate_up = fin(torch.cat((_rows(src.get(m + "gate_proj.weight", (F, H)), r, n),
                                           _rows(src.get(m + "up_proj.weight", (F, H)), r, n)), 0))
             lw.w_down = fin(_cols(src.get(m + "down_proj.weight", (H, F)), r, n))
-        layers[i] = lw
+        layers[i] = quantize_layer(cfg, lw)
         if progress is not None:
             progress(li + 1, len(lrange))
     embed = final_norm = lm_head = None
@@ -403,7 +424,7 @@ def _fast_shard(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device) ->
         else:
             lw.w_gate_up = src.get(p + "gu", (2 * cfg.ffn // n, H))
             lw.w_down = src.get(p + "d", (H, cfg.ffn // n))
-        layers[i] = lw
+        layers[i] = quantize_layer(cfg, lw)
     embed = src.get("embed", (cfg.vocab, H)) if spec.is_first_stage else None
     final_norm = torch.ones(H, dtype=dt, device=device) if spec.is_last_stage else None
     lm_head = src.get("lm_head", (vocab_shard(cfg.vocab, n), H)) if spec.is_last_stage else None

@@ -1,0 +1,176 @@
+// Shared by the tcgen05 GEMM kernels (bf16 weights, fp8 weights): problem description and the
+// epilogue run by warps 2..5 — accumulator read-back, bias / residual, split-K reduction in split
+// order by the last CTA of a tile, and the tensor-parallel hand-over of a row-parallel output.
+#pragma once
+#include "tc_common.cuh"
+#include "tp_handover.cuh"
+
+namespace gemm {
+
+constexpr int BM = 128;  // output features per CTA (TMEM lanes)
+constexpr int BK = 64;   // K elements per pipeline step (one 128-byte swizzle atom of bf16)
+
+struct GemmParams {
+  int M, N, K;            // x rows, W rows (output features), reduction length
+  int kb_per_split;       // K blocks handled by one split
+  int splits;
+  const __nv_bfloat16* bias;       // [N] or null
+  const __nv_bfloat16* residual;   // [M, ldo] or null (may alias out)
+  __nv_bfloat16* out;              // [M, ldo]
+  int ldo;
+  float* partial;         // [splits, M, N] fp32 (split-K only)
+  int* counters;          // [tiles] zero-initialised, self-resetting
+  int* err;               // device error word
+  TpHandover ho;          // row-parallel output handed to every rank (n_push > 0): `out` is then not written
+};
+
+// Called by the four epilogue warps (threads 64..191) once the MMA warp has committed `acc_full`.
+template <int BN>
+__device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uint64_t* acc_full, int* abort_flag,
+                                         int* is_last_s, int n0, int m0, int split, int nkb, int warp, int lane) {
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int n = n0 + quad * 32 + lane;       // output feature owned by this thread
+    bool ok = tc::mbar_wait(acc_full, 0);
+    if (!ok) { atomicExch(p.err, tc::ERR_ACC_TIMEOUT); *abort_flag = 1; }
+    tc::tc_fence_after();
+    ok = ok && !*(volatile int*)abort_flag && nkb > 0;
+    const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
+    if (p.splits == 1) {
+      float bias = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        tc::tmem_ld16(taddr + c, v);   // warp-collective: executed by all lanes regardless of bounds
+        tc::tmem_ld_wait();
+        if (ok && n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) {
+            int m = m0 + c + j;
+            if (m < p.M) {
+              float y = v[j] + bias;
+              size_t o = (size_t)m * p.ldo + n;
+              if (p.residual) y += __bfloat162float(p.residual[o]);
+              const __nv_bfloat16 yb = __float2bfloat16_rn(y);
+              if (p.ho.n_push > 0) {
+                for (int r = 0; r < p.ho.n_push; r++) p.ho.push_dst[r][o] = yb;     // peer stores
+              } else {
+                p.out[o] = yb;
+              }
+            }
+          }
+        }
+      }
+    } else {
+      // split-K: publish the fp32 partial tile
+      float* part = p.partial + (size_t)split * p.M * p.N;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        tc::tmem_ld16(taddr + c, v);
+        tc::tmem_ld_wait();
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) {
+            int m = m0 + c + j;
+            if (m < p.M) part[(size_t)m * p.N + n] = ok ? v[j] : 0.f;
+          }
+        }
+      }
+      __threadfence();
+      // named barrier over the 4 epilogue warps (128 threads), then one thread takes a ticket
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        int ticket = atomicAdd(&p.counters[tile], 1);
+        *is_last_s = (ticket == p.splits - 1);
+        if (*is_last_s) p.counters[tile] = 0;  // self-reset for the next launch / graph replay
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*is_last_s) {
+        // The last split of this tile to arrive sums the partial planes.  All 128 epilogue threads take
+        // part: a thread owns four consecutive features and every fourth row, and keeps eight 16-byte
+        // loads in flight per row (the planes are a split apart in memory), so the reduce costs a few
+        // L2 round trips instead of one per (split, row).  Splits are added in index order: the sum
+        // does not depend on which CTA came last.
+        __threadfence();
+        const int et = threadIdx.x - 64;          // 0..127 among the epilogue warps
+        const int nq = n0 + (et & 31) * 4;
+        const int mcount = min(BN, p.M - m0);
+        const size_t plane = (size_t)p.M * p.N;
+        const bool vec = (p.N & 3) == 0 && nq + 3 < p.N;
+        for (int mm = et >> 5; mm < mcount; mm += 8) {      // two rows per pass: up to 16 loads in flight per thread
+          const bool two = mm + 4 < mcount;
+          const float* base0 = p.partial + (size_t)(m0 + mm) * p.N + nq;
+          const float* base1 = base0 + (size_t)4 * p.N;
+          float y[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+          if (vec) {
+            int sp = 0;
+            for (; sp + 8 <= p.splits; sp += 8) {
+              float4 v[2][8];
+#pragma unroll
+              for (int u = 0; u < 8; u++) {
+                v[0][u] = __ldcg(reinterpret_cast<const float4*>(base0 + (size_t)(sp + u) * plane));
+                v[1][u] = two ? __ldcg(reinterpret_cast<const float4*>(base1 + (size_t)(sp + u) * plane)) : make_float4(0, 0, 0, 0);
+              }
+#pragma unroll
+              for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int u = 0; u < 8; u++) { y[r][0] += v[r][u].x; y[r][1] += v[r][u].y; y[r][2] += v[r][u].z; y[r][3] += v[r][u].w; }
+            }
+            float4 t[2][7];
+            const int rem = p.splits - sp;
+#pragma unroll
+            for (int u = 0; u < 7; u++) {
+              t[0][u] = u < rem ? __ldcg(reinterpret_cast<const float4*>(base0 + (size_t)(sp + u) * plane)) : make_float4(0, 0, 0, 0);
+              t[1][u] = (two && u < rem) ? __ldcg(reinterpret_cast<const float4*>(base1 + (size_t)(sp + u) * plane)) : make_float4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+              for (int u = 0; u < 7; u++) { y[r][0] += t[r][u].x; y[r][1] += t[r][u].y; y[r][2] += t[r][u].z; y[r][3] += t[r][u].w; }
+          } else {
+            for (int sp = 0; sp < p.splits; sp++)
+#pragma unroll
+              for (int j = 0; j < 4; j++)
+                if (nq + j < p.N) {
+                  y[0][j] += __ldcg(base0 + (size_t)sp * plane + j);
+                  if (two) y[1][j] += __ldcg(base1 + (size_t)sp * plane + j);
+                }
+          }
+#pragma unroll
+          for (int r = 0; r < 2; r++) {
+            if (r == 1 && !two) break;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              if (nq + j < p.N) {
+                size_t o = (size_t)(m0 + mm + 4 * r) * p.ldo + nq + j;
+                float v = y[r][j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
+                if (p.residual) v += __bfloat162float(p.residual[o]);
+                const __nv_bfloat16 yb = __float2bfloat16_rn(v);
+                if (p.ho.n_push > 0) {
+                  for (int rr = 0; rr < p.ho.n_push; rr++) p.ho.push_dst[rr][o] = yb;
+                } else {
+                  p.out[o] = yb;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  // ---- hand-over: when every CTA of the grid is past its stores, raise one flag per rank ----
+  if (p.ho.n_push > 0 && warp >= 2) {
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (warp == 2 && lane == 0) {
+      const int total = gridDim.x * gridDim.y * gridDim.z;
+      if (atomicAdd(p.ho.push_ticket, 1) == total - 1) {
+        *p.ho.push_ticket = 0;
+        __threadfence_system();
+        for (int r = 0; r < p.ho.n_push; r++) tp_red_release_sys_add(p.ho.push_flag[r], 1);
+      }
+    }
+  }
+}
+
+}  // namespace gemm

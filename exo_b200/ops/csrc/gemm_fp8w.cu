@@ -1,0 +1,248 @@
+// Linear layer with block-scaled fp8 (e4m3) weights and bf16 activations on the tcgen05 tensor cores:
+//   out[M, N] = x[M, K] . bf16(Wq[N, K] * scale)^T  (+bias)(+residual)
+//
+// The weight bytes are what decode is bound by, so they cross HBM once, as fp8.  The CTA has the
+// roles of the bf16 GEMM (warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue) and the
+// epilogue warps work during the main loop as well: a TMA ring delivers raw [128 x 64] byte tiles
+// plus the activation tile; thread r of the four warps turns row r of a raw tile into 64 bf16
+// values — the e4m3 bit pattern is re-based into a bf16 pattern with two logic ops per pair and one
+// packed bf16 multiply applies the block scale together with the exponent re-bias — and stores them
+// in the 128-byte-swizzled layout the MMA reads.  A second, shorter ring holds the converted tiles.
+// Scales: one e8m0 byte per 32 weights of a row ("mxfp8"), or one fp32 per 128x128 block ("dsfp8").
+//
+// The accumulator read-back, split-K and hand-over epilogue is the bf16 kernel's.
+#include <cuda_bf16.h>
+
+#include <cstring>
+
+#include "gemm_common.cuh"
+
+const CUtensorMap* exo_tmap_2d_u8(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+int exo_gemm_scratch(int** err, int** counters, float** partial, size_t* partial_floats);
+
+namespace {
+
+using gemm::BK;
+using gemm::BM;
+using gemm::GemmParams;
+
+struct ScaleParams {
+  const void* scale;
+  int kind;      // 1 = e8m0 [N, K/32], 2 = fp32 [ceil(N/128), ld]
+  int ld;        // row pitch of the scale matrix in elements
+};
+
+template <int BN, int RS, int AS>
+struct SmemF {
+  alignas(1024) __nv_bfloat16 a[AS][BM * BK];
+  alignas(1024) __nv_bfloat16 b[RS][BN * BK];
+  alignas(128) uint8_t raw[RS][BM * BK];
+  uint64_t raw_full[RS], raw_empty[RS], a_full[AS], a_empty[AS], acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+};
+
+// x holds two e4m3 bytes at bits [15:8] and [31:24].  Moving exponent and mantissa down by four
+// bits gives bf16 patterns worth value * 2^-120 (subnormals included); c2 = two copies of the
+// bf16 2^120 * scale.
+__device__ __forceinline__ uint32_t cvt_pair(uint32_t x, uint32_t c2) {
+  uint32_t y = (x & 0x80008000u) | ((x >> 4) & 0x07F007F0u);
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&y), *reinterpret_cast<__nv_bfloat162*>(&c2));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint4 cvt8(uint32_t w0, uint32_t w1, uint32_t c2) {
+  uint4 o;
+  o.x = cvt_pair(__byte_perm(w0, 0, 0x1404), c2);
+  o.y = cvt_pair(__byte_perm(w0, 0, 0x3424), c2);
+  o.z = cvt_pair(__byte_perm(w1, 0, 0x1404), c2);
+  o.w = cvt_pair(__byte_perm(w1, 0, 0x3424), c2);
+  return o;
+}
+// bf16 x2 of 2^120 * 2^(e - 127) for an e8m0 byte (exponent field e + 120, kept finite)
+__device__ __forceinline__ uint32_t c2_from_e8m0(uint32_t e) {
+  uint32_t f = min(e + 120u, 254u) << 7;
+  return f | (f << 16);
+}
+__device__ __forceinline__ uint32_t c2_from_f32(float s) {
+  __nv_bfloat16 b = __float2bfloat16_rn(fminf(s * 1.329227995784916e36f, 3.0e38f));     // * 2^120
+  uint32_t f = *reinterpret_cast<uint16_t*>(&b);
+  return f | (f << 16);
+}
+
+template <int BN, int RS, int AS>
+__global__ void __launch_bounds__(192, 1)
+gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p,
+                 const ScaleParams sp) {
+  extern __shared__ uint8_t smem_raw[];
+  using S = SmemF<BN, RS, AS>;
+  S& s = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t STAGE_BYTES = BM * BK + BN * BK * 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb0 = split * p.kb_per_split;
+  const int nkb = min(p.kb_per_split, kb_total - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < RS; i++) { tc::mbar_init(&s.raw_full[i], 1); tc::mbar_init(&s.raw_empty[i], 1); }
+    for (int i = 0; i < AS; i++) { tc::mbar_init(&s.a_full[i], 128); tc::mbar_init(&s.a_empty[i], 1); }
+    tc::mbar_init(&s.acc_full, 1);
+    s.abort_flag = 0;
+    s.is_last = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+
+  if (warp == 0) {
+    if (tc::elect_one()) {
+      tc::prefetch_tmap(&tmap_w);
+      tc::prefetch_tmap(&tmap_x);
+      for (int i = 0; i < nkb; i++) {
+        const int rs = i % RS;
+        if (i >= RS && !tc::mbar_wait(&s.raw_empty[rs], ((i / RS) - 1) & 1)) {
+          atomicExch(p.err, tc::ERR_EMPTY_TIMEOUT);
+          s.abort_flag = 1;
+          break;
+        }
+        tc::mbar_expect_tx(&s.raw_full[rs], STAGE_BYTES);
+        const int k = (kb0 + i) * BK;
+        tc::tma_load_2d(s.raw[rs], &tmap_w, k, n0, &s.raw_full[rs]);
+        tc::tma_load_2d(s.b[rs], &tmap_x, k, m0, &s.raw_full[rs]);
+      }
+    }
+  } else if (warp == 1) {
+    if (tc::elect_one()) {
+      constexpr uint32_t idesc = tc::umma_idesc_bf16(BM, BN);
+      for (int i = 0; i < nkb; i++) {
+        const int rs = i % RS, as = i % AS;
+        if (!tc::mbar_wait(&s.a_full[as], (i / AS) & 1) || !tc::mbar_wait(&s.raw_full[rs], (i / RS) & 1)) {
+          atomicExch(p.err, tc::ERR_FULL_TIMEOUT);
+          s.abort_flag = 1;
+          break;
+        }
+        tc::tc_fence_after();
+        const uint64_t ad = tc::umma_desc_sw128(tc::smem_u32(s.a[as]));
+        const uint64_t bd = tc::umma_desc_sw128(tc::smem_u32(s.b[rs]));
+#pragma unroll
+        for (int k = 0; k < BK / 16; k++) tc::umma_bf16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) != 0);
+        tc::umma_commit(&s.a_empty[as]);
+        tc::umma_commit(&s.raw_empty[rs]);
+      }
+      tc::umma_commit(&s.acc_full);
+    }
+  } else {
+    // ---- converters: row r of every raw tile ----
+    const int r = (warp - 2) * 32 + lane;
+    const int n = n0 + r;
+    const int k32 = p.K / 32;
+    uint8_t* const a_row_base = reinterpret_cast<uint8_t*>(s.a[0]) + r * 128;
+    for (int i = 0; i < nkb; i++) {
+      const int rs = i % RS, as = i % AS;
+      // scales of this row's two 32-blocks (mxfp8) or of the 128x128 block (dsfp8): in flight during the wait
+      const int kb = kb0 + i;
+      uint32_t c_lo = 0, c_hi = 0;
+      if (n < p.N) {
+        if (sp.kind == 1) {
+          const uint8_t* sc = reinterpret_cast<const uint8_t*>(sp.scale) + (size_t)n * sp.ld + 2 * kb;
+          c_lo = 2 * kb < k32 ? c2_from_e8m0(__ldg(sc)) : 0u;
+          c_hi = 2 * kb + 1 < k32 ? c2_from_e8m0(__ldg(sc + 1)) : 0u;
+        } else {
+          c_lo = c_hi = c2_from_f32(__ldg(reinterpret_cast<const float*>(sp.scale) + (size_t)(n >> 7) * sp.ld + (kb >> 1)));
+        }
+      }
+      if (!tc::mbar_wait(&s.raw_full[rs], (i / RS) & 1) ||
+          (i >= AS && !tc::mbar_wait(&s.a_empty[as], ((i / AS) - 1) & 1))) {
+        atomicExch(p.err, tc::ERR_TILE_TIMEOUT);
+        s.abort_flag = 1;
+        break;
+      }
+      tc::tc_fence_after();
+      const uint4* src = reinterpret_cast<const uint4*>(s.raw[rs] + r * 64);
+      uint8_t* dst = a_row_base + (size_t)as * (BM * BK * 2);
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const uint4 w = src[q];
+        const uint32_t c2 = q < 2 ? c_lo : c_hi;
+        *reinterpret_cast<uint4*>(dst + (((2 * q) ^ (r & 7)) << 4)) = cvt8(w.x, w.y, c2);
+        *reinterpret_cast<uint4*>(dst + (((2 * q + 1) ^ (r & 7)) << 4)) = cvt8(w.z, w.w, c2);
+      }
+      tc::fence_proxy_async();       // the MMA reads these stores through the async proxy
+      tc::mbar_arrive(&s.a_full[as]);
+    }
+    gemm::epilogue<BN>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+template <int BN, int RS, int AS>
+int launch_fp8w(const CUtensorMap* tw, const CUtensorMap* tx, const GemmParams& p, const ScaleParams& sp, cudaStream_t st) {
+  using S = SmemF<BN, RS, AS>;
+  const size_t smem = sizeof(S) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_fp8w_kernel<BN, RS, AS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
+  gemm_fp8w_kernel<BN, RS, AS><<<grid, 192, smem, st>>>(*tw, *tx, p, sp);
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // namespace
+
+// scale_kind: 1 = e8m0 bytes [N, K/32]; 2 = fp32 [ceil(N/128), ceil(K/128)].
+EXO_API int exo_gemm_fp8w(const void* x, const void* Wq, const void* scale, int scale_kind, const void* bias,
+                          const void* residual, void* out, int M, int N, int K, int ldo, int splits, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 32 != 0 || K < BK || (scale_kind != 1 && scale_kind != 2)) return -2;
+  GemmParams p;
+  size_t partial_floats = 0;
+  if (exo_gemm_scratch(&p.err, &p.counters, &p.partial, &partial_floats)) return -4;
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const CUtensorMap* tw = exo_tmap_2d_u8(Wq, N, K, BM);
+  const CUtensorMap* tx = exo_tmap_2d_bf16(x, M, K, bn);
+  if (!tw || !tx) return -5;
+  p.M = M; p.N = N; p.K = K;
+  const int kb_total = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > kb_total) splits = kb_total;
+  p.kb_per_split = (kb_total + splits - 1) / splits;
+  splits = (kb_total + p.kb_per_split - 1) / p.kb_per_split;
+  p.splits = splits;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.residual = (const __nv_bfloat16*)residual;
+  p.out = (__nv_bfloat16*)out;
+  p.ldo = ldo;
+  memset(&p.ho, 0, sizeof(p.ho));
+  if (splits > 1) {
+    const long tiles = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+    if ((size_t)splits * M * N > partial_floats || tiles > (1 << 16)) return -6;
+  }
+  ScaleParams sp;
+  sp.scale = scale;
+  sp.kind = scale_kind;
+  sp.ld = scale_kind == 1 ? K / 32 : (K + 127) / 128;
+  switch (bn) {
+    case 16: return launch_fp8w<16, 8, 3>(tw, tx, p, sp, st);     // 48 + 16 + 64 KB
+    case 32: return launch_fp8w<32, 8, 3>(tw, tx, p, sp, st);     // 48 + 32 + 64 KB
+    case 64: return launch_fp8w<64, 6, 3>(tw, tx, p, sp, st);     // 48 + 48 + 48 KB
+    case 128: return launch_fp8w<128, 4, 3>(tw, tx, p, sp, st);   // 48 + 64 + 32 KB
+    default: return launch_fp8w<256, 4, 2>(tw, tx, p, sp, st);    // 32 + 128 + 32 KB
+  }
+}

@@ -17,27 +17,13 @@
 #include <unordered_map>
 
 #include <cstring>
-#include "tc_common.cuh"
-#include "tp_handover.cuh"
+#include "gemm_common.cuh"
 
 namespace {
 
-constexpr int BM = 128;  // output features per CTA (TMEM lanes)
-constexpr int BK = 64;   // K elements per stage (128 bytes of bf16: one swizzle atom)
-
-struct GemmParams {
-  int M, N, K;            // x rows, W rows (output features), reduction length
-  int kb_per_split;       // K blocks handled by one split
-  int splits;
-  const __nv_bfloat16* bias;       // [N] or null
-  const __nv_bfloat16* residual;   // [M, ldo] or null (may alias out)
-  __nv_bfloat16* out;              // [M, ldo]
-  int ldo;
-  float* partial;         // [splits, M, N] fp32 (split-K only)
-  int* counters;          // [tiles] zero-initialised, self-resetting
-  int* err;               // device error word
-  TpHandover ho;          // row-parallel output handed to every rank (n_push > 0): `out` is then not written
-};
+using gemm::BM;
+using gemm::BK;
+using gemm::GemmParams;
 
 template <int BN, int STAGES>
 struct Smem {
@@ -122,150 +108,7 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       tc::umma_commit(&s.acc_full);  // accumulator complete (also arrives if we bailed out: nothing pending)
     }
   } else {
-    // ------------------------------ epilogue (warps 2..5) ------------------------------
-    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
-    const int n = n0 + quad * 32 + lane;       // output feature owned by this thread
-    bool ok = tc::mbar_wait(&s.acc_full, 0);
-    if (!ok) { atomicExch(p.err, tc::ERR_ACC_TIMEOUT); s.abort_flag = 1; }
-    tc::tc_fence_after();
-    ok = ok && !*(volatile int*)&s.abort_flag && nkb > 0;
-    const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
-    if (p.splits == 1) {
-      float bias = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        float v[16];
-        tc::tmem_ld16(taddr + c, v);   // warp-collective: executed by all lanes regardless of bounds
-        tc::tmem_ld_wait();
-        if (ok && n < p.N) {
-#pragma unroll
-          for (int j = 0; j < 16; j++) {
-            int m = m0 + c + j;
-            if (m < p.M) {
-              float y = v[j] + bias;
-              size_t o = (size_t)m * p.ldo + n;
-              if (p.residual) y += __bfloat162float(p.residual[o]);
-              const __nv_bfloat16 yb = __float2bfloat16_rn(y);
-              if (p.ho.n_push > 0) {
-                for (int r = 0; r < p.ho.n_push; r++) p.ho.push_dst[r][o] = yb;     // peer stores
-              } else {
-                p.out[o] = yb;
-              }
-            }
-          }
-        }
-      }
-    } else {
-      // split-K: publish the fp32 partial tile
-      float* part = p.partial + (size_t)split * p.M * p.N;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        float v[16];
-        tc::tmem_ld16(taddr + c, v);
-        tc::tmem_ld_wait();
-        if (n < p.N) {
-#pragma unroll
-          for (int j = 0; j < 16; j++) {
-            int m = m0 + c + j;
-            if (m < p.M) part[(size_t)m * p.N + n] = ok ? v[j] : 0.f;
-          }
-        }
-      }
-      __threadfence();
-      // named barrier over the 4 epilogue warps (128 threads), then one thread takes a ticket
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (warp == 2 && lane == 0) {
-        int tile = blockIdx.y * gridDim.x + blockIdx.x;
-        int ticket = atomicAdd(&p.counters[tile], 1);
-        s.is_last = (ticket == p.splits - 1);
-        if (s.is_last) p.counters[tile] = 0;  // self-reset for the next launch / graph replay
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (s.is_last) {
-        // The last split of this tile to arrive sums the partial planes.  All 128 epilogue threads take
-        // part: a thread owns four consecutive features and every fourth row, and keeps eight 16-byte
-        // loads in flight per row (the planes are a split apart in memory), so the reduce costs a few
-        // L2 round trips instead of one per (split, row).  Splits are added in index order: the sum
-        // does not depend on which CTA came last.
-        __threadfence();
-        const int et = threadIdx.x - 64;          // 0..127 among the epilogue warps
-        const int nq = n0 + (et & 31) * 4;
-        const int mcount = min(BN, p.M - m0);
-        const size_t plane = (size_t)p.M * p.N;
-        const bool vec = (p.N & 3) == 0 && nq + 3 < p.N;
-        for (int mm = et >> 5; mm < mcount; mm += 8) {      // two rows per pass: up to 16 loads in flight per thread
-          const bool two = mm + 4 < mcount;
-          const float* base0 = p.partial + (size_t)(m0 + mm) * p.N + nq;
-          const float* base1 = base0 + (size_t)4 * p.N;
-          float y[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-          if (vec) {
-            int sp = 0;
-            for (; sp + 8 <= p.splits; sp += 8) {
-              float4 v[2][8];
-#pragma unroll
-              for (int u = 0; u < 8; u++) {
-                v[0][u] = __ldcg(reinterpret_cast<const float4*>(base0 + (size_t)(sp + u) * plane));
-                v[1][u] = two ? __ldcg(reinterpret_cast<const float4*>(base1 + (size_t)(sp + u) * plane)) : make_float4(0, 0, 0, 0);
-              }
-#pragma unroll
-              for (int r = 0; r < 2; r++)
-#pragma unroll
-                for (int u = 0; u < 8; u++) { y[r][0] += v[r][u].x; y[r][1] += v[r][u].y; y[r][2] += v[r][u].z; y[r][3] += v[r][u].w; }
-            }
-            float4 t[2][7];
-            const int rem = p.splits - sp;
-#pragma unroll
-            for (int u = 0; u < 7; u++) {
-              t[0][u] = u < rem ? __ldcg(reinterpret_cast<const float4*>(base0 + (size_t)(sp + u) * plane)) : make_float4(0, 0, 0, 0);
-              t[1][u] = (two && u < rem) ? __ldcg(reinterpret_cast<const float4*>(base1 + (size_t)(sp + u) * plane)) : make_float4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int r = 0; r < 2; r++)
-#pragma unroll
-              for (int u = 0; u < 7; u++) { y[r][0] += t[r][u].x; y[r][1] += t[r][u].y; y[r][2] += t[r][u].z; y[r][3] += t[r][u].w; }
-          } else {
-            for (int sp = 0; sp < p.splits; sp++)
-#pragma unroll
-              for (int j = 0; j < 4; j++)
-                if (nq + j < p.N) {
-                  y[0][j] += __ldcg(base0 + (size_t)sp * plane + j);
-                  if (two) y[1][j] += __ldcg(base1 + (size_t)sp * plane + j);
-                }
-          }
-#pragma unroll
-          for (int r = 0; r < 2; r++) {
-            if (r == 1 && !two) break;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              if (nq + j < p.N) {
-                size_t o = (size_t)(m0 + mm + 4 * r) * p.ldo + nq + j;
-                float v = y[r][j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
-                if (p.residual) v += __bfloat162float(p.residual[o]);
-                const __nv_bfloat16 yb = __float2bfloat16_rn(v);
-                if (p.ho.n_push > 0) {
-                  for (int rr = 0; rr < p.ho.n_push; rr++) p.ho.push_dst[rr][o] = yb;
-                } else {
-                  p.out[o] = yb;
-                }
-              }
-            }
-          }
-        }
-      }
-    }
-  }
-  // ---- hand-over: when every CTA of the grid is past its stores, raise one flag per rank ----
-  if (p.ho.n_push > 0 && warp >= 2) {
-    __threadfence_system();
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (warp == 2 && lane == 0) {
-      const int total = gridDim.x * gridDim.y * gridDim.z;
-      if (atomicAdd(p.ho.push_ticket, 1) == total - 1) {
-        *p.ho.push_ticket = 0;
-        __threadfence_system();
-        for (int r = 0; r < p.ho.n_push; r++) tp_red_release_sys_add(p.ho.push_flag[r], 1);
-      }
-    }
+    gemm::epilogue<BN>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
   }
   // ------------------------------ teardown ------------------------------
   tc::tc_fence_before();
@@ -298,7 +141,7 @@ EncodeFn get_encode() {
 }
 
 struct Key {
-  const void* base; uint64_t rows, cols; uint32_t box;
+  const void* base; uint64_t rows, cols; uint32_t box;   // box: rows of the box, | 1<<31 for the byte-typed maps
   bool operator==(const Key& o) const { return base == o.base && rows == o.rows && cols == o.cols && box == o.box; }
 };
 struct KeyHash {
@@ -339,6 +182,39 @@ const CUtensorMap* exo_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t co
   }
   g_maps[k] = m;
   return m;
+}
+
+// Row-major [rows, cols] byte matrix (fp8 payloads) with a [box_rows x 64] box, no swizzle: the
+// consumer reads the tile with ordinary shared-memory loads.
+const CUtensorMap* exo_tmap_2d_u8(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  std::lock_guard<std::mutex> lk(g_maps_mu);
+  Key k{base, rows, cols, box_rows | (1u << 31)};
+  auto it = g_maps.find(k);
+  if (it != g_maps.end()) return it->second;
+  EncodeFn enc = get_encode();
+  if (!enc || cols % 16 != 0 || ((uintptr_t)base & 15)) return nullptr;
+  CUtensorMap* m = new CUtensorMap;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { delete m; return nullptr; }
+  g_maps[k] = m;
+  return m;
+}
+
+// The current device's scratch of the GEMM family (null / 0 before exo_gemm_init).
+int exo_gemm_scratch(int** err, int** counters, float** partial, size_t* partial_floats) {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_err[dev]) return -4;
+  *err = g_err[dev];
+  *counters = g_counters[dev];
+  *partial = g_partial[dev];
+  *partial_floats = g_partial_floats[dev];
+  return 0;
 }
 
 // Per-device scratch set up on first use (NOT inside stream capture: call exo_gemm_init first).

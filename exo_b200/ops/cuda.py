@@ -13,6 +13,7 @@ from pathlib import Path
 import torch
 
 from . import reference as ref
+from .quant import Fp8Weight
 
 _lib: C.CDLL | None = None
 _SO = Path(__file__).resolve().parent / "_kernels.so"
@@ -68,6 +69,13 @@ class _Sig:
     exo_gemm_last_error = (_i, [])
     exo_gemm_splits = (_i, [_i, _i, _i])
     exo_gemm_bf16 = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+    exo_gemm_fp8w = (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+    exo_moe_route = (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p])
+    exo_moe_tile_rows = (_i, [_i, _i])
+    exo_moe_max_tiles = (_i, [_i, _i, _i])
+    exo_moe_plan_ints = (_l, [_i, _i])
+    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
+    exo_moe_experts_gemv = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
 
 
 def _st() -> int:
@@ -162,6 +170,29 @@ def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False):
     return swiglu(out) if swiglu_out else out
 
 
+def linear_fp8(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=False):
+    """Block-scaled fp8 weights, bf16 activations: the weights cross HBM as bytes and are widened to
+    bf16 inside the tcgen05 GEMM's pipeline (every batch size; the norm is a separate kernel)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16:
+        raise KernelError("fp8 weights are served with bf16 activations")
+    if norm_w is not None:
+        x, _ = rmsnorm(x, norm_w, eps)
+    out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    if M == 0:
+        return swiglu(out) if swiglu_out else out
+    ensure_gemm_init(x.device)
+    lib = load()
+    splits = lib.exo_gemm_splits(M, N, K)
+    while splits > 1 and splits * M * N > GEMM_PARTIAL_FLOATS:
+        splits -= 1
+    _chk(lib.exo_gemm_fp8w(_ptr(x), _ptr(w.q), _ptr(w.scale), 1 if w.kind == "mxfp8" else 2, _ptr(bias), _ptr(residual),
+                           _ptr(out), M, N, K, N, splits, _st()), "gemm_fp8w")
+    _count()
+    return swiglu(out) if swiglu_out else out
+
+
 def gemm_check() -> None:
     """Raise if any tensor-core kernel since the last check recorded a wait timeout."""
     code = load().exo_gemm_last_error()
@@ -191,6 +222,8 @@ def linear(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=Fals
     M, K = x.shape
     N = w.shape[0]
     lib = load()
+    if isinstance(w, Fp8Weight):
+        return linear_fp8(x, w, bias, residual, norm_w, eps, swiglu_out)
     if (use_stream_gemv and 0 < M <= 2 and x.dtype == torch.bfloat16
             and lib.exo_gemv_stream_supported(M, N, K, int(swiglu_out))):
         ensure_stream_init(x.device)
@@ -324,9 +357,56 @@ def mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale,
     return ref.mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora)
 
 
+MOE_GEMV_MAX_TOKENS = 4    # up to this many tokens the experts run as grouped GEMVs (no sort, two launches)
+use_moe_kernels = os.environ.get("EXO_DISABLE_MOE_KERNELS") != "1"
+
+
 def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling):
-    return ref.moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling)
+    T, E = logits.shape
+    if (not use_moe_kernels or E > 512 or top_k > 16 or n_group > 32 or logits.dtype not in _DT
+            or (bias is not None and bias.dtype not in _DT)):
+        return ref.moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling)
+    logits = logits.contiguous()
+    w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    sig = kind != "softmax"
+    _chk(load().exo_moe_route(_ptr(logits), _ptr(bias) if sig else None, _ptr(w), _ptr(ids), T, E, top_k,
+                              n_group if sig else 1, topk_group if sig else 1, _dt(logits),
+                              _dt(bias) if (sig and bias is not None) else BF16, int(sig), int(bool(norm_topk)),
+                              float(scaling), _st()), "moe_route")
+    _count()
+    return w, ids
 
 
 def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0):
-    return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
+    T, H = x.shape
+    E, F2, _ = w_gate_up.shape
+    F, k = F2 // 2, ids.shape[1]
+    if (not use_moe_kernels or isinstance(w_gate_up, Fp8Weight) or x.dtype != torch.bfloat16
+            or w_gate_up.dtype != torch.bfloat16 or H % 8 or F % 8
+            or H < 64 or F < 64 or E > 1024):
+        return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
+    x, ids = x.contiguous(), ids.contiguous().to(torch.int32)
+    weights = weights.contiguous().float()
+    w_gate_up, w_down = w_gate_up.contiguous(), w_down.contiguous()
+    out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+    P = T * k
+    lib = load()
+    if T <= MOE_GEMV_MAX_TOKENS and H * 2 <= 200 * 1024 and k * F * 2 <= 200 * 1024:
+        hs = torch.empty(P, F, dtype=x.dtype, device=x.device)
+        _chk(lib.exo_moe_experts_gemv(_ptr(x), _ptr(w_gate_up), _ptr(w_down), _ptr(weights), _ptr(ids), _ptr(out), _ptr(hs),
+                                      T, k, H, F, E, expert_offset, _st()), "moe_experts_gemv")
+        _count(2)
+        return out
+    ensure_gemm_init(x.device)
+    bn = lib.exo_moe_tile_rows(P, E)
+    scratch = torch.empty(lib.exo_moe_plan_ints(E, lib.exo_moe_max_tiles(P, E, bn)), dtype=torch.int32, device=x.device)
+    pos = torch.empty(P, dtype=torch.int32, device=x.device)
+    xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
+    hs = torch.empty(P, F, dtype=x.dtype, device=x.device)
+    ys = torch.empty(P, H, dtype=x.dtype, device=x.device)
+    _chk(lib.exo_moe_experts_grouped(_ptr(x), _ptr(w_gate_up), _ptr(w_down), _ptr(weights), _ptr(ids), _ptr(out),
+                                     _ptr(scratch), _ptr(pos), _ptr(xs), _ptr(hs), _ptr(ys), T, k, H, F, E, expert_offset,
+                                     _st()), "moe_experts_grouped")
+    _count(7)
+    return out

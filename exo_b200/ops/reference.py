@@ -25,7 +25,10 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            residual: torch.Tensor | None = None) -> torch.Tensor:
-    """``y = x @ w.T (+bias) (+residual)`` with fp32 accumulation; ``w`` is ``[out, in]``."""
+    """``y = x @ w.T (+bias) (+residual)`` with fp32 accumulation; ``w`` is ``[out, in]`` (a block-scaled
+    fp8 weight stands for its bf16 dequantisation)."""
+    if hasattr(w, "dequantize"):
+        w = w.dequantize()
     y = x.float() @ w.float().t()
     if bias is not None:
         y = y + bias.float()

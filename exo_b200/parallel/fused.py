@@ -61,7 +61,7 @@ class Handover:
             K._count()
             self.done = True
             return K.linear(xn, w, bias, None, None, 0.0, swiglu)
-        if self.done or not lib.exo_gemv_stream_supported(M, N, Kd, int(swiglu)):
+        if self.done or not isinstance(w, torch.Tensor) or not lib.exo_gemv_stream_supported(M, N, Kd, int(swiglu)):
             return K.linear(self.value(), w, bias, None, norm_w, eps, swiglu)
         y = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device=self.out.device)
         K._chk(lib.exo_gemv_stream_tp(None, w.data_ptr(), K._ptr(bias), y.data_ptr(), K._ptr(norm_w), eps, M, N, Kd, int(swiglu),
@@ -187,7 +187,8 @@ class FusedComm:
         residual = resolve(residual)
         M, Kd = x.shape
         N = w.shape[0]
-        fits = self.use_handover and x.dtype == torch.bfloat16 and 0 < M and M * N * 2 <= self.handover_slot
+        fits = (self.use_handover and x.dtype == torch.bfloat16 and 0 < M and M * N * 2 <= self.handover_slot
+                and isinstance(w, torch.Tensor))       # block-scaled fp8 weights take the GEMM + all-reduce path
         if fits and M <= 2 and K.use_stream_gemv and self.lib.exo_gemv_stream_supported(M, N, Kd, 0):
             K.ensure_stream_init(x.device)
             parity = self._ho & 1

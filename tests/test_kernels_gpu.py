@@ -240,3 +240,60 @@ def test_sample_matches_reference(K, V):
     assert (got == want).sum().item() >= B - 1, (got, want)
     probs = torch.softmax(logits / temp.clamp_min(1e-6)[:, None], -1)
     assert (probs.gather(1, got[:, None]) > 0).all()
+
+
+@pytest.mark.parametrize("kind,E,k,n_group,topk_group,dtype", [
+    ("softmax", 128, 8, 1, 1, torch.bfloat16), ("softmax", 60, 4, 1, 1, torch.float32),
+    ("sigmoid", 256, 8, 8, 4, torch.float32), ("sigmoid", 64, 6, 1, 1, torch.bfloat16)])
+def test_moe_route(K, kind, E, k, n_group, topk_group, dtype):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    # distinct values in every row, also after rounding to bf16: the top-k has no ties to break
+    logits = torch.stack([torch.randperm(E, device="cuda", generator=g) for _ in range(37)]).float().mul(6.0 / E).sub(3.0).to(dtype)
+    bias = 0.1 * torch.randn(E, device="cuda", generator=g) if kind == "sigmoid" else None
+    w, ids = K.moe_route(logits, k, kind, True, bias, n_group, topk_group, 2.5)
+    rw, rids = ref.moe_route(logits, k, kind, True, bias, n_group, topk_group, 2.5)
+    assert w.dtype == torch.float32 and ids.dtype == torch.int32
+    assert torch.equal(ids.sort(-1)[0], rids.sort(-1)[0])
+    assert torch.equal(ids, rids)
+    close(w, rw, 1e-4, 1e-5)
+    w2, _ = K.moe_route(logits, k, kind, False, bias, n_group, topk_group, 1.0)
+    close(w2, ref.moe_route(logits, k, kind, False, bias, n_group, topk_group, 1.0)[0], 1e-4, 1e-5)
+
+
+@pytest.mark.parametrize("T,E,k,H,F,offset,E_all", [
+    (1, 8, 2, 256, 128, 0, 8), (3, 16, 4, 512, 192, 16, 64),            # grouped GEMVs
+    (40, 8, 2, 256, 128, 0, 8), (300, 16, 8, 512, 384, 32, 64), (2048, 4, 2, 256, 256, 0, 4)])   # grouped tcgen05 GEMMs
+def test_moe_experts(K, T, E, k, H, F, offset, E_all):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    wgu = (torch.randn(E, 2 * F, H, device="cuda", generator=g) / math.sqrt(H)).bfloat16()
+    wd = (torch.randn(E, H, F, device="cuda", generator=g) / math.sqrt(F)).bfloat16()
+    logits = torch.randn(T, E_all, device="cuda", generator=g)
+    w, ids = ref.moe_route(logits, k, "softmax", True)
+    out = K.moe_experts(x, wgu, wd, w, ids, offset)
+    want = ref.moe_experts(x, wgu, wd, w, ids, offset)
+    assert K.load().exo_gemm_last_error() == 0
+    close(out, want, 2e-2, 2e-2)
+    # the same call again (plan scratch and tensor maps are reused) gives the same bits
+    assert torch.equal(out, K.moe_experts(x, wgu, wd, w, ids, offset))
+
+
+@pytest.mark.parametrize("kind", ["mxfp8", "dsfp8"])
+@pytest.mark.parametrize("M,N,K_", [(1, 256, 256), (5, 384, 1024), (32, 1000, 4096), (200, 512, 96), (300, 640, 2048)])
+def test_gemm_fp8_weights(K, kind, M, N, K_):
+    from exo_b200.ops import quant
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(M, K_, device="cuda", generator=g).bfloat16()
+    # magnitudes spread over several octaves per block so that every block scale and the subnormal codes are exercised
+    w = torch.randn(N, K_, device="cuda", generator=g) * torch.exp2(torch.randint(-6, 3, (N, 1), device="cuda", generator=g).float())
+    wq = quant.quantize(w.bfloat16(), kind)
+    bias = torch.randn(N, device="cuda", generator=g).bfloat16()
+    res = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    want = ref.linear(x.float(), wq, bias.float(), res.float())
+    out = K.linear(x, wq, bias, res)
+    assert K.load().exo_gemm_last_error() == 0
+    close(out, want, 1e-2, 1e-2)
+    # against the unquantised weights the error is the fp8 rounding (2^-4 relative per weight, averaged down by the sum)
+    close(K.linear(x, wq), ref.linear(x.float(), w.bfloat16().float()), 5e-2, 5e-2)
+    sw = K.linear(x, quant.quantize(w[: N // 2 * 2].bfloat16(), kind), swiglu_out=True)
+    close(sw, ref.swiglu(ref.linear(x, quant.quantize(w[: N // 2 * 2].bfloat16(), kind))), 3e-2, 3e-2)
