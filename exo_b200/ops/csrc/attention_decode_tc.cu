@@ -701,7 +701,7 @@ EXO_API int exo_decode_attn_tc(const void* q, const void* kcache, const void* vc
   static int two_wg = -1;
   if (two_wg < 0) {
     const char* ev = getenv("EXO_DECODE_ATTN_WARPGROUPS");
-    two_wg = (ev && ev[0] == '2') ? 1 : 0;      // the two-warpgroup variant is opt-in
+    two_wg = (ev && ev[0] == '1') ? 0 : 1;      // two warpgroups unless EXO_DECODE_ATTN_WARPGROUPS=1
   }
   if (two_wg) {
     size_t smem2 = sizeof(Smem2) + 1024;

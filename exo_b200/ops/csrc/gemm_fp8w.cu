@@ -15,6 +15,7 @@
 
 #include <cstring>
 
+#include "fp8_convert.cuh"
 #include "gemm_common.cuh"
 
 const CUtensorMap* exo_tmap_2d_u8(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
@@ -25,6 +26,7 @@ namespace {
 using gemm::BK;
 using gemm::BM;
 using gemm::GemmParams;
+using namespace fp8cvt;
 
 struct ScaleParams {
   const void* scale;
@@ -43,35 +45,8 @@ struct SmemF {
   int is_last;
 };
 
-// x holds two e4m3 bytes at bits [15:8] and [31:24].  Moving exponent and mantissa down by four
-// bits gives bf16 patterns worth value * 2^-120 (subnormals included); c2 = two copies of the
-// bf16 2^120 * scale.
-__device__ __forceinline__ uint32_t cvt_pair(uint32_t x, uint32_t c2) {
-  uint32_t y = (x & 0x80008000u) | ((x >> 4) & 0x07F007F0u);
-  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&y), *reinterpret_cast<__nv_bfloat162*>(&c2));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-__device__ __forceinline__ uint4 cvt8(uint32_t w0, uint32_t w1, uint32_t c2) {
-  uint4 o;
-  o.x = cvt_pair(__byte_perm(w0, 0, 0x1404), c2);
-  o.y = cvt_pair(__byte_perm(w0, 0, 0x3424), c2);
-  o.z = cvt_pair(__byte_perm(w1, 0, 0x1404), c2);
-  o.w = cvt_pair(__byte_perm(w1, 0, 0x3424), c2);
-  return o;
-}
-// bf16 x2 of 2^120 * 2^(e - 127) for an e8m0 byte (exponent field e + 120, kept finite)
-__device__ __forceinline__ uint32_t c2_from_e8m0(uint32_t e) {
-  uint32_t f = min(e + 120u, 254u) << 7;
-  return f | (f << 16);
-}
-__device__ __forceinline__ uint32_t c2_from_f32(float s) {
-  __nv_bfloat16 b = __float2bfloat16_rn(fminf(s * 1.329227995784916e36f, 3.0e38f));     // * 2^120
-  uint32_t f = *reinterpret_cast<uint16_t*>(&b);
-  return f | (f << 16);
-}
-
 template <int BN, int RS, int AS>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, (BN <= 64 ? 2 : 1))
 gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p,
                  const ScaleParams sp) {
   extern __shared__ uint8_t smem_raw[];
@@ -142,23 +117,12 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   } else {
     // ---- converters: row r of every raw tile ----
     const int r = (warp - 2) * 32 + lane;
-    const int n = n0 + r;
-    const int k32 = p.K / 32;
-    uint8_t* const a_row_base = reinterpret_cast<uint8_t*>(s.a[0]) + r * 128;
+    ScaleStream sc;
+    sc.init(sp.scale, sp.kind, sp.ld, n0 + r, kb0, nkb, p.K, n0 + r < p.N);
     for (int i = 0; i < nkb; i++) {
       const int rs = i % RS, as = i % AS;
-      // scales of this row's two 32-blocks (mxfp8) or of the 128x128 block (dsfp8): in flight during the wait
-      const int kb = kb0 + i;
-      uint32_t c_lo = 0, c_hi = 0;
-      if (n < p.N) {
-        if (sp.kind == 1) {
-          const uint8_t* sc = reinterpret_cast<const uint8_t*>(sp.scale) + (size_t)n * sp.ld + 2 * kb;
-          c_lo = 2 * kb < k32 ? c2_from_e8m0(__ldg(sc)) : 0u;
-          c_hi = 2 * kb + 1 < k32 ? c2_from_e8m0(__ldg(sc + 1)) : 0u;
-        } else {
-          c_lo = c_hi = c2_from_f32(__ldg(reinterpret_cast<const float*>(sp.scale) + (size_t)(n >> 7) * sp.ld + (kb >> 1)));
-        }
-      }
+      uint32_t c_lo, c_hi;
+      sc.next(i, c_lo, c_hi);
       if (!tc::mbar_wait(&s.raw_full[rs], (i / RS) & 1) ||
           (i >= AS && !tc::mbar_wait(&s.a_empty[as], ((i / AS) - 1) & 1))) {
         atomicExch(p.err, tc::ERR_TILE_TIMEOUT);
@@ -166,15 +130,7 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         break;
       }
       tc::tc_fence_after();
-      const uint4* src = reinterpret_cast<const uint4*>(s.raw[rs] + r * 64);
-      uint8_t* dst = a_row_base + (size_t)as * (BM * BK * 2);
-#pragma unroll
-      for (int q = 0; q < 4; q++) {
-        const uint4 w = src[q];
-        const uint32_t c2 = q < 2 ? c_lo : c_hi;
-        *reinterpret_cast<uint4*>(dst + (((2 * q) ^ (r & 7)) << 4)) = cvt8(w.x, w.y, c2);
-        *reinterpret_cast<uint4*>(dst + (((2 * q + 1) ^ (r & 7)) << 4)) = cvt8(w.z, w.w, c2);
-      }
+      convert_row(s.raw[rs], reinterpret_cast<uint8_t*>(s.a[as]), r, c_lo, c_hi);
       tc::fence_proxy_async();       // the MMA reads these stores through the async proxy
       tc::mbar_arrive(&s.a_full[as]);
     }
@@ -223,6 +179,7 @@ EXO_API int exo_gemm_fp8w(const void* x, const void* Wq, const void* scale, int 
   if (splits < 1) splits = 1;
   if (splits > kb_total) splits = kb_total;
   p.kb_per_split = (kb_total + splits - 1) / splits;
+  if (splits > 1) p.kb_per_split = (p.kb_per_split + 7) & ~7;     // splits start on a 16-byte boundary of the scale rows
   splits = (kb_total + p.kb_per_split - 1) / p.kb_per_split;
   p.splits = splits;
   p.bias = (const __nv_bfloat16*)bias;
@@ -239,9 +196,10 @@ EXO_API int exo_gemm_fp8w(const void* x, const void* Wq, const void* scale, int 
   sp.kind = scale_kind;
   sp.ld = scale_kind == 1 ? K / 32 : (K + 127) / 128;
   switch (bn) {
-    case 16: return launch_fp8w<16, 8, 3>(tw, tx, p, sp, st);     // 48 + 16 + 64 KB
-    case 32: return launch_fp8w<32, 8, 3>(tw, tx, p, sp, st);     // 48 + 32 + 64 KB
-    case 64: return launch_fp8w<64, 6, 3>(tw, tx, p, sp, st);     // 48 + 48 + 48 KB
+    // decode shapes: two CTAs per SM (eight converter warps hide each other's latencies)
+    case 16: return launch_fp8w<16, 6, 2>(tw, tx, p, sp, st);     // 32 + 12 + 48 KB
+    case 32: return launch_fp8w<32, 6, 2>(tw, tx, p, sp, st);     // 32 + 24 + 48 KB
+    case 64: return launch_fp8w<64, 4, 2>(tw, tx, p, sp, st);     // 32 + 32 + 32 KB
     case 128: return launch_fp8w<128, 4, 3>(tw, tx, p, sp, st);   // 48 + 64 + 32 KB
     default: return launch_fp8w<256, 4, 2>(tw, tx, p, sp, st);    // 32 + 128 + 32 KB
   }

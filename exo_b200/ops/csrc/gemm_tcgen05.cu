@@ -16,6 +16,7 @@
 #include <mutex>
 #include <unordered_map>
 
+#include <cstdlib>
 #include <cstring>
 #include "gemm_common.cuh"
 
@@ -25,9 +26,12 @@ using gemm::BM;
 using gemm::BK;
 using gemm::GemmParams;
 
-template <int BN, int STAGES>
+// TWO: the CTA owns two 128-feature weight tiles (two accumulators) that share every activation
+// tile, so a [256 x 256] output block costs 64 KB of shared-memory traffic per K step instead of
+// 96 KB — the prefill shapes are bound by the L2 -> SM path, not by the tensor pipe.
+template <int BN, int STAGES, bool TWO>
 struct Smem {
-  alignas(1024) __nv_bfloat16 a[STAGES][BM * BK];
+  alignas(1024) __nv_bfloat16 a[STAGES][(TWO ? 2 : 1) * BM * BK];
   alignas(1024) __nv_bfloat16 b[STAGES][BN * BK];
   uint64_t full[STAGES], empty[STAGES], acc_full;
   uint32_t tmem_base;
@@ -35,17 +39,17 @@ struct Smem {
   int is_last;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool TWO>
 __global__ void __launch_bounds__(192, (BN <= 128 ? 2 : 1))
 gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  using S = Smem<BN, STAGES>;
+  using S = Smem<BN, STAGES, TWO>;
   S& s = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-  constexpr uint32_t STAGE_BYTES = (BM * BK + BN * BK) * 2;
+  constexpr uint32_t TMEM_COLS = (TWO ? 2 : 1) * BN < 32 ? 32 : (TWO ? 2 : 1) * BN;
+  constexpr uint32_t STAGE_BYTES = ((TWO ? 2 : 1) * BM * BK + BN * BK) * 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int n0 = blockIdx.x * BM * (TWO ? 2 : 1), m0 = blockIdx.y * BN, split = blockIdx.z;
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
   const int nkb = min(p.kb_per_split, kb_total - kb0);
@@ -81,6 +85,7 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         tc::mbar_expect_tx(&s.full[st], STAGE_BYTES);
         int k = (kb0 + i) * BK;
         tc::tma_load_2d(s.a[st], &tmap_w, k, n0, &s.full[st]);
+        if constexpr (TWO) tc::tma_load_2d(s.a[st] + BM * BK, &tmap_w, k, n0 + BM, &s.full[st]);
         tc::tma_load_2d(s.b[st], &tmap_x, k, m0, &s.full[st]);
       }
     }
@@ -101,14 +106,21 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         uint64_t ad = tc::umma_desc_sw128(tc::smem_u32(s.a[st]));
         uint64_t bd = tc::umma_desc_sw128(tc::smem_u32(s.b[st]));
 #pragma unroll
-        for (int k = 0; k < BK / 16; k++)  // +32 bytes per K step of 16 bf16 → +2 in the >>4 address field
+        for (int k = 0; k < BK / 16; k++) {  // +32 bytes per K step of 16 bf16 → +2 in the >>4 address field
           tc::umma_bf16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) != 0);
+          if constexpr (TWO) {
+            const uint64_t ad2 = tc::umma_desc_sw128(tc::smem_u32(s.a[st] + BM * BK));
+            tc::umma_bf16(tmem + BN, ad2 + 2 * k, bd + 2 * k, idesc, (i | k) != 0);
+          }
+        }
         tc::umma_commit(&s.empty[st]);  // stage reusable once these MMAs have read it
       }
       tc::umma_commit(&s.acc_full);  // accumulator complete (also arrives if we bailed out: nothing pending)
     }
   } else {
     gemm::epilogue<BN>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
+    // second accumulator: plain stores only (the launcher uses TWO without split-K or hand-over)
+    if constexpr (TWO) gemm::epilogue<BN>(p, tmem + BN, &s.acc_full, &s.abort_flag, &s.is_last, n0 + BM, m0, split, nkb, warp, lane);
   }
   // ------------------------------ teardown ------------------------------
   tc::tc_fence_before();
@@ -251,19 +263,20 @@ EXO_API int exo_gemm_last_error() {
   return v;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool TWO = false>
 static int launch_gemm(const CUtensorMap* tw, const CUtensorMap* tx, GemmParams p, cudaStream_t st) {
-  using S = Smem<BN, STAGES>;
+  using S = Smem<BN, STAGES, TWO>;
   size_t smem = sizeof(S) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_swapped_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+    if (cudaFuncSetAttribute(gemm_swapped_kernel<BN, STAGES, TWO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return -3;
     attr_set = true;
   }
-  dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
-  gemm_swapped_kernel<BN, STAGES><<<grid, 192, smem, st>>>(*tw, *tx, p);
+  constexpr int FEATS = BM * (TWO ? 2 : 1);
+  dim3 grid((p.N + FEATS - 1) / FEATS, (p.M + BN - 1) / BN, p.splits);
+  gemm_swapped_kernel<BN, STAGES, TWO><<<grid, 192, smem, st>>>(*tw, *tx, p);
   EXO_CHECK_LAUNCH();
   return 0;
 }
@@ -336,6 +349,9 @@ static int gemm_launch(const void* x, const void* W, const void* bias, const voi
     case 32: return launch_gemm<32, 5>(tw, tx, p, st);   //  5 x 20 KB
     case 64: return launch_gemm<64, 4>(tw, tx, p, st);   //  4 x 24 KB
     case 128: return launch_gemm<128, 3>(tw, tx, p, st); //  3 x 32 KB  (two CTAs per SM)
-    default: return launch_gemm<256, 4>(tw, tx, p, st);  //  4 x 48 KB  (one CTA per SM)
+    default:
+      if (splits == 1 && !ho && N >= 2 * BM && !getenv("EXO_GEMM_SINGLE_TILE"))
+        return launch_gemm<256, 3, true>(tw, tx, p, st);   //  3 x 64 KB, two accumulators (512 TMEM columns)
+      return launch_gemm<256, 4>(tw, tx, p, st);  //  4 x 48 KB  (one CTA per SM)
   }
 }

@@ -44,7 +44,8 @@ __device__ __forceinline__ void bulk_g2s(void* smem, const void* gmem, uint32_t 
                : "memory");
 }
 
-template <int M, int JV, int RB, bool NORM, bool SWIGLU>
+// HO: 0 = plain projection, 1 = its output is handed over to every rank, 2 = its input is a hand-over
+template <int M, int JV, int RB, bool NORM, bool SWIGLU, int HO>
 __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
   const int KS = K / CONSUMER_WARPS;          // this warp's K slice
   const int k_lo = warp * KS, nvec = KS / 8;  // in 16-byte vectors
   pdl_wait();                                 // x comes from the previous kernel
-  if (p.ho.n_part > 0) {
+  if constexpr (HO == 2) {
     // x is handed over by the row-parallel projection of every rank: wait for all of them (bounded)
     if (warp == 0 && lane < p.ho.n_part) tp_wait_flag(p.ho.part_flag[lane], p.ho.status);
     asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
     for (int j = 0; j < JV; j++) {
       const int v = lane + 32 * j;
       if (v < nvec) {
-        if (p.ho.n_part > 0) {
+        if constexpr (HO == 2) {
           // residual + partials in rank order, rounded to bf16: the same bits on every rank and the same
           // value a separate all-reduce would have left in memory
           const size_t off = (size_t)m * K + k_lo + v * 8;
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
     }
   }
   // ---- tensor-parallel hand-over (consumer warps only; the producer warp has returned) ----
-  if (p.ho.n_push > 0) {
+  if constexpr (HO == 1) {
     // y sits in this GPU's memory.  The last CTA to finish copies it into every rank's staging slot with
     // 16-byte peer stores, orders them with ONE system-scope fence and raises the flags (a fence per CTA
     // after scattered 2-byte peer stores measured slower than a separate all-reduce kernel).
@@ -278,7 +279,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
       if (threadIdx.x < p.ho.n_push) tp_red_release_sys_add(p.ho.push_flag[threadIdx.x], 1);
     }
   }
-  if (p.ho.n_part > 0) {
+  if constexpr (HO == 2) {
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (threadIdx.x == 0 && atomicAdd(p.ho.part_ticket, 1) == (int)gridDim.x - 1) {
       *p.ho.part_ticket = 0;                               // every CTA has read the partials: clear for the parity's next use
@@ -293,19 +294,27 @@ int* g_err_stream[16] = {nullptr};
 template <int M, int JV, int RB>
 int launch_stream_rb(const StreamParams& p, bool norm, bool swiglu, int grid, size_t smem, cudaStream_t st) {
   cudaError_t e;
-#define L(NORM, SW)                                                                                              \
+#define L(NORM, SW, HO)                                                                                          \
   {                                                                                                              \
     static bool attr = false;                                                                                    \
     if (!attr) {                                                                                                 \
-      if (cudaFuncSetAttribute(gemv_stream_kernel<M, JV, RB, NORM, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                               200 * 1024) != cudaSuccess)                                                       \
+      if (cudaFuncSetAttribute(gemv_stream_kernel<M, JV, RB, NORM, SW, HO>,                                      \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)          \
         return -3;                                                                                               \
       attr = true;                                                                                               \
     }                                                                                                            \
-    e = launch_pdl(gemv_stream_kernel<M, JV, RB, NORM, SW>, dim3(grid), dim3(THREADS), smem, st, p);              \
+    e = launch_pdl(gemv_stream_kernel<M, JV, RB, NORM, SW, HO>, dim3(grid), dim3(THREADS), smem, st, p);          \
   }
-  if (norm) { if (swiglu) L(true, true) else L(true, false) }
-  else { if (swiglu) L(false, true) else L(false, false) }
+  // The hand-over roles are separate instantiations: a row-parallel projection that pushes its output has
+  // neither norm nor SwiGLU, and a projection that consumes a hand-over always normalises it first.
+  if (p.ho.n_push > 0) {
+    if (norm || swiglu) return -2;
+    L(false, false, 1)
+  } else if (p.ho.n_part > 0) {
+    if (!norm) return -2;
+    if (swiglu) L(true, true, 2) else L(true, false, 2)
+  } else if (norm) { if (swiglu) L(true, true, 0) else L(true, false, 0) }
+  else { if (swiglu) L(false, true, 0) else L(false, false, 0) }
 #undef L
   return (int)e;
 }

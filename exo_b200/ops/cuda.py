@@ -74,7 +74,7 @@ class _Sig:
     exo_moe_tile_rows = (_i, [_i, _i])
     exo_moe_max_tiles = (_i, [_i, _i, _i])
     exo_moe_plan_ints = (_l, [_i, _i])
-    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
+    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p])
     exo_moe_experts_gemv = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
 
 
@@ -382,17 +382,20 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0):
     T, H = x.shape
     E, F2, _ = w_gate_up.shape
     F, k = F2 // 2, ids.shape[1]
-    if (not use_moe_kernels or isinstance(w_gate_up, Fp8Weight) or x.dtype != torch.bfloat16
-            or w_gate_up.dtype != torch.bfloat16 or H % 8 or F % 8
-            or H < 64 or F < 64 or E > 1024):
+    fp8 = isinstance(w_gate_up, Fp8Weight)
+    ok = (use_moe_kernels and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and H % 8 == 0 and F % 8 == 0
+          and H >= 64 and F >= 64 and E <= 1024)
+    if fp8:
+        ok = ok and isinstance(w_down, Fp8Weight) and H % 32 == 0 and F % 32 == 0 and (
+            w_gate_up.kind == "mxfp8" or (F2 % 128 == 0 and H % 128 == 0))
+    if not ok:
         return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
     x, ids = x.contiguous(), ids.contiguous().to(torch.int32)
     weights = weights.contiguous().float()
-    w_gate_up, w_down = w_gate_up.contiguous(), w_down.contiguous()
     out = torch.empty(T, H, dtype=x.dtype, device=x.device)
     P = T * k
     lib = load()
-    if T <= MOE_GEMV_MAX_TOKENS and H * 2 <= 200 * 1024 and k * F * 2 <= 200 * 1024:
+    if not fp8 and T <= MOE_GEMV_MAX_TOKENS and H * 2 <= 200 * 1024 and k * F * 2 <= 200 * 1024:
         hs = torch.empty(P, F, dtype=x.dtype, device=x.device)
         _chk(lib.exo_moe_experts_gemv(_ptr(x), _ptr(w_gate_up), _ptr(w_down), _ptr(weights), _ptr(ids), _ptr(out), _ptr(hs),
                                       T, k, H, F, E, expert_offset, _st()), "moe_experts_gemv")
@@ -405,8 +408,13 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0):
     xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
     hs = torch.empty(P, F, dtype=x.dtype, device=x.device)
     ys = torch.empty(P, H, dtype=x.dtype, device=x.device)
-    _chk(lib.exo_moe_experts_grouped(_ptr(x), _ptr(w_gate_up), _ptr(w_down), _ptr(weights), _ptr(ids), _ptr(out),
+    if fp8:
+        kind = 1 if w_gate_up.kind == "mxfp8" else 2
+        wgu, wd, sgu, sd = w_gate_up.q, w_down.q, w_gate_up.scale, w_down.scale
+    else:
+        kind, wgu, wd, sgu, sd = 0, w_gate_up.contiguous(), w_down.contiguous(), None, None
+    _chk(lib.exo_moe_experts_grouped(_ptr(x), _ptr(wgu), _ptr(wd), _ptr(weights), _ptr(ids), _ptr(out),
                                      _ptr(scratch), _ptr(pos), _ptr(xs), _ptr(hs), _ptr(ys), T, k, H, F, E, expert_offset,
-                                     _st()), "moe_experts_grouped")
+                                     kind, _ptr(sgu), _ptr(sd), _st()), "moe_experts_grouped")
     _count(7)
     return out

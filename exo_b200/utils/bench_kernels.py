@@ -1,6 +1,6 @@
 """Micro-benchmarks of the individual sm_100a kernels against the measured roofline.
 
-    python -m exo_b200.utils.bench_kernels [--only gemv,gemm,attn,prefill] [--peaks MEASURED_PEAKS.json]
+    python -m exo_b200.utils.bench_kernels [--only gemv,gemm,fp8,moe,attn,prefill] [--peaks MEASURED_PEAKS.json]
 
 Every case is timed with CUDA events after warm-up; a 256 MB buffer is overwritten between
 iterations so that no operand survives in the 126 MB L2.  Output: achieved GB/s or TFLOP/s and
@@ -72,11 +72,48 @@ def timeit_rot(fns, reps: int = 0, iters: int = 5) -> float:
     return best
 
 
+def small_cases(only: set[str]) -> None:
+    """One case per section, a few hundred MB on the device, three eager launches each."""
+    from ..ops import quant
+    K.load()
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def rnd(*s):
+        return (torch.randn(*s, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    calls = []
+    if "fp8" in only:
+        x, w = rnd(32, 4096), quant.quantize(rnd(28672, 4096), "mxfp8")
+        calls.append(lambda: K.linear(x, w))
+        x2 = rnd(2048, 4096)
+        calls.append(lambda: K.linear(x2, w))
+    if "gemm" in only:
+        xg, wg = rnd(2048, 4096), rnd(28672, 4096)
+        calls.append(lambda: K.gemm_bf16(xg, wg))
+    if "moe" in only:
+        E_all, E, k, H, F = 128, 16, 8, 4096, 1536
+        wgu, wd = rnd(E, 2 * F, H), rnd(E, H, F)
+        for T in (32, 4096):
+            xm = rnd(T, H)
+            wt, ids = K.moe_route(torch.randn(T, E_all, device="cuda", generator=g), k, "softmax", True, None, 1, 1, 1.0)
+            calls.append(lambda xm=xm, wt=wt, ids=ids: K.moe_experts(xm, wgu, wd, wt, ids, 0))
+    for _ in range(3):
+        for c in calls:
+            c()
+    torch.cuda.synchronize()
+    K.gemm_check()
+    print("small cases done:", len(calls))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="gemv,gemm,attn,prefill,misc")
+    ap.add_argument("--only", default="gemv,gemm,fp8,moe,attn,prefill,misc")
     ap.add_argument("--peaks", default=str(Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"))
+    ap.add_argument("--small", action="store_true",
+                    help="one modest case per section, launched eagerly three times (the form to run under a profiler)")
     a = ap.parse_args()
+    if a.small:
+        small_cases(set(a.only.split(",")))
+        return
     hbm, tf, basis = 6650.0, 1590.0, "fallback"
     try:
         p = json.loads(Path(a.peaks).read_text())
@@ -113,6 +150,40 @@ def main() -> None:
                 fl = 2.0 * M * N * Kd / 1e12
                 print(f"gemm M={M} N={N} K={Kd}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s ({gb / ms * 1e3 / hbm:4.2f})  "
                       f"{fl / ms * 1e3:7.1f} TFLOP/s ({fl / ms * 1e3 / tf:4.2f}) of {basis}")
+        K.gemm_check()
+    if "fp8" in only:
+        # block-scaled fp8 weights (1 byte per weight + 1/32 byte of scale): the roofline is the bytes read
+        from ..ops import quant
+        for M in (1, 32, 64, 2048):
+            for N, Kd in ((6144, 4096), (28672, 4096), (4096, 14336)):
+                x = rnd(M, Kd)
+                copies = max(2, -(-(400 << 20) // (N * Kd)))
+                ws = [quant.quantize(rnd(N, Kd), "mxfp8") for _ in range(copies)]
+                ms = timeit_rot([(lambda w=w: K.linear(x, w)) for w in ws])
+                gb = (N * Kd * (1 + 1 / 32) + (M * Kd + M * N) * 2) / 1e9
+                fl = 2.0 * M * N * Kd / 1e12
+                print(f"gemm-fp8w M={M} N={N} K={Kd}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s ({gb / ms * 1e3 / hbm:4.2f})  "
+                      f"{fl / ms * 1e3:7.1f} TFLOP/s ({fl / ms * 1e3 / tf:4.2f}) of {basis}")
+        K.gemm_check()
+    if "moe" in only:
+        # one rank's share of a Qwen3-235B-A22B layer under EP8: 16 local experts of 128, top-8, H 4096, F 1536
+        E_all, E, k, H, F = 128, 16, 8, 4096, 1536
+        for T in (1, 32, 256, 4096):
+            x = rnd(T, H)
+            logits = torch.randn(T, E_all, device="cuda", generator=g)
+            w, ids = K.moe_route(logits, k, "softmax", True, None, 1, 1, 1.0)
+            copies = max(2, -(-(400 << 20) // (E * 3 * F * H * 2)))
+            ex = [(rnd(E, 2 * F, H), rnd(E, H, F)) for _ in range(copies)]
+            ms = timeit_rot([(lambda a=a, b=b: K.moe_experts(x, a, b, w, ids, 0)) for a, b in ex])
+            local = (ids < E)
+            active = int(torch.unique(ids[local]).numel())
+            pairs = int(local.sum())
+            gb = active * 3 * F * H * 2 / 1e9
+            fl = 2.0 * pairs * 3 * F * H / 1e12
+            print(f"moe-experts T={T} ({pairs} local pairs, {active}/{E} experts): {ms * 1e3:8.1f} us  "
+                  f"{gb / ms * 1e3:7.0f} GB/s ({gb / ms * 1e3 / hbm:4.2f})  {fl / ms * 1e3:7.1f} TFLOP/s ({fl / ms * 1e3 / tf:4.2f}) of {basis}")
+            ms = timeit_rot([(lambda: K.moe_route(logits, k, "softmax", True, None, 1, 1, 1.0)) for _ in range(4)])
+            print(f"moe-route T={T} E={E_all} k={k}: {ms * 1e3:8.1f} us")
         K.gemm_check()
     if "attn" in only:
         Hq, Hkv, D, bs = 32, 8, 128, 16

@@ -77,7 +77,7 @@ def test_gemv_stream(K, M, N, K_):
 
 
 @pytest.mark.parametrize("M,N,K_", [(9, 256, 64), (5, 4096, 4096), (16, 4096, 4096), (32, 6144, 4096), (48, 1024, 14336),
-                                     (100, 384, 512), (128, 4096, 1024), (300, 2048, 4096), (2048, 1536, 2048),
+                                     (100, 384, 512), (128, 4096, 1024), (300, 2048, 4096), (2048, 1536, 2048), (513, 1000, 320), (257, 384, 4096),
                                      (17, 128256 // 8, 4096)])
 def test_gemm_tcgen05(K, M, N, K_):
     g = torch.Generator(device="cuda").manual_seed(2)
@@ -297,3 +297,18 @@ def test_gemm_fp8_weights(K, kind, M, N, K_):
     close(K.linear(x, wq), ref.linear(x.float(), w.bfloat16().float()), 5e-2, 5e-2)
     sw = K.linear(x, quant.quantize(w[: N // 2 * 2].bfloat16(), kind), swiglu_out=True)
     close(sw, ref.swiglu(ref.linear(x, quant.quantize(w[: N // 2 * 2].bfloat16(), kind))), 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("kind", ["mxfp8", "dsfp8"])
+@pytest.mark.parametrize("T,E,k,H,F,offset,E_all", [(2, 8, 2, 256, 128, 0, 8), (300, 16, 8, 512, 384, 32, 64), (1500, 4, 2, 256, 256, 0, 4)])
+def test_moe_experts_fp8(K, kind, T, E, k, H, F, offset, E_all):
+    from exo_b200.ops import quant
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    wgu = quant.quantize((torch.randn(E, 2 * F, H, device="cuda", generator=g) / math.sqrt(H)).bfloat16(), kind)
+    wd = quant.quantize((torch.randn(E, H, F, device="cuda", generator=g) / math.sqrt(F)).bfloat16(), kind)
+    logits = torch.randn(T, E_all, device="cuda", generator=g)
+    w, ids = ref.moe_route(logits, k, "softmax", True)
+    out = K.moe_experts(x, wgu, wd, w, ids, offset)
+    assert K.load().exo_gemm_last_error() == 0
+    close(out, ref.moe_experts(x, wgu, wd, w, ids, offset), 2e-2, 2e-2)
