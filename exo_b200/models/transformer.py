@@ -166,7 +166,7 @@ class Decoder:
         wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, cfg.router, cfg.norm_topk_prob, lw.router_bias,
                                  cfg.n_group, cfg.topk_group, cfg.routed_scaling)
         elo, _ = expert_range(cfg, self.spec)
-        y = ops.moe_experts(x, lw.e_gate_up, lw.e_down, wts, ids, elo)
+        y = ops.moe_experts(x, lw.e_gate_up, lw.e_down, wts, ids, elo, cfg.n_experts)
         if lw.s_gate_up is not None:
             y = ops.linear(ops.linear(x, lw.s_gate_up, swiglu=True), lw.s_down, residual=y)
         return self.comm.all_reduce(y, h)

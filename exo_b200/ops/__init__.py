@@ -94,9 +94,9 @@ def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling
     return ref.moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling)
 
 
-def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0):
+def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None):
     if x.is_cuda:
-        return cuda_ops().moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
+        return cuda_ops().moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, n_experts_total)
     return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
 
 

@@ -32,17 +32,29 @@ __device__ __forceinline__ uint32_t c2_from_f32(float s) {
   return f | (f << 16);
 }
 
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts16(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // Row `r` (0..127) of a raw [128 x 64] byte tile -> row r of a 128-byte-swizzled bf16 [128 x 64] tile.
-// c_lo / c_hi: the multipliers of the row's two 32-weight blocks.
-__device__ __forceinline__ void convert_row(const uint8_t* raw_tile, uint8_t* a_tile, int r, uint32_t c_lo, uint32_t c_hi) {
-  const uint4* src = reinterpret_cast<const uint4*>(raw_tile + r * 64);
-  uint8_t* dst = a_tile + r * 128;
+// c_lo / c_hi: the multipliers of the row's two 32-weight blocks.  `raw_tile` / `a_tile` are
+// shared-memory addresses (cvta'd).  The rows of the raw tile are 64 bytes apart, so the threads of
+// a warp start at different 16-byte pieces of their rows ((q + r/2) mod 4): eight neighbouring
+// threads then touch eight different bank groups.
+__device__ __forceinline__ void convert_row(uint32_t raw_tile, uint32_t a_tile, int r, uint32_t c_lo, uint32_t c_hi) {
+  const uint32_t src = raw_tile + r * 64, dst = a_tile + r * 128;
 #pragma unroll
   for (int q = 0; q < 4; q++) {
-    const uint4 w = src[q];
-    const uint32_t c2 = q < 2 ? c_lo : c_hi;
-    *reinterpret_cast<uint4*>(dst + (((2 * q) ^ (r & 7)) << 4)) = cvt8(w.x, w.y, c2);
-    *reinterpret_cast<uint4*>(dst + (((2 * q + 1) ^ (r & 7)) << 4)) = cvt8(w.z, w.w, c2);
+    const int qq = (q + (r >> 1)) & 3;
+    const uint4 w = lds16(src + qq * 16);
+    const uint32_t c2 = qq < 2 ? c_lo : c_hi;
+    sts16(dst + (((2 * qq) ^ (r & 7)) << 4), cvt8(w.x, w.y, c2));
+    sts16(dst + (((2 * qq + 1) ^ (r & 7)) << 4), cvt8(w.z, w.w, c2));
   }
 }
 

@@ -25,7 +25,9 @@ struct GemmParams {
 };
 
 // Called by the four epilogue warps (threads 64..191) once the MMA warp has committed `acc_full`.
-template <int BN>
+// HO: the output goes to every rank's hand-over slot instead of `out` (a separate instantiation, so that the
+// plain kernel's store loop carries none of it).
+template <int BN, bool HO = false>
 __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uint64_t* acc_full, int* abort_flag,
                                          int* is_last_s, int n0, int m0, int split, int nkb, int warp, int lane) {
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
@@ -51,7 +53,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
               size_t o = (size_t)m * p.ldo + n;
               if (p.residual) y += __bfloat162float(p.residual[o]);
               const __nv_bfloat16 yb = __float2bfloat16_rn(y);
-              if (p.ho.n_push > 0) {
+              if constexpr (HO) {
                 for (int r = 0; r < p.ho.n_push; r++) p.ho.push_dst[r][o] = yb;     // peer stores
               } else {
                 p.out[o] = yb;
@@ -147,7 +149,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
                 float v = y[r][j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
                 if (p.residual) v += __bfloat162float(p.residual[o]);
                 const __nv_bfloat16 yb = __float2bfloat16_rn(v);
-                if (p.ho.n_push > 0) {
+                if constexpr (HO) {
                   for (int rr = 0; rr < p.ho.n_push; rr++) p.ho.push_dst[rr][o] = yb;
                 } else {
                   p.out[o] = yb;
@@ -159,7 +161,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
       }
     }
   // ---- hand-over: when every CTA of the grid is past its stores, raise one flag per rank ----
-  if (p.ho.n_push > 0 && warp >= 2) {
+  if constexpr (HO) {
     __threadfence_system();
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (warp == 2 && lane == 0) {

@@ -130,7 +130,7 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         break;
       }
       tc::tc_fence_after();
-      convert_row(s.raw[rs], reinterpret_cast<uint8_t*>(s.a[as]), r, c_lo, c_hi);
+      convert_row(tc::smem_u32(s.raw[rs]), tc::smem_u32(s.a[as]), r, c_lo, c_hi);
       tc::fence_proxy_async();       // the MMA reads these stores through the async proxy
       tc::mbar_arrive(&s.a_full[as]);
     }

@@ -39,7 +39,7 @@ struct Smem {
   int is_last;
 };
 
-template <int BN, int STAGES, bool TWO>
+template <int BN, int STAGES, bool TWO, bool HO>
 __global__ void __launch_bounds__(192, (BN <= 128 ? 2 : 1))
 gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmParams p) {
@@ -118,7 +118,7 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       tc::umma_commit(&s.acc_full);  // accumulator complete (also arrives if we bailed out: nothing pending)
     }
   } else {
-    gemm::epilogue<BN>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
+    gemm::epilogue<BN, HO>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
     // second accumulator: plain stores only (the launcher uses TWO without split-K or hand-over)
     if constexpr (TWO) gemm::epilogue<BN>(p, tmem + BN, &s.acc_full, &s.abort_flag, &s.is_last, n0 + BM, m0, split, nkb, warp, lane);
   }
@@ -263,22 +263,30 @@ EXO_API int exo_gemm_last_error() {
   return v;
 }
 
-template <int BN, int STAGES, bool TWO = false>
-static int launch_gemm(const CUtensorMap* tw, const CUtensorMap* tx, GemmParams p, cudaStream_t st) {
+template <int BN, int STAGES, bool TWO = false, bool HO = false>
+static int launch_gemm_ho(const CUtensorMap* tw, const CUtensorMap* tx, const GemmParams& p, cudaStream_t st) {
   using S = Smem<BN, STAGES, TWO>;
   size_t smem = sizeof(S) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_swapped_kernel<BN, STAGES, TWO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+    if (cudaFuncSetAttribute(gemm_swapped_kernel<BN, STAGES, TWO, HO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return -3;
     attr_set = true;
   }
   constexpr int FEATS = BM * (TWO ? 2 : 1);
   dim3 grid((p.N + FEATS - 1) / FEATS, (p.M + BN - 1) / BN, p.splits);
-  gemm_swapped_kernel<BN, STAGES, TWO><<<grid, 192, smem, st>>>(*tw, *tx, p);
+  gemm_swapped_kernel<BN, STAGES, TWO, HO><<<grid, 192, smem, st>>>(*tw, *tx, p);
   EXO_CHECK_LAUNCH();
   return 0;
+}
+
+template <int BN, int STAGES, bool TWO = false>
+static int launch_gemm(const CUtensorMap* tw, const CUtensorMap* tx, const GemmParams& p, cudaStream_t st) {
+  if constexpr (!TWO) {
+    if (p.ho.n_push > 0) return launch_gemm_ho<BN, STAGES, false, true>(tw, tx, p, st);
+  }
+  return launch_gemm_ho<BN, STAGES, TWO, false>(tw, tx, p, st);
 }
 
 // Suggested split count for a (M, N, K) problem: fill the 148 SMs when there are few output tiles.
@@ -349,9 +357,14 @@ static int gemm_launch(const void* x, const void* W, const void* bias, const voi
     case 32: return launch_gemm<32, 5>(tw, tx, p, st);   //  5 x 20 KB
     case 64: return launch_gemm<64, 4>(tw, tx, p, st);   //  4 x 24 KB
     case 128: return launch_gemm<128, 3>(tw, tx, p, st); //  3 x 32 KB  (two CTAs per SM)
-    default:
-      if (splits == 1 && !ho && N >= 2 * BM && !getenv("EXO_GEMM_SINGLE_TILE"))
+    default: {
+      // Two accumulators per CTA halve the CTA count and make each ~1.74x as long (measured): take them when
+      // that wins after rounding both to whole waves over the 148 SMs.
+      const long t2 = (long)((N + 2 * BM - 1) / (2 * BM)) * ((M + 255) / 256), t1 = (long)((N + BM - 1) / BM) * ((M + 255) / 256);
+      const bool two_wins = 1.74 * (double)((t2 + 147) / 148) < (double)((t1 + 147) / 148);
+      if (splits == 1 && !ho && N >= 2 * BM && two_wins && !getenv("EXO_GEMM_SINGLE_TILE"))
         return launch_gemm<256, 3, true>(tw, tx, p, st);   //  3 x 64 KB, two accumulators (512 TMEM columns)
       return launch_gemm<256, 4>(tw, tx, p, st);  //  4 x 48 KB  (one CTA per SM)
+    }
   }
 }

@@ -376,8 +376,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           s.abort_flag = 1;
           break;
         }
-        fp8cvt::convert_row(s.raw[st], reinterpret_cast<uint8_t*>(s.a[st]), r, c0, c1);
-        if (DUAL) fp8cvt::convert_row(s.raw[st] + BM * BK, reinterpret_cast<uint8_t*>(s.a[st] + BM * BK), r, d0, d1);
+        fp8cvt::convert_row(tc::smem_u32(s.raw[st]), tc::smem_u32(s.a[st]), r, c0, c1);
+        if (DUAL) fp8cvt::convert_row(tc::smem_u32(s.raw[st]) + BM * BK, tc::smem_u32(s.a[st]) + BM * BK * 2, r, d0, d1);
         tc::fence_proxy_async();
         tc::mbar_arrive(&s.conv[st]);
       }
@@ -586,14 +586,16 @@ EXO_API long exo_moe_plan_ints(int E, int max_tiles) { return 3L * E + 1 + 4L * 
 EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const void* w_down, const void* weights,
                                     const void* ids, void* out, void* scratch, void* pos, void* xs, void* hs, void* ys, int T,
                                     int k, int H, int F, int E, int expert_offset, int scale_kind, const void* scale_gate_up,
-                                    const void* scale_down, cudaStream_t st) {
+                                    const void* scale_down, int tile_rows, cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > 1024 || H % 8 || F % 8 || H < BK || F < BK) return -2;
   if (scale_kind && (H % 32 || F % 32 || (scale_kind == 2 && ((2 * F) % 128 || H % 128)))) return -2;
   int* err = exo_tc_err_ptr();
   if (!err) return -4;
   const int P = T * k;
-  const int bn = exo_moe_tile_rows(P, E), max_tiles = exo_moe_max_tiles(P, E, bn);
+  // tile_rows: 16/32/64/128 chosen by the caller from the pairs it EXPECTS to be local (0 = from all pairs)
+  const int bn = (tile_rows == 16 || tile_rows == 32 || tile_rows == 64 || tile_rows == 128) ? tile_rows : exo_moe_tile_rows(P, E);
+  const int max_tiles = exo_moe_max_tiles(P, E, bn);
   int* counts = (int*)scratch;
   int* offsets = counts + E;
   int* cursor = offsets + E;

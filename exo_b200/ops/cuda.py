@@ -74,7 +74,7 @@ class _Sig:
     exo_moe_tile_rows = (_i, [_i, _i])
     exo_moe_max_tiles = (_i, [_i, _i, _i])
     exo_moe_plan_ints = (_l, [_i, _i])
-    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p])
+    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p])
     exo_moe_experts_gemv = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
 
 
@@ -378,7 +378,7 @@ def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling
     return w, ids
 
 
-def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0):
+def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None):
     T, H = x.shape
     E, F2, _ = w_gate_up.shape
     F, k = F2 // 2, ids.shape[1]
@@ -402,7 +402,8 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0):
         _count(2)
         return out
     ensure_gemm_init(x.device)
-    bn = lib.exo_moe_tile_rows(P, E)
+    # under expert parallelism only E / n_experts_total of the pairs are expected here: size the tiles for those
+    bn = lib.exo_moe_tile_rows(max(1, P * E // max(E, n_experts_total or E)), E)
     scratch = torch.empty(lib.exo_moe_plan_ints(E, lib.exo_moe_max_tiles(P, E, bn)), dtype=torch.int32, device=x.device)
     pos = torch.empty(P, dtype=torch.int32, device=x.device)
     xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
@@ -415,6 +416,6 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0):
         kind, wgu, wd, sgu, sd = 0, w_gate_up.contiguous(), w_down.contiguous(), None, None
     _chk(lib.exo_moe_experts_grouped(_ptr(x), _ptr(wgu), _ptr(wd), _ptr(weights), _ptr(ids), _ptr(out),
                                      _ptr(scratch), _ptr(pos), _ptr(xs), _ptr(hs), _ptr(ys), T, k, H, F, E, expert_offset,
-                                     kind, _ptr(sgu), _ptr(sd), _st()), "moe_experts_grouped")
+                                     kind, _ptr(sgu), _ptr(sd), bn, _st()), "moe_experts_grouped")
     _count(7)
     return out

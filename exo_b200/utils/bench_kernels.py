@@ -95,7 +95,7 @@ def small_cases(only: set[str]) -> None:
         for T in (32, 4096):
             xm = rnd(T, H)
             wt, ids = K.moe_route(torch.randn(T, E_all, device="cuda", generator=g), k, "softmax", True, None, 1, 1, 1.0)
-            calls.append(lambda xm=xm, wt=wt, ids=ids: K.moe_experts(xm, wgu, wd, wt, ids, 0))
+            calls.append(lambda xm=xm, wt=wt, ids=ids: K.moe_experts(xm, wgu, wd, wt, ids, 0, E_all))
     for _ in range(3):
         for c in calls:
             c()
@@ -174,7 +174,7 @@ def main() -> None:
             w, ids = K.moe_route(logits, k, "softmax", True, None, 1, 1, 1.0)
             copies = max(2, -(-(400 << 20) // (E * 3 * F * H * 2)))
             ex = [(rnd(E, 2 * F, H), rnd(E, H, F)) for _ in range(copies)]
-            ms = timeit_rot([(lambda a=a, b=b: K.moe_experts(x, a, b, w, ids, 0)) for a, b in ex])
+            ms = timeit_rot([(lambda a=a, b=b: K.moe_experts(x, a, b, w, ids, 0, E_all)) for a, b in ex])
             local = (ids < E)
             active = int(torch.unique(ids[local]).numel())
             pairs = int(local.sum())

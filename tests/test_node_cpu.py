@@ -79,6 +79,9 @@ def test_two_nodes_place_generate_in_every_dialect_and_delete(cluster_env):
                     return st if ok and len(st["topology"]["connections"]) > 0 else None
                 st = await wait_for(ready)
                 assert (await http.get("/node_id")).json() == ids[0]
+                # the dashboard (one static page that polls /state) is served from the root
+                page = await http.get("/")
+                assert page.status_code == 200 and "exo-b200" in page.text and "/instance/previews" in page.text
                 # previews offer 1- and 2-GPU placements; the tensor one spans both nodes
                 pv = (await http.get("/instance/previews", params={"model_id": "org/tiny"})).json()["previews"]
                 sizes = sorted({len(p["instance"]["NvlinkInstance"]["shardAssignments"]["nodeToRunner"]) for p in pv if p["instance"]})
