@@ -40,6 +40,8 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--no-also", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="pre-flight only: run the first N layers of the model (the JSON line then says so and is not a result)")
     return ap.parse_args()
 
 
@@ -126,6 +128,9 @@ def main() -> None:
     from exo_b200.ops import cuda as K
 
     cfg = preset(args.model)
+    if args.layers:
+        from dataclasses import replace
+        cfg = replace(cfg, n_layers=min(args.layers, cfg.n_layers))
     spec = ShardSpec(tp_rank=rank, tp_size=world)
     comm = None
     comm_name = "none"
@@ -279,7 +284,9 @@ def main() -> None:
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(main_res["dev_ms_per_step"], 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
-            "config": {"model": cfg.name, "global_batch": args.batch, "seq_len": args.prompt,
+            "config": {"model": cfg.name + (f" (REDUCED to {cfg.n_layers} layers: pre-flight, not a result)" if args.layers else ""),
+                       "weights": cfg.quant if cfg.quant != "none" else "bf16",
+                       "global_batch": args.batch, "seq_len": args.prompt,
                        "decode_context": f"{args.prompt}+", "parallelism": f"tp{world}", "comm": comm_name,
                        "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no explicit flush",
                        "kv": "paged, block 16"},

@@ -241,8 +241,7 @@ class ModelWeights:
                 if isinstance(v, torch.Tensor):
                     yield v
                 elif isinstance(v, Fp8Weight):
-                    yield v.q
-                    yield v.scale
+                    yield from v.storage()
 
 
 QUANTIZED_FIELDS = ("wqkv", "wo", "w_gate_up", "w_down", "e_gate_up", "e_down", "s_gate_up", "s_down", "wq_a", "wq_b", "wkv_a")

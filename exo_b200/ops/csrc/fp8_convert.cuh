@@ -58,57 +58,28 @@ __device__ __forceinline__ void convert_row(uint32_t raw_tile, uint32_t a_tile, 
   }
 }
 
-// The multipliers of ONE weight row, handed out K block by K block (64 weights = two 1x32 blocks).
-// The loads run ahead of their use: with e8m0 scales and a 16-byte aligned start, one 16-byte load
-// covers eight K blocks and the next one is issued eight blocks early; otherwise the scales of
-// block i+1 are requested while block i is being converted.  kind 1: e8m0 bytes [rows, ld = K/32];
-// kind 2: fp32 [rows/128, ld = ceil(K/128)].
-struct ScaleStream {
-  const uint8_t* row8;
-  const float* rowf;
-  int kind, kb0, nkb, k32;
-  bool valid, vec;
-  uint4 cur, nxt;
-  uint32_t n_lo, n_hi;
+// Tiled weight storage (see ops/quant.py): every 128x64 block of the matrix is TILE_BYTES
+// consecutive bytes — 8192 e4m3 values row-major, then 256 bytes of scales: 128 rows x 2 e8m0 bytes
+// (kind 1) or one fp32 (kind 2).  A pipeline stage is one bulk copy of a tile.
+constexpr uint32_t TILE_BODY = 128 * 64, TILE_BYTES = TILE_BODY + 256;
 
-  __device__ __forceinline__ void fetch(int kb, uint32_t& lo, uint32_t& hi) const {
-    if (kind == 1) {
-      lo = 2 * kb < k32 ? c2_from_e8m0(__ldg(row8 + 2 * kb)) : 0u;
-      hi = 2 * kb + 1 < k32 ? c2_from_e8m0(__ldg(row8 + 2 * kb + 1)) : 0u;
-    } else {
-      lo = hi = c2_from_f32(__ldg(rowf + (kb >> 1)));
-    }
+__device__ __forceinline__ void bulk_g2s(uint32_t smem, const void* gmem, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem), "l"(gmem), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// multipliers of row r of the tile at shared address `tile`
+__device__ __forceinline__ void tile_scales(uint32_t tile, int kind, int r, uint32_t& c_lo, uint32_t& c_hi) {
+  if (kind == 1) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(tile + TILE_BODY + 2 * r));
+    c_lo = c2_from_e8m0(v & 0xffu);
+    c_hi = c2_from_e8m0((v >> 8) & 0xffu);
+  } else {
+    float f;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(tile + TILE_BODY));
+    c_lo = c_hi = c2_from_f32(f);
   }
-  __device__ __forceinline__ void init(const void* scale, int kind_, int ld, long n, int kb0_, int nkb_, int K, bool valid_) {
-    kind = kind_; kb0 = kb0_; nkb = nkb_; k32 = K / 32; valid = valid_ && nkb_ > 0;
-    row8 = reinterpret_cast<const uint8_t*>(scale) + (size_t)n * ld;
-    rowf = reinterpret_cast<const float*>(scale) + (size_t)(n >> 7) * ld;
-    vec = kind == 1 && (ld & 15) == 0 && (kb0 & 7) == 0 && (K & 63) == 0 && ((reinterpret_cast<uintptr_t>(scale) & 15) == 0);
-    cur = nxt = make_uint4(0, 0, 0, 0);
-    n_lo = n_hi = 0;
-    if (!valid) return;
-    if (vec) cur = __ldg(reinterpret_cast<const uint4*>(row8 + 2 * kb0));
-    else fetch(kb0, n_lo, n_hi);
-  }
-  // multipliers of K block kb0 + i; call with i = 0, 1, 2, ... in order
-  __device__ __forceinline__ void next(int i, uint32_t& c_lo, uint32_t& c_hi) {
-    if (!valid) { c_lo = c_hi = 0; return; }
-    if (vec) {
-      const int j = i & 7;
-      if (j == 0) {
-        if (i) cur = nxt;
-        if (i + 8 < nkb) nxt = __ldg(reinterpret_cast<const uint4*>(row8 + 2 * (kb0 + i + 8)));
-      }
-      const int wsel = j >> 1;
-      const uint32_t w = wsel == 0 ? cur.x : wsel == 1 ? cur.y : wsel == 2 ? cur.z : cur.w;
-      const uint32_t sh = (j & 1) * 16;
-      c_lo = c2_from_e8m0((w >> sh) & 0xffu);
-      c_hi = c2_from_e8m0((w >> (sh + 8)) & 0xffu);
-    } else {
-      c_lo = n_lo; c_hi = n_hi;
-      if (i + 1 < nkb) fetch(kb0 + i + 1, n_lo, n_hi);
-    }
-  }
-};
+}
 
 }  // namespace fp8cvt

@@ -32,7 +32,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
                                          int* is_last_s, int n0, int m0, int split, int nkb, int warp, int lane) {
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
     const int n = n0 + quad * 32 + lane;       // output feature owned by this thread
-    bool ok = tc::mbar_wait(acc_full, 0);
+    bool ok = tc::mbar_wait_backoff(acc_full, 0, 400);
     if (!ok) { atomicExch(p.err, tc::ERR_ACC_TIMEOUT); *abort_flag = 1; }
     tc::tc_fence_after();
     ok = ok && !*(volatile int*)abort_flag && nkb > 0;

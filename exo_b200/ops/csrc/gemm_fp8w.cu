@@ -3,8 +3,9 @@
 //
 // The weight bytes are what decode is bound by, so they cross HBM once, as fp8.  The CTA has the
 // roles of the bf16 GEMM (warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue) and the
-// epilogue warps work during the main loop as well: a TMA ring delivers raw [128 x 64] byte tiles
-// plus the activation tile; thread r of the four warps turns row r of a raw tile into 64 bf16
+// epilogue warps work during the main loop as well: the weights are stored tiled (each 128x64 block
+// contiguous, its scales behind it), so one bulk copy per stage brings a raw tile and its scales as
+// 8448 consecutive DRAM bytes, next to the TMA load of the activation tile; thread r of the four warps turns row r of a raw tile into 64 bf16
 // values — the e4m3 bit pattern is re-based into a bf16 pattern with two logic ops per pair and one
 // packed bf16 multiply applies the block scale together with the exponent re-bias — and stores them
 // in the 128-byte-swizzled layout the MMA reads.  A second, shorter ring holds the converted tiles.
@@ -18,7 +19,6 @@
 #include "fp8_convert.cuh"
 #include "gemm_common.cuh"
 
-const CUtensorMap* exo_tmap_2d_u8(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 int exo_gemm_scratch(int** err, int** counters, float** partial, size_t* partial_floats);
 
 namespace {
@@ -29,16 +29,16 @@ using gemm::GemmParams;
 using namespace fp8cvt;
 
 struct ScaleParams {
-  const void* scale;
-  int kind;      // 1 = e8m0 [N, K/32], 2 = fp32 [ceil(N/128), ld]
-  int ld;        // row pitch of the scale matrix in elements
+  const uint8_t* tiles;   // [ceil(N/128), kt, TILE_BYTES]
+  int kind;               // 1 = e8m0 per 1x32, 2 = fp32 per tile
+  int kt;                 // tiles along K
 };
 
 template <int BN, int RS, int AS>
 struct SmemF {
   alignas(1024) __nv_bfloat16 a[AS][BM * BK];
   alignas(1024) __nv_bfloat16 b[RS][BN * BK];
-  alignas(128) uint8_t raw[RS][BM * BK];
+  alignas(128) uint8_t raw[RS][TILE_BYTES];
   uint64_t raw_full[RS], raw_empty[RS], a_full[AS], a_empty[AS], acc_full;
   uint32_t tmem_base;
   int abort_flag;
@@ -47,13 +47,12 @@ struct SmemF {
 
 template <int BN, int RS, int AS>
 __global__ void __launch_bounds__(192, (BN <= 64 ? 2 : 1))
-gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p,
-                 const ScaleParams sp) {
+gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p, const ScaleParams sp) {
   extern __shared__ uint8_t smem_raw[];
   using S = SmemF<BN, RS, AS>;
   S& s = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-  constexpr uint32_t STAGE_BYTES = BM * BK + BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = TILE_BYTES + BN * BK * 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
   const int kb_total = (p.K + BK - 1) / BK;
@@ -79,8 +78,8 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
   if (warp == 0) {
     if (tc::elect_one()) {
-      tc::prefetch_tmap(&tmap_w);
       tc::prefetch_tmap(&tmap_x);
+      const uint8_t* wt = sp.tiles + ((size_t)blockIdx.x * sp.kt + kb0) * TILE_BYTES;
       for (int i = 0; i < nkb; i++) {
         const int rs = i % RS;
         if (i >= RS && !tc::mbar_wait(&s.raw_empty[rs], ((i / RS) - 1) & 1)) {
@@ -90,7 +89,7 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
         tc::mbar_expect_tx(&s.raw_full[rs], STAGE_BYTES);
         const int k = (kb0 + i) * BK;
-        tc::tma_load_2d(s.raw[rs], &tmap_w, k, n0, &s.raw_full[rs]);
+        bulk_g2s(tc::smem_u32(s.raw[rs]), wt + (size_t)i * TILE_BYTES, TILE_BYTES, tc::smem_u32(&s.raw_full[rs]));
         tc::tma_load_2d(s.b[rs], &tmap_x, k, m0, &s.raw_full[rs]);
       }
     }
@@ -117,19 +116,17 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   } else {
     // ---- converters: row r of every raw tile ----
     const int r = (warp - 2) * 32 + lane;
-    ScaleStream sc;
-    sc.init(sp.scale, sp.kind, sp.ld, n0 + r, kb0, nkb, p.K, n0 + r < p.N);
     for (int i = 0; i < nkb; i++) {
       const int rs = i % RS, as = i % AS;
-      uint32_t c_lo, c_hi;
-      sc.next(i, c_lo, c_hi);
-      if (!tc::mbar_wait(&s.raw_full[rs], (i / RS) & 1) ||
-          (i >= AS && !tc::mbar_wait(&s.a_empty[as], ((i / AS) - 1) & 1))) {
+      if (!tc::mbar_wait_backoff(&s.raw_full[rs], (i / RS) & 1, 32, 1u << 24) ||
+          (i >= AS && !tc::mbar_wait_backoff(&s.a_empty[as], ((i / AS) - 1) & 1, 32, 1u << 24))) {
         atomicExch(p.err, tc::ERR_TILE_TIMEOUT);
         s.abort_flag = 1;
         break;
       }
       tc::tc_fence_after();
+      uint32_t c_lo, c_hi;
+      tile_scales(tc::smem_u32(s.raw[rs]), sp.kind, r, c_lo, c_hi);
       convert_row(tc::smem_u32(s.raw[rs]), tc::smem_u32(s.a[as]), r, c_lo, c_hi);
       tc::fence_proxy_async();       // the MMA reads these stores through the async proxy
       tc::mbar_arrive(&s.a_full[as]);
@@ -145,7 +142,7 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 }
 
 template <int BN, int RS, int AS>
-int launch_fp8w(const CUtensorMap* tw, const CUtensorMap* tx, const GemmParams& p, const ScaleParams& sp, cudaStream_t st) {
+int launch_fp8w(const CUtensorMap* tx, const GemmParams& p, const ScaleParams& sp, cudaStream_t st) {
   using S = SmemF<BN, RS, AS>;
   const size_t smem = sizeof(S) + 1024;
   static bool attr_set = false;
@@ -155,31 +152,29 @@ int launch_fp8w(const CUtensorMap* tw, const CUtensorMap* tx, const GemmParams& 
     attr_set = true;
   }
   dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
-  gemm_fp8w_kernel<BN, RS, AS><<<grid, 192, smem, st>>>(*tw, *tx, p, sp);
+  gemm_fp8w_kernel<BN, RS, AS><<<grid, 192, smem, st>>>(*tx, p, sp);
   EXO_CHECK_LAUNCH();
   return 0;
 }
 
 }  // namespace
 
-// scale_kind: 1 = e8m0 bytes [N, K/32]; 2 = fp32 [ceil(N/128), ceil(K/128)].
-EXO_API int exo_gemm_fp8w(const void* x, const void* Wq, const void* scale, int scale_kind, const void* bias,
+// `tiles`: the weight in the tiled form [ceil(N/128), ceil(K/64), 8448]; scale_kind 1 = e8m0 per 1x32, 2 = fp32 per tile.
+EXO_API int exo_gemm_fp8w(const void* x, const void* tiles, int scale_kind, const void* bias,
                           const void* residual, void* out, int M, int N, int K, int ldo, int splits, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
-  if (K % 32 != 0 || K < BK || (scale_kind != 1 && scale_kind != 2)) return -2;
+  if (K % 8 != 0 || K < BK || (scale_kind != 1 && scale_kind != 2) || ((uintptr_t)tiles & 15)) return -2;
   GemmParams p;
   size_t partial_floats = 0;
   if (exo_gemm_scratch(&p.err, &p.counters, &p.partial, &partial_floats)) return -4;
   const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  const CUtensorMap* tw = exo_tmap_2d_u8(Wq, N, K, BM);
   const CUtensorMap* tx = exo_tmap_2d_bf16(x, M, K, bn);
-  if (!tw || !tx) return -5;
+  if (!tx) return -5;
   p.M = M; p.N = N; p.K = K;
   const int kb_total = (K + BK - 1) / BK;
   if (splits < 1) splits = 1;
   if (splits > kb_total) splits = kb_total;
   p.kb_per_split = (kb_total + splits - 1) / splits;
-  if (splits > 1) p.kb_per_split = (p.kb_per_split + 7) & ~7;     // splits start on a 16-byte boundary of the scale rows
   splits = (kb_total + p.kb_per_split - 1) / p.kb_per_split;
   p.splits = splits;
   p.bias = (const __nv_bfloat16*)bias;
@@ -192,15 +187,15 @@ EXO_API int exo_gemm_fp8w(const void* x, const void* Wq, const void* scale, int 
     if ((size_t)splits * M * N > partial_floats || tiles > (1 << 16)) return -6;
   }
   ScaleParams sp;
-  sp.scale = scale;
+  sp.tiles = (const uint8_t*)tiles;
   sp.kind = scale_kind;
-  sp.ld = scale_kind == 1 ? K / 32 : (K + 127) / 128;
+  sp.kt = kb_total;
   switch (bn) {
     // decode shapes: two CTAs per SM (eight converter warps hide each other's latencies)
-    case 16: return launch_fp8w<16, 6, 2>(tw, tx, p, sp, st);     // 32 + 12 + 48 KB
-    case 32: return launch_fp8w<32, 6, 2>(tw, tx, p, sp, st);     // 32 + 24 + 48 KB
-    case 64: return launch_fp8w<64, 4, 2>(tw, tx, p, sp, st);     // 32 + 32 + 32 KB
-    case 128: return launch_fp8w<128, 4, 3>(tw, tx, p, sp, st);   // 48 + 64 + 32 KB
-    default: return launch_fp8w<256, 4, 2>(tw, tx, p, sp, st);    // 32 + 128 + 32 KB
+    case 16: return launch_fp8w<16, 6, 2>(tx, p, sp, st);     // 32 + 12 + 48 KB
+    case 32: return launch_fp8w<32, 6, 2>(tx, p, sp, st);     // 32 + 24 + 48 KB
+    case 64: return launch_fp8w<64, 4, 2>(tx, p, sp, st);     // 32 + 32 + 32 KB
+    case 128: return launch_fp8w<128, 4, 3>(tx, p, sp, st);   // 48 + 64 + 32 KB
+    default: return launch_fp8w<256, 4, 2>(tx, p, sp, st);    // 32 + 128 + 32 KB
   }
 }

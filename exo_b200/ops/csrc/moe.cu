@@ -26,7 +26,6 @@
 #include "tc_common.cuh"
 
 int* exo_tc_err_ptr();
-const CUtensorMap* exo_tmap_2d_u8(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
 namespace {
 
@@ -255,9 +254,9 @@ struct GroupedParams {
   int K;
   __nv_bfloat16* out;     // [P, n_out]
   int* err;
-  // block-scaled fp8 expert weights (FP8 kernels only): the 2-D view's scales
-  const void* scale;
-  int scale_kind, scale_ld;
+  // block-scaled fp8 expert weights (FP8 kernels only): tiled storage [E, nt, kt, TILE_BYTES] (see fp8_convert.cuh)
+  const uint8_t* tiles;
+  int scale_kind, nt, kt;
 };
 
 // FP8: the weight tiles arrive as bytes in `raw` and the four epilogue warps widen them into `a`
@@ -266,7 +265,7 @@ template <int BN, int STAGES, bool DUAL, bool FP8>
 struct GSmem {
   alignas(1024) __nv_bfloat16 a[STAGES][(DUAL ? 2 : 1) * BM * BK];
   alignas(1024) __nv_bfloat16 b[STAGES][BN * BK];
-  alignas(128) uint8_t raw[FP8 ? STAGES : 1][FP8 ? (DUAL ? 2 : 1) * BM * BK : 128];
+  alignas(128) uint8_t raw[FP8 ? STAGES : 1][FP8 ? (DUAL ? 2 : 1) * fp8cvt::TILE_BYTES : 128];
   uint64_t full[STAGES], empty[STAGES], conv[STAGES], acc_full;
   uint32_t tmem_base;
   int abort_flag;
@@ -282,7 +281,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   S& s = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * BN;
   constexpr uint32_t TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
-  constexpr uint32_t STAGE_BYTES = (DUAL ? 2 : 1) * BM * BK * (FP8 ? 1 : 2) + BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = (DUAL ? 2 : 1) * (FP8 ? fp8cvt::TILE_BYTES : BM * BK * 2) + BN * BK * 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int* tile = p.plan + 1 + 4 * blockIdx.y;
   const int expert = __ldg(tile), row0 = __ldg(tile + 1), rows = __ldg(tile + 2);
@@ -323,8 +322,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         }
         tc::mbar_expect_tx(&s.full[st], STAGE_BYTES);
         if constexpr (FP8) {
-          tc::tma_load_2d(s.raw[st], &tmap_w, i * BK, wrow, &s.full[st]);
-          if (DUAL) tc::tma_load_2d(s.raw[st] + BM * BK, &tmap_w, i * BK, wrow + half, &s.full[st]);
+          // tile (expert, feature tile j, K block i); the up half of a gate/up pair is nt/2 feature tiles further on
+          const uint8_t* t0 = p.tiles + (((size_t)expert * p.nt + blockIdx.x) * p.kt + i) * fp8cvt::TILE_BYTES;
+          fp8cvt::bulk_g2s(tc::smem_u32(s.raw[st]), t0, fp8cvt::TILE_BYTES, tc::smem_u32(&s.full[st]));
+          if (DUAL)
+            fp8cvt::bulk_g2s(tc::smem_u32(s.raw[st]) + fp8cvt::TILE_BYTES, t0 + (size_t)(p.nt / 2) * p.kt * fp8cvt::TILE_BYTES,
+                             fp8cvt::TILE_BYTES, tc::smem_u32(&s.full[st]));
         } else {
           tc::tma_load_2d(s.a[st], &tmap_w, i * BK, wrow, &s.full[st]);
           if (DUAL) tc::tma_load_2d(s.a[st] + BM * BK, &tmap_w, i * BK, wrow + half, &s.full[st]);
@@ -362,29 +365,28 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       // widen row r of every raw tile (both halves of a gate/up stage); the stage's `a` buffers are free because
       // the producer only refilled the stage after the MMAs that read them had completed
       const int r = (warp - 2) * 32 + lane;
-      const bool row_ok = n0 + r < (DUAL ? half : p.rows_w);
-      fp8cvt::ScaleStream sc0, sc1;
-      sc0.init(p.scale, p.scale_kind, p.scale_ld, (long)wrow + r, 0, nkb, p.K, row_ok);
-      sc1.init(p.scale, p.scale_kind, p.scale_ld, (long)wrow + half + r, 0, nkb, p.K, row_ok && DUAL);
       for (int i = 0; i < nkb; i++) {
         const int st = i % STAGES;
-        uint32_t c0, c1, d0 = 0, d1 = 0;
-        sc0.next(i, c0, c1);
-        if (DUAL) sc1.next(i, d0, d1);
-        if (!tc::mbar_wait(&s.full[st], (i / STAGES) & 1)) {
+        if (!tc::mbar_wait_backoff(&s.full[st], (i / STAGES) & 1, 32, 1u << 24)) {
           atomicExch(p.err, tc::ERR_TILE_TIMEOUT);
           s.abort_flag = 1;
           break;
         }
-        fp8cvt::convert_row(tc::smem_u32(s.raw[st]), tc::smem_u32(s.a[st]), r, c0, c1);
-        if (DUAL) fp8cvt::convert_row(tc::smem_u32(s.raw[st]) + BM * BK, tc::smem_u32(s.a[st]) + BM * BK * 2, r, d0, d1);
+        const uint32_t raw0 = tc::smem_u32(s.raw[st]);
+        uint32_t c0, c1;
+        fp8cvt::tile_scales(raw0, p.scale_kind, r, c0, c1);
+        fp8cvt::convert_row(raw0, tc::smem_u32(s.a[st]), r, c0, c1);
+        if (DUAL) {
+          fp8cvt::tile_scales(raw0 + fp8cvt::TILE_BYTES, p.scale_kind, r, c0, c1);
+          fp8cvt::convert_row(raw0 + fp8cvt::TILE_BYTES, tc::smem_u32(s.a[st]) + BM * BK * 2, r, c0, c1);
+        }
         tc::fence_proxy_async();
         tc::mbar_arrive(&s.conv[st]);
       }
     }
     const int quad = warp & 3;
     const int n = n0 + quad * 32 + lane;
-    bool ok = tc::mbar_wait(&s.acc_full, 0);
+    bool ok = tc::mbar_wait_backoff(&s.acc_full, 0, 400);
     if (!ok) { atomicExch(p.err, tc::ERR_ACC_TIMEOUT); s.abort_flag = 1; }
     tc::tc_fence_after();
     ok = ok && !*(volatile int*)&s.abort_flag;
@@ -441,7 +443,7 @@ int launch_grouped(const CUtensorMap* tw, const CUtensorMap* tx, const GroupedPa
 template <bool DUAL>
 int grouped_dispatch(int bn, const CUtensorMap* tw, const CUtensorMap* tx, const GroupedParams& p, int n_tiles_w,
                      int max_tiles, cudaStream_t st) {
-  if (p.scale) {      // fp8 weights: a stage also holds the raw byte tiles
+  if (p.tiles) {      // fp8 weights: a stage also holds the raw byte tiles
     switch (bn) {
       case 16: return launch_grouped<16, 4, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);     // dual: 4 x 50 KB
       case 32: return launch_grouped<32, 4, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);     // dual: 4 x 52 KB
@@ -581,15 +583,14 @@ EXO_API long exo_moe_plan_ints(int E, int max_tiles) { return 3L * E + 1 + 4L * 
 
 // The whole expert block for T tokens (grouped tcgen05 GEMMs).  `scratch` holds exo_moe_plan_ints
 // ints, `pos` P ints, `xs`/`ys` [P, H] and `hs` [P, F] bf16.
-// Block-scaled fp8 experts: `scale_kind` 1 (e8m0 per 1x32) or 2 (fp32 per 128x128) with the scale tensors of the stacked
-// weights; 0 = bf16 weights (scales ignored).
+// Block-scaled fp8 experts: `scale_kind` 1 (e8m0 per 1x32) or 2 (fp32 per tile) and `w_gate_up` / `w_down` in the tiled
+// form [E, 2F/128, H/64, 8448] / [E, ceil(H/128), F/64, 8448]; 0 = bf16 weights.
 EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const void* w_down, const void* weights,
                                     const void* ids, void* out, void* scratch, void* pos, void* xs, void* hs, void* ys, int T,
-                                    int k, int H, int F, int E, int expert_offset, int scale_kind, const void* scale_gate_up,
-                                    const void* scale_down, int tile_rows, cudaStream_t st) {
+                                    int k, int H, int F, int E, int expert_offset, int scale_kind, int tile_rows, cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > 1024 || H % 8 || F % 8 || H < BK || F < BK) return -2;
-  if (scale_kind && (H % 32 || F % 32 || (scale_kind == 2 && ((2 * F) % 128 || H % 128)))) return -2;
+  if (scale_kind && (H % 64 || F % 128)) return -2;      // whole K tiles; gate and up halves on tile boundaries
   int* err = exo_tc_err_ptr();
   if (!err) return -4;
   const int P = T * k;
@@ -606,24 +607,23 @@ EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const 
   moe_scatter_kernel<<<(P + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const int*)ids, P, k, H, expert_offset, E, offsets,
                                                   cursor, (int*)pos, (__nv_bfloat16*)xs);
   EXO_CHECK_LAUNCH();
-  const CUtensorMap* t_wgu = scale_kind ? exo_tmap_2d_u8(w_gate_up, (uint64_t)E * 2 * F, H, BM)
-                                        : exo_tmap_2d_bf16(w_gate_up, (uint64_t)E * 2 * F, H, BM);
   const CUtensorMap* t_xs = exo_tmap_2d_bf16(xs, P, H, bn);
-  const CUtensorMap* t_wd = scale_kind ? exo_tmap_2d_u8(w_down, (uint64_t)E * H, F, BM)
-                                       : exo_tmap_2d_bf16(w_down, (uint64_t)E * H, F, BM);
+  // fp8: the weights are not read through a tensor map (the activations' map stands in for the unused argument)
+  const CUtensorMap* t_wgu = scale_kind ? t_xs : exo_tmap_2d_bf16(w_gate_up, (uint64_t)E * 2 * F, H, BM);
+  const CUtensorMap* t_wd = scale_kind ? t_xs : exo_tmap_2d_bf16(w_down, (uint64_t)E * H, F, BM);
   const CUtensorMap* t_hs = exo_tmap_2d_bf16(hs, P, F, bn);
   if (!t_wgu || !t_xs || !t_wd || !t_hs) return -5;
   GroupedParams g;
   g.plan = plan; g.err = err;
   g.rows_w = 2 * F; g.n_out = F; g.K = H; g.out = (__nv_bfloat16*)hs;
   g.scale_kind = scale_kind;
-  g.scale = scale_kind ? scale_gate_up : nullptr;
-  g.scale_ld = scale_kind == 1 ? H / 32 : (H + 127) / 128;
+  g.tiles = scale_kind ? (const uint8_t*)w_gate_up : nullptr;
+  g.nt = 2 * F / BM; g.kt = H / BK;
   int rc = grouped_dispatch<true>(bn, t_wgu, t_xs, g, (F + BM - 1) / BM, max_tiles, st);
   if (rc) return rc;
   g.rows_w = H; g.n_out = H; g.K = F; g.out = (__nv_bfloat16*)ys;
-  g.scale = scale_kind ? scale_down : nullptr;
-  g.scale_ld = scale_kind == 1 ? F / 32 : (F + 127) / 128;
+  g.tiles = scale_kind ? (const uint8_t*)w_down : nullptr;
+  g.nt = (H + BM - 1) / BM; g.kt = F / BK;
   rc = grouped_dispatch<false>(bn, t_wd, t_hs, g, (H + BM - 1) / BM, max_tiles, st);
   if (rc) return rc;
   moe_combine_kernel<<<T, 256, 0, st>>>((const __nv_bfloat16*)ys, (const int*)pos, (const float*)weights, k, H,

@@ -39,10 +39,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: returns false after `budget` failed polls (each poll may suspend for a
-// hardware-defined time, so the wall-clock bound is of the order of a second).
+// hardware-defined time, so the wall-clock bound is of the order of a second).  The parked form
+// (`try_wait`) is kept on purpose: polling with `test_wait` measured the same on every kernel here
+// and would make the bound depend on the poll rate.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t budget = (1u << 22)) {
   for (uint32_t i = 0; i < budget; i++)
     if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// The same with a sleep between polls, for waits that are long by design (epilogue warps waiting for
+// a whole main loop, converter warps waiting for data): a warp that polls back to back takes issue
+// slots from the TMA-producer and MMA-issuer warps that share its scheduler.  Bounded like the above
+// (budget x (ns + poll) is of the order of seconds).
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, uint32_t ns, uint32_t budget = (1u << 22)) {
+  if (mbar_try_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < budget; i++) {
+    __nanosleep(ns);
+    if (mbar_try_wait(bar, parity)) return true;
+  }
   return false;
 }
 

@@ -16,7 +16,7 @@ from . import reference as ref
 from .quant import Fp8Weight
 
 _lib: C.CDLL | None = None
-_SO = Path(__file__).resolve().parent / "_kernels.so"
+_SO = Path(os.environ.get("EXO_KERNELS_SO") or Path(__file__).resolve().parent / "_kernels.so")     # override: A/B runs of two builds
 
 BF16, F32 = 0, 1
 _DT = {torch.bfloat16: BF16, torch.float32: F32}
@@ -69,12 +69,12 @@ class _Sig:
     exo_gemm_last_error = (_i, [])
     exo_gemm_splits = (_i, [_i, _i, _i])
     exo_gemm_bf16 = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p])
-    exo_gemm_fp8w = (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+    exo_gemm_fp8w = (_i, [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
     exo_moe_route = (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p])
     exo_moe_tile_rows = (_i, [_i, _i])
     exo_moe_max_tiles = (_i, [_i, _i, _i])
     exo_moe_plan_ints = (_l, [_i, _i])
-    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p])
+    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p])
     exo_moe_experts_gemv = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
 
 
@@ -187,7 +187,7 @@ def linear_fp8(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=
     splits = lib.exo_gemm_splits(M, N, K)
     while splits > 1 and splits * M * N > GEMM_PARTIAL_FLOATS:
         splits -= 1
-    _chk(lib.exo_gemm_fp8w(_ptr(x), _ptr(w.q), _ptr(w.scale), 1 if w.kind == "mxfp8" else 2, _ptr(bias), _ptr(residual),
+    _chk(lib.exo_gemm_fp8w(_ptr(x), _ptr(w.to_tiled().tiles), 1 if w.kind == "mxfp8" else 2, _ptr(bias), _ptr(residual),
                            _ptr(out), M, N, K, N, splits, _st()), "gemm_fp8w")
     _count()
     return swiglu(out) if swiglu_out else out
@@ -386,8 +386,7 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_t
     ok = (use_moe_kernels and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and H % 8 == 0 and F % 8 == 0
           and H >= 64 and F >= 64 and E <= 1024)
     if fp8:
-        ok = ok and isinstance(w_down, Fp8Weight) and H % 32 == 0 and F % 32 == 0 and (
-            w_gate_up.kind == "mxfp8" or (F2 % 128 == 0 and H % 128 == 0))
+        ok = ok and isinstance(w_down, Fp8Weight) and H % 64 == 0 and F % 128 == 0
     if not ok:
         return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
     x, ids = x.contiguous(), ids.contiguous().to(torch.int32)
@@ -411,11 +410,11 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_t
     ys = torch.empty(P, H, dtype=x.dtype, device=x.device)
     if fp8:
         kind = 1 if w_gate_up.kind == "mxfp8" else 2
-        wgu, wd, sgu, sd = w_gate_up.q, w_down.q, w_gate_up.scale, w_down.scale
+        wgu, wd = w_gate_up.to_tiled().tiles, w_down.to_tiled().tiles
     else:
-        kind, wgu, wd, sgu, sd = 0, w_gate_up.contiguous(), w_down.contiguous(), None, None
+        kind, wgu, wd = 0, w_gate_up.contiguous(), w_down.contiguous()
     _chk(lib.exo_moe_experts_grouped(_ptr(x), _ptr(wgu), _ptr(wd), _ptr(weights), _ptr(ids), _ptr(out),
                                      _ptr(scratch), _ptr(pos), _ptr(xs), _ptr(hs), _ptr(ys), T, k, H, F, E, expert_offset,
-                                     kind, _ptr(sgu), _ptr(sd), bn, _st()), "moe_experts_grouped")
+                                     kind, bn, _st()), "moe_experts_grouped")
     _count(7)
     return out

@@ -24,40 +24,102 @@ MX_BLOCK = 32
 DS_BLOCK = 128
 
 
+TILE_N, TILE_K = 128, 64
+TILE_TAIL = 256                                   # per-tile scales: 128 rows x 2 e8m0 bytes, or one fp32 + padding
+TILE_BYTES = TILE_N * TILE_K + TILE_TAIL          # 8448: what one pipeline stage of the GEMM copies, contiguous in memory
+
+
 @dataclass
 class Fp8Weight:
-    """A quantised ``[N, K]`` (or stacked ``[E, N, K]``) weight matrix."""
-    q: torch.Tensor          # float8_e4m3fn, same shape as the weight
-    scale: torch.Tensor      # uint8 [..., N, K/32] (mxfp8) or float32 [..., ceil(N/128), ceil(K/128)] (dsfp8)
-    kind: str                # "mxfp8" | "dsfp8"
+    """A quantised ``[N, K]`` (or stacked ``[E, N, K]``) weight matrix.
+
+    Two storage forms.  *Plain*: ``q`` row-major plus ``scale`` (what the packers produce and the
+    CPU definition reads).  *Tiled* (what the GPU kernels stream): ``tiles [..., N/128, K/64, 8448]``
+    bytes — every 128x64 block of the matrix contiguous, followed by its scales — so that a
+    pipeline stage is ONE 8448-byte bulk copy of consecutive DRAM bytes, and the scales arrive in
+    shared memory with the weights.  ``to_tiled()`` converts in place and drops the plain form."""
+    q: torch.Tensor | None          # float8_e4m3fn, same shape as the weight
+    scale: torch.Tensor | None      # uint8 [..., N, K/32] (mxfp8) or float32 [..., ceil(N/128), ceil(K/128)] (dsfp8)
+    kind: str                       # "mxfp8" | "dsfp8"
+    tiles: torch.Tensor | None = None
+    logical_shape: tuple[int, ...] | None = None
 
     @property
     def shape(self) -> torch.Size:
-        return self.q.shape
+        return torch.Size(self.logical_shape) if self.q is None else self.q.shape
 
     @property
     def device(self) -> torch.device:
-        return self.q.device
+        return (self.tiles if self.q is None else self.q).device
 
     @property
     def is_cuda(self) -> bool:
-        return self.q.is_cuda
+        return self.device.type == "cuda"
 
     @property
     def dtype(self) -> torch.dtype:
         return torch.bfloat16
 
+    def storage(self) -> list[torch.Tensor]:
+        return [t for t in (self.q, self.scale, self.tiles) if t is not None]
+
     def nbytes(self) -> int:
-        return self.q.numel() + self.scale.numel() * self.scale.element_size()
+        return sum(t.numel() * t.element_size() for t in self.storage())
 
     def to(self, device) -> "Fp8Weight":
-        return Fp8Weight(self.q.to(device), self.scale.to(device), self.kind)
+        mv = lambda t: None if t is None else t.to(device)      # noqa: E731
+        return Fp8Weight(mv(self.q), mv(self.scale), self.kind, mv(self.tiles), self.logical_shape)
+
+    def to_tiled(self) -> "Fp8Weight":
+        if self.tiles is None:
+            self.logical_shape = tuple(self.q.shape)
+            self.tiles = pack_tiles(self.q, self.scale, self.kind)
+            self.q = self.scale = None
+        return self
+
+    def plain(self) -> tuple[torch.Tensor, torch.Tensor]:
+        if self.q is not None:
+            return self.q, self.scale
+        return unpack_tiles(self.tiles, self.logical_shape, self.kind)
 
     def dequantize(self, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
         return dequantize(self).to(dtype)
 
     def __getitem__(self, i) -> "Fp8Weight":      # one expert of a stacked weight
+        if self.q is None:
+            return Fp8Weight(None, None, self.kind, self.tiles[i], tuple(self.logical_shape[1:]))
         return Fp8Weight(self.q[i], self.scale[i], self.kind)
+
+
+def pack_tiles(q: torch.Tensor, scale: torch.Tensor, kind: str) -> torch.Tensor:
+    """``[..., N, K]`` e4m3 + scales -> ``[..., ceil(N/128), ceil(K/64), 8448]`` bytes (zero padded)."""
+    *lead, N, K = q.shape
+    nt, kt = -(-N // TILE_N), -(-K // TILE_K)
+    qb = torch.zeros(*lead, nt * TILE_N, kt * TILE_K, dtype=torch.uint8, device=q.device)
+    qb[..., :N, :K] = q.view(torch.uint8)
+    body = qb.view(*lead, nt, TILE_N, kt, TILE_K).transpose(-3, -2).reshape(*lead, nt, kt, TILE_N * TILE_K)
+    tail = torch.zeros(*lead, nt, kt, TILE_TAIL, dtype=torch.uint8, device=q.device)
+    if kind == "mxfp8":
+        sb = torch.zeros(*lead, nt * TILE_N, kt * 2, dtype=torch.uint8, device=q.device)
+        sb[..., :N, :K // MX_BLOCK] = scale
+        tail[..., :] = sb.view(*lead, nt, TILE_N, kt, 2).transpose(-3, -2).reshape(*lead, nt, kt, TILE_TAIL)
+    else:
+        per_tile = scale.float()[..., :, torch.arange(kt, device=q.device) // 2]          # [..., nt, kt]
+        tail[..., :4] = per_tile.contiguous().view(torch.uint8).view(*lead, nt, kt, 4)
+    return torch.cat((body, tail), dim=-1).contiguous()
+
+
+def unpack_tiles(tiles: torch.Tensor, shape: tuple[int, ...], kind: str) -> tuple[torch.Tensor, torch.Tensor]:
+    *lead, N, K = shape
+    nt, kt = tiles.shape[-3], tiles.shape[-2]
+    body = tiles[..., :TILE_N * TILE_K].reshape(*lead, nt, kt, TILE_N, TILE_K).transpose(-3, -2)
+    q = body.reshape(*lead, nt * TILE_N, kt * TILE_K)[..., :N, :K].contiguous().view(torch.float8_e4m3fn)
+    tail = tiles[..., TILE_N * TILE_K:]
+    if kind == "mxfp8":
+        sb = tail.reshape(*lead, nt, kt, TILE_N, 2).transpose(-3, -2).reshape(*lead, nt * TILE_N, kt * 2)
+        return q, sb[..., :N, :K // MX_BLOCK].contiguous()
+    per_tile = tail[..., :4].contiguous().view(torch.float32).reshape(*lead, nt, kt)
+    return q, per_tile[..., ::2][..., :-(-K // DS_BLOCK)].contiguous()
 
 
 def _e8m0_to_float(e: torch.Tensor) -> torch.Tensor:
@@ -92,21 +154,25 @@ def quantize_dsfp8(w: torch.Tensor) -> Fp8Weight:
 
 
 def quantize(w: torch.Tensor, kind: str) -> Fp8Weight:
+    """Pack ``w``; on a CUDA device the result is left in the tiled form the kernels stream."""
     if kind == "mxfp8":
-        return quantize_mxfp8(w)
-    if kind == "dsfp8":
-        return quantize_dsfp8(w)
-    raise ValueError(f"unknown quantisation {kind!r}")
+        out = quantize_mxfp8(w)
+    elif kind == "dsfp8":
+        out = quantize_dsfp8(w)
+    else:
+        raise ValueError(f"unknown quantisation {kind!r}")
+    return out.to_tiled() if w.is_cuda else out
 
 
 def dequantize(w: Fp8Weight) -> torch.Tensor:
     """``bf16(e4m3 * scale)`` as float32 values."""
-    *lead, N, K = w.q.shape
-    qf = w.q.float()
+    q, scale = w.plain()
+    *lead, N, K = q.shape
+    qf = q.float()
     if w.kind == "mxfp8":
-        s = _e8m0_to_float(w.scale).repeat_interleave(MX_BLOCK, dim=-1)
+        s = _e8m0_to_float(scale).repeat_interleave(MX_BLOCK, dim=-1)
     else:
-        s = w.scale.repeat_interleave(DS_BLOCK, dim=-2).repeat_interleave(DS_BLOCK, dim=-1)[..., :N, :K]
+        s = scale.repeat_interleave(DS_BLOCK, dim=-2).repeat_interleave(DS_BLOCK, dim=-1)[..., :N, :K]
     return (qf * s).bfloat16().float()
 
 
