@@ -48,13 +48,44 @@ __device__ __forceinline__ void sts16(uint32_t addr, const uint4& v) {
 // threads then touch eight different bank groups.
 __device__ __forceinline__ void convert_row(uint32_t raw_tile, uint32_t a_tile, int r, uint32_t c_lo, uint32_t c_hi) {
   const uint32_t src = raw_tile + r * 64, dst = a_tile + r * 128;
+  const int rot = (r >> 1) & 3;
+  // all loads first, all stores last: the 32 independent pair conversions in between can then be interleaved by
+  // the compiler (one warp per scheduler converts, so its own instruction-level parallelism is what hides latency)
+  uint4 w[4], o[8];
+#pragma unroll
+  for (int q = 0; q < 4; q++) w[q] = lds16(src + ((q + rot) & 3) * 16);
 #pragma unroll
   for (int q = 0; q < 4; q++) {
-    const int qq = (q + (r >> 1)) & 3;
-    const uint4 w = lds16(src + qq * 16);
-    const uint32_t c2 = qq < 2 ? c_lo : c_hi;
-    sts16(dst + (((2 * qq) ^ (r & 7)) << 4), cvt8(w.x, w.y, c2));
-    sts16(dst + (((2 * qq + 1) ^ (r & 7)) << 4), cvt8(w.z, w.w, c2));
+    const uint32_t c2 = ((q + rot) & 3) < 2 ? c_lo : c_hi;
+    o[2 * q] = cvt8(w[q].x, w[q].y, c2);
+    o[2 * q + 1] = cvt8(w[q].z, w[q].w, c2);
+  }
+#pragma unroll
+  for (int q = 0; q < 4; q++) {
+    const int qq = (q + rot) & 3;
+    sts16(dst + (((2 * qq) ^ (r & 7)) << 4), o[2 * q]);
+    sts16(dst + (((2 * qq + 1) ^ (r & 7)) << 4), o[2 * q + 1]);
+  }
+}
+
+// Half a row: bytes [32h, 32h + 32) of row r -> chunks 4h .. 4h+3 of the swizzled bf16 row, all under
+// one multiplier.  Two threads per row (256 converter threads per tile) halve the per-thread chain.
+__device__ __forceinline__ void convert_half_row(uint32_t raw_tile, uint32_t a_tile, int r, int h, uint32_t c2) {
+  const uint32_t src = raw_tile + r * 64 + h * 32, dst = a_tile + r * 128;
+  const int rot = (r >> 1) & 1;
+  uint4 w[2], o[4];
+#pragma unroll
+  for (int q = 0; q < 2; q++) w[q] = lds16(src + ((q + rot) & 1) * 16);
+#pragma unroll
+  for (int q = 0; q < 2; q++) {
+    o[2 * q] = cvt8(w[q].x, w[q].y, c2);
+    o[2 * q + 1] = cvt8(w[q].z, w[q].w, c2);
+  }
+#pragma unroll
+  for (int q = 0; q < 2; q++) {
+    const int qq = 2 * h + ((q + rot) & 1);
+    sts16(dst + (((2 * qq) ^ (r & 7)) << 4), o[2 * q]);
+    sts16(dst + (((2 * qq + 1) ^ (r & 7)) << 4), o[2 * q + 1]);
   }
 }
 

@@ -2,8 +2,8 @@
 //   out[M, N] = x[M, K] . bf16(Wq[N, K] * scale)^T  (+bias)(+residual)
 //
 // The weight bytes are what decode is bound by, so they cross HBM once, as fp8.  The CTA has the
-// roles of the bf16 GEMM (warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue) and the
-// epilogue warps work during the main loop as well: the weights are stored tiled (each 128x64 block
+// roles of the bf16 GEMM (warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue) plus four
+// more warps; warps 2..9 work during the main loop as converters (two threads per weight row): the weights are stored tiled (each 128x64 block
 // contiguous, its scales behind it), so one bulk copy per stage brings a raw tile and its scales as
 // 8448 consecutive DRAM bytes, next to the TMA load of the activation tile; thread r of the four warps turns row r of a raw tile into 64 bf16
 // values — the e4m3 bit pattern is re-based into a bf16 pattern with two logic ops per pair and one
@@ -14,6 +14,7 @@
 // The accumulator read-back, split-K and hand-over epilogue is the bf16 kernel's.
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "fp8_convert.cuh"
@@ -46,7 +47,7 @@ struct SmemF {
 };
 
 template <int BN, int RS, int AS>
-__global__ void __launch_bounds__(192, (BN <= 64 ? 2 : 1))
+__global__ void __launch_bounds__(320, (BN <= 64 ? 2 : 1))
 gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p, const ScaleParams sp) {
   extern __shared__ uint8_t smem_raw[];
   using S = SmemF<BN, RS, AS>;
@@ -61,7 +62,7 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p,
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < RS; i++) { tc::mbar_init(&s.raw_full[i], 1); tc::mbar_init(&s.raw_empty[i], 1); }
-    for (int i = 0; i < AS; i++) { tc::mbar_init(&s.a_full[i], 128); tc::mbar_init(&s.a_empty[i], 1); }
+    for (int i = 0; i < AS; i++) { tc::mbar_init(&s.a_full[i], 256); tc::mbar_init(&s.a_empty[i], 1); }
     tc::mbar_init(&s.acc_full, 1);
     s.abort_flag = 0;
     s.is_last = 0;
@@ -114,8 +115,8 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p,
       tc::umma_commit(&s.acc_full);
     }
   } else {
-    // ---- converters: row r of every raw tile ----
-    const int r = (warp - 2) * 32 + lane;
+    // ---- converters: thread c of 256 takes half h = c / 128 of row r = c % 128 of every raw tile ----
+    const int c = threadIdx.x - 64, r = c & 127, h = c >> 7;
     for (int i = 0; i < nkb; i++) {
       const int rs = i % RS, as = i % AS;
       if (!tc::mbar_wait_backoff(&s.raw_full[rs], (i / RS) & 1, 32, 1u << 24) ||
@@ -127,10 +128,11 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p,
       tc::tc_fence_after();
       uint32_t c_lo, c_hi;
       tile_scales(tc::smem_u32(s.raw[rs]), sp.kind, r, c_lo, c_hi);
-      convert_row(tc::smem_u32(s.raw[rs]), tc::smem_u32(s.a[as]), r, c_lo, c_hi);
+      convert_half_row(tc::smem_u32(s.raw[rs]), tc::smem_u32(s.a[as]), r, h, h ? c_hi : c_lo);
       tc::fence_proxy_async();       // the MMA reads these stores through the async proxy
       tc::mbar_arrive(&s.a_full[as]);
     }
+    if (warp < 6)     // warps 2..5 own the four TMEM lane quadrants
     gemm::epilogue<BN>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
   }
   tc::tc_fence_before();
@@ -139,6 +141,171 @@ gemm_fp8w_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p,
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, TMEM_COLS);
   }
+}
+
+// ---- A operand in tensor memory -----------------------------------------------------------------
+// The widened weights need not go back through shared memory: the MMA can take its A operand from
+// tensor memory (row i of the [128 x 16] operand on lane i, two bf16 per 32-bit column), which is
+// exactly how the converter threads hold them — thread (quadrant, lane) owns weight row
+// 32*quadrant + lane.  So a converter loads its half row from the raw tile, widens it in registers
+// and writes 16 columns with one tcgen05.st; no swizzled store, no proxy fence, and the MMA reads
+// only the activation tile from shared memory.  Per K block the shared-memory traffic drops from
+// ~57 KB to ~24 KB (BN = 32), which is what bounded the shared-memory form.
+template <int BN, int RS>
+struct SmemFT {
+  alignas(1024) __nv_bfloat16 b[RS][BN * BK];
+  alignas(128) uint8_t raw[RS][TILE_BYTES];
+  uint64_t raw_full[RS], raw_empty[RS], a_full[4], a_empty[4], acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+};
+
+__device__ __forceinline__ void tmem_st16u(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"((uint32_t)acc)
+      : "memory");
+}
+
+template <int BN, int RS>
+__global__ void __launch_bounds__(320, (BN <= 64 ? 2 : 1))
+gemm_fp8w_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p, const ScaleParams sp) {
+  extern __shared__ uint8_t smem_raw[];
+  using S = SmemFT<BN, RS>;
+  S& s = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int AS = 4;                                    // A stages in tensor memory, 32 columns each
+  constexpr uint32_t A_COL = BN < 32 ? 32 : BN;            // accumulator first, then the A ring
+  constexpr uint32_t NEED = A_COL + AS * 32;
+  constexpr uint32_t TMEM_COLS = NEED <= 64 ? 64 : NEED <= 128 ? 128 : NEED <= 256 ? 256 : 512;
+  constexpr uint32_t STAGE_BYTES = TILE_BYTES + BN * BK * 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb0 = split * p.kb_per_split;
+  const int nkb = min(p.kb_per_split, kb_total - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < RS; i++) {
+      tc::mbar_init(&s.raw_full[i], 1);
+      tc::mbar_init(&s.raw_empty[i], 1);
+    }
+    for (int i = 0; i < AS; i++) { tc::mbar_init(&s.a_full[i], 256); tc::mbar_init(&s.a_empty[i], 1); }
+    tc::mbar_init(&s.acc_full, 1);
+    s.abort_flag = 0;
+    s.is_last = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+
+  if (warp == 0) {
+    if (tc::elect_one()) {
+      tc::prefetch_tmap(&tmap_x);
+      const uint8_t* wt = sp.tiles + ((size_t)blockIdx.x * sp.kt + kb0) * TILE_BYTES;
+      for (int i = 0; i < nkb; i++) {
+        const int rs = i % RS;
+        if (i >= RS && !tc::mbar_wait(&s.raw_empty[rs], ((i / RS) - 1) & 1)) {
+          atomicExch(p.err, tc::ERR_EMPTY_TIMEOUT);
+          s.abort_flag = 1;
+          break;
+        }
+        tc::mbar_expect_tx(&s.raw_full[rs], STAGE_BYTES);
+        bulk_g2s(tc::smem_u32(s.raw[rs]), wt + (size_t)i * TILE_BYTES, TILE_BYTES, tc::smem_u32(&s.raw_full[rs]));
+        tc::tma_load_2d(s.b[rs], &tmap_x, (kb0 + i) * BK, m0, &s.raw_full[rs]);
+      }
+    }
+  } else if (warp == 1) {
+    if (tc::elect_one()) {
+      constexpr uint32_t idesc = tc::umma_idesc_bf16(BM, BN);
+      for (int i = 0; i < nkb; i++) {
+        const int rs = i % RS, as = i % AS;
+        if (!tc::mbar_wait(&s.a_full[as], (i / AS) & 1) || !tc::mbar_wait(&s.raw_full[rs], (i / RS) & 1)) {
+          atomicExch(p.err, tc::ERR_FULL_TIMEOUT);
+          s.abort_flag = 1;
+          break;
+        }
+        tc::tc_fence_after();
+        const uint64_t bd = tc::umma_desc_sw128(tc::smem_u32(s.b[rs]));
+        const uint32_t a_t = tmem + A_COL + as * 32;
+#pragma unroll
+        for (int k = 0; k < BK / 16; k++) umma_bf16_ts(tmem, a_t + 8 * k, bd + 2 * k, idesc, (i | k) != 0);
+        tc::umma_commit(&s.a_empty[as]);
+        tc::umma_commit(&s.raw_empty[rs]);   // the raw bytes were consumed before a_full; the activation tile only now
+      }
+      tc::umma_commit(&s.acc_full);
+    }
+  } else {
+    // converters: warp w works on lane quadrant w % 4 (the only TMEM lanes it may touch); warps 2..5 take the first
+    // 32 weights of their rows' K block, warps 6..9 the second 32
+    const int quad = warp & 3, h = (warp - 2) >> 2, r = quad * 32 + lane;
+    const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16) + A_COL + 16 * h;
+    for (int i = 0; i < nkb; i++) {
+      const int rs = i % RS, as = i % AS;
+      if (!tc::mbar_wait_backoff(&s.raw_full[rs], (i / RS) & 1, 32, 1u << 24) ||
+          (i >= AS && !tc::mbar_wait_backoff(&s.a_empty[as], ((i / AS) - 1) & 1, 32, 1u << 24))) {
+        atomicExch(p.err, tc::ERR_TILE_TIMEOUT);
+        s.abort_flag = 1;
+        break;
+      }
+      tc::tc_fence_after();
+      const uint32_t raw = tc::smem_u32(s.raw[rs]);
+      uint32_t c_lo, c_hi;
+      tile_scales(raw, sp.kind, r, c_lo, c_hi);
+      const uint32_t c2 = h ? c_hi : c_lo;
+      const uint4 w0 = lds16(raw + r * 64 + h * 32 + ((r >> 1) & 1) * 16);
+      const uint4 w1 = lds16(raw + r * 64 + h * 32 + (((r >> 1) & 1) ^ 1) * 16);
+      const uint4 lo = ((r >> 1) & 1) ? w1 : w0, hi = ((r >> 1) & 1) ? w0 : w1;     // bytes 0..15 / 16..31 of the half row
+      uint32_t o[16];
+      const uint4 o0 = cvt8(lo.x, lo.y, c2), o1 = cvt8(lo.z, lo.w, c2), o2 = cvt8(hi.x, hi.y, c2), o3 = cvt8(hi.z, hi.w, c2);
+      o[0] = o0.x; o[1] = o0.y; o[2] = o0.z; o[3] = o0.w; o[4] = o1.x; o[5] = o1.y; o[6] = o1.z; o[7] = o1.w;
+      o[8] = o2.x; o[9] = o2.y; o[10] = o2.z; o[11] = o2.w; o[12] = o3.x; o[13] = o3.y; o[14] = o3.z; o[15] = o3.w;
+      tmem_st16u(lane_base + as * 32, o);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      tc::tc_fence_before();
+      tc::mbar_arrive(&s.a_full[as]);
+    }
+    if (warp < 6)     // warps 2..5 own the four TMEM lane quadrants of the accumulator
+      gemm::epilogue<BN>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+template <int BN, int RS>
+int launch_fp8w_ta(const CUtensorMap* tx, const GemmParams& p, const ScaleParams& sp, cudaStream_t st) {
+  using S = SmemFT<BN, RS>;
+  const size_t smem = sizeof(S) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_fp8w_ta_kernel<BN, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
+  gemm_fp8w_ta_kernel<BN, RS><<<grid, 320, smem, st>>>(*tx, p, sp);
+  EXO_CHECK_LAUNCH();
+  return 0;
 }
 
 template <int BN, int RS, int AS>
@@ -152,7 +319,7 @@ int launch_fp8w(const CUtensorMap* tx, const GemmParams& p, const ScaleParams& s
     attr_set = true;
   }
   dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
-  gemm_fp8w_kernel<BN, RS, AS><<<grid, 192, smem, st>>>(*tx, p, sp);
+  gemm_fp8w_kernel<BN, RS, AS><<<grid, 320, smem, st>>>(*tx, p, sp);
   EXO_CHECK_LAUNCH();
   return 0;
 }
@@ -190,6 +357,17 @@ EXO_API int exo_gemm_fp8w(const void* x, const void* tiles, int scale_kind, cons
   sp.tiles = (const uint8_t*)tiles;
   sp.kind = scale_kind;
   sp.kt = kb_total;
+  static int smem_a = -1;
+  if (smem_a < 0) { const char* e = getenv("EXO_FP8_SMEM_A"); smem_a = (e && e[0] == '1') ? 1 : 0; }
+  if (!smem_a) {      // A operand from tensor memory (default); EXO_FP8_SMEM_A=1 selects the shared-memory form below
+    switch (bn) {
+      case 16: return launch_fp8w_ta<16, 8>(tx, p, sp, st);     // 8 x (8.25 + 2) KB
+      case 32: return launch_fp8w_ta<32, 8>(tx, p, sp, st);     // 8 x (8.25 + 4) KB
+      case 64: return launch_fp8w_ta<64, 6>(tx, p, sp, st);     // 6 x (8.25 + 8) KB
+      case 128: return launch_fp8w_ta<128, 6>(tx, p, sp, st);   // 6 x (8.25 + 16) KB
+      default: return launch_fp8w_ta<256, 4>(tx, p, sp, st);    // 4 x (8.25 + 32) KB
+    }
+  }
   switch (bn) {
     // decode shapes: two CTAs per SM (eight converter warps hide each other's latencies)
     case 16: return launch_fp8w<16, 6, 2>(tx, p, sp, st);     // 32 + 12 + 48 KB

@@ -272,7 +272,7 @@ struct GSmem {
 };
 
 template <int BN, int STAGES, bool DUAL, bool FP8>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(FP8 ? 320 : 192, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                         const GroupedParams p) {
   if ((int)blockIdx.y >= __ldg(p.plan)) return;     // past the last tile of this step: uniform exit, nothing held
@@ -293,7 +293,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     for (int i = 0; i < STAGES; i++) {
       tc::mbar_init(&s.full[i], 1);
       tc::mbar_init(&s.empty[i], 1);
-      tc::mbar_init(&s.conv[i], 128);
+      tc::mbar_init(&s.conv[i], 256);
     }
     tc::mbar_init(&s.acc_full, 1);
     s.abort_flag = 0;
@@ -362,9 +362,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
   } else {
     if constexpr (FP8) {
-      // widen row r of every raw tile (both halves of a gate/up stage); the stage's `a` buffers are free because
-      // the producer only refilled the stage after the MMAs that read them had completed
-      const int r = (warp - 2) * 32 + lane;
+      // 256 converter threads (warps 2..9): for a gate/up stage the first 128 widen the gate tile and the others the up
+      // tile, a row each; otherwise two threads share a row.  The stage's `a` buffers are free because the producer
+      // only refilled the stage after the MMAs that read them had completed.
+      const int c = threadIdx.x - 64, r = c & 127, g = c >> 7;
       for (int i = 0; i < nkb; i++) {
         const int st = i % STAGES;
         if (!tc::mbar_wait_backoff(&s.full[st], (i / STAGES) & 1, 32, 1u << 24)) {
@@ -372,18 +373,17 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           s.abort_flag = 1;
           break;
         }
-        const uint32_t raw0 = tc::smem_u32(s.raw[st]);
+        const uint32_t raw0 = tc::smem_u32(s.raw[st]) + (DUAL ? g * fp8cvt::TILE_BYTES : 0);
+        const uint32_t a0 = tc::smem_u32(s.a[st]) + (DUAL ? g * BM * BK * 2 : 0);
         uint32_t c0, c1;
         fp8cvt::tile_scales(raw0, p.scale_kind, r, c0, c1);
-        fp8cvt::convert_row(raw0, tc::smem_u32(s.a[st]), r, c0, c1);
-        if (DUAL) {
-          fp8cvt::tile_scales(raw0 + fp8cvt::TILE_BYTES, p.scale_kind, r, c0, c1);
-          fp8cvt::convert_row(raw0 + fp8cvt::TILE_BYTES, tc::smem_u32(s.a[st]) + BM * BK * 2, r, c0, c1);
-        }
+        if (DUAL) fp8cvt::convert_row(raw0, a0, r, c0, c1);
+        else fp8cvt::convert_half_row(raw0, a0, r, g, g ? c1 : c0);
         tc::fence_proxy_async();
         tc::mbar_arrive(&s.conv[st]);
       }
     }
+    if (!FP8 || warp < 6) {       // warps 2..5 own the four TMEM lane quadrants
     const int quad = warp & 3;
     const int n = n0 + quad * 32 + lane;
     bool ok = tc::mbar_wait_backoff(&s.acc_full, 0, 400);
@@ -414,6 +414,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         }
       }
     }
+    }
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -435,7 +436,7 @@ int launch_grouped(const CUtensorMap* tw, const CUtensorMap* tx, const GroupedPa
       return -3;
     attr_set = true;
   }
-  moe_grouped_gemm_kernel<BN, STAGES, DUAL, FP8><<<dim3(n_tiles_w, max_tiles), 192, smem, st>>>(*tw, *tx, p);
+  moe_grouped_gemm_kernel<BN, STAGES, DUAL, FP8><<<dim3(n_tiles_w, max_tiles), FP8 ? 320 : 192, smem, st>>>(*tw, *tx, p);
   EXO_CHECK_LAUNCH();
   return 0;
 }
