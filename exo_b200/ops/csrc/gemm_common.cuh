@@ -175,4 +175,36 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
   }
 }
 
+// Gate/up pair: accumulator 0 holds the gate rows [n0, n0+128), accumulator 1 (BN columns further on) the up rows of
+// the same features; writes silu(gate) * up to out[M, F] (ldo = F).  Each projection is rounded to bf16 before
+// the activation, as the unfused form (GEMM, then the SwiGLU kernel) does.
+template <int BN>
+__device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, uint32_t tmem, uint64_t* acc_full, int* abort_flag, int n0,
+                                                int m0, int nkb, int warp, int lane) {
+  const int quad = warp & 3;
+  const int n = n0 + quad * 32 + lane, F = p.N / 2;
+  bool ok = tc::mbar_wait_backoff(acc_full, 0, 400);
+  if (!ok) { atomicExch(p.err, tc::ERR_ACC_TIMEOUT); *abort_flag = 1; }
+  tc::tc_fence_after();
+  ok = ok && !*(volatile int*)abort_flag && nkb > 0;
+  const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 16) {
+    float g[16], u[16];
+    tc::tmem_ld16(taddr + c, g);
+    tc::tmem_ld16(taddr + BN + c, u);
+    tc::tmem_ld_wait();
+    if (ok && n < F) {
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        const int m = m0 + c + j;
+        if (m < p.M) {
+          const float gb = __bfloat162float(__float2bfloat16_rn(g[j])), ub = __bfloat162float(__float2bfloat16_rn(u[j]));
+          p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(silu_f(gb) * ub);
+        }
+      }
+    }
+  }
+}
+
 }  // namespace gemm

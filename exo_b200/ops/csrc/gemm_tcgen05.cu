@@ -39,7 +39,9 @@ struct Smem {
   int is_last;
 };
 
-template <int BN, int STAGES, bool TWO, bool HO>
+// GLU (with TWO): the two weight tiles are the gate rows and the up rows of the same 128 features of a fused
+// [gate; up] matrix and the epilogue writes silu(gate) * up — the SwiGLU kernel and its traffic disappear.
+template <int BN, int STAGES, bool TWO, bool HO, bool GLU = false>
 __global__ void __launch_bounds__(192, (BN <= 128 ? 2 : 1))
 gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmParams p) {
@@ -49,7 +51,8 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   constexpr uint32_t TMEM_COLS = (TWO ? 2 : 1) * BN < 32 ? 32 : (TWO ? 2 : 1) * BN;
   constexpr uint32_t STAGE_BYTES = ((TWO ? 2 : 1) * BM * BK + BN * BK) * 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM * (TWO ? 2 : 1), m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int n0 = blockIdx.x * BM * ((TWO && !GLU) ? 2 : 1), m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int second = GLU ? p.N / 2 : BM;      // row distance of the second weight tile
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
   const int nkb = min(p.kb_per_split, kb_total - kb0);
@@ -85,7 +88,7 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         tc::mbar_expect_tx(&s.full[st], STAGE_BYTES);
         int k = (kb0 + i) * BK;
         tc::tma_load_2d(s.a[st], &tmap_w, k, n0, &s.full[st]);
-        if constexpr (TWO) tc::tma_load_2d(s.a[st] + BM * BK, &tmap_w, k, n0 + BM, &s.full[st]);
+        if constexpr (TWO) tc::tma_load_2d(s.a[st] + BM * BK, &tmap_w, k, n0 + second, &s.full[st]);
         tc::tma_load_2d(s.b[st], &tmap_x, k, m0, &s.full[st]);
       }
     }
@@ -118,9 +121,13 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       tc::umma_commit(&s.acc_full);  // accumulator complete (also arrives if we bailed out: nothing pending)
     }
   } else {
+    if constexpr (GLU) {
+      gemm::epilogue_swiglu<BN>(p, tmem, &s.acc_full, &s.abort_flag, n0, m0, nkb, warp, lane);
+    } else {
     gemm::epilogue<BN, HO>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
     // second accumulator: plain stores only (the launcher uses TWO without split-K or hand-over)
     if constexpr (TWO) gemm::epilogue<BN>(p, tmem + BN, &s.acc_full, &s.abort_flag, &s.is_last, n0 + BM, m0, split, nkb, warp, lane);
+    }
   }
   // ------------------------------ teardown ------------------------------
   tc::tc_fence_before();
@@ -281,6 +288,22 @@ static int launch_gemm_ho(const CUtensorMap* tw, const CUtensorMap* tx, const Ge
   return 0;
 }
 
+static int launch_gemm_glu(const CUtensorMap* tw, const CUtensorMap* tx, const GemmParams& p, cudaStream_t st) {
+  using S = Smem<256, 3, true>;
+  const size_t smem = sizeof(S) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_swapped_kernel<256, 3, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  dim3 grid((p.N / 2 + BM - 1) / BM, (p.M + 255) / 256, 1);
+  gemm_swapped_kernel<256, 3, true, false, true><<<grid, 192, smem, st>>>(*tw, *tx, p);
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
 template <int BN, int STAGES, bool TWO = false>
 static int launch_gemm(const CUtensorMap* tw, const CUtensorMap* tx, const GemmParams& p, cudaStream_t st) {
   if constexpr (!TWO) {
@@ -310,6 +333,27 @@ static int gemm_launch(const void* x, const void* W, const void* bias, const voi
 EXO_API int exo_gemm_bf16(const void* x, const void* W, const void* bias, const void* residual, void* out, int M, int N,
                           int K, int ldo, int splits, cudaStream_t st) {
   return gemm_launch(x, W, bias, residual, out, M, N, K, ldo, splits, nullptr, st);
+}
+
+// Fused gate/up projection with the SwiGLU in the epilogue: W = [gate (F rows); up (F rows)], out[M, F].
+// Prefill shapes only (M >= 256, no bias): returns -2 otherwise and the caller takes the two-kernel form.
+EXO_API int exo_gemm_bf16_swiglu(const void* x, const void* W, void* out, int M, int N, int K, cudaStream_t st) {
+  if (M < 256 || (N & 1) || K % 8 != 0 || K < BK) return -2;
+  int dev;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !g_err[dev]) return -4;
+  const CUtensorMap* tw = exo_tmap_2d_bf16(W, N, K, BM);
+  const CUtensorMap* tx = exo_tmap_2d_bf16(x, M, K, 256);
+  if (!tw || !tx) return -5;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K;
+  p.kb_per_split = (K + BK - 1) / BK;
+  p.splits = 1;
+  p.out = (__nv_bfloat16*)out;
+  p.ldo = N / 2;
+  p.err = g_err[dev];
+  return launch_gemm_glu(tw, tx, p, st);
 }
 
 // Row-parallel projection whose [M, N] output goes into every rank's hand-over slot (see tp_handover.cuh).

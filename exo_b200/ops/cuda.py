@@ -69,6 +69,7 @@ class _Sig:
     exo_gemm_last_error = (_i, [])
     exo_gemm_splits = (_i, [_i, _i, _i])
     exo_gemm_bf16 = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+    exo_gemm_bf16_swiglu = (_i, [_p, _p, _p, _i, _i, _i, _p])
     exo_gemm_fp8w = (_i, [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
     exo_moe_route = (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p])
     exo_moe_tile_rows = (_i, [_i, _i])
@@ -160,6 +161,12 @@ def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False):
     ensure_gemm_init(x.device)
     M, K = x.shape
     N = w.shape[0]
+    if swiglu_out and M >= 256 and bias is None and residual is None and N % 2 == 0 and use_fused_swiglu:
+        # prefill: gate and up tiles share a CTA and the activation is applied in the epilogue
+        out = torch.empty(M, N // 2, dtype=x.dtype, device=x.device)
+        _chk(lib.exo_gemm_bf16_swiglu(_ptr(x), _ptr(w), _ptr(out), M, N, K, _st()), "gemm_bf16_swiglu")
+        _count()
+        return out
     out = torch.empty(M, N, dtype=x.dtype, device=x.device)
     splits = lib.exo_gemm_splits(M, N, K)
     while splits > 1 and splits * M * N > GEMM_PARTIAL_FLOATS:
@@ -204,6 +211,7 @@ def gemm_check() -> None:
 
 
 gemm_impl = None if os.environ.get("EXO_DISABLE_TCGEN05") == "1" else gemm_bf16
+use_fused_swiglu = os.environ.get("EXO_DISABLE_FUSED_SWIGLU") != "1"
 
 
 def ensure_stream_init(device) -> None:

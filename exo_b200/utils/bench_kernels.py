@@ -96,6 +96,14 @@ def small_cases(only: set[str]) -> None:
             xm = rnd(T, H)
             wt, ids = K.moe_route(torch.randn(T, E_all, device="cuda", generator=g), k, "softmax", True, None, 1, 1, 1.0)
             calls.append(lambda xm=xm, wt=wt, ids=ids: K.moe_experts(xm, wgu, wd, wt, ids, 0, E_all))
+    if "attn" in only:
+        Hq, Hkv, D, bs, B, ctx = 32, 8, 128, 16, 32, 2048
+        nb = B * (ctx // bs + 1) + 1
+        bt = (torch.arange(B * (ctx // bs + 1), device="cuda", dtype=torch.int32) + 1).view(B, -1)
+        sl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+        cu = torch.arange(B + 1, device="cuda", dtype=torch.int32)
+        q, kc, vc = rnd(B, Hq, D), rnd(nb, bs, Hkv, D), rnd(nb, bs, Hkv, D)
+        calls.append(lambda: K.paged_attention(q, kc, vc, bt, sl, cu, D ** -0.5, max_q_len=1))
     for _ in range(3):
         for c in calls:
             c()
@@ -182,6 +190,14 @@ def main() -> None:
             fl = 2.0 * pairs * 3 * F * H / 1e12
             print(f"moe-experts T={T} ({pairs} local pairs, {active}/{E} experts): {ms * 1e3:8.1f} us  "
                   f"{gb / ms * 1e3:7.0f} GB/s ({gb / ms * 1e3 / hbm:4.2f})  {fl / ms * 1e3:7.1f} TFLOP/s ({fl / ms * 1e3 / tf:4.2f}) of {basis}")
+            if T >= 32:     # the same experts as block-scaled fp8 (the grouped kernel serves every token count)
+                from ..ops import quant
+                exq = [(quant.quantize(a, "mxfp8"), quant.quantize(b, "mxfp8")) for a, b in ex]
+                ms = timeit_rot([(lambda a=a, b=b: K.moe_experts(x, a, b, w, ids, 0, E_all)) for a, b in exq])
+                gbq = gb / 2 * (1 + 1 / 32)
+                print(f"moe-experts-fp8 T={T}: {ms * 1e3:8.1f} us  {gbq / ms * 1e3:7.0f} GB/s ({gbq / ms * 1e3 / hbm:4.2f})  "
+                      f"{fl / ms * 1e3:7.1f} TFLOP/s ({fl / ms * 1e3 / tf:4.2f}) of {basis}")
+                del exq
             ms = timeit_rot([(lambda: K.moe_route(logits, k, "softmax", True, None, 1, 1, 1.0)) for _ in range(4)])
             print(f"moe-route T={T} E={E_all} k={k}: {ms * 1e3:8.1f} us")
         K.gemm_check()

@@ -312,3 +312,20 @@ def test_moe_experts_fp8(K, kind, T, E, k, H, F, offset, E_all):
     out = K.moe_experts(x, wgu, wd, w, ids, offset)
     assert K.load().exo_gemm_last_error() == 0
     close(out, ref.moe_experts(x, wgu, wd, w, ids, offset), 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("M,F,K_", [(256, 512, 256), (700, 1792, 1024), (2048, 1000, 512)])
+def test_gemm_tcgen05_fused_swiglu(K, M, F, K_):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(M, K_, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * F, K_, device="cuda", generator=g) / math.sqrt(K_)).bfloat16()
+    got = K.gemm_bf16(x, w, swiglu_out=True)
+    K.gemm_check()
+    assert got.shape == (M, F)
+    close(got, ref.swiglu(ref.linear(x, w)), 2e-2, 2e-2)
+    K.use_fused_swiglu = False
+    try:
+        unfused = K.gemm_bf16(x, w, swiglu_out=True)
+    finally:
+        K.use_fused_swiglu = True
+    close(got, unfused, 1e-2, 1e-2)
