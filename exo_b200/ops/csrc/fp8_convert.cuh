@@ -113,4 +113,38 @@ __device__ __forceinline__ void tile_scales(uint32_t tile, int kind, int r, uint
   }
 }
 
+// ---- widened weights straight into tensor memory (the MMA's A operand) ----------------------------
+// A [128 x 16] bf16 A operand in tensor memory has row i on lane i and two values per 32-bit column, which is how a
+// converter thread holds its row: `n_words` consecutive columns are written with one tcgen05.st.
+__device__ __forceinline__ void tmem_st16w(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_fence() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+// bytes [32h, 32h+32) of row r of the raw tile -> 16 columns at `taddr` (the caller adds lane quadrant, stage and 16*h)
+__device__ __forceinline__ void convert_half_row_tmem(uint32_t raw_tile, uint32_t taddr, int r, int h, uint32_t c2) {
+  const int rot = (r >> 1) & 1;
+  const uint4 w0 = lds16(raw_tile + r * 64 + h * 32 + rot * 16);
+  const uint4 w1 = lds16(raw_tile + r * 64 + h * 32 + (rot ^ 1) * 16);
+  const uint4 lo = rot ? w1 : w0, hi = rot ? w0 : w1;
+  const uint4 o0 = cvt8(lo.x, lo.y, c2), o1 = cvt8(lo.z, lo.w, c2), o2 = cvt8(hi.x, hi.y, c2), o3 = cvt8(hi.z, hi.w, c2);
+  uint32_t o[16] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w, o2.x, o2.y, o2.z, o2.w, o3.x, o3.y, o3.z, o3.w};
+  tmem_st16w(taddr, o);
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor], kind::f16
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"((uint32_t)acc)
+      : "memory");
+}
+
 }  // namespace fp8cvt

@@ -259,11 +259,11 @@ struct GroupedParams {
   int scale_kind, nt, kt;
 };
 
-// FP8: the weight tiles arrive as bytes in `raw` and the four epilogue warps widen them into `a`
-// (see gemm_fp8w.cu) before the MMA warp may use the stage.
+// FP8: the weight tiles arrive as bytes in `raw`; eight converter warps widen them into tensor memory, from where
+// the MMA takes its A operand (see gemm_fp8w.cu), before the MMA warp may use the stage.
 template <int BN, int STAGES, bool DUAL, bool FP8>
 struct GSmem {
-  alignas(1024) __nv_bfloat16 a[STAGES][(DUAL ? 2 : 1) * BM * BK];
+  alignas(1024) __nv_bfloat16 a[FP8 ? 1 : STAGES][FP8 ? 64 : (DUAL ? 2 : 1) * BM * BK];     // unused with fp8 weights
   alignas(1024) __nv_bfloat16 b[STAGES][BN * BK];
   alignas(128) uint8_t raw[FP8 ? STAGES : 1][FP8 ? (DUAL ? 2 : 1) * fp8cvt::TILE_BYTES : 128];
   uint64_t full[STAGES], empty[STAGES], conv[STAGES], acc_full;
@@ -280,7 +280,11 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   using S = GSmem<BN, STAGES, DUAL, FP8>;
   S& s = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * BN;
-  constexpr uint32_t TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
+  constexpr uint32_t A_COLS = (DUAL ? 64 : 32);                   // fp8: one stage of widened weights in tensor memory
+  constexpr uint32_t A_COL0 = ACC_COLS < 32 ? 32 : ACC_COLS;
+  constexpr uint32_t NEED = A_COL0 + (FP8 ? STAGES * A_COLS : 0);
+  constexpr uint32_t TMEM_COLS = NEED <= 32 ? 32 : NEED <= 64 ? 64 : NEED <= 128 ? 128 : NEED <= 256 ? 256 : 512;
+  static_assert(NEED <= 512, "accumulators and the A ring must fit the 512 tensor-memory columns");
   constexpr uint32_t STAGE_BYTES = (DUAL ? 2 : 1) * (FP8 ? fp8cvt::TILE_BYTES : BM * BK * 2) + BN * BK * 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int* tile = p.plan + 1 + 4 * blockIdx.y;
@@ -346,14 +350,23 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           break;
         }
         tc::tc_fence_after();
-        const uint64_t ad = tc::umma_desc_sw128(tc::smem_u32(s.a[st]));
         const uint64_t bd = tc::umma_desc_sw128(tc::smem_u32(s.b[st]));
+        if constexpr (FP8) {
+          const uint32_t a_t = tmem + A_COL0 + st * A_COLS;
 #pragma unroll
-        for (int k = 0; k < BK / 16; k++) {
-          tc::umma_bf16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) != 0);
-          if (DUAL) {
-            const uint64_t ud = tc::umma_desc_sw128(tc::smem_u32(s.a[st] + BM * BK));
-            tc::umma_bf16(tmem + BN, ud + 2 * k, bd + 2 * k, idesc, (i | k) != 0);
+          for (int k = 0; k < BK / 16; k++) {
+            fp8cvt::umma_bf16_ts(tmem, a_t + 8 * k, bd + 2 * k, idesc, (i | k) != 0);
+            if (DUAL) fp8cvt::umma_bf16_ts(tmem + BN, a_t + 32 + 8 * k, bd + 2 * k, idesc, (i | k) != 0);
+          }
+        } else {
+          const uint64_t ad = tc::umma_desc_sw128(tc::smem_u32(s.a[st]));
+#pragma unroll
+          for (int k = 0; k < BK / 16; k++) {
+            tc::umma_bf16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) != 0);
+            if (DUAL) {
+              const uint64_t ud = tc::umma_desc_sw128(tc::smem_u32(s.a[st] + BM * BK));
+              tc::umma_bf16(tmem + BN, ud + 2 * k, bd + 2 * k, idesc, (i | k) != 0);
+            }
           }
         }
         tc::umma_commit(&s.empty[st]);
@@ -362,10 +375,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
   } else {
     if constexpr (FP8) {
-      // 256 converter threads (warps 2..9): for a gate/up stage the first 128 widen the gate tile and the others the up
-      // tile, a row each; otherwise two threads share a row.  The stage's `a` buffers are free because the producer
-      // only refilled the stage after the MMAs that read them had completed.
-      const int c = threadIdx.x - 64, r = c & 127, g = c >> 7;
+      // 256 converter threads (warps 2..9).  Warp w may touch the tensor-memory lanes of quadrant w % 4 only, so it
+      // widens the rows of that quadrant: warps 2..5 take the first 32 weights of every row's K block (of both tiles of
+      // a gate/up stage), warps 6..9 the second 32.  The stage's columns are free: the producer only refilled the
+      // stage after the MMAs that read them had completed.
+      const int quad = warp & 3, h = (warp - 2) >> 2, r = quad * 32 + lane;
+      const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16) + A_COL0 + 16 * h;
       for (int i = 0; i < nkb; i++) {
         const int st = i % STAGES;
         if (!tc::mbar_wait_backoff(&s.full[st], (i / STAGES) & 1, 32, 1u << 24)) {
@@ -373,13 +388,16 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           s.abort_flag = 1;
           break;
         }
-        const uint32_t raw0 = tc::smem_u32(s.raw[st]) + (DUAL ? g * fp8cvt::TILE_BYTES : 0);
-        const uint32_t a0 = tc::smem_u32(s.a[st]) + (DUAL ? g * BM * BK * 2 : 0);
+        tc::tc_fence_after();
+        const uint32_t raw0 = tc::smem_u32(s.raw[st]);
         uint32_t c0, c1;
         fp8cvt::tile_scales(raw0, p.scale_kind, r, c0, c1);
-        if (DUAL) fp8cvt::convert_row(raw0, a0, r, c0, c1);
-        else fp8cvt::convert_half_row(raw0, a0, r, g, g ? c1 : c0);
-        tc::fence_proxy_async();
+        fp8cvt::convert_half_row_tmem(raw0, lane_base + st * A_COLS, r, h, h ? c1 : c0);
+        if (DUAL) {
+          fp8cvt::tile_scales(raw0 + fp8cvt::TILE_BYTES, p.scale_kind, r, c0, c1);
+          fp8cvt::convert_half_row_tmem(raw0 + fp8cvt::TILE_BYTES, lane_base + st * A_COLS + 32, r, h, h ? c1 : c0);
+        }
+        fp8cvt::tmem_st_fence();
         tc::mbar_arrive(&s.conv[st]);
       }
     }
@@ -446,10 +464,12 @@ int grouped_dispatch(int bn, const CUtensorMap* tw, const CUtensorMap* tx, const
                      int max_tiles, cudaStream_t st) {
   if (p.tiles) {      // fp8 weights: a stage also holds the raw byte tiles
     switch (bn) {
-      case 16: return launch_grouped<16, 4, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);     // dual: 4 x 50 KB
-      case 32: return launch_grouped<32, 4, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);     // dual: 4 x 52 KB
-      case 64: return launch_grouped<64, 3, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);     // dual: 3 x 56 KB
-      default: return launch_grouped<128, 3, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);    // dual: 3 x 64 KB
+      // stages: shared memory holds raw tiles and token tiles only; the widened weights take 32 (64 for a gate/up
+      // pair) tensor-memory columns per stage next to the accumulators
+      case 16: return launch_grouped<16, 6, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);
+      case 32: return launch_grouped<32, 6, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);
+      case 64: return launch_grouped<64, 5, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);
+      default: return launch_grouped<128, 4, DUAL, true>(tw, tx, p, n_tiles_w, max_tiles, st);
     }
   }
   switch (bn) {
