@@ -40,7 +40,8 @@ class Executor:
         self.host = torch.zeros(words, dtype=torch.int32, pin_memory=self.cuda)
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(words, dtype=torch.int32, device=self.device)
-        self.use_graphs = self.cuda if use_graphs is None else use_graphs
+        # MLA attention is still PyTorch ops with host reads of the sequence lengths: such a step cannot be captured
+        self.use_graphs = (self.cuda and not cfg.mla) if use_graphs is None else use_graphs
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self.out_host = torch.zeros(self.max_B, dtype=torch.int32, pin_memory=self.cuda)
         self.prev_sampled = torch.zeros(max(self.max_B, 256), dtype=torch.int32, device=self.device)

@@ -203,6 +203,70 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
   if (e == 1023) plan[0] = min(s_tiles[1023], max_tiles);
 }
 
+// Up to 4096 pairs (decode batches): count, offsets, tile list and every pair's row in ONE block, so that the plan
+// costs one launch instead of memset + count + plan, and the row copy needs no atomics.
+__global__ void __launch_bounds__(1024) moe_plan_small_kernel(const int* __restrict__ ids, int P, int expert_offset, int E, int bn,
+                                                              int max_tiles, int* __restrict__ plan, int* __restrict__ pos) {
+  __shared__ int s_cnt[1024], s_rows[1024], s_tiles[1024];
+  const int t = threadIdx.x;
+  s_cnt[t] = 0;
+  __syncthreads();
+  int slot[4], ex[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int i = t + j * 1024;
+    slot[j] = -1;
+    ex[j] = 0;
+    if (i < P) {
+      const int e = ids[i] - expert_offset;
+      if (e >= 0 && e < E) { ex[j] = e; slot[j] = atomicAdd(&s_cnt[e], 1); }
+    }
+  }
+  __syncthreads();
+  const int cnt = t < E ? s_cnt[t] : 0, nt = (cnt + bn - 1) / bn;
+  s_rows[t] = cnt;
+  s_tiles[t] = nt;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {
+    const int a = t >= d ? s_rows[t - d] : 0, b = t >= d ? s_tiles[t - d] : 0;
+    __syncthreads();
+    s_rows[t] += a;
+    s_tiles[t] += b;
+    __syncthreads();
+  }
+  const int row0 = s_rows[t] - cnt, tile0 = s_tiles[t] - nt;
+  if (t == 1023) plan[0] = min(s_tiles[1023], max_tiles);
+  __syncthreads();
+  s_cnt[t] = row0;                      // reuse: first row of expert t
+  if (t < E) {
+    for (int i = 0; i < nt && tile0 + i < max_tiles; i++) {
+      int* q = plan + 1 + 4 * (tile0 + i);
+      q[0] = t;
+      q[1] = row0 + i * bn;
+      q[2] = min(bn, cnt - i * bn);
+      q[3] = 0;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int i = t + j * 1024;
+    if (i < P) pos[i] = slot[j] >= 0 ? s_cnt[ex[j]] + slot[j] : -1;
+  }
+}
+
+// One warp per pair: copy the token's row to the place the plan gave it.
+__global__ void __launch_bounds__(256) moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ pos, int P,
+                                                              int k, int H, __nv_bfloat16* __restrict__ xs) {
+  const int pair = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (pair >= P) return;
+  const int dst = pos[pair];
+  if (dst < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(pair / k) * H);
+  uint4* d = reinterpret_cast<uint4*>(xs + (size_t)dst * H);
+  for (int i = lane; i < H / 8; i += 32) d[i] = src[i];
+}
+
 // One warp per pair: take a slot in the expert's segment and copy the token's row there.
 __global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
                                                           int P, int k, int H, int expert_offset, int E,
@@ -622,11 +686,16 @@ EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const 
   int* offsets = counts + E;
   int* cursor = offsets + E;
   int* plan = cursor + E;
-  if (cudaMemsetAsync(counts, 0, sizeof(int) * E, st) != cudaSuccess) return -7;
-  moe_count_kernel<<<(P + 255) / 256, 256, 0, st>>>((const int*)ids, P, expert_offset, E, counts);
-  moe_plan_kernel<<<1, 1024, 0, st>>>(counts, E, bn, max_tiles, offsets, cursor, plan);
-  moe_scatter_kernel<<<(P + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const int*)ids, P, k, H, expert_offset, E, offsets,
-                                                  cursor, (int*)pos, (__nv_bfloat16*)xs);
+  if (P <= 4096) {      // decode batches: the whole plan in one block, then a plain row gather
+    moe_plan_small_kernel<<<1, 1024, 0, st>>>((const int*)ids, P, expert_offset, E, bn, max_tiles, plan, (int*)pos);
+    moe_gather_rows_kernel<<<(P + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const int*)pos, P, k, H, (__nv_bfloat16*)xs);
+  } else {
+    if (cudaMemsetAsync(counts, 0, sizeof(int) * E, st) != cudaSuccess) return -7;
+    moe_count_kernel<<<(P + 255) / 256, 256, 0, st>>>((const int*)ids, P, expert_offset, E, counts);
+    moe_plan_kernel<<<1, 1024, 0, st>>>(counts, E, bn, max_tiles, offsets, cursor, plan);
+    moe_scatter_kernel<<<(P + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const int*)ids, P, k, H, expert_offset, E, offsets,
+                                                    cursor, (int*)pos, (__nv_bfloat16*)xs);
+  }
   EXO_CHECK_LAUNCH();
   const CUtensorMap* t_xs = exo_tmap_2d_bf16(xs, P, H, bn);
   // fp8: the weights are not read through a tensor map (the activations' map stands in for the unused argument)

@@ -262,7 +262,8 @@ def test_moe_route(K, kind, E, k, n_group, topk_group, dtype):
 
 @pytest.mark.parametrize("T,E,k,H,F,offset,E_all", [
     (1, 8, 2, 256, 128, 0, 8), (3, 16, 4, 512, 192, 16, 64),            # grouped GEMVs
-    (40, 8, 2, 256, 128, 0, 8), (300, 16, 8, 512, 384, 32, 64), (2048, 4, 2, 256, 256, 0, 4)])   # grouped tcgen05 GEMMs
+    (40, 8, 2, 256, 128, 0, 8), (300, 16, 8, 512, 384, 32, 64), (2048, 4, 2, 256, 256, 0, 4),   # grouped tcgen05 GEMMs, one-block plan
+    (3000, 4, 2, 256, 256, 0, 4)])                                                                 # more than 4096 pairs: multi-kernel plan
 def test_moe_experts(K, T, E, k, H, F, offset, E_all):
     g = torch.Generator(device="cuda").manual_seed(2)
     x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
@@ -300,7 +301,7 @@ def test_gemm_fp8_weights(K, kind, M, N, K_):
 
 
 @pytest.mark.parametrize("kind", ["mxfp8", "dsfp8"])
-@pytest.mark.parametrize("T,E,k,H,F,offset,E_all", [(2, 8, 2, 256, 128, 0, 8), (300, 16, 8, 512, 384, 32, 64), (1500, 4, 2, 256, 256, 0, 4)])
+@pytest.mark.parametrize("T,E,k,H,F,offset,E_all", [(2, 8, 2, 256, 128, 0, 8), (300, 16, 8, 512, 384, 32, 64), (2500, 4, 2, 256, 256, 0, 4)])
 def test_moe_experts_fp8(K, kind, T, E, k, H, F, offset, E_all):
     from exo_b200.ops import quant
     g = torch.Generator(device="cuda").manual_seed(4)
