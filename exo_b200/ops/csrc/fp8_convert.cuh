@@ -1,6 +1,7 @@
 // Widening block-scaled e4m3 weights to bf16 inside a kernel (shared by the fp8-weight GEMMs).
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace fp8cvt {
@@ -110,6 +111,51 @@ __device__ __forceinline__ void tile_scales(uint32_t tile, int kind, int r, uint
     float f;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(tile + TILE_BODY));
     c_lo = c_hi = c2_from_f32(f);
+  }
+}
+
+// ---- e4m3 -> f16 with the hardware converter ------------------------------------------------------
+// With f16 operands on both sides of the MMA the widening is two instructions per pair: the packed
+// e4m3x2 -> f16x2 conversion (exact) and one packed multiply by the block scale (a power of two for
+// e8m0 scales: exact too while the product stays in f16's range, which block-scaled weights do).
+__device__ __forceinline__ void cvt4_f16(uint32_t w, uint32_t s2, uint32_t& p0, uint32_t& p1) {
+  uint32_t a, b;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+      : "=r"(a), "=r"(b)
+      : "r"(w));
+  __half2 x = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&s2));
+  __half2 y = __hmul2(*reinterpret_cast<__half2*>(&b), *reinterpret_cast<__half2*>(&s2));
+  p0 = *reinterpret_cast<uint32_t*>(&x);
+  p1 = *reinterpret_cast<uint32_t*>(&y);
+}
+// f16 x2 of 2^(e - 127); scales below f16's subnormal range become 0, above its range the largest power of two
+__device__ __forceinline__ uint32_t s2_f16_from_e8m0(uint32_t e) {
+  const int ex = (int)e - 127;                 // value 2^ex
+  uint32_t h;
+  if (ex >= -14) h = (uint32_t)min(ex + 15, 30) << 10;          // normal
+  else if (ex >= -24) h = 1u << (ex + 24);                      // subnormal: 2^ex = 2^-24 * 2^(ex+24)
+  else h = 0;
+  return h | (h << 16);
+}
+__device__ __forceinline__ uint32_t s2_f16_from_f32(float s) {
+  __half b = __float2half_rn(fminf(s, 65504.f));
+  uint32_t h = *reinterpret_cast<uint16_t*>(&b);
+  return h | (h << 16);
+}
+// f16 multipliers of row r of the tile at shared address `tile`
+__device__ __forceinline__ void tile_scales_f16(uint32_t tile, int kind, int r, uint32_t& s_lo, uint32_t& s_hi) {
+  if (kind == 1) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(tile + 128 * 64 + 2 * r));
+    s_lo = s2_f16_from_e8m0(v & 0xffu);
+    s_hi = s2_f16_from_e8m0((v >> 8) & 0xffu);
+  } else {
+    float f;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(tile + 128 * 64));
+    s_lo = s_hi = s2_f16_from_f32(f);
   }
 }
 

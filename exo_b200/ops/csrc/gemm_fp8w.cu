@@ -178,7 +178,9 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
       : "memory");
 }
 
-template <int BN, int RS>
+// F16: both MMA operands are f16 (the activations arrive converted, the weights are widened with the hardware
+// e4m3 -> f16 converter): half the widening instructions of the bf16 form.
+template <int BN, int RS, bool F16>
 __global__ void __launch_bounds__(320, (BN <= 64 ? 2 : 1))
 gemm_fp8w_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p, const ScaleParams sp) {
   extern __shared__ uint8_t smem_raw[];
@@ -233,7 +235,8 @@ gemm_fp8w_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     }
   } else if (warp == 1) {
     if (tc::elect_one()) {
-      constexpr uint32_t idesc = tc::umma_idesc_bf16(BM, BN);
+      // kind::f16 descriptor: operand formats 1 = bf16, 0 = f16 (bits 7..9 and 10..12); fp32 accumulation either way
+      constexpr uint32_t idesc = F16 ? (tc::umma_idesc_bf16(BM, BN) & ~((1u << 7) | (1u << 10))) : tc::umma_idesc_bf16(BM, BN);
       for (int i = 0; i < nkb; i++) {
         const int rs = i % RS, as = i % AS;
         if (!tc::mbar_wait(&s.a_full[as], (i / AS) & 1) || !tc::mbar_wait(&s.raw_full[rs], (i / RS) & 1)) {
@@ -267,15 +270,21 @@ gemm_fp8w_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
       tc::tc_fence_after();
       const uint32_t raw = tc::smem_u32(s.raw[rs]);
       uint32_t c_lo, c_hi;
-      tile_scales(raw, sp.kind, r, c_lo, c_hi);
+      if constexpr (F16) tile_scales_f16(raw, sp.kind, r, c_lo, c_hi);
+      else tile_scales(raw, sp.kind, r, c_lo, c_hi);
       const uint32_t c2 = h ? c_hi : c_lo;
       const uint4 w0 = lds16(raw + r * 64 + h * 32 + ((r >> 1) & 1) * 16);
       const uint4 w1 = lds16(raw + r * 64 + h * 32 + (((r >> 1) & 1) ^ 1) * 16);
       const uint4 lo = ((r >> 1) & 1) ? w1 : w0, hi = ((r >> 1) & 1) ? w0 : w1;     // bytes 0..15 / 16..31 of the half row
       uint32_t o[16];
-      const uint4 o0 = cvt8(lo.x, lo.y, c2), o1 = cvt8(lo.z, lo.w, c2), o2 = cvt8(hi.x, hi.y, c2), o3 = cvt8(hi.z, hi.w, c2);
-      o[0] = o0.x; o[1] = o0.y; o[2] = o0.z; o[3] = o0.w; o[4] = o1.x; o[5] = o1.y; o[6] = o1.z; o[7] = o1.w;
-      o[8] = o2.x; o[9] = o2.y; o[10] = o2.z; o[11] = o2.w; o[12] = o3.x; o[13] = o3.y; o[14] = o3.z; o[15] = o3.w;
+      if constexpr (F16) {
+        cvt4_f16(lo.x, c2, o[0], o[1]); cvt4_f16(lo.y, c2, o[2], o[3]); cvt4_f16(lo.z, c2, o[4], o[5]); cvt4_f16(lo.w, c2, o[6], o[7]);
+        cvt4_f16(hi.x, c2, o[8], o[9]); cvt4_f16(hi.y, c2, o[10], o[11]); cvt4_f16(hi.z, c2, o[12], o[13]); cvt4_f16(hi.w, c2, o[14], o[15]);
+      } else {
+        const uint4 o0 = cvt8(lo.x, lo.y, c2), o1 = cvt8(lo.z, lo.w, c2), o2 = cvt8(hi.x, hi.y, c2), o3 = cvt8(hi.z, hi.w, c2);
+        o[0] = o0.x; o[1] = o0.y; o[2] = o0.z; o[3] = o0.w; o[4] = o1.x; o[5] = o1.y; o[6] = o1.z; o[7] = o1.w;
+        o[8] = o2.x; o[9] = o2.y; o[10] = o2.z; o[11] = o2.w; o[12] = o3.x; o[13] = o3.y; o[14] = o3.z; o[15] = o3.w;
+      }
       tmem_st16u(lane_base + as * 32, o);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc::tc_fence_before();
@@ -292,20 +301,38 @@ gemm_fp8w_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
   }
 }
 
-template <int BN, int RS>
-int launch_fp8w_ta(const CUtensorMap* tx, const GemmParams& p, const ScaleParams& sp, cudaStream_t st) {
+template <int BN, int RS, bool F16>
+int launch_fp8w_ta_t(const CUtensorMap* tx, const GemmParams& p, const ScaleParams& sp, cudaStream_t st) {
   using S = SmemFT<BN, RS>;
   const size_t smem = sizeof(S) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_fp8w_ta_kernel<BN, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_fp8w_ta_kernel<BN, RS, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return -3;
     attr_set = true;
   }
   dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
-  gemm_fp8w_ta_kernel<BN, RS><<<grid, 320, smem, st>>>(*tx, p, sp);
+  gemm_fp8w_ta_kernel<BN, RS, F16><<<grid, 320, smem, st>>>(*tx, p, sp);
   EXO_CHECK_LAUNCH();
   return 0;
+}
+template <int BN, int RS>
+int launch_fp8w_ta(const CUtensorMap* tx, const GemmParams& p, const ScaleParams& sp, bool f16, cudaStream_t st) {
+  return f16 ? launch_fp8w_ta_t<BN, RS, true>(tx, p, sp, st) : launch_fp8w_ta_t<BN, RS, false>(tx, p, sp, st);
+}
+
+// x bf16 -> f16 (saturating), for the f16-operand form of the GEMM
+__global__ void bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ y, long n8) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float f[8];
+  unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+  uint4 o;
+  __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; j++)
+    h[j] = __floats2half2_rn(fminf(fmaxf(f[2 * j], -65504.f), 65504.f), fminf(fmaxf(f[2 * j + 1], -65504.f), 65504.f));
+  reinterpret_cast<uint4*>(y)[i] = o;
 }
 
 template <int BN, int RS, int AS>
@@ -327,8 +354,29 @@ int launch_fp8w(const CUtensorMap* tx, const GemmParams& p, const ScaleParams& s
 }  // namespace
 
 // `tiles`: the weight in the tiled form [ceil(N/128), ceil(K/64), 8448]; scale_kind 1 = e8m0 per 1x32, 2 = fp32 per tile.
+EXO_API int exo_bf16_to_f16(const void* x, void* y, long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 8) return -2;
+  bf16_to_f16_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__half*)y, n / 8);
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+static int gemm_fp8w_impl(const void* x, const void* tiles, int scale_kind, const void* bias, const void* residual, void* out,
+                          int M, int N, int K, int ldo, int splits, bool x_f16, cudaStream_t st);
+
 EXO_API int exo_gemm_fp8w(const void* x, const void* tiles, int scale_kind, const void* bias,
                           const void* residual, void* out, int M, int N, int K, int ldo, int splits, cudaStream_t st) {
+  return gemm_fp8w_impl(x, tiles, scale_kind, bias, residual, out, M, N, K, ldo, splits, false, st);
+}
+// The same with f16 activations `x16` (see exo_bf16_to_f16): both MMA operands f16.
+EXO_API int exo_gemm_fp8w_f16(const void* x16, const void* tiles, int scale_kind, const void* bias,
+                              const void* residual, void* out, int M, int N, int K, int ldo, int splits, cudaStream_t st) {
+  return gemm_fp8w_impl(x16, tiles, scale_kind, bias, residual, out, M, N, K, ldo, splits, true, st);
+}
+
+static int gemm_fp8w_impl(const void* x, const void* tiles, int scale_kind, const void* bias, const void* residual, void* out,
+                          int M, int N, int K, int ldo, int splits, bool x_f16, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || K < BK || (scale_kind != 1 && scale_kind != 2) || ((uintptr_t)tiles & 15)) return -2;
   GemmParams p;
@@ -359,13 +407,13 @@ EXO_API int exo_gemm_fp8w(const void* x, const void* tiles, int scale_kind, cons
   sp.kt = kb_total;
   static int smem_a = -1;
   if (smem_a < 0) { const char* e = getenv("EXO_FP8_SMEM_A"); smem_a = (e && e[0] == '1') ? 1 : 0; }
-  if (!smem_a) {      // A operand from tensor memory (default); EXO_FP8_SMEM_A=1 selects the shared-memory form below
+  if (!smem_a || x_f16) {      // A operand from tensor memory (default); EXO_FP8_SMEM_A=1 selects the shared-memory form below
     switch (bn) {
-      case 16: return launch_fp8w_ta<16, 8>(tx, p, sp, st);     // 8 x (8.25 + 2) KB
-      case 32: return launch_fp8w_ta<32, 8>(tx, p, sp, st);     // 8 x (8.25 + 4) KB
-      case 64: return launch_fp8w_ta<64, 6>(tx, p, sp, st);     // 6 x (8.25 + 8) KB
-      case 128: return launch_fp8w_ta<128, 6>(tx, p, sp, st);   // 6 x (8.25 + 16) KB
-      default: return launch_fp8w_ta<256, 4>(tx, p, sp, st);    // 4 x (8.25 + 32) KB
+      case 16: return launch_fp8w_ta<16, 8>(tx, p, sp, x_f16, st);     // 8 x (8.25 + 2) KB
+      case 32: return launch_fp8w_ta<32, 8>(tx, p, sp, x_f16, st);     // 8 x (8.25 + 4) KB
+      case 64: return launch_fp8w_ta<64, 6>(tx, p, sp, x_f16, st);     // 6 x (8.25 + 8) KB
+      case 128: return launch_fp8w_ta<128, 6>(tx, p, sp, x_f16, st);   // 6 x (8.25 + 16) KB
+      default: return launch_fp8w_ta<256, 4>(tx, p, sp, x_f16, st);    // 4 x (8.25 + 32) KB
     }
   }
   switch (bn) {

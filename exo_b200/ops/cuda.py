@@ -71,6 +71,8 @@ class _Sig:
     exo_gemm_bf16 = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p])
     exo_gemm_bf16_swiglu = (_i, [_p, _p, _p, _i, _i, _i, _p])
     exo_gemm_fp8w = (_i, [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+    exo_gemm_fp8w_f16 = (_i, [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+    exo_bf16_to_f16 = (_i, [_p, _p, _l, _p])
     exo_moe_route = (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p])
     exo_moe_tile_rows = (_i, [_i, _i])
     exo_moe_max_tiles = (_i, [_i, _i, _i])
@@ -194,9 +196,19 @@ def linear_fp8(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=
     splits = lib.exo_gemm_splits(M, N, K)
     while splits > 1 and splits * M * N > GEMM_PARTIAL_FLOATS:
         splits -= 1
-    _chk(lib.exo_gemm_fp8w(_ptr(x), _ptr(w.to_tiled().tiles), 1 if w.kind == "mxfp8" else 2, _ptr(bias), _ptr(residual),
-                           _ptr(out), M, N, K, N, splits, _st()), "gemm_fp8w")
-    _count()
+    kind = 1 if w.kind == "mxfp8" else 2
+    if fp8_f16_operands and K % 8 == 0:
+        # f16 on both sides of the MMA: the activations are converted once (saturating), the weights with the hardware
+        # e4m3 -> f16 converter inside the GEMM
+        x16 = torch.empty(M, K, dtype=torch.float16, device=x.device)
+        _chk(lib.exo_bf16_to_f16(_ptr(x), _ptr(x16), M * K, _st()), "bf16_to_f16")
+        _chk(lib.exo_gemm_fp8w_f16(_ptr(x16), _ptr(w.to_tiled().tiles), kind, _ptr(bias), _ptr(residual),
+                                   _ptr(out), M, N, K, N, splits, _st()), "gemm_fp8w_f16")
+        _count(2)
+    else:
+        _chk(lib.exo_gemm_fp8w(_ptr(x), _ptr(w.to_tiled().tiles), kind, _ptr(bias), _ptr(residual),
+                               _ptr(out), M, N, K, N, splits, _st()), "gemm_fp8w")
+        _count()
     return swiglu(out) if swiglu_out else out
 
 
@@ -212,6 +224,7 @@ def gemm_check() -> None:
 
 gemm_impl = None if os.environ.get("EXO_DISABLE_TCGEN05") == "1" else gemm_bf16
 use_fused_swiglu = os.environ.get("EXO_DISABLE_FUSED_SWIGLU") != "1"
+fp8_f16_operands = os.environ.get("EXO_FP8_F16_OPERANDS", "1") == "1"     # 0: bf16 operands (five instead of two widening instructions per pair)
 
 
 def ensure_stream_init(device) -> None:

@@ -294,6 +294,14 @@ def test_gemm_fp8_weights(K, kind, M, N, K_):
     out = K.linear(x, wq, bias, res)
     assert K.load().exo_gemm_last_error() == 0
     close(out, want, 1e-2, 1e-2)
+    # the other operand form (f16 on both sides of the MMA by default, bf16 as the alternative) agrees
+    K.fp8_f16_operands = not K.fp8_f16_operands
+    try:
+        other = K.linear(x, wq, bias, res)
+    finally:
+        K.fp8_f16_operands = not K.fp8_f16_operands
+    assert K.load().exo_gemm_last_error() == 0
+    close(other, want, 1e-2, 1e-2)
     # against the unquantised weights the error is the fp8 rounding (2^-4 relative per weight, averaged down by the sum)
     close(K.linear(x, wq), ref.linear(x.float(), w.bfloat16().float()), 5e-2, 5e-2)
     sw = K.linear(x, quant.quantize(w[: N // 2 * 2].bfloat16(), kind), swiglu_out=True)
