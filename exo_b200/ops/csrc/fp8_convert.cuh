@@ -183,6 +183,17 @@ __device__ __forceinline__ void convert_half_row_tmem(uint32_t raw_tile, uint32_
   uint32_t o[16] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w, o2.x, o2.y, o2.z, o2.w, o3.x, o3.y, o3.z, o3.w};
   tmem_st16w(taddr, o);
 }
+// the same with f16 results (hardware e4m3 -> f16 converter and one packed multiply by the f16 scale `s2`)
+__device__ __forceinline__ void convert_half_row_tmem_f16(uint32_t raw_tile, uint32_t taddr, int r, int h, uint32_t s2) {
+  const int rot = (r >> 1) & 1;
+  const uint4 w0 = lds16(raw_tile + r * 64 + h * 32 + rot * 16);
+  const uint4 w1 = lds16(raw_tile + r * 64 + h * 32 + (rot ^ 1) * 16);
+  const uint4 lo = rot ? w1 : w0, hi = rot ? w0 : w1;
+  uint32_t o[16];
+  cvt4_f16(lo.x, s2, o[0], o[1]); cvt4_f16(lo.y, s2, o[2], o[3]); cvt4_f16(lo.z, s2, o[4], o[5]); cvt4_f16(lo.w, s2, o[6], o[7]);
+  cvt4_f16(hi.x, s2, o[8], o[9]); cvt4_f16(hi.y, s2, o[10], o[11]); cvt4_f16(hi.z, s2, o[12], o[13]); cvt4_f16(hi.w, s2, o[14], o[15]);
+  tmem_st16w(taddr, o);
+}
 // D[tmem] (+)= A[tmem] * B[smem descriptor], kind::f16
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool acc) {
   asm volatile(

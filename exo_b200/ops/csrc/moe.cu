@@ -160,6 +160,18 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const RouteParams p) {
   }
 }
 
+// eight bf16 -> eight f16 (saturating): token rows for the f16-operand form of the fp8 expert GEMMs
+__device__ __forceinline__ uint4 bf16x8_to_f16x8(const uint4& v) {
+  float f[8];
+  unpack8(v, f);
+  uint4 o;
+  __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; j++)
+    h[j] = __floats2half2_rn(fminf(fmaxf(f[2 * j], -65504.f), 65504.f), fminf(fmaxf(f[2 * j + 1], -65504.f), 65504.f));
+  return o;
+}
+
 // ------------------------------------------------------------------------------------------
 // plan: counts -> offsets and the tile list
 // ------------------------------------------------------------------------------------------
@@ -257,21 +269,21 @@ __global__ void __launch_bounds__(1024) moe_plan_small_kernel(const int* __restr
 
 // One warp per pair: copy the token's row to the place the plan gave it.
 __global__ void __launch_bounds__(256) moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ pos, int P,
-                                                              int k, int H, __nv_bfloat16* __restrict__ xs) {
+                                                              int k, int H, __nv_bfloat16* __restrict__ xs, int to_f16) {
   const int pair = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (pair >= P) return;
   const int dst = pos[pair];
   if (dst < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(pair / k) * H);
   uint4* d = reinterpret_cast<uint4*>(xs + (size_t)dst * H);
-  for (int i = lane; i < H / 8; i += 32) d[i] = src[i];
+  for (int i = lane; i < H / 8; i += 32) d[i] = to_f16 ? bf16x8_to_f16x8(src[i]) : src[i];
 }
 
 // One warp per pair: take a slot in the expert's segment and copy the token's row there.
 __global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
                                                           int P, int k, int H, int expert_offset, int E,
                                                           const int* __restrict__ offsets, int* __restrict__ cursor,
-                                                          int* __restrict__ pos, __nv_bfloat16* __restrict__ xs) {
+                                                          int* __restrict__ pos, __nv_bfloat16* __restrict__ xs, int to_f16) {
   const int pair = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (pair >= P) return;
   const int e = ids[pair] - expert_offset;
@@ -284,7 +296,7 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* _
   if (dst < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(pair / k) * H);
   uint4* d = reinterpret_cast<uint4*>(xs + (size_t)dst * H);
-  for (int i = lane; i < H / 8; i += 32) d[i] = src[i];
+  for (int i = lane; i < H / 8; i += 32) d[i] = to_f16 ? bf16x8_to_f16x8(src[i]) : src[i];
 }
 
 __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, const int* __restrict__ pos,
@@ -321,6 +333,8 @@ struct GroupedParams {
   // block-scaled fp8 expert weights (FP8 kernels only): tiled storage [E, nt, kt, TILE_BYTES] (see fp8_convert.cuh)
   const uint8_t* tiles;
   int scale_kind, nt, kt;
+  int f16;                // fp8 kernels: both MMA operands f16 (token rows arrive as f16)
+  int out_f16;            // write `out` as f16 (the gate/up result that feeds an f16 down projection)
 };
 
 // FP8: the weight tiles arrive as bytes in `raw`; eight converter warps widen them into tensor memory, from where
@@ -405,7 +419,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
   } else if (warp == 1) {
     if (tc::elect_one()) {
-      constexpr uint32_t idesc = tc::umma_idesc_bf16(BM, BN);
+      constexpr uint32_t idesc_bf = tc::umma_idesc_bf16(BM, BN), idesc_h = idesc_bf & ~((1u << 7) | (1u << 10));     // operand formats: 1 = bf16, 0 = f16
+      const uint32_t idesc = (FP8 && p.f16) ? idesc_h : idesc_bf;
       for (int i = 0; i < nkb; i++) {
         const int st = i % STAGES;
         if ((FP8 && !tc::mbar_wait(&s.conv[st], (i / STAGES) & 1)) || !tc::mbar_wait(&s.full[st], (i / STAGES) & 1)) {
@@ -455,11 +470,20 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         tc::tc_fence_after();
         const uint32_t raw0 = tc::smem_u32(s.raw[st]);
         uint32_t c0, c1;
-        fp8cvt::tile_scales(raw0, p.scale_kind, r, c0, c1);
-        fp8cvt::convert_half_row_tmem(raw0, lane_base + st * A_COLS, r, h, h ? c1 : c0);
-        if (DUAL) {
-          fp8cvt::tile_scales(raw0 + fp8cvt::TILE_BYTES, p.scale_kind, r, c0, c1);
-          fp8cvt::convert_half_row_tmem(raw0 + fp8cvt::TILE_BYTES, lane_base + st * A_COLS + 32, r, h, h ? c1 : c0);
+        if (p.f16) {
+          fp8cvt::tile_scales_f16(raw0, p.scale_kind, r, c0, c1);
+          fp8cvt::convert_half_row_tmem_f16(raw0, lane_base + st * A_COLS, r, h, h ? c1 : c0);
+          if (DUAL) {
+            fp8cvt::tile_scales_f16(raw0 + fp8cvt::TILE_BYTES, p.scale_kind, r, c0, c1);
+            fp8cvt::convert_half_row_tmem_f16(raw0 + fp8cvt::TILE_BYTES, lane_base + st * A_COLS + 32, r, h, h ? c1 : c0);
+          }
+        } else {
+          fp8cvt::tile_scales(raw0, p.scale_kind, r, c0, c1);
+          fp8cvt::convert_half_row_tmem(raw0, lane_base + st * A_COLS, r, h, h ? c1 : c0);
+          if (DUAL) {
+            fp8cvt::tile_scales(raw0 + fp8cvt::TILE_BYTES, p.scale_kind, r, c0, c1);
+            fp8cvt::convert_half_row_tmem(raw0 + fp8cvt::TILE_BYTES, lane_base + st * A_COLS + 32, r, h, h ? c1 : c0);
+          }
         }
         fp8cvt::tmem_st_fence();
         tc::mbar_arrive(&s.conv[st]);
@@ -491,7 +515,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             } else {
               y = g[j];
             }
-            p.out[(size_t)(row0 + c + j) * p.n_out + n] = __float2bfloat16_rn(y);
+            const size_t o = (size_t)(row0 + c + j) * p.n_out + n;
+            if (FP8 && p.out_f16) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(fminf(fmaxf(y, -65504.f), 65504.f));
+            else p.out[o] = __float2bfloat16_rn(y);
           }
         }
       }
@@ -672,7 +698,8 @@ EXO_API long exo_moe_plan_ints(int E, int max_tiles) { return 3L * E + 1 + 4L * 
 // form [E, 2F/128, H/64, 8448] / [E, ceil(H/128), F/64, 8448]; 0 = bf16 weights.
 EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const void* w_down, const void* weights,
                                     const void* ids, void* out, void* scratch, void* pos, void* xs, void* hs, void* ys, int T,
-                                    int k, int H, int F, int E, int expert_offset, int scale_kind, int tile_rows, cudaStream_t st) {
+                                    int k, int H, int F, int E, int expert_offset, int scale_kind, int tile_rows, int f16_operands, cudaStream_t st) {
+  const int f16 = (scale_kind && f16_operands) ? 1 : 0;
   if (T <= 0) return 0;
   if (E > 1024 || H % 8 || F % 8 || H < BK || F < BK) return -2;
   if (scale_kind && (H % 64 || F % 128)) return -2;      // whole K tiles; gate and up halves on tile boundaries
@@ -688,13 +715,13 @@ EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const 
   int* plan = cursor + E;
   if (P <= 4096) {      // decode batches: the whole plan in one block, then a plain row gather
     moe_plan_small_kernel<<<1, 1024, 0, st>>>((const int*)ids, P, expert_offset, E, bn, max_tiles, plan, (int*)pos);
-    moe_gather_rows_kernel<<<(P + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const int*)pos, P, k, H, (__nv_bfloat16*)xs);
+    moe_gather_rows_kernel<<<(P + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const int*)pos, P, k, H, (__nv_bfloat16*)xs, f16);
   } else {
     if (cudaMemsetAsync(counts, 0, sizeof(int) * E, st) != cudaSuccess) return -7;
     moe_count_kernel<<<(P + 255) / 256, 256, 0, st>>>((const int*)ids, P, expert_offset, E, counts);
     moe_plan_kernel<<<1, 1024, 0, st>>>(counts, E, bn, max_tiles, offsets, cursor, plan);
     moe_scatter_kernel<<<(P + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const int*)ids, P, k, H, expert_offset, E, offsets,
-                                                    cursor, (int*)pos, (__nv_bfloat16*)xs);
+                                                    cursor, (int*)pos, (__nv_bfloat16*)xs, f16);
   }
   EXO_CHECK_LAUNCH();
   const CUtensorMap* t_xs = exo_tmap_2d_bf16(xs, P, H, bn);
@@ -707,11 +734,13 @@ EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const 
   g.plan = plan; g.err = err;
   g.rows_w = 2 * F; g.n_out = F; g.K = H; g.out = (__nv_bfloat16*)hs;
   g.scale_kind = scale_kind;
+  g.f16 = f16; g.out_f16 = f16;
   g.tiles = scale_kind ? (const uint8_t*)w_gate_up : nullptr;
   g.nt = 2 * F / BM; g.kt = H / BK;
   int rc = grouped_dispatch<true>(bn, t_wgu, t_xs, g, (F + BM - 1) / BM, max_tiles, st);
   if (rc) return rc;
   g.rows_w = H; g.n_out = H; g.K = F; g.out = (__nv_bfloat16*)ys;
+  g.out_f16 = 0;
   g.tiles = scale_kind ? (const uint8_t*)w_down : nullptr;
   g.nt = (H + BM - 1) / BM; g.kt = F / BK;
   rc = grouped_dispatch<false>(bn, t_wd, t_hs, g, (H + BM - 1) / BM, max_tiles, st);

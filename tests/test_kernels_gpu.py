@@ -318,9 +318,15 @@ def test_moe_experts_fp8(K, kind, T, E, k, H, F, offset, E_all):
     wd = quant.quantize((torch.randn(E, H, F, device="cuda", generator=g) / math.sqrt(F)).bfloat16(), kind)
     logits = torch.randn(T, E_all, device="cuda", generator=g)
     w, ids = ref.moe_route(logits, k, "softmax", True)
-    out = K.moe_experts(x, wgu, wd, w, ids, offset)
-    assert K.load().exo_gemm_last_error() == 0
-    close(out, ref.moe_experts(x, wgu, wd, w, ids, offset), 2e-2, 2e-2)
+    want = ref.moe_experts(x, wgu, wd, w, ids, offset)
+    for f16 in (True, False):       # f16 operands on both sides of the MMAs (default) and the bf16 form
+        K.fp8_f16_operands = f16
+        try:
+            out = K.moe_experts(x, wgu, wd, w, ids, offset)
+        finally:
+            K.fp8_f16_operands = True
+        assert K.load().exo_gemm_last_error() == 0
+        close(out, want, 2e-2, 2e-2)
 
 
 @pytest.mark.parametrize("M,F,K_", [(256, 512, 256), (700, 1792, 1024), (2048, 1000, 512)])
