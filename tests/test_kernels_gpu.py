@@ -295,11 +295,11 @@ def test_gemm_fp8_weights(K, kind, M, N, K_):
     assert K.load().exo_gemm_last_error() == 0
     close(out, want, 1e-2, 1e-2)
     # the other operand form (f16 on both sides of the MMA by default, bf16 as the alternative) agrees
-    K.fp8_f16_operands = not K.fp8_f16_operands
+    old_min, K.FP8_F16_MIN_WEIGHTS = K.FP8_F16_MIN_WEIGHTS, 0          # small test shapes take the f16 form too
     try:
         other = K.linear(x, wq, bias, res)
     finally:
-        K.fp8_f16_operands = not K.fp8_f16_operands
+        K.FP8_F16_MIN_WEIGHTS = old_min
     assert K.load().exo_gemm_last_error() == 0
     close(other, want, 1e-2, 1e-2)
     # against the unquantised weights the error is the fp8 rounding (2^-4 relative per weight, averaged down by the sum)
