@@ -34,12 +34,70 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ re
     out[row * cols + c] = Cvt<T>::from_f(Cvt<T>::to_f(hr[c]) * rstd * Cvt<T>::to_f(w[c]));
 }
 
+// bf16 rows of up to 512 * VPT * 8 values: every thread keeps its 16-byte vectors in registers, so the row is read
+// once (x and the residual), summed, and written once (the new residual stream and the normalised row).
+template <int VPT>
+__global__ void __launch_bounds__(512) rmsnorm_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res,
+                                                          const uint4* __restrict__ w, uint4* __restrict__ out,
+                                                          uint4* __restrict__ h_out, int nvec, float eps) {
+  __shared__ float red[32];
+  const size_t base = (size_t)blockIdx.x * nvec;
+  pdl_trigger();
+  pdl_wait();
+  float h[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; j++) {
+    const int v = threadIdx.x + j * 512;
+    if (v < nvec) {
+      unpack8(x[base + v], h[j]);
+      if (res) {
+        float r[8];
+        unpack8(res[base + v], r);
+#pragma unroll
+        for (int e = 0; e < 8; e++) h[j][e] += r[e];
+        const uint4 hq = pack8(h[j]);
+        h_out[base + v] = hq;
+        unpack8(hq, h[j]);      // normalise the value the residual stream actually keeps
+      }
+#pragma unroll
+      for (int e = 0; e < 8; e++) ss += h[j][e] * h[j][e];
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / (nvec * 8) + eps);
+#pragma unroll
+  for (int j = 0; j < VPT; j++) {
+    const int v = threadIdx.x + j * 512;
+    if (v < nvec) {
+      float wf[8];
+      unpack8(w[v], wf);
+#pragma unroll
+      for (int e = 0; e < 8; e++) h[j][e] = h[j][e] * rstd * wf[e];
+      out[base + v] = pack8(h[j]);
+    }
+  }
+}
+
 EXO_API int exo_rmsnorm(const void* x, const void* res, const void* w, void* out, void* h_out, int rows, int cols,
                         float eps, int dtype, cudaStream_t st) {
   if (rows == 0) return 0;
   if (res && !h_out) return -2;
   int threads = cols >= 2048 ? 512 : 256;
   cudaError_t e;
+  const bool aligned = !(((uintptr_t)x | (uintptr_t)res | (uintptr_t)w | (uintptr_t)out | (uintptr_t)h_out) & 15);
+  if (dtype == EXO_BF16 && cols % 8 == 0 && cols >= 1024 && cols <= 512 * 4 * 8 && aligned) {
+    const int nvec = cols / 8;
+#define RV(V)                                                                                                        \
+  e = launch_pdl(rmsnorm_vec_kernel<V>, dim3(rows), dim3(512), 0, st, (const uint4*)x, (const uint4*)res, (const uint4*)w, \
+                 (uint4*)out, (uint4*)h_out, nvec, eps)
+    if (nvec <= 512) RV(1);
+    else if (nvec <= 1024) RV(2);
+    else RV(4);
+#undef RV
+    if (e != cudaSuccess) return (int)e;
+    EXO_CHECK_LAUNCH();
+    return 0;
+  }
   if (dtype == EXO_BF16)
     e = launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, st, (const __nv_bfloat16*)x,
                    (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (__nv_bfloat16*)h_out, cols,
