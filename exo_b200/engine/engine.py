@@ -57,13 +57,15 @@ class Engine:
 
     # ---- requests ----
     def submit(self, prompt: list[int], params: SamplingParams | None = None, req_id: str | None = None,
-               use_prefix_cache: bool = True, media=None, kv_prefill=None) -> str:
-        """Queue a request.  ``kv_prefill = (n_tokens, [(k, v) per local layer])`` installs KV computed
+               use_prefix_cache: bool = True, media=None, kv_prefill=None, embeds=None) -> str:
+        """Queue a request.  ``embeds = [(position, rows [n, hidden])]`` replaces the token embeddings of those prompt
+        positions (image features spliced over placeholder tokens; ``media`` carries their content hashes for the prefix cache).  ``kv_prefill = (n_tokens, [(k, v) per local layer])`` installs KV computed
         elsewhere (a prefill instance) for the first ``n_tokens`` prompt tokens; prefill continues after them."""
         rid = req_id or uuid.uuid4().hex
         if not prompt:
             raise ValueError("empty prompt")
         s = Sequence(rid, list(prompt), params or SamplingParams(), media=media, use_prefix_cache=use_prefix_cache)
+        s.embeds = list(embeds) if embeds else None
         if kv_prefill is not None:
             n, layers = kv_prefill
             n = min(int(n), len(prompt) - 1)       # the last prompt token is always computed here (it yields the logits)
@@ -76,6 +78,19 @@ class Engine:
         self.seqs[rid] = s
         self.sched.add(s)
         return rid
+
+    def _embed_patches(self, entries) -> list | None:
+        """Rows of this step's packed token batch whose embeddings come from ``Sequence.embeds``: ``[(row, rows)]``."""
+        out, row = [], 0
+        for s, n in entries:
+            if s.embeds and s.n_computed < len(s.prompt):
+                lo, hi = s.n_computed, s.n_computed + n
+                for start, t in s.embeds:
+                    a, b = max(lo, start), min(hi, start + t.shape[0])
+                    if a < b:
+                        out.append((row + a - lo, t[a - start:b - start]))
+            row += n
+        return out or None
 
     # ---- KV hand-over (prefill/decode disaggregation) ----
     def _slots(self, blocks: list[int], n_tokens: int) -> torch.Tensor:
@@ -139,6 +154,7 @@ class Engine:
         proc = self._processor(entries)
         if want_lp and proc is None:
             proc = lambda x: x  # noqa: E731 - forces the eager path that keeps logits
+        self.exe.model.embed_patches = self._embed_patches(entries)
         ids = self.exe.run(plan, proc)
         sampled = self.exe.fetch(ids)
         lp = None

@@ -168,6 +168,7 @@ class Sequence:
     n_published: int = 0         # full blocks already registered in the prefix cache
     finished: bool = False
     finish_reason: str | None = None
+    embeds: list | None = None   # [(first prompt position, rows [n, hidden])]: input embeddings that replace the token embeddings (vision)
     cancelled: bool = False
     t_submit: float = 0.0
     t_first_token: float = 0.0

@@ -177,6 +177,11 @@ class Decoder:
         local-vocab logits ``[B', V/N]``; other stages return ``h`` to send to the next stage."""
         cfg, w = self.cfg, self.w
         h = ops.embedding(w.embed, inp.tokens) if self.spec.is_first_stage else hidden_in
+        patches = getattr(self, "embed_patches", None)
+        if patches and self.spec.is_first_stage:      # input embeddings supplied by the caller (image features); prefill steps only
+            for r0, rows in patches:
+                h[r0:r0 + rows.shape[0]] = rows.to(device=h.device, dtype=h.dtype)
+            self.embed_patches = None
         for i in self.spec.layers(cfg):
             lw = w.layers[i]
             h = (self._attn_mla if cfg.mla else self._attn_gqa)(lw, h, inp, kv.layers[i])

@@ -116,6 +116,28 @@ class ServingEngine(Engine):
         self.prefill_running: dict[str, tuple[_PrefillJob, Any, int]] = {}
         self.remote: dict[str, _RemoteFetch] = {}
         self.remote_prefills = 0
+        self.vision = None          # VisionProcessor, built on the first request that carries images
+
+    # ---- images ----
+    def _with_images(self, ids: list[int], images: list[str]):
+        """Prompt ids with every image expanded to its feature rows: ``(ids, embeds, media)`` for the token engine.
+        Single-rank engines only (the plan broadcast to other ranks carries token ids, not embeddings)."""
+        from .vision import VisionConfig, VisionProcessor, VisionTower, splice
+        exe = self.te.exe
+        if exe.spec.tp_size * exe.spec.pp_size != 1:
+            raise ValueError("image inputs need a single-rank instance")
+        if self.vision is None:
+            dtype = torch.float32 if exe.device.type == "cpu" else torch.bfloat16
+            self.vision = VisionProcessor(VisionTower(VisionConfig(out_hidden=self.cfg.hidden), exe.device, dtype))
+        feats = [self.vision.features(b) for b in images]
+        ph = None
+        conv = getattr(self.tok, "convert_tokens_to_ids", None)
+        if conv is not None:
+            cand = conv("<|image_pad|>")
+            if isinstance(cand, int) and cand >= 0 and cand != getattr(self.tok, "unk_token_id", None):
+                ph = cand
+        fill = ph if ph is not None else (getattr(self.tok, "pad_token_id", None) or 0)
+        return splice(ids, ph, feats, fill)
 
     # ---- Engine interface ----
     def warmup(self) -> None:
@@ -237,6 +259,9 @@ class ServingEngine(Engine):
         ids = self.tok.encode(text, add_special_tokens=not getattr(self.tok, "chat_template", None))
         if not ids:
             ids = [getattr(self.tok, "bos_token_id", 0) or 0]
+        embeds = media = None
+        if p.images:
+            ids, embeds, media = self._with_images(ids, list(p.images))
         if len(ids) >= self.cfg.max_position:
             raise ValueError(f"prompt of {len(ids)} tokens exceeds the context length {self.cfg.max_position}")
         parser = None
@@ -251,10 +276,11 @@ class ServingEngine(Engine):
         stops = [p.stop] if isinstance(p.stop, str) else list(p.stop or [])
         rid = str(task.task_id)
         self.reqs[rid] = _Request(task, ids, Detokenizer(self.tok, ids), parser, stops)
-        if self._want_remote_prefill(p, ids):
+        if embeds is None and self._want_remote_prefill(p, ids):
             self.remote[rid] = _RemoteFetch(task, ids, p.prefill_endpoint, self.model_id)
             return
-        self.te.submit(ids, self._sampling(p), req_id=rid, use_prefix_cache=p.use_prefix_cache or not p.bench)
+        self.te.submit(ids, self._sampling(p), req_id=rid, use_prefix_cache=p.use_prefix_cache or not p.bench, media=media,
+                       embeds=embeds)
 
     def cancel(self, task_id: TaskId) -> None:
         r = self.reqs.pop(str(task_id), None)

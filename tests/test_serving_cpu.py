@@ -157,3 +157,30 @@ def test_two_stage_pipeline_serving_on_gloo_matches_single_rank(tmp_path):
     evs = drive(inst2, n2, r2, lambda: [t2])
     two = [e.chunk.token_id for e in evs if isinstance(e, ChunkGenerated) and isinstance(e.chunk, TokenChunk)]
     assert len(two) == 8 and two == one
+
+
+def test_image_inputs_reach_the_engine_as_spliced_features(tmp_path):
+    """A request with images: the runner encodes them, the prompt grows by the images' feature rows, different
+    images give different continuations, and the same image again hits the prefix cache."""
+    import base64
+    import io
+
+    import numpy as np
+    from PIL import Image
+
+    def png(seed):
+        buf = io.BytesIO()
+        Image.fromarray((np.random.default_rng(seed).random((56, 84, 3)) * 255).astype("uint8")).save(buf, format="PNG")
+        return base64.b64encode(buf.getvalue()).decode()
+    d, cfg = make_checkpoint(tmp_path)
+    inst, nodes, rids = instance(d, 1)
+    plain = gen_task(inst, "describe", max_output_tokens=6)
+    a1 = gen_task(inst, "describe", max_output_tokens=6, images=[png(1)])
+    b = gen_task(inst, "describe", max_output_tokens=6, images=[png(2)])
+    a2 = gen_task(inst, "describe", max_output_tokens=6, images=[png(1)])
+    evs = drive(inst, nodes, rids, lambda: [plain, a1, b, a2])
+    finals = [c for c in (e.chunk for e in evs if isinstance(e, ChunkGenerated) and isinstance(e.chunk, TokenChunk)) if c.finish_reason]
+    assert len(finals) == 4, [c.finish_reason for c in finals]
+    n_plain, n_a1, n_b, n_a2 = (c.usage.prompt_tokens for c in finals)
+    assert n_a1 == n_b == n_a2 and n_a1 - n_plain == 6          # 84x56 pixels = 3 x 2 cells of 28 pixels
+    assert finals[3].usage.prompt_tokens_details.cached_tokens > 0 and finals[1].usage.prompt_tokens_details.cached_tokens == 0

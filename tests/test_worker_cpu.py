@@ -125,10 +125,10 @@ def _run_supervised(inst, nodes, rids, script):
         async with anyio.create_task_group() as tg:
             tg.start_soon(s.run)
             await script(s)
-            with anyio.move_on_after(20):
+            with anyio.move_on_after(45):     # a loaded machine takes seconds to spawn the child and to notice its death
                 while not isinstance(s.status, (RunnerShutdown, RunnerFailed)):
                     await anyio.sleep(0.05)
-            await anyio.sleep(0.3)
+            await anyio.sleep(1.0)
             out.extend(ev_r.collect())
             tg.cancel_scope.cancel()
     anyio.run(main)
