@@ -98,3 +98,24 @@ def test_bf16_moe_and_fp8_models_on_gpu_track_the_cpu_definition(name, quant):
     got = e2.exe.last_logits.float()[0].cpu()
     err = (got - want).abs().max().item()
     assert err < 0.06 * want.abs().max().item() + 0.06, err
+
+
+def test_embedding_splice_on_gpu_equals_the_tokens_it_stands_for():
+    """Feature rows passed as ``embeds`` replace the placeholder tokens' embeddings in the GPU prefill step too."""
+    from dataclasses import replace
+    cfg = replace(preset("tiny-llama"), dtype="bf16")
+    w = build_weights(cfg, ShardSpec(), RandomSource(seed=0, dtype=torch.bfloat16), device="cuda")
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(5, cfg.vocab, (300,), generator=g).tolist()
+    stand_in = torch.randint(5, cfg.vocab, (40,), generator=g).tolist()
+    real = prompt[:100] + stand_in + prompt[140:]
+    holes = prompt[:100] + [0] * 40 + prompt[140:]
+    rows = w.embed[torch.tensor(stand_in, device="cuda")]
+    want = Engine(cfg, w, n_blocks=64, device="cuda").generate(real, SamplingParams(max_tokens=6, **GREEDY))
+    for chunk in (4096, 128):
+        eng = Engine(cfg, w, n_blocks=64, device="cuda", prefill_chunk=chunk)
+        rid = eng.submit(holes, SamplingParams(max_tokens=6, **GREEDY), embeds=[(100, rows)], media=[(100, 140, b"x" * 32)])
+        got = []
+        while eng.has_work:
+            got += [o.token for o in eng.step() if o.req_id == rid and o.token is not None]
+        assert got == want, (chunk, got, want)
