@@ -37,9 +37,15 @@ class Executor:
         self.max_T, self.max_B = max_tokens_per_step, max_seqs
         words = PlanLayout(max(self.max_T, self.max_B), self.max_B, self.max_blocks).words
         self.cuda = self.device.type == "cuda"
-        self.host = torch.zeros(words, dtype=torch.int32, pin_memory=self.cuda)
-        self.host_np = self.host.numpy()
+        # Pinned staging for the packed plan: a small ring, so that a caller which queues several steps without
+        # reading results back never overwrites a buffer whose host-to-device copy is still pending (a slot is
+        # reused only after the event recorded behind its copy has completed).
+        self.hosts = [torch.zeros(words, dtype=torch.int32, pin_memory=self.cuda) for _ in range(4 if self.cuda else 1)]
+        self.hosts_np = [h.numpy() for h in self.hosts]
+        self.host_events: list[torch.cuda.Event | None] = [None] * len(self.hosts)
+        self.n_runs = 0
         self.dev = torch.zeros(words, dtype=torch.int32, device=self.device)
+        self.n_blocks = n_blocks
         # MLA attention is still PyTorch ops with host reads of the sequence lengths: such a step cannot be captured
         self.use_graphs = (self.cuda and not cfg.mla) if use_graphs is None else use_graphs
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
@@ -109,6 +115,19 @@ class Executor:
         self.prev_sampled[:ids.numel()].copy_(ids)
         return ids
 
+    def _validate(self, plan: StepPlan) -> None:
+        """Reject a plan that addresses KV storage this rank does not have.  The kernels index the pool with the
+        plan's slots and block tables unchecked; the leader's allocator and this rank's pool are sized from an
+        agreed block count, and this is the guard behind that agreement."""
+        n_slots = self.n_blocks * self.block_size
+        if plan.n_tokens and (int(plan.slots.max()) >= n_slots or int(plan.slots.min()) < 0):
+            raise ValueError(f"step plan writes KV slot {int(plan.slots.max())} outside this rank's pool of {n_slots} slots")
+        if plan.block_tables.size and (int(plan.block_tables.max()) >= self.n_blocks or int(plan.block_tables.min()) < 0):
+            raise ValueError(f"step plan reads KV block {int(plan.block_tables.max())} outside this rank's pool of "
+                             f"{self.n_blocks} blocks")
+        if plan.block_tables.shape[1] > self.max_blocks and plan.is_decode:
+            raise ValueError("step plan's block table is wider than this rank's decode graphs")
+
     # ------------------------------------------------------------------ step
     def run(self, plan: StepPlan, logits_processor=None) -> torch.Tensor:
         """Execute one step; returns the sampled ids ``[n_seqs]`` on device (int32)."""
@@ -119,8 +138,17 @@ class Executor:
         else:
             bB, bT = plan.n_seqs, plan.n_tokens
         mb = self.max_blocks if decode else max(1, plan.block_tables.shape[1])
-        L = plan.pack(self.host_np, bT, bB, mb)
-        self.dev[:L.words].copy_(self.host[:L.words], non_blocking=True)
+        self._validate(plan)
+        slot = self.n_runs % len(self.hosts)
+        self.n_runs += 1
+        if self.host_events[slot] is not None:
+            self.host_events[slot].synchronize()
+        L = plan.pack(self.hosts_np[slot], bT, bB, mb)
+        self.dev[:L.words].copy_(self.hosts[slot][:L.words], non_blocking=True)
+        if self.cuda:
+            ev = self.host_events[slot] or torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self.host_events[slot] = ev
         self.h2d_bytes += L.words * 4
         greedy = bool(plan.flags & FLAG_ALL_GREEDY)
         from_prev = bool(plan.flags & 1)
@@ -172,5 +200,8 @@ class Executor:
         self.out_host[:n].copy_(ids, non_blocking=True)
         if self.cuda:
             torch.cuda.current_stream(self.device).synchronize()
+            # the step's kernels have completed: an expired device-side wait (a peer that stopped answering, a stuck
+            # pipeline) must end the runner instead of streaming tokens made from unsummed data
+            ops.cuda_ops().check_status(self.device)
         self.d2h_bytes += n * 4
         return self.out_host[:n].numpy().copy()

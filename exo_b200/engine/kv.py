@@ -176,7 +176,6 @@ class Sequence:
     t_prefill_start: float = 0.0
     rng_state: int = 0
     final_blocks: list[int] = field(default_factory=list)   # block ids at the moment the sequence finished
-    embeds: object | None = None  # optional [n_prompt, H] tensor rows replacing token embeddings (vision)
 
     @property
     def tokens(self) -> list[int]:

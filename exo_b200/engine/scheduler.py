@@ -123,9 +123,12 @@ class Scheduler:
         """Pick the work of the next step.  Returns the plan and ``[(seq, n_new_tokens)]``."""
         entries: list[tuple[Sequence, int]] = []
         budget = self.prefill_chunk
-        # 1. decode tokens of running sequences (and continuation chunks of running prefills)
+        # 1. decode tokens of running sequences (and continuation chunks of running prefills).  Blocks are secured
+        #    for every decoding sequence first: making room may preempt a sequence that was looked at earlier in
+        #    this very call, so the entries are only built once no further eviction can happen.
+        decoding: list[Sequence] = []
         for s in list(self.running):
-            if s.in_prefill:
+            if s.in_prefill or s not in self.running:
                 continue
             while not self._ensure_blocks(s, s.n_tokens):
                 if not self._preempt_one(s):
@@ -133,8 +136,11 @@ class Scheduler:
                     break
             if s.finished or s not in self.running:
                 continue
-            entries.append((s, 1))
-            budget -= 1
+            decoding.append(s)
+        for s in decoding:
+            if s in self.running and not s.finished:      # still seated after the later sequences' preemptions
+                entries.append((s, 1))
+                budget -= 1
         for s in list(self.running):
             if not s.in_prefill or budget <= 0:
                 continue

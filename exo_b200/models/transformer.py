@@ -59,8 +59,18 @@ class StepInputs:
 
 
 def resolve(h):
-    """Tensor behind ``h``: a tensor-parallel hand-over (``parallel.fused.Handover``) is finished first."""
+    """Tensor behind ``h``: a pending tensor-parallel reduction (``parallel.fused.Handover`` / ``Reduction``) is
+    finished first."""
     return h if isinstance(h, torch.Tensor) or h is None else h.value()
+
+
+def reduced_and_normed(h, norm_w, eps):
+    """``(h, rmsnorm(h) * norm_w)`` where ``h`` may still be a pending reduction: the sum over ranks, the residual
+    add and the norm are then one kernel."""
+    if isinstance(h, torch.Tensor):
+        return h, ops.rmsnorm(h, norm_w, eps)[0]
+    x = h.norm(norm_w, eps)
+    return h.value(), x
 
 
 class KVPool:
@@ -125,9 +135,8 @@ class Decoder:
 
     def _attn_mla(self, lw, h, inp: StepInputs, kv) -> torch.Tensor:
         cfg = self.cfg
-        h = resolve(h)
+        h, x = reduced_and_normed(h, lw.attn_norm, cfg.rms_eps)
         T = h.shape[0]
-        x, _ = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps)
         if lw.wq_a is not None:
             q = ops.norm_linear(ops.linear(x, lw.wq_a), lw.q_a_norm, cfg.rms_eps, lw.wq_b)
         else:
@@ -160,8 +169,7 @@ class Decoder:
         ranks of the weighted expert outputs (shared-expert partial folded into the same sum).
         """
         cfg = self.cfg
-        h = resolve(h)
-        x, _ = ops.rmsnorm(h, lw.ffn_norm, cfg.rms_eps)
+        h, x = reduced_and_normed(h, lw.ffn_norm, cfg.rms_eps)
         logits = ops.linear(x, lw.router)
         wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, cfg.router, cfg.norm_topk_prob, lw.router_bias,
                                  cfg.n_group, cfg.topk_group, cfg.routed_scaling)

@@ -9,6 +9,10 @@
 //                    status  int32 at +512                       device-side error word (timeouts)
 //   [4 KB, ...)      staging [2 parities][n_ranks][slot_bytes]   partials pushed by each source rank
 //   [... , end)      gather  [gather_bytes]                      all-gather target (vocab logits)
+//   then             hand-over staging, and the regions of the in-switch reduction (see "reduce + norm" below):
+//                    partial [2 parities][x_bytes]  this rank's not-yet-reduced projection output
+//                    hbuf / nbuf [2][x_bytes]       residual stream / normalised rows written by the two-shot form
+//   header +2048     barrier flags int32 [2 parities][8] "partial ready", +2112 [2][8] "rows broadcast", +2176 tickets [2]
 //
 // One-shot all-reduce (small / decode-sized tensors): every rank pushes its partial into every
 // rank's staging[parity][src], signals with a release-scoped remote atomic, waits (bounded) until
@@ -19,6 +23,7 @@
 // Waits are bounded by a globaltimer budget: on expiry the kernel records an error code in the
 // status word and returns normally, so the context stays usable and the host raises.
 #include "common.cuh"
+#include "status.h"
 #include "tp_handover.cuh"
 
 namespace {
@@ -27,7 +32,7 @@ constexpr int MAX_RANKS = 8;
 // hand-over region of the header: flags int32 [2][8] at +1024, producer tickets [2] at +1280, consumer tickets [2] at +1344
 constexpr size_t HO_FLAGS = 1024, HO_PTICKET = 1280, HO_CTICKET = 1344;
 constexpr size_t HDR_BYTES = 4096;
-constexpr unsigned long long WAIT_NS = 2000000000ull;  // 2 s
+constexpr size_t BAR_IN = 2048, BAR_OUT = 2112, BAR_TICKET = 2176;
 
 struct CommCtx {
   uint8_t* arena[MAX_RANKS];  // arena[r] = base of rank r's arena as mapped in this process
@@ -36,6 +41,11 @@ struct CommCtx {
   size_t gather_off;          // byte offset of the gather region
   size_t handover_off;        // byte offset of the hand-over staging [2 parities][n][handover_slot] (0 = none)
   size_t handover_slot;       // bytes of one hand-over slot
+  uint8_t* mc;                // multicast address of the arena (nullptr: plain peer loads / stores)
+  size_t x_off, x_bytes;      // partial buffers [2 parities][x_bytes] (0 = none)
+  size_t h_off, n_off;        // two-shot outputs [2][x_bytes]: residual stream, normalised rows
+  int* status;                // device-writable status word (host-mapped)
+  unsigned long long wait_ns; // budget of every wait on a peer
 };
 
 __device__ __forceinline__ int* flag_ptr(uint8_t* arena, int parity, int src) {
@@ -72,9 +82,9 @@ __device__ bool wait_all(const CommCtx& c, int parity, int need) {
     const int* f = flag_ptr(c.arena[c.rank], parity, threadIdx.x);
     unsigned long long t0 = gtime();
     while (ld_acquire_sys(f) < need) {
-      if (gtime() - t0 > WAIT_NS) {
+      if (gtime() - t0 > c.wait_ns) {
         ok_s = 0;
-        atomicExch(reinterpret_cast<int*>(c.arena[c.rank] + 512), 4 /* peer timeout */);
+        atomicExch(c.status, 4 /* peer timeout */);
         break;
       }
       __nanosleep(64);
@@ -212,6 +222,187 @@ allgather_cols_kernel(const CommCtx c, const uint4* __restrict__ in, int rows, i
   finish_and_reset(c, parity);
 }
 
+
+// ---- reduce + norm: the all-reduce after a row-parallel projection, fused with the residual add and the RMSNorm ----
+//
+// The projection (our GEMM) writes this rank's partial  y_r [rows, cols]  into partial[parity] of its OWN arena: no
+// peer stores.  One kernel then forms   h = residual + sum_r y_r   and   x = RMSNorm(h) * w:
+//   * one-shot (decode batches): every rank reduces every row.  With the multicast mapping one
+//     `multimem.ld_reduce` per 16 bytes returns the sum over all ranks, formed inside NVSwitch; without it the rows
+//     are read from each peer's arena with plain loads and summed in rank order.
+//   * two-shot (prefill chunks): rank j reduces rows [j R, (j+1) R) only, and writes its h and x rows into every
+//     rank's hbuf / nbuf (`multimem.st`, or peer stores): (n-1)/n + 2/n of the tensor per direction instead of n-1.
+// Synchronisation: CTA 0 raises "partial ready" on every rank once (one remote atomic per peer and collective, not
+// per CTA); every CTA waits for all ranks' flags (bounded).  The last CTA of the grid (local ticket) clears the
+// flags of the parity; in the two-shot form it first raises "rows broadcast" on every rank and waits for everyone
+// else's, so that when the kernel completes all rows have landed.  Parities alternate per collective, and a rank
+// cannot get two collectives ahead of a peer (it needs that peer's next partial), which is what makes reuse safe.
+
+__device__ __forceinline__ int* bar_ptr(uint8_t* arena, size_t base, int parity, int src) {
+  return reinterpret_cast<int*>(arena + base) + parity * MAX_RANKS + src;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_st16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Bounded wait of the whole CTA until every rank has raised flag (base, parity) at least once.
+__device__ bool wait_ranks(const CommCtx& c, size_t base, int parity) {
+  __shared__ int ok_w;
+  if (threadIdx.x == 0) ok_w = 1;
+  __syncthreads();
+  if (threadIdx.x < c.n) {
+    const int* f = bar_ptr(c.arena[c.rank], base, parity, threadIdx.x);
+    const unsigned long long t0 = gtime();
+    while (ld_acquire_sys(f) < 1) {
+      if (gtime() - t0 > c.wait_ns) {
+        ok_w = 0;
+        atomicExch(c.status, 4 /* peer timeout */);
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  __syncthreads();
+  return ok_w != 0;
+}
+
+constexpr int RN_THREADS = 256;
+constexpr int RN_VPT = 4;   // 16-byte vectors per thread and row: rows of up to 8192 elements stay in registers
+
+// Sum over ranks of one 16-byte vector of partial[parity] at element offset `off`.
+template <bool MC>
+__device__ __forceinline__ void reduce_vec(const CommCtx& c, int parity, size_t off, float* acc) {
+  const size_t byte_off = c.x_off + (size_t)parity * c.x_bytes + off * 2;
+  if constexpr (MC) {
+    unpack8(multimem_ld_reduce_bf16x8(c.mc + byte_off), acc);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; e++) acc[e] = 0.f;
+    for (int r = 0; r < c.n; r++) {
+      float f[8];
+      unpack8(ld_cg16(c.arena[r] + byte_off), f);
+#pragma unroll
+      for (int e = 0; e < 8; e++) acc[e] += f[e];
+    }
+  }
+}
+
+// TWO = false: h_out / x_out are this rank's private [rows, cols] tensors and every rank computes all rows.
+// TWO = true:  this rank computes rows [rank R, (rank + 1) R) and broadcasts them into hbuf / nbuf[parity] of every rank.
+template <bool MC, bool TWO>
+__global__ void __launch_bounds__(RN_THREADS)
+reduce_norm_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ norm_w,
+                   float eps, __nv_bfloat16* h_out, __nv_bfloat16* x_out, int rows, int cols, int parity) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[RN_THREADS / 32];
+  __shared__ int last_s;
+  if (blockIdx.x == 0 && threadIdx.x < c.n) {
+    __threadfence_system();   // the partial was written by earlier kernels of this stream: publish it system-wide
+    red_release_sys_add(bar_ptr(c.arena[threadIdx.x], BAR_IN, parity, c.rank), 1);
+  }
+  const bool ok = wait_ranks(c, BAR_IN, parity);
+  const int n_vec = cols / 8;
+  int row0 = 0, row1 = rows;
+  if (TWO) {
+    const int per = (rows + c.n - 1) / c.n;
+    row0 = min(rows, c.rank * per);
+    row1 = min(rows, row0 + per);
+  }
+  if (ok) {
+    for (int row = row0 + blockIdx.x; row < row1; row += gridDim.x) {
+      const size_t base = (size_t)row * cols;
+      float v[RN_VPT][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < RN_VPT; j++) {
+        const int iv = threadIdx.x + j * RN_THREADS;
+        if (iv < n_vec) {
+          const size_t off = base + (size_t)iv * 8;
+          reduce_vec<MC>(c, parity, off, v[j]);
+          if (residual) {
+            float r8[8];
+            unpack8(*reinterpret_cast<const uint4*>(residual + off), r8);
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[j][e] += r8[e];
+          }
+          const uint4 packed = pack8(v[j]);          // the residual stream is kept in bf16: normalise what is stored
+          if (TWO) {
+            const size_t boff = c.h_off + (size_t)parity * c.x_bytes + off * 2;
+            if (MC) multimem_st16(c.mc + boff, packed);
+            else
+              for (int r = 0; r < c.n; r++) *reinterpret_cast<uint4*>(c.arena[r] + boff) = packed;
+          } else {
+            *reinterpret_cast<uint4*>(h_out + off) = packed;
+          }
+          unpack8(packed, v[j]);
+#pragma unroll
+          for (int e = 0; e < 8; e++) ss += v[j][e] * v[j][e];
+        }
+      }
+      if (norm_w) {
+        ss = warp_sum(ss);
+        __syncthreads();                               // red[] of the previous row has been read
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < RN_THREADS / 32; w++) tot += red[w];
+        const float rstd = rsqrtf(tot / cols + eps);
+#pragma unroll
+        for (int j = 0; j < RN_VPT; j++) {
+          const int iv = threadIdx.x + j * RN_THREADS;
+          if (iv < n_vec) {
+            const size_t off = base + (size_t)iv * 8;
+            float w8[8];
+            unpack8(*reinterpret_cast<const uint4*>(norm_w + (size_t)iv * 8), w8);
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[j][e] = v[j][e] * rstd * w8[e];
+            const uint4 packed = pack8(v[j]);
+            if (TWO) {
+              const size_t boff = c.n_off + (size_t)parity * c.x_bytes + off * 2;
+              if (MC) multimem_st16(c.mc + boff, packed);
+              else
+                for (int r = 0; r < c.n; r++) *reinterpret_cast<uint4*>(c.arena[r] + boff) = packed;
+            } else {
+              *reinterpret_cast<uint4*>(x_out + off) = packed;
+            }
+          }
+        }
+      }
+    }
+  }
+  // ---- last CTA of the grid: (two-shot) tell everyone my rows are out and wait for theirs, then clear the flags ----
+  if (TWO) __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* tk = reinterpret_cast<int*>(c.arena[c.rank] + BAR_TICKET) + parity;
+    __threadfence();
+    const int last = atomicAdd(tk, 1) == (int)gridDim.x - 1;
+    if (last) *tk = 0;
+    last_s = last;
+  }
+  __syncthreads();
+  if (!last_s) return;
+  if (TWO) {
+    __threadfence_system();
+    if (threadIdx.x < c.n) red_release_sys_add(bar_ptr(c.arena[threadIdx.x], BAR_OUT, parity, c.rank), 1);
+    wait_ranks(c, BAR_OUT, parity);
+  }
+  if (threadIdx.x < c.n) {
+    *bar_ptr(c.arena[c.rank], BAR_IN, parity, threadIdx.x) = 0;
+    if (TWO) *bar_ptr(c.arena[c.rank], BAR_OUT, parity, threadIdx.x) = 0;
+    __threadfence_system();
+  }
+}
+
 CommCtx g_ctx[16];
 bool g_ctx_set[16] = {false};
 
@@ -246,25 +437,35 @@ EXO_API size_t exo_comm_header_bytes() { return HDR_BYTES; }
 // arenas: n pointers (index = rank; own arena at [rank]).
 EXO_API size_t exo_comm_handover_bytes(int n, size_t slot) { return 2 * (size_t)n * slot; }
 
-EXO_API int exo_comm_init(void** arenas, int n, int rank, size_t slot_bytes, size_t gather_off, size_t handover_off,
-                          size_t handover_slot) {
+// `mc` = multicast address of the arena or null; x_off / x_bytes / h_off / n_off describe the regions of the
+// reduce + norm kernels (x_bytes = 0: not present).
+EXO_API int exo_comm_init(void** arenas, void* mc, int n, int rank, size_t slot_bytes, size_t gather_off, size_t handover_off,
+                          size_t handover_slot, size_t x_off, size_t x_bytes, size_t h_off, size_t n_off) {
   int dev;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || n > MAX_RANKS) return -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || n > MAX_RANKS || n < 1 || rank < 0 || rank >= n) return -1;
+  int* status = exo_status_word(EXO_STATUS_COMM);
+  if (!status) return -1;
   CommCtx c;
   for (int i = 0; i < MAX_RANKS; i++) c.arena[i] = i < n ? (uint8_t*)arenas[i] : nullptr;
   c.n = n; c.rank = rank; c.slot_bytes = slot_bytes; c.gather_off = gather_off; c.handover_off = handover_off; c.handover_slot = handover_slot;
+  c.mc = (uint8_t*)mc; c.x_off = x_off; c.x_bytes = x_bytes; c.h_off = h_off; c.n_off = n_off;
+  c.status = status;
+  c.wait_ns = exo_wait_budget_ns();
   g_ctx[dev] = c;
   g_ctx_set[dev] = true;
   return 0;
 }
 
-EXO_API int exo_comm_status() {  // reads and clears the device-side error word (synchronises)
-  int dev, v = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return 0;
-  uint8_t* a = g_ctx[dev].arena[g_ctx[dev].rank];
-  cudaMemcpy(&v, a + 512, sizeof(int), cudaMemcpyDeviceToHost);
-  if (v) cudaMemset(a + 512, 0, sizeof(int));
-  return v;
+// Forget the communicator of the current device (after its arenas have been unmapped).
+EXO_API int exo_comm_reset() {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16) return -1;
+  g_ctx_set[dev] = false;
+  return 0;
+}
+
+EXO_API int exo_comm_status() {  // reads and clears the status word of the collectives; does not touch the device
+  return exo_status_take(EXO_STATUS_COMM, 1);
 }
 
 static int grid_for(int n_vec) {
@@ -279,7 +480,8 @@ EXO_API int exo_allreduce_bf16(const void* in, const void* residual, void* out, 
   int dev;
   cudaGetDevice(&dev);
   if (dev >= 16 || !g_ctx_set[dev]) return -4;
-  const CommCtx& c = g_ctx[dev];
+  CommCtx c = g_ctx[dev];
+  c.wait_ns = exo_wait_budget_ns();
   if (n_elems % 8) return -2;
   const int n_vec = (int)(n_elems / 8);
   const size_t bytes = (size_t)n_elems * 2;
@@ -303,7 +505,8 @@ EXO_API int exo_allgather_cols_bf16(const void* in, int rows, int cols, int pari
   int dev;
   cudaGetDevice(&dev);
   if (dev >= 16 || !g_ctx_set[dev]) return -4;
-  const CommCtx& c = g_ctx[dev];
+  CommCtx c = g_ctx[dev];
+  c.wait_ns = exo_wait_budget_ns();
   if (cols % 8) return -2;
   int total = rows * (cols / 8);
   cudaError_t e = launch_pdl(allgather_cols_kernel, dim3(grid_for(total)), dim3(256), 0, st, c, (const uint4*)in, rows,
@@ -311,6 +514,59 @@ EXO_API int exo_allgather_cols_bf16(const void* in, int rows, int cols, int pari
   if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
   return 0;
+}
+
+
+// h = residual + sum over ranks of partial[parity];  x = RMSNorm(h) * norm_w  (norm_w null: h only).
+// The partial must have been written into this rank's partial[parity] region (exo_comm_region(0, parity)) by
+// earlier work of the same stream.  two_shot = 0: h_out / x_out are private tensors of the caller.
+// two_shot = 1: the results land in exo_comm_region(1 / 2, parity) on every rank; h_out / x_out are ignored.
+// rows * cols * 2 must fit the region; cols % 8 == 0 and cols <= 8192.
+EXO_API int exo_reduce_norm_bf16(const void* residual, const void* norm_w, float eps, void* h_out, void* x_out, int rows,
+                                 int cols, int parity, int two_shot, cudaStream_t st) {
+  int dev;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !g_ctx_set[dev]) return -4;
+  CommCtx c = g_ctx[dev];
+  c.wait_ns = exo_wait_budget_ns();
+  if (rows <= 0 || cols % 8 || cols > 8 * RN_THREADS * RN_VPT) return -2;
+  if (!c.x_bytes || (size_t)rows * cols * 2 > c.x_bytes) return -6;
+  const auto* res = (const __nv_bfloat16*)residual;
+  const auto* nw = (const __nv_bfloat16*)norm_w;
+  auto* ho = (__nv_bfloat16*)h_out;
+  auto* xo = (__nv_bfloat16*)x_out;
+  cudaError_t e;
+  if (two_shot) {
+    const int per = (rows + c.n - 1) / c.n;
+    const int grid = per < 148 ? per : 148;
+    e = c.mc ? launch_pdl(reduce_norm_kernel<true, true>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, cols, parity)
+             : launch_pdl(reduce_norm_kernel<false, true>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, cols, parity);
+  } else {
+    if (!h_out || (norm_w && !x_out)) return -2;
+    const int grid = rows < 296 ? rows : 296;
+    e = c.mc ? launch_pdl(reduce_norm_kernel<true, false>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, cols, parity)
+             : launch_pdl(reduce_norm_kernel<false, false>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, cols, parity);
+  }
+  if (e != cudaSuccess) return (int)e;
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+// Local address of a region of the reduce + norm kernels: which = 0 partial, 1 hbuf, 2 nbuf.
+EXO_API void* exo_comm_region(int which, int parity) {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return nullptr;
+  const CommCtx& c = g_ctx[dev];
+  if (!c.x_bytes) return nullptr;
+  const size_t off = which == 0 ? c.x_off : which == 1 ? c.h_off : c.n_off;
+  return c.arena[c.rank] + off + (size_t)(parity & 1) * c.x_bytes;
+}
+
+// 1 when the communicator of the current device reduces through the NVLink multicast mapping.
+EXO_API int exo_comm_has_multicast() {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return 0;
+  return g_ctx[dev].mc ? 1 : 0;
 }
 
 // ---- hand-over (row-parallel projection -> consumer, no collective kernel) -----------------------
@@ -324,7 +580,7 @@ __global__ void __launch_bounds__(256) handover_finish_kernel(const TpHandover h
   __shared__ int ok_s;
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
-  if (threadIdx.x < h.n_part && !tp_wait_flag(h.part_flag[threadIdx.x], h.status)) ok_s = 0;
+  if (threadIdx.x < h.n_part && !tp_wait_flag(h.part_flag[threadIdx.x], h.status, h.wait_ns)) ok_s = 0;
   __syncthreads();
   if (ok_s) {
     for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += gridDim.x * blockDim.x) {
@@ -364,7 +620,7 @@ __global__ void __launch_bounds__(256) handover_rmsnorm_kernel(const TpHandover 
   __shared__ float red[8];
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
-  if (threadIdx.x < h.n_part && !tp_wait_flag(h.part_flag[threadIdx.x], h.status)) ok_s = 0;
+  if (threadIdx.x < h.n_part && !tp_wait_flag(h.part_flag[threadIdx.x], h.status, h.wait_ns)) ok_s = 0;
   __syncthreads();
   const size_t row = (size_t)blockIdx.x * cols;
   const int n_vec = cols / 8;
@@ -427,7 +683,8 @@ int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems) {
   if (!c.handover_off || (size_t)n_elems * 2 > c.handover_slot) return -6;
   memset(out, 0, sizeof(*out));
   uint8_t* mine = c.arena[c.rank];
-  out->status = reinterpret_cast<int*>(mine + 512);
+  out->status = c.status;
+  out->wait_ns = exo_wait_budget_ns();
   if (mode == 1) {
     out->n_push = c.n;
     for (int r = 0; r < c.n; r++) {

@@ -19,6 +19,7 @@
 #include <cstdlib>
 #include <cstring>
 #include "gemm_common.cuh"
+#include "status.h"
 
 namespace {
 
@@ -168,61 +169,64 @@ struct KeyHash {
     return std::hash<uint64_t>()((uint64_t)k.base * 1000003u ^ k.rows * 7919u ^ k.cols * 104729u ^ k.box);
   }
 };
-std::unordered_map<Key, CUtensorMap*, KeyHash> g_maps;
+std::unordered_map<Key, CUtensorMap, KeyHash> g_maps;   // descriptors by value: eviction never frees what a caller holds
 std::mutex g_maps_mu;
+
+// Lookups hand out a COPY of the cached descriptor in a per-thread ring.  A launcher fetches a handful of maps
+// (weights, activations, K, V ...) and then launches, so a pointer stays valid for the next RING - 1 lookups of the
+// same thread whatever happens to the cache in between (another thread's insert may evict everything).
+constexpr int TMAP_RING = 32;
+const CUtensorMap* ring_copy(const CUtensorMap& m) {
+  thread_local CUtensorMap ring[TMAP_RING];
+  thread_local int next = 0;
+  CUtensorMap* slot = &ring[next];
+  next = (next + 1) % TMAP_RING;
+  *slot = m;
+  return slot;
+}
 
 int* g_err[16] = {nullptr};
 int* g_counters[16] = {nullptr};
 float* g_partial[16] = {nullptr};
 size_t g_partial_floats[16] = {0};
 constexpr int MAX_TILES = 1 << 16;
+constexpr size_t MAX_CACHED_MAPS = 8192;
+
+const CUtensorMap* tmap_lookup(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool bytes) {
+  std::lock_guard<std::mutex> lk(g_maps_mu);
+  Key k{base, rows, cols, box_rows | (bytes ? (1u << 31) : 0u)};
+  auto it = g_maps.find(k);
+  if (it != g_maps.end()) return ring_copy(it->second);
+  EncodeFn enc = get_encode();
+  const uint64_t el = bytes ? 1 : 2;
+  if (!enc || (cols * el) % 16 != 0 || ((uintptr_t)base & 15)) return nullptr;
+  CUtensorMap m;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * el};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&m, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   bytes ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return nullptr;
+  if (g_maps.size() >= MAX_CACHED_MAPS) g_maps.clear();  // activations come and go: bound the cache (re-encoding is cheap)
+  g_maps[k] = m;
+  return ring_copy(m);
+}
 
 }  // namespace
 
+// K-major bf16 [rows, cols] matrix, [box_rows x 64] box, 128-byte swizzle.  The returned pointer addresses a
+// per-thread copy that stays valid for the next 31 lookups made by the calling thread.
 const CUtensorMap* exo_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  std::lock_guard<std::mutex> lk(g_maps_mu);
-  Key k{base, rows, cols, box_rows};
-  auto it = g_maps.find(k);
-  if (it != g_maps.end()) return it->second;
-  EncodeFn enc = get_encode();
-  if (!enc || (cols * 2) % 16 != 0 || ((uintptr_t)base & 15)) return nullptr;
-  CUtensorMap* m = new CUtensorMap;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) { delete m; return nullptr; }
-  if (g_maps.size() > 8192) {  // activations come and go: bound the cache
-    for (auto& kv : g_maps) delete kv.second;
-    g_maps.clear();
-  }
-  g_maps[k] = m;
-  return m;
+  return tmap_lookup(base, rows, cols, box_rows, false);
 }
 
 // Row-major [rows, cols] byte matrix (fp8 payloads) with a [box_rows x 64] box, no swizzle: the
-// consumer reads the tile with ordinary shared-memory loads.
+// consumer reads the tile with ordinary shared-memory loads.  Same pointer lifetime as above.
 const CUtensorMap* exo_tmap_2d_u8(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  std::lock_guard<std::mutex> lk(g_maps_mu);
-  Key k{base, rows, cols, box_rows | (1u << 31)};
-  auto it = g_maps.find(k);
-  if (it != g_maps.end()) return it->second;
-  EncodeFn enc = get_encode();
-  if (!enc || cols % 16 != 0 || ((uintptr_t)base & 15)) return nullptr;
-  CUtensorMap* m = new CUtensorMap;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols};
-  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) { delete m; return nullptr; }
-  g_maps[k] = m;
-  return m;
+  return tmap_lookup(base, rows, cols, box_rows, true);
 }
 
 // The current device's scratch of the GEMM family (null / 0 before exo_gemm_init).
@@ -241,8 +245,8 @@ EXO_API int exo_gemm_init(long partial_floats) {
   int dev;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16) return -1;
   if (!g_err[dev]) {
-    if (cudaMalloc(&g_err[dev], sizeof(int)) != cudaSuccess) return -1;
-    cudaMemset(g_err[dev], 0, sizeof(int));
+    g_err[dev] = exo_status_word(EXO_STATUS_TC);      // host-mapped status word: the serving loop reads it without a copy
+    if (!g_err[dev]) return -1;
     if (cudaMalloc(&g_counters[dev], MAX_TILES * sizeof(int)) != cudaSuccess) return -1;
     cudaMemset(g_counters[dev], 0, MAX_TILES * sizeof(int));
   }
@@ -261,14 +265,8 @@ int* exo_tc_err_ptr() {
   return g_err[dev];
 }
 
-// Reads and clears the device error word (synchronises the device).
-EXO_API int exo_gemm_last_error() {
-  int dev, v = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_err[dev]) return 0;
-  cudaMemcpy(&v, g_err[dev], sizeof(int), cudaMemcpyDeviceToHost);
-  if (v) cudaMemset(g_err[dev], 0, sizeof(int));
-  return v;
-}
+// Reads and clears the tensor-core kernels' status word (no device access; call once the kernels have completed).
+EXO_API int exo_gemm_last_error() { return exo_status_take(EXO_STATUS_TC, 1); }
 
 template <int BN, int STAGES, bool TWO = false, bool HO = false>
 static int launch_gemm_ho(const CUtensorMap* tw, const CUtensorMap* tx, const GemmParams& p, cudaStream_t st) {
@@ -406,7 +404,8 @@ static int gemm_launch(const void* x, const void* W, const void* bias, const voi
       // that wins after rounding both to whole waves over the 148 SMs.
       const long t2 = (long)((N + 2 * BM - 1) / (2 * BM)) * ((M + 255) / 256), t1 = (long)((N + BM - 1) / BM) * ((M + 255) / 256);
       const bool two_wins = 1.74 * (double)((t2 + 147) / 148) < (double)((t1 + 147) / 148);
-      if (splits == 1 && !ho && N >= 2 * BM && two_wins && !getenv("EXO_GEMM_SINGLE_TILE"))
+      static const bool single_tile = getenv("EXO_GEMM_SINGLE_TILE") != nullptr;   // A/B switch, read once
+      if (splits == 1 && !ho && N >= 2 * BM && two_wins && !single_tile)
         return launch_gemm<256, 3, true>(tw, tx, p, st);   //  3 x 64 KB, two accumulators (512 TMEM columns)
       return launch_gemm<256, 4>(tw, tx, p, st);  //  4 x 48 KB  (one CTA per SM)
     }

@@ -16,6 +16,7 @@
 // (a stage then carries RS/2 gate rows and the matching RS/2 up rows as two copies).
 #include <cstdlib>
 #include <cstring>
+#include "status.h"
 #include "tc_common.cuh"
 #include "tp_handover.cuh"
 
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
   pdl_wait();                                 // x comes from the previous kernel
   if constexpr (HO == 2) {
     // x is handed over by the row-parallel projection of every rank: wait for all of them (bounded)
-    if (warp == 0 && lane < p.ho.n_part) tp_wait_flag(p.ho.part_flag[lane], p.ho.status);
+    if (warp == 0 && lane < p.ho.n_part) tp_wait_flag(p.ho.part_flag[lane], p.ho.status, p.ho.wait_ns);
     asm volatile("bar.sync 1, 256;" ::: "memory");
   }
   float xr[M][JV][8];
@@ -337,20 +338,12 @@ int launch_stream(const StreamParams& p, bool norm, bool swiglu, int grid, size_
 EXO_API int exo_gemv_stream_init() {
   int dev;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16) return -1;
-  if (!g_err_stream[dev]) {
-    if (cudaMalloc(&g_err_stream[dev], sizeof(int)) != cudaSuccess) return -1;
-    cudaMemset(g_err_stream[dev], 0, sizeof(int));
-  }
-  return 0;
+  if (!g_err_stream[dev]) g_err_stream[dev] = exo_status_word(EXO_STATUS_GEMV);    // host-mapped: read without a copy
+  return g_err_stream[dev] ? 0 : -1;
 }
 
-EXO_API int exo_gemv_stream_last_error() {
-  int dev, v = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_err_stream[dev]) return 0;
-  cudaMemcpy(&v, g_err_stream[dev], sizeof(int), cudaMemcpyDeviceToHost);
-  if (v) cudaMemset(g_err_stream[dev], 0, sizeof(int));
-  return v;
-}
+// Reads and clears the streaming kernels' status word (no device access; call once the kernels have completed).
+EXO_API int exo_gemv_stream_last_error() { return exo_status_take(EXO_STATUS_GEMV, 1); }
 
 // CTAs co-resident per SM (EXO_GEMV_CTAS_PER_SM, 1 or 2).  With 2, each CTA's ring is half as deep
 // and the grid twice as wide: the same bytes are in flight per SM, and a CTA of the NEXT kernel in

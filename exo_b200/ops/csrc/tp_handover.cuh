@@ -27,7 +27,8 @@ struct TpHandover {
   int n_part;
   const __nv_bfloat16* x_res;               // residual stream before the reduction (may be null)
   __nv_bfloat16* x_out;                     // reduced residual stream (written by CTA 0; may be null)
-  int* status;                              // device error word of the arena
+  int* status;                              // device-writable status word of the collectives
+  unsigned long long wait_ns;               // budget of a wait on a peer
 };
 
 __device__ __forceinline__ int tp_ld_acquire_sys(const int* p) {
@@ -49,11 +50,11 @@ __device__ __forceinline__ unsigned long long tp_gtime() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// One thread per source rank polls; returns false after ~2 s (and records code 4 in the status word).
-__device__ __forceinline__ bool tp_wait_flag(int* flag, int* status) {
+// One thread per source rank polls; returns false when the budget runs out (and records code 4 in the status word).
+__device__ __forceinline__ bool tp_wait_flag(int* flag, int* status, unsigned long long wait_ns) {
   const unsigned long long t0 = tp_gtime();
   while (tp_ld_acquire_sys(flag) < 1) {
-    if (tp_gtime() - t0 > 2000000000ull) {
+    if (tp_gtime() - t0 > wait_ns) {
       atomicExch(status, 4);
       return false;
     }

@@ -156,7 +156,7 @@ def ensure_gemm_init(device) -> None:
         _gemm_ready.add(dev)
 
 
-def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False):
+def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False, out=None):
     """tcgen05 GEMM ``x[M,K] @ w[N,K].T``; per-device scratch is set up on first use, which
     must therefore happen outside CUDA-graph capture (the executor warms up before capturing)."""
     lib = load()
@@ -169,7 +169,8 @@ def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False):
         _chk(lib.exo_gemm_bf16_swiglu(_ptr(x), _ptr(w), _ptr(out), M, N, K, _st()), "gemm_bf16_swiglu")
         _count()
         return out
-    out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    if out is None or swiglu_out:
+        out = torch.empty(M, N, dtype=x.dtype, device=x.device)
     splits = lib.exo_gemm_splits(M, N, K)
     while splits > 1 and splits * M * N > GEMM_PARTIAL_FLOATS:
         splits -= 1
@@ -179,7 +180,7 @@ def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False):
     return swiglu(out) if swiglu_out else out
 
 
-def linear_fp8(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=False):
+def linear_fp8(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=False, out=None):
     """Block-scaled fp8 weights, bf16 activations: the weights cross HBM as bytes and are widened to
     bf16 inside the tcgen05 GEMM's pipeline (every batch size; the norm is a separate kernel)."""
     M, K = x.shape
@@ -188,7 +189,8 @@ def linear_fp8(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=
         raise KernelError("fp8 weights are served with bf16 activations")
     if norm_w is not None:
         x, _ = rmsnorm(x, norm_w, eps)
-    out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    if out is None or swiglu_out:
+        out = torch.empty(M, N, dtype=x.dtype, device=x.device)
     if M == 0:
         return swiglu(out) if swiglu_out else out
     ensure_gemm_init(x.device)
@@ -213,13 +215,48 @@ def linear_fp8(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=
 
 
 def gemm_check() -> None:
-    """Raise if any tensor-core kernel since the last check recorded a wait timeout."""
+    """Raise if any tensor-core or streaming kernel since the last check recorded a wait that ran out.  The status
+    words live in host-mapped memory: this reads them without touching the device, so the kernels of interest
+    must have completed (the caller has just read back the step's results)."""
     code = load().exo_gemm_last_error()
     if code:
         raise KernelError(f"tcgen05 GEMM reported device-side timeout code {code}")
     code = load().exo_gemv_stream_last_error()
     if code:
         raise KernelError(f"streaming GEMV reported device-side timeout code {code}")
+
+
+class DeviceWaitTimeout(KernelError):
+    """A bounded wait on a peer GPU ran out inside a collective kernel (status word 2)."""
+
+
+_status_words: dict[int, "C.Array"] = {}
+
+
+def check_status(device=None) -> None:
+    """Raise if any kernel of the library recorded an expired wait since the last call.
+
+    The three status words (tensor-core kernels, streaming GEMV, peer-memory collectives) sit in pinned host
+    memory that the GPU writes directly, so this is three host loads: the serving loop calls it after every
+    step, right after the sampled ids have been read back (the step's kernels have then completed)."""
+    dev = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    words = _status_words.get(dev)
+    if words is None:
+        lib = load()
+        lib.exo_status_host_ptr.restype = C.c_void_p
+        lib.exo_status_host_ptr.argtypes = []
+        with torch.cuda.device(dev):
+            ptr = lib.exo_status_host_ptr()
+        if not ptr:
+            raise KernelError("cannot allocate the device status block")
+        words = _status_words[dev] = (C.c_int * 4).from_address(ptr)
+    tc, gemv, comm = words[0], words[1], words[2]
+    if not (tc or gemv or comm):
+        return
+    words[0] = words[1] = words[2] = 0
+    if comm:
+        raise DeviceWaitTimeout(f"cuda:{dev}: a collective kernel gave up waiting for a peer GPU (code {comm})")
+    raise KernelError(f"cuda:{dev}: a kernel's pipeline wait ran out (tensor-core code {tc}, streaming GEMV code {gemv})")
 
 
 gemm_impl = None if os.environ.get("EXO_DISABLE_TCGEN05") == "1" else gemm_bf16
@@ -239,15 +276,24 @@ def ensure_stream_init(device) -> None:
         _stream_ready.add(dev)
 
 
-def linear(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=False):
-    """Dispatch by batch rows: M <= 8 → fused small-batch kernel; bf16 larger M → tcgen05 GEMM;
-    fp32 larger M → CUDA-core tiled kernel (oracle configs only)."""
+def linear(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=False, out=None):
+    """Dispatch by batch rows: M <= 2 → streaming GEMV; bf16 larger M → tcgen05 GEMM; fp32 larger M → CUDA-core
+    tiled kernel (oracle configs only).  ``out`` (contiguous ``[M, N]``, no SwiGLU) receives the result where the
+    kernel can write it directly, else it is copied there."""
+    if out is not None:
+        M, N = x.shape[0], w.shape[0]
+        direct = (not swiglu_out and out.is_contiguous() and M > SMALL_M
+                  and (isinstance(w, Fp8Weight) or (x.dtype == torch.bfloat16 and gemm_impl is not None and norm_w is None
+                                                    and x.shape[1] >= 64 and x.shape[1] % 8 == 0)))
+        if not direct:
+            out.copy_(linear(x, w, bias, residual, norm_w, eps, swiglu_out))
+            return out
     x = x.contiguous()
     M, K = x.shape
     N = w.shape[0]
     lib = load()
     if isinstance(w, Fp8Weight):
-        return linear_fp8(x, w, bias, residual, norm_w, eps, swiglu_out)
+        return linear_fp8(x, w, bias, residual, norm_w, eps, swiglu_out, out)
     if (use_stream_gemv and 0 < M <= 2 and x.dtype == torch.bfloat16
             and lib.exo_gemv_stream_supported(M, N, K, int(swiglu_out))):
         ensure_stream_init(x.device)
@@ -266,7 +312,7 @@ def linear(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=Fals
     if norm_w is not None:
         x, _ = rmsnorm(x, norm_w, eps)
     if x.dtype == torch.bfloat16 and gemm_impl is not None and K >= 64 and K % 8 == 0:
-        return gemm_impl(x, w, bias, residual, swiglu_out)
+        return gemm_impl(x, w, bias, residual, swiglu_out, out)
     out = torch.empty(M, N, dtype=x.dtype, device=x.device)
     _chk(lib.exo_linear_tiled(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, _dt(x), _st()),
          "linear_tiled")

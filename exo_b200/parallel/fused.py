@@ -1,19 +1,33 @@
-"""Tensor-parallel communicator on NVLink peer memory: the product path.
+"""Tensor-parallel communicator on NVLink symmetric memory: the product path.
 
-Each rank allocates one arena, exports it with CUDA IPC, and maps every peer's arena
-(handles travel once through ``torch.distributed.all_gather_object``).  From then on the
-collectives of the decode / prefill hot path are our own kernels storing into peer HBM through
-NVSwitch — no NCCL call per layer.  This replaces the ``mx.distributed.all_sum`` the reference
-issues after every row-parallel projection (``src/exo/worker/engines/mlx/auto_parallel.py:465-469``
-and its ``ring`` / ``jaccl`` transports, ``src/exo/worker/engines/mlx/utils_mlx.py:104-143``).
+Each rank owns one arena.  Where the driver allows it the arena is a virtual-memory allocation whose
+file descriptor travels to the peers over a Unix socket, every rank maps every arena, and all of
+them are bound to one NVLink multicast object, so that a kernel can read the SUM of a buffer over all
+ranks with one ``multimem.ld_reduce`` (NVSwitch forms it) or write all ranks with one ``multimem.st``.
+Otherwise the arena is a ``cudaMalloc`` block shared through CUDA IPC and the same kernels use plain
+peer loads and stores.  From then on the collectives of the decode / prefill hot path are our own
+kernels — no NCCL call per layer.  This replaces the ``mx.distributed.all_sum`` the reference issues
+after every row-parallel projection (``src/exo/worker/engines/mlx/auto_parallel.py:465-469``) and its
+``ring`` / ``jaccl`` transports (``src/exo/worker/engines/mlx/utils_mlx.py:104-143``).
 
-Device-side waits are bounded (2 s): a rank whose peer never signals records an error code that
-``check()`` turns into ``CollectiveTimeout`` on the host; nothing spins forever.
+Three forms of "row-parallel projection, then sum over ranks":
+
+* batch <= 2: the streaming GEMV pushes its rows into every rank's staging slot and the next
+  RMSNorm + GEMV sums them in its prologue (:class:`Handover`): no collective kernel at all;
+* decode batches: the GEMM writes its partial into this rank's own arena and ONE kernel forms
+  ``residual + sum`` and the RMSNorm of it, reading the sum through the switch (:class:`Reduction`);
+* prefill chunks: the same kernel in its two-shot form (each rank reduces and normalises 1/N of the
+  rows and broadcasts them).
+
+Device-side waits are bounded (``EXO_COLLECTIVE_TIMEOUT_US``): a rank whose peer never signals
+records a code in a host-mapped status word that ``check()`` turns into ``CollectiveTimeout``.
 """
 from __future__ import annotations
 
 import ctypes as C
 import os
+import socket
+import uuid
 
 import torch
 import torch.distributed as dist
@@ -34,6 +48,64 @@ class _RawBuffer:
 
 
 HANDOVER_ROWS = 256           # rows of the residual stream one hand-over slot holds (decode batches)
+ONE_SHOT_MAX_BYTES = 4 << 20  # (n - 1) * tensor bytes above which the reduction goes two-shot
+
+_SIGS = {
+    "exo_symm_alloc": (C.c_void_p, [C.c_size_t]), "exo_symm_free": (C.c_int, [C.c_void_p]),
+    "exo_symm_handle": (C.c_int, [C.c_void_p, C.c_void_p]), "exo_symm_open": (C.c_void_p, [C.c_void_p]),
+    "exo_symm_close": (C.c_int, [C.c_void_p]), "exo_comm_header_bytes": (C.c_size_t, []),
+    "exo_comm_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int] + [C.c_size_t] * 8),
+    "exo_comm_reset": (C.c_int, []),
+    "exo_comm_handover_bytes": (C.c_size_t, [C.c_int, C.c_size_t]),
+    "exo_tp_handover_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                          C.c_int, C.c_void_p]),
+    "exo_gemm_bf16_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                   C.c_void_p]),
+    "exo_tp_handover_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
+    "exo_gemv_stream_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
+                                     C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "exo_comm_status": (C.c_int, []),
+    "exo_allreduce_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
+    "exo_allgather_cols_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "exo_reduce_norm_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                       C.c_int, C.c_void_p]),
+    "exo_comm_region": (C.c_void_p, [C.c_int, C.c_int]),
+    "exo_comm_has_multicast": (C.c_int, []),
+    "exo_vmm_supported": (C.c_int, []), "exo_vmm_granularity": (C.c_size_t, [C.c_int, C.c_int]),
+    "exo_vmm_alloc": (C.c_void_p, [C.c_size_t, C.POINTER(C.c_int)]), "exo_vmm_import": (C.c_void_p, [C.c_int, C.c_size_t]),
+    "exo_mc_create": (C.c_ulonglong, [C.c_size_t, C.c_int, C.POINTER(C.c_int)]), "exo_mc_import": (C.c_ulonglong, [C.c_int]),
+    "exo_mc_add_device": (C.c_int, [C.c_ulonglong]),
+    "exo_mc_bind_and_map": (C.c_void_p, [C.c_ulonglong, C.c_void_p, C.c_size_t]),
+    "exo_vmm_unmap": (C.c_int, [C.c_void_p]),
+    "exo_set_collective_timeout_us": (C.c_int, [C.c_long]),
+}
+
+
+def bind(lib: C.CDLL) -> C.CDLL:
+    """Declare the signatures of the communicator's entry points on the loaded kernel library."""
+    for name, (res, args) in _SIGS.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+def arena_layout(lib, n: int, max_rows: int, hidden: int, vocab_shard: int, max_gather_rows: int) -> dict:
+    """Byte offsets of the arena's regions (identical on every rank)."""
+    hdr = lib.exo_comm_header_bytes()
+    one_shot = 512 << 10
+    two_shot = 2 * (max_rows * hidden * 2 + n - 1) // n
+    slot = (max(one_shot, two_shot) + 4095) // 4096 * 4096
+    gather_off = hdr + 2 * n * slot
+    gather_bytes = max_gather_rows * n * vocab_shard * 2
+    handover_off = (gather_off + gather_bytes + 4095) // 4096 * 4096
+    handover_slot = (HANDOVER_ROWS * hidden * 2 + 4095) // 4096 * 4096
+    x_off = (handover_off + lib.exo_comm_handover_bytes(n, handover_slot) + 4095) // 4096 * 4096
+    x_bytes = (max_rows * hidden * 2 + 4095) // 4096 * 4096
+    h_off = x_off + 2 * x_bytes
+    n_off = h_off + 2 * x_bytes
+    return dict(slot=slot, gather_off=gather_off, gather_bytes=gather_bytes, handover_off=handover_off,
+                handover_slot=handover_slot, x_off=x_off, x_bytes=x_bytes, h_off=h_off, n_off=n_off,
+                total=n_off + 2 * x_bytes)
 
 
 class Handover:
@@ -51,8 +123,6 @@ class Handover:
         M, Kd = self.shape
         N = w.shape[0]
         lib = self.comm.lib
-        if not self.done and os.environ.get("EXO_TP_HANDOVER_CONSUME") == "0":
-            return K.linear(self.value(), w, bias, None, norm_w, eps, swiglu)      # measurement aid: stand-alone finish kernel
         if not self.done and M > 2 and Kd % 8 == 0:
             # batched decode: one kernel finishes the reduction, leaves the residual stream and the normalised rows
             xn = torch.empty_like(self.out)
@@ -70,6 +140,10 @@ class Handover:
         self.done = True
         return y
 
+    def norm(self, norm_w, eps) -> torch.Tensor:
+        """RMSNorm of the reduced residual stream (which ``value()`` then returns)."""
+        return K.rmsnorm(self.value(), norm_w, eps)[0]
+
     def value(self) -> torch.Tensor:
         if not self.done:
             n = self.shape[0] * self.shape[1]
@@ -80,9 +154,85 @@ class Handover:
         return self.out
 
 
+class Reduction:
+    """A row-parallel projection's partial sitting in this rank's arena, not yet summed over the ranks.
+
+    The first consumer decides the kernel: ``norm_linear`` / ``norm`` run the fused
+    ``residual + sum`` + RMSNorm kernel, ``value()`` alone runs it without the norm.  In the two-shot
+    form the results are views of the arena; they stay valid until the collective after next."""
+
+    def __init__(self, comm: "FusedComm", parity: int, residual: torch.Tensor | None, rows: int, cols: int):
+        self.comm, self.parity, self.residual, self.shape = comm, parity, residual, (rows, cols)
+        self.out: torch.Tensor | None = None
+        self.xn: torch.Tensor | None = None
+
+    def _run(self, norm_w, eps: float) -> None:
+        comm = self.comm
+        M, H = self.shape
+        two = comm.two_shot(M, H)
+        if two:
+            self.out = comm.region(1, self.parity, M, H)
+            xn = comm.region(2, self.parity, M, H) if norm_w is not None else None
+        else:
+            self.out = torch.empty(M, H, dtype=torch.bfloat16, device=comm.device)
+            xn = torch.empty_like(self.out) if norm_w is not None else None
+        K._chk(comm.lib.exo_reduce_norm_bf16(K._ptr(self.residual), K._ptr(norm_w), float(eps), self.out.data_ptr(),
+                                             K._ptr(xn), M, H, self.parity, int(two), K._st()), "reduce_norm")
+        K._count()
+        comm.n_collectives += 1
+        self.xn = xn
+
+    def norm(self, norm_w, eps) -> torch.Tensor:
+        if self.out is None:
+            self._run(norm_w, eps)
+            return self.xn
+        return K.rmsnorm(self.out, norm_w, eps)[0]
+
+    def norm_linear(self, norm_w, eps, w, bias=None, swiglu=False):
+        if self.out is None:
+            return K.linear(self.norm(norm_w, eps), w, bias, None, None, 0.0, swiglu)
+        return K.linear(self.out, w, bias, None, norm_w, eps, swiglu)
+
+    def value(self) -> torch.Tensor:
+        if self.out is None:
+            self._run(None, 0.0)
+        return self.out
+
+
 def resolve(h):
-    """A tensor for ``h``: hand-overs are finished, tensors pass through."""
-    return h.value() if isinstance(h, Handover) else h
+    """A tensor for ``h``: pending reductions are finished, tensors pass through."""
+    return h.value() if isinstance(h, (Handover, Reduction)) else h
+
+
+def _exchange_fds(rank: int, n: int, mine: list[int], group) -> dict[int, list[int]]:
+    """Every rank sends ``mine`` (file descriptors) to every other rank over Unix sockets (SCM_RIGHTS)."""
+    name = f"\0exo-symm-{os.getpid()}-{uuid.uuid4().hex[:12]}"      # abstract namespace: nothing to unlink
+    srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    srv.bind(name)
+    srv.listen(n)
+    names: list[str | None] = [None] * n
+    dist.all_gather_object(names, name, group=group)
+    outs = []
+    for r in range(n):
+        if r == rank:
+            continue
+        s = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        s.connect(names[r])
+        socket.send_fds(s, [rank.to_bytes(4, "little")], mine)
+        outs.append(s)
+    got: dict[int, list[int]] = {}
+    srv.settimeout(120)
+    for _ in range(n - 1):
+        c, _addr = srv.accept()
+        c.settimeout(120)
+        msg, fds, _flags, _a = socket.recv_fds(c, 4, 8)
+        got[int.from_bytes(msg[:4], "little")] = list(fds)
+        c.close()
+    dist.barrier(group=group)
+    for s in outs:
+        s.close()
+    srv.close()
+    return got
 
 
 class FusedComm:
@@ -92,49 +242,66 @@ class FusedComm:
         self.size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.device = device
-        lib = K.load()
-        for name, (res, args) in {
-            "exo_symm_alloc": (C.c_void_p, [C.c_size_t]), "exo_symm_free": (C.c_int, [C.c_void_p]),
-            "exo_symm_handle": (C.c_int, [C.c_void_p, C.c_void_p]), "exo_symm_open": (C.c_void_p, [C.c_void_p]),
-            "exo_symm_close": (C.c_int, [C.c_void_p]), "exo_comm_header_bytes": (C.c_size_t, []),
-            "exo_comm_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t]),
-            "exo_comm_handover_bytes": (C.c_size_t, [C.c_int, C.c_size_t]),
-            "exo_tp_handover_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
-                                                  C.c_int, C.c_void_p]),
-            "exo_gemm_bf16_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                                           C.c_void_p]),
-            "exo_tp_handover_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
-            "exo_gemv_stream_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
-                                             C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
-            "exo_comm_status": (C.c_int, []),
-            "exo_allreduce_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
-            "exo_allgather_cols_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
-        }.items():
-            fn = getattr(lib, name)
-            fn.restype, fn.argtypes = res, args
-        self.lib = lib
+        self.lib = lib = bind(K.load())
         n = self.size
-        hdr = lib.exo_comm_header_bytes()
-        one_shot = 512 << 10
-        two_shot = 2 * (max_rows * hidden * 2 + n - 1) // n
-        self.slot_bytes = (max(one_shot, two_shot) + 4095) // 4096 * 4096
+        torch.cuda.set_device(device)
+        from ..shared import constants
+        lib.exo_set_collective_timeout_us(int(constants.EXO_COLLECTIVE_TIMEOUT_US))
+        L = arena_layout(lib, n, max_rows, hidden, vocab_shard, max_gather_rows)
+        self.layout = L
+        self.slot_bytes = L["slot"]
         self.max_elems = max_rows * hidden
+        self.max_rows, self.hidden = max_rows, hidden
         self.vocab_shard = vocab_shard
         self.max_gather_rows = max_gather_rows
-        self.gather_off = hdr + 2 * n * self.slot_bytes
-        gather_bytes = max_gather_rows * n * vocab_shard * 2
-        self.handover_off = (self.gather_off + gather_bytes + 4095) // 4096 * 4096
-        self.handover_slot = (HANDOVER_ROWS * hidden * 2 + 4095) // 4096 * 4096
-        self.arena_bytes = self.handover_off + lib.exo_comm_handover_bytes(n, self.handover_slot)
-        torch.cuda.set_device(device)
-        self.local = lib.exo_symm_alloc(self.arena_bytes)
+        self.gather_off = L["gather_off"]
+        self.handover_off, self.handover_slot = L["handover_off"], L["handover_slot"]
+        self.mc_ptr = 0
+        self.transport = "ipc"
+        self.peers: list[int] = []
+        # every rank must take the same transport: agree on the weakest capability
+        cap = lib.exo_vmm_supported() if os.environ.get("EXO_COMM_TRANSPORT", "vmm") != "ipc" else 0
+        if os.environ.get("EXO_COMM_MULTICAST", "1") == "0":
+            cap = min(cap, 1)
+        caps: list[int | None] = [None] * n
+        dist.all_gather_object(caps, cap, group=group)
+        cap = min(int(c) for c in caps)
+        if cap >= 1:
+            self._open_vmm(L["total"], cap >= 2)
+        else:
+            self._open_ipc(L["total"])
+        arr = (C.c_void_p * n)(*self.peers)
+        K._chk(lib.exo_comm_init(arr, self.mc_ptr or None, n, self.rank, L["slot"], L["gather_off"], L["handover_off"],
+                                 L["handover_slot"], L["x_off"], L["x_bytes"], L["h_off"], L["n_off"]), "comm init")
+        dist.barrier(group=group)
+        raw = torch.as_tensor(_RawBuffer(self.local + self.gather_off, L["gather_bytes"]), device=device)
+        self.gather_buf = raw.view(torch.bfloat16)
+        self._views: dict[tuple[int, int], torch.Tensor] = {}
+        for which in (0, 1, 2):
+            for parity in (0, 1):
+                p = lib.exo_comm_region(which, parity)
+                self._views[(which, parity)] = torch.as_tensor(_RawBuffer(p, L["x_bytes"]), device=device).view(torch.bfloat16)
+        self._ar = 0
+        self._ho = 0             # hand-overs issued so far (parity = low bit)
+        self._rn = 0             # reduce + norm collectives issued so far
+        self.n_collectives = 0
+        self.n_handovers = 0
+        self.use_handover = os.environ.get("EXO_DISABLE_TP_HANDOVER") != "1"
+        self.use_reduce_norm = os.environ.get("EXO_DISABLE_REDUCE_NORM") != "1"
+        # the GEMM-epilogue variant (batches > 2) measured slower than GEMM + reduction kernel: off unless asked for
+        self.handover_gemm = os.environ.get("EXO_TP_HANDOVER_GEMM") == "1"
+
+    # ---- arena set-up ----
+    def _open_ipc(self, total: int) -> None:
+        lib, n = self.lib, self.size
+        self.arena_bytes = total
+        self.local = lib.exo_symm_alloc(total)
         if not self.local:
-            raise RuntimeError(f"cannot allocate {self.arena_bytes >> 20} MiB symmetric arena")
+            raise RuntimeError(f"cannot allocate {total >> 20} MiB symmetric arena")
         handle = C.create_string_buffer(64)
         K._chk(lib.exo_symm_handle(self.local, handle), "ipc handle")
         handles: list[bytes | None] = [None] * n
-        dist.all_gather_object(handles, handle.raw, group=group)
-        self.peers: list[int] = []
+        dist.all_gather_object(handles, handle.raw, group=self.group)
         for r, h in enumerate(handles):
             if r == self.rank:
                 self.peers.append(self.local)
@@ -143,26 +310,83 @@ class FusedComm:
                 if not p:
                     raise RuntimeError(f"rank {self.rank}: cannot map arena of rank {r} (no peer access?)")
                 self.peers.append(p)
-        arr = (C.c_void_p * n)(*self.peers)
-        K._chk(lib.exo_comm_init(arr, n, self.rank, self.slot_bytes, self.gather_off, self.handover_off,
-                                 self.handover_slot), "comm init")
-        dist.barrier(group=group)
-        raw = torch.as_tensor(_RawBuffer(self.local + self.gather_off, gather_bytes), device=device)
-        self.gather_buf = raw.view(torch.bfloat16)
-        self._ar = 0
-        self._ho = 0             # hand-overs issued so far (parity = low bit)
-        self.n_collectives = 0
-        self.n_handovers = 0
-        self.use_handover = os.environ.get("EXO_DISABLE_TP_HANDOVER") != "1"
-        # the GEMM-epilogue variant (batches > 2) measured slower than GEMM + all-reduce kernel: off unless asked for
-        self.handover_gemm = os.environ.get("EXO_TP_HANDOVER_GEMM") == "1"
+
+    def _open_vmm(self, total: int, multicast: bool) -> None:
+        lib, n, rank = self.lib, self.size, self.rank
+        gran = lib.exo_vmm_granularity(n, int(multicast)) or (2 << 20)
+        total = (total + gran - 1) // gran * gran
+        self.arena_bytes = total
+        fd = C.c_int(-1)
+        self.local = lib.exo_vmm_alloc(total, C.byref(fd))
+        ok = bool(self.local)
+        mc_handle, mc_fd = 0, C.c_int(-1)
+        if ok and multicast and rank == 0:
+            mc_handle = lib.exo_mc_create(total, n, C.byref(mc_fd))
+        flags: list[tuple | None] = [None] * n
+        dist.all_gather_object(flags, (ok, bool(mc_handle) if rank == 0 else None), group=self.group)
+        if not all(f[0] for f in flags):
+            raise RuntimeError(f"rank {rank}: cannot allocate a {total >> 20} MiB virtual-memory arena")
+        multicast = multicast and bool(flags[0][1])
+        mine = [fd.value] + ([mc_fd.value] if (rank == 0 and multicast) else [])
+        got = _exchange_fds(rank, n, mine, self.group)
+        for r in range(n):
+            if r == rank:
+                self.peers.append(self.local)
+                continue
+            p = lib.exo_vmm_import(got[r][0], total)
+            if not p:
+                raise RuntimeError(f"rank {rank}: cannot map the arena of rank {r}")
+            self.peers.append(p)
+        if multicast:
+            if rank != 0:
+                mc_handle = lib.exo_mc_import(got[0][1])
+            added = bool(mc_handle) and lib.exo_mc_add_device(mc_handle) == 0
+            oks: list[bool | None] = [None] * n
+            dist.all_gather_object(oks, added, group=self.group)        # also: every device is added before anyone binds
+            if all(oks):
+                self.mc_ptr = lib.exo_mc_bind_and_map(mc_handle, self.local, total) or 0
+            oks = [None] * n
+            dist.all_gather_object(oks, bool(self.mc_ptr), group=self.group)
+            if not all(oks):                                             # all or nobody: the kernels of all ranks must agree
+                if self.mc_ptr:
+                    lib.exo_vmm_unmap(self.mc_ptr)
+                self.mc_ptr = 0
+        for fds in got.values():
+            for f in fds:
+                os.close(f)
+        for f in mine:
+            os.close(f)
+        self.transport = "vmm+multicast" if self.mc_ptr else "vmm"
+
+    # ---- regions of the reduce + norm kernels ----
+    def region(self, which: int, parity: int, rows: int, cols: int) -> torch.Tensor:
+        """``[rows, cols]`` bf16 view of region ``which`` (0 partial, 1 residual stream, 2 normalised rows)."""
+        return self._views[(which, parity)][:rows * cols].view(rows, cols)
+
+    def two_shot(self, rows: int, cols: int) -> bool:
+        return rows >= 2 * self.size and (self.size - 1) * rows * cols * 2 > ONE_SHOT_MAX_BYTES
+
+    def fits(self, rows: int, cols: int) -> bool:
+        return (self.use_reduce_norm and 0 < rows and rows * cols * 2 <= self.layout["x_bytes"] and cols % 8 == 0
+                and cols <= 8192)
+
+    def partial_out(self, rows: int, cols: int) -> tuple[torch.Tensor, int]:
+        """Buffer for the next reduction's partial (write the projection output here) and its parity."""
+        parity = self._rn & 1
+        self._rn += 1
+        return self.region(0, parity, rows, cols), parity
 
     # ---- collectives ----
     def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
-        """``residual + sum over ranks of x`` (bf16), identical bits on every rank."""
-        x = x.contiguous()
+        """``residual + sum over ranks of x`` (bf16)."""
         if x.dtype != torch.bfloat16 or x.numel() % 8:
             raise K.KernelError("fused all-reduce takes bf16 tensors whose size is a multiple of 8")
+        residual = resolve(residual)
+        if x.dim() == 2 and self.fits(x.shape[0], x.shape[1]):
+            buf, parity = self.partial_out(x.shape[0], x.shape[1])
+            buf.copy_(x)
+            return Reduction(self, parity, residual, x.shape[0], x.shape[1]).value()
+        x = x.contiguous()
         if x.numel() > self.max_elems:
             # larger than one arena slot (a long prefill chunk): reduce it in row blocks that fit
             if x.dim() != 2 or x.shape[1] > self.max_elems:
@@ -181,14 +405,13 @@ class FusedComm:
         return out
 
     def row_linear(self, x: torch.Tensor, w: torch.Tensor, residual=None):
-        """``residual + all-reduce(x @ w.T)``.  At decode batch sizes the projection itself stores its rows
-        into every rank's staging slot and a :class:`Handover` is returned: the next ``norm_linear`` (or
-        ``resolve``) forms the sum, so no collective kernel is launched."""
+        """``residual + all-reduce(x @ w.T)``, returned as a pending :class:`Handover` / :class:`Reduction`
+        where the shapes allow it: the next ``norm_linear`` (or ``resolve``) then forms the sum."""
         residual = resolve(residual)
         M, Kd = x.shape
         N = w.shape[0]
         fits = (self.use_handover and x.dtype == torch.bfloat16 and 0 < M and M * N * 2 <= self.handover_slot
-                and isinstance(w, torch.Tensor))       # block-scaled fp8 weights take the GEMM + all-reduce path
+                and isinstance(w, torch.Tensor))       # block-scaled fp8 weights take the GEMM + reduction path
         if fits and M <= 2 and K.use_stream_gemv and self.lib.exo_gemv_stream_supported(M, N, Kd, 0):
             K.ensure_stream_init(x.device)
             parity = self._ho & 1
@@ -214,6 +437,16 @@ class FusedComm:
             K._count()
             self.n_handovers += 1
             return Handover(self, parity, residual, M, N)
+        if x.dtype == torch.bfloat16 and self.fits(M, N):
+            buf, parity = self.partial_out(M, N)
+            K.linear(x, w, out=buf)                      # the projection writes straight into this rank's arena
+            return Reduction(self, parity, residual, M, N)
+        if x.dtype == torch.bfloat16 and M > 0 and N % 8 == 0 and N <= 8192 and self.use_reduce_norm:
+            # longer than the arena region: row blocks that fit, each reduced by its own collective
+            rows = max(8, (self.layout["x_bytes"] // (N * 2)) // 8 * 8)
+            parts = [resolve(self.row_linear(x[r:r + rows], w, None if residual is None else residual[r:r + rows])).clone()
+                     for r in range(0, M, rows)]
+            return torch.cat(parts, dim=0)
         return self.all_reduce(ops.linear(x, w), residual)
 
     def gather_vocab(self, logits_local: torch.Tensor) -> torch.Tensor:
@@ -242,11 +475,27 @@ class FusedComm:
         dist.barrier(group=self.group)
 
     def close(self) -> None:
+        """Ordered teardown: every rank is idle before any mapping goes away (the multicast binding first)."""
+        if not self.peers:
+            return
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
-        for r, p in enumerate(self.peers):
-            if r != self.rank and p:
-                self.lib.exo_symm_close(p)
-        dist.barrier(group=self.group)
-        self.lib.exo_symm_free(self.local)
+        self._views.clear()
+        self.lib.exo_comm_reset()
+        if self.transport == "ipc":
+            for r, p in enumerate(self.peers):
+                if r != self.rank and p:
+                    self.lib.exo_symm_close(p)
+            dist.barrier(group=self.group)
+            self.lib.exo_symm_free(self.local)
+        else:
+            if self.mc_ptr:
+                self.lib.exo_vmm_unmap(self.mc_ptr)
+                self.mc_ptr = 0
+            dist.barrier(group=self.group)
+            for r, p in enumerate(self.peers):
+                if r != self.rank and p:
+                    self.lib.exo_vmm_unmap(p)
+            dist.barrier(group=self.group)
+            self.lib.exo_vmm_unmap(self.local)
         self.peers = []

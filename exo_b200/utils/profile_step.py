@@ -32,12 +32,21 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill"])
     ap.add_argument("--graphs", action="store_true")
+    ap.add_argument("--tp-shard", type=int, default=1,
+                    help="run ONE rank's share of an N-way tensor-parallel model on this GPU (heads, FFN and vocabulary "
+                         "divided by N, no communication): every kernel then has the shape it has under TP-N")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     cfg = preset(a.model)
     if a.layers:
         cfg.n_layers = a.layers
+    if a.tp_shard > 1:
+        n = a.tp_shard
+        cfg.n_heads //= n
+        cfg.n_kv_heads = max(1, cfg.n_kv_heads // n)
+        cfg.ffn //= n
+        cfg.vocab = -(-cfg.vocab // n)
     w = fast_random_weights(cfg, ShardSpec(), dev)
     bs = 16
     B = a.batch if a.mode == "decode" else 1
@@ -78,7 +87,7 @@ def main() -> None:
     e1.record()
     torch.cuda.synchronize()
     torch.cuda.nvtx.range_pop()
-    print(f"{a.mode} batch={B} context={a.context} layers={cfg.n_layers}: "
+    print(f"{a.mode} batch={B} context={a.context} layers={cfg.n_layers} tp-shard={a.tp_shard}: "
           f"{e0.elapsed_time(e1) / a.steps:.3f} ms/step (eager={not a.graphs})")
 
 

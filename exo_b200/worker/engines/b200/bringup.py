@@ -208,7 +208,18 @@ class B200Builder(Builder):
             budget = 256 << 20
         cap = int(os.environ.get("EXO_MAX_KV_BLOCKS", "0"))
         n = max(64, budget // per_block)
-        return min(n, cap) if cap else n
+        n = min(n, cap) if cap else n
+        return self._agree_min(n)
+
+    def _agree_min(self, n: int) -> int:
+        """The smallest value over the instance's ranks.  Only rank 0's allocator hands out block ids, and every
+        rank indexes its own pool with them: a rank with less free memory, or a pipeline stage with more layers or
+        the vocabulary head, would otherwise receive slots past the end of its pool."""
+        if self.world == 1 or self.control is None or not dist.is_initialized():
+            return n
+        t = torch.tensor([n], dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.control.group)
+        return int(t.item())
 
     def build(self) -> Engine:
         assert self.cfg is not None and self.weights is not None

@@ -1,0 +1,141 @@
+"""The peer-memory collectives on ONE GPU: the peer is a second local arena whose flags the test sets by hand.
+
+Kernels that wait on one another are never launched side by side on one device; here the "peer" has no
+kernel at all: its partial is written by the host and its arrival flag is either pre-set (the normal
+case) or left unset (the wait must run out, the kernel must return, and the status word must say so).
+"""
+import ctypes as C
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BAR_IN, BAR_OUT = 2048 // 4, 2112 // 4      # int32 word offsets of the barrier flags in the arena header
+
+
+def _setup(n_ranks, rank, rows, hidden):
+    from exo_b200.ops import cuda as K
+    from exo_b200.parallel.fused import arena_layout, bind
+    lib = bind(K.load())
+    K.ensure_gemm_init(torch.device("cuda", 0))
+    L = arena_layout(lib, n_ranks, rows, hidden, 64, 8)
+    arenas = [torch.zeros(L["total"], dtype=torch.uint8, device="cuda") for _ in range(n_ranks)]
+    arr = (C.c_void_p * n_ranks)(*[a.data_ptr() for a in arenas])
+    rc = lib.exo_comm_init(arr, None, n_ranks, rank, L["slot"], L["gather_off"], L["handover_off"], L["handover_slot"],
+                           L["x_off"], L["x_bytes"], L["h_off"], L["n_off"])
+    assert rc == 0
+    return lib, K, L, arenas
+
+
+def _region(arena, L, which, parity, rows, cols):
+    off = {0: L["x_off"], 1: L["h_off"], 2: L["n_off"]}[which] + parity * L["x_bytes"]
+    return arena[off:off + rows * cols * 2].view(torch.bfloat16).view(rows, cols)
+
+
+def _flags(arena):
+    return arena[:4096].view(torch.int32)
+
+
+def _ref(parts, res, w, eps):
+    h = (sum(p.float() for p in parts) + res.float()).bfloat16()
+    hf = h.float()
+    x = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    return h, x.bfloat16()
+
+
+@pytest.mark.parametrize("rows,cols", [(3, 4096), (32, 4096), (200, 1024), (17, 7168), (64, 8192)])
+def test_one_shot_reduce_norm_against_fp32_reference(rows, cols):
+    lib, K, L, (A, B) = _setup(2, 0, 256, 8192)
+    g = torch.Generator(device="cuda").manual_seed(rows * 31 + cols)
+    st = torch.cuda.current_stream().cuda_stream
+    for it in range(4):                                  # both parities, twice: the flags must come back clean
+        parity = it & 1
+        xa = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+        xb = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+        res = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+        w = (1 + 0.1 * torch.randn(cols, device="cuda", generator=g)).bfloat16()
+        _region(A, L, 0, parity, rows, cols).copy_(xa)
+        _region(B, L, 0, parity, rows, cols).copy_(xb)
+        _flags(A)[BAR_IN + parity * 8 + 1] = 1          # the peer's "partial ready"
+        h = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
+        x = torch.empty_like(h)
+        with_norm = it != 3
+        rc = lib.exo_reduce_norm_bf16(res.data_ptr(), w.data_ptr() if with_norm else None, 1e-5, h.data_ptr(),
+                                      x.data_ptr() if with_norm else None, rows, cols, parity, 0, st)
+        assert rc == 0
+        torch.cuda.synchronize()
+        want_h, want_x = _ref([xa, xb], res, w, 1e-5)
+        assert torch.equal(h, want_h)                    # fp32 sum in rank order, one rounding: exact
+        if with_norm:
+            assert (x.float() - want_x.float()).abs().max() <= 0.02 * want_x.float().abs().max()
+        f = _flags(A)
+        assert int(f[BAR_IN + parity * 8].item()) == 0 and int(f[BAR_IN + parity * 8 + 1].item()) == 0
+        assert int(_flags(B)[BAR_IN + parity * 8].item()) == it // 2 + 1     # our signal reached the peer's arena
+    K.check_status()
+    lib.exo_comm_reset()
+
+
+def test_two_shot_reduce_norm_writes_this_ranks_rows_into_every_arena():
+    rows, cols = 1000, 4096
+    lib, K, L, (A, B) = _setup(2, 0, 1024, 4096)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    xa = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+    xb = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+    res = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(cols, device="cuda", generator=g)).bfloat16()
+    parity = 1
+    _region(A, L, 0, parity, rows, cols).copy_(xa)
+    _region(B, L, 0, parity, rows, cols).copy_(xb)
+    _flags(A)[BAR_IN + parity * 8 + 1] = 1
+    _flags(A)[BAR_OUT + parity * 8 + 1] = 1              # the peer's "rows broadcast"
+    rc = lib.exo_reduce_norm_bf16(res.data_ptr(), w.data_ptr(), 1e-5, None, None, rows, cols, parity, 1,
+                                  torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    want_h, want_x = _ref([xa, xb], res, w, 1e-5)
+    mine = (rows + 1) // 2                               # rank 0 owns the first half of the rows
+    for arena in (A, B):
+        h = _region(arena, L, 1, parity, rows, cols)
+        x = _region(arena, L, 2, parity, rows, cols)
+        assert torch.equal(h[:mine], want_h[:mine])
+        assert (x[:mine].float() - want_x[:mine].float()).abs().max() <= 0.02 * want_x.float().abs().max()
+        assert float(h[mine:].float().abs().max()) == 0.0   # the peer's rows are the peer's to write
+    K.check_status()
+    lib.exo_comm_reset()
+
+
+def test_a_wait_that_runs_out_returns_sets_the_status_word_and_leaves_the_context_usable():
+    from exo_b200.ops.cuda import DeviceWaitTimeout
+    rows, cols = 8, 4096
+    lib, K, L, (A, B) = _setup(2, 0, 256, 4096)
+    lib.exo_set_collective_timeout_us(20000)             # 20 ms instead of the serving default
+    try:
+        x = torch.randn(rows, cols, device="cuda").bfloat16()
+        h = torch.empty_like(x)
+        st = torch.cuda.current_stream().cuda_stream
+        _region(A, L, 0, 0, rows, cols).copy_(x)
+        # nobody raises the peer's flag: the kernel must give up after ~20 ms and return normally
+        assert lib.exo_reduce_norm_bf16(None, None, 0.0, h.data_ptr(), None, rows, cols, 0, 0, st) == 0
+        torch.cuda.synchronize()
+        with pytest.raises(DeviceWaitTimeout):
+            K.check_status()
+        K.check_status()                                 # the word was cleared by the raise
+        # the older push-style all-reduce kernel takes the same path
+        out = torch.empty_like(x)
+        assert lib.exo_allreduce_bf16(x.data_ptr(), None, out.data_ptr(), x.numel(), 0, st) == 0
+        torch.cuda.synchronize()
+        assert lib.exo_comm_status() == 4
+        # a healthy collective right afterwards: the peer's flag is there, the result is exact
+        _region(B, L, 0, 0, rows, cols).copy_(x)
+        _flags(A)[BAR_IN + 1] = 1
+        assert lib.exo_reduce_norm_bf16(None, None, 0.0, h.data_ptr(), None, rows, cols, 0, 0, st) == 0
+        torch.cuda.synchronize()
+        K.check_status()
+        assert torch.equal(h, (x.float() * 2).bfloat16())
+        # and an ordinary kernel still runs on this context
+        y = K.rmsnorm(x, torch.ones(cols, device="cuda", dtype=torch.bfloat16), 1e-5)[0]
+        assert torch.isfinite(y.float()).all()
+    finally:
+        lib.exo_set_collective_timeout_us(2000000)
+        lib.exo_comm_reset()

@@ -8,13 +8,34 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+WORLDS = [2, 4, 8]
+
+
+def needs(world):
+    return pytest.mark.skipif(torch.cuda.device_count() < world, reason=f"needs {world} GPUs")
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
 
 
-def _run(fn, world, *args):
+def _run(fn, world, *args, env=None):
+    import torch.multiprocessing as mp
+    old = {k: os.environ.get(k) for k in (env or {})}
+    os.environ.update(env or {})          # spawned children inherit the parent's environment
+    try:
+        return _run_inner(fn, world, *args)
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+
+
+def _run_inner(fn, world, *args):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -68,6 +89,7 @@ def _collectives(rank, world):
         other = got.clone()
         dist.broadcast(other, 0)
         assert torch.equal(mine, other), "ranks disagree on the reduced tensor"
+    transport = comm.transport
     shard = torch.randn(5, 4008, device=dev, generator=g).bfloat16()
     full = comm.gather_vocab(shard).clone()
     parts = [torch.empty_like(shard) for _ in range(world)]
@@ -75,7 +97,50 @@ def _collectives(rank, world):
     assert torch.equal(full, torch.cat(parts, -1))
     comm.check()
     comm.close()
-    return worst
+    return worst, transport
+
+
+def _reduce_norm(rank, world):
+    """Row-parallel projection -> (sum over ranks + residual + RMSNorm) as one kernel, one-shot and two-shot."""
+    import torch.distributed as dist
+    from exo_b200 import ops
+    from exo_b200.ops import reference as ref
+    from exo_b200.parallel.fused import FusedComm, Reduction
+    dev = torch.device("cuda", rank)
+    H, Kr = 4096, 1024
+    comm = FusedComm(dev, max_rows=2048, hidden=H, vocab_shard=4008)
+    shared = torch.Generator(device=dev).manual_seed(5)
+    mine = torch.Generator(device=dev).manual_seed(50 + rank)
+    w_o = (torch.randn(H, Kr, device=dev, generator=mine) / 32).bfloat16()
+    w_up = (torch.randn(1024, H, device=dev, generator=shared) / 64).bfloat16()
+    norm_w = (1 + 0.1 * torch.randn(H, device=dev, generator=shared)).bfloat16()
+    worst, kinds = 0.0, set()
+    for it, M in enumerate((3, 32, 64, 256, 2048, 17, 1500, 2048)):
+        x = torch.randn(M, Kr, device=dev, generator=mine).bfloat16()
+        res = torch.randn(M, H, device=dev, generator=shared).bfloat16()
+        h = comm.row_linear(x, w_o, res)
+        assert isinstance(h, Reduction)
+        kinds.add(comm.two_shot(M, H))
+        if it % 3 == 2:
+            got_h = h.value().clone()                     # no norm wanted: plain all-reduce + residual
+            got_y = ops.norm_linear(got_h, norm_w, 1e-5, w_up)
+        else:
+            got_y = ops.norm_linear(h, norm_w, 1e-5, w_up)
+            got_h = h.value().clone()
+        part = ref.linear(x.float(), w_o.float()).bfloat16().float()
+        dist.all_reduce(part)
+        want_h = (part + res.float()).bfloat16()
+        want_y = ref.linear(ref.rmsnorm(want_h.float(), norm_w.float(), 1e-5)[0], w_up.float())
+        worst = max(worst, ((got_h.float() - want_h.float()).abs().max() / want_h.float().abs().max()).item(),
+                    ((got_y.float() - want_y).abs().max() / want_y.abs().max()).item())
+        other = got_h.clone()
+        dist.broadcast(other, 0)
+        assert torch.equal(other, got_h), "ranks disagree on the reduced residual stream"
+    assert kinds == {False, True}
+    comm.check()
+    t = comm.transport
+    comm.close()
+    return worst, t
 
 
 def _engine(rank, world, kind):
@@ -115,10 +180,22 @@ def _engine(rank, world, kind):
     return [got[i] for i in ids], first_logits
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_collectives_match_nccl():
-    res = _run(_collectives, 2)
-    assert max(r[1] for r in res) < 2e-2
+@pytest.mark.parametrize("world", [pytest.param(w, marks=needs(w)) for w in WORLDS])
+def test_fused_collectives_match_nccl(world):
+    res = _run(_collectives, world)
+    assert max(r[1][0] for r in res) < 2e-2
+
+
+@pytest.mark.parametrize("transport", ["vmm+multicast", "vmm", "ipc"])
+@pytest.mark.parametrize("world", [pytest.param(w, marks=needs(w)) for w in WORLDS])
+def test_reduce_norm_kernel_matches_all_reduce_then_norm(world, transport):
+    env = {"vmm+multicast": {}, "vmm": {"EXO_COMM_MULTICAST": "0"}, "ipc": {"EXO_COMM_TRANSPORT": "ipc"}}[transport]
+    res = _run(_reduce_norm, world, env=env)
+    assert max(r[1][0] for r in res) < 2e-2
+    got = {r[1][1] for r in res}
+    assert len(got) == 1                                  # every rank took the same transport
+    if transport != "vmm+multicast":                      # multicast needs NVSwitch support; the others must be exact
+        assert got == {transport}
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")

@@ -1,0 +1,59 @@
+"""Scheduler behaviour under KV pressure (host only)."""
+import numpy as np
+
+from exo_b200.engine.kv import BlockAllocator, SamplingParams, Sequence
+from exo_b200.engine.scheduler import Scheduler
+
+
+def _run_step(sched):
+    plan, entries = sched.schedule()
+    if plan is None:
+        return None, []
+    # every entry's slots must lie inside blocks the sequence owns at plan time
+    t = 0
+    for b, (s, n) in enumerate(entries):
+        assert s.blocks, "a scheduled sequence must hold blocks"
+        owned = set(s.blocks)
+        for slot in plan.slots[t:t + n]:
+            assert int(slot) // sched.alloc.block_size in owned
+        t += n
+    sched.commit(entries, np.full(len(entries), 7, np.int64))
+    return plan, entries
+
+
+def test_preempting_a_sequence_already_looked_at_this_step_drops_its_entry():
+    """Three blocks of 16 tokens.  A (5-token prompt) decodes next to B (31-token prompt); when B needs its third
+    block, A — examined earlier in the same scheduling pass — is the only possible victim.  The step must go on
+    without A instead of carrying a stale entry for a sequence that no longer owns blocks."""
+    alloc = BlockAllocator(3, 16)
+    sched = Scheduler(alloc, max_seqs=4, prefill_chunk=64, max_blocks_per_seq=8)
+    greedy = SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True)
+    a = Sequence("a", list(range(5)), greedy, use_prefix_cache=False)
+    b = Sequence("b", list(range(31)), greedy, use_prefix_cache=False)
+    sched.add(a)
+    sched.add(b)
+    for _ in range(12):
+        plan, entries = _run_step(sched)
+        if plan is None:
+            break
+        ids = [s.req_id for s, _ in entries]
+        assert len(ids) == len(set(ids))
+    assert sched.n_preempted >= 1
+    # the preempted sequence is either waiting to be recomputed or running again with blocks of its own
+    for s in (a, b):
+        if not s.finished and s in sched.running:
+            assert s.blocks
+
+
+def test_block_pool_is_conserved_across_preemption_and_finish():
+    alloc = BlockAllocator(4, 16)
+    sched = Scheduler(alloc, max_seqs=4, prefill_chunk=32, max_blocks_per_seq=8)
+    p = SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
+    for i, n in enumerate((5, 17, 30)):
+        sched.add(Sequence(f"s{i}", list(range(n)), p, use_prefix_cache=False))
+    for _ in range(400):
+        if not sched.has_work:
+            break
+        _run_step(sched)
+    assert not sched.has_work
+    assert alloc.n_free == 4 and all(r == 0 for r in alloc.ref)
