@@ -33,6 +33,7 @@ constexpr int MAX_RANKS = 8;
 constexpr size_t HO_FLAGS = 1024, HO_PTICKET = 1280, HO_CTICKET = 1344;
 constexpr size_t HDR_BYTES = 4096;
 constexpr size_t BAR_IN = 2048, BAR_OUT = 2112, BAR_TICKET = 2176;
+constexpr size_t LL_EPOCH = 2304, LL_TICKET = 2368;   // flag-in-data hand-over: int32 [2 parities] each
 
 struct CommCtx {
   uint8_t* arena[MAX_RANKS];  // arena[r] = base of rank r's arena as mapped in this process
@@ -44,6 +45,7 @@ struct CommCtx {
   uint8_t* mc;                // multicast address of the arena (nullptr: plain peer loads / stores)
   size_t x_off, x_bytes;      // partial buffers [2 parities][x_bytes] (0 = none)
   size_t h_off, n_off;        // two-shot outputs [2][x_bytes]: residual stream, normalised rows
+  size_t ll_off, ll_slot;     // flag-in-data hand-over slots [2 parities][n_ranks][ll_slot] (ll_slot = 0: none)
   int* status;                // device-writable status word (host-mapped)
   unsigned long long wait_ns; // budget of every wait on a peer
 };
@@ -438,9 +440,10 @@ EXO_API size_t exo_comm_header_bytes() { return HDR_BYTES; }
 EXO_API size_t exo_comm_handover_bytes(int n, size_t slot) { return 2 * (size_t)n * slot; }
 
 // `mc` = multicast address of the arena or null; x_off / x_bytes / h_off / n_off describe the regions of the
-// reduce + norm kernels (x_bytes = 0: not present).
+// reduce + norm kernels (x_bytes = 0: not present), ll_off / ll_slot those of the flag-in-data hand-over.
 EXO_API int exo_comm_init(void** arenas, void* mc, int n, int rank, size_t slot_bytes, size_t gather_off, size_t handover_off,
-                          size_t handover_slot, size_t x_off, size_t x_bytes, size_t h_off, size_t n_off) {
+                          size_t handover_slot, size_t x_off, size_t x_bytes, size_t h_off, size_t n_off, size_t ll_off,
+                          size_t ll_slot) {
   int dev;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || n > MAX_RANKS || n < 1 || rank < 0 || rank >= n) return -1;
   int* status = exo_status_word(EXO_STATUS_COMM);
@@ -449,6 +452,7 @@ EXO_API int exo_comm_init(void** arenas, void* mc, int n, int rank, size_t slot_
   for (int i = 0; i < MAX_RANKS; i++) c.arena[i] = i < n ? (uint8_t*)arenas[i] : nullptr;
   c.n = n; c.rank = rank; c.slot_bytes = slot_bytes; c.gather_off = gather_off; c.handover_off = handover_off; c.handover_slot = handover_slot;
   c.mc = (uint8_t*)mc; c.x_off = x_off; c.x_bytes = x_bytes; c.h_off = h_off; c.n_off = n_off;
+  c.ll_off = ll_off; c.ll_slot = ll_slot;
   c.status = status;
   c.wait_ns = exo_wait_budget_ns();
   g_ctx[dev] = c;
@@ -674,17 +678,69 @@ __global__ void __launch_bounds__(256) handover_rmsnorm_kernel(const TpHandover 
   }
 }
 
+
+// Stand-alone consumer of a flag-in-data hand-over (nobody took it in a projection's prologue):
+// out = residual + sum_r slot[r].  The last CTA advances the parity's epoch.
+__global__ void __launch_bounds__(256) ll_finish_kernel(const TpHandover h, __nv_bfloat16* out, int n_vec) {
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t seq = (uint32_t)(*reinterpret_cast<volatile const int*>(h.ll_epoch) + 1);
+  bool ok = true;
+  for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += gridDim.x * blockDim.x) {
+    float acc[8];
+    if (h.x_res) unpack8(reinterpret_cast<const uint4*>(h.x_res)[v], acc);
+    else {
+#pragma unroll
+      for (int e = 0; e < 8; e++) acc[e] = 0.f;
+    }
+    for (int r = 0; r < h.n_ll; r++) {
+      uint4 d = make_uint4(0, 0, 0, 0);
+      if (ok && !tp_ll_wait8(h.ll_part[r] + (size_t)v * 4, seq, h.wait_ns, reinterpret_cast<uint32_t*>(&d))) {
+        ok = false;
+        atomicExch(h.status, 4);
+      }
+      float f[8];
+      unpack8(d, f);
+#pragma unroll
+      for (int e = 0; e < 8; e++) acc[e] += f[e];
+    }
+    reinterpret_cast<uint4*>(out)[v] = pack8(acc);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(h.ll_ticket, 1) == (int)gridDim.x - 1) {
+    *h.ll_ticket = 0;
+    *reinterpret_cast<volatile int*>(h.ll_epoch) = (int)seq;
+    __threadfence();
+  }
+}
+
 }  // namespace
 
 int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems) {
   int dev;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return -4;
   const CommCtx& c = g_ctx[dev];
-  if (!c.handover_off || (size_t)n_elems * 2 > c.handover_slot) return -6;
   memset(out, 0, sizeof(*out));
+  if (mode <= 2 && (!c.handover_off || (size_t)n_elems * 2 > c.handover_slot)) return -6;
   uint8_t* mine = c.arena[c.rank];
   out->status = c.status;
   out->wait_ns = exo_wait_budget_ns();
+  if (mode == 3 || mode == 4) {
+    // two bf16 per 8-byte word: n_elems values take 4 * n_elems bytes of a slot
+    if (!c.ll_slot || (size_t)n_elems * 4 > c.ll_slot || (n_elems & 1)) return -6;
+    out->n_ll = c.n;
+    out->ll_epoch = reinterpret_cast<int*>(mine + LL_EPOCH) + parity;
+    const size_t my_slot = c.ll_off + ((size_t)parity * c.n + c.rank) * c.ll_slot;
+    if (mode == 3) {
+      out->ll_mc = c.mc ? reinterpret_cast<uint2*>(c.mc + my_slot) : nullptr;
+      for (int r = 0; r < c.n; r++) out->ll_dst[r] = reinterpret_cast<uint2*>(c.arena[r] + my_slot);
+    } else {
+      for (int r = 0; r < c.n; r++)
+        out->ll_part[r] = reinterpret_cast<const uint2*>(mine + c.ll_off + ((size_t)parity * c.n + r) * c.ll_slot);
+      out->ll_ticket = reinterpret_cast<int*>(mine + LL_TICKET) + parity;
+    }
+    return 0;
+  }
   if (mode == 1) {
     out->n_push = c.n;
     for (int r = 0; r < c.n; r++) {
@@ -700,6 +756,22 @@ int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems) {
     }
     out->part_ticket = reinterpret_cast<int*>(mine + HO_CTICKET) + parity;
   }
+  return 0;
+}
+
+// out = residual + sum over ranks of the flag-in-data hand-over on `parity` (n_elems multiple of 8).
+EXO_API int exo_tp_ll_finish(const void* residual, void* out, long n_elems, int parity, cudaStream_t st) {
+  if (n_elems % 8) return -2;
+  TpHandover h;
+  int rc = exo_tp_handover_fill(&h, 4, parity, n_elems);
+  if (rc) return rc;
+  h.x_res = (const __nv_bfloat16*)residual;
+  const int n_vec = (int)(n_elems / 8);
+  int grid = (n_vec + 255) / 256;
+  if (grid > 32) grid = 32;
+  cudaError_t e = launch_pdl(ll_finish_kernel, dim3(grid), dim3(256), 0, st, h, (__nv_bfloat16*)out, n_vec);
+  if (e != cudaSuccess) return (int)e;
+  EXO_CHECK_LAUNCH();
   return 0;
 }
 

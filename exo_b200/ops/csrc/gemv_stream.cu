@@ -45,7 +45,8 @@ __device__ __forceinline__ void bulk_g2s(void* smem, const void* gmem, uint32_t 
                : "memory");
 }
 
-// HO: 0 = plain projection, 1 = its output is handed over to every rank, 2 = its input is a hand-over
+// HO: 0 = plain projection, 1 = its output is handed over to every rank (flag-in-data words, see tp_handover.cuh),
+// 2 = its input is such a hand-over
 template <int M, int JV, int RB, bool NORM, bool SWIGLU, int HO>
 __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -97,11 +98,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
   const int KS = K / CONSUMER_WARPS;          // this warp's K slice
   const int k_lo = warp * KS, nvec = KS / 8;  // in 16-byte vectors
   pdl_wait();                                 // x comes from the previous kernel
-  if constexpr (HO == 2) {
-    // x is handed over by the row-parallel projection of every rank: wait for all of them (bounded)
-    if (warp == 0 && lane < p.ho.n_part) tp_wait_flag(p.ho.part_flag[lane], p.ho.status, p.ho.wait_ns);
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-  }
+  uint32_t ll_seq = 0;
+  bool ll_ok = true;
+  if constexpr (HO != 0) ll_seq = (uint32_t)(*reinterpret_cast<volatile const int*>(p.ho.ll_epoch) + 1);
   float xr[M][JV][8];
   float ss[M];
 #pragma unroll
@@ -112,8 +111,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
       const int v = lane + 32 * j;
       if (v < nvec) {
         if constexpr (HO == 2) {
-          // residual + partials in rank order, rounded to bf16: the same bits on every rank and the same
-          // value a separate all-reduce would have left in memory
+          // x is handed over by the row-parallel projection of every rank: residual + partials in rank order,
+          // rounded to bf16 (the same bits on every rank, and the value a separate all-reduce would have left in
+          // memory).  Each lane polls exactly the words it needs until they carry this hand-over's sequence number.
           const size_t off = (size_t)m * K + k_lo + v * 8;
           float acc[8];
           if (p.ho.x_res) unpack8(*reinterpret_cast<const uint4*>(p.ho.x_res + off), acc);
@@ -121,9 +121,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
 #pragma unroll
             for (int e = 0; e < 8; e++) acc[e] = 0.f;
           }
-          for (int r = 0; r < p.ho.n_part; r++) {
+          for (int r = 0; r < p.ho.n_ll; r++) {
+            uint4 d = make_uint4(0, 0, 0, 0);
+            if (ll_ok && !tp_ll_wait8(p.ho.ll_part[r] + off / 2, ll_seq, p.ho.wait_ns, reinterpret_cast<uint32_t*>(&d))) {
+              ll_ok = false;
+              atomicExch(p.ho.status, 4 /* peer timeout */);
+            }
             float f[8];
-            unpack8(tp_ld_cg16(p.ho.part[r] + off), f);
+            unpack8(d, f);
 #pragma unroll
             for (int e = 0; e < 8; e++) acc[e] += f[e];
           }
@@ -240,6 +245,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
             p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(silu_f(gsum) * usum);   // column-parallel: never handed over
           }
         }
+      } else if (HO == 1) {
+        // row-parallel projection under tensor parallelism: two adjacent outputs + the sequence number leave for
+        // every rank's slot as one 8-byte store, straight from the registers that hold them
+        if (t < (RS / 2) * M) {
+          const int pr = t / M, m = t % M, n = g * RS + 2 * pr;
+          if (n < p.N) {
+            float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; w++) {
+              y0 += pb[((2 * pr) * CONSUMER_WARPS + w) * M + m];
+              y1 += pb[((2 * pr + 1) * CONSUMER_WARPS + w) * M + m];
+            }
+            y0 *= rstd[m];
+            y1 *= rstd[m];
+            if (p.bias) { y0 += __bfloat162float(p.bias[n]); y1 += __bfloat162float(p.bias[n + 1]); }
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(y0, y1);
+            tp_ll_store(p.ho, ((size_t)m * p.ldo + n) / 2, *reinterpret_cast<const uint32_t*>(&pk), ll_seq);
+          }
+        }
       } else if (t < RS * M) {
         const int r = t / M, m = t % M, n = g * RS + r;
         if (n < p.N) {
@@ -254,38 +278,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
       }
     }
   }
-  // ---- tensor-parallel hand-over (consumer warps only; the producer warp has returned) ----
-  if constexpr (HO == 1) {
-    // y sits in this GPU's memory.  The last CTA to finish copies it into every rank's staging slot with
-    // 16-byte peer stores, orders them with ONE system-scope fence and raises the flags (a fence per CTA
-    // after scattered 2-byte peer stores measured slower than a separate all-reduce kernel).
-    __shared__ int last_s;
-    __threadfence();
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    if (threadIdx.x == 0) {
-      const int last = atomicAdd(p.ho.push_ticket, 1) == (int)gridDim.x - 1;
-      if (last) *p.ho.push_ticket = 0;
-      last_s = last;
-    }
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    if (last_s) {
-      __threadfence();
-      const int n_vec = M * p.ldo / 8;
-      for (int v = threadIdx.x; v < n_vec; v += CONSUMER_WARPS * 32) {
-        const uint4 val = tp_ld_cg16(reinterpret_cast<const uint4*>(p.out) + v);
-        for (int r = 0; r < p.ho.n_push; r++) reinterpret_cast<uint4*>(p.ho.push_dst[r])[v] = val;
-      }
-      __threadfence_system();
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (threadIdx.x < p.ho.n_push) tp_red_release_sys_add(p.ho.push_flag[threadIdx.x], 1);
-    }
-  }
   if constexpr (HO == 2) {
+    // every CTA has read the slots once it is here: the last one advances the parity's epoch, which is what the
+    // next hand-over on this parity (two hand-overs from now) will stamp its words with
     asm volatile("bar.sync 1, 256;" ::: "memory");
-    if (threadIdx.x == 0 && atomicAdd(p.ho.part_ticket, 1) == (int)gridDim.x - 1) {
-      *p.ho.part_ticket = 0;                               // every CTA has read the partials: clear for the parity's next use
-      for (int r = 0; r < p.ho.n_part; r++) *p.ho.part_flag[r] = 0;
-      __threadfence_system();
+    if (threadIdx.x == 0 && atomicAdd(p.ho.ll_ticket, 1) == (int)gridDim.x - 1) {
+      *p.ho.ll_ticket = 0;
+      *reinterpret_cast<volatile int*>(p.ho.ll_epoch) = (int)ll_seq;
+      __threadfence();
     }
   }
 }
@@ -308,10 +308,10 @@ int launch_stream_rb(const StreamParams& p, bool norm, bool swiglu, int grid, si
   }
   // The hand-over roles are separate instantiations: a row-parallel projection that pushes its output has
   // neither norm nor SwiGLU, and a projection that consumes a hand-over always normalises it first.
-  if (p.ho.n_push > 0) {
+  if (p.ho.n_ll > 0 && p.ho.ll_epoch && !p.ho.ll_ticket) {
     if (norm || swiglu) return -2;
     L(false, false, 1)
-  } else if (p.ho.n_part > 0) {
+  } else if (p.ho.n_ll > 0) {
     if (!norm) return -2;
     if (swiglu) L(true, true, 2) else L(true, false, 2)
   } else if (norm) { if (swiglu) L(true, true, 0) else L(true, false, 0) }
@@ -404,14 +404,14 @@ EXO_API int exo_gemv_stream(const void* x, const void* W, const void* bias, cons
   return gemv_stream_launch(x, W, bias, residual, out, norm_w, eps, M, N, K, swiglu, nullptr, st);
 }
 
-// Row-parallel projection whose output is handed to every rank (mode 1: `out` is not written), or a
+// Row-parallel projection whose output is handed to every rank (mode 1: `out` is not written; N must be even), or a
 // projection whose input is the hand-over of the previous one (mode 2: x = x_res + partials, and
 // the reduced residual stream is left in x_out).  `parity` alternates per hand-over.
 EXO_API int exo_gemv_stream_tp(const void* x, const void* W, const void* bias, void* out, const void* norm_w, float eps,
                                int M, int N, int K, int swiglu, int mode, int parity, const void* x_res, void* x_out,
                                cudaStream_t st) {
   TpHandover ho;
-  int rc = exo_tp_handover_fill(&ho, mode, parity, mode == 1 ? (long)M * N : (long)M * K);
+  int rc = exo_tp_handover_fill(&ho, mode == 1 ? 3 : 4, parity, mode == 1 ? (long)M * N : (long)M * K);
   if (rc) return rc;
   if (mode == 2) {
     ho.x_res = (const __nv_bfloat16*)x_res;
@@ -434,7 +434,9 @@ static int gemv_stream_launch(const void* x, const void* W, const void* bias, co
   if (ho) p.ho = *ho; else memset(&p.ho, 0, sizeof(p.ho));
   const int row_bytes = K * 2;
   int RS, stages; size_t fixed;
-  stream_config(M, K, swiglu, &RS, &stages, &fixed);
+  const bool push = ho && ho->n_ll > 0 && !ho->ll_ticket;       // outputs leave in pairs: an even number of rows per stage
+  if (push && (N & 1)) return -2;
+  if (!stream_config(M, K, swiglu || push, &RS, &stages, &fixed)) return -2;
   const int rows_total = swiglu ? N / 2 : N;
   const int rows_per_group = swiglu ? RS / 2 : RS;
   p.RS = RS;

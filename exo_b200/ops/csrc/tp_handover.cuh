@@ -29,6 +29,13 @@ struct TpHandover {
   __nv_bfloat16* x_out;                     // reduced residual stream (written by CTA 0; may be null)
   int* status;                              // device-writable status word of the collectives
   unsigned long long wait_ns;               // budget of a wait on a peer
+  // ---- flag-in-data hand-over of decode rows (batch <= 2), see below ----
+  uint2* ll_mc;                             // multicast address of slot[parity][my rank] (null: store to ll_dst[r])
+  uint2* ll_dst[TP_MAX_RANKS];              // rank r's slot[parity][my rank]
+  const uint2* ll_part[TP_MAX_RANKS];       // my slots [parity][source rank]
+  int* ll_epoch;                            // local: completed hand-overs of this parity
+  int* ll_ticket;                           // local: consumer CTAs that have read the slots
+  int n_ll;                                 // ranks (0: not a flag-in-data hand-over)
 };
 
 __device__ __forceinline__ int tp_ld_acquire_sys(const int* p) {
@@ -63,6 +70,43 @@ __device__ __forceinline__ bool tp_wait_flag(int* flag, int* status, unsigned lo
   return true;
 }
 
+// Flag-in-data hand-over.  Every 8-byte word carries two bf16 outputs and the hand-over's sequence number
+// (epoch + 1), written with ONE 8-byte store, which arrives whole: the consumer polls the words it needs until
+// their sequence number matches, so there is no separate flag, no system-scope fence and no "last CTA" step on
+// the producer's side — a row is on its way to every rank the moment it is computed.  With the multicast mapping
+// one `multimem.st` reaches all ranks.  The local epoch word of a parity is advanced by the consumer's last CTA;
+// all ranks perform the same sequence of hand-overs, so their epochs agree.
+__device__ __forceinline__ void tp_ll_store(const TpHandover& h, size_t word, uint32_t data, uint32_t seq) {
+  if (h.ll_mc) {
+    asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(h.ll_mc + word), "r"(data), "r"(seq) : "memory");
+  } else {
+    for (int r = 0; r < h.n_ll; r++)
+      asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(h.ll_dst[r] + word), "r"(data), "r"(seq) : "memory");
+  }
+}
+// 16 bytes = two words {data0, seq0, data1, seq1}
+__device__ __forceinline__ uint4 tp_ll_load2(const uint2* p) {
+  uint4 r;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  return r;
+}
+// Polls until the four words at `p` (eight bf16 values) carry `seq`; returns false when the budget runs out.
+__device__ __forceinline__ bool tp_ll_wait8(const uint2* p, uint32_t seq, unsigned long long wait_ns, uint32_t* data4) {
+  unsigned long long t0 = 0;
+  for (unsigned it = 0;; it++) {
+    const uint4 a = tp_ll_load2(p), b = tp_ll_load2(p + 2);
+    if (a.y == seq && a.w == seq && b.y == seq && b.w == seq) {
+      data4[0] = a.x; data4[1] = a.z; data4[2] = b.x; data4[3] = b.z;
+      return true;
+    }
+    if ((it & 63) == 63) {
+      const unsigned long long now = tp_gtime();
+      if (!t0) t0 = now;
+      else if (now - t0 > wait_ns) return false;
+    }
+  }
+}
+
 // Host: fills `out` for the current device from the communicator set up by exo_comm_init.
-// mode 1 = producer fields, 2 = consumer fields.  Returns 0, or <0 without a communicator / slot too small.
+// mode 1 = producer fields, 2 = consumer fields, 3 / 4 = producer / consumer of a flag-in-data hand-over.  Returns 0, or <0 without a communicator / slot too small.
 extern "C" int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems);

@@ -48,13 +48,14 @@ class _RawBuffer:
 
 
 HANDOVER_ROWS = 256           # rows of the residual stream one hand-over slot holds (decode batches)
+LL_ROWS = 2                   # rows handed over by the streaming GEMV with flag-in-data words
 ONE_SHOT_MAX_BYTES = 4 << 20  # (n - 1) * tensor bytes above which the reduction goes two-shot
 
 _SIGS = {
     "exo_symm_alloc": (C.c_void_p, [C.c_size_t]), "exo_symm_free": (C.c_int, [C.c_void_p]),
     "exo_symm_handle": (C.c_int, [C.c_void_p, C.c_void_p]), "exo_symm_open": (C.c_void_p, [C.c_void_p]),
     "exo_symm_close": (C.c_int, [C.c_void_p]), "exo_comm_header_bytes": (C.c_size_t, []),
-    "exo_comm_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int] + [C.c_size_t] * 8),
+    "exo_comm_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int] + [C.c_size_t] * 10),
     "exo_comm_reset": (C.c_int, []),
     "exo_comm_handover_bytes": (C.c_size_t, [C.c_int, C.c_size_t]),
     "exo_tp_handover_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
@@ -62,6 +63,7 @@ _SIGS = {
     "exo_gemm_bf16_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p]),
     "exo_tp_handover_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
+    "exo_tp_ll_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
     "exo_gemv_stream_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "exo_comm_status": (C.c_int, []),
@@ -103,9 +105,11 @@ def arena_layout(lib, n: int, max_rows: int, hidden: int, vocab_shard: int, max_
     x_bytes = (max_rows * hidden * 2 + 4095) // 4096 * 4096
     h_off = x_off + 2 * x_bytes
     n_off = h_off + 2 * x_bytes
+    ll_off = n_off + 2 * x_bytes
+    ll_slot = (LL_ROWS * hidden * 4 + 4095) // 4096 * 4096      # 8-byte words of two bf16 values + sequence number
     return dict(slot=slot, gather_off=gather_off, gather_bytes=gather_bytes, handover_off=handover_off,
                 handover_slot=handover_slot, x_off=x_off, x_bytes=x_bytes, h_off=h_off, n_off=n_off,
-                total=n_off + 2 * x_bytes)
+                ll_off=ll_off, ll_slot=ll_slot, total=ll_off + 2 * n * ll_slot)
 
 
 class Handover:
@@ -113,17 +117,18 @@ class Handover:
     staging slots.  ``norm_linear`` consumes it inside the next projection; ``value()`` gives the tensor
     (running the stand-alone finish kernel if nobody consumed it)."""
 
-    def __init__(self, comm: "FusedComm", parity: int, residual: torch.Tensor | None, rows: int, cols: int):
+    def __init__(self, comm: "FusedComm", parity: int, residual: torch.Tensor | None, rows: int, cols: int, ll: bool = True):
         self.comm, self.parity, self.residual, self.shape = comm, parity, residual, (rows, cols)
         ref = residual if residual is not None else None
         self.out = torch.empty(rows, cols, dtype=torch.bfloat16, device=comm.device) if ref is None else torch.empty_like(ref)
         self.done = False
+        self.ll = ll      # flag-in-data words from the streaming GEMV (else: the GEMM epilogue's staged rows + flags)
 
     def norm_linear(self, norm_w, eps, w, bias=None, swiglu=False):
         M, Kd = self.shape
         N = w.shape[0]
         lib = self.comm.lib
-        if not self.done and M > 2 and Kd % 8 == 0:
+        if not self.done and not self.ll and Kd % 8 == 0:
             # batched decode: one kernel finishes the reduction, leaves the residual stream and the normalised rows
             xn = torch.empty_like(self.out)
             K._chk(lib.exo_tp_handover_rmsnorm(K._ptr(self.residual), norm_w.data_ptr(), eps, self.out.data_ptr(), xn.data_ptr(),
@@ -131,7 +136,8 @@ class Handover:
             K._count()
             self.done = True
             return K.linear(xn, w, bias, None, None, 0.0, swiglu)
-        if self.done or not isinstance(w, torch.Tensor) or not lib.exo_gemv_stream_supported(M, N, Kd, int(swiglu)):
+        if (self.done or not self.ll or not isinstance(w, torch.Tensor)
+                or not lib.exo_gemv_stream_supported(M, N, Kd, int(swiglu))):
             return K.linear(self.value(), w, bias, None, norm_w, eps, swiglu)
         y = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device=self.out.device)
         K._chk(lib.exo_gemv_stream_tp(None, w.data_ptr(), K._ptr(bias), y.data_ptr(), K._ptr(norm_w), eps, M, N, Kd, int(swiglu),
@@ -147,8 +153,8 @@ class Handover:
     def value(self) -> torch.Tensor:
         if not self.done:
             n = self.shape[0] * self.shape[1]
-            K._chk(self.comm.lib.exo_tp_handover_finish(K._ptr(self.residual), self.out.data_ptr(), n, self.parity, K._st()),
-                   "handover finish")
+            fn = self.comm.lib.exo_tp_ll_finish if self.ll else self.comm.lib.exo_tp_handover_finish
+            K._chk(fn(K._ptr(self.residual), self.out.data_ptr(), n, self.parity, K._st()), "handover finish")
             K._count()
             self.done = True
         return self.out
@@ -272,7 +278,8 @@ class FusedComm:
             self._open_ipc(L["total"])
         arr = (C.c_void_p * n)(*self.peers)
         K._chk(lib.exo_comm_init(arr, self.mc_ptr or None, n, self.rank, L["slot"], L["gather_off"], L["handover_off"],
-                                 L["handover_slot"], L["x_off"], L["x_bytes"], L["h_off"], L["n_off"]), "comm init")
+                                 L["handover_slot"], L["x_off"], L["x_bytes"], L["h_off"], L["n_off"], L["ll_off"],
+                                 L["ll_slot"]), "comm init")
         dist.barrier(group=group)
         raw = torch.as_tensor(_RawBuffer(self.local + self.gather_off, L["gather_bytes"]), device=device)
         self.gather_buf = raw.view(torch.bfloat16)
@@ -282,7 +289,8 @@ class FusedComm:
                 p = lib.exo_comm_region(which, parity)
                 self._views[(which, parity)] = torch.as_tensor(_RawBuffer(p, L["x_bytes"]), device=device).view(torch.bfloat16)
         self._ar = 0
-        self._ho = 0             # hand-overs issued so far (parity = low bit)
+        self._ho = 0             # GEMM-epilogue hand-overs issued so far (parity = low bit)
+        self._ll = 0             # flag-in-data hand-overs issued so far
         self._rn = 0             # reduce + norm collectives issued so far
         self.n_collectives = 0
         self.n_handovers = 0
@@ -412,17 +420,17 @@ class FusedComm:
         N = w.shape[0]
         fits = (self.use_handover and x.dtype == torch.bfloat16 and 0 < M and M * N * 2 <= self.handover_slot
                 and isinstance(w, torch.Tensor))       # block-scaled fp8 weights take the GEMM + reduction path
-        if fits and M <= 2 and K.use_stream_gemv and self.lib.exo_gemv_stream_supported(M, N, Kd, 0):
+        if (fits and M <= LL_ROWS and N % 8 == 0 and K.use_stream_gemv
+                and self.lib.exo_gemv_stream_supported(M, N, Kd, 1)):     # 1: rows leave in pairs, like the gate/up form
             K.ensure_stream_init(x.device)
-            parity = self._ho & 1
-            self._ho += 1
+            parity = self._ll & 1
+            self._ll += 1
             x = x.contiguous()
-            y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)      # this rank's partial (pushed by the kernel's last CTA)
-            K._chk(self.lib.exo_gemv_stream_tp(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), None, 0.0, M, N, Kd, 0, 1, parity,
+            K._chk(self.lib.exo_gemv_stream_tp(x.data_ptr(), w.data_ptr(), None, None, None, 0.0, M, N, Kd, 0, 1, parity,
                                                None, None, K._st()), "gemv_stream_tp push")
             K._count()
             self.n_handovers += 1
-            return Handover(self, parity, residual, M, N)
+            return Handover(self, parity, residual, M, N, ll=True)
         if (fits and self.handover_gemm and M > K.SMALL_M and K.gemm_impl is not None and Kd >= 64 and Kd % 8 == 0
                 and N % 8 == 0):
             # batched decode: the tcgen05 GEMM's epilogue does the peer stores
@@ -436,7 +444,7 @@ class FusedComm:
             K._chk(self.lib.exo_gemm_bf16_tp(x.data_ptr(), w.data_ptr(), None, M, N, Kd, splits, parity, K._st()), "gemm_tp push")
             K._count()
             self.n_handovers += 1
-            return Handover(self, parity, residual, M, N)
+            return Handover(self, parity, residual, M, N, ll=False)
         if x.dtype == torch.bfloat16 and self.fits(M, N):
             buf, parity = self.partial_out(M, N)
             K.linear(x, w, out=buf)                      # the projection writes straight into this rank's arena

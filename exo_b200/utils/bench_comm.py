@@ -62,7 +62,7 @@ def main() -> None:
     dist.init_process_group("nccl", device_id=dev)
     from ..ops import cuda as K
     from ..parallel.comm import NcclComm
-    from ..parallel.fused import FusedComm
+    from ..parallel.fused import FusedComm, Reduction
     K.load()
     H = a.hidden
     fused = FusedComm(dev, max_rows=4096, hidden=H, vocab_shard=1024)
@@ -73,24 +73,38 @@ def main() -> None:
         if rank == 0:
             print(msg, flush=True)
 
-    say(f"ranks {world}; link basis {LINK_GBS:.0f} GB/s per direction (measured peer copy)")
-    for rows in (1, 32, 256, 2048, 4096):
+    say(f"ranks {world}; transport {fused.transport}; link basis {LINK_GBS:.0f} GB/s per direction (measured peer copy)")
+    from .. import ops
+    nw = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    for rows in (4, 32, 256, 2048, 4096):
         x = (torch.randn(rows, H, device="cuda", generator=g) * 0.1).bfloat16()
         res = torch.zeros_like(x)
         S = rows * H * 2
         reps = 64 if rows <= 256 else 8
-        t_f = timed(lambda: fused.all_reduce(x, res), reps)
-        t_n = timed(lambda: nccl.all_reduce(x, res), reps)
-        ideal_ms = 2 * (world - 1) / world * S / (LINK_GBS * 1e9) * 1e3
-        say(f"all-reduce [{rows} x {H}] bf16 ({S >> 10} KiB): peer-memory {t_f * 1e3:8.1f} us   NCCL {t_n * 1e3:8.1f} us   "
-            f"two-shot link time {ideal_ms * 1e3:7.1f} us -> {ideal_ms / t_f:4.2f} of the link roofline (peer-memory)")
+
+        def ours():
+            # what the model does after a row-parallel projection: the partial sits in the arena, one kernel forms
+            # residual + sum over ranks and the RMSNorm of it
+            buf, parity = fused.partial_out(rows, H)
+            buf.copy_(x)
+            return Reduction(fused, parity, res, rows, H).norm(nw, 1e-5)
+
+        def base():
+            return ops.rmsnorm(nccl.all_reduce(x, res), nw, 1e-5)[0]
+        t_f = timed(ours, reps)
+        t_c = timed(lambda: fused.region(0, 0, rows, H).copy_(x), reps)        # the staging copy alone (a GEMM writes there directly)
+        t_n = timed(base, reps)
+        two = fused.two_shot(rows, H)
+        wire = (2 * (world - 1) / world * S) if two else ((world - 1) * S)      # bytes leaving each GPU
+        ideal_ms = wire / (LINK_GBS * 1e9) * 1e3
+        say(f"sum over ranks + residual + RMSNorm [{rows} x {H}] bf16 ({S >> 10} KiB, {'two' if two else 'one'}-shot): "
+            f"fused kernel {(t_f - t_c) * 1e3:8.1f} us (+{t_c * 1e3:.1f} us staging copy)   NCCL all-reduce + norm kernel "
+            f"{t_n * 1e3:8.1f} us   link time {ideal_ms * 1e3:7.1f} us -> {ideal_ms / max(t_f - t_c, 1e-9):4.2f} of the link roofline")
     # row-parallel down projection of a decode step: hand-over (no collective kernel; the sum is formed by the consumer)
     # against projection + all-reduce.  The consumer here is the next layer's RMSNorm + qkv projection.
     Kd = a.ffn // world
     w_down = (torch.randn(H, Kd, device="cuda", generator=g) * 0.02).bfloat16()
     w_qkv = (torch.randn(H + 2 * (H // 4), H, device="cuda", generator=g) * 0.02).bfloat16()
-    nw = torch.ones(H, device="cuda", dtype=torch.bfloat16)
-    from .. import ops
     for rows in (1, 2):
         x = (torch.randn(rows, Kd, device="cuda", generator=g) * 0.1).bfloat16()
         res = torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)

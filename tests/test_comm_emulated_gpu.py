@@ -23,7 +23,7 @@ def _setup(n_ranks, rank, rows, hidden):
     arenas = [torch.zeros(L["total"], dtype=torch.uint8, device="cuda") for _ in range(n_ranks)]
     arr = (C.c_void_p * n_ranks)(*[a.data_ptr() for a in arenas])
     rc = lib.exo_comm_init(arr, None, n_ranks, rank, L["slot"], L["gather_off"], L["handover_off"], L["handover_slot"],
-                           L["x_off"], L["x_bytes"], L["h_off"], L["n_off"])
+                           L["x_off"], L["x_bytes"], L["h_off"], L["n_off"], L["ll_off"], L["ll_slot"])
     assert rc == 0
     return lib, K, L, arenas
 
@@ -136,6 +136,62 @@ def test_a_wait_that_runs_out_returns_sets_the_status_word_and_leaves_the_contex
         # and an ordinary kernel still runs on this context
         y = K.rmsnorm(x, torch.ones(cols, device="cuda", dtype=torch.bfloat16), 1e-5)[0]
         assert torch.isfinite(y.float()).all()
+    finally:
+        lib.exo_set_collective_timeout_us(2000000)
+        lib.exo_comm_reset()
+
+
+def _ll_slot(arena, L, n_ranks, parity, src, n_values):
+    off = L["ll_off"] + (parity * n_ranks + src) * L["ll_slot"]
+    return arena[off:off + n_values * 4].view(torch.int32).view(-1, 2)      # [words, (two bf16, sequence number)]
+
+
+@pytest.mark.parametrize("M", [1, 2])
+def test_flag_in_data_handover_between_streaming_projections(M):
+    """Row-parallel GEMV pushes (data, sequence) words; the next RMSNorm + GEMV polls them in its prologue."""
+    from exo_b200.ops import reference as ref
+    H, Kr, N2 = 4096, 1024, 6144
+    lib, K, L, (A, B) = _setup(2, 0, 256, H)
+    K.ensure_stream_init(torch.device("cuda", 0))
+    g = torch.Generator(device="cuda").manual_seed(11 + M)
+    st = torch.cuda.current_stream().cuda_stream
+    w_o = (torch.randn(H, Kr, device="cuda", generator=g) / 32).bfloat16()
+    w_up = (torch.randn(N2, H, device="cuda", generator=g) / 64).bfloat16()
+    norm_w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).bfloat16()
+    for it in range(4):                                   # both parities twice: the epoch must advance each time
+        parity, seq = it & 1, it // 2 + 1
+        x = torch.randn(M, Kr, device="cuda", generator=g).bfloat16()
+        res = torch.randn(M, H, device="cuda", generator=g).bfloat16()
+        peer = torch.randn(M, H, device="cuda", generator=g).bfloat16()       # what rank 1's projection would have sent
+        words = _ll_slot(A, L, 2, parity, 1, M * H)
+        words[:, 0] = peer.view(torch.int32).view(-1)
+        words[:, 1] = seq
+        assert lib.exo_gemv_stream_tp(x.data_ptr(), w_o.data_ptr(), None, None, None, 0.0, M, H, Kr, 0, 1, parity,
+                                      None, None, st) == 0
+        h_out = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+        y = torch.empty(M, N2, dtype=torch.bfloat16, device="cuda")
+        assert lib.exo_gemv_stream_tp(None, w_up.data_ptr(), None, y.data_ptr(), norm_w.data_ptr(), 1e-5, M, N2, H, 0, 2,
+                                      parity, res.data_ptr(), h_out.data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        mine = ref.linear(x.float(), w_o.float()).bfloat16()
+        # our words reached both arenas with this hand-over's sequence number
+        for arena in (A, B):
+            got = _ll_slot(arena, L, 2, parity, 0, M * H)
+            assert bool((got[:, 1] == seq).all())
+            sent = got[:, 0].contiguous().view(torch.bfloat16).view(M, H)
+            assert (sent.float() - mine.float()).abs().max() <= 0.02 * mine.float().abs().max()
+        sent = _ll_slot(A, L, 2, parity, 0, M * H)[:, 0].contiguous().view(torch.bfloat16).view(M, H)
+        want_h = (res.float() + sent.float() + peer.float()).bfloat16()
+        assert torch.equal(h_out, want_h)
+        want_y = ref.linear(ref.rmsnorm(want_h.float(), norm_w.float(), 1e-5)[0], w_up.float())
+        assert (y.float() - want_y).abs().max() <= 0.02 * want_y.abs().max()
+    K.check_status()
+    # a hand-over nobody pushed: the consumer gives up within the budget and says so
+    lib.exo_set_collective_timeout_us(20000)
+    try:
+        assert lib.exo_tp_ll_finish(None, h_out.data_ptr(), M * H, 0, st) == 0
+        torch.cuda.synchronize()
+        assert lib.exo_comm_status() == 4
     finally:
         lib.exo_set_collective_timeout_us(2000000)
         lib.exo_comm_reset()
