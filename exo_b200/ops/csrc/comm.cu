@@ -9,7 +9,7 @@
 //                    status  int32 at +512                       device-side error word (timeouts)
 //   [4 KB, ...)      staging [2 parities][n_ranks][slot_bytes]   partials pushed by each source rank
 //   [... , end)      gather  [gather_bytes]                      all-gather target (vocab logits)
-//   then             hand-over staging, and the regions of the in-switch reduction (see "reduce + norm" below):
+//   then             the regions of the in-switch reduction (see "reduce + norm" below):
 //                    partial [2 parities][x_bytes]  this rank's not-yet-reduced projection output
 //                    hbuf / nbuf [2][x_bytes]       residual stream / normalised rows written by the two-shot form
 //   header +2048     barrier flags int32 [2 parities][8] "partial ready", +2112 [2][8] "rows broadcast", +2176 tickets [2]
@@ -29,8 +29,6 @@
 namespace {
 
 constexpr int MAX_RANKS = 8;
-// hand-over region of the header: flags int32 [2][8] at +1024, producer tickets [2] at +1280, consumer tickets [2] at +1344
-constexpr size_t HO_FLAGS = 1024, HO_PTICKET = 1280, HO_CTICKET = 1344;
 constexpr size_t HDR_BYTES = 4096;
 constexpr size_t BAR_IN = 2048, BAR_OUT = 2112, BAR_TICKET = 2176;
 constexpr size_t LL_EPOCH = 2304, LL_TICKET = 2368;   // flag-in-data hand-over: int32 [2 parities] each
@@ -40,8 +38,6 @@ struct CommCtx {
   int n, rank;
   size_t slot_bytes;          // bytes of one staging slot
   size_t gather_off;          // byte offset of the gather region
-  size_t handover_off;        // byte offset of the hand-over staging [2 parities][n][handover_slot] (0 = none)
-  size_t handover_slot;       // bytes of one hand-over slot
   uint8_t* mc;                // multicast address of the arena (nullptr: plain peer loads / stores)
   size_t x_off, x_bytes;      // partial buffers [2 parities][x_bytes] (0 = none)
   size_t h_off, n_off;        // two-shot outputs [2][x_bytes]: residual stream, normalised rows
@@ -437,12 +433,9 @@ EXO_API int exo_symm_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 EXO_API size_t exo_comm_header_bytes() { return HDR_BYTES; }
 
 // arenas: n pointers (index = rank; own arena at [rank]).
-EXO_API size_t exo_comm_handover_bytes(int n, size_t slot) { return 2 * (size_t)n * slot; }
-
 // `mc` = multicast address of the arena or null; x_off / x_bytes / h_off / n_off describe the regions of the
 // reduce + norm kernels (x_bytes = 0: not present), ll_off / ll_slot those of the flag-in-data hand-over.
-EXO_API int exo_comm_init(void** arenas, void* mc, int n, int rank, size_t slot_bytes, size_t gather_off, size_t handover_off,
-                          size_t handover_slot, size_t x_off, size_t x_bytes, size_t h_off, size_t n_off, size_t ll_off,
+EXO_API int exo_comm_init(void** arenas, void* mc, int n, int rank, size_t slot_bytes, size_t gather_off, size_t x_off, size_t x_bytes, size_t h_off, size_t n_off, size_t ll_off,
                           size_t ll_slot) {
   int dev;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || n > MAX_RANKS || n < 1 || rank < 0 || rank >= n) return -1;
@@ -450,7 +443,7 @@ EXO_API int exo_comm_init(void** arenas, void* mc, int n, int rank, size_t slot_
   if (!status) return -1;
   CommCtx c;
   for (int i = 0; i < MAX_RANKS; i++) c.arena[i] = i < n ? (uint8_t*)arenas[i] : nullptr;
-  c.n = n; c.rank = rank; c.slot_bytes = slot_bytes; c.gather_off = gather_off; c.handover_off = handover_off; c.handover_slot = handover_slot;
+  c.n = n; c.rank = rank; c.slot_bytes = slot_bytes; c.gather_off = gather_off;
   c.mc = (uint8_t*)mc; c.x_off = x_off; c.x_bytes = x_bytes; c.h_off = h_off; c.n_off = n_off;
   c.ll_off = ll_off; c.ll_slot = ll_slot;
   c.status = status;
@@ -576,109 +569,6 @@ EXO_API int exo_comm_has_multicast() {
 // ---- hand-over (row-parallel projection -> consumer, no collective kernel) -----------------------
 namespace {
 
-// Stand-alone consumer: out = residual + sum_r slot[r]; used when the next op cannot take the
-// hand-over itself.  One CTA per 2048 elements; flags are cleared by the last CTA.
-__global__ void __launch_bounds__(256) handover_finish_kernel(const TpHandover h, __nv_bfloat16* out, int n_vec) {
-  pdl_trigger();
-  pdl_wait();
-  __shared__ int ok_s;
-  if (threadIdx.x == 0) ok_s = 1;
-  __syncthreads();
-  if (threadIdx.x < h.n_part && !tp_wait_flag(h.part_flag[threadIdx.x], h.status, h.wait_ns)) ok_s = 0;
-  __syncthreads();
-  if (ok_s) {
-    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += gridDim.x * blockDim.x) {
-      float acc[8];
-      if (h.x_res) unpack8(reinterpret_cast<const uint4*>(h.x_res)[v], acc);
-      else {
-#pragma unroll
-        for (int e = 0; e < 8; e++) acc[e] = 0.f;
-      }
-      for (int r = 0; r < h.n_part; r++) {
-        float f[8];
-        unpack8(ld_cg16(reinterpret_cast<const uint4*>(h.part[r]) + v), f);
-#pragma unroll
-        for (int e = 0; e < 8; e++) acc[e] += f[e];
-      }
-      reinterpret_cast<uint4*>(out)[v] = pack8(acc);
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(h.part_ticket, 1) == (int)gridDim.x - 1) {
-      *h.part_ticket = 0;
-      for (int r = 0; r < h.n_part; r++) *h.part_flag[r] = 0;
-      __threadfence_system();
-    }
-  }
-}
-
-// Consumer for batches that go through the GEMM: one CTA per row forms h = residual + sum_r slot[r]
-// (rank order, rounded to bf16), leaves it in h_out and writes RMSNorm(h) * w into x_out.
-__global__ void __launch_bounds__(256) handover_rmsnorm_kernel(const TpHandover h, const __nv_bfloat16* norm_w, float eps,
-                                                               __nv_bfloat16* x_out, int cols) {
-  pdl_trigger();
-  pdl_wait();
-  __shared__ int ok_s;
-  __shared__ float red[8];
-  if (threadIdx.x == 0) ok_s = 1;
-  __syncthreads();
-  if (threadIdx.x < h.n_part && !tp_wait_flag(h.part_flag[threadIdx.x], h.status, h.wait_ns)) ok_s = 0;
-  __syncthreads();
-  const size_t row = (size_t)blockIdx.x * cols;
-  const int n_vec = cols / 8;
-  float ss = 0.f;
-  if (ok_s) {
-    for (int v = threadIdx.x; v < n_vec; v += blockDim.x) {
-      float acc[8];
-      if (h.x_res) unpack8(reinterpret_cast<const uint4*>(h.x_res + row)[v], acc);
-      else {
-#pragma unroll
-        for (int e = 0; e < 8; e++) acc[e] = 0.f;
-      }
-      for (int r = 0; r < h.n_part; r++) {
-        float f[8];
-        unpack8(ld_cg16(reinterpret_cast<const uint4*>(h.part[r] + row) + v), f);
-#pragma unroll
-        for (int e = 0; e < 8; e++) acc[e] += f[e];
-      }
-      const uint4 packed = pack8(acc);
-      reinterpret_cast<uint4*>(h.x_out + row)[v] = packed;
-      unpack8(packed, acc);
-#pragma unroll
-      for (int e = 0; e < 8; e++) ss += acc[e] * acc[e];
-    }
-  }
-  ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  float tot = 0.f;
-#pragma unroll
-  for (int w = 0; w < 8; w++) tot += red[w];
-  const float rstd = rsqrtf(tot / cols + eps);
-  if (ok_s) {
-    for (int v = threadIdx.x; v < n_vec; v += blockDim.x) {     // second pass re-reads what this CTA just wrote
-      float a[8], w8[8];
-      unpack8(reinterpret_cast<const uint4*>(h.x_out + row)[v], a);
-      unpack8(reinterpret_cast<const uint4*>(norm_w)[v], w8);
-#pragma unroll
-      for (int e = 0; e < 8; e++) a[e] = a[e] * rstd * w8[e];
-      reinterpret_cast<uint4*>(x_out + row)[v] = pack8(a);
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(h.part_ticket, 1) == (int)gridDim.x - 1) {
-      *h.part_ticket = 0;
-      for (int r = 0; r < h.n_part; r++) *h.part_flag[r] = 0;
-      __threadfence_system();
-    }
-  }
-}
-
-
 // Stand-alone consumer of a flag-in-data hand-over (nobody took it in a projection's prologue):
 // out = residual + sum_r slot[r].  The last CTA advances the parity's epoch.
 __global__ void __launch_bounds__(256) ll_finish_kernel(const TpHandover h, __nv_bfloat16* out, int n_vec) {
@@ -693,18 +583,78 @@ __global__ void __launch_bounds__(256) ll_finish_kernel(const TpHandover h, __nv
 #pragma unroll
       for (int e = 0; e < 8; e++) acc[e] = 0.f;
     }
-    for (int r = 0; r < h.n_ll; r++) {
-      uint4 d = make_uint4(0, 0, 0, 0);
-      if (ok && !tp_ll_wait8(h.ll_part[r] + (size_t)v * 4, seq, h.wait_ns, reinterpret_cast<uint32_t*>(&d))) {
-        ok = false;
-        atomicExch(h.status, 4);
-      }
-      float f[8];
-      unpack8(d, f);
-#pragma unroll
-      for (int e = 0; e < 8; e++) acc[e] += f[e];
+    if (ok && !tp_ll_gather8(h, (size_t)v * 4, seq, acc)) {
+      ok = false;
+      atomicExch(h.status, 4);
     }
     reinterpret_cast<uint4*>(out)[v] = pack8(acc);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(h.ll_ticket, 1) == (int)gridDim.x - 1) {
+    *h.ll_ticket = 0;
+    *reinterpret_cast<volatile int*>(h.ll_epoch) = (int)seq;
+    __threadfence();
+  }
+}
+
+
+// Consumer of a flag-in-data hand-over for decode batches (the producer is the GEMM's epilogue): one CTA per row
+// forms h = residual + sum_r slot[r] (rank order, rounded to bf16), leaves it in h_out and writes RMSNorm(h) * w
+// into x_out (norm_w null: h only).  The whole collective is ONE one-way trip of the producers' stores; nothing
+// is signalled back.  The last CTA advances the parity's epoch.
+template <int V>
+__global__ void __launch_bounds__(256)
+ll_reduce_norm_kernel(const TpHandover h, const __nv_bfloat16* __restrict__ norm_w, float eps, __nv_bfloat16* h_out,
+                      __nv_bfloat16* x_out, int rows, int cols) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[8];
+  const uint32_t seq = (uint32_t)(*reinterpret_cast<volatile const int*>(h.ll_epoch) + 1);
+  const int n_vec = cols / 8;
+  bool ok = true;      // after the first wait that ran out, the rest of this thread's words are not polled again
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = (size_t)row * cols;
+    float v[V][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+      const int iv = threadIdx.x + j * 256;
+      if (iv < n_vec) {
+        const size_t off = base + (size_t)iv * 8;
+        if (h.x_res) unpack8(*reinterpret_cast<const uint4*>(h.x_res + off), v[j]);
+        else {
+#pragma unroll
+          for (int e = 0; e < 8; e++) v[j][e] = 0.f;
+        }
+        if (ok && !tp_ll_gather8(h, off / 2, seq, v[j])) { ok = false; atomicExch(h.status, 4); }
+        const uint4 packed = pack8(v[j]);
+        *reinterpret_cast<uint4*>(h_out + off) = packed;
+        unpack8(packed, v[j]);
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss += v[j][e] * v[j][e];
+      }
+    }
+    if (norm_w) {
+      ss = warp_sum(ss);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; w++) tot += red[w];
+      const float rstd = rsqrtf(tot / cols + eps);
+#pragma unroll
+      for (int j = 0; j < V; j++) {
+        const int iv = threadIdx.x + j * 256;
+        if (iv < n_vec) {
+          float w8[8];
+          unpack8(*reinterpret_cast<const uint4*>(norm_w + (size_t)iv * 8), w8);
+#pragma unroll
+          for (int e = 0; e < 8; e++) v[j][e] = v[j][e] * rstd * w8[e];
+          *reinterpret_cast<uint4*>(x_out + base + (size_t)iv * 8) = pack8(v[j]);
+        }
+      }
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0 && atomicAdd(h.ll_ticket, 1) == (int)gridDim.x - 1) {
@@ -721,7 +671,6 @@ int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems) {
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return -4;
   const CommCtx& c = g_ctx[dev];
   memset(out, 0, sizeof(*out));
-  if (mode <= 2 && (!c.handover_off || (size_t)n_elems * 2 > c.handover_slot)) return -6;
   uint8_t* mine = c.arena[c.rank];
   out->status = c.status;
   out->wait_ns = exo_wait_budget_ns();
@@ -741,21 +690,29 @@ int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems) {
     }
     return 0;
   }
-  if (mode == 1) {
-    out->n_push = c.n;
-    for (int r = 0; r < c.n; r++) {
-      out->push_dst[r] = reinterpret_cast<__nv_bfloat16*>(c.arena[r] + c.handover_off + ((size_t)parity * c.n + c.rank) * c.handover_slot);
-      out->push_flag[r] = reinterpret_cast<int*>(c.arena[r] + HO_FLAGS) + parity * MAX_RANKS + c.rank;
-    }
-    out->push_ticket = reinterpret_cast<int*>(mine + HO_PTICKET) + parity;
-  } else {
-    out->n_part = c.n;
-    for (int r = 0; r < c.n; r++) {
-      out->part[r] = reinterpret_cast<const __nv_bfloat16*>(mine + c.handover_off + ((size_t)parity * c.n + r) * c.handover_slot);
-      out->part_flag[r] = reinterpret_cast<int*>(mine + HO_FLAGS) + parity * MAX_RANKS + r;
-    }
-    out->part_ticket = reinterpret_cast<int*>(mine + HO_CTICKET) + parity;
-  }
+  return -2;
+}
+
+
+// h_out = residual + sum over ranks of the flag-in-data hand-over on `parity`; x_out = RMSNorm(h_out) * norm_w
+// (norm_w null: h_out only).  [rows, cols] bf16, cols % 8 == 0, cols <= 8192.
+EXO_API int exo_tp_ll_reduce_norm(const void* residual, const void* norm_w, float eps, void* h_out, void* x_out, int rows,
+                                  int cols, int parity, cudaStream_t st) {
+  if (cols % 8 || cols > 8192 || rows <= 0 || !h_out || (norm_w && !x_out)) return -2;
+  TpHandover h;
+  int rc = exo_tp_handover_fill(&h, 4, parity, (long)((rows + 1) & ~1) * cols);
+  if (rc) return rc;
+  h.x_res = (const __nv_bfloat16*)residual;
+  const int per_thread = (cols / 8 + 255) / 256;
+  cudaError_t e;
+  if (per_thread <= 2)
+    e = launch_pdl(ll_reduce_norm_kernel<2>, dim3(rows), dim3(256), 0, st, h, (const __nv_bfloat16*)norm_w, eps,
+                   (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out, rows, cols);
+  else
+    e = launch_pdl(ll_reduce_norm_kernel<4>, dim3(rows), dim3(256), 0, st, h, (const __nv_bfloat16*)norm_w, eps,
+                   (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out, rows, cols);
+  if (e != cudaSuccess) return (int)e;
+  EXO_CHECK_LAUNCH();
   return 0;
 }
 
@@ -770,38 +727,6 @@ EXO_API int exo_tp_ll_finish(const void* residual, void* out, long n_elems, int 
   int grid = (n_vec + 255) / 256;
   if (grid > 32) grid = 32;
   cudaError_t e = launch_pdl(ll_finish_kernel, dim3(grid), dim3(256), 0, st, h, (__nv_bfloat16*)out, n_vec);
-  if (e != cudaSuccess) return (int)e;
-  EXO_CHECK_LAUNCH();
-  return 0;
-}
-
-// out = residual + sum over ranks of the partials handed over on `parity` (n_elems multiple of 8).
-EXO_API int exo_tp_handover_finish(const void* residual, void* out, long n_elems, int parity, cudaStream_t st) {
-  if (n_elems % 8) return -2;
-  TpHandover h;
-  int rc = exo_tp_handover_fill(&h, 2, parity, n_elems);
-  if (rc) return rc;
-  h.x_res = (const __nv_bfloat16*)residual;
-  const int n_vec = (int)(n_elems / 8);
-  int grid = (n_vec + 255) / 256;
-  if (grid > 32) grid = 32;
-  cudaError_t e = launch_pdl(handover_finish_kernel, dim3(grid), dim3(256), 0, st, h, (__nv_bfloat16*)out, n_vec);
-  if (e != cudaSuccess) return (int)e;
-  EXO_CHECK_LAUNCH();
-  return 0;
-}
-
-// h_out = residual + sum of the handed-over partials; x_out = RMSNorm(h_out) * norm_w.   [rows, cols], cols % 8 == 0
-EXO_API int exo_tp_handover_rmsnorm(const void* residual, const void* norm_w, float eps, void* h_out, void* x_out, int rows,
-                                    int cols, int parity, cudaStream_t st) {
-  if (cols % 8 || rows <= 0) return -2;
-  TpHandover h;
-  int rc = exo_tp_handover_fill(&h, 2, parity, (long)rows * cols);
-  if (rc) return rc;
-  h.x_res = (const __nv_bfloat16*)residual;
-  h.x_out = (__nv_bfloat16*)h_out;
-  cudaError_t e = launch_pdl(handover_rmsnorm_kernel, dim3(rows), dim3(256), 0, st, h, (const __nv_bfloat16*)norm_w, eps,
-                             (__nv_bfloat16*)x_out, cols);
   if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
   return 0;

@@ -21,17 +21,19 @@ struct GemmParams {
   float* partial;         // [splits, M, N] fp32 (split-K only)
   int* counters;          // [tiles] zero-initialised, self-resetting
   int* err;               // device error word
-  TpHandover ho;          // row-parallel output handed to every rank (n_push > 0): `out` is then not written
+  TpHandover ho;          // row-parallel output handed to every rank (n_ll > 0): `out` is then not written
 };
 
 // Called by the four epilogue warps (threads 64..191) once the MMA warp has committed `acc_full`.
-// HO: the output goes to every rank's hand-over slot instead of `out` (a separate instantiation, so that the
-// plain kernel's store loop carries none of it).
+// HO: the output goes to every rank's hand-over slot as flag-in-data words instead of `out` (a separate
+// instantiation, so that the plain kernel's store loop carries none of it); N must be even.
 template <int BN, bool HO = false>
 __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uint64_t* acc_full, int* abort_flag,
                                          int* is_last_s, int n0, int m0, int split, int nkb, int warp, int lane) {
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
     const int n = n0 + quad * 32 + lane;       // output feature owned by this thread
+    uint32_t ll_seq = 0;                       // sequence number of this hand-over's words (see tp_handover.cuh)
+    if constexpr (HO) ll_seq = (uint32_t)(*reinterpret_cast<volatile const int*>(p.ho.ll_epoch) + 1);
     bool ok = tc::mbar_wait_backoff(acc_full, 0, 400);
     if (!ok) { atomicExch(p.err, tc::ERR_ACC_TIMEOUT); *abort_flag = 1; }
     tc::tc_fence_after();
@@ -44,7 +46,22 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
         float v[16];
         tc::tmem_ld16(taddr + c, v);   // warp-collective: executed by all lanes regardless of bounds
         tc::tmem_ld_wait();
-        if (ok && n < p.N) {
+        if constexpr (HO) {
+          // Hand-over: adjacent lanes own adjacent features.  Lanes pair up, the even lane keeps the even rows and
+          // the odd lane the odd rows of the pair's two features, and each word (two bf16 + sequence number)
+          // leaves for every rank as one 8-byte store.  Warp-collective: no lane may skip the shuffles.
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            const float mine0 = v[j] + bias, mine1 = v[j + 1] + bias;
+            const float other = __shfl_xor_sync(0xffffffffu, (lane & 1) ? mine0 : mine1, 1);
+            const int m = m0 + c + j + (lane & 1);
+            const int ne = n & ~1;
+            if (ok && m < p.M && ne < p.N) {
+              const __nv_bfloat162 pk = (lane & 1) ? __floats2bfloat162_rn(other, mine1) : __floats2bfloat162_rn(mine0, other);
+              tp_ll_store(p.ho, ((size_t)m * p.ldo + ne) / 2, *reinterpret_cast<const uint32_t*>(&pk), ll_seq);
+            }
+          }
+        } else if (ok && n < p.N) {
 #pragma unroll
           for (int j = 0; j < 16; j++) {
             int m = m0 + c + j;
@@ -52,12 +69,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
               float y = v[j] + bias;
               size_t o = (size_t)m * p.ldo + n;
               if (p.residual) y += __bfloat162float(p.residual[o]);
-              const __nv_bfloat16 yb = __float2bfloat16_rn(y);
-              if constexpr (HO) {
-                for (int r = 0; r < p.ho.n_push; r++) p.ho.push_dst[r][o] = yb;     // peer stores
-              } else {
-                p.out[o] = yb;
-              }
+              p.out[o] = __float2bfloat16_rn(y);
             }
           }
         }
@@ -142,17 +154,25 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
 #pragma unroll
           for (int r = 0; r < 2; r++) {
             if (r == 1 && !two) break;
+            if constexpr (HO) {
+              // a thread holds four consecutive features of one row: two words (N is even under a hand-over)
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-              if (nq + j < p.N) {
-                size_t o = (size_t)(m0 + mm + 4 * r) * p.ldo + nq + j;
-                float v = y[r][j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
-                if (p.residual) v += __bfloat162float(p.residual[o]);
-                const __nv_bfloat16 yb = __float2bfloat16_rn(v);
-                if constexpr (HO) {
-                  for (int rr = 0; rr < p.ho.n_push; rr++) p.ho.push_dst[rr][o] = yb;
-                } else {
-                  p.out[o] = yb;
+              for (int j = 0; j < 4; j += 2) {
+                if (nq + j < p.N) {
+                  const float a = y[r][j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
+                  const float b2 = y[r][j + 1] + (p.bias ? __bfloat162float(p.bias[nq + j + 1]) : 0.f);
+                  const __nv_bfloat162 pk = __floats2bfloat162_rn(a, b2);
+                  tp_ll_store(p.ho, ((size_t)(m0 + mm + 4 * r) * p.ldo + nq + j) / 2, *reinterpret_cast<const uint32_t*>(&pk), ll_seq);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                if (nq + j < p.N) {
+                  size_t o = (size_t)(m0 + mm + 4 * r) * p.ldo + nq + j;
+                  float v = y[r][j] + (p.bias ? __bfloat162float(p.bias[nq + j]) : 0.f);
+                  if (p.residual) v += __bfloat162float(p.residual[o]);
+                  p.out[o] = __float2bfloat16_rn(v);
                 }
               }
             }
@@ -160,19 +180,6 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
         }
       }
     }
-  // ---- hand-over: when every CTA of the grid is past its stores, raise one flag per rank ----
-  if constexpr (HO) {
-    __threadfence_system();
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (warp == 2 && lane == 0) {
-      const int total = gridDim.x * gridDim.y * gridDim.z;
-      if (atomicAdd(p.ho.push_ticket, 1) == total - 1) {
-        *p.ho.push_ticket = 0;
-        __threadfence_system();
-        for (int r = 0; r < p.ho.n_push; r++) tp_red_release_sys_add(p.ho.push_flag[r], 1);
-      }
-    }
-  }
 }
 
 // Gate/up pair: accumulator 0 holds the gate rows [n0, n0+128), accumulator 1 (BN columns further on) the up rows of

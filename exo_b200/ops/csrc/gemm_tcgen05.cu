@@ -305,7 +305,7 @@ static int launch_gemm_glu(const CUtensorMap* tw, const CUtensorMap* tx, const G
 template <int BN, int STAGES, bool TWO = false>
 static int launch_gemm(const CUtensorMap* tw, const CUtensorMap* tx, const GemmParams& p, cudaStream_t st) {
   if constexpr (!TWO) {
-    if (p.ho.n_push > 0) return launch_gemm_ho<BN, STAGES, false, true>(tw, tx, p, st);
+    if (p.ho.n_ll > 0) return launch_gemm_ho<BN, STAGES, false, true>(tw, tx, p, st);
   }
   return launch_gemm_ho<BN, STAGES, TWO, false>(tw, tx, p, st);
 }
@@ -354,11 +354,13 @@ EXO_API int exo_gemm_bf16_swiglu(const void* x, const void* W, void* out, int M,
   return launch_gemm_glu(tw, tx, p, st);
 }
 
-// Row-parallel projection whose [M, N] output goes into every rank's hand-over slot (see tp_handover.cuh).
+// Row-parallel projection whose [M, N] output goes into every rank's hand-over slot as flag-in-data words
+// (see tp_handover.cuh); N even.
 EXO_API int exo_gemm_bf16_tp(const void* x, const void* W, const void* bias, int M, int N, int K, int splits, int parity,
                              cudaStream_t st) {
+  if (N & 1) return -2;
   TpHandover ho;
-  int rc = exo_tp_handover_fill(&ho, 1, parity, (long)M * N);
+  int rc = exo_tp_handover_fill(&ho, 3, parity, (long)((M + 1) & ~1) * N);
   if (rc) return rc;
   return gemm_launch(x, W, bias, nullptr, nullptr, M, N, K, N, splits, &ho, st);
 }

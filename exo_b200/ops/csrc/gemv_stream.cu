@@ -121,16 +121,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
 #pragma unroll
             for (int e = 0; e < 8; e++) acc[e] = 0.f;
           }
-          for (int r = 0; r < p.ho.n_ll; r++) {
-            uint4 d = make_uint4(0, 0, 0, 0);
-            if (ll_ok && !tp_ll_wait8(p.ho.ll_part[r] + off / 2, ll_seq, p.ho.wait_ns, reinterpret_cast<uint32_t*>(&d))) {
-              ll_ok = false;
-              atomicExch(p.ho.status, 4 /* peer timeout */);
-            }
-            float f[8];
-            unpack8(d, f);
-#pragma unroll
-            for (int e = 0; e < 8; e++) acc[e] += f[e];
+          if (ll_ok && !tp_ll_gather8(p.ho, off / 2, ll_seq, acc)) {
+            ll_ok = false;
+            atomicExch(p.ho.status, 4 /* peer timeout */);
           }
           const uint4 packed = pack8(acc);
           if (blockIdx.x == 0 && p.ho.x_out) *reinterpret_cast<uint4*>(p.ho.x_out + off) = packed;

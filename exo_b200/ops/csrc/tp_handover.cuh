@@ -1,35 +1,22 @@
-// Tensor-parallel hand-over between a row-parallel projection and the kernel that consumes its
-// all-reduced output, without a collective kernel in between.
+// Tensor-parallel hand-over between a row-parallel projection and the kernel that consumes its all-reduced
+// output, without a collective kernel in between (decode batches).
 //
-// Producer (row-parallel GEMV): every output element is stored straight into the staging slot
-// `[parity][my rank]` of EVERY rank's arena (peer stores over NVSwitch) as the row groups finish;
-// the last CTA of the grid then bumps one flag per rank with a release-scoped remote atomic.
-// Consumer (the next RMSNorm + GEMV, or the stand-alone finish kernel): waits — bounded — until all
-// ranks' flags for `parity` are up, forms  x = residual + sum_r slot[parity][r]  in rank order
-// (every rank gets the same bits), and its last CTA clears the flags for the parity's next use.
-// Two hand-overs in flight are kept apart by the parity bit; a rank cannot run two ahead of a
-// peer because consuming hand-over k needs that peer's push k.
+// Producer (row-parallel GEMV, or the GEMM's epilogue): every pair of adjacent outputs is stored straight into
+// the slot `[parity][my rank]` of EVERY rank's arena as one 8-byte word that also carries the hand-over's
+// sequence number.  Consumer (the next RMSNorm + GEMV, or the reduce + RMSNorm kernel): polls — bounded — the
+// words it needs until they carry that number, and forms  x = residual + sum_r slot[parity][r]  in rank order
+// (every rank gets the same bits).  Two hand-overs in flight are kept apart by the parity bit; a rank cannot run
+// two ahead of a peer because consuming hand-over k needs that peer's push k.
 #pragma once
 #include <cuda_bf16.h>
 
 constexpr int TP_MAX_RANKS = 8;
 
 struct TpHandover {
-  // producer side (n_push > 0)
-  __nv_bfloat16* push_dst[TP_MAX_RANKS];    // rank r's staging slot for my partial
-  int* push_flag[TP_MAX_RANKS];             // rank r's flag word for (parity, me)
-  int* push_ticket;                         // local: CTAs that finished pushing
-  int n_push;
-  // consumer side (n_part > 0)
-  const __nv_bfloat16* part[TP_MAX_RANKS];  // my staging slots, one per source rank
-  int* part_flag[TP_MAX_RANKS];             // my flag words for (parity, src)
-  int* part_ticket;                         // local: CTAs that finished reading
-  int n_part;
   const __nv_bfloat16* x_res;               // residual stream before the reduction (may be null)
   __nv_bfloat16* x_out;                     // reduced residual stream (written by CTA 0; may be null)
   int* status;                              // device-writable status word of the collectives
   unsigned long long wait_ns;               // budget of a wait on a peer
-  // ---- flag-in-data hand-over of decode rows (batch <= 2), see below ----
   uint2* ll_mc;                             // multicast address of slot[parity][my rank] (null: store to ll_dst[r])
   uint2* ll_dst[TP_MAX_RANKS];              // rank r's slot[parity][my rank]
   const uint2* ll_part[TP_MAX_RANKS];       // my slots [parity][source rank]
@@ -57,19 +44,6 @@ __device__ __forceinline__ unsigned long long tp_gtime() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// One thread per source rank polls; returns false when the budget runs out (and records code 4 in the status word).
-__device__ __forceinline__ bool tp_wait_flag(int* flag, int* status, unsigned long long wait_ns) {
-  const unsigned long long t0 = tp_gtime();
-  while (tp_ld_acquire_sys(flag) < 1) {
-    if (tp_gtime() - t0 > wait_ns) {
-      atomicExch(status, 4);
-      return false;
-    }
-    __nanosleep(32);
-  }
-  return true;
-}
-
 // Flag-in-data hand-over.  Every 8-byte word carries two bf16 outputs and the hand-over's sequence number
 // (epoch + 1), written with ONE 8-byte store, which arrives whole: the consumer polls the words it needs until
 // their sequence number matches, so there is no separate flag, no system-scope fence and no "last CTA" step on
@@ -107,6 +81,44 @@ __device__ __forceinline__ bool tp_ll_wait8(const uint2* p, uint32_t seq, unsign
   }
 }
 
+// The same for all source ranks at once: the loads of every rank are in flight together (one L2 round trip per
+// poll instead of one per rank), then the eight values are added to `acc` in rank order, so every rank forms the
+// same bits.  Returns false when the budget runs out (acc is then left partly summed).
+__device__ __forceinline__ bool tp_ll_gather8(const TpHandover& h, size_t word, uint32_t seq, float* acc) {
+  uint4 a[TP_MAX_RANKS], b[TP_MAX_RANKS];
+  unsigned pending = (1u << h.n_ll) - 1u;
+  unsigned long long t0 = 0;
+  for (unsigned it = 0; pending; it++) {
+#pragma unroll
+    for (int r = 0; r < TP_MAX_RANKS; r++)
+      if ((pending >> r) & 1u) {
+        a[r] = tp_ll_load2(h.ll_part[r] + word);
+        b[r] = tp_ll_load2(h.ll_part[r] + word + 2);
+      }
+#pragma unroll
+    for (int r = 0; r < TP_MAX_RANKS; r++)
+      if (((pending >> r) & 1u) && a[r].y == seq && a[r].w == seq && b[r].y == seq && b[r].w == seq) pending &= ~(1u << r);
+    if (pending && (it & 63) == 63) {
+      const unsigned long long now = tp_gtime();
+      if (!t0) t0 = now;
+      else if (now - t0 > h.wait_ns) return false;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < TP_MAX_RANKS; r++)
+    if (r < h.n_ll) {
+      const uint4 d = make_uint4(a[r].x, a[r].z, b[r].x, b[r].z);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(p2[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+  return true;
+}
+
 // Host: fills `out` for the current device from the communicator set up by exo_comm_init.
-// mode 1 = producer fields, 2 = consumer fields, 3 / 4 = producer / consumer of a flag-in-data hand-over.  Returns 0, or <0 without a communicator / slot too small.
+// mode 3 / 4 = producer / consumer of a flag-in-data hand-over.  Returns 0, or <0 without a communicator / slot too small.
 extern "C" int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems);

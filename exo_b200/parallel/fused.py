@@ -12,9 +12,11 @@ after every row-parallel projection (``src/exo/worker/engines/mlx/auto_parallel.
 
 Three forms of "row-parallel projection, then sum over ranks":
 
-* batch <= 2: the streaming GEMV pushes its rows into every rank's staging slot and the next
-  RMSNorm + GEMV sums them in its prologue (:class:`Handover`): no collective kernel at all;
-* decode batches: the GEMM writes its partial into this rank's own arena and ONE kernel forms
+* decode batches up to 64 rows: the projection kernel itself (streaming GEMV, or the GEMM's epilogue) sends its
+  rows to every rank as flag-in-data words, one ``multimem.st`` per 8 bytes; the consumer polls the words it
+  needs (:class:`Handover`).  One one-way trip per collective, no flag, no fence; for one or two rows the
+  consumer is the next RMSNorm + GEMV's prologue, so no collective kernel runs at all;
+* larger batches: the GEMM writes its partial into this rank's own arena and ONE kernel forms
   ``residual + sum`` and the RMSNorm of it, reading the sum through the switch (:class:`Reduction`);
 * prefill chunks: the same kernel in its two-shot form (each rank reduces and normalises 1/N of the
   rows and broadcasts them).
@@ -47,23 +49,20 @@ class _RawBuffer:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
-HANDOVER_ROWS = 256           # rows of the residual stream one hand-over slot holds (decode batches)
-LL_ROWS = 2                   # rows handed over by the streaming GEMV with flag-in-data words
+LL_ROWS = 64                  # largest decode batch handed over with flag-in-data words (one one-way trip per collective)
 ONE_SHOT_MAX_BYTES = 4 << 20  # (n - 1) * tensor bytes above which the reduction goes two-shot
 
 _SIGS = {
     "exo_symm_alloc": (C.c_void_p, [C.c_size_t]), "exo_symm_free": (C.c_int, [C.c_void_p]),
     "exo_symm_handle": (C.c_int, [C.c_void_p, C.c_void_p]), "exo_symm_open": (C.c_void_p, [C.c_void_p]),
     "exo_symm_close": (C.c_int, [C.c_void_p]), "exo_comm_header_bytes": (C.c_size_t, []),
-    "exo_comm_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int] + [C.c_size_t] * 10),
+    "exo_comm_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int] + [C.c_size_t] * 8),
     "exo_comm_reset": (C.c_int, []),
-    "exo_comm_handover_bytes": (C.c_size_t, [C.c_int, C.c_size_t]),
-    "exo_tp_handover_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
-                                          C.c_int, C.c_void_p]),
     "exo_gemm_bf16_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p]),
-    "exo_tp_handover_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
     "exo_tp_ll_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
+    "exo_tp_ll_reduce_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                        C.c_void_p]),
     "exo_gemv_stream_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "exo_comm_status": (C.c_int, []),
@@ -99,46 +98,49 @@ def arena_layout(lib, n: int, max_rows: int, hidden: int, vocab_shard: int, max_
     slot = (max(one_shot, two_shot) + 4095) // 4096 * 4096
     gather_off = hdr + 2 * n * slot
     gather_bytes = max_gather_rows * n * vocab_shard * 2
-    handover_off = (gather_off + gather_bytes + 4095) // 4096 * 4096
-    handover_slot = (HANDOVER_ROWS * hidden * 2 + 4095) // 4096 * 4096
-    x_off = (handover_off + lib.exo_comm_handover_bytes(n, handover_slot) + 4095) // 4096 * 4096
+    x_off = (gather_off + gather_bytes + 4095) // 4096 * 4096
     x_bytes = (max_rows * hidden * 2 + 4095) // 4096 * 4096
     h_off = x_off + 2 * x_bytes
     n_off = h_off + 2 * x_bytes
     ll_off = n_off + 2 * x_bytes
     ll_slot = (LL_ROWS * hidden * 4 + 4095) // 4096 * 4096      # 8-byte words of two bf16 values + sequence number
-    return dict(slot=slot, gather_off=gather_off, gather_bytes=gather_bytes, handover_off=handover_off,
-                handover_slot=handover_slot, x_off=x_off, x_bytes=x_bytes, h_off=h_off, n_off=n_off,
+    return dict(slot=slot, gather_off=gather_off, gather_bytes=gather_bytes, x_off=x_off, x_bytes=x_bytes, h_off=h_off, n_off=n_off,
                 ll_off=ll_off, ll_slot=ll_slot, total=ll_off + 2 * n * ll_slot)
 
 
 class Handover:
-    """The not-yet-reduced output of a row-parallel projection: partials of all ranks sit in this rank's
-    staging slots.  ``norm_linear`` consumes it inside the next projection; ``value()`` gives the tensor
-    (running the stand-alone finish kernel if nobody consumed it)."""
+    """The not-yet-reduced output of a row-parallel projection of a decode step: every rank's rows sit in this
+    rank's slots as flag-in-data words (two bf16 values and the hand-over's sequence number per 8-byte store), sent
+    by the projection kernel itself.  ``norm_linear`` consumes them: for one or two rows inside the next streaming
+    projection's prologue (no kernel in between), for larger batches in one reduce + RMSNorm kernel.  ``value()``
+    gives the reduced tensor (running the stand-alone kernel if nobody consumed the hand-over)."""
 
-    def __init__(self, comm: "FusedComm", parity: int, residual: torch.Tensor | None, rows: int, cols: int, ll: bool = True):
+    def __init__(self, comm: "FusedComm", parity: int, residual: torch.Tensor | None, rows: int, cols: int):
         self.comm, self.parity, self.residual, self.shape = comm, parity, residual, (rows, cols)
         ref = residual if residual is not None else None
         self.out = torch.empty(rows, cols, dtype=torch.bfloat16, device=comm.device) if ref is None else torch.empty_like(ref)
         self.done = False
-        self.ll = ll      # flag-in-data words from the streaming GEMV (else: the GEMM epilogue's staged rows + flags)
+
+    def norm(self, norm_w, eps) -> torch.Tensor:
+        """RMSNorm of the reduced residual stream (which ``value()`` then returns), one kernel."""
+        if self.done:
+            return K.rmsnorm(self.out, norm_w, eps)[0]
+        M, Kd = self.shape
+        xn = torch.empty_like(self.out)
+        K._chk(self.comm.lib.exo_tp_ll_reduce_norm(K._ptr(self.residual), norm_w.data_ptr(), float(eps), self.out.data_ptr(),
+                                                  xn.data_ptr(), M, Kd, self.parity, K._st()), "ll reduce norm")
+        K._count()
+        self.done = True
+        return xn
 
     def norm_linear(self, norm_w, eps, w, bias=None, swiglu=False):
         M, Kd = self.shape
         N = w.shape[0]
         lib = self.comm.lib
-        if not self.done and not self.ll and Kd % 8 == 0:
-            # batched decode: one kernel finishes the reduction, leaves the residual stream and the normalised rows
-            xn = torch.empty_like(self.out)
-            K._chk(lib.exo_tp_handover_rmsnorm(K._ptr(self.residual), norm_w.data_ptr(), eps, self.out.data_ptr(), xn.data_ptr(),
-                                               M, Kd, self.parity, K._st()), "handover rmsnorm")
-            K._count()
-            self.done = True
-            return K.linear(xn, w, bias, None, None, 0.0, swiglu)
-        if (self.done or not self.ll or not isinstance(w, torch.Tensor)
-                or not lib.exo_gemv_stream_supported(M, N, Kd, int(swiglu))):
-            return K.linear(self.value(), w, bias, None, norm_w, eps, swiglu)
+        if self.done:
+            return K.linear(self.out, w, bias, None, norm_w, eps, swiglu)
+        if M > 2 or not isinstance(w, torch.Tensor) or not lib.exo_gemv_stream_supported(M, N, Kd, int(swiglu)):
+            return K.linear(self.norm(norm_w, eps), w, bias, None, None, 0.0, swiglu)
         y = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device=self.out.device)
         K._chk(lib.exo_gemv_stream_tp(None, w.data_ptr(), K._ptr(bias), y.data_ptr(), K._ptr(norm_w), eps, M, N, Kd, int(swiglu),
                                       2, self.parity, K._ptr(self.residual), self.out.data_ptr(), K._st()), "gemv_stream_tp consume")
@@ -146,15 +148,11 @@ class Handover:
         self.done = True
         return y
 
-    def norm(self, norm_w, eps) -> torch.Tensor:
-        """RMSNorm of the reduced residual stream (which ``value()`` then returns)."""
-        return K.rmsnorm(self.value(), norm_w, eps)[0]
-
     def value(self) -> torch.Tensor:
         if not self.done:
             n = self.shape[0] * self.shape[1]
-            fn = self.comm.lib.exo_tp_ll_finish if self.ll else self.comm.lib.exo_tp_handover_finish
-            K._chk(fn(K._ptr(self.residual), self.out.data_ptr(), n, self.parity, K._st()), "handover finish")
+            K._chk(self.comm.lib.exo_tp_ll_finish(K._ptr(self.residual), self.out.data_ptr(), n, self.parity, K._st()),
+                   "handover finish")
             K._count()
             self.done = True
         return self.out
@@ -261,7 +259,6 @@ class FusedComm:
         self.vocab_shard = vocab_shard
         self.max_gather_rows = max_gather_rows
         self.gather_off = L["gather_off"]
-        self.handover_off, self.handover_slot = L["handover_off"], L["handover_slot"]
         self.mc_ptr = 0
         self.transport = "ipc"
         self.peers: list[int] = []
@@ -277,9 +274,8 @@ class FusedComm:
         else:
             self._open_ipc(L["total"])
         arr = (C.c_void_p * n)(*self.peers)
-        K._chk(lib.exo_comm_init(arr, self.mc_ptr or None, n, self.rank, L["slot"], L["gather_off"], L["handover_off"],
-                                 L["handover_slot"], L["x_off"], L["x_bytes"], L["h_off"], L["n_off"], L["ll_off"],
-                                 L["ll_slot"]), "comm init")
+        K._chk(lib.exo_comm_init(arr, self.mc_ptr or None, n, self.rank, L["slot"], L["gather_off"], L["x_off"], L["x_bytes"],
+                                 L["h_off"], L["n_off"], L["ll_off"], L["ll_slot"]), "comm init")
         dist.barrier(group=group)
         raw = torch.as_tensor(_RawBuffer(self.local + self.gather_off, L["gather_bytes"]), device=device)
         self.gather_buf = raw.view(torch.bfloat16)
@@ -289,15 +285,12 @@ class FusedComm:
                 p = lib.exo_comm_region(which, parity)
                 self._views[(which, parity)] = torch.as_tensor(_RawBuffer(p, L["x_bytes"]), device=device).view(torch.bfloat16)
         self._ar = 0
-        self._ho = 0             # GEMM-epilogue hand-overs issued so far (parity = low bit)
-        self._ll = 0             # flag-in-data hand-overs issued so far
+        self._ll = 0             # flag-in-data hand-overs issued so far (parity = low bit)
         self._rn = 0             # reduce + norm collectives issued so far
         self.n_collectives = 0
         self.n_handovers = 0
         self.use_handover = os.environ.get("EXO_DISABLE_TP_HANDOVER") != "1"
         self.use_reduce_norm = os.environ.get("EXO_DISABLE_REDUCE_NORM") != "1"
-        # the GEMM-epilogue variant (batches > 2) measured slower than GEMM + reduction kernel: off unless asked for
-        self.handover_gemm = os.environ.get("EXO_TP_HANDOVER_GEMM") == "1"
 
     # ---- arena set-up ----
     def _open_ipc(self, total: int) -> None:
@@ -418,10 +411,11 @@ class FusedComm:
         residual = resolve(residual)
         M, Kd = x.shape
         N = w.shape[0]
-        fits = (self.use_handover and x.dtype == torch.bfloat16 and 0 < M and M * N * 2 <= self.handover_slot
+        fits = (self.use_handover and x.dtype == torch.bfloat16 and 0 < M <= LL_ROWS and N % 8 == 0
+                and ((M + 1) & ~1) * N * 4 <= self.layout["ll_slot"]
                 and isinstance(w, torch.Tensor))       # block-scaled fp8 weights take the GEMM + reduction path
-        if (fits and M <= LL_ROWS and N % 8 == 0 and K.use_stream_gemv
-                and self.lib.exo_gemv_stream_supported(M, N, Kd, 1)):     # 1: rows leave in pairs, like the gate/up form
+        if fits and M <= 2 and K.use_stream_gemv and self.lib.exo_gemv_stream_supported(M, N, Kd, 1):
+            # (1: rows leave in pairs, like the gate/up form)
             K.ensure_stream_init(x.device)
             parity = self._ll & 1
             self._ll += 1
@@ -430,13 +424,12 @@ class FusedComm:
                                                None, None, K._st()), "gemv_stream_tp push")
             K._count()
             self.n_handovers += 1
-            return Handover(self, parity, residual, M, N, ll=True)
-        if (fits and self.handover_gemm and M > K.SMALL_M and K.gemm_impl is not None and Kd >= 64 and Kd % 8 == 0
-                and N % 8 == 0):
-            # batched decode: the tcgen05 GEMM's epilogue does the peer stores
+            return Handover(self, parity, residual, M, N)
+        if fits and K.gemm_impl is not None and Kd >= 64 and Kd % 8 == 0:
+            # decode batch: the tcgen05 GEMM's epilogue sends the words
             K.ensure_gemm_init(x.device)
-            parity = self._ho & 1
-            self._ho += 1
+            parity = self._ll & 1
+            self._ll += 1
             x = x.contiguous()
             splits = self.lib.exo_gemm_splits(M, N, Kd)
             while splits > 1 and splits * M * N > K.GEMM_PARTIAL_FLOATS:
@@ -444,7 +437,7 @@ class FusedComm:
             K._chk(self.lib.exo_gemm_bf16_tp(x.data_ptr(), w.data_ptr(), None, M, N, Kd, splits, parity, K._st()), "gemm_tp push")
             K._count()
             self.n_handovers += 1
-            return Handover(self, parity, residual, M, N, ll=False)
+            return Handover(self, parity, residual, M, N)
         if x.dtype == torch.bfloat16 and self.fits(M, N):
             buf, parity = self.partial_out(M, N)
             K.linear(x, w, out=buf)                      # the projection writes straight into this rank's arena

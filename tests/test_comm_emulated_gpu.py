@@ -22,8 +22,8 @@ def _setup(n_ranks, rank, rows, hidden):
     L = arena_layout(lib, n_ranks, rows, hidden, 64, 8)
     arenas = [torch.zeros(L["total"], dtype=torch.uint8, device="cuda") for _ in range(n_ranks)]
     arr = (C.c_void_p * n_ranks)(*[a.data_ptr() for a in arenas])
-    rc = lib.exo_comm_init(arr, None, n_ranks, rank, L["slot"], L["gather_off"], L["handover_off"], L["handover_slot"],
-                           L["x_off"], L["x_bytes"], L["h_off"], L["n_off"], L["ll_off"], L["ll_slot"])
+    rc = lib.exo_comm_init(arr, None, n_ranks, rank, L["slot"], L["gather_off"], L["x_off"], L["x_bytes"], L["h_off"],
+                           L["n_off"], L["ll_off"], L["ll_slot"])
     assert rc == 0
     return lib, K, L, arenas
 
@@ -195,3 +195,44 @@ def test_flag_in_data_handover_between_streaming_projections(M):
     finally:
         lib.exo_set_collective_timeout_us(2000000)
         lib.exo_comm_reset()
+
+
+@pytest.mark.parametrize("M,Kr", [(5, 2048), (32, 2048), (64, 1792), (33, 128), (64, 256)])
+def test_gemm_epilogue_handover_and_reduce_norm_kernel(M, Kr):
+    """Decode-batch row-parallel GEMM whose epilogue sends (data, sequence) words (split-K and single-pass tiles),
+    consumed by the reduce + RMSNorm kernel."""
+    from exo_b200.ops import reference as ref
+    H = 4096
+    lib, K, L, (A, B) = _setup(2, 0, 256, H)
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + Kr)
+    st = torch.cuda.current_stream().cuda_stream
+    w_o = (torch.randn(H, Kr, device="cuda", generator=g) / 32).bfloat16()
+    norm_w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).bfloat16()
+    for it in range(4):
+        parity, seq = it & 1, it // 2 + 1
+        x = torch.randn(M, Kr, device="cuda", generator=g).bfloat16()
+        res = torch.randn(M, H, device="cuda", generator=g).bfloat16()
+        peer = torch.randn(M, H, device="cuda", generator=g).bfloat16()
+        words = _ll_slot(A, L, 2, parity, 1, M * H)
+        words[:, 0] = peer.view(torch.int32).view(-1)
+        words[:, 1] = seq
+        splits = lib.exo_gemm_splits(M, H, Kr)
+        assert lib.exo_gemm_bf16_tp(x.data_ptr(), w_o.data_ptr(), None, M, H, Kr, splits, parity, st) == 0
+        h = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+        xn = torch.empty_like(h)
+        with_norm = it != 2
+        assert lib.exo_tp_ll_reduce_norm(res.data_ptr(), norm_w.data_ptr() if with_norm else None, 1e-5, h.data_ptr(),
+                                         xn.data_ptr() if with_norm else None, M, H, parity, st) == 0
+        torch.cuda.synchronize()
+        sent = _ll_slot(B, L, 2, parity, 0, M * H)                 # what reached the peer's arena
+        assert bool((sent[:, 1] == seq).all())
+        mine = sent[:, 0].contiguous().view(torch.bfloat16).view(M, H)
+        want_mine = ref.linear(x.float(), w_o.float())
+        assert (mine.float() - want_mine).abs().max() <= 0.02 * want_mine.abs().max()
+        want_h = (res.float() + mine.float() + peer.float()).bfloat16()
+        assert torch.equal(h, want_h)
+        if with_norm:
+            want_x = ref.rmsnorm(want_h.float(), norm_w.float(), 1e-5)[0]
+            assert (xn.float() - want_x).abs().max() <= 0.02 * want_x.abs().max()
+    K.check_status()
+    lib.exo_comm_reset()

@@ -219,7 +219,6 @@ def _handover(rank, world):
     from exo_b200.parallel.fused import FusedComm, Handover
     dev = torch.device("cuda", rank)
     comm = FusedComm(dev, max_rows=256, hidden=4096, vocab_shard=4008)
-    comm.handover_gemm = True                                      # also exercise the GEMM-epilogue variant
     shared = torch.Generator(device=dev).manual_seed(5)           # same on every rank
     mine = torch.Generator(device=dev).manual_seed(50 + rank)     # this rank's shard
     H, Kr = 4096, 2048
@@ -229,7 +228,7 @@ def _handover(rank, world):
     norm_w = (1 + 0.1 * torch.randn(H, device=dev, generator=shared)).bfloat16()
     worst = 0.0
     for it in range(10):                                           # both parities, several times: flags must come back clean
-        M = (1, 2, 1, 2, 1, 2, 32, 5, 200, 64)[it]                 # GEMV path (<= 2 rows) and GEMM path
+        M = (1, 2, 1, 2, 1, 2, 32, 5, 63, 64)[it]                  # streaming GEMV (<= 2 rows) and GEMM epilogue
         x = torch.randn(M, Kr, device=dev, generator=mine).bfloat16()
         res = torch.randn(M, H, device=dev, generator=shared).bfloat16()
         h = comm.row_linear(x, w_o, res)
