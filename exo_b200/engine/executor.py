@@ -46,8 +46,11 @@ class Executor:
         self.n_runs = 0
         self.dev = torch.zeros(words, dtype=torch.int32, device=self.device)
         self.n_blocks = n_blocks
-        # MLA attention is still PyTorch ops with host reads of the sequence lengths: such a step cannot be captured
-        self.use_graphs = (self.cuda and not cfg.mla) if use_graphs is None else use_graphs
+        # MLA models whose dimensions the latent-attention kernel does not take (toy configs) run that op as PyTorch
+        # ops with host reads of the sequence lengths: such a step cannot be captured
+        mla_ok = not cfg.mla or (cfg.kv_lora_rank == 512 and cfg.qk_rope_dim == 64 and cfg.qk_nope_dim == 128
+                                 and cfg.v_head_dim == 128 and cfg.dtype == "bf16")
+        self.use_graphs = (self.cuda and mla_ok) if use_graphs is None else use_graphs
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self.out_host = torch.zeros(self.max_B, dtype=torch.int32, pin_memory=self.cuda)
         self.prev_sampled = torch.zeros(max(self.max_B, 256), dtype=torch.int32, device=self.device)

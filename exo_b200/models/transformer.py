@@ -142,19 +142,19 @@ class Decoder:
         else:
             q = ops.linear(x, lw.wq_b)
         q = q.view(T, self.n_q, cfg.qk_nope_dim + cfg.qk_rope_dim)
-        q_nope, q_rope = q[..., :cfg.qk_nope_dim], q[..., cfg.qk_nope_dim:]
         kva = ops.linear(x, lw.wkv_a)
-        c_kv, _ = ops.rmsnorm(kva[:, :cfg.kv_lora_rank].contiguous(), lw.kv_a_norm, cfg.rms_eps)
-        k_rope = ref.rope(kva[:, None, cfg.kv_lora_rank:], inp.positions, self.inv_freq, self.rope_mscale, True)[:, 0]
-        q_rope = ref.rope(q_rope, inp.positions, self.inv_freq, self.rope_mscale, True)
         ckv = kv[0]
-        ckv.view(-1, ckv.shape[-1])[inp.slots.long()] = torch.cat((c_kv, k_rope), -1).to(ckv.dtype)
-        # weight absorption: scores are taken in the kv_lora latent space
-        q_lat = torch.einsum("thn,hnc->thc", q_nope.float(), lw.w_uk.float()).to(h.dtype)
-        o_lat = ops.mla_paged_attention(q_lat, q_rope.contiguous(), ckv, inp.block_tables, inp.seq_lens, inp.cu_q,
-                                        self.scale, cfg.kv_lora_rank, inp.max_q_len)
-        o = torch.einsum("thc,hvc->thv", o_lat.float(), lw.w_uv.float()).to(h.dtype)
-        return self.comm.row_linear(o.reshape(T, -1), lw.wo, h)
+        ops.mla_kv_append(kva, lw.kv_a_norm, cfg.rms_eps, inp.positions, self.inv_freq, self.rope_mscale, ckv, inp.slots,
+                          cfg.kv_lora_rank)
+        # weight absorption: scores are taken in the kv_lora latent space, the cache row is K and V at once
+        if T > 64 and getattr(lw, "w_uk_t", None) is None and lw.w_uk.is_cuda:
+            lw.w_uk_t = lw.w_uk.transpose(1, 2).contiguous()        # [H, kv_lora, nope]: the prefill GEMMs' layout
+        q_full = ops.mla_q_absorb(q, lw.w_uk, inp.positions, self.inv_freq, self.rope_mscale, cfg.qk_nope_dim,
+                                  cfg.kv_lora_rank, getattr(lw, "w_uk_t", None))
+        o_lat = ops.mla_paged_attention(q_full, ckv, inp.block_tables, inp.seq_lens, inp.cu_q, self.scale,
+                                        cfg.kv_lora_rank, inp.max_q_len)
+        o = ops.mla_o_absorb(o_lat, lw.w_uv)
+        return self.comm.row_linear(o, lw.wo, h)
 
     # ------------------------------------------------------------------ ffn
     def _ffn_dense(self, lw, h) -> torch.Tensor:

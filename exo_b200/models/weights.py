@@ -207,6 +207,7 @@ class LayerWeights:
     kv_a_norm: torch.Tensor | None = None
     w_uk: torch.Tensor | None = None   # [h_local, nope, kv_lora]
     w_uv: torch.Tensor | None = None   # [h_local, v, kv_lora]
+    w_uk_t: torch.Tensor | None = None  # [h_local, kv_lora, nope]: transposed copy made on first prefill (GEMM layout)
     # dense FFN
     w_gate_up: torch.Tensor | None = None  # [2F/N, H]  (gate rows then up rows)
     w_down: torch.Tensor | None = None     # [H, F/N]

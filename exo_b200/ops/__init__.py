@@ -81,11 +81,33 @@ def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, slid
     return ref.paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, sliding_window, sinks)
 
 
-def mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora, max_q_len=None):
-    if q_lat.is_cuda:
-        return cuda_ops().mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora,
-                                              max_q_len)
-    return ref.mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora)
+def mla_kv_append(kva, norm_w, eps, positions, inv_freq, mscale, cache, slots, kv_lora):
+    """Append the new tokens' rows ``[rmsnorm(latent) | rope(k_rope)]`` to the paged latent cache."""
+    if kva.is_cuda:
+        return cuda_ops().mla_kv_append(kva, norm_w, eps, positions, inv_freq, mscale, cache, slots, kv_lora)
+    return ref.mla_kv_append(kva, norm_w, eps, positions, inv_freq, mscale, cache, slots, kv_lora)
+
+
+def mla_q_absorb(q, w_uk, positions, inv_freq, mscale, nope, kv_lora, w_uk_t=None):
+    """``q [T, H, nope + rope]`` -> queries in cache space ``[T, H, kv_lora + rope]`` (``q_nope . W_UK``, rotated rope)."""
+    if q.is_cuda:
+        return cuda_ops().mla_q_absorb(q, w_uk, positions, inv_freq, mscale, nope, kv_lora, w_uk_t)
+    return ref.mla_q_absorb(q, w_uk, positions, inv_freq, mscale, nope)
+
+
+def mla_o_absorb(o_lat, w_uv):
+    """``o_lat [T, H, kv_lora]`` -> ``[T, H * v]`` through ``W_UV``."""
+    if o_lat.is_cuda:
+        return cuda_ops().mla_o_absorb(o_lat, w_uv)
+    return ref.mla_o_absorb(o_lat, w_uv)
+
+
+def mla_paged_attention(q_full, ckv, block_tables, seq_lens, cu_q, scale, kv_lora, max_q_len=None):
+    """Absorbed MLA attention of ``q_full [T, H, kv_lora + rope]`` over the paged latent cache -> ``[T, H, kv_lora]``."""
+    if q_full.is_cuda:
+        return cuda_ops().mla_paged_attention(q_full, ckv, block_tables, seq_lens, cu_q, scale, kv_lora, max_q_len)
+    return ref.mla_paged_attention(q_full[..., :kv_lora], q_full[..., kv_lora:], ckv, block_tables, seq_lens, cu_q, scale,
+                                   kv_lora)
 
 
 def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling):

@@ -434,14 +434,14 @@ mla_kv_append_kernel(const __nv_bfloat16* __restrict__ kva, const __nv_bfloat16*
 __global__ void __launch_bounds__(256)
 mla_q_absorb_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ w_uk,
                     const int* __restrict__ positions, const float* __restrict__ inv_freq, float mscale,
-                    __nv_bfloat16* out, int T, int H) {
+                    __nv_bfloat16* out, int T, int H, int rope_only) {
   pdl_trigger();
   constexpr int NOPE = 128, QD = NOPE + ROPE;
   __shared__ float wsm[NOPE][64 + 1];
   __shared__ float qs[NOPE];
   __shared__ float part[4][64];
   const int h = blockIdx.x, tid = threadIdx.x;
-  if (blockIdx.y == 8) {
+  if (blockIdx.y == 8 || rope_only) {
     pdl_wait();
     for (int i = tid; i < T * (ROPE / 2); i += 256) {
       const int t = i / (ROPE / 2), pr = i % (ROPE / 2);
@@ -592,13 +592,15 @@ EXO_API int exo_mla_kv_append(const void* kva, const void* norm_w, float eps, co
   return 0;
 }
 
-// q [T, H, 192] (128 nope + 64 rope) and W_UK [H, 128, 512] -> out [T, H, 576].  Decode batches (T <= 64).
+// q [T, H, 192] (128 nope + 64 rope) and W_UK [H, 128, 512] -> out [T, H, 576].  Meant for decode batches
+// (every block walks all T tokens).  rope_only: just out[..., 512:576] = RoPE(q[..., 128:192]); the latent part is
+// then the caller's (prefill chunks run it as tensor-core GEMMs per head).
 EXO_API int exo_mla_q_absorb(const void* q, const void* w_uk, const int* positions, const float* inv_freq, float mscale,
-                             void* out, int T, int H, int nope, int kv_lora, int rope_dim, cudaStream_t st) {
+                             void* out, int T, int H, int nope, int kv_lora, int rope_dim, int rope_only, cudaStream_t st) {
   if (T <= 0) return 0;
   if (nope != 128 || kv_lora != LAT || rope_dim != ROPE) return -2;
-  cudaError_t e = launch_pdl(mla_q_absorb_kernel, dim3(H, 9), dim3(256), 0, st, (const __nv_bfloat16*)q,
-                             (const __nv_bfloat16*)w_uk, positions, inv_freq, mscale, (__nv_bfloat16*)out, T, H);
+  cudaError_t e = launch_pdl(mla_q_absorb_kernel, dim3(H, rope_only ? 1 : 9), dim3(256), 0, st, (const __nv_bfloat16*)q,
+                             (const __nv_bfloat16*)w_uk, positions, inv_freq, mscale, (__nv_bfloat16*)out, T, H, rope_only);
   if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
   return 0;

@@ -73,6 +73,12 @@ class _Sig:
     exo_gemm_fp8w = (_i, [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
     exo_gemm_fp8w_f16 = (_i, [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
     exo_bf16_to_f16 = (_i, [_p, _p, _l, _p])
+    exo_mla_attn_splits = (_i, [_i, _i])
+    exo_mla_attn_workspace = (_l, [_i, _i, _i])
+    exo_mla_attn_tc = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _p])
+    exo_mla_kv_append = (_i, [_p, _p, _f, _p, _p, _f, _p, _p, _i, _i, _i, _p])
+    exo_mla_q_absorb = (_i, [_p, _p, _p, _p, _f, _p, _i, _i, _i, _i, _i, _i, _p])
+    exo_mla_o_absorb = (_i, [_p, _p, _p, _i, _i, _i, _i, _p])
     exo_moe_route = (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p])
     exo_moe_tile_rows = (_i, [_i, _i])
     exo_moe_max_tiles = (_i, [_i, _i, _i])
@@ -422,9 +428,113 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform):
     return out
 
 
-# ---- ops whose kernels are composed from the above / from torch on device for now ----------
-def mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora, max_q_len=None):
-    return ref.mla_paged_attention(q_lat, q_rope, ckv, block_tables, seq_lens, cu_q, scale, kv_lora)
+# ---- multi-head latent attention (DeepSeek-V2/V3, Kimi): absorbed form over the latent cache ----------------------
+MLA_SMALL_T = 64      # up to this many tokens the absorbed projections run as CUDA-core kernels (weights read once)
+use_mla_kernels = os.environ.get("EXO_DISABLE_MLA_KERNELS") != "1"
+_mla_tickets: dict[int | None, torch.Tensor] = {}
+
+
+def _mla_dims_ok(kv_lora, rope_dim, dtype) -> bool:
+    return use_mla_kernels and kv_lora == 512 and rope_dim == 64 and dtype == torch.bfloat16
+
+
+def mla_kv_append(kva, norm_w, eps, positions, inv_freq, mscale, cache, slots, kv_lora):
+    """Cache rows of the new tokens: ``[RMSNorm(kva[:, :kv_lora]) * norm_w | RoPE(kva[:, kv_lora:])]`` (adjacent-pair rope)."""
+    rope_dim = kva.shape[1] - kv_lora
+    if not (_mla_dims_ok(kv_lora, rope_dim, kva.dtype) and cache.dtype == torch.bfloat16):
+        return ref.mla_kv_append(kva, norm_w, eps, positions, inv_freq, mscale, cache, slots, kv_lora)
+    kva = kva.contiguous()
+    _chk(load().exo_mla_kv_append(_ptr(kva), _ptr(norm_w), float(eps), _ptr(positions), _ptr(inv_freq), float(mscale),
+                                  _ptr(cache), _ptr(slots), kva.shape[0], kv_lora, rope_dim, _st()), "mla_kv_append")
+    _count()
+
+
+def _heads_gemm(x_htk, w_hnk):
+    """``out[h] = x[h] @ w[h].T`` for every head with the tcgen05 GEMM: ``[H, T, K] x [H, N, K] -> [H, T, N]``."""
+    H, T, _ = x_htk.shape
+    out = torch.empty(H, T, w_hnk.shape[1], dtype=x_htk.dtype, device=x_htk.device)
+    for h in range(H):
+        gemm_bf16(x_htk[h], w_hnk[h], out=out[h])
+    return out
+
+
+def mla_q_absorb(q, w_uk, positions, inv_freq, mscale, nope, kv_lora, w_uk_t=None):
+    """Queries in cache space: ``[T, H, nope + rope] -> [T, H, kv_lora + rope]`` with ``q_nope . W_UK`` in front and
+    the rotated rope sub-vector behind.  ``w_uk [H, nope, kv_lora]``; ``w_uk_t [H, kv_lora, nope]`` serves prefill."""
+    T, H, qd = q.shape
+    rope_dim = qd - nope
+    if not (_mla_dims_ok(kv_lora, rope_dim, q.dtype) and nope == 128 and w_uk.dtype == torch.bfloat16):
+        return ref.mla_q_absorb(q, w_uk, positions, inv_freq, mscale, nope)
+    q = q.contiguous()
+    out = torch.empty(T, H, kv_lora + rope_dim, dtype=q.dtype, device=q.device)
+    small = T <= MLA_SMALL_T or gemm_impl is None
+    _chk(load().exo_mla_q_absorb(_ptr(q), _ptr(w_uk), _ptr(positions), _ptr(inv_freq), float(mscale), _ptr(out), T, H, nope,
+                                 kv_lora, rope_dim, int(not small), _st()), "mla_q_absorb")
+    _count()
+    if not small:
+        ensure_gemm_init(q.device)
+        wt = w_uk_t if w_uk_t is not None else w_uk.transpose(1, 2).contiguous()
+        lat = _heads_gemm(q[..., :nope].transpose(0, 1).contiguous(), wt)          # [H, T, kv_lora]
+        out[..., :kv_lora] = lat.transpose(0, 1)
+        _count(H)
+    return out
+
+
+def mla_o_absorb(o_lat, w_uv):
+    """Attention output back to head space: ``[T, H, kv_lora] x w_uv [H, v, kv_lora] -> [T, H * v]``."""
+    T, H, L = o_lat.shape
+    V = w_uv.shape[1]
+    if not (use_mla_kernels and L == 512 and V == 128 and o_lat.dtype == torch.bfloat16 and w_uv.dtype == torch.bfloat16):
+        return ref.mla_o_absorb(o_lat, w_uv)
+    o_lat = o_lat.contiguous()
+    if T <= MLA_SMALL_T or gemm_impl is None:
+        out = torch.empty(T, H * V, dtype=o_lat.dtype, device=o_lat.device)
+        _chk(load().exo_mla_o_absorb(_ptr(o_lat), _ptr(w_uv), _ptr(out), T, H, V, L, _st()), "mla_o_absorb")
+        _count()
+        return out
+    ensure_gemm_init(o_lat.device)
+    o = _heads_gemm(o_lat.transpose(0, 1).contiguous(), w_uv)                        # [H, T, V]
+    _count(H)
+    return o.transpose(0, 1).reshape(T, H * V)
+
+
+def mla_paged_attention(q_full, ckv, block_tables, seq_lens, cu_q, scale, kv_lora, max_q_len=None):
+    """Absorbed MLA attention: ``q_full [T, H, kv_lora + rope]`` (see :func:`mla_q_absorb`) over the paged latent cache
+    ``ckv [n_blocks, block, kv_lora + rope]``; returns ``o_lat [T, H, kv_lora]``."""
+    T, H, qd = q_full.shape
+    rope_dim = qd - kv_lora
+    nblk, bs, _ = ckv.shape
+    B = seq_lens.numel()
+    ok = _mla_dims_ok(kv_lora, rope_dim, q_full.dtype) and ckv.dtype == torch.bfloat16 and bs == 16 and (H % 16 == 0 or H in (1, 2, 4, 8))
+    if not ok:
+        return ref.mla_paged_attention(q_full[..., :kv_lora], q_full[..., kv_lora:], ckv, block_tables, seq_lens, cu_q, scale,
+                                       kv_lora)
+    lib = load()
+    ensure_gemm_init(q_full.device)
+    q_full = q_full.contiguous()
+    out = torch.empty(T, H, kv_lora, dtype=q_full.dtype, device=q_full.device)
+    decode = max_q_len == 1 and T == B
+    groups = max(1, H // 16)
+    max_blocks = block_tables.shape[1]
+    tok_seq = None
+    if decode:
+        ns = lib.exo_mla_attn_splits(T * groups, max_blocks * bs)
+    else:
+        ns = 1
+        tok_seq = torch.empty(T, dtype=torch.int32, device=q_full.device)
+        _chk(lib.exo_token_seq(_ptr(cu_q), _ptr(tok_seq), B, _st()), "token_seq")
+        _count()
+    ws = tk = None
+    if ns > 1:
+        ws = _workspace(q_full.device, lib.exo_mla_attn_workspace(T, H, ns))
+        tk = _mla_tickets.get(q_full.device.index)
+        if tk is None or tk.numel() < T * groups:
+            tk = _mla_tickets[q_full.device.index] = torch.zeros(max(T * groups, 1 << 12), dtype=torch.int32, device=q_full.device)
+    _chk(lib.exo_mla_attn_tc(_ptr(q_full), _ptr(ckv), _ptr(block_tables), _ptr(seq_lens), None if decode else _ptr(cu_q),
+                             _ptr(tok_seq), _ptr(out), _ptr(ws), _ptr(tk), float(scale), T, H, kv_lora, rope_dim, nblk,
+                             max_blocks, bs, ns, _st()), "mla_attn_tc")
+    _count()
+    return out
 
 
 MOE_GEMV_MAX_TOKENS = 4    # up to this many tokens the experts run as grouped GEMVs (no sort, two launches)

@@ -190,6 +190,27 @@ def mla_paged_attention(q_lat: torch.Tensor, q_rope: torch.Tensor, ckv: torch.Te
     return out
 
 
+def mla_kv_append(kva: torch.Tensor, norm_w: torch.Tensor, eps: float, positions: torch.Tensor, inv_freq: torch.Tensor,
+                  mscale: float, cache: torch.Tensor, slots: torch.Tensor, kv_lora: int) -> None:
+    """Write the new tokens' latent-cache rows: ``[rmsnorm(kva[:, :kv_lora]) | rope(kva[:, kv_lora:])]``."""
+    c_kv, _ = rmsnorm(kva[:, :kv_lora].contiguous(), norm_w, eps)
+    k_rope = rope(kva[:, None, kv_lora:], positions, inv_freq, mscale, True)[:, 0]
+    cache.view(-1, cache.shape[-1])[slots.long()] = torch.cat((c_kv, k_rope), -1).to(cache.dtype)
+
+
+def mla_q_absorb(q: torch.Tensor, w_uk: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, mscale: float,
+                 nope: int) -> torch.Tensor:
+    """``q [T, H, nope + r]`` -> ``[T, H, kv_lora + r]``: ``q_nope . W_UK[h]`` in front, the rotated rope part behind."""
+    q_lat = torch.einsum("thn,hnc->thc", q[..., :nope].float(), w_uk.float()).to(q.dtype)
+    q_rope = rope(q[..., nope:], positions, inv_freq, mscale, True)
+    return torch.cat((q_lat, q_rope), -1)
+
+
+def mla_o_absorb(o_lat: torch.Tensor, w_uv: torch.Tensor) -> torch.Tensor:
+    """``o_lat [T, H, kv_lora]`` with ``w_uv [H, v, kv_lora]`` -> ``[T, H * v]``."""
+    return torch.einsum("thc,hvc->thv", o_lat.float(), w_uv.float()).to(o_lat.dtype).reshape(o_lat.shape[0], -1)
+
+
 def moe_route(logits: torch.Tensor, top_k: int, kind: str = "softmax", norm_topk: bool = True,
               bias: torch.Tensor | None = None, n_group: int = 1, topk_group: int = 1,
               scaling: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
