@@ -70,7 +70,8 @@ def reduced_and_normed(h, norm_w, eps):
     if isinstance(h, torch.Tensor):
         return h, ops.rmsnorm(h, norm_w, eps)[0]
     x = h.norm(norm_w, eps)
-    return h.value(), x
+    return h, x       # h stays the reduction object: in its two-shot form the stream is sharded by rows, and only a
+    #                   consumer that needs every row (``resolve``) pays for gathering it
 
 
 class KVPool:

@@ -30,7 +30,7 @@ namespace {
 
 constexpr int MAX_RANKS = 8;
 constexpr size_t HDR_BYTES = 4096;
-constexpr size_t BAR_IN = 2048, BAR_OUT = 2112, BAR_TICKET = 2176;
+constexpr size_t BAR_IN = 2048, BAR_OUT = 2112, BAR_TICKET = 2176, BAR_GATHER = 2240;   // tickets: int32 [3]; gather flags [8]
 constexpr size_t LL_EPOCH = 2304, LL_TICKET = 2368;   // flag-in-data hand-over: int32 [2 parities] each
 
 struct CommCtx {
@@ -271,99 +271,98 @@ __device__ bool wait_ranks(const CommCtx& c, size_t base, int parity) {
   return ok_w != 0;
 }
 
-constexpr int RN_THREADS = 256;
-constexpr int RN_VPT = 4;   // 16-byte vectors per thread and row: rows of up to 8192 elements stay in registers
+constexpr int RN_THREADS = 256, RN_WARPS = RN_THREADS / 32;
 
-// Sum over ranks of one 16-byte vector of partial[parity] at element offset `off`.
-template <bool MC>
-__device__ __forceinline__ void reduce_vec(const CommCtx& c, int parity, size_t off, float* acc) {
-  const size_t byte_off = c.x_off + (size_t)parity * c.x_bytes + off * 2;
-  if constexpr (MC) {
-    unpack8(multimem_ld_reduce_bf16x8(c.mc + byte_off), acc);
-  } else {
-#pragma unroll
-    for (int e = 0; e < 8; e++) acc[e] = 0.f;
-    for (int r = 0; r < c.n; r++) {
-      float f[8];
-      unpack8(ld_cg16(c.arena[r] + byte_off), f);
-#pragma unroll
-      for (int e = 0; e < 8; e++) acc[e] += f[e];
-    }
-  }
-}
-
-// TWO = false: h_out / x_out are this rank's private [rows, cols] tensors and every rank computes all rows.
-// TWO = true:  this rank computes rows [rank R, (rank + 1) R) and broadcasts them into hbuf / nbuf[parity] of every rank.
-template <bool MC, bool TWO>
+// One warp per row: all of the row's 16-byte vectors are requested before the first is used (VPL of them per
+// lane), the row stays in registers as packed bf16 between the sum of squares and the scaling, and warps never
+// wait for one another inside the row loop.
+//   TWO = false: h_out / x_out are this rank's private [rows, cols] tensors and every rank computes all rows.
+//   TWO = true:  this rank computes rows [rank R, (rank + 1) R) only.  Its normalised rows go into nbuf[parity] of
+//                EVERY rank; its residual-stream rows go into hbuf[parity] of every rank when `bcast_h`, else into
+//                the same rows of the private h_out (the stream then stays sharded by rows: the next reduction of
+//                the same shape needs exactly these rows as its residual).
+template <bool MC, bool TWO, int VPL>
 __global__ void __launch_bounds__(RN_THREADS)
 reduce_norm_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ norm_w,
-                   float eps, __nv_bfloat16* h_out, __nv_bfloat16* x_out, int rows, int cols, int parity) {
+                   float eps, __nv_bfloat16* h_out, __nv_bfloat16* x_out, int rows, int cols, int parity, int bcast_h) {
   pdl_trigger();
   pdl_wait();
-  __shared__ float red[RN_THREADS / 32];
   __shared__ int last_s;
   if (blockIdx.x == 0 && threadIdx.x < c.n) {
     __threadfence_system();   // the partial was written by earlier kernels of this stream: publish it system-wide
     red_release_sys_add(bar_ptr(c.arena[threadIdx.x], BAR_IN, parity, c.rank), 1);
   }
   const bool ok = wait_ranks(c, BAR_IN, parity);
-  const int n_vec = cols / 8;
+  const int n_vec = cols / 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int row0 = 0, row1 = rows;
   if (TWO) {
     const int per = (rows + c.n - 1) / c.n;
     row0 = min(rows, c.rank * per);
     row1 = min(rows, row0 + per);
   }
+  const size_t part_off = c.x_off + (size_t)parity * c.x_bytes;
   if (ok) {
-    for (int row = row0 + blockIdx.x; row < row1; row += gridDim.x) {
+    for (int row = row0 + blockIdx.x * RN_WARPS + warp; row < row1; row += gridDim.x * RN_WARPS) {
       const size_t base = (size_t)row * cols;
-      float v[RN_VPT][8];
+      uint4 hp[VPL];
+      if (MC) {
+#pragma unroll
+        for (int j = 0; j < VPL; j++) {
+          const int iv = lane + 32 * j;
+          if (iv < n_vec) hp[j] = multimem_ld_reduce_bf16x8(c.mc + part_off + (base + (size_t)iv * 8) * 2);
+        }
+      }
       float ss = 0.f;
 #pragma unroll
-      for (int j = 0; j < RN_VPT; j++) {
-        const int iv = threadIdx.x + j * RN_THREADS;
+      for (int j = 0; j < VPL; j++) {
+        const int iv = lane + 32 * j;
         if (iv < n_vec) {
           const size_t off = base + (size_t)iv * 8;
-          reduce_vec<MC>(c, parity, off, v[j]);
+          float v[8];
+          if (MC) unpack8(hp[j], v);
+          else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = 0.f;
+            for (int r = 0; r < c.n; r++) {
+              float f[8];
+              unpack8(ld_cg16(c.arena[r] + part_off + off * 2), f);
+#pragma unroll
+              for (int e = 0; e < 8; e++) v[e] += f[e];
+            }
+          }
           if (residual) {
             float r8[8];
             unpack8(*reinterpret_cast<const uint4*>(residual + off), r8);
 #pragma unroll
-            for (int e = 0; e < 8; e++) v[j][e] += r8[e];
+            for (int e = 0; e < 8; e++) v[e] += r8[e];
           }
-          const uint4 packed = pack8(v[j]);          // the residual stream is kept in bf16: normalise what is stored
-          if (TWO) {
+          hp[j] = pack8(v);                            // the residual stream is kept in bf16: normalise what is stored
+          if (TWO && bcast_h) {
             const size_t boff = c.h_off + (size_t)parity * c.x_bytes + off * 2;
-            if (MC) multimem_st16(c.mc + boff, packed);
+            if (MC) multimem_st16(c.mc + boff, hp[j]);
             else
-              for (int r = 0; r < c.n; r++) *reinterpret_cast<uint4*>(c.arena[r] + boff) = packed;
+              for (int r = 0; r < c.n; r++) *reinterpret_cast<uint4*>(c.arena[r] + boff) = hp[j];
           } else {
-            *reinterpret_cast<uint4*>(h_out + off) = packed;
+            *reinterpret_cast<uint4*>(h_out + off) = hp[j];
           }
-          unpack8(packed, v[j]);
+          unpack8(hp[j], v);
 #pragma unroll
-          for (int e = 0; e < 8; e++) ss += v[j][e] * v[j][e];
+          for (int e = 0; e < 8; e++) ss += v[e] * v[e];
         }
       }
       if (norm_w) {
-        ss = warp_sum(ss);
-        __syncthreads();                               // red[] of the previous row has been read
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-        __syncthreads();
-        float tot = 0.f;
+        const float rstd = rsqrtf(warp_sum(ss) / cols + eps);
 #pragma unroll
-        for (int w = 0; w < RN_THREADS / 32; w++) tot += red[w];
-        const float rstd = rsqrtf(tot / cols + eps);
-#pragma unroll
-        for (int j = 0; j < RN_VPT; j++) {
-          const int iv = threadIdx.x + j * RN_THREADS;
+        for (int j = 0; j < VPL; j++) {
+          const int iv = lane + 32 * j;
           if (iv < n_vec) {
             const size_t off = base + (size_t)iv * 8;
-            float w8[8];
+            float v[8], w8[8];
+            unpack8(hp[j], v);
             unpack8(*reinterpret_cast<const uint4*>(norm_w + (size_t)iv * 8), w8);
 #pragma unroll
-            for (int e = 0; e < 8; e++) v[j][e] = v[j][e] * rstd * w8[e];
-            const uint4 packed = pack8(v[j]);
+            for (int e = 0; e < 8; e++) v[e] = v[e] * rstd * w8[e];
+            const uint4 packed = pack8(v);
             if (TWO) {
               const size_t boff = c.n_off + (size_t)parity * c.x_bytes + off * 2;
               if (MC) multimem_st16(c.mc + boff, packed);
@@ -397,6 +396,44 @@ reduce_norm_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ residual, 
   if (threadIdx.x < c.n) {
     *bar_ptr(c.arena[c.rank], BAR_IN, parity, threadIdx.x) = 0;
     if (TWO) *bar_ptr(c.arena[c.rank], BAR_OUT, parity, threadIdx.x) = 0;
+    __threadfence_system();
+  }
+}
+
+// All-gather of residual-stream rows that a two-shot reduction left sharded: this rank's rows [rank R, (rank + 1) R)
+// of `src` go into hbuf[parity] of every rank; when the kernel completes every rank's rows have landed.
+template <bool MC>
+__global__ void __launch_bounds__(RN_THREADS)
+gather_rows_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ src, int rows, int cols, int parity) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ int last_s;
+  const int per = (rows + c.n - 1) / c.n;
+  const int row0 = min(rows, c.rank * per), row1 = min(rows, row0 + per);
+  const size_t v0 = (size_t)row0 * cols / 8, v1 = (size_t)row1 * cols / 8;
+  const size_t hb = c.h_off + (size_t)parity * c.x_bytes;
+  for (size_t v = v0 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < v1; v += (size_t)gridDim.x * blockDim.x) {
+    const uint4 x = reinterpret_cast<const uint4*>(src)[v];
+    if (MC) multimem_st16(c.mc + hb + v * 16, x);
+    else
+      for (int r = 0; r < c.n; r++) *reinterpret_cast<uint4*>(c.arena[r] + hb + v * 16) = x;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* tk = reinterpret_cast<int*>(c.arena[c.rank] + BAR_TICKET) + 2;      // third ticket word: the gathers' own
+    __threadfence();
+    const int last = atomicAdd(tk, 1) == (int)gridDim.x - 1;
+    if (last) *tk = 0;
+    last_s = last;
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence_system();
+  if (threadIdx.x < c.n) red_release_sys_add(bar_ptr(c.arena[threadIdx.x], BAR_GATHER, 0, c.rank), 1);
+  wait_ranks(c, BAR_GATHER, 0);
+  if (threadIdx.x < c.n) {
+    *bar_ptr(c.arena[c.rank], BAR_GATHER, 0, threadIdx.x) = 0;
     __threadfence_system();
   }
 }
@@ -516,34 +553,64 @@ EXO_API int exo_allgather_cols_bf16(const void* in, int rows, int cols, int pari
 
 // h = residual + sum over ranks of partial[parity];  x = RMSNorm(h) * norm_w  (norm_w null: h only).
 // The partial must have been written into this rank's partial[parity] region (exo_comm_region(0, parity)) by
-// earlier work of the same stream.  two_shot = 0: h_out / x_out are private tensors of the caller.
-// two_shot = 1: the results land in exo_comm_region(1 / 2, parity) on every rank; h_out / x_out are ignored.
+// earlier work of the same stream.
+//   two_shot = 0: h_out / x_out are private [rows, cols] tensors of the caller; every rank computes every row.
+//   two_shot = 1: x lands in exo_comm_region(2, parity) on every rank (x_out ignored).  bcast_h != 0: so does h, in
+//                 exo_comm_region(1, parity) (h_out ignored); bcast_h == 0: only this rank's rows
+//                 [rank R, (rank+1) R), R = ceil(rows / n), of the private h_out are written.
 // rows * cols * 2 must fit the region; cols % 8 == 0 and cols <= 8192.
 EXO_API int exo_reduce_norm_bf16(const void* residual, const void* norm_w, float eps, void* h_out, void* x_out, int rows,
-                                 int cols, int parity, int two_shot, cudaStream_t st) {
+                                 int cols, int parity, int two_shot, int bcast_h, cudaStream_t st) {
   int dev;
   cudaGetDevice(&dev);
   if (dev >= 16 || !g_ctx_set[dev]) return -4;
   CommCtx c = g_ctx[dev];
   c.wait_ns = exo_wait_budget_ns();
-  if (rows <= 0 || cols % 8 || cols > 8 * RN_THREADS * RN_VPT) return -2;
+  if (rows <= 0 || cols % 8 || cols > 8192) return -2;
   if (!c.x_bytes || (size_t)rows * cols * 2 > c.x_bytes) return -6;
+  if ((!two_shot || !bcast_h) && !h_out) return -2;
+  if (!two_shot && norm_w && !x_out) return -2;
   const auto* res = (const __nv_bfloat16*)residual;
   const auto* nw = (const __nv_bfloat16*)norm_w;
   auto* ho = (__nv_bfloat16*)h_out;
   auto* xo = (__nv_bfloat16*)x_out;
+  const int my_rows = two_shot ? (rows + c.n - 1) / c.n : rows;
+  int grid = (my_rows + RN_WARPS - 1) / RN_WARPS;
+  if (grid > 296) grid = 296;
+  const bool wide = cols > 4096;      // vectors per lane: 16 up to 4096 columns, 32 up to 8192
   cudaError_t e;
+#define RN_LAUNCH(MCV, TWOV)                                                                                                  \
+  e = wide ? launch_pdl(reduce_norm_kernel<MCV, TWOV, 32>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, \
+                        cols, parity, bcast_h)                                                                                 \
+           : launch_pdl(reduce_norm_kernel<MCV, TWOV, 16>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, \
+                        cols, parity, bcast_h)
   if (two_shot) {
-    const int per = (rows + c.n - 1) / c.n;
-    const int grid = per < 148 ? per : 148;
-    e = c.mc ? launch_pdl(reduce_norm_kernel<true, true>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, cols, parity)
-             : launch_pdl(reduce_norm_kernel<false, true>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, cols, parity);
+    if (c.mc) { RN_LAUNCH(true, true); } else { RN_LAUNCH(false, true); }
   } else {
-    if (!h_out || (norm_w && !x_out)) return -2;
-    const int grid = rows < 296 ? rows : 296;
-    e = c.mc ? launch_pdl(reduce_norm_kernel<true, false>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, cols, parity)
-             : launch_pdl(reduce_norm_kernel<false, false>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, cols, parity);
+    if (c.mc) { RN_LAUNCH(true, false); } else { RN_LAUNCH(false, false); }
   }
+#undef RN_LAUNCH
+  if (e != cudaSuccess) return (int)e;
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+// Completes a residual stream that a two-shot reduction left sharded by rows: every rank's rows of `src`
+// ([rows, cols], this rank's rows valid) are gathered into exo_comm_region(1, parity) of every rank.
+EXO_API int exo_gather_rows_bf16(const void* src, int rows, int cols, int parity, cudaStream_t st) {
+  int dev;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !g_ctx_set[dev]) return -4;
+  CommCtx c = g_ctx[dev];
+  c.wait_ns = exo_wait_budget_ns();
+  if (rows <= 0 || cols % 8) return -2;
+  if (!c.x_bytes || (size_t)rows * cols * 2 > c.x_bytes) return -6;
+  const size_t vecs = (size_t)((rows + c.n - 1) / c.n) * cols / 8;
+  int grid = (int)((vecs + RN_THREADS - 1) / RN_THREADS);
+  if (grid > 148) grid = 148;
+  if (grid < 1) grid = 1;
+  cudaError_t e = c.mc ? launch_pdl(gather_rows_kernel<true>, dim3(grid), dim3(RN_THREADS), 0, st, c, (const __nv_bfloat16*)src, rows, cols, parity)
+                       : launch_pdl(gather_rows_kernel<false>, dim3(grid), dim3(RN_THREADS), 0, st, c, (const __nv_bfloat16*)src, rows, cols, parity);
   if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
   return 0;

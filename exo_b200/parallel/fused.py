@@ -69,7 +69,8 @@ _SIGS = {
     "exo_allreduce_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
     "exo_allgather_cols_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "exo_reduce_norm_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
-                                       C.c_int, C.c_void_p]),
+                                       C.c_int, C.c_int, C.c_void_p]),
+    "exo_gather_rows_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "exo_comm_region": (C.c_void_p, [C.c_int, C.c_int]),
     "exo_comm_has_multicast": (C.c_int, []),
     "exo_vmm_supported": (C.c_int, []), "exo_vmm_granularity": (C.c_size_t, [C.c_int, C.c_int]),
@@ -161,45 +162,68 @@ class Handover:
 class Reduction:
     """A row-parallel projection's partial sitting in this rank's arena, not yet summed over the ranks.
 
-    The first consumer decides the kernel: ``norm_linear`` / ``norm`` run the fused
-    ``residual + sum`` + RMSNorm kernel, ``value()`` alone runs it without the norm.  In the two-shot
-    form the results are views of the arena; they stay valid until the collective after next."""
+    The first consumer decides the kernel: ``norm_linear`` / ``norm`` run the fused ``residual + sum`` + RMSNorm
+    kernel, ``value()`` alone runs it without the norm.  In the two-shot form (prefill chunks) each rank reduces
+    and normalises 1/N of the rows; the normalised rows are broadcast, while the residual stream stays SHARDED by
+    rows (``local_rows``) when a norm was asked for: the next reduction of the same shape needs exactly this rank's
+    rows as its residual, so the full stream is only gathered if somebody asks for it with ``value()``.  Results
+    that are views of the arena stay valid until the collective after next."""
 
-    def __init__(self, comm: "FusedComm", parity: int, residual: torch.Tensor | None, rows: int, cols: int):
+    def __init__(self, comm: "FusedComm", parity: int, residual, rows: int, cols: int):
         self.comm, self.parity, self.residual, self.shape = comm, parity, residual, (rows, cols)
-        self.out: torch.Tensor | None = None
+        self.out: torch.Tensor | None = None           # the full reduced residual stream
+        self.local_rows: torch.Tensor | None = None    # [rows, cols] with only this rank's rows valid (sharded form)
         self.xn: torch.Tensor | None = None
 
     def _run(self, norm_w, eps: float) -> None:
         comm = self.comm
         M, H = self.shape
         two = comm.two_shot(M, H)
+        sharded = two and norm_w is not None
+        res = comm.residual_for(self.residual, M, H, two)
+        xn = None
         if two:
-            self.out = comm.region(1, self.parity, M, H)
+            h_buf = torch.empty(M, H, dtype=torch.bfloat16, device=comm.device) if sharded else comm.region(1, self.parity, M, H)
             xn = comm.region(2, self.parity, M, H) if norm_w is not None else None
         else:
-            self.out = torch.empty(M, H, dtype=torch.bfloat16, device=comm.device)
-            xn = torch.empty_like(self.out) if norm_w is not None else None
-        K._chk(comm.lib.exo_reduce_norm_bf16(K._ptr(self.residual), K._ptr(norm_w), float(eps), self.out.data_ptr(),
-                                             K._ptr(xn), M, H, self.parity, int(two), K._st()), "reduce_norm")
+            h_buf = torch.empty(M, H, dtype=torch.bfloat16, device=comm.device)
+            xn = torch.empty_like(h_buf) if norm_w is not None else None
+        K._chk(comm.lib.exo_reduce_norm_bf16(K._ptr(res), K._ptr(norm_w), float(eps), h_buf.data_ptr(), K._ptr(xn), M, H,
+                                             self.parity, int(two), int(not sharded), K._st()), "reduce_norm")
         K._count()
         comm.n_collectives += 1
         self.xn = xn
+        if sharded:
+            self.local_rows = h_buf
+        else:
+            self.out = h_buf
+
+    @property
+    def pending(self) -> bool:
+        return self.out is None and self.local_rows is None
 
     def norm(self, norm_w, eps) -> torch.Tensor:
-        if self.out is None:
+        if self.pending:
             self._run(norm_w, eps)
             return self.xn
-        return K.rmsnorm(self.out, norm_w, eps)[0]
+        return K.rmsnorm(self.value(), norm_w, eps)[0]
 
     def norm_linear(self, norm_w, eps, w, bias=None, swiglu=False):
-        if self.out is None:
+        if self.pending:
             return K.linear(self.norm(norm_w, eps), w, bias, None, None, 0.0, swiglu)
-        return K.linear(self.out, w, bias, None, norm_w, eps, swiglu)
+        return K.linear(self.value(), w, bias, None, norm_w, eps, swiglu)
 
     def value(self) -> torch.Tensor:
-        if self.out is None:
+        if self.pending:
             self._run(None, 0.0)
+        if self.out is None:
+            # the stream was left sharded by rows: gather every rank's rows (one more collective, off the layer loop)
+            M, H = self.shape
+            comm = self.comm
+            K._chk(comm.lib.exo_gather_rows_bf16(self.local_rows.data_ptr(), M, H, self.parity, K._st()), "gather_rows")
+            K._count()
+            comm.n_collectives += 1
+            self.out = comm.region(1, self.parity, M, H)
         return self.out
 
 
@@ -371,6 +395,14 @@ class FusedComm:
         return (self.use_reduce_norm and 0 < rows and rows * cols * 2 <= self.layout["x_bytes"] and cols % 8 == 0
                 and cols <= 8192)
 
+    def residual_for(self, residual, rows: int, cols: int, two_shot: bool):
+        """The tensor a reduction of ``[rows, cols]`` adds: a residual stream that the previous two-shot reduction left
+        sharded by rows is used as it is when this reduction is two-shot over the same shape (same row ownership)."""
+        if isinstance(residual, Reduction) and not residual.pending and residual.out is None:
+            if two_shot and residual.shape == (rows, cols):
+                return residual.local_rows
+        return resolve(residual)
+
     def partial_out(self, rows: int, cols: int) -> tuple[torch.Tensor, int]:
         """Buffer for the next reduction's partial (write the projection output here) and its parity."""
         parity = self._rn & 1
@@ -382,11 +414,11 @@ class FusedComm:
         """``residual + sum over ranks of x`` (bf16)."""
         if x.dtype != torch.bfloat16 or x.numel() % 8:
             raise K.KernelError("fused all-reduce takes bf16 tensors whose size is a multiple of 8")
-        residual = resolve(residual)
         if x.dim() == 2 and self.fits(x.shape[0], x.shape[1]):
             buf, parity = self.partial_out(x.shape[0], x.shape[1])
             buf.copy_(x)
             return Reduction(self, parity, residual, x.shape[0], x.shape[1]).value()
+        residual = resolve(residual)
         x = x.contiguous()
         if x.numel() > self.max_elems:
             # larger than one arena slot (a long prefill chunk): reduce it in row blocks that fit
@@ -408,7 +440,6 @@ class FusedComm:
     def row_linear(self, x: torch.Tensor, w: torch.Tensor, residual=None):
         """``residual + all-reduce(x @ w.T)``, returned as a pending :class:`Handover` / :class:`Reduction`
         where the shapes allow it: the next ``norm_linear`` (or ``resolve``) then forms the sum."""
-        residual = resolve(residual)
         M, Kd = x.shape
         N = w.shape[0]
         fits = (self.use_handover and x.dtype == torch.bfloat16 and 0 < M <= LL_ROWS and N % 8 == 0
@@ -424,7 +455,7 @@ class FusedComm:
                                                None, None, K._st()), "gemv_stream_tp push")
             K._count()
             self.n_handovers += 1
-            return Handover(self, parity, residual, M, N)
+            return Handover(self, parity, resolve(residual), M, N)
         if fits and K.gemm_impl is not None and Kd >= 64 and Kd % 8 == 0:
             # decode batch: the tcgen05 GEMM's epilogue sends the words
             K.ensure_gemm_init(x.device)
@@ -437,11 +468,12 @@ class FusedComm:
             K._chk(self.lib.exo_gemm_bf16_tp(x.data_ptr(), w.data_ptr(), None, M, N, Kd, splits, parity, K._st()), "gemm_tp push")
             K._count()
             self.n_handovers += 1
-            return Handover(self, parity, residual, M, N)
+            return Handover(self, parity, resolve(residual), M, N)
         if x.dtype == torch.bfloat16 and self.fits(M, N):
             buf, parity = self.partial_out(M, N)
             K.linear(x, w, out=buf)                      # the projection writes straight into this rank's arena
             return Reduction(self, parity, residual, M, N)
+        residual = resolve(residual)
         if x.dtype == torch.bfloat16 and M > 0 and N % 8 == 0 and N <= 8192 and self.use_reduce_norm:
             # longer than the arena region: row blocks that fit, each reduced by its own collective
             rows = max(8, (self.layout["x_bytes"] // (N * 2)) // 8 * 8)

@@ -62,7 +62,7 @@ def test_one_shot_reduce_norm_against_fp32_reference(rows, cols):
         x = torch.empty_like(h)
         with_norm = it != 3
         rc = lib.exo_reduce_norm_bf16(res.data_ptr(), w.data_ptr() if with_norm else None, 1e-5, h.data_ptr(),
-                                      x.data_ptr() if with_norm else None, rows, cols, parity, 0, st)
+                                      x.data_ptr() if with_norm else None, rows, cols, parity, 0, 1, st)
         assert rc == 0
         torch.cuda.synchronize()
         want_h, want_x = _ref([xa, xb], res, w, 1e-5)
@@ -89,8 +89,8 @@ def test_two_shot_reduce_norm_writes_this_ranks_rows_into_every_arena():
     _region(B, L, 0, parity, rows, cols).copy_(xb)
     _flags(A)[BAR_IN + parity * 8 + 1] = 1
     _flags(A)[BAR_OUT + parity * 8 + 1] = 1              # the peer's "rows broadcast"
-    rc = lib.exo_reduce_norm_bf16(res.data_ptr(), w.data_ptr(), 1e-5, None, None, rows, cols, parity, 1,
-                                  torch.cuda.current_stream().cuda_stream)
+    st = torch.cuda.current_stream().cuda_stream
+    rc = lib.exo_reduce_norm_bf16(res.data_ptr(), w.data_ptr(), 1e-5, None, None, rows, cols, parity, 1, 1, st)
     assert rc == 0
     torch.cuda.synchronize()
     want_h, want_x = _ref([xa, xb], res, w, 1e-5)
@@ -101,6 +101,27 @@ def test_two_shot_reduce_norm_writes_this_ranks_rows_into_every_arena():
         assert torch.equal(h[:mine], want_h[:mine])
         assert (x[:mine].float() - want_x[:mine].float()).abs().max() <= 0.02 * want_x.float().abs().max()
         assert float(h[mine:].float().abs().max()) == 0.0   # the peer's rows are the peer's to write
+    # sharded form: the residual stream's rows stay in a private tensor, only the normalised rows are broadcast
+    parity = 0
+    _region(A, L, 0, parity, rows, cols).copy_(xa)
+    _region(B, L, 0, parity, rows, cols).copy_(xb)
+    _flags(A)[BAR_IN + parity * 8 + 1] = 1
+    _flags(A)[BAR_OUT + parity * 8 + 1] = 1
+    h_priv = torch.zeros(rows, cols, dtype=torch.bfloat16, device="cuda")
+    assert lib.exo_reduce_norm_bf16(res.data_ptr(), w.data_ptr(), 1e-5, h_priv.data_ptr(), None, rows, cols, parity, 1, 0, st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(h_priv[:mine], want_h[:mine]) and float(h_priv[mine:].float().abs().max()) == 0.0
+    for arena in (A, B):
+        assert float(_region(arena, L, 1, parity, rows, cols).float().abs().max()) == 0.0      # hbuf untouched
+        x = _region(arena, L, 2, parity, rows, cols)
+        assert (x[:mine].float() - want_x[:mine].float()).abs().max() <= 0.02 * want_x.float().abs().max()
+    # ... and gathered on request: this rank's rows go to every arena's hbuf
+    GATHER = 2240 // 4
+    _flags(A)[GATHER + 1] = 1
+    assert lib.exo_gather_rows_bf16(h_priv.data_ptr(), rows, cols, parity, st) == 0
+    torch.cuda.synchronize()
+    for arena in (A, B):
+        assert torch.equal(_region(arena, L, 1, parity, rows, cols)[:mine], want_h[:mine])
     K.check_status()
     lib.exo_comm_reset()
 
@@ -116,7 +137,7 @@ def test_a_wait_that_runs_out_returns_sets_the_status_word_and_leaves_the_contex
         st = torch.cuda.current_stream().cuda_stream
         _region(A, L, 0, 0, rows, cols).copy_(x)
         # nobody raises the peer's flag: the kernel must give up after ~20 ms and return normally
-        assert lib.exo_reduce_norm_bf16(None, None, 0.0, h.data_ptr(), None, rows, cols, 0, 0, st) == 0
+        assert lib.exo_reduce_norm_bf16(None, None, 0.0, h.data_ptr(), None, rows, cols, 0, 0, 1, st) == 0
         torch.cuda.synchronize()
         with pytest.raises(DeviceWaitTimeout):
             K.check_status()
@@ -129,7 +150,7 @@ def test_a_wait_that_runs_out_returns_sets_the_status_word_and_leaves_the_contex
         # a healthy collective right afterwards: the peer's flag is there, the result is exact
         _region(B, L, 0, 0, rows, cols).copy_(x)
         _flags(A)[BAR_IN + 1] = 1
-        assert lib.exo_reduce_norm_bf16(None, None, 0.0, h.data_ptr(), None, rows, cols, 0, 0, st) == 0
+        assert lib.exo_reduce_norm_bf16(None, None, 0.0, h.data_ptr(), None, rows, cols, 0, 0, 1, st) == 0
         torch.cuda.synchronize()
         K.check_status()
         assert torch.equal(h, (x.float() * 2).bfloat16())
