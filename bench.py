@@ -6,11 +6,16 @@ tensor parallelism on N B200s of one node (synthetic prompts, random-init weight
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...   # N>1
 
 Two timed regions of exactly K decode steps each, both bracketed by barrier + synchronize and
-timed with CUDA events, max over ranks:
+timed with CUDA events, max over ranks, each repeated until about a second has been timed (the
+median repeat is reported):
   * device: pre-built step plans replayed back to back (input tokens taken from the previous
     step's samples on device) → ``value``;
   * end to end: the public ``Engine.step()`` call, which every step copies the packed plan from
     pinned host memory to the device and reads the sampled ids back → ``e2e``.
+On N > 1 GPUs the ranks are arranged as in serving: rank 0 owns the scheduler and publishes every
+step's plan through the shared-memory plan channel, the other ranks execute the plans they receive.
+The same decode loop is then repeated with the NCCL communicator (projection, ``ncclAllReduce``,
+separate residual add and norm) and ``vs_baseline`` is the ratio of the two.
 Measurement follows the reference's definition of generation throughput (tokens after the
 first divided by the time between first and last token, ``bench/METHODOLOGY.md:37-63`` in the
 reference) with EOS ignored so that exactly the requested number of tokens is produced.
@@ -40,6 +45,8 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--no-also", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL-communicator arm behind vs_baseline")
+    ap.add_argument("--min-timed-s", type=float, default=1.0, help="repeat each K-step region until this much is timed")
     ap.add_argument("--layers", type=int, default=0,
                     help="pre-flight only: run the first N layers of the model (the JSON line then says so and is not a result)")
     return ap.parse_args()
@@ -115,6 +122,7 @@ def main() -> None:
             sys.exit("launch with torch.distributed.run for --gpus > 1")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    chan = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -123,41 +131,49 @@ def main() -> None:
     from exo_b200.models.config import preset
     from exo_b200.models.weights import ShardSpec, fast_random_weights
     from exo_b200.engine.engine import Engine
+    from exo_b200.engine.executor import Executor
     from exo_b200.engine.kv import SamplingParams
-    from exo_b200.engine.plan import StepPlan, FLAG_ALL_GREEDY, FLAG_TOKENS_FROM_PREV
+    from exo_b200.engine.plan import StepPlan, FLAG_ALL_GREEDY, FLAG_TOKENS_FROM_PREV, bucket
     from exo_b200.ops import cuda as K
+
+    if world > 1:
+        from exo_b200.worker.engines.b200.bringup import PlanChannel
+        chan = PlanChannel(dist.new_group(backend="gloo"), rank, world)
 
     cfg = preset(args.model)
     if args.layers:
         from dataclasses import replace
         cfg = replace(cfg, n_layers=min(args.layers, cfg.n_layers))
     spec = ShardSpec(tp_rank=rank, tp_size=world)
-    comm = None
-    comm_name = "none"
-    if world > 1:
-        want = args.comm
-        if want in ("auto", "fused"):
-            try:
-                from exo_b200.parallel.fused import FusedComm
-                comm = FusedComm(dev, max_rows=max(args.prompt, 256), hidden=cfg.hidden,
-                                 vocab_shard=-(-cfg.vocab // world))
-                comm_name = "fused-p2p"
-            except Exception as e:  # noqa: BLE001
-                if want == "fused":
-                    raise
-                if rank == 0:
-                    print(f"[bench] fused comm unavailable ({e!r}); using NCCL", file=sys.stderr)
-        if comm is None:
-            from exo_b200.parallel.comm import NcclComm
-            comm = NcclComm()
-            comm_name = "nccl"
+
+    def make_comm(kind: str):
+        if world == 1:
+            return None, "none"
+        if kind == "fused":
+            from exo_b200.parallel.fused import FusedComm
+            c = FusedComm(dev, max_rows=max(min(args.prompt, 4096), 256), hidden=cfg.hidden, vocab_shard=-(-cfg.vocab // world))
+            return c, f"fused ({c.transport})"
+        from exo_b200.parallel.comm import NcclComm
+        return NcclComm(), "nccl"
+
+    want = "nccl" if args.comm == "nccl" else "fused"
+    try:
+        comm, comm_name = make_comm(want)
+    except Exception as e:  # noqa: BLE001
+        if args.comm == "fused":
+            raise
+        if rank == 0:
+            print(f"[bench] fused comm unavailable ({e!r}); using NCCL", file=sys.stderr)
+        comm, comm_name = make_comm("nccl")
 
     note(f"comm={comm_name}; building weights")
-    weights = fast_random_weights(cfg, spec, dev, seed=0)
+    weights = fast_random_weights(cfg, spec, dev, seed=0, router_std=1.0 if cfg.n_experts else None)
     torch.cuda.synchronize()
     note("weights ready")
     max_b = max(args.batch, 1 if args.no_also else args.also_batch)
-    per_seq_blocks = -(-(args.prompt + 2 * args.warmup + 4 * args.steps + 64) // 16)
+    MAX_REPEATS = max(1, 2048 // max(1, args.steps))        # bounds the KV each sequence may grow into
+    decode_room = 2 * MAX_REPEATS * args.steps + 2 * args.steps + 4 * max(args.warmup, 3) + 64
+    per_seq_blocks = -(-(args.prompt + decode_room) // 16)
     n_blocks = max_b * per_seq_blocks + 64
 
     def barrier() -> None:
@@ -172,124 +188,209 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def make_engine() -> Engine:
-        return Engine(cfg, weights, spec, comm, n_blocks=n_blocks, max_seqs=max(max_b, 8), prefill_chunk=4096,
-                      max_blocks_per_seq=per_seq_blocks, device=dev, seed=0)
+    def agree(v: int) -> int:
+        """Rank 0's value on every rank (repeat counts are decided by the leader's clock)."""
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.int64)
+        dist.broadcast(t, 0)
+        return int(t.item())
 
-    eng = make_engine()
+    class Rank:
+        """This rank's part in the serving topology: the leader schedules and publishes plans, followers execute them."""
+
+        def __init__(self, the_comm):
+            self.leader = rank == 0
+            if self.leader:
+                self.eng = Engine(cfg, weights, spec, the_comm, n_blocks=n_blocks, max_seqs=max(max_b, 8), prefill_chunk=4096,
+                                  max_blocks_per_seq=per_seq_blocks, device=dev, seed=0,
+                                  plan_sink=(lambda p: chan.send(p, [])) if chan is not None else None)
+                self.exe = self.eng.exe
+            else:
+                self.eng = None
+                self.exe = Executor(cfg, weights, spec, the_comm, n_blocks=n_blocks, max_blocks_per_seq=per_seq_blocks,
+                                    max_tokens_per_step=4096, max_seqs=max(max_b, 8), device=dev)
+
+        def run(self, marker: str, fn=None) -> None:
+            """Leader: do ``fn`` (which steps the engine / publishes plans), then publish ``marker``.
+            Follower: execute published plans until ``marker`` arrives."""
+            if self.leader:
+                if fn is not None:
+                    fn()
+                if chan is not None:
+                    chan.send(None, [marker])
+                return
+            while True:
+                plan, fin, _stop = chan.recv()
+                if plan is not None:
+                    self.exe.run(plan)
+                if marker in fin:
+                    return
+
+    me = Rank(comm)
     rng = np.random.default_rng(1234)
     greedy = dict(temperature=0.0, ignore_eos=True)
 
-    # ---------------- TTFT (one 2048-token prompt, admission -> first sampled token) ----------------
-    def ttft_once() -> float:
-        prompt = rng.integers(0, cfg.vocab, args.prompt).tolist()
+    # ---------------- TTFT (one prompt, admission -> first sampled token) ----------------
+    def ttft_once(r: "Rank") -> float:
+        def go():
+            prompt = rng.integers(0, cfg.vocab, args.prompt).tolist()
+            rid = r.eng.submit(prompt, SamplingParams(max_tokens=1, **greedy), use_prefix_cache=False)
+            got = False
+            while not got:
+                for o in r.eng.step():
+                    got |= o.req_id == rid and o.token is not None
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        rid = eng.submit(prompt, SamplingParams(max_tokens=1, **greedy), use_prefix_cache=False)
-        got = False
-        while not got:
-            for o in eng.step():
-                got |= o.req_id == rid and o.token is not None
+        r.run("ttft", go)
         e1.record()
         torch.cuda.synchronize()
         return max_over_ranks(e0.elapsed_time(e1))
 
     note("ttft warm-up")
-    ttft_once()  # warm-up (kernel loading, descriptor caches)
+    ttft_once(me)  # warm-up (kernel loading, descriptor caches)
     note("ttft timed")
-    ttfts = [ttft_once() for _ in range(3)]
+    ttfts = [ttft_once(me) for _ in range(3)]
     note(f"ttft {ttfts}")
     ttft_ms = min(ttfts)
-    K.gemm_check()
+    K.check_status()
 
     # ---------------- decode ----------------
-    def decode_bench(B: int, steps: int, warm: int) -> dict:
-        for s in list(eng.seqs):
-            eng.cancel(s)
-        rids = [eng.submit(rng.integers(0, cfg.vocab, args.prompt).tolist(),
-                           SamplingParams(max_tokens=10 ** 6, **greedy), use_prefix_cache=False) for _ in range(B)]
-        while any(eng.seqs[r].in_prefill or not eng.seqs[r].output for r in rids):
-            eng.step()
-        note(f"decode B={B}: prefill done, warming up")
-        for _ in range(max(warm, 3)):
-            eng.step()
-        note("e2e timed loop")
-        # --- end to end: public API, H2D of the plan and D2H of the ids every step ---
-        h0, d0 = eng.exe.h2d_bytes, eng.exe.d2h_bytes
-        sampler = ClockSampler(local)
+    def decode_bench(r: "Rank", B: int, steps: int, warm: int, e2e: bool = True) -> dict:
+        warm = max(warm, 3)
+        rids: list[str] = []
+
+        def prefill():
+            for s in list(r.eng.seqs):
+                r.eng.cancel(s)
+            rids.extend(r.eng.submit(rng.integers(0, cfg.vocab, args.prompt).tolist(),
+                                     SamplingParams(max_tokens=10 ** 6, **greedy), use_prefix_cache=False) for _ in range(B))
+            while any(r.eng.seqs[x].in_prefill or not r.eng.seqs[x].output for x in rids):
+                r.eng.step()
+            for _ in range(warm):
+                r.eng.step()
+        r.run("prefilled", prefill)
+        # estimate the step time on the leader to size the repeats
         barrier()
+        t0 = time.perf_counter()
+        r.run("probe", lambda: [r.eng.step() for _ in range(3)])
+        barrier()
+        est_ms = (time.perf_counter() - t0) * 1e3 / 3
+        repeats = agree(int(min(MAX_REPEATS, max(1, -(-args.min_timed_s * 1e3 // (est_ms * steps))))))
+        note(f"decode B={B}: step ~{est_ms:.2f} ms, {repeats} repeat(s) of {steps} steps")
+        sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            eng.step()
-        e1.record()
-        barrier()
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1))
-        h2d = (eng.exe.h2d_bytes - h0) // steps
-        d2h = (eng.exe.d2h_bytes - d0) // steps
+        # --- end to end: public API, H2D of the plan and D2H of the ids every step ---
+        e2e_ms: list[float] = []
+        h2d = d2h = 0
+        if e2e:
+            for _ in range(repeats):
+                h0, d0 = r.exe.h2d_bytes, r.exe.d2h_bytes
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r.run("e2e", lambda: [r.eng.step() for _ in range(steps)])
+                e1.record()
+                barrier()
+                e2e_ms.append(max_over_ranks(e0.elapsed_time(e1)))
+                h2d, d2h = (r.exe.h2d_bytes - h0) // steps, (r.exe.d2h_bytes - d0) // steps
         # --- device: pre-built plans, tokens chained on device ---
-        seqs = [eng.seqs[r] for r in rids]
-        bs = eng.alloc.block_size
-        for s in seqs:
-            assert eng.sched._ensure_blocks(s, s.n_tokens + steps + warm + 8)
-        mb = max(len(s.blocks) for s in seqs)
-        bt = np.zeros((B, mb), np.int32)
-        for b, s in enumerate(seqs):
-            bt[b, :len(s.blocks)] = s.blocks
-        base = np.array([s.n_tokens - 1 for s in seqs], np.int32)
-        rows = np.arange(B, dtype=np.int32)
+        plans: list[StepPlan] = []
+        if r.leader:
+            seqs = [r.eng.seqs[x] for x in rids]
+            bs = r.eng.alloc.block_size
+            total = warm + repeats * steps
+            for s in seqs:
+                assert r.eng.sched._ensure_blocks(s, s.n_tokens + total + 8)
+            mb = max(len(s.blocks) for s in seqs)
+            bt = np.zeros((B, mb), np.int32)
+            for b, s in enumerate(seqs):
+                bt[b, :len(s.blocks)] = s.blocks
+            base = np.array([s.n_tokens - 1 for s in seqs], np.int32)
+            rows = np.arange(B, dtype=np.int32)
+            for i in range(total):
+                pos = base + i
+                plans.append(StepPlan(n_tokens=B, n_seqs=B, max_q_len=1, flags=FLAG_ALL_GREEDY | FLAG_TOKENS_FROM_PREV,
+                                      tokens=np.zeros(B, np.int32), positions=pos, slots=bt[rows, pos // bs] * bs + pos % bs,
+                                      cu_q=np.arange(B + 1, dtype=np.int32), seq_lens=pos + 1, logit_rows=rows,
+                                      top_k=np.zeros(B, np.int32), temperature=np.zeros(B, np.float32),
+                                      top_p=np.ones(B, np.float32), min_p=np.zeros(B, np.float32),
+                                      uniform=np.zeros(B, np.float32), prev_rows=rows, block_tables=bt))
 
-        def plan_at(i: int) -> StepPlan:
-            pos = base + i
-            return StepPlan(n_tokens=B, n_seqs=B, max_q_len=1, flags=FLAG_ALL_GREEDY | FLAG_TOKENS_FROM_PREV,
-                            tokens=np.zeros(B, np.int32), positions=pos, slots=bt[rows, pos // bs] * bs + pos % bs,
-                            cu_q=np.arange(B + 1, dtype=np.int32), seq_lens=pos + 1, logit_rows=rows,
-                            top_k=np.zeros(B, np.int32), temperature=np.zeros(B, np.float32),
-                            top_p=np.ones(B, np.float32), min_p=np.zeros(B, np.float32),
-                            uniform=np.zeros(B, np.float32), prev_rows=rows, block_tables=bt)
-        note("device timed loop")
-        plans = [plan_at(i) for i in range(steps + max(warm, 3))]
-        for i in range(max(warm, 3)):
-            eng.exe.run(plans[i])
+        def replay(lo: int, hi: int):
+            def go():
+                for i in range(lo, hi):
+                    if chan is not None:
+                        chan.send(plans[i], [])
+                    r.exe.run(plans[i])
+            return go
+        r.run("dev-warm", replay(0, warm))
         launches_before = K.launch_count
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(steps):
-            eng.exe.run(plans[max(warm, 3) + i])
-        e1.record()
-        barrier()
+        dev_ms: list[float] = []
+        for k in range(repeats):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r.run("dev", replay(warm + k * steps, warm + (k + 1) * steps))
+            e1.record()
+            barrier()
+            dev_ms.append(max_over_ranks(e0.elapsed_time(e1)))
         clocks = sampler.stop() if rank == 0 else {}
-        dev_ms = max_over_ranks(e0.elapsed_time(e1))
-        key = (eng.exe.graphs and next(iter(eng.exe.graphs))) or None
-        K.gemm_check()
-        return {"B": B, "dev_ms_per_step": dev_ms / steps, "e2e_ms_per_step": e2e_ms / steps,
-                "dev_tok_s": B * steps / (dev_ms / 1e3), "e2e_tok_s": B * steps / (e2e_ms / 1e3),
-                "h2d": int(h2d), "d2h": int(d2h), "clocks": clocks, "eager_launches": K.launch_count - launches_before}
+        K.check_status()
+        if r.leader:
+            # the device holds the state of the last plan: nothing ran ahead of, or tore, the staged plans
+            L = r.exe.last_layout
+            got = r.exe.dev[L.seq_lens:L.seq_lens + B].cpu().numpy()
+            assert (got == plans[-1].seq_lens).all(), "device-side plan state does not match the last plan"
+        d_ms = statistics.median(dev_ms) / steps
+        e_ms = statistics.median(e2e_ms) / steps if e2e_ms else float("nan")
+        return {"B": B, "dev_ms_per_step": d_ms, "e2e_ms_per_step": e_ms, "dev_tok_s": B / (d_ms / 1e3),
+                "e2e_tok_s": B / (e_ms / 1e3) if e2e_ms else None, "h2d": int(h2d), "d2h": int(d2h), "clocks": clocks,
+                "repeats": repeats, "timed_s": round(sum(dev_ms) / 1e3, 3),
+                "eager_launches": K.launch_count - launches_before}
 
+    main_res = decode_bench(me, args.batch, args.steps, args.warmup)
     # kernels per decode step = launches recorded while the step's graph was captured
-    main_res = decode_bench(args.batch, args.steps, args.warmup)
-    per_step_launches = getattr(eng.exe, "launches_per_graph", {}).get(
-        __import__("exo_b200.engine.plan", fromlist=["bucket"]).bucket(args.batch, (1, 2, 4, 8, 16, 32, 64, 128, 256)), 0)
+    per_step_launches = getattr(me.exe, "launches_per_graph", {}).get(bucket(args.batch, (1, 2, 4, 8, 16, 32, 64, 128, 256)), 0)
     also = None
     if not args.no_also and args.also_batch != args.batch:
-        also = decode_bench(args.also_batch, max(16, args.steps // 2), args.warmup)
+        also = decode_bench(me, args.also_batch, max(16, args.steps // 2), args.warmup)
+
+    # ---------------- the same decode loop on the NCCL communicator: the baseline behind vs_baseline ----------------
+    base_res = None
+    if world > 1 and want == "fused" and not args.no_baseline and comm_name.startswith("fused"):
+        note("baseline arm (NCCL communicator)")
+        for s in (list(me.eng.seqs) if me.leader else []):
+            me.eng.cancel(s)
+        me_fused, me = me, None
+        me_fused.exe.graphs.clear()
+        del me_fused
+        torch.cuda.empty_cache()
+        nccl_comm, _ = make_comm("nccl")
+        base = Rank(nccl_comm)
+        base_res = decode_bench(base, args.batch, args.steps, args.warmup, e2e=False)
 
     if rank == 0:
         out = {
             "metric": f"decode_tok_s_bs{args.batch}", "value": round(main_res["dev_tok_s"], 2), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(main_res["dev_ms_per_step"], 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
+            "vs_baseline": round(main_res["dev_tok_s"] / base_res["dev_tok_s"], 3) if base_res else None,
+            "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
             "config": {"model": cfg.name + (f" (REDUCED to {cfg.n_layers} layers: pre-flight, not a result)" if args.layers else ""),
                        "weights": cfg.quant if cfg.quant != "none" else "bf16",
                        "global_batch": args.batch, "seq_len": args.prompt,
                        "decode_context": f"{args.prompt}+", "parallelism": f"tp{world}", "comm": comm_name,
+                       "topology": "rank 0 schedules and publishes each step's plan over shared memory; the other ranks execute it"
+                                   if world > 1 else "single process",
                        "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no explicit flush",
-                       "kv": "paged, block 16"},
+                       "kv": "paged, block 16",
+                       "timing": f"median of {main_res['repeats']} repeat(s) of {args.steps} steps ({main_res['timed_s']} s timed)",
+                       "baseline": ("same decode loop on the NCCL communicator (projection, ncclAllReduce, residual add, norm): "
+                                    f"{base_res['dev_tok_s']:.1f} tok/s" if base_res else
+                                    "none at one GPU (no published Llama-3.1-8B number; the baseline arm needs a collective)")},
             "clocks": main_res["clocks"],
             "e2e": {"value": round(main_res["e2e_tok_s"], 2), "unit": "tokens/s",
                     "h2d_bytes_per_step": main_res["h2d"], "d2h_bytes_per_step": main_res["d2h"]},
@@ -305,10 +406,19 @@ def main() -> None:
     sys.stdout.flush()
     sys.stderr.flush()
     if world > 1:
-        # Leave without tearing NCCL down: destroying a communicator whose collectives were captured
-        # in still-alive CUDA graphs blocked for minutes (both ranks sat in destroy_process_group).
+        # Unmap the symmetric arena in order (every rank idle, multicast binding first), then leave without tearing
+        # NCCL down: destroying a communicator whose collectives were captured in still-alive CUDA graphs blocked for
+        # minutes (both ranks sat in destroy_process_group).
         dist.barrier()
         torch.cuda.synchronize()
+        if comm is not None and hasattr(comm, "close"):
+            try:
+                comm.close()
+            except Exception as e:  # noqa: BLE001
+                print(f"[bench r{rank}] arena teardown: {e!r}", file=sys.stderr)
+        if chan is not None:
+            chan.close()
+        dist.barrier()
         os._exit(0)
 
 

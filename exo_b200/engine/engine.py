@@ -18,7 +18,7 @@ from ..models.weights import ModelWeights, ShardSpec
 from ..ops import reference as ref
 from .executor import Executor
 from .kv import BlockAllocator, SamplingParams, Sequence
-from .plan import StepPlan
+from .plan import FLAG_EAGER, StepPlan
 from .scheduler import Scheduler
 
 
@@ -148,12 +148,14 @@ class Engine:
         plan, entries = self.sched.schedule()
         if plan is None:
             return []
-        if self.plan_sink is not None:
-            self.plan_sink(plan)
         want_lp = any(s.params.logprobs for s, _ in entries)
         proc = self._processor(entries)
         if want_lp and proc is None:
             proc = lambda x: x  # noqa: E731 - forces the eager path that keeps logits
+        if proc is not None:
+            plan.flags |= FLAG_EAGER      # every rank must take the same path: a graph capture runs the step more than once
+        if self.plan_sink is not None:
+            self.plan_sink(plan)
         self.exe.model.embed_patches = self._embed_patches(entries)
         ids = self.exe.run(plan, proc)
         sampled = self.exe.fetch(ids)

@@ -17,7 +17,7 @@ from .. import ops
 from ..models.config import ModelConfig
 from ..models.transformer import Decoder, KVPool, StepInputs
 from ..models.weights import ModelWeights, ShardSpec
-from .plan import HEADER, PlanLayout, StepPlan, bucket, FLAG_ALL_GREEDY
+from .plan import HEADER, PlanLayout, StepPlan, bucket, FLAG_ALL_GREEDY, FLAG_EAGER
 
 DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 
@@ -46,6 +46,7 @@ class Executor:
         self.n_runs = 0
         self.dev = torch.zeros(words, dtype=torch.int32, device=self.device)
         self.n_blocks = n_blocks
+        self.last_layout: PlanLayout | None = None
         # MLA models whose dimensions the latent-attention kernel does not take (toy configs) run that op as PyTorch
         # ops with host reads of the sequence lengths: such a step cannot be captured
         mla_ok = not cfg.mla or (cfg.kv_lora_rank == 512 and cfg.qk_rope_dim == 64 and cfg.qk_nope_dim == 128
@@ -147,6 +148,7 @@ class Executor:
         if self.host_events[slot] is not None:
             self.host_events[slot].synchronize()
         L = plan.pack(self.hosts_np[slot], bT, bB, mb)
+        self.last_layout = L
         self.dev[:L.words].copy_(self.hosts[slot][:L.words], non_blocking=True)
         if self.cuda:
             ev = self.host_events[slot] or torch.cuda.Event()
@@ -156,7 +158,7 @@ class Executor:
         greedy = bool(plan.flags & FLAG_ALL_GREEDY)
         from_prev = bool(plan.flags & 1)
         self.n_launch_steps += 1
-        if decode and self.use_graphs and logits_processor is None:
+        if decode and self.use_graphs and logits_processor is None and not (plan.flags & FLAG_EAGER):
             key = (bB, greedy, from_prev)
             if key not in self.graphs:
                 self._capture(key, L)

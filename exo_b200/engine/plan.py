@@ -22,6 +22,7 @@ import numpy as np
 HEADER = 8
 FLAG_TOKENS_FROM_PREV = 1  # decode: take input tokens from the previous step's samples on device
 FLAG_ALL_GREEDY = 2
+FLAG_EAGER = 4             # the leader runs this step outside its CUDA graphs (logits processors): followers do the same
 
 
 @dataclass

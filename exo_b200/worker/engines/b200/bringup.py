@@ -35,32 +35,118 @@ from .tokenizer import eos_ids, load_tokenizer
 
 
 class PlanChannel:
-    """Control messages from rank 0 to the other ranks of the instance (gloo broadcast)."""
+    """Control messages from rank 0 to the other ranks of the instance, through a shared-memory ring.
 
-    def __init__(self, group, rank: int):
+    Every step the leader publishes ``(packed plan | None, finished task ids, stop flag)``.  The ranks of an
+    instance are processes of one box, so the message is a memcpy into a POSIX shared-memory segment followed by a
+    sequence-number store; followers spin on the number (a few microseconds end to end) and acknowledge by storing
+    the number they have consumed, which is what lets the leader reuse a slot.  The rendezvous (segment name) and
+    the one-off agreements of the bring-up still go through the ``gloo`` group.  This stands where the reference has
+    its per-step task / cancel agreement collectives on the CPU stream
+    (``src/exo/worker/engines/mlx/utils_mlx.py:833-938``)."""
+
+    SLOTS = 4
+    HDR_WORDS = 64           # int64: [0] last published sequence number, [8 + r] last number consumed by rank r
+
+    def __init__(self, group, rank: int, world: int | None = None, slot_bytes: int = 4 << 20):
+        from multiprocessing import shared_memory
         self.group, self.rank = group, rank
+        self.world = world if world is not None else dist.get_world_size(group)
+        self.slot_bytes = slot_bytes
+        self.seq = 0
+        size = self.HDR_WORDS * 8 + self.SLOTS * slot_bytes
+        box: list[Any] = [None]
+        if rank == 0:
+            self.shm = shared_memory.SharedMemory(create=True, size=size)
+            box[0] = self.shm.name
+        dist.broadcast_object_list(box, src=0, group=group)
+        if rank != 0:
+            self.shm = shared_memory.SharedMemory(name=box[0])
+            try:        # the leader owns the segment: keep this process's resource tracker from unlinking it at exit
+                from multiprocessing import resource_tracker
+                resource_tracker.unregister(self.shm._name, "shared_memory")
+            except Exception:  # noqa: BLE001
+                pass
+        self.hdr = np.ndarray((self.HDR_WORDS,), dtype=np.int64, buffer=self.shm.buf)
+        if rank == 0:
+            self.hdr[:] = 0
+        dist.barrier(group=group)
+        self.timeout_s = float(os.environ.get("EXO_GROUP_TIMEOUT_S", "120"))
+
+    def _slot(self, seq: int) -> np.ndarray:
+        off = self.HDR_WORDS * 8 + (seq % self.SLOTS) * self.slot_bytes
+        return np.ndarray((self.slot_bytes // 4,), dtype=np.int32, buffer=self.shm.buf, offset=off)
+
+    @staticmethod
+    def _wait(cond, timeout_s: float, what: str) -> None:
+        import time
+        t0 = None
+        spins = 0
+        while not cond():
+            spins += 1
+            if spins < 2000:
+                continue
+            if t0 is None:
+                t0 = time.perf_counter()
+            elif time.perf_counter() - t0 > timeout_s:
+                raise TimeoutError(f"plan channel: {what}")
+            time.sleep(20e-6)
 
     def send(self, plan: StepPlan | None, finished: list[str], stop: bool = False) -> None:
-        packed = None
+        seq = self.seq + 1
+        # a slot is free once every follower has consumed the message that used it last
+        need = seq - self.SLOTS
+        if need > 0:
+            acks = self.hdr[8 + 1:8 + self.world]
+            self._wait(lambda: int(acks.min()) >= need, self.timeout_s, "a follower stopped consuming plans")
+        slot = self._slot(seq)
+        words = 0
         if plan is not None:
             mb = max(1, plan.block_tables.shape[1])
-            buf = np.zeros(PlanLayout(plan.n_tokens, plan.n_seqs, mb).words, np.int32)
-            plan.pack(buf, plan.n_tokens, plan.n_seqs, mb)
-            packed = buf
-        dist.broadcast_object_list([(packed, finished, stop)], src=0, group=self.group)
+            words = PlanLayout(plan.n_tokens, plan.n_seqs, mb).words
+            if (8 + words) * 4 > self.slot_bytes:
+                raise ValueError(f"step plan of {words} words does not fit the plan channel's {self.slot_bytes} byte slots")
+            plan.pack(slot[8:], plan.n_tokens, plan.n_seqs, mb)
+        tail = ("\n".join(finished)).encode()
+        if (8 + words) * 4 + len(tail) > self.slot_bytes:
+            raise ValueError("plan channel message too large")
+        slot[0:4] = (1 if plan is not None else 0, words, len(tail), 1 if stop else 0)
+        if tail:
+            np.frombuffer(self.shm.buf, dtype=np.uint8, count=len(tail),
+                          offset=self.HDR_WORDS * 8 + (seq % self.SLOTS) * self.slot_bytes + (8 + words) * 4)[:] = np.frombuffer(tail, np.uint8)
+        self.hdr[0] = seq          # published: the payload stores above are ordered before this one (x86 TSO)
+        self.seq = seq
 
     def recv(self) -> tuple[StepPlan | None, list[str], bool]:
-        box: list[Any] = [None]
-        dist.broadcast_object_list(box, src=0, group=self.group)
-        packed, finished, stop = box[0]
-        return (StepPlan.unpack(packed) if packed is not None else None), finished, stop
+        seq = self.seq + 1
+        self._wait(lambda: int(self.hdr[0]) >= seq, self.timeout_s, "the leader stopped publishing plans")
+        slot = self._slot(seq)
+        has_plan, words, n_tail, stop = (int(x) for x in slot[0:4])
+        plan = StepPlan.unpack(slot[8:8 + words]) if has_plan else None
+        finished: list[str] = []
+        if n_tail:
+            off = self.HDR_WORDS * 8 + (seq % self.SLOTS) * self.slot_bytes + (8 + words) * 4
+            finished = bytes(self.shm.buf[off:off + n_tail]).decode().split("\n")
+        self.hdr[8 + self.rank] = seq
+        self.seq = seq
+        return plan, finished, bool(stop)
 
     def close(self) -> None:
         if self.rank == 0:
             try:
                 self.send(None, [], stop=True)
-            except RuntimeError:
+            except (RuntimeError, TimeoutError, ValueError):
                 pass
+        shm, self.shm = getattr(self, "shm", None), None
+        if shm is None:
+            return
+        self.hdr = None
+        try:
+            shm.close()
+            if self.rank == 0:
+                shm.unlink()
+        except (BufferError, FileNotFoundError, OSError):
+            pass
 
 
 class LeaderServingEngine(ServingEngine):
@@ -166,7 +252,7 @@ class B200Builder(Builder):
                                 timeout=datetime.timedelta(seconds=int(os.environ.get("EXO_GROUP_TIMEOUT_S", "120"))),
                                 **({"device_id": self.device} if backend == "nccl" else {}))
         ctl = dist.new_group(backend="gloo") if backend == "nccl" else dist.group.WORLD
-        self.control = PlanChannel(ctl, self.rank)
+        self.control = PlanChannel(ctl, self.rank, self.world)
         tp, pp = self.spec.tp_size, self.spec.pp_size
         if pp > 1:      # every rank creates every group, in the same order: one per stage, then one per lane
             stage_groups = [dist.new_group([s * tp + t for t in range(tp)]) for s in range(pp)]
@@ -221,6 +307,12 @@ class B200Builder(Builder):
         dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.control.group)
         return int(t.item())
 
+    def _graphs(self) -> bool | None:
+        """CUDA graphs for decode steps.  Every rank executes the same plans in the same order and the leader marks
+        the steps it runs eagerly, so all ranks capture and replay at the same steps; pipeline stages exchange
+        activations with blocking point-to-point calls and stay eager."""
+        return None if self.spec.pp_size == 1 else False
+
     def build(self) -> Engine:
         assert self.cfg is not None and self.weights is not None
         cfg = self.cfg
@@ -241,7 +333,7 @@ class B200Builder(Builder):
         if self.rank != 0:
             exe = Executor(cfg, self.weights, self.spec, self.comm, n_blocks=n_blocks, max_blocks_per_seq=mbs,
                            max_tokens_per_step=constants.PREFILL_CHUNK, max_seqs=max_seqs, device=self.device,
-                           use_graphs=False, pipe=self.pipe)
+                           use_graphs=self._graphs(), pipe=self.pipe)
             assert self.control is not None
             return FollowerServingEngine(exe, self.control)
         tok = load_tokenizer(self.model_dir, cfg.vocab)
@@ -250,7 +342,7 @@ class B200Builder(Builder):
         cls = LeaderServingEngine if self.world > 1 else ServingEngine
         te = TokenEngine(cfg, self.weights, self.spec, self.comm, n_blocks=n_blocks, max_seqs=max_seqs,
                          prefill_chunk=constants.PREFILL_CHUNK, max_blocks_per_seq=mbs, device=self.device,
-                         use_graphs=None if self.world == 1 else False, pipe=self.pipe)
+                         use_graphs=self._graphs(), pipe=self.pipe)
         eng = cls(cfg, te, tok, str(self.card.model_id), self.card.family, eos, self.card.reasoning_dialect, self.rank,
                   self.control)
         if self.world > 1:

@@ -4,7 +4,8 @@ It plays the part the reference's tests give to a monkey-patched MLX (fake group
 fake warm-up: ``src/exo/worker/tests/unittests/test_runner/test_event_ordering.py:123-140``) and
 implements the reference's host-side fault hooks: the magic prompts ``EXO RUNNER MUST FAIL`` /
 ``MUST OOM`` / ``MUST TIMEOUT`` (``src/exo/worker/runner/llm_inference/batch_generator.py:67-86``;
-the OOM is a simulated allocation failure, never a real device allocation).
+the OOM is a simulated allocation failure, never a real device allocation), plus ``MUST LOSE A PEER``: the
+exception the GPU executor raises when a collective kernel's bounded wait on a peer ran out.
 """
 from __future__ import annotations
 
@@ -36,6 +37,8 @@ class FakeEngine(Engine):
                 raise MemoryError("Simulated allocation failure (requested by prompt)")
             if "EXO RUNNER MUST TIMEOUT" in text:
                 time.sleep(3600)
+            if "EXO RUNNER MUST LOSE A PEER" in text:
+                self.lose_peer = True
         self.active[task.task_id] = 0
 
     def cancel(self, task_id: TaskId) -> None:
@@ -47,6 +50,11 @@ class FakeEngine(Engine):
         return bool(self.active)
 
     def step(self) -> Iterable[tuple[TaskId, StepItem]]:
+        if getattr(self, "lose_peer", False):
+            # what the B200 executor raises after a step whose collective kernel gave up waiting for a peer GPU
+            # (host-side stand-in: no device is involved)
+            from ...ops.cuda import DeviceWaitTimeout
+            raise DeviceWaitTimeout("cuda:0: a collective kernel gave up waiting for a peer GPU (code 4)")
         out: list[tuple[TaskId, StepItem]] = []
         for tid in list(self.active):
             if tid in self.cancelled:

@@ -16,7 +16,8 @@ PATTERNS: tuple[tuple[str, str, re.Pattern[str]], ...] = (
     ("cuda_oom", "The GPU ran out of memory", re.compile(r"CUDA out of memory|cudaErrorMemoryAllocation|OutOfMemoryError", re.I)),
     ("cuda_fault", "A CUDA kernel faulted", re.compile(r"illegal memory access|an illegal instruction|misaligned address|Xid \d+|unspecified launch failure", re.I)),
     ("nccl_error", "An NCCL collective failed", re.compile(r"NCCL (WARN|error)|ncclUnhandledCudaError|ncclSystemError|ncclRemoteError", re.I)),
-    ("collective_timeout", "A rank stopped answering inside a collective", re.compile(r"CollectiveTimeout|Watchdog caught collective operation timeout|device-side wait on a peer timed out", re.I)),
+    ("collective_timeout", "A rank stopped answering inside a collective", re.compile(r"CollectiveTimeout|DeviceWaitTimeout|gave up waiting for a peer GPU|Watchdog caught collective operation timeout|device-side wait on a peer timed out", re.I)),
+    ("kernel_timeout", "A kernel's internal pipeline wait ran out", re.compile(r"pipeline wait ran out|device-side timeout code", re.I)),
     ("peer_access", "GPU peer access is unavailable", re.compile(r"cannot map arena|peer access|cudaErrorPeerAccess", re.I)),
     ("kernel_missing", "The native kernel library is missing", re.compile(r"_kernels\.so is missing|KernelError: .* is missing", re.I)),
     ("checkpoint", "The model checkpoint is incomplete or unreadable", re.compile(r"no \*\.safetensors under|checkpoint shape .* != expected|safetensors", re.I)),

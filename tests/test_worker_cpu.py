@@ -172,6 +172,23 @@ def test_runner_death_becomes_runner_failed_and_error_chunk():
     assert any(isinstance(e, TaskStatusUpdated) and e.task_status == TaskStatus.Failed for e in evs)
 
 
+def test_a_collective_that_gave_up_on_a_peer_ends_the_runner_with_a_diagnostic():
+    """The executor raises after a step whose device-side wait on a peer ran out (it reads the status words every
+    step); the runner process dies, the supervisor reports RunnerFailed with the collective-timeout diagnostic and
+    an ErrorChunk for the request in flight.  The failure is made on the host: no GPU takes part."""
+    inst, nodes, rids = instance(1)
+
+    async def script(s):
+        await s.start_task(LoadModel(instance_id=inst.instance_id))
+        await s.start_task(StartWarmup(instance_id=inst.instance_id))
+        await s.start_task(_tg_task(inst, "EXO RUNNER MUST LOSE A PEER"))
+    evs = _run_supervised(inst, nodes, rids, script)
+    failed = [e.runner_status for e in evs if isinstance(e, RunnerStatusUpdated) and isinstance(e.runner_status, RunnerFailed)]
+    assert failed and any(d.kind == "collective_timeout" for d in failed[-1].diagnostics)
+    errs = [e.chunk for e in evs if isinstance(e, ChunkGenerated) and isinstance(e.chunk, ErrorChunk)]
+    assert errs and "peer GPU" in errs[0].error_message
+
+
 def test_immediate_exception_hook_and_oom_diagnostic():
     inst, nodes, rids = instance(1, immediate_exception=True)
 
