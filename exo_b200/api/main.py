@@ -201,7 +201,7 @@ class API:
         st = self.state
         return place_instance(PlaceInstance(model_card=card, sharding=sharding, instance_meta=meta, min_nodes=min_nodes),
                               st.topology, st.instances, st.node_memory, st.node_backends, required_nodes=required,
-                              download_status=st.downloads, gpu_index=self._gpu_index())
+                              download_status=st.downloads, gpu_index=self._gpu_index(), node_nvlink=st.node_nvlink)
 
     # ---- state ----
     def get_state(self, path: str = ""):

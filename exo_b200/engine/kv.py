@@ -154,7 +154,7 @@ class SamplingParams:
         return self.repetition_penalty != 1.0 or self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
 
 
-@dataclass
+@dataclass(eq=False)          # identity semantics: sequences live in lists that are searched every step
 class Sequence:
     req_id: str
     prompt: list[int]
@@ -180,6 +180,29 @@ class Sequence:
     @property
     def tokens(self) -> list[int]:
         return self.prompt + self.output
+
+    def token_at(self, i: int) -> int:
+        n = len(self.prompt)
+        return self.prompt[i] if i < n else self.output[i - n]
+
+    def token_span(self, lo: int, hi: int) -> list[int]:
+        """Tokens ``[lo, hi)`` of prompt + output without building the concatenated list."""
+        n = len(self.prompt)
+        if hi <= n:
+            return self.prompt[lo:hi]
+        if lo >= n:
+            return self.output[lo - n:hi - n]
+        return self.prompt[lo:] + self.output[:hi - n]
+
+    def blocks_array(self):
+        """``blocks`` as an int32 array.  Rebuilt when the list object was replaced (admission, preemption) or has
+        grown (one block every block_size tokens); the list is never edited in the middle."""
+        import numpy as np
+        c = self.__dict__.get("_blk_np")
+        if c is None or c[0] is not self.blocks or c[1].shape[0] != len(self.blocks):
+            c = (self.blocks, np.asarray(self.blocks, np.int32))
+            self.__dict__["_blk_np"] = c
+        return c[1]
 
     @property
     def n_tokens(self) -> int:

@@ -152,8 +152,7 @@ class Scheduler:
         # 2. admit newcomers while there is token budget and a free seat
         while self.waiting and len(self.running) < self.max_seqs and budget > 0:
             s = self.waiting[0]
-            full = s.tokens  # after preemption the generated tokens are recomputed as prompt
-            if len(full) >= self.max_context:
+            if s.n_tokens >= self.max_context:      # after preemption the generated tokens are recomputed as prompt
                 self.waiting.popleft()
                 s.finished, s.finish_reason = True, "length"
                 continue
@@ -202,16 +201,20 @@ class Scheduler:
         t = 0
         all_greedy = True
         for b, (s, n) in enumerate(entries):
-            all_toks = s.tokens
             lo = s.n_computed
-            tokens[t:t + n] = all_toks[lo:lo + n]
-            pos = np.arange(lo, lo + n, dtype=np.int32)
-            positions[t:t + n] = pos
-            blk = np.asarray(s.blocks, np.int32)
-            slots[t:t + n] = blk[pos // bs] * bs + pos % bs
+            blk = s.blocks_array()
+            if n == 1:                   # decode row: no temporaries
+                tokens[t] = s.token_at(lo)
+                positions[t] = lo
+                slots[t] = int(blk[lo // bs]) * bs + lo % bs
+            else:
+                tokens[t:t + n] = s.token_span(lo, lo + n)
+                pos = np.arange(lo, lo + n, dtype=np.int32)
+                positions[t:t + n] = pos
+                slots[t:t + n] = blk[pos // bs] * bs + pos % bs
             cu_q[b + 1] = t + n
             seq_lens[b] = lo + n
-            if lo + n == len(all_toks):  # the step reaches the sequence's last token → sample
+            if lo + n == s.n_tokens:  # the step reaches the sequence's last token → sample
                 logit_rows[b] = t + n - 1
                 p = s.params
                 temp[b], top_p[b], min_p[b], top_k[b] = p.temperature, p.top_p, p.min_p, p.top_k

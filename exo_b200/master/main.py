@@ -153,7 +153,8 @@ class Master:
         elif isinstance(cmd, PlaceInstance):
             target = place_instance(cmd, st.topology, st.instances, st.node_memory, st.node_backends,
                                     download_status=st.downloads,
-                                    gpu_index={n: v.gpu_index for n, v in st.node_nvlink.items()} or self.gpu_index)
+                                    gpu_index={n: v.gpu_index for n, v in st.node_nvlink.items()} or self.gpu_index,
+                                    node_nvlink=st.node_nvlink)
             for ev in get_transition_events(st.instances, target, st.tasks):
                 await self._emit(ev)
         elif isinstance(cmd, CreateInstance):

@@ -26,8 +26,10 @@ from ..shared.wire import (CfgShardMetadata, DownloadCompleted, DownloadOngoing,
                            InstanceMeta, MemoryUsage, NvlinkInstance, PipelineShardMetadata, ShardAssignments, Sharding,
                            ShardMetadata, TensorShardMetadata)
 
-HBM_GBS = 6500.0              # per-GPU streaming bandwidth assumed by the cost model
-AR_LATENCY_US = 6.0           # one small fused all-reduce over NVSwitch (measured order of magnitude)
+# Fallbacks of the cost model, used until the nodes' link probes have reported (``utils.link_probe``: device-copy
+# bandwidth of each GPU's HBM, copy bandwidth and small-copy latency to each peer):
+HBM_GBS = 6500.0              # per-GPU streaming bandwidth
+AR_LATENCY_US = 6.0           # one small fused all-reduce over NVSwitch
 P2P_HOP_US = 12.0             # one pipeline activation hop
 MEMORY_HEADROOM = 0.92        # fraction of free HBM a shard may claim (KV pool comes out of the rest)
 KV_RESERVE_FRACTION = 0.10    # at least this share of a GPU stays free for KV blocks
@@ -56,18 +58,31 @@ def allocate_layers_proportionally(total_layers: int, fractions: Sequence[float]
     return base
 
 
-def estimate_decode_step_us(card: ModelCard, tp: int, pp: int, nvlink_gbps: float, batch: int = 1) -> float:
-    """Rough decode-step latency of a (tp, pp) shape: weight streaming + collectives + stage hops."""
+def estimate_decode_step_us(card: ModelCard, tp: int, pp: int, nvlink_gbps: float, batch: int = 1,
+                            hbm_gbps: float = 0.0, link_latency_us: float = 0.0) -> float:
+    """Rough decode-step latency of a (tp, pp) shape: weight streaming + collectives + stage hops.  ``hbm_gbps`` and
+    ``link_latency_us`` are the measured figures of the chosen GPUs (0: use the fallbacks above)."""
     bytes_per_gpu = card.storage_size.in_bytes / (tp * pp)
-    stream_us = bytes_per_gpu / (HBM_GBS * 1e3)             # GB/s → bytes/us
+    stream_us = bytes_per_gpu / ((hbm_gbps or HBM_GBS) * 1e3)             # GB/s → bytes/us
     per_stage = stream_us
     ar_bytes = 2 * batch * card.hidden_size
     link = max(nvlink_gbps, 1.0) * 1e3
-    ar_us = 0.0 if tp == 1 else AR_LATENCY_US + ar_bytes * (tp - 1) / link
+    # a small collective is one one-way trip of the pushed words (plus the consumer's poll): the measured small-copy
+    # latency stands in for it when the probe has run
+    ar_fixed = link_latency_us or AR_LATENCY_US
+    ar_us = 0.0 if tp == 1 else ar_fixed + ar_bytes * (tp - 1) / link
     layers_per_stage = card.n_layers / pp
     per_stage += 2 * layers_per_stage * ar_us
     # decode walks the stages one after the other
-    return pp * per_stage + (pp - 1) * P2P_HOP_US
+    return pp * per_stage + (pp - 1) * max(P2P_HOP_US, 2 * link_latency_us)
+
+
+def is_moe_card(card: ModelCard) -> bool:
+    """Mixture-of-experts models name their active parameter count in the model id (``-A22B``, ``-A3B``) or are of a
+    family that has no dense members; their experts are spread over the tensor-parallel ranks."""
+    import re
+    name = f"{card.model_id} {card.base_model}"
+    return bool(re.search(r"-A\d+(\.\d+)?B\b", name)) or card.family in ("deepseek", "kimi", "minimax") or "MoE" in name
 
 
 def _tensor_ok(card: ModelCard, n: int) -> bool:
@@ -154,7 +169,8 @@ def get_shard_assignments(card: ModelCard, nodes: Sequence[NodeId], sharding: Sh
     return ShardAssignments(model_id=card.model_id, runner_to_shard=r2s, node_to_runner=n2r)
 
 
-def choose_shape(card: ModelCard, n: int, sharding: Sharding, nvlink_gbps: float) -> tuple[int, int]:
+def choose_shape(card: ModelCard, n: int, sharding: Sharding, nvlink_gbps: float, hbm_gbps: float = 0.0,
+                 link_latency_us: float = 0.0) -> tuple[int, int]:
     """(tp, pp) for ``n`` GPUs.  Tensor requests may fall back to PP2 x TP-n/2 when the cost model
     says the halved all-reduce fan-in wins; Pipeline requests keep pure layer stages."""
     if n == 1:
@@ -167,14 +183,16 @@ def choose_shape(card: ModelCard, n: int, sharding: Sharding, nvlink_gbps: float
     shapes = [s for s in shapes if _tensor_ok(card, s[0])]
     if not shapes:
         raise ValueError("no tensor-parallel shape divides this model")
-    return min(shapes, key=lambda s: estimate_decode_step_us(card, s[0], s[1], nvlink_gbps))
+    return min(shapes, key=lambda s: estimate_decode_step_us(card, s[0], s[1], nvlink_gbps, 1, hbm_gbps, link_latency_us))
 
 
 def place_instance(command: PlaceInstance, topology: Topology, current_instances: Mapping[InstanceId, Instance],
                    node_memory: Mapping[NodeId, MemoryUsage], node_backends: Mapping[NodeId, list[Backend]],
                    required_nodes: set[NodeId] | None = None,
                    download_status: Mapping[NodeId, Sequence[DownloadProgress]] | None = None,
-                   gpu_index: Mapping[NodeId, int] | None = None) -> dict[InstanceId, Instance]:
+                   gpu_index: Mapping[NodeId, int] | None = None,
+                   node_nvlink: Mapping[NodeId, object] | None = None) -> dict[InstanceId, Instance]:
+    """``node_nvlink`` (``State.node_nvlink``) carries each GPU's link-probe figures for the cost model."""
     card = command.model_card
     groups = candidate_groups(topology, node_memory, command.min_nodes, required_nodes)
     groups = [g for g in groups if _fits(card, g, node_memory)]
@@ -202,13 +220,16 @@ def place_instance(command: PlaceInstance, topology: Topology, current_instances
     chosen = max(groups, key=lambda g: (_download_score(g, card.model_id, dl),
                                         sum(node_memory[n].ram_available.in_bytes for n in g)))
     sharding = command.sharding if len(chosen) > 1 else Sharding.Pipeline
-    tp, pp = choose_shape(card, len(chosen), sharding, topology.min_nvlink_gbps(chosen) if len(chosen) > 1 else 0.0)
+    infos = [node_nvlink[n] for n in chosen if node_nvlink and n in node_nvlink]
+    hbm = min((i.hbm_gbps for i in infos if getattr(i, "hbm_gbps", 0.0)), default=0.0)
+    lat = max((p.latency_us for i in infos for p in getattr(i, "peers", []) if getattr(p, "measured", False)), default=0.0)
+    tp, pp = choose_shape(card, len(chosen), sharding, topology.min_nvlink_gbps(chosen) if len(chosen) > 1 else 0.0, hbm, lat)
     gidx = dict(gpu_index or {})
     assignments = get_shard_assignments(card, chosen, sharding, tp, pp, node_memory, gidx)
     iid = InstanceId()
     target = dict(deepcopy(dict(current_instances)))
     shape = f"tp{tp}" if pp == 1 else (f"pp{pp}" if tp == 1 else f"pp{pp}xtp{tp}")
-    if card.family in ("qwen", "deepseek", "kimi") and tp > 1 and "A" in card.base_model:
+    if is_moe_card(card) and tp > 1:
         shape += f"+ep{tp}"
     target[iid] = NvlinkInstance(instance_id=iid, shard_assignments=assignments, rendezvous_port=random_ephemeral_port(),
                                  gpu_by_node={n: gidx.get(n, i) for i, n in enumerate(chosen)}, parallelism=shape)

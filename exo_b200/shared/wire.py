@@ -102,8 +102,10 @@ class ThunderboltBridgeStatus(FrozenModel):
 class NvlinkPeer(FrozenModel):
     peer_gpu: int
     links: int = 0
-    gbps: float = 0.0
+    gbps: float = 0.0          # one-direction copy bandwidth: measured by the link probe, else links x nominal
     p2p: bool = True
+    latency_us: float = 0.0    # small peer copy (0: not measured)
+    measured: bool = False
 
 
 class NodeNvlinkInfo(FrozenModel):
@@ -111,6 +113,7 @@ class NodeNvlinkInfo(FrozenModel):
     gpu_index: int
     uuid: str = ""
     peers: Sequence[NvlinkPeer] = []
+    hbm_gbps: float = 0.0      # measured device-copy bandwidth of this GPU's HBM (0: not measured)
 
 
 # gathered-info messages (what the telemetry task of a node emits)

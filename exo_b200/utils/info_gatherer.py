@@ -99,18 +99,33 @@ def friendly_name(gpu: int | None) -> str:
     return host if gpu is None else f"{host}/gpu{gpu}"
 
 
-def nvlink_info(me: GpuSample, n_gpus: int) -> NodeNvlinkInfo:
+def nvlink_info(me: GpuSample, n_gpus: int, measured: dict | None = None) -> NodeNvlinkInfo:
     """Peer table of one GPU.  Behind NVSwitch NVML reports no per-peer link count (links end at
-    the switch), so a P2P-capable peer gets the GPU's whole active link budget."""
+    the switch), so a P2P-capable peer gets the GPU's whole active link budget.  ``measured`` is the link probe's
+    result (``utils.link_probe``): where it has a figure for a peer, that figure replaces links x nominal."""
     peers = []
+    got = (measured or {}).get("peers", {})
     for j in range(n_gpus):
         if j == me.index:
             continue
         ok = bool(me.p2p_ok[j]) if j < len(me.p2p_ok) else False
         direct = me.nvlink_peers_links[j] if j < len(me.nvlink_peers_links) else 0
         links = direct or (me.active_links or NVSWITCH_DEFAULT_LINKS if ok else 0)
-        peers.append(NvlinkPeer(peer_gpu=j, links=links, gbps=links * NVLINK5_GBPS_PER_LINK, p2p=ok))
-    return NodeNvlinkInfo(gpu_index=me.index, uuid=me.uuid, peers=peers)
+        m = got.get(str(j)) or {}
+        if ok and m.get("gbps"):
+            peers.append(NvlinkPeer(peer_gpu=j, links=links, gbps=float(m["gbps"]), p2p=ok,
+                                    latency_us=float(m.get("latency_us", 0.0)), measured=True))
+        else:
+            peers.append(NvlinkPeer(peer_gpu=j, links=links, gbps=links * NVLINK5_GBPS_PER_LINK, p2p=ok))
+    return NodeNvlinkInfo(gpu_index=me.index, uuid=me.uuid, peers=peers, hbm_gbps=float((measured or {}).get("hbm_gbps", 0.0)))
+
+
+def link_probe(gpu: int, peers: list[int], uuid: str) -> dict | None:
+    """Measured copy bandwidths of this GPU (own HBM, each peer); tests replace this hook."""
+    if os.environ.get("EXO_LINK_PROBE", "1") == "0" or not kernels_available():
+        return None
+    from .link_probe import measure
+    return measure(gpu, peers, uuid)
 
 
 def kernels_available() -> bool:
@@ -126,6 +141,8 @@ class InfoGatherer:
         self.gpu_index = gpu_index if gpu_index is not None else node_gpu_index()
         self.iv = dict(memory=memory_interval, perf=perf_interval, disk=disk_interval, network=network_interval,
                        misc=misc_interval, nvlink=nvlink_interval)
+        self._measured: dict | None = None
+        self._probe_tried = False
 
     # ---- single readings (also used directly by tests and the power sampler) ----
     def _gpus(self) -> list[GpuSample]:
@@ -180,7 +197,17 @@ class InfoGatherer:
     def nvlink(self) -> NodeNvlink | None:
         gpus = self._gpus()
         me = self._mine(gpus)
-        return NodeNvlink(info=nvlink_info(me, len(gpus))) if me is not None else None
+        if me is None:
+            return None
+        if self._measured is None and not self._probe_tried and len(gpus) > 0:
+            # once per node: the probe runs in a child process (tens of seconds the first time, cached afterwards)
+            self._probe_tried = True
+            peers = [j for j in range(len(gpus)) if j != me.index and j < len(me.p2p_ok) and me.p2p_ok[j]]
+            try:
+                self._measured = link_probe(me.index, peers, me.uuid)
+            except Exception:  # noqa: BLE001 - telemetry must survive a failing probe
+                self._measured = None
+        return NodeNvlink(info=nvlink_info(me, len(gpus), self._measured))
 
     # ---- periodic tasks ----
     async def _every(self, seconds: float, read: Callable[[], GatheredInfo | None]) -> None:

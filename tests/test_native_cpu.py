@@ -122,3 +122,46 @@ def test_pidfile_lock(tmp_path):
 def test_nvml_enumerate_without_driver_is_empty_not_fatal():
     gpus, err = native.nvml_enumerate()
     assert isinstance(gpus, list) and (gpus or err)
+
+
+def test_discovery_answers_hello_with_whatsup_in_the_wire_format_and_ignores_other_namespaces():
+    """Packet-level discovery (reference wire format, ``rust/networking/src/discovery.rs:313-336``): a Hello
+    ``{magic "EXO", kind 1, nonce[8], namespace[8]}`` from the same namespace is answered with a WhatsUp
+    ``{magic, kind 2, nonce echoed, id[16] right-aligned, port little-endian}``; another namespace gets nothing."""
+    import socket
+    import struct
+    import time
+    with socket.socket(socket.AF_INET6, socket.SOCK_DGRAM) as probe:
+        probe.bind(("::", 0))
+        disc_port = probe.getsockname()[1]
+    bus = native.Bus("ab12", "disc-test", 0, disc_port)
+    try:
+        time.sleep(0.2)
+        with socket.socket(socket.AF_INET6, socket.SOCK_DGRAM) as s:
+            s.settimeout(3)
+            nonce = b"nonce-01"
+            hello = b"EXO" + bytes([1]) + nonce + struct.pack("<Q", native.namespace_hash("disc-test"))
+            s.sendto(hello, ("::1", disc_port))
+            pkt, _ = s.recvfrom(64)
+            assert len(pkt) == 30 and pkt[:3] == b"EXO" and pkt[3] == 2
+            assert pkt[4:12] == nonce
+            assert pkt[12:28].hex() == "ab12".rjust(32, "0")
+            assert pkt[28] | (pkt[29] << 8) == bus.listen_port
+            other = b"EXO" + bytes([1]) + b"nonce-02" + struct.pack("<Q", native.namespace_hash("someone-else"))
+            s.sendto(other, ("::1", disc_port))
+            s.settimeout(0.5)
+            try:
+                s.recvfrom(64)
+                raise AssertionError("a Hello from another namespace must not be answered")
+            except socket.timeout:
+                pass
+            # a truncated packet and a wrong magic are dropped without a reply either
+            s.sendto(b"EX", ("::1", disc_port))
+            s.sendto(b"XXX" + bytes([1]) + bytes(16), ("::1", disc_port))
+            try:
+                s.recvfrom(64)
+                raise AssertionError("malformed discovery packets must be ignored")
+            except socket.timeout:
+                pass
+    finally:
+        bus.close()
