@@ -1,6 +1,6 @@
 """Micro-benchmarks of the individual sm_100a kernels against the measured roofline.
 
-    python -m exo_b200.utils.bench_kernels [--only gemv,gemm,fp8,moe,attn,prefill] [--peaks MEASURED_PEAKS.json]
+    python -m exo_b200.utils.bench_kernels [--only gemv,gemm,fp8,moe,attn,mla,prefill] [--peaks MEASURED_PEAKS.json]
 
 Every case is timed with CUDA events after warm-up; a 256 MB buffer is overwritten between
 iterations so that no operand survives in the 126 MB L2.  Output: achieved GB/s or TFLOP/s and
@@ -114,7 +114,7 @@ def small_cases(only: set[str]) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="gemv,gemm,fp8,moe,attn,prefill,misc")
+    ap.add_argument("--only", default="gemv,gemm,fp8,moe,attn,mla,prefill,misc")
     ap.add_argument("--peaks", default=str(Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"))
     ap.add_argument("--small", action="store_true",
                     help="one modest case per section, launched eagerly three times (the form to run under a profiler)")
@@ -216,6 +216,33 @@ def main() -> None:
                              for kc, vc in caches])
             print(f"decode-attn B={B} ctx={ctx}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s  "
                   f"{gb / ms * 1e3 / hbm:5.2f} of {basis} HBM")
+    if "mla" in only:
+        # DeepSeek-V3 attention of one rank under TP8: 16 heads over the shared latent cache (576 values per token)
+        H, L, R, bs = 16, 512, 64, 16
+        for B, ctx in ((1, 8192), (16, 8192), (64, 4096)):
+            per = ctx // bs + 1
+            bt = (torch.arange(B * per, device="cuda", dtype=torch.int32) + 1).view(B, -1)
+            sl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+            cu = torch.arange(B + 1, device="cuda", dtype=torch.int32)
+            q = rnd(B, H, L + R)
+            gb = B * ctx * (L + R) * 2 / 1e9
+            copies = max(2, int(0.4 / gb) + 1)
+            caches = [rnd(B * per + 1, bs, L + R) for _ in range(copies)]
+            ms = timeit_rot([(lambda c=c: K.mla_paged_attention(q, c, bt, sl, cu, 192 ** -0.5, L, 1)) for c in caches])
+            print(f"mla-decode-attn B={B} ctx={ctx} heads={H}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s  "
+                  f"{gb / ms * 1e3 / hbm:5.2f} of {basis} HBM")
+        T = 2048
+        per = T // bs + 1
+        c = rnd(per + 1, bs, L + R)
+        bt = (torch.arange(per, device="cuda", dtype=torch.int32) + 1).view(1, -1)
+        sl = torch.tensor([T], device="cuda", dtype=torch.int32)
+        cu = torch.tensor([0, T], device="cuda", dtype=torch.int32)
+        q = rnd(T, H, L + R)
+        ms = timeit(lambda: K.mla_paged_attention(q, c, bt, sl, cu, 192 ** -0.5, L, T), iters=5)
+        fl = 2.0 * T * T / 2 * H * (2 * L + R) / 1e12
+        print(f"mla-prefill-attn T={T} heads={H}: {ms * 1e3:8.1f} us  {fl / ms * 1e3:7.1f} TFLOP/s (causal)  "
+              f"{fl / ms * 1e3 / tf:5.2f} of {basis} bf16")
+        K.check_status()
     if "prefill" in only:
         Hq, Hkv, D, bs = 32, 8, 128, 16
         for T in (512, 2048, 4096):
