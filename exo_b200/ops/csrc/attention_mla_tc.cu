@@ -12,7 +12,7 @@
 //
 // One CTA = (split of the keys, group of up to 16 heads, query token); 128 threads, thread t owns TMEM lane t:
 // key t of the block for the softmax, output dims t, 128 + t, 256 + t, 384 + t for the result.  The same kernel
-// serves decode (one token per sequence, split-KV with a ticketed merge) and prefill chunks (the token's causal
+// serves decode (one token per sequence, split-KV merged by a second small kernel) and prefill chunks (the token's causal
 // limit is its key count).  The reference computes this attention with mlx-lm's DeepSeek model and slices the
 // absorbed projections per rank (src/exo/worker/engines/mlx/auto_parallel.py:688-721).
 // Every wait is bounded: on a timeout the kernel records a code, drains and returns.
@@ -52,7 +52,6 @@ struct Params {
   __nv_bfloat16* out;        // [T, H, 512]
   float* part_o;             // [T * H, ns, 512]
   float* part_ml;            // [T * H, ns, 2]
-  int* tickets;              // [T * groups]
   int* err;
   float scale_log2;
   int H, groups, max_blocks, ns;
@@ -343,35 +342,6 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           p.part_ml[row * 2 + 1] = l_tot[g];
         }
       }
-      __threadfence();
-      __syncthreads();
-      if (tid == 0) {
-        int* tk = p.tickets + (size_t)t * p.groups + grp;
-        const int old = atomicAdd(tk, 1);
-        s.is_last = old == p.ns - 1;
-        if (s.is_last) *tk = 0;
-      }
-      __syncthreads();
-      if (s.is_last > 0) {
-        __threadfence();
-#pragma unroll 1
-        for (int g = 0; g < G; g++) {
-          const size_t row0 = ((size_t)q_row + g) * p.ns;
-          float M = -INFINITY;
-          for (int sp = 0; sp < p.ns; sp++) M = fmaxf(M, __ldcg(p.part_ml + (row0 + sp) * 2));
-          float L = 0.f, o[NT] = {0.f, 0.f, 0.f, 0.f};
-          for (int sp = 0; sp < p.ns; sp++) {
-            const float m_s = __ldcg(p.part_ml + (row0 + sp) * 2);
-            const float w = m_s == -INFINITY ? 0.f : ex2(m_s - M);
-            L += __ldcg(p.part_ml + (row0 + sp) * 2 + 1) * w;
-#pragma unroll
-            for (int dt = 0; dt < NT; dt++) o[dt] += __ldcg(p.part_o + (row0 + sp) * LAT + dt * 128 + tid) * w;
-          }
-#pragma unroll
-          for (int dt = 0; dt < NT; dt++)
-            p.out[((size_t)q_row + g) * LAT + dt * 128 + tid] = __float2bfloat16_rn(L > 0.f ? o[dt] / L : 0.f);
-        }
-      }
     }
   }
   // ---- unwind: give copies that may still be in flight a bounded time to land, free the TMEM ----
@@ -382,6 +352,52 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// Merge of the key splits: one CTA per (token, head) column, 128 threads x 4 output dims.  A kernel of its own so
+// that the 16 .. 128 columns of a token are merged by as many SMs at once (merged by the last split's CTA alone, the
+// partials of all heads were one CTA's serial chain of L2 round trips, longer than the attention itself).
+__global__ void __launch_bounds__(128)
+mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* out, int ns) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float w_s[32];
+  __shared__ float inv_s;
+  const size_t col = blockIdx.x;
+  const int tid = threadIdx.x;
+  if (tid < 32) {
+    const float m_s = tid < ns ? __ldcg(part_ml + (col * ns + tid) * 2) : -INFINITY;
+    const float l_s = tid < ns ? __ldcg(part_ml + (col * ns + tid) * 2 + 1) : 0.f;
+    float M = m_s;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float w = m_s == -INFINITY ? 0.f : ex2(m_s - M);
+    float L = l_s * w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    w_s[tid] = w;
+    if (tid == 0) inv_s = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
+  const float* po = part_o + col * ns * LAT + tid;
+  float o[NT] = {0.f, 0.f, 0.f, 0.f};
+  int sp = 0;
+  for (; sp + 4 <= ns; sp += 4) {
+    float v[4][NT];
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+#pragma unroll
+      for (int dt = 0; dt < NT; dt++) v[u][dt] = __ldcg(po + (size_t)(sp + u) * LAT + dt * 128);
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+#pragma unroll
+      for (int dt = 0; dt < NT; dt++) o[dt] += v[u][dt] * w_s[sp + u];
+  }
+  for (; sp < ns; sp++)
+#pragma unroll
+    for (int dt = 0; dt < NT; dt++) o[dt] += __ldcg(po + (size_t)sp * LAT + dt * 128) * w_s[sp];
+#pragma unroll
+  for (int dt = 0; dt < NT; dt++) out[col * LAT + dt * 128 + tid] = __float2bfloat16_rn(o[dt] * inv_s);
 }
 
 // ---- small CUDA-core kernels around the attention: cache append, query absorption, output absorption ----------
@@ -524,10 +540,10 @@ EXO_API int exo_mla_attn_splits(int n_ctas_unsplit, int max_len) {
 EXO_API long exo_mla_attn_workspace(int T, int H, int ns) { return (long)T * H * ns * (LAT + 2) + 64; }
 
 // q [T, H, 576] bf16 in cache space (see exo_mla_q_absorb), cache [n_blocks, 16, 576] bf16, out [T, H, 512].
-// cu_q / tok_seq null: decode (token t is sequence t).  `tickets` [T * groups] zero before the first launch.
+// cu_q / tok_seq null: decode (token t is sequence t).  ns > 1 needs `workspace` (exo_mla_attn_workspace floats).
 // Returns -2 for shapes this kernel does not take.
 EXO_API int exo_mla_attn_tc(const void* q, const void* cache, const int* block_tables, const int* seq_lens, const int* cu_q,
-                            const int* tok_seq, void* out, float* workspace, int* tickets, float scale, int T, int H,
+                            const int* tok_seq, void* out, float* workspace, float scale, int T, int H,
                             int kv_lora, int rope_dim, int n_blocks, int max_blocks, int block_size, int ns,
                             cudaStream_t st) {
   if (T <= 0) return 0;
@@ -550,9 +566,9 @@ EXO_API int exo_mla_attn_tc(const void* q, const void* cache, const int* block_t
   p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = cu_q; p.tok_seq = tok_seq;
   p.out = (__nv_bfloat16*)out;
   p.part_o = workspace; p.part_ml = workspace ? workspace + (size_t)T * H * ns * LAT : nullptr;
-  p.tickets = tickets; p.err = err; p.scale_log2 = scale * 1.4426950408889634f;
+  p.err = err; p.scale_log2 = scale * 1.4426950408889634f;
   p.H = H; p.groups = groups; p.max_blocks = max_blocks; p.ns = ns;
-  if (ns > 1 && (!workspace || !tickets)) return -2;
+  if (ns > 1 && !workspace) return -2;
   dim3 grid(ns, groups, T);
   cudaError_t e = cudaSuccess;
 #define LAUNCH(GG)                                                                                                \
@@ -576,6 +592,12 @@ EXO_API int exo_mla_attn_tc(const void* q, const void* cache, const int* block_t
 #undef LAUNCH
   if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
+  if (ns > 1) {
+    e = launch_pdl(mla_merge_kernel, dim3(T * H), dim3(128), 0, st, (const float*)p.part_o, (const float*)p.part_ml,
+                   (__nv_bfloat16*)out, ns);
+    if (e != cudaSuccess) return (int)e;
+    EXO_CHECK_LAUNCH();
+  }
   return 0;
 }
 

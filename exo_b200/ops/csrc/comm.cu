@@ -284,11 +284,15 @@ constexpr int RN_THREADS = 256, RN_WARPS = RN_THREADS / 32;
 template <bool MC, bool TWO, int VPL>
 __global__ void __launch_bounds__(RN_THREADS)
 reduce_norm_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ norm_w,
-                   float eps, __nv_bfloat16* h_out, __nv_bfloat16* x_out, int rows, int cols, int parity, int bcast_h) {
+                   float eps, __nv_bfloat16* h_out, __nv_bfloat16* x_out, int rows, int cols, int parity, int mode) {
   pdl_trigger();
   pdl_wait();
   __shared__ int last_s;
+  const bool bcast_h = mode & 1, defer_wait = mode & 2;
   if (blockIdx.x == 0 && threadIdx.x < c.n) {
+    // a deferred-wait collective of this parity left its "rows broadcast" flags up for the GEMM that consumed them:
+    // clear them before anybody can be told to start this one
+    if (TWO) *bar_ptr(c.arena[c.rank], BAR_OUT, parity, threadIdx.x) = 0;
     __threadfence_system();   // the partial was written by earlier kernels of this stream: publish it system-wide
     red_release_sys_add(bar_ptr(c.arena[threadIdx.x], BAR_IN, parity, c.rank), 1);
   }
@@ -391,11 +395,13 @@ reduce_norm_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ residual, 
   if (TWO) {
     __threadfence_system();
     if (threadIdx.x < c.n) red_release_sys_add(bar_ptr(c.arena[threadIdx.x], BAR_OUT, parity, c.rank), 1);
-    wait_ranks(c, BAR_OUT, parity);
+    // deferred: the consumer (a GEMM that waits for each owner's flag before it loads that owner's rows) does the
+    // waiting, tile by tile, so its first tiles run while the last rows are still on their way
+    if (!defer_wait) wait_ranks(c, BAR_OUT, parity);
   }
   if (threadIdx.x < c.n) {
     *bar_ptr(c.arena[c.rank], BAR_IN, parity, threadIdx.x) = 0;
-    if (TWO) *bar_ptr(c.arena[c.rank], BAR_OUT, parity, threadIdx.x) = 0;
+    if (TWO && !defer_wait) *bar_ptr(c.arena[c.rank], BAR_OUT, parity, threadIdx.x) = 0;
     __threadfence_system();
   }
 }
@@ -555,12 +561,13 @@ EXO_API int exo_allgather_cols_bf16(const void* in, int rows, int cols, int pari
 // The partial must have been written into this rank's partial[parity] region (exo_comm_region(0, parity)) by
 // earlier work of the same stream.
 //   two_shot = 0: h_out / x_out are private [rows, cols] tensors of the caller; every rank computes every row.
-//   two_shot = 1: x lands in exo_comm_region(2, parity) on every rank (x_out ignored).  bcast_h != 0: so does h, in
-//                 exo_comm_region(1, parity) (h_out ignored); bcast_h == 0: only this rank's rows
-//                 [rank R, (rank+1) R), R = ceil(rows / n), of the private h_out are written.
+//   two_shot = 1: x lands in exo_comm_region(2, parity) on every rank (x_out ignored).  mode bit 0 set: so does h, in
+//                 exo_comm_region(1, parity) (h_out ignored); clear: only this rank's rows [rank R, (rank+1) R),
+//                 R = ceil(rows / n), of the private h_out are written.  mode bit 1 set: the kernel does not wait for
+//                 the other ranks' rows; the consumer must (exo_comm_gate + a gated GEMM).
 // rows * cols * 2 must fit the region; cols % 8 == 0 and cols <= 8192.
 EXO_API int exo_reduce_norm_bf16(const void* residual, const void* norm_w, float eps, void* h_out, void* x_out, int rows,
-                                 int cols, int parity, int two_shot, int bcast_h, cudaStream_t st) {
+                                 int cols, int parity, int two_shot, int mode, cudaStream_t st) {
   int dev;
   cudaGetDevice(&dev);
   if (dev >= 16 || !g_ctx_set[dev]) return -4;
@@ -568,7 +575,9 @@ EXO_API int exo_reduce_norm_bf16(const void* residual, const void* norm_w, float
   c.wait_ns = exo_wait_budget_ns();
   if (rows <= 0 || cols % 8 || cols > 8192) return -2;
   if (!c.x_bytes || (size_t)rows * cols * 2 > c.x_bytes) return -6;
+  const int bcast_h = mode & 1;
   if ((!two_shot || !bcast_h) && !h_out) return -2;
+  if (!two_shot) mode &= 1;
   if (!two_shot && norm_w && !x_out) return -2;
   const auto* res = (const __nv_bfloat16*)residual;
   const auto* nw = (const __nv_bfloat16*)norm_w;
@@ -581,9 +590,9 @@ EXO_API int exo_reduce_norm_bf16(const void* residual, const void* norm_w, float
   cudaError_t e;
 #define RN_LAUNCH(MCV, TWOV)                                                                                                  \
   e = wide ? launch_pdl(reduce_norm_kernel<MCV, TWOV, 32>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, \
-                        cols, parity, bcast_h)                                                                                 \
+                        cols, parity, mode)                                                                                    \
            : launch_pdl(reduce_norm_kernel<MCV, TWOV, 16>, dim3(grid), dim3(RN_THREADS), 0, st, c, res, nw, eps, ho, xo, rows, \
-                        cols, parity, bcast_h)
+                        cols, parity, mode)
   if (two_shot) {
     if (c.mc) { RN_LAUNCH(true, true); } else { RN_LAUNCH(false, true); }
   } else {
@@ -592,6 +601,21 @@ EXO_API int exo_reduce_norm_bf16(const void* residual, const void* norm_w, float
 #undef RN_LAUNCH
   if (e != cudaSuccess) return (int)e;
   EXO_CHECK_LAUNCH();
+  return 0;
+}
+
+// What a GEMM needs to consume the rows of a deferred-wait two-shot reduction as they arrive: rank j's rows
+// [j R, (j+1) R), R = ceil(rows / n), are complete once flags[j] >= 1.  Returns 0, or <0 without a communicator.
+int exo_comm_gate(int parity, int rows, const int** flags, int* rows_per_flag, int* rank, unsigned long long* wait_ns,
+                  int** status) {
+  int dev;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return -4;
+  const CommCtx& c = g_ctx[dev];
+  *flags = reinterpret_cast<const int*>(c.arena[c.rank] + BAR_OUT) + (parity & 1) * MAX_RANKS;
+  *rows_per_flag = (rows + c.n - 1) / c.n;
+  *rank = c.rank;
+  *wait_ns = exo_wait_budget_ns();
+  *status = c.status;
   return 0;
 }
 

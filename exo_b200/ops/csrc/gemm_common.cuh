@@ -22,6 +22,12 @@ struct GemmParams {
   int* counters;          // [tiles] zero-initialised, self-resetting
   int* err;               // device error word
   TpHandover ho;          // row-parallel output handed to every rank (n_ll > 0): `out` is then not written
+  // all-gather -> GEMM: the activation rows arrive from the other ranks while the kernel runs (null: plain GEMM)
+  const int* row_flags;   // row_flags[j] >= 1 once rows [j * rows_per_flag, (j + 1) * rows_per_flag) have landed
+  int rows_per_flag;
+  int m_tile_shift;       // row tiles are walked starting at this rank's own rows, which are there first
+  unsigned long long gate_wait_ns;
+  int* gate_status;       // status word of the collectives (a peer that never delivers: code 4)
 };
 
 // Called by the four epilogue warps (threads 64..191) once the MMA warp has committed `acc_full`.

@@ -180,7 +180,9 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
 
 // F16: both MMA operands are f16 (the activations arrive converted, the weights are widened with the hardware
 // e4m3 -> f16 converter): half the widening instructions of the bf16 form.
-template <int BN, int RS, bool F16>
+// HO: the output leaves for every rank's hand-over slot as flag-in-data words (row-parallel projection of a decode
+// step under tensor parallelism, see tp_handover.cuh) instead of being stored to `out`.
+template <int BN, int RS, bool F16, bool HO = false>
 __global__ void __launch_bounds__(320, (BN <= 64 ? 2 : 1))
 gemm_fp8w_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p, const ScaleParams sp) {
   extern __shared__ uint8_t smem_raw[];
@@ -291,7 +293,7 @@ gemm_fp8w_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
       tc::mbar_arrive(&s.a_full[as]);
     }
     if (warp < 6)     // warps 2..5 own the four TMEM lane quadrants of the accumulator
-      gemm::epilogue<BN>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
+      gemm::epilogue<BN, HO>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -301,23 +303,29 @@ gemm_fp8w_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
   }
 }
 
-template <int BN, int RS, bool F16>
+template <int BN, int RS, bool F16, bool HO = false>
 int launch_fp8w_ta_t(const CUtensorMap* tx, const GemmParams& p, const ScaleParams& sp, cudaStream_t st) {
   using S = SmemFT<BN, RS>;
   const size_t smem = sizeof(S) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_fp8w_ta_kernel<BN, RS, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_fp8w_ta_kernel<BN, RS, F16, HO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return -3;
     attr_set = true;
   }
   dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
-  gemm_fp8w_ta_kernel<BN, RS, F16><<<grid, 320, smem, st>>>(*tx, p, sp);
+  gemm_fp8w_ta_kernel<BN, RS, F16, HO><<<grid, 320, smem, st>>>(*tx, p, sp);
   EXO_CHECK_LAUNCH();
   return 0;
 }
 template <int BN, int RS>
 int launch_fp8w_ta(const CUtensorMap* tx, const GemmParams& p, const ScaleParams& sp, bool f16, cudaStream_t st) {
+  if (p.ho.n_ll > 0) {
+    if constexpr (BN <= 64)       // hand-overs are decode batches
+      return f16 ? launch_fp8w_ta_t<BN, RS, true, true>(tx, p, sp, st) : launch_fp8w_ta_t<BN, RS, false, true>(tx, p, sp, st);
+    else
+      return -2;
+  }
   return f16 ? launch_fp8w_ta_t<BN, RS, true>(tx, p, sp, st) : launch_fp8w_ta_t<BN, RS, false>(tx, p, sp, st);
 }
 
@@ -363,11 +371,21 @@ EXO_API int exo_bf16_to_f16(const void* x, void* y, long n, cudaStream_t st) {
 }
 
 static int gemm_fp8w_impl(const void* x, const void* tiles, int scale_kind, const void* bias, const void* residual, void* out,
-                          int M, int N, int K, int ldo, int splits, bool x_f16, cudaStream_t st);
+                          int M, int N, int K, int ldo, int splits, bool x_f16, cudaStream_t st, const TpHandover* ho = nullptr);
 
 EXO_API int exo_gemm_fp8w(const void* x, const void* tiles, int scale_kind, const void* bias,
                           const void* residual, void* out, int M, int N, int K, int ldo, int splits, cudaStream_t st) {
   return gemm_fp8w_impl(x, tiles, scale_kind, bias, residual, out, M, N, K, ldo, splits, false, st);
+}
+// Row-parallel projection of a decode batch (M <= 64) under tensor parallelism: the [M, N] output goes to every rank's
+// hand-over slot as flag-in-data words (see tp_handover.cuh); N even.  x_f16: the activations are f16 (as below).
+EXO_API int exo_gemm_fp8w_tp(const void* x, const void* tiles, int scale_kind, const void* bias, int M, int N, int K,
+                             int splits, int parity, int x_f16, cudaStream_t st) {
+  if ((N & 1) || M > 64) return -2;
+  TpHandover ho;
+  int rc = exo_tp_handover_fill(&ho, 3, parity, (long)((M + 1) & ~1) * N);
+  if (rc) return rc;
+  return gemm_fp8w_impl(x, tiles, scale_kind, bias, nullptr, nullptr, M, N, K, N, splits, x_f16 != 0, st, &ho);
 }
 // The same with f16 activations `x16` (see exo_bf16_to_f16): both MMA operands f16.
 EXO_API int exo_gemm_fp8w_f16(const void* x16, const void* tiles, int scale_kind, const void* bias,
@@ -376,7 +394,7 @@ EXO_API int exo_gemm_fp8w_f16(const void* x16, const void* tiles, int scale_kind
 }
 
 static int gemm_fp8w_impl(const void* x, const void* tiles, int scale_kind, const void* bias, const void* residual, void* out,
-                          int M, int N, int K, int ldo, int splits, bool x_f16, cudaStream_t st) {
+                          int M, int N, int K, int ldo, int splits, bool x_f16, cudaStream_t st, const TpHandover* ho) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || K < BK || (scale_kind != 1 && scale_kind != 2) || ((uintptr_t)tiles & 15)) return -2;
   GemmParams p;
@@ -396,7 +414,8 @@ static int gemm_fp8w_impl(const void* x, const void* tiles, int scale_kind, cons
   p.residual = (const __nv_bfloat16*)residual;
   p.out = (__nv_bfloat16*)out;
   p.ldo = ldo;
-  memset(&p.ho, 0, sizeof(p.ho));
+  if (ho) p.ho = *ho; else memset(&p.ho, 0, sizeof(p.ho));
+  p.row_flags = nullptr; p.rows_per_flag = 1; p.m_tile_shift = 0; p.gate_wait_ns = 0; p.gate_status = nullptr;
   if (splits > 1) {
     const long tiles = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     if ((size_t)splits * M * N > partial_floats || tiles > (1 << 16)) return -6;
@@ -407,7 +426,7 @@ static int gemm_fp8w_impl(const void* x, const void* tiles, int scale_kind, cons
   sp.kt = kb_total;
   static int smem_a = -1;
   if (smem_a < 0) { const char* e = getenv("EXO_FP8_SMEM_A"); smem_a = (e && e[0] == '1') ? 1 : 0; }
-  if (!smem_a || x_f16) {      // A operand from tensor memory (default); EXO_FP8_SMEM_A=1 selects the shared-memory form below
+  if (!smem_a || x_f16 || ho) {      // A operand from tensor memory (default); EXO_FP8_SMEM_A=1 selects the shared-memory form below
     switch (bn) {
       case 16: return launch_fp8w_ta<16, 8>(tx, p, sp, x_f16, st);     // 8 x (8.25 + 2) KB
       case 32: return launch_fp8w_ta<32, 8>(tx, p, sp, x_f16, st);     // 8 x (8.25 + 4) KB

@@ -52,7 +52,8 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   constexpr uint32_t TMEM_COLS = (TWO ? 2 : 1) * BN < 32 ? 32 : (TWO ? 2 : 1) * BN;
   constexpr uint32_t STAGE_BYTES = ((TWO ? 2 : 1) * BM * BK + BN * BK) * 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM * ((TWO && !GLU) ? 2 : 1), m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int n0 = blockIdx.x * BM * ((TWO && !GLU) ? 2 : 1), split = blockIdx.z;
+  const int m0 = (int)((blockIdx.y + (unsigned)p.m_tile_shift) % gridDim.y) * BN;
   const int second = GLU ? p.N / 2 : BM;      // row distance of the second weight tile
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
@@ -79,7 +80,29 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     if (tc::elect_one()) {
       tc::prefetch_tmap(&tmap_w);
       tc::prefetch_tmap(&tmap_x);
-      for (int i = 0; i < nkb; i++) {
+      bool gate_ok = true;
+      if (p.row_flags) {
+        // all-gather -> GEMM: this CTA's activation rows belong to one or two ranks; wait (bounded) until those ranks
+        // have delivered them, then order the wait before the TMA engine's reads of the same memory
+        const int o_lo = m0 / p.rows_per_flag, o_hi = (min(p.M, m0 + BN) - 1) / p.rows_per_flag;
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+        for (int o = o_lo; o <= o_hi && gate_ok; o++) {
+          while (tp_ld_acquire_sys(p.row_flags + o) < 1) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (now - t0 > p.gate_wait_ns) {
+              atomicExch(p.gate_status, 4 /* peer timeout */);
+              s.abort_flag = 1;
+              gate_ok = false;
+              break;
+            }
+            __nanosleep(64);
+          }
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
+      for (int i = 0; i < nkb && gate_ok; i++) {
         int st = i % STAGES;
         if (i >= STAGES && !tc::mbar_wait(&s.empty[st], ((i / STAGES) - 1) & 1)) {
           atomicExch(p.err, tc::ERR_EMPTY_TIMEOUT);
@@ -333,9 +356,46 @@ EXO_API int exo_gemm_bf16(const void* x, const void* W, const void* bias, const 
   return gemm_launch(x, W, bias, residual, out, M, N, K, ldo, splits, nullptr, st);
 }
 
+int exo_comm_gate(int parity, int rows, const int** flags, int* rows_per_flag, int* rank, unsigned long long* wait_ns,
+                  int** status);
+
+// Fills the all-gather -> GEMM fields of `p`: the rows of `x` are the broadcast output of the deferred-wait two-shot
+// reduction on `parity` (see comm.cu); the row tiles are walked starting at this rank's own rows.
+static int gate_params(GemmParams* p, int parity, int M, int bn) {
+  int rank = 0;
+  int rc = exo_comm_gate(parity, M, &p->row_flags, &p->rows_per_flag, &rank, &p->gate_wait_ns, &p->gate_status);
+  if (rc) return rc;
+  p->m_tile_shift = (rank * p->rows_per_flag) / bn;
+  return 0;
+}
+
+static int g_gate_parity = -1;      // >= 0: the next GEMM launched from this thread is gated on that parity
+
+// All-gather -> GEMM: like exo_gemm_bf16 (M >= 256, no split-K), with the activation rows arriving from the other
+// ranks while the kernel runs.
+EXO_API int exo_gemm_bf16_gated(const void* x, const void* W, const void* bias, const void* residual, void* out, int M, int N,
+                                int K, int ldo, int parity, cudaStream_t st) {
+  if (M < 256) return -2;
+  g_gate_parity = parity;
+  int rc = gemm_launch(x, W, bias, residual, out, M, N, K, ldo, 1, nullptr, st);
+  g_gate_parity = -1;
+  return rc;
+}
+
 // Fused gate/up projection with the SwiGLU in the epilogue: W = [gate (F rows); up (F rows)], out[M, F].
 // Prefill shapes only (M >= 256, no bias): returns -2 otherwise and the caller takes the two-kernel form.
+static int gemm_swiglu_launch(const void* x, const void* W, void* out, int M, int N, int K, int gate_parity, cudaStream_t st);
+
 EXO_API int exo_gemm_bf16_swiglu(const void* x, const void* W, void* out, int M, int N, int K, cudaStream_t st) {
+  return gemm_swiglu_launch(x, W, out, M, N, K, -1, st);
+}
+
+// The same with the activation rows gated on the deferred-wait two-shot reduction of `parity`.
+EXO_API int exo_gemm_bf16_swiglu_gated(const void* x, const void* W, void* out, int M, int N, int K, int parity, cudaStream_t st) {
+  return gemm_swiglu_launch(x, W, out, M, N, K, parity, st);
+}
+
+static int gemm_swiglu_launch(const void* x, const void* W, void* out, int M, int N, int K, int gate_parity, cudaStream_t st) {
   if (M < 256 || (N & 1) || K % 8 != 0 || K < BK) return -2;
   int dev;
   cudaGetDevice(&dev);
@@ -351,6 +411,10 @@ EXO_API int exo_gemm_bf16_swiglu(const void* x, const void* W, void* out, int M,
   p.out = (__nv_bfloat16*)out;
   p.ldo = N / 2;
   p.err = g_err[dev];
+  if (gate_parity >= 0) {
+    int rc = gate_params(&p, gate_parity, M, 256);
+    if (rc) return rc;
+  }
   return launch_gemm_glu(tw, tx, p, st);
 }
 
@@ -392,6 +456,11 @@ static int gemm_launch(const void* x, const void* W, const void* bias, const voi
   p.counters = g_counters[dev];
   p.err = g_err[dev];
   if (ho) p.ho = *ho; else memset(&p.ho, 0, sizeof(p.ho));
+  p.row_flags = nullptr; p.rows_per_flag = 1; p.m_tile_shift = 0; p.gate_wait_ns = 0; p.gate_status = nullptr;
+  if (g_gate_parity >= 0) {
+    int rc = gate_params(&p, g_gate_parity, M, bn);
+    if (rc) return rc;
+  }
   if (splits > 1) {
     long tiles = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     if ((size_t)splits * M * N > g_partial_floats[dev] || tiles > MAX_TILES) return -6;

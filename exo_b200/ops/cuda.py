@@ -70,12 +70,14 @@ class _Sig:
     exo_gemm_splits = (_i, [_i, _i, _i])
     exo_gemm_bf16 = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p])
     exo_gemm_bf16_swiglu = (_i, [_p, _p, _p, _i, _i, _i, _p])
+    exo_gemm_bf16_gated = (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+    exo_gemm_bf16_swiglu_gated = (_i, [_p, _p, _p, _i, _i, _i, _i, _p])
     exo_gemm_fp8w = (_i, [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
     exo_gemm_fp8w_f16 = (_i, [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
     exo_bf16_to_f16 = (_i, [_p, _p, _l, _p])
     exo_mla_attn_splits = (_i, [_i, _i])
     exo_mla_attn_workspace = (_l, [_i, _i, _i])
-    exo_mla_attn_tc = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _p])
+    exo_mla_attn_tc = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _p])
     exo_mla_kv_append = (_i, [_p, _p, _f, _p, _p, _f, _p, _p, _i, _i, _i, _p])
     exo_mla_q_absorb = (_i, [_p, _p, _p, _p, _f, _p, _i, _i, _i, _i, _i, _i, _p])
     exo_mla_o_absorb = (_i, [_p, _p, _p, _i, _i, _i, _i, _p])
@@ -162,9 +164,19 @@ def ensure_gemm_init(device) -> None:
         _gemm_ready.add(dev)
 
 
-def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False, out=None):
+def gated_gemm_ok(M: int, N: int, K: int, swiglu_out: bool) -> bool:
+    """Shapes for which :func:`gemm_bf16` accepts ``gate_parity`` (the all-gather -> GEMM form)."""
+    return (gemm_impl is not None and M >= 256 and K >= 64 and K % 8 == 0
+            and (not swiglu_out or (N % 2 == 0 and use_fused_swiglu)))
+
+
+def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False, out=None, gate_parity=None):
     """tcgen05 GEMM ``x[M,K] @ w[N,K].T``; per-device scratch is set up on first use, which
-    must therefore happen outside CUDA-graph capture (the executor warms up before capturing)."""
+    must therefore happen outside CUDA-graph capture (the executor warms up before capturing).
+
+    ``gate_parity``: ``x`` is the broadcast output of a deferred-wait two-shot reduction on that parity
+    (``parallel.fused``): each CTA waits for the flag of the rank that owns its activation rows before loading them,
+    so the GEMM starts on the rows that are there while the others are still crossing NVLink (all-gather -> GEMM)."""
     lib = load()
     ensure_gemm_init(x.device)
     M, K = x.shape
@@ -172,7 +184,20 @@ def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False, out=None):
     if swiglu_out and M >= 256 and bias is None and residual is None and N % 2 == 0 and use_fused_swiglu:
         # prefill: gate and up tiles share a CTA and the activation is applied in the epilogue
         out = torch.empty(M, N // 2, dtype=x.dtype, device=x.device)
-        _chk(lib.exo_gemm_bf16_swiglu(_ptr(x), _ptr(w), _ptr(out), M, N, K, _st()), "gemm_bf16_swiglu")
+        if gate_parity is not None:
+            _chk(lib.exo_gemm_bf16_swiglu_gated(_ptr(x), _ptr(w), _ptr(out), M, N, K, int(gate_parity), _st()),
+                 "gemm_bf16_swiglu_gated")
+        else:
+            _chk(lib.exo_gemm_bf16_swiglu(_ptr(x), _ptr(w), _ptr(out), M, N, K, _st()), "gemm_bf16_swiglu")
+        _count()
+        return out
+    if gate_parity is not None:
+        if swiglu_out or M < 256:
+            raise KernelError("gated GEMM takes prefill shapes (M >= 256) and, with SwiGLU, the fused epilogue")
+        if out is None:
+            out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        _chk(lib.exo_gemm_bf16_gated(_ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, N, int(gate_parity),
+                                     _st()), "gemm_bf16_gated")
         _count()
         return out
     if out is None or swiglu_out:
@@ -431,7 +456,6 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform):
 # ---- multi-head latent attention (DeepSeek-V2/V3, Kimi): absorbed form over the latent cache ----------------------
 MLA_SMALL_T = 64      # up to this many tokens the absorbed projections run as CUDA-core kernels (weights read once)
 use_mla_kernels = os.environ.get("EXO_DISABLE_MLA_KERNELS") != "1"
-_mla_tickets: dict[int | None, torch.Tensor] = {}
 
 
 def _mla_dims_ok(kv_lora, rope_dim, dtype) -> bool:
@@ -524,16 +548,11 @@ def mla_paged_attention(q_full, ckv, block_tables, seq_lens, cu_q, scale, kv_lor
         tok_seq = torch.empty(T, dtype=torch.int32, device=q_full.device)
         _chk(lib.exo_token_seq(_ptr(cu_q), _ptr(tok_seq), B, _st()), "token_seq")
         _count()
-    ws = tk = None
-    if ns > 1:
-        ws = _workspace(q_full.device, lib.exo_mla_attn_workspace(T, H, ns))
-        tk = _mla_tickets.get(q_full.device.index)
-        if tk is None or tk.numel() < T * groups:
-            tk = _mla_tickets[q_full.device.index] = torch.zeros(max(T * groups, 1 << 12), dtype=torch.int32, device=q_full.device)
+    ws = _workspace(q_full.device, lib.exo_mla_attn_workspace(T, H, ns)) if ns > 1 else None
     _chk(lib.exo_mla_attn_tc(_ptr(q_full), _ptr(ckv), _ptr(block_tables), _ptr(seq_lens), None if decode else _ptr(cu_q),
-                             _ptr(tok_seq), _ptr(out), _ptr(ws), _ptr(tk), float(scale), T, H, kv_lora, rope_dim, nblk,
+                             _ptr(tok_seq), _ptr(out), _ptr(ws), float(scale), T, H, kv_lora, rope_dim, nblk,
                              max_blocks, bs, ns, _st()), "mla_attn_tc")
-    _count()
+    _count(2 if ns > 1 else 1)
     return out
 
 

@@ -60,6 +60,8 @@ _SIGS = {
     "exo_comm_reset": (C.c_int, []),
     "exo_gemm_bf16_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p]),
+    "exo_gemm_fp8w_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                   C.c_int, C.c_void_p]),
     "exo_tp_ll_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
     "exo_tp_ll_reduce_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                         C.c_void_p]),
@@ -175,11 +177,12 @@ class Reduction:
         self.local_rows: torch.Tensor | None = None    # [rows, cols] with only this rank's rows valid (sharded form)
         self.xn: torch.Tensor | None = None
 
-    def _run(self, norm_w, eps: float) -> None:
+    def _run(self, norm_w, eps: float, defer_wait: bool = False) -> None:
         comm = self.comm
         M, H = self.shape
         two = comm.two_shot(M, H)
         sharded = two and norm_w is not None
+        defer_wait = defer_wait and sharded
         res = comm.residual_for(self.residual, M, H, two)
         xn = None
         if two:
@@ -189,7 +192,8 @@ class Reduction:
             h_buf = torch.empty(M, H, dtype=torch.bfloat16, device=comm.device)
             xn = torch.empty_like(h_buf) if norm_w is not None else None
         K._chk(comm.lib.exo_reduce_norm_bf16(K._ptr(res), K._ptr(norm_w), float(eps), h_buf.data_ptr(), K._ptr(xn), M, H,
-                                             self.parity, int(two), int(not sharded), K._st()), "reduce_norm")
+                                             self.parity, int(two), int(not sharded) | (2 if defer_wait else 0), K._st()),
+               "reduce_norm")
         K._count()
         comm.n_collectives += 1
         self.xn = xn
@@ -210,6 +214,14 @@ class Reduction:
 
     def norm_linear(self, norm_w, eps, w, bias=None, swiglu=False):
         if self.pending:
+            M, H = self.shape
+            comm = self.comm
+            if (comm.use_gated_gemm and comm.two_shot(M, H) and isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16
+                    and K.gated_gemm_ok(M, w.shape[0], H, swiglu) and (bias is None or not swiglu)):
+                # all-gather -> GEMM: the reduction kernel does not wait for the other ranks' normalised rows; the
+                # projection's CTAs wait for the owner of their rows, starting with this rank's own
+                self._run(norm_w, eps, defer_wait=True)
+                return K.gemm_bf16(self.xn, w, bias, None, swiglu, gate_parity=self.parity)
             return K.linear(self.norm(norm_w, eps), w, bias, None, None, 0.0, swiglu)
         return K.linear(self.value(), w, bias, None, norm_w, eps, swiglu)
 
@@ -315,6 +327,7 @@ class FusedComm:
         self.n_handovers = 0
         self.use_handover = os.environ.get("EXO_DISABLE_TP_HANDOVER") != "1"
         self.use_reduce_norm = os.environ.get("EXO_DISABLE_REDUCE_NORM") != "1"
+        self.use_gated_gemm = os.environ.get("EXO_DISABLE_GATED_GEMM") != "1"      # A/B: two-shot with its own trailing wait
 
     # ---- arena set-up ----
     def _open_ipc(self, total: int) -> None:
@@ -442,9 +455,31 @@ class FusedComm:
         where the shapes allow it: the next ``norm_linear`` (or ``resolve``) then forms the sum."""
         M, Kd = x.shape
         N = w.shape[0]
+        fp8 = isinstance(w, K.Fp8Weight)
         fits = (self.use_handover and x.dtype == torch.bfloat16 and 0 < M <= LL_ROWS and N % 8 == 0
-                and ((M + 1) & ~1) * N * 4 <= self.layout["ll_slot"]
-                and isinstance(w, torch.Tensor))       # block-scaled fp8 weights take the GEMM + reduction path
+                and ((M + 1) & ~1) * N * 4 <= self.layout["ll_slot"] and (fp8 or isinstance(w, torch.Tensor)))
+        if fits and fp8 and Kd % 8 == 0 and Kd >= 64:
+            # block-scaled fp8 weights: the fp8-weight GEMM's epilogue sends the words (every decode batch size)
+            K.ensure_gemm_init(x.device)
+            parity = self._ll & 1
+            self._ll += 1
+            x = x.contiguous()
+            splits = self.lib.exo_gemm_splits(M, N, Kd)
+            while splits > 1 and splits * M * N > K.GEMM_PARTIAL_FLOATS:
+                splits -= 1
+            kind = 1 if w.kind == "mxfp8" else 2
+            f16 = K.fp8_f16_operands and N * Kd >= K.FP8_F16_MIN_WEIGHTS
+            if f16:
+                x16 = torch.empty(M, Kd, dtype=torch.float16, device=x.device)
+                K._chk(self.lib.exo_bf16_to_f16(K._ptr(x), K._ptr(x16), M * Kd, K._st()), "bf16_to_f16")
+                K._count()
+                x = x16
+            K._chk(self.lib.exo_gemm_fp8w_tp(x.data_ptr(), K._ptr(w.to_tiled().tiles), kind, None, M, N, Kd, splits, parity,
+                                             int(f16), K._st()), "gemm_fp8w_tp push")
+            K._count()
+            self.n_handovers += 1
+            return Handover(self, parity, resolve(residual), M, N)
+        fits = fits and not fp8
         if fits and M <= 2 and K.use_stream_gemv and self.lib.exo_gemv_stream_supported(M, N, Kd, 1):
             # (1: rows leave in pairs, like the gate/up form)
             K.ensure_stream_init(x.device)

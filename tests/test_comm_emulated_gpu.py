@@ -257,3 +257,53 @@ def test_gemm_epilogue_handover_and_reduce_norm_kernel(M, Kr):
             assert (xn.float() - want_x).abs().max() <= 0.02 * want_x.abs().max()
     K.check_status()
     lib.exo_comm_reset()
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_gated_gemm_consumes_rows_of_a_deferred_two_shot_reduction(swiglu):
+    """All-gather -> GEMM: the reduction kernel leaves without waiting for the peer's rows; the projection's CTAs wait
+    for the flag of the rank that owns their rows.  Here the peer's rows and its flag are put in place by hand."""
+    from exo_b200.ops import reference as ref
+    rows, cols, N = 1024, 4096, 2048
+    lib, K, L, (A, B) = _setup(2, 0, 1024, cols)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    st = torch.cuda.current_stream().cuda_stream
+    xa = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+    xb = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+    res = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+    nw = (1 + 0.1 * torch.randn(cols, device="cuda", generator=g)).bfloat16()
+    w = (torch.randn(N, cols, device="cuda", generator=g) / 64).bfloat16()
+    want_h, want_x = _ref([xa, xb], res, nw, 1e-5)
+    parity, mine = 1, rows // 2
+    _region(A, L, 0, parity, rows, cols).copy_(xa)
+    _region(B, L, 0, parity, rows, cols).copy_(xb)
+    _flags(A)[BAR_IN + parity * 8 + 1] = 1
+    h_priv = torch.zeros(rows, cols, dtype=torch.bfloat16, device="cuda")
+    # mode 2: residual stream sharded (bit 0 clear), no trailing wait (bit 1 set)
+    assert lib.exo_reduce_norm_bf16(res.data_ptr(), nw.data_ptr(), 1e-5, h_priv.data_ptr(), None, rows, cols, parity, 1, 2, st) == 0
+    torch.cuda.synchronize()
+    xn = _region(A, L, 2, parity, rows, cols)
+    assert int(_flags(A)[BAR_OUT + parity * 8 + 0].item()) == 1          # our rows are flagged; the flag stays up for the GEMM
+    assert float(xn[mine:].float().abs().max()) == 0.0                    # the peer's rows have not arrived
+    xn[mine:].copy_(want_x[mine:])                                        # ... now they have
+    _flags(A)[BAR_OUT + parity * 8 + 1] = 1
+    got = K.gemm_bf16(xn, w, None, None, swiglu, gate_parity=parity)
+    torch.cuda.synchronize()
+    K.check_status()
+    full = torch.cat((xn[:mine], want_x[mine:]))
+    want = ref.linear(full.float(), w.float())
+    if swiglu:
+        want = ref.swiglu(want.bfloat16().float())
+    assert (got.float() - want).abs().max() <= 0.03 * want.abs().max()
+    # a peer that never delivers: the gated GEMM gives up within the budget and says so
+    lib.exo_set_collective_timeout_us(20000)
+    try:
+        _flags(A)[BAR_OUT + parity * 8 + 1] = 0
+        K.gemm_bf16(xn, w, None, None, swiglu, gate_parity=parity)
+        torch.cuda.synchronize()
+        assert lib.exo_comm_status() == 4
+        K.gemm_check() if False else None
+        lib.exo_gemm_last_error()                                         # the MMA warp's own wait ran out too: clear it
+    finally:
+        lib.exo_set_collective_timeout_us(2000000)
+        lib.exo_comm_reset()
