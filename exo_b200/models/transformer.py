@@ -35,6 +35,9 @@ class LocalComm:
     def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         return x if residual is None else x + residual
 
+    def row_sum(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        return self.all_reduce(x, residual)
+
     def gather_vocab(self, logits_local: torch.Tensor) -> torch.Tensor:
         return logits_local
 
@@ -178,7 +181,7 @@ class Decoder:
         y = ops.moe_experts(x, lw.e_gate_up, lw.e_down, wts, ids, elo, cfg.n_experts)
         if lw.s_gate_up is not None:
             y = ops.linear(ops.linear(x, lw.s_gate_up, swiglu=True), lw.s_down, residual=y)
-        return self.comm.all_reduce(y, h)
+        return self.comm.row_sum(y, h)      # may stay pending: the next layer's norm is fused into the reduction
 
     # ------------------------------------------------------------------ forward
     def forward(self, inp: StepInputs, kv: KVPool, hidden_in: torch.Tensor | None = None):

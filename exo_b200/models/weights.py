@@ -129,10 +129,21 @@ class RandomSource(TensorSource):
 
 
 class SafetensorsSource(TensorSource):
-    """Lazy reader of a HF checkpoint directory (memory-mapped, one tensor at a time)."""
+    """Lazy reader of a HF checkpoint directory (memory-mapped, one tensor at a time).
+
+    Pre-quantised checkpoints are dequantised tensor by tensor as they are read (the serving quantisation is then
+    applied to the result after sharding, ``quantize_layer``), so the cards that name such repositories load:
+
+    * FP8 block-scaled (DeepSeek-V3 style): ``X.weight`` in e4m3 with ``X.weight_scale_inv`` fp32 ``[N/128, K/128]``;
+    * FP8 per-tensor / per-channel (compressed-tensors style): ``X.weight`` in e4m3 with ``X.weight_scale``;
+    * MLX affine groups (the mlx-community ``*-4bit`` / ``*-8bit`` repositories the reference loads with
+      ``mlx_lm.utils.load_model``, ``src/exo/worker/engines/mlx/utils_mlx.py:163-286``): ``X.weight`` packed in uint32,
+      ``X.scales`` / ``X.biases`` per group of ``group_size`` input features, ``bits`` and ``group_size`` from the
+      ``quantization`` entry of ``config.json`` (with per-module overrides).
+    """
 
     _ST = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "F8_E4M3": torch.float8_e4m3fn,
-           "I32": torch.int32, "I64": torch.int64, "U8": torch.uint8, "I8": torch.int8}
+           "I32": torch.int32, "I64": torch.int64, "U8": torch.uint8, "I8": torch.int8, "U32": torch.int32}
 
     def __init__(self, path: str | Path, device: str | torch.device = "cpu", dtype: torch.dtype = torch.bfloat16):
         self.path, self.device, self.dtype = Path(path), torch.device(device), dtype
@@ -149,6 +160,14 @@ class SafetensorsSource(TensorSource):
                     continue
                 b, e = v["data_offsets"]
                 self.index[k] = (f, v["dtype"], tuple(v["shape"]), 8 + n + b, e - b)
+        self.quant: dict = {}
+        cfg_file = self.path / "config.json"
+        if cfg_file.exists():
+            try:
+                c = json.loads(cfg_file.read_text())
+                self.quant = c.get("quantization") or c.get("quantization_config") or {}
+            except (OSError, ValueError):
+                self.quant = {}
 
     def has(self, name: str) -> bool:
         return name in self.index
@@ -156,13 +175,61 @@ class SafetensorsSource(TensorSource):
     def names(self) -> Iterator[str]:
         return iter(self.index)
 
-    def get(self, name: str, shape: tuple[int, ...] | None = None) -> torch.Tensor:
+    def _raw(self, name: str) -> torch.Tensor:
         f, dt, shp, off, nbytes = self.index[name]
         import numpy as np
         raw = np.memmap(f, dtype=np.uint8, mode="r", offset=off, shape=(nbytes,))
-        t = torch.frombuffer(bytearray(raw), dtype=self._ST[dt]).view(shp)
-        if shape is not None and tuple(shape) != tuple(shp):
-            raise ValueError(f"{name}: checkpoint shape {shp} != expected {shape}")
+        return torch.frombuffer(bytearray(raw), dtype=self._ST[dt]).view(shp)
+
+    def _mlx_params(self, module: str) -> tuple[int, int]:
+        """(bits, group_size) of an MLX-quantised module: the per-module entry wins over the global one."""
+        q = self.quant
+        over = q.get(module) if isinstance(q.get(module), dict) else None
+        bits = int((over or q).get("bits", 4))
+        group = int((over or q).get("group_size", 64))
+        return bits, group
+
+    def stored_format(self, name: str) -> str:
+        """How ``name`` is stored: ``plain``, ``fp8_block``, ``fp8_scale`` or ``mlx_affine``."""
+        if name.endswith(".weight"):
+            stem = name[:-len(".weight")]
+            dt = self.index[name][1]
+            if dt == "F8_E4M3" and stem + ".weight_scale_inv" in self.index:
+                return "fp8_block"
+            if dt == "F8_E4M3" and stem + ".weight_scale" in self.index:
+                return "fp8_scale"
+            if dt == "U32" and stem + ".scales" in self.index:
+                return "mlx_affine"
+        return "plain"
+
+    def get(self, name: str, shape: tuple[int, ...] | None = None) -> torch.Tensor:
+        t = self._raw(name)
+        fmt = self.stored_format(name)
+        if fmt != "plain":
+            stem = name[:-len(".weight")]
+            if fmt == "fp8_block":
+                sc = self._raw(stem + ".weight_scale_inv").float()
+                n_out, n_in = t.shape
+                blk = self.quant.get("weight_block_size") or [128, 128]       # DeepSeek-V3: 128 x 128 blocks
+                bn, bk = int(blk[0]), int(blk[1])
+                if -(-n_out // bn) != sc.shape[0] or -(-n_in // bk) != sc.shape[1]:
+                    raise ValueError(f"{name}: scale grid {tuple(sc.shape)} does not match {bn} x {bk} blocks of {tuple(t.shape)}")
+                t = t.float() * sc.repeat_interleave(bn, 0)[:n_out].repeat_interleave(bk, 1)[:, :n_in]
+            elif fmt == "fp8_scale":
+                sc = self._raw(stem + ".weight_scale").float()
+                t = t.float() * (sc.reshape(-1, 1) if sc.numel() > 1 else sc.reshape(1, 1))
+            else:
+                bits, group = self._mlx_params(stem)
+                if 32 % bits:
+                    raise ValueError(f"{name}: {bits}-bit MLX packing is not supported (4- and 8-bit repositories are)")
+                per = 32 // bits
+                packed = t.to(torch.int64) & 0xFFFFFFFF                               # uint32 words
+                shifts = torch.arange(per, dtype=torch.int64) * bits
+                q = ((packed.unsqueeze(-1) >> shifts) & ((1 << bits) - 1)).reshape(*t.shape[:-1], t.shape[-1] * per)
+                scales, biases = self._raw(stem + ".scales").float(), self._raw(stem + ".biases").float()
+                t = q.float() * scales.repeat_interleave(group, -1) + biases.repeat_interleave(group, -1)
+        if shape is not None and tuple(shape) != tuple(t.shape):
+            raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} != expected {shape}")
         if t.is_floating_point():
             t = t.to(self.dtype)
         return t.to(self.device)
@@ -171,11 +238,12 @@ class SafetensorsSource(TensorSource):
 def write_safetensors(path: str | Path, tensors: dict[str, torch.Tensor]) -> None:
     """Minimal safetensors writer (used by tests and by the fp8 re-pack cache)."""
     names = {torch.bfloat16: "BF16", torch.float16: "F16", torch.float32: "F32", torch.int32: "I32",
-             torch.int64: "I64", torch.uint8: "U8", torch.int8: "I8", torch.float8_e4m3fn: "F8_E4M3"}
+             torch.int64: "I64", torch.uint8: "U8", torch.int8: "I8", torch.float8_e4m3fn: "F8_E4M3",
+             torch.uint32: "U32"}
     header, blobs, off = {}, [], 0
     for k, t in tensors.items():
         t = t.contiguous().cpu()
-        b = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        b = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[k] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
         blobs.append(b)
         off += len(b)

@@ -755,6 +755,18 @@ ll_reduce_norm_kernel(const TpHandover h, const __nv_bfloat16* __restrict__ norm
   }
 }
 
+
+// Producer of a flag-in-data hand-over for a tensor that some other kernel computed (the combined expert outputs of
+// a MoE layer): reads y [rows, cols] bf16 and sends it to every rank's slot as (two values, sequence number) words.
+__global__ void __launch_bounds__(256) ll_push_kernel(const TpHandover h, const __nv_bfloat16* __restrict__ y, size_t n_words) {
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t seq = (uint32_t)(*reinterpret_cast<volatile const int*>(h.ll_epoch) + 1);
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(y);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += (size_t)gridDim.x * blockDim.x)
+    tp_ll_store(h, i, src[i], seq);
+}
+
 }  // namespace
 
 int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems) {
@@ -784,6 +796,24 @@ int exo_tp_handover_fill(TpHandover* out, int mode, int parity, long n_elems) {
   return -2;
 }
 
+
+
+// Sends y [rows, cols] bf16 (rows * cols even) to every rank as the hand-over of `parity`; consumed like a
+// projection's own hand-over (exo_tp_ll_reduce_norm / exo_tp_ll_finish / the streaming GEMV's prologue).
+EXO_API int exo_tp_ll_push(const void* y, int rows, int cols, int parity, cudaStream_t st) {
+  const long n = (long)rows * cols;
+  if (n <= 0 || (n & 1)) return -2;
+  TpHandover h;
+  int rc = exo_tp_handover_fill(&h, 3, parity, n);
+  if (rc) return rc;
+  const size_t n_words = (size_t)n / 2;
+  int grid = (int)((n_words + 255) / 256);
+  if (grid > 148) grid = 148;
+  cudaError_t e = launch_pdl(ll_push_kernel, dim3(grid), dim3(256), 0, st, h, (const __nv_bfloat16*)y, n_words);
+  if (e != cudaSuccess) return (int)e;
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
 
 // h_out = residual + sum over ranks of the flag-in-data hand-over on `parity`; x_out = RMSNorm(h_out) * norm_w
 // (norm_w null: h_out only).  [rows, cols] bf16, cols % 8 == 0, cols <= 8192.

@@ -43,6 +43,9 @@ class DistComm:
     def row_linear(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         return self.all_reduce(ops.linear(x, w), residual)
 
+    def row_sum(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        return self.all_reduce(x, residual)
+
     def gather_vocab(self, logits_local: torch.Tensor) -> torch.Tensor:
         logits_local = logits_local.contiguous()
         parts = [torch.empty_like(logits_local) for _ in range(self.size)]

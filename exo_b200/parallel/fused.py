@@ -63,6 +63,7 @@ _SIGS = {
     "exo_gemm_fp8w_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_int, C.c_void_p]),
     "exo_tp_ll_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p]),
+    "exo_tp_ll_push": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "exo_tp_ll_reduce_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                         C.c_void_p]),
     "exo_gemv_stream_tp": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
@@ -423,14 +424,35 @@ class FusedComm:
         return self.region(0, parity, rows, cols), parity
 
     # ---- collectives ----
-    def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
-        """``residual + sum over ranks of x`` (bf16)."""
+    def row_sum(self, x: torch.Tensor, residual=None):
+        """``residual + sum over ranks of x`` as a pending :class:`Handover` / :class:`Reduction` (or a tensor when
+        the shape takes neither): the consumer's norm is then fused into the same kernel.  ``x`` was computed by some
+        other kernel (the combined expert outputs of a MoE layer); decode batches go out as flag-in-data words."""
         if x.dtype != torch.bfloat16 or x.numel() % 8:
             raise K.KernelError("fused all-reduce takes bf16 tensors whose size is a multiple of 8")
-        if x.dim() == 2 and self.fits(x.shape[0], x.shape[1]):
-            buf, parity = self.partial_out(x.shape[0], x.shape[1])
-            buf.copy_(x)
-            return Reduction(self, parity, residual, x.shape[0], x.shape[1]).value()
+        if x.dim() == 2:
+            M, N = x.shape
+            if (self.use_handover and 0 < M <= LL_ROWS and N % 8 == 0 and N <= 8192
+                    and ((M + 1) & ~1) * N * 4 <= self.layout["ll_slot"]):
+                x = x.contiguous()
+                parity = self._ll & 1
+                self._ll += 1
+                K._chk(self.lib.exo_tp_ll_push(x.data_ptr(), M, N, parity, K._st()), "ll push")
+                K._count()
+                self.n_handovers += 1
+                return Handover(self, parity, resolve(residual), M, N)
+            if self.fits(M, N):
+                buf, parity = self.partial_out(M, N)
+                buf.copy_(x)
+                return Reduction(self, parity, residual, M, N)
+        return self._all_reduce_slots(x, residual)
+
+    def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``residual + sum over ranks of x`` (bf16)."""
+        return resolve(self.row_sum(x, residual))
+
+    def _all_reduce_slots(self, x: torch.Tensor, residual=None) -> torch.Tensor:
+        """Shapes the hand-over and the reduce + norm kernels do not take: the push-style kernels over staging slots."""
         residual = resolve(residual)
         x = x.contiguous()
         if x.numel() > self.max_elems:
@@ -438,7 +460,7 @@ class FusedComm:
             if x.dim() != 2 or x.shape[1] > self.max_elems:
                 raise K.KernelError(f"tensor of {x.numel()} elements exceeds the arena slot ({self.max_elems})")
             rows = max(8, (self.max_elems // x.shape[1]) // 8 * 8)
-            parts = [self.all_reduce(x[r:r + rows], None if residual is None else residual[r:r + rows])
+            parts = [self._all_reduce_slots(x[r:r + rows], None if residual is None else residual[r:r + rows])
                      for r in range(0, x.shape[0], rows)]
             return torch.cat(parts, dim=0)
         out = torch.empty_like(x)

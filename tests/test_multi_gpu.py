@@ -292,3 +292,73 @@ def test_tp2_decode_with_handover_reproduces_the_all_reduce_tokens():
     off = _run(_engine_handover, 2, False)
     assert on[0][1][0] == on[1][1][0] == off[0][1][0] and len(on[0][1][0]) == 24
     assert on[0][1][1] > 0 and off[0][1][1] == 0          # the decode steps really went through the hand-over
+
+
+def _family_cfg(name):
+    from exo_b200.models.config import ModelConfig, RopeConfig
+    if name == "llama":
+        return ModelConfig(name="t-llama", n_layers=2, hidden=1024, n_heads=8, n_kv_heads=8, head_dim=128, ffn=2048, vocab=4096,
+                           rope=RopeConfig(theta=500000.0), dtype="bf16")
+    if name == "kv-replicated":        # 2 KV heads on up to 8 ranks: every KV head lives on several ranks
+        return ModelConfig(name="t-kvrep", n_layers=2, hidden=1024, n_heads=8, n_kv_heads=2, head_dim=128, ffn=2048, vocab=4096,
+                           rope=RopeConfig(theta=500000.0), dtype="bf16")
+    if name == "mxfp8":
+        return ModelConfig(name="t-fp8", n_layers=2, hidden=1024, n_heads=8, n_kv_heads=8, head_dim=128, ffn=2048, vocab=4096,
+                           rope=RopeConfig(theta=500000.0), dtype="bf16", quant="mxfp8")
+    if name == "moe":
+        return ModelConfig(name="t-moe", family="qwen3_moe", n_layers=2, hidden=1024, n_heads=8, n_kv_heads=8, head_dim=128,
+                           ffn=2048, vocab=4096, qk_norm=True, n_experts=16, n_experts_per_tok=2, moe_ffn=512,
+                           router="softmax", dtype="bf16")
+    if name == "mla":
+        return ModelConfig(name="t-mla", family="deepseek_v3", n_layers=2, hidden=1024, n_heads=16, n_kv_heads=16, head_dim=192,
+                           ffn=2048, vocab=4096, mla=True, q_lora_rank=256, kv_lora_rank=512, qk_nope_dim=128, qk_rope_dim=64,
+                           v_head_dim=128, n_experts=16, n_experts_per_tok=2, moe_ffn=512, n_shared_experts=1,
+                           first_dense_layers=1, router="sigmoid", routed_scaling=1.5, n_group=2, topk_group=1,
+                           router_bias=True, dtype="bf16")
+    raise KeyError(name)
+
+
+def _family_engine(rank, world, name):
+    """Prefill of two prompts and a few decode steps (eager prefill, graph decode) of one model family under TP."""
+    from exo_b200.engine.engine import Engine
+    from exo_b200.engine.kv import SamplingParams
+    from exo_b200.models.oracle import oracle_prompt
+    from exo_b200.models.weights import RandomSource, ShardSpec, build_weights, vocab_shard
+    dev = torch.device("cuda", rank)
+    cfg = _family_cfg(name)
+    spec = ShardSpec(tp_rank=rank, tp_size=world)
+    w = build_weights(cfg, spec, RandomSource(seed=0, std=0.05, dtype=torch.bfloat16), device=dev)
+    comm = None
+    if world > 1:
+        from exo_b200.parallel.fused import FusedComm
+        comm = FusedComm(dev, max_rows=512, hidden=cfg.hidden, vocab_shard=vocab_shard(cfg.vocab, world))
+    eng = Engine(cfg, w, spec, comm, n_blocks=128, device=dev, max_seqs=4)
+    prompts = [oracle_prompt(n, cfg.vocab, seed=n).tolist() for n in (300, 37)]       # 300 rows: a two-shot prefill at 8 ranks
+    ids = [eng.submit(p, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True), use_prefix_cache=False) for p in prompts]
+    got = {i: [] for i in ids}
+    first = None
+    while eng.has_work:
+        outs = eng.step()
+        if first is None:
+            first = eng.exe.last_logits.float().cpu()
+        for o in outs:
+            if o.token is not None:
+                got[o.req_id].append(o.token)
+    if comm is not None:
+        comm.check()
+        comm.close()
+    return [got[i] for i in ids], first
+
+
+@pytest.mark.parametrize("name", ["llama", "kv-replicated", "mxfp8", "moe", "mla"])
+@pytest.mark.parametrize("world", [pytest.param(w, marks=needs(w)) for w in WORLDS])
+def test_model_families_under_tensor_parallelism_track_the_single_gpu_run(world, name):
+    """Every rank of a TP run produces the same tokens, and the first step's logits stay within bf16 rounding of the
+    single-GPU engine on the same weights (heads, KV-head replication, experts, fp8 weights, latent attention)."""
+    one = _run(_family_engine, 1, name)
+    many = _run(_family_engine, world, name)
+    toks = [r[1][0] for r in many]
+    assert all(t == toks[0] for t in toks), "ranks disagree on the generated tokens"
+    assert all(len(t) == 8 for t in toks[0])
+    a, b = many[0][1][1], one[0][1][1]
+    assert (a - b).abs().max() < 0.08 * b.abs().max() + 0.08, float((a - b).abs().max())
