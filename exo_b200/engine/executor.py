@@ -208,5 +208,7 @@ class Executor:
             # the step's kernels have completed: an expired device-side wait (a peer that stopped answering, a stuck
             # pipeline) must end the runner instead of streaming tokens made from unsummed data
             ops.cuda_ops().check_status(self.device)
+            if ops.cuda_ops().CHECKS:
+                ops.cuda_ops().verify_guards()
         self.d2h_bytes += n * 4
         return self.out_host[:n].numpy().copy()

@@ -607,6 +607,7 @@ EXO_API int exo_mla_kv_append(const void* kva, const void* norm_w, float eps, co
                               cudaStream_t st) {
   if (T <= 0) return 0;
   if (kv_lora != LAT || rope_dim != ROPE) return -2;
+  EXO_REQUIRE_ALIGNED16(kva); EXO_REQUIRE_ALIGNED16(norm_w); EXO_REQUIRE_ALIGNED16(cache);
   cudaError_t e = launch_pdl(mla_kv_append_kernel, dim3(T), dim3(128), 0, st, (const __nv_bfloat16*)kva,
                              (const __nv_bfloat16*)norm_w, eps, positions, inv_freq, mscale, (__nv_bfloat16*)cache, slots, T);
   if (e != cudaSuccess) return (int)e;
@@ -633,6 +634,7 @@ EXO_API int exo_mla_o_absorb(const void* o_lat, const void* w_uv, void* out, int
                              cudaStream_t st) {
   if (T <= 0) return 0;
   if (v_dim != 128 || kv_lora != LAT) return -2;
+  EXO_REQUIRE_ALIGNED16(o_lat); EXO_REQUIRE_ALIGNED16(w_uv);
   cudaError_t e = launch_pdl(mla_o_absorb_kernel, dim3(H, 16), dim3(256), 0, st, (const __nv_bfloat16*)o_lat,
                              (const __nv_bfloat16*)w_uv, (__nv_bfloat16*)out, T, H);
   if (e != cudaSuccess) return (int)e;

@@ -32,6 +32,7 @@ constexpr int MAX_RANKS = 8;
 constexpr size_t HDR_BYTES = 4096;
 constexpr size_t BAR_IN = 2048, BAR_OUT = 2112, BAR_TICKET = 2176, BAR_GATHER = 2240;   // tickets: int32 [3]; gather flags [8]
 constexpr size_t LL_EPOCH = 2304, LL_TICKET = 2368;   // flag-in-data hand-over: int32 [2 parities] each
+constexpr size_t RN_EPOCH = 2432;                     // two-shot reductions completed per parity: int32 [2]
 
 struct CommCtx {
   uint8_t* arena[MAX_RANKS];  // arena[r] = base of rank r's arena as mapped in this process
@@ -250,6 +251,31 @@ __device__ __forceinline__ void multimem_st16(void* mc_addr, const uint4& v) {
                ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait of the whole CTA until every rank's flag (base, parity) has reached `need` (wrap-safe comparison).
+__device__ bool wait_ranks_ge(const CommCtx& c, size_t base, int parity, int need) {
+  __shared__ int ok_g;
+  if (threadIdx.x == 0) ok_g = 1;
+  __syncthreads();
+  if (threadIdx.x < c.n) {
+    const int* f = bar_ptr(c.arena[c.rank], base, parity, threadIdx.x);
+    const unsigned long long t0 = gtime();
+    while (ld_acquire_sys(f) - need < 0) {
+      if (gtime() - t0 > c.wait_ns) {
+        ok_g = 0;
+        atomicExch(c.status, 4 /* peer timeout */);
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  __syncthreads();
+  return ok_g != 0;
+}
+
 // Bounded wait of the whole CTA until every rank has raised flag (base, parity) at least once.
 __device__ bool wait_ranks(const CommCtx& c, size_t base, int parity) {
   __shared__ int ok_w;
@@ -290,9 +316,6 @@ reduce_norm_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ residual, 
   __shared__ int last_s;
   const bool bcast_h = mode & 1, defer_wait = mode & 2;
   if (blockIdx.x == 0 && threadIdx.x < c.n) {
-    // a deferred-wait collective of this parity left its "rows broadcast" flags up for the GEMM that consumed them:
-    // clear them before anybody can be told to start this one
-    if (TWO) *bar_ptr(c.arena[c.rank], BAR_OUT, parity, threadIdx.x) = 0;
     __threadfence_system();   // the partial was written by earlier kernels of this stream: publish it system-wide
     red_release_sys_add(bar_ptr(c.arena[threadIdx.x], BAR_IN, parity, c.rank), 1);
   }
@@ -393,15 +416,23 @@ reduce_norm_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ residual, 
   __syncthreads();
   if (!last_s) return;
   if (TWO) {
+    // "rows broadcast" flags carry the number of the two-shot reduction on this parity (never reset): rank j's rows of
+    // reduction e are complete once flag[j] >= e.  Every rank performs the same sequence, so the numbers agree.
+    int* ep = reinterpret_cast<int*>(c.arena[c.rank] + RN_EPOCH) + parity;
+    const int epoch = *reinterpret_cast<volatile int*>(ep) + 1;
     __threadfence_system();
-    if (threadIdx.x < c.n) red_release_sys_add(bar_ptr(c.arena[threadIdx.x], BAR_OUT, parity, c.rank), 1);
+    if (threadIdx.x < c.n) st_release_sys(bar_ptr(c.arena[threadIdx.x], BAR_OUT, parity, c.rank), epoch);
     // deferred: the consumer (a GEMM that waits for each owner's flag before it loads that owner's rows) does the
     // waiting, tile by tile, so its first tiles run while the last rows are still on their way
-    if (!defer_wait) wait_ranks(c, BAR_OUT, parity);
+    if (!defer_wait) wait_ranks_ge(c, BAR_OUT, parity, epoch);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *reinterpret_cast<volatile int*>(ep) = epoch;
+      __threadfence();
+    }
   }
   if (threadIdx.x < c.n) {
     *bar_ptr(c.arena[c.rank], BAR_IN, parity, threadIdx.x) = 0;
-    if (TWO && !defer_wait) *bar_ptr(c.arena[c.rank], BAR_OUT, parity, threadIdx.x) = 0;
     __threadfence_system();
   }
 }
@@ -575,6 +606,7 @@ EXO_API int exo_reduce_norm_bf16(const void* residual, const void* norm_w, float
   c.wait_ns = exo_wait_budget_ns();
   if (rows <= 0 || cols % 8 || cols > 8192) return -2;
   if (!c.x_bytes || (size_t)rows * cols * 2 > c.x_bytes) return -6;
+  EXO_REQUIRE_ALIGNED16(residual); EXO_REQUIRE_ALIGNED16(norm_w); EXO_REQUIRE_ALIGNED16(h_out); EXO_REQUIRE_ALIGNED16(x_out);
   const int bcast_h = mode & 1;
   if ((!two_shot || !bcast_h) && !h_out) return -2;
   if (!two_shot) mode &= 1;
@@ -605,13 +637,15 @@ EXO_API int exo_reduce_norm_bf16(const void* residual, const void* norm_w, float
 }
 
 // What a GEMM needs to consume the rows of a deferred-wait two-shot reduction as they arrive: rank j's rows
-// [j R, (j+1) R), R = ceil(rows / n), are complete once flags[j] >= 1.  Returns 0, or <0 without a communicator.
-int exo_comm_gate(int parity, int rows, const int** flags, int* rows_per_flag, int* rank, unsigned long long* wait_ns,
-                  int** status) {
+// [j R, (j+1) R), R = ceil(rows / n), are complete once flags[j] >= *epoch (the reduction kernel, which precedes the
+// GEMM in the stream, has advanced the epoch word by then).  Returns 0, or <0 without a communicator.
+int exo_comm_gate(int parity, int rows, const int** flags, const int** epoch, int* rows_per_flag, int* rank,
+                  unsigned long long* wait_ns, int** status) {
   int dev;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || !g_ctx_set[dev]) return -4;
   const CommCtx& c = g_ctx[dev];
   *flags = reinterpret_cast<const int*>(c.arena[c.rank] + BAR_OUT) + (parity & 1) * MAX_RANKS;
+  *epoch = reinterpret_cast<const int*>(c.arena[c.rank] + RN_EPOCH) + (parity & 1);
   *rows_per_flag = (rows + c.n - 1) / c.n;
   *rank = c.rank;
   *wait_ns = exo_wait_budget_ns();
@@ -629,6 +663,7 @@ EXO_API int exo_gather_rows_bf16(const void* src, int rows, int cols, int parity
   c.wait_ns = exo_wait_budget_ns();
   if (rows <= 0 || cols % 8) return -2;
   if (!c.x_bytes || (size_t)rows * cols * 2 > c.x_bytes) return -6;
+  EXO_REQUIRE_ALIGNED16(src);
   const size_t vecs = (size_t)((rows + c.n - 1) / c.n) * cols / 8;
   int grid = (int)((vecs + RN_THREADS - 1) / RN_THREADS);
   if (grid > 148) grid = 148;
@@ -820,6 +855,7 @@ EXO_API int exo_tp_ll_push(const void* y, int rows, int cols, int parity, cudaSt
 EXO_API int exo_tp_ll_reduce_norm(const void* residual, const void* norm_w, float eps, void* h_out, void* x_out, int rows,
                                   int cols, int parity, cudaStream_t st) {
   if (cols % 8 || cols > 8192 || rows <= 0 || !h_out || (norm_w && !x_out)) return -2;
+  EXO_REQUIRE_ALIGNED16(residual); EXO_REQUIRE_ALIGNED16(norm_w); EXO_REQUIRE_ALIGNED16(h_out); EXO_REQUIRE_ALIGNED16(x_out);
   TpHandover h;
   int rc = exo_tp_handover_fill(&h, 4, parity, (long)((rows + 1) & ~1) * cols);
   if (rc) return rc;
@@ -840,6 +876,7 @@ EXO_API int exo_tp_ll_reduce_norm(const void* residual, const void* norm_w, floa
 // out = residual + sum over ranks of the flag-in-data hand-over on `parity` (n_elems multiple of 8).
 EXO_API int exo_tp_ll_finish(const void* residual, void* out, long n_elems, int parity, cudaStream_t st) {
   if (n_elems % 8) return -2;
+  EXO_REQUIRE_ALIGNED16(residual); EXO_REQUIRE_ALIGNED16(out);
   TpHandover h;
   int rc = exo_tp_handover_fill(&h, 4, parity, n_elems);
   if (rc) return rc;

@@ -9,11 +9,33 @@
 // dtype codes used by every launcher
 enum { EXO_BF16 = 0, EXO_F32 = 1 };
 
+// Built with -DEXO_KERNEL_CHECKS=1 (EXO_KERNEL_CHECKS=1 python -m exo_b200.build) every launcher waits for its kernel
+// and reports an execution error as ITS return code, so a fault is attributed to the launch that made it instead
+// of surfacing at some later call; launchers of vectorised kernels also refuse pointers that are not 16-byte
+// aligned.  (Not for graph capture: the synchronisation is illegal there.)
+#ifdef EXO_KERNEL_CHECKS
+#define EXO_CHECK_LAUNCH()                                                        \
+  do {                                                                            \
+    cudaError_t e__ = cudaGetLastError();                                         \
+    if (e__ != cudaSuccess) return (int)e__;                                      \
+    cudaStreamCaptureStatus cs__ = cudaStreamCaptureStatusNone;                   \
+    if (cudaStreamIsCapturing(0, &cs__) == cudaSuccess && cs__ == cudaStreamCaptureStatusNone) { \
+      e__ = cudaDeviceSynchronize();                                              \
+      if (e__ != cudaSuccess) return (int)e__;                                    \
+    }                                                                             \
+  } while (0)
+#define EXO_REQUIRE_ALIGNED16(p)                                                  \
+  do {                                                                            \
+    if ((p) && (reinterpret_cast<uintptr_t>(p) & 15)) return -8;                  \
+  } while (0)
+#else
 #define EXO_CHECK_LAUNCH()                         \
   do {                                             \
     cudaError_t e__ = cudaGetLastError();          \
     if (e__ != cudaSuccess) return (int)e__;       \
   } while (0)
+#define EXO_REQUIRE_ALIGNED16(p) do { } while (0)
+#endif
 
 template <typename T> struct Cvt;
 template <> struct Cvt<float> {

@@ -23,7 +23,8 @@ struct GemmParams {
   int* err;               // device error word
   TpHandover ho;          // row-parallel output handed to every rank (n_ll > 0): `out` is then not written
   // all-gather -> GEMM: the activation rows arrive from the other ranks while the kernel runs (null: plain GEMM)
-  const int* row_flags;   // row_flags[j] >= 1 once rows [j * rows_per_flag, (j + 1) * rows_per_flag) have landed
+  const int* row_flags;   // row_flags[j] >= *row_epoch once rows [j * rows_per_flag, (j + 1) * rows_per_flag) have landed
+  const int* row_epoch;   // number of the reduction that produced these rows (device word, read when the kernel runs)
   int rows_per_flag;
   int m_tile_shift;       // row tiles are walked starting at this rank's own rows, which are there first
   unsigned long long gate_wait_ns;

@@ -415,7 +415,7 @@ static int gemm_fp8w_impl(const void* x, const void* tiles, int scale_kind, cons
   p.out = (__nv_bfloat16*)out;
   p.ldo = ldo;
   if (ho) p.ho = *ho; else memset(&p.ho, 0, sizeof(p.ho));
-  p.row_flags = nullptr; p.rows_per_flag = 1; p.m_tile_shift = 0; p.gate_wait_ns = 0; p.gate_status = nullptr;
+  p.row_flags = nullptr; p.row_epoch = nullptr; p.rows_per_flag = 1; p.m_tile_shift = 0; p.gate_wait_ns = 0; p.gate_status = nullptr;
   if (splits > 1) {
     const long tiles = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     if ((size_t)splits * M * N > partial_floats || tiles > (1 << 16)) return -6;

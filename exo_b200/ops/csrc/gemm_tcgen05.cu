@@ -87,8 +87,9 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const int o_lo = m0 / p.rows_per_flag, o_hi = (min(p.M, m0 + BN) - 1) / p.rows_per_flag;
         unsigned long long t0;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+        const int need = *reinterpret_cast<const volatile int*>(p.row_epoch);
         for (int o = o_lo; o <= o_hi && gate_ok; o++) {
-          while (tp_ld_acquire_sys(p.row_flags + o) < 1) {
+          while (tp_ld_acquire_sys(p.row_flags + o) - need < 0) {
             unsigned long long now;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
             if (now - t0 > p.gate_wait_ns) {
@@ -356,14 +357,14 @@ EXO_API int exo_gemm_bf16(const void* x, const void* W, const void* bias, const 
   return gemm_launch(x, W, bias, residual, out, M, N, K, ldo, splits, nullptr, st);
 }
 
-int exo_comm_gate(int parity, int rows, const int** flags, int* rows_per_flag, int* rank, unsigned long long* wait_ns,
-                  int** status);
+int exo_comm_gate(int parity, int rows, const int** flags, const int** epoch, int* rows_per_flag, int* rank,
+                  unsigned long long* wait_ns, int** status);
 
 // Fills the all-gather -> GEMM fields of `p`: the rows of `x` are the broadcast output of the deferred-wait two-shot
 // reduction on `parity` (see comm.cu); the row tiles are walked starting at this rank's own rows.
 static int gate_params(GemmParams* p, int parity, int M, int bn) {
   int rank = 0;
-  int rc = exo_comm_gate(parity, M, &p->row_flags, &p->rows_per_flag, &rank, &p->gate_wait_ns, &p->gate_status);
+  int rc = exo_comm_gate(parity, M, &p->row_flags, &p->row_epoch, &p->rows_per_flag, &rank, &p->gate_wait_ns, &p->gate_status);
   if (rc) return rc;
   p->m_tile_shift = (rank * p->rows_per_flag) / bn;
   return 0;
@@ -456,7 +457,7 @@ static int gemm_launch(const void* x, const void* W, const void* bias, const voi
   p.counters = g_counters[dev];
   p.err = g_err[dev];
   if (ho) p.ho = *ho; else memset(&p.ho, 0, sizeof(p.ho));
-  p.row_flags = nullptr; p.rows_per_flag = 1; p.m_tile_shift = 0; p.gate_wait_ns = 0; p.gate_status = nullptr;
+  p.row_flags = nullptr; p.row_epoch = nullptr; p.rows_per_flag = 1; p.m_tile_shift = 0; p.gate_wait_ns = 0; p.gate_status = nullptr;
   if (g_gate_parity >= 0) {
     int rc = gate_params(&p, g_gate_parity, M, bn);
     if (rc) return rc;

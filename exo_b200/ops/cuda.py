@@ -112,6 +112,52 @@ def _dt(t: torch.Tensor) -> int:
 
 launch_count = 0  # launches issued through this module (read by the benchmark)
 
+# ---- EXO_KERNEL_CHECKS=1: the stand-in for a memory checker ----------------------------------------------------------
+# Outputs are allocated with a guard band behind them that is filled with a pattern before the launch and verified
+# after it (an out-of-bounds store of a kernel shows up as a broken band, attributed to the op that made it), index
+# tensors that kernels dereference unchecked (KV slots, block tables, token ids) are validated on the host, and the
+# kernel library, when it was built with the same variable set, waits for every kernel and reports its fault as the
+# launcher's return code.  Every check synchronises: this is a debugging flavour, never on in serving or benchmarks.
+CHECKS = os.environ.get("EXO_KERNEL_CHECKS") == "1"
+_GUARD = 256          # guard elements behind every output
+_guards: list[tuple[torch.Tensor, int, str]] = []
+
+
+def _empty(*shape, dtype, device, what: str = "output") -> torch.Tensor:
+    if not CHECKS:
+        return torch.empty(*shape, dtype=dtype, device=device)
+    shape = tuple(shape[0]) if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)) else tuple(shape)
+    n = 1
+    for d in shape:
+        n *= int(d)
+    flat = torch.empty(n + _GUARD, dtype=dtype, device=device)
+    flat[n:].view(torch.uint8).fill_(0xA5)
+    _guards.append((flat, n, what))
+    return flat[:n].view(shape)
+
+
+def _empty_like(x: torch.Tensor, what: str = "output") -> torch.Tensor:
+    return _empty(tuple(x.shape), dtype=x.dtype, device=x.device, what=what) if CHECKS else torch.empty_like(x)
+
+
+def verify_guards() -> None:
+    """Raise if any kernel since the last call wrote behind the end of one of its outputs (checks mode only)."""
+    if not _guards:
+        return
+    torch.cuda.synchronize()
+    bad = [what for flat, n, what in _guards if not bool((flat[n:].view(torch.uint8) == 0xA5).all())]
+    _guards.clear()
+    if bad:
+        raise KernelError(f"guard band behind {bad[0]} was overwritten: a kernel stored out of bounds")
+
+
+def _check_indices(what: str, idx: torch.Tensor, limit: int) -> None:
+    """Checks mode: every entry of an index tensor a kernel dereferences must lie in ``[0, limit)``."""
+    if CHECKS and idx.numel():
+        lo, hi = int(idx.min()), int(idx.max())
+        if lo < 0 or hi >= limit:
+            raise KernelError(f"{what}: index range [{lo}, {hi}] outside [0, {limit})")
+
 
 def _count(n: int = 1) -> None:
     global launch_count
@@ -121,8 +167,8 @@ def _count(n: int = 1) -> None:
 # ------------------------------------------------------------------------------------------
 def rmsnorm(x, w, eps, residual=None):
     x = x.contiguous()
-    out = torch.empty_like(x)
-    h = torch.empty_like(x) if residual is not None else x
+    out = _empty_like(x, "rmsnorm out")
+    h = _empty_like(x, "rmsnorm h") if residual is not None else x
     _chk(load().exo_rmsnorm(_ptr(x), _ptr(residual), _ptr(w), _ptr(out), _ptr(h) if residual is not None else None,
                             x.shape[0], x.shape[1], eps, _dt(x), _st()), "rmsnorm")
     _count()
@@ -140,7 +186,8 @@ def swiglu(gate_up):
 
 def embedding(table, ids):
     ids = ids.to(torch.int32)
-    out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    _check_indices("embedding token ids", ids, table.shape[0])
+    out = _empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device, what="embedding out")
     _chk(load().exo_embedding(_ptr(table), _ptr(ids), _ptr(out), ids.numel(), table.shape[1], table.shape[0],
                               _dt(table), _st()), "embedding")
     _count()
@@ -201,7 +248,7 @@ def gemm_bf16(x, w, bias=None, residual=None, swiglu_out=False, out=None, gate_p
         _count()
         return out
     if out is None or swiglu_out:
-        out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        out = _empty(M, N, dtype=x.dtype, device=x.device, what="gemm out")
     splits = lib.exo_gemm_splits(M, N, K)
     while splits > 1 and splits * M * N > GEMM_PARTIAL_FLOATS:
         splits -= 1
@@ -355,7 +402,8 @@ def qk_rope_append(qkv, positions, inv_freq, mscale, n_q, n_kv, head_dim, kcache
                    k_norm=None, eps=1e-6):
     qkv = qkv.contiguous()
     T = qkv.shape[0]
-    q = torch.empty(T, n_q, head_dim, dtype=qkv.dtype, device=qkv.device)
+    _check_indices("KV slots", slots, kcache.shape[0] * kcache.shape[1])
+    q = _empty(T, n_q, head_dim, dtype=qkv.dtype, device=qkv.device, what="rope q")
     rot = inv_freq.numel() * 2
     _chk(load().exo_qk_rope_append(_ptr(qkv), _ptr(positions), _ptr(inv_freq), float(mscale), n_q, n_kv, head_dim, rot,
                                    _ptr(q), _ptr(kcache), _ptr(vcache), _ptr(slots), _ptr(q_norm), _ptr(k_norm),
@@ -389,8 +437,11 @@ def paged_attention(q, kcache, vcache, block_tables, seq_lens, cu_q, scale, slid
     T, Hq, D = q.shape
     nblk, bs, Hkv, _ = kcache.shape
     B = seq_lens.numel()
-    out = torch.empty_like(q)
+    out = _empty_like(q, "attention out")
     max_blocks = block_tables.shape[1]
+    if CHECKS:
+        _check_indices("block tables", block_tables, nblk)
+        _check_indices("sequence lengths", seq_lens, max_blocks * bs + 1)
     if max_q_len == 1 and T == B:
         tk = _tickets.get(q.device.index)
         if tk is None or tk.numel() < B * Hq:

@@ -37,23 +37,6 @@ def _flags(arena):
     return arena[:4096].view(torch.int32)
 
 
-def _raise_flag_while_running(arena, word):
-    """Set a flag word to 1 by DMA from pinned host memory on a side stream, a few times over some milliseconds.
-
-    The two-shot kernels clear their "rows broadcast" flags when they start, so that flag cannot be put in place
-    before the launch; a copy-engine transfer needs no SM and lands while the kernel is polling (its wait budget is
-    seconds).  No second kernel is involved."""
-    import time
-    one = torch.ones(1, dtype=torch.int32).pin_memory()
-    side = torch.cuda.Stream()
-    dst = _flags(arena)[word:word + 1]
-    for _ in range(20):
-        with torch.cuda.stream(side):
-            dst.copy_(one, non_blocking=True)
-        time.sleep(0.002)
-    side.synchronize()
-
-
 def _ref(parts, res, w, eps):
     h = (sum(p.float() for p in parts) + res.float()).bfloat16()
     hf = h.float()
@@ -105,11 +88,10 @@ def test_two_shot_reduce_norm_writes_this_ranks_rows_into_every_arena():
     _region(A, L, 0, parity, rows, cols).copy_(xa)
     _region(B, L, 0, parity, rows, cols).copy_(xb)
     _flags(A)[BAR_IN + parity * 8 + 1] = 1
+    _flags(A)[BAR_OUT + parity * 8 + 1] = 1              # the peer's "rows broadcast": number of the reduction on this parity
     st = torch.cuda.current_stream().cuda_stream
-    torch.cuda.synchronize()
     rc = lib.exo_reduce_norm_bf16(res.data_ptr(), w.data_ptr(), 1e-5, None, None, rows, cols, parity, 1, 1, st)
     assert rc == 0
-    _raise_flag_while_running(A, BAR_OUT + parity * 8 + 1)      # the peer's "rows broadcast"
     torch.cuda.synchronize()
     want_h, want_x = _ref([xa, xb], res, w, 1e-5)
     mine = (rows + 1) // 2                               # rank 0 owns the first half of the rows
@@ -124,10 +106,9 @@ def test_two_shot_reduce_norm_writes_this_ranks_rows_into_every_arena():
     _region(A, L, 0, parity, rows, cols).copy_(xa)
     _region(B, L, 0, parity, rows, cols).copy_(xb)
     _flags(A)[BAR_IN + parity * 8 + 1] = 1
+    _flags(A)[BAR_OUT + parity * 8 + 1] = 1
     h_priv = torch.zeros(rows, cols, dtype=torch.bfloat16, device="cuda")
-    torch.cuda.synchronize()
     assert lib.exo_reduce_norm_bf16(res.data_ptr(), w.data_ptr(), 1e-5, h_priv.data_ptr(), None, rows, cols, parity, 1, 0, st) == 0
-    _raise_flag_while_running(A, BAR_OUT + parity * 8 + 1)
     torch.cuda.synchronize()
     assert torch.equal(h_priv[:mine], want_h[:mine]) and float(h_priv[mine:].float().abs().max()) == 0.0
     for arena in (A, B):
