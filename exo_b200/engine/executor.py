@@ -10,6 +10,8 @@ is one memcpy and one graph launch.  This is the role the reference gives to mlx
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -52,6 +54,8 @@ class Executor:
         mla_ok = not cfg.mla or (cfg.kv_lora_rank == 512 and cfg.qk_rope_dim == 64 and cfg.qk_nope_dim == 128
                                  and cfg.v_head_dim == 128 and cfg.dtype == "bf16")
         self.use_graphs = (self.cuda and mla_ok) if use_graphs is None else use_graphs
+        if self.cuda and os.environ.get("EXO_KERNEL_CHECKS") == "1":
+            self.use_graphs = False       # the checking flavour synchronises after every op: nothing can be captured
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self.out_host = torch.zeros(self.max_B, dtype=torch.int32, pin_memory=self.cuda)
         self.prev_sampled = torch.zeros(max(self.max_B, 256), dtype=torch.int32, device=self.device)
