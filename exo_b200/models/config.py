@@ -34,7 +34,7 @@ class RopeConfig:
 @dataclass
 class ModelConfig:
     name: str = "model"
-    family: str = "llama"  # llama | qwen3 | qwen3_moe | deepseek_v3 | gpt_oss
+    family: str = "llama"  # llama | qwen3 | qwen3_moe | deepseek_v3 | gpt_oss | glm4_moe | mixtral
     n_layers: int = 2
     hidden: int = 256
     n_heads: int = 4
@@ -163,9 +163,15 @@ class ModelConfig:
         eos = g("eos_token_id", default=())
         if isinstance(eos, int):
             eos = (eos,)
-        family = {"llama": "llama", "mistral": "llama", "qwen2": "llama", "qwen3": "qwen3",
+        # one entry per checkpoint family the engine can shard (the reference keeps one sharding strategy per family,
+        # ``src/exo/worker/engines/mlx/auto_parallel.py:500-599``); architectures that share a block structure share
+        # an entry: Ministral / Mistral-3 text models are Llama blocks, GLM-4.x-MoE-Lite and Kimi are DeepSeek-V3
+        # blocks (MLA + sigmoid-routed experts)
+        family = {"llama": "llama", "mistral": "llama", "ministral": "llama", "ministral3": "llama", "mistral3": "llama",
+                  "qwen2": "llama", "qwen3": "qwen3",
                   "qwen3_moe": "qwen3_moe", "deepseek_v3": "deepseek_v3", "deepseek_v32": "deepseek_v3",
-                  "kimi_k2": "deepseek_v3", "gpt_oss": "gpt_oss"}.get(mt, "llama")
+                  "deepseek_v2": "deepseek_v3", "kimi_k2": "deepseek_v3", "glm4_moe_lite": "deepseek_v3",
+                  "glm4_moe": "glm4_moe", "mixtral": "mixtral", "gpt_oss": "gpt_oss"}.get(mt, "llama")
         mc = ModelConfig(
             name=name, family=family,
             n_layers=g("num_hidden_layers", "n_layer"), hidden=hidden, n_heads=n_heads,
@@ -173,7 +179,7 @@ class ModelConfig:
             ffn=g("intermediate_size", default=4 * hidden), vocab=g("vocab_size"),
             rms_eps=float(g("rms_norm_eps", default=1e-5)), rope=rope,
             tie_embeddings=bool(g("tie_word_embeddings", default=False)),
-            qk_norm=family in ("qwen3", "qwen3_moe"),
+            qk_norm=family in ("qwen3", "qwen3_moe") or (family == "glm4_moe" and bool(g("use_qk_norm", default=False))),
             attn_bias=bool(g("attention_bias", default=mt == "qwen2")),
             max_position=int(g("max_position_embeddings", default=131072)),
             eos_token_ids=tuple(eos),
@@ -186,6 +192,30 @@ class ModelConfig:
             mc.moe_ffn = g("moe_intermediate_size")
             mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
             mc.router = "softmax"
+        if family == "glm4_moe":
+            # GLM-4.5 / 4.6: grouped-query attention with half-rotary RoPE and q/k/v biases, DeepSeek-style experts
+            # (sigmoid scores + correction bias, shared expert, leading dense layers)
+            mc.n_experts = g("n_routed_experts", default=0)
+            mc.n_experts_per_tok = g("num_experts_per_tok", default=0)
+            mc.moe_ffn = g("moe_intermediate_size", default=0)
+            mc.n_shared_experts = g("n_shared_experts", default=0) or 0
+            mc.first_dense_layers = g("first_k_dense_replace", default=0)
+            mc.router = "sigmoid"
+            mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
+            mc.routed_scaling = float(g("routed_scaling_factor", default=1.0))
+            mc.n_group = g("n_group", default=1) or 1
+            mc.topk_group = g("topk_group", default=1) or 1
+            mc.router_bias = True
+            if "partial_rotary_factor" not in cfg:
+                mc.rope.partial_rotary_factor = 0.5
+        if family == "mixtral":
+            # every layer is a sparse block: softmax over the top-k router logits (= softmax then renormalise)
+            mc.n_experts = g("num_local_experts", default=8)
+            mc.n_experts_per_tok = g("num_experts_per_tok", default=2)
+            mc.moe_ffn = g("intermediate_size")
+            mc.router = "softmax"
+            mc.norm_topk_prob = True
+            mc.sliding_window = 0
         if family == "deepseek_v3":
             mc.mla = True
             mc.q_lora_rank = g("q_lora_rank", default=0) or 0
@@ -249,6 +279,27 @@ def preset(name: str) -> ModelConfig:
         return ModelConfig(name="tiny-moe", family="qwen3_moe", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2,
                            head_dim=64, ffn=512, vocab=1024, qk_norm=True, n_experts=8, n_experts_per_tok=2,
                            moe_ffn=128, router="softmax", dtype="fp32")
+    if n in ("tiny-qwen3",):       # dense with per-head q/k RMSNorm
+        return ModelConfig(name="tiny-qwen3", family="qwen3", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                           ffn=512, vocab=1024, rms_eps=1e-6, qk_norm=True, dtype="fp32")
+    if n in ("tiny-qwen2",):       # q/k/v biases, tied embeddings
+        return ModelConfig(name="tiny-qwen2", family="llama", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                           ffn=512, vocab=1024, attn_bias=True, tie_embeddings=True, dtype="fp32")
+    if n in ("tiny-glm4-moe",):    # half-rotary RoPE, biases, sigmoid router with correction bias, shared expert, one dense layer
+        return ModelConfig(name="tiny-glm4-moe", family="glm4_moe", n_layers=3, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                           ffn=512, vocab=1024, attn_bias=True, rope=RopeConfig(theta=10000.0, partial_rotary_factor=0.5),
+                           n_experts=8, n_experts_per_tok=2, moe_ffn=128, n_shared_experts=1, first_dense_layers=1,
+                           router="sigmoid", routed_scaling=1.0, router_bias=True, dtype="fp32")
+    if n in ("tiny-mixtral",):     # every layer sparse, top-2 softmax, block_sparse_moe.* tensor names
+        return ModelConfig(name="tiny-mixtral", family="mixtral", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                           ffn=512, vocab=1024, n_experts=4, n_experts_per_tok=2, moe_ffn=256, router="softmax", dtype="fp32")
+    if n in ("tiny-gpt-oss",):     # attention sinks and a sliding window on every other layer's worth of context
+        return ModelConfig(name="tiny-gpt-oss", family="gpt_oss", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                           ffn=512, vocab=1024, attn_bias=True, attn_sinks=True, sliding_window=32, dtype="fp32")
+    if n in ("tiny-yarn",):        # YaRN-scaled RoPE on a Llama block
+        return ModelConfig(name="tiny-yarn", family="llama", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                           ffn=512, vocab=1024, rope=RopeConfig(theta=10000.0, kind="yarn", factor=4.0, original_max_position=64),
+                           dtype="fp32")
     if n in ("tiny-mla",):
         return ModelConfig(name="tiny-mla", family="deepseek_v3", n_layers=3, hidden=256, n_heads=4, n_kv_heads=4,
                            head_dim=48, ffn=512, vocab=1024, mla=True, q_lora_rank=64, kv_lora_rank=32,
@@ -258,4 +309,5 @@ def preset(name: str) -> ModelConfig:
     raise KeyError(f"unknown preset {name!r}")
 
 
-PRESETS = ("tiny-llama", "llama-3.1-8b", "llama-3.1-70b", "qwen3-235b-a22b", "deepseek-v3", "tiny-moe", "tiny-mla")
+PRESETS = ("tiny-llama", "llama-3.1-8b", "llama-3.1-70b", "qwen3-235b-a22b", "deepseek-v3", "tiny-moe", "tiny-mla",
+           "tiny-qwen3", "tiny-qwen2", "tiny-glm4-moe", "tiny-mixtral", "tiny-gpt-oss", "tiny-yarn")

@@ -85,17 +85,30 @@ class OracleModel:
         g = c.n_heads // n_kv
         sc = torch.einsum("thgd,nhd->hgtn", q.view(T, n_kv, g, -1), K) * scale
         qpos = torch.arange(n - T, n)[:, None]
-        sc = sc.masked_fill(~(torch.arange(n)[None, :] <= qpos)[None, None], float("-inf"))
-        o = torch.einsum("hgtn,nhd->thgd", torch.softmax(sc, -1), V).reshape(T, c.n_heads * dv)
+        keys = torch.arange(n)[None, :]
+        vis = keys <= qpos
+        if c.sliding_window:
+            vis &= keys > qpos - c.sliding_window          # the last `window` keys up to and including the query's own
+        sc = sc.masked_fill(~vis[None, None], float("-inf"))
+        if c.attn_sinks:
+            # one learned logit per head joins the softmax and absorbs probability mass, but contributes no value
+            sink = self.W(p + "sinks", (c.n_heads,)).view(n_kv, g, 1, 1).expand(n_kv, g, T, 1)
+            pr = torch.softmax(torch.cat((sc, sink), -1), -1)[..., :n]
+        else:
+            pr = torch.softmax(sc, -1)
+        o = torch.einsum("hgtn,nhd->thgd", pr, V).reshape(T, c.n_heads * dv)
         return o @ self.W(p + "o_proj.weight", (H, c.n_heads * dv)).t()
 
     def _ffn(self, i: int, x: torch.Tensor) -> torch.Tensor:
-        c, p, H = self.cfg, f"model.layers.{i}.mlp.", self.cfg.hidden
+        from .weights import moe_names
+        c, H = self.cfg, self.cfg.hidden
+        nm = moe_names(c)
+        p = f"model.layers.{i}." + (nm["prefix"] if c.layer_is_moe(i) else "mlp.")
 
-        def mlp(prefix: str, F_: int, t: torch.Tensor) -> torch.Tensor:
-            g = t @ self.W(prefix + "gate_proj.weight", (F_, H)).t()
-            u = t @ self.W(prefix + "up_proj.weight", (F_, H)).t()
-            return (F.silu(g) * u) @ self.W(prefix + "down_proj.weight", (H, F_)).t()
+        def mlp(prefix: str, F_: int, t: torch.Tensor, names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")) -> torch.Tensor:
+            g = t @ self.W(prefix + names[0], (F_, H)).t()
+            u = t @ self.W(prefix + names[1], (F_, H)).t()
+            return (F.silu(g) * u) @ self.W(prefix + names[2], (H, F_)).t()
 
         if not c.layer_is_moe(i):
             return mlp(p, c.ffn, x)
@@ -107,7 +120,7 @@ class OracleModel:
         for t in range(x.shape[0]):
             for j in range(ids.shape[1]):
                 e = int(ids[t, j])
-                y[t] += wts[t, j] * mlp(f"{p}experts.{e}.", c.moe_ffn, x[t:t + 1])[0]
+                y[t] += wts[t, j] * mlp(f"{p}experts.{e}.", c.moe_ffn, x[t:t + 1], (nm["gate"], nm["up"], nm["down"]))[0]
         if c.n_shared_experts:
             y = y + mlp(p + "shared_experts.", c.moe_ffn * c.n_shared_experts, x)
         return y

@@ -313,6 +313,14 @@ class ModelWeights:
                     yield from v.storage()
 
 
+def moe_names(cfg: ModelConfig) -> dict[str, str]:
+    """Checkpoint tensor names of a sparse block: Mixtral keeps ``block_sparse_moe.experts.N.w1 / w3 / w2`` (gate, up,
+    down); the DeepSeek / Qwen / GLM families ``mlp.experts.N.gate_proj / up_proj / down_proj``."""
+    if cfg.family == "mixtral":
+        return {"prefix": "block_sparse_moe.", "gate": "w1.weight", "up": "w3.weight", "down": "w2.weight"}
+    return {"prefix": "mlp.", "gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+
 QUANTIZED_FIELDS = ("wqkv", "wo", "w_gate_up", "w_down", "e_gate_up", "e_down", "s_gate_up", "s_down", "wq_a", "wq_b", "wkv_a")
 
 
@@ -382,9 +390,10 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
                 lw.k_norm = fin(src.get(a + "k_norm.weight", (D,)))
             if cfg.attn_sinks:
                 lw.sinks = fin(_rows(src.get(a + "sinks", (cfg.n_heads,)), r, n), torch.float32)
-        m = p + "mlp."
+        m = p + moe_names(cfg)["prefix"]
         if cfg.layer_is_moe(i):
             E, F = cfg.n_experts, cfg.moe_ffn
+            nm = moe_names(cfg)
             lw.router = fin(src.get(m + "gate.weight", (E, H)))
             if cfg.router_bias:
                 lw.router_bias = fin(src.get(m + "gate.e_score_correction_bias", (E,)), torch.float32)
@@ -392,8 +401,8 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             gus, dns = [], []
             for e in range(elo, ehi):
                 ep = f"{m}experts.{e}."
-                gus.append(torch.cat((src.get(ep + "gate_proj.weight", (F, H)), src.get(ep + "up_proj.weight", (F, H))), 0))
-                dns.append(src.get(ep + "down_proj.weight", (H, F)))
+                gus.append(torch.cat((src.get(ep + nm["gate"], (F, H)), src.get(ep + nm["up"], (F, H))), 0))
+                dns.append(src.get(ep + nm["down"], (H, F)))
             lw.e_gate_up = fin(torch.stack(gus))
             lw.e_down = fin(torch.stack(dns))
             if cfg.n_shared_experts:

@@ -1,0 +1,101 @@
+"""Checkpoint families: ``config.json`` → engine config, and checkpoint tensor names → sharded weights.
+
+Each case writes a tiny ``config.json`` in the published layout of one family, checks the fields the engine derives
+from it, writes a random checkpoint under that family's tensor names and compares the engine's greedy tokens with the
+fp32 oracle that reads the same names independently.
+"""
+import json
+
+import pytest
+import torch
+
+from exo_b200.engine.engine import Engine
+from exo_b200.engine.kv import SamplingParams
+from exo_b200.models.config import ModelConfig
+from exo_b200.models.oracle import OracleModel
+from exo_b200.models.weights import RandomSource, SafetensorsSource, ShardSpec, build_weights, write_safetensors
+
+BASE = {"hidden_size": 128, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 32,
+        "intermediate_size": 256, "vocab_size": 512, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+        "max_position_embeddings": 512}
+
+CASES = {
+    "ministral": ({"model_type": "ministral3", "architectures": ["Ministral3ForCausalLM"]},
+                  dict(family="llama", is_moe=False)),
+    "mistral3-nested": ({"model_type": "mistral3", "text_config": {**BASE, "model_type": "ministral3"}},
+                        dict(family="llama", is_moe=False)),
+    "mixtral": ({"model_type": "mixtral", "num_local_experts": 4, "num_experts_per_tok": 2},
+                dict(family="mixtral", is_moe=True, n_experts=4, router="softmax", first_dense_layers=0)),
+    "glm4-moe": ({"model_type": "glm4_moe", "n_routed_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 64,
+                  "n_shared_experts": 1, "first_k_dense_replace": 1, "attention_bias": True, "use_qk_norm": True,
+                  "partial_rotary_factor": 0.5, "norm_topk_prob": True, "routed_scaling_factor": 1.5, "n_group": 1,
+                  "topk_group": 1},
+                 dict(family="glm4_moe", is_moe=True, router="sigmoid", router_bias=True, qk_norm=True, attn_bias=True,
+                      first_dense_layers=1, routed_scaling=1.5)),
+    "glm4-moe-lite": ({"model_type": "glm4_moe_lite", "n_routed_experts": 8, "num_experts_per_tok": 2,
+                       "moe_intermediate_size": 64, "n_shared_experts": 1, "first_k_dense_replace": 1, "q_lora_rank": 64,
+                       "kv_lora_rank": 32, "qk_nope_head_dim": 16, "qk_rope_head_dim": 16, "v_head_dim": 16,
+                       "norm_topk_prob": True, "routed_scaling_factor": 1.0, "n_group": 1, "topk_group": 1},
+                      dict(family="deepseek_v3", mla=True, is_moe=True, router="sigmoid")),
+    "qwen2": ({"model_type": "qwen2", "tie_word_embeddings": True}, dict(family="llama", attn_bias=True, tie_embeddings=True)),
+}
+
+
+def write_config(d, extra):
+    d.mkdir(parents=True, exist_ok=True)
+    cfg = extra if "text_config" in extra else {**BASE, **extra}
+    (d / "config.json").write_text(json.dumps(cfg))
+    return ModelConfig.from_pretrained(d)
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_config_json_of_each_family_maps_to_engine_fields(name, tmp_path):
+    extra, want = CASES[name]
+    cfg = write_config(tmp_path / name, extra)
+    for k, v in want.items():
+        assert getattr(cfg, k) == v, (name, k, getattr(cfg, k), v)
+    if name == "glm4-moe":
+        assert cfg.rope.partial_rotary_factor == 0.5
+
+
+class Recorder(RandomSource):
+    """A random source that remembers every tensor it was asked for, to write them out as a checkpoint."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.seen: dict[str, torch.Tensor] = {}
+
+    def get(self, name, shape=None):
+        if name in self.seen:
+            return self.seen[name]
+        t = super().get(name, shape)
+        if name.endswith("e_score_correction_bias"):         # non-zero, so the selection bias matters to the tokens
+            t = torch.empty(shape).normal_(0.0, 0.1, generator=self._gen(name))
+        self.seen[name] = t
+        return t
+
+
+@pytest.mark.parametrize("name", ["mixtral", "glm4-moe", "glm4-moe-lite", "ministral"])
+def test_checkpoint_under_family_names_loads_and_matches_oracle(name, tmp_path):
+    extra, _ = CASES[name]
+    d = tmp_path / name
+    cfg = write_config(d, extra)
+    cfg.dtype = "fp32"
+    rec = Recorder(seed=3, std=0.05)
+    oracle = OracleModel(cfg, rec)
+    prompt_t = torch.randint(0, cfg.vocab, (17,), generator=torch.Generator().manual_seed(1))
+    prompt = [int(t) for t in prompt_t]
+    want = oracle.greedy(prompt_t, 6)
+    build_weights(cfg, ShardSpec(), rec, device="cpu")        # touch every tensor the engine reads (unrouted experts too)
+    names = set(rec.seen)
+    if name == "mixtral":
+        assert any(".block_sparse_moe.experts.0.w1.weight" in n for n in names) and not any(".mlp." in n for n in names)
+    if name.startswith("glm4-moe"):
+        assert any(n.endswith("mlp.gate.e_score_correction_bias") for n in names)
+        assert any(n.endswith("layers.0.mlp.gate_proj.weight") for n in names)       # the leading dense layer
+        assert any(n.endswith("mlp.shared_experts.gate_proj.weight") for n in names)
+    write_safetensors(d / "model.safetensors", {k: v.contiguous() for k, v in rec.seen.items()})
+    w = build_weights(cfg, ShardSpec(), SafetensorsSource(d, dtype=torch.float32), device="cpu")
+    eng = Engine(cfg, w, n_blocks=16, device="cpu")
+    got = eng.generate(prompt, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    assert got == want
