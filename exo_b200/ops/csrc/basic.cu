@@ -341,7 +341,8 @@ template <typename T>
 __global__ void sample_kernel(const T* __restrict__ logits, const float* __restrict__ temperature,
                               const int* __restrict__ top_k, const float* __restrict__ top_p,
                               const float* __restrict__ min_p, const float* __restrict__ uniform,
-                              int* __restrict__ out, int V, size_t stride) {
+                              int* __restrict__ out, const int* __restrict__ need, int V, size_t stride) {
+  if (need && !need[blockIdx.x]) return;  // rows the multi-CTA sampler already finished
   __shared__ float red[32];
   __shared__ float sv[32];
   __shared__ int si[32];
@@ -453,16 +454,23 @@ __global__ void sample_kernel(const T* __restrict__ logits, const float* __restr
   }
 }
 
-EXO_API int exo_sample(const void* logits, const float* temperature, const int* top_k, const float* top_p,
-                       const float* min_p, const float* uniform, int* out, int rows, int V, long stride, int dtype,
-                       cudaStream_t st) {
+// need: per-row switch (nullptr = every row); rows whose entry is 0 return at once
+int exo_sample_rows(const void* logits, const float* temperature, const int* top_k, const float* top_p,
+                    const float* min_p, const float* uniform, int* out, const int* need, int rows, int V, long stride,
+                    int dtype, cudaStream_t st) {
   if (rows == 0) return 0;
   if (dtype == EXO_BF16)
     sample_kernel<__nv_bfloat16><<<rows, 1024, 0, st>>>((const __nv_bfloat16*)logits, temperature, top_k, top_p, min_p,
-                                                        uniform, out, V, (size_t)stride);
+                                                        uniform, out, need, V, (size_t)stride);
   else
     sample_kernel<float><<<rows, 1024, 0, st>>>((const float*)logits, temperature, top_k, top_p, min_p, uniform, out,
-                                                V, (size_t)stride);
+                                                need, V, (size_t)stride);
   EXO_CHECK_LAUNCH();
   return 0;
+}
+
+EXO_API int exo_sample(const void* logits, const float* temperature, const int* top_k, const float* top_p,
+                       const float* min_p, const float* uniform, int* out, int rows, int V, long stride, int dtype,
+                       cudaStream_t st) {
+  return exo_sample_rows(logits, temperature, top_k, top_p, min_p, uniform, out, nullptr, rows, V, stride, dtype, st);
 }

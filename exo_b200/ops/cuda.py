@@ -50,6 +50,8 @@ class _Sig:
     exo_argmax_chunks = (_i, [_i, _i])
     exo_argmax = (_i, [_p, _p, _p, _p, _i, _i, _i, _l, _i, _p])
     exo_sample = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _l, _i, _p])
+    exo_sample_workspace = (_l, [_i])
+    exo_sample_fast = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _l, _i, _p])
     exo_paged_decode_workspace = (_l, [_i, _i, _i, _i])
     exo_paged_decode_splits = (_i, [_i, _i, _i])
     exo_paged_decode = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p])
@@ -495,12 +497,31 @@ def argmax(logits):
     return out
 
 
+_sample_ws: dict[int, tuple[int, torch.Tensor]] = {}      # device index -> zero-initialised scratch of the multi-CTA sampler
+use_fast_sampler = os.environ.get("EXO_DISABLE_FAST_SAMPLER") != "1"
+
+
 def sample(logits, temperature, top_k, top_p, min_p, uniform):
+    """Filtered sampling, one token per row: three multi-CTA passes (histogram, boundary bin, draw) plus the single-CTA
+    bisection kernel for rows whose distribution is too flat for the histogram to resolve."""
     rows, V = logits.shape
+    lib = load()
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    _chk(load().exo_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform),
-                           _ptr(out), rows, V, logits.stride(0), _dt(logits), _st()), "sample")
-    _count()
+    if not use_fast_sampler:
+        _chk(lib.exo_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform),
+                            _ptr(out), rows, V, logits.stride(0), _dt(logits), _st()), "sample")
+        _count()
+        return out
+    dev = logits.device.index or 0
+    cap, ws = _sample_ws.get(dev, (0, None))
+    if rows > cap:
+        # grown outside any stream capture in practice: the executor's warm-up steps run before it captures
+        cap = max(64, 1 << (rows - 1).bit_length())
+        ws = torch.zeros(int(lib.exo_sample_workspace(cap)), dtype=torch.uint8, device=logits.device)
+        _sample_ws[dev] = (cap, ws)
+    _chk(lib.exo_sample_fast(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform),
+                             _ptr(out), _ptr(ws), cap, rows, V, logits.stride(0), _dt(logits), _st()), "sample")
+    _count(4)
     return out
 
 

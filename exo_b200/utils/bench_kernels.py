@@ -267,6 +267,21 @@ def main() -> None:
         mp = torch.full((32,), 0.05, device="cuda")
         u = torch.rand(32, device="cuda")
         print(f"sample 32x128256: {timeit(lambda: K.sample(logits, t, tk, tp, mp, u)) * 1e3:.1f} us")
+        # the sampler on the three kinds of rows it meets, each over distinct logits back to back inside a graph
+        peaked = [rnd(32, 128256) * 2 for _ in range(8)]
+        for lg in peaked:
+            lg[:, ::3001] += 14.0
+        flat = [rnd(32, 128256) * 0.05 for _ in range(8)]
+        settings = {"temp 0.7, min_p 0.05 (the API default)": (0, 1.0, 0.05), "top_k 40": (40, 1.0, 0.0),
+                    "top_p 0.95": (0, 0.95, 0.0), "top_k 20, top_p 0.9, min_p 0.05": (20, 0.9, 0.05)}
+        for label, (k_, p_, m_) in settings.items():
+            tk_, tp_, mp_ = torch.full_like(tk, k_), torch.full_like(tp, p_), torch.full_like(mp, m_)
+            for kind, rows in (("peaked", peaked), ("flat", flat)):
+                for fast in (True, False):
+                    K.use_fast_sampler = fast
+                    dt = timeit_rot([lambda lg=lg: K.sample(lg, t, tk_, tp_, mp_, u) for lg in rows])
+                    print(f"sample 32x128256 {kind:6s} {label:42s} {'multi-CTA' if fast else 'bisection'}: {dt * 1e3:.1f} us")
+        K.use_fast_sampler = True
         x, w = rnd(32, 4096), rnd(4096)
         print(f"rmsnorm 32x4096: {timeit(lambda: K.rmsnorm(x, w, 1e-5, x)) * 1e3:.1f} us")
 

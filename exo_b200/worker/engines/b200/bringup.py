@@ -337,7 +337,7 @@ class B200Builder(Builder):
             assert self.control is not None
             return FollowerServingEngine(exe, self.control)
         tok = load_tokenizer(self.model_dir, cfg.vocab)
-        eos = eos_ids(tok, self.model_dir, cfg.eos_token_ids)
+        eos = eos_ids(tok, self.model_dir, cfg.eos_token_ids, str(self.card.model_id))
         cfg.eos_token_ids = eos
         cls = LeaderServingEngine if self.world > 1 else ServingEngine
         te = TokenEngine(cfg, self.weights, self.spec, self.comm, n_blocks=n_blocks, max_seqs=max_seqs,

@@ -242,6 +242,62 @@ def test_sample_matches_reference(K, V):
     assert (probs.gather(1, got[:, None]) > 0).all()
 
 
+def _keep_set(logits, temp, top_k, top_p, min_p):
+    """Boolean keep mask of the reference filter chain, fp32."""
+    V = logits.shape[1]
+    probs = torch.softmax(logits.float() / temp.clamp_min(1e-6)[:, None], -1)
+    sp, si = probs.sort(-1, descending=True)
+    k = torch.where(top_k > 0, top_k, torch.full_like(top_k, V))[:, None]
+    keep = (torch.arange(V, device=logits.device)[None] < k) & ((sp.cumsum(-1) - sp) < top_p[:, None]) \
+        & (sp >= min_p[:, None] * sp[:, :1])
+    keep[:, 0] = True
+    return torch.zeros_like(keep).scatter_(1, si, keep), probs
+
+
+@pytest.mark.parametrize("shape", ["peaked", "flat", "masked"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sample_distribution_shapes(K, shape, dtype):
+    """Peaked rows (what a trained model emits), nearly flat rows (random weights: the boundary bin overflows and the
+    bisection kernel takes the row) and rows with -inf entries, over the filter settings the API exposes."""
+    g = torch.Generator(device="cuda").manual_seed(11)
+    B, V = 32, 128256
+    if shape == "peaked":
+        logits = torch.randn(B, V, device="cuda", generator=g) * 2.0
+        hot = torch.randint(0, V, (B, 40), device="cuda", generator=g)
+        logits.scatter_(1, hot, 12.0 + 3.0 * torch.rand(B, 40, device="cuda", generator=g))
+    elif shape == "flat":
+        logits = torch.randn(B, V, device="cuda", generator=g) * 0.05
+    else:
+        logits = torch.randn(B, V, device="cuda", generator=g) * 3.0
+        logits[:, V // 2:] = float("-inf")
+    logits = logits.to(dtype)
+    temp = torch.tensor([0.7, 1.0, 0.3, 1.5, 0.0, 0.7, 1.0, 0.6] * 4, device="cuda")
+    top_k = torch.tensor([0, 40, 0, 0, 0, 20, 1, 0] * 4, device="cuda", dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 0.95, 0.8, 1.0, 0.9, 1.0, 0.999] * 4, device="cuda")
+    min_p = torch.tensor([0.05, 0.0, 0.0, 0.02, 0.0, 0.05, 0.0, 0.0] * 4, device="cuda")
+    u = torch.rand(B, device="cuda", generator=g)
+    got = K.sample(logits, temp, top_k, top_p, min_p, u).long()
+    again = K.sample(logits, temp, top_k, top_p, min_p, u).long()
+    assert torch.equal(got, again)                      # fixed-point sums: the same draw every time
+    want = ref.sample(logits, temp, top_k, top_p, min_p, u)
+    keep, probs = _keep_set(logits, temp, top_k, top_p, min_p)
+    sampled = temp > 0
+    assert torch.equal(got[~sampled], want[~sampled])
+    # every draw comes from the reference keep set, bar ties at its edge (bf16 logits repeat values): the drawn token's
+    # probability is then at least the smallest kept one
+    floor = torch.where(keep, probs, torch.ones_like(probs)).min(-1).values
+    assert (probs.gather(1, got[:, None])[:, 0] >= floor * (1 - 1e-5)).all()
+    # and it is the same token as the fp32 inverse CDF except where the draw sits on an edge of the CDF
+    assert (got == want).sum().item() >= B - 3, (got, want)
+    # the position of the draw in the kept CDF matches the uniform number
+    kept = probs * keep
+    cdf = kept.cumsum(-1) / kept.sum(-1, keepdim=True)
+    hi = cdf.gather(1, got[:, None])[:, 0]
+    lo = hi - (kept / kept.sum(-1, keepdim=True)).gather(1, got[:, None])[:, 0]
+    ok = (u >= lo - 1e-4) & (u <= hi + 1e-4)
+    assert ok[sampled].all(), (u, lo, hi)
+
+
 @pytest.mark.parametrize("kind,E,k,n_group,topk_group,dtype", [
     ("softmax", 128, 8, 1, 1, torch.bfloat16), ("softmax", 60, 4, 1, 1, torch.float32),
     ("sigmoid", 256, 8, 8, 4, torch.float32), ("sigmoid", 64, 6, 1, 1, torch.bfloat16)])
