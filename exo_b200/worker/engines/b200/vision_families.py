@@ -1,0 +1,278 @@
+"""Image processors and towers of the vision-language families, and the tensor names they load.
+
+The reference drives three processor families through ``mlx_vlm`` / ``transformers`` classes
+(``src/exo/worker/engines/mlx/vision.py:487-624``): the Qwen-VL grid processor (``image_grid_thw``, tokens =
+``t*h*w / merge²``), the Kimi-VL native-resolution processor (``image_grid_hws``, a patch budget, 2x2 merge) and the
+fixed-budget Gemma processor (every image becomes the same number of soft tokens).  Here each is a small class that
+turns PIL images into the tower's input and the per-image token count, written from the published algorithms, plus the
+Qwen2-VL tower itself (fused qkv, 2-D rotary positions, per-image attention, LayerNorm + MLP patch merger) in plain
+PyTorch on the engine's device, loading the checkpoint's ``visual.*`` tensors
+(``src/exo/worker/engines/mlx/vision.py:277-485`` does the loading and key remapping for its towers).
+
+``family_for(config.json)`` picks the processor; ``VisionProcessor`` (``vision.py``) owns the feature cache and the
+splice into the prompt whichever family produced the rows.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+import torch.nn.functional as F
+
+CLIP_MEAN, CLIP_STD = (0.48145466, 0.4578275, 0.40821073), (0.26862954, 0.26130258, 0.27577711)
+HALF = (0.5, 0.5, 0.5)
+
+
+def _to_tensor(im, size_wh: tuple[int, int] | None, resample, mean, std) -> torch.Tensor:
+    """PIL image → normalised ``[3, H, W]`` fp32 (optionally resized first)."""
+    import numpy as np
+    im = im.convert("RGB")
+    if size_wh is not None and im.size != size_wh:
+        im = im.resize(size_wh, resample)
+    x = torch.from_numpy(np.asarray(im, dtype=np.uint8).copy()).permute(2, 0, 1).float() * (1.0 / 255.0)
+    return (x - torch.tensor(mean)[:, None, None]) / torch.tensor(std)[:, None, None]
+
+
+def smart_resize(h: int, w: int, factor: int, min_pixels: int, max_pixels: int) -> tuple[int, int]:
+    """Target size of the Qwen-VL processors: both sides multiples of ``factor`` (patch x merge), the area inside
+    ``[min_pixels, max_pixels]``, the aspect ratio kept as far as the rounding allows."""
+    if max(h, w) / max(1, min(h, w)) > 200:
+        raise ValueError(f"aspect ratio {max(h, w) / min(h, w):.1f} is beyond what the processor takes (200)")
+    hb, wb = max(factor, round(h / factor) * factor), max(factor, round(w / factor) * factor)
+    if hb * wb > max_pixels:
+        beta = math.sqrt(h * w / max_pixels)
+        hb = max(factor, math.floor(h / beta / factor) * factor)
+        wb = max(factor, math.floor(w / beta / factor) * factor)
+    elif hb * wb < min_pixels:
+        beta = math.sqrt(min_pixels / (h * w))
+        hb, wb = math.ceil(h * beta / factor) * factor, math.ceil(w * beta / factor) * factor
+    return hb, wb
+
+
+@dataclass
+class QwenVLProcessor:
+    """Qwen2-VL / Qwen2.5-VL / Qwen3-VL: resize to a grid of ``patch``-sized patches, duplicate the frame to fill the
+    temporal patch, and lay the patches out so that the ``merge x merge`` patches of one output token are adjacent."""
+    patch: int = 14
+    merge: int = 2
+    temporal: int = 2
+    min_pixels: int = 56 * 56
+    max_pixels: int = 28 * 28 * 1280
+    mean: tuple[float, ...] = CLIP_MEAN
+    std: tuple[float, ...] = CLIP_STD
+
+    @classmethod
+    def from_config(cls, pre: dict[str, Any]) -> "QwenVLProcessor":
+        size = pre.get("size") or {}
+        return cls(patch=pre.get("patch_size", 14), merge=pre.get("merge_size", 2), temporal=pre.get("temporal_patch_size", 2),
+                   min_pixels=pre.get("min_pixels") or size.get("shortest_edge", 56 * 56),
+                   max_pixels=pre.get("max_pixels") or size.get("longest_edge", 28 * 28 * 1280),
+                   mean=tuple(pre.get("image_mean", CLIP_MEAN)), std=tuple(pre.get("image_std", CLIP_STD)))
+
+    def __call__(self, images: list) -> tuple[torch.Tensor, torch.Tensor, list[int]]:
+        """→ ``(patches [sum t*h*w, 3*temporal*patch²], grid_thw [n, 3], tokens per image)``."""
+        from PIL import Image
+        p, m, tp = self.patch, self.merge, self.temporal
+        rows, grids = [], []
+        for im in images:
+            w0, h0 = im.size
+            h, w = smart_resize(h0, w0, p * m, self.min_pixels, self.max_pixels)
+            x = _to_tensor(im, (w, h), Image.BICUBIC, self.mean, self.std)
+            gh, gw = h // p, w // p
+            x = x[None].expand(tp, -1, -1, -1)                                   # one still image fills the temporal patch
+            x = x.reshape(1, tp, 3, gh // m, m, p, gw // m, m, p)
+            x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8)                             # t, h/m, w/m, m, m, C, tp, p, p
+            rows.append(x.reshape(gh * gw, 3 * tp * p * p))
+            grids.append((1, gh, gw))
+        grid = torch.tensor(grids, dtype=torch.long)
+        return torch.cat(rows), grid, [t * h * w // (m * m) for t, h, w in grids]
+
+
+@dataclass
+class KimiVLProcessor:
+    """Kimi-VL (MoonViT): native resolution up to a patch budget, then padding to whole ``merge``-blocks.
+
+    An image with more than ``in_token_limit`` patches is shrunk (aspect kept) until it fits; the result is padded with
+    zeros on the right / bottom to a multiple of ``patch x merge`` and cut into ``[N, 3, patch, patch]`` patches in
+    row-major order; ``image_grid_hws`` carries the patch grid of each image."""
+    patch: int = 14
+    merge: tuple[int, int] = (2, 2)
+    in_token_limit: int = 4096
+    mean: tuple[float, ...] = HALF
+    std: tuple[float, ...] = HALF
+
+    @classmethod
+    def from_config(cls, pre: dict[str, Any]) -> "KimiVLProcessor":
+        return cls(patch=pre.get("patch_size", 14), merge=tuple(pre.get("merge_kernel_size", (2, 2))),
+                   in_token_limit=pre.get("in_token_limit", 4096), mean=tuple(pre.get("image_mean", HALF)),
+                   std=tuple(pre.get("image_std", HALF)))
+
+    def target(self, w: int, h: int) -> tuple[int, int, int, int]:
+        """``(resize_w, resize_h, padded_w, padded_h)``."""
+        p = self.patch
+        if (w // p) * (h // p) > self.in_token_limit:
+            s = math.sqrt(self.in_token_limit / ((w / p) * (h / p)))
+            w, h = max(p, int(w * s)), max(p, int(h * s))
+        cw, ch = p * self.merge[1], p * self.merge[0]
+        return w, h, -(-w // cw) * cw, -(-h // ch) * ch
+
+    def __call__(self, images: list) -> tuple[torch.Tensor, torch.Tensor, list[int]]:
+        from PIL import Image
+        p = self.patch
+        rows, grids = [], []
+        for im in images:
+            w, h, pw, ph = self.target(*im.size)
+            x = _to_tensor(im, (w, h), Image.BICUBIC, self.mean, self.std)
+            x = F.pad(x, (0, pw - w, 0, ph - h))
+            gh, gw = ph // p, pw // p
+            rows.append(x.reshape(3, gh, p, gw, p).permute(1, 3, 0, 2, 4).reshape(gh * gw, 3, p, p))
+            grids.append((gh, gw))
+        mh, mw = self.merge
+        return torch.cat(rows), torch.tensor(grids, dtype=torch.long), [gh * gw // (mh * mw) for gh, gw in grids]
+
+
+@dataclass
+class GemmaProcessor:
+    """Gemma-3: every image is resized to one square and becomes ``tokens_per_image`` soft tokens (the tower's
+    ``size/patch`` squared patches are average-pooled down to that many by the projector)."""
+    size: int = 896
+    tokens_per_image: int = 256
+    mean: tuple[float, ...] = HALF
+    std: tuple[float, ...] = HALF
+
+    @classmethod
+    def from_config(cls, pre: dict[str, Any], cfg: dict[str, Any] | None = None) -> "GemmaProcessor":
+        size = pre.get("size") or {}
+        return cls(size=size.get("height", 896), tokens_per_image=(cfg or {}).get("mm_tokens_per_image", 256),
+                   mean=tuple(pre.get("image_mean", HALF)), std=tuple(pre.get("image_std", HALF)))
+
+    def __call__(self, images: list) -> tuple[torch.Tensor, None, list[int]]:
+        from PIL import Image
+        x = torch.stack([_to_tensor(im, (self.size, self.size), Image.BILINEAR, self.mean, self.std) for im in images])
+        return x, None, [self.tokens_per_image] * len(images)
+
+    @staticmethod
+    def pool(patch_rows: torch.Tensor, tokens: int) -> torch.Tensor:
+        """``[side², C]`` tower outputs → ``[tokens, C]`` by average pooling over the patch grid (the projector's first step)."""
+        n, c = patch_rows.shape
+        side, out = math.isqrt(n), math.isqrt(tokens)
+        g = patch_rows.t().reshape(1, c, side, side)
+        return F.avg_pool2d(g, side // out, side // out).reshape(c, out * out).t()
+
+
+def family_for(config: dict[str, Any], preprocessor: dict[str, Any] | None = None):
+    """The image processor of a checkpoint, from its ``config.json`` (``model_type``) and ``preprocessor_config.json``;
+    ``None`` for a text-only model."""
+    mt = str(config.get("model_type", "")).lower()
+    pre = preprocessor or {}
+    if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "qwen3_5", "qwen3_5_moe"):
+        proc = QwenVLProcessor.from_config(pre)
+        vc = config.get("vision_config") or {}
+        if "patch_size" in vc and "patch_size" not in pre:
+            proc.patch = vc["patch_size"]
+        if mt.startswith("qwen3") and "image_mean" not in pre:
+            proc.mean = proc.std = HALF
+        return proc
+    if mt in ("kimi_vl", "kimi_k25", "kimi_k2_5"):
+        return KimiVLProcessor.from_config(pre)
+    if mt in ("gemma3", "gemma3n", "gemma4"):
+        return GemmaProcessor.from_config(pre, config)
+    return None
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Qwen2-VL tower
+# ---------------------------------------------------------------------------------------------------------------------
+@dataclass
+class QwenVLTowerConfig:
+    depth: int = 32
+    embed_dim: int = 1280
+    heads: int = 16
+    mlp_ratio: float = 4.0
+    patch: int = 14
+    merge: int = 2
+    temporal: int = 2
+    out_hidden: int = 3584
+
+    @classmethod
+    def from_config(cls, vc: dict[str, Any]) -> "QwenVLTowerConfig":
+        return cls(depth=vc.get("depth", 32), embed_dim=vc.get("embed_dim", 1280), heads=vc.get("num_heads", 16),
+                   mlp_ratio=vc.get("mlp_ratio", 4.0), patch=vc.get("patch_size", 14), merge=vc.get("spatial_merge_size", 2),
+                   temporal=vc.get("temporal_patch_size", 2), out_hidden=vc.get("hidden_size", 3584))
+
+
+def _rot_half(x: torch.Tensor) -> torch.Tensor:
+    a, b = x.chunk(2, -1)
+    return torch.cat((-b, a), -1)
+
+
+@dataclass
+class QwenVLTower:
+    """The Qwen2-VL vision transformer over ``QwenVLProcessor`` patches.
+
+    ``weights`` maps the checkpoint's names with the ``visual.`` prefix removed (``patch_embed.proj.weight`` as the 5-D
+    convolution kernel, ``blocks.N.{norm1,norm2,attn.qkv,attn.proj,mlp.fc1,mlp.fc2}``, ``merger.{ln_q,mlp.0,mlp.2}``).
+    Positions are 2-D rotary (row and column halves of each head's first half), attention is full within an image and
+    never crosses images, the MLP activation is ``x * sigmoid(1.702 x)``, and the merger normalises every patch, joins
+    the ``merge²`` neighbours and maps them to the decoder's hidden size."""
+    cfg: QwenVLTowerConfig
+    weights: dict[str, torch.Tensor]
+    device: torch.device = field(default_factory=lambda: torch.device("cpu"))
+    dtype: torch.dtype = torch.float32
+
+    def __post_init__(self) -> None:
+        self.w = {k: v.to(device=self.device, dtype=self.dtype) for k, v in self.weights.items()}
+        self.w["patch_embed.proj.weight"] = self.w["patch_embed.proj.weight"].reshape(self.cfg.embed_dim, -1)
+
+    @classmethod
+    def from_source(cls, src, cfg: QwenVLTowerConfig, device, dtype, prefix: str = "visual.") -> "QwenVLTower":
+        """Read the tower's tensors from a checkpoint reader (``models.weights.SafetensorsSource``)."""
+        names = [n for n in src.names() if n.startswith(prefix)]
+        if not names:
+            raise KeyError(f"checkpoint has no {prefix}* tensors")
+        return cls(cfg, {n[len(prefix):]: src.get(n, None) for n in names}, torch.device(device), dtype)
+
+    def _rotary(self, grid_thw: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        c = self.cfg
+        hd = c.embed_dim // c.heads
+        inv = 1.0 / (10000.0 ** (torch.arange(0, hd // 2, 2, dtype=torch.float32, device=self.device) / (hd // 2)))
+        ids = []
+        for t, h, w in grid_thw.tolist():
+            m = c.merge
+            hp = torch.arange(h, device=self.device)[:, None].expand(h, w)
+            wp = torch.arange(w, device=self.device)[None, :].expand(h, w)
+            order = lambda g: g.reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).reshape(-1)   # noqa: E731
+            ids.append(torch.stack((order(hp), order(wp)), -1).repeat(t, 1))
+        pos = torch.cat(ids).float()                                            # [N, 2]
+        ang = torch.cat((pos[:, :1] * inv, pos[:, 1:] * inv), -1)               # [N, hd/2]
+        ang = torch.cat((ang, ang), -1)                                         # [N, hd]
+        return ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    @torch.no_grad()
+    def __call__(self, patches: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        c, w = self.cfg, self.w
+        E, H = c.embed_dim, c.heads
+        hd = E // H
+        x = patches.to(device=self.device, dtype=self.dtype) @ w["patch_embed.proj.weight"].t()
+        cos, sin = self._rotary(grid_thw)
+        cos, sin = cos.to(self.dtype), sin.to(self.dtype)
+        spans = (grid_thw[:, 0] * grid_thw[:, 1] * grid_thw[:, 2]).tolist()
+        for i in range(c.depth):
+            b = f"blocks.{i}."
+            y = F.layer_norm(x, (E,), w[b + "norm1.weight"], w[b + "norm1.bias"], 1e-6)
+            q, k, v = (y @ w[b + "attn.qkv.weight"].t() + w[b + "attn.qkv.bias"]).view(-1, 3, H, hd).unbind(1)
+            q, k = q * cos + _rot_half(q) * sin, k * cos + _rot_half(k) * sin
+            outs, o = [], 0
+            for n in spans:                                                     # attention never crosses images
+                qs, ks, vs = (t[o:o + n].transpose(0, 1)[None] for t in (q, k, v))
+                outs.append(F.scaled_dot_product_attention(qs, ks, vs)[0].transpose(0, 1).reshape(n, E))
+                o += n
+            x = x + torch.cat(outs) @ w[b + "attn.proj.weight"].t() + w[b + "attn.proj.bias"]
+            y = F.layer_norm(x, (E,), w[b + "norm2.weight"], w[b + "norm2.bias"], 1e-6)
+            y = y @ w[b + "mlp.fc1.weight"].t() + w[b + "mlp.fc1.bias"]
+            x = x + (y * torch.sigmoid(1.702 * y)) @ w[b + "mlp.fc2.weight"].t() + w[b + "mlp.fc2.bias"]
+        x = F.layer_norm(x, (E,), w["merger.ln_q.weight"], w["merger.ln_q.bias"], 1e-6).view(-1, c.merge * c.merge * E)
+        x = F.gelu(x @ w["merger.mlp.0.weight"].t() + w["merger.mlp.0.bias"])
+        return x @ w["merger.mlp.2.weight"].t() + w["merger.mlp.2.bias"]

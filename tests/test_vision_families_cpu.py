@@ -1,0 +1,98 @@
+"""Family image processors and the Qwen2-VL tower against the ``transformers`` implementations of the same models."""
+import numpy as np
+import pytest
+import torch
+from PIL import Image
+
+from exo_b200.worker.engines.b200.vision_families import (GemmaProcessor, KimiVLProcessor, QwenVLProcessor, QwenVLTower,
+                                                          QwenVLTowerConfig, family_for, smart_resize)
+
+
+def picture(h, w, seed=0):
+    rng = np.random.default_rng(seed)
+    base = rng.integers(0, 255, (h // 8 + 1, w // 8 + 1, 3), dtype=np.uint8)
+    return Image.fromarray(base).resize((w, h), Image.BILINEAR)       # smooth content: resampling filters agree closely
+
+
+@pytest.mark.parametrize("hw", [(300, 500), (64, 48), (2000, 1500), (28, 900)])
+def test_qwen_vl_processor_matches_transformers(hw):
+    from transformers.models.qwen2_vl.image_processing_qwen2_vl import Qwen2VLImageProcessor
+    ref = Qwen2VLImageProcessor()
+    imgs = [picture(*hw, seed=1), picture(hw[0] // 2 + 30, hw[1] // 2 + 30, seed=2)]
+    want = ref(images=imgs, return_tensors="pt")
+    patches, grid, tokens = QwenVLProcessor.from_config(ref.to_dict())(imgs)
+    assert torch.equal(grid, want["image_grid_thw"])
+    assert tokens == [int(t * h * w) // 4 for t, h, w in grid.tolist()]
+    assert patches.shape == want["pixel_values"].shape
+    # the layouts are identical; values differ by the resize filters' rounding to 8 bits (a few grey levels at most)
+    diff = (patches - want["pixel_values"].float()).abs()
+    assert diff.max() < 0.08 and diff.mean() < 2e-3, (diff.max(), diff.mean())
+
+
+def test_smart_resize_bounds():
+    assert smart_resize(300, 500, 28, 56 * 56, 28 * 28 * 1280) == (308, 504)
+    h, w = smart_resize(4000, 6000, 28, 56 * 56, 28 * 28 * 1280)
+    assert h % 28 == 0 and w % 28 == 0 and h * w <= 28 * 28 * 1280 and abs(h / w - 4000 / 6000) < 0.02
+    h, w = smart_resize(10, 20, 28, 56 * 56, 28 * 28 * 1280)
+    assert h * w >= 56 * 56
+    with pytest.raises(ValueError):
+        smart_resize(10, 4000, 28, 56 * 56, 28 * 28 * 1280)
+
+
+def test_qwen_vl_tower_matches_transformers():
+    from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLVisionConfig
+    from transformers.models.qwen2_vl.modeling_qwen2_vl import Qwen2VisionTransformerPretrainedModel
+    torch.manual_seed(0)
+    vc = Qwen2VLVisionConfig(depth=3, embed_dim=64, hidden_size=96, num_heads=4, mlp_ratio=4, patch_size=14,
+                             spatial_merge_size=2, temporal_patch_size=2)
+    vc._attn_implementation = "eager"
+    hf = Qwen2VisionTransformerPretrainedModel(vc).eval().float()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    proc = QwenVLProcessor()
+    patches, grid, tokens = proc([picture(120, 200, 3), picture(90, 60, 4)])
+    with torch.no_grad():
+        want = hf(patches, grid_thw=grid)
+    want = getattr(want, "pooler_output", want)
+    want = want[0] if isinstance(want, tuple) else want
+    tower = QwenVLTower(QwenVLTowerConfig.from_config(vc.to_dict()), dict(hf.state_dict()))
+    got = tower(patches, grid)
+    assert got.shape == (sum(tokens), 96) == tuple(want.shape)
+    torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-4)
+
+
+def test_gemma_processor_matches_transformers():
+    from transformers.models.gemma3.image_processing_gemma3 import Gemma3ImageProcessor
+    ref = Gemma3ImageProcessor(size={"height": 896, "width": 896})
+    imgs = [picture(300, 500, 5), picture(1000, 700, 6)]
+    want = ref(images=imgs, return_tensors="pt")["pixel_values"]
+    x, grid, tokens = GemmaProcessor.from_config(ref.to_dict(), {"mm_tokens_per_image": 256})(imgs)
+    assert grid is None and tokens == [256, 256] and x.shape == want.shape == (2, 3, 896, 896)
+    diff = (x - want.float()).abs()
+    assert diff.max() < 0.05 and diff.mean() < 2e-3, (diff.max(), diff.mean())
+    rows = torch.arange(64 * 64 * 2, dtype=torch.float32).reshape(64 * 64, 2)
+    pooled = GemmaProcessor.pool(rows, 256)
+    assert pooled.shape == (256, 2)
+    torch.testing.assert_close(pooled[0], rows.reshape(64, 64, 2)[:4, :4].reshape(16, 2).mean(0))
+
+
+def test_kimi_vl_processor_grid_budget_and_padding():
+    proc = KimiVLProcessor()
+    patches, grid, tokens = proc([picture(100, 150, 7)])
+    assert grid.tolist() == [[8, 12]] and patches.shape == (96, 3, 14, 14) and tokens == [24]   # padded 100x150 -> 112x168
+    assert torch.all(patches.reshape(8, 12, 3, 14, 14)[7, :, :, 2:, :] == 0)                   # rows past pixel 100 are padding
+    big = picture(2000, 3000, 8)
+    patches, grid, tokens = proc([big])
+    gh, gw = grid[0].tolist()
+    assert (gh - 2) * (gw - 2) <= 4096 and gh % 2 == 0 and gw % 2 == 0 and abs(gh / gw - 2 / 3) < 0.05
+    assert tokens == [gh * gw // 4]
+
+
+def test_family_selection_from_config_json():
+    assert isinstance(family_for({"model_type": "qwen2_5_vl", "vision_config": {"patch_size": 14}}), QwenVLProcessor)
+    q3 = family_for({"model_type": "qwen3_vl", "vision_config": {"patch_size": 16}})
+    assert q3.patch == 16 and q3.mean == (0.5, 0.5, 0.5)
+    assert isinstance(family_for({"model_type": "kimi_vl"}), KimiVLProcessor)
+    g = family_for({"model_type": "gemma3", "mm_tokens_per_image": 256}, {"size": {"height": 896, "width": 896}})
+    assert isinstance(g, GemmaProcessor) and g.size == 896
+    assert family_for({"model_type": "llama"}) is None
