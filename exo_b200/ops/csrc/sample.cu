@@ -3,7 +3,7 @@
 //   p_i = softmax(l / T);  keep i  iff  #{p > p_i} < top_k  and  mass{p > p_i} < top_p  and  p_i >= min_p * p_max
 //   (the arg-max is always kept); then inverse CDF over the kept tokens in vocabulary order with the caller's uniform.
 //
-// Work is in q_i = exp((l_i - l_max) / T) in (0, 1] and in u_i = -ln q_i.  Every sum of q is kept in 2^-40 fixed point
+// Work is in q_i = exp((l_i - l_max) / T) in (0, 1] and in u_i = -ln q_i.  Every sum of q is kept in 2^-32 fixed point
 // (64-bit integer adds are associative), so the result does not depend on the order in which CTAs or atomics land:
 // ranks of a tensor-parallel group that sample the same logits pick the same token.
 //
@@ -27,7 +27,7 @@ constexpr float BINS_PER_U = 32.f;
 constexpr int CAP = 1024;           // boundary-bin entries resolved exactly
 constexpr int NT = 512;
 constexpr int MAX_CHUNKS = 64;
-constexpr float FX_ONE = 1099511627776.f;   // 2^40
+constexpr float FX_ONE = 4294967296.f;   // 2^32
 typedef unsigned long long u64;
 
 struct RowWs {                      // per-row scratch, zero-initialised once; the kernels leave tickets and n_list at zero
@@ -51,6 +51,27 @@ struct RowWs {                      // per-row scratch, zero-initialised once; t
 
 template <typename T>
 __device__ __forceinline__ float ldf(const T* p) { return Cvt<T>::to_f(*p); }
+
+// f(index, value) for every token of [c0, c1), each thread taking 16-byte groups when the row allows it
+template <typename T, typename F>
+__device__ __forceinline__ void for_tokens(const T* __restrict__ x, int c0, int c1, F f) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  int tid = threadIdx.x;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    int a0 = (c0 + VEC - 1) / VEC * VEC, a1 = c1 / VEC * VEC;
+    if (a0 >= a1) { a0 = c1; a1 = c1; }
+    for (int i = c0 + tid; i < a0; i += NT) f(i, ldf(x + i));
+    for (int i = a0 + tid * VEC; i < a1; i += NT * VEC) {
+      uint4 v = *reinterpret_cast<const uint4*>(x + i);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int j = 0; j < VEC; j++) f(i + j, Cvt<T>::to_f(e[j]));
+    }
+    for (int i = a1 + tid; i < c1; i += NT) f(i, ldf(x + i));
+  } else {
+    for (int i = c0 + tid; i < c1; i += NT) f(i, ldf(x + i));
+  }
+}
 
 __device__ __forceinline__ void merge_max(const RowWs* ws, int chunks, float& lmax, int& bi) {
   // every thread of warp 0 ends with the row's max and arg-max (lowest index among equals)
@@ -92,10 +113,9 @@ __global__ void __launch_bounds__(NT) sample_max_kernel(const T* __restrict__ lo
   int c0 = c * chunk, c1 = min(V, c0 + chunk);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = c0 + tid; i < c1; i += NT) {
-    float v = ldf(x + i);
-    if (v > best) { best = v; bi = i; }
-  }
+  for_tokens(x, c0, c1, [&](int i, float v) {
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -123,8 +143,9 @@ __global__ void __launch_bounds__(NT) sample_hist_kernel(const T* __restrict__ l
                                                          const int* __restrict__ top_k, const float* __restrict__ top_p,
                                                          const float* __restrict__ min_p, RowWs* __restrict__ wsa,
                                                          int V, size_t stride, int chunk, int chunks) {
-  __shared__ int h_cnt[NB];
-  __shared__ u64 h_mass[NB];
+  // the mass of a bin is summed as two 16-bit halves of the 2^-32 fixed-point value: 32-bit shared-memory adds, and no
+  // half can overflow within one chunk (at most 65536 tokens)
+  __shared__ unsigned h_cnt[NB], h_hi[NB], h_lo[NB];
   __shared__ float s_lmax;
   __shared__ int s_last;
   __shared__ int s_wc[NT / 32];
@@ -135,7 +156,7 @@ __global__ void __launch_bounds__(NT) sample_hist_kernel(const T* __restrict__ l
   float temp = temperature[row];
   if (temp <= 0.f) return;          // greedy rows: pass 3 writes the arg-max
   RowWs* ws = wsa + row;
-  for (int i = tid; i < NB; i += NT) { h_cnt[i] = 0; h_mass[i] = 0; }
+  for (int i = tid; i < NB; i += NT) { h_cnt[i] = 0; h_hi[i] = 0; h_lo[i] = 0; }
   if (tid < 32) {
     float lm; int bi;
     merge_max(ws, chunks, lm, bi);
@@ -147,24 +168,28 @@ __global__ void __launch_bounds__(NT) sample_hist_kernel(const T* __restrict__ l
   int c0 = c * chunk, c1 = min(V, c0 + chunk);
   int far_cnt = 0;                  // u beyond the histogram: one shared bin, summed in registers first
   u64 far_mass = 0;
-  for (int i = c0 + tid; i < c1; i += NT) {
-    float u = (lmax - ldf(x + i)) * inv_t;
+  for_tokens(x, c0, c1, [&](int i, float l) {
+    float u = (lmax - l) * inv_t;
     u64 fx = to_fx(__expf(-u));
     int b = bin_of(u);
     if (b == NB - 1) { far_cnt++; far_mass += fx; }
-    else { atomicAdd(&h_cnt[b], 1); atomicAdd(&h_mass[b], fx); }
-  }
+    else {
+      atomicAdd(&h_cnt[b], 1u);
+      atomicAdd(&h_hi[b], (unsigned)(fx >> 16));
+      atomicAdd(&h_lo[b], (unsigned)(fx & 0xffffu));
+    }
+  });
   if (__any_sync(0xffffffffu, far_cnt)) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       far_cnt += __shfl_xor_sync(0xffffffffu, far_cnt, o);
       far_mass += __shfl_xor_sync(0xffffffffu, far_mass, o);
     }
-    if ((tid & 31) == 0 && far_cnt) { atomicAdd(&h_cnt[NB - 1], far_cnt); atomicAdd(&h_mass[NB - 1], far_mass); }
+    if ((tid & 31) == 0 && far_cnt) { atomicAdd(&ws->cnt[NB - 1], far_cnt); atomicAdd(&ws->mass[NB - 1], far_mass); }
   }
   __syncthreads();
   for (int i = tid; i < NB; i += NT)
-    if (h_cnt[i]) { atomicAdd(&ws->cnt[i], h_cnt[i]); atomicAdd(&ws->mass[i], h_mass[i]); }
+    if (h_cnt[i]) { atomicAdd(&ws->cnt[i], (int)h_cnt[i]); atomicAdd(&ws->mass[i], ((u64)h_hi[i] << 16) + h_lo[i]); }
   __threadfence();
   __syncthreads();
   if (tid == 0) s_last = atomicAdd(&ws->ticket2, 1) == chunks - 1;
@@ -266,8 +291,8 @@ __global__ void __launch_bounds__(NT) sample_draw_kernel(const T* __restrict__ l
   const T* x = logits + (size_t)row * stride;
   int c0 = c * chunk, c1 = min(V, c0 + chunk);
   u64 loc = 0;
-  for (int i = c0 + tid; i < c1; i += NT) {
-    float u = (lmax - ldf(x + i)) * inv_t;
+  for_tokens(x, c0, c1, [&](int i, float l) {
+    float u = (lmax - l) * inv_t;
     float q = __expf(-u);
     int b = bin_of(u);
     if (b == b_star && resolve) {
@@ -276,7 +301,7 @@ __global__ void __launch_bounds__(NT) sample_draw_kernel(const T* __restrict__ l
     }
     bool keep = (b < b_star && q >= mp) || i == bi;
     if (keep) loc += to_fx(q);
-  }
+  });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) loc += __shfl_xor_sync(0xffffffffu, loc, o);
   if (lane == 0) s_red[w] = loc;
@@ -305,6 +330,7 @@ __global__ void __launch_bounds__(NT) sample_draw_kernel(const T* __restrict__ l
     u64 pmass = __ldcg(&ws->pmass), cm = __ldcg(&ws->c_mass);
     int cc = __ldcg(&ws->c_cnt);
     u64 fmin = to_fx(mp);
+    u64 lowest = ~0ull;
     for (int i = tid; i < n; i += NT) {
       u64 me = __ldcg(&ws->list[i]);
       int gt = 0;
@@ -313,8 +339,14 @@ __global__ void __launch_bounds__(NT) sample_draw_kernel(const T* __restrict__ l
         u64 o = __ldcg(&ws->list[j]);
         if (o > me) { gt++; mgt += o; }
       }
-      if (cc + gt < k && cm + mgt < pmass) atomicMin(&s_tau, me);
+      if (cc + gt < k && cm + mgt < pmass && me < lowest) lowest = me;
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      u64 ov = __shfl_xor_sync(0xffffffffu, lowest, o);
+      lowest = ov < lowest ? ov : lowest;
+    }
+    if (lane == 0 && lowest != ~0ull) atomicMin(&s_tau, lowest);
     __syncthreads();
     u64 tau = s_tau;
     // the kept entries join their chunks (min-p applies to them like to everyone else)
