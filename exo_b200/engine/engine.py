@@ -18,7 +18,7 @@ from ..models.weights import ModelWeights, ShardSpec
 from ..ops import reference as ref
 from .executor import Executor
 from .kv import BlockAllocator, SamplingParams, Sequence
-from .plan import FLAG_EAGER, StepPlan
+from .plan import FLAG_EAGER, FLAG_NO_SAMPLE, StepPlan
 from .scheduler import Scheduler
 
 
@@ -157,8 +157,15 @@ class Engine:
         if self.plan_sink is not None:
             self.plan_sink(plan)
         self.exe.model.embed_patches = self._embed_patches(entries)
-        ids = self.exe.run(plan, proc)
-        sampled = self.exe.fetch(ids)
+        if plan.flags & FLAG_NO_SAMPLE:
+            # prompt chunks only: nothing to read back, so the host goes straight on to the next chunk while this one
+            # runs (and, with pipeline stages, while the later stages still work on it)
+            self.exe.run(plan)
+            sampled = np.zeros(plan.n_seqs, np.int32)
+            want_lp = False
+        else:
+            ids = self.exe.run(plan, proc)
+            sampled = self.exe.fetch(ids)
         lp = None
         if want_lp:
             k = max(1, max(s.params.top_logprobs for s, _ in entries))

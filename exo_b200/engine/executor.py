@@ -19,7 +19,7 @@ from .. import ops
 from ..models.config import ModelConfig
 from ..models.transformer import Decoder, KVPool, StepInputs
 from ..models.weights import ModelWeights, ShardSpec
-from .plan import HEADER, PlanLayout, StepPlan, bucket, FLAG_ALL_GREEDY, FLAG_EAGER
+from .plan import HEADER, PlanLayout, StepPlan, bucket, FLAG_ALL_GREEDY, FLAG_EAGER, FLAG_NO_SAMPLE
 
 DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 
@@ -102,15 +102,34 @@ class Executor:
                              samp["min_p"], samp["uniform"])
         return ids.to(torch.int32)
 
+    def _forward_only(self, inp: StepInputs) -> torch.Tensor:
+        """A step of prompt chunks none of which ends its sequence: the layers run (the KV cache fills), the vocabulary
+        projection and the sampler do not, and with pipeline stages nothing travels back, so a stage starts on the
+        next chunk as soon as it has handed this one on (the reference's ``pipeline_parallel_prefill``,
+        ``src/exo/worker/engines/mlx/generator/generate.py:164-279``)."""
+        spec, pipe = self.spec, self.pipe
+        h_in = None
+        if pipe is not None and not spec.is_first_stage:
+            h_in = pipe.recv_hidden(inp.tokens.shape[0], self.cfg.hidden, self._act_dtype(), self.device)
+        out = self.model.forward(inp, self.kv, h_in, need_logits=False)
+        if pipe is not None:
+            pipe.consumed()
+            if not spec.is_last_stage:
+                pipe.send_hidden(out)
+        return self.prev_sampled[:0]
+
+    def _act_dtype(self) -> torch.dtype:
+        return torch.bfloat16 if self.cfg.dtype == "bf16" else torch.float32
+
     def _forward_sample_pipelined(self, inp: StepInputs, samp: dict[str, torch.Tensor], greedy: bool) -> torch.Tensor:
         """One pipeline stage of a step: receive the residual stream, run this stage's layers, pass
         it on; the last stage samples and its ids go back to every stage of the lane."""
         spec, pipe = self.spec, self.pipe
         h_in = None
         if not spec.is_first_stage:
-            dt = torch.bfloat16 if self.cfg.dtype == "bf16" else torch.float32
-            h_in = pipe.recv_hidden(torch.empty(inp.tokens.shape[0], self.cfg.hidden, dtype=dt, device=self.device))
+            h_in = pipe.recv_hidden(inp.tokens.shape[0], self.cfg.hidden, self._act_dtype(), self.device)
         out = self.model.forward(inp, self.kv, h_in)
+        pipe.consumed()
         n = inp.logit_rows.numel()
         if spec.is_last_stage:
             logits = self.model.comm.gather_vocab(out)
@@ -171,6 +190,8 @@ class Executor:
             return out[:plan.n_seqs]
         inp, samp = self._views(L)
         inp.max_q_len = plan.max_q_len
+        if plan.flags & FLAG_NO_SAMPLE:
+            return self._forward_only(inp)
         if logits_processor is None:
             return self._forward_sample(inp, samp, greedy, from_prev)[:plan.n_seqs]
         # slow path (penalties / logit bias / logprobs): processor edits full logits before sampling

@@ -23,6 +23,7 @@ HEADER = 8
 FLAG_TOKENS_FROM_PREV = 1  # decode: take input tokens from the previous step's samples on device
 FLAG_ALL_GREEDY = 2
 FLAG_EAGER = 4             # the leader runs this step outside its CUDA graphs (logits processors): followers do the same
+FLAG_NO_SAMPLE = 8         # every row is a prompt chunk that stops short of its sequence's end: no logits, no ids, no read-back
 
 
 @dataclass

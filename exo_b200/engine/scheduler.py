@@ -17,7 +17,7 @@ from collections import deque
 import numpy as np
 
 from .kv import BlockAllocator, OutOfBlocks, Sequence
-from .plan import StepPlan, FLAG_ALL_GREEDY
+from .plan import StepPlan, FLAG_ALL_GREEDY, FLAG_NO_SAMPLE
 
 
 class Scheduler:
@@ -200,6 +200,7 @@ class Scheduler:
         bt = np.zeros((B, max_blocks), np.int32)
         t = 0
         all_greedy = True
+        samples = False
         for b, (s, n) in enumerate(entries):
             lo = s.n_computed
             blk = s.blocks_array()
@@ -215,6 +216,7 @@ class Scheduler:
             cu_q[b + 1] = t + n
             seq_lens[b] = lo + n
             if lo + n == s.n_tokens:  # the step reaches the sequence's last token → sample
+                samples = True
                 logit_rows[b] = t + n - 1
                 p = s.params
                 temp[b], top_p[b], min_p[b], top_k[b] = p.temperature, p.top_p, p.min_p, p.top_k
@@ -224,7 +226,7 @@ class Scheduler:
             bt[b, :len(blk)] = blk
             t += n
         return StepPlan(n_tokens=T, n_seqs=B, max_q_len=max(n for _, n in entries),
-                        flags=FLAG_ALL_GREEDY if all_greedy else 0, tokens=tokens, positions=positions, slots=slots,
+                        flags=(FLAG_ALL_GREEDY if all_greedy else 0) | (0 if samples else FLAG_NO_SAMPLE), tokens=tokens, positions=positions, slots=slots,
                         cu_q=cu_q, seq_lens=seq_lens, logit_rows=logit_rows, top_k=top_k, temperature=temp,
                         top_p=top_p, min_p=min_p, uniform=uni, prev_rows=np.full(B, -1, np.int32), block_tables=bt,
                         req_ids=tuple(s.req_id for s, _ in entries))

@@ -184,9 +184,10 @@ class Decoder:
         return self.comm.row_sum(y, h)      # may stay pending: the next layer's norm is fused into the reduction
 
     # ------------------------------------------------------------------ forward
-    def forward(self, inp: StepInputs, kv: KVPool, hidden_in: torch.Tensor | None = None):
+    def forward(self, inp: StepInputs, kv: KVPool, hidden_in: torch.Tensor | None = None, need_logits: bool = True):
         """Run this shard over the residual stream ``h [T, H]``.  The last pipeline stage returns
-        local-vocab logits ``[B', V/N]``; other stages return ``h`` to send to the next stage."""
+        local-vocab logits ``[B', V/N]`` (``None`` when the caller needs none: a prompt chunk that only fills the
+        cache); other stages return ``h`` to send to the next stage."""
         cfg, w = self.cfg, self.w
         h = ops.embedding(w.embed, inp.tokens) if self.spec.is_first_stage else hidden_in
         patches = getattr(self, "embed_patches", None)
@@ -200,6 +201,9 @@ class Decoder:
             h = self._ffn_moe(lw, h) if cfg.layer_is_moe(i) else self._ffn_dense(lw, h)
         if not self.spec.is_last_stage:
             return resolve(h)
+        if not need_logits:
+            resolve(h)          # completes the last layer's reduction on every rank alike
+            return None
         # only the rows whose logits are needed go through the final norm + vocabulary GEMM
         hs = h if (inp.max_q_len == 1 and inp.logit_rows.numel() == h.shape[0]) else resolve(h)[inp.logit_rows.long()]
         return ops.norm_linear(hs, w.final_norm, cfg.rms_eps, w.lm_head)

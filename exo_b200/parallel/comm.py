@@ -14,6 +14,8 @@ in the reference's ``PipelineFirstLayer`` / ``PipelineLastLayer`` (``auto_parall
 """
 from __future__ import annotations
 
+from collections import deque
+
 import torch
 import torch.distributed as dist
 
@@ -78,6 +80,8 @@ class PipeComm:
     (4 bytes per sequence) travel back.
     """
 
+    RX_SLOTS = 3
+
     def __init__(self, pp_rank: int, pp_size: int, tp_rank: int, tp_size: int, lane_group=None):
         self.pp_rank, self.pp_size = pp_rank, pp_size
         self.lane_group = lane_group          # the pp_size ranks that share this tp_rank
@@ -86,18 +90,70 @@ class PipeComm:
         self.next = g(pp_rank + 1) if pp_rank < pp_size - 1 else None
         self.last = g(pp_size - 1)
         self.n_hops = 0
+        # CUDA: hops run beside the compute stream.  Receives land in a ring of buffers this object owns (memory the
+        # caching allocator may hand out again is not safe to fill from another stream), each reusable once the step
+        # that read it has been enqueued and its event has passed; sends are started when the stage's output is ready
+        # and the compute stream goes on without waiting for the peer to take them.
+        self.stream = None
+        self.rx: list[torch.Tensor] = []
+        self.rx_done: list = [None] * self.RX_SLOTS
+        self.rx_last = -1
+        self.sends: deque = deque()
 
-    def recv_hidden(self, like: torch.Tensor) -> torch.Tensor:
-        buf = like.float() if (like.device.type == "cpu" and like.dtype == torch.bfloat16) else like
-        dist.recv(buf, self.prev)
+    def _ring(self, T: int, hidden: int, dtype, device) -> torch.Tensor:
+        if self.stream is None:
+            self.stream = torch.cuda.Stream(device=device)
+        if not self.rx or self.rx[0].shape[0] < T or self.rx[0].dtype != dtype:
+            rows = max(T, self.rx[0].shape[0] if self.rx else 0)
+            torch.cuda.current_stream(device).synchronize()      # rare: the first step, or a larger chunk than any before
+            self.stream.synchronize()
+            self.rx = [torch.empty(rows, hidden, dtype=dtype, device=device) for _ in range(self.RX_SLOTS)]
+            self.rx_done = [None] * self.RX_SLOTS
+        self.rx_last = (self.rx_last + 1) % self.RX_SLOTS
+        return self.rx[self.rx_last][:T]
+
+    def recv_hidden(self, T: int, hidden: int, dtype, device) -> torch.Tensor:
+        """The residual stream ``[T, hidden]`` of this step from the previous stage."""
+        device = torch.device(device)
         self.n_hops += 1
-        return buf.to(like.dtype)
+        if device.type != "cuda":
+            buf = torch.empty(T, hidden, dtype=torch.float32 if dtype == torch.bfloat16 else dtype)   # gloo has no bf16
+            dist.recv(buf, self.prev)
+            return buf.to(dtype)
+        buf = self._ring(T, hidden, dtype, device)
+        done = self.rx_done[self.rx_last]
+        if done is not None:
+            self.stream.wait_event(done)
+        with torch.cuda.stream(self.stream):
+            work = dist.irecv(buf, self.prev)
+        work.wait()                          # the compute stream waits for the data, the host does not
+        return buf
+
+    def consumed(self) -> None:
+        """The step that read the last received buffer has been enqueued on the current stream."""
+        if self.stream is not None and self.rx_last >= 0 and self.rx:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.rx[0].device))
+            self.rx_done[self.rx_last] = ev
 
     def send_hidden(self, h: torch.Tensor) -> None:
-        if h.device.type == "cpu" and h.dtype == torch.bfloat16:
-            h = h.float()
-        dist.send(h.contiguous(), self.next)
         self.n_hops += 1
+        if h.device.type != "cuda":
+            dist.send((h.float() if h.dtype == torch.bfloat16 else h).contiguous(), self.next)
+            return
+        if self.stream is None:
+            self.stream = torch.cuda.Stream(device=h.device)
+        h = h.contiguous()
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(h.device))
+        self.stream.wait_event(ready)
+        with torch.cuda.stream(self.stream):
+            work = dist.isend(h, self.next)
+        h.record_stream(self.stream)
+        self.sends.append((work, h))         # the tensor stays referenced until the transfer is known to be over
+        while len(self.sends) > 4:
+            old, _ = self.sends.popleft()
+            old.wait()
 
     def share_ids(self, ids: torch.Tensor) -> torch.Tensor:
         dist.broadcast(ids, src=self.last, group=self.lane_group)

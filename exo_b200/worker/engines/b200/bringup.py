@@ -317,13 +317,11 @@ class B200Builder(Builder):
         assert self.cfg is not None and self.weights is not None
         cfg = self.cfg
         if self.spec.tp_size > 1:
-            # the peer-memory collectives span the whole rank group: with pipeline stages the TP group is a
-            # subset, and the stage-local all-reduce goes through the process group instead
-            if (self.device.type == "cuda" and cfg.dtype == "bf16" and self.spec.pp_size == 1
-                    and os.environ.get("EXO_COMM", "fused") == "fused"):
+            # the peer-memory collectives span one tensor-parallel group: the whole instance, or one pipeline stage
+            if self.device.type == "cuda" and cfg.dtype == "bf16" and os.environ.get("EXO_COMM", "fused") == "fused":
                 from ....parallel.fused import FusedComm
                 self.comm = FusedComm(self.device, max_rows=constants.PREFILL_CHUNK, hidden=cfg.hidden,
-                                      vocab_shard=vocab_shard(cfg.vocab, self.spec.tp_size))
+                                      vocab_shard=vocab_shard(cfg.vocab, self.spec.tp_size), group=self.tp_group)
             else:
                 from ....parallel.comm import DistComm
                 self.comm = DistComm(self.tp_group)

@@ -57,3 +57,32 @@ def test_block_pool_is_conserved_across_preemption_and_finish():
         _run_step(sched)
     assert not sched.has_work
     assert alloc.n_free == 4 and all(r == 0 for r in alloc.ref)
+
+
+def test_prompt_chunks_short_of_the_end_carry_the_no_sample_flag_and_skip_the_read_back():
+    """A 100-token prompt in chunks of 32: the first three steps neither project logits nor read ids back; the fourth
+    (which reaches the last prompt token) samples.  A decode row riding along makes the step sample again."""
+    import torch
+
+    from exo_b200.engine.engine import Engine
+    from exo_b200.engine.plan import FLAG_NO_SAMPLE
+    from exo_b200.models.config import preset
+    from exo_b200.models.weights import RandomSource, ShardSpec, build_weights
+    alloc = BlockAllocator(32, 16)
+    sched = Scheduler(alloc, max_seqs=4, prefill_chunk=32, max_blocks_per_seq=16)
+    greedy = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    sched.add(Sequence("long", list(range(100)), greedy, use_prefix_cache=False))
+    flags = []
+    for _ in range(5):
+        plan, _ = _run_step(sched)
+        flags.append(bool(plan.flags & FLAG_NO_SAMPLE))
+    assert flags == [True, True, True, False, False]
+    # through the engine: the fetches counted are those of sampling steps only, and the tokens equal a one-chunk run
+    cfg = preset("tiny-llama")
+    w = build_weights(cfg, ShardSpec(), RandomSource(seed=0), device="cpu")
+    prompt = [int(t) for t in torch.randint(0, cfg.vocab, (100,), generator=torch.Generator().manual_seed(3))]
+    chunked = Engine(cfg, w, n_blocks=32, device="cpu", prefill_chunk=32)
+    whole = Engine(cfg, w, n_blocks=32, device="cpu", prefill_chunk=256)
+    a = chunked.generate(prompt, greedy)
+    assert a == whole.generate(prompt, greedy)
+    assert chunked.n_steps == 3 + 4 and chunked.exe.d2h_bytes == 4 * 4 and whole.exe.d2h_bytes == 4 * 4
