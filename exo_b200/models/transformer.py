@@ -126,6 +126,31 @@ class Decoder:
         else:
             self.scale = cfg.head_dim ** -0.5
 
+    def _mega_ready(self, kv: "KVPool", tokens: torch.Tensor) -> bool:
+        """Whether the whole-step decode kernel serves this shard (decided once): a dense bf16 model held by one rank,
+        128-wide heads, no attention sinks or sliding window, shapes the kernel is built for."""
+        state = getattr(self, "_mega", None)
+        if state is None:
+            cfg, spec = self.cfg, self.spec
+            ok = (tokens.is_cuda and tokens.dtype == torch.int32 and cfg.dtype == "bf16" and spec.tp_size == 1
+                  and spec.pp_size == 1 and not cfg.mla and isinstance(self.w.embed, torch.Tensor)
+                  and self.w.embed.dtype == torch.bfloat16
+                  and not cfg.is_moe and not cfg.sliding_window and not cfg.attn_sinks and isinstance(self.comm, LocalComm)
+                  and isinstance(self.w.lm_head, torch.Tensor) and self.w.lm_head.dtype == torch.bfloat16
+                  and getattr(self, "embed_patches", None) is None)
+            if ok:
+                from ..ops import cuda as K
+                layers = [self.w.layers[i] for i in spec.layers(cfg)]
+                ok = K.DecodeMega.supported(cfg, layers, self.n_q, self.n_kv, self.inv_freq)
+                if ok:
+                    self._mega = K.DecodeMega(cfg, layers, [kv.layers[i] for i in spec.layers(cfg)], self.w.embed,
+                                              self.w.final_norm, self.w.lm_head, self.n_q, self.n_kv, tokens.device)
+                    self._mega_kv = kv
+            if not ok:
+                self._mega = False
+            state = self._mega
+        return bool(state) and self._mega_kv is kv and not getattr(self, "embed_patches", None)
+
     # ------------------------------------------------------------------ attention
     def _attn_gqa(self, lw, h, inp: StepInputs, kv) -> torch.Tensor:
         cfg = self.cfg
@@ -189,6 +214,10 @@ class Decoder:
         local-vocab logits ``[B', V/N]`` (``None`` when the caller needs none: a prompt chunk that only fills the
         cache); other stages return ``h`` to send to the next stage."""
         cfg, w = self.cfg, self.w
+        if need_logits and inp.max_q_len == 1 and inp.tokens.shape[0] == 1 and self._mega_ready(kv, inp.tokens):
+            # batch-1 decode of a dense model on one GPU: the whole step, embedding to logits, is one persistent kernel
+            return self._mega(inp.tokens, inp.positions, inp.slots, inp.block_tables, inp.seq_lens, self.inv_freq,
+                              self.rope_mscale, cfg.rms_eps, self.scale)
         h = ops.embedding(w.embed, inp.tokens) if self.spec.is_first_stage else hidden_in
         patches = getattr(self, "embed_patches", None)
         if patches and self.spec.is_first_stage:      # input embeddings supplied by the caller (image features); prefill steps only

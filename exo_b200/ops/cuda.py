@@ -50,6 +50,10 @@ class _Sig:
     exo_argmax_chunks = (_i, [_i, _i])
     exo_argmax = (_i, [_p, _p, _p, _p, _i, _i, _i, _l, _i, _p])
     exo_sample = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _l, _i, _p])
+    exo_decode_mega_variant = (_i, [_i, _i, _i, _i, _i, _i])
+    exo_decode_mega_workspace = (_l, [_i, _i, _i, _i])
+    exo_decode_mega = (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _f, _f, _f, _i, _i, _i, _i, _i, _i, _i,
+                            _i, _p, _p])
     exo_sample_workspace = (_l, [_i])
     exo_sample_fast = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _l, _i, _p])
     exo_paged_decode_workspace = (_l, [_i, _i, _i, _i])
@@ -495,6 +499,78 @@ def argmax(logits):
                         _st()), "argmax")
     _count(2)
     return out
+
+
+# ---- whole-step decode kernel (batch 1, dense models, one GPU) -----------------------------------------------------
+# Off unless asked for: on Llama-3.1-8B the one-kernel step measured slower than the per-op path (the five dependent phases
+# of a layer each stall the weight stream for a few microseconds, which the per-op kernels overlap through PDL).
+use_decode_mega = os.environ.get("EXO_DECODE_MEGA") == "1"
+
+
+class DecodeMega:
+    """Device-side tables and scratch of ``exo_decode_mega`` for one model shard: built once, reused every step."""
+
+    FIELDS = ("wqkv", "bqkv", "wo", "w_gate_up", "w_down", "attn_norm", "ffn_norm", "q_norm", "k_norm")
+
+    def __init__(self, cfg, layers, kv_layers, embed, final_norm, lm_head, n_q, n_kv, device):
+        lib = load()
+        rows = []
+        self.keep = []
+        for lw, (kc, vc) in zip(layers, kv_layers):
+            ptrs = []
+            for f in self.FIELDS:
+                t = getattr(lw, f, None)
+                ptrs.append(0 if t is None else t.data_ptr())
+                if t is not None and not t.is_contiguous():
+                    raise ValueError(f"{f} must be contiguous")
+            rows.append(ptrs + [kc.data_ptr(), vc.data_ptr()])
+            self.keep.append((lw, kc, vc))
+        self.table = torch.tensor(rows, dtype=torch.int64).to(device)
+        self.n_layers = len(rows)
+        H, F = cfg.hidden, lw.w_down.shape[1]
+        self.H, self.F, self.n_q, self.n_kv, self.D = H, F, n_q, n_kv, cfg.head_dim
+        self.embed, self.final_norm, self.lm_head, self.vocab = embed, final_norm, lm_head, lm_head.shape[0]
+        self.ws = torch.zeros(int(lib.exo_decode_mega_workspace(H, F, n_q, n_kv)), dtype=torch.uint8, device=device)
+        self.block_size = kv_layers[0][0].shape[1]
+        self.n_sm = torch.cuda.get_device_properties(device).multi_processor_count
+        self.trace = (torch.zeros(148 * 1024, dtype=torch.int64, device=device)
+                      if os.environ.get("EXO_DECODE_MEGA_TRACE") == "1" else None)
+
+    @staticmethod
+    def supported(cfg, layers, n_q, n_kv, inv_freq) -> bool:
+        if not use_decode_mega or not layers:
+            return False
+        lw = layers[0]
+        plain = all(isinstance(getattr(l, f, None), torch.Tensor) and getattr(l, f).dtype == torch.bfloat16
+                    for l in layers for f in ("wqkv", "wo", "w_gate_up", "w_down"))
+        if not plain:
+            return False
+        F = lw.w_down.shape[1]
+        return bool(load().exo_decode_mega_variant(cfg.hidden, F, n_q, n_kv, cfg.head_dim, inv_freq.numel() * 2))
+
+    def __call__(self, tokens, positions, slots, block_table, seq_lens, inv_freq, mscale, eps, scale):
+        """One decode step from the token id ``tokens [1]`` (int32) to ``logits [1, vocab]``."""
+        logits = torch.empty(1, self.vocab, dtype=torch.bfloat16, device=tokens.device)
+        _chk(load().exo_decode_mega(_ptr(self.table), self.n_layers, _ptr(self.embed), _ptr(tokens), _ptr(self.final_norm),
+                                    _ptr(self.lm_head), _ptr(logits), self.vocab, _ptr(self.ws), _ptr(positions), _ptr(slots),
+                                    _ptr(block_table), _ptr(seq_lens), _ptr(inv_freq), float(mscale), float(eps),
+                                    float(scale), inv_freq.numel() * 2, self.H, self.F, self.n_q, self.n_kv, self.D,
+                                    self.block_size, self.n_sm, _ptr(self.trace), _st()), "decode_mega")
+        _count()
+        return logits
+
+    def arrivals_us(self) -> torch.Tensor:
+        """With the trace on: ``[n_ctas, 2 + 5 * n_layers]`` microseconds (relative to the earliest stamp) at which each
+        CTA started and then finished each phase of the last step (per layer: QKV, attention, O, gate/up, down; last
+        the vocabulary projection)."""
+        t = self.trace.view(148, 1024).cpu()[: min(148, self.n_sm), : 2 + 5 * self.n_layers].double()
+        return (t - t.min()) / 1e3
+
+    def cycles(self) -> torch.Tensor:
+        """With the trace on: ``[3, n_ctas, 2 + 5 * n_layers]`` cumulative SM cycles that one warp of each CTA had spent
+        waiting for weight stages, computing, and waiting at the block barrier by the end of each phase."""
+        t = self.trace.view(148, 4, 256).cpu()[: min(148, self.n_sm), 1:, : 2 + 5 * self.n_layers].double()
+        return t.permute(1, 0, 2)
 
 
 _sample_ws: dict[int, tuple[int, torch.Tensor]] = {}      # device index -> zero-initialised scratch of the multi-CTA sampler

