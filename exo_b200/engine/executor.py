@@ -56,6 +56,8 @@ class Executor:
         self.use_graphs = (self.cuda and mla_ok) if use_graphs is None else use_graphs
         if self.cuda and os.environ.get("EXO_KERNEL_CHECKS") == "1":
             self.use_graphs = False       # the checking flavour synchronises after every op: nothing can be captured
+        if self.pipe is not None:
+            self.use_graphs = False       # stage hops run on a side stream and wait on the peer: not capturable
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self.out_host = torch.zeros(self.max_B, dtype=torch.int32, pin_memory=self.cuda)
         self.prev_sampled = torch.zeros(max(self.max_B, 256), dtype=torch.int32, device=self.device)

@@ -46,6 +46,7 @@ class ModelConfig:
     rope: RopeConfig = field(default_factory=RopeConfig)
     tie_embeddings: bool = False
     qk_norm: bool = False  # per-head RMSNorm on q and k (Qwen3)
+    qk_norm_full: bool = False  # RMSNorm over the whole q and the whole k projection, all heads together (MiniMax)
     attn_bias: bool = False
     max_position: int = 131072
     dtype: str = "bf16"  # bf16 | fp32
@@ -171,7 +172,8 @@ class ModelConfig:
                   "qwen2": "llama", "qwen3": "qwen3",
                   "qwen3_moe": "qwen3_moe", "deepseek_v3": "deepseek_v3", "deepseek_v32": "deepseek_v3",
                   "deepseek_v2": "deepseek_v3", "kimi_k2": "deepseek_v3", "glm4_moe_lite": "deepseek_v3",
-                  "glm4_moe": "glm4_moe", "mixtral": "mixtral", "gpt_oss": "gpt_oss"}.get(mt, "llama")
+                  "glm4_moe": "glm4_moe", "mixtral": "mixtral", "minimax": "minimax", "minimax_m2": "minimax",
+                  "gpt_oss": "gpt_oss"}.get(mt, "llama")
         mc = ModelConfig(
             name=name, family=family,
             n_layers=g("num_hidden_layers", "n_layer"), hidden=hidden, n_heads=n_heads,
@@ -208,6 +210,18 @@ class ModelConfig:
             mc.router_bias = True
             if "partial_rotary_factor" not in cfg:
                 mc.rope.partial_rotary_factor = 0.5
+        if family == "minimax":
+            # MiniMax-M2: every layer sparse (sigmoid scores + correction bias, no shared expert), q / k normalised
+            # over their whole width, rotary on the first `rotary_dim` of each head
+            mc.n_experts = g("num_local_experts", default=0)
+            mc.n_experts_per_tok = g("num_experts_per_tok", default=0)
+            mc.moe_ffn = g("intermediate_size")
+            mc.router = "sigmoid"
+            mc.router_bias = True
+            mc.norm_topk_prob = True
+            mc.qk_norm_full = bool(g("use_qk_norm", default=True))
+            if g("rotary_dim", default=None):
+                mc.rope.partial_rotary_factor = g("rotary_dim") / mc.head_dim
         if family == "mixtral":
             # every layer is a sparse block: softmax over the top-k router logits (= softmax then renormalise)
             mc.n_experts = g("num_local_experts", default=8)
@@ -293,6 +307,10 @@ def preset(name: str) -> ModelConfig:
     if n in ("tiny-mixtral",):     # every layer sparse, top-2 softmax, block_sparse_moe.* tensor names
         return ModelConfig(name="tiny-mixtral", family="mixtral", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
                            ffn=512, vocab=1024, n_experts=4, n_experts_per_tok=2, moe_ffn=256, router="softmax", dtype="fp32")
+    if n in ("tiny-minimax",):     # full-width q/k norm, half-rotary, sigmoid router with correction bias on every layer
+        return ModelConfig(name="tiny-minimax", family="minimax", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                           ffn=512, vocab=1024, qk_norm_full=True, rope=RopeConfig(theta=10000.0, partial_rotary_factor=0.5),
+                           n_experts=8, n_experts_per_tok=2, moe_ffn=128, router="sigmoid", router_bias=True, dtype="fp32")
     if n in ("tiny-gpt-oss",):     # attention sinks and a sliding window on every other layer's worth of context
         return ModelConfig(name="tiny-gpt-oss", family="gpt_oss", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
                            ffn=512, vocab=1024, attn_bias=True, attn_sinks=True, sliding_window=32, dtype="fp32")
@@ -310,4 +328,4 @@ def preset(name: str) -> ModelConfig:
 
 
 PRESETS = ("tiny-llama", "llama-3.1-8b", "llama-3.1-70b", "qwen3-235b-a22b", "deepseek-v3", "tiny-moe", "tiny-mla",
-           "tiny-qwen3", "tiny-qwen2", "tiny-glm4-moe", "tiny-mixtral", "tiny-gpt-oss", "tiny-yarn")
+           "tiny-qwen3", "tiny-qwen2", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-yarn")

@@ -71,6 +71,9 @@ class OracleModel:
                 q = q + self.W(p + "q_proj.bias", (c.n_heads * D,))
                 k = k + self.W(p + "k_proj.bias", (c.n_kv_heads * D,))
                 v = v + self.W(p + "v_proj.bias", (c.n_kv_heads * D,))
+            if c.qk_norm_full:
+                q = self._norm(q, self.W(p + "q_norm.weight", (c.n_heads * D,)), c.rms_eps)
+                k = self._norm(k, self.W(p + "k_norm.weight", (c.n_kv_heads * D,)), c.rms_eps)
             q, k, v = q.view(T, c.n_heads, D), k.view(T, c.n_kv_heads, D), v.view(T, c.n_kv_heads, D)
             if c.qk_norm:
                 q = self._norm(q, self.W(p + "q_norm.weight", (D,)), c.rms_eps)
@@ -113,7 +116,7 @@ class OracleModel:
         if not c.layer_is_moe(i):
             return mlp(p, c.ffn, x)
         logits = x @ self.W(p + "gate.weight", (c.n_experts, H)).t()
-        bias = self.src.get(p + "gate.e_score_correction_bias", (c.n_experts,)) if c.router_bias else None
+        bias = self.src.get(p + nm["bias"], (c.n_experts,)) if c.router_bias else None
         wts, ids = ref.moe_route(logits, c.n_experts_per_tok, c.router, c.norm_topk_prob, bias, c.n_group,
                                  c.topk_group, c.routed_scaling)
         y = torch.zeros_like(x)

@@ -35,6 +35,10 @@ class LocalComm:
     def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         return x if residual is None else x + residual
 
+    def all_reduce_stat(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum of a few fp32 numbers per token over the ranks (normalisation statistics)."""
+        return x
+
     def row_sum(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         return self.all_reduce(x, residual)
 
@@ -156,11 +160,33 @@ class Decoder:
         cfg = self.cfg
         qkv = ops.norm_linear(h, lw.attn_norm, cfg.rms_eps, lw.wqkv, lw.bqkv)
         kc, vc = kv
+        q_norm, k_norm = lw.q_norm, lw.k_norm
+        if cfg.qk_norm_full:
+            qkv = self._full_width_qk_norm(qkv, lw)
+            q_norm = k_norm = None
         q = ops.qk_rope_append(qkv, inp.positions, self.inv_freq, self.rope_mscale, self.n_q, self.n_kv,
-                               cfg.head_dim, kc, vc, inp.slots, lw.q_norm, lw.k_norm, cfg.rms_eps)
+                               cfg.head_dim, kc, vc, inp.slots, q_norm, k_norm, cfg.rms_eps)
         o = ops.paged_attention(q, kc, vc, inp.block_tables, inp.seq_lens, inp.cu_q, self.scale,
                                 cfg.sliding_window, lw.sinks, inp.max_q_len)
         return self.comm.row_linear(o.reshape(o.shape[0], -1), lw.wo, h)
+
+    def _full_width_qk_norm(self, qkv: torch.Tensor, lw) -> torch.Tensor:
+        """RMSNorm of q over ALL query heads and of k over ALL key heads (MiniMax).  Under tensor parallelism a rank
+        holds a slice of the columns: the ranks sum their sums of squares (two numbers per token) instead of gathering
+        q and k, which is what the reference does (``src/exo/worker/engines/mlx/auto_parallel.py:1023-1048``).  A KV head
+        that several ranks replicate is counted once."""
+        cfg, D = self.cfg, self.cfg.head_dim
+        nq, nk = self.n_q * D, self.n_kv * D
+        q, k = qkv[:, :nq].float(), qkv[:, nq:nq + nk].float()
+        rep = max(1, self.spec.tp_size * self.n_kv // cfg.n_kv_heads)         # ranks holding each KV head
+        ss = torch.stack((q.pow(2).sum(-1), k.pow(2).sum(-1) / rep), -1)
+        ss = self.comm.all_reduce_stat(ss)
+        rq = torch.rsqrt(ss[:, :1] / (cfg.n_heads * D) + cfg.rms_eps)
+        rk = torch.rsqrt(ss[:, 1:] / (cfg.n_kv_heads * D) + cfg.rms_eps)
+        out = qkv.clone()
+        out[:, :nq] = (q * rq * lw.q_norm.float()).to(qkv.dtype)
+        out[:, nq:nq + nk] = (k * rk * lw.k_norm.float()).to(qkv.dtype)
+        return out
 
     def _attn_mla(self, lw, h, inp: StepInputs, kv) -> torch.Tensor:
         cfg = self.cfg

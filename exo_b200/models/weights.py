@@ -316,9 +316,11 @@ class ModelWeights:
 def moe_names(cfg: ModelConfig) -> dict[str, str]:
     """Checkpoint tensor names of a sparse block: Mixtral keeps ``block_sparse_moe.experts.N.w1 / w3 / w2`` (gate, up,
     down); the DeepSeek / Qwen / GLM families ``mlp.experts.N.gate_proj / up_proj / down_proj``."""
-    if cfg.family == "mixtral":
-        return {"prefix": "block_sparse_moe.", "gate": "w1.weight", "up": "w3.weight", "down": "w2.weight"}
-    return {"prefix": "mlp.", "gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+    if cfg.family in ("mixtral", "minimax"):
+        return {"prefix": "block_sparse_moe.", "gate": "w1.weight", "up": "w3.weight", "down": "w2.weight",
+                "bias": "e_score_correction_bias"}
+    return {"prefix": "mlp.", "gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight",
+            "bias": "gate.e_score_correction_bias"}
 
 
 QUANTIZED_FIELDS = ("wqkv", "wo", "w_gate_up", "w_down", "e_gate_up", "e_down", "s_gate_up", "s_down", "wq_a", "wq_b", "wkv_a")
@@ -388,6 +390,9 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             if cfg.qk_norm:
                 lw.q_norm = fin(src.get(a + "q_norm.weight", (D,)))
                 lw.k_norm = fin(src.get(a + "k_norm.weight", (D,)))
+            if cfg.qk_norm_full:      # one weight per output column of q / k: this rank's slice of it
+                lw.q_norm = fin(_rows(src.get(a + "q_norm.weight", (cfg.n_heads * D,)), r, n))
+                lw.k_norm = fin(src.get(a + "k_norm.weight", (cfg.n_kv_heads * D,))[klo * D:khi * D])
             if cfg.attn_sinks:
                 lw.sinks = fin(_rows(src.get(a + "sinks", (cfg.n_heads,)), r, n), torch.float32)
         m = p + moe_names(cfg)["prefix"]
@@ -396,7 +401,7 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             nm = moe_names(cfg)
             lw.router = fin(src.get(m + "gate.weight", (E, H)))
             if cfg.router_bias:
-                lw.router_bias = fin(src.get(m + "gate.e_score_correction_bias", (E,)), torch.float32)
+                lw.router_bias = fin(src.get(m + nm["bias"], (E,)), torch.float32)
             elo, ehi = expert_range(cfg, spec)
             gus, dns = [], []
             for e in range(elo, ehi):
@@ -486,6 +491,10 @@ def _fast_shard(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device) ->
             if cfg.qk_norm:
                 lw.q_norm = torch.ones(D, dtype=dt, device=device)
                 lw.k_norm = torch.ones(D, dtype=dt, device=device)
+            if cfg.qk_norm_full:
+                hq, hkv = local_heads(cfg, spec)
+                lw.q_norm = torch.ones(hq * D, dtype=dt, device=device)
+                lw.k_norm = torch.ones(hkv * D, dtype=dt, device=device)
         if cfg.layer_is_moe(i):
             E, F = cfg.n_experts, cfg.moe_ffn
             el = E // n

@@ -42,6 +42,11 @@ class DistComm:
         self.n_collectives += 1
         return x if residual is None else x + residual
 
+    def all_reduce_stat(self, x: torch.Tensor) -> torch.Tensor:
+        x = x.contiguous()
+        dist.all_reduce(x, group=self.group)
+        return x
+
     def row_linear(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         return self.all_reduce(ops.linear(x, w), residual)
 

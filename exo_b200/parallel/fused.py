@@ -564,6 +564,13 @@ class FusedComm:
     def barrier(self) -> None:
         dist.barrier(group=self.group)
 
+    def all_reduce_stat(self, x: torch.Tensor) -> torch.Tensor:
+        """A few fp32 numbers per token (normalisation statistics): the process group's all-reduce, which is
+        stream-ordered and capturable; the arenas carry bf16 rows."""
+        x = x.contiguous()
+        dist.all_reduce(x, group=self.group)
+        return x
+
     def close(self) -> None:
         """Ordered teardown: every rank is idle before any mapping goes away (the multicast binding first)."""
         if not self.peers:

@@ -37,6 +37,9 @@ CASES = {
                        "kv_lora_rank": 32, "qk_nope_head_dim": 16, "qk_rope_head_dim": 16, "v_head_dim": 16,
                        "norm_topk_prob": True, "routed_scaling_factor": 1.0, "n_group": 1, "topk_group": 1},
                       dict(family="deepseek_v3", mla=True, is_moe=True, router="sigmoid")),
+    "minimax": ({"model_type": "minimax_m2", "num_local_experts": 8, "num_experts_per_tok": 2, "use_qk_norm": True,
+                 "rotary_dim": 16},
+                dict(family="minimax", is_moe=True, router="sigmoid", router_bias=True, qk_norm_full=True, moe_ffn=256)),
     "qwen2": ({"model_type": "qwen2", "tie_word_embeddings": True}, dict(family="llama", attn_bias=True, tie_embeddings=True)),
 }
 
@@ -75,7 +78,7 @@ class Recorder(RandomSource):
         return t
 
 
-@pytest.mark.parametrize("name", ["mixtral", "glm4-moe", "glm4-moe-lite", "ministral"])
+@pytest.mark.parametrize("name", ["mixtral", "glm4-moe", "glm4-moe-lite", "ministral", "minimax"])
 def test_checkpoint_under_family_names_loads_and_matches_oracle(name, tmp_path):
     extra, _ = CASES[name]
     d = tmp_path / name
@@ -90,6 +93,9 @@ def test_checkpoint_under_family_names_loads_and_matches_oracle(name, tmp_path):
     names = set(rec.seen)
     if name == "mixtral":
         assert any(".block_sparse_moe.experts.0.w1.weight" in n for n in names) and not any(".mlp." in n for n in names)
+    if name == "minimax":
+        assert any(n.endswith("block_sparse_moe.e_score_correction_bias") for n in names)
+        assert rec.seen["model.layers.0.self_attn.q_norm.weight"].shape == (4 * 32,) and cfg.rope.partial_rotary_factor == 0.5
     if name.startswith("glm4-moe"):
         assert any(n.endswith("mlp.gate.e_score_correction_bias") for n in names)
         assert any(n.endswith("layers.0.mlp.gate_proj.weight") for n in names)       # the leading dense layer

@@ -39,10 +39,11 @@ def _worker(rank, world, port, name, prompt, n_new, q):
 # One row per checkpoint family / block feature the engine shards (the reference's counterpart is its table of tiny
 # random-init configs, ``src/exo/worker/tests/unittests/test_mlx/test_tp_bit_exact.py:15-307``): Llama, Qwen2 (biases,
 # tied embeddings), Qwen3 (q/k norm), Qwen3-MoE, DeepSeek-V3 / Kimi / GLM-MoE-Lite (MLA + sigmoid experts), GLM-4.x-MoE
-# (half-rotary, biases, shared expert), Mixtral (block_sparse_moe), GPT-OSS attention (sinks + sliding window), YaRN.
+# (half-rotary, biases, shared expert), Mixtral (block_sparse_moe), MiniMax (q/k norm over all heads: a cross-rank
+# statistic; KV heads replicated at 4 ranks), GPT-OSS attention (sinks + sliding window), YaRN.
 FAMILIES = [("tiny-llama", 2), ("tiny-llama", 4), ("tiny-moe", 2), ("tiny-mla", 2), ("tiny-mla", 4), ("tiny-qwen3", 2),
             ("tiny-qwen2", 2), ("tiny-glm4-moe", 2), ("tiny-glm4-moe", 4), ("tiny-mixtral", 2), ("tiny-mixtral", 4),
-            ("tiny-gpt-oss", 2), ("tiny-yarn", 2)]
+            ("tiny-minimax", 2), ("tiny-minimax", 4), ("tiny-gpt-oss", 2), ("tiny-yarn", 2)]
 
 
 @pytest.mark.parametrize("name,world", FAMILIES)
