@@ -141,18 +141,28 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--use-prefix-cache", action="store_true")
     ap.add_argument("--model-dir", default=None, help="local checkpoint directory: exact prompt sizing with its tokenizer")
     ap.add_argument("--place", action="store_true", help="place an instance first (and delete it afterwards)")
-    ap.add_argument("--sharding", default="Tensor", choices=["Tensor", "Pipeline"])
+    ap.add_argument("--sharding", default="Tensor", choices=["Tensor", "Pipeline", "both"])
+    ap.add_argument("--instance-meta", default="any")
     ap.add_argument("--min-nodes", type=int, default=1)
+    ap.add_argument("--max-nodes", type=int, default=0)
+    ap.add_argument("--settle-timeout", type=float, default=60.0)
+    ap.add_argument("--ready-timeout", type=float, default=1800.0)
+    ap.add_argument("--danger-delete-downloads", action="store_true")
+    ap.add_argument("--reuse-instance", action="store_true")
     ap.add_argument("--json-out", default=None)
     ap.add_argument("--stdout", action="store_true")
     a = ap.parse_args(argv)
     client = ExoClient(a.host, a.port)
-    placed = None
+    harness = None
     if a.place:
-        client.place(a.model, a.sharding, a.min_nodes)
-    iid = client.wait_ready(a.model)
-    if a.place:
-        placed = iid
+        # resolve the name, wait for a placement of the wanted shape, make room and download, launch, wait until ready
+        from .harness import Harness
+        harness = Harness(client, log=lambda m: print(m, file=sys.stderr))
+        a.model, _iid, dl = harness.instance_for(a)
+        if dl is not None:
+            print(f"downloaded in {dl:.0f}s", file=sys.stderr)
+    else:
+        client.wait_ready(a.model)
     counter = local_token_counter(a.model_dir) or server_token_counter(client, a.model)
     out = open(a.json_out, "a") if a.json_out else None
     rc = 0
@@ -185,8 +195,8 @@ def main(argv: list[str] | None = None) -> int:
     finally:
         if out:
             out.close()
-        if placed:
-            client.delete_instance(placed)
+        if harness is not None:
+            harness.teardown()
     return rc
 
 

@@ -13,6 +13,7 @@ constexpr int BK = 64;   // K elements per pipeline step (one 128-byte swizzle a
 struct GemmParams {
   int M, N, K;            // x rows, W rows (output features), reduction length
   int kb_per_split;       // K blocks handled by one split
+  int bn_rows;            // activation rows per CTA when fewer than the kernel's BN (0: BN); a multiple of 16
   int splits;
   const __nv_bfloat16* bias;       // [N] or null
   const __nv_bfloat16* residual;   // [M, ldo] or null (may alias out)
@@ -36,7 +37,7 @@ struct GemmParams {
 // instantiation, so that the plain kernel's store loop carries none of it); N must be even.
 template <int BN, bool HO = false>
 __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uint64_t* acc_full, int* abort_flag,
-                                         int* is_last_s, int n0, int m0, int split, int nkb, int warp, int lane) {
+                                         int* is_last_s, int n0, int m0, int split, int nkb, int warp, int lane, int bn = BN) {
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
     const int n = n0 + quad * 32 + lane;       // output feature owned by this thread
     uint32_t ll_seq = 0;                       // sequence number of this hand-over's words (see tp_handover.cuh)
@@ -49,7 +50,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
     if (p.splits == 1) {
       float bias = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
+      for (int c = 0; c < bn; c += 16) {
         float v[16];
         tc::tmem_ld16(taddr + c, v);   // warp-collective: executed by all lanes regardless of bounds
         tc::tmem_ld_wait();
@@ -194,7 +195,7 @@ __device__ __forceinline__ void epilogue(const GemmParams& p, uint32_t tmem, uin
 // the activation, as the unfused form (GEMM, then the SwiGLU kernel) does.
 template <int BN>
 __device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, uint32_t tmem, uint64_t* acc_full, int* abort_flag, int n0,
-                                                int m0, int nkb, int warp, int lane) {
+                                                int m0, int nkb, int warp, int lane, int bn = BN) {
   const int quad = warp & 3;
   const int n = n0 + quad * 32 + lane, F = p.N / 2;
   bool ok = tc::mbar_wait_backoff(acc_full, 0, 400);
@@ -203,7 +204,7 @@ __device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, uint32_t tm
   ok = ok && !*(volatile int*)abort_flag && nkb > 0;
   const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
-  for (int c = 0; c < BN; c += 16) {
+  for (int c = 0; c < bn; c += 16) {
     float g[16], u[16];
     tc::tmem_ld16(taddr + c, g);
     tc::tmem_ld16(taddr + BN + c, u);

@@ -50,10 +50,13 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   using S = Smem<BN, STAGES, TWO>;
   S& s = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr uint32_t TMEM_COLS = (TWO ? 2 : 1) * BN < 32 ? 32 : (TWO ? 2 : 1) * BN;
-  constexpr uint32_t STAGE_BYTES = ((TWO ? 2 : 1) * BM * BK + BN * BK) * 2;
+  // the two-accumulator (prefill) kernels may run with fewer activation rows per CTA than BN, so that the tile count
+  // fits whole waves over the SMs: the accumulators keep their BN-column spacing, the MMAs and the epilogue are bn wide
+  const int bn = (TWO && p.bn_rows > 0) ? p.bn_rows : BN;
+  const uint32_t STAGE_BYTES = ((TWO ? 2 : 1) * BM * BK + bn * BK) * 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM * ((TWO && !GLU) ? 2 : 1), split = blockIdx.z;
-  const int m0 = (int)((blockIdx.y + (unsigned)p.m_tile_shift) % gridDim.y) * BN;
+  const int m0 = (int)((blockIdx.y + (unsigned)p.m_tile_shift) % gridDim.y) * bn;
   const int second = GLU ? p.N / 2 : BM;      // row distance of the second weight tile
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
@@ -84,7 +87,7 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       if (p.row_flags) {
         // all-gather -> GEMM: this CTA's activation rows belong to one or two ranks; wait (bounded) until those ranks
         // have delivered them, then order the wait before the TMA engine's reads of the same memory
-        const int o_lo = m0 / p.rows_per_flag, o_hi = (min(p.M, m0 + BN) - 1) / p.rows_per_flag;
+        const int o_lo = m0 / p.rows_per_flag, o_hi = (min(p.M, m0 + bn) - 1) / p.rows_per_flag;
         unsigned long long t0;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
         const int need = *reinterpret_cast<const volatile int*>(p.row_epoch);
@@ -120,7 +123,7 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (tc::elect_one()) {
-      constexpr uint32_t idesc = tc::umma_idesc_bf16(BM, BN);
+      const uint32_t idesc = tc::umma_idesc_bf16(BM, bn);
       bool ok = true;
       for (int i = 0; i < nkb && ok; i++) {
         int st = i % STAGES;
@@ -147,11 +150,11 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     }
   } else {
     if constexpr (GLU) {
-      gemm::epilogue_swiglu<BN>(p, tmem, &s.acc_full, &s.abort_flag, n0, m0, nkb, warp, lane);
+      gemm::epilogue_swiglu<BN>(p, tmem, &s.acc_full, &s.abort_flag, n0, m0, nkb, warp, lane, bn);
     } else {
-    gemm::epilogue<BN, HO>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane);
+    gemm::epilogue<BN, HO>(p, tmem, &s.acc_full, &s.abort_flag, &s.is_last, n0, m0, split, nkb, warp, lane, bn);
     // second accumulator: plain stores only (the launcher uses TWO without split-K or hand-over)
-    if constexpr (TWO) gemm::epilogue<BN>(p, tmem + BN, &s.acc_full, &s.abort_flag, &s.is_last, n0 + BM, m0, split, nkb, warp, lane);
+    if constexpr (TWO) gemm::epilogue<BN>(p, tmem + BN, &s.acc_full, &s.abort_flag, &s.is_last, n0 + BM, m0, split, nkb, warp, lane, bn);
     }
   }
   // ------------------------------ teardown ------------------------------
@@ -304,7 +307,8 @@ static int launch_gemm_ho(const CUtensorMap* tw, const CUtensorMap* tx, const Ge
     attr_set = true;
   }
   constexpr int FEATS = BM * (TWO ? 2 : 1);
-  dim3 grid((p.N + FEATS - 1) / FEATS, (p.M + BN - 1) / BN, p.splits);
+  const int bn = (TWO && p.bn_rows > 0) ? p.bn_rows : BN;
+  dim3 grid((p.N + FEATS - 1) / FEATS, (p.M + bn - 1) / bn, p.splits);
   gemm_swapped_kernel<BN, STAGES, TWO, HO><<<grid, 192, smem, st>>>(*tw, *tx, p);
   EXO_CHECK_LAUNCH();
   return 0;
@@ -320,7 +324,8 @@ static int launch_gemm_glu(const CUtensorMap* tw, const CUtensorMap* tx, const G
       return -3;
     attr_set = true;
   }
-  dim3 grid((p.N / 2 + BM - 1) / BM, (p.M + 255) / 256, 1);
+  const int bn = p.bn_rows > 0 ? p.bn_rows : 256;
+  dim3 grid((p.N / 2 + BM - 1) / BM, (p.M + bn - 1) / bn, 1);
   gemm_swapped_kernel<256, 3, true, false, true><<<grid, 192, smem, st>>>(*tw, *tx, p);
   EXO_CHECK_LAUNCH();
   return 0;
@@ -332,6 +337,23 @@ static int launch_gemm(const CUtensorMap* tw, const CUtensorMap* tx, const GemmP
     if (p.ho.n_ll > 0) return launch_gemm_ho<BN, STAGES, false, true>(tw, tx, p, st);
   }
   return launch_gemm_ho<BN, STAGES, TWO, false>(tw, tx, p, st);
+}
+
+// Activation rows per CTA of a two-accumulator (prefill) launch with `tiles_n` feature tiles: the multiple of 16 in
+// [128, 256] that minimises  waves x (rows + fixed)  over the 148 SMs, where `fixed` stands for a tile's prologue and
+// epilogue (about 15 % of a full tile's main loop).  256 rows on 24 feature tiles and M = 2048 is 192 CTAs = two
+// waves, the second 30 % full; 176 rows is 288 CTAs = two waves of 0.69-size tiles.
+static int fit_rows(long tiles_n, int M) {
+  static const bool off = getenv("EXO_GEMM_FIXED_ROWS") != nullptr;      // A/B switch, read once
+  if (off) return 256;
+  int best = 256;
+  long best_cost = -1;
+  for (int bn = 256; bn >= 128; bn -= 16) {
+    const long ctas = tiles_n * ((M + bn - 1) / bn);
+    const long cost = ((ctas + 147) / 148) * (bn + 38);
+    if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+  return best;
 }
 
 // Suggested split count for a (M, N, K) problem: fill the 148 SMs when there are few output tiles.
@@ -401,19 +423,21 @@ static int gemm_swiglu_launch(const void* x, const void* W, void* out, int M, in
   int dev;
   cudaGetDevice(&dev);
   if (dev >= 16 || !g_err[dev]) return -4;
+  const int bn = fit_rows((N / 2 + BM - 1) / BM, M);
   const CUtensorMap* tw = exo_tmap_2d_bf16(W, N, K, BM);
-  const CUtensorMap* tx = exo_tmap_2d_bf16(x, M, K, 256);
+  const CUtensorMap* tx = exo_tmap_2d_bf16(x, M, K, bn);
   if (!tw || !tx) return -5;
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K;
   p.kb_per_split = (K + BK - 1) / BK;
+  p.bn_rows = bn;
   p.splits = 1;
   p.out = (__nv_bfloat16*)out;
   p.ldo = N / 2;
   p.err = g_err[dev];
   if (gate_parity >= 0) {
-    int rc = gate_params(&p, gate_parity, M, 256);
+    int rc = gate_params(&p, gate_parity, M, bn);
     if (rc) return rc;
   }
   return launch_gemm_glu(tw, tx, p, st);
@@ -438,11 +462,23 @@ static int gemm_launch(const void* x, const void* W, const void* bias, const voi
   cudaGetDevice(&dev);
   if (dev >= 16 || !g_err[dev]) return -4;  // exo_gemm_init not called on this device
   int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  // prefill shapes: decide here whether the two-accumulator kernel runs, and with how many rows per CTA
+  bool two = false;
+  if (bn == 256) {
+    // Two accumulators per CTA halve the CTA count and make each ~1.74x as long (measured): take them when
+    // that wins after rounding both to whole waves over the 148 SMs.
+    const long t2 = (long)((N + 2 * BM - 1) / (2 * BM)) * ((M + 255) / 256), t1 = (long)((N + BM - 1) / BM) * ((M + 255) / 256);
+    const bool two_wins = 1.74 * (double)((t2 + 147) / 148) < (double)((t1 + 147) / 148);
+    static const bool single_tile = getenv("EXO_GEMM_SINGLE_TILE") != nullptr;   // A/B switch, read once
+    two = splits <= 1 && !ho && N >= 2 * BM && two_wins && !single_tile;
+    if (two) bn = fit_rows((N + 2 * BM - 1) / (2 * BM), M);
+  }
   const CUtensorMap* tw = exo_tmap_2d_bf16(W, N, K, BM);
   const CUtensorMap* tx = exo_tmap_2d_bf16(x, M, K, bn);
   if (!tw || !tx) return -5;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
+  p.bn_rows = two ? bn : 0;
   int kb_total = (K + BK - 1) / BK;
   if (splits < 1) splits = 1;
   if (splits > kb_total) splits = kb_total;
@@ -466,20 +502,13 @@ static int gemm_launch(const void* x, const void* W, const void* bias, const voi
     long tiles = (long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     if ((size_t)splits * M * N > g_partial_floats[dev] || tiles > MAX_TILES) return -6;
   }
+  if (two) return launch_gemm<256, 3, true>(tw, tx, p, st);   //  3 x 64 KB, two accumulators (512 TMEM columns)
   switch (bn) {
     case 16: return launch_gemm<16, 5>(tw, tx, p, st);   //  5 x 18 KB
     case 32: return launch_gemm<32, 5>(tw, tx, p, st);   //  5 x 20 KB
     case 64: return launch_gemm<64, 4>(tw, tx, p, st);   //  4 x 24 KB
     case 128: return launch_gemm<128, 3>(tw, tx, p, st); //  3 x 32 KB  (two CTAs per SM)
-    default: {
-      // Two accumulators per CTA halve the CTA count and make each ~1.74x as long (measured): take them when
-      // that wins after rounding both to whole waves over the 148 SMs.
-      const long t2 = (long)((N + 2 * BM - 1) / (2 * BM)) * ((M + 255) / 256), t1 = (long)((N + BM - 1) / BM) * ((M + 255) / 256);
-      const bool two_wins = 1.74 * (double)((t2 + 147) / 148) < (double)((t1 + 147) / 148);
-      static const bool single_tile = getenv("EXO_GEMM_SINGLE_TILE") != nullptr;   // A/B switch, read once
-      if (splits == 1 && !ho && N >= 2 * BM && two_wins && !single_tile)
-        return launch_gemm<256, 3, true>(tw, tx, p, st);   //  3 x 64 KB, two accumulators (512 TMEM columns)
+    default:
       return launch_gemm<256, 4>(tw, tx, p, st);  //  4 x 48 KB  (one CTA per SM)
-    }
   }
 }

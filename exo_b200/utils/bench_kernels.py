@@ -104,10 +104,53 @@ def small_cases(only: set[str]) -> None:
         cu = torch.arange(B + 1, device="cuda", dtype=torch.int32)
         q, kc, vc = rnd(B, Hq, D), rnd(nb, bs, Hkv, D), rnd(nb, bs, Hkv, D)
         calls.append(lambda: K.paged_attention(q, kc, vc, bt, sl, cu, D ** -0.5, max_q_len=1))
+    if "mla" in only:
+        H, kvl, rope, bs, B, ctx = 16, 512, 64, 16, 16, 8192
+        nbk = B * (ctx // bs) + 1
+        btm = (torch.arange(B * (ctx // bs), device="cuda", dtype=torch.int32) + 1).view(B, -1)
+        slm = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+        cum = torch.arange(B + 1, device="cuda", dtype=torch.int32)
+        qm, ckv = rnd(B, H, kvl + rope), rnd(nbk, bs, kvl + rope)
+        calls.append(lambda: K.mla_paged_attention(qm, ckv, btm, slm, cum, (128 + rope) ** -0.5, kvl, max_q_len=1))
+    if "misc" in only:
+        lg = rnd(32, 128256) * 40
+        lg[:, ::3001] += 14.0
+        t = torch.full((32,), 0.7, device="cuda")
+        tk = torch.full((32,), 20, device="cuda", dtype=torch.int32)
+        tp, mp, u = torch.full((32,), 0.9, device="cuda"), torch.full((32,), 0.05, device="cuda"), torch.rand(32, device="cuda")
+        calls.append(lambda: K.sample(lg, t, tk, tp, mp, u))
+    if "comm" in only:
+        # the reduce + residual + RMSNorm kernel of a two-rank group on ONE GPU: the peer is a second local arena whose
+        # partial and arrival flag the host writes (no kernel waits on another kernel)
+        import ctypes as C
+
+        from ..parallel.fused import arena_layout, bind
+        lib = bind(K.load())
+        K.ensure_gemm_init(torch.device("cuda", 0))
+        rows, cols = 256, 4096
+        L = arena_layout(lib, 2, rows, cols, 64, 8)
+        arenas = [torch.zeros(L["total"], dtype=torch.uint8, device="cuda") for _ in range(2)]
+        arr = (C.c_void_p * 2)(*[a.data_ptr() for a in arenas])
+        assert lib.exo_comm_init(arr, None, 2, 0, L["slot"], L["gather_off"], L["x_off"], L["x_bytes"], L["h_off"], L["n_off"],
+                                 L["ll_off"], L["ll_slot"]) == 0
+        res, w = rnd(rows, cols), rnd(cols)
+        hh, xx = torch.empty_like(res), torch.empty_like(res)
+        state = {"it": 0}
+
+        def reduce_once():
+            parity = state["it"] & 1
+            state["it"] += 1
+            arenas[0][:4096].view(torch.int32)[2048 // 4 + parity * 8 + 1] = 1        # the peer's "partial ready"
+            lib.exo_reduce_norm_bf16(res.data_ptr(), w.data_ptr(), 1e-5, hh.data_ptr(), xx.data_ptr(), rows, cols, parity, 0, 1,
+                                     torch.cuda.current_stream().cuda_stream)
+        calls.append(reduce_once)
     for _ in range(3):
         for c in calls:
             c()
     torch.cuda.synchronize()
+    if "comm" in only:
+        K.check_status()
+        lib.exo_comm_reset()
     K.gemm_check()
     print("small cases done:", len(calls))
 

@@ -56,3 +56,92 @@ def test_prefill_decode_bench_planning_and_tables(tmp_path):
     cfg.write_text('[defaults]\nmodel = "org/m"\npp = "1024,4096"\nrepeat = 3\n')
     a = pdb.parse_args(["--config", str(cfg), "--tg", "64"])
     assert (a.model, pdb.ints(a.pp), a.repeat, pdb.ints(a.tg)) == ("org/m", [1024, 4096], 3, [64])
+
+
+class FakeCluster:
+    """The slice of the HTTP API the harness uses, in memory."""
+
+    def __init__(self):
+        gib = 1 << 30
+        self.models = [{"hugging_face_id": "meta-llama/Llama-3.1-8B-Instruct", "storage_size_megabytes": 16 * 1024},
+                       {"hugging_face_id": "meta-llama/Llama-3.1-70B-Instruct", "storage_size_megabytes": 140 * 1024},
+                       {"hugging_face_id": "Qwen/Qwen3-8B", "storage_size_megabytes": 16 * 1024}]
+        shard = lambda m: {"TensorShardMetadata": {"modelCard": {"modelId": m}}}
+        self.state_ = {"instances": {}, "runners": {}, "nodeDisk": {"n1": {"available": {"inBytes": 20 * gib}}, "n2": {"available": {"inBytes": 4 * gib}}},
+                       "downloads": {"n1": [], "n2": [{"DownloadCompleted": {"shardMetadata": shard("Qwen/Qwen3-8B"), "total": {"inBytes": 16 * gib}}},
+                                                      {"DownloadCompleted": {"shardMetadata": shard("org/small"), "total": {"inBytes": 1 * gib}}}]},
+                       "nodeMemory": {"n1": {}, "n2": {}}}
+        self.preview_calls, self.deleted, self.started = 0, [], []
+        self.shard = shard
+
+    def get(self, path, **params):
+        if path == "/models":
+            return {"data": self.models}
+        raise KeyError(path)
+
+    def previews(self, model_id):
+        self.preview_calls += 1
+        if self.preview_calls < 3:
+            return []                                  # the second node has not joined yet
+        inst = lambda nodes: {"NvlinkInstance": {"shardAssignments": {"modelId": model_id, "nodeToRunner": {n: "r" + n for n in nodes},
+                                                                      "runnerToShard": {"r" + n: self.shard(model_id) for n in nodes}}}}
+        return [{"sharding": "Tensor", "instance": inst(["n1", "n2"])}, {"sharding": "Pipeline", "instance": inst(["n1", "n2"])},
+                {"sharding": "Tensor", "instance": inst(["n1"])}, {"sharding": "Tensor", "instance": None, "error": "no memory"}]
+
+    def state(self):
+        return self.state_
+
+    def delete(self, path):
+        node, model = path.split("/", 3)[2:]
+        self.deleted.append((node, model))
+        self.state_["downloads"][node] = [e for e in self.state_["downloads"][node]
+                                          if next(iter(e["DownloadCompleted"]["shardMetadata"].values()))["modelCard"]["modelId"] != model]
+
+    def post(self, path, body, timeout=None):
+        if path == "/download/start":
+            self.started.append(body["targetNodeId"])
+            model = next(iter(body["shardMetadata"].values()))["modelCard"]["modelId"]
+            self.state_["downloads"][body["targetNodeId"]].append({"DownloadCompleted": {"shardMetadata": self.shard(model), "total": {"inBytes": 1}}})
+        elif path == "/instance":
+            inst = body["instance"]
+            self.state_["instances"]["i1"] = inst
+            for r in next(iter(inst.values()))["shardAssignments"]["runnerToShard"]:
+                self.state_["runners"][r] = {"RunnerReady": {}}
+
+    def instances_of(self, model_id):
+        return [(i, t) for i, t in self.state_["instances"].items() if next(iter(t.values()))["shardAssignments"]["modelId"] == model_id]
+
+    def delete_instance(self, iid):
+        self.state_["instances"].pop(iid)
+
+
+def test_harness_resolves_places_frees_disk_downloads_and_launches():
+    import argparse
+
+    import pytest
+
+    from exo_b200.bench.harness import Harness, add_instance_args
+    fc = FakeCluster()
+    logs: list[str] = []
+    h = Harness(fc, log=logs.append, sleep=lambda s: None)
+    assert h.resolve_model("Llama-3.1-8B-Instruct") == "meta-llama/Llama-3.1-8B-Instruct"
+    assert h.resolve_model("qwen3-8b") == "Qwen/Qwen3-8B" and h.resolve_model("org/unknown") == "org/unknown"
+    with pytest.raises(ValueError):
+        h.resolve_model("llama-3.1")
+    ap = argparse.ArgumentParser()
+    add_instance_args(ap)
+    a = ap.parse_args(["--model", "Llama-3.1-8B-Instruct", "--min-nodes", "2"])
+    with pytest.raises(RuntimeError, match="GiB free"):             # n2 has 4 GiB free, the model needs 16
+        h.instance_for(a)
+    a = ap.parse_args(["--model", "Llama-3.1-8B-Instruct", "--min-nodes", "2", "--danger-delete-downloads"])
+    model, iid, dl = h.instance_for(a)
+    assert model == "meta-llama/Llama-3.1-8B-Instruct" and iid == "i1" and dl is not None
+    assert fc.preview_calls >= 3 and any("no placement" in ln for ln in logs)       # waited for the cluster to settle
+    assert fc.deleted == [("n2", "org/small"), ("n2", "Qwen/Qwen3-8B")] and sorted(fc.started) == ["n1", "n2"]   # smallest first
+    snap = h.snapshot()
+    assert snap["instances"]["i1"]["nodes"] == ["n1", "n2"] and snap["instances"]["i1"]["kind"] == "NvlinkInstance"
+    a2 = ap.parse_args(["--model", "Llama-3.1-8B-Instruct", "--reuse-instance"])
+    assert h.instance_for(a2)[1] == "i1"
+    h.teardown()
+    assert not fc.state_["instances"]
+    assert len(h.placements(model, "Pipeline", "nvlink", 1, 0, 1.0)) == 1 and h.placements(model, "Tensor", "ring", 1, 0, 0.0) == []
