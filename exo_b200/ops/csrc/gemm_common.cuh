@@ -14,6 +14,7 @@ struct GemmParams {
   int M, N, K;            // x rows, W rows (output features), reduction length
   int kb_per_split;       // K blocks handled by one split
   int bn_rows;            // activation rows per CTA when fewer than the kernel's BN (0: BN); a multiple of 16
+  int rows_fastest;       // 1: blockIdx.x walks the row tiles and blockIdx.y the feature tiles (prefill launches)
   int splits;
   const __nv_bfloat16* bias;       // [N] or null
   const __nv_bfloat16* residual;   // [M, ldo] or null (may alias out)

@@ -398,6 +398,7 @@ static int gemm_fp8w_impl(const void* x, const void* tiles, int scale_kind, cons
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || K < BK || (scale_kind != 1 && scale_kind != 2) || ((uintptr_t)tiles & 15)) return -2;
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   size_t partial_floats = 0;
   if (exo_gemm_scratch(&p.err, &p.counters, &p.partial, &partial_floats)) return -4;
   const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;

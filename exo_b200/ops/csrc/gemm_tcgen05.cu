@@ -50,13 +50,18 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   using S = Smem<BN, STAGES, TWO>;
   S& s = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr uint32_t TMEM_COLS = (TWO ? 2 : 1) * BN < 32 ? 32 : (TWO ? 2 : 1) * BN;
-  // the two-accumulator (prefill) kernels may run with fewer activation rows per CTA than BN, so that the tile count
-  // fits whole waves over the SMs: the accumulators keep their BN-column spacing, the MMAs and the epilogue are bn wide
-  const int bn = (TWO && p.bn_rows > 0) ? p.bn_rows : BN;
+  // the prefill kernels (BN = 256) may run with fewer activation rows per CTA than BN, so that the tile count fits
+  // whole waves over the SMs: the accumulators keep their BN-column spacing, the MMAs and the epilogue are bn wide
+  const int bn = p.bn_rows > 0 ? p.bn_rows : BN;
   const uint32_t STAGE_BYTES = ((TWO ? 2 : 1) * BM * BK + bn * BK) * 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM * ((TWO && !GLU) ? 2 : 1), split = blockIdx.z;
-  const int m0 = (int)((blockIdx.y + (unsigned)p.m_tile_shift) % gridDim.y) * bn;
+  // Prefill launches walk the row tiles fastest: the CTAs that run together then share a few weight tiles (each read
+  // from HBM once) and re-read the activations, which are the smaller operand and stay in L2; with the feature tiles
+  // fastest every wave streamed a different set of weight tiles and a matrix larger than L2 was re-read once per row tile.
+  const unsigned tile_n = p.rows_fastest ? blockIdx.y : blockIdx.x, tile_m = p.rows_fastest ? blockIdx.x : blockIdx.y;
+  const unsigned tiles_m = p.rows_fastest ? gridDim.x : gridDim.y;
+  const int n0 = (int)tile_n * BM * ((TWO && !GLU) ? 2 : 1), split = blockIdx.z;
+  const int m0 = (int)((tile_m + (unsigned)p.m_tile_shift) % tiles_m) * bn;
   const int second = GLU ? p.N / 2 : BM;      // row distance of the second weight tile
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
@@ -307,8 +312,9 @@ static int launch_gemm_ho(const CUtensorMap* tw, const CUtensorMap* tx, const Ge
     attr_set = true;
   }
   constexpr int FEATS = BM * (TWO ? 2 : 1);
-  const int bn = (TWO && p.bn_rows > 0) ? p.bn_rows : BN;
+  const int bn = p.bn_rows > 0 ? p.bn_rows : BN;
   dim3 grid((p.N + FEATS - 1) / FEATS, (p.M + bn - 1) / bn, p.splits);
+  if (p.rows_fastest) grid = dim3(grid.y, grid.x, 1);
   gemm_swapped_kernel<BN, STAGES, TWO, HO><<<grid, 192, smem, st>>>(*tw, *tx, p);
   EXO_CHECK_LAUNCH();
   return 0;
@@ -326,6 +332,7 @@ static int launch_gemm_glu(const CUtensorMap* tw, const CUtensorMap* tx, const G
   }
   const int bn = p.bn_rows > 0 ? p.bn_rows : 256;
   dim3 grid((p.N / 2 + BM - 1) / BM, (p.M + bn - 1) / bn, 1);
+  if (p.rows_fastest) grid = dim3(grid.y, grid.x, 1);
   gemm_swapped_kernel<256, 3, true, false, true><<<grid, 192, smem, st>>>(*tw, *tx, p);
   EXO_CHECK_LAUNCH();
   return 0;
@@ -339,21 +346,27 @@ static int launch_gemm(const CUtensorMap* tw, const CUtensorMap* tx, const GemmP
   return launch_gemm_ho<BN, STAGES, TWO, false>(tw, tx, p, st);
 }
 
-// Activation rows per CTA of a two-accumulator (prefill) launch with `tiles_n` feature tiles: the multiple of 16 in
-// [128, 256] that minimises  waves x (rows + fixed)  over the 148 SMs, where `fixed` stands for a tile's prologue and
-// epilogue (about 15 % of a full tile's main loop).  256 rows on 24 feature tiles and M = 2048 is 192 CTAs = two
-// waves, the second 30 % full; 176 rows is 288 CTAs = two waves of 0.69-size tiles.
-static int fit_rows(long tiles_n, int M) {
+// Activation rows per CTA of a prefill launch with `tiles_n` feature tiles: the multiple of 16 in [128, 256] that
+// minimises  waves x (rows + fixed)  over the 148 SMs, where `fixed` stands for a tile's prologue and epilogue (about
+// 15 % of a full tile's main loop).  Returns the rows and, in *cost, that product (for comparing tile shapes).
+// Example: two-accumulator tiles, N = 6144 (24 feature tiles), M = 2048: 256 rows is 192 CTAs = two waves, the second
+// 30 % full; 176 rows is 288 CTAs = two waves of 0.69-size tiles.
+static int fit_rows(long tiles_n, int M, long* cost_out = nullptr) {
   static const bool off = getenv("EXO_GEMM_FIXED_ROWS") != nullptr;      // A/B switch, read once
-  if (off) return 256;
   int best = 256;
   long best_cost = -1;
-  for (int bn = 256; bn >= 128; bn -= 16) {
+  for (int bn = 256; bn >= (off ? 256 : 128); bn -= 16) {
     const long ctas = tiles_n * ((M + bn - 1) / bn);
     const long cost = ((ctas + 147) / 148) * (bn + 38);
     if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
   }
+  if (cost_out) *cost_out = best_cost;
   return best;
+}
+
+static int rows_fastest_default() {
+  static const int v = getenv("EXO_GEMM_FEATURES_FASTEST") ? 0 : 1;      // A/B switch, read once
+  return v;
 }
 
 // Suggested split count for a (M, N, K) problem: fill the 148 SMs when there are few output tiles.
@@ -432,6 +445,7 @@ static int gemm_swiglu_launch(const void* x, const void* W, void* out, int M, in
   p.M = M; p.N = N; p.K = K;
   p.kb_per_split = (K + BK - 1) / BK;
   p.bn_rows = bn;
+  p.rows_fastest = rows_fastest_default();
   p.splits = 1;
   p.out = (__nv_bfloat16*)out;
   p.ldo = N / 2;
@@ -464,21 +478,24 @@ static int gemm_launch(const void* x, const void* W, const void* bias, const voi
   int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   // prefill shapes: decide here whether the two-accumulator kernel runs, and with how many rows per CTA
   bool two = false;
-  if (bn == 256) {
-    // Two accumulators per CTA halve the CTA count and make each ~1.74x as long (measured): take them when
-    // that wins after rounding both to whole waves over the 148 SMs.
-    const long t2 = (long)((N + 2 * BM - 1) / (2 * BM)) * ((M + 255) / 256), t1 = (long)((N + BM - 1) / BM) * ((M + 255) / 256);
-    const bool two_wins = 1.74 * (double)((t2 + 147) / 148) < (double)((t1 + 147) / 148);
+  int fitted = 0;
+  if (bn == 256 && splits <= 1 && !ho) {
+    // Two accumulators per CTA halve the CTA count and make each ~1.74x as long (measured): take them when that
+    // wins after both shapes got the row count that fits them best into whole waves over the 148 SMs.
+    long c1 = 0, c2 = 0;
+    const int r1 = fit_rows((N + BM - 1) / BM, M, &c1), r2 = fit_rows((N + 2 * BM - 1) / (2 * BM), M, &c2);
     static const bool single_tile = getenv("EXO_GEMM_SINGLE_TILE") != nullptr;   // A/B switch, read once
-    two = splits <= 1 && !ho && N >= 2 * BM && two_wins && !single_tile;
-    if (two) bn = fit_rows((N + 2 * BM - 1) / (2 * BM), M);
+    two = N >= 2 * BM && !single_tile && 1.74 * (double)c2 < (double)c1;
+    bn = fitted = two ? r2 : r1;
   }
   const CUtensorMap* tw = exo_tmap_2d_bf16(W, N, K, BM);
   const CUtensorMap* tx = exo_tmap_2d_bf16(x, M, K, bn);
   if (!tw || !tx) return -5;
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K;
-  p.bn_rows = two ? bn : 0;
+  p.bn_rows = fitted;
+  p.rows_fastest = fitted > 0 && rows_fastest_default();
   int kb_total = (K + BK - 1) / BK;
   if (splits < 1) splits = 1;
   if (splits > kb_total) splits = kb_total;
