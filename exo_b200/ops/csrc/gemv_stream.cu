@@ -435,10 +435,16 @@ static int gemv_stream_launch(const void* x, const void* W, const void* bias, co
   p.RS = RS;
   p.n_groups = (rows_total + rows_per_group - 1) / rows_per_group;
   p.stage_bytes = RS * row_bytes;
-  p.stages = stages;
-  const size_t smem = fixed + (size_t)stages * p.stage_bytes;
   const int max_grid = 148 * ctas_per_sm();
   int grid = p.n_groups < max_grid ? p.n_groups : max_grid;
+  // A CTA that has only one or two row groups to stream (a tensor-parallel shard, a small projection) needs no deeper
+  // ring than that: the shared memory it leaves free lets the next kernel's CTAs become resident while this one still
+  // runs, and their weight stream starts before the programmatic-dependent-launch wait.
+  const int per_cta = (p.n_groups + grid - 1) / grid;
+  static const bool full_ring = getenv("EXO_GEMV_FULL_RING") != nullptr;   // A/B switch, read once
+  if (!full_ring && stages > per_cta) stages = per_cta < 2 ? 2 : per_cta;
+  p.stages = stages;
+  const size_t smem = fixed + (size_t)stages * p.stage_bytes;
   const int jv = (K / 8 / 8 + 31) / 32;
   int rc;
 #define BY_JV(MM)                                                                              \
