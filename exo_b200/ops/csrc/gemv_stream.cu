@@ -22,7 +22,10 @@
 
 namespace {
 
-constexpr int CONSUMER_WARPS = 8;
+#ifndef EXO_GEMV_WARPS
+#define EXO_GEMV_WARPS 8
+#endif
+constexpr int CONSUMER_WARPS = EXO_GEMV_WARPS;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int RS_MAX = 32;
 
@@ -152,7 +155,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
       float v = warp_sum(ss[m]);
       if (lane == 0) red[warp * M + m] = v;
     }
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
 #pragma unroll
     for (int m = 0; m < M; m++) {
       float t = 0.f;
@@ -217,7 +220,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
     }
     __syncwarp();
     if (lane == 0) tc::mbar_arrive(&empty[st]);  // this warp is done reading the stage
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
     // finalise: thread t handles (row slot, m)
     const int t = threadIdx.x;
     if (ok) {
@@ -274,7 +277,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const StreamPar
   if constexpr (HO == 2) {
     // every CTA has read the slots once it is here: the last one advances the parity's epoch, which is what the
     // next hand-over on this parity (two hand-overs from now) will stamp its words with
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
     if (threadIdx.x == 0 && atomicAdd(p.ho.ll_ticket, 1) == (int)gridDim.x - 1) {
       *p.ho.ll_ticket = 0;
       *reinterpret_cast<volatile int*>(p.ho.ll_epoch) = (int)ll_seq;
@@ -379,8 +382,8 @@ static bool stream_config(int M, int K, int swiglu, int* RS_out, int* stages_out
 // Returns 1 when (M, N, K) is served by the streaming kernel.
 EXO_API int exo_gemv_stream_supported(int M, int N, int K, int swiglu) {
   if (M < 1 || M > 2) return 0;
-  if (K % 64 != 0 || K < 256) return 0;
-  int jv = (K / 8 / 8 + 31) / 32;
+  if (K % (8 * CONSUMER_WARPS) != 0 || K < 256) return 0;
+  int jv = (K / 8 / CONSUMER_WARPS + 31) / 32;
   if (jv > 16 || (M == 2 && jv > 8)) return 0;
   if (swiglu && (N % 2)) return 0;
   if ((long)N * K < (1 << 20)) return 0;  // tiny matrices: the plain kernel has less set-up
@@ -445,7 +448,7 @@ static int gemv_stream_launch(const void* x, const void* W, const void* bias, co
   if (!full_ring && stages > per_cta) stages = per_cta < 2 ? 2 : per_cta;
   p.stages = stages;
   const size_t smem = fixed + (size_t)stages * p.stage_bytes;
-  const int jv = (K / 8 / 8 + 31) / 32;
+  const int jv = (K / 8 / CONSUMER_WARPS + 31) / 32;
   int rc;
 #define BY_JV(MM)                                                                              \
   if (jv <= 1) rc = launch_stream<MM, 1>(p, norm_w != nullptr, swiglu != 0, grid, smem, st);      \
