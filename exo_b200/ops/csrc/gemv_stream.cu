@@ -296,7 +296,7 @@ int launch_stream_rb(const StreamParams& p, bool norm, bool swiglu, int grid, si
     static bool attr = false;                                                                                    \
     if (!attr) {                                                                                                 \
       if (cudaFuncSetAttribute(gemv_stream_kernel<M, JV, RB, NORM, SW, HO>,                                      \
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)          \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)          \
         return -3;                                                                                               \
       attr = true;                                                                                               \
     }                                                                                                            \
@@ -366,7 +366,8 @@ static bool stream_config(int M, int K, int swiglu, int* RS_out, int* stages_out
   // The whole shared memory of the SM is the ring: ~190 KB in flight per SM is what it takes to
   // cover HBM latency at full bandwidth (a 104 KB ring, tried so that the next kernel's CTA could
   // co-reside and prefetch, lost 25 % of the bandwidth).
-  size_t budget = ctas_per_sm() == 2 ? 104 * 1024 : 196 * 1024;
+  static const size_t big = getenv("EXO_GEMV_RING_KB") ? (size_t)atoi(getenv("EXO_GEMV_RING_KB")) * 1024 : (size_t)196 * 1024;   // A/B switch, read once (227 KB measured 1-3 % slower)
+  size_t budget = ctas_per_sm() == 2 ? 104 * 1024 : big;
   if (ctas_per_sm() == 2 && (size_t)RS * row_bytes > 16 * 1024) {   // smaller stages so that the ring still has depth
     RS = (16 * 1024) / row_bytes;
     if (RS < 1) RS = 1;
