@@ -75,7 +75,8 @@ class Executor:
             tokens=d[L.tokens:L.tokens + L.T], positions=d[L.positions:L.positions + L.T],
             slots=d[L.slots:L.slots + L.T], cu_q=d[L.cu_q:L.cu_q + L.B + 1], seq_lens=d[L.seq_lens:L.seq_lens + L.B],
             block_tables=d[L.block_tables:L.block_tables + L.B * L.max_blocks].view(L.B, L.max_blocks),
-            logit_rows=d[L.logit_rows:L.logit_rows + L.B], max_q_len=1)
+            logit_rows=d[L.logit_rows:L.logit_rows + L.B], max_q_len=1,
+            state_slots=d[L.state_slots:L.state_slots + L.B])
         samp = dict(top_k=d[L.top_k:L.top_k + L.B], temperature=f[L.temperature:L.temperature + L.B],
                     top_p=f[L.top_p:L.top_p + L.B], min_p=f[L.min_p:L.min_p + L.B],
                     uniform=f[L.uniform:L.uniform + L.B], prev_rows=d[L.prev_rows:L.prev_rows + L.B])

@@ -176,6 +176,7 @@ class Sequence:
     t_prefill_start: float = 0.0
     rng_state: int = 0
     final_blocks: list[int] = field(default_factory=list)   # block ids at the moment the sequence finished
+    state_slot: int = 0          # seat of the sequence's recurrent state while it is running (0: none)
 
     @property
     def tokens(self) -> list[int]:

@@ -9,7 +9,7 @@ broadcast of a packed int32 buffer.
 
 Packed layout (int32 words): ``[T, B, R, max_q_len, flags, bucket_T, bucket_B, max_blocks]``
 then ``tokens[T'] positions[T'] slots[T'] cu_q[B'+1] seq_lens[B'] logit_rows[B']
-top_k[B'] temperature[B'] top_p[B'] min_p[B'] uniform[B'] block_tables[B'*max_blocks]`` where
+top_k[B'] temperature[B'] top_p[B'] min_p[B'] uniform[B'] prev_rows[B'] state_slots[B'] block_tables[B'*max_blocks]`` where
 ``T'``/``B'`` are the padded (bucket) sizes, floats are bit-cast.  Padding rows point at the
 reserved scratch block 0 so that a graph captured for the bucket runs unchanged.
 """
@@ -47,6 +47,7 @@ class PlanLayout:
         self.min_p = o; o += self.B
         self.uniform = o; o += self.B
         self.prev_rows = o; o += self.B
+        self.state_slots = o; o += self.B
         o = (o + 3) // 4 * 4  # keep the table 16-byte aligned
         self.block_tables = o; o += self.B * self.max_blocks
         self.words = o
@@ -73,6 +74,7 @@ class StepPlan:
     prev_rows: np.ndarray     # [B] int32 row of the previous step's samples feeding this row (-1: use tokens)
     block_tables: np.ndarray  # [B, max_blocks] int32
     req_ids: tuple[str, ...] = ()
+    state_slots: np.ndarray | None = None   # [B] int32 seat of each sequence's recurrent state (0: none / padding rows)
 
     @property
     def is_decode(self) -> bool:
@@ -108,6 +110,8 @@ class StepPlan:
         fv[L.uniform:L.uniform + B] = self.uniform
         out[L.prev_rows:L.prev_rows + bucket_B] = -1
         out[L.prev_rows:L.prev_rows + B] = self.prev_rows
+        if self.state_slots is not None:
+            out[L.state_slots:L.state_slots + B] = self.state_slots
         bt = out[L.block_tables:L.block_tables + bucket_B * max_blocks].reshape(bucket_B, max_blocks)
         bt[:B, :self.block_tables.shape[1]] = self.block_tables
         return L
@@ -125,7 +129,8 @@ class StepPlan:
             top_k=buf[L.top_k:L.top_k + B].copy(), temperature=fv[L.temperature:L.temperature + B].copy(),
             top_p=fv[L.top_p:L.top_p + B].copy(), min_p=fv[L.min_p:L.min_p + B].copy(),
             uniform=fv[L.uniform:L.uniform + B].copy(), prev_rows=buf[L.prev_rows:L.prev_rows + B].copy(),
-            block_tables=buf[L.block_tables:L.block_tables + bB * mb].reshape(bB, mb)[:B].copy())
+            block_tables=buf[L.block_tables:L.block_tables + bB * mb].reshape(bB, mb)[:B].copy(),
+            state_slots=buf[L.state_slots:L.state_slots + B].copy())
 
 
 def bucket(n: int, buckets: tuple[int, ...]) -> int:

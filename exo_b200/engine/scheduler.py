@@ -34,6 +34,9 @@ class Scheduler:
         self.rng = np.random.default_rng(seed)
         self._rngs: dict[str, np.random.Generator] = {}
         self.n_preempted = 0
+        # seats 1..max_seqs for per-sequence recurrent state (linear-attention layers); seat 0 is the scratch seat of
+        # padding rows.  A sequence holds a seat exactly while it is in `running`.
+        self._free_seats = list(range(max_seqs, 0, -1))
 
     # ---- request lifecycle ----
     def add(self, seq: Sequence) -> None:
@@ -63,7 +66,13 @@ class Scheduler:
         s.blocks = []
         if s in self.running:
             self.running.remove(s)
+        self._release_seat(s)
         self._rngs.pop(s.req_id, None)
+
+    def _release_seat(self, s: Sequence) -> None:
+        if s.state_slot:
+            self._free_seats.append(s.state_slot)
+            s.state_slot = 0
 
     @property
     def has_work(self) -> bool:
@@ -113,6 +122,7 @@ class Scheduler:
             victim.blocks, victim.n_computed, victim.n_published = [], 0, 0
             # generated tokens become part of the prompt to recompute
             self.running.remove(victim)
+            self._release_seat(victim)          # its recurrent state is recomputed with its KV
             self.waiting.appendleft(victim)
             self.n_preempted += 1
             return True
@@ -170,6 +180,7 @@ class Scheduler:
                 break
             self.waiting.popleft()
             s.t_prefill_start = time.perf_counter()
+            s.state_slot = self._free_seats.pop() if self._free_seats else 0
             self.running.append(s)
             entries.append((s, n))
             budget -= n
@@ -229,7 +240,8 @@ class Scheduler:
                         flags=(FLAG_ALL_GREEDY if all_greedy else 0) | (0 if samples else FLAG_NO_SAMPLE), tokens=tokens, positions=positions, slots=slots,
                         cu_q=cu_q, seq_lens=seq_lens, logit_rows=logit_rows, top_k=top_k, temperature=temp,
                         top_p=top_p, min_p=min_p, uniform=uni, prev_rows=np.full(B, -1, np.int32), block_tables=bt,
-                        req_ids=tuple(s.req_id for s, _ in entries))
+                        req_ids=tuple(s.req_id for s, _ in entries),
+                        state_slots=np.fromiter((s.state_slot for s, _ in entries), np.int32, B))
 
     # ---- results ----
     def commit(self, entries: list[tuple[Sequence, int]], sampled: np.ndarray) -> list[tuple[Sequence, int | None]]:

@@ -63,6 +63,7 @@ class StepInputs:
     block_tables: torch.Tensor  # [B, max_blocks] int32
     logit_rows: torch.Tensor    # [B'] int32/64 rows of the T tokens whose logits are wanted
     max_q_len: int = 1
+    state_slots: torch.Tensor | None = None   # [B] int32 seats of the sequences' recurrent state (linear-attention layers)
 
 
 def resolve(h):
