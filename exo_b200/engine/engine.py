@@ -64,6 +64,10 @@ class Engine:
         rid = req_id or uuid.uuid4().hex
         if not prompt:
             raise ValueError("empty prompt")
+        if self.cfg.has_linear_layers:
+            # a gated-delta-rule layer's state summarises the WHOLE prefix and exists only at the sequence's current
+            # end: cached blocks, or KV computed elsewhere, carry no such state, so the prompt is always computed here
+            use_prefix_cache, kv_prefill = False, None
         s = Sequence(rid, list(prompt), params or SamplingParams(), media=media, use_prefix_cache=use_prefix_cache)
         s.embeds = list(embeds) if embeds else None
         if kv_prefill is not None:

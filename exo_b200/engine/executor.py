@@ -34,7 +34,7 @@ class Executor:
         self.spec = spec or ShardSpec()
         self.device = torch.device(device)
         self.model = Decoder(cfg, weights, self.spec, comm)
-        self.kv = KVPool(cfg, self.spec, n_blocks, block_size, self.device)
+        self.kv = KVPool(cfg, self.spec, n_blocks, block_size, self.device, max_seqs=max_seqs)
         self.block_size, self.max_blocks = block_size, max_blocks_per_seq
         self.max_T, self.max_B = max_tokens_per_step, max_seqs
         words = PlanLayout(max(self.max_T, self.max_B), self.max_B, self.max_blocks).words

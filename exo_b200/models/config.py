@@ -34,7 +34,7 @@ class RopeConfig:
 @dataclass
 class ModelConfig:
     name: str = "model"
-    family: str = "llama"  # llama | qwen3 | qwen3_moe | deepseek_v3 | gpt_oss | glm4_moe | mixtral
+    family: str = "llama"  # llama | qwen3 | qwen3_moe | qwen3_next | deepseek_v3 | gpt_oss | glm4_moe | mixtral | minimax
     n_layers: int = 2
     hidden: int = 256
     n_heads: int = 4
@@ -75,6 +75,22 @@ class ModelConfig:
     sliding_window: int = 0
     attn_sinks: bool = False
     eos_token_ids: tuple[int, ...] = ()
+    # hybrid models (Qwen3-Next, Qwen3.5 / 3.6): per layer "full" (softmax attention over the paged cache) or "linear"
+    # (gated delta rule over a fixed-size recurrent state); empty = every layer "full"
+    layer_types: tuple[str, ...] = ()
+    lin_k_heads: int = 0
+    lin_v_heads: int = 0
+    lin_k_dim: int = 0
+    lin_v_dim: int = 0
+    lin_conv: int = 4           # taps of the causal depthwise convolution in front of the delta rule
+    lin_split_proj: bool = False  # checkpoint keeps in_proj_qkv / z / b / a apart (Qwen3.5) instead of qkvz / ba grouped per key head
+    attn_gate: bool = False     # q_proj carries a second, per-head gate: attention output * sigmoid(gate)
+    norm_one_plus: bool = False  # RMSNorm weights stored as (w - 1); folded to w when the checkpoint is read
+    shared_expert_ffn: int = 0  # one shared expert of this width beside the routed ones ...
+    shared_expert_gate: bool = False  # ... scaled per token by sigmoid(x . w_gate)
+    moe_every: int = 1          # layer i is sparse when (i + 1) % moe_every == 0 ...
+    mlp_only_layers: tuple[int, ...] = ()  # ... and i is not listed here
+    weight_prefix: str = "model."  # "model.language_model." in checkpoints that wrap the text model
 
     # -------- derived --------
     @property
@@ -90,7 +106,23 @@ class ModelConfig:
         return self.n_experts > 0
 
     def layer_is_moe(self, i: int) -> bool:
-        return self.is_moe and i >= self.first_dense_layers
+        return (self.is_moe and i >= self.first_dense_layers and (i + 1) % self.moe_every == 0
+                and i not in self.mlp_only_layers)
+
+    def layer_is_linear(self, i: int) -> bool:
+        return bool(self.layer_types) and self.layer_types[i] == "linear"
+
+    @property
+    def has_linear_layers(self) -> bool:
+        return "linear" in self.layer_types
+
+    @property
+    def lin_key_dim(self) -> int:
+        return self.lin_k_heads * self.lin_k_dim
+
+    @property
+    def lin_value_dim(self) -> int:
+        return self.lin_v_heads * self.lin_v_dim
 
     @property
     def kv_bytes_per_token_per_layer(self) -> int:
@@ -108,12 +140,16 @@ class ModelConfig:
                     + h * (self.kv_lora_rank + self.qk_rope_dim)
                     + self.kv_lora_rank * self.n_heads * (self.qk_nope_dim + self.v_head_dim)
                     + self.n_heads * self.v_head_dim * h)
+        if self.attn_gate:
+            attn += h * self.q_dim
+        lin = (h * (2 * self.lin_key_dim + 2 * self.lin_value_dim + 2 * self.lin_v_heads)
+               + self.lin_conv * (2 * self.lin_key_dim + self.lin_value_dim) + self.lin_value_dim * h)
         total = 0
         for i in range(self.n_layers):
-            total += attn + 2 * h
+            total += (lin if self.layer_is_linear(i) else attn) + 2 * h
             if self.layer_is_moe(i):
                 total += self.n_experts * 3 * h * self.moe_ffn + h * self.n_experts
-                total += self.n_shared_experts * 3 * h * self.moe_ffn
+                total += self.n_shared_experts * 3 * h * self.moe_ffn + 3 * h * self.shared_expert_ffn
             else:
                 total += 3 * h * self.ffn
         total += self.vocab * h * (1 if self.tie_embeddings else 2) + h
@@ -146,7 +182,10 @@ class ModelConfig:
         n_heads = g("num_attention_heads", "n_head")
         n_kv = g("num_key_value_heads", default=n_heads)
         head_dim = g("head_dim", default=hidden // n_heads)
-        rope_scaling = g("rope_scaling", default=None) or {}
+        rope_scaling = g("rope_scaling", "rope_parameters", default=None) or {}
+        for key in ("rope_theta", "partial_rotary_factor"):               # newer configs keep every RoPE field in one table
+            if key in rope_scaling and (key not in cfg or cfg.get("rope_parameters")):
+                cfg = {**cfg, key: rope_scaling[key]}
         kind = rope_scaling.get("rope_type", rope_scaling.get("type", "default"))
         rope = RopeConfig(
             theta=float(g("rope_theta", default=10000.0)),
@@ -173,6 +212,8 @@ class ModelConfig:
                   "qwen3_moe": "qwen3_moe", "deepseek_v3": "deepseek_v3", "deepseek_v32": "deepseek_v3",
                   "deepseek_v2": "deepseek_v3", "kimi_k2": "deepseek_v3", "glm4_moe_lite": "deepseek_v3",
                   "glm4_moe": "glm4_moe", "mixtral": "mixtral", "minimax": "minimax", "minimax_m2": "minimax",
+                  "qwen3_next": "qwen3_next", "qwen3_5": "qwen3_next", "qwen3_5_text": "qwen3_next",
+                  "qwen3_5_moe": "qwen3_next", "qwen3_5_moe_text": "qwen3_next",
                   "gpt_oss": "gpt_oss"}.get(mt, "llama")
         mc = ModelConfig(
             name=name, family=family,
@@ -181,7 +222,7 @@ class ModelConfig:
             ffn=g("intermediate_size", default=4 * hidden), vocab=g("vocab_size"),
             rms_eps=float(g("rms_norm_eps", default=1e-5)), rope=rope,
             tie_embeddings=bool(g("tie_word_embeddings", default=False)),
-            qk_norm=family in ("qwen3", "qwen3_moe") or (family == "glm4_moe" and bool(g("use_qk_norm", default=False))),
+            qk_norm=family in ("qwen3", "qwen3_moe", "qwen3_next") or (family == "glm4_moe" and bool(g("use_qk_norm", default=False))),
             attn_bias=bool(g("attention_bias", default=mt == "qwen2")),
             max_position=int(g("max_position_embeddings", default=131072)),
             eos_token_ids=tuple(eos),
@@ -194,6 +235,35 @@ class ModelConfig:
             mc.moe_ffn = g("moe_intermediate_size")
             mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
             mc.router = "softmax"
+        if family == "qwen3_next":
+            # Qwen3-Next / Qwen3.5 / 3.6: three gated-delta-rule layers to one gated softmax-attention layer, RMSNorm
+            # weights stored zero-centred, quarter-rotary RoPE, softmax-routed experts plus one sigmoid-gated shared expert
+            n_l = mc.n_layers
+            every = int(g("full_attention_interval", default=4))
+            types = g("layer_types", default=None) or ["linear_attention" if (i + 1) % every else "full_attention" for i in range(n_l)]
+            mc.layer_types = tuple("linear" if t == "linear_attention" else "full" for t in types)
+            mc.lin_k_heads = g("linear_num_key_heads", default=16)
+            mc.lin_v_heads = g("linear_num_value_heads", default=32)
+            mc.lin_k_dim = g("linear_key_head_dim", default=128)
+            mc.lin_v_dim = g("linear_value_head_dim", default=128)
+            mc.lin_conv = g("linear_conv_kernel_dim", default=4)
+            mc.lin_split_proj = mt != "qwen3_next"
+            mc.attn_gate = True
+            mc.norm_one_plus = True
+            if "partial_rotary_factor" not in cfg:
+                mc.rope.partial_rotary_factor = 0.25
+            mc.n_experts = g("num_experts", default=0) or 0
+            if mc.n_experts:
+                mc.n_experts_per_tok = g("num_experts_per_tok")
+                mc.moe_ffn = g("moe_intermediate_size")
+                mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
+                mc.router = "softmax"
+                mc.shared_expert_ffn = g("shared_expert_intermediate_size", default=0) or 0
+                mc.shared_expert_gate = mc.shared_expert_ffn > 0
+                mc.moe_every = int(g("decoder_sparse_step", default=1))
+                mc.mlp_only_layers = tuple(g("mlp_only_layers", default=()) or ())
+            if mt != "qwen3_next":
+                mc.weight_prefix = "model.language_model."
         if family == "glm4_moe":
             # GLM-4.5 / 4.6: grouped-query attention with half-rotary RoPE and q/k/v biases, DeepSeek-style experts
             # (sigmoid scores + correction bias, shared expert, leading dense layers)
@@ -318,6 +388,21 @@ def preset(name: str) -> ModelConfig:
         return ModelConfig(name="tiny-yarn", family="llama", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
                            ffn=512, vocab=1024, rope=RopeConfig(theta=10000.0, kind="yarn", factor=4.0, original_max_position=64),
                            dtype="fp32")
+    if n in ("tiny-qwen3-next",):  # linear, linear, full, linear: gated delta rule + gated attention, experts with a gated shared expert
+        return ModelConfig(name="tiny-qwen3-next", family="qwen3_next", n_layers=4, hidden=256, n_heads=4, n_kv_heads=2,
+                           head_dim=64, ffn=512, vocab=1024, rms_eps=1e-6, qk_norm=True,
+                           rope=RopeConfig(theta=10000.0, partial_rotary_factor=0.25),
+                           layer_types=("linear", "linear", "full", "linear"), lin_k_heads=2, lin_v_heads=4, lin_k_dim=64,
+                           lin_v_dim=64, lin_conv=4, attn_gate=True, norm_one_plus=True, n_experts=8, n_experts_per_tok=2,
+                           moe_ffn=128, router="softmax", shared_expert_ffn=128, shared_expert_gate=True, dtype="fp32")
+    if n in ("qwen3-next-80b-a3b", "qwen3-next"):
+        return ModelConfig(name="qwen3-next-80b-a3b", family="qwen3_next", n_layers=48, hidden=2048, n_heads=16, n_kv_heads=2,
+                           head_dim=256, ffn=5120, vocab=151936, rms_eps=1e-6, qk_norm=True,
+                           rope=RopeConfig(theta=10000000.0, partial_rotary_factor=0.25),
+                           layer_types=tuple("full" if (i + 1) % 4 == 0 else "linear" for i in range(48)),
+                           lin_k_heads=16, lin_v_heads=32, lin_k_dim=128, lin_v_dim=128, lin_conv=4, attn_gate=True,
+                           norm_one_plus=True, n_experts=512, n_experts_per_tok=10, moe_ffn=512, router="softmax",
+                           shared_expert_ffn=512, shared_expert_gate=True, quant="mxfp8")
     if n in ("tiny-mla",):
         return ModelConfig(name="tiny-mla", family="deepseek_v3", n_layers=3, hidden=256, n_heads=4, n_kv_heads=4,
                            head_dim=48, ffn=512, vocab=1024, mla=True, q_lora_rank=64, kv_lora_rank=32,
@@ -328,4 +413,4 @@ def preset(name: str) -> ModelConfig:
 
 
 PRESETS = ("tiny-llama", "llama-3.1-8b", "llama-3.1-70b", "qwen3-235b-a22b", "deepseek-v3", "tiny-moe", "tiny-mla",
-           "tiny-qwen3", "tiny-qwen2", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-yarn")
+           "tiny-qwen3", "tiny-qwen2", "tiny-qwen3-next", "qwen3-next-80b-a3b", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-yarn")

@@ -26,6 +26,9 @@ class OracleModel:
         self.k: list[torch.Tensor | None] = [None] * cfg.n_layers
         self.v: list[torch.Tensor | None] = [None] * cfg.n_layers
         self._cache: dict[str, torch.Tensor] = {}
+        self.lin_hist: dict[int, torch.Tensor] = {}     # per gated-delta-rule layer: every convolution input so far
+        self.lin_state: dict[int, torch.Tensor] = {}    # ... and the [hv, dk, dv] state
+        self.one = 1.0 if cfg.norm_one_plus else 0.0    # zero-centred RMSNorm weights (hub layout of the hybrid models)
 
     def W(self, name: str, shape: tuple[int, ...]) -> torch.Tensor:
         if name not in self._cache:
@@ -36,9 +39,65 @@ class OracleModel:
     def _norm(x, w, eps):
         return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
 
+    def _linear_attn(self, i: int, x: torch.Tensor) -> torch.Tensor:
+        """Gated delta rule, token by token, straight from the checkpoint's tensors in their stored (per-key-head
+        grouped, or split) row order."""
+        c, p = self.cfg, f"{self.cfg.weight_prefix}layers.{i}.linear_attn."
+        T, H = x.shape[0], c.hidden
+        hk, hv, dk, dv = c.lin_k_heads, c.lin_v_heads, c.lin_k_dim, c.lin_v_dim
+        kd, vd, r = hk * dk, hv * dv, hv // hk
+        if c.lin_split_proj:
+            mixed = x @ self.W(p + "in_proj_qkv.weight", (2 * kd + vd, H)).t()
+            z = (x @ self.W(p + "in_proj_z.weight", (vd, H)).t()).view(T, hv, dv)
+            b = x @ self.W(p + "in_proj_b.weight", (hv, H)).t()
+            a = x @ self.W(p + "in_proj_a.weight", (hv, H)).t()
+        else:
+            qkvz = (x @ self.W(p + "in_proj_qkvz.weight", (2 * kd + 2 * vd, H)).t()).view(T, hk, 2 * dk + 2 * r * dv)
+            ba = (x @ self.W(p + "in_proj_ba.weight", (2 * hv, H)).t()).view(T, hk, 2 * r)
+            q_, k_, v_, z = qkvz.split((dk, dk, r * dv, r * dv), -1)
+            mixed = torch.cat((q_.reshape(T, kd), k_.reshape(T, kd), v_.reshape(T, vd)), -1)
+            z = z.reshape(T, hv, dv)
+            b, a = ba[..., :r].reshape(T, hv), ba[..., r:].reshape(T, hv)
+        hist = self.lin_hist.get(i)
+        hist = mixed if hist is None else torch.cat((hist, mixed), 0)
+        self.lin_hist[i] = hist
+        w = self.W(p + "conv1d.weight", (2 * kd + vd, 1, c.lin_conv))[:, 0]
+        n0 = hist.shape[0] - T
+        conv = torch.zeros_like(mixed)
+        for t in range(T):
+            for j in range(c.lin_conv):
+                src_t = n0 + t - (c.lin_conv - 1) + j
+                if src_t >= 0:
+                    conv[t] += hist[src_t] * w[:, j]
+        conv = F.silu(conv)
+        q, k, v = conv.split((kd, kd, vd), -1)
+        q, k, v = q.view(T, hk, dk), k.view(T, hk, dk), v.view(T, hv, dv)
+        q = q / q.norm(dim=-1, keepdim=True).clamp_min(1e-6) * dk ** -0.5
+        k = k / k.norm(dim=-1, keepdim=True).clamp_min(1e-6)
+        beta = torch.sigmoid(b)
+        g = -self.W(p + "A_log", (hv,)).exp() * F.softplus(a + self.W(p + "dt_bias", (hv,)))
+        S = self.lin_state.get(i)
+        if S is None:
+            S = torch.zeros(hv, dk, dv)
+        out = torch.zeros(T, hv, dv)
+        for t in range(T):
+            for h in range(hv):
+                kh, qh = k[t, h // r], q[t, h // r]
+                S[h] = S[h] * g[t, h].exp()
+                delta = (v[t, h] - kh @ S[h]) * beta[t, h]
+                S[h] = S[h] + torch.outer(kh, delta)
+                out[t, h] = qh @ S[h]
+        self.lin_state[i] = S
+        out = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + c.rms_eps) * self.W(p + "norm.weight", (dv,))
+        out = out * F.silu(z)
+        return out.reshape(T, vd) @ self.W(p + "out_proj.weight", (H, vd)).t()
+
     def _attn(self, i: int, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
-        c, p = self.cfg, f"model.layers.{i}.self_attn."
+        c, p = self.cfg, f"{self.cfg.weight_prefix}layers.{i}.self_attn."
         T, H, D = x.shape[0], c.hidden, c.head_dim
+        if c.layer_is_linear(i):
+            return self._linear_attn(i, x)
+        gate = None
         if c.mla:
             qk = c.qk_nope_dim + c.qk_rope_dim
             if c.q_lora_rank:
@@ -64,7 +123,11 @@ class OracleModel:
                 scale *= m * m
             n_kv, dv = c.n_heads, c.v_head_dim
         else:
-            q = x @ self.W(p + "q_proj.weight", (c.n_heads * D, H)).t()
+            if c.attn_gate:
+                qg = (x @ self.W(p + "q_proj.weight", (c.n_heads * 2 * D, H)).t()).view(T, c.n_heads, 2 * D)
+                q, gate = qg[..., :D].reshape(T, c.n_heads * D), qg[..., D:].reshape(T, c.n_heads * D)
+            else:
+                q = x @ self.W(p + "q_proj.weight", (c.n_heads * D, H)).t()
             k = x @ self.W(p + "k_proj.weight", (c.n_kv_heads * D, H)).t()
             v = x @ self.W(p + "v_proj.weight", (c.n_kv_heads * D, H)).t()
             if c.attn_bias:
@@ -76,8 +139,8 @@ class OracleModel:
                 k = self._norm(k, self.W(p + "k_norm.weight", (c.n_kv_heads * D,)), c.rms_eps)
             q, k, v = q.view(T, c.n_heads, D), k.view(T, c.n_kv_heads, D), v.view(T, c.n_kv_heads, D)
             if c.qk_norm:
-                q = self._norm(q, self.W(p + "q_norm.weight", (D,)), c.rms_eps)
-                k = self._norm(k, self.W(p + "k_norm.weight", (D,)), c.rms_eps)
+                q = self._norm(q, self.W(p + "q_norm.weight", (D,)) + self.one, c.rms_eps)
+                k = self._norm(k, self.W(p + "k_norm.weight", (D,)) + self.one, c.rms_eps)
             q = ref.rope(q, pos, self.inv_freq, self.mscale)
             k = ref.rope(k, pos, self.inv_freq, self.mscale)
             scale, n_kv, dv = D ** -0.5, c.n_kv_heads, D
@@ -100,13 +163,15 @@ class OracleModel:
         else:
             pr = torch.softmax(sc, -1)
         o = torch.einsum("hgtn,nhd->thgd", pr, V).reshape(T, c.n_heads * dv)
+        if gate is not None:
+            o = o * torch.sigmoid(gate)
         return o @ self.W(p + "o_proj.weight", (H, c.n_heads * dv)).t()
 
     def _ffn(self, i: int, x: torch.Tensor) -> torch.Tensor:
         from .weights import moe_names
         c, H = self.cfg, self.cfg.hidden
         nm = moe_names(c)
-        p = f"model.layers.{i}." + (nm["prefix"] if c.layer_is_moe(i) else "mlp.")
+        p = f"{self.cfg.weight_prefix}layers.{i}." + (nm["prefix"] if c.layer_is_moe(i) else "mlp.")
 
         def mlp(prefix: str, F_: int, t: torch.Tensor, names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")) -> torch.Tensor:
             g = t @ self.W(prefix + names[0], (F_, H)).t()
@@ -126,19 +191,24 @@ class OracleModel:
                 y[t] += wts[t, j] * mlp(f"{p}experts.{e}.", c.moe_ffn, x[t:t + 1], (nm["gate"], nm["up"], nm["down"]))[0]
         if c.n_shared_experts:
             y = y + mlp(p + "shared_experts.", c.moe_ffn * c.n_shared_experts, x)
+        if c.shared_expert_ffn:
+            sh = mlp(p + "shared_expert.", c.shared_expert_ffn, x)
+            if c.shared_expert_gate:
+                sh = sh * torch.sigmoid(x @ self.W(p + "shared_expert_gate.weight", (1, H)).t())
+            y = y + sh
         return y
 
     def forward(self, tokens: torch.Tensor, start_pos: int) -> torch.Tensor:
         """Logits ``[T, V]`` for ``tokens [T]`` appended at ``start_pos``."""
         c = self.cfg
         pos = torch.arange(start_pos, start_pos + tokens.numel())
-        h = self.W("model.embed_tokens.weight", (c.vocab, c.hidden))[tokens.long()]
+        h = self.W(c.weight_prefix + "embed_tokens.weight", (c.vocab, c.hidden))[tokens.long()]
         for i in range(c.n_layers):
-            p = f"model.layers.{i}."
-            h = h + self._attn(i, self._norm(h, self.W(p + "input_layernorm.weight", (c.hidden,)), c.rms_eps), pos)
-            h = h + self._ffn(i, self._norm(h, self.W(p + "post_attention_layernorm.weight", (c.hidden,)), c.rms_eps))
-        h = self._norm(h, self.W("model.norm.weight", (c.hidden,)), c.rms_eps)
-        head = "model.embed_tokens.weight" if c.tie_embeddings else "lm_head.weight"
+            p = f"{self.cfg.weight_prefix}layers.{i}."
+            h = h + self._attn(i, self._norm(h, self.W(p + "input_layernorm.weight", (c.hidden,)) + self.one, c.rms_eps), pos)
+            h = h + self._ffn(i, self._norm(h, self.W(p + "post_attention_layernorm.weight", (c.hidden,)) + self.one, c.rms_eps))
+        h = self._norm(h, self.W(c.weight_prefix + "norm.weight", (c.hidden,)) + self.one, c.rms_eps)
+        head = c.weight_prefix + "embed_tokens.weight" if c.tie_embeddings else "lm_head.weight"
         return h @ self.W(head, (c.vocab, c.hidden)).t()
 
     def greedy(self, prompt: torch.Tensor, n_new: int) -> list[int]:

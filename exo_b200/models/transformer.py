@@ -20,7 +20,7 @@ import torch
 from .. import ops
 from ..ops import reference as ref
 from .config import ModelConfig
-from .weights import ModelWeights, ShardSpec, local_heads, expert_range
+from .weights import ModelWeights, ShardSpec, local_heads, expert_range, linear_heads
 
 
 class LocalComm:
@@ -86,13 +86,20 @@ class KVPool:
     """Paged KV storage for the layers this rank holds (block size 16 by default)."""
 
     def __init__(self, cfg: ModelConfig, spec: ShardSpec, n_blocks: int, block_size: int = 16,
-                 device: str | torch.device = "cpu", dtype: torch.dtype | None = None):
+                 device: str | torch.device = "cpu", dtype: torch.dtype | None = None, max_seqs: int = 64):
         self.cfg, self.block_size, self.n_blocks = cfg, block_size, n_blocks
         dt = dtype or (torch.bfloat16 if cfg.dtype == "bf16" else torch.float32)
         self.layers: dict[int, tuple[torch.Tensor, torch.Tensor | None]] = {}
         _, hkv = local_heads(cfg, spec)
         for i in spec.layers(cfg):
-            if cfg.mla:
+            if cfg.layer_is_linear(i):
+                # a gated-delta-rule layer keeps no keys and values: per sequence seat (seat 0 = scratch) the last
+                # taps-1 inputs of its convolution and the [dk, dv] state of every value head, the latter in fp32
+                hk, hv = linear_heads(cfg, spec)
+                conv = torch.zeros(max_seqs + 1, 2 * hk * cfg.lin_k_dim + hv * cfg.lin_v_dim, cfg.lin_conv - 1, dtype=dt, device=device)
+                rec = torch.zeros(max_seqs + 1, hv, cfg.lin_k_dim, cfg.lin_v_dim, dtype=torch.float32, device=device)
+                self.layers[i] = (conv, rec)
+            elif cfg.mla:
                 c = torch.zeros(n_blocks, block_size, cfg.kv_lora_rank + cfg.qk_rope_dim, dtype=dt, device=device)
                 self.layers[i] = (c, None)
             else:
@@ -103,11 +110,23 @@ class KVPool:
     @staticmethod
     def bytes_per_block(cfg: ModelConfig, spec: ShardSpec, block_size: int = 16) -> int:
         el = 2 if cfg.dtype == "bf16" else 4
-        n_layers = len(spec.layers(cfg))
+        n_layers = sum(1 for i in spec.layers(cfg) if not cfg.layer_is_linear(i))
         if cfg.mla:
             return n_layers * block_size * (cfg.kv_lora_rank + cfg.qk_rope_dim) * el
         _, hkv = local_heads(cfg, spec)
         return n_layers * 2 * block_size * hkv * cfg.head_dim * el
+
+
+    @staticmethod
+    def state_bytes(cfg: ModelConfig, spec: ShardSpec, max_seqs: int) -> int:
+        """Bytes of recurrent state (all gated-delta-rule layers of this shard, ``max_seqs`` seats plus scratch)."""
+        n = sum(1 for i in spec.layers(cfg) if cfg.layer_is_linear(i))
+        if not n:
+            return 0
+        el = 2 if cfg.dtype == "bf16" else 4
+        hk, hv = linear_heads(cfg, spec)
+        per_seat = (2 * hk * cfg.lin_k_dim + hv * cfg.lin_v_dim) * (cfg.lin_conv - 1) * el + hv * cfg.lin_k_dim * cfg.lin_v_dim * 4
+        return n * (max_seqs + 1) * per_seat
 
 
 class Decoder:
@@ -138,7 +157,7 @@ class Decoder:
         if state is None:
             cfg, spec = self.cfg, self.spec
             ok = (tokens.is_cuda and tokens.dtype == torch.int32 and cfg.dtype == "bf16" and spec.tp_size == 1
-                  and spec.pp_size == 1 and not cfg.mla and isinstance(self.w.embed, torch.Tensor)
+                  and spec.pp_size == 1 and not cfg.mla and not cfg.layer_types and isinstance(self.w.embed, torch.Tensor)
                   and self.w.embed.dtype == torch.bfloat16
                   and not cfg.is_moe and not cfg.sliding_window and not cfg.attn_sinks and isinstance(self.comm, LocalComm)
                   and isinstance(self.w.lm_head, torch.Tensor) and self.w.lm_head.dtype == torch.bfloat16
@@ -165,11 +184,27 @@ class Decoder:
         if cfg.qk_norm_full:
             qkv = self._full_width_qk_norm(qkv, lw)
             q_norm = k_norm = None
-        q = ops.qk_rope_append(qkv, inp.positions, self.inv_freq, self.rope_mscale, self.n_q, self.n_kv,
+        width = (self.n_q + 2 * self.n_kv) * cfg.head_dim
+        q = ops.qk_rope_append(qkv[:, :width] if cfg.attn_gate else qkv, inp.positions, self.inv_freq, self.rope_mscale, self.n_q, self.n_kv,
                                cfg.head_dim, kc, vc, inp.slots, q_norm, k_norm, cfg.rms_eps)
         o = ops.paged_attention(q, kc, vc, inp.block_tables, inp.seq_lens, inp.cu_q, self.scale,
                                 cfg.sliding_window, lw.sinks, inp.max_q_len)
-        return self.comm.row_linear(o.reshape(o.shape[0], -1), lw.wo, h)
+        o = o.reshape(o.shape[0], -1)
+        if cfg.attn_gate:        # the projection's last n_q*D columns gate the attention output per element
+            o = ops.sigmoid_gate(o, qkv[:, (self.n_q + 2 * self.n_kv) * cfg.head_dim:])
+        return self.comm.row_linear(o, lw.wo, h)
+
+    def _attn_linear(self, lw, h, inp: StepInputs, state) -> torch.Tensor:
+        """Gated delta rule in place of softmax attention (``src/exo/worker/engines/mlx/auto_parallel.py:1150-1200`` shards
+        the same layer by key-head groups): input projection, then one op for convolution + recurrence + gated norm over
+        this rank's heads and the sequences' state seats, then the row-parallel output projection."""
+        cfg = self.cfg
+        proj = ops.norm_linear(h, lw.attn_norm, cfg.rms_eps, lw.lin_in)
+        hk, hv = linear_heads(cfg, self.spec)
+        conv_state, rec_state = state
+        o = ops.gated_delta(proj, lw.lin_conv_w, lw.lin_a_log, lw.lin_dt_bias, lw.lin_norm, cfg.rms_eps, conv_state, rec_state,
+                            inp.state_slots, inp.cu_q, inp.positions, hk, hv, cfg.lin_k_dim, cfg.lin_v_dim)
+        return self.comm.row_linear(o, lw.lin_out, h)
 
     def _full_width_qk_norm(self, qkv: torch.Tensor, lw) -> torch.Tensor:
         """RMSNorm of q over ALL query heads and of k over ALL key heads (MiniMax).  Under tensor parallelism a rank
@@ -231,7 +266,11 @@ class Decoder:
                                  cfg.n_group, cfg.topk_group, cfg.routed_scaling)
         elo, _ = expert_range(cfg, self.spec)
         y = ops.moe_experts(x, lw.e_gate_up, lw.e_down, wts, ids, elo, cfg.n_experts)
-        if lw.s_gate_up is not None:
+        if lw.s_gate is not None:
+            # this rank's slice of the shared expert, scaled per token by sigmoid(x . w_gate) (the gate is replicated)
+            sh = ops.linear(ops.linear(x, lw.s_gate_up, swiglu=True), lw.s_down)
+            y = ops.scaled_add(y, sh, ops.linear(x, lw.s_gate))
+        elif lw.s_gate_up is not None:
             y = ops.linear(ops.linear(x, lw.s_gate_up, swiglu=True), lw.s_down, residual=y)
         return self.comm.row_sum(y, h)      # may stay pending: the next layer's norm is fused into the reduction
 
@@ -253,7 +292,8 @@ class Decoder:
             self.embed_patches = None
         for i in self.spec.layers(cfg):
             lw = w.layers[i]
-            h = (self._attn_mla if cfg.mla else self._attn_gqa)(lw, h, inp, kv.layers[i])
+            attn = self._attn_linear if cfg.layer_is_linear(i) else self._attn_mla if cfg.mla else self._attn_gqa
+            h = attn(lw, h, inp, kv.layers[i])
             h = self._ffn_moe(lw, h) if cfg.layer_is_moe(i) else self._ffn_dense(lw, h)
         if not self.spec.is_last_stage:
             return resolve(h)

@@ -286,6 +286,14 @@ class LayerWeights:
     e_down: torch.Tensor | None = None       # [E_local, H, F]
     s_gate_up: torch.Tensor | None = None    # shared experts, TP-sliced
     s_down: torch.Tensor | None = None
+    s_gate: torch.Tensor | None = None       # [1, H]: sigmoid gate on the shared expert's output (Qwen3-Next)
+    # gated-delta-rule layer (rows of lin_in: q | k | v | z | b | a of this rank's heads)
+    lin_in: torch.Tensor | None = None       # [2*hk*dk + 2*hv*dv + 2*hv, H] local
+    lin_conv_w: torch.Tensor | None = None   # [2*hk*dk + hv*dv, taps] fp32
+    lin_a_log: torch.Tensor | None = None    # [hv] fp32
+    lin_dt_bias: torch.Tensor | None = None  # [hv] fp32
+    lin_norm: torch.Tensor | None = None     # [dv]
+    lin_out: torch.Tensor | None = None      # [H, hv*dv] local
 
 
 @dataclass
@@ -323,7 +331,66 @@ def moe_names(cfg: ModelConfig) -> dict[str, str]:
             "bias": "gate.e_score_correction_bias"}
 
 
-QUANTIZED_FIELDS = ("wqkv", "wo", "w_gate_up", "w_down", "e_gate_up", "e_down", "s_gate_up", "s_down", "wq_a", "wq_b", "wkv_a")
+QUANTIZED_FIELDS = ("wqkv", "wo", "w_gate_up", "w_down", "e_gate_up", "e_down", "s_gate_up", "s_down", "wq_a", "wq_b", "wkv_a",
+                    "lin_out")
+
+
+def linear_heads(cfg: ModelConfig, spec: ShardSpec) -> tuple[int, int]:
+    """``(key heads, value heads)`` of a gated-delta-rule layer on this rank: key heads are split over the ranks and
+    each takes its ``lin_v_heads / lin_k_heads`` value heads along."""
+    if cfg.lin_k_heads % spec.tp_size:
+        raise ValueError(f"{cfg.lin_k_heads} linear-attention key heads do not split over {spec.tp_size} ranks")
+    return cfg.lin_k_heads // spec.tp_size, cfg.lin_v_heads // spec.tp_size
+
+
+def _linear_attention_weights(cfg: ModelConfig, spec: ShardSpec, src: "TensorSource", p: str, lw: "LayerWeights", fin,
+                              hf_form: bool) -> None:
+    """Read one gated-delta-rule layer and bring its input projection into the row order ``q | k | v | z | b | a``.
+
+    Qwen3-Next stores ``in_proj_qkvz`` / ``in_proj_ba`` grouped per key head (``[q k v.. z..]`` and ``[b.. a..]`` of one key
+    head, then the next); Qwen3.5 stores ``in_proj_qkv`` (already ``q | k | v`` over all heads), ``in_proj_z``, ``in_proj_b``
+    and ``in_proj_a``.  ``hf_form``: the convolution weight is ``[C, 1, taps]`` (hub layout) rather than ``[C, taps, 1]``."""
+    H, r, n = cfg.hidden, spec.tp_rank, spec.tp_size
+    hk, hv, dk, dv = cfg.lin_k_heads, cfg.lin_v_heads, cfg.lin_k_dim, cfg.lin_v_dim
+    kd, vd, ratio = hk * dk, hv * dv, hv // hk
+    a = p + "linear_attn."
+    if cfg.lin_split_proj:
+        wqkv = src.get(a + "in_proj_qkv.weight", (2 * kd + vd, H))
+        wq, wk, wv = wqkv[:kd], wqkv[kd:2 * kd], wqkv[2 * kd:]
+        wz = src.get(a + "in_proj_z.weight", (vd, H))
+        wb = src.get(a + "in_proj_b.weight", (hv, H))
+        wa = src.get(a + "in_proj_a.weight", (hv, H))
+    else:
+        g = src.get(a + "in_proj_qkvz.weight", (2 * kd + 2 * vd, H)).view(hk, 2 * dk + 2 * ratio * dv, H)
+        wq, wk = g[:, :dk].reshape(kd, H), g[:, dk:2 * dk].reshape(kd, H)
+        wv = g[:, 2 * dk:2 * dk + ratio * dv].reshape(vd, H)
+        wz = g[:, 2 * dk + ratio * dv:].reshape(vd, H)
+        ba = src.get(a + "in_proj_ba.weight", (2 * hv, H)).view(hk, 2 * ratio, H)
+        wb, wa = ba[:, :ratio].reshape(hv, H), ba[:, ratio:].reshape(hv, H)
+    lw.lin_in = fin(torch.cat([_rows(t, r, n) for t in (wq, wk, wv, wz, wb, wa)], 0))
+    C, taps = 2 * kd + vd, cfg.lin_conv
+    cw = src.get(a + "conv1d.weight", (C, 1, taps) if hf_form else (C, taps, 1)).reshape(C, taps)
+    lw.lin_conv_w = fin(torch.cat((_rows(cw[:kd], r, n), _rows(cw[kd:2 * kd], r, n), _rows(cw[2 * kd:], r, n)), 0), torch.float32)
+    lw.lin_a_log = fin(_rows(src.get(a + "A_log", (hv,)), r, n), torch.float32)
+    lw.lin_dt_bias = fin(_rows(src.get(a + "dt_bias", (hv,)), r, n), torch.float32)
+    lw.lin_norm = fin(src.get(a + "norm.weight", (dv,)))
+    lw.lin_out = fin(_cols(src.get(a + "out_proj.weight", (H, vd)), r, n))
+
+
+def _expert_tensor(src: "TensorSource", m: str, e: int, part: str, shape: tuple[int, ...]) -> torch.Tensor:
+    """Weight ``part`` (``gate_proj.weight`` ...) of routed expert ``e``: one tensor per expert (hub layout), or a slice of
+    the stacked ``switch_mlp.<part>`` tensor that MLX conversions write."""
+    name = f"{m}experts.{e}.{part}"
+    if src.has(name) or not src.has(f"{m}switch_mlp.{part}"):
+        return src.get(name, shape)
+    cache = getattr(src, "_stacked", None)
+    if cache is None or cache[0] != m:           # the stacked tensors of one layer at a time
+        cache = (m, {})
+        src._stacked = cache
+    if part not in cache[1]:
+        cache[1][part] = src.get(f"{m}switch_mlp.{part}", None)
+    return cache[1][part][e]
+
 
 
 def quantize_layer(cfg: ModelConfig, lw: "LayerWeights") -> "LayerWeights":
@@ -353,12 +420,29 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
 
     layers: dict[int, LayerWeights] = {}
     lrange = spec.layers(cfg)
+    root = cfg.weight_prefix
+    if root != "model." and not src.has(root + "embed_tokens.weight") and src.has("model.embed_tokens.weight"):
+        root = "model."                      # a text-only export of a checkpoint family that usually wraps the text model
+    # hybrid models: hub checkpoints keep RMSNorm weights zero-centred and the convolution as [C, 1, taps]; MLX
+    # conversions have already added the 1 and moved the tap axis
+    hf_form = True
+    if cfg.has_linear_layers and isinstance(src, SafetensorsSource):
+        first = next(i for i in range(cfg.n_layers) if cfg.layer_is_linear(i))
+        hf_form = src.index[f"{root}layers.{first}.linear_attn.conv1d.weight"][2][-1] != 1
+    one = 1.0 if (cfg.norm_one_plus and hf_form) else 0.0
+
+    def norm(name: str, shape: tuple[int, ...]) -> torch.Tensor:
+        t = src.get(name, shape)
+        return fin(t.float() + one) if one else fin(t)
+
     for li, i in enumerate(lrange):
-        p = f"model.layers.{i}."
-        lw = LayerWeights(attn_norm=fin(src.get(p + "input_layernorm.weight", (H,))),
-                          ffn_norm=fin(src.get(p + "post_attention_layernorm.weight", (H,))))
+        p = f"{root}layers.{i}."
+        lw = LayerWeights(attn_norm=norm(p + "input_layernorm.weight", (H,)),
+                          ffn_norm=norm(p + "post_attention_layernorm.weight", (H,)))
         a = p + "self_attn."
-        if cfg.mla:
+        if cfg.layer_is_linear(i):
+            _linear_attention_weights(cfg, spec, src, p, lw, fin, hf_form)
+        elif cfg.mla:
             qk = cfg.qk_nope_dim + cfg.qk_rope_dim
             hl = cfg.n_heads // n
             if cfg.q_lora_rank:
@@ -377,10 +461,16 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             lw.wo = fin(_cols(src.get(a + "o_proj.weight", (H, cfg.n_heads * cfg.v_head_dim)), r, n))
         else:
             klo, khi = kv_head_range(cfg, spec)
-            wq = _rows(src.get(a + "q_proj.weight", (cfg.n_heads * D, H)), r, n)
+            gate_rows: tuple[torch.Tensor, ...] = ()
+            if cfg.attn_gate:          # q_proj holds [q, gate] per head: the gate rows go behind v
+                qg = src.get(a + "q_proj.weight", (cfg.n_heads * 2 * D, H)).view(cfg.n_heads, 2, D, H)
+                wq = _rows(qg[:, 0].reshape(cfg.n_heads * D, H), r, n)
+                gate_rows = (_rows(qg[:, 1].reshape(cfg.n_heads * D, H), r, n),)
+            else:
+                wq = _rows(src.get(a + "q_proj.weight", (cfg.n_heads * D, H)), r, n)
             wk = src.get(a + "k_proj.weight", (cfg.n_kv_heads * D, H))[klo * D:khi * D]
             wv = src.get(a + "v_proj.weight", (cfg.n_kv_heads * D, H))[klo * D:khi * D]
-            lw.wqkv = fin(torch.cat((wq, wk, wv), 0))
+            lw.wqkv = fin(torch.cat((wq, wk, wv) + gate_rows, 0))
             if cfg.attn_bias:
                 bq = _rows(src.get(a + "q_proj.bias", (cfg.n_heads * D,)), r, n)
                 bk = src.get(a + "k_proj.bias", (cfg.n_kv_heads * D,))[klo * D:khi * D]
@@ -388,8 +478,8 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
                 lw.bqkv = fin(torch.cat((bq, bk, bv), 0))
             lw.wo = fin(_cols(src.get(a + "o_proj.weight", (H, cfg.n_heads * D)), r, n))
             if cfg.qk_norm:
-                lw.q_norm = fin(src.get(a + "q_norm.weight", (D,)))
-                lw.k_norm = fin(src.get(a + "k_norm.weight", (D,)))
+                lw.q_norm = norm(a + "q_norm.weight", (D,))
+                lw.k_norm = norm(a + "k_norm.weight", (D,))
             if cfg.qk_norm_full:      # one weight per output column of q / k: this rank's slice of it
                 lw.q_norm = fin(_rows(src.get(a + "q_norm.weight", (cfg.n_heads * D,)), r, n))
                 lw.k_norm = fin(src.get(a + "k_norm.weight", (cfg.n_kv_heads * D,))[klo * D:khi * D])
@@ -406,8 +496,8 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             gus, dns = [], []
             for e in range(elo, ehi):
                 ep = f"{m}experts.{e}."
-                gus.append(torch.cat((src.get(ep + nm["gate"], (F, H)), src.get(ep + nm["up"], (F, H))), 0))
-                dns.append(src.get(ep + nm["down"], (H, F)))
+                gus.append(torch.cat((_expert_tensor(src, m, e, nm["gate"], (F, H)), _expert_tensor(src, m, e, nm["up"], (F, H))), 0))
+                dns.append(_expert_tensor(src, m, e, nm["down"], (H, F)))
             lw.e_gate_up = fin(torch.stack(gus))
             lw.e_down = fin(torch.stack(dns))
             if cfg.n_shared_experts:
@@ -416,6 +506,13 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
                 lw.s_gate_up = fin(torch.cat((_rows(src.get(sp + "gate_proj.weight", (Fs, H)), r, n),
                                               _rows(src.get(sp + "up_proj.weight", (Fs, H)), r, n)), 0))
                 lw.s_down = fin(_cols(src.get(sp + "down_proj.weight", (H, Fs)), r, n))
+            if cfg.shared_expert_ffn:
+                Fs, sp = cfg.shared_expert_ffn, m + "shared_expert."
+                lw.s_gate_up = fin(torch.cat((_rows(src.get(sp + "gate_proj.weight", (Fs, H)), r, n),
+                                              _rows(src.get(sp + "up_proj.weight", (Fs, H)), r, n)), 0))
+                lw.s_down = fin(_cols(src.get(sp + "down_proj.weight", (H, Fs)), r, n))
+                if cfg.shared_expert_gate:
+                    lw.s_gate = fin(src.get(m + "shared_expert_gate.weight", (1, H)))
         else:
             F = cfg.ffn
             lw.w_gate_up = fin(torch.cat((_rows(src.get(m + "gate_proj.weight", (F, H)), r, n),
@@ -426,10 +523,10 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             progress(li + 1, len(lrange))
     embed = final_norm = lm_head = None
     if spec.is_first_stage or (cfg.tie_embeddings and spec.is_last_stage):
-        embed = fin(src.get("model.embed_tokens.weight", (cfg.vocab, H)))
+        embed = fin(src.get(root + "embed_tokens.weight", (cfg.vocab, H)))
     if spec.is_last_stage:
-        final_norm = fin(src.get("model.norm.weight", (H,)))
-        name = "model.embed_tokens.weight" if cfg.tie_embeddings or not src.has("lm_head.weight") else "lm_head.weight"
+        final_norm = norm(root + "norm.weight", (H,))
+        name = root + "embed_tokens.weight" if cfg.tie_embeddings or not src.has("lm_head.weight") else "lm_head.weight"
         full = src.get(name, (cfg.vocab, H))
         vpad = vocab_shard(cfg.vocab, n)
         lm_head = fin(full[min(r * vpad, cfg.vocab):min((r + 1) * vpad, cfg.vocab)])
@@ -472,7 +569,16 @@ def _fast_shard(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device) ->
     for i in spec.layers(cfg):
         p = f"L{i}."
         lw = LayerWeights(attn_norm=torch.ones(H, dtype=dt, device=device), ffn_norm=torch.ones(H, dtype=dt, device=device))
-        if cfg.mla:
+        if cfg.layer_is_linear(i):
+            hk, hv = linear_heads(cfg, spec)
+            kd, vd = hk * cfg.lin_k_dim, hv * cfg.lin_v_dim
+            lw.lin_in = src.get(p + "lin_in", (2 * kd + 2 * vd + 2 * hv, H))
+            lw.lin_conv_w = src.get(p + "lin_conv", (2 * kd + vd, cfg.lin_conv)).float() * 10
+            lw.lin_a_log = src.get(p + "lin_a", (hv,)).float()
+            lw.lin_dt_bias = src.get(p + "lin_dt", (hv,)).float()
+            lw.lin_norm = torch.ones(cfg.lin_v_dim, dtype=dt, device=device)
+            lw.lin_out = src.get(p + "lin_out", (H, vd))
+        elif cfg.mla:
             qk = cfg.qk_nope_dim + cfg.qk_rope_dim
             if cfg.q_lora_rank:
                 lw.wq_a = src.get(p + "qa", (cfg.q_lora_rank, H))
@@ -486,7 +592,7 @@ def _fast_shard(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device) ->
             lw.w_uv = src.get(p + "uv", (hq, cfg.v_head_dim, cfg.kv_lora_rank))
             lw.wo = src.get(p + "o", (H, hq * cfg.v_head_dim))
         else:
-            lw.wqkv = src.get(p + "qkv", ((hq + 2 * hkv) * D, H))
+            lw.wqkv = src.get(p + "qkv", ((hq + 2 * hkv + (hq if cfg.attn_gate else 0)) * D, H))
             lw.wo = src.get(p + "o", (H, hq * D))
             if cfg.qk_norm:
                 lw.q_norm = torch.ones(D, dtype=dt, device=device)
@@ -503,10 +609,12 @@ def _fast_shard(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device) ->
                 lw.router_bias = torch.zeros(E, dtype=torch.float32, device=device)
             lw.e_gate_up = src.get(p + "egu", (el, 2 * F, H))
             lw.e_down = src.get(p + "ed", (el, H, F))
-            if cfg.n_shared_experts:
-                Fs = F * cfg.n_shared_experts // n
+            if cfg.n_shared_experts or cfg.shared_expert_ffn:
+                Fs = (F * cfg.n_shared_experts or cfg.shared_expert_ffn) // n
                 lw.s_gate_up = src.get(p + "sgu", (2 * Fs, H))
                 lw.s_down = src.get(p + "sd", (H, Fs))
+                if cfg.shared_expert_gate:
+                    lw.s_gate = src.get(p + "sg", (1, H))
         else:
             lw.w_gate_up = src.get(p + "gu", (2 * cfg.ffn // n, H))
             lw.w_down = src.get(p + "d", (H, cfg.ffn // n))

@@ -138,3 +138,27 @@ def argmax(logits):
     if logits.is_cuda:
         return cuda_ops().argmax(logits)
     return logits.float().argmax(-1)
+
+
+def gated_delta(proj, conv_w, a_log, dt_bias, norm_w, eps, conv_state, rec_state, seats, cu_q, positions, hk, hv, dk, dv):
+    """A gated-delta-rule layer between its projections over a ragged batch: causal convolution + SiLU, L2-normalised
+    q/k, the recurrence over each sequence's state seat, gated RMSNorm (``reference.gated_delta`` is the definition)."""
+    if proj.is_cuda:
+        return cuda_ops().gated_delta(proj, conv_w, a_log, dt_bias, norm_w, eps, conv_state, rec_state, seats, cu_q,
+                                      positions, hk, hv, dk, dv)
+    return ref.gated_delta(proj, conv_w, a_log, dt_bias, norm_w, eps, conv_state, rec_state, seats, cu_q, positions,
+                           hk, hv, dk, dv)
+
+
+def sigmoid_gate(x, gate):
+    """``x * sigmoid(gate)``, element by element (``gate`` may be a column slice of a wider tensor)."""
+    if x.is_cuda:
+        return cuda_ops().sigmoid_gate(x, gate)
+    return (x.float() * torch.sigmoid(gate.float())).to(x.dtype)
+
+
+def scaled_add(y, x, logit):
+    """``y + x * sigmoid(logit)`` with one ``logit`` per row."""
+    if x.is_cuda:
+        return cuda_ops().scaled_add(y, x, logit)
+    return (y.float() + x.float() * torch.sigmoid(logit.float())).to(y.dtype)

@@ -45,6 +45,9 @@ _p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_long
 class _Sig:
     exo_rmsnorm = (_i, [_p, _p, _p, _p, _p, _i, _i, _f, _i, _p])
     exo_swiglu = (_i, [_p, _p, _i, _i, _i, _p])
+    exo_gated_delta = (_i, [_p, _i, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p])
+    exo_sigmoid_gate = (_i, [_p, _p, _i, _p, _i, _i, _i, _p])
+    exo_scaled_add = (_i, [_p, _p, _p, _p, _i, _i, _i, _p])
     exo_embedding = (_i, [_p, _p, _p, _i, _i, _i, _i, _p])
     exo_qk_rope_append = (_i, [_p, _p, _p, _f, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _f, _i, _i, _p])
     exo_argmax_chunks = (_i, [_i, _i])
@@ -186,6 +189,45 @@ def swiglu(gate_up):
     rows, F2 = gate_up.shape
     out = torch.empty(rows, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
     _chk(load().exo_swiglu(_ptr(gate_up), _ptr(out), rows, F2 // 2, _dt(gate_up), _st()), "swiglu")
+    _count()
+    return out
+
+
+def gated_delta(proj, conv_w, a_log, dt_bias, norm_w, eps, conv_state, rec_state, seats, cu_q, positions, hk, hv, dk, dv):
+    """Convolution + gated delta rule + gated norm of one linear-attention layer (three launches, no host reads)."""
+    proj = proj.contiguous()
+    T, ld = proj.shape
+    B = cu_q.numel() - 1
+    C = 2 * hk * dk + hv * dv
+    if ld != C + hv * dv + 2 * hv or conv_state.dtype != proj.dtype or rec_state.dtype != torch.float32:
+        raise KernelError(f"gated_delta: projection width {ld} / state dtypes do not fit hk={hk} hv={hv} dk={dk} dv={dv}")
+    if CHECKS:
+        _check_indices("state seats", seats, rec_state.shape[0])
+    y = _empty(T, C, dtype=proj.dtype, device=proj.device, what="gated_delta conv")
+    out = _empty(T, hv * dv, dtype=proj.dtype, device=proj.device, what="gated_delta out")
+    _chk(load().exo_gated_delta(_ptr(proj), ld, _ptr(conv_w), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), float(eps),
+                                _ptr(conv_state), _ptr(rec_state), _ptr(seats), _ptr(cu_q), _ptr(positions), T, B, hk, hv,
+                                dk, dv, conv_w.shape[1], _ptr(y), _ptr(out), _dt(proj), _st()), "gated_delta")
+    _count(3)
+    return out
+
+
+def sigmoid_gate(x, gate):
+    x = x.contiguous()
+    rows, n = x.shape
+    if gate.stride(-1) != 1 or gate.shape != x.shape:
+        gate = gate.contiguous()
+    out = _empty_like(x, "sigmoid_gate out")
+    _chk(load().exo_sigmoid_gate(_ptr(x), _ptr(gate), gate.stride(0), _ptr(out), rows, n, _dt(x), _st()), "sigmoid_gate")
+    _count()
+    return out
+
+
+def scaled_add(y, x, logit):
+    y, x, logit = y.contiguous(), x.contiguous(), logit.contiguous()
+    rows, n = x.shape
+    out = _empty_like(x, "scaled_add out")
+    _chk(load().exo_scaled_add(_ptr(y), _ptr(x), _ptr(logit), _ptr(out), rows, n, _dt(x), _st()), "scaled_add")
     _count()
     return out
 

@@ -310,3 +310,121 @@ def top_logprobs(logits: torch.Tensor, chosen: torch.Tensor, k: int) -> tuple[to
     lp = torch.log_softmax(logits.float(), -1)
     tv, ti = lp.topk(k, dim=-1)
     return lp.gather(1, chosen.long()[:, None])[:, 0], tv, ti
+
+
+# ----------------------------------------------------------------------------
+# Gated delta rule (the linear-attention layers of Qwen3-Next / Qwen3.5)
+# ----------------------------------------------------------------------------
+def gated_delta_sequence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                         state: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """The recurrence itself, one token after another, for ONE sequence.
+
+    ``q, k [L, hv, dk]`` (already L2-normalised, q already scaled), ``v [L, hv, dv]``, ``g, beta [L, hv]``,
+    ``state [hv, dk, dv]`` fp32.  Per token: ``S <- S * exp(g)``; ``delta = (v - k . S) * beta``;
+    ``S <- S + k (x) delta``; ``o = q . S``.  Returns ``(o [L, hv, dv], S)``."""
+    S = state.clone()
+    out = torch.empty(v.shape, dtype=torch.float32, device=v.device)
+    for t in range(q.shape[0]):
+        S = S * g[t].exp()[:, None, None]
+        mem = (S * k[t][:, :, None]).sum(1)
+        delta = (v[t] - mem) * beta[t][:, None]
+        S = S + k[t][:, :, None] * delta[:, None, :]
+        out[t] = (S * q[t][:, :, None]).sum(1)
+    return out, S
+
+
+def gated_delta_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                        state: torch.Tensor, chunk: int = 64) -> tuple[torch.Tensor, torch.Tensor]:
+    """The same map as ``gated_delta_sequence`` in its chunk-parallel form (matrix products over blocks of ``chunk``
+    tokens; the state crosses chunk borders only).  Within a chunk the dependency of token i on the deltas of tokens
+    j < i is a unit lower-triangular system, solved by forward substitution; everything else is GEMM-shaped."""
+    L, hv, dk = q.shape
+    dv = v.shape[-1]
+    pad = (-L) % chunk
+    if pad:
+        z = lambda t: torch.cat((t, t.new_zeros((pad,) + t.shape[1:])), 0)      # noqa: E731
+        q, k, v, g, beta = z(q), z(k), z(v), z(g), z(beta)
+    n = (L + pad) // chunk
+    # [hv, n, chunk, .]
+    hd = lambda t: t.reshape(n, chunk, hv, -1).permute(2, 0, 1, 3).float()         # noqa: E731
+    q, k, v = hd(q), hd(k), hd(v)
+    g = g.reshape(n, chunk, hv).permute(2, 0, 1).float()
+    beta = beta.reshape(n, chunk, hv).permute(2, 0, 1).float()
+    gc = g.cumsum(-1)                                                  # decay from the chunk's start to each token
+    kb, vb = k * beta[..., None], v * beta[..., None]
+    tri_incl = torch.triu(torch.ones(chunk, chunk, dtype=torch.bool, device=q.device), 0)
+    decay = (gc[..., :, None] - gc[..., None, :]).tril().exp().tril()  # exp(gc_i - gc_j) for j <= i
+    A = -((kb @ k.transpose(-1, -2)) * decay).masked_fill(tri_incl, 0)
+    for i in range(1, chunk):                                          # (I - A)^-1 by forward substitution
+        row = A[..., i, :i].clone()
+        A[..., i, :i] = row + (row.unsqueeze(-1) * A[..., :i, :i].clone()).sum(-2)
+    A = A + torch.eye(chunk, dtype=A.dtype, device=A.device)
+    u = A @ vb                                                         # deltas if the incoming state were zero
+    w = A @ (kb * gc.exp()[..., None])                                 # what the incoming state takes away from them
+    S = state.float().clone()
+    out = torch.empty(hv, n, chunk, dv, dtype=torch.float32, device=q.device)
+    tri_excl = torch.triu(torch.ones(chunk, chunk, dtype=torch.bool, device=q.device), 1)
+    for c in range(n):
+        qc, kc = q[:, c], k[:, c]
+        attn = ((qc @ kc.transpose(-1, -2)) * decay[:, c]).masked_fill(tri_excl, 0)
+        delta = u[:, c] - w[:, c] @ S
+        out[:, c] = (qc * gc[:, c, :, None].exp()) @ S + attn @ delta
+        last = gc[:, c, -1]
+        S = S * last[:, None, None].exp() + (kc * (last[:, None] - gc[:, c]).exp()[..., None]).transpose(-1, -2) @ delta
+    out = out.permute(1, 2, 0, 3).reshape(n * chunk, hv, dv)[:L]
+    return out, S
+
+
+def gated_delta(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor,
+                eps: float, conv_state: torch.Tensor, rec_state: torch.Tensor, seats: torch.Tensor, cu_q: torch.Tensor,
+                positions: torch.Tensor, hk: int, hv: int, dk: int, dv: int, chunk: int = 64) -> torch.Tensor:
+    """One gated-delta-rule layer between its input projection and its output projection, over a ragged batch.
+
+    ``proj [T, 2*hk*dk + 2*hv*dv + 2*hv]`` holds, per token, ``q | k | v | z | b | a``.  Per sequence ``s`` (tokens
+    ``cu_q[s] .. cu_q[s+1]``, state seat ``seats[s]``; a sequence whose first token has position 0 starts from zero
+    state):
+
+    1. ``q | k | v`` go through a causal depthwise convolution with ``conv_w [2*hk*dk + hv*dv, taps]`` whose history is
+       the seat's ``conv_state [., channels, taps-1]``, then SiLU;
+    2. q and k are L2-normalised per head, q scaled by ``dk**-0.5``; a key head serves ``hv / hk`` value heads;
+    3. ``beta = sigmoid(b)``, ``g = -exp(a_log) * softplus(a + dt_bias)``; the recurrence of ``gated_delta_sequence``
+       runs from the seat's ``rec_state [., hv, dk, dv]`` and leaves the new state there;
+    4. the output is RMS-normalised per value head, times ``norm_w [dv]``, times ``silu(z)``.
+
+    Returns ``[T, hv*dv]`` in ``proj``'s dtype.  Definition followed: ``Qwen3NextGatedDeltaNet.forward`` of the
+    ``transformers`` library (the reference runs the same layer through ``mlx_lm.models.qwen3_next``)."""
+    T = proj.shape[0]
+    kd, vd = hk * dk, hv * dv
+    taps = conv_w.shape[1]
+    qkv, z, b, a = proj.float().split((2 * kd + vd, vd, hv, hv), -1)
+    out = torch.zeros(T, hv, dv, dtype=torch.float32, device=proj.device)
+    cu = cu_q.tolist()
+    seat_l = seats.tolist()
+    w = conv_w.float()
+    for s in range(len(cu) - 1):
+        t0, t1 = cu[s], cu[s + 1]
+        if t1 <= t0:
+            continue
+        seat = seat_l[s]
+        fresh = int(positions[t0]) == 0
+        hist = torch.zeros(taps - 1, 2 * kd + vd, device=proj.device) if fresh else conv_state[seat].float().t()
+        x = torch.cat((hist, qkv[t0:t1]), 0)                                     # [taps-1+L, C]
+        conv_state[seat] = x[-(taps - 1):].t().to(conv_state.dtype)
+        y = sum(x[j:j + (t1 - t0)] * w[:, j] for j in range(taps))
+        y = torch.nn.functional.silu(y)
+        q, k, v = y.split((kd, kd, vd), -1)
+        L = t1 - t0
+        q, k = q.reshape(L, hk, dk), k.reshape(L, hk, dk)
+        q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+        k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+        q, k = q.repeat_interleave(hv // hk, 1), k.repeat_interleave(hv // hk, 1)
+        beta = torch.sigmoid(b[t0:t1])
+        g = -a_log.float().exp() * torch.nn.functional.softplus(a[t0:t1] + dt_bias.float())
+        S0 = torch.zeros_like(rec_state[seat]) if fresh else rec_state[seat]
+        fn = gated_delta_sequence if L < chunk else gated_delta_chunked
+        o, S1 = fn(q, k, v.reshape(L, hv, dv), g, beta, S0.float())
+        rec_state[seat] = S1.to(rec_state.dtype)
+        out[t0:t1] = o
+    out = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+    out = out * torch.nn.functional.silu(z.reshape(T, hv, dv))
+    return out.reshape(T, vd).to(proj.dtype)

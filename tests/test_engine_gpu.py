@@ -73,6 +73,32 @@ def test_moe_and_mla_on_gpu_match_oracle_fp32():
         assert eng.generate(p, SamplingParams(max_tokens=8, **GREEDY)) == want
 
 
+def test_hybrid_linear_attention_model_on_gpu_matches_oracle_and_graphs():
+    """Qwen3-Next-shaped model: gated-delta-rule layers (recurrent state per sequence seat) beside gated softmax attention.
+    fp32 against the oracle with a chunked prompt; bf16 with CUDA graphs against eager, several sequences at once."""
+    cfg = preset("tiny-qwen3-next")
+    w = build_weights(cfg, ShardSpec(), RandomSource(seed=0), device="cuda")
+    p = oracle_prompt(40, cfg.vocab, seed=3).tolist()
+    want = OracleModel(cfg, RandomSource(seed=0)).greedy(torch.tensor(p), 8)
+    eng = Engine(cfg, w, n_blocks=64, device="cuda", use_graphs=False, prefill_chunk=16)
+    assert eng.generate(p, SamplingParams(max_tokens=8, **GREEDY)) == want
+    cfg = preset("tiny-qwen3-next")
+    cfg.dtype = "bf16"
+    w = fast_random_weights(cfg, ShardSpec(), "cuda")
+    prompts = [oracle_prompt(n, cfg.vocab, seed=n).tolist() for n in (50, 31, 77)]
+    outs = []
+    for graphs in (False, True):
+        eng = Engine(cfg, w, n_blocks=128, device="cuda", use_graphs=graphs, max_seqs=4)
+        ids = [eng.submit(q, SamplingParams(max_tokens=12, **GREEDY)) for q in prompts]
+        got = {i: [] for i in ids}
+        while eng.has_work:
+            for o in eng.step():
+                if o.token is not None:
+                    got[o.req_id].append(o.token)
+        outs.append([got[i] for i in ids])
+    assert outs[0] == outs[1] and all(len(x) == 12 for x in outs[0])
+
+
 @pytest.mark.parametrize("name,quant", [("tiny-moe", "none"), ("tiny-moe", "mxfp8"), ("tiny-llama", "mxfp8"), ("tiny-mla", "dsfp8")])
 def test_bf16_moe_and_fp8_models_on_gpu_track_the_cpu_definition(name, quant):
     """bf16 activations through the MoE kernels (router, grouped GEMMs / GEMVs) and the fp8-weight GEMMs, with and

@@ -40,6 +40,21 @@ CASES = {
     "minimax": ({"model_type": "minimax_m2", "num_local_experts": 8, "num_experts_per_tok": 2, "use_qk_norm": True,
                  "rotary_dim": 16},
                 dict(family="minimax", is_moe=True, router="sigmoid", router_bias=True, qk_norm_full=True, moe_ffn=256)),
+    "qwen3-next": ({"model_type": "qwen3_next", "num_hidden_layers": 4, "linear_num_key_heads": 2, "linear_num_value_heads": 4,
+                    "linear_key_head_dim": 32, "linear_value_head_dim": 32, "linear_conv_kernel_dim": 4, "num_experts": 8,
+                    "num_experts_per_tok": 2, "moe_intermediate_size": 64, "shared_expert_intermediate_size": 64,
+                    "decoder_sparse_step": 1, "mlp_only_layers": [1], "norm_topk_prob": True, "rms_norm_eps": 1e-6},
+                   dict(family="qwen3_next", is_moe=True, router="softmax", qk_norm=True, attn_gate=True, norm_one_plus=True,
+                        layer_types=("linear", "linear", "linear", "full"), lin_split_proj=False, shared_expert_gate=True,
+                        mlp_only_layers=(1,))),
+    "qwen3.5": ({"model_type": "qwen3_5", "text_config": {**BASE, "model_type": "qwen3_5_text", "num_hidden_layers": 3,
+                                                          "layer_types": ["linear_attention", "full_attention", "linear_attention"],
+                                                          "linear_num_key_heads": 2, "linear_num_value_heads": 2,
+                                                          "linear_key_head_dim": 32, "linear_value_head_dim": 64,
+                                                          "rope_parameters": {"rope_theta": 50000.0, "rope_type": "default",
+                                                                              "partial_rotary_factor": 0.5}}},
+                dict(family="qwen3_next", is_moe=False, lin_split_proj=True, weight_prefix="model.language_model.",
+                     layer_types=("linear", "full", "linear"), attn_gate=True)),
     "qwen2": ({"model_type": "qwen2", "tie_word_embeddings": True}, dict(family="llama", attn_bias=True, tie_embeddings=True)),
 }
 
@@ -59,6 +74,10 @@ def test_config_json_of_each_family_maps_to_engine_fields(name, tmp_path):
         assert getattr(cfg, k) == v, (name, k, getattr(cfg, k), v)
     if name == "glm4-moe":
         assert cfg.rope.partial_rotary_factor == 0.5
+    if name == "qwen3-next":
+        assert cfg.rope.partial_rotary_factor == 0.25 and [cfg.layer_is_moe(i) for i in range(4)] == [True, False, True, True]
+    if name == "qwen3.5":
+        assert cfg.rope.partial_rotary_factor == 0.5 and cfg.rope.theta == 50000.0
 
 
 class Recorder(RandomSource):
@@ -78,7 +97,7 @@ class Recorder(RandomSource):
         return t
 
 
-@pytest.mark.parametrize("name", ["mixtral", "glm4-moe", "glm4-moe-lite", "ministral", "minimax"])
+@pytest.mark.parametrize("name", ["mixtral", "glm4-moe", "glm4-moe-lite", "ministral", "minimax", "qwen3-next", "qwen3.5"])
 def test_checkpoint_under_family_names_loads_and_matches_oracle(name, tmp_path):
     extra, _ = CASES[name]
     d = tmp_path / name
@@ -96,6 +115,12 @@ def test_checkpoint_under_family_names_loads_and_matches_oracle(name, tmp_path):
     if name == "minimax":
         assert any(n.endswith("block_sparse_moe.e_score_correction_bias") for n in names)
         assert rec.seen["model.layers.0.self_attn.q_norm.weight"].shape == (4 * 32,) and cfg.rope.partial_rotary_factor == 0.5
+    if name == "qwen3-next":
+        assert rec.seen["model.layers.0.linear_attn.in_proj_qkvz.weight"].shape == (2 * 64 + 2 * 128, 128)
+        assert rec.seen["model.layers.3.self_attn.q_proj.weight"].shape == (4 * 2 * 32, 128)
+        assert "model.layers.0.mlp.shared_expert_gate.weight" in names and "model.layers.1.mlp.gate_proj.weight" in names
+    if name == "qwen3.5":
+        assert "model.language_model.layers.0.linear_attn.in_proj_qkv.weight" in names
     if name.startswith("glm4-moe"):
         assert any(n.endswith("mlp.gate.e_score_correction_bias") for n in names)
         assert any(n.endswith("layers.0.mlp.gate_proj.weight") for n in names)       # the leading dense layer

@@ -1,0 +1,103 @@
+"""Qwen3-Next (gated delta rule + gated attention + shared-expert gate) against the ``transformers`` implementation.
+
+A tiny randomly initialised ``Qwen3NextForCausalLM`` is exported under the hub's tensor names; the engine loads that
+checkpoint and must reproduce the library's logits over a prompt (chunked prefill included: the recurrent state and the
+convolution history cross chunk and step borders) and its greedy continuation.
+"""
+import json
+
+import pytest
+import torch
+
+from exo_b200.engine.engine import Engine
+from exo_b200.engine.kv import SamplingParams
+from exo_b200.models.config import ModelConfig
+from exo_b200.models.transformer import Decoder, KVPool, StepInputs
+from exo_b200.models.weights import SafetensorsSource, ShardSpec, build_weights, write_safetensors
+
+tf = pytest.importorskip("transformers")
+if not hasattr(tf, "Qwen3NextForCausalLM"):
+    pytest.skip("this transformers build has no Qwen3-Next", allow_module_level=True)
+
+
+@pytest.fixture(scope="module")
+def exported(tmp_path_factory):
+    torch.manual_seed(0)
+    hc = tf.Qwen3NextConfig(
+        vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=32, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
+        linear_value_head_dim=32, linear_conv_kernel_dim=4, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+        shared_expert_intermediate_size=64, decoder_sparse_step=1, mlp_only_layers=[1], norm_topk_prob=True,
+        rms_norm_eps=1e-6, max_position_embeddings=512, tie_word_embeddings=False)
+    model = tf.Qwen3NextForCausalLM(hc).float().eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            p.normal_(0, 0.2 if "norm" in n else 0.5 if ("A_log" in n or "dt_bias" in n) else 0.08)
+    tensors = {}
+    for k, v in model.state_dict().items():
+        if k.endswith("mlp.experts.gate_up_proj"):          # the library keeps experts stacked; the hub keeps one tensor each
+            stem, F = k[:-len("gate_up_proj")], v.shape[1] // 2
+            for e in range(v.shape[0]):
+                tensors[f"{stem}{e}.gate_proj.weight"] = v[e, :F].clone()
+                tensors[f"{stem}{e}.up_proj.weight"] = v[e, F:].clone()
+        elif k.endswith("mlp.experts.down_proj"):
+            stem = k[:-len("down_proj")]
+            for e in range(v.shape[0]):
+                tensors[f"{stem}{e}.down_proj.weight"] = v[e].clone()
+        else:
+            tensors[k] = v.clone()
+    d = tmp_path_factory.mktemp("qwen3next")
+    (d / "config.json").write_text(json.dumps(hc.to_dict()))
+    write_safetensors(d / "model.safetensors", tensors)
+    cfg = ModelConfig.from_pretrained(d)
+    cfg.dtype = "fp32"
+    return model, cfg, d
+
+
+def test_config_fields(exported):
+    _, cfg, _ = exported
+    assert cfg.family == "qwen3_next" and cfg.layer_types == ("linear", "linear", "linear", "full")
+    assert cfg.rope.partial_rotary_factor == 0.25 and cfg.attn_gate and cfg.norm_one_plus and cfg.shared_expert_gate
+    assert [cfg.layer_is_moe(i) for i in range(4)] == [True, False, True, True]
+
+
+def _step(dec, kv, toks, start, seat=1):
+    T = len(toks)
+    n = start + T
+    bt = torch.arange(1, 1 + (n + 15) // 16, dtype=torch.int32)[None]
+    pos = torch.arange(start, n, dtype=torch.int32)
+    inp = StepInputs(tokens=torch.tensor(toks, dtype=torch.int32), positions=pos, slots=(16 + pos).int(),
+                     cu_q=torch.tensor([0, T], dtype=torch.int32), seq_lens=torch.tensor([n], dtype=torch.int32),
+                     block_tables=bt, logit_rows=torch.arange(T), max_q_len=T,
+                     state_slots=torch.tensor([seat], dtype=torch.int32))
+    return dec.logits(inp, kv)
+
+
+def test_logits_match_library_across_chunks_and_steps(exported):
+    model, cfg, d = exported
+    w = build_weights(cfg, ShardSpec(), SafetensorsSource(d, dtype=torch.float32), device="cpu")
+    dec = Decoder(cfg, w)
+    kv = KVPool(cfg, ShardSpec(), n_blocks=16, device="cpu", max_seqs=2)
+    toks = torch.randint(0, cfg.vocab, (1, 100), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        want = model(toks).logits[0]
+    got = torch.cat((_step(dec, kv, toks[0, :70].tolist(), 0),          # longer than one chunk of the chunked form
+                     _step(dec, kv, toks[0, 70:97].tolist(), 70),       # continues from the stored state (sequential form)
+                     _step(dec, kv, toks[0, 97:98].tolist(), 97),       # single-token steps
+                     _step(dec, kv, toks[0, 98:99].tolist(), 98),
+                     _step(dec, kv, toks[0, 99:100].tolist(), 99)), 0)
+    assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), float((got - want).abs().max())
+    # a new sequence on the same seat starts from zero state (its first position is 0)
+    again = _step(dec, kv, toks[0, :10].tolist(), 0)
+    assert torch.allclose(again, want[:10], atol=2e-3, rtol=2e-3)
+
+
+def test_engine_greedy_matches_library(exported):
+    model, cfg, d = exported
+    w = build_weights(cfg, ShardSpec(), SafetensorsSource(d, dtype=torch.float32), device="cpu")
+    prompt = torch.randint(0, cfg.vocab, (1, 23), generator=torch.Generator().manual_seed(9))
+    with torch.no_grad():
+        want = model.generate(prompt, max_new_tokens=8, do_sample=False)[0, 23:].tolist()
+    eng = Engine(cfg, w, n_blocks=32, device="cpu", prefill_chunk=16)      # the prompt takes two prefill chunks
+    got = eng.generate(prompt[0].tolist(), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    assert got == want

@@ -402,3 +402,53 @@ def test_gemm_tcgen05_fused_swiglu(K, M, F, K_):
     finally:
         K.use_fused_swiglu = True
     close(got, unfused, 1e-2, 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hk,hv,dk,dv,lens", [
+    (2, 4, 32, 32, [5, 1, 70]),          # toy heads; a sequence longer than one chunk of the chunked definition
+    (2, 2, 64, 64, [1, 1, 1, 1]),        # decode-shaped: one token per sequence
+    (4, 8, 128, 128, [130, 1, 17]),      # Qwen3-Next head sizes (512-thread CTAs)
+])
+def test_gated_delta_rule(K, dtype, hk, hv, dk, dv, lens):
+    """Convolution + recurrence + gated norm against the fp32 definition, over two consecutive steps: the second step
+    continues every sequence from the state the first one left in its seat (one sequence restarts from position 0)."""
+    g = torch.Generator(device="cuda").manual_seed(1)
+    B, C, taps, seats_n = len(lens), 2 * hk * dk + hv * dv, 4, 8
+    W = C + hv * dv + 2 * hv
+    conv_w = torch.randn(C, taps, device="cuda", generator=g) * 0.5
+    a_log = torch.randn(hv, device="cuda", generator=g) * 0.5
+    dt_bias = torch.randn(hv, device="cuda", generator=g) * 0.5
+    norm_w = (1 + 0.1 * torch.randn(dv, device="cuda", generator=g)).to(dtype)
+    seats = torch.tensor([3, 1, 5, 2][:B], dtype=torch.int32, device="cuda")
+    conv_k = torch.randn(seats_n, C, taps - 1, device="cuda", generator=g).to(dtype)          # stale content of the seats
+    rec_k = torch.randn(seats_n, hv, dk, dv, device="cuda", generator=g)
+    conv_r, rec_r = conv_k.clone(), rec_k.clone()
+    start = [0] * B
+    for step, step_lens in enumerate((lens, [3] * B)):
+        T = sum(step_lens)
+        cu = torch.tensor([0] + list(torch.tensor(step_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        if step == 1:
+            start[0] = 0                                                                      # seat reused by a new sequence
+        pos = torch.cat([torch.arange(s, s + n) for s, n in zip(start, step_lens)]).to(torch.int32).cuda()
+        proj = torch.randn(T, W, device="cuda", generator=g).to(dtype)
+        got = K.gated_delta(proj, conv_w, a_log, dt_bias, norm_w, 1e-6, conv_k, rec_k, seats, cu, pos, hk, hv, dk, dv)
+        want = ref.gated_delta(proj.float(), conv_w, a_log, dt_bias, norm_w.float(), 1e-6, conv_r, rec_r, seats, cu, pos,
+                               hk, hv, dk, dv)
+        tol = 3e-2 if dtype == torch.bfloat16 else 2e-3
+        close(got, want, tol, tol)
+        used = seats.long()
+        close(rec_k[used], rec_r[used], tol, tol)
+        close(conv_k[used], conv_r[used], 1e-2, 1e-2)
+        start = [s + n for s, n in zip(start, step_lens)]
+
+
+def test_sigmoid_gate_and_scaled_add(K):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    for dtype in (torch.float32, torch.bfloat16):
+        wide = torch.randn(37, 3 * 96, device="cuda", generator=g).to(dtype)
+        x = torch.randn(37, 96, device="cuda", generator=g).to(dtype)
+        close(K.sigmoid_gate(x, wide[:, 192:]), x.float() * torch.sigmoid(wide[:, 192:].float()))
+        y = torch.randn(37, 96, device="cuda", generator=g).to(dtype)
+        logit = torch.randn(37, 1, device="cuda", generator=g).to(dtype)
+        close(K.scaled_add(y, x, logit), y.float() + x.float() * torch.sigmoid(logit.float()))

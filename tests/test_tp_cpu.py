@@ -43,7 +43,8 @@ def _worker(rank, world, port, name, prompt, n_new, q):
 # statistic; KV heads replicated at 4 ranks), GPT-OSS attention (sinks + sliding window), YaRN.
 FAMILIES = [("tiny-llama", 2), ("tiny-llama", 4), ("tiny-moe", 2), ("tiny-mla", 2), ("tiny-mla", 4), ("tiny-qwen3", 2),
             ("tiny-qwen2", 2), ("tiny-glm4-moe", 2), ("tiny-glm4-moe", 4), ("tiny-mixtral", 2), ("tiny-mixtral", 4),
-            ("tiny-minimax", 2), ("tiny-minimax", 4), ("tiny-gpt-oss", 2), ("tiny-yarn", 2)]
+            ("tiny-minimax", 2), ("tiny-minimax", 4), ("tiny-gpt-oss", 2), ("tiny-yarn", 2),
+            ("tiny-qwen3-next", 2)]     # gated-delta-rule heads split by key-head group, state per rank
 
 
 @pytest.mark.parametrize("name,world", FAMILIES)
