@@ -214,9 +214,16 @@ class Executor:
         stream.wait_stream(torch.cuda.current_stream(self.device))
         saved = self.prev_sampled.clone()  # warm-up runs must not disturb the token chain
         with torch.cuda.stream(stream):  # warm-up outside capture (per-device scratch set-up)
+            # a recurrent layer's state update is not idempotent (appending the same KV row twice is): the warm-up
+            # runs advance the scratch seat instead of the sequences' own
+            seats = inp.state_slots.clone() if self.cfg.has_linear_layers else None
+            if seats is not None:
+                inp.state_slots.zero_()
             for _ in range(2):
                 self._forward_sample(inp, samp, greedy, from_prev)
                 self.prev_sampled.copy_(saved)
+            if seats is not None:
+                inp.state_slots.copy_(seats)
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()

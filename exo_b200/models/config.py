@@ -390,7 +390,7 @@ def preset(name: str) -> ModelConfig:
                            dtype="fp32")
     if n in ("tiny-qwen3-next",):  # linear, linear, full, linear: gated delta rule + gated attention, experts with a gated shared expert
         return ModelConfig(name="tiny-qwen3-next", family="qwen3_next", n_layers=4, hidden=256, n_heads=4, n_kv_heads=2,
-                           head_dim=64, ffn=512, vocab=1024, rms_eps=1e-6, qk_norm=True,
+                           head_dim=256, ffn=512, vocab=1024, rms_eps=1e-6, qk_norm=True,
                            rope=RopeConfig(theta=10000.0, partial_rotary_factor=0.25),
                            layer_types=("linear", "linear", "full", "linear"), lin_k_heads=2, lin_v_heads=4, lin_k_dim=64,
                            lin_v_dim=64, lin_conv=4, attn_gate=True, norm_one_plus=True, n_experts=8, n_experts_per_tok=2,

@@ -235,6 +235,7 @@ EXO_API int exo_paged_decode(const void* q, const void* kcache, const void* vcac
   float* part_o = workspace;
   float* part_ml = workspace + (size_t)B * Hq * n_splits * D;
   int GT = (g % 4 == 0) ? 4 : (g % 2 == 0 ? 2 : 1);
+  if (D == 256) GT = 1;      // 32 dims per lane: one query head's state per CTA is what the register file holds
   dim3 grid(n_splits, Hkv * (g / GT), B);
   cudaError_t e = cudaSuccess;
 #define LAUNCH(TT, DD, GG)                                                                                        \
@@ -248,10 +249,12 @@ EXO_API int exo_paged_decode(const void* q, const void* kcache, const void* vcac
   if (dtype == EXO_BF16) {
     if (D == 128) { BY_G(__nv_bfloat16, 128); }
     else if (D == 64) { BY_G(__nv_bfloat16, 64); }
+    else if (D == 256) { LAUNCH(__nv_bfloat16, 256, 1); }
     else return -2;
   } else {
     if (D == 128) { BY_G(float, 128); }
     else if (D == 64) { BY_G(float, 64); }
+    else if (D == 256) { LAUNCH(float, 256, 1); }
     else return -2;
   }
 #undef BY_G
