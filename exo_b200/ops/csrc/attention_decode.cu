@@ -2,7 +2,8 @@
 //
 // Grid (n_splits, Hkv * (g / GT), B).  A CTA streams its slice of one KV head once and scores
 // it against GT query heads that share that KV head (GQA), so K/V bytes are read once per group.
-// Inside a warp, 8 lanes cooperate on one key (D/8 dims each), 4 lane-groups x 2 keys are in
+// Inside a warp, LW lanes cooperate on one key (8 lanes with D/8 dims each; 16 lanes at D = 256, which keeps the
+// per-lane state at 16 dims), 32/LW lane-groups x 2 keys are in
 // flight per iteration; every (lane-group, head) keeps its own online-softmax state, merged at the
 // end through shuffles and shared memory.  Each split publishes (m, l, o) partials to a workspace
 // and takes a ticket; the CTA that draws the last ticket of its (sequence, head group) merges the
@@ -16,12 +17,14 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
                     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
                     T* __restrict__ out, float scale, int Hq, int Hkv, int max_blocks, int block_size, int window,
                     const float* __restrict__ sinks) {
-  constexpr int DPL = D / 8;  // dims per lane
-  constexpr int U = 2;        // keys per lane-group per iteration
+  constexpr int LW = D > 128 ? 16 : 8;  // lanes per key
+  constexpr int NLG = 32 / LW;          // lane groups (keys side by side) per warp
+  constexpr int DPL = D / LW;           // dims per lane
+  constexpr int U = 2;                  // keys per lane-group per iteration
   const int split = blockIdx.x, n_splits = gridDim.x, b = blockIdx.z;
   const int g = Hq / Hkv, tiles_per_kv = g / GT;
   const int kvh = blockIdx.y / tiles_per_kv, h0 = kvh * g + (blockIdx.y % tiles_per_kv) * GT;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 3, ls = lane & 7;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane / LW, ls = lane % LW;
   pdl_trigger();
   pdl_wait();  // q, the appended K/V row and the step inputs come from the preceding kernels
   const int n = seq_lens[b];
@@ -41,12 +44,12 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
     l[i] = 0.f;
   }
   const int* bt = block_tables + (size_t)b * max_blocks;
-  for (int base = t0 + warp * (4 * U); base < t1; base += 16 * U) {  // warp-uniform trip count
+  for (int base = t0 + warp * (NLG * U); base < t1; base += 4 * NLG * U) {  // warp-uniform trip count
     float kf[U][DPL], vf[U][DPL];
     bool valid[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
-      int t = base + u * 4 + lg;
+      int t = base + u * NLG + lg;
       valid[u] = t < t1 && t >= lo_lim;
       if (valid[u]) {
         int blk = bt[t / block_size];
@@ -74,9 +77,8 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
         float a = 0.f;
 #pragma unroll
         for (int d = 0; d < DPL; d++) a += qr[i][d] * kf[u][d];
-        a += __shfl_xor_sync(0xffffffffu, a, 1);
-        a += __shfl_xor_sync(0xffffffffu, a, 2);
-        a += __shfl_xor_sync(0xffffffffu, a, 4);
+#pragma unroll
+        for (int o = 1; o < LW; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
         s[u] = valid[u] ? a : -INFINITY;
       }
       float mn = fmaxf(m[i], fmaxf(s[0], s[1]));
@@ -90,11 +92,11 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
       }
     }
   }
-  // merge the 4 lane-groups of the warp
+  // merge the lane-groups of the warp
 #pragma unroll
   for (int i = 0; i < GT; i++) {
 #pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
+    for (int o = LW; o <= 16; o <<= 1) {
       float mo = __shfl_xor_sync(0xffffffffu, m[i], o), lo2 = __shfl_xor_sync(0xffffffffu, l[i], o);
       float mn = fmaxf(m[i], mo);
       float c0 = (m[i] == -INFINITY) ? 0.f : __expf(m[i] - mn), c1 = (mo == -INFINITY) ? 0.f : __expf(mo - mn);
@@ -235,7 +237,6 @@ EXO_API int exo_paged_decode(const void* q, const void* kcache, const void* vcac
   float* part_o = workspace;
   float* part_ml = workspace + (size_t)B * Hq * n_splits * D;
   int GT = (g % 4 == 0) ? 4 : (g % 2 == 0 ? 2 : 1);
-  if (D == 256) GT = 1;      // 32 dims per lane: one query head's state per CTA is what the register file holds
   dim3 grid(n_splits, Hkv * (g / GT), B);
   cudaError_t e = cudaSuccess;
 #define LAUNCH(TT, DD, GG)                                                                                        \
@@ -249,12 +250,12 @@ EXO_API int exo_paged_decode(const void* q, const void* kcache, const void* vcac
   if (dtype == EXO_BF16) {
     if (D == 128) { BY_G(__nv_bfloat16, 128); }
     else if (D == 64) { BY_G(__nv_bfloat16, 64); }
-    else if (D == 256) { LAUNCH(__nv_bfloat16, 256, 1); }
+    else if (D == 256) { BY_G(__nv_bfloat16, 256); }
     else return -2;
   } else {
     if (D == 128) { BY_G(float, 128); }
     else if (D == 64) { BY_G(float, 64); }
-    else if (D == 256) { LAUNCH(float, 256, 1); }
+    else if (D == 256) { BY_G(float, 256); }
     else return -2;
   }
 #undef BY_G

@@ -208,7 +208,7 @@ def gated_delta(proj, conv_w, a_log, dt_bias, norm_w, eps, conv_state, rec_state
     _chk(load().exo_gated_delta(_ptr(proj), ld, _ptr(conv_w), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), float(eps),
                                 _ptr(conv_state), _ptr(rec_state), _ptr(seats), _ptr(cu_q), _ptr(positions), T, B, hk, hv,
                                 dk, dv, conv_w.shape[1], _ptr(y), _ptr(out), _dt(proj), _st()), "gated_delta")
-    _count(3)
+    _count(3)          # (a fourth, the output norm, when a small grid has its heads split by columns)
     return out
 
 

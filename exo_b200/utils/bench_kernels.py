@@ -1,6 +1,6 @@
 """Micro-benchmarks of the individual sm_100a kernels against the measured roofline.
 
-    python -m exo_b200.utils.bench_kernels [--only gemv,gemm,fp8,moe,attn,mla,prefill] [--peaks MEASURED_PEAKS.json]
+    python -m exo_b200.utils.bench_kernels [--only gemv,gemm,fp8,moe,attn,mla,prefill,gdn,misc] [--peaks MEASURED_PEAKS.json]
 
 Every case is timed with CUDA events after warm-up; a 256 MB buffer is overwritten between
 iterations so that no operand survives in the 126 MB L2.  Output: achieved GB/s or TFLOP/s and
@@ -299,6 +299,42 @@ def main() -> None:
             fl = 4.0 * T * T * Hq * D / 2 / 1e12
             print(f"prefill-attn T={T}: {ms * 1e3:8.1f} us  {fl / ms * 1e3:7.1f} TFLOP/s (causal)  "
                   f"{fl / ms * 1e3 / tf:5.2f} of {basis} bf16")
+    if "gdn" in only:
+        # Qwen3-Next linear-attention layer between its projections: 16 key heads, 32 value heads, 128 x 128 state per head
+        hk, hv, dk, dv, taps = 16, 32, 128, 128, 4
+        C = 2 * hk * dk + hv * dv
+        W = C + hv * dv + 2 * hv
+        conv_w = torch.randn(C, taps, device="cuda") * 0.3
+        a_log, dt_b, nw = torch.randn(hv, device="cuda") * 0.3, torch.randn(hv, device="cuda") * 0.3, rnd(dv)
+        for B, L in ((1, 1), (32, 1), (128, 1), (1, 2048), (4, 2048)):
+            T = B * L
+            n_state = min(64, max(2, int(0.3e9 / (B * hv * dk * dv * 4)) + 1))          # rotate over more state than the L2 holds
+            recs = [torch.zeros(B + 1, hv, dk, dv, device="cuda") for _ in range(n_state)]
+            conv = torch.zeros(B + 1, C, taps - 1, device="cuda", dtype=torch.bfloat16)
+            seats = torch.arange(1, B + 1, device="cuda", dtype=torch.int32)
+            cu = (torch.arange(B + 1, device="cuda", dtype=torch.int32) * L)
+            pos = (torch.arange(L, device="cuda", dtype=torch.int32) + 7).repeat(B)
+            proj = rnd(T, W)
+            ms = timeit_rot([(lambda r=r: K.gated_delta(proj, conv_w, a_log, dt_b, nw, 1e-6, conv, r, seats, cu, pos, hk, hv, dk, dv))
+                             for r in recs])
+            gb = (2 * B * hv * dk * dv * 4 + T * (W + C + hv * dv) * 2) / 1e9
+            print(f"gated-delta B={B} L={L}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s ({gb / ms * 1e3 / hbm:4.2f} of {basis} HBM)  "
+                  f"{ms * 1e3 / L:6.2f} us per token of a sequence")
+        # full-attention layers of the same model: 16 query heads over 2 KV heads of 256 dims
+        Hq, Hkv, D, bs = 16, 2, 256, 16
+        for B, ctx in ((1, 2048), (32, 2048), (32, 8192)):
+            nb = B * (ctx // bs + 1) + 1
+            bt = (torch.arange(B * (ctx // bs + 1), device="cuda", dtype=torch.int32) + 1).view(B, -1)
+            sl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+            cu = torch.arange(B + 1, device="cuda", dtype=torch.int32)
+            q = rnd(B, Hq, D)
+            gb = B * ctx * Hkv * D * 2 * 2 / 1e9
+            copies = max(2, int(0.4 / gb) + 1)
+            caches = [(rnd(nb, bs, Hkv, D), rnd(nb, bs, Hkv, D)) for _ in range(copies)]
+            ms = timeit_rot([(lambda kc=kc, vc=vc: K.paged_attention(q, kc, vc, bt, sl, cu, D ** -0.5, max_q_len=1))
+                             for kc, vc in caches])
+            print(f"decode-attn D=256 B={B} ctx={ctx}: {ms * 1e3:8.1f} us  {gb / ms * 1e3:7.0f} GB/s  "
+                  f"{gb / ms * 1e3 / hbm:5.2f} of {basis} HBM")
     if "misc" in only:
         logits = rnd(32, 128256)
         print(f"argmax 32x128256: {timeit(lambda: K.argmax(logits)) * 1e3:.1f} us")

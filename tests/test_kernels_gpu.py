@@ -125,7 +125,7 @@ def _paged_setup(dtype, B, Hq, Hkv, D, lens, qlens, bs=16, seed=0):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (4, 2, 64), (8, 1, 128), (16, 16, 64)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (4, 2, 64), (8, 1, 128), (16, 16, 64), (16, 2, 256), (4, 2, 256), (2, 2, 256)])
 def test_paged_decode(K, dtype, Hq, Hkv, D):
     lens = [1, 17, 300, 2049]
     q, kc, vc, bt, sl, cu = _paged_setup(dtype, 4, Hq, Hkv, D, lens, [1] * 4)
