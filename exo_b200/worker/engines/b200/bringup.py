@@ -290,6 +290,8 @@ class B200Builder(Builder):
         if self.device.type == "cuda":
             free, _total = torch.cuda.mem_get_info(self.device)
             budget = int(free * constants.EXO_GPU_MEMORY_FRACTION)
+            # hybrid models: the sequences' recurrent state is allocated beside the paged cache
+            budget -= KVPool.state_bytes(cfg, self.spec, max(constants.EXO_MAX_CONCURRENT_REQUESTS, 8))
         else:
             budget = 256 << 20
         cap = int(os.environ.get("EXO_MAX_KV_BLOCKS", "0"))

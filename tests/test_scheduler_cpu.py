@@ -59,6 +59,32 @@ def test_block_pool_is_conserved_across_preemption_and_finish():
     assert alloc.n_free == 4 and all(r == 0 for r in alloc.ref)
 
 
+def test_state_seats_are_distinct_while_running_and_return_on_finish_and_preemption():
+    """Every running sequence holds its own seat (1..max_seqs; 0 is the scratch seat of padding rows) for its recurrent
+    state; the plan carries the seats row by row; a finished or preempted sequence gives its seat back."""
+    alloc = BlockAllocator(4, 16)
+    sched = Scheduler(alloc, max_seqs=3, prefill_chunk=32, max_blocks_per_seq=8)
+    p = SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
+    for i, n in enumerate((5, 17, 30)):
+        sched.add(Sequence(f"s{i}", list(range(n)), p, use_prefix_cache=False))
+    seen = set()
+    for _ in range(400):
+        if not sched.has_work:
+            break
+        plan, entries = _run_step(sched)
+        if plan is None:
+            continue
+        seats = [s.state_slot for s in sched.running]
+        assert all(1 <= x <= 3 for x in seats) and len(set(seats)) == len(seats)
+        assert list(plan.state_slots[:len(entries)]) == [s.state_slot or plan.state_slots[i] for i, (s, _) in enumerate(entries)]
+        assert all(1 <= int(x) <= 3 for x in plan.state_slots[:len(entries)])
+        seen.update(int(x) for x in plan.state_slots[:len(entries)])
+        for s in sched.waiting:
+            assert s.state_slot == 0
+    assert not sched.has_work and sched.n_preempted >= 1
+    assert sorted(sched._free_seats) == [1, 2, 3] and len(seen) >= 2
+
+
 def test_prompt_chunks_short_of_the_end_carry_the_no_sample_flag_and_skip_the_read_back():
     """A 100-token prompt in chunks of 32: the first three steps neither project logits nor read ids back; the fourth
     (which reaches the last prompt token) samples.  A decode row riding along makes the step sample again."""
