@@ -206,11 +206,13 @@ class ModelConfig:
         # one entry per checkpoint family the engine can shard (the reference keeps one sharding strategy per family,
         # ``src/exo/worker/engines/mlx/auto_parallel.py:500-599``); architectures that share a block structure share
         # an entry: Ministral / Mistral-3 text models are Llama blocks, GLM-4.x-MoE-Lite and Kimi are DeepSeek-V3
-        # blocks (MLA + sigmoid-routed experts)
+        # blocks (MLA + sigmoid-routed experts); GLM-5 is the DeepSeek-V3.2 block, whose sparse-attention indexer is not
+        # used (every key is attended, which is what the indexer selects from)
         family = {"llama": "llama", "mistral": "llama", "ministral": "llama", "ministral3": "llama", "mistral3": "llama",
                   "qwen2": "llama", "qwen3": "qwen3",
                   "qwen3_moe": "qwen3_moe", "deepseek_v3": "deepseek_v3", "deepseek_v32": "deepseek_v3",
                   "deepseek_v2": "deepseek_v3", "kimi_k2": "deepseek_v3", "glm4_moe_lite": "deepseek_v3",
+                  "glm_moe_dsa": "deepseek_v3",
                   "glm4_moe": "glm4_moe", "mixtral": "mixtral", "minimax": "minimax", "minimax_m2": "minimax",
                   "qwen3_next": "qwen3_next", "qwen3_5": "qwen3_next", "qwen3_5_text": "qwen3_next",
                   "qwen3_5_moe": "qwen3_next", "qwen3_5_moe_text": "qwen3_next",
@@ -312,6 +314,9 @@ class ModelConfig:
             mc.moe_ffn = g("moe_intermediate_size", default=0)
             mc.n_shared_experts = g("n_shared_experts", default=0) or 0
             mc.first_dense_layers = g("first_k_dense_replace", default=0)
+            kinds = g("mlp_layer_types", default=None)          # GLM-5 lists every layer's kind instead
+            if kinds and "first_k_dense_replace" not in cfg:
+                mc.first_dense_layers = next((i for i, k in enumerate(kinds) if k != "dense"), len(kinds))
             mc.router = "sigmoid" if g("scoring_func", default="sigmoid") == "sigmoid" else "softmax"
             mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
             mc.routed_scaling = float(g("routed_scaling_factor", default=1.0))

@@ -37,6 +37,12 @@ CASES = {
                        "kv_lora_rank": 32, "qk_nope_head_dim": 16, "qk_rope_head_dim": 16, "v_head_dim": 16,
                        "norm_topk_prob": True, "routed_scaling_factor": 1.0, "n_group": 1, "topk_group": 1},
                       dict(family="deepseek_v3", mla=True, is_moe=True, router="sigmoid")),
+    "glm5": ({"model_type": "glm_moe_dsa", "n_routed_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 64,
+              "n_shared_experts": 1, "mlp_layer_types": ["dense", "sparse"], "q_lora_rank": 64, "kv_lora_rank": 32,
+              "qk_nope_head_dim": 24, "qk_rope_head_dim": 16, "v_head_dim": 32, "norm_topk_prob": True,
+              "routed_scaling_factor": 2.5, "n_group": 1, "topk_group": 1, "index_topk": 2048, "index_head_dim": 128,
+              "index_n_heads": 32},
+             dict(family="deepseek_v3", mla=True, is_moe=True, router="sigmoid", first_dense_layers=1, v_head_dim=32)),
     "minimax": ({"model_type": "minimax_m2", "num_local_experts": 8, "num_experts_per_tok": 2, "use_qk_norm": True,
                  "rotary_dim": 16},
                 dict(family="minimax", is_moe=True, router="sigmoid", router_bias=True, qk_norm_full=True, moe_ffn=256)),
@@ -97,7 +103,7 @@ class Recorder(RandomSource):
         return t
 
 
-@pytest.mark.parametrize("name", ["mixtral", "glm4-moe", "glm4-moe-lite", "ministral", "minimax", "qwen3-next", "qwen3.5"])
+@pytest.mark.parametrize("name", ["mixtral", "glm4-moe", "glm4-moe-lite", "glm5", "ministral", "minimax", "qwen3-next", "qwen3.5"])
 def test_checkpoint_under_family_names_loads_and_matches_oracle(name, tmp_path):
     extra, _ = CASES[name]
     d = tmp_path / name

@@ -317,6 +317,12 @@ def _family_cfg(name):
                            v_head_dim=128, n_experts=16, n_experts_per_tok=2, moe_ffn=512, n_shared_experts=1,
                            first_dense_layers=1, router="sigmoid", routed_scaling=1.5, n_group=2, topk_group=1,
                            router_bias=True, dtype="bf16")
+    if name == "hybrid":     # Qwen3-Next: gated-delta-rule heads split by key-head group, gated attention with 256-wide heads
+        return ModelConfig(name="t-hybrid", family="qwen3_next", n_layers=4, hidden=1024, n_heads=8, n_kv_heads=2, head_dim=256,
+                           ffn=2048, vocab=4096, rms_eps=1e-6, qk_norm=True, rope=RopeConfig(theta=1e7, partial_rotary_factor=0.25),
+                           layer_types=("linear", "linear", "full", "linear"), lin_k_heads=8, lin_v_heads=16, lin_k_dim=128,
+                           lin_v_dim=128, attn_gate=True, norm_one_plus=True, n_experts=16, n_experts_per_tok=2, moe_ffn=512,
+                           router="softmax", shared_expert_ffn=512, shared_expert_gate=True, dtype="bf16")
     raise KeyError(name)
 
 
@@ -352,7 +358,7 @@ def _family_engine(rank, world, name):
     return [got[i] for i in ids], first
 
 
-@pytest.mark.parametrize("name", ["llama", "kv-replicated", "mxfp8", "moe", "mla"])
+@pytest.mark.parametrize("name", ["llama", "kv-replicated", "mxfp8", "moe", "mla", "hybrid"])
 @pytest.mark.parametrize("world", [pytest.param(w, marks=needs(w)) for w in WORLDS])
 def test_model_families_under_tensor_parallelism_track_the_single_gpu_run(world, name):
     """Every rank of a TP run produces the same tokens, and the first step's logits stay within bf16 rounding of the
