@@ -15,9 +15,12 @@
 //           last CTA of the row resolves the exact threshold inside b* from the list (all pairs, <= CAP entries), adds
 //           the list's kept entries to their chunks, picks the chunk that holds uniform * total and walks it
 //
-// A row whose boundary bin holds more than CAP tokens (a nearly flat distribution) is flagged and re-done by the
-// single-CTA bisection kernel in basic.cu, which the launcher always enqueues behind pass 3 (it returns at once for
-// rows that are not flagged).
+// A row whose boundary bin holds more than CAP tokens (a nearly flat distribution) goes through one more pass between 2
+// and 3: the boundary bin alone is histogrammed again in NB sub-bins (width 2^-15 in u), which finds the boundary
+// sub-bin; pass 3 then lists that sub-bin.  Rows without such a bin return from the extra pass at once.  Only a row
+// whose boundary SUB-bin still holds more than CAP tokens (many equal logits) is flagged and re-done by the single-CTA
+// bisection kernel in basic.cu, which the launcher always enqueues behind pass 3 (it returns at once for rows that are
+// not flagged).
 #include "common.cuh"
 
 namespace {
@@ -38,6 +41,8 @@ struct RowWs {                      // per-row scratch, zero-initialised once; t
   u64 chunk_mass[MAX_CHUNKS];
   u64 list[CAP];
   int list_chunk[CAP];
+  int cnt2[NB];                     // second level: the boundary bin alone, in NB sub-bins
+  u64 mass2[NB];
   u64 c_mass;                       // mass of the bins below b*
   u64 pmass;                        // top_p * total mass (fixed point); ~0 when top-p is off
   int c_cnt;                        // tokens in the bins below b*
@@ -46,7 +51,9 @@ struct RowWs {                      // per-row scratch, zero-initialised once; t
   int n_list;
   int ticket2, ticket3;
   int fallback;
-  int pad;
+  int refine;                       // 1: the boundary bin is too full for the list and gets a second histogram
+  int s_star;                       // boundary sub-bin (NB: none, the whole bin is on one side)
+  int ticket_r;
 };
 
 template <typename T>
@@ -98,6 +105,18 @@ __device__ __forceinline__ int bin_of(float u) {
   int b = (int)(u * BINS_PER_U);
   return b < 0 ? 0 : (b > NB - 1 ? NB - 1 : b);
 }
+// sub-bin of a token that lies in bin b
+__device__ __forceinline__ int sub_bin_of(float u, int b) {
+  int s = (int)((u * BINS_PER_U - (float)b) * (float)NB);
+  return s < 0 ? 0 : (s > NB - 1 ? NB - 1 : s);
+}
+// the tokens of a row fall into three classes against the boundary (b*, s*): kept whole, listed, dropped
+__device__ __forceinline__ bool above_boundary(int b, float u, int b_star, int refined, int s_star) {
+  return b < b_star || (refined && b == b_star && sub_bin_of(u, b) < s_star);
+}
+__device__ __forceinline__ bool on_boundary(int b, float u, int b_star, int refined, int s_star) {
+  return b == b_star && (!refined || sub_bin_of(u, b) == s_star);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(NT) sample_max_kernel(const T* __restrict__ logits, RowWs* __restrict__ wsa, int V,
@@ -108,7 +127,7 @@ __global__ void __launch_bounds__(NT) sample_max_kernel(const T* __restrict__ lo
   pdl_wait();
   int row = blockIdx.y, c = blockIdx.x, tid = threadIdx.x;
   RowWs* ws = wsa + row;
-  for (int i = c * NT + tid; i < NB; i += chunks * NT) { ws->cnt[i] = 0; ws->mass[i] = 0; }
+  for (int i = c * NT + tid; i < NB; i += chunks * NT) { ws->cnt[i] = 0; ws->mass[i] = 0; ws->cnt2[i] = 0; ws->mass2[i] = 0; }
   const T* x = logits + (size_t)row * stride;
   int c0 = c * chunk, c1 = min(V, c0 + chunk);
   float best = -INFINITY;
@@ -225,7 +244,7 @@ __global__ void __launch_bounds__(NT) sample_hist_kernel(const T* __restrict__ l
   u64 pmass = tp >= 1.f ? ~0ull : (u64)((double)tp * (double)total);
   if (tid == 0) {
     ws->pmass = pmass;
-    ws->b_star = NB; ws->resolve = 0; ws->c_cnt = 0; ws->c_mass = 0; ws->fallback = 0;
+    ws->b_star = NB; ws->resolve = 0; ws->c_cnt = 0; ws->c_mass = 0; ws->fallback = 0; ws->refine = 0; ws->s_star = NB;
     ws->ticket2 = 0;
   }
   __syncthreads();
@@ -248,6 +267,99 @@ __global__ void __launch_bounds__(NT) sample_hist_kernel(const T* __restrict__ l
       ws->c_cnt = cb;
       ws->c_mass = mb;
       if (!dropped && !under_floor) {
+        if (n <= CAP) ws->resolve = 1; else ws->refine = 1;
+      }
+    }
+  }
+}
+
+// Second level, for rows whose boundary bin is too full: the same histogram over that bin alone (CTAs of other rows
+// return at once), and the same scan, continued from the count and mass of the bins below it.
+template <typename T>
+__global__ void __launch_bounds__(NT) sample_refine_kernel(const T* __restrict__ logits,
+                                                           const float* __restrict__ temperature,
+                                                           const int* __restrict__ top_k, RowWs* __restrict__ wsa, int V,
+                                                           size_t stride, int chunk, int chunks) {
+  __shared__ unsigned h_cnt[NB], h_hi[NB], h_lo[NB];
+  __shared__ float s_lmax;
+  __shared__ int s_last;
+  __shared__ int s_wc[NT / 32];
+  __shared__ u64 s_wm[NT / 32];
+  pdl_trigger();
+  pdl_wait();
+  int row = blockIdx.y, c = blockIdx.x, tid = threadIdx.x;
+  RowWs* ws = wsa + row;
+  float temp = temperature[row];
+  if (temp <= 0.f || !__ldcg(&ws->refine)) return;
+  for (int i = tid; i < NB; i += NT) { h_cnt[i] = 0; h_hi[i] = 0; h_lo[i] = 0; }
+  if (tid < 32) {
+    float lm; int bi;
+    merge_max(ws, chunks, lm, bi);
+    if (tid == 0) s_lmax = lm;
+  }
+  __syncthreads();
+  float lmax = s_lmax, inv_t = 1.f / fmaxf(temp, 1e-6f);
+  const int b_star = __ldcg(&ws->b_star);
+  const T* x = logits + (size_t)row * stride;
+  int c0 = c * chunk, c1 = min(V, c0 + chunk);
+  for_tokens(x, c0, c1, [&](int i, float l) {
+    float u = (lmax - l) * inv_t;
+    if (bin_of(u) != b_star) return;
+    u64 fx = to_fx(__expf(-u));
+    int sb = sub_bin_of(u, b_star);
+    atomicAdd(&h_cnt[sb], 1u);
+    atomicAdd(&h_hi[sb], (unsigned)(fx >> 16));
+    atomicAdd(&h_lo[sb], (unsigned)(fx & 0xffffu));
+  });
+  __syncthreads();
+  for (int i = tid; i < NB; i += NT)
+    if (h_cnt[i]) { atomicAdd(&ws->cnt2[i], (int)h_cnt[i]); atomicAdd(&ws->mass2[i], ((u64)h_hi[i] << 16) + h_lo[i]); }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(&ws->ticket_r, 1) == chunks - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // ---- the row's last CTA: the boundary sub-bin.  Thread t owns sub-bins [2t, 2t+2). ----
+  int k = top_k[row];
+  if (k <= 0 || k > V) k = V;
+  int n0 = __ldcg(&ws->cnt2[2 * tid]), n1 = __ldcg(&ws->cnt2[2 * tid + 1]);
+  u64 m0 = __ldcg(&ws->mass2[2 * tid]), m1 = __ldcg(&ws->mass2[2 * tid + 1]);
+  int cs = n0 + n1;
+  u64 ms = m0 + m1;
+  int lane = tid & 31, w = tid >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int oc = __shfl_up_sync(0xffffffffu, cs, o);
+    u64 om = __shfl_up_sync(0xffffffffu, ms, o);
+    if (lane >= o) { cs += oc; ms += om; }
+  }
+  if (lane == 31) { s_wc[w] = cs; s_wm[w] = ms; }
+  __syncthreads();
+  const int base_c = __ldcg(&ws->c_cnt);
+  const u64 base_m = __ldcg(&ws->c_mass), pmass = __ldcg(&ws->pmass);
+  int pc = base_c;
+  u64 pm = base_m;
+  for (int j = 0; j < w; j++) { pc += s_wc[j]; pm += s_wm[j]; }
+  int c_excl = pc + cs - (n0 + n1);       // tokens above sub-bin 2t (the lower bins included)
+  u64 m_excl = pm + ms - (m0 + m1);
+  __syncthreads();
+  if (tid == 0) { ws->ticket_r = 0; ws->s_star = NB; }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 2; j++) {
+    int sb = 2 * tid + j;
+    int cb = j ? c_excl + n0 : c_excl, cb1 = cb + (j ? n1 : n0);
+    u64 mb = j ? m_excl + m0 : m_excl, mb1 = mb + (j ? m1 : m0);
+    bool whole = cb1 <= k && mb1 <= pmass;
+    bool prev_whole = cb <= k && mb <= pmass;       // true for sub-bin 0: the bin was not dropped whole
+    if (!whole && prev_whole) {
+      bool dropped = cb >= k || mb >= pmass;
+      int n = j ? n1 : n0;
+      ws->s_star = sb;
+      ws->c_cnt = cb;
+      ws->c_mass = mb;
+      if (!dropped) {
         if (n <= CAP) ws->resolve = 1; else ws->fallback = 1;
       }
     }
@@ -288,6 +400,7 @@ __global__ void __launch_bounds__(NT) sample_draw_kernel(const T* __restrict__ l
   }
   float lmax = s_lmax, inv_t = 1.f / fmaxf(temp, 1e-6f), mp = min_p[row];
   int b_star = __ldcg(&ws->b_star), resolve = __ldcg(&ws->resolve);
+  const int refined = __ldcg(&ws->refine), s_star = __ldcg(&ws->s_star);
   const T* x = logits + (size_t)row * stride;
   int c0 = c * chunk, c1 = min(V, c0 + chunk);
   u64 loc = 0;
@@ -295,11 +408,11 @@ __global__ void __launch_bounds__(NT) sample_draw_kernel(const T* __restrict__ l
     float u = (lmax - l) * inv_t;
     float q = __expf(-u);
     int b = bin_of(u);
-    if (b == b_star && resolve) {
+    if (resolve && on_boundary(b, u, b_star, refined, s_star)) {
       int slot = atomicAdd(&ws->n_list, 1);
       if (slot < CAP) { ws->list[slot] = to_fx(q); ws->list_chunk[slot] = i == bi ? -1 : c; }  // the arg-max is counted below
     }
-    bool keep = (b < b_star && q >= mp) || i == bi;
+    bool keep = (above_boundary(b, u, b_star, refined, s_star) && q >= mp) || i == bi;
     if (keep) loc += to_fx(q);
   });
 #pragma unroll
@@ -389,7 +502,8 @@ __global__ void __launch_bounds__(NT) sample_draw_kernel(const T* __restrict__ l
     float q = __expf(-u);
     int b = bin_of(u);
     u64 fx = to_fx(q);
-    bool keep = (b < b_star && q >= mp) || (b == b_star && resolve && fx >= tau && fx >= fmin) || i == bi;
+    bool keep = (above_boundary(b, u, b_star, refined, s_star) && q >= mp) ||
+                (resolve && on_boundary(b, u, b_star, refined, s_star) && fx >= tau && fx >= fmin) || i == bi;
     if (keep) mine += fx;
   }
   u64 incl = mine;
@@ -411,7 +525,8 @@ __global__ void __launch_bounds__(NT) sample_draw_kernel(const T* __restrict__ l
       float q = __expf(-u);
       int b = bin_of(u);
       u64 fx = to_fx(q);
-      bool keep = (b < b_star && q >= mp) || (b == b_star && resolve && fx >= tau && fx >= fmin) || i == bi;
+      bool keep = (above_boundary(b, u, b_star, refined, s_star) && q >= mp) ||
+                  (resolve && on_boundary(b, u, b_star, refined, s_star) && fx >= tau && fx >= fmin) || i == bi;
       if (!keep) continue;
       run += fx;
       if (run > target) { s_pick = i; break; }
@@ -461,6 +576,9 @@ EXO_API int exo_sample_fast(const void* logits, const float* temperature, const 
   if (e != cudaSuccess) return (int)e;                                                                                \
   e = launch_pdl(sample_hist_kernel<T>, grid, dim3(NT), 0, st, (const T*)logits, temperature, top_k, top_p, min_p, ws, \
                  V, (size_t)stride, chunk, chunks);                                                                   \
+  if (e != cudaSuccess) return (int)e;                                                                                \
+  e = launch_pdl(sample_refine_kernel<T>, grid, dim3(NT), 0, st, (const T*)logits, temperature, top_k, ws, V,          \
+                 (size_t)stride, chunk, chunks);                                                                      \
   if (e != cudaSuccess) return (int)e;                                                                                \
   e = launch_pdl(sample_draw_kernel<T>, grid, dim3(NT), 0, st, (const T*)logits, temperature, top_k, min_p, uniform,   \
                  ws, out, need, V, (size_t)stride, chunk, chunks);                                                    \

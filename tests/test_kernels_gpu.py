@@ -257,8 +257,8 @@ def _keep_set(logits, temp, top_k, top_p, min_p):
 @pytest.mark.parametrize("shape", ["peaked", "flat", "masked"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_sample_distribution_shapes(K, shape, dtype):
-    """Peaked rows (what a trained model emits), nearly flat rows (random weights: the boundary bin overflows and the
-    bisection kernel takes the row) and rows with -inf entries, over the filter settings the API exposes."""
+    """Peaked rows (what a trained model emits), nearly flat rows (random weights: the boundary bin overflows and is histogrammed
+    a second time; bf16 rows, full of equal values, still end in the bisection kernel) and rows with -inf entries, over the filter settings the API exposes."""
     g = torch.Generator(device="cuda").manual_seed(11)
     B, V = 32, 128256
     if shape == "peaked":
