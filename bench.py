@@ -47,6 +47,10 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--no-also", action="store_true")
     ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL-communicator arm behind vs_baseline")
     ap.add_argument("--min-timed-s", type=float, default=1.0, help="repeat each K-step region until this much is timed")
+    ap.add_argument("--pp", type=int, default=1, help="pipeline stages (the N GPUs become PP stages x N/PP tensor-parallel lanes)")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="pre-flight only, one GPU: hold rank 0's shard of an N-way tensor-parallel split with identity "
+                         "collectives (kernel shapes and launch counts of one rank; the tokens mean nothing)")
     ap.add_argument("--layers", type=int, default=0,
                     help="pre-flight only: run the first N layers of the model (the JSON line then says so and is not a result)")
     return ap.parse_args()
@@ -144,17 +148,36 @@ def main() -> None:
     if args.layers:
         from dataclasses import replace
         cfg = replace(cfg, n_layers=min(args.layers, cfg.n_layers))
-    spec = ShardSpec(tp_rank=rank, tp_size=world)
+    pp = max(1, args.pp)
+    if world % pp or cfg.n_layers < pp:
+        raise SystemExit(f"--pp {pp} does not divide {world} GPUs / {cfg.n_layers} layers")
+    tp = world // pp
+    pp_rank, tp_rank = divmod(rank, tp)
+    per_stage = cfg.n_layers // pp
+    spec = ShardSpec(tp_rank=tp_rank, tp_size=tp, pp_rank=pp_rank, pp_size=pp, layer_start=pp_rank * per_stage,
+                     layer_end=cfg.n_layers if pp_rank == pp - 1 else (pp_rank + 1) * per_stage)
+    if args.shard_of > 1 and world == 1:
+        spec = ShardSpec(tp_rank=0, tp_size=args.shard_of)
+    pipe, stage_group = None, None
+    if pp > 1:
+        # every rank creates every group, in the same order: the lanes' stage-to-stage links and the stages' TP groups
+        from exo_b200.parallel.comm import PipeComm
+        stage_groups = [dist.new_group([s * tp + t for t in range(tp)]) for s in range(pp)]
+        lane_groups = [dist.new_group([s * tp + t for s in range(pp)]) for t in range(tp)]
+        stage_group = stage_groups[pp_rank]
+        pipe = PipeComm(pp_rank, pp, tp_rank, tp, lane_groups[tp_rank])
 
     def make_comm(kind: str):
-        if world == 1:
+        if tp == 1:
             return None, "none"
         if kind == "fused":
+            from exo_b200.models.weights import vocab_shard
             from exo_b200.parallel.fused import FusedComm
-            c = FusedComm(dev, max_rows=max(min(args.prompt, 4096), 256), hidden=cfg.hidden, vocab_shard=-(-cfg.vocab // world))
+            c = FusedComm(dev, max_rows=max(min(args.prompt, 4096), 256), hidden=cfg.hidden, vocab_shard=vocab_shard(cfg.vocab, tp),
+                          **({"group": stage_group} if stage_group is not None else {}))
             return c, f"fused ({c.transport})"
         from exo_b200.parallel.comm import NcclComm
-        return NcclComm(), "nccl"
+        return (NcclComm(stage_group) if stage_group is not None else NcclComm()), "nccl"
 
     want = "nccl" if args.comm == "nccl" else "fused"
     try:
@@ -204,12 +227,12 @@ def main() -> None:
             if self.leader:
                 self.eng = Engine(cfg, weights, spec, the_comm, n_blocks=n_blocks, max_seqs=max(max_b, 8), prefill_chunk=4096,
                                   max_blocks_per_seq=per_seq_blocks, device=dev, seed=0,
-                                  plan_sink=(lambda p: chan.send(p, [])) if chan is not None else None)
+                                  plan_sink=(lambda p: chan.send(p, [])) if chan is not None else None, pipe=pipe)
                 self.exe = self.eng.exe
             else:
                 self.eng = None
                 self.exe = Executor(cfg, weights, spec, the_comm, n_blocks=n_blocks, max_blocks_per_seq=per_seq_blocks,
-                                    max_tokens_per_step=4096, max_seqs=max(max_b, 8), device=dev)
+                                    max_tokens_per_step=4096, max_seqs=max(max_b, 8), device=dev, pipe=pipe)
 
         def run(self, marker: str, fn=None) -> None:
             """Leader: do ``fn`` (which steps the engine / publishes plans), then publish ``marker``.
@@ -379,10 +402,11 @@ def main() -> None:
             "ms_per_step": round(main_res["dev_ms_per_step"], 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": round(main_res["dev_tok_s"] / base_res["dev_tok_s"], 3) if base_res else None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
-            "config": {"model": cfg.name + (f" (REDUCED to {cfg.n_layers} layers: pre-flight, not a result)" if args.layers else ""),
+            "config": {"model": cfg.name + (f" (REDUCED to {cfg.n_layers} layers: pre-flight, not a result)" if args.layers else "")
+                       + (f" (ONE RANK'S SHARD of a {args.shard_of}-way split, no collectives: pre-flight, not a result)" if args.shard_of > 1 and world == 1 else ""),
                        "weights": cfg.quant if cfg.quant != "none" else "bf16",
                        "global_batch": args.batch, "seq_len": args.prompt,
-                       "decode_context": f"{args.prompt}+", "parallelism": f"tp{world}", "comm": comm_name,
+                       "decode_context": f"{args.prompt}+", "parallelism": f"tp{world}" if pp == 1 else f"pp{pp}xtp{tp}", "comm": comm_name,
                        "topology": "rank 0 schedules and publishes each step's plan over shared memory; the other ranks execute it"
                                    if world > 1 else "single process",
                        "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no explicit flush",

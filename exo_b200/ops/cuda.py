@@ -45,6 +45,7 @@ _p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_long
 class _Sig:
     exo_rmsnorm = (_i, [_p, _p, _p, _p, _p, _i, _i, _f, _i, _p])
     exo_swiglu = (_i, [_p, _p, _i, _i, _i, _p])
+    exo_moe_experts_gemv_fp8 = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p])
     exo_gated_delta = (_i, [_p, _i, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p])
     exo_sigmoid_gate = (_i, [_p, _p, _i, _p, _i, _i, _i, _p])
     exo_scaled_add = (_i, [_p, _p, _p, _p, _i, _i, _i, _p])
@@ -748,6 +749,7 @@ def mla_paged_attention(q_full, ckv, block_tables, seq_lens, cu_q, scale, kv_lor
 
 MOE_GEMV_MAX_TOKENS = 4    # up to this many tokens the experts run as grouped GEMVs (no sort, two launches)
 use_moe_kernels = os.environ.get("EXO_DISABLE_MOE_KERNELS") != "1"
+use_moe_gemv_fp8 = os.environ.get("EXO_DISABLE_MOE_GEMV_FP8") != "1"    # off: small batches of fp8 experts take the grouped GEMM
 
 
 def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling):
@@ -787,6 +789,17 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_t
         hs = torch.empty(P, F, dtype=x.dtype, device=x.device)
         _chk(lib.exo_moe_experts_gemv(_ptr(x), _ptr(w_gate_up), _ptr(w_down), _ptr(weights), _ptr(ids), _ptr(out), _ptr(hs),
                                       T, k, H, F, E, expert_offset, _st()), "moe_experts_gemv")
+        _count(2)
+        return out
+    if (fp8 and use_moe_gemv_fp8 and T <= MOE_GEMV_MAX_TOKENS and -(-H // 64) * 128 <= 200 * 1024
+            and k * -(-F // 64) * 128 <= 200 * 1024):
+        # a handful of tokens: stream the chosen experts' fp8 tiles on CUDA cores over all SMs (two launches) instead of
+        # the grouped tensor-core GEMM, which keeps one CTA per 128 features of a pair busy and the rest of the GPU idle
+        hs = torch.empty(P, F, dtype=x.dtype, device=x.device)
+        kind = 1 if w_gate_up.kind == "mxfp8" else 2
+        _chk(lib.exo_moe_experts_gemv_fp8(_ptr(x), _ptr(w_gate_up.to_tiled().tiles), _ptr(w_down.to_tiled().tiles), _ptr(weights),
+                                          _ptr(ids), _ptr(out), _ptr(hs), T, k, H, F, E, expert_offset, kind, _st()),
+             "moe_experts_gemv_fp8")
         _count(2)
         return out
     ensure_gemm_init(x.device)

@@ -219,7 +219,7 @@ def main() -> None:
     if "moe" in only:
         # one rank's share of a Qwen3-235B-A22B layer under EP8: 16 local experts of 128, top-8, H 4096, F 1536
         E_all, E, k, H, F = 128, 16, 8, 4096, 1536
-        for T in (1, 32, 256, 4096):
+        for T in (1, 4, 32, 256, 4096):
             x = rnd(T, H)
             logits = torch.randn(T, E_all, device="cuda", generator=g)
             w, ids = K.moe_route(logits, k, "softmax", True, None, 1, 1, 1.0)
@@ -233,17 +233,38 @@ def main() -> None:
             fl = 2.0 * pairs * 3 * F * H / 1e12
             print(f"moe-experts T={T} ({pairs} local pairs, {active}/{E} experts): {ms * 1e3:8.1f} us  "
                   f"{gb / ms * 1e3:7.0f} GB/s ({gb / ms * 1e3 / hbm:4.2f})  {fl / ms * 1e3:7.1f} TFLOP/s ({fl / ms * 1e3 / tf:4.2f}) of {basis}")
-            if T >= 32:     # the same experts as block-scaled fp8 (the grouped kernel serves every token count)
+            if True:        # the same experts as block-scaled fp8
                 from ..ops import quant
                 exq = [(quant.quantize(a, "mxfp8"), quant.quantize(b, "mxfp8")) for a, b in ex]
-                ms = timeit_rot([(lambda a=a, b=b: K.moe_experts(x, a, b, w, ids, 0, E_all)) for a, b in exq])
                 gbq = gb / 2 * (1 + 1 / 32)
-                print(f"moe-experts-fp8 T={T}: {ms * 1e3:8.1f} us  {gbq / ms * 1e3:7.0f} GB/s ({gbq / ms * 1e3 / hbm:4.2f})  "
-                      f"{fl / ms * 1e3:7.1f} TFLOP/s ({fl / ms * 1e3 / tf:4.2f}) of {basis}")
+                for gemv in ((True, False) if T <= K.MOE_GEMV_MAX_TOKENS else (False,)):
+                    K.use_moe_gemv_fp8 = gemv
+                    ms = timeit_rot([(lambda a=a, b=b: K.moe_experts(x, a, b, w, ids, 0, E_all)) for a, b in exq])
+                    print(f"moe-experts-fp8 T={T} ({'streaming GEMV' if gemv else 'grouped GEMM'}): {ms * 1e3:8.1f} us  "
+                          f"{gbq / ms * 1e3:7.0f} GB/s ({gbq / ms * 1e3 / hbm:4.2f})  "
+                          f"{fl / ms * 1e3:7.1f} TFLOP/s ({fl / ms * 1e3 / tf:4.2f}) of {basis}")
+                K.use_moe_gemv_fp8 = True
                 del exq
             ms = timeit_rot([(lambda: K.moe_route(logits, k, "softmax", True, None, 1, 1, 1.0)) for _ in range(4)])
             print(f"moe-route T={T} E={E_all} k={k}: {ms * 1e3:8.1f} us")
         K.gemm_check()
+    if "moegemv" in only:
+        # decode-sized batches of block-scaled fp8 experts with every chosen expert local (the streaming GEMV pair alone):
+        # a Qwen3-235B rank (H 4096, F 1536) and a DeepSeek-V3 rank (H 7168, F 2048), one token, eight experts
+        from ..ops import quant
+        for name, E, k, H, F, kind in (("qwen3-235b", 16, 8, 4096, 1536, "mxfp8"), ("deepseek-v3", 32, 8, 7168, 2048, "dsfp8")):
+            x = rnd(1, H)
+            ids = torch.randperm(E, device="cuda")[:k].to(torch.int32).view(1, k)
+            w = torch.full((1, k), 1.0 / k, device="cuda")
+            exq = [(quant.quantize(rnd(E, 2 * F, H), kind), quant.quantize(rnd(E, H, F), kind)) for _ in range(2)]
+            gbq = k * 3 * F * H * (1 + 1 / 32) / 1e9
+            for gemv in (True, False):
+                K.use_moe_gemv_fp8 = gemv
+                ms = timeit_rot([(lambda a=a, b=b: K.moe_experts(x, a, b, w, ids, 0, E)) for a, b in exq])
+                print(f"moe-experts-fp8 {name} T=1, {k} local pairs ({'streaming GEMV' if gemv else 'grouped GEMM'}): {ms * 1e3:8.1f} us  "
+                      f"{gbq / ms * 1e3:7.0f} GB/s ({gbq / ms * 1e3 / hbm:4.2f} of {basis} HBM)")
+            K.use_moe_gemv_fp8 = True
+            del exq
     if "attn" in only:
         Hq, Hkv, D, bs = 32, 8, 128, 16
         for B, ctx in ((1, 2048), (1, 8192), (32, 2048), (64, 4096)):

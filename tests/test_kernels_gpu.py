@@ -367,7 +367,11 @@ def test_gemm_fp8_weights(K, kind, M, N, K_):
 
 
 @pytest.mark.parametrize("kind", ["mxfp8", "dsfp8"])
-@pytest.mark.parametrize("T,E,k,H,F,offset,E_all", [(2, 8, 2, 256, 128, 0, 8), (300, 16, 8, 512, 384, 32, 64), (2500, 4, 2, 256, 256, 0, 4)])
+@pytest.mark.parametrize("T,E,k,H,F,offset,E_all", [
+    (2, 8, 2, 256, 128, 0, 8), (300, 16, 8, 512, 384, 32, 64), (2500, 4, 2, 256, 256, 0, 4),
+    # a handful of tokens take the streaming GEMV pair: an expert-parallel shard (most pairs live elsewhere), reduction
+    # lengths that are not a multiple of the 16-tile unroll, every expert local
+    (1, 8, 8, 7168, 2048, 8, 64), (4, 8, 8, 7168, 2048, 8, 64), (3, 16, 4, 2048, 512, 0, 16), (4, 4, 2, 1088, 384, 0, 4)])
 def test_moe_experts_fp8(K, kind, T, E, k, H, F, offset, E_all):
     from exo_b200.ops import quant
     g = torch.Generator(device="cuda").manual_seed(4)
