@@ -190,7 +190,11 @@ def main() -> None:
         comm, comm_name = make_comm("nccl")
 
     note(f"comm={comm_name}; building weights")
-    weights = fast_random_weights(cfg, spec, dev, seed=0, router_std=1.0 if cfg.n_experts else None)
+    # router weights: N(0, 1) for softmax routers (widely spread logits, no two alike); sigmoid routers get N(0, 1/H) so
+    # that the LOGITS are N(0, 1): larger ones saturate the sigmoid, every score ties at 1.0 and the top-k then picks
+    # the lowest expert ids for every token, i.e. all of one rank's experts and none of the others'
+    router_std = None if not cfg.n_experts else (cfg.hidden ** -0.5 if cfg.router == "sigmoid" else 1.0)
+    weights = fast_random_weights(cfg, spec, dev, seed=0, router_std=router_std)
     torch.cuda.synchronize()
     note("weights ready")
     max_b = max(args.batch, 1 if args.no_also else args.also_batch)

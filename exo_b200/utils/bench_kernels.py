@@ -254,15 +254,17 @@ def main() -> None:
         from ..ops import quant
         for name, E, k, H, F, kind in (("qwen3-235b", 16, 8, 4096, 1536, "mxfp8"), ("deepseek-v3", 32, 8, 7168, 2048, "dsfp8")):
             x = rnd(1, H)
-            ids = torch.randperm(E, device="cuda")[:k].to(torch.int32).view(1, k)
             w = torch.full((1, k), 1.0 / k, device="cuda")
-            exq = [(quant.quantize(rnd(E, 2 * F, H), kind), quant.quantize(rnd(E, H, F), kind)) for _ in range(2)]
-            gbq = k * 3 * F * H * (1 + 1 / 32) / 1e9
-            for gemv in (True, False):
-                K.use_moe_gemv_fp8 = gemv
-                ms = timeit_rot([(lambda a=a, b=b: K.moe_experts(x, a, b, w, ids, 0, E)) for a, b in exq])
-                print(f"moe-experts-fp8 {name} T=1, {k} local pairs ({'streaming GEMV' if gemv else 'grouped GEMM'}): {ms * 1e3:8.1f} us  "
-                      f"{gbq / ms * 1e3:7.0f} GB/s ({gbq / ms * 1e3 / hbm:4.2f} of {basis} HBM)")
+            exq = [(quant.quantize(rnd(E, 2 * F, H), kind), quant.quantize(rnd(E, H, F), kind)) for _ in range(4)]
+            for n_local in (k, 2, 1):       # the rest of the token's experts live on other ranks
+                ids = torch.randperm(E, device="cuda")[:k].to(torch.int32).view(1, k)
+                ids[0, n_local:] += 10000
+                gbq = n_local * 3 * F * H * (1 + 1 / 32) / 1e9
+                for gemv in (True, False):
+                    K.use_moe_gemv_fp8 = gemv
+                    ms = timeit_rot([(lambda a=a, b=b: K.moe_experts(x, a, b, w, ids, 0, E)) for a, b in exq], reps=16)
+                    print(f"moe-experts-fp8 {name} T=1, {n_local} of {k} pairs local ({'streaming GEMV' if gemv else 'grouped GEMM'}): "
+                          f"{ms * 1e3:8.1f} us  {gbq / ms * 1e3:7.0f} GB/s ({gbq / ms * 1e3 / hbm:4.2f} of {basis} HBM)")
             K.use_moe_gemv_fp8 = True
             del exq
     if "attn" in only:
