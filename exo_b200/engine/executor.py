@@ -17,7 +17,7 @@ import torch
 
 from .. import ops
 from ..models.config import ModelConfig
-from ..models.transformer import Decoder, KVPool, StepInputs
+from ..models.transformer import Decoder, KVPool, StepInputs, make_decoder, make_kv_pool
 from ..models.weights import ModelWeights, ShardSpec
 from .plan import HEADER, PlanLayout, StepPlan, bucket, FLAG_ALL_GREEDY, FLAG_EAGER, FLAG_NO_SAMPLE
 
@@ -33,8 +33,8 @@ class Executor:
         self.pipe = pipe if (pipe is not None and pipe.pp_size > 1) else None
         self.spec = spec or ShardSpec()
         self.device = torch.device(device)
-        self.model = Decoder(cfg, weights, self.spec, comm)
-        self.kv = KVPool(cfg, self.spec, n_blocks, block_size, self.device, max_seqs=max_seqs)
+        self.model = make_decoder(cfg, weights, self.spec, comm)
+        self.kv = make_kv_pool(cfg, self.spec, n_blocks, block_size, self.device, max_seqs=max_seqs)
         self.block_size, self.max_blocks = block_size, max_blocks_per_seq
         self.max_T, self.max_B = max_tokens_per_step, max_seqs
         words = PlanLayout(max(self.max_T, self.max_B), self.max_B, self.max_blocks).words

@@ -19,7 +19,7 @@ from typing import Any
 @dataclass
 class RopeConfig:
     theta: float = 10000.0
-    kind: str = "default"  # default | linear | llama3 | yarn
+    kind: str = "default"  # default | linear | llama3 | yarn | proportional (zero frequencies beyond the rotary share)
     factor: float = 1.0
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
@@ -91,6 +91,21 @@ class ModelConfig:
     moe_every: int = 1          # layer i is sparse when (i + 1) % moe_every == 0 ...
     mlp_only_layers: tuple[int, ...] = ()  # ... and i is not listed here
     weight_prefix: str = "model."  # "model.language_model." in checkpoints that wrap the text model
+    # Gemma-4: "sliding" layers (local window, head_dim) alternate with "full" layers (global_head_dim, own KV head count,
+    # optionally v = k), norms before AND after attention / MLP, GeGLU, optional per-layer input embeddings, optional
+    # expert block beside the dense MLP, the last layers optionally re-using the KV of earlier ones
+    global_head_dim: int = 0
+    global_kv_heads: int = 0
+    k_eq_v: bool = False
+    kv_shared_layers: int = 0
+    ple_dim: int = 0            # width of the per-layer input embeddings (0: none)
+    ple_vocab: int = 0
+    moe_beside_mlp: bool = False
+    double_wide_mlp: bool = False
+    logit_softcap: float = 0.0
+    act: str = "silu"           # silu | gelu_tanh
+    embed_scale: float = 1.0
+    rope_global: RopeConfig | None = None   # RoPE of the "full" layers when it differs from `rope`
 
     # -------- derived --------
     @property
@@ -108,6 +123,27 @@ class ModelConfig:
     def layer_is_moe(self, i: int) -> bool:
         return (self.is_moe and i >= self.first_dense_layers and (i + 1) % self.moe_every == 0
                 and i not in self.mlp_only_layers)
+
+    def layer_is_sliding(self, i: int) -> bool:
+        return bool(self.layer_types) and self.layer_types[i] == "sliding"
+
+    def attn_dims(self, i: int) -> tuple[int, int]:
+        """``(KV heads, head_dim)`` of layer ``i`` (Gemma-4's full-attention layers have their own)."""
+        if self.family == "gemma4" and not self.layer_is_sliding(i):
+            kvh = self.global_kv_heads if (self.k_eq_v and self.global_kv_heads) else self.n_kv_heads
+            return kvh, self.global_head_dim or self.head_dim
+        return self.n_kv_heads, self.head_dim
+
+    def kv_source_layer(self, i: int) -> int:
+        """The layer whose KV cache layer ``i`` reads: itself, or (Gemma-4, last `kv_shared_layers` layers) the last
+        layer of the same type before the sharing starts."""
+        first = self.n_layers - self.kv_shared_layers
+        if not self.kv_shared_layers or i < first:
+            return i
+        for j in range(first - 1, -1, -1):
+            if self.layer_types[j] == self.layer_types[i]:
+                return j
+        return i
 
     def layer_is_linear(self, i: int) -> bool:
         return bool(self.layer_types) and self.layer_types[i] == "linear"
@@ -216,6 +252,7 @@ class ModelConfig:
                   "glm4_moe": "glm4_moe", "mixtral": "mixtral", "minimax": "minimax", "minimax_m2": "minimax",
                   "qwen3_next": "qwen3_next", "qwen3_5": "qwen3_next", "qwen3_5_text": "qwen3_next",
                   "qwen3_5_moe": "qwen3_next", "qwen3_5_moe_text": "qwen3_next",
+                  "gemma4": "gemma4", "gemma4_text": "gemma4",
                   "gpt_oss": "gpt_oss"}.get(mt, "llama")
         mc = ModelConfig(
             name=name, family=family,
@@ -265,6 +302,42 @@ class ModelConfig:
                 mc.moe_every = int(g("decoder_sparse_step", default=1))
                 mc.mlp_only_layers = tuple(g("mlp_only_layers", default=()) or ())
             if mt != "qwen3_next":
+                mc.weight_prefix = "model.language_model."
+        if family == "gemma4":
+            n_l = mc.n_layers
+            types = g("layer_types", default=None) or ["sliding_attention" if (i + 1) % 6 else "full_attention" for i in range(n_l)]
+            types = list(types)
+            types[-1] = "full_attention"
+            mc.layer_types = tuple("sliding" if t == "sliding_attention" else "full" for t in types)
+            mc.sliding_window = int(g("sliding_window", default=512))
+            mc.head_dim = g("head_dim", default=256)
+            mc.global_head_dim = g("global_head_dim", default=512) or mc.head_dim
+            mc.k_eq_v = bool(g("attention_k_eq_v", default=False))
+            mc.global_kv_heads = g("num_global_key_value_heads", default=0) or 0
+            mc.kv_shared_layers = g("num_kv_shared_layers", default=0) or 0
+            mc.ple_dim = g("hidden_size_per_layer_input", default=256) or 0
+            mc.ple_vocab = g("vocab_size_per_layer_input", default=mc.vocab) or mc.vocab
+            mc.moe_beside_mlp = bool(g("enable_moe_block", default=False))
+            mc.double_wide_mlp = bool(g("use_double_wide_mlp", default=False))
+            mc.logit_softcap = float(g("final_logit_softcapping", default=0.0) or 0.0)
+            mc.act = "gelu_tanh"
+            mc.embed_scale = float(mc.hidden) ** 0.5
+            mc.qk_norm = True
+            mc.tie_embeddings = bool(g("tie_word_embeddings", default=True))
+            rp = g("rope_parameters", default=None) or {}
+            loc = rp.get("sliding_attention") or {"rope_type": "default", "rope_theta": 10000.0}
+            glo = rp.get("full_attention") or {"rope_type": "proportional", "partial_rotary_factor": 0.25, "rope_theta": 1000000.0}
+            mc.rope = RopeConfig(theta=float(loc.get("rope_theta", 10000.0)))
+            mc.rope_global = RopeConfig(theta=float(glo.get("rope_theta", 1000000.0)),
+                                        kind="proportional" if glo.get("rope_type") == "proportional" else "default",
+                                        partial_rotary_factor=float(glo.get("partial_rotary_factor", 1.0)))
+            if mc.moe_beside_mlp:
+                mc.n_experts = g("num_experts")
+                mc.n_experts_per_tok = g("top_k_experts")
+                mc.moe_ffn = g("moe_intermediate_size")
+                mc.router = "softmax"
+                mc.norm_topk_prob = True
+            if mt != "gemma4_text" or "language_model" in str(cfg.get("architectures", "")):
                 mc.weight_prefix = "model.language_model."
         if family == "glm4_moe":
             # GLM-4.5 / 4.6: grouped-query attention with half-rotary RoPE and q/k/v biases, DeepSeek-style experts
@@ -408,6 +481,14 @@ def preset(name: str) -> ModelConfig:
                            lin_k_heads=16, lin_v_heads=32, lin_k_dim=128, lin_v_dim=128, lin_conv=4, attn_gate=True,
                            norm_one_plus=True, n_experts=512, n_experts_per_tok=10, moe_ffn=512, router="softmax",
                            shared_expert_ffn=512, shared_expert_gate=True, quant="mxfp8")
+    if n in ("tiny-gemma4",):      # sliding / full layers with their own head sizes, v = k on full layers, per-layer inputs, shared KV
+        return ModelConfig(name="tiny-gemma4", family="gemma4", n_layers=6, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                           ffn=512, vocab=1024, rms_eps=1e-6, qk_norm=True, tie_embeddings=True,
+                           layer_types=("sliding", "full", "sliding", "full", "sliding", "full"), sliding_window=32,
+                           global_head_dim=128, global_kv_heads=1, k_eq_v=True, kv_shared_layers=2, ple_dim=32, ple_vocab=1024,
+                           logit_softcap=30.0, act="gelu_tanh", embed_scale=16.0, rope=RopeConfig(theta=10000.0),
+                           rope_global=RopeConfig(theta=1000000.0, kind="proportional", partial_rotary_factor=0.25),
+                           weight_prefix="model.", dtype="fp32")
     if n in ("tiny-mla",):
         return ModelConfig(name="tiny-mla", family="deepseek_v3", n_layers=3, hidden=256, n_heads=4, n_kv_heads=4,
                            head_dim=48, ffn=512, vocab=1024, mla=True, q_lora_rank=64, kv_lora_rank=32,
@@ -418,4 +499,4 @@ def preset(name: str) -> ModelConfig:
 
 
 PRESETS = ("tiny-llama", "llama-3.1-8b", "llama-3.1-70b", "qwen3-235b-a22b", "deepseek-v3", "tiny-moe", "tiny-mla",
-           "tiny-qwen3", "tiny-qwen2", "tiny-qwen3-next", "qwen3-next-80b-a3b", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-yarn")
+           "tiny-qwen3", "tiny-qwen2", "tiny-gemma4", "tiny-qwen3-next", "qwen3-next-80b-a3b", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-yarn")

@@ -109,6 +109,9 @@ class KVPool:
 
     @staticmethod
     def bytes_per_block(cfg: ModelConfig, spec: ShardSpec, block_size: int = 16) -> int:
+        if cfg.family == "gemma4":
+            from .gemma4 import Gemma4KV
+            return Gemma4KV.bytes_per_block(cfg, spec, block_size)
         el = 2 if cfg.dtype == "bf16" else 4
         n_layers = sum(1 for i in spec.layers(cfg) if not cfg.layer_is_linear(i))
         if cfg.mla:
@@ -308,3 +311,19 @@ class Decoder:
         """Full-vocabulary logits ``[B', V]`` (vocab shards gathered across the TP group)."""
         out = self.forward(inp, kv)
         return self.comm.gather_vocab(out)[:, :self.cfg.vocab]
+
+
+def make_decoder(cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None = None, comm=None) -> Decoder:
+    """The forward implementation of the model's family."""
+    if cfg.family == "gemma4":
+        from .gemma4 import Gemma4Decoder
+        return Gemma4Decoder(cfg, weights, spec, comm)
+    return Decoder(cfg, weights, spec, comm)
+
+
+def make_kv_pool(cfg: ModelConfig, spec: ShardSpec, n_blocks: int, block_size: int = 16, device="cpu", dtype=None,
+                 max_seqs: int = 64) -> KVPool:
+    if cfg.family == "gemma4":
+        from .gemma4 import Gemma4KV
+        return Gemma4KV(cfg, spec, n_blocks, block_size, device, dtype, max_seqs)
+    return KVPool(cfg, spec, n_blocks, block_size, device, dtype, max_seqs)

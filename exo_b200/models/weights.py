@@ -410,6 +410,9 @@ def quantize_layer(cfg: ModelConfig, lw: "LayerWeights") -> "LayerWeights":
 def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: str | torch.device = "cpu",
                   progress: Callable[[int, int], None] | None = None) -> ModelWeights:
     """Materialise this rank's shard from ``src`` (full tensors are sliced, then dropped)."""
+    if cfg.family == "gemma4":
+        from .gemma4 import build_gemma4_weights
+        return build_gemma4_weights(cfg, spec, src, device, progress)
     dt = _DTYPES[cfg.dtype]
     dev = torch.device(device)
     r, n = spec.tp_rank, spec.tp_size

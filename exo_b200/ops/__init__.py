@@ -57,19 +57,27 @@ def swiglu(gate_up):
 
 
 def qk_rope_append(qkv, positions, inv_freq, mscale, n_q, n_kv, head_dim, kcache, vcache, slots,
-                   q_norm=None, k_norm=None, eps=1e-6):
+                   q_norm=None, k_norm=None, eps=1e-6, v_unit_norm=False):
     """Split fused ``qkv [T,(n_q+2n_kv)*D]``, apply optional per-head RMSNorm and RoPE to q/k,
-    append k/v to the paged cache at ``slots``.  Returns ``q [T, n_q, D]``."""
+    append k/v to the paged cache at ``slots``.  Returns ``q [T, n_q, D]``.  ``v_unit_norm``: v heads are RMS-normalised
+    (no weight) before they are stored (Gemma-4).  With ``n_kv == 0`` only q is processed (a layer that reads another
+    layer's cache)."""
     if qkv.is_cuda:
         return cuda_ops().qk_rope_append(qkv, positions, inv_freq, mscale, n_q, n_kv, head_dim, kcache, vcache,
-                                         slots, q_norm, k_norm, eps)
+                                         slots, q_norm, k_norm, eps, v_unit_norm)
     T = qkv.shape[0]
     q, k, v = qkv.split((n_q * head_dim, n_kv * head_dim, n_kv * head_dim), dim=-1)
     q, k, v = q.reshape(T, n_q, head_dim), k.reshape(T, n_kv, head_dim), v.reshape(T, n_kv, head_dim)
     if q_norm is not None:
-        q, k = ref.head_rmsnorm(q, q_norm, eps), ref.head_rmsnorm(k, k_norm, eps)
-    q, k = ref.rope(q, positions, inv_freq, mscale), ref.rope(k, positions, inv_freq, mscale)
-    ref.kv_append(k, v, kcache, vcache, slots)
+        q = ref.head_rmsnorm(q, q_norm, eps)
+        if n_kv:
+            k = ref.head_rmsnorm(k, k_norm, eps)
+    q = ref.rope(q, positions, inv_freq, mscale)
+    if n_kv:
+        k = ref.rope(k, positions, inv_freq, mscale)
+        if v_unit_norm:
+            v = ref.head_rmsnorm(v, torch.ones(head_dim, device=v.device), eps)
+        ref.kv_append(k, v, kcache, vcache, slots)
     return q
 
 
@@ -162,3 +170,10 @@ def scaled_add(y, x, logit):
     if x.is_cuda:
         return cuda_ops().scaled_add(y, x, logit)
     return (y.float() + x.float() * torch.sigmoid(logit.float())).to(y.dtype)
+
+
+def geglu(gate_up):
+    """``gelu_tanh(gate_up[:, :F]) * gate_up[:, F:]``."""
+    if gate_up.is_cuda:
+        return cuda_ops().geglu(gate_up)
+    return ref.geglu(gate_up)

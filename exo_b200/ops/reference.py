@@ -37,6 +37,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return y.to(x.dtype)
 
 
+def geglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``gelu_tanh(gate) * up`` over ``[.., 2F]`` (gate columns first)."""
+    F_ = gate_up.shape[-1] // 2
+    g, u = gate_up[..., :F_].float(), gate_up[..., F_:].float()
+    return (torch.nn.functional.gelu(g, approximate="tanh") * u).to(gate_up.dtype)
+
+
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     """``silu(gate) * up`` for ``gate_up = [gate | up]`` concatenated on the last dim."""
     g, u = gate_up.float().chunk(2, dim=-1)
@@ -50,6 +57,13 @@ def rope_inv_freq(head_dim: int, rope) -> tuple[torch.Tensor, float]:
     blending with a linear ramp, the convention the reference patches in at
     ``src/exo/worker/engines/mlx/patches/standard_yarn_rope.py:10-67``).
     """
+    if rope.kind == "proportional":
+        # rotation over the WHOLE head (pairs i, i + head_dim/2) with the frequencies of the first
+        # partial_rotary_factor * head_dim / 2 pairs taken against head_dim and the others zero (Gemma-4 full layers)
+        n = int(rope.partial_rotary_factor * head_dim // 2)
+        inv = 1.0 / (rope.theta ** (torch.arange(0, 2 * n, 2, dtype=torch.float64) / head_dim))
+        inv = torch.cat((inv / rope.factor, torch.zeros(head_dim // 2 - n, dtype=torch.float64)))
+        return inv.float(), 1.0
     rot = int(head_dim * rope.partial_rotary_factor)
     rot -= rot % 2
     idx = torch.arange(0, rot, 2, dtype=torch.float64)
