@@ -231,9 +231,9 @@ class Gemma4Decoder(Decoder):
         wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, "softmax", True, None, 1, 1, 1.0)
         x2 = ops.rmsnorm(h, lw.pre_ffn_norm_2, cfg.rms_eps)[0]
         elo, _ = expert_range(cfg, self.spec)
-        if x2.is_cuda:
-            raise NotImplementedError("Gemma-4 expert block (GeGLU experts) has no CUDA kernels yet")
-        y = gelu_experts(x2, lw.e_gate_up, lw.e_down, wts, ids, elo)
+        # GeGLU experts: the grouped expert kernels are SwiGLU; this block runs as PyTorch ops on either device (with host
+        # reads of the routing, so a model with it is not captured in CUDA graphs)
+        y = gelu_experts(x2, lw.e_gate_up, lw.e_down, wts, ids.long(), elo)
         return resolve(self.comm.row_sum(y))
 
     # ------------------------------------------------------------------ forward

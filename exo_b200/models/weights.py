@@ -116,7 +116,7 @@ class RandomSource(TensorSource):
         return g
 
     def get(self, name: str, shape: tuple[int, ...]) -> torch.Tensor:
-        if "norm" in name and name.endswith("weight"):
+        if ("norm" in name and name.endswith("weight")) or name.endswith("layer_scalar"):
             return torch.ones(shape, dtype=self.dtype, device=self.device)
         if name.endswith("e_score_correction_bias"):
             return torch.zeros(shape, dtype=torch.float32, device=self.device)

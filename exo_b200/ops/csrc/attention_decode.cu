@@ -2,8 +2,8 @@
 //
 // Grid (n_splits, Hkv * (g / GT), B).  A CTA streams its slice of one KV head once and scores
 // it against GT query heads that share that KV head (GQA), so K/V bytes are read once per group.
-// Inside a warp, LW lanes cooperate on one key (8 lanes with D/8 dims each; 16 lanes at D = 256, which keeps the
-// per-lane state at 16 dims), 32/LW lane-groups x 2 keys are in
+// Inside a warp, LW lanes cooperate on one key (8 lanes with D/8 dims each; 16 lanes at D = 256 and 32 at D = 512, which keeps
+// the per-lane state at 16 dims), 32/LW lane-groups x 2 keys are in
 // flight per iteration; every (lane-group, head) keeps its own online-softmax state, merged at the
 // end through shuffles and shared memory.  Each split publishes (m, l, o) partials to a workspace
 // and takes a ticket; the CTA that draws the last ticket of its (sequence, head group) merges the
@@ -17,7 +17,7 @@ paged_decode_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
                     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
                     T* __restrict__ out, float scale, int Hq, int Hkv, int max_blocks, int block_size, int window,
                     const float* __restrict__ sinks) {
-  constexpr int LW = D > 128 ? 16 : 8;  // lanes per key
+  constexpr int LW = D > 256 ? 32 : D > 128 ? 16 : 8;  // lanes per key (16 dims per lane from 128 up)
   constexpr int NLG = 32 / LW;          // lane groups (keys side by side) per warp
   constexpr int DPL = D / LW;           // dims per lane
   constexpr int U = 2;                  // keys per lane-group per iteration
@@ -238,6 +238,7 @@ EXO_API int exo_paged_decode(const void* q, const void* kcache, const void* vcac
   float* part_ml = workspace + (size_t)B * Hq * n_splits * D;
   int GT = (g % 4 == 0) ? 4 : (g % 2 == 0 ? 2 : 1);
   dim3 grid(n_splits, Hkv * (g / GT), B);
+  if (D == 512 && (size_t)4 * GT * D * sizeof(float) > 40 * 1024) return -2;
   cudaError_t e = cudaSuccess;
 #define LAUNCH(TT, DD, GG)                                                                                        \
   e = launch_pdl(paged_decode_kernel<TT, DD, GG>, grid, dim3(128), 0, st, (const TT*)q, (const TT*)kcache,         \
@@ -251,11 +252,13 @@ EXO_API int exo_paged_decode(const void* q, const void* kcache, const void* vcac
     if (D == 128) { BY_G(__nv_bfloat16, 128); }
     else if (D == 64) { BY_G(__nv_bfloat16, 64); }
     else if (D == 256) { BY_G(__nv_bfloat16, 256); }
+    else if (D == 512) { BY_G(__nv_bfloat16, 512); }
     else return -2;
   } else {
     if (D == 128) { BY_G(float, 128); }
     else if (D == 64) { BY_G(float, 64); }
     else if (D == 256) { BY_G(float, 256); }
+    else if (D == 512) { BY_G(float, 512); }
     else return -2;
   }
 #undef BY_G

@@ -92,6 +92,7 @@ EXO_API int exo_paged_ragged(const void* q, const void* kcache, const void* vcac
   int g = Hq / Hkv;
   if (g * Hkv != Hq) return -2;
   int GT = (g % 4 == 0) ? 4 : (g % 2 == 0 ? 2 : 1);
+  if (D == 512 && GT > 2) GT = 2;      // 16 values per lane and head: two heads' state is what the registers hold
   long warps = (long)T_ * Hkv * (g / GT);
   int blocks = (int)((warps + 3) / 4);
 #define LAUNCH(TT, DD, GG)                                                                                          \
@@ -106,11 +107,13 @@ EXO_API int exo_paged_ragged(const void* q, const void* kcache, const void* vcac
     if (D == 128) { BY_G(__nv_bfloat16, 128); }
     else if (D == 64) { BY_G(__nv_bfloat16, 64); }
     else if (D == 256) { BY_G(__nv_bfloat16, 256); }
+    else if (D == 512) { if (GT == 2) LAUNCH(__nv_bfloat16, 512, 2); else LAUNCH(__nv_bfloat16, 512, 1); }
     else return -2;
   } else {
     if (D == 128) { BY_G(float, 128); }
     else if (D == 64) { BY_G(float, 64); }
     else if (D == 256) { BY_G(float, 256); }
+    else if (D == 512) { if (GT == 2) LAUNCH(float, 512, 2); else LAUNCH(float, 512, 1); }
     else return -2;
   }
 #undef BY_G

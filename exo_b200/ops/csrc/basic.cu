@@ -125,6 +125,32 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, siz
   }
 }
 
+// out[r, c] = gelu_tanh(gu[r, c]) * gu[r, F + c]
+template <typename T>
+__global__ void geglu_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t rows, int F) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t n = rows * (size_t)F;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    size_t r = i / F;
+    int c = (int)(i - r * F);
+    float g = Cvt<T>::to_f(gu[r * 2 * F + c]), u = Cvt<T>::to_f(gu[r * 2 * F + F + c]);
+    float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+    out[i] = Cvt<T>::from_f(0.5f * g * (1.f + t) * u);
+  }
+}
+
+EXO_API int exo_geglu(const void* gu, void* out, int rows, int F, int dtype, cudaStream_t st) {
+  size_t n = (size_t)rows * F;
+  if (n == 0) return 0;
+  int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (dtype == EXO_BF16)
+    geglu_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F);
+  else
+    geglu_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)out, rows, F);
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
 EXO_API int exo_swiglu(const void* gu, void* out, int rows, int F, int dtype, cudaStream_t st) {
   size_t n = (size_t)rows * F;
   if (n == 0) return 0;
@@ -171,7 +197,7 @@ __global__ void qk_rope_append_kernel(const T* __restrict__ qkv, const int* __re
                                       const float* __restrict__ inv_freq, float mscale, int n_q, int n_kv, int rot,
                                       T* __restrict__ q_out, T* __restrict__ kcache, T* __restrict__ vcache,
                                       const int* __restrict__ slots, const T* __restrict__ q_norm,
-                                      const T* __restrict__ k_norm, float eps, int T_) {
+                                      const T* __restrict__ k_norm, float eps, int T_, int v_unit_norm) {
   constexpr int E = D / 32;
   int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   int heads = n_q + 2 * n_kv;
@@ -182,6 +208,15 @@ __global__ void qk_rope_append_kernel(const T* __restrict__ qkv, const int* __re
 #pragma unroll
   for (int j = 0; j < E; j++) v[j] = Cvt<T>::to_f(src[j * 32 + lane]);
   bool is_q = hd < n_q, is_k = !is_q && hd < n_q + n_kv;
+  if (!is_q && !is_k && v_unit_norm) {      // v heads normalised without a weight (Gemma-4)
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < E; j++) ss += v[j] * v[j];
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / D + eps);
+#pragma unroll
+    for (int j = 0; j < E; j++) v[j] *= rstd;
+  }
   if (is_q || is_k) {
     const T* nw = is_q ? q_norm : k_norm;
     if (nw) {
@@ -225,7 +260,7 @@ __global__ void qk_rope_append_kernel(const T* __restrict__ qkv, const int* __re
 EXO_API int exo_qk_rope_append(const void* qkv, const int* positions, const float* inv_freq, float mscale, int n_q,
                                int n_kv, int head_dim, int rot, void* q_out, void* kcache, void* vcache,
                                const int* slots, const void* q_norm, const void* k_norm, float eps, int T_, int dtype,
-                               cudaStream_t st) {
+                               int v_unit_norm, cudaStream_t st) {
   if (T_ == 0) return 0;
   if (rot % 64 != 0 || rot > head_dim) return -2;
   long warps = (long)T_ * (n_q + 2 * n_kv);
@@ -233,16 +268,18 @@ EXO_API int exo_qk_rope_append(const void* qkv, const int* positions, const floa
 #define LAUNCH(TT, DD)                                                                                              \
   qk_rope_append_kernel<TT, DD><<<blocks, 256, 0, st>>>((const TT*)qkv, positions, inv_freq, mscale, n_q, n_kv, rot, \
                                                         (TT*)q_out, (TT*)kcache, (TT*)vcache, slots,                 \
-                                                        (const TT*)q_norm, (const TT*)k_norm, eps, T_)
+                                                        (const TT*)q_norm, (const TT*)k_norm, eps, T_, v_unit_norm)
   if (dtype == EXO_BF16) {
     if (head_dim == 128) LAUNCH(__nv_bfloat16, 128);
     else if (head_dim == 64) LAUNCH(__nv_bfloat16, 64);
     else if (head_dim == 256) LAUNCH(__nv_bfloat16, 256);
+    else if (head_dim == 512) LAUNCH(__nv_bfloat16, 512);
     else return -2;
   } else {
     if (head_dim == 128) LAUNCH(float, 128);
     else if (head_dim == 64) LAUNCH(float, 64);
     else if (head_dim == 256) LAUNCH(float, 256);
+    else if (head_dim == 512) LAUNCH(float, 512);
     else return -2;
   }
 #undef LAUNCH

@@ -50,7 +50,8 @@ class _Sig:
     exo_sigmoid_gate = (_i, [_p, _p, _i, _p, _i, _i, _i, _p])
     exo_scaled_add = (_i, [_p, _p, _p, _p, _i, _i, _i, _p])
     exo_embedding = (_i, [_p, _p, _p, _i, _i, _i, _i, _p])
-    exo_qk_rope_append = (_i, [_p, _p, _p, _f, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _f, _i, _i, _p])
+    exo_qk_rope_append = (_i, [_p, _p, _p, _f, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _p])
+    exo_geglu = (_i, [_p, _p, _i, _i, _i, _p])
     exo_argmax_chunks = (_i, [_i, _i])
     exo_argmax = (_i, [_p, _p, _p, _p, _i, _i, _i, _l, _i, _p])
     exo_sample = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _l, _i, _p])
@@ -229,6 +230,15 @@ def scaled_add(y, x, logit):
     rows, n = x.shape
     out = _empty_like(x, "scaled_add out")
     _chk(load().exo_scaled_add(_ptr(y), _ptr(x), _ptr(logit), _ptr(out), rows, n, _dt(x), _st()), "scaled_add")
+    _count()
+    return out
+
+
+def geglu(gate_up):
+    gate_up = gate_up.contiguous()
+    rows, F2 = gate_up.shape
+    out = torch.empty(rows, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    _chk(load().exo_geglu(_ptr(gate_up), _ptr(out), rows, F2 // 2, _dt(gate_up), _st()), "geglu")
     _count()
     return out
 
@@ -448,15 +458,18 @@ def linear(x, w, bias=None, residual=None, norm_w=None, eps=0.0, swiglu_out=Fals
 
 
 def qk_rope_append(qkv, positions, inv_freq, mscale, n_q, n_kv, head_dim, kcache, vcache, slots, q_norm=None,
-                   k_norm=None, eps=1e-6):
+                   k_norm=None, eps=1e-6, v_unit_norm=False):
     qkv = qkv.contiguous()
     T = qkv.shape[0]
-    _check_indices("KV slots", slots, kcache.shape[0] * kcache.shape[1])
+    if qkv.shape[1] != (n_q + 2 * n_kv) * head_dim:
+        raise KernelError(f"qk_rope_append: {qkv.shape[1]} columns for {n_q} + 2 x {n_kv} heads of {head_dim}")
+    if n_kv:
+        _check_indices("KV slots", slots, kcache.shape[0] * kcache.shape[1])
     q = _empty(T, n_q, head_dim, dtype=qkv.dtype, device=qkv.device, what="rope q")
     rot = inv_freq.numel() * 2
     _chk(load().exo_qk_rope_append(_ptr(qkv), _ptr(positions), _ptr(inv_freq), float(mscale), n_q, n_kv, head_dim, rot,
                                    _ptr(q), _ptr(kcache), _ptr(vcache), _ptr(slots), _ptr(q_norm), _ptr(k_norm),
-                                   float(eps), T, _dt(qkv), _st()), "qk_rope_append")
+                                   float(eps), T, _dt(qkv), int(bool(v_unit_norm)), _st()), "qk_rope_append")
     _count()
     return q
 

@@ -61,6 +61,14 @@ CASES = {
                                                                               "partial_rotary_factor": 0.5}}},
                 dict(family="qwen3_next", is_moe=False, lin_split_proj=True, weight_prefix="model.language_model.",
                      layer_types=("linear", "full", "linear"), attn_gate=True)),
+    "gemma4-multimodal": ({"model_type": "gemma4", "text_config": {**BASE, "model_type": "gemma4_text", "num_hidden_layers": 6,
+                                                                    "head_dim": 32, "global_head_dim": 64, "sliding_window": 16,
+                                                                    "hidden_size_per_layer_input": 8, "attention_k_eq_v": True,
+                                                                    "num_global_key_value_heads": 1, "num_kv_shared_layers": 2,
+                                                                    "final_logit_softcapping": 30.0}},
+                          dict(family="gemma4", weight_prefix="model.language_model.", k_eq_v=True, global_kv_heads=1, ple_dim=8,
+                               kv_shared_layers=2, act="gelu_tanh", logit_softcap=30.0, sliding_window=16,
+                               layer_types=("sliding",) * 5 + ("full",))),
     "qwen2": ({"model_type": "qwen2", "tie_word_embeddings": True}, dict(family="llama", attn_bias=True, tie_embeddings=True)),
 }
 

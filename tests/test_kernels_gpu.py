@@ -125,13 +125,57 @@ def _paged_setup(dtype, B, Hq, Hkv, D, lens, qlens, bs=16, seed=0):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (4, 2, 64), (8, 1, 128), (16, 16, 64), (16, 2, 256), (4, 2, 256), (2, 2, 256)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (4, 2, 64), (8, 1, 128), (16, 16, 64), (16, 2, 256), (4, 2, 256), (2, 2, 256),
+                                        (8, 2, 512), (4, 4, 512), (2, 1, 512)])
 def test_paged_decode(K, dtype, Hq, Hkv, D):
     lens = [1, 17, 300, 2049]
     q, kc, vc, bt, sl, cu = _paged_setup(dtype, 4, Hq, Hkv, D, lens, [1] * 4)
     got = K.paged_attention(q, kc, vc, bt, sl, cu, D ** -0.5, max_q_len=1)
     want = ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, cu, D ** -0.5)
     close(got, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 512), (2, 1, 512), (4, 2, 256)])
+def test_ragged_attention_wide_heads(K, dtype, Hq, Hkv, D):
+    """Prompt-shaped queries over 256- and 512-wide heads (the generic kernel: these widths are not on the tensor cores)."""
+    lens, qlens = [70, 33, 5], [40, 33, 1]
+    q, kc, vc, bt, sl, cu = _paged_setup(dtype, 3, Hq, Hkv, D, lens, qlens)
+    got = K.paged_attention(q, kc, vc, bt, sl, cu, 1.0 / 16, max_q_len=max(qlens))
+    want = ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, cu, 1.0 / 16)
+    close(got, want)
+
+
+def test_rope_append_unit_norm_v_and_query_only(K):
+    """The Gemma-4 forms of the fused split/norm/RoPE/append: v normalised without a weight, full-head rotation with
+    zero frequencies, 512-wide heads, and a layer that reads another layer's cache (q only)."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    from exo_b200 import ops
+    from exo_b200.models.config import RopeConfig
+    for dtype, D, hq, hkv in ((torch.float32, 512, 2, 1), (torch.bfloat16, 128, 4, 2)):
+        T = 9
+        inv = ref.rope_inv_freq(D, RopeConfig(theta=1e6, kind="proportional", partial_rotary_factor=0.25))[0].cuda()
+        qkv = torch.randn(T, (hq + 2 * hkv) * D, device="cuda", generator=g).to(dtype)
+        qn, kn = (1 + 0.1 * torch.randn(2, D, device="cuda", generator=g)).to(dtype)
+        pos = torch.arange(3, 3 + T, device="cuda", dtype=torch.int32)
+        slots = (16 + torch.arange(T, device="cuda")).int()
+        kc, vc = (torch.zeros(4, 16, hkv, D, device="cuda", dtype=dtype) for _ in range(2))
+        q = K.qk_rope_append(qkv, pos, inv, 1.0, hq, hkv, D, kc, vc, slots, qn, kn, 1e-6, True)
+        kc2, vc2 = kc.cpu().float() * 0, vc.cpu().float() * 0
+        q2 = ops.qk_rope_append(qkv.cpu().float(), pos.cpu(), inv.cpu(), 1.0, hq, hkv, D, kc2, vc2, slots.cpu(), qn.cpu().float(),
+                                kn.cpu().float(), 1e-6, True)
+        close(q.cpu(), q2)
+        close(kc.cpu(), kc2)
+        close(vc.cpu(), vc2)
+        only_q = K.qk_rope_append(qkv[:, :hq * D], pos, inv, 1.0, hq, 0, D, kc, vc, slots, qn, qn, 1e-6)
+        close(only_q.cpu(), q2)
+
+
+def test_geglu(K):
+    g = torch.Generator(device="cuda").manual_seed(4)
+    for dtype in (torch.float32, torch.bfloat16):
+        x = (2 * torch.randn(33, 2 * 96, device="cuda", generator=g)).to(dtype)
+        close(K.geglu(x), ref.geglu(x.float()))
 
 
 def test_paged_decode_window_and_sinks(K):
