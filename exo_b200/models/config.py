@@ -202,7 +202,8 @@ class ModelConfig:
     @staticmethod
     def from_hf(cfg: dict[str, Any], name: str = "model") -> "ModelConfig":
         """Build from a HuggingFace ``config.json`` dict (text_config is unwrapped)."""
-        if "text_config" in cfg and isinstance(cfg["text_config"], dict):
+        wrapped = "text_config" in cfg and isinstance(cfg["text_config"], dict)      # a multimodal checkpoint around a text model
+        if wrapped:
             inner = dict(cfg["text_config"])
             inner.setdefault("model_type", cfg.get("model_type", "llama"))
             cfg = inner
@@ -337,7 +338,7 @@ class ModelConfig:
                 mc.moe_ffn = g("moe_intermediate_size")
                 mc.router = "softmax"
                 mc.norm_topk_prob = True
-            if mt != "gemma4_text" or "language_model" in str(cfg.get("architectures", "")):
+            if wrapped or mt != "gemma4_text":
                 mc.weight_prefix = "model.language_model."
         if family == "glm4_moe":
             # GLM-4.5 / 4.6: grouped-query attention with half-rotary RoPE and q/k/v biases, DeepSeek-style experts
