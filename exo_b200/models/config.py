@@ -106,6 +106,11 @@ class ModelConfig:
     act: str = "silu"           # silu | gelu_tanh
     embed_scale: float = 1.0
     rope_global: RopeConfig | None = None   # RoPE of the "full" layers when it differs from `rope`
+    # Nemotron-H: every layer is ONE mixer behind one norm: "mamba" (Mamba-2; its state uses the lin_* fields: groups as key
+    # heads, state size as key dim, SSM heads and head dim as value heads and dim), "attention" (no position encoding),
+    # "mlp" or "moe" (non-gated relu^2, sigmoid router, shared expert, optional latent projection around the experts)
+    block_types: tuple[str, ...] = ()
+    moe_latent: int = 0
 
     # -------- derived --------
     @property
@@ -121,6 +126,8 @@ class ModelConfig:
         return self.n_experts > 0
 
     def layer_is_moe(self, i: int) -> bool:
+        if self.block_types:
+            return self.block_types[i] == "moe"
         return (self.is_moe and i >= self.first_dense_layers and (i + 1) % self.moe_every == 0
                 and i not in self.mlp_only_layers)
 
@@ -253,8 +260,15 @@ class ModelConfig:
                   "glm4_moe": "glm4_moe", "mixtral": "mixtral", "minimax": "minimax", "minimax_m2": "minimax",
                   "qwen3_next": "qwen3_next", "qwen3_5": "qwen3_next", "qwen3_5_text": "qwen3_next",
                   "qwen3_5_moe": "qwen3_next", "qwen3_5_moe_text": "qwen3_next",
-                  "gemma4": "gemma4", "gemma4_text": "gemma4",
+                  "gemma4": "gemma4", "gemma4_text": "gemma4", "nemotron_h": "nemotron_h",
                   "gpt_oss": "gpt_oss"}.get(mt, "llama")
+        blocks = None
+        if family == "nemotron_h":
+            blocks = g("layers_block_type", default=None)
+            if blocks is None:
+                pat = g("hybrid_override_pattern", default="M-M*")
+                blocks = [{"M": "mamba", "*": "attention", "-": "mlp", "E": "moe"}[c] for c in pat]
+            cfg = {**cfg, "num_hidden_layers": len(blocks)}
         mc = ModelConfig(
             name=name, family=family,
             n_layers=g("num_hidden_layers", "n_layer"), hidden=hidden, n_heads=n_heads,
@@ -304,6 +318,28 @@ class ModelConfig:
                 mc.mlp_only_layers = tuple(g("mlp_only_layers", default=()) or ())
             if mt != "qwen3_next":
                 mc.weight_prefix = "model.language_model."
+        if family == "nemotron_h":
+            mc.block_types = tuple(blocks)
+            mc.layer_types = tuple("linear" if b == "mamba" else "full" for b in blocks)
+            mc.lin_k_heads = g("n_groups", default=8)
+            mc.lin_k_dim = g("ssm_state_size", default=128)
+            mc.lin_v_heads = g("mamba_num_heads", default=128)
+            mc.lin_v_dim = g("mamba_head_dim", default=64)
+            mc.lin_conv = g("conv_kernel", default=4)
+            mc.rms_eps = float(g("layer_norm_epsilon", "rms_norm_eps", default=1e-5))
+            mc.act = "relu2"
+            mc.rope = RopeConfig(partial_rotary_factor=0.0)             # attention layers carry no position encoding
+            mc.n_experts = g("n_routed_experts", default=0) if "moe" in blocks else 0
+            if mc.n_experts:
+                mc.n_experts_per_tok = g("num_experts_per_tok", default=2)
+                mc.moe_ffn = g("moe_intermediate_size")
+                mc.shared_expert_ffn = g("moe_shared_expert_intermediate_size", default=0) or 0
+                mc.router, mc.router_bias = "sigmoid", True
+                mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
+                mc.routed_scaling = float(g("routed_scaling_factor", default=1.0))
+                mc.n_group, mc.topk_group = g("n_group", default=1) or 1, g("topk_group", default=1) or 1
+                mc.moe_latent = g("moe_latent_size", default=0) or 0
+            mc.weight_prefix = "backbone."
         if family == "gemma4":
             n_l = mc.n_layers
             types = g("layer_types", default=None) or ["sliding_attention" if (i + 1) % 6 else "full_attention" for i in range(n_l)]
@@ -482,6 +518,14 @@ def preset(name: str) -> ModelConfig:
                            lin_k_heads=16, lin_v_heads=32, lin_k_dim=128, lin_v_dim=128, lin_conv=4, attn_gate=True,
                            norm_one_plus=True, n_experts=512, n_experts_per_tok=10, moe_ffn=512, router="softmax",
                            shared_expert_ffn=512, shared_expert_gate=True, quant="mxfp8")
+    if n in ("tiny-nemotron-h",):  # Mamba-2, attention without positions, relu^2 experts with a shared expert, a plain MLP block
+        return ModelConfig(name="tiny-nemotron-h", family="nemotron_h", n_layers=6, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                           ffn=512, vocab=1024, rms_eps=1e-5, rope=RopeConfig(partial_rotary_factor=0.0),
+                           block_types=("mamba", "moe", "attention", "mlp", "mamba", "moe"),
+                           layer_types=("linear", "full", "full", "full", "linear", "full"), lin_k_heads=2, lin_k_dim=64,
+                           lin_v_heads=8, lin_v_dim=32, lin_conv=4, act="relu2", n_experts=8, n_experts_per_tok=2, moe_ffn=128,
+                           shared_expert_ffn=192, router="sigmoid", router_bias=True, routed_scaling=1.5,
+                           weight_prefix="backbone.", dtype="fp32")
     if n in ("tiny-gemma4",):      # sliding / full layers with their own head sizes, v = k on full layers, per-layer inputs, shared KV
         return ModelConfig(name="tiny-gemma4", family="gemma4", n_layers=6, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
                            ffn=512, vocab=1024, rms_eps=1e-6, qk_norm=True, tie_embeddings=True,
@@ -500,4 +544,4 @@ def preset(name: str) -> ModelConfig:
 
 
 PRESETS = ("tiny-llama", "llama-3.1-8b", "llama-3.1-70b", "qwen3-235b-a22b", "deepseek-v3", "tiny-moe", "tiny-mla",
-           "tiny-qwen3", "tiny-qwen2", "tiny-gemma4", "tiny-qwen3-next", "qwen3-next-80b-a3b", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-yarn")
+           "tiny-qwen3", "tiny-qwen2", "tiny-gemma4", "tiny-nemotron-h", "tiny-qwen3-next", "qwen3-next-80b-a3b", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-yarn")

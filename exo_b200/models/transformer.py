@@ -92,6 +92,9 @@ class KVPool:
         self.layers: dict[int, tuple[torch.Tensor, torch.Tensor | None]] = {}
         _, hkv = local_heads(cfg, spec)
         for i in spec.layers(cfg):
+            if cfg.block_types and cfg.block_types[i] in ("mlp", "moe"):
+                self.layers[i] = (None, None)         # a layer without a sequence mixer keeps nothing
+                continue
             if cfg.layer_is_linear(i):
                 # a gated-delta-rule layer keeps no keys and values: per sequence seat (seat 0 = scratch) the last
                 # taps-1 inputs of its convolution and the [dk, dv] state of every value head, the latter in fp32
@@ -113,7 +116,8 @@ class KVPool:
             from .gemma4 import Gemma4KV
             return Gemma4KV.bytes_per_block(cfg, spec, block_size)
         el = 2 if cfg.dtype == "bf16" else 4
-        n_layers = sum(1 for i in spec.layers(cfg) if not cfg.layer_is_linear(i))
+        n_layers = sum(1 for i in spec.layers(cfg) if not cfg.layer_is_linear(i)
+                       and not (cfg.block_types and cfg.block_types[i] in ("mlp", "moe")))
         if cfg.mla:
             return n_layers * block_size * (cfg.kv_lora_rank + cfg.qk_rope_dim) * el
         _, hkv = local_heads(cfg, spec)
@@ -318,6 +322,9 @@ def make_decoder(cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None
     if cfg.family == "gemma4":
         from .gemma4 import Gemma4Decoder
         return Gemma4Decoder(cfg, weights, spec, comm)
+    if cfg.family == "nemotron_h":
+        from .nemotron_h import NemotronHDecoder
+        return NemotronHDecoder(cfg, weights, spec, comm)
     return Decoder(cfg, weights, spec, comm)
 
 

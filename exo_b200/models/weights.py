@@ -413,6 +413,9 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
     if cfg.family == "gemma4":
         from .gemma4 import build_gemma4_weights
         return build_gemma4_weights(cfg, spec, src, device, progress)
+    if cfg.family == "nemotron_h":
+        from .nemotron_h import build_nemotron_h_weights
+        return build_nemotron_h_weights(cfg, spec, src, device, progress)
     dt = _DTYPES[cfg.dtype]
     dev = torch.device(device)
     r, n = spec.tp_rank, spec.tp_size

@@ -177,3 +177,16 @@ def geglu(gate_up):
     if gate_up.is_cuda:
         return cuda_ops().geglu(gate_up)
     return ref.geglu(gate_up)
+
+
+def mamba2(proj, conv_w, conv_b, a_log, dt_bias, skip, norm_w, eps, conv_state, ssm_state, seats, cu_q, positions, groups, heads,
+           d_state, head_dim):
+    """A Mamba-2 mixer between its projections over a ragged batch (``reference.mamba2`` is the definition)."""
+    fn = cuda_ops().mamba2 if proj.is_cuda else ref.mamba2
+    return fn(proj, conv_w, conv_b, a_log, dt_bias, skip, norm_w, eps, conv_state, ssm_state, seats, cu_q, positions, groups,
+              heads, d_state, head_dim)
+
+
+def relu2(x):
+    """``relu(x)^2`` (torch ops on either device: not a hot path of its own, it sits between two GEMMs)."""
+    return torch.relu(x).square()

@@ -43,7 +43,7 @@ constexpr int GDN_CONV_TOK = 16;
 template <typename T>
 __global__ void gdn_conv_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ w, const T* __restrict__ conv_state,
                                 const int* __restrict__ cu_q, const int* __restrict__ seats, const int* __restrict__ positions,
-                                int T_, int B, int C, int taps, int n_tok, T* __restrict__ y) {
+                                int T_, int B, int C, int taps, int n_tok, const float* __restrict__ bias, T* __restrict__ y) {
   __shared__ int s_seq[GDN_CONV_TOK];
   const int base = blockIdx.y * n_tok;
   if (threadIdx.x < n_tok) {
@@ -73,7 +73,7 @@ __global__ void gdn_conv_kernel(const T* __restrict__ proj, int ld, const float*
       continue;
     }
     const SeqInfo q = seq_info(s, cu_q, seats, positions);
-    float acc = 0.f;
+    float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps; j++) {
       const int src = t - hist + j;
       float x;
@@ -131,12 +131,17 @@ static size_t gdn_smem_bytes(int dk, int dv, size_t elem) {
   return 2 * GDN_TB * (2 * dk + 2 * dv) * elem + (2 * GDN_TB * (dk / 16) * GDN_SEG + GDN_TB * dv + 3 * GDN_TB) * sizeof(float);
 }
 
-template <typename T, int DK>
+// MODE 0: gated delta rule as described above.  MODE 1: the Mamba-2 state-space recurrence on the same machinery, with
+// q := C, k := B (one pair per group of heads, not normalised), v := x, the `a` column holding dt:
+//   dt = softplus(a + dt_bias);  S *= exp(-exp(a_log) dt);  S += B (x) (dt x);  y = C.S + skip[h] * x
+// and the raw y stored (the grouped gated norm over several heads is mamba_norm_kernel's).
+template <typename T, int DK, int MODE>
 __global__ void __launch_bounds__(DK >= 64 ? 512 : 256) gdn_delta_kernel(
     const T* __restrict__ y, const T* __restrict__ proj, int ld, int z_off, int b_off, int a_off,
     const float* __restrict__ a_log, const float* __restrict__ dt_bias, const T* __restrict__ norm_w, float eps,
     float* __restrict__ rec_state, const int* __restrict__ cu_q, const int* __restrict__ seats,
-    const int* __restrict__ positions, int hk, int hv, int DV, int nsplit, int aligned, T* __restrict__ out) {
+    const int* __restrict__ positions, int hk, int hv, int DV, int nsplit, int aligned, const float* __restrict__ skip,
+    T* __restrict__ out) {
   constexpr int PL = DK / 16;          // lanes per column pair
   constexpr int QK = PL * GDN_SEG;     // floats per token of q (or k) in shared memory
   constexpr int TB = GDN_TB;
@@ -229,8 +234,9 @@ __global__ void __launch_bounds__(DK >= 64 ? 512 : 256) gdn_delta_kernel(
     // ---- A: gates of this block, then start the next block's copies and wait for this block's
     if (tid < nb) {
       const float xa = pre_a + dtb;
-      s_decay[tid] = __expf(neg_a * (xa > 20.f ? xa : log1pf(__expf(xa))));      // exp(-exp(a_log) * softplus(a + dt_bias))
-      s_beta[tid] = 1.f / (1.f + __expf(-pre_b));
+      const float sp = xa > 20.f ? xa : log1pf(__expf(xa));
+      s_decay[tid] = __expf(neg_a * sp);                                          // exp(-exp(a_log) * softplus(a + dt_bias))
+      s_beta[tid] = MODE == 0 ? 1.f / (1.f + __expf(-pre_b)) : sp;                // sigmoid(b), or the time step itself
     }
     if (tb0 + TB < sq.t1) {
       issue(tb0 + TB, stage ^ 1);
@@ -251,7 +257,7 @@ __global__ void __launch_bounds__(DK >= 64 ? 512 : 256) gdn_delta_kernel(
       qs = warp_sum(qs);
       ks = warp_sum(ks);
       qk = warp_sum(qk);
-      const float qn = rsqrtf(qs + 1e-6f) * q_scale, kn = rsqrtf(ks + 1e-6f);
+      const float qn = MODE == 0 ? rsqrtf(qs + 1e-6f) * q_scale : 1.f, kn = MODE == 0 ? rsqrtf(ks + 1e-6f) : 1.f;
 #pragma unroll
       for (int r = 0; r < DK / 32; r++) {
         s_q[tok * QK + gdn_at(r * 32 + lane)] = qv[r] * qn;
@@ -296,9 +302,10 @@ __global__ void __launch_bounds__(DK >= 64 ? 512 : 256) gdn_delta_kernel(
         o1 += __shfl_xor_sync(0xffffffffu, o1, m);
       }
       const float beta = s_beta[tok], qk = s_qk[tok];
-      const float d0 = (v0 - mem0) * beta, d1 = (v1 - mem1) * beta;
+      const float d0 = (MODE == 0 ? v0 - mem0 : v0) * beta, d1 = (MODE == 0 ? v1 - mem1 : v1) * beta;
       o0 += qk * d0;
       o1 += qk * d1;
+      if (MODE == 1) { o0 += skip[h] * v0; o1 += skip[h] * v1; }
 #pragma unroll
       for (int i = 0; i < 16; i++) { S0[i] += kr[i] * d0; S1[i] += kr[i] * d1; }
       if (part == 0) *reinterpret_cast<float2*>(s_o + tok * DVs + j0) = make_float2(o0, o1);
@@ -307,7 +314,7 @@ __global__ void __launch_bounds__(DK >= 64 ? 512 : 256) gdn_delta_kernel(
     // ---- C: RMSNorm over each head output, * weight * silu(z)
     for (int tok = warp; tok < nb; tok += n_warps) {
       T* dst = out + (size_t)(tb0 + tok) * hv * DV + h * DV + c0;
-      if (nsplit > 1) {                   // this CTA sees a slice of the head: raw outputs, normalised by the next kernel
+      if (nsplit > 1 || MODE == 1) {      // a slice of the head (or the state-space form): raw outputs, normalised by the next kernel
         for (int jj = lane; jj < DVs; jj += 32) dst[jj] = Cvt<T>::from_f(s_o[tok * DVs + jj]);
         continue;
       }
@@ -349,6 +356,30 @@ __global__ void gdn_norm_gate_kernel(T* __restrict__ out, const T* __restrict__ 
   }
 }
 
+// Mamba-2 output: y * silu(z), RMS-normalised over groups of `gsize` neighbouring channels, times the weight.  One warp
+// per (token, group); in place over the raw outputs.
+template <typename T>
+__global__ void mamba_norm_kernel(T* __restrict__ out, const T* __restrict__ proj, int ld, int z_off, const T* __restrict__ norm_w,
+                                  float eps, int rows, int width, int gsize) {
+  const int groups = width / gsize;
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= rows * groups) return;
+  const int t = w / groups, g = w % groups;
+  T* o = out + (size_t)t * width + g * gsize;
+  const T* z = proj + (size_t)t * ld + z_off + g * gsize;
+  float ss = 0.f;
+  for (int j = lane; j < gsize; j += 32) {
+    const float v = Cvt<T>::to_f(o[j]) * silu_f(Cvt<T>::to_f(z[j]));
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float rs = rsqrtf(ss / (float)gsize + eps);
+  for (int j = lane; j < gsize; j += 32) {
+    const float v = Cvt<T>::to_f(o[j]) * silu_f(Cvt<T>::to_f(z[j]));
+    o[j] = Cvt<T>::from_f(v * rs * Cvt<T>::to_f(norm_w[g * gsize + j]));
+  }
+}
+
 template <typename T>
 __global__ void sigmoid_gate_kernel(const T* __restrict__ x, const T* __restrict__ gate, int ldg, T* __restrict__ out, size_t rows,
                                     int n) {
@@ -377,14 +408,15 @@ __global__ void scaled_add_kernel(const T* __restrict__ y, const T* __restrict__
 template <typename T>
 int launch_gated_delta(const void* proj, int ld, const float* conv_w, const float* a_log, const float* dt_bias, const void* norm_w,
                        float eps, void* conv_state, float* rec_state, const int* seats, const int* cu_q, const int* positions,
-                       int T_, int B, int hk, int hv, int dk, int dv, int taps, void* y, void* out, cudaStream_t st) {
+                       int T_, int B, int hk, int hv, int dk, int dv, int taps, void* y, void* out, int mode,
+                       const float* conv_bias, const float* skip, int norm_group, cudaStream_t st) {
   const int C = 2 * hk * dk + hv * dv;
   if (taps < 2 || taps > MAX_TAPS || dv % 32 || dv * (dk / 32) > (dk >= 64 ? 512 : 256) || hv % hk) return -2;
   if (T_ == 0 || B == 0) return 0;
   const int n_tok = T_ >= 1024 ? GDN_CONV_TOK : 1;
   dim3 gc((C + 255) / 256, (T_ + n_tok - 1) / n_tok);
   gdn_conv_kernel<T><<<gc, 256, 0, st>>>((const T*)proj, ld, conv_w, (const T*)conv_state, cu_q, seats, positions, T_, B, C, taps,
-                                         n_tok, (T*)y);
+                                         n_tok, conv_bias, (T*)y);
   dim3 gs((C + 255) / 256, B);
   gdn_conv_state_kernel<T><<<gs, 256, 0, st>>>((const T*)proj, ld, (T*)conv_state, cu_q, seats, positions, C, taps);
   // heads x sequences fill the GPU by themselves in a batched decode; a single prompt gets its heads split by columns
@@ -398,24 +430,31 @@ int launch_gated_delta(const void* proj, int ld, const float* conv_w, const floa
   const int aligned = ((uintptr_t)y % 16 == 0 && (uintptr_t)proj % 16 == 0 && (C * el) % 16 == 0 && ((size_t)ld * el) % 16 == 0 &&
                        (dk * el) % 16 == 0 && (dvs * el) % 16 == 0 && (z_off * el) % 16 == 0) ? 1 : 0;
   const size_t smem = gdn_smem_bytes(dk, dvs, el);
-#define EXO_GDN(DK)                                                                                                          \
+#define EXO_GDN_M(DK, MM)                                                                                                    \
   do {                                                                                                                       \
     static bool opted = false;                                                                                               \
     if (!opted) {                                                                                                            \
-      if (cudaFuncSetAttribute(gdn_delta_kernel<T, DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess) \
+      if (cudaFuncSetAttribute(gdn_delta_kernel<T, DK, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess) \
         return -3;                                                                                                           \
       opted = true;                                                                                                          \
     }                                                                                                                        \
-    gdn_delta_kernel<T, DK><<<gd, (dvs / 2) * (DK / 16), smem, st>>>((const T*)y, (const T*)proj, ld, z_off, b_off, a_off, a_log, \
-                                                                     dt_bias, (const T*)norm_w, eps, rec_state, cu_q, seats, \
-                                                                     positions, hk, hv, dv, nsplit, aligned, (T*)out);       \
+    gdn_delta_kernel<T, DK, MM><<<gd, (dvs / 2) * (DK / 16), smem, st>>>((const T*)y, (const T*)proj, ld, z_off, b_off, a_off, a_log, \
+                                                                         dt_bias, (const T*)norm_w, eps, rec_state, cu_q, seats, \
+                                                                         positions, hk, hv, dv, nsplit, aligned, skip, (T*)out); \
   } while (0)
+#define EXO_GDN(DK) do { if (mode == 1) EXO_GDN_M(DK, 1); else EXO_GDN_M(DK, 0); } while (0)
   if (dk == 128) EXO_GDN(128);
   else if (dk == 64) EXO_GDN(64);
   else if (dk == 32) EXO_GDN(32);
   else return -2;
 #undef EXO_GDN
-  if (nsplit > 1) {
+#undef EXO_GDN_M
+  if (mode == 1) {
+    const int width = hv * dv;
+    const long warps = (long)T_ * (width / norm_group);
+    mamba_norm_kernel<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>((T*)out, (const T*)proj, ld, z_off, (const T*)norm_w, eps,
+                                                                                T_, width, norm_group);
+  } else if (nsplit > 1) {
     const long warps = (long)T_ * hv;
     gdn_norm_gate_kernel<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>((T*)out, (const T*)proj, ld, z_off, (const T*)norm_w,
                                                                                   eps, T_, hv, dv);
@@ -428,15 +467,18 @@ int launch_gated_delta(const void* proj, int ld, const float* conv_w, const floa
 // proj [T, ld]: q | k | v | z | b | a of this rank's heads; y [T, 2*hk*dk + hv*dv] scratch; out [T, hv*dv].
 // Returns -2 for head sizes the kernels are not built for (dk in {32, 64, 128}; dv a multiple of 32 with
 // dv * dk / 32 threads fitting a CTA: dv <= 128 at dk = 128, else dv <= 256).
+// mode 0: gated delta rule (norm_w [dv]).  mode 1: Mamba-2 (proj columns C | B | x | z | dt | dt; conv_bias [channels], skip
+// [hv] = the D of the skip connection, norm_w [hv*dv] applied over groups of norm_group channels).
 EXO_API int exo_gated_delta(const void* proj, int ld, const float* conv_w, const float* a_log, const float* dt_bias,
                             const void* norm_w, float eps, void* conv_state, float* rec_state, const int* seats, const int* cu_q,
                             const int* positions, int T, int B, int hk, int hv, int dk, int dv, int taps, void* y, void* out,
-                            int dtype, cudaStream_t st) {
+                            int dtype, int mode, const float* conv_bias, const float* skip, int norm_group, cudaStream_t st) {
+  if (mode == 1 && (!skip || norm_group <= 0 || (hv * dv) % norm_group)) return -2;
   int rc = dtype == EXO_BF16
                ? launch_gated_delta<__nv_bfloat16>(proj, ld, conv_w, a_log, dt_bias, norm_w, eps, conv_state, rec_state, seats, cu_q,
-                                                   positions, T, B, hk, hv, dk, dv, taps, y, out, st)
+                                                   positions, T, B, hk, hv, dk, dv, taps, y, out, mode, conv_bias, skip, norm_group, st)
                : launch_gated_delta<float>(proj, ld, conv_w, a_log, dt_bias, norm_w, eps, conv_state, rec_state, seats, cu_q,
-                                           positions, T, B, hk, hv, dk, dv, taps, y, out, st);
+                                           positions, T, B, hk, hv, dk, dv, taps, y, out, mode, conv_bias, skip, norm_group, st);
   if (rc) return rc;
   EXO_CHECK_LAUNCH();
   return 0;

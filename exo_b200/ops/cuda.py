@@ -46,7 +46,7 @@ class _Sig:
     exo_rmsnorm = (_i, [_p, _p, _p, _p, _p, _i, _i, _f, _i, _p])
     exo_swiglu = (_i, [_p, _p, _i, _i, _i, _p])
     exo_moe_experts_gemv_fp8 = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p])
-    exo_gated_delta = (_i, [_p, _i, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p])
+    exo_gated_delta = (_i, [_p, _i, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _i, _p, _p, _i, _p])
     exo_sigmoid_gate = (_i, [_p, _p, _i, _p, _i, _i, _i, _p])
     exo_scaled_add = (_i, [_p, _p, _p, _p, _i, _i, _i, _p])
     exo_embedding = (_i, [_p, _p, _p, _i, _i, _i, _i, _p])
@@ -209,8 +209,31 @@ def gated_delta(proj, conv_w, a_log, dt_bias, norm_w, eps, conv_state, rec_state
     out = _empty(T, hv * dv, dtype=proj.dtype, device=proj.device, what="gated_delta out")
     _chk(load().exo_gated_delta(_ptr(proj), ld, _ptr(conv_w), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), float(eps),
                                 _ptr(conv_state), _ptr(rec_state), _ptr(seats), _ptr(cu_q), _ptr(positions), T, B, hk, hv,
-                                dk, dv, conv_w.shape[1], _ptr(y), _ptr(out), _dt(proj), _st()), "gated_delta")
+                                dk, dv, conv_w.shape[1], _ptr(y), _ptr(out), _dt(proj), 0, None, None, 0, _st()), "gated_delta")
     _count(3)          # (a fourth, the output norm, when a small grid has its heads split by columns)
+    return out
+
+
+def mamba2(proj, conv_w, conv_b, a_log, dt_bias, skip, norm_w, eps, conv_state, ssm_state, seats, cu_q, positions, groups, heads,
+           d_state, head_dim):
+    """Mamba-2 mixer between its projections (columns C | B | x | z | dt | dt): the gated-delta-rule kernels in their
+    state-space mode plus the grouped gated norm (four launches, no host reads)."""
+    proj = proj.contiguous()
+    T, ld = proj.shape
+    B = cu_q.numel() - 1
+    C = 2 * groups * d_state + heads * head_dim
+    if ld != C + heads * head_dim + 2 * heads or conv_state.dtype != proj.dtype or ssm_state.dtype != torch.float32:
+        raise KernelError(f"mamba2: projection width {ld} / state dtypes do not fit groups={groups} heads={heads}")
+    if CHECKS:
+        _check_indices("state seats", seats, ssm_state.shape[0])
+    y = _empty(T, C, dtype=proj.dtype, device=proj.device, what="mamba2 conv")
+    out = _empty(T, heads * head_dim, dtype=proj.dtype, device=proj.device, what="mamba2 out")
+    gsize = heads * head_dim // groups
+    _chk(load().exo_gated_delta(_ptr(proj), ld, _ptr(conv_w), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), float(eps),
+                                _ptr(conv_state), _ptr(ssm_state), _ptr(seats), _ptr(cu_q), _ptr(positions), T, B, groups, heads,
+                                d_state, head_dim, conv_w.shape[1], _ptr(y), _ptr(out), _dt(proj), 1, _ptr(conv_b), _ptr(skip),
+                                gsize, _st()), "mamba2")
+    _count(4)
     return out
 
 

@@ -442,3 +442,76 @@ def gated_delta(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, d
     out = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
     out = out * torch.nn.functional.silu(z.reshape(T, hv, dv))
     return out.reshape(T, vd).to(proj.dtype)
+
+
+def mamba2(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor | None, a_log: torch.Tensor, dt_bias: torch.Tensor,
+           skip: torch.Tensor, norm_w: torch.Tensor, eps: float, conv_state: torch.Tensor, ssm_state: torch.Tensor,
+           seats: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor, groups: int, heads: int, d_state: int,
+           head_dim: int) -> torch.Tensor:
+    """A Mamba-2 mixer between its input and output projections over a ragged batch.
+
+    ``proj [T, 2*groups*d_state + 2*heads*head_dim + 2*heads]`` holds, per token, ``C | B | x | z | dt | dt`` (the time step
+    twice: the layout is the gated delta rule's, whose kernels run this recurrence too).  Per sequence (state seat
+    ``seats[s]``; a first token at position 0 starts from zero state):
+
+    1. ``C | B | x`` go through the causal depthwise convolution (``conv_w [channels, taps]``, ``conv_b``) with the seat's
+       history, then SiLU;
+    2. per head ``h`` of group ``g``: ``dt = softplus(dt + dt_bias[h])``, ``S <- S * exp(-exp(a_log[h]) * dt) +
+       B_g (x) (dt * x_h)``, ``y_h = C_g . S + skip[h] * x_h`` with ``S [d_state, head_dim]`` kept in
+       ``ssm_state [., heads, d_state, head_dim]``;
+    3. ``y * silu(z)`` is RMS-normalised over groups of ``heads*head_dim/groups`` channels and scaled by ``norm_w``.
+
+    Definition followed: ``NemotronHMamba2Mixer.torch_forward`` of the ``transformers`` library, with the time step
+    limited to ``(0, inf)`` as the kernels of ``mamba_ssm`` and the reference's ``mlx_lm.models.nemotron_h`` do."""
+    T = proj.shape[0]
+    gn, width = groups * d_state, heads * head_dim
+    taps = conv_w.shape[1]
+    cbx, z, dt, _ = proj.float().split((2 * gn + width, width, heads, heads), -1)
+    out = torch.zeros(T, heads, head_dim, dtype=torch.float32, device=proj.device)
+    cu, seat_l = cu_q.tolist(), seats.tolist()
+    w = conv_w.float()
+    A = -a_log.float().exp()
+    rep = heads // groups
+    for s in range(len(cu) - 1):
+        t0, t1 = cu[s], cu[s + 1]
+        if t1 <= t0:
+            continue
+        seat = seat_l[s]
+        fresh = int(positions[t0]) == 0
+        hist = torch.zeros(taps - 1, 2 * gn + width, device=proj.device) if fresh else conv_state[seat].float().t()
+        xin = torch.cat((hist, cbx[t0:t1]), 0)
+        conv_state[seat] = xin[-(taps - 1):].t().to(conv_state.dtype)
+        L = t1 - t0
+        yc = sum(xin[j:j + L] * w[:, j] for j in range(taps))
+        if conv_b is not None:
+            yc = yc + conv_b.float()
+        yc = torch.nn.functional.silu(yc)
+        Cm, Bm, x = yc.split((gn, gn, width), -1)
+        Cm = Cm.reshape(L, groups, d_state).repeat_interleave(rep, 1)
+        Bm = Bm.reshape(L, groups, d_state).repeat_interleave(rep, 1)
+        x = x.reshape(L, heads, head_dim)
+        step = torch.nn.functional.softplus(dt[t0:t1] + dt_bias.float())             # [L, heads]
+        S = torch.zeros_like(ssm_state[seat], dtype=torch.float32) if fresh else ssm_state[seat].float().clone()
+        for t in range(L):
+            S = S * (step[t] * A).exp()[:, None, None] + Bm[t][:, :, None] * (step[t][:, None] * x[t])[:, None, :]
+            out[t0 + t] = (S * Cm[t][:, :, None]).sum(1) + skip.float()[:, None] * x[t]
+        ssm_state[seat] = S.to(ssm_state.dtype)
+    y = out.reshape(T, width) * torch.nn.functional.silu(z)
+    gsize = width // groups
+    yg = y.reshape(T, groups, gsize)
+    yg = yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + eps)
+    return (yg.reshape(T, width) * norm_w.float()).to(proj.dtype)
+
+
+def relu2_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor,
+                  expert_offset: int = 0) -> torch.Tensor:
+    """Weighted sum of NON-gated experts ``down(relu(up(x))^2)`` (Nemotron-H): ``w_up [E, F, H]``, ``w_down [E, H, F]``."""
+    T, H = x.shape
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for e in range(w_up.shape[0]):
+        tok, slot = torch.where(ids == e + expert_offset)
+        if tok.numel() == 0:
+            continue
+        h = torch.relu(linear(x[tok], w_up[e]).float()).pow(2).to(x.dtype)
+        out.index_add_(0, tok, linear(h, w_down[e]).float() * weights[tok, slot][:, None])
+    return out.to(x.dtype)

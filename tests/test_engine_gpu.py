@@ -99,6 +99,25 @@ def test_hybrid_linear_attention_model_on_gpu_matches_oracle_and_graphs():
     assert outs[0] == outs[1] and all(len(x) == 12 for x in outs[0])
 
 
+def test_nemotron_h_on_gpu_matches_the_cpu_engine():
+    """Nemotron-H-shaped model (Mamba-2 layers on the state-space kernels, attention without positions, relu^2 MLP and
+    experts): fp32 on the GPU reproduces the CPU engine's tokens with a chunked prompt and two sequences in flight."""
+    cfg = preset("tiny-nemotron-h")
+    prompts = [oracle_prompt(n, cfg.vocab, seed=n).tolist() for n in (70, 23)]
+    outs = []
+    for dev in ("cpu", "cuda"):
+        w = build_weights(cfg, ShardSpec(), RandomSource(seed=0, std=0.05), device=dev)
+        eng = Engine(cfg, w, n_blocks=64, device=dev, prefill_chunk=32, max_seqs=4)
+        ids = [eng.submit(q, SamplingParams(max_tokens=8, **GREEDY)) for q in prompts]
+        got = {i: [] for i in ids}
+        while eng.has_work:
+            for o in eng.step():
+                if o.token is not None:
+                    got[o.req_id].append(o.token)
+        outs.append([got[i] for i in ids])
+    assert outs[0] == outs[1] and all(len(x) == 8 for x in outs[0])
+
+
 def test_gemma4_on_gpu_matches_the_cpu_engine_and_graphs():
     """Gemma-4-shaped model (sliding and full layers with their own head sizes, v = k, shared-KV layers, per-layer inputs,
     soft-capped logits): fp32 on the GPU reproduces the CPU engine's tokens with a chunked prompt; bf16 with CUDA graphs

@@ -491,6 +491,43 @@ def test_gated_delta_rule(K, dtype, hk, hv, dk, dv, lens):
         start = [s + n for s, n in zip(start, step_lens)]
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("groups,heads,d_state,head_dim,lens", [(2, 8, 32, 32, [5, 1, 70]), (1, 4, 128, 64, [40, 1, 1, 1]),
+                                                                 (8, 16, 128, 64, [130, 17])])
+def test_mamba2(K, dtype, groups, heads, d_state, head_dim, lens):
+    """Mamba-2 mixer (convolution with bias, state-space recurrence, skip, grouped gated norm) against the fp32 definition
+    over two consecutive steps; the second continues from the seats' state."""
+    g = torch.Generator(device="cuda").manual_seed(2)
+    B, taps, seats_n = len(lens), 4, 8
+    width, gn = heads * head_dim, groups * d_state
+    C = 2 * gn + width
+    W = C + width + 2 * heads
+    conv_w = torch.randn(C, taps, device="cuda", generator=g) * 0.5
+    conv_b = torch.randn(C, device="cuda", generator=g) * 0.2
+    a_log, dt_bias = torch.randn(heads, device="cuda", generator=g) * 0.5, torch.randn(heads, device="cuda", generator=g) * 0.5
+    skip = 1 + 0.2 * torch.randn(heads, device="cuda", generator=g)
+    norm_w = (1 + 0.1 * torch.randn(width, device="cuda", generator=g)).to(dtype)
+    seats = torch.tensor([3, 1, 5, 2][:B], dtype=torch.int32, device="cuda")
+    conv_k = torch.randn(seats_n, C, taps - 1, device="cuda", generator=g).to(dtype)
+    ssm_k = torch.randn(seats_n, heads, d_state, head_dim, device="cuda", generator=g)
+    conv_r, ssm_r = conv_k.clone(), ssm_k.clone()
+    start = [0] * B
+    for step_lens in (lens, [3] * B):
+        T = sum(step_lens)
+        cu = torch.tensor([0] + list(torch.tensor(step_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        pos = torch.cat([torch.arange(s, s + n) for s, n in zip(start, step_lens)]).to(torch.int32).cuda()
+        proj = torch.randn(T, W, device="cuda", generator=g).to(dtype)
+        proj[:, -heads:] = proj[:, -2 * heads:-heads]                                          # the time step sits in both slots
+        got = K.mamba2(proj, conv_w, conv_b, a_log, dt_bias, skip, norm_w, 1e-5, conv_k, ssm_k, seats, cu, pos, groups, heads,
+                       d_state, head_dim)
+        want = ref.mamba2(proj.float(), conv_w, conv_b, a_log, dt_bias, skip, norm_w.float(), 1e-5, conv_r, ssm_r, seats, cu, pos,
+                          groups, heads, d_state, head_dim)
+        tol = 3e-2 if dtype == torch.bfloat16 else 2e-3
+        close(got, want, tol, tol)
+        close(ssm_k[seats.long()], ssm_r[seats.long()], tol, tol)
+        start = [s + n for s, n in zip(start, step_lens)]
+
+
 def test_sigmoid_gate_and_scaled_add(K):
     g = torch.Generator(device="cuda").manual_seed(2)
     for dtype in (torch.float32, torch.bfloat16):

@@ -45,14 +45,15 @@ FAMILIES = [("tiny-llama", 2), ("tiny-llama", 4), ("tiny-moe", 2), ("tiny-mla", 
             ("tiny-qwen2", 2), ("tiny-glm4-moe", 2), ("tiny-glm4-moe", 4), ("tiny-mixtral", 2), ("tiny-mixtral", 4),
             ("tiny-minimax", 2), ("tiny-minimax", 4), ("tiny-gpt-oss", 2), ("tiny-yarn", 2),
             ("tiny-qwen3-next", 2),     # gated-delta-rule heads split by key-head group, state per rank
-            ("tiny-gemma4", 2)]         # per-layer head sizes, one global KV head on two ranks, replicated per-layer inputs
+            ("tiny-gemma4", 2),         # per-layer head sizes, one global KV head on two ranks, replicated per-layer inputs
+            ("tiny-nemotron-h", 2)]     # Mamba-2 heads and groups split, relu^2 experts whole, shared expert sliced
 
 
 @pytest.mark.parametrize("name,world", FAMILIES)
 def test_tp_ranks_reproduce_oracle_tokens(name, world):
     cfg = preset(name)
     prompt = oracle_prompt(48, cfg.vocab, seed=11).tolist()
-    if cfg.family == "gemma4":      # the oracle model has no Gemma-4 block (the library is its oracle): compare with one rank
+    if cfg.family in ("gemma4", "nemotron_h"):      # the oracle model has no such block (the library is its oracle): compare with one rank
         from exo_b200.engine.engine import Engine
         from exo_b200.engine.kv import SamplingParams
         from exo_b200.models.weights import ShardSpec, build_weights
@@ -106,7 +107,7 @@ def test_pipeline_stages_reproduce_oracle_tokens(name, world, pp):
     stage (chunked prefill of 48 tokens in 32-token chunks, then decode), ids come back to rank 0."""
     cfg = preset(name)
     prompt = oracle_prompt(48, cfg.vocab, seed=11).tolist()
-    if cfg.family == "gemma4":      # the oracle model has no Gemma-4 block (the library is its oracle): compare with one rank
+    if cfg.family in ("gemma4", "nemotron_h"):      # the oracle model has no such block (the library is its oracle): compare with one rank
         from exo_b200.engine.engine import Engine
         from exo_b200.engine.kv import SamplingParams
         from exo_b200.models.weights import ShardSpec, build_weights
