@@ -69,6 +69,13 @@ CASES = {
                           dict(family="gemma4", weight_prefix="model.language_model.", k_eq_v=True, global_kv_heads=1, ple_dim=8,
                                kv_shared_layers=2, act="gelu_tanh", logit_softcap=30.0, sliding_window=16,
                                layer_types=("sliding",) * 5 + ("full",))),
+    "nemotron-h-pattern": ({"model_type": "nemotron_h", "hybrid_override_pattern": "M-M*ME", "ssm_state_size": 64, "mamba_num_heads": 8,
+                            "mamba_head_dim": 32, "n_groups": 2, "conv_kernel": 4, "n_routed_experts": 8, "num_experts_per_tok": 2,
+                            "moe_intermediate_size": 64, "moe_shared_expert_intermediate_size": 96, "layer_norm_epsilon": 1e-5},
+                           dict(family="nemotron_h", n_layers=6, block_types=("mamba", "mlp", "mamba", "attention", "mamba", "moe"),
+                                layer_types=("linear", "full", "linear", "full", "linear", "full"), act="relu2", router="sigmoid",
+                                lin_k_heads=2, lin_k_dim=64, lin_v_heads=8, lin_v_dim=32, shared_expert_ffn=96,
+                                weight_prefix="backbone.")),
     "qwen2": ({"model_type": "qwen2", "tie_word_embeddings": True}, dict(family="llama", attn_bias=True, tie_embeddings=True)),
 }
 
