@@ -58,8 +58,6 @@ class Executor:
             self.use_graphs = False       # the checking flavour synchronises after every op: nothing can be captured
         if self.pipe is not None:
             self.use_graphs = False       # stage hops run on a side stream and wait on the peer: not capturable
-        if (cfg.family == "gemma4" and cfg.moe_beside_mlp) or (cfg.family == "nemotron_h" and cfg.n_experts):
-            self.use_graphs = False       # GeGLU / relu^2 expert blocks run as PyTorch ops that read the routing on the host
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self.out_host = torch.zeros(self.max_B, dtype=torch.int32, pin_memory=self.cuda)
         self.prev_sampled = torch.zeros(max(self.max_B, 256), dtype=torch.int32, device=self.device)

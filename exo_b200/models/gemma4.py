@@ -231,9 +231,7 @@ class Gemma4Decoder(Decoder):
         wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, "softmax", True, None, 1, 1, 1.0)
         x2 = ops.rmsnorm(h, lw.pre_ffn_norm_2, cfg.rms_eps)[0]
         elo, _ = expert_range(cfg, self.spec)
-        # GeGLU experts: the grouped expert kernels are SwiGLU; this block runs as PyTorch ops on either device (with host
-        # reads of the routing, so a model with it is not captured in CUDA graphs)
-        y = gelu_experts(x2, lw.e_gate_up, lw.e_down, wts, ids.long(), elo)
+        y = ops.moe_experts(x2, lw.e_gate_up, lw.e_down, wts, ids, elo, cfg.n_experts, act="gelu_tanh")
         return resolve(self.comm.row_sum(y))
 
     # ------------------------------------------------------------------ forward
@@ -283,17 +281,3 @@ class Gemma4Decoder(Decoder):
         if cfg.logit_softcap:
             logits = (torch.tanh(logits.float() / cfg.logit_softcap) * cfg.logit_softcap).to(logits.dtype)
         return logits
-
-
-def gelu_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor,
-                 expert_offset: int = 0) -> torch.Tensor:
-    """Weighted sum of GeGLU experts (the definition; ``ops.reference.moe_experts`` is its SwiGLU twin)."""
-    T, H = x.shape
-    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
-    for e in range(w_gate_up.shape[0]):
-        tok, slot = torch.where(ids == e + expert_offset)
-        if tok.numel() == 0:
-            continue
-        y = ref.linear(ref.geglu(ref.linear(x[tok], w_gate_up[e])), w_down[e]).float()
-        out.index_add_(0, tok, y * weights[tok, slot][:, None])
-    return out.to(x.dtype)

@@ -173,9 +173,7 @@ class NemotronHDecoder(Decoder):
                                  cfg.topk_group, cfg.routed_scaling)
         elo, _ = expert_range(cfg, self.spec)
         xin = ops.linear(x, lw.lat_in) if lw.lat_in is not None else x
-        # non-gated relu^2 experts: the grouped expert kernels are SwiGLU; this block runs as PyTorch ops on either device
-        # (with host reads of the routing, so a model with it is not captured in CUDA graphs)
-        y = ref.relu2_experts(xin, lw.e_up, lw.e_down, wts, ids.long(), elo)
+        y = ops.moe_experts(xin, lw.e_up, lw.e_down, wts, ids, elo, cfg.n_experts, act="relu2")
         if lw.lat_out is not None:
             y = ops.linear(y, lw.lat_out)          # of this rank's partial sum: the projection is linear
         if lw.w_up is not None:

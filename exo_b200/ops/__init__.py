@@ -124,10 +124,12 @@ def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling
     return ref.moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling)
 
 
-def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None):
+def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None, act="silu"):
+    """Weighted sum of the routed experts.  ``act``: ``silu`` / ``gelu_tanh`` (gated) or ``relu2`` (``w_gate_up`` is then the
+    single up projection ``[E, F, H]``)."""
     if x.is_cuda:
-        return cuda_ops().moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, n_experts_total)
-    return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
+        return cuda_ops().moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, n_experts_total, act)
+    return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, act)
 
 
 def embedding(table, ids):

@@ -323,6 +323,12 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
 // ------------------------------------------------------------------------------------------
 constexpr int BM = 128, BK = 64;
 
+// expert activations: 0 silu(gate) * up, 1 gelu_tanh(gate) * up, 2 relu(up)^2 (no gate: one projection of F rows)
+enum { ACT_SWIGLU = 0, ACT_GEGLU = 1, ACT_RELU2 = 2 };
+__device__ __forceinline__ float gelu_tanh_f(float g) {
+  return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
 struct GroupedParams {
   const int* plan;        // [1 + 4 * max_tiles]
   int rows_w;             // weight rows per expert in the 2-D view (2F for gate_up, H for down)
@@ -335,6 +341,7 @@ struct GroupedParams {
   int scale_kind, nt, kt;
   int f16;                // fp8 kernels: both MMA operands f16 (token rows arrive as f16)
   int out_f16;            // write `out` as f16 (the gate/up result that feeds an f16 down projection)
+  int act;                // DUAL kernels: ACT_SWIGLU / ACT_GEGLU; single kernels: ACT_RELU2 squares the rectified output
 };
 
 // FP8: the weight tiles arrive as bytes in `raw`; eight converter warps widen them into tensor memory, from where
@@ -511,9 +518,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             float y;
             if (DUAL) {   // the projection is rounded to bf16 before the activation, as the unfused form does
               const float gb = __bfloat162float(__float2bfloat16_rn(g[j])), ub = __bfloat162float(__float2bfloat16_rn(u[j]));
-              y = silu_f(gb) * ub;
+              y = (p.act == ACT_GEGLU ? gelu_tanh_f(gb) : silu_f(gb)) * ub;
             } else {
               y = g[j];
+              if (p.act == ACT_RELU2) {
+                const float rb = fmaxf(__bfloat162float(__float2bfloat16_rn(y)), 0.f);
+                y = rb * rb;
+              }
             }
             const size_t o = (size_t)(row0 + c + j) * p.n_out + n;
             if (FP8 && p.out_f16) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(fminf(fmaxf(y, -65504.f), 65504.f));
@@ -609,7 +620,7 @@ __device__ __forceinline__ float dot_row(const __nv_bfloat16* __restrict__ w, co
 // hs[pair, f] = silu(Wg[e][f] . x[t]) * (Wu[e][f] . x[t])
 __global__ void __launch_bounds__(GV_THREADS)
 moe_gemv_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu, const int* __restrict__ ids,
-                        int k, int H, int F, int expert_offset, int E, __nv_bfloat16* __restrict__ hs) {
+                        int k, int H, int F, int expert_offset, int E, int act, __nv_bfloat16* __restrict__ hs) {
   extern __shared__ __align__(16) uint8_t gv_smem[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gv_smem);
   const int pair = blockIdx.y;
@@ -619,16 +630,17 @@ moe_gemv_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   for (int i = threadIdx.x; i < H / 8; i += GV_THREADS) reinterpret_cast<uint4*>(xs)[i] = src[i];
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const __nv_bfloat16* wg = w_gu + (size_t)e * 2 * F * H;
+  const __nv_bfloat16* wg = w_gu + (size_t)e * (act == ACT_RELU2 ? 1 : 2) * F * H;
   for (int r = warp; r < GV_ROWS; r += GV_THREADS / 32) {
     const int f = blockIdx.x * GV_ROWS + r;
     if (f >= F) break;
     float g = dot_row(wg + (size_t)f * H, xs, H, lane);
-    float u = dot_row(wg + (size_t)(F + f) * H, xs, H, lane);
+    float u = act == ACT_RELU2 ? 0.f : dot_row(wg + (size_t)(F + f) * H, xs, H, lane);
     if (lane == 0) {
       g = __bfloat162float(__float2bfloat16_rn(g));
       u = __bfloat162float(__float2bfloat16_rn(u));
-      hs[(size_t)pair * F + f] = __float2bfloat16_rn(silu_f(g) * u);
+      const float y = act == ACT_RELU2 ? fmaxf(g, 0.f) * fmaxf(g, 0.f) : (act == ACT_GEGLU ? gelu_tanh_f(g) : silu_f(g)) * u;
+      hs[(size_t)pair * F + f] = __float2bfloat16_rn(y);
     }
   }
 }
@@ -698,9 +710,11 @@ EXO_API long exo_moe_plan_ints(int E, int max_tiles) { return 3L * E + 1 + 4L * 
 // form [E, 2F/128, H/64, 8448] / [E, ceil(H/128), F/64, 8448]; 0 = bf16 weights.
 EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const void* w_down, const void* weights,
                                     const void* ids, void* out, void* scratch, void* pos, void* xs, void* hs, void* ys, int T,
-                                    int k, int H, int F, int E, int expert_offset, int scale_kind, int tile_rows, int f16_operands, cudaStream_t st) {
+                                    int k, int H, int F, int E, int expert_offset, int scale_kind, int tile_rows, int f16_operands,
+                                    int act, cudaStream_t st) {
   const int f16 = (scale_kind && f16_operands) ? 1 : 0;
   if (T <= 0) return 0;
+  if (act < 0 || act > ACT_RELU2 || (act == ACT_RELU2 && scale_kind)) return -2;     // non-gated experts: bf16 weights only
   if (E > 1024 || H % 8 || F % 8 || H < BK || F < BK) return -2;
   if (scale_kind && (H % 64 || F % 128)) return -2;      // whole K tiles; gate and up halves on tile boundaries
   int* err = exo_tc_err_ptr();
@@ -726,21 +740,25 @@ EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const 
   EXO_CHECK_LAUNCH();
   const CUtensorMap* t_xs = exo_tmap_2d_bf16(xs, P, H, bn);
   // fp8: the weights are not read through a tensor map (the activations' map stands in for the unused argument)
-  const CUtensorMap* t_wgu = scale_kind ? t_xs : exo_tmap_2d_bf16(w_gate_up, (uint64_t)E * 2 * F, H, BM);
+  const int up_rows = act == ACT_RELU2 ? F : 2 * F;          // rows of the first projection per expert
+  const CUtensorMap* t_wgu = scale_kind ? t_xs : exo_tmap_2d_bf16(w_gate_up, (uint64_t)E * up_rows, H, BM);
   const CUtensorMap* t_wd = scale_kind ? t_xs : exo_tmap_2d_bf16(w_down, (uint64_t)E * H, F, BM);
   const CUtensorMap* t_hs = exo_tmap_2d_bf16(hs, P, F, bn);
   if (!t_wgu || !t_xs || !t_wd || !t_hs) return -5;
   GroupedParams g;
   g.plan = plan; g.err = err;
-  g.rows_w = 2 * F; g.n_out = F; g.K = H; g.out = (__nv_bfloat16*)hs;
+  g.rows_w = up_rows; g.n_out = F; g.K = H; g.out = (__nv_bfloat16*)hs;
   g.scale_kind = scale_kind;
   g.f16 = f16; g.out_f16 = f16;
+  g.act = act;
   g.tiles = scale_kind ? (const uint8_t*)w_gate_up : nullptr;
-  g.nt = 2 * F / BM; g.kt = H / BK;
-  int rc = grouped_dispatch<true>(bn, t_wgu, t_xs, g, (F + BM - 1) / BM, max_tiles, st);
+  g.nt = up_rows / BM; g.kt = H / BK;
+  int rc = act == ACT_RELU2 ? grouped_dispatch<false>(bn, t_wgu, t_xs, g, (F + BM - 1) / BM, max_tiles, st)
+                            : grouped_dispatch<true>(bn, t_wgu, t_xs, g, (F + BM - 1) / BM, max_tiles, st);
   if (rc) return rc;
   g.rows_w = H; g.n_out = H; g.K = F; g.out = (__nv_bfloat16*)ys;
   g.out_f16 = 0;
+  g.act = ACT_SWIGLU;
   g.tiles = scale_kind ? (const uint8_t*)w_down : nullptr;
   g.nt = (H + BM - 1) / BM; g.kt = F / BK;
   rc = grouped_dispatch<false>(bn, t_wd, t_hs, g, (H + BM - 1) / BM, max_tiles, st);
@@ -753,9 +771,9 @@ EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const 
 
 // The same block for a handful of tokens: two grouped GEMV kernels, no plan.  `hs` is [T*k, F].
 EXO_API int exo_moe_experts_gemv(const void* x, const void* w_gate_up, const void* w_down, const void* weights, const void* ids,
-                                 void* out, void* hs, int T, int k, int H, int F, int E, int expert_offset, cudaStream_t st) {
+                                 void* out, void* hs, int T, int k, int H, int F, int E, int expert_offset, int act, cudaStream_t st) {
   if (T <= 0) return 0;
-  if (H % 8 || F % 8) return -2;
+  if (H % 8 || F % 8 || act < 0 || act > ACT_RELU2) return -2;
   const size_t sm1 = (size_t)H * 2, sm2 = (size_t)k * F * 2;
   if (sm1 > 200 * 1024 || sm2 > 200 * 1024) return -2;
   static bool attr_set = false;
@@ -766,7 +784,7 @@ EXO_API int exo_moe_experts_gemv(const void* x, const void* w_gate_up, const voi
     attr_set = true;
   }
   moe_gemv_gate_up_kernel<<<dim3((F + GV_ROWS - 1) / GV_ROWS, T * k), GV_THREADS, sm1, st>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate_up, (const int*)ids, k, H, F, expert_offset, E, (__nv_bfloat16*)hs);
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate_up, (const int*)ids, k, H, F, expert_offset, E, act, (__nv_bfloat16*)hs);
   moe_gemv_down_kernel<<<dim3((H + GV_ROWS - 1) / GV_ROWS, T), GV_THREADS, sm2, st>>>(
       (const __nv_bfloat16*)hs, (const __nv_bfloat16*)w_down, (const int*)ids, (const float*)weights, k, H, F, expert_offset, E,
       (__nv_bfloat16*)out);

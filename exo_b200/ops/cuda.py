@@ -96,8 +96,8 @@ class _Sig:
     exo_moe_tile_rows = (_i, [_i, _i])
     exo_moe_max_tiles = (_i, [_i, _i, _i])
     exo_moe_plan_ints = (_l, [_i, _i])
-    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p])
-    exo_moe_experts_gemv = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
+    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p])
+    exo_moe_experts_gemv = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p])
 
 
 def _st() -> int:
@@ -805,17 +805,23 @@ def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling
     return w, ids
 
 
-def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None):
+MOE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+
+
+def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None, act="silu"):
+    """``act``: ``silu`` / ``gelu_tanh`` (gated: ``w_gate_up [E, 2F, H]``) or ``relu2`` (not gated: ``w_gate_up [E, F, H]``)."""
     T, H = x.shape
     E, F2, _ = w_gate_up.shape
-    F, k = F2 // 2, ids.shape[1]
+    F, k = (F2 if act == "relu2" else F2 // 2), ids.shape[1]
     fp8 = isinstance(w_gate_up, Fp8Weight)
+    if fp8 and act != "silu":
+        raise KernelError("block-scaled fp8 experts are built for SwiGLU only")
     ok = (use_moe_kernels and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and H % 8 == 0 and F % 8 == 0
           and H >= 64 and F >= 64 and E <= 1024)
     if fp8:
         ok = ok and isinstance(w_down, Fp8Weight) and H % 64 == 0 and F % 128 == 0
     if not ok:
-        return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset)
+        return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, act)
     x, ids = x.contiguous(), ids.contiguous().to(torch.int32)
     weights = weights.contiguous().float()
     out = torch.empty(T, H, dtype=x.dtype, device=x.device)
@@ -824,7 +830,7 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_t
     if not fp8 and T <= MOE_GEMV_MAX_TOKENS and H * 2 <= 200 * 1024 and k * F * 2 <= 200 * 1024:
         hs = torch.empty(P, F, dtype=x.dtype, device=x.device)
         _chk(lib.exo_moe_experts_gemv(_ptr(x), _ptr(w_gate_up), _ptr(w_down), _ptr(weights), _ptr(ids), _ptr(out), _ptr(hs),
-                                      T, k, H, F, E, expert_offset, _st()), "moe_experts_gemv")
+                                      T, k, H, F, E, expert_offset, MOE_ACTS[act], _st()), "moe_experts_gemv")
         _count(2)
         return out
     if (fp8 and use_moe_gemv_fp8 and T <= MOE_GEMV_MAX_TOKENS and -(-H // 64) * 128 <= 200 * 1024
@@ -853,6 +859,6 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_t
         kind, wgu, wd = 0, w_gate_up.contiguous(), w_down.contiguous()
     _chk(lib.exo_moe_experts_grouped(_ptr(x), _ptr(wgu), _ptr(wd), _ptr(weights), _ptr(ids), _ptr(out),
                                      _ptr(scratch), _ptr(pos), _ptr(xs), _ptr(hs), _ptr(ys), T, k, H, F, E, expert_offset,
-                                     kind, bn, int(fp8_f16_operands), _st()), "moe_experts_grouped")
+                                     kind, bn, int(fp8_f16_operands), MOE_ACTS[act], _st()), "moe_experts_grouped")
     _count(7)
     return out

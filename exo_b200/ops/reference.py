@@ -258,8 +258,9 @@ def moe_route(logits: torch.Tensor, top_k: int, kind: str = "softmax", norm_topk
 
 
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, weights: torch.Tensor,
-                ids: torch.Tensor, expert_offset: int = 0) -> torch.Tensor:
-    """Weighted sum of SwiGLU experts: ``w_gate_up [E, 2F, H]``, ``w_down [E, H, F]``.
+                ids: torch.Tensor, expert_offset: int = 0, act: str = "silu") -> torch.Tensor:
+    """Weighted sum of experts: ``w_gate_up [E, 2F, H]``, ``w_down [E, H, F]``; ``act`` ``silu`` (SwiGLU), ``gelu_tanh``
+    (GeGLU) or ``relu2`` (``w_gate_up [E, F, H]``, no gate: ``down(relu(up x)^2)``).
 
     Only experts ``expert_offset <= id < expert_offset+E`` are evaluated (the caller's local
     shard under expert parallelism); others contribute zero.
@@ -271,7 +272,8 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         tok, slot = torch.where(ids == e + expert_offset)
         if tok.numel() == 0:
             continue
-        h = swiglu(linear(x[tok], w_gate_up[e]))
+        pre = linear(x[tok], w_gate_up[e])
+        h = swiglu(pre) if act == "silu" else geglu(pre) if act == "gelu_tanh" else torch.relu(pre.float()).pow(2).to(pre.dtype)
         y = linear(h, w_down[e]).float()
         out.index_add_(0, tok, y * weights[tok, slot][:, None])
     return out.to(x.dtype)
@@ -501,17 +503,3 @@ def mamba2(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor | None
     yg = y.reshape(T, groups, gsize)
     yg = yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + eps)
     return (yg.reshape(T, width) * norm_w.float()).to(proj.dtype)
-
-
-def relu2_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor,
-                  expert_offset: int = 0) -> torch.Tensor:
-    """Weighted sum of NON-gated experts ``down(relu(up(x))^2)`` (Nemotron-H): ``w_up [E, F, H]``, ``w_down [E, H, F]``."""
-    T, H = x.shape
-    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
-    for e in range(w_up.shape[0]):
-        tok, slot = torch.where(ids == e + expert_offset)
-        if tok.numel() == 0:
-            continue
-        h = torch.relu(linear(x[tok], w_up[e]).float()).pow(2).to(x.dtype)
-        out.index_add_(0, tok, linear(h, w_down[e]).float() * weights[tok, slot][:, None])
-    return out.to(x.dtype)

@@ -99,6 +99,26 @@ def test_hybrid_linear_attention_model_on_gpu_matches_oracle_and_graphs():
     assert outs[0] == outs[1] and all(len(x) == 12 for x in outs[0])
 
 
+def test_nemotron_h_bf16_graphs_equal_eager():
+    """bf16 Nemotron-H-shaped model: the decode step (Mamba-2 kernels, relu^2 experts on the grouped expert kernels) under
+    CUDA graphs gives the tokens of the eager run."""
+    cfg = preset("tiny-nemotron-h")
+    cfg.dtype = "bf16"
+    w = build_weights(cfg, ShardSpec(), RandomSource(seed=0, std=0.05, dtype=torch.bfloat16), device="cuda")
+    prompts = [oracle_prompt(n, cfg.vocab, seed=n).tolist() for n in (50, 31, 77)]
+    outs = []
+    for graphs in (False, True):
+        eng = Engine(cfg, w, n_blocks=128, device="cuda", use_graphs=graphs, max_seqs=4)
+        ids = [eng.submit(q, SamplingParams(max_tokens=12, **GREEDY)) for q in prompts]
+        got = {i: [] for i in ids}
+        while eng.has_work:
+            for o in eng.step():
+                if o.token is not None:
+                    got[o.req_id].append(o.token)
+        outs.append([got[i] for i in ids])
+    assert outs[0] == outs[1] and all(len(x) == 12 for x in outs[0])
+
+
 def test_nemotron_h_on_gpu_matches_the_cpu_engine():
     """Nemotron-H-shaped model (Mamba-2 layers on the state-space kernels, attention without positions, relu^2 MLP and
     experts): fp32 on the GPU reproduces the CPU engine's tokens with a chunked prompt and two sequences in flight."""

@@ -381,6 +381,25 @@ def test_moe_experts(K, T, E, k, H, F, offset, E_all):
     assert torch.equal(out, K.moe_experts(x, wgu, wd, w, ids, offset))
 
 
+@pytest.mark.parametrize("act", ["gelu_tanh", "relu2"])
+@pytest.mark.parametrize("T,E,k,H,F,offset,E_all", [(2, 8, 2, 256, 128, 0, 8), (3, 16, 4, 512, 192, 16, 64),
+                                                     (300, 16, 8, 512, 384, 32, 64), (2048, 4, 2, 256, 320, 0, 4)])
+def test_moe_experts_other_activations(K, act, T, E, k, H, F, offset, E_all):
+    """GeGLU experts (Gemma-4) and non-gated relu^2 experts (Nemotron-H: one up projection of F rows) on the grouped GEMV
+    and the grouped tcgen05 GEMM paths."""
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    rows = F if act == "relu2" else 2 * F
+    wup = (torch.randn(E, rows, H, device="cuda", generator=g) / math.sqrt(H)).bfloat16()
+    wd = (torch.randn(E, H, F, device="cuda", generator=g) / math.sqrt(F)).bfloat16()
+    logits = torch.randn(T, E_all, device="cuda", generator=g)
+    w, ids = ref.moe_route(logits, k, "softmax", True)
+    out = K.moe_experts(x, wup, wd, w, ids, offset, None, act)
+    want = ref.moe_experts(x, wup, wd, w, ids, offset, act)
+    assert K.load().exo_gemm_last_error() == 0
+    close(out, want, 2e-2, 2e-2)
+
+
 @pytest.mark.parametrize("kind", ["mxfp8", "dsfp8"])
 @pytest.mark.parametrize("M,N,K_", [(1, 256, 256), (5, 384, 1024), (32, 1000, 4096), (200, 512, 96), (300, 640, 2048)])
 def test_gemm_fp8_weights(K, kind, M, N, K_):
