@@ -127,7 +127,7 @@ def test_nemotron_h_on_gpu_matches_the_cpu_engine():
     outs = []
     for dev in ("cpu", "cuda"):
         w = build_weights(cfg, ShardSpec(), RandomSource(seed=0, std=0.05), device=dev)
-        eng = Engine(cfg, w, n_blocks=64, device=dev, prefill_chunk=32, max_seqs=4)
+        eng = Engine(cfg, w, n_blocks=64, device=dev, prefill_chunk=32, max_seqs=4, use_graphs=False)     # fp32 experts: PyTorch ops
         ids = [eng.submit(q, SamplingParams(max_tokens=8, **GREEDY)) for q in prompts]
         got = {i: [] for i in ids}
         while eng.has_work:
