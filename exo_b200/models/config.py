@@ -253,7 +253,9 @@ class ModelConfig:
         # blocks (MLA + sigmoid-routed experts); GLM-5 is the DeepSeek-V3.2 block, whose sparse-attention indexer is not
         # used (every key is attended, which is what the indexer selects from)
         family = {"llama": "llama", "mistral": "llama", "ministral": "llama", "ministral3": "llama", "mistral3": "llama",
-                  "qwen2": "llama", "qwen3": "qwen3",
+                  "qwen2": "llama", "qwen3": "qwen3", "qwen2_vl": "llama", "qwen2_vl_text": "llama", "qwen2_5_vl": "llama",
+                  "qwen2_5_vl_text": "llama", "qwen3_vl": "qwen3", "qwen3_vl_text": "qwen3", "qwen3_vl_moe": "qwen3_moe",
+                  "qwen3_vl_moe_text": "qwen3_moe", "kimi_vl": "deepseek_v3", "kimi_k25": "deepseek_v3",
                   "qwen3_moe": "qwen3_moe", "deepseek_v3": "deepseek_v3", "deepseek_v32": "deepseek_v3",
                   "deepseek_v2": "deepseek_v3", "kimi_k2": "deepseek_v3", "glm4_moe_lite": "deepseek_v3",
                   "glm_moe_dsa": "deepseek_v3",
@@ -277,7 +279,7 @@ class ModelConfig:
             rms_eps=float(g("rms_norm_eps", default=1e-5)), rope=rope,
             tie_embeddings=bool(g("tie_word_embeddings", default=False)),
             qk_norm=family in ("qwen3", "qwen3_moe", "qwen3_next") or (family == "glm4_moe" and bool(g("use_qk_norm", default=False))),
-            attn_bias=bool(g("attention_bias", default=mt == "qwen2")),
+            attn_bias=bool(g("attention_bias", default=mt in ("qwen2", "qwen2_vl", "qwen2_vl_text", "qwen2_5_vl", "qwen2_5_vl_text"))),
             max_position=int(g("max_position_embeddings", default=131072)),
             eos_token_ids=tuple(eos),
             sliding_window=int(g("sliding_window", default=0) or 0) if mt == "gpt_oss" else 0,

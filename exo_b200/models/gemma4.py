@@ -30,7 +30,7 @@ from .. import ops
 from ..ops import reference as ref
 from .config import ModelConfig
 from .transformer import Decoder, KVPool, StepInputs, resolve
-from .weights import (ModelWeights, ShardSpec, TensorSource, _DTYPES, _cols, _rows, expert_range, vocab_shard)
+from .weights import (ModelWeights, ShardSpec, TensorSource, _DTYPES, _cols, _rows, expert_range, text_model_root, vocab_shard)
 
 
 @dataclass
@@ -85,9 +85,7 @@ def build_gemma4_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, d
     dev = torch.device(device)
     r, n = spec.tp_rank, spec.tp_size
     H, L = cfg.hidden, cfg.n_layers
-    root = cfg.weight_prefix
-    if root != "model." and not src.has(root + "embed_tokens.weight") and src.has("model.embed_tokens.weight"):
-        root = "model."
+    root = text_model_root(cfg, src)
 
     def fin(t: torch.Tensor, dtype: torch.dtype | None = None) -> torch.Tensor:
         return t.to(device=dev, dtype=dtype or dt).contiguous()

@@ -25,7 +25,7 @@ from ..ops import reference as ref
 from .config import ModelConfig
 from .transformer import Decoder, KVPool, StepInputs, resolve
 from .weights import (ModelWeights, ShardSpec, TensorSource, _DTYPES, _cols, _rows, expert_range, kv_head_range, linear_heads,
-                      vocab_shard)
+                      text_model_root, vocab_shard)
 
 
 @dataclass
@@ -61,9 +61,7 @@ def build_nemotron_h_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSourc
     dev = torch.device(device)
     r, n = spec.tp_rank, spec.tp_size
     H = cfg.hidden
-    root = cfg.weight_prefix
-    if not src.has(root + "embeddings.weight") and src.has("model.embeddings.weight"):
-        root = "model."
+    root = text_model_root(cfg, src, "embeddings.weight")
 
     def fin(t: torch.Tensor, dtype: torch.dtype | None = None) -> torch.Tensor:
         return t.to(device=dev, dtype=dtype or dt).contiguous()

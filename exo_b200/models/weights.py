@@ -321,6 +321,16 @@ class ModelWeights:
                     yield from v.storage()
 
 
+def text_model_root(cfg: ModelConfig, src: "TensorSource", embed: str = "embed_tokens.weight") -> str:
+    """Prefix of the decoder's tensors in a checkpoint.  Multimodal repositories wrap the text model (``model.language_model.``
+    in the Qwen-VL / Gemma layouts, ``language_model.model.`` in the Kimi-VL / LLaVA ones), and text-only exports of such
+    families drop the wrapper again: the configured prefix is tried first, then the known ones."""
+    for root in dict.fromkeys((cfg.weight_prefix, "model.", "model.language_model.", "language_model.model.", "backbone.")):
+        if src.has(root + embed):
+            return root
+    return cfg.weight_prefix
+
+
 def moe_names(cfg: ModelConfig) -> dict[str, str]:
     """Checkpoint tensor names of a sparse block: Mixtral keeps ``block_sparse_moe.experts.N.w1 / w3 / w2`` (gate, up,
     down); the DeepSeek / Qwen / GLM families ``mlp.experts.N.gate_proj / up_proj / down_proj``."""
@@ -426,9 +436,7 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
 
     layers: dict[int, LayerWeights] = {}
     lrange = spec.layers(cfg)
-    root = cfg.weight_prefix
-    if root != "model." and not src.has(root + "embed_tokens.weight") and src.has("model.embed_tokens.weight"):
-        root = "model."                      # a text-only export of a checkpoint family that usually wraps the text model
+    root = text_model_root(cfg, src)
     # hybrid models: hub checkpoints keep RMSNorm weights zero-centred and the convolution as [C, 1, taps]; MLX
     # conversions have already added the 1 and moved the tap axis
     hf_form = True
@@ -532,7 +540,9 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
         embed = fin(src.get(root + "embed_tokens.weight", (cfg.vocab, H)))
     if spec.is_last_stage:
         final_norm = norm(root + "norm.weight", (H,))
-        name = root + "embed_tokens.weight" if cfg.tie_embeddings or not src.has("lm_head.weight") else "lm_head.weight"
+        head = next((h for h in ("lm_head.weight", root[:-len("model.")] + "lm_head.weight") if src.has(h)), None) \
+            if root.endswith("model.") else ("lm_head.weight" if src.has("lm_head.weight") else None)
+        name = root + "embed_tokens.weight" if cfg.tie_embeddings or head is None else head
         full = src.get(name, (cfg.vocab, H))
         vpad = vocab_shard(cfg.vocab, n)
         lm_head = fin(full[min(r * vpad, cfg.vocab):min((r + 1) * vpad, cfg.vocab)])

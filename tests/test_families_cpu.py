@@ -151,3 +151,30 @@ def test_checkpoint_under_family_names_loads_and_matches_oracle(name, tmp_path):
     eng = Engine(cfg, w, n_blocks=16, device="cpu")
     got = eng.generate(prompt, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
     assert got == want
+
+
+@pytest.mark.parametrize("wrapper,prefix", [("qwen3_vl", "model.language_model."), ("kimi_vl", "language_model.model.")])
+def test_text_model_inside_a_multimodal_checkpoint_is_found(wrapper, prefix, tmp_path):
+    """Multimodal repositories keep the decoder under a wrapper prefix (and other tensors beside it): the loader finds the
+    text model whichever of the known layouts the repository uses."""
+    inner = {**BASE, "model_type": "qwen3_vl_text"} if wrapper == "qwen3_vl" else \
+        {**BASE, "model_type": "deepseek_v3", "n_routed_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 64,
+         "n_shared_experts": 1, "first_k_dense_replace": 1, "q_lora_rank": 64, "kv_lora_rank": 32, "qk_nope_head_dim": 16,
+         "qk_rope_head_dim": 16, "v_head_dim": 16, "norm_topk_prob": True, "routed_scaling_factor": 1.0, "n_group": 1, "topk_group": 1}
+    d = tmp_path / wrapper
+    cfg = write_config(d, {"model_type": wrapper, "text_config": inner})
+    cfg.dtype = "fp32"
+    assert cfg.family == ("qwen3" if wrapper == "qwen3_vl" else "deepseek_v3")
+    rec = Recorder(seed=4, std=0.05)
+    flat = ModelConfig(**{**cfg.to_dict(), "rope": cfg.rope, "weight_prefix": "model."})
+    oracle = OracleModel(flat, rec)
+    prompt_t = torch.randint(0, cfg.vocab, (15,), generator=torch.Generator().manual_seed(2))
+    want = oracle.greedy(prompt_t, 5)
+    build_weights(flat, ShardSpec(), rec, device="cpu")
+    tensors = {(prefix + k[len("model."):] if k.startswith("model.") else ("language_model." + k if prefix.startswith("language") else k)): v.contiguous()
+               for k, v in rec.seen.items()}
+    tensors["vision_tower.patch_embed.weight"] = torch.zeros(4, 4)
+    write_safetensors(d / "model.safetensors", tensors)
+    w = build_weights(cfg, ShardSpec(), SafetensorsSource(d, dtype=torch.float32), device="cpu")
+    eng = Engine(cfg, w, n_blocks=16, device="cpu")
+    assert eng.generate([int(t) for t in prompt_t], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)) == want
