@@ -104,6 +104,10 @@ class Engine:
 
     def export_kv(self, blocks: list[int], n_tokens: int) -> list[tuple[torch.Tensor, torch.Tensor | None]]:
         """KV of the first ``n_tokens`` positions held in ``blocks``, per local layer: ``[n_tokens, heads, dim]``."""
+        if self.cfg.has_linear_layers:
+            # the paged cache is only part of such a model's memory of a prompt: the recurrent layers' state is not
+            # addressed by position and is not exported, so another instance could not continue from this KV
+            raise NotImplementedError(f"{self.cfg.name}: models with recurrent layers cannot hand their prompt state to another instance")
         slots = self._slots(blocks, n_tokens)
         out = []
         for i in self.exe.spec.layers(self.cfg):

@@ -212,7 +212,8 @@ class ServingEngine(Engine):
     # ---- disaggregation: decode side ----
     def _want_remote_prefill(self, p, ids: list[int]) -> bool:
         return (bool(p.prefill_endpoint) and len(ids) > constants.REMOTE_PREFILL_MIN_TOKENS
-                and self.te.exe.spec.tp_size == 1 and self.te.exe.spec.pp_size == 1 and not self.cfg.mla)
+                and self.te.exe.spec.tp_size == 1 and self.te.exe.spec.pp_size == 1 and not self.cfg.mla
+                and not self.cfg.has_linear_layers and self.cfg.family != "gemma4")     # position-addressed, uniform KV only
 
     def _admit_remote(self) -> None:
         for rid, f in list(self.remote.items()):
