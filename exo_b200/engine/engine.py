@@ -51,6 +51,9 @@ class Engine:
         self.exe = Executor(cfg, weights, spec, comm, n_blocks=n_blocks, block_size=block_size,
                             max_blocks_per_seq=mbs, max_tokens_per_step=max(prefill_chunk, max_seqs),
                             max_seqs=max_seqs, device=device, use_graphs=use_graphs, pipe=pipe)
+        if self.exe.kv.n_snapshots:         # hybrid model: prefixes are reusable up to blocks with a state snapshot
+            self.alloc.enable_snapshots(self.exe.kv.n_snapshots)
+            self.sched.state_snapshots = True
         self.seqs: dict[str, Sequence] = {}
         self.plan_sink = plan_sink  # callable(StepPlan): broadcasts the plan to follower ranks
         self.n_steps = 0
@@ -65,9 +68,10 @@ class Engine:
         if not prompt:
             raise ValueError("empty prompt")
         if self.cfg.has_linear_layers:
-            # a gated-delta-rule layer's state summarises the WHOLE prefix and exists only at the sequence's current
-            # end: cached blocks, or KV computed elsewhere, carry no such state, so the prompt is always computed here
-            use_prefix_cache, kv_prefill = False, None
+            # a recurrent layer's state summarises the WHOLE prefix: KV computed elsewhere carries no such state, and
+            # cached blocks are reusable only up to one whose end-of-block state was snapshotted (the scheduler's rule)
+            kv_prefill = None
+            use_prefix_cache = use_prefix_cache and self.sched.state_snapshots
         s = Sequence(rid, list(prompt), params or SamplingParams(), media=media, use_prefix_cache=use_prefix_cache)
         s.embeds = list(embeds) if embeds else None
         if kv_prefill is not None:

@@ -17,9 +17,9 @@ import torch
 
 from .. import ops
 from ..models.config import ModelConfig
-from ..models.transformer import Decoder, KVPool, StepInputs, make_decoder, make_kv_pool
+from ..models.transformer import Decoder, KVPool, StepInputs, default_state_snapshots, make_decoder, make_kv_pool
 from ..models.weights import ModelWeights, ShardSpec
-from .plan import HEADER, PlanLayout, StepPlan, bucket, FLAG_ALL_GREEDY, FLAG_EAGER, FLAG_NO_SAMPLE
+from .plan import HEADER, PlanLayout, StepPlan, bucket, FLAG_ALL_GREEDY, FLAG_EAGER, FLAG_NO_SAMPLE, STATE_RESTORE, STATE_SAVE
 
 DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 
@@ -28,13 +28,14 @@ class Executor:
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None = None, comm=None,
                  n_blocks: int = 256, block_size: int = 16, max_blocks_per_seq: int = 256,
                  max_tokens_per_step: int = 4096, max_seqs: int = 64, device: str | torch.device = "cpu",
-                 use_graphs: bool | None = None, pipe=None):
+                 use_graphs: bool | None = None, pipe=None, n_snapshots: int | None = None):
         self.cfg = cfg
         self.pipe = pipe if (pipe is not None and pipe.pp_size > 1) else None
         self.spec = spec or ShardSpec()
         self.device = torch.device(device)
         self.model = make_decoder(cfg, weights, self.spec, comm)
-        self.kv = make_kv_pool(cfg, self.spec, n_blocks, block_size, self.device, max_seqs=max_seqs)
+        self.kv = make_kv_pool(cfg, self.spec, n_blocks, block_size, self.device, max_seqs=max_seqs,
+                               n_snapshots=default_state_snapshots(cfg, max_seqs) if n_snapshots is None else n_snapshots)
         self.block_size, self.max_blocks = block_size, max_blocks_per_seq
         self.max_T, self.max_B = max_tokens_per_step, max_seqs
         words = PlanLayout(max(self.max_T, self.max_B), self.max_B, self.max_blocks).words
@@ -160,7 +161,19 @@ class Executor:
 
     # ------------------------------------------------------------------ step
     def run(self, plan: StepPlan, logits_processor=None) -> torch.Tensor:
-        """Execute one step; returns the sampled ids ``[n_seqs]`` on device (int32)."""
+        """Execute one step; returns the sampled ids ``[n_seqs]`` on device (int32).  The plan's state instructions
+        (hybrid models: recurrent state copied from a prefix-cache snapshot into a sequence's seat before the step, or
+        from a seat into a snapshot after it) are stream-ordered device copies around the step's kernels."""
+        for kind, seat, snap in plan.state_ops:
+            if kind == STATE_RESTORE:
+                self.kv.restore_state(seat, snap)
+        out = self._run_step(plan, logits_processor)
+        for kind, seat, snap in plan.state_ops:
+            if kind == STATE_SAVE:
+                self.kv.save_state(seat, snap)
+        return out
+
+    def _run_step(self, plan: StepPlan, logits_processor=None) -> torch.Tensor:
         decode = plan.is_decode
         if decode:
             bB = bucket(plan.n_seqs, DECODE_BUCKETS)

@@ -31,6 +31,10 @@ class BlockAllocator:
         self.lru: OrderedDict[int, None] = OrderedDict()  # cached, unreferenced blocks (oldest first)
         self.hits = 0
         self.queries = 0
+        # recurrent-state snapshots of hybrid models: the state of a sequence at the END of a cached block, keyed by that
+        # block's chain hash (a prefix can only be reused up to a block that has one); least recently used first
+        self.snap_of: OrderedDict[bytes, int] = OrderedDict()
+        self.free_snaps: list[int] = []
 
     # ---- allocation ----
     @property
@@ -44,6 +48,7 @@ class BlockAllocator:
             b, _ = self.lru.popitem(last=False)
             h = self.hash_of.pop(b)
             del self.by_hash[h]
+            self._drop_snapshot(h)
         else:
             raise OutOfBlocks("KV pool exhausted")
         self.ref[b] = 1
@@ -121,6 +126,38 @@ class BlockAllocator:
         for b, h in list(self.hash_of.items()):
             del self.by_hash[h]
             del self.hash_of[b]
+        for h in list(self.snap_of):
+            self._drop_snapshot(h)
+
+    # ---- recurrent-state snapshots ----
+    def enable_snapshots(self, n: int) -> None:
+        self.free_snaps = list(range(n - 1, -1, -1))
+
+    def _drop_snapshot(self, h: bytes) -> None:
+        sid = self.snap_of.pop(h, None)
+        if sid is not None:
+            self.free_snaps.append(sid)
+
+    def snapshot_at(self, h: bytes) -> int | None:
+        """Snapshot holding the state at the end of the block with chain hash ``h`` (refreshes its age)."""
+        sid = self.snap_of.get(h)
+        if sid is not None:
+            self.snap_of.move_to_end(h)
+        return sid
+
+    def reserve_snapshot(self, h: bytes) -> int | None:
+        """A snapshot id for the state at the end of block ``h``: ``None`` if one exists already or none can be had;
+        the least recently used snapshot gives way when the pool is full."""
+        if h in self.snap_of:
+            return None
+        if self.free_snaps:
+            sid = self.free_snaps.pop()
+        elif self.snap_of:
+            _, sid = self.snap_of.popitem(last=False)
+        else:
+            return None
+        self.snap_of[h] = sid
+        return sid
 
     def usage(self) -> float:
         return 1.0 - len(self.free) / max(1, self.n_blocks)
@@ -177,6 +214,7 @@ class Sequence:
     rng_state: int = 0
     final_blocks: list[int] = field(default_factory=list)   # block ids at the moment the sequence finished
     state_slot: int = 0          # seat of the sequence's recurrent state while it is running (0: none)
+    restore_snap: int | None = None   # snapshot to copy into the seat before the sequence's first step (prefix reuse)
 
     @property
     def tokens(self) -> list[int]:

@@ -9,7 +9,9 @@ broadcast of a packed int32 buffer.
 
 Packed layout (int32 words): ``[T, B, R, max_q_len, flags, bucket_T, bucket_B, max_blocks]``
 then ``tokens[T'] positions[T'] slots[T'] cu_q[B'+1] seq_lens[B'] logit_rows[B']
-top_k[B'] temperature[B'] top_p[B'] min_p[B'] uniform[B'] prev_rows[B'] state_slots[B'] block_tables[B'*max_blocks]`` where
+top_k[B'] temperature[B'] top_p[B'] min_p[B'] uniform[B'] prev_rows[B'] state_slots[B'] block_tables[B'*max_blocks]
+state_ops[1 + 3*MAX_STATE_OPS]`` (count, then ``kind, seat, snapshot`` triples: host-side instructions to copy recurrent state
+between sequence seats and prefix-cache snapshots around the step) where
 ``T'``/``B'`` are the padded (bucket) sizes, floats are bit-cast.  Padding rows point at the
 reserved scratch block 0 so that a graph captured for the bucket runs unchanged.
 """
@@ -24,6 +26,8 @@ FLAG_TOKENS_FROM_PREV = 1  # decode: take input tokens from the previous step's 
 FLAG_ALL_GREEDY = 2
 FLAG_EAGER = 4             # the leader runs this step outside its CUDA graphs (logits processors): followers do the same
 FLAG_NO_SAMPLE = 8         # every row is a prompt chunk that stops short of its sequence's end: no logits, no ids, no read-back
+MAX_STATE_OPS = 32
+STATE_RESTORE, STATE_SAVE = 1, 2   # snapshot -> seat before the step's kernels; seat -> snapshot after them
 
 
 @dataclass
@@ -50,6 +54,7 @@ class PlanLayout:
         self.state_slots = o; o += self.B
         o = (o + 3) // 4 * 4  # keep the table 16-byte aligned
         self.block_tables = o; o += self.B * self.max_blocks
+        self.state_ops = o; o += 1 + 3 * MAX_STATE_OPS
         self.words = o
 
 
@@ -75,6 +80,7 @@ class StepPlan:
     block_tables: np.ndarray  # [B, max_blocks] int32
     req_ids: tuple[str, ...] = ()
     state_slots: np.ndarray | None = None   # [B] int32 seat of each sequence's recurrent state (0: none / padding rows)
+    state_ops: tuple[tuple[int, int, int], ...] = ()   # (STATE_RESTORE | STATE_SAVE, seat, snapshot)
 
     @property
     def is_decode(self) -> bool:
@@ -114,6 +120,10 @@ class StepPlan:
             out[L.state_slots:L.state_slots + B] = self.state_slots
         bt = out[L.block_tables:L.block_tables + bucket_B * max_blocks].reshape(bucket_B, max_blocks)
         bt[:B, :self.block_tables.shape[1]] = self.block_tables
+        assert len(self.state_ops) <= MAX_STATE_OPS
+        out[L.state_ops] = len(self.state_ops)
+        for j, op in enumerate(self.state_ops):
+            out[L.state_ops + 1 + 3 * j:L.state_ops + 4 + 3 * j] = op
         return L
 
     @staticmethod
@@ -130,7 +140,9 @@ class StepPlan:
             top_p=fv[L.top_p:L.top_p + B].copy(), min_p=fv[L.min_p:L.min_p + B].copy(),
             uniform=fv[L.uniform:L.uniform + B].copy(), prev_rows=buf[L.prev_rows:L.prev_rows + B].copy(),
             block_tables=buf[L.block_tables:L.block_tables + bB * mb].reshape(bB, mb)[:B].copy(),
-            state_slots=buf[L.state_slots:L.state_slots + B].copy())
+            state_slots=buf[L.state_slots:L.state_slots + B].copy(),
+            state_ops=tuple(tuple(int(x) for x in buf[L.state_ops + 1 + 3 * j:L.state_ops + 4 + 3 * j])
+                            for j in range(int(buf[L.state_ops]))))
 
 
 def bucket(n: int, buckets: tuple[int, ...]) -> int:

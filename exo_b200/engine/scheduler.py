@@ -17,7 +17,7 @@ from collections import deque
 import numpy as np
 
 from .kv import BlockAllocator, OutOfBlocks, Sequence
-from .plan import StepPlan, FLAG_ALL_GREEDY, FLAG_NO_SAMPLE
+from .plan import MAX_STATE_OPS, STATE_RESTORE, STATE_SAVE, StepPlan, FLAG_ALL_GREEDY, FLAG_NO_SAMPLE
 
 
 class Scheduler:
@@ -37,6 +37,9 @@ class Scheduler:
         # seats 1..max_seqs for per-sequence recurrent state (linear-attention layers); seat 0 is the scratch seat of
         # padding rows.  A sequence holds a seat exactly while it is in `running`.
         self._free_seats = list(range(max_seqs, 0, -1))
+        # models with recurrent layers: a cached prefix is only usable up to a block whose end-of-block state was
+        # snapshotted (`BlockAllocator.snap_of`); set by the engine when the model has such layers and a snapshot pool
+        self.state_snapshots = False
 
     # ---- request lifecycle ----
     def add(self, seq: Sequence) -> None:
@@ -108,10 +111,38 @@ class Scheduler:
             # never reuse the whole prompt: the last token must be recomputed to get logits
             hashes = self.alloc.block_hashes(s.tokens[:s.n_tokens - 1], s.media)
             got = self.alloc.match_prefix(hashes)
+            if self.state_snapshots:
+                # keep the longest run of cached blocks that ends in a block with a state snapshot
+                keep, snap = 0, None
+                for j in range(len(got), 0, -1):
+                    snap = self.alloc.snapshot_at(hashes[j - 1])
+                    if snap is not None:
+                        keep = j
+                        break
+                self.alloc.release_all(got[keep:])
+                got = got[:keep]
+                s.restore_snap = snap if keep else None
             s.blocks = got
             s.n_computed = s.n_cached_prefix = len(got) * bs
             s.n_published = len(got)
         return True
+
+    def _snapshot_boundary(self, s: Sequence) -> int:
+        """Token count at which a prompt's recurrent state is snapshotted: the last block boundary before the prompt's
+        final token (that token is always computed by the request itself).  0: none."""
+        if not self.state_snapshots or not s.use_prefix_cache:
+            return 0
+        bs = self.alloc.block_size
+        return ((len(s.prompt) - 1) // bs) * bs
+
+    def _chunk(self, s: Sequence, budget: int) -> int:
+        """Tokens of ``s`` to compute this step: up to the budget, and never across its snapshot boundary (the state must
+        be taken exactly there)."""
+        n = min(s.n_tokens - s.n_computed, budget)
+        b = self._snapshot_boundary(s)
+        if s.n_computed < b < s.n_computed + n:
+            n = b - s.n_computed
+        return n
 
     def _preempt_one(self, keep: Sequence) -> bool:
         """Evict the most recently admitted running sequence (recompute later)."""
@@ -120,6 +151,7 @@ class Scheduler:
                 continue
             self.alloc.release_all(victim.blocks)
             victim.blocks, victim.n_computed, victim.n_published = [], 0, 0
+            victim.restore_snap = None
             # generated tokens become part of the prompt to recompute
             self.running.remove(victim)
             self._release_seat(victim)          # its recurrent state is recomputed with its KV
@@ -154,7 +186,7 @@ class Scheduler:
         for s in list(self.running):
             if not s.in_prefill or budget <= 0:
                 continue
-            n = min(s.n_tokens - s.n_computed, budget)
+            n = self._chunk(s, budget)
             if not self._ensure_blocks(s, s.n_computed + n):
                 continue
             entries.append((s, n))
@@ -167,8 +199,7 @@ class Scheduler:
                 s.finished, s.finish_reason = True, "length"
                 continue
             self._admit(s)
-            todo = s.n_tokens - s.n_computed
-            n = min(todo, budget)
+            n = self._chunk(s, budget)
             if not self._ensure_blocks(s, s.n_computed + n):
                 if not self.running and not entries:
                     # cannot ever fit
@@ -236,7 +267,19 @@ class Scheduler:
                     uni[b] = self._uniform(s)
             bt[b, :len(blk)] = blk
             t += n
-        return StepPlan(n_tokens=T, n_seqs=B, max_q_len=max(n for _, n in entries),
+        ops: list[tuple[int, int, int]] = []
+        if self.state_snapshots:
+            for s, n in entries:
+                if s.restore_snap is not None and len(ops) < MAX_STATE_OPS:
+                    ops.append((STATE_RESTORE, s.state_slot, s.restore_snap))
+                s.restore_snap = None
+            for s, n in entries:
+                b = self._snapshot_boundary(s)
+                if b >= bs and s.n_computed < b == s.n_computed + n and s.state_slot and len(ops) < MAX_STATE_OPS:
+                    sid = self.alloc.reserve_snapshot(self.alloc.block_hashes(s.tokens[:b], s.media)[-1])
+                    if sid is not None:
+                        ops.append((STATE_SAVE, s.state_slot, sid))
+        return StepPlan(n_tokens=T, n_seqs=B, max_q_len=max(n for _, n in entries), state_ops=tuple(ops),
                         flags=(FLAG_ALL_GREEDY if all_greedy else 0) | (0 if samples else FLAG_NO_SAMPLE), tokens=tokens, positions=positions, slots=slots,
                         cu_q=cu_q, seq_lens=seq_lens, logit_rows=logit_rows, top_k=top_k, temperature=temp,
                         top_p=top_p, min_p=min_p, uniform=uni, prev_rows=np.full(B, -1, np.int32), block_tables=bt,

@@ -164,6 +164,7 @@ class Gemma4KV(KVPool):
         self.cfg, self.block_size, self.n_blocks = cfg, block_size, n_blocks
         dt = dtype or (torch.bfloat16 if cfg.dtype == "bf16" else torch.float32)
         self.layers = {}
+        self.snapshots, self.n_snapshots = {}, 0
         for i in spec.layers(cfg):
             j = cfg.kv_source_layer(i)
             if j != i and j in self.layers:

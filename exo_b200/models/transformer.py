@@ -86,10 +86,13 @@ class KVPool:
     """Paged KV storage for the layers this rank holds (block size 16 by default)."""
 
     def __init__(self, cfg: ModelConfig, spec: ShardSpec, n_blocks: int, block_size: int = 16,
-                 device: str | torch.device = "cpu", dtype: torch.dtype | None = None, max_seqs: int = 64):
+                 device: str | torch.device = "cpu", dtype: torch.dtype | None = None, max_seqs: int = 64, n_snapshots: int = 0):
         self.cfg, self.block_size, self.n_blocks = cfg, block_size, n_blocks
         dt = dtype or (torch.bfloat16 if cfg.dtype == "bf16" else torch.float32)
         self.layers: dict[int, tuple[torch.Tensor, torch.Tensor | None]] = {}
+        # prefix-cache snapshots of the recurrent layers' state: (convolution history, state) per layer, `n_snapshots` slots
+        self.snapshots: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+        self.n_snapshots = n_snapshots if cfg.has_linear_layers else 0
         _, hkv = local_heads(cfg, spec)
         for i in spec.layers(cfg):
             if cfg.block_types and cfg.block_types[i] in ("mlp", "moe"):
@@ -102,6 +105,9 @@ class KVPool:
                 conv = torch.zeros(max_seqs + 1, 2 * hk * cfg.lin_k_dim + hv * cfg.lin_v_dim, cfg.lin_conv - 1, dtype=dt, device=device)
                 rec = torch.zeros(max_seqs + 1, hv, cfg.lin_k_dim, cfg.lin_v_dim, dtype=torch.float32, device=device)
                 self.layers[i] = (conv, rec)
+                if self.n_snapshots:
+                    self.snapshots[i] = (torch.zeros(self.n_snapshots, *conv.shape[1:], dtype=dt, device=device),
+                                         torch.zeros(self.n_snapshots, *rec.shape[1:], dtype=torch.float32, device=device))
             elif cfg.mla:
                 c = torch.zeros(n_blocks, block_size, cfg.kv_lora_rank + cfg.qk_rope_dim, dtype=dt, device=device)
                 self.layers[i] = (c, None)
@@ -123,6 +129,19 @@ class KVPool:
         _, hkv = local_heads(cfg, spec)
         return n_layers * 2 * block_size * hkv * cfg.head_dim * el
 
+
+    def save_state(self, seat: int, snap: int) -> None:
+        """Copy a sequence seat's recurrent state into a snapshot slot (stream-ordered device copies)."""
+        for i, (conv_s, rec_s) in self.snapshots.items():
+            conv, rec = self.layers[i]
+            conv_s[snap].copy_(conv[seat])
+            rec_s[snap].copy_(rec[seat])
+
+    def restore_state(self, seat: int, snap: int) -> None:
+        for i, (conv_s, rec_s) in self.snapshots.items():
+            conv, rec = self.layers[i]
+            conv[seat].copy_(conv_s[snap])
+            rec[seat].copy_(rec_s[snap])
 
     @staticmethod
     def state_bytes(cfg: ModelConfig, spec: ShardSpec, max_seqs: int) -> int:
@@ -317,6 +336,12 @@ class Decoder:
         return self.comm.gather_vocab(out)[:, :self.cfg.vocab]
 
 
+def default_state_snapshots(cfg: ModelConfig, max_seqs: int) -> int:
+    """Snapshot slots for the recurrent state of a hybrid model's cached prefixes (0 for every other model).  Each slot
+    is as large as one sequence seat; every rank of an instance derives the same number from the same arguments."""
+    return max(2, min(16, max_seqs)) if cfg.has_linear_layers else 0
+
+
 def make_decoder(cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None = None, comm=None) -> Decoder:
     """The forward implementation of the model's family."""
     if cfg.family == "gemma4":
@@ -329,8 +354,8 @@ def make_decoder(cfg: ModelConfig, weights: ModelWeights, spec: ShardSpec | None
 
 
 def make_kv_pool(cfg: ModelConfig, spec: ShardSpec, n_blocks: int, block_size: int = 16, device="cpu", dtype=None,
-                 max_seqs: int = 64) -> KVPool:
+                 max_seqs: int = 64, n_snapshots: int = 0) -> KVPool:
     if cfg.family == "gemma4":
         from .gemma4 import Gemma4KV
         return Gemma4KV(cfg, spec, n_blocks, block_size, device, dtype, max_seqs)
-    return KVPool(cfg, spec, n_blocks, block_size, device, dtype, max_seqs)
+    return KVPool(cfg, spec, n_blocks, block_size, device, dtype, max_seqs, n_snapshots)

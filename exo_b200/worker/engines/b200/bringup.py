@@ -21,7 +21,7 @@ from ....engine.engine import Engine as TokenEngine
 from ....engine.executor import Executor
 from ....engine.plan import HEADER, PlanLayout, StepPlan
 from ....models.config import ModelConfig
-from ....models.transformer import KVPool
+from ....models.transformer import default_state_snapshots, KVPool
 from ....parallel.comm import PipeComm
 from ....models.weights import (RandomSource, SafetensorsSource, ShardSpec, build_weights, fast_random_weights,
                                 vocab_shard)
@@ -291,7 +291,8 @@ class B200Builder(Builder):
             free, _total = torch.cuda.mem_get_info(self.device)
             budget = int(free * constants.EXO_GPU_MEMORY_FRACTION)
             # hybrid models: the sequences' recurrent state is allocated beside the paged cache
-            budget -= KVPool.state_bytes(cfg, self.spec, max(constants.EXO_MAX_CONCURRENT_REQUESTS, 8))
+            seats = max(constants.EXO_MAX_CONCURRENT_REQUESTS, 8)
+            budget -= KVPool.state_bytes(cfg, self.spec, seats + default_state_snapshots(cfg, seats))
         else:
             budget = 256 << 20
         cap = int(os.environ.get("EXO_MAX_KV_BLOCKS", "0"))

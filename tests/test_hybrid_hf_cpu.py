@@ -101,3 +101,41 @@ def test_engine_greedy_matches_library(exported):
     eng = Engine(cfg, w, n_blocks=32, device="cpu", prefill_chunk=16)      # the prompt takes two prefill chunks
     got = eng.generate(prompt[0].tolist(), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     assert got == want
+
+
+def test_prefix_reuse_restores_the_recurrent_state(exported):
+    """A second request that shares a prompt prefix re-uses the cached blocks up to the snapshotted block boundary: its
+    recurrent layers continue from the state saved there, and the tokens equal those of an engine that computes the
+    whole prompt."""
+    from exo_b200.engine.plan import STATE_RESTORE, STATE_SAVE, StepPlan
+    _, cfg, d = exported
+    w = build_weights(cfg, ShardSpec(), SafetensorsSource(d, dtype=torch.float32), device="cpu")
+    g = torch.Generator().manual_seed(3)
+    first = torch.randint(0, cfg.vocab, (45,), generator=g).tolist()
+    second = first[:40] + torch.randint(0, cfg.vocab, (21,), generator=g).tolist()        # 40 shared tokens, then its own
+    greedy = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    fresh = Engine(cfg, w, n_blocks=32, device="cpu").generate(second, greedy)             # generate(): prefix cache off
+    eng = Engine(cfg, w, n_blocks=32, device="cpu", prefill_chunk=64)
+    assert eng.sched.state_snapshots and eng.exe.kv.n_snapshots >= 2
+    plans = []
+    eng.exe.run, run = (lambda plan, *a, **k: (plans.append(plan), run(plan, *a, **k))[1]), eng.exe.run
+    outs = {}
+    for prompt in (first, second):
+        rid = eng.submit(prompt, greedy)
+        while eng.has_work:
+            for o in eng.step():
+                if o.token is not None:
+                    outs.setdefault(o.req_id, []).append(o.token)
+        outs[rid] = outs.pop(rid)
+    ops = [op for p in plans for op in p.state_ops]
+    # the first prompt (45 tokens) is cut at 32 = the last block boundary before its final token, and saved there
+    assert [p.n_tokens for p in plans[:2]] == [32, 13] and ops[0][0] == STATE_SAVE
+    # the second re-uses those two blocks: restore, then 61 - 32 tokens of its own, cut again at its boundary (48)
+    seq2 = [p for p in plans if p.state_ops and p.state_ops[0][0] == STATE_RESTORE][0]
+    assert seq2.positions[0] == 32 and seq2.n_tokens == 16 and seq2.state_ops[0][2] == ops[0][2]
+    assert list(outs.values())[1] == fresh
+    # the instructions travel inside the packed plan (tensor-parallel followers unpack them)
+    import numpy as np
+    buf = np.zeros(4096, np.int32)
+    seq2.pack(buf, seq2.n_tokens, seq2.n_seqs, seq2.block_tables.shape[1])
+    assert StepPlan.unpack(buf).state_ops == seq2.state_ops

@@ -112,3 +112,36 @@ def test_prompt_chunks_short_of_the_end_carry_the_no_sample_flag_and_skip_the_re
     a = chunked.generate(prompt, greedy)
     assert a == whole.generate(prompt, greedy)
     assert chunked.n_steps == 3 + 4 and chunked.exe.d2h_bytes == 4 * 4 and whole.exe.d2h_bytes == 4 * 4
+
+
+def test_state_snapshots_follow_their_blocks_and_age_out():
+    """A snapshot belongs to the cached block whose end it describes: it disappears with that block, the least recently
+    used one gives way when the pool is full, and a prefix is only matched up to a block that has one."""
+    alloc = BlockAllocator(4, 16)
+    alloc.enable_snapshots(2)
+    toks = list(range(64))
+    h = alloc.block_hashes(toks)
+    blocks = [alloc.alloc() for _ in range(3)]
+    for b, hh in zip(blocks, h):
+        alloc.publish(b, hh)
+    assert alloc.reserve_snapshot(h[0]) == 0 and alloc.reserve_snapshot(h[1]) == 1
+    assert alloc.reserve_snapshot(h[0]) is None                      # exists already
+    assert alloc.snapshot_at(h[0]) == 0                              # ... and is now the most recently used
+    assert alloc.reserve_snapshot(h[2]) == 1 and alloc.snapshot_at(h[1]) is None      # the pool was full: h[1]'s gave way
+    # scheduler side: three cached blocks, snapshots at the ends of blocks 0 and 2 only
+    sched = Scheduler(alloc, max_seqs=2, prefill_chunk=64, max_blocks_per_seq=8)
+    sched.state_snapshots = True
+    alloc.release_all(blocks)
+    s = Sequence("a", toks[:40] + [999] * 9, SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    sched.add(s)
+    plan, entries = sched.schedule()
+    assert s.n_cached_prefix == 16 and plan.state_ops[0] == (1, s.state_slot, 0)       # block 1 has no snapshot: stop at block 0
+    assert plan.n_tokens == 48 - 16                                  # and the chunk ends at this prompt's own boundary (48)
+    # evicting a cached block takes its snapshot along
+    alloc2 = BlockAllocator(1, 16)
+    alloc2.enable_snapshots(1)
+    b = alloc2.alloc()
+    alloc2.publish(b, h[0])
+    assert alloc2.reserve_snapshot(h[0]) == 0
+    alloc2.release(b)
+    assert alloc2.alloc() == b and alloc2.snapshot_at(h[0]) is None and alloc2.free_snaps == [0]
