@@ -97,6 +97,21 @@ def test_hybrid_linear_attention_model_on_gpu_matches_oracle_and_graphs():
                     got[o.req_id].append(o.token)
         outs.append([got[i] for i in ids])
     assert outs[0] == outs[1] and all(len(x) == 12 for x in outs[0])
+    # prefix reuse: a prompt that contains an earlier one (a chat's next turn) continues from the recurrent state that was
+    # snapshotted at the earlier prompt's last block boundary (80 of its 90 tokens)
+    a = oracle_prompt(90, cfg.vocab, seed=1).tolist()
+    b = a[:85] + oracle_prompt(30, cfg.vocab, seed=2).tolist()
+    fresh = Engine(cfg, w, n_blocks=128, device="cuda", max_seqs=4).generate(b, SamplingParams(max_tokens=10, **GREEDY))
+    eng = Engine(cfg, w, n_blocks=128, device="cuda", max_seqs=4)
+    got = {}
+    for q in (a, b):
+        rid = eng.submit(q, SamplingParams(max_tokens=10, **GREEDY))
+        seq = eng.seqs[rid]
+        while eng.has_work:
+            for o in eng.step():
+                if o.token is not None:
+                    got.setdefault(o.req_id, []).append(o.token)
+    assert seq.n_cached_prefix == 80 and got[rid] == fresh
 
 
 def test_nemotron_h_bf16_graphs_equal_eager():
