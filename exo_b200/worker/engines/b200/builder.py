@@ -119,16 +119,78 @@ class ServingEngine(Engine):
         self.vision = None          # VisionProcessor, built on the first request that carries images
 
     # ---- images ----
+    def _checkpoint_vision(self, device, dtype):
+        """``(processor, tower, placeholder token, wrap)`` built from the model's own checkpoint when it carries a vision
+        tower this engine knows (Qwen2-VL family, Gemma-4); ``None`` otherwise (the generic tower then stands in).
+        ``wrap``: tokens put before and after an image's soft tokens."""
+        import json
+        from ....models.weights import SafetensorsSource
+        from .vision_families import (Gemma4Processor, Gemma4VisionConfig, Gemma4VisionTower, QwenVLProcessor, QwenVLTower,
+                                      QwenVLTowerConfig, family_for)
+        d = find_model_dir(self.model_id)
+        if d is None or not (d / "config.json").exists() or not any(d.glob("*.safetensors")):
+            return None
+        config = json.loads((d / "config.json").read_text())
+        pre = json.loads((d / "preprocessor_config.json").read_text()) if (d / "preprocessor_config.json").exists() else {}
+        proc = family_for(config, pre)
+        src = SafetensorsSource(d, device="cpu", dtype=torch.float32)
+        names = list(src.names())
+        tok_id = lambda t: self.tok.convert_tokens_to_ids(t) if hasattr(self.tok, "convert_tokens_to_ids") else None   # noqa: E731
+        if isinstance(proc, Gemma4Processor):
+            prefix = next((p for p in ("model.vision_tower.", "vision_tower.") if any(n.startswith(p) for n in names)), None)
+            if prefix is None:
+                return None
+            emb = prefix.replace("vision_tower.", "embed_vision.")
+            tower = Gemma4VisionTower.from_source(src, Gemma4VisionConfig.from_config(config.get("vision_config") or {}), device, dtype,
+                                                  prefix, emb)
+            ph = config.get("image_token_id") or tok_id(getattr(self.tok, "image_token", "<|image|>"))
+            wrap = (config.get("boi_token_id") or tok_id(getattr(self.tok, "boi_token", "<|image>")),
+                    config.get("eoi_token_id") or tok_id(getattr(self.tok, "eoi_token", "<image|>")))
+            return proc, tower, ph, wrap
+        if isinstance(proc, QwenVLProcessor) and str(config.get("model_type")) in ("qwen2_vl", "qwen2_5_vl"):
+            prefix = next((p for p in ("visual.", "model.visual.") if any(n.startswith(p) for n in names)), None)
+            if prefix is None or str(config.get("model_type")) != "qwen2_vl":       # (the 2.5 tower adds windows and RMSNorm)
+                return None
+            tower = QwenVLTower.from_source(src, QwenVLTowerConfig.from_config(config.get("vision_config") or {}), device, dtype, prefix)
+            return proc, tower, config.get("image_token_id") or tok_id("<|image_pad|>"), None
+        return None
+
     def _with_images(self, ids: list[int], images: list[str]):
         """Prompt ids with every image expanded to its feature rows: ``(ids, embeds, media)`` for the token engine.
         Single-rank engines only (the plan broadcast to other ranks carries token ids, not embeddings)."""
-        from .vision import VisionConfig, VisionProcessor, VisionTower, splice
+        import base64
+        import hashlib
+        import io
+        from .vision import ImageFeatures, VisionConfig, VisionProcessor, VisionTower, splice
         exe = self.te.exe
         if exe.spec.tp_size * exe.spec.pp_size != 1:
             raise ValueError("image inputs need a single-rank instance")
+        dtype = torch.float32 if exe.device.type == "cpu" else torch.bfloat16
         if self.vision is None:
-            dtype = torch.float32 if exe.device.type == "cpu" else torch.bfloat16
-            self.vision = VisionProcessor(VisionTower(VisionConfig(out_hidden=self.cfg.hidden), exe.device, dtype))
+            self.vision = self._checkpoint_vision(exe.device, dtype) or VisionProcessor(
+                VisionTower(VisionConfig(out_hidden=self.cfg.hidden), exe.device, dtype))
+        if isinstance(self.vision, tuple):
+            from PIL import Image
+            proc, tower, ph, wrap = self.vision
+            feats = []
+            for b in images:
+                raw = base64.b64decode(b.split(",", 1)[1] if b.startswith("data:") else b)
+                im = Image.open(io.BytesIO(raw))
+                a, g, _counts = proc([im])
+                rows = tower(a[0], g[0]) if isinstance(a, list) else tower(a, g)
+                feats.append(ImageFeatures(hashlib.sha256(raw).digest(), rows))
+            fill = ph if ph is not None else (getattr(self.tok, "pad_token_id", None) or 0)
+            out, embeds, media = splice(ids, ph, feats, fill)
+            if wrap and all(isinstance(t, int) and t >= 0 for t in wrap):
+                # begin / end markers around every image's soft tokens (later images shift by the markers put before them)
+                shifted, k = [], 0
+                for (pos, rows), (a0, a1, dg) in zip(embeds, media):
+                    out[pos + k:pos + k] = [wrap[0]]
+                    out[pos + k + 1 + rows.shape[0]:pos + k + 1 + rows.shape[0]] = [wrap[1]]
+                    shifted.append(((pos + k + 1, rows), (a0 + k + 1, a1 + k + 1, dg)))
+                    k += 2
+                embeds, media = [e for e, _ in shifted], [m for _, m in shifted]
+            return out, embeds, media
         feats = [self.vision.features(b) for b in images]
         ph = None
         conv = getattr(self.tok, "convert_tokens_to_ids", None)

@@ -177,7 +177,9 @@ def family_for(config: dict[str, Any], preprocessor: dict[str, Any] | None = Non
         return proc
     if mt in ("kimi_vl", "kimi_k25", "kimi_k2_5"):
         return KimiVLProcessor.from_config(pre)
-    if mt in ("gemma3", "gemma3n", "gemma4"):
+    if mt == "gemma4":
+        return Gemma4Processor.from_config(pre, config)
+    if mt in ("gemma3", "gemma3n"):
         return GemmaProcessor.from_config(pre, config)
     return None
 
@@ -276,3 +278,181 @@ class QwenVLTower:
         x = F.layer_norm(x, (E,), w["merger.ln_q.weight"], w["merger.ln_q.bias"], 1e-6).view(-1, c.merge * c.merge * E)
         x = F.gelu(x @ w["merger.mlp.0.weight"].t() + w["merger.mlp.0.bias"])
         return x @ w["merger.mlp.2.weight"].t() + w["merger.mlp.2.bias"]
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Gemma-4: aspect-preserving patches with (x, y) positions, its own vision transformer
+# ---------------------------------------------------------------------------------------------------------------------
+@dataclass
+class Gemma4Processor:
+    """Every image is resized (bicubic, aspect ratio kept) to the largest size whose sides are multiples of
+    ``pool * patch`` and that gives at most ``max_soft_tokens * pool²`` patches; pixels stay in ``[0, 1]`` (the tower
+    rescales).  Returns per image its patch rows ``[n, 3 * patch²]`` (patch pixels in (row, column, channel) order), the
+    patches' integer ``(x, y)`` positions and the number of soft tokens (``n / pool²``)."""
+    patch: int = 16
+    max_soft_tokens: int = 280
+    pool: int = 3
+
+    @classmethod
+    def from_config(cls, pre: dict[str, Any], cfg: dict[str, Any] | None = None) -> "Gemma4Processor":
+        vc = (cfg or {}).get("vision_config") or {}
+        return cls(patch=pre.get("patch_size", vc.get("patch_size", 16)), max_soft_tokens=pre.get("max_soft_tokens", 280),
+                   pool=pre.get("pooling_kernel_size", vc.get("pooling_kernel_size", 3)))
+
+    def target(self, h: int, w: int) -> tuple[int, int]:
+        max_patches = self.max_soft_tokens * self.pool ** 2
+        factor = math.sqrt(max_patches * self.patch ** 2 / (h * w))
+        side = self.pool * self.patch
+        th, tw = int(math.floor(factor * h / side)) * side, int(math.floor(factor * w / side)) * side
+        longest = (max_patches // self.pool ** 2) * side
+        if th == 0 and tw == 0:
+            raise ValueError(f"image {h}x{w} cannot be resized to a multiple of {side}")
+        if th == 0:
+            th, tw = side, min(int(math.floor(w / h)) * side, longest)
+        elif tw == 0:
+            tw, th = side, min(int(math.floor(h / w)) * side, longest)
+        return th, tw
+
+    def __call__(self, images: list) -> tuple[list[torch.Tensor], list[torch.Tensor], list[int]]:
+        import torchvision.transforms.v2.functional as TF
+        patches, positions, counts = [], [], []
+        for im in images:
+            x = TF.pil_to_tensor(im.convert("RGB"))                                    # [3, H, W] uint8
+            th, tw = self.target(x.shape[-2], x.shape[-1])
+            if (th, tw) != tuple(x.shape[-2:]):
+                x = TF.resize(x, [th, tw], interpolation=TF.InterpolationMode.BICUBIC, antialias=True)
+            x = x.float() / 255.0
+            ph, pw = th // self.patch, tw // self.patch
+            rows = x.reshape(3, ph, self.patch, pw, self.patch).permute(1, 3, 2, 4, 0).reshape(ph * pw, -1)
+            xs, ys = torch.meshgrid(torch.arange(pw), torch.arange(ph), indexing="xy")
+            patches.append(rows)
+            positions.append(torch.stack((xs, ys), -1).reshape(ph * pw, 2))
+            counts.append(ph * pw // self.pool ** 2)
+        return patches, positions, counts
+
+
+@dataclass
+class Gemma4VisionConfig:
+    hidden: int = 768
+    ffn: int = 3072
+    layers: int = 16
+    heads: int = 12
+    kv_heads: int = 12
+    head_dim: int = 64
+    eps: float = 1e-6
+    theta: float = 100.0
+    patch: int = 16
+    pool: int = 3
+    table: int = 10240
+    clipped: bool = False
+    standardize: bool = False
+
+    @classmethod
+    def from_config(cls, vc: dict[str, Any]) -> "Gemma4VisionConfig":
+        rp = vc.get("rope_parameters") or {}
+        return cls(hidden=vc.get("hidden_size", 768), ffn=vc.get("intermediate_size", 3072), layers=vc.get("num_hidden_layers", 16),
+                   heads=vc.get("num_attention_heads", 12), kv_heads=vc.get("num_key_value_heads", 12), head_dim=vc.get("head_dim", 64),
+                   eps=vc.get("rms_norm_eps", 1e-6), theta=rp.get("rope_theta", 100.0), patch=vc.get("patch_size", 16),
+                   pool=vc.get("pooling_kernel_size", 3), table=vc.get("position_embedding_size", 10240),
+                   clipped=bool(vc.get("use_clipped_linears", False)), standardize=bool(vc.get("standardize", False)))
+
+
+@dataclass
+class Gemma4VisionTower:
+    """Gemma-4's vision encoder and its projection into the decoder's hidden size, one image at a time (no padding
+    patches: an image's own patches are all the encoder sees, which is what the library's padding mask amounts to).
+
+    ``weights``: the checkpoint's tensors with the ``model.vision_tower.`` prefix removed, plus the embedder's
+    ``embed_vision.embedding_projection.weight``.  Patch pixels are mapped to ``[-1, 1]``, projected, and given learned
+    (x, y) position embeddings; every layer has norms on both sides of attention and MLP, q / k normalised with a weight
+    and v without one, 2-D rotary positions (the first half of each head turns with x, the second with y, both with the
+    frequencies of a quarter-width head), softmax scale 1, GeGLU; the pooler averages ``pool x pool`` neighbours and
+    scales by ``sqrt(hidden)``; the embedder normalises (no weight) and projects."""
+    cfg: Gemma4VisionConfig
+    weights: dict[str, torch.Tensor]
+    device: torch.device = field(default_factory=lambda: torch.device("cpu"))
+    dtype: torch.dtype = torch.float32
+
+    def __post_init__(self) -> None:
+        self.w = {k: v.to(device=self.device, dtype=self.dtype if v.is_floating_point() else v.dtype) for k, v in self.weights.items()}
+
+    @classmethod
+    def from_source(cls, src, cfg: Gemma4VisionConfig, device, dtype, prefix: str = "model.vision_tower.",
+                    embedder: str = "model.embed_vision.") -> "Gemma4VisionTower":
+        names = [n for n in src.names() if n.startswith(prefix)]
+        if not names:
+            raise KeyError(f"checkpoint has no {prefix}* tensors")
+        w = {n[len(prefix):]: src.get(n, None) for n in names}
+        w.update({"embed_vision." + n[len(embedder):]: src.get(n, None) for n in src.names() if n.startswith(embedder)})
+        return cls(cfg, w, torch.device(device), dtype)
+
+    def _norm(self, x: torch.Tensor, w: torch.Tensor | None) -> torch.Tensor:
+        y = x.float() * torch.pow(x.float().pow(2).mean(-1, keepdim=True) + self.cfg.eps, -0.5)
+        return (y * w.float() if w is not None else y).to(x.dtype)
+
+    def _linear(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        w = self.w
+        if self.cfg.clipped:
+            x = torch.clamp(x, w[name + ".input_min"], w[name + ".input_max"])
+        y = x @ w[name + ".linear.weight"].t()
+        if self.cfg.clipped:
+            y = torch.clamp(y, w[name + ".output_min"], w[name + ".output_max"])
+        return y
+
+    def _rotary(self, pos: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        c = self.cfg
+        half = c.head_dim // 2                                                          # channels that turn with one axis
+        inv = 1.0 / (c.theta ** (torch.arange(0, half, 2, dtype=torch.float32, device=self.device) / half))
+        parts = []
+        for axis in range(2):
+            ang = pos[:, axis:axis + 1].float() * inv                                   # [N, half/2]
+            parts.append(torch.cat((ang, ang), -1))
+        ang = torch.cat(parts, -1)                                                      # [N, head_dim]
+        return ang.cos()[:, None, :].to(self.dtype), ang.sin()[:, None, :].to(self.dtype)
+
+    @staticmethod
+    def _turn(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """Each half of the head is rotated on its own (pairs i, i + quarter within the half)."""
+        out = []
+        for xs, cs, ss in zip(x.chunk(2, -1), cos.chunk(2, -1), sin.chunk(2, -1)):
+            out.append(xs * cs + _rot_half(xs) * ss)
+        return torch.cat(out, -1)
+
+    @torch.no_grad()
+    def __call__(self, patches: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """``patches [n, 3*patch²]`` in ``[0, 1]``, ``positions [n, 2]`` (x, y) → ``[n / pool², decoder hidden]``."""
+        c, w = self.cfg, self.w
+        pos = positions.to(self.device).long()
+        x = (2 * (patches.to(device=self.device, dtype=self.dtype) - 0.5)) @ w["patch_embedder.input_proj.weight"].t()
+        table = w["patch_embedder.position_embedding_table"]
+        x = x + table[0][pos[:, 0]] + table[1][pos[:, 1]]
+        cos, sin = self._rotary(pos)
+        n, H, KV, D = x.shape[0], c.heads, c.kv_heads, c.head_dim
+        for i in range(c.layers):
+            b = f"encoder.layers.{i}."
+            y = self._norm(x, w[b + "input_layernorm.weight"])
+            q = self._norm(self._linear(y, b + "self_attn.q_proj").view(n, H, D), w[b + "self_attn.q_norm.weight"])
+            k = self._norm(self._linear(y, b + "self_attn.k_proj").view(n, KV, D), w[b + "self_attn.k_norm.weight"])
+            v = self._norm(self._linear(y, b + "self_attn.v_proj").view(n, KV, D), None)
+            q, k = self._turn(q, cos, sin), self._turn(k, cos, sin)
+            if KV != H:
+                k, v = k.repeat_interleave(H // KV, 1), v.repeat_interleave(H // KV, 1)
+            o = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None], scale=1.0)
+            o = self._linear(o[0].transpose(0, 1).reshape(n, H * D), b + "self_attn.o_proj")
+            x = x + self._norm(o, w[b + "post_attention_layernorm.weight"])
+            y = self._norm(x, w[b + "pre_feedforward_layernorm.weight"])
+            y = F.gelu(self._linear(y, b + "mlp.gate_proj"), approximate="tanh") * self._linear(y, b + "mlp.up_proj")
+            x = x + self._norm(self._linear(y, b + "mlp.down_proj"), w[b + "post_feedforward_layernorm.weight"])
+        # pool x pool neighbours (by position) are averaged; the grid's width in kernels orders the outputs row by row
+        kq = c.pool
+        if kq > 1:
+            cells = torch.div(pos, kq, rounding_mode="floor")
+            per_row = (int(pos[:, 0].max()) + 1) // kq
+            idx = cells[:, 0] + per_row * cells[:, 1]
+            out = torch.zeros(n // (kq * kq), x.shape[1], dtype=torch.float32, device=self.device)
+            out.index_add_(0, idx, x.float() / (kq * kq))
+            x = out.to(self.dtype)
+        x = x * c.hidden ** 0.5
+        if c.standardize:
+            x = (x - w["std_bias"]) * w["std_scale"]
+        return self._norm(x, None) @ w["embed_vision.embedding_projection.weight"].t()

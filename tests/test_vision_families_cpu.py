@@ -96,3 +96,82 @@ def test_family_selection_from_config_json():
     g = family_for({"model_type": "gemma3", "mm_tokens_per_image": 256}, {"size": {"height": 896, "width": 896}})
     assert isinstance(g, GemmaProcessor) and g.size == 896
     assert family_for({"model_type": "llama"}) is None
+
+
+def test_gemma4_processor_and_tower_match_transformers():
+    """Gemma-4: the aspect-preserving patch processor against the library's, and the vision encoder + multimodal embedder
+    against ``Gemma4VisionModel`` / ``Gemma4MultimodalEmbedder`` on a random tiny configuration."""
+    tf = pytest.importorskip("transformers")
+    if not hasattr(tf, "Gemma4ForConditionalGeneration"):
+        pytest.skip("this transformers build has no Gemma-4")
+    from PIL import Image
+    from transformers.models.gemma4.image_processing_gemma4 import Gemma4ImageProcessor
+    from transformers.models.gemma4.modeling_gemma4 import Gemma4MultimodalEmbedder, Gemma4VisionModel
+    from exo_b200.worker.engines.b200.vision_families import Gemma4Processor, Gemma4VisionConfig, Gemma4VisionTower, family_for
+    rng = np.random.default_rng(0)
+    im = Image.fromarray(rng.integers(0, 255, (150, 260, 3), dtype=np.uint8))
+    proc = family_for({"model_type": "gemma4", "vision_config": {"patch_size": 16, "pooling_kernel_size": 3}}, {"max_soft_tokens": 70})
+    assert isinstance(proc, Gemma4Processor)
+    rows, pos, counts = proc([im])
+    ref = Gemma4ImageProcessor(max_soft_tokens=70)(images=[im], return_tensors="pt")
+    n = rows[0].shape[0]
+    assert counts == list(ref["num_soft_tokens_per_image"]) and n == counts[0] * 9
+    assert torch.equal(pos[0], ref["image_position_ids"][0, :n]) and (ref["image_position_ids"][0, n:] == -1).all()
+    assert (rows[0] - ref["pixel_values"][0, :n]).abs().max() < 2 / 255
+    torch.manual_seed(0)
+    vc = tf.Gemma4VisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                               head_dim=16, patch_size=16, pooling_kernel_size=3, position_embedding_size=64)
+    import types
+    tc = types.SimpleNamespace(hidden_size=96)                  # all the embedder reads of the text configuration
+    tower, emb = Gemma4VisionModel(vc).float().eval(), Gemma4MultimodalEmbedder(vc, tc).float().eval()
+    with torch.no_grad():
+        for m in (tower, emb):
+            for name, p in m.named_parameters():
+                p.normal_(1.0 if "norm" in name else 0.0, 0.2 if "norm" in name else 0.1)
+        want = emb(tower(pixel_values=ref["pixel_values"], pixel_position_ids=ref["image_position_ids"]).last_hidden_state)
+    weights = dict(tower.state_dict())
+    weights.update({"embed_vision." + k: v for k, v in emb.state_dict().items()})
+    mine = Gemma4VisionTower(Gemma4VisionConfig.from_config(vc.to_dict()), weights)
+    got = mine(rows[0], pos[0])
+    assert got.shape == want.shape == (counts[0], 96)
+    assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), float((got - want).abs().max())
+
+
+def test_serving_engine_uses_the_checkpoints_own_tower(tmp_path):
+    """A checkpoint folder with Gemma-4 tower tensors: the serving engine expands an image to the tower's soft tokens between
+    the begin / end markers, and the spliced rows are the tower's output."""
+    tf = pytest.importorskip("transformers")
+    if not hasattr(tf, "Gemma4ForConditionalGeneration"):
+        pytest.skip("this transformers build has no Gemma-4")
+    import base64
+    import io
+    import json
+    import types
+    from PIL import Image
+    from safetensors.torch import save_file
+    from transformers.models.gemma4.modeling_gemma4 import Gemma4MultimodalEmbedder, Gemma4VisionModel
+    from exo_b200.worker.engines.b200.builder import ServingEngine
+    from exo_b200.worker.engines.b200.vision_families import Gemma4Processor
+    torch.manual_seed(0)
+    vc = tf.Gemma4VisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                               head_dim=16, patch_size=16, pooling_kernel_size=3, position_embedding_size=64)
+    tower, emb = Gemma4VisionModel(vc).float().eval(), Gemma4MultimodalEmbedder(vc, types.SimpleNamespace(hidden_size=96)).float().eval()
+    sd = {"model.vision_tower." + k: v.contiguous() for k, v in tower.state_dict().items()}
+    sd.update({"model.embed_vision." + k: v.contiguous() for k, v in emb.state_dict().items()})
+    save_file(sd, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "gemma4", "vision_config": vc.to_dict(), "image_token_id": 7,
+                                                      "boi_token_id": 5, "eoi_token_id": 6}))
+    (tmp_path / "preprocessor_config.json").write_text(json.dumps({"max_soft_tokens": 70}))
+    eng = object.__new__(ServingEngine)
+    eng.model_id, eng.vision, eng.tok = str(tmp_path), None, types.SimpleNamespace(pad_token_id=0)
+    eng.cfg = types.SimpleNamespace(hidden=96)
+    eng.te = types.SimpleNamespace(exe=types.SimpleNamespace(spec=types.SimpleNamespace(tp_size=1, pp_size=1), device=torch.device("cpu")))
+    buf = io.BytesIO()
+    Image.fromarray(np.random.default_rng(1).integers(0, 255, (120, 200, 3), dtype=np.uint8)).save(buf, format="PNG")
+    b64 = base64.b64encode(buf.getvalue()).decode()
+    ids, embeds, media = eng._with_images([2, 11, 7, 12, 7, 13], [b64, b64])
+    assert isinstance(eng.vision[0], Gemma4Processor)
+    n = embeds[0][1].shape[0]
+    assert ids == [2, 11, 5] + [7] * n + [6, 12, 5] + [7] * n + [6, 13]
+    assert [p for p, _ in embeds] == [3, 3 + n + 3] and [(a, b) for a, b, _ in media] == [(3, 3 + n), (6 + n, 6 + 2 * n)]
+    assert embeds[0][1].shape == (n, 96) and torch.equal(embeds[0][1], embeds[1][1])
