@@ -147,9 +147,10 @@ class ServingEngine(Engine):
             wrap = (config.get("boi_token_id") or tok_id(getattr(self.tok, "boi_token", "<|image>")),
                     config.get("eoi_token_id") or tok_id(getattr(self.tok, "eoi_token", "<image|>")))
             return proc, tower, ph, wrap
-        if isinstance(proc, QwenVLProcessor) and str(config.get("model_type")) in ("qwen2_vl", "qwen2_5_vl"):
-            prefix = next((p for p in ("visual.", "model.visual.") if any(n.startswith(p) for n in names)), None)
-            if prefix is None or str(config.get("model_type")) != "qwen2_vl":       # (the 2.5 tower adds windows and RMSNorm)
+        if isinstance(proc, QwenVLProcessor):
+            # Qwen2-VL and the Qwen3-VL line (Qwen3.5 / 3.6 included); the windowed Qwen2.5-VL tower is not built
+            prefix = next((p for p in ("visual.", "model.visual.", "vision_tower.") if any(n.startswith(p) for n in names)), None)
+            if prefix is None or str(config.get("model_type")) == "qwen2_5_vl":
                 return None
             tower = QwenVLTower.from_source(src, QwenVLTowerConfig.from_config(config.get("vision_config") or {}), device, dtype, prefix)
             return proc, tower, config.get("image_token_id") or tok_id("<|image_pad|>"), None

@@ -197,9 +197,18 @@ class QwenVLTowerConfig:
     merge: int = 2
     temporal: int = 2
     out_hidden: int = 3584
+    variant: str = "qwen2"          # "qwen3": Qwen3-VL / Qwen3.5 / Qwen3.6 (learned position table, tanh-GELU MLP, other tensor names)
+    mlp_dim: int = 0                # qwen3: the MLP's width (qwen2 derives it from mlp_ratio)
+    n_pos: int = 2304               # qwen3: entries of the learned position table (a square grid)
+    act: str = "gelu_pytorch_tanh"  # qwen3: MLP activation
 
     @classmethod
     def from_config(cls, vc: dict[str, Any]) -> "QwenVLTowerConfig":
+        if "out_hidden_size" in vc:                                             # Qwen3-VL and later
+            return cls(depth=vc.get("depth", 27), embed_dim=vc.get("hidden_size", 1152), heads=vc.get("num_heads", 16),
+                       patch=vc.get("patch_size", 16), merge=vc.get("spatial_merge_size", 2), temporal=vc.get("temporal_patch_size", 2),
+                       out_hidden=vc["out_hidden_size"], variant="qwen3", mlp_dim=vc.get("intermediate_size", 4304),
+                       n_pos=vc.get("num_position_embeddings", 2304), act=vc.get("hidden_act", "gelu_pytorch_tanh"))
         return cls(depth=vc.get("depth", 32), embed_dim=vc.get("embed_dim", 1280), heads=vc.get("num_heads", 16),
                    mlp_ratio=vc.get("mlp_ratio", 4.0), patch=vc.get("patch_size", 14), merge=vc.get("spatial_merge_size", 2),
                    temporal=vc.get("temporal_patch_size", 2), out_hidden=vc.get("hidden_size", 3584))
@@ -218,7 +227,13 @@ class QwenVLTower:
     convolution kernel, ``blocks.N.{norm1,norm2,attn.qkv,attn.proj,mlp.fc1,mlp.fc2}``, ``merger.{ln_q,mlp.0,mlp.2}``).
     Positions are 2-D rotary (row and column halves of each head's first half), attention is full within an image and
     never crosses images, the MLP activation is ``x * sigmoid(1.702 x)``, and the merger normalises every patch, joins
-    the ``merge²`` neighbours and maps them to the decoder's hidden size."""
+    the ``merge²`` neighbours and maps them to the decoder's hidden size.
+
+    ``variant == "qwen3"`` (Qwen3-VL, Qwen3.5, Qwen3.6): the patch projection has a bias, a learned ``pos_embed`` table over a
+    square grid is interpolated bilinearly to the image's patch grid and added, the MLP is ``linear_fc1`` / ``linear_fc2``
+    with the configured activation, and the merger's tensors are ``merger.{norm,linear_fc1,linear_fc2}``.  The extra
+    mergers that feed intermediate features to the first decoder layers of Qwen3-VL are not run: the tower returns the
+    input embeddings only."""
     cfg: QwenVLTowerConfig
     weights: dict[str, torch.Tensor]
     device: torch.device = field(default_factory=lambda: torch.device("cpu"))
@@ -226,7 +241,10 @@ class QwenVLTower:
 
     def __post_init__(self) -> None:
         self.w = {k: v.to(device=self.device, dtype=self.dtype) for k, v in self.weights.items()}
-        self.w["patch_embed.proj.weight"] = self.w["patch_embed.proj.weight"].reshape(self.cfg.embed_dim, -1)
+        k = self.w["patch_embed.proj.weight"]
+        if k.dim() == 5 and k.shape[1] != 3 and k.shape[-1] == 3:               # channels-last kernel (MLX checkpoints)
+            k = k.permute(0, 4, 1, 2, 3)
+        self.w["patch_embed.proj.weight"] = k.reshape(self.cfg.embed_dim, -1)
 
     @classmethod
     def from_source(cls, src, cfg: QwenVLTowerConfig, device, dtype, prefix: str = "visual.") -> "QwenVLTower":
@@ -235,6 +253,22 @@ class QwenVLTower:
         if not names:
             raise KeyError(f"checkpoint has no {prefix}* tensors")
         return cls(cfg, {n[len(prefix):]: src.get(n, None) for n in names}, torch.device(device), dtype)
+
+    def _position_table(self, grid_thw: torch.Tensor) -> torch.Tensor:
+        """The learned position table resampled to every image's grid (bilinear, corners aligned), in patch order."""
+        c, tab = self.cfg, self.w["pos_embed.weight"]
+        side, m = int(c.n_pos ** 0.5), c.merge
+        out = []
+        for t, h, w in grid_thw.tolist():
+            ys, xs = torch.linspace(0, side - 1, h, device=self.device), torch.linspace(0, side - 1, w, device=self.device)
+            y0, x0 = ys.int(), xs.int()
+            y1, x1 = (y0 + 1).clip(max=side - 1), (x0 + 1).clip(max=side - 1)
+            dy, dx = (ys - y0).to(tab.dtype)[:, None, None], (xs - x0).to(tab.dtype)[None, :, None]
+            g = lambda a, b: tab[(a.long()[:, None] * side + b.long()[None, :])]          # noqa: E731   [h, w, E]
+            e = g(y0, x0) * (1 - dy) * (1 - dx) + g(y0, x1) * (1 - dy) * dx + g(y1, x0) * dy * (1 - dx) + g(y1, x1) * dy * dx
+            e = e.view(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+            out.append(e.repeat(t, 1))
+        return torch.cat(out)
 
     def _rotary(self, grid_thw: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         c = self.cfg
@@ -258,9 +292,14 @@ class QwenVLTower:
         E, H = c.embed_dim, c.heads
         hd = E // H
         x = patches.to(device=self.device, dtype=self.dtype) @ w["patch_embed.proj.weight"].t()
+        q3 = c.variant == "qwen3"
+        if q3:
+            x = x + w["patch_embed.proj.bias"] + self._position_table(grid_thw)
+        fc1, fc2 = ("mlp.linear_fc1", "mlp.linear_fc2") if q3 else ("mlp.fc1", "mlp.fc2")
         cos, sin = self._rotary(grid_thw)
         cos, sin = cos.to(self.dtype), sin.to(self.dtype)
-        spans = (grid_thw[:, 0] * grid_thw[:, 1] * grid_thw[:, 2]).tolist()
+        spans = [h * w for t, h, w in grid_thw.tolist() for _ in range(t)] if q3 else \
+            (grid_thw[:, 0] * grid_thw[:, 1] * grid_thw[:, 2]).tolist()
         for i in range(c.depth):
             b = f"blocks.{i}."
             y = F.layer_norm(x, (E,), w[b + "norm1.weight"], w[b + "norm1.bias"], 1e-6)
@@ -273,8 +312,22 @@ class QwenVLTower:
                 o += n
             x = x + torch.cat(outs) @ w[b + "attn.proj.weight"].t() + w[b + "attn.proj.bias"]
             y = F.layer_norm(x, (E,), w[b + "norm2.weight"], w[b + "norm2.bias"], 1e-6)
-            y = y @ w[b + "mlp.fc1.weight"].t() + w[b + "mlp.fc1.bias"]
-            x = x + (y * torch.sigmoid(1.702 * y)) @ w[b + "mlp.fc2.weight"].t() + w[b + "mlp.fc2.bias"]
+            y = y @ w[b + fc1 + ".weight"].t() + w[b + fc1 + ".bias"]
+            if not q3:
+                y = y * torch.sigmoid(1.702 * y)
+            elif c.act in ("gelu_pytorch_tanh", "gelu_tanh"):
+                y = F.gelu(y, approximate="tanh")
+            elif c.act == "gelu":
+                y = F.gelu(y)
+            elif c.act == "silu":
+                y = F.silu(y)
+            else:
+                raise ValueError(f"vision MLP activation {c.act!r}")
+            x = x + y @ w[b + fc2 + ".weight"].t() + w[b + fc2 + ".bias"]
+        if q3:
+            x = F.layer_norm(x, (E,), w["merger.norm.weight"], w["merger.norm.bias"], 1e-6).view(-1, c.merge * c.merge * E)
+            x = F.gelu(x @ w["merger.linear_fc1.weight"].t() + w["merger.linear_fc1.bias"])
+            return x @ w["merger.linear_fc2.weight"].t() + w["merger.linear_fc2.bias"]
         x = F.layer_norm(x, (E,), w["merger.ln_q.weight"], w["merger.ln_q.bias"], 1e-6).view(-1, c.merge * c.merge * E)
         x = F.gelu(x @ w["merger.mlp.0.weight"].t() + w["merger.mlp.0.bias"])
         return x @ w["merger.mlp.2.weight"].t() + w["merger.mlp.2.bias"]

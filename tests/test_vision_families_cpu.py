@@ -61,6 +61,39 @@ def test_qwen_vl_tower_matches_transformers():
     torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-4)
 
 
+@pytest.mark.parametrize("family", ["qwen3_vl", "qwen3_5"])
+def test_qwen3_vl_tower_matches_transformers(family):
+    """The Qwen3-VL / Qwen3.5 tower (interpolated position table, tanh-GELU MLP, renamed merger) against the library's."""
+    tf = pytest.importorskip("transformers")
+    if family == "qwen3_vl":
+        from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLVisionConfig as VC
+        from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLVisionModel as VM
+        extra = {"deepstack_visual_indexes": []}
+    else:
+        from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5VisionConfig as VC
+        from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5VisionModel as VM
+        extra = {}
+    torch.manual_seed(0)
+    vc = VC(depth=2, hidden_size=64, intermediate_size=160, num_heads=4, patch_size=16, spatial_merge_size=2, temporal_patch_size=2,
+            out_hidden_size=96, num_position_embeddings=36, **extra)
+    vc._attn_implementation = "eager"
+    hf = VM(vc).eval().float()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    proc = family_for({"model_type": family, "vision_config": vc.to_dict()}, {})
+    assert proc.patch == 16 and proc.mean == (0.5, 0.5, 0.5)
+    patches, grid, tokens = proc([picture(120, 200, 3), picture(90, 70, 4)])
+    with torch.no_grad():
+        want = hf(patches, grid_thw=grid)
+    want = getattr(want, "pooler_output", want)
+    want = want[0] if isinstance(want, tuple) else want
+    cfg = QwenVLTowerConfig.from_config(vc.to_dict())
+    assert cfg.variant == "qwen3" and cfg.mlp_dim == 160 and cfg.n_pos == 36
+    got = QwenVLTower(cfg, dict(hf.state_dict()))(patches, grid)
+    assert got.shape == (sum(tokens), 96) == tuple(want.shape)
+    torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-4)
+
+
 def test_gemma_processor_matches_transformers():
     from transformers.models.gemma3.image_processing_gemma3 import Gemma3ImageProcessor
     ref = Gemma3ImageProcessor(size={"height": 896, "width": 896})
