@@ -115,7 +115,9 @@ class ImageEngine(Engine):
             if p.size in (None, "auto"):
                 height, width = init.shape[0], init.shape[1]
         adv = p.advanced_params
-        steps = (adv.num_inference_steps if adv and adv.num_inference_steps else None) or steps_for_quality(p.quality or "medium")
+        table = getattr(self.runner.m, "default_steps", None)            # the model's own step counts per quality level
+        steps = (adv.num_inference_steps if adv and adv.num_inference_steps else None) or \
+            (table.get(p.quality or "medium", table["medium"]) if table else steps_for_quality(p.quality or "medium"))
         seed = adv.seed if adv and adv.seed is not None else 0
         guidance = adv.guidance if adv and getattr(adv, "guidance", None) is not None else None
         partials = p.partial_images if (p.stream and p.partial_images) else 0
@@ -221,20 +223,36 @@ class ImageBuilder(Builder):
         groups = [list(range(0, half)), list(range(half, self.world))] if self.cfg_parallel else [list(range(self.world))]
         self.pipe_groups = [dist.new_group(g) for g in groups]
 
-    def load(self) -> Iterator[LoadProgress]:
-        cfg = DitConfig.for_card(self.card.n_layers, self.card.hidden_size, self.card.uses_cfg)
+    def _stage(self, n_blocks: int) -> range:
         pipe_world = self.world // 2 if (self.cfg_parallel and self.world % 2 == 0) else self.world
         pipe_rank = self.rank % pipe_world
-        per = -(-cfg.n_blocks // pipe_world)
-        blocks = range(min(cfg.n_blocks, pipe_rank * per), min(cfg.n_blocks, (pipe_rank + 1) * per))
+        per = -(-n_blocks // pipe_world)
+        return range(min(n_blocks, pipe_rank * per), min(n_blocks, (pipe_rank + 1) * per))
+
+    def load(self) -> Iterator[LoadProgress]:
+        """FLUX.1 checkpoint folders (``transformer/``, ``vae/``, text encoders) load as ``FluxModel``, this stage's blocks
+        only; any other card (or a card whose folder is not on disk) gets the seeded stand-in transformer."""
+        from ..b200.builder import find_model_dir
+        root = find_model_dir(str(self.card.model_id))
+        if root is not None and (root / "transformer" / "config.json").exists() and "flux" in str(getattr(self.card, "family", "flux")).lower():
+            from .flux import FluxConfig, FluxModel
+            blocks = self._stage(FluxConfig.from_folder(root).n_blocks)
+            yield LoadProgress(0, len(blocks))
+            dtype = torch.float32 if self.device.type == "cpu" else torch.bfloat16
+            self.model = FluxModel.from_folder(root, blocks=blocks, device=self.device, dtype=dtype)
+            yield LoadProgress(len(blocks), len(blocks))
+            return
+        cfg = DitConfig.for_card(self.card.n_layers, self.card.hidden_size, self.card.uses_cfg)
+        blocks = self._stage(cfg.n_blocks)
         yield LoadProgress(0, len(blocks))
         self.model = Dit(cfg, seed=0, blocks=blocks, device=self.device)
         yield LoadProgress(len(blocks), len(blocks))
 
     def build(self) -> Engine:
         assert self.model is not None
+        sync = os.environ.get("EXO_IMAGE_SYNC_STEPS") or getattr(self.model, "num_sync_steps", 1)
         runner = DiffusionRunner(self.model, rank=self.rank, world=self.world, cfg_parallel=self.cfg_parallel,
-                                 num_sync_steps=int(os.environ.get("EXO_IMAGE_SYNC_STEPS", "1")), pipe_groups=self.pipe_groups)
+                                 num_sync_steps=int(sync), pipe_groups=self.pipe_groups)
         return ImageEngine(runner, str(self.card.model_id), self.rank, self.world, self.control)
 
     def close(self) -> None:

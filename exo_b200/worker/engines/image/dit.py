@@ -5,8 +5,9 @@ followed by single-stream blocks, adaLN modulation from the timestep and a poole
 rectified-flow Euler sampling; ``src/exo/worker/engines/image/models/{flux,qwen}/*``,
 ``pipeline/runner.py``).  This module has the same structure at configurable size so the
 serving path, the pipeline / CFG / patch parallel schedules and the API can be exercised end to
-end.  Loading the published FLUX / Qwen-Image checkpoints (their text encoders and VAE) is not
-implemented: weights are drawn from a seed, identically on every rank.
+end with weights drawn from a seed, identically on every rank; it stands in for model cards whose
+checkpoint folder is not on disk (and for Qwen-Image, whose checkpoint loader is not built).  The
+published FLUX.1 checkpoints run on ``flux.FluxModel``, which has this class's interface.
 """
 from __future__ import annotations
 
@@ -172,13 +173,16 @@ class Dit:
     def embed_tokens(self, lat: torch.Tensor, gh: int, gw: int) -> torch.Tensor:
         return F.linear(self.patchify(lat), self.img_in) + self.pos_embed(gh, gw)
 
-    def run_blocks(self, txt, img, vec, caches=None, rows: slice | None = None):
+    def run_blocks(self, txt, img, vec, caches=None, rows: slice | None = None, grid: tuple[int, int] | None = None):
         for i in self.block_range:
             txt, img = self.blocks[i].forward(txt, img, vec, None if caches is None else caches[i], rows)
         return txt, img
 
-    def head(self, img: torch.Tensor, gh: int, gw: int) -> torch.Tensor:
-        return self.unpatchify(F.linear(F.layer_norm(img, (self.cfg.hidden,)), self.img_out), gh, gw)
+    def head_tokens(self, img: torch.Tensor, vec: torch.Tensor | None = None) -> torch.Tensor:
+        return F.linear(F.layer_norm(img, (self.cfg.hidden,)), self.img_out)
+
+    def head(self, img: torch.Tensor, gh: int, gw: int, vec: torch.Tensor | None = None) -> torch.Tensor:
+        return self.unpatchify(self.head_tokens(img, vec), gh, gw)
 
     def velocity(self, lat: torch.Tensor, t: float, txt: torch.Tensor, pooled: torch.Tensor) -> torch.Tensor:
         gh, gw = lat.shape[1] // self.cfg.patch, lat.shape[2] // self.cfg.patch

@@ -53,12 +53,12 @@ class DiffusionRunner:
             txt, img = txt0, m.embed_tokens(lat, gh, gw)
         else:
             txt = self._recv(txt0, self.base + self.pipe_rank - 1)
-            img = self._recv(torch.empty(gh * gw, m.cfg.hidden, device=m.device), self.base + self.pipe_rank - 1)
-        txt, img = m.run_blocks(txt, img, vec, caches)
+            img = self._recv(torch.empty(gh * gw, m.cfg.hidden, device=m.device, dtype=txt0.dtype), self.base + self.pipe_rank - 1)
+        txt, img = m.run_blocks(txt, img, vec, caches, None, (gh, gw))
         if not self.last:
             self._send(txt, self.base + self.pipe_rank + 1)
             self._send(img, self.base + self.pipe_rank + 1)
-        v = m.head(img, gh, gw) if self.last else torch.empty_like(lat)
+        v = m.head(img, gh, gw, vec) if self.last else torch.empty_like(lat)
         if self.pipe_world > 1:
             dist.broadcast(v, src=self.base + self.pipe_world - 1, group=self.group)
         return v
@@ -78,14 +78,14 @@ class DiffusionRunner:
                 txt, img = txt0, tokens_in[rows]
             else:
                 txt = self._recv(txt0, self.base + self.pipe_rank - 1)
-                img = self._recv(torch.empty(n, m.cfg.hidden, device=m.device), self.base + self.pipe_rank - 1)
-            txt, img = m.run_blocks(txt, img, vec, caches, rows)
+                img = self._recv(torch.empty(n, m.cfg.hidden, device=m.device, dtype=txt0.dtype), self.base + self.pipe_rank - 1)
+            txt, img = m.run_blocks(txt, img, vec, caches, rows, (gh, gw))
             if not self.last:
                 self._send(txt, self.base + self.pipe_rank + 1)
                 self._send(img, self.base + self.pipe_rank + 1)
                 self.n_patch_hops += 1
             else:
-                out[rows] = torch.nn.functional.linear(torch.nn.functional.layer_norm(img, (m.cfg.hidden,)), m.img_out)
+                out[rows] = m.head_tokens(img, vec)
         v = m.unpatchify(out, gh, gw) if self.last else torch.empty_like(lat)
         dist.broadcast(v, src=self.base + P - 1, group=self.group)
         return v
@@ -119,13 +119,17 @@ class DiffusionRunner:
         gh, gw = m.grid(height, width)
         p = m.cfg.patch
         noise = torch.randn(m.cfg.latent_channels, gh * p, gw * p, generator=torch.Generator().manual_seed(seed)).to(m.device)
-        start = 1.0
         lat = noise
+        if hasattr(m, "guidance_value"):
+            m.guidance_value = g                            # guidance-distilled models take the scale as an input
+        kontext = init_image is not None and getattr(m.cfg, "kontext", False)
+        if hasattr(m, "set_context"):
+            m.set_context(init_image.to(m.device) if kontext else None, gh, gw)     # the reference picture as extra tokens
+        if kontext:
+            init_image = None
         if init_image is not None:
-            start = min(1.0, max(0.05, 1.0 - strength))     # high fidelity = little noise
-            start = 1.0 - start if strength <= 1.0 else 1.0
             x0 = m.encode_image(init_image.to(m.device), gh, gw)
-        ts = timesteps(steps, 1.0)
+        ts = m.schedule(steps, gh * gw) if hasattr(m, "schedule") else timesteps(steps, 1.0)
         if init_image is not None:
             skip = min(steps - 1, int(round(steps * (1.0 - strength))))
             ts = ts[skip:]
