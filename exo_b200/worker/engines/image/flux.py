@@ -422,6 +422,13 @@ class FluxModel:
         return torch.stack((torch.full_like(ys, frame), ys, xs), -1).reshape(gh * gw, 3)
 
     def _rope(self, n_txt: int, grid: tuple[int, int], rows: slice | None):
+        key = (n_txt, grid, None if rows is None else (rows.start, rows.stop), self.context_grid if self.context is not None else None)
+        if getattr(self, "_rope_key", None) == key:
+            return self._rope_val
+        self._rope_key, self._rope_val = key, self._rope_tables(n_txt, grid, rows)
+        return self._rope_val
+
+    def _rope_tables(self, n_txt: int, grid: tuple[int, int], rows: slice | None):
         ids = self._ids(*grid)
         if rows is not None:
             ids = ids[rows]
@@ -455,8 +462,20 @@ class FluxModel:
         k, v = torch.cat((kt, ki), 1), torch.cat((vt, vi), 1)
         flat = lambda a: a.transpose(0, 1).reshape(a.shape[1], self.cfg.hidden)     # noqa: E731
         q = torch.cat((qt, qi), 1)                                  # one call over both streams (a 4-D call picks the fused kernel)
-        o = flat(F.scaled_dot_product_attention(q[None], k[None], v[None])[0])
+        o = flat(self._sdpa(q[None], k[None], v[None])[0])
         return o[:nt], o[nt:]
+
+    def _sdpa(self, q, k, v):
+        """Attention through the library's fused kernels; ``EXO_FLUX_SDPA=cudnn|flash|efficient|math`` pins one."""
+        import os
+        pin = os.environ.get("EXO_FLUX_SDPA", "")
+        if not pin or q.device.type != "cuda":
+            return F.scaled_dot_product_attention(q, k, v)
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        which = {"cudnn": SDPBackend.CUDNN_ATTENTION, "flash": SDPBackend.FLASH_ATTENTION, "efficient": SDPBackend.EFFICIENT_ATTENTION,
+                 "math": SDPBackend.MATH}[pin]
+        with sdpa_kernel([which]):
+            return F.scaled_dot_product_attention(q, k, v)
 
     def _joint(self, b: int, txt, img, vec, rope, cache, rows):
         p = f"transformer_blocks.{b}."
