@@ -82,7 +82,8 @@ def is_moe_card(card: ModelCard) -> bool:
     family that has no dense members; their experts are spread over the tensor-parallel ranks."""
     import re
     name = f"{card.model_id} {card.base_model}"
-    return bool(re.search(r"-A\d+(\.\d+)?B\b", name)) or card.family in ("deepseek", "kimi", "minimax") or "MoE" in name
+    return (bool(re.search(r"-A\d+(\.\d+)?B\b", name, re.IGNORECASE)) or card.family in ("deepseek", "kimi", "minimax", "glm", "step")
+            or "MoE" in name or "Coder-Next" in name or "gpt-oss" in name.lower())
 
 
 def _tensor_ok(card: ModelCard, n: int) -> bool:

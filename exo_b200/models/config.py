@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import json
 import math
-from dataclasses import dataclass, field, asdict
+from dataclasses import dataclass, field, asdict, replace
 from pathlib import Path
 from typing import Any
 
@@ -111,6 +111,13 @@ class ModelConfig:
     # "mlp" or "moe" (non-gated relu^2, sigmoid router, shared expert, optional latent projection around the experts)
     block_types: tuple[str, ...] = ()
     moe_latent: int = 0
+    # Step-3.5: per-layer query-head counts, RoPE (base, rotary share, scaling only on some layer types), a sigmoid gate per
+    # head on the attention output, SwiGLU outputs clamped on some layers (0 = not clamped)
+    layer_n_heads: tuple[int, ...] = ()
+    layer_rope: tuple[RopeConfig, ...] = ()
+    head_gate: bool = False
+    swiglu_limits: tuple[float, ...] = ()
+    swiglu_limits_shared: tuple[float, ...] = ()
 
     # -------- derived --------
     @property
@@ -133,6 +140,23 @@ class ModelConfig:
 
     def layer_is_sliding(self, i: int) -> bool:
         return bool(self.layer_types) and self.layer_types[i] == "sliding"
+
+    def q_heads(self, i: int) -> int:
+        """Query heads of layer ``i`` (Step-3.5's sliding-window layers have more than its full-attention layers)."""
+        return self.layer_n_heads[i] if self.layer_n_heads else self.n_heads
+
+    def rope_of(self, i: int) -> RopeConfig:
+        return self.layer_rope[i] if self.layer_rope else self.rope
+
+    def window_of(self, i: int) -> int:
+        """Sliding window of layer ``i`` (0 = every earlier key): per layer type where the model names layer types."""
+        if self.family == "step3p5":
+            return self.sliding_window if self.layer_is_sliding(i) else 0
+        return self.sliding_window
+
+    def swiglu_limit(self, i: int, shared: bool = False) -> float:
+        t = self.swiglu_limits_shared if shared else self.swiglu_limits
+        return float(t[i] or 0.0) if i < len(t) else 0.0
 
     def attn_dims(self, i: int) -> tuple[int, int]:
         """``(KV heads, head_dim)`` of layer ``i`` (Gemma-4's full-attention layers have their own)."""
@@ -231,8 +255,9 @@ class ModelConfig:
             if key in rope_scaling and (key not in cfg or cfg.get("rope_parameters")):
                 cfg = {**cfg, key: rope_scaling[key]}
         kind = rope_scaling.get("rope_type", rope_scaling.get("type", "default"))
+        theta0 = g("rope_theta", default=10000.0)
         rope = RopeConfig(
-            theta=float(g("rope_theta", default=10000.0)),
+            theta=float(theta0[0] if isinstance(theta0, (list, tuple)) else theta0),      # a list: one base per layer (Step-3.5)
             kind=kind if kind in ("default", "linear", "llama3", "yarn") else "default",
             factor=float(rope_scaling.get("factor", 1.0)),
             low_freq_factor=float(rope_scaling.get("low_freq_factor", 1.0)),
@@ -263,7 +288,7 @@ class ModelConfig:
                   "qwen3_next": "qwen3_next", "qwen3_5": "qwen3_next", "qwen3_5_text": "qwen3_next",
                   "qwen3_5_moe": "qwen3_next", "qwen3_5_moe_text": "qwen3_next",
                   "gemma4": "gemma4", "gemma4_text": "gemma4", "nemotron_h": "nemotron_h",
-                  "gpt_oss": "gpt_oss"}.get(mt, "llama")
+                  "gpt_oss": "gpt_oss", "step3p5": "step3p5"}.get(mt, "llama")
         blocks = None
         if family == "nemotron_h":
             blocks = g("layers_block_type", default=None)
@@ -378,6 +403,50 @@ class ModelConfig:
                 mc.norm_topk_prob = True
             if wrapped or mt != "gemma4_text":
                 mc.weight_prefix = "model.language_model."
+        if family == "step3p5":
+            # Step-3.5: one full-attention layer to three sliding-window layers that have more query heads; zero-centred
+            # RMSNorm everywhere (q / k norms included); RoPE base and rotary share per layer, long-context scaling only on
+            # the layer types named; a sigmoid gate per head on the attention output; sigmoid-routed experts with a
+            # selection bias, scaled, plus one shared expert; the first layers dense; SwiGLU clamped on some layers
+            n_l = mc.n_layers
+            types = list(g("layer_types", default=None) or ["full_attention" if i % 4 == 0 else "sliding_attention" for i in range(n_l)])[:n_l]
+            mc.layer_types = tuple("sliding" if t == "sliding_attention" else "full" for t in types)
+            mc.n_kv_heads = g("num_attention_groups", "num_key_value_heads", default=mc.n_kv_heads)
+            mc.sliding_window = int(g("sliding_window", default=512) or 0)
+            other = g("attention_other_setting", default=None) or {}
+            if other:
+                if other.get("num_attention_groups", mc.n_kv_heads) != mc.n_kv_heads or other.get("head_dim", mc.head_dim) != mc.head_dim:
+                    raise ValueError("Step-3.5 layer types with their own KV-head count or head size are not supported")
+                mc.layer_n_heads = tuple(other["num_attention_heads"] if t == other.get("attention_type", "sliding_attention") else mc.n_heads
+                                         for t in types)
+            thetas = g("rope_theta", default=10000.0)
+            thetas = list(thetas) if isinstance(thetas, (list, tuple)) else [thetas] * n_l
+            shares = list(g("partial_rotary_factors", default=None) or [1.0] * n_l)
+            use = list(g("use_rope_layers", default=None) or [True] * n_l)
+            only = g("yarn_only_types", default=None) or []
+            ropes = []
+            for i in range(n_l):
+                scaled = not only or types[i] in only
+                base = mc.rope if scaled else RopeConfig()
+                ropes.append(replace(base, theta=float(thetas[i]), partial_rotary_factor=float(shares[i]) if use[i] else 0.0))
+            mc.layer_rope = tuple(ropes)
+            mc.rope = ropes[0]
+            mc.qk_norm = True
+            mc.norm_one_plus = True
+            mc.head_gate = bool(g("use_head_wise_attn_gate", default=False))
+            mc.n_experts = g("moe_num_experts", default=0) or 0
+            mc.n_experts_per_tok = g("moe_top_k", default=0) or 0
+            mc.moe_ffn = g("moe_intermediate_size", default=0) or 0
+            mc.shared_expert_ffn = g("share_expert_dim", default=0) or 0
+            mc.router = str(g("moe_router_activation", default="sigmoid"))
+            mc.router_bias = bool(g("use_moe_router_bias", default=True))
+            mc.norm_topk_prob = bool(g("norm_expert_weight", default=True))
+            mc.routed_scaling = float(g("moe_router_scaling_factor", default=1.0))
+            enum = g("moe_layers_enum", default=None)
+            moe_layers = {int(x) for x in str(enum).split(",") if x.strip()} if enum is not None else set(range(1, n_l))
+            mc.mlp_only_layers = tuple(i for i in range(n_l) if i not in moe_layers)
+            mc.swiglu_limits = tuple(float(x or 0.0) for x in (g("swiglu_limits", default=None) or ()))
+            mc.swiglu_limits_shared = tuple(float(x or 0.0) for x in (g("swiglu_limits_shared", default=None) or ()))
         if family == "glm4_moe":
             # GLM-4.5 / 4.6: grouped-query attention with half-rotary RoPE and q/k/v biases, DeepSeek-style experts
             # (sigmoid scores + correction bias, shared expert, leading dense layers)
@@ -498,6 +567,15 @@ def preset(name: str) -> ModelConfig:
         return ModelConfig(name="tiny-minimax", family="minimax", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
                            ffn=512, vocab=1024, qk_norm_full=True, rope=RopeConfig(theta=10000.0, partial_rotary_factor=0.5),
                            n_experts=8, n_experts_per_tok=2, moe_ffn=128, router="sigmoid", router_bias=True, dtype="fp32")
+    if n in ("tiny-step3p5",):     # full / sliding layers with different query-head counts and RoPE, head gates, clamped SwiGLU
+        types = ("full", "sliding", "sliding", "full")
+        ropes = tuple(RopeConfig(theta=50000.0 if t == "full" else 10000.0, partial_rotary_factor=0.5 if t == "full" else 1.0) for t in types)
+        return ModelConfig(name="tiny-step3p5", family="step3p5", n_layers=4, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512,
+                           vocab=1024, qk_norm=True, norm_one_plus=True, layer_types=types, sliding_window=24,
+                           layer_n_heads=tuple(8 if t == "sliding" else 4 for t in types), layer_rope=ropes, rope=ropes[0], head_gate=True,
+                           n_experts=8, n_experts_per_tok=2, moe_ffn=128, shared_expert_ffn=128, router="sigmoid", router_bias=True,
+                           norm_topk_prob=True, routed_scaling=3.0, mlp_only_layers=(0,), swiglu_limits=(0.0, 0.0, 0.0, 0.05),
+                           swiglu_limits_shared=(0.0, 0.0, 0.04, 0.04), dtype="fp32")
     if n in ("tiny-gpt-oss",):     # attention sinks and a sliding window on every other layer's worth of context
         return ModelConfig(name="tiny-gpt-oss", family="gpt_oss", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
                            ffn=512, vocab=1024, attn_bias=True, attn_sinks=True, sliding_window=32, dtype="fp32")
@@ -546,4 +624,4 @@ def preset(name: str) -> ModelConfig:
 
 
 PRESETS = ("tiny-llama", "llama-3.1-8b", "llama-3.1-70b", "qwen3-235b-a22b", "deepseek-v3", "tiny-moe", "tiny-mla",
-           "tiny-qwen3", "tiny-qwen2", "tiny-gemma4", "tiny-nemotron-h", "tiny-qwen3-next", "qwen3-next-80b-a3b", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-yarn")
+           "tiny-qwen3", "tiny-qwen2", "tiny-gemma4", "tiny-nemotron-h", "tiny-qwen3-next", "qwen3-next-80b-a3b", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-step3p5", "tiny-yarn")

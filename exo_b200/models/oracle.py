@@ -123,11 +123,16 @@ class OracleModel:
                 scale *= m * m
             n_kv, dv = c.n_heads, c.v_head_dim
         else:
+            n_heads = c.q_heads(i)                                 # Step-3.5: head count, RoPE and window per layer
+            if c.layer_rope:
+                inv_freq, mscale = ref.rope_inv_freq(D, c.rope_of(i))
+            else:
+                inv_freq, mscale = self.inv_freq, self.mscale
             if c.attn_gate:
                 qg = (x @ self.W(p + "q_proj.weight", (c.n_heads * 2 * D, H)).t()).view(T, c.n_heads, 2 * D)
                 q, gate = qg[..., :D].reshape(T, c.n_heads * D), qg[..., D:].reshape(T, c.n_heads * D)
             else:
-                q = x @ self.W(p + "q_proj.weight", (c.n_heads * D, H)).t()
+                q = x @ self.W(p + "q_proj.weight", (n_heads * D, H)).t()
             k = x @ self.W(p + "k_proj.weight", (c.n_kv_heads * D, H)).t()
             v = x @ self.W(p + "v_proj.weight", (c.n_kv_heads * D, H)).t()
             if c.attn_bias:
@@ -137,24 +142,25 @@ class OracleModel:
             if c.qk_norm_full:
                 q = self._norm(q, self.W(p + "q_norm.weight", (c.n_heads * D,)), c.rms_eps)
                 k = self._norm(k, self.W(p + "k_norm.weight", (c.n_kv_heads * D,)), c.rms_eps)
-            q, k, v = q.view(T, c.n_heads, D), k.view(T, c.n_kv_heads, D), v.view(T, c.n_kv_heads, D)
+            q, k, v = q.view(T, n_heads, D), k.view(T, c.n_kv_heads, D), v.view(T, c.n_kv_heads, D)
             if c.qk_norm:
                 q = self._norm(q, self.W(p + "q_norm.weight", (D,)) + self.one, c.rms_eps)
                 k = self._norm(k, self.W(p + "k_norm.weight", (D,)) + self.one, c.rms_eps)
-            q = ref.rope(q, pos, self.inv_freq, self.mscale)
-            k = ref.rope(k, pos, self.inv_freq, self.mscale)
+            q = ref.rope(q, pos, inv_freq, mscale)
+            k = ref.rope(k, pos, inv_freq, mscale)
             scale, n_kv, dv = D ** -0.5, c.n_kv_heads, D
         self.k[i] = k if self.k[i] is None else torch.cat((self.k[i], k), 0)
         self.v[i] = v if self.v[i] is None else torch.cat((self.v[i], v), 0)
         K, V = self.k[i], self.v[i]
         n = K.shape[0]
-        g = c.n_heads // n_kv
+        n_heads = c.n_heads if c.mla else n_heads
+        g = n_heads // n_kv
         sc = torch.einsum("thgd,nhd->hgtn", q.view(T, n_kv, g, -1), K) * scale
         qpos = torch.arange(n - T, n)[:, None]
         keys = torch.arange(n)[None, :]
         vis = keys <= qpos
-        if c.sliding_window:
-            vis &= keys > qpos - c.sliding_window          # the last `window` keys up to and including the query's own
+        if c.window_of(i):
+            vis &= keys > qpos - c.window_of(i)            # the last `window` keys up to and including the query's own
         sc = sc.masked_fill(~vis[None, None], float("-inf"))
         if c.attn_sinks:
             # one learned logit per head joins the softmax and absorbs probability mass, but contributes no value
@@ -162,10 +168,13 @@ class OracleModel:
             pr = torch.softmax(torch.cat((sc, sink), -1), -1)[..., :n]
         else:
             pr = torch.softmax(sc, -1)
-        o = torch.einsum("hgtn,nhd->thgd", pr, V).reshape(T, c.n_heads * dv)
+        o = torch.einsum("hgtn,nhd->thgd", pr, V).reshape(T, n_heads * dv)
         if gate is not None:
             o = o * torch.sigmoid(gate)
-        return o @ self.W(p + "o_proj.weight", (H, c.n_heads * dv)).t()
+        if c.head_gate:          # one sigmoid gate per head, projected from the layer's (normed) input
+            hg = torch.sigmoid(x @ self.W(p + "g_proj.weight", (n_heads, H)).t())
+            o = (o.view(T, n_heads, dv) * hg[..., None]).reshape(T, n_heads * dv)
+        return o @ self.W(p + "o_proj.weight", (H, n_heads * dv)).t()
 
     def _ffn(self, i: int, x: torch.Tensor) -> torch.Tensor:
         from .weights import moe_names
@@ -173,11 +182,17 @@ class OracleModel:
         nm = moe_names(c)
         p = f"{self.cfg.weight_prefix}layers.{i}." + (nm["prefix"] if c.layer_is_moe(i) else "mlp.")
 
-        def mlp(prefix: str, F_: int, t: torch.Tensor, names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")) -> torch.Tensor:
+        def mlp(prefix: str, F_: int, t: torch.Tensor, names=("gate_proj.weight", "up_proj.weight", "down_proj.weight"),
+                limit: float = 0.0) -> torch.Tensor:
             g = t @ self.W(prefix + names[0], (F_, H)).t()
             u = t @ self.W(prefix + names[1], (F_, H)).t()
-            return (F.silu(g) * u) @ self.W(prefix + names[2], (H, F_)).t()
+            a = F.silu(g)
+            if limit:
+                a, u = a.clamp(max=limit), u.clamp(-limit, limit)
+            return (a * u) @ self.W(prefix + names[2], (H, F_)).t()
 
+        if c.family == "step3p5":
+            return self._ffn_step(i, x, mlp)
         if not c.layer_is_moe(i):
             return mlp(p, c.ffn, x)
         logits = x @ self.W(p + "gate.weight", (c.n_experts, H)).t()
@@ -197,6 +212,28 @@ class OracleModel:
                 sh = sh * torch.sigmoid(x @ self.W(p + "shared_expert_gate.weight", (1, H)).t())
             y = y + sh
         return y
+
+    def _ffn_step(self, i: int, x: torch.Tensor, mlp) -> torch.Tensor:
+        """Step-3.5: dense MLP or (stacked) sigmoid-routed experts + shared expert, SwiGLU clamped where the layer says so."""
+        c, H = self.cfg, self.cfg.hidden
+        p = f"{c.weight_prefix}layers.{i}."
+        if not c.layer_is_moe(i):
+            return mlp(p + "mlp.", c.ffn, x, limit=c.swiglu_limit(i, shared=True))
+        E, F_ = c.n_experts, c.moe_ffn
+        logits = x @ self.W(p + "moe.gate.weight", (E, H)).t()
+        wts, ids = ref.moe_route(logits, c.n_experts_per_tok, c.router, c.norm_topk_prob, self.src.get(p + "moe.router_bias", (E,)),
+                                 1, 1, c.routed_scaling)
+        wg, wu, wd = (self.W(p + f"moe.{n}_proj.weight", sh) for n, sh in (("gate", (E, F_, H)), ("up", (E, F_, H)), ("down", (E, H, F_))))
+        lim = c.swiglu_limit(i)
+        y = torch.zeros_like(x)
+        for t in range(x.shape[0]):
+            for j in range(ids.shape[1]):
+                e = int(ids[t, j])
+                a, u = F.silu(x[t] @ wg[e].t()), x[t] @ wu[e].t()
+                if lim:
+                    a, u = a.clamp(max=lim), u.clamp(-lim, lim)
+                y[t] += wts[t, j] * ((a * u) @ wd[e].t())
+        return y + mlp(p + "share_expert.", c.shared_expert_ffn, x, limit=c.swiglu_limit(i, shared=True))
 
     def forward(self, tokens: torch.Tensor, start_pos: int) -> torch.Tensor:
         """Logits ``[T, V]`` for ``tokens [T]`` appended at ``start_pos``."""

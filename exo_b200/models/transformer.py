@@ -204,20 +204,32 @@ class Decoder:
     # ------------------------------------------------------------------ attention
     def _attn_gqa(self, lw, h, inp: StepInputs, kv) -> torch.Tensor:
         cfg = self.cfg
-        qkv = ops.norm_linear(h, lw.attn_norm, cfg.rms_eps, lw.wqkv, lw.bqkv)
+        n_q = lw.n_q or self.n_q                                   # layers may have their own head count, RoPE and window
+        inv_freq, mscale = (self.inv_freq, self.rope_mscale) if lw.inv_freq is None else (lw.inv_freq, lw.rope_mscale)
+        window = cfg.sliding_window if lw.window < 0 else lw.window
+        head_gate = None
+        if lw.w_head_gate is not None:
+            # the gate reads the same normed hidden state as q / k / v: norm once, project twice
+            h, x = reduced_and_normed(h, lw.attn_norm, cfg.rms_eps)
+            qkv = ops.linear(x, lw.wqkv, lw.bqkv)
+            head_gate = torch.nn.functional.linear(x, lw.w_head_gate)
+        else:
+            qkv = ops.norm_linear(h, lw.attn_norm, cfg.rms_eps, lw.wqkv, lw.bqkv)
         kc, vc = kv
         q_norm, k_norm = lw.q_norm, lw.k_norm
         if cfg.qk_norm_full:
             qkv = self._full_width_qk_norm(qkv, lw)
             q_norm = k_norm = None
-        width = (self.n_q + 2 * self.n_kv) * cfg.head_dim
-        q = ops.qk_rope_append(qkv[:, :width] if cfg.attn_gate else qkv, inp.positions, self.inv_freq, self.rope_mscale, self.n_q, self.n_kv,
+        width = (n_q + 2 * self.n_kv) * cfg.head_dim
+        q = ops.qk_rope_append(qkv[:, :width] if cfg.attn_gate else qkv, inp.positions, inv_freq, mscale, n_q, self.n_kv,
                                cfg.head_dim, kc, vc, inp.slots, q_norm, k_norm, cfg.rms_eps)
         o = ops.paged_attention(q, kc, vc, inp.block_tables, inp.seq_lens, inp.cu_q, self.scale,
-                                cfg.sliding_window, lw.sinks, inp.max_q_len)
+                                window, lw.sinks, inp.max_q_len)
+        if head_gate is not None:
+            o = (o.view(o.shape[0], n_q, -1) * torch.sigmoid(head_gate.float())[..., None].to(o.dtype))
         o = o.reshape(o.shape[0], -1)
         if cfg.attn_gate:        # the projection's last n_q*D columns gate the attention output per element
-            o = ops.sigmoid_gate(o, qkv[:, (self.n_q + 2 * self.n_kv) * cfg.head_dim:])
+            o = ops.sigmoid_gate(o, qkv[:, (n_q + 2 * self.n_kv) * cfg.head_dim:])
         return self.comm.row_linear(o, lw.wo, h)
 
     def _attn_linear(self, lw, h, inp: StepInputs, state) -> torch.Tensor:
@@ -275,7 +287,10 @@ class Decoder:
 
     # ------------------------------------------------------------------ ffn
     def _ffn_dense(self, lw, h) -> torch.Tensor:
-        act = ops.norm_linear(h, lw.ffn_norm, self.cfg.rms_eps, lw.w_gate_up, swiglu=True)
+        if lw.shared_limit:      # clamped SwiGLU: the activation is its own op
+            act = ops.swiglu(ops.norm_linear(h, lw.ffn_norm, self.cfg.rms_eps, lw.w_gate_up), lw.shared_limit)
+        else:
+            act = ops.norm_linear(h, lw.ffn_norm, self.cfg.rms_eps, lw.w_gate_up, swiglu=True)
         return self.comm.row_linear(act, lw.w_down, h)
 
     def _ffn_moe(self, lw, h) -> torch.Tensor:
@@ -291,8 +306,10 @@ class Decoder:
         wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, cfg.router, cfg.norm_topk_prob, lw.router_bias,
                                  cfg.n_group, cfg.topk_group, cfg.routed_scaling)
         elo, _ = expert_range(cfg, self.spec)
-        y = ops.moe_experts(x, lw.e_gate_up, lw.e_down, wts, ids, elo, cfg.n_experts)
-        if lw.s_gate is not None:
+        y = ops.moe_experts(x, lw.e_gate_up, lw.e_down, wts, ids, elo, cfg.n_experts, limit=lw.act_limit)
+        if lw.shared_limit and lw.s_gate_up is not None:
+            y = ops.linear(ops.swiglu(ops.linear(x, lw.s_gate_up), lw.shared_limit), lw.s_down, residual=y)
+        elif lw.s_gate is not None:
             # this rank's slice of the shared expert, scaled per token by sigmoid(x . w_gate) (the gate is replicated)
             sh = ops.linear(ops.linear(x, lw.s_gate_up, swiglu=True), lw.s_down)
             y = ops.scaled_add(y, sh, ops.linear(x, lw.s_gate))

@@ -294,6 +294,14 @@ class LayerWeights:
     lin_dt_bias: torch.Tensor | None = None  # [hv] fp32
     lin_norm: torch.Tensor | None = None     # [dv]
     lin_out: torch.Tensor | None = None      # [H, hv*dv] local
+    # per-layer attention parameters where layers differ (Step-3.5); the defaults mean "the model-wide value"
+    n_q: int = 0                             # local query heads
+    inv_freq: torch.Tensor | None = None     # this layer's RoPE frequencies
+    rope_mscale: float = 1.0
+    window: int = -1                         # sliding window (0 = none, -1 = the model's)
+    w_head_gate: torch.Tensor | None = None  # [hq local, H]: one sigmoid gate per head on the attention output
+    act_limit: float = 0.0                   # clamped SwiGLU in the routed experts (0 = plain)
+    shared_limit: float = 0.0                # ... in the shared expert / the dense MLP
 
 
 @dataclass
@@ -426,6 +434,9 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
     if cfg.family == "nemotron_h":
         from .nemotron_h import build_nemotron_h_weights
         return build_nemotron_h_weights(cfg, spec, src, device, progress)
+    if cfg.family == "step3p5":
+        from .step3p5 import build_step3p5_weights
+        return build_step3p5_weights(cfg, spec, src, device, progress)
     dt = _DTYPES[cfg.dtype]
     dev = torch.device(device)
     r, n = spec.tp_rank, spec.tp_size

@@ -50,10 +50,11 @@ def norm_linear(h, norm_w, eps, w, bias=None, swiglu=False):
     return ref.swiglu(y) if swiglu else y
 
 
-def swiglu(gate_up):
+def swiglu(gate_up, limit=0.0):
+    """``silu(gate) * up``; ``limit`` > 0 caps the activated gate at ``limit`` and clamps ``up`` to ``+-limit``."""
     if gate_up.is_cuda:
-        return cuda_ops().swiglu(gate_up)
-    return ref.swiglu(gate_up)
+        return cuda_ops().swiglu(gate_up, limit)
+    return ref.swiglu(gate_up, limit)
 
 
 def qk_rope_append(qkv, positions, inv_freq, mscale, n_q, n_kv, head_dim, kcache, vcache, slots,
@@ -124,12 +125,12 @@ def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling
     return ref.moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling)
 
 
-def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None, act="silu"):
+def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None, act="silu", limit=0.0):
     """Weighted sum of the routed experts.  ``act``: ``silu`` / ``gelu_tanh`` (gated) or ``relu2`` (``w_gate_up`` is then the
     single up projection ``[E, F, H]``)."""
     if x.is_cuda:
-        return cuda_ops().moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, n_experts_total, act)
-    return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, act)
+        return cuda_ops().moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, n_experts_total, act, limit)
+    return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, act, limit)
 
 
 def embedding(table, ids):

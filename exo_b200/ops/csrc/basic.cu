@@ -125,6 +125,32 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, siz
   }
 }
 
+// out[r, c] = min(silu(gu[r, c]), limit) * clamp(gu[r, F + c], -limit, limit)      (Step-3.5's clamped SwiGLU)
+template <typename T>
+__global__ void swiglu_clamp_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t rows, int F, float limit) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t n = rows * (size_t)F;
+  for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    size_t r = i / F;
+    int c = (int)(i - r * F);
+    float g = Cvt<T>::to_f(gu[r * 2 * F + c]), u = Cvt<T>::to_f(gu[r * 2 * F + F + c]);
+    out[i] = Cvt<T>::from_f(fminf(silu_f(g), limit) * fminf(fmaxf(u, -limit), limit));
+  }
+}
+
+EXO_API int exo_swiglu_clamp(const void* gu, void* out, int rows, int F, float limit, int dtype, cudaStream_t st) {
+  size_t n = (size_t)rows * F;
+  if (n == 0) return 0;
+  if (!(limit > 0.f)) return -2;
+  int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (dtype == EXO_BF16)
+    swiglu_clamp_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F, limit);
+  else
+    swiglu_clamp_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)out, rows, F, limit);
+  EXO_CHECK_LAUNCH();
+  return 0;
+}
+
 // out[r, c] = gelu_tanh(gu[r, c]) * gu[r, F + c]
 template <typename T>
 __global__ void geglu_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t rows, int F) {

@@ -342,6 +342,7 @@ struct GroupedParams {
   int f16;                // fp8 kernels: both MMA operands f16 (token rows arrive as f16)
   int out_f16;            // write `out` as f16 (the gate/up result that feeds an f16 down projection)
   int act;                // DUAL kernels: ACT_SWIGLU / ACT_GEGLU; single kernels: ACT_RELU2 squares the rectified output
+  float limit;            // > 0: SwiGLU with the activated gate capped at +limit and the up projection clamped to +-limit (Step-3.5)
 };
 
 // FP8: the weight tiles arrive as bytes in `raw`; eight converter warps widen them into tensor memory, from where
@@ -518,7 +519,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             float y;
             if (DUAL) {   // the projection is rounded to bf16 before the activation, as the unfused form does
               const float gb = __bfloat162float(__float2bfloat16_rn(g[j])), ub = __bfloat162float(__float2bfloat16_rn(u[j]));
-              y = (p.act == ACT_GEGLU ? gelu_tanh_f(gb) : silu_f(gb)) * ub;
+              float a = p.act == ACT_GEGLU ? gelu_tanh_f(gb) : silu_f(gb), ul = ub;
+              if (p.limit > 0.f) { a = fminf(a, p.limit); ul = fminf(fmaxf(ub, -p.limit), p.limit); }
+              y = a * ul;
             } else {
               y = g[j];
               if (p.act == ACT_RELU2) {
@@ -620,7 +623,7 @@ __device__ __forceinline__ float dot_row(const __nv_bfloat16* __restrict__ w, co
 // hs[pair, f] = silu(Wg[e][f] . x[t]) * (Wu[e][f] . x[t])
 __global__ void __launch_bounds__(GV_THREADS)
 moe_gemv_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu, const int* __restrict__ ids,
-                        int k, int H, int F, int expert_offset, int E, int act, __nv_bfloat16* __restrict__ hs) {
+                        int k, int H, int F, int expert_offset, int E, int act, float limit, __nv_bfloat16* __restrict__ hs) {
   extern __shared__ __align__(16) uint8_t gv_smem[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gv_smem);
   const int pair = blockIdx.y;
@@ -639,7 +642,9 @@ moe_gemv_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
     if (lane == 0) {
       g = __bfloat162float(__float2bfloat16_rn(g));
       u = __bfloat162float(__float2bfloat16_rn(u));
-      const float y = act == ACT_RELU2 ? fmaxf(g, 0.f) * fmaxf(g, 0.f) : (act == ACT_GEGLU ? gelu_tanh_f(g) : silu_f(g)) * u;
+      float a = act == ACT_GEGLU ? gelu_tanh_f(g) : silu_f(g);
+      if (limit > 0.f) { a = fminf(a, limit); u = fminf(fmaxf(u, -limit), limit); }
+      const float y = act == ACT_RELU2 ? fmaxf(g, 0.f) * fmaxf(g, 0.f) : a * u;
       hs[(size_t)pair * F + f] = __float2bfloat16_rn(y);
     }
   }
@@ -711,7 +716,7 @@ EXO_API long exo_moe_plan_ints(int E, int max_tiles) { return 3L * E + 1 + 4L * 
 EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const void* w_down, const void* weights,
                                     const void* ids, void* out, void* scratch, void* pos, void* xs, void* hs, void* ys, int T,
                                     int k, int H, int F, int E, int expert_offset, int scale_kind, int tile_rows, int f16_operands,
-                                    int act, cudaStream_t st) {
+                                    int act, float limit, cudaStream_t st) {
   const int f16 = (scale_kind && f16_operands) ? 1 : 0;
   if (T <= 0) return 0;
   if (act < 0 || act > ACT_RELU2 || (act == ACT_RELU2 && scale_kind)) return -2;     // non-gated experts: bf16 weights only
@@ -751,6 +756,7 @@ EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const 
   g.scale_kind = scale_kind;
   g.f16 = f16; g.out_f16 = f16;
   g.act = act;
+  g.limit = act == ACT_SWIGLU ? limit : 0.f;
   g.tiles = scale_kind ? (const uint8_t*)w_gate_up : nullptr;
   g.nt = up_rows / BM; g.kt = H / BK;
   int rc = act == ACT_RELU2 ? grouped_dispatch<false>(bn, t_wgu, t_xs, g, (F + BM - 1) / BM, max_tiles, st)
@@ -759,6 +765,7 @@ EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const 
   g.rows_w = H; g.n_out = H; g.K = F; g.out = (__nv_bfloat16*)ys;
   g.out_f16 = 0;
   g.act = ACT_SWIGLU;
+  g.limit = 0.f;
   g.tiles = scale_kind ? (const uint8_t*)w_down : nullptr;
   g.nt = (H + BM - 1) / BM; g.kt = F / BK;
   rc = grouped_dispatch<false>(bn, t_wd, t_hs, g, (H + BM - 1) / BM, max_tiles, st);
@@ -771,7 +778,8 @@ EXO_API int exo_moe_experts_grouped(const void* x, const void* w_gate_up, const 
 
 // The same block for a handful of tokens: two grouped GEMV kernels, no plan.  `hs` is [T*k, F].
 EXO_API int exo_moe_experts_gemv(const void* x, const void* w_gate_up, const void* w_down, const void* weights, const void* ids,
-                                 void* out, void* hs, int T, int k, int H, int F, int E, int expert_offset, int act, cudaStream_t st) {
+                                 void* out, void* hs, int T, int k, int H, int F, int E, int expert_offset, int act, float limit,
+                                 cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8 || F % 8 || act < 0 || act > ACT_RELU2) return -2;
   const size_t sm1 = (size_t)H * 2, sm2 = (size_t)k * F * 2;
@@ -784,7 +792,8 @@ EXO_API int exo_moe_experts_gemv(const void* x, const void* w_gate_up, const voi
     attr_set = true;
   }
   moe_gemv_gate_up_kernel<<<dim3((F + GV_ROWS - 1) / GV_ROWS, T * k), GV_THREADS, sm1, st>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate_up, (const int*)ids, k, H, F, expert_offset, E, act, (__nv_bfloat16*)hs);
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate_up, (const int*)ids, k, H, F, expert_offset, E, act,
+      act == ACT_SWIGLU ? limit : 0.f, (__nv_bfloat16*)hs);
   moe_gemv_down_kernel<<<dim3((H + GV_ROWS - 1) / GV_ROWS, T), GV_THREADS, sm2, st>>>(
       (const __nv_bfloat16*)hs, (const __nv_bfloat16*)w_down, (const int*)ids, (const float*)weights, k, H, F, expert_offset, E,
       (__nv_bfloat16*)out);

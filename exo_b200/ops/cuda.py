@@ -45,6 +45,7 @@ _p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_long
 class _Sig:
     exo_rmsnorm = (_i, [_p, _p, _p, _p, _p, _i, _i, _f, _i, _p])
     exo_swiglu = (_i, [_p, _p, _i, _i, _i, _p])
+    exo_swiglu_clamp = (_i, [_p, _p, _i, _i, _f, _i, _p])
     exo_moe_experts_gemv_fp8 = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p])
     exo_gated_delta = (_i, [_p, _i, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _i, _p, _p, _i, _p])
     exo_sigmoid_gate = (_i, [_p, _p, _i, _p, _i, _i, _i, _p])
@@ -96,8 +97,8 @@ class _Sig:
     exo_moe_tile_rows = (_i, [_i, _i])
     exo_moe_max_tiles = (_i, [_i, _i, _i])
     exo_moe_plan_ints = (_l, [_i, _i])
-    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p])
-    exo_moe_experts_gemv = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p])
+    exo_moe_experts_grouped = (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p])
+    exo_moe_experts_gemv = (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _p])
 
 
 def _st() -> int:
@@ -186,11 +187,14 @@ def rmsnorm(x, w, eps, residual=None):
     return out, h
 
 
-def swiglu(gate_up):
+def swiglu(gate_up, limit=0.0):
     gate_up = gate_up.contiguous()
     rows, F2 = gate_up.shape
     out = torch.empty(rows, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
-    _chk(load().exo_swiglu(_ptr(gate_up), _ptr(out), rows, F2 // 2, _dt(gate_up), _st()), "swiglu")
+    if limit:
+        _chk(load().exo_swiglu_clamp(_ptr(gate_up), _ptr(out), rows, F2 // 2, float(limit), _dt(gate_up), _st()), "swiglu_clamp")
+    else:
+        _chk(load().exo_swiglu(_ptr(gate_up), _ptr(out), rows, F2 // 2, _dt(gate_up), _st()), "swiglu")
     _count()
     return out
 
@@ -808,8 +812,9 @@ def moe_route(logits, top_k, kind, norm_topk, bias, n_group, topk_group, scaling
 MOE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
 
 
-def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None, act="silu"):
-    """``act``: ``silu`` / ``gelu_tanh`` (gated: ``w_gate_up [E, 2F, H]``) or ``relu2`` (not gated: ``w_gate_up [E, F, H]``)."""
+def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_total=None, act="silu", limit=0.0):
+    """``act``: ``silu`` / ``gelu_tanh`` (gated: ``w_gate_up [E, 2F, H]``) or ``relu2`` (not gated: ``w_gate_up [E, F, H]``).
+    ``limit`` > 0 (with ``silu``): the activated gate is capped at ``limit`` and the up projection clamped to ``+-limit``."""
     T, H = x.shape
     E, F2, _ = w_gate_up.shape
     F, k = (F2 if act == "relu2" else F2 // 2), ids.shape[1]
@@ -821,7 +826,7 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_t
     if fp8:
         ok = ok and isinstance(w_down, Fp8Weight) and H % 64 == 0 and F % 128 == 0
     if not ok:
-        return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, act)
+        return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, act, limit)
     x, ids = x.contiguous(), ids.contiguous().to(torch.int32)
     weights = weights.contiguous().float()
     out = torch.empty(T, H, dtype=x.dtype, device=x.device)
@@ -830,10 +835,10 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_t
     if not fp8 and T <= MOE_GEMV_MAX_TOKENS and H * 2 <= 200 * 1024 and k * F * 2 <= 200 * 1024:
         hs = torch.empty(P, F, dtype=x.dtype, device=x.device)
         _chk(lib.exo_moe_experts_gemv(_ptr(x), _ptr(w_gate_up), _ptr(w_down), _ptr(weights), _ptr(ids), _ptr(out), _ptr(hs),
-                                      T, k, H, F, E, expert_offset, MOE_ACTS[act], _st()), "moe_experts_gemv")
+                                      T, k, H, F, E, expert_offset, MOE_ACTS[act], float(limit), _st()), "moe_experts_gemv")
         _count(2)
         return out
-    if (fp8 and use_moe_gemv_fp8 and T <= MOE_GEMV_MAX_TOKENS and -(-H // 64) * 128 <= 200 * 1024
+    if (fp8 and use_moe_gemv_fp8 and not limit and T <= MOE_GEMV_MAX_TOKENS and -(-H // 64) * 128 <= 200 * 1024
             and k * -(-F // 64) * 128 <= 200 * 1024):
         # a handful of tokens: stream the chosen experts' fp8 tiles on CUDA cores over all SMs (two launches) instead of
         # the grouped tensor-core GEMM, which keeps one CTA per 128 features of a pair busy and the rest of the GPU idle
@@ -859,6 +864,6 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_t
         kind, wgu, wd = 0, w_gate_up.contiguous(), w_down.contiguous()
     _chk(lib.exo_moe_experts_grouped(_ptr(x), _ptr(wgu), _ptr(wd), _ptr(weights), _ptr(ids), _ptr(out),
                                      _ptr(scratch), _ptr(pos), _ptr(xs), _ptr(hs), _ptr(ys), T, k, H, F, E, expert_offset,
-                                     kind, bn, int(fp8_f16_operands), MOE_ACTS[act], _st()), "moe_experts_grouped")
+                                     kind, bn, int(fp8_f16_operands), MOE_ACTS[act], float(limit), _st()), "moe_experts_grouped")
     _count(7)
     return out

@@ -44,10 +44,14 @@ def geglu(gate_up: torch.Tensor) -> torch.Tensor:
     return (torch.nn.functional.gelu(g, approximate="tanh") * u).to(gate_up.dtype)
 
 
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    """``silu(gate) * up`` for ``gate_up = [gate | up]`` concatenated on the last dim."""
+def swiglu(gate_up: torch.Tensor, limit: float = 0.0) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up = [gate | up]`` concatenated on the last dim.  ``limit`` > 0: the activated gate is
+    capped at ``limit`` and ``up`` clamped to ``+-limit`` (Step-3.5)."""
     g, u = gate_up.float().chunk(2, dim=-1)
-    return (F.silu(g) * u).to(gate_up.dtype)
+    a = F.silu(g)
+    if limit:
+        a, u = a.clamp(max=limit), u.clamp(-limit, limit)
+    return (a * u).to(gate_up.dtype)
 
 
 def rope_inv_freq(head_dim: int, rope) -> tuple[torch.Tensor, float]:
@@ -258,7 +262,7 @@ def moe_route(logits: torch.Tensor, top_k: int, kind: str = "softmax", norm_topk
 
 
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, weights: torch.Tensor,
-                ids: torch.Tensor, expert_offset: int = 0, act: str = "silu") -> torch.Tensor:
+                ids: torch.Tensor, expert_offset: int = 0, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """Weighted sum of experts: ``w_gate_up [E, 2F, H]``, ``w_down [E, H, F]``; ``act`` ``silu`` (SwiGLU), ``gelu_tanh``
     (GeGLU) or ``relu2`` (``w_gate_up [E, F, H]``, no gate: ``down(relu(up x)^2)``).
 
@@ -273,7 +277,7 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         if tok.numel() == 0:
             continue
         pre = linear(x[tok], w_gate_up[e])
-        h = swiglu(pre) if act == "silu" else geglu(pre) if act == "gelu_tanh" else torch.relu(pre.float()).pow(2).to(pre.dtype)
+        h = swiglu(pre, limit) if act == "silu" else geglu(pre) if act == "gelu_tanh" else torch.relu(pre.float()).pow(2).to(pre.dtype)
         y = linear(h, w_down[e]).float()
         out.index_add_(0, tok, y * weights[tok, slot][:, None])
     return out.to(x.dtype)

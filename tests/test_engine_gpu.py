@@ -153,6 +153,34 @@ def test_nemotron_h_on_gpu_matches_the_cpu_engine():
     assert outs[0] == outs[1] and all(len(x) == 8 for x in outs[0])
 
 
+def test_step35_on_gpu_matches_the_cpu_engine_and_graphs():
+    """Step-3.5-shaped model (layers with their own query-head count, RoPE and window, a gate per head, sigmoid-routed
+    experts with clamped SwiGLU beside a shared expert): fp32 on the GPU reproduces the CPU engine's tokens with a chunked
+    prompt; bf16 under CUDA graphs equals eager."""
+    cfg = preset("tiny-step3p5")
+    p = oracle_prompt(70, cfg.vocab, seed=3).tolist()
+    want = Engine(cfg, build_weights(cfg, ShardSpec(), RandomSource(seed=0, std=0.05), device="cpu"), n_blocks=64, device="cpu",
+                  prefill_chunk=32).generate(p, SamplingParams(max_tokens=8, **GREEDY))
+    w = build_weights(cfg, ShardSpec(), RandomSource(seed=0, std=0.05), device="cuda")
+    eng = Engine(cfg, w, n_blocks=64, device="cuda", use_graphs=False, prefill_chunk=32)
+    assert eng.generate(p, SamplingParams(max_tokens=8, **GREEDY)) == want
+    cfg = preset("tiny-step3p5")
+    cfg.dtype = "bf16"
+    w = build_weights(cfg, ShardSpec(), RandomSource(seed=0, std=0.05, dtype=torch.bfloat16), device="cuda")
+    prompts = [oracle_prompt(n, cfg.vocab, seed=n).tolist() for n in (50, 31, 77)]
+    outs = []
+    for graphs in (False, True):
+        eng = Engine(cfg, w, n_blocks=128, device="cuda", use_graphs=graphs, max_seqs=4)
+        ids = [eng.submit(q, SamplingParams(max_tokens=12, **GREEDY), use_prefix_cache=False) for q in prompts]
+        got = {i: [] for i in ids}
+        while eng.has_work:
+            for o in eng.step():
+                if o.token is not None:
+                    got[o.req_id].append(o.token)
+        outs.append([got[i] for i in ids])
+    assert outs[0] == outs[1] and all(len(x) == 12 for x in outs[0])
+
+
 def test_gemma4_on_gpu_matches_the_cpu_engine_and_graphs():
     """Gemma-4-shaped model (sliding and full layers with their own head sizes, v = k, shared-KV layers, per-layer inputs,
     soft-capped logits): fp32 on the GPU reproduces the CPU engine's tokens with a chunked prompt; bf16 with CUDA graphs

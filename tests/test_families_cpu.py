@@ -76,6 +76,22 @@ CASES = {
                                 layer_types=("linear", "full", "linear", "full", "linear", "full"), act="relu2", router="sigmoid",
                                 lin_k_heads=2, lin_k_dim=64, lin_v_heads=8, lin_v_dim=32, shared_expert_ffn=96,
                                 weight_prefix="backbone.")),
+    "step3.5": ({"model_type": "step3p5", "architectures": ["Step3p5ForCausalLM"], "num_hidden_layers": 4, "num_attention_groups": 2,
+                 "layer_types": ["full_attention", "sliding_attention", "sliding_attention", "full_attention", "full_attention"],
+                 "sliding_window": 8, "attention_other_setting": {"attention_type": "sliding_attention", "num_attention_heads": 8,
+                                                                  "num_attention_groups": 2, "head_dim": 32},
+                 "use_head_wise_attn_gate": True, "rope_theta": [500000.0, 10000.0, 10000.0, 500000.0, 500000.0],
+                 "partial_rotary_factors": [0.5, 1.0, 1.0, 0.5, 0.5], "yarn_only_types": ["full_attention"],
+                 "rope_scaling": {"rope_type": "llama3", "factor": 2.0, "original_max_position_embeddings": 64, "low_freq_factor": 1.0,
+                                  "high_freq_factor": 4.0},
+                 "moe_num_experts": 8, "moe_top_k": 2, "moe_intermediate_size": 64, "share_expert_dim": 96, "moe_layers_enum": "1,2,3",
+                 "norm_expert_weight": True, "moe_router_activation": "sigmoid", "moe_router_scaling_factor": 3.0,
+                 "use_moe_router_bias": True, "need_fp32_gate": True, "swiglu_limits": [0, 0, 0.08, 0.08, 0],
+                 "swiglu_limits_shared": [0.05, 0, 0, 0.06, 0], "num_nextn_predict_layers": 1, "att_impl_type": "GQA"},
+                dict(family="step3p5", is_moe=True, router="sigmoid", router_bias=True, routed_scaling=3.0, norm_topk_prob=True,
+                     qk_norm=True, norm_one_plus=True, head_gate=True, n_kv_heads=2, layer_n_heads=(4, 8, 8, 4), sliding_window=8,
+                     layer_types=("full", "sliding", "sliding", "full"), mlp_only_layers=(0,), shared_expert_ffn=96, moe_ffn=64,
+                     swiglu_limits=(0.0, 0.0, 0.08, 0.08, 0.0))),
     "qwen2": ({"model_type": "qwen2", "tie_word_embeddings": True}, dict(family="llama", attn_bias=True, tie_embeddings=True)),
 }
 
@@ -99,6 +115,11 @@ def test_config_json_of_each_family_maps_to_engine_fields(name, tmp_path):
         assert cfg.rope.partial_rotary_factor == 0.25 and [cfg.layer_is_moe(i) for i in range(4)] == [True, False, True, True]
     if name == "qwen3.5":
         assert cfg.rope.partial_rotary_factor == 0.5 and cfg.rope.theta == 50000.0
+    if name == "step3.5":
+        assert [cfg.window_of(i) for i in range(4)] == [0, 8, 8, 0] and [cfg.layer_is_moe(i) for i in range(4)] == [False, True, True, True]
+        assert [(r.theta, r.partial_rotary_factor, r.kind) for r in cfg.layer_rope] == [
+            (500000.0, 0.5, "llama3"), (10000.0, 1.0, "default"), (10000.0, 1.0, "default"), (500000.0, 0.5, "llama3")]
+        assert cfg.swiglu_limit(0, shared=True) == 0.05 and cfg.swiglu_limit(2) == 0.08 and cfg.swiglu_limit(9) == 0.0
 
 
 class Recorder(RandomSource):
@@ -151,6 +172,40 @@ def test_checkpoint_under_family_names_loads_and_matches_oracle(name, tmp_path):
     eng = Engine(cfg, w, n_blocks=16, device="cpu")
     got = eng.generate(prompt, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
     assert got == want
+
+
+def test_step35_hub_and_mlx_layouts_load_to_the_same_tokens(tmp_path):
+    """Step-3.5 under the hub export's names (stacked experts under ``moe.``, ``share_expert`` beside it, zero-centred norms, a
+    next-token-prediction layer past the decoder's depth) and under an MLX conversion's (``mlp.switch_mlp`` / ``mlp.gate`` /
+    ``mlp.share_expert``, norm weights with the 1 added): both give the oracle's tokens."""
+    extra, _ = CASES["step3.5"]
+    d = tmp_path / "hub"
+    cfg = write_config(d, extra)
+    cfg.dtype = "fp32"
+    rec = Recorder(seed=5, std=0.05)
+    prompt_t = torch.randint(0, cfg.vocab, (21,), generator=torch.Generator().manual_seed(2))
+    prompt = [int(t) for t in prompt_t]
+    want = OracleModel(cfg, rec).greedy(prompt_t, 6)
+    build_weights(cfg, ShardSpec(), rec, device="cpu")
+    names = set(rec.seen)
+    assert rec.seen["model.layers.1.self_attn.q_proj.weight"].shape == (8 * 32, 128) and rec.seen["model.layers.0.self_attn.g_proj.weight"].shape == (4, 128)
+    assert rec.seen["model.layers.1.moe.gate_proj.weight"].shape == (8, 64, 128) and "model.layers.1.share_expert.down_proj.weight" in names
+    assert "model.layers.0.mlp.gate_proj.weight" in names and "model.layers.1.moe.router_bias" in names
+    hub = {k: v.contiguous() for k, v in rec.seen.items()}
+    hub["model.layers.4.self_attn.q_proj.weight"] = torch.zeros(4, 4)            # a prediction head's layer: never read
+    write_safetensors(d / "model.safetensors", hub)
+    run = lambda folder: Engine(cfg, build_weights(cfg, ShardSpec(), SafetensorsSource(folder, dtype=torch.float32), device="cpu"),   # noqa: E731
+                                n_blocks=16, device="cpu").generate(prompt, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    assert run(d) == want
+    mlx = {}
+    for k, v in rec.seen.items():
+        k2 = (k.replace(".moe.gate.weight", ".mlp.gate.gate.weight").replace(".moe.router_bias", ".mlp.gate.router_bias")
+              .replace(".moe.", ".mlp.switch_mlp.").replace(".share_expert.", ".mlp.share_expert."))
+        mlx[k2] = (v + 1.0 if "norm" in k else v).contiguous()
+    d2 = tmp_path / "mlx"
+    write_config(d2, extra)
+    write_safetensors(d2 / "model.safetensors", mlx)
+    assert run(d2) == want
 
 
 @pytest.mark.parametrize("wrapper,prefix", [("qwen3_vl", "model.language_model."), ("kimi_vl", "language_model.model.")])

@@ -260,6 +260,8 @@ def test_swiglu_embedding_argmax(K):
     g = torch.Generator(device="cuda").manual_seed(5)
     gu = torch.randn(7, 2 * 300, device="cuda", generator=g).bfloat16()
     close(K.swiglu(gu), ref.swiglu(gu.float()))
+    close(K.swiglu(gu, 0.6), ref.swiglu(gu.float(), 0.6))                       # capped gate, clamped up projection
+    assert float(K.swiglu(gu, 0.6).float().abs().max()) <= 0.36 + 1e-3 and float(K.swiglu(gu).float().abs().max()) > 0.5
     table = torch.randn(1000, 256, device="cuda", generator=g).bfloat16()
     ids = torch.randint(0, 1000, (33,), device="cuda", generator=g).int()
     assert torch.equal(K.embedding(table, ids), table[ids.long()])
@@ -398,6 +400,29 @@ def test_moe_experts_other_activations(K, act, T, E, k, H, F, offset, E_all):
     want = ref.moe_experts(x, wup, wd, w, ids, offset, act)
     assert K.load().exo_gemm_last_error() == 0
     close(out, want, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("T,E,k,H,F,offset,E_all", [(2, 8, 2, 256, 128, 0, 8), (300, 16, 8, 512, 384, 32, 64)])
+def test_moe_experts_clamped_swiglu(K, T, E, k, H, F, offset, E_all):
+    """Step-3.5's clamped SwiGLU in the routed experts: grouped GEMV and grouped tcgen05 paths, bf16 and block-scaled fp8."""
+    from exo_b200.ops import quant
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    wgu = (torch.randn(E, 2 * F, H, device="cuda", generator=g) / math.sqrt(H)).bfloat16()
+    wd = (torch.randn(E, H, F, device="cuda", generator=g) / math.sqrt(F)).bfloat16()
+    w, ids = ref.moe_route(torch.randn(T, E_all, device="cuda", generator=g), k, "softmax", True)
+    lim = 0.4
+    out = K.moe_experts(x, wgu, wd, w, ids, offset, None, "silu", lim)
+    want = ref.moe_experts(x, wgu, wd, w, ids, offset, "silu", lim)
+    assert K.load().exo_gemm_last_error() == 0
+    close(out, want, 2e-2, 2e-2)
+    plain = ref.moe_experts(x, wgu, wd, w, ids, offset)
+    assert float((want.float() - plain.float()).abs().max()) > 0.05           # the limit bites at these magnitudes
+    if H % 64 == 0 and F % 128 == 0:
+        qgu, qd = quant.quantize(wgu, "mxfp8"), quant.quantize(wd, "mxfp8")
+        out8 = K.moe_experts(x, qgu, qd, w, ids, offset, None, "silu", lim)
+        want8 = ref.moe_experts(x, qgu, qd, w, ids, offset, "silu", lim)
+        close(out8, want8, 3e-2, 3e-2)
 
 
 @pytest.mark.parametrize("kind", ["mxfp8", "dsfp8"])

@@ -171,3 +171,18 @@ def test_builtin_cards_load():
     c = card_cache.get("meta-llama/Llama-3.1-8B-Instruct")
     assert c is not None and c.n_layers == 32 and c.sampling_defaults.temperature == 0.6
     assert len(card_cache.list_all()) >= 30
+
+
+def test_cards_of_every_served_family_load_and_place():
+    """One card per family the engine loads: the sparse ones are recognised as such by the planner, vision shows as a capability."""
+    from exo_b200.master.placement import is_moe_card
+    cards = {str(c.model_id): c for c in card_cache.list_all()}
+    assert len(cards) >= 120
+    for mid, moe in (("mlx-community/Step-3.5-Flash-8Bit", True), ("mlx-community/Qwen3-Next-80B-A3B-Instruct-8bit", True),
+                     ("mlx-community/Qwen3.5-9B-8bit", False), ("mlx-community/gemma-4-26b-a4b-it-8bit", True),
+                     ("mlx-community/gemma-4-31b-it-8bit", False), ("mlx-community/NVIDIA-Nemotron-3-Nano-30B-A3B-MLX-8Bit", True),
+                     ("mlx-community/GLM-4.7-8bit-gs32", True), ("mlx-community/MiniMax-M2.5-8bit", True),
+                     ("mlx-community/Qwen3-Coder-Next-8bit", True), ("meta-llama/Llama-3.1-8B-Instruct", False)):
+        assert mid in cards and is_moe_card(cards[mid]) is moe, mid
+    assert "vision" in cards["mlx-community/Qwen3.5-9B-8bit"].capabilities and cards["mlx-community/Step-3.5-Flash-8Bit"].n_layers == 45
+    assert all(c.backends and c.storage_size.in_bytes > 0 for c in cards.values())

@@ -46,7 +46,8 @@ FAMILIES = [("tiny-llama", 2), ("tiny-llama", 4), ("tiny-moe", 2), ("tiny-mla", 
             ("tiny-minimax", 2), ("tiny-minimax", 4), ("tiny-gpt-oss", 2), ("tiny-yarn", 2),
             ("tiny-qwen3-next", 2),     # gated-delta-rule heads split by key-head group, state per rank
             ("tiny-gemma4", 2),         # per-layer head sizes, one global KV head on two ranks, replicated per-layer inputs
-            ("tiny-nemotron-h", 2)]     # Mamba-2 heads and groups split, relu^2 experts whole, shared expert sliced
+            ("tiny-nemotron-h", 2),     # Mamba-2 heads and groups split, relu^2 experts whole, shared expert sliced
+            ("tiny-step3p5", 2)]        # per-layer query-head counts and RoPE, head gates split with the heads, clamped SwiGLU
 
 
 @pytest.mark.parametrize("name,world", FAMILIES)
