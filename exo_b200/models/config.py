@@ -570,9 +570,9 @@ def preset(name: str) -> ModelConfig:
     if n in ("tiny-step3p5",):     # full / sliding layers with different query-head counts and RoPE, head gates, clamped SwiGLU
         types = ("full", "sliding", "sliding", "full")
         ropes = tuple(RopeConfig(theta=50000.0 if t == "full" else 10000.0, partial_rotary_factor=0.5 if t == "full" else 1.0) for t in types)
-        return ModelConfig(name="tiny-step3p5", family="step3p5", n_layers=4, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512,
+        return ModelConfig(name="tiny-step3p5", family="step3p5", n_layers=4, hidden=256, n_heads=2, n_kv_heads=2, head_dim=128, ffn=512,
                            vocab=1024, qk_norm=True, norm_one_plus=True, layer_types=types, sliding_window=24,
-                           layer_n_heads=tuple(8 if t == "sliding" else 4 for t in types), layer_rope=ropes, rope=ropes[0], head_gate=True,
+                           layer_n_heads=tuple(4 if t == "sliding" else 2 for t in types), layer_rope=ropes, rope=ropes[0], head_gate=True,
                            n_experts=8, n_experts_per_tok=2, moe_ffn=128, shared_expert_ffn=128, router="sigmoid", router_bias=True,
                            norm_topk_prob=True, routed_scaling=3.0, mlp_only_layers=(0,), swiglu_limits=(0.0, 0.0, 0.0, 0.05),
                            swiglu_limits_shared=(0.0, 0.0, 0.04, 0.04), dtype="fp32")
