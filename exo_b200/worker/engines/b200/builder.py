@@ -121,12 +121,12 @@ class ServingEngine(Engine):
     # ---- images ----
     def _checkpoint_vision(self, device, dtype):
         """``(processor, tower, placeholder token, wrap)`` built from the model's own checkpoint when it carries a vision
-        tower this engine knows (Qwen2-VL family, Gemma-4); ``None`` otherwise (the generic tower then stands in).
+        tower this engine knows (Qwen2-VL, Qwen3-VL / Qwen3.5, Gemma-4, Kimi-K2.5); ``None`` otherwise (the generic tower then stands in).
         ``wrap``: tokens put before and after an image's soft tokens."""
         import json
         from ....models.weights import SafetensorsSource
-        from .vision_families import (Gemma4Processor, Gemma4VisionConfig, Gemma4VisionTower, QwenVLProcessor, QwenVLTower,
-                                      QwenVLTowerConfig, family_for)
+        from .vision_families import (Gemma4Processor, Gemma4VisionConfig, Gemma4VisionTower, KimiTower, KimiTowerConfig, KimiVLProcessor,
+                                      QwenVLProcessor, QwenVLTower, QwenVLTowerConfig, family_for)
         d = find_model_dir(self.model_id)
         if d is None or not (d / "config.json").exists() or not any(d.glob("*.safetensors")):
             return None
@@ -147,6 +147,11 @@ class ServingEngine(Engine):
             wrap = (config.get("boi_token_id") or tok_id(getattr(self.tok, "boi_token", "<|image>")),
                     config.get("eoi_token_id") or tok_id(getattr(self.tok, "eoi_token", "<image|>")))
             return proc, tower, ph, wrap
+        if isinstance(proc, KimiVLProcessor) and str(config.get("model_type")) in ("kimi_k25", "kimi_k2_5"):
+            if not any(n.startswith("vision_tower.") for n in names):
+                return None
+            tower = KimiTower.from_source(src, KimiTowerConfig.from_config(config.get("vision_config") or {}), device, dtype)
+            return proc, tower, config.get("media_placeholder_token_id") or tok_id("<|media_pad|>"), None
         if isinstance(proc, QwenVLProcessor):
             # Qwen2-VL and the Qwen3-VL line (Qwen3.5 / 3.6 included); the windowed Qwen2.5-VL tower is not built
             prefix = next((p for p in ("visual.", "model.visual.", "vision_tower.") if any(n.startswith(p) for n in names)), None)

@@ -509,3 +509,130 @@ class Gemma4VisionTower:
         if c.standardize:
             x = (x - w["std_bias"]) * w["std_scale"]
         return self._norm(x, None) @ w["embed_vision.embedding_projection.weight"].t()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Kimi-K2.5 / K2.6: MoonViT with a resampled 2-D position table, 2-D rotary positions, 2x2 merge, MLP projector
+# ---------------------------------------------------------------------------------------------------------------------
+@dataclass
+class KimiTowerConfig:
+    patch: int = 14
+    pos_h: int = 64                   # the learned position table's grid
+    pos_w: int = 64
+    pos_t: int = 4
+    heads: int = 16
+    layers: int = 27
+    hidden: int = 1152
+    mlp_dim: int = 4304
+    merge: tuple[int, int] = (2, 2)
+    out_hidden: int = 1152            # the decoder's hidden size
+    proj_eps: float = 1e-5
+
+    @classmethod
+    def from_config(cls, vc: dict[str, Any]) -> "KimiTowerConfig":
+        h = vc.get("hidden_size", 1152)
+        return cls(patch=vc.get("patch_size", 14), pos_h=vc.get("init_pos_emb_height", 64), pos_w=vc.get("init_pos_emb_width", 64),
+                   pos_t=vc.get("init_pos_emb_time", 4), heads=vc.get("num_attention_heads", 16), layers=vc.get("num_hidden_layers", 27),
+                   hidden=h, mlp_dim=vc.get("intermediate_size", 4304), merge=tuple(vc.get("merge_kernel_size", (2, 2))),
+                   out_hidden=vc.get("mm_hidden_size") or h, proj_eps=vc.get("projector_ln_eps", 1e-5))
+
+
+@dataclass
+class KimiTower:
+    """The Kimi-K2.5 vision tower and projector over ``KimiVLProcessor`` patches.
+
+    ``weights``: the checkpoint's ``vision_tower.*`` tensors without that prefix (``patch_embed.proj``, ``patch_embed.pos_emb.weight``
+    ``[H, W, C]``, ``encoder.blocks.N.{norm0,norm1,wqkv,wo,mlp.fc0,mlp.fc1}``, ``encoder.final_layernorm``) and the projector's
+    as ``mm_projector.{pre_norm,proj.0,proj.2}`` (or ``linear_1`` / ``linear_2``).  A patch is a ``patch x patch`` convolution;
+    the learned position table is resampled bicubically to the image's grid (frames after the first add a fixed sinusoid of
+    the frame index); rotary positions turn adjacent channel pairs, alternately by column and by row; attention is full
+    within one image (all of its frames) and never crosses images; the ``merge`` neighbours of the frame-averaged grid are
+    normalised one by one, joined, and mapped to the decoder's width by a two-layer GELU MLP."""
+    cfg: KimiTowerConfig
+    weights: dict[str, torch.Tensor]
+    device: torch.device = field(default_factory=lambda: torch.device("cpu"))
+    dtype: torch.dtype = torch.float32
+
+    def __post_init__(self) -> None:
+        self.w = {k: v.to(device=self.device, dtype=self.dtype) for k, v in self.weights.items()}
+        for old, new in (("mm_projector.linear_1.", "mm_projector.proj.0."), ("mm_projector.linear_2.", "mm_projector.proj.2.")):
+            for k in [k for k in self.w if k.startswith(old)]:
+                self.w[new + k[len(old):]] = self.w.pop(k)
+
+    @classmethod
+    def from_source(cls, src, cfg: KimiTowerConfig, device, dtype, prefix: str = "vision_tower.", projector: str = "mm_projector.") -> "KimiTower":
+        names = [n for n in src.names() if n.startswith(prefix)]
+        if not names:
+            raise KeyError(f"checkpoint has no {prefix}* tensors")
+        w = {n[len(prefix):]: src.get(n, None) for n in names}
+        w.update({"mm_projector." + n[len(projector):]: src.get(n, None) for n in src.names() if n.startswith(projector)})
+        return cls(cfg, w, torch.device(device), dtype)
+
+    def _positions(self, grid_thw: list[tuple[int, int, int]]) -> torch.Tensor:
+        c, tab = self.cfg, self.w["patch_embed.pos_emb.weight"]
+        out = []
+        for t, h, w in grid_thw:
+            e = tab if (h, w) == tuple(tab.shape[:2]) else \
+                F.interpolate(tab.permute(2, 0, 1)[None].float(), size=(h, w), mode="bicubic")[0].permute(1, 2, 0).to(tab.dtype)
+            e = e.reshape(h * w, -1)
+            if t > 1:
+                half = c.hidden // 2
+                omega = 1.0 / 10000 ** (torch.arange(half, dtype=torch.float32, device=self.device) / half)
+                ang = torch.arange(t, dtype=torch.float32, device=self.device)[:, None] * omega
+                e = (e[None] + torch.cat((ang.sin(), ang.cos()), 1)[:, None].to(e.dtype)).reshape(t * h * w, -1)
+            out.append(e)
+        return torch.cat(out)
+
+    def _rotary(self, grid_thw: list[tuple[int, int, int]]) -> tuple[torch.Tensor, torch.Tensor]:
+        hd = self.cfg.hidden // self.cfg.heads
+        f = 1.0 / (10000.0 ** (torch.arange(0, hd, 4, dtype=torch.float32, device=self.device)[: hd // 4] / hd))
+        angs = []
+        for t, h, w in grid_thw:
+            ys, xs = torch.meshgrid(torch.arange(h, device=self.device), torch.arange(w, device=self.device), indexing="ij")
+            a = torch.stack((xs.reshape(-1, 1).float() * f, ys.reshape(-1, 1).float() * f), -1).reshape(h * w, hd // 2)
+            angs.append(a.repeat(t, 1))
+        ang = torch.cat(angs)                                                    # [N, hd/2]: x, y, x, y, ... per frequency
+        return ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    @staticmethod
+    def _turn(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        a, b = x.float().reshape(*x.shape[:-1], -1, 2).unbind(-1)
+        return torch.stack((a * cos - b * sin, a * sin + b * cos), -1).flatten(-2).to(x.dtype)
+
+    def _lin(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        return F.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
+
+    @torch.no_grad()
+    def __call__(self, patches: torch.Tensor, grid: torch.Tensor) -> torch.Tensor:
+        """``patches [N, 3, patch, patch]``, ``grid [n, 2]`` (h, w) or ``[n, 3]`` (t, h, w) → ``[sum h*w/merge, out_hidden]``."""
+        c, w = self.cfg, self.w
+        g = [(1, int(r[0]), int(r[1])) if len(r) == 2 else (int(r[0]), int(r[1]), int(r[2])) for r in grid.tolist()]
+        E, H = c.hidden, c.heads
+        x = F.conv2d(patches.to(device=self.device, dtype=self.dtype), w["patch_embed.proj.weight"], w.get("patch_embed.proj.bias"),
+                     stride=c.patch).reshape(patches.shape[0], E)
+        x = x + self._positions(g)
+        cos, sin = self._rotary(g)
+        spans = [t * h * ww for t, h, ww in g]
+        for i in range(c.layers):
+            b = f"encoder.blocks.{i}."
+            y = F.layer_norm(x, (E,), w[b + "norm0.weight"], w[b + "norm0.bias"])
+            q, k, v = self._lin(y, b + "wqkv").view(-1, 3, H, E // H).unbind(1)
+            q, k = self._turn(q, cos, sin), self._turn(k, cos, sin)
+            outs, o = [], 0
+            for n in spans:
+                qs, ks, vs = (t[o:o + n].transpose(0, 1)[None] for t in (q, k, v))
+                outs.append(F.scaled_dot_product_attention(qs, ks, vs)[0].transpose(0, 1).reshape(n, E))
+                o += n
+            x = x + self._lin(torch.cat(outs), b + "wo")
+            y = F.layer_norm(x, (E,), w[b + "norm1.weight"], w[b + "norm1.bias"])
+            x = x + self._lin(F.gelu(self._lin(y, b + "mlp.fc0"), approximate="tanh"), b + "mlp.fc1")
+        x = F.layer_norm(x, (E,), w["encoder.final_layernorm.weight"], w["encoder.final_layernorm.bias"])
+        kh, kw = c.merge
+        merged, o = [], 0
+        for (t, h, ww), n in zip(g, spans):
+            v = x[o:o + n].view(t, h // kh, kh, ww // kw, kw, E).mean(0)           # frames are averaged before the merge
+            merged.append(v.permute(0, 2, 1, 3, 4).reshape(-1, kh * kw, E))
+            o += n
+        m = torch.cat(merged)
+        m = F.layer_norm(m, (E,), w["mm_projector.pre_norm.weight"], w["mm_projector.pre_norm.bias"], c.proj_eps).view(-1, kh * kw * E)
+        return self._lin(F.gelu(self._lin(m, "mm_projector.proj.0")), "mm_projector.proj.2")

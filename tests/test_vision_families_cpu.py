@@ -208,3 +208,63 @@ def test_serving_engine_uses_the_checkpoints_own_tower(tmp_path):
     assert ids == [2, 11, 5] + [7] * n + [6, 12, 5] + [7] * n + [6, 13]
     assert [p for p, _ in embeds] == [3, 3 + n + 3] and [(a, b) for a, b, _ in media] == [(3, 3 + n), (6 + n, 6 + 2 * n)]
     assert embeds[0][1].shape == (n, 96) and torch.equal(embeds[0][1], embeds[1][1])
+
+
+def test_kimi_k25_tower_matches_its_parts_in_vllm():
+    """The Kimi-K2.5 tower against a model assembled from the pure-PyTorch pieces of the vLLM implementation in this image
+    (patch embedding + position table, 2-D rotary tables and their application, the frame-pooling merger) with plain linear
+    layers in place of its tensor-parallel ones."""
+    kv = pytest.importorskip("vllm.model_executor.models.kimi_k25_vit")
+    import torch.nn.functional as F
+    from exo_b200.worker.engines.b200.vision_families import KimiTower, KimiTowerConfig
+    torch.manual_seed(0)
+    cfg = KimiTowerConfig(patch=14, pos_h=6, pos_w=4, pos_t=4, heads=2, layers=2, hidden=32, mlp_dim=48, out_hidden=40)
+    E, H = cfg.hidden, cfg.heads
+    embed = kv.MoonVision3dPatchEmbed(out_dim=E, patch_size=14, pos_emb_height=6, pos_emb_width=4, pos_emb_time=4).float()
+    rope = kv.Rope2DPosEmbRepeated(E // H, 64, 64)
+    w = {"patch_embed.proj.weight": embed.proj.weight.detach(), "patch_embed.proj.bias": embed.proj.bias.detach(),
+         "patch_embed.pos_emb.weight": embed.pos_emb.weight.detach()}
+    lin = lambda o, i: (torch.randn(o, i) * 0.2, torch.randn(o) * 0.1)          # noqa: E731
+    for i in range(cfg.layers):
+        b = f"encoder.blocks.{i}."
+        for n, (o, k) in {"wqkv": (3 * E, E), "wo": (E, E), "mlp.fc0": (cfg.mlp_dim, E), "mlp.fc1": (E, cfg.mlp_dim)}.items():
+            w[b + n + ".weight"], w[b + n + ".bias"] = lin(o, k)
+        for n in ("norm0", "norm1"):
+            w[b + n + ".weight"], w[b + n + ".bias"] = 1 + torch.randn(E) * 0.1, torch.randn(E) * 0.1
+    w["encoder.final_layernorm.weight"], w["encoder.final_layernorm.bias"] = 1 + torch.randn(E) * 0.1, torch.randn(E) * 0.1
+    w["mm_projector.pre_norm.weight"], w["mm_projector.pre_norm.bias"] = 1 + torch.randn(E) * 0.1, torch.randn(E) * 0.1
+    w["mm_projector.linear_1.weight"], w["mm_projector.linear_1.bias"] = lin(4 * E, 4 * E)      # vLLM's names for proj.0 / proj.2
+    w["mm_projector.linear_2.weight"], w["mm_projector.linear_2.bias"] = lin(cfg.out_hidden, 4 * E)
+    grid = torch.tensor([[1, 6, 4], [2, 6, 4]])                                  # the table's own grid: no resampling on that side
+    n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    patches = torch.randn(n, 3, 14, 14)
+    with torch.no_grad():
+        x = embed(patches, grid)
+        fc = rope.get_freqs_cis(grid, torch.device("cpu"))
+        spans = (grid[:, 0] * grid[:, 1] * grid[:, 2]).tolist()
+        for i in range(cfg.layers):
+            b = f"encoder.blocks.{i}."
+            y = F.layer_norm(x, (E,), w[b + "norm0.weight"], w[b + "norm0.bias"])
+            q, k, v = F.linear(y, w[b + "wqkv.weight"], w[b + "wqkv.bias"]).view(n, 3, H, E // H).unbind(1)
+            q, k = kv.apply_rope(q, k, fc)
+            outs, o = [], 0
+            for s in spans:
+                outs.append(F.scaled_dot_product_attention(*(t[o:o + s].transpose(0, 1)[None] for t in (q, k, v)))[0].transpose(0, 1).reshape(s, E))
+                o += s
+            x = x + F.linear(torch.cat(outs), w[b + "wo.weight"], w[b + "wo.bias"])
+            y = F.layer_norm(x, (E,), w[b + "norm1.weight"], w[b + "norm1.bias"])
+            x = x + F.linear(F.gelu(F.linear(y, w[b + "mlp.fc0.weight"], w[b + "mlp.fc0.bias"]), approximate="tanh"), w[b + "mlp.fc1.weight"], w[b + "mlp.fc1.bias"])
+        x = F.layer_norm(x, (E,), w["encoder.final_layernorm.weight"], w["encoder.final_layernorm.bias"])
+        m = torch.cat(kv.tpool_patch_merger(x, grid, (2, 2)))
+        m = F.layer_norm(m, (E,), w["mm_projector.pre_norm.weight"], w["mm_projector.pre_norm.bias"], 1e-5).view(-1, 4 * E)
+        want = F.linear(F.gelu(F.linear(m, w["mm_projector.linear_1.weight"], w["mm_projector.linear_1.bias"])),
+                        w["mm_projector.linear_2.weight"], w["mm_projector.linear_2.bias"])
+    got = KimiTower(cfg, dict(w))(patches, grid)
+    assert got.shape == want.shape == (2 * 6 * 4 // 4, cfg.out_hidden)
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-4), float((got - want).abs().max())
+    # another grid: the position table is resampled bicubically
+    tower = KimiTower(cfg, dict(w))
+    e = tower._positions([(1, 8, 6)])
+    ref_e = F.interpolate(w["patch_embed.pos_emb.weight"].permute(2, 0, 1)[None], size=(8, 6), mode="bicubic")[0].permute(1, 2, 0).reshape(48, E)
+    assert torch.allclose(e, ref_e, atol=1e-6)
+    assert tower(torch.randn(48, 3, 14, 14), torch.tensor([[8, 6]])).shape == (12, cfg.out_hidden)
