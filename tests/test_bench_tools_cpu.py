@@ -145,3 +145,119 @@ def test_harness_resolves_places_frees_disk_downloads_and_launches():
     h.teardown()
     assert not fc.state_["instances"]
     assert len(h.placements(model, "Pipeline", "nvlink", 1, 0, 1.0)) == 1 and h.placements(model, "Tensor", "ring", 1, 0, 0.0) == []
+
+
+def test_tool_call_eval_runs_every_dialect_with_followups_and_scenario_files(tmp_path):
+    """The evaluator against a scripted HTTP server: chat / Messages / Responses request forms, history translation,
+    a no-call scenario, the follow-up turn after a tool result, nested array arguments, scenario files."""
+    import json
+    import threading
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+    from exo_b200.bench import eval_tool_calls as etc
+    from exo_b200.bench.client import ExoClient
+    seen = []
+
+    def answer(path, body):
+        """Call `get_weather` / `add` / `write_todos` when the last turn asks for it; answer in text after a tool result."""
+        seen.append((path, body))
+        if path == "/v1/chat/completions":
+            msgs, last = body["messages"], body["messages"][-1]
+            after_result = last["role"] == "tool" and len([m for m in msgs if m["role"] == "tool"]) == (2 if "Rome" in msgs[0]["content"] else 1)
+            text = msgs[0]["content"]
+        elif path == "/v1/messages":
+            last = body["messages"][-1]
+            results = sum(b["type"] == "tool_result" for m in body["messages"] if isinstance(m["content"], list) for b in m["content"])
+            text = body["messages"][0]["content"]
+            after_result = isinstance(last["content"], list) and last["content"][0]["type"] == "tool_result" and results == (2 if "Rome" in text else 1)
+        else:
+            items = body["input"]
+            text = items[0]["content"]
+            after_result = items[-1].get("type") == "function_call_output" and \
+                sum(i.get("type") == "function_call_output" for i in items) == (2 if "Rome" in text else 1)
+        call = None
+        if not after_result and "Do not use any tool" not in text:
+            call = ("get_weather", {"city": "Rome" if "Rome" in text else "Paris"}) if "weather" in text else \
+                ("write_todos", {"todos": [{"title": "buy milk", "done": False}, {"title": "call Ana", "done": True}]}) if "to-do" in text else \
+                ("add", {"a": 17, "b": 25})
+        if path == "/v1/chat/completions":
+            m = {"role": "assistant", "content": None if call else "Bonjour / done."}
+            if call:
+                m["tool_calls"] = [{"id": "c9", "type": "function", "function": {"name": call[0], "arguments": json.dumps(call[1])}}]
+            return {"choices": [{"message": m, "finish_reason": "tool_calls" if call else "stop"}]}
+        if path == "/v1/messages":
+            return {"content": [{"type": "tool_use", "id": "tu1", "name": call[0], "input": call[1]}] if call else [{"type": "text", "text": "Bonjour."}],
+                    "stop_reason": "tool_use" if call else "end_turn"}
+        return {"status": "completed", "output": [{"type": "function_call", "call_id": "fc1", "name": call[0], "arguments": json.dumps(call[1])}] if call
+                else [{"type": "message", "content": [{"type": "output_text", "text": "Bonjour."}]}]}
+
+    class H(BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            out = json.dumps(answer(self.path, body)).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(out)))
+            self.end_headers()
+            self.wfile.write(out)
+
+        def log_message(self, *a):
+            pass
+    srv = HTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        c = ExoClient("127.0.0.1", srv.server_address[1])
+        rows = [etc.run_scenario(c, "m", sc, d) for sc in etc.BUILTIN for d in ("chat", "claude", "responses")]
+        assert all(r["passed"] for r in rows), [r for r in rows if not r["passed"]]
+        s = etc.summarize(rows)
+        assert s["passed"] == s["total"] == 15 and s["by_dialect"]["claude"] == {"passed": 5, "total": 5}
+        assert sum(r.get("followup_ok", False) for r in rows) == 6                # weather and add, three dialects each
+        # the history with an earlier call and its result reaches each dialect in its own form
+        hist = [b for p, b in seen if p == "/v1/messages" and "Rome" in str(b["messages"][0]["content"])][0]["messages"]
+        assert hist[1]["content"][0] == {"type": "tool_use", "id": "call_1", "name": "get_weather", "input": {"city": "Paris"}}
+        assert hist[2]["content"][0]["type"] == "tool_result" and hist[2]["content"][0]["tool_use_id"] == "call_1"
+        resp = [b for p, b in seen if p == "/v1/responses" and "Rome" in str(b["input"][0].get("content"))][0]["input"]
+        assert [i.get("type", "message") for i in resp] == ["message", "function_call", "function_call_output"]
+        # a model that calls a tool where none is wanted, or answers in text where one is, fails
+        bad = etc.Scenario("x", [{"role": "user", "content": "What is the weather in Paris?"}], [etc.WEATHER], expect_call=False)
+        assert not etc.run_scenario(c, "m", bad, "chat")["passed"]
+        bad2 = etc.Scenario("y", [{"role": "user", "content": "Say hi. Do not use any tool."}], [etc.WEATHER], expect="get_weather", required=["city"])
+        assert not etc.run_scenario(c, "m", bad2, "responses")["passed"]
+    finally:
+        srv.shutdown()
+    # scenario files
+    (tmp_path / "s.toml").write_text("""
+[tools.lookup]
+description = "Look a word up"
+required = ["word"]
+[tools.lookup.properties.word]
+type = "string"
+
+[[scenarios]]
+name = "lookup"
+description = "one call"
+expect_tool_call = true
+expected_function = "lookup"
+required_arg_keys = ["word"]
+tools = ["lookup"]
+tool_result = { meaning = "a greeting" }
+[[scenarios.messages]]
+role = "user"
+content = "Look up 'hello'."
+[[scenarios.messages]]
+role = "assistant"
+tool_calls = [{ id = "a1", name = "lookup", arguments = { word = "hi" } }]
+[[scenarios.messages]]
+role = "tool"
+tool_call_id = "a1"
+content = "short for hello"
+""")
+    (sc,) = etc.load_scenarios(tmp_path / "s.toml")
+    assert sc.expect == "lookup" and sc.tools[0]["function"]["parameters"]["required"] == ["word"] and sc.tool_result == {"meaning": "a greeting"}
+    assert json.loads(sc.messages[1]["tool_calls"][0]["function"]["arguments"]) == {"word": "hi"} and sc.prompt == "Look up 'hello'."
+    (tmp_path / "s.jsonl").write_text(json.dumps({"prompt": "add 1 and 2", "tools": [etc.CALC], "expect": "add", "required": ["a", "b"]}) + "\n")
+    (sj,) = etc.load_scenarios(tmp_path / "s.jsonl")
+    assert sj.messages == [{"role": "user", "content": "add 1 and 2"}] and all(etc.score_call("add", {"a": 1, "b": 2}, sj).values())
+    todo = etc.BUILTIN[4]
+    assert not etc.score_call("write_todos", {"todos": [{"title": "x"}]}, todo)["args_ok"]          # an item without `done`
+    assert etc.score_call("write_todos", {"todos": json.dumps([{"title": "x", "done": True}])}, todo)["json_ok"]
+    assert not etc.score_call("get_weather", {"city": "Paris", "unit": "kelvin"}, etc.BUILTIN[0])["args_ok"]   # outside the enum
