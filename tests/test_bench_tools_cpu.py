@@ -261,3 +261,82 @@ content = "short for hello"
     assert not etc.score_call("write_todos", {"todos": [{"title": "x"}]}, todo)["args_ok"]          # an item without `done`
     assert etc.score_call("write_todos", {"todos": json.dumps([{"title": "x", "done": True}])}, todo)["json_ok"]
     assert not etc.score_call("get_weather", {"city": "Paris", "unit": "kelvin"}, etc.BUILTIN[0])["args_ok"]   # outside the enum
+
+
+def test_exo_bench_streaming_metrics_sampler_pairs_and_dry_run(capsys):
+    """`exo_bench` against a scripted server: paired pp / tg lists, a streamed run with client-side timings, the GPU sampler
+    on a fake NVML, and the dry run."""
+    import json
+    import threading
+    import time
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+    from exo_b200.bench import exo_bench as eb
+    assert eb.plan_runs([512, 2048], [64, 128], False) == [(512, 64), (2048, 128)]
+    assert len(eb.plan_runs([512, 2048], [64, 128], True)) == 4 and eb.plan_runs([512], [64, 128], False) == [(512, 64), (512, 128)]
+
+    class Nvml:
+        calls = 0
+
+        def nvmlInit(self): pass
+        def nvmlDeviceGetCount(self): return 2
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+        def nvmlDeviceGetUtilizationRates(self, h): Nvml.calls += 1; return type("U", (), {"gpu": 50 + 10 * h})()
+        def nvmlDeviceGetTemperature(self, h, kind): return 60 + h
+        def nvmlDeviceGetPowerUsage(self, h): return 700_000
+        def nvmlDeviceGetClockInfo(self, h, kind): return 1900
+    with eb.SystemMetricsSampler(0.01, nvml=Nvml()) as sm:
+        time.sleep(0.08)
+    s = sm.summary()
+    assert s["samples"] >= 3 and s["gpus"][1]["util"] == {"mean": 60.0, "max": 60.0} and s["gpus"][0]["power_w"]["max"] == 700.0
+    assert eb.SystemMetricsSampler(nvml=eb._NoNvml()).summary() is None
+    bodies = []
+
+    class H(BaseHTTPRequestHandler):
+        def do_GET(self):
+            out = json.dumps({"previews": [{"sharding": "Tensor", "instance_meta": "Nvlink", "error": None, "instance": {
+                "NvlinkInstance": {"shardAssignments": {"nodeToRunner": {"a": "r0", "b": "r1"}}}}}, {"error": "no memory"}]}).encode()
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(out)))
+            self.end_headers()
+            self.wfile.write(out)
+
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            bodies.append(body)
+            n_prompt = len(body["messages"][0]["content"]) // 2 + 5
+            stats = {"prompt_tps": 1000.0, "generation_tps": 50.0, "prompt_tokens": n_prompt, "generation_tokens": body["max_tokens"]}
+            self.send_response(200)
+            if body.get("stream"):
+                self.send_header("Content-Type", "text/event-stream")
+                self.end_headers()
+                for i in range(3):
+                    self.wfile.write(("data: " + json.dumps({"choices": [{"delta": {"content": "x"}}]}) + "\n\n").encode())
+                    self.wfile.flush()
+                    time.sleep(0.01)
+                self.wfile.write(("data: " + json.dumps({"choices": [{"delta": {}, "finish_reason": "length"}]}) + "\n\n").encode())
+                self.wfile.write((": generation_stats " + json.dumps(stats) + "\n\n").encode())
+                self.wfile.write(b"data: [DONE]\n\n")
+                return
+            out = json.dumps({"usage": {"prompt_tokens": n_prompt, "completion_tokens": body["max_tokens"]}, "generation_stats": stats}).encode()
+            self.send_header("Content-Length", str(len(out)))
+            self.end_headers()
+            self.wfile.write(out)
+
+        def log_message(self, *a):
+            pass
+    srv = HTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    port = str(srv.server_address[1])
+    try:
+        assert eb.main(["--port", port, "--model", "m", "--pp", "64,128", "--tg", "4,8", "--dry-run"]) == 0
+        dry = json.loads(capsys.readouterr().out)
+        assert [(r["pp"], r["tg"]) for r in dry["runs"]] == [(64, 4), (128, 8)] and dry["placements"] == [
+            {"sharding": "Tensor", "instance_meta": "Nvlink", "nodes": 2}]
+        assert not bodies
+        client = eb.ExoClient("127.0.0.1", int(port))
+        r = eb.stream_request(client, "m", "a " * 20, 4, False)
+        assert r["client_chunks"] == 3 and r["client_ttft_s"] > 0 and r["client_gap_ms_p50"] >= 5 and r["generation_tps"] == 50.0 and r["tg_tokens"] == 4
+        rows = eb.concurrent_requests(lambda: eb.ExoClient("127.0.0.1", int(port)), 3, "m", "a " * 20, 4, False, eb.stream_request)
+        assert len(rows) == 3 and all(x["client_chunks"] == 3 for x in rows) and eb.aggregate(rows, 3)["agg_gen_tps"] == 150.0
+    finally:
+        srv.shutdown()
