@@ -213,6 +213,23 @@ def test_decode_attention_tcgen05(K, Hq, Hkv, window):
     assert torch.equal(got, again)      # tickets were left clean and the merge order is fixed
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(12, 1), (24, 2)])
+def test_attention_with_twelve_query_heads_per_kv_head(K, Hq, Hkv):
+    """Step-3.5's sliding-window layers under tensor parallelism: 12 query heads share a KV head (not a power of two), with
+    a window, in decode and in prompt-shaped steps."""
+    from exo_b200.ops import cuda as c
+    lens = [1, 127, 129, 1000, 3001]
+    q, kc, vc, bt, sl, cu = _paged_setup(torch.bfloat16, 5, Hq, Hkv, 128, lens, [1] * 5, seed=7)
+    got = K.paged_attention(q, kc, vc, bt, sl, cu, 128 ** -0.5, sliding_window=512, max_q_len=1)
+    close(got, ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, cu, 128 ** -0.5, 512))
+    lens, qlens = [300, 777, 1, 700], [300, 260, 1, 517]
+    q, kc, vc, bt, sl, cu = _paged_setup(torch.bfloat16, 4, Hq, Hkv, 128, lens, qlens, seed=8)
+    got = K.paged_attention(q, kc, vc, bt, sl, cu, 128 ** -0.5, sliding_window=200, max_q_len=max(qlens))
+    torch.cuda.synchronize()
+    c.gemm_check()
+    close(got, ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, cu, 128 ** -0.5, 200))
+
+
 @pytest.mark.parametrize("window", [0, 200])
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
 def test_prefill_attention_tcgen05(K, Hq, Hkv, window):
