@@ -576,6 +576,16 @@ def preset(name: str) -> ModelConfig:
                            n_experts=8, n_experts_per_tok=2, moe_ffn=128, shared_expert_ffn=128, router="sigmoid", router_bias=True,
                            norm_topk_prob=True, routed_scaling=3.0, mlp_only_layers=(0,), swiglu_limits=(0.0, 0.0, 0.0, 0.05),
                            swiglu_limits_shared=(0.0, 0.0, 0.04, 0.04), dtype="fp32")
+    if n in ("step-3.5-flash",):   # the published model's shape (benchmarks with weights from a seed): 196 B parameters, 11 B active
+        L = 45
+        types = tuple("full" if i % 4 == 0 else "sliding" for i in range(L))
+        ropes = tuple(RopeConfig(theta=5000000.0 if t == "full" else 10000.0, partial_rotary_factor=0.5 if t == "full" else 1.0) for t in types)
+        return ModelConfig(name="step-3.5-flash", family="step3p5", n_layers=L, hidden=4096, n_heads=64, n_kv_heads=8, head_dim=128, ffn=11264,
+                           vocab=128896, qk_norm=True, norm_one_plus=True, layer_types=types, sliding_window=512,
+                           layer_n_heads=tuple(96 if t == "sliding" else 64 for t in types), layer_rope=ropes, rope=ropes[0], head_gate=True,
+                           n_experts=288, n_experts_per_tok=8, moe_ffn=1280, shared_expert_ffn=1280, router="sigmoid", router_bias=True,
+                           norm_topk_prob=True, routed_scaling=3.0, mlp_only_layers=(0, 1, 2), swiglu_limits=(0.0,) * 43 + (7.0, 7.0),
+                           swiglu_limits_shared=(0.0,) * 43 + (16.0, 16.0), max_position=262144, quant="mxfp8")
     if n in ("tiny-gpt-oss",):     # attention sinks and a sliding window on every other layer's worth of context
         return ModelConfig(name="tiny-gpt-oss", family="gpt_oss", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
                            ffn=512, vocab=1024, attn_bias=True, attn_sinks=True, sliding_window=32, dtype="fp32")
@@ -624,4 +634,4 @@ def preset(name: str) -> ModelConfig:
 
 
 PRESETS = ("tiny-llama", "llama-3.1-8b", "llama-3.1-70b", "qwen3-235b-a22b", "deepseek-v3", "tiny-moe", "tiny-mla",
-           "tiny-qwen3", "tiny-qwen2", "tiny-gemma4", "tiny-nemotron-h", "tiny-qwen3-next", "qwen3-next-80b-a3b", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-step3p5", "tiny-yarn")
+           "tiny-qwen3", "tiny-qwen2", "tiny-gemma4", "tiny-nemotron-h", "tiny-qwen3-next", "qwen3-next-80b-a3b", "tiny-glm4-moe", "tiny-mixtral", "tiny-minimax", "tiny-gpt-oss", "tiny-step3p5", "step-3.5-flash", "tiny-yarn")

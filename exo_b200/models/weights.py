@@ -619,8 +619,17 @@ def _fast_shard(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device) ->
             lw.w_uv = src.get(p + "uv", (hq, cfg.v_head_dim, cfg.kv_lora_rank))
             lw.wo = src.get(p + "o", (H, hq * cfg.v_head_dim))
         else:
+            hq = cfg.q_heads(i) // n
             lw.wqkv = src.get(p + "qkv", ((hq + 2 * hkv + (hq if cfg.attn_gate else 0)) * D, H))
             lw.wo = src.get(p + "o", (H, hq * D))
+            if cfg.family == "step3p5":      # per-layer head count, RoPE, window, head gate and SwiGLU limits
+                from ..ops import reference as ref
+                lw.n_q, lw.window = hq, cfg.window_of(i)
+                inv, lw.rope_mscale = ref.rope_inv_freq(D, cfg.rope_of(i))
+                lw.inv_freq = inv.to(device)
+                if cfg.head_gate:
+                    lw.w_head_gate = src.get(p + "hg", (hq, H))
+                lw.act_limit, lw.shared_limit = cfg.swiglu_limit(i), cfg.swiglu_limit(i, shared=True)
             if cfg.qk_norm:
                 lw.q_norm = torch.ones(D, dtype=dt, device=device)
                 lw.k_norm = torch.ones(D, dtype=dt, device=device)
