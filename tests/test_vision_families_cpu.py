@@ -268,3 +268,66 @@ def test_kimi_k25_tower_matches_its_parts_in_vllm():
     ref_e = F.interpolate(w["patch_embed.pos_emb.weight"].permute(2, 0, 1)[None], size=(8, 6), mode="bicubic")[0].permute(1, 2, 0).reshape(48, E)
     assert torch.allclose(e, ref_e, atol=1e-6)
     assert tower(torch.randn(48, 3, 14, 14), torch.tensor([[8, 6]])).shape == (12, cfg.out_hidden)
+
+
+def test_serving_engine_builds_qwen35_and_kimi_towers_from_checkpoint_folders(tmp_path):
+    """Checkpoint folders of a Qwen3.5 model (``model.visual.*``) and of a Kimi-K2.5 model (``vision_tower.*`` + ``mm_projector.*``):
+    the serving engine picks the matching processor and tower and expands an image at the family's placeholder token."""
+    import base64
+    import io
+    import json
+    import types
+    from safetensors.torch import save_file
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5VisionConfig
+    from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5VisionModel
+    from exo_b200.worker.engines.b200.builder import ServingEngine
+    from exo_b200.worker.engines.b200.vision_families import KimiTower, KimiTowerConfig, KimiVLProcessor
+
+    def engine(folder):
+        eng = object.__new__(ServingEngine)
+        eng.model_id, eng.vision, eng.tok = str(folder), None, types.SimpleNamespace(pad_token_id=0)
+        eng.cfg = types.SimpleNamespace(hidden=96)
+        eng.te = types.SimpleNamespace(exe=types.SimpleNamespace(spec=types.SimpleNamespace(tp_size=1, pp_size=1), device=torch.device("cpu")))
+        return eng
+    buf = io.BytesIO()
+    picture(120, 200, 1).save(buf, format="PNG")
+    b64 = base64.b64encode(buf.getvalue()).decode()
+    # Qwen3.5
+    torch.manual_seed(0)
+    vc = Qwen3_5VisionConfig(depth=1, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=16, spatial_merge_size=2, temporal_patch_size=2,
+                             out_hidden_size=96, num_position_embeddings=36)
+    q = tmp_path / "qwen"
+    q.mkdir()
+    save_file({"model.visual." + k: v.contiguous() for k, v in Qwen3_5VisionModel(vc).float().state_dict().items()}, str(q / "model.safetensors"))
+    (q / "config.json").write_text(json.dumps({"model_type": "qwen3_5", "vision_config": vc.to_dict(), "image_token_id": 9}))
+    eng = engine(q)
+    ids, embeds, media = eng._with_images([1, 9, 2], [b64])
+    proc, tower, ph, wrap = eng.vision
+    assert isinstance(proc, QwenVLProcessor) and isinstance(tower, QwenVLTower) and tower.cfg.variant == "qwen3" and ph == 9 and wrap is None
+    n = embeds[0][1].shape[0]
+    assert ids == [1] + [9] * n + [2] and embeds[0][1].shape == (n, 96) and media[0][:2] == (1, 1 + n)
+    # Kimi-K2.5
+    cfg = KimiTowerConfig(patch=14, pos_h=8, pos_w=8, heads=2, layers=1, hidden=32, mlp_dim=48, out_hidden=96)
+    E = cfg.hidden
+    w = {"vision_tower.patch_embed.proj.weight": torch.randn(E, 3, 14, 14) * 0.05, "vision_tower.patch_embed.proj.bias": torch.zeros(E),
+         "vision_tower.patch_embed.pos_emb.weight": torch.randn(8, 8, E) * 0.1}
+    for name, (o, i) in {"wqkv": (3 * E, E), "wo": (E, E), "mlp.fc0": (48, E), "mlp.fc1": (E, 48)}.items():
+        w[f"vision_tower.encoder.blocks.0.{name}.weight"], w[f"vision_tower.encoder.blocks.0.{name}.bias"] = torch.randn(o, i) * 0.1, torch.zeros(o)
+    for name in ("encoder.blocks.0.norm0", "encoder.blocks.0.norm1", "encoder.final_layernorm"):
+        w[f"vision_tower.{name}.weight"], w[f"vision_tower.{name}.bias"] = torch.ones(E), torch.zeros(E)
+    w["mm_projector.pre_norm.weight"], w["mm_projector.pre_norm.bias"] = torch.ones(E), torch.zeros(E)
+    w["mm_projector.proj.0.weight"], w["mm_projector.proj.0.bias"] = torch.randn(4 * E, 4 * E) * 0.1, torch.zeros(4 * E)
+    w["mm_projector.proj.2.weight"], w["mm_projector.proj.2.bias"] = torch.randn(96, 4 * E) * 0.1, torch.zeros(96)
+    k = tmp_path / "kimi"
+    k.mkdir()
+    save_file({n_: t.contiguous() for n_, t in w.items()}, str(k / "model.safetensors"))
+    (k / "config.json").write_text(json.dumps({"model_type": "kimi_k25", "media_placeholder_token_id": 77, "vision_config": {
+        "patch_size": 14, "init_pos_emb_height": 8, "init_pos_emb_width": 8, "num_attention_heads": 2, "num_hidden_layers": 1,
+        "hidden_size": E, "intermediate_size": 48, "mm_hidden_size": 96}}))
+    (k / "preprocessor_config.json").write_text(json.dumps({"in_token_limit": 64}))
+    eng = engine(k)
+    ids, embeds, _ = eng._with_images([1, 77, 2], [b64])
+    proc, tower, ph, _wrap = eng.vision
+    assert isinstance(proc, KimiVLProcessor) and isinstance(tower, KimiTower) and ph == 77
+    n = embeds[0][1].shape[0]
+    assert 0 < n <= 32 and ids == [1] + [77] * n + [2] and embeds[0][1].shape == (n, 96)
