@@ -145,34 +145,70 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank(rank, port, mode, q):
+def _rank(rank, port, mode, q, world=2):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=2)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         cfg = tiny(kontext=mode == "kontext")
-        model = FluxModel.random(cfg, blocks=range(rank * 2, rank * 2 + 2))
-        r = DiffusionRunner(model, rank=rank, world=2, num_sync_steps=99 if mode == "pipe_sync" else 1, pipe_groups=[dist.new_group([0, 1])])
+        per = cfg.n_blocks // world
+        model = FluxModel.random(cfg, blocks=range(rank * per, (rank + 1) * per))
+        r = DiffusionRunner(model, rank=rank, world=world, num_sync_steps=99 if mode == "pipe_sync" else 1,
+                            pipe_groups=[dist.new_group(list(range(world)))])
+        r.async_patches = mode != "step_by_step"
         init = torch.full((32, 48, 3), 90, dtype=torch.uint8) if mode == "kontext" else None
-        img = list(r.generate("a red fox", 32, 48, 4, 7, init_image=init))[-1][1]
-        q.put((rank, img, r.n_patch_hops))
+        calls = [0]
+
+        def agree() -> bool:                 # what the serving engine does: a host-side collective every time it is asked
+            calls[0] += 1
+            flag = torch.tensor([1.0 if (mode == "cancelled" and calls[0] == 3) else 0.0])
+            dist.all_reduce(flag)
+            return bool(flag.item())
+        long = mode in ("cancel_checks", "cancelled")
+        out = list(r.generate("a red fox", 32, 48, 10 if long else 4, 7, init_image=init, partial_images=1 if mode == "previews" else 0,
+                              **({"should_stop": agree} if long else {})))
+        if mode == "cancelled":
+            q.put((rank, torch.zeros(1), calls[0], out))
+            return
+        q.put((rank, out[-1][1], r.n_patch_hops, [o[1] for o in out[:-1]]))
     finally:
         dist.destroy_process_group()
+
+
+def _run_ranks(mode, world=2):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank, args=(r, port, mode, q, world)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict((r, (img, hops, prev)) for r, img, hops, prev in (q.get(timeout=180) for _ in range(world)))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return got
+
+
+def test_patches_flowing_across_steps_equal_the_step_by_step_schedule():
+    """The continuous patch flow (rows go from the last stage straight back to the first) computes exactly what the
+    step-by-step patch schedule computes; four stages keep every pair's messages in order; previews reach every rank."""
+    a, b = _run_ranks("pipefusion"), _run_ranks("step_by_step")
+    assert torch.equal(a[0][0], a[1][0]) and (a[0][0].float() - b[0][0].float()).abs().max() <= 1 and a[0][1] == b[0][1] == 6
+    four = _run_ranks("pipefusion", world=4)
+    assert all(torch.equal(four[0][0], four[r][0]) for r in range(4)) and four[0][1] == 3 * 4 and four[3][1] == 0
+    # ten steps: cancellation is agreed on at steps 0, 1 (whole-image steps) and then every fourth patch step, without stalling the flow
+    cc = _run_ranks("cancel_checks")
+    assert torch.equal(cc[0][0], cc[1][0]) and cc[0][1] == 9 * 2
+    stopped = _run_ranks("cancelled")
+    assert stopped[0][1] == stopped[1][1] == 3 and stopped[0][2] == [] and stopped[1][2] == []      # both ranks left at the same check
+    pv = _run_ranks("previews")
+    assert len(pv[0][2]) == 1 and torch.equal(pv[0][2][0], pv[1][2][0]) and pv[0][2][0].shape == (32, 48, 3)
 
 
 @pytest.mark.parametrize("mode", ["pipe_sync", "pipefusion", "kontext"])
 def test_two_stage_schedules_against_single_rank(mode):
     init = torch.full((32, 48, 3), 90, dtype=torch.uint8) if mode == "kontext" else None
     want = list(DiffusionRunner(FluxModel.random(tiny(kontext=mode == "kontext"))).generate("a red fox", 32, 48, 4, 7, init_image=init))[-1][1]
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_rank, args=(r, port, mode, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    got = dict((r, (img, hops)) for r, img, hops in (q.get(timeout=180) for _ in range(2)))
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
+    got = _run_ranks(mode)
     assert torch.equal(got[0][0], got[1][0])
     diff = (got[0][0].float() - want.float()).abs()
     if mode == "pipe_sync":
