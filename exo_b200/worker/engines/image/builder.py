@@ -253,6 +253,7 @@ class ImageBuilder(Builder):
         sync = os.environ.get("EXO_IMAGE_SYNC_STEPS") or getattr(self.model, "num_sync_steps", 1)
         runner = DiffusionRunner(self.model, rank=self.rank, world=self.world, cfg_parallel=self.cfg_parallel,
                                  num_sync_steps=int(sync), pipe_groups=self.pipe_groups)
+        runner.async_patches = os.environ.get("EXO_IMAGE_ASYNC_PATCHES", "1") != "0"     # 0: one step at a time (stages wait for its end)
         return ImageEngine(runner, str(self.card.model_id), self.rank, self.world, self.control)
 
     def close(self) -> None:
