@@ -56,6 +56,7 @@ class Engine:
             self.sched.state_snapshots = True
         self.seqs: dict[str, Sequence] = {}
         self.plan_sink = plan_sink  # callable(StepPlan): broadcasts the plan to follower ranks
+        self.embed_sink = None      # callable([(row, rows)]): hands caller-supplied embedding rows to the follower ranks
         self.n_steps = 0
 
     # ---- requests ----
@@ -166,9 +167,14 @@ class Engine:
             proc = lambda x: x  # noqa: E731 - forces the eager path that keeps logits
         if proc is not None:
             plan.flags |= FLAG_EAGER      # every rank must take the same path: a graph capture runs the step more than once
+        patches = self._embed_patches(entries)
+        # rows whose embeddings the caller supplied: the other ranks learn where they go with the plan and get the rows after it
+        plan.embeds = [(int(r0), int(rows.shape[0])) for r0, rows in patches] if patches else None
         if self.plan_sink is not None:
             self.plan_sink(plan)
-        self.exe.model.embed_patches = self._embed_patches(entries)
+            if patches and self.embed_sink is not None:
+                self.embed_sink(patches)
+        self.exe.model.embed_patches = patches
         if plan.flags & FLAG_NO_SAMPLE:
             # prompt chunks only: nothing to read back, so the host goes straight on to the next chunk while this one
             # runs (and, with pipeline stages, while the later stages still work on it)

@@ -23,7 +23,7 @@ from ....engine.plan import HEADER, PlanLayout, StepPlan
 from ....models.config import ModelConfig
 from ....models.transformer import default_state_snapshots, KVPool
 from ....parallel.comm import PipeComm
-from ....models.weights import (RandomSource, SafetensorsSource, ShardSpec, build_weights, fast_random_weights,
+from ....models.weights import (_DTYPES, RandomSource, SafetensorsSource, ShardSpec, build_weights, fast_random_weights,
                                 vocab_shard)
 from ....shared import constants
 from ....shared.base import TaskId
@@ -107,13 +107,19 @@ class PlanChannel:
             if (8 + words) * 4 > self.slot_bytes:
                 raise ValueError(f"step plan of {words} words does not fit the plan channel's {self.slot_bytes} byte slots")
             plan.pack(slot[8:], plan.n_tokens, plan.n_seqs, mb)
+        # caller-supplied embedding rows of this step (image features): (first row, row count) pairs behind the plan; the rows
+        # themselves follow on the device group (``LeaderServingEngine._send_rows``)
+        embeds = list(getattr(plan, "embeds", None) or []) if plan is not None else []
+        for j, (r0, n_rows) in enumerate(embeds):
+            slot[8 + words + 2 * j], slot[8 + words + 2 * j + 1] = r0, n_rows
+        words_all = words + 2 * len(embeds)
         tail = ("\n".join(finished)).encode()
-        if (8 + words) * 4 + len(tail) > self.slot_bytes:
+        if (8 + words_all) * 4 + len(tail) > self.slot_bytes:
             raise ValueError("plan channel message too large")
-        slot[0:4] = (1 if plan is not None else 0, words, len(tail), 1 if stop else 0)
+        slot[0:5] = (1 if plan is not None else 0, words, len(tail), 1 if stop else 0, len(embeds))
         if tail:
             np.frombuffer(self.shm.buf, dtype=np.uint8, count=len(tail),
-                          offset=self.HDR_WORDS * 8 + (seq % self.SLOTS) * self.slot_bytes + (8 + words) * 4)[:] = np.frombuffer(tail, np.uint8)
+                          offset=self.HDR_WORDS * 8 + (seq % self.SLOTS) * self.slot_bytes + (8 + words_all) * 4)[:] = np.frombuffer(tail, np.uint8)
         self.hdr[0] = seq          # published: the payload stores above are ordered before this one (x86 TSO)
         self.seq = seq
 
@@ -121,11 +127,13 @@ class PlanChannel:
         seq = self.seq + 1
         self._wait(lambda: int(self.hdr[0]) >= seq, self.timeout_s, "the leader stopped publishing plans")
         slot = self._slot(seq)
-        has_plan, words, n_tail, stop = (int(x) for x in slot[0:4])
+        has_plan, words, n_tail, stop, n_embeds = (int(x) for x in slot[0:5])
         plan = StepPlan.unpack(slot[8:8 + words]) if has_plan else None
+        if plan is not None:
+            plan.embeds = [(int(slot[8 + words + 2 * j]), int(slot[8 + words + 2 * j + 1])) for j in range(n_embeds)] or None
         finished: list[str] = []
         if n_tail:
-            off = self.HDR_WORDS * 8 + (seq % self.SLOTS) * self.slot_bytes + (8 + words) * 4
+            off = self.HDR_WORDS * 8 + (seq % self.SLOTS) * self.slot_bytes + (8 + words + 2 * n_embeds) * 4
             finished = bytes(self.shm.buf[off:off + n_tail]).decode().split("\n")
         self.hdr[8 + self.rank] = seq
         self.seq = seq
@@ -166,6 +174,13 @@ class LeaderServingEngine(ServingEngine):
     def _sink(self, plan: StepPlan) -> None:
         self.control.send(plan, [])
 
+    def _send_rows(self, patches) -> None:
+        """Caller-supplied embedding rows (image features) of the plan just published, to every other rank: one broadcast
+        per run of rows on the instance's device group, in the order of the plan's ``embeds`` pairs."""
+        exe = self.te.exe
+        for _r0, rows in patches:
+            dist.broadcast(rows.to(device=exe.device, dtype=_DTYPES[self.cfg.dtype]).contiguous(), src=0)
+
 
 class FollowerServingEngine(Engine):
     """Ranks > 0: execute broadcast plans; know tasks only by id."""
@@ -183,12 +198,24 @@ class FollowerServingEngine(Engine):
         while True:
             plan, finished, stop = self.control.recv()
             if plan is not None:
-                self.exe.run(plan)
+                self._run(plan)
             if stop:
                 self.stopped = True
                 return
             if finished:
                 return
+
+    def _run(self, plan: StepPlan) -> None:
+        """Execute a broadcast plan; embedding rows the leader supplies for it (image features) arrive first."""
+        if getattr(plan, "embeds", None):
+            cfg = self.exe.model.cfg
+            patches = []
+            for r0, n_rows in plan.embeds:
+                t = torch.empty(n_rows, cfg.hidden, dtype=_DTYPES[cfg.dtype], device=self.exe.device)
+                dist.broadcast(t, src=0)
+                patches.append((r0, t))
+            self.exe.model.embed_patches = patches if self.exe.spec.is_first_stage else None
+        self.exe.run(plan)
 
     def submit(self, task: GenerationTask) -> None:
         self.active.add(str(task.task_id))
@@ -203,7 +230,7 @@ class FollowerServingEngine(Engine):
     def step(self) -> Iterable[tuple[TaskId, StepItem]]:
         plan, finished, stop = self.control.recv()
         if plan is not None:
-            self.exe.run(plan)
+            self._run(plan)
         out: list[tuple[TaskId, StepItem]] = []
         for t in finished:
             if t in self.active:
@@ -348,6 +375,7 @@ class B200Builder(Builder):
                   self.control)
         if self.world > 1:
             te.plan_sink = eng._sink
+            te.embed_sink = eng._send_rows
         elif constants.ENABLE_DISAGGREGATION and not cfg.mla:
             eng.enable_prefill_server()      # its port travels in RunnerReady; the master pairs instances through links
         return eng

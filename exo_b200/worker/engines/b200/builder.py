@@ -163,14 +163,12 @@ class ServingEngine(Engine):
 
     def _with_images(self, ids: list[int], images: list[str]):
         """Prompt ids with every image expanded to its feature rows: ``(ids, embeds, media)`` for the token engine.
-        Single-rank engines only (the plan broadcast to other ranks carries token ids, not embeddings)."""
+        On a multi-rank instance this runs on rank 0; the rows follow each step's plan to the other ranks."""
         import base64
         import hashlib
         import io
         from .vision import ImageFeatures, VisionConfig, VisionProcessor, VisionTower, splice
         exe = self.te.exe
-        if exe.spec.tp_size * exe.spec.pp_size != 1:
-            raise ValueError("image inputs need a single-rank instance")
         dtype = torch.float32 if exe.device.type == "cpu" else torch.bfloat16
         if self.vision is None:
             self.vision = self._checkpoint_vision(exe.device, dtype) or VisionProcessor(

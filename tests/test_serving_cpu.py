@@ -184,3 +184,25 @@ def test_image_inputs_reach_the_engine_as_spliced_features(tmp_path):
     n_plain, n_a1, n_b, n_a2 = (c.usage.prompt_tokens for c in finals)
     assert n_a1 == n_b == n_a2 and n_a1 - n_plain == 6          # 84x56 pixels = 3 x 2 cells of 28 pixels
     assert finals[3].usage.prompt_tokens_details.cached_tokens > 0 and finals[1].usage.prompt_tokens_details.cached_tokens == 0
+
+
+@pytest.mark.parametrize("pp", [1, 2])
+def test_image_inputs_on_two_ranks_match_one_rank(tmp_path, pp):
+    """Image features are computed on rank 0 and follow the step plans to the other ranks (tensor-parallel ranks all embed
+    the prompt; with pipeline stages only the first does): the tokens equal those of a single-rank instance."""
+    import base64
+    import io
+
+    import numpy as np
+    from PIL import Image
+    buf = io.BytesIO()
+    Image.fromarray((np.random.default_rng(4).random((56, 84, 3)) * 255).astype("uint8")).save(buf, format="PNG")
+    img = base64.b64encode(buf.getvalue()).decode()
+    d, cfg = make_checkpoint(tmp_path)
+
+    def tokens(n, pp_):
+        inst, nodes, rids = instance(d, n, pp=pp_)
+        t = gen_task(inst, "describe", max_output_tokens=6, images=[img], bench=True)
+        return [e.chunk.token_id for e in drive(inst, nodes, rids, lambda: [t]) if isinstance(e, ChunkGenerated) and isinstance(e.chunk, TokenChunk)]
+    one, two = tokens(1, 1), tokens(2, pp)
+    assert len(one) == 6 and two == one
