@@ -68,22 +68,31 @@ class Engine:
         rid = req_id or uuid.uuid4().hex
         if not prompt:
             raise ValueError("empty prompt")
+        seat = 0
         if self.cfg.has_linear_layers:
-            # a recurrent layer's state summarises the WHOLE prefix: KV computed elsewhere carries no such state, and
-            # cached blocks are reusable only up to one whose end-of-block state was snapshotted (the scheduler's rule)
-            kv_prefill = None
+            # a recurrent layer's state summarises the WHOLE prefix: cached blocks are reusable only up to one whose
+            # end-of-block state was snapshotted (the scheduler's rule), and KV computed elsewhere is usable only together
+            # with the recurrent layers' states after exactly those tokens, installed into a seat of this engine
             use_prefix_cache = use_prefix_cache and self.sched.state_snapshots
+            if kv_prefill is not None:
+                if self.sched._free_seats and any(isinstance(e[0], str) for e in kv_prefill[1]) and int(kv_prefill[0]) < len(prompt):
+                    seat = self.sched._free_seats.pop()
+                else:
+                    kv_prefill = None
         s = Sequence(rid, list(prompt), params or SamplingParams(), media=media, use_prefix_cache=use_prefix_cache)
         s.embeds = list(embeds) if embeds else None
         if kv_prefill is not None:
             n, layers = kv_prefill
-            n = min(int(n), len(prompt) - 1)       # the last prompt token is always computed here (it yields the logits)
+            # the last prompt token is always computed here (it yields the logits); recurrent states cannot be cut short
+            n = int(n) if seat else min(int(n), len(prompt) - 1)
             if n > 0 and self.sched._ensure_blocks(s, n):
-                self.import_kv(s.blocks, n, layers)
-                s.n_computed = n
+                self.import_kv(s.blocks, n, layers, seat)
+                s.n_computed, s.state_slot = n, seat
             else:
                 self.alloc.release_all(s.blocks)
                 s.blocks = []
+                if seat:
+                    self.sched._free_seats.append(seat)
         self.seqs[rid] = s
         self.sched.add(s)
         return rid
@@ -107,23 +116,33 @@ class Engine:
         b = torch.tensor(blocks[:-(-n_tokens // bs)], dtype=torch.long, device=self.exe.device)
         return (b[:, None] * bs + torch.arange(bs, device=self.exe.device)[None, :]).reshape(-1)[:n_tokens]
 
-    def export_kv(self, blocks: list[int], n_tokens: int) -> list[tuple[torch.Tensor, torch.Tensor | None]]:
-        """KV of the first ``n_tokens`` positions held in ``blocks``, per local layer: ``[n_tokens, heads, dim]``."""
-        if self.cfg.has_linear_layers:
-            # the paged cache is only part of such a model's memory of a prompt: the recurrent layers' state is not
-            # addressed by position and is not exported, so another instance could not continue from this KV
-            raise NotImplementedError(f"{self.cfg.name}: models with recurrent layers cannot hand their prompt state to another instance")
+    def export_kv(self, blocks: list[int], n_tokens: int, seat: int = 0) -> list[tuple]:
+        """What this engine remembers of the first ``n_tokens`` positions, per local layer: ``(k, v)`` rows ``[n_tokens, heads,
+        dim]`` from ``blocks`` for attention layers; ``("state", [tensors])`` for recurrent layers (their state in ``seat``,
+        which must be the state after exactly ``n_tokens`` tokens) and for layers that keep nothing (no tensors)."""
+        if self.cfg.has_linear_layers and not seat:
+            raise ValueError(f"{self.cfg.name}: the recurrent layers' state lives in a seat; none was given")
         slots = self._slots(blocks, n_tokens)
-        out = []
+        out: list[tuple] = []
         for i in self.exe.spec.layers(self.cfg):
             k, v = self.exe.kv.layers[i]
-            out.append((k.view(-1, *k.shape[2:])[slots], None if v is None else v.view(-1, *v.shape[2:])[slots]))
+            if k is None:
+                out.append(("state", []))
+            elif self.cfg.layer_is_linear(i):
+                out.append(("state", [k[seat].clone(), v[seat].clone()]))
+            else:
+                out.append((k.view(-1, *k.shape[2:])[slots], None if v is None else v.view(-1, *v.shape[2:])[slots]))
         return out
 
-    def import_kv(self, blocks: list[int], n_tokens: int, layers) -> None:
+    def import_kv(self, blocks: list[int], n_tokens: int, layers, seat: int = 0) -> None:
         slots = self._slots(blocks, n_tokens)
-        for i, (k_new, v_new) in zip(self.exe.spec.layers(self.cfg), layers):
+        for i, entry in zip(self.exe.spec.layers(self.cfg), layers):
             k, v = self.exe.kv.layers[i]
+            if isinstance(entry[0], str):             # ("state", tensors): a recurrent layer's state, or nothing
+                for dst, src in zip((k, v), entry[1]):
+                    dst[seat] = src.to(device=dst.device, dtype=dst.dtype).view(dst[seat].shape)
+                continue
+            k_new, v_new = entry
             k.view(-1, *k.shape[2:])[slots] = k_new[:n_tokens].to(device=k.device, dtype=k.dtype)
             if v is not None and v_new is not None:
                 v.view(-1, *v.shape[2:])[slots] = v_new[:n_tokens].to(device=v.device, dtype=v.dtype)

@@ -214,6 +214,7 @@ class Sequence:
     rng_state: int = 0
     final_blocks: list[int] = field(default_factory=list)   # block ids at the moment the sequence finished
     state_slot: int = 0          # seat of the sequence's recurrent state while it is running (0: none)
+    final_seat: int = 0          # the seat at the moment the sequence finished
     restore_snap: int | None = None   # snapshot to copy into the seat before the sequence's first step (prefix reuse)
 
     @property

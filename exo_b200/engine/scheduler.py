@@ -65,6 +65,7 @@ class Scheduler:
         s.finished, s.finish_reason = True, reason
         self._publish_full_blocks(s)
         s.final_blocks = list(s.blocks)       # still holds the sequence's KV until the allocator hands them out again
+        s.final_seat = s.state_slot            # ... and this seat its recurrent state until another sequence sits there
         self.alloc.release_all(s.blocks)
         s.blocks = []
         if s in self.running:
@@ -211,7 +212,8 @@ class Scheduler:
                 break
             self.waiting.popleft()
             s.t_prefill_start = time.perf_counter()
-            s.state_slot = self._free_seats.pop() if self._free_seats else 0
+            if not s.state_slot:                   # (a sequence whose prompt state was installed from elsewhere already sits)
+                s.state_slot = self._free_seats.pop() if self._free_seats else 0
             self.running.append(s)
             entries.append((s, n))
             budget -= n

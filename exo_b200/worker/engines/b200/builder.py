@@ -231,13 +231,18 @@ class ServingEngine(Engine):
             return False
         if job.error is not None:
             raise RuntimeError(job.error)
-        dt = _DTYPE_NAME[job.layers[0][0].dtype] if job.layers else "float32"
+        kv_layers = [(li, e) for li, e in enumerate(job.layers) if not isinstance(e[0], str)]
+        dt = _DTYPE_NAME[kv_layers[0][1][0].dtype] if kv_layers else "float32"
         dproto.write_header(wfile, dproto.Header(request_id=request.request_id, model_id=self.model_id,
                                                  num_layers=len(job.layers), dtype=dt, start_pos=request.start_pos))
+        for li, e in enumerate(job.layers):          # recurrent layers: their whole state, once
+            if isinstance(e[0], str):
+                dproto.write_message(wfile, dproto.ArraysState(layer_idx=li, arrays=[
+                    dproto.TensorBlob(_DTYPE_NAME[t.dtype], tuple(t.shape), t.contiguous().view(torch.uint8).numpy().tobytes()) for t in e[1]]))
         lo = min(request.start_pos, job.n_tokens)
         for t0 in range(lo, job.n_tokens, KV_CHUNK_TOKENS):
             t1 = min(job.n_tokens, t0 + KV_CHUNK_TOKENS)
-            for li, (k, v) in enumerate(job.layers):
+            for li, (k, v) in kv_layers:
                 kb = k[t0:t1].contiguous().view(torch.uint8).numpy().tobytes()
                 vb = b"" if v is None else v[t0:t1].contiguous().view(torch.uint8).numpy().tobytes()
                 dproto.write_message(wfile, dproto.KVChunk(layer_idx=li, num_tokens=t1 - t0, n_heads=k.shape[1] if k.dim() == 3 else 1,
@@ -269,7 +274,8 @@ class ServingEngine(Engine):
         job, seq, target = self.prefill_running.pop(rid)
         try:
             # the sequence's blocks were just released but nothing has been allocated since: the data is intact
-            job.layers = [(k.cpu(), None if v is None else v.cpu()) for k, v in self.te.export_kv(seq.final_blocks, target)]
+            job.layers = [(e[0], [t.cpu() for t in e[1]]) if isinstance(e[0], str) else (e[0].cpu(), None if e[1] is None else e[1].cpu())
+                          for e in self.te.export_kv(seq.final_blocks, target, seq.final_seat)]
             job.n_tokens = target
         except Exception as e:  # noqa: BLE001
             job.error = str(e)
@@ -279,7 +285,7 @@ class ServingEngine(Engine):
     def _want_remote_prefill(self, p, ids: list[int]) -> bool:
         return (bool(p.prefill_endpoint) and len(ids) > constants.REMOTE_PREFILL_MIN_TOKENS
                 and self.te.exe.spec.tp_size == 1 and self.te.exe.spec.pp_size == 1 and not self.cfg.mla
-                and not self.cfg.has_linear_layers and self.cfg.family != "gemma4")     # position-addressed, uniform KV only
+                and self.cfg.family != "gemma4")      # (its layers' KV shapes differ and some layers share another's cache)
 
     def _admit_remote(self) -> None:
         for rid, f in list(self.remote.items()):
@@ -296,6 +302,10 @@ class ServingEngine(Engine):
                     dt = _TORCH_DTYPE[f.result.header.dtype]
                     layers = []
                     for li in range(f.result.header.num_layers):
+                        if li in f.result.states:        # a recurrent layer's state (or a layer that keeps nothing)
+                            layers.append(("state", [torch.frombuffer(bytearray(b.data), dtype=_TORCH_DTYPE[b.dtype]).view(b.shape)
+                                                     for b in f.result.states[li].arrays]))
+                            continue
                         chunks = f.result.chunks[li]
                         shape = (-1, chunks[0].n_heads, chunks[0].head_dim)
                         k = torch.frombuffer(bytearray(b"".join(c.keys for c in chunks)), dtype=dt).view(shape)

@@ -70,11 +70,11 @@ def test_server_reports_errors_in_band():
         srv.stop()
 
 
-def _serving_engine(model_id="tiny"):
+def _serving_engine(model_id="tiny", name="tiny-llama"):
     from exo_b200.engine.engine import Engine
     from exo_b200.worker.engines.b200.builder import ServingEngine
     from exo_b200.worker.engines.b200.tokenizer import ByteTokenizer
-    cfg = preset("tiny-llama")
+    cfg = preset(name)
     cfg.vocab = 512
     cfg.dtype = "fp32"
     w = build_weights(cfg, ShardSpec(), RandomSource(seed=0, dtype=torch.float32))
@@ -102,9 +102,22 @@ def _run(engine, task, pump=None):
     raise AssertionError("generation did not finish")
 
 
-def test_kv_handover_between_prefill_and_decode_engines(monkeypatch):
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-qwen3-next", "tiny-nemotron-h"])
+def test_kv_handover_between_prefill_and_decode_engines(monkeypatch, name):
+    """Dense model: the prompt's KV rows travel.  Models with recurrent layers (gated delta rule, Mamba-2): the attention layers'
+    KV rows and, once per layer, the recurrent layers' state after exactly the handed-over tokens, installed into a seat of
+    the decode engine."""
     monkeypatch.setattr(constants, "REMOTE_PREFILL_MIN_TOKENS", 16)
     prompt = "the quick brown fox jumps over the lazy dog " * 5       # ~220 byte tokens, several 64-token chunks
+    _engine = _serving_engine
+    globals()["_serving_engine"] = lambda model_id="tiny": _engine(model_id, name)
+    try:
+        _handover(prompt, name)
+    finally:
+        globals()["_serving_engine"] = _engine
+
+
+def _handover(prompt, name):
     want = _run(_serving_engine(), _task(prompt))
 
     prefill, decode = _serving_engine(), _serving_engine()
@@ -126,6 +139,11 @@ def test_kv_handover_between_prefill_and_decode_engines(monkeypatch):
         assert decode.remote_prefills == 1
         # the decode engine computed only the prompt's tail + the new tokens: far fewer steps than a local prefill
         assert decode.te.n_steps - steps_before <= 1 + 6
+        if name != "tiny-llama":
+            assert decode.te.sched._free_seats and len(decode.te.sched._free_seats) == decode.te.sched.max_seqs     # the seat came back
+            # a second request re-uses seats on both sides
+            assert _run(decode, _task(prompt + "again", endpoint=f"127.0.0.1:{port}")) == _run(_serving_engine(), _task(prompt + "again"))
+            assert decode.remote_prefills == 2
         # an unreachable endpoint falls back to local prefill, same tokens
         again = _serving_engine()
         assert _run(again, _task(prompt, endpoint="127.0.0.1:9")) == want and again.remote_prefills == 0
