@@ -143,7 +143,8 @@ class Engine:
                     dst[seat] = src.to(device=dst.device, dtype=dst.dtype).view(dst[seat].shape)
                 continue
             k_new, v_new = entry
-            k.view(-1, *k.shape[2:])[slots] = k_new[:n_tokens].to(device=k.device, dtype=k.dtype)
+            rows = k.view(-1, *k.shape[2:])
+            rows[slots] = k_new[:n_tokens].to(device=k.device, dtype=k.dtype).reshape(-1, *rows.shape[1:])      # (a latent cache has no head axis)
             if v is not None and v_new is not None:
                 v.view(-1, *v.shape[2:])[slots] = v_new[:n_tokens].to(device=v.device, dtype=v.dtype)
 

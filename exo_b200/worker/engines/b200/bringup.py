@@ -376,7 +376,7 @@ class B200Builder(Builder):
         if self.world > 1:
             te.plan_sink = eng._sink
             te.embed_sink = eng._send_rows
-        elif constants.ENABLE_DISAGGREGATION and not cfg.mla:
+        elif constants.ENABLE_DISAGGREGATION:
             eng.enable_prefill_server()      # its port travels in RunnerReady; the master pairs instances through links
         return eng
 

@@ -284,7 +284,7 @@ class ServingEngine(Engine):
     # ---- disaggregation: decode side ----
     def _want_remote_prefill(self, p, ids: list[int]) -> bool:
         return (bool(p.prefill_endpoint) and len(ids) > constants.REMOTE_PREFILL_MIN_TOKENS
-                and self.te.exe.spec.tp_size == 1 and self.te.exe.spec.pp_size == 1 and not self.cfg.mla
+                and self.te.exe.spec.tp_size == 1 and self.te.exe.spec.pp_size == 1
                 and self.cfg.family != "gemma4")      # (its layers' KV shapes differ and some layers share another's cache)
 
     def _admit_remote(self) -> None:
@@ -309,7 +309,8 @@ class ServingEngine(Engine):
                         chunks = f.result.chunks[li]
                         shape = (-1, chunks[0].n_heads, chunks[0].head_dim)
                         k = torch.frombuffer(bytearray(b"".join(c.keys for c in chunks)), dtype=dt).view(shape)
-                        v = torch.frombuffer(bytearray(b"".join(c.values for c in chunks)), dtype=dt).view(shape)
+                        vb = b"".join(c.values for c in chunks)          # empty: a latent cache has keys only (MLA)
+                        v = torch.frombuffer(bytearray(vb), dtype=dt).view(shape) if vb else None
                         layers.append((k, v))
                     kv = (f.result.total_tokens, layers)
                     self.remote_prefills += 1
