@@ -284,8 +284,7 @@ class ServingEngine(Engine):
     # ---- disaggregation: decode side ----
     def _want_remote_prefill(self, p, ids: list[int]) -> bool:
         return (bool(p.prefill_endpoint) and len(ids) > constants.REMOTE_PREFILL_MIN_TOKENS
-                and self.te.exe.spec.tp_size == 1 and self.te.exe.spec.pp_size == 1
-                and self.cfg.family != "gemma4")      # (its layers' KV shapes differ and some layers share another's cache)
+                and self.te.exe.spec.tp_size == 1 and self.te.exe.spec.pp_size == 1)
 
     def _admit_remote(self) -> None:
         for rid, f in list(self.remote.items()):

@@ -102,7 +102,7 @@ def _run(engine, task, pump=None):
     raise AssertionError("generation did not finish")
 
 
-@pytest.mark.parametrize("name", ["tiny-llama", "tiny-mla", "tiny-qwen3-next", "tiny-nemotron-h"])
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-mla", "tiny-qwen3-next", "tiny-nemotron-h", "tiny-gemma4"])
 def test_kv_handover_between_prefill_and_decode_engines(monkeypatch, name):
     """Dense model: the prompt's KV rows travel.  Models with recurrent layers (gated delta rule, Mamba-2): the attention layers'
     KV rows and, once per layer, the recurrent layers' state after exactly the handed-over tokens, installed into a seat of
@@ -139,7 +139,7 @@ def _handover(prompt, name):
         assert decode.remote_prefills == 1
         # the decode engine computed only the prompt's tail + the new tokens: far fewer steps than a local prefill
         assert decode.te.n_steps - steps_before <= 1 + 6
-        if name not in ("tiny-llama", "tiny-mla"):
+        if name not in ("tiny-llama", "tiny-mla", "tiny-gemma4"):
             assert decode.te.sched._free_seats and len(decode.te.sched._free_seats) == decode.te.sched.max_seqs     # the seat came back
             # a second request re-uses seats on both sides
             assert _run(decode, _task(prompt + "again", endpoint=f"127.0.0.1:{port}")) == _run(_serving_engine(), _task(prompt + "again"))
