@@ -266,3 +266,38 @@ def test_image_builder_serves_a_checkpoint_folder(tmp_path, monkeypatch):
                              advanced_params=AdvancedImageParams(seed=5))
     edited, _ = run(ImageEdits(instance_id=inst.instance_id, command_id="c2", task_params=e))
     assert edited.shape == (64, 96, 3) and b.model.context is not None
+
+
+def test_text_encoders_load_from_the_checkpoint_folder(tmp_path):
+    """``text_encoder/`` (CLIP) and ``text_encoder_2/`` (T5) with their tokenizers, as the published folders lay them out: the
+    prompt becomes T5 token features (projected to the model width) and CLIP's pooled vector, and conditions the prediction."""
+    tf = pytest.importorskip("transformers")
+    from tokenizers import Tokenizer, models, pre_tokenizers, processors
+    cfg = tiny(text_dim=48, pooled_dim=24)
+    root = tmp_path / "FLUX.1-schnell"
+    write_folder(root, tiny(guidance_embeds=False, dynamic_shift=False))
+    vocab = {w: i for i, w in enumerate(["<pad>", "</s>", "<unk>", "a", "red", "fox", "blue", "whale", "on", "the", "hill"])}
+    for sub, max_len in (("tokenizer", 12), ("tokenizer_2", 256)):
+        t = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+        t.pre_tokenizer = pre_tokenizers.Whitespace()
+        t.post_processor = processors.TemplateProcessing(single="$A </s>", special_tokens=[("</s>", 1)])      # CLIP pools at the end token
+        (root / sub).mkdir()
+        t.save(str(root / sub / "tokenizer.json"))
+        (root / sub / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "PreTrainedTokenizerFast", "model_max_length": max_len,
+                                                                      "pad_token": "<pad>", "eos_token": "</s>", "unk_token": "<unk>"}))
+    torch.manual_seed(0)
+    tf.CLIPTextModel(tf.CLIPTextConfig(vocab_size=len(vocab), hidden_size=24, intermediate_size=32, num_hidden_layers=1, num_attention_heads=2,
+                                       max_position_embeddings=12, eos_token_id=1, pad_token_id=0, bos_token_id=2)).save_pretrained(root / "text_encoder")
+    tf.T5EncoderModel(tf.T5Config(vocab_size=len(vocab), d_model=48, d_kv=8, d_ff=64, num_layers=1, num_heads=2, pad_token_id=0,
+                                  eos_token_id=1, decoder_start_token_id=0)).save_pretrained(root / "text_encoder_2")
+    m = FluxModel.from_folder(root, device="cpu", dtype=torch.float32)
+    assert m.text is not None and m.cfg.text_len == 256 and not m.cfg.guidance_embeds
+    txt, pooled = m.encode_text("a red fox on the hill")
+    assert txt.shape == (256, m.cfg.hidden) and pooled.shape == (24,)
+    txt2, pooled2 = m.encode_text("a blue whale")
+    assert not torch.allclose(txt[:3], txt2[:3]) and not torch.allclose(pooled, pooled2)
+    lat = torch.randn(16, 8, 12)
+    v1, v2 = m.velocity(lat, 0.5, txt, pooled), m.velocity(lat, 0.5, txt2, pooled2)
+    assert v1.shape == lat.shape and not torch.allclose(v1, v2)
+    img = list(DiffusionRunner(m).generate("a red fox", 32, 48, 2, 3))[-1][1]
+    assert img.shape == (32, 48, 3)
