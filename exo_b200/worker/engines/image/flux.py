@@ -335,8 +335,8 @@ class FluxModel:
         enc = None
         if text and (root / "text_encoder").exists() and (root / "text_encoder_2").exists():
             from transformers import AutoTokenizer, CLIPTextModel, T5EncoderModel
-            enc = (AutoTokenizer.from_pretrained(root / "tokenizer"), CLIPTextModel.from_pretrained(root / "text_encoder", torch_dtype=dtype).to(device).eval(),
-                   AutoTokenizer.from_pretrained(root / "tokenizer_2"), T5EncoderModel.from_pretrained(root / "text_encoder_2", torch_dtype=dtype).to(device).eval())
+            enc = (AutoTokenizer.from_pretrained(root / "tokenizer"), CLIPTextModel.from_pretrained(root / "text_encoder", dtype=dtype).to(device).eval(),
+                   AutoTokenizer.from_pretrained(root / "tokenizer_2"), T5EncoderModel.from_pretrained(root / "text_encoder_2", dtype=dtype).to(device).eval())
         return cls(cfg, w, vae, blocks=blocks, device=device, dtype=dtype, text_encoders=enc)
 
     # ---- small helpers ----
