@@ -136,7 +136,8 @@ class SafetensorsSource(TensorSource):
 
     * FP8 block-scaled (DeepSeek-V3 style): ``X.weight`` in e4m3 with ``X.weight_scale_inv`` fp32 ``[N/128, K/128]``;
     * FP8 per-tensor / per-channel (compressed-tensors style): ``X.weight`` in e4m3 with ``X.weight_scale``;
-    * MLX affine groups (the mlx-community ``*-4bit`` / ``*-8bit`` repositories the reference loads with
+    * MLX affine groups of 2 to 6 and 8 bits, and MLX's microscaling modes (``mxfp4``, ``mxfp8``, ``nvfp4``: codes with one scale
+      per group and no bias) (the mlx-community ``*-4bit`` / ``*-8bit`` repositories the reference loads with
       ``mlx_lm.utils.load_model``, ``src/exo/worker/engines/mlx/utils_mlx.py:163-286``): ``X.weight`` packed in uint32,
       ``X.scales`` / ``X.biases`` per group of ``group_size`` input features, ``bits`` and ``group_size`` from the
       ``quantization`` entry of ``config.json`` (with per-module overrides).
@@ -189,6 +190,11 @@ class SafetensorsSource(TensorSource):
         group = int((over or q).get("group_size", 64))
         return bits, group
 
+    def _mlx_mode(self, module: str) -> str:
+        q = self.quant
+        over = q.get(module) if isinstance(q.get(module), dict) else None
+        return (over or q).get("mode", "affine")
+
     def stored_format(self, name: str) -> str:
         """How ``name`` is stored: ``plain``, ``fp8_block``, ``fp8_scale`` or ``mlx_affine``."""
         if name.endswith(".weight"):
@@ -220,19 +226,55 @@ class SafetensorsSource(TensorSource):
                 t = t.float() * (sc.reshape(-1, 1) if sc.numel() > 1 else sc.reshape(1, 1))
             else:
                 bits, group = self._mlx_params(stem)
-                if 32 % bits:
-                    raise ValueError(f"{name}: {bits}-bit MLX packing is not supported (4- and 8-bit repositories are)")
-                per = 32 // bits
-                packed = t.to(torch.int64) & 0xFFFFFFFF                               # uint32 words
-                shifts = torch.arange(per, dtype=torch.int64) * bits
-                q = ((packed.unsqueeze(-1) >> shifts) & ((1 << bits) - 1)).reshape(*t.shape[:-1], t.shape[-1] * per)
-                scales, biases = self._raw(stem + ".scales").float(), self._raw(stem + ".biases").float()
-                t = q.float() * scales.repeat_interleave(group, -1) + biases.repeat_interleave(group, -1)
+                if bits not in (2, 3, 4, 5, 6, 8):
+                    raise ValueError(f"{name}: {bits}-bit MLX packing is not supported (2- to 6- and 8-bit repositories are)")
+                q = _mlx_unpack(t, bits)
+                scales = self._raw(stem + ".scales")
+                mode = str(self._mlx_mode(stem))
+                if stem + ".biases" in self.index:                                    # affine groups: q * scale + bias
+                    t = q.float() * scales.float().repeat_interleave(group, -1) + self._raw(stem + ".biases").float().repeat_interleave(group, -1)
+                else:
+                    # microscaling formats: 4-bit e2m1 or 8-bit e4m3 codes with one power-of-two (e8m0) scale per group of 32,
+                    # or e2m1 codes with an e4m3 scale per group of 16 (nvfp4)
+                    if bits == 4:
+                        vals = _FP4_E2M1.to(q.device)[q]
+                    elif bits == 8:
+                        vals = q.to(torch.uint8).view(torch.float8_e4m3fn).float()
+                    else:
+                        raise ValueError(f"{name}: {bits}-bit codes without biases are not a known MLX format")
+                    raw = scales.view(torch.uint8) if scales.dtype != torch.uint8 else scales
+                    sc = raw.view(torch.float8_e4m3fn).float() if mode == "nvfp4" else torch.exp2(raw.float() - 127.0)
+                    group = vals.shape[-1] // sc.shape[-1]
+                    t = vals * sc.repeat_interleave(group, -1)
         if shape is not None and tuple(shape) != tuple(t.shape):
             raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} != expected {shape}")
         if t.is_floating_point():
             t = t.to(self.dtype)
         return t.to(self.device)
+
+
+_FP4_E2M1 = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0])
+
+
+def _mlx_unpack(t: torch.Tensor, bits: int) -> torch.Tensor:
+    """Codes of an MLX-packed weight ``[..., words]`` (uint32): ``bits``-wide fields, lowest bits first.  Widths that divide 32
+    sit whole inside a word; 3-, 5- and 6-bit fields run on across byte boundaries (8 values in 3 or 5 bytes, 4 values in 3
+    bytes), so the words are read as a little-endian byte stream and regrouped."""
+    mask = (1 << bits) - 1
+    if 32 % bits == 0:
+        per = 32 // bits
+        packed = t.to(torch.int64) & 0xFFFFFFFF
+        shifts = torch.arange(per, dtype=torch.int64) * bits
+        return ((packed.unsqueeze(-1) >> shifts) & mask).reshape(*t.shape[:-1], t.shape[-1] * per)
+    import math
+    g_bytes = math.lcm(bits, 8) // 8
+    g_vals = g_bytes * 8 // bits
+    by = t.contiguous().view(torch.uint8).reshape(*t.shape[:-1], -1, g_bytes).to(torch.int64)
+    word = torch.zeros(by.shape[:-1], dtype=torch.int64)
+    for j in range(g_bytes):
+        word |= by[..., j] << (8 * j)
+    shifts = torch.arange(g_vals, dtype=torch.int64) * bits
+    return ((word.unsqueeze(-1) >> shifts) & mask).reshape(*t.shape[:-1], -1)
 
 
 def write_safetensors(path: str | Path, tensors: dict[str, torch.Tensor]) -> None:

@@ -49,9 +49,75 @@ def test_per_module_mlx_override_and_unsupported_width(tmp_path):
     write_safetensors(tmp_path / "model.safetensors", {"m.weight": packed8, "m.scales": s8, "m.biases": b8})
     got = SafetensorsSource(tmp_path, dtype=torch.float32).get("m.weight")
     assert got.shape == (8, 64) and (got - w).abs().max() < 0.004
-    (tmp_path / "config.json").write_text(json.dumps({"quantization": {"group_size": 64, "bits": 5}}))
-    with pytest.raises(ValueError, match="5-bit"):
+    (tmp_path / "config.json").write_text(json.dumps({"quantization": {"group_size": 64, "bits": 7}}))
+    with pytest.raises(ValueError, match="7-bit"):
         SafetensorsSource(tmp_path, dtype=torch.float32).get("m.weight")
+
+
+def _bitstream_pack(q: torch.Tensor, bits: int) -> torch.Tensor:
+    """Codes ``[n, k]`` as a little-endian bit stream per row (lowest bits first), returned as uint32 words."""
+    n, k = q.shape
+    b = ((q.to(torch.int64).unsqueeze(-1) >> torch.arange(bits)) & 1).reshape(n, k * bits)           # the bits in stream order
+    by = (b.reshape(n, -1, 8) << torch.arange(8)).sum(-1).to(torch.uint8)
+    return by.contiguous().view(torch.int32).view(torch.uint32)
+
+
+@pytest.mark.parametrize("bits", [3, 5, 6])
+def test_mlx_odd_bit_widths_run_across_byte_boundaries(tmp_path, bits):
+    """3-, 5- and 6-bit repositories: fields run on across bytes (8 values in 3 or 5 bytes, 4 values in 3 bytes); a stacked
+    expert tensor (three axes) unpacks along its last axis."""
+    g = torch.Generator().manual_seed(bits)
+    group, n, k = 64, 12, 128
+    q = torch.randint(0, 1 << bits, (n, k), generator=g)
+    scales, biases = (torch.rand(n, k // group, generator=g) * 0.01 + 0.001).half(), (torch.randn(n, k // group, generator=g) * 0.05).half()
+    want = q.float() * scales.float().repeat_interleave(group, -1) + biases.float().repeat_interleave(group, -1)
+    packed = _bitstream_pack(q, bits)
+    assert packed.shape == (n, k * bits // 32)
+    # spot-check the layout against the byte arithmetic of the format: the third 3-bit value straddles bytes 0 and 1, the second
+    # 6-bit value bytes 0 and 1, the second 5-bit value bytes 0 and 1
+    by = packed.view(torch.uint8)[0].to(torch.int64)
+    if bits == 3:
+        assert int(q[0, 2]) == int(((by[0] & 0xC0) >> 6) + ((by[1] & 0x1) << 2))
+    if bits == 6:
+        assert int(q[0, 1]) == int(((by[0] >> 6) & 0x03) + ((by[1] & 0x0F) << 2))
+    if bits == 5:
+        assert int(q[0, 1]) == int(((by[0] >> 5) & 0x07) + ((by[1] & 0x03) << 3))
+    (tmp_path / "config.json").write_text(json.dumps({"quantization": {"group_size": group, "bits": bits}}))
+    write_safetensors(tmp_path / "model.safetensors", {
+        "m.weight": packed, "m.scales": scales, "m.biases": biases,
+        "e.weight": packed.view(3, 4, -1).contiguous(), "e.scales": scales.view(3, 4, -1).contiguous(), "e.biases": biases.view(3, 4, -1).contiguous()})
+    src = SafetensorsSource(tmp_path, dtype=torch.float32)
+    assert torch.equal(src.get("m.weight", (n, k)), want)
+    assert torch.equal(src.get("e.weight", (3, 4, k)), want.view(3, 4, k))
+
+
+@pytest.mark.parametrize("mode", ["mxfp4", "nvfp4", "mxfp8"])
+def test_mlx_microscaling_modes(tmp_path, mode):
+    """Codes without biases: e2m1 (or e4m3) values times one scale per group — a power of two per 32 values, or an e4m3 number per
+    16 values."""
+    g = torch.Generator().manual_seed(1)
+    n, k = 6, 64
+    bits, group = (8, 32) if mode == "mxfp8" else (4, 16 if mode == "nvfp4" else 32)
+    q = torch.randint(0, 1 << bits, (n, k), generator=g)
+    if bits == 8:
+        q = q.clamp(max=0x7E)                                   # keep away from the NaN code
+        vals = q.to(torch.uint8).view(torch.float8_e4m3fn).float()
+    else:
+        vals = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0])[q]
+    if mode == "nvfp4":
+        sc8 = torch.randint(0x20, 0x50, (n, k // group), generator=g).to(torch.uint8)
+        sc = sc8.view(torch.float8_e4m3fn).float()
+    else:
+        sc8 = torch.randint(120, 132, (n, k // group), generator=g).to(torch.uint8)
+        sc = torch.exp2(sc8.float() - 127)
+    want = vals * sc.repeat_interleave(group, -1)
+    per = 32 // bits
+    words = (q.reshape(n, k // per, per).to(torch.int64) << (torch.arange(per) * bits)).sum(-1)
+    packed = torch.where(words >= (1 << 31), words - (1 << 32), words).to(torch.int32).view(torch.uint32)
+    (tmp_path / "config.json").write_text(json.dumps({"quantization": {"group_size": group, "bits": bits, "mode": mode}}))
+    write_safetensors(tmp_path / "model.safetensors", {"m.weight": packed, "m.scales": sc8})
+    got = SafetensorsSource(tmp_path, dtype=torch.float32).get("m.weight", (n, k))
+    assert torch.equal(got, want)
 
 
 def test_fp8_block_scaled_and_scaled_weights(tmp_path):
