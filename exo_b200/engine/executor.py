@@ -54,7 +54,8 @@ class Executor:
         # ops with host reads of the sequence lengths: such a step cannot be captured
         mla_ok = not cfg.mla or (cfg.kv_lora_rank == 512 and cfg.qk_rope_dim == 64 and cfg.qk_nope_dim == 128
                                  and cfg.v_head_dim == 128 and cfg.dtype == "bf16")
-        self.use_graphs = (self.cuda and mla_ok) if use_graphs is None else use_graphs
+        eager_experts = cfg.expert_bias and bool(cfg.n_experts)      # GPT-OSS experts run as PyTorch ops with host reads
+        self.use_graphs = (self.cuda and mla_ok and not eager_experts) if use_graphs is None else (use_graphs and not eager_experts)
         if self.cuda and os.environ.get("EXO_KERNEL_CHECKS") == "1":
             self.use_graphs = False       # the checking flavour synchronises after every op: nothing can be captured
         if self.pipe is not None:

@@ -28,6 +28,7 @@ class RopeConfig:
     beta_slow: float = 1.0
     mscale: float = 1.0
     mscale_all_dim: float = 0.0
+    truncate: bool = True       # YaRN: round the correction range to whole dimensions (GPT-OSS does not)
     partial_rotary_factor: float = 1.0
 
 
@@ -113,6 +114,11 @@ class ModelConfig:
     moe_latent: int = 0
     # Step-3.5: per-layer query-head counts, RoPE (base, rotary share, scaling only on some layer types), a sigmoid gate per
     # head on the attention output, SwiGLU outputs clamped on some layers (0 = not clamped)
+    # GPT-OSS experts: a bias on the router and on both expert projections, gate / up interleaved in the checkpoint,
+    # (up + 1) * gate * sigmoid(1.702 gate) with the gate capped and the up projection clamped at `oai_limit`
+    router_linear_bias: bool = False
+    expert_bias: bool = False
+    oai_limit: float = 7.0
     layer_n_heads: tuple[int, ...] = ()
     layer_rope: tuple[RopeConfig, ...] = ()
     head_gate: bool = False
@@ -150,7 +156,7 @@ class ModelConfig:
 
     def window_of(self, i: int) -> int:
         """Sliding window of layer ``i`` (0 = every earlier key): per layer type where the model names layer types."""
-        if self.family == "step3p5":
+        if self.family == "step3p5" or (self.family == "gpt_oss" and self.layer_types):
             return self.sliding_window if self.layer_is_sliding(i) else 0
         return self.sliding_window
 
@@ -267,6 +273,7 @@ class ModelConfig:
             beta_slow=float(rope_scaling.get("beta_slow", 1.0)),
             mscale=float(rope_scaling.get("mscale", 1.0)),
             mscale_all_dim=float(rope_scaling.get("mscale_all_dim", 0.0)),
+            truncate=bool(rope_scaling.get("truncate", True)),
             partial_rotary_factor=float(g("partial_rotary_factor", default=1.0)),
         )
         eos = g("eos_token_id", default=())
@@ -475,6 +482,22 @@ class ModelConfig:
             mc.qk_norm_full = bool(g("use_qk_norm", default=True))
             if g("rotary_dim", default=None):
                 mc.rope.partial_rotary_factor = g("rotary_dim") / mc.head_dim
+        if mt == "gpt_oss":
+            # GPT-OSS: sliding and full attention alternate, sinks, biases everywhere, YaRN without rounding, top-k then
+            # softmax routing with a router bias, experts with biases and the capped (up + 1) * gate * sigmoid(1.702 gate)
+            n_l = mc.n_layers
+            types = list(g("layer_types", default=None) or ["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(n_l)])
+            mc.layer_types = tuple("sliding" if t == "sliding_attention" else "full" for t in types)
+            mc.sliding_window = int(g("sliding_window", default=128) or 0)
+            mc.attn_bias = bool(g("attention_bias", default=True))
+            mc.n_experts = g("num_local_experts", default=0) or 0
+            if mc.n_experts:
+                mc.n_experts_per_tok = g("num_experts_per_tok", "experts_per_token", default=4)
+                mc.moe_ffn = g("intermediate_size")
+                mc.router, mc.norm_topk_prob = "softmax", True
+                mc.router_linear_bias = mc.expert_bias = True
+                mc.act = "swiglu_oai"
+                mc.oai_limit = float(g("swiglu_limit", default=7.0))
         if family == "mixtral":
             # every layer is a sparse block: softmax over the top-k router logits (= softmax then renormalise)
             mc.n_experts = g("num_local_experts", default=8)

@@ -174,7 +174,10 @@ class OracleModel:
         if c.head_gate:          # one sigmoid gate per head, projected from the layer's (normed) input
             hg = torch.sigmoid(x @ self.W(p + "g_proj.weight", (n_heads, H)).t())
             o = (o.view(T, n_heads, dv) * hg[..., None]).reshape(T, n_heads * dv)
-        return o @ self.W(p + "o_proj.weight", (H, n_heads * dv)).t()
+        out = o @ self.W(p + "o_proj.weight", (H, n_heads * dv)).t()
+        if c.attn_bias and c.family == "gpt_oss":          # GPT-OSS has a bias on the output projection too
+            out = out + self.W(p + "o_proj.bias", (H,))
+        return out
 
     def _ffn(self, i: int, x: torch.Tensor) -> torch.Tensor:
         from .weights import moe_names

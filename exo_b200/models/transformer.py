@@ -230,6 +230,8 @@ class Decoder:
         o = o.reshape(o.shape[0], -1)
         if cfg.attn_gate:        # the projection's last n_q*D columns gate the attention output per element
             o = ops.sigmoid_gate(o, qkv[:, (n_q + 2 * self.n_kv) * cfg.head_dim:])
+        if lw.bo is not None:    # the output projection's bias joins the residual: it is added once, not once per rank
+            h = resolve(h) + lw.bo
         return self.comm.row_linear(o, lw.wo, h)
 
     def _attn_linear(self, lw, h, inp: StepInputs, state) -> torch.Tensor:
@@ -302,6 +304,12 @@ class Decoder:
         """
         cfg = self.cfg
         h, x = reduced_and_normed(h, lw.ffn_norm, cfg.rms_eps)
+        if lw.e_gate_up_b is not None:       # GPT-OSS: biased router and experts, its own activation
+            logits = ops.linear(x, lw.router).float() + lw.router_b
+            wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, "softmax", True, None, 1, 1, 1.0)
+            elo, _ = expert_range(cfg, self.spec)
+            y = ops.moe_experts_oai(x, lw.e_gate_up, lw.e_gate_up_b, lw.e_down, lw.e_down_b, wts, ids, elo, cfg.oai_limit)
+            return self.comm.row_sum(y, h)
         logits = ops.linear(x, lw.router)
         wts, ids = ops.moe_route(logits, cfg.n_experts_per_tok, cfg.router, cfg.norm_topk_prob, lw.router_bias,
                                  cfg.n_group, cfg.topk_group, cfg.routed_scaling)

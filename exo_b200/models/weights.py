@@ -306,6 +306,7 @@ class LayerWeights:
     wqkv: torch.Tensor | None = None   # [(hq + 2 hkv) * D, H] local
     bqkv: torch.Tensor | None = None
     wo: torch.Tensor | None = None     # [H, hq * Dv] local
+    bo: torch.Tensor | None = None     # [H]: bias of the output projection (GPT-OSS), added once after the ranks' sum
     q_norm: torch.Tensor | None = None
     k_norm: torch.Tensor | None = None
     sinks: torch.Tensor | None = None
@@ -329,6 +330,9 @@ class LayerWeights:
     s_gate_up: torch.Tensor | None = None    # shared experts, TP-sliced
     s_down: torch.Tensor | None = None
     s_gate: torch.Tensor | None = None       # [1, H]: sigmoid gate on the shared expert's output (Qwen3-Next)
+    router_b: torch.Tensor | None = None     # [E]: bias of the router's linear layer (GPT-OSS)
+    e_gate_up_b: torch.Tensor | None = None  # [E_local, 2F]: expert biases (GPT-OSS)
+    e_down_b: torch.Tensor | None = None     # [E_local, H]
     # gated-delta-rule layer (rows of lin_in: q | k | v | z | b | a of this rank's heads)
     lin_in: torch.Tensor | None = None       # [2*hk*dk + 2*hv*dv + 2*hv, H] local
     lin_conv_w: torch.Tensor | None = None   # [2*hk*dk + hv*dv, taps] fp32
@@ -453,6 +457,37 @@ def _expert_tensor(src: "TensorSource", m: str, e: int, part: str, shape: tuple[
 
 
 
+def _mxfp4_blocks(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """``blocks [..., K/32, 16]`` bytes of two e2m1 codes each (low nibble first) and ``scales [..., K/32]`` (e8m0) → ``[..., K]``."""
+    b = blocks.to(torch.int64)
+    codes = torch.stack((b & 0xF, b >> 4), -1).reshape(*blocks.shape[:-1], 32)
+    vals = _FP4_E2M1[codes] * torch.exp2(scales.float() - 127.0)[..., None]
+    return vals.reshape(*blocks.shape[:-2], -1)
+
+
+def _gpt_oss_experts(cfg: ModelConfig, spec: ShardSpec, src: "TensorSource", m: str, lw: "LayerWeights", fin) -> None:
+    """GPT-OSS sparse block: ``router.{weight,bias}``; ``experts.gate_up_proj [E, H, 2F]`` with gate and up columns interleaved
+    (or ``gate_up_proj_blocks`` / ``_scales``: 4-bit e2m1 codes in 32-value blocks with a power-of-two scale, rows first), its
+    bias ``[E, 2F]``; ``experts.down_proj [E, F, H]`` (or blocks ``[E, H, F/32, 16]``) and its bias.  Stored here as gate rows then
+    up rows ``[E_local, 2F, H]`` and ``[E_local, H, F]``; experts are split over the ranks."""
+    E, F, H = cfg.n_experts, cfg.moe_ffn, cfg.hidden
+    elo, ehi = expert_range(cfg, spec)
+    lw.router = fin(src.get(m + "router.weight", (E, H)))
+    lw.router_b = fin(src.get(m + "router.bias", (E,)), torch.float32)
+    x = m + "experts."
+    if src.has(x + "gate_up_proj_blocks") and not src.has(x + "gate_up_proj"):
+        gu = _mxfp4_blocks(src.get(x + "gate_up_proj_blocks", None)[elo:ehi], src.get(x + "gate_up_proj_scales", None)[elo:ehi])      # [e, 2F, H]
+        dn = _mxfp4_blocks(src.get(x + "down_proj_blocks", None)[elo:ehi], src.get(x + "down_proj_scales", None)[elo:ehi])            # [e, H, F]
+    else:
+        gu = src.get(x + "gate_up_proj", (E, H, 2 * F))[elo:ehi].transpose(1, 2)
+        dn = src.get(x + "down_proj", (E, F, H))[elo:ehi].transpose(1, 2)
+    gb = src.get(x + "gate_up_proj_bias", (E, 2 * F))[elo:ehi]
+    lw.e_gate_up = fin(torch.cat((gu[:, 0::2], gu[:, 1::2]), 1))           # de-interleave: gate rows, then up rows
+    lw.e_gate_up_b = fin(torch.cat((gb[:, 0::2], gb[:, 1::2]), 1), torch.float32)
+    lw.e_down = fin(dn)
+    lw.e_down_b = fin(src.get(x + "down_proj_bias", (E, H))[elo:ehi], torch.float32)
+
+
 def quantize_layer(cfg: ModelConfig, lw: "LayerWeights") -> "LayerWeights":
     """Pack this layer's projection matrices as block-scaled fp8 when the model card is served
     quantised (``cfg.quant``); norms, router, and the absorbed MLA factors stay bf16.  Runs on the
@@ -507,6 +542,7 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
         lw = LayerWeights(attn_norm=norm(p + "input_layernorm.weight", (H,)),
                           ffn_norm=norm(p + "post_attention_layernorm.weight", (H,)))
         a = p + "self_attn."
+        lw.window = cfg.window_of(i)
         if cfg.layer_is_linear(i):
             _linear_attention_weights(cfg, spec, src, p, lw, fin, hf_form)
         elif cfg.mla:
@@ -544,6 +580,8 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
                 bv = src.get(a + "v_proj.bias", (cfg.n_kv_heads * D,))[klo * D:khi * D]
                 lw.bqkv = fin(torch.cat((bq, bk, bv), 0))
             lw.wo = fin(_cols(src.get(a + "o_proj.weight", (H, cfg.n_heads * D)), r, n))
+            if cfg.attn_bias and cfg.family == "gpt_oss" and src.has(a + "o_proj.bias"):
+                lw.bo = fin(src.get(a + "o_proj.bias", (H,)))
             if cfg.qk_norm:
                 lw.q_norm = norm(a + "q_norm.weight", (D,))
                 lw.k_norm = norm(a + "k_norm.weight", (D,))
@@ -553,7 +591,9 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             if cfg.attn_sinks:
                 lw.sinks = fin(_rows(src.get(a + "sinks", (cfg.n_heads,)), r, n), torch.float32)
         m = p + moe_names(cfg)["prefix"]
-        if cfg.layer_is_moe(i):
+        if cfg.layer_is_moe(i) and cfg.expert_bias:
+            _gpt_oss_experts(cfg, spec, src, m, lw, fin)
+        elif cfg.layer_is_moe(i):
             E, F = cfg.n_experts, cfg.moe_ffn
             nm = moe_names(cfg)
             lw.router = fin(src.get(m + "gate.weight", (E, H)))

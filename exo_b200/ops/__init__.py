@@ -133,6 +133,12 @@ def moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset=0, n_experts_t
     return ref.moe_experts(x, w_gate_up, w_down, weights, ids, expert_offset, act, limit)
 
 
+def moe_experts_oai(x, w_gate_up, b_gate_up, w_down, b_down, weights, ids, expert_offset=0, limit=7.0):
+    """GPT-OSS experts (biases, capped ``(up + 1) * gate * sigmoid(1.702 gate)``): PyTorch ops on either device (the host reads
+    which experts are hit, so a step that runs them cannot be captured in a CUDA graph)."""
+    return ref.moe_experts_oai(x, w_gate_up, b_gate_up, w_down, b_down, weights, ids, expert_offset, limit)
+
+
 def embedding(table, ids):
     if table.is_cuda:
         return cuda_ops().embedding(table, ids)

@@ -85,8 +85,11 @@ def rope_inv_freq(head_dim: int, rope) -> tuple[torch.Tensor, float]:
     elif rope.kind == "yarn":
         def corr_dim(n_rot: float) -> float:
             return rot * math.log(rope.original_max_position / (n_rot * 2 * math.pi)) / (2 * math.log(rope.theta))
-        low = max(math.floor(corr_dim(rope.beta_fast)), 0)
-        high = min(math.ceil(corr_dim(rope.beta_slow)), rot // 2 - 1)
+        lo_f, hi_f = corr_dim(rope.beta_fast), corr_dim(rope.beta_slow)
+        if getattr(rope, "truncate", True):
+            lo_f, hi_f = math.floor(lo_f), math.ceil(hi_f)
+        low = max(lo_f, 0)
+        high = min(hi_f, rot // 2 - 1)
         if low == high:
             high += 0.001
         ramp = ((torch.arange(rot // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
@@ -279,6 +282,26 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         pre = linear(x[tok], w_gate_up[e])
         h = swiglu(pre, limit) if act == "silu" else geglu(pre) if act == "gelu_tanh" else torch.relu(pre.float()).pow(2).to(pre.dtype)
         y = linear(h, w_down[e]).float()
+        out.index_add_(0, tok, y * weights[tok, slot][:, None])
+    return out.to(x.dtype)
+
+
+def moe_experts_oai(x: torch.Tensor, w_gate_up: torch.Tensor, b_gate_up: torch.Tensor, w_down: torch.Tensor, b_down: torch.Tensor,
+                    weights: torch.Tensor, ids: torch.Tensor, expert_offset: int = 0, limit: float = 7.0, alpha: float = 1.702) -> torch.Tensor:
+    """GPT-OSS experts: ``w_gate_up [E, 2F, H]`` (gate rows, then up rows) and ``w_down [E, H, F]`` with biases ``[E, 2F]`` /
+    ``[E, H]``; ``(up + 1) * gate * sigmoid(alpha * gate)`` with the gate capped at ``limit`` and the up projection clamped to
+    ``+-limit``.  Experts outside ``[expert_offset, expert_offset + E)`` contribute zero."""
+    T, H = x.shape
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for e in range(w_gate_up.shape[0]):
+        tok, slot = torch.where(ids == e + expert_offset)
+        if tok.numel() == 0:
+            continue
+        pre = linear(x[tok], w_gate_up[e]).float() + b_gate_up[e].float()
+        g, u = pre.chunk(2, dim=-1)
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+        h = ((u + 1.0) * g * torch.sigmoid(alpha * g)).to(x.dtype)
+        y = linear(h, w_down[e]).float() + b_down[e].float()
         out.index_add_(0, tok, y * weights[tok, slot][:, None])
     return out.to(x.dtype)
 
