@@ -318,7 +318,7 @@ class ModelConfig:
             attn_sinks=mt == "gpt_oss",
         )
         if family == "qwen3_moe":
-            mc.n_experts = g("num_experts")
+            mc.n_experts = g("num_experts", "num_local_experts")
             mc.n_experts_per_tok = g("num_experts_per_tok")
             mc.moe_ffn = g("moe_intermediate_size")
             mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
@@ -340,7 +340,7 @@ class ModelConfig:
             mc.norm_one_plus = True
             if "partial_rotary_factor" not in cfg:
                 mc.rope.partial_rotary_factor = 0.25
-            mc.n_experts = g("num_experts", default=0) or 0
+            mc.n_experts = g("num_experts", "num_local_experts", default=0) or 0
             if mc.n_experts:
                 mc.n_experts_per_tok = g("num_experts_per_tok")
                 mc.moe_ffn = g("moe_intermediate_size")
@@ -403,7 +403,7 @@ class ModelConfig:
                                         kind="proportional" if glo.get("rope_type") == "proportional" else "default",
                                         partial_rotary_factor=float(glo.get("partial_rotary_factor", 1.0)))
             if mc.moe_beside_mlp:
-                mc.n_experts = g("num_experts")
+                mc.n_experts = g("num_experts", "num_local_experts")
                 mc.n_experts_per_tok = g("top_k_experts")
                 mc.moe_ffn = g("moe_intermediate_size")
                 mc.router = "softmax"

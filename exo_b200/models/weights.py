@@ -445,6 +445,18 @@ def _expert_tensor(src: "TensorSource", m: str, e: int, part: str, shape: tuple[
     """Weight ``part`` (``gate_proj.weight`` ...) of routed expert ``e``: one tensor per expert (hub layout), or a slice of
     the stacked ``switch_mlp.<part>`` tensor that MLX conversions write."""
     name = f"{m}experts.{e}.{part}"
+    if not src.has(name) and src.has(f"{m}experts.gate_up_proj"):
+        # checkpoints saved by recent `transformers`: all experts in `experts.gate_up_proj [E, 2F, H]` (gate rows, then up rows)
+        # and `experts.down_proj [E, H, F]`
+        cache = getattr(src, "_fused", None)
+        if cache is None or cache[0] != m:
+            cache = (m, src.get(f"{m}experts.gate_up_proj", None), src.get(f"{m}experts.down_proj", None))
+            src._fused = cache
+        kind = {"gate_proj.weight": 0, "w1.weight": 0, "up_proj.weight": 1, "w3.weight": 1}.get(part, 2)
+        if kind == 2:
+            return cache[2][e]
+        F_ = cache[1].shape[1] // 2
+        return cache[1][e, kind * F_:(kind + 1) * F_]
     if src.has(name) or not src.has(f"{m}switch_mlp.{part}"):
         return src.get(name, shape)
     cache = getattr(src, "_stacked", None)
@@ -591,6 +603,8 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             if cfg.attn_sinks:
                 lw.sinks = fin(_rows(src.get(a + "sinks", (cfg.n_heads,)), r, n), torch.float32)
         m = p + moe_names(cfg)["prefix"]
+        if cfg.layer_is_moe(i) and not src.has(m + "gate.weight") and src.has(p + "mlp.gate.weight"):
+            m = p + "mlp."               # (recent `transformers` saves Mixtral-style blocks under `mlp.` as well)
         if cfg.layer_is_moe(i) and cfg.expert_bias:
             _gpt_oss_experts(cfg, spec, src, m, lw, fin)
         elif cfg.layer_is_moe(i):
