@@ -285,7 +285,7 @@ def test_exo_bench_streaming_metrics_sampler_pairs_and_dry_run(capsys):
         def nvmlDeviceGetPowerUsage(self, h): return 700_000
         def nvmlDeviceGetClockInfo(self, h, kind): return 1900
     with eb.SystemMetricsSampler(0.01, nvml=Nvml()) as sm:
-        time.sleep(0.08)
+        time.sleep(0.4)
     s = sm.summary()
     assert s["samples"] >= 3 and s["gpus"][1]["util"] == {"mean": 60.0, "max": 60.0} and s["gpus"][0]["power_w"]["max"] == 700.0
     assert eb.SystemMetricsSampler(nvml=eb._NoNvml()).summary() is None

@@ -251,7 +251,7 @@ def test_coordinator_start_complete_delete_and_read_only(env, monkeypatch):
             assert hub.calls["get"] == gets
             # delete resets to pending and removes the files
             await cmd_s.send(ForwarderDownloadCommand(origin="x", command=DeleteDownload(target_node_id=node, model_id=ModelId(REPO))))
-            with anyio.fail_after(5):
+            with anyio.fail_after(30):
                 while ModelId(REPO) in dc.download_status:
                     await anyio.sleep(0.02)
             assert not (rw / "org--tiny").exists()
@@ -264,7 +264,7 @@ def test_coordinator_start_complete_delete_and_read_only(env, monkeypatch):
             ro_shard = full_shard(card("org/ro"))
             gets = hub.calls["get"]
             await cmd_s.send(ForwarderDownloadCommand(origin="x", command=StartDownload(target_node_id=node, shard_metadata=ro_shard)))
-            with anyio.fail_after(5):
+            with anyio.fail_after(30):
                 while not isinstance(dc.download_status.get(ModelId("org/ro")), DownloadCompleted):
                     await anyio.sleep(0.02)
             assert dc.download_status[ModelId("org/ro")].read_only and hub.calls["get"] == gets
@@ -282,7 +282,7 @@ def test_coordinator_offline_fails_and_hub_error_becomes_failed(env, monkeypatch
         async with anyio.create_task_group() as tg:
             tg.start_soon(dc.run)
             await cmd_s.send(ForwarderDownloadCommand(origin="x", command=StartDownload(target_node_id=node, shard_metadata=shard)))
-            with anyio.fail_after(5):
+            with anyio.fail_after(30):
                 while not isinstance(dc.download_status.get(ModelId(REPO)), DownloadFailed):
                     await anyio.sleep(0.02)
             assert "offline mode" in dc.download_status[ModelId(REPO)].error_message and hub.calls["tree"] == 0
@@ -292,7 +292,7 @@ def test_coordinator_offline_fails_and_hub_error_becomes_failed(env, monkeypatch
         async with anyio.create_task_group() as tg:
             tg.start_soon(dc.run)
             await cmd_s.send(ForwarderDownloadCommand(origin="x", command=StartDownload(target_node_id=node, shard_metadata=shard)))
-            with anyio.fail_after(10):
+            with anyio.fail_after(30):
                 while not isinstance(dc.download_status.get(ModelId(REPO)), DownloadFailed):
                     await anyio.sleep(0.02)
             assert "Access denied" in dc.download_status[ModelId(REPO)].error_message
