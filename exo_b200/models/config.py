@@ -519,8 +519,9 @@ class ModelConfig:
             mc.n_shared_experts = g("n_shared_experts", default=0) or 0
             mc.first_dense_layers = g("first_k_dense_replace", default=0)
             kinds = g("mlp_layer_types", default=None)          # GLM-5 lists every layer's kind instead
-            if kinds and "first_k_dense_replace" not in cfg:
+            if kinds:                                            # the list wins where both are given, as in the library
                 mc.first_dense_layers = next((i for i, k in enumerate(kinds) if k != "dense"), len(kinds))
+                mc.mlp_only_layers = tuple(i for i, k in enumerate(kinds) if k == "dense" and i >= mc.first_dense_layers)
             mc.router = "sigmoid" if g("scoring_func", default="sigmoid") == "sigmoid" else "softmax"
             mc.norm_topk_prob = bool(g("norm_topk_prob", default=True))
             mc.routed_scaling = float(g("routed_scaling_factor", default=1.0))
