@@ -116,6 +116,7 @@ class ModelConfig:
     # head on the attention output, SwiGLU outputs clamped on some layers (0 = not clamped)
     # GPT-OSS experts: a bias on the router and on both expert projections, gate / up interleaved in the checkpoint,
     # (up + 1) * gate * sigmoid(1.702 gate) with the gate capped and the up projection clamped at `oai_limit`
+    mla_rope_neox: bool = False  # MLA rotary dims turn as (i, i + d/2) pairs (GLM-5) instead of adjacent pairs (DeepSeek)
     router_linear_bias: bool = False
     expert_bias: bool = False
     oai_limit: float = 7.0
@@ -508,6 +509,7 @@ class ModelConfig:
             mc.sliding_window = 0
         if family == "deepseek_v3":
             mc.mla = True
+            mc.mla_rope_neox = mt == "glm_moe_dsa"
             mc.q_lora_rank = g("q_lora_rank", default=0) or 0
             mc.kv_lora_rank = g("kv_lora_rank")
             mc.qk_nope_dim = g("qk_nope_head_dim")

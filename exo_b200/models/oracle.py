@@ -109,8 +109,8 @@ class OracleModel:
             q = q.view(T, c.n_heads, qk)
             kva = x @ self.W(p + "kv_a_proj_with_mqa.weight", (c.kv_lora_rank + c.qk_rope_dim, H)).t()
             ckv = self._norm(kva[:, :c.kv_lora_rank], self.W(p + "kv_a_layernorm.weight", (c.kv_lora_rank,)), c.rms_eps)
-            k_rope = ref.rope(kva[:, None, c.kv_lora_rank:], pos, self.inv_freq, self.mscale, True)
-            q_rope = ref.rope(q[..., c.qk_nope_dim:], pos, self.inv_freq, self.mscale, True)
+            k_rope = ref.rope(kva[:, None, c.kv_lora_rank:], pos, self.inv_freq, self.mscale, not c.mla_rope_neox)
+            q_rope = ref.rope(q[..., c.qk_nope_dim:], pos, self.inv_freq, self.mscale, not c.mla_rope_neox)
             kvb = ckv @ self.W(p + "kv_b_proj.weight", (c.n_heads * (c.qk_nope_dim + c.v_head_dim), c.kv_lora_rank)).t()
             kvb = kvb.view(T, c.n_heads, c.qk_nope_dim + c.v_head_dim)
             k = torch.cat((kvb[..., :c.qk_nope_dim], k_rope.expand(T, c.n_heads, c.qk_rope_dim)), -1)

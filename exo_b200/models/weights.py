@@ -566,8 +566,20 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
                 wq_b = src.get(a + "q_b_proj.weight", (cfg.n_heads * qk, cfg.q_lora_rank))
             else:
                 wq_b = src.get(a + "q_proj.weight", (cfg.n_heads * qk, H))
+            wkv_a = src.get(a + "kv_a_proj_with_mqa.weight", (cfg.kv_lora_rank + cfg.qk_rope_dim, H))
+            if cfg.mla_rope_neox:
+                # this model turns the rotary dims as (i, i + d/2) pairs; the kernels turn adjacent pairs.  Re-ordering the
+                # rotary rows of both projections (row 2i <- i, row 2i + 1 <- i + d/2) makes the two the same rotation, and
+                # q . k does not change when both sides are re-ordered alike
+                dr = cfg.qk_rope_dim
+                perm = torch.stack((torch.arange(dr // 2), torch.arange(dr // 2) + dr // 2), 1).reshape(-1)
+                wq_b = wq_b.view(cfg.n_heads, qk, -1).clone()
+                wq_b[:, cfg.qk_nope_dim:] = wq_b[:, cfg.qk_nope_dim:][:, perm]
+                wq_b = wq_b.view(cfg.n_heads * qk, -1)
+                wkv_a = wkv_a.clone()
+                wkv_a[cfg.kv_lora_rank:] = wkv_a[cfg.kv_lora_rank:][perm]
             lw.wq_b = fin(_rows(wq_b, r, n))
-            lw.wkv_a = fin(src.get(a + "kv_a_proj_with_mqa.weight", (cfg.kv_lora_rank + cfg.qk_rope_dim, H)))
+            lw.wkv_a = fin(wkv_a)
             lw.kv_a_norm = fin(src.get(a + "kv_a_layernorm.weight", (cfg.kv_lora_rank,)))
             wkv_b = src.get(a + "kv_b_proj.weight", (cfg.n_heads * (cfg.qk_nope_dim + cfg.v_head_dim), cfg.kv_lora_rank))
             wkv_b = wkv_b.view(cfg.n_heads, cfg.qk_nope_dim + cfg.v_head_dim, cfg.kv_lora_rank)[r * hl:(r + 1) * hl]

@@ -38,6 +38,9 @@ CASES = {
     "glm4-moe-lite": ("Glm4MoeLiteForCausalLM", "Glm4MoeLiteConfig", dict(q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8,
                                                                           v_head_dim=16, num_key_value_heads=4, **MOE)),
     "ministral3": ("Ministral3ForCausalLM", "Ministral3Config", dict(head_dim=16, sliding_window=None)),
+    "glm5": ("GlmMoeDsaForCausalLM", "GlmMoeDsaConfig", dict(q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                                                             num_key_value_heads=4, index_topk=2048, index_head_dim=16, index_n_heads=2,
+                                                             mlp_layer_types=["dense", "sparse", "sparse"], **MOE)),
     "minimax-m2": ("MiniMaxM2ForCausalLM", "MiniMaxM2Config", dict(head_dim=16, num_local_experts=4, num_experts_per_tok=2, use_qk_norm=True,
                                                                    rotary_dim=8, intermediate_size=32,
                                                                    rope_parameters={"rope_type": "default", "rope_theta": 5000000.0,
