@@ -623,7 +623,7 @@ def build_weights(cfg: ModelConfig, spec: ShardSpec, src: TensorSource, device: 
             E, F = cfg.n_experts, cfg.moe_ffn
             nm = moe_names(cfg)
             lw.router = fin(src.get(m + "gate.weight", (E, H)))
-            if cfg.router_bias:
+            if cfg.router_bias and src.has(m + nm["bias"]):      # (DeepSeek-V2 checkpoints have no selection bias)
                 lw.router_bias = fin(src.get(m + nm["bias"], (E,)), torch.float32)
             elo, ehi = expert_range(cfg, spec)
             gus, dns = [], []

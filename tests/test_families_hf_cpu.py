@@ -41,6 +41,11 @@ CASES = {
     "glm5": ("GlmMoeDsaForCausalLM", "GlmMoeDsaConfig", dict(q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
                                                              num_key_value_heads=4, index_topk=2048, index_head_dim=16, index_n_heads=2,
                                                              mlp_layer_types=["dense", "sparse", "sparse"], **MOE)),
+    "deepseek-v2-lite": ("DeepseekV2ForCausalLM", "DeepseekV2Config", dict(q_lora_rank=None, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                                                                           v_head_dim=16, num_key_value_heads=4, n_routed_experts=8, num_experts_per_tok=2,
+                                                                           moe_intermediate_size=32, n_shared_experts=1, first_k_dense_replace=1,
+                                                                           n_group=1, topk_group=1, norm_topk_prob=False, routed_scaling_factor=1.0,
+                                                                           topk_method="greedy", scoring_func="softmax")),
     "minimax-m2": ("MiniMaxM2ForCausalLM", "MiniMaxM2Config", dict(head_dim=16, num_local_experts=4, num_experts_per_tok=2, use_qk_norm=True,
                                                                    rotary_dim=8, intermediate_size=32,
                                                                    rope_parameters={"rope_type": "default", "rope_theta": 5000000.0,
